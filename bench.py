@@ -1,0 +1,247 @@
+#!/usr/bin/env python
+"""Headline benchmark: decode tokens/s of the 27B-class hybrid decoder with fp8 KV.
+
+    python bench.py --gpus N --steps K --warmup W
+
+Config (BASELINE.json, second and third entries): 64 layers in a 3 GDN : 1 gated-GQA
+pattern, hidden 5120, 24/4 heads of 256, GDN 16/48 heads of 128, FFN 17408, vocab 248320,
+random-init bf16 weights, fp8-E4M3 per-row KV cache, batch 32, 2048-token uniform-random
+prompts, greedy decode.  One "step" is one decode round of the whole batch.  N > 1 runs the
+same model tensor-parallel over N ranks (strong scaling: the batch does not grow).
+
+Timing: W untimed warm-up rounds, then exactly K rounds bracketed by barrier +
+synchronize, timed with CUDA events on the launching stream, max over ranks.  The weights
+(54 GB) are far larger than L2, so no explicit flush is needed between rounds.
+`value` is the device-timed graph loop (token ids and positions advance on the device);
+`e2e` runs the same K rounds through Generator.decode_step(): pinned-host descriptor -> one
+H2D copy -> graph -> D2H of the sampled ids, every round.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+BASELINE_DECODE_TOK_S = 86.4  # reference, Qwen3.6-27B nvfp4, 7,680-token prompt, one RTX 5090 (docs/performance.md:537)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                mx = float(r[2])
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def reference_arm(args) -> int:
+    # The reference is a CMake/C++ project without setup.py or pyproject.toml, so
+    # `pip install --target baseline/_ref /root/reference` fails ("not installable"); its CMake
+    # build needs FFmpeg and libcurl development packages and CUDA >= 13.1 for sm_100a, none
+    # of which exist offline here.
+    print(json.dumps({"impl": "reference",
+                      "unavailable": "reference is a CMake C++/CUDA project (no setup.py/pyproject: pip install "
+                                     "refused; needs FFmpeg+libcurl dev libs and CUDA>=13.1 for sm_100a)"}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--prompt-len", type=int, default=2048)
+    ap.add_argument("--kv-format", default="fp8")
+    ap.add_argument("--model", default="qwen3.6-27b")
+    ap.add_argument("--layers", type=int, default=0, help="debug only: shrink the layer count (result is marked invalid)")
+    ap.add_argument("--no-ttft", action="store_true")
+    ap.add_argument("--pdl", type=int, default=1)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import torch.distributed as dist
+
+    from ninfer_fusion_b200 import load_native
+    from ninfer_fusion_b200.models.config import get_config
+    from ninfer_fusion_b200.models.weights import random_weights
+    from ninfer_fusion_b200.runtime.generator import Generator
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            print("bench.py: launch with torch.distributed.run for --gpus > 1", file=sys.stderr)
+            return 2
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    load_native()
+    cfg = get_config(args.model)
+    if args.layers:
+        cfg = cfg.shrink(args.layers)
+    comm = shard = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+        from ninfer_fusion_b200.parallel.tp import TensorParallel
+
+        comm = TensorParallel(cfg, rank, world, device, max_tokens=max(args.batch, 2048))
+        shard = comm.geometry
+        weights = comm.random_shard_weights(seed=0)
+    else:
+        weights = random_weights(cfg, device, seed=0)
+
+    B, L, K, W = args.batch, args.prompt_len, args.steps, args.warmup
+    max_ctx = L + 2 * (K + W) + 64
+    gen = Generator(cfg, weights, device, max_batch=B, max_context=max_ctx, kv_format=args.kv_format, page_size=64,
+                    prefill_chunk=2048, use_graph=True, pdl=bool(args.pdl), shard=shard, comm=comm)
+    g = torch.Generator().manual_seed(1234)
+    prompts = [torch.randint(0, cfg.vocab, (L,), generator=g).tolist() for _ in range(B)]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    # ---- TTFT: one 2048-token prompt, prefill to first token, p50 of 5 ----
+    ttft_ms = None
+    if not args.no_ttft:
+        samples = []
+        for i in range(6):
+            barrier()
+            t0 = time.perf_counter()
+            gen.prefill(prompts[:1])
+            torch.cuda.synchronize(device)
+            samples.append((time.perf_counter() - t0) * 1e3)
+        ttft_ms = statistics.median(samples[1:])
+
+    # ---- batch prefill (untimed set-up of the decode state) ----
+    barrier()
+    t0 = time.perf_counter()
+    gen.prefill(prompts)
+    torch.cuda.synchronize(device)
+    prefill_s = time.perf_counter() - t0
+
+    # ---- device-timed decode: K graph replays, ids/positions advance on the device ----
+    graph, finish = gen.decode_device_loop(W + K)
+    for _ in range(W):
+        graph.replay()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        graph.replay()
+    e1.record()
+    barrier()
+    dev_ms = e0.elapsed_time(e1)
+    finish()
+    gen.model.status.check("after device-timed decode")
+
+    # ---- end to end through the public step API: H2D descriptors + graph + D2H ids per round ----
+    for _ in range(W):
+        gen.decode_step()
+    barrier()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    for _ in range(K):
+        gen.decode_step()
+    e3.record()
+    barrier()
+    e2e_ms = e2.elapsed_time(e3)
+    clocks = sampler.stop()
+    gen.model.status.check("after end-to-end decode")
+
+    t = torch.tensor([dev_ms, e2e_ms, ttft_ms or 0.0], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms, ttft_max = (float(v) for v in t.tolist())
+    if rank == 0:
+        value = B * K / (dev_ms / 1e3)
+        e2e_value = B * K / (e2e_ms / 1e3)
+        launches = gen.model.ops.launches_last_forward * K
+        out = {
+            "metric": "decode tokens/sec/box + p50 TTFT at 1/2/4/8 B200, 27B hybrid fp8-KV",
+            "value": round(value, 2), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": round(value / BASELINE_DECODE_TOK_S, 3), "dtype": "bf16",
+            "data": "synthetic uniform-random token prompts, random-init weights",
+            "config": {"model": cfg.name + ("" if not args.layers else " (SHRUNK: INVALID)"), "global_batch": B,
+                       "seq_len": L, "parallelism": f"tp{world}", "kv": args.kv_format + "-e4m3-row" if args.kv_format == "fp8" else args.kv_format,
+                       "weights": "bf16", "decode": "greedy, CUDA graph per round",
+                       "l2": "inputs larger than L2 (weights 54 GB streamed every round), no flush",
+                       "baseline_note": "vs_baseline divides by the reference's single-request decode tok/s (86.4, 27B nvfp4, RTX 5090)"},
+            "ttft_ms_p50": round(ttft_max, 2) if ttft_ms is not None else None,
+            "ttft_config": {"prompt_tokens": L, "batch": 1, "prefill_chunk": 2048},
+            "batch_prefill_s": round(prefill_s, 3),
+            "clocks": clocks,
+            "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s", "ms_per_step": round(e2e_ms / K, 4),
+                    "h2d_bytes_per_step": gen.bufs_decode.h2d_bytes(), "d2h_bytes_per_step": 4 * B},
+            "gpu_launches": launches,
+        }
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

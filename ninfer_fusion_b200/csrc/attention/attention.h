@@ -1,0 +1,60 @@
+// Host entry points of the attention family (plain C++ ABI).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../kv/kv_layout.h"
+
+namespace nfb {
+
+struct AttnPrepParams {
+  const __nv_bfloat16* proj;  // [T, ld_proj] fused projection output
+  long long ld_proj;
+  int q_off, k_off, v_off;    // column offsets of the Q / K / V blocks inside a row
+  int T, n_q_heads, n_kv_heads, head_dim;
+  const __nv_bfloat16* q_norm_w;  // [head_dim] or nullptr
+  const __nv_bfloat16* k_norm_w;
+  float eps;
+  int unit_offset;
+  int rot_dim;                // rotary dims (first rot_dim of each head), 0 = no RoPE
+  const float* inv_freq;      // [rot_dim / 2] device
+  float rope_attn_factor;     // YaRN attention factor folded into sin/cos (1 when unused)
+  const int* rope_pos;        // [T, pos_axes]
+  int pos_axes;               // 1 (text) or 3 (MRoPE t/h/w)
+  const int* token_seq;       // [T] row of the block table (-1 = padding)
+  const int* cache_pos;       // [T] position inside the sequence's KV cache
+  const int* block_table;     // [n_seq, table_stride] page ids (-1 = unmapped)
+  int table_stride;
+  __nv_bfloat16* q_out;       // [T, n_q_heads, head_dim]
+  KvLayer kv;
+};
+const char* attn_prep(const AttnPrepParams& p, cudaStream_t stream, bool pdl);
+
+struct PagedAttnParams {
+  const __nv_bfloat16* q;     // [Tq, n_q_heads, head_dim]
+  int Tq, n_q_heads, n_kv_heads, head_dim;
+  const int* q_seq;           // [Tq] block-table row of each query token
+  const int* q_kv_len;        // [Tq] number of visible keys (cache_pos + 1)
+  const int* block_table;
+  int table_stride;
+  KvLayer kv;
+  float sm_scale;
+  int split_keys;             // keys per split (multiple of 128); splits cover absolute ranges
+  int n_splits;               // grid.z = ceil(max_kv_len / split_keys)
+  float* part_o;              // [Tq, n_q_heads, n_splits, head_dim] fp32 un-normalised
+  float* part_ml;             // [Tq, n_q_heads, n_splits, 2] (max, sum)
+  // merge epilogue
+  const __nv_bfloat16* gate;  // optional [Tq, ld_gate] sigmoid gate, column h*head_dim + d
+  long long ld_gate;
+  __nv_bfloat16* out;         // [Tq, n_q_heads * head_dim]
+  // optional tree-verify mask: bit j of tree_mask[t] set = query t may see the key at
+  // position (tree_base[t] + j); keys below tree_base[t] are always visible.
+  const unsigned long long* tree_mask;
+  const int* tree_base;
+};
+// Split-KV paged attention over quantised pages with in-register dequantisation,
+// followed by the (m, l, o) merge fused with the output sigmoid gate.
+const char* paged_attention(const PagedAttnParams& p, cudaStream_t stream, bool pdl);
+
+}  // namespace nfb

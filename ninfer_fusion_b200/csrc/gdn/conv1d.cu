@@ -1,0 +1,92 @@
+// Depthwise causal conv1d (4 taps) + SiLU for the GDN q/k/v channels, ragged
+// batches, with the per-sequence 3-column history.  One thread owns a channel
+// pair of one token and gathers its four taps from the projection rows (or the
+// history for taps that fall before the sequence's first token of this call).
+//
+// Reference: include/ninfer/ops/causal_conv1d_silu.h, src/ops/kernel/causal_conv1d.cuh
+// (state = last 3 columns, oldest -> newest).
+#include "gdn.h"
+
+#include "../common/ptx.cuh"
+
+namespace nfb {
+
+namespace {
+
+__device__ __forceinline__ float2 ld2(const __nv_bfloat16* p) {
+  const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(p);
+  return make_float2(__bfloat162float(v.x), __bfloat162float(v.y));
+}
+
+// input of sequence `seq` at token index tau (global index), channel pair c.
+__device__ __forceinline__ float2 tap(const ConvParams& p, int tau, int seq_start, int slot, int c) {
+  if (tau >= seq_start) return ld2(p.x + static_cast<long long>(tau) * p.ld_x + p.c_off + c);
+  const int j = tau - seq_start + 3;  // 0..2
+  return ld2(p.conv_state + (static_cast<long long>(slot) * 3 + j) * p.C + c);
+}
+
+__global__ void __launch_bounds__(128) conv1d_silu_kernel(const ConvParams p) {
+  pdl_launch_next();
+  pdl_wait_prior();
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 2;
+  const int t = blockIdx.x;
+  if (c >= p.C) return;
+  const int seq = p.token_seq[t];
+  if (seq < 0) return;
+  const int start = p.cu_seqlens[seq];
+  const int slot = p.state_slot[seq];
+  const uint4 wv = *reinterpret_cast<const uint4*>(p.w + static_cast<long long>(c) * 4);  // 2 channels x 4 taps
+  const __nv_bfloat16* wp = reinterpret_cast<const __nv_bfloat16*>(&wv);
+  float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 x = tap(p, t - 3 + j, start, slot, c);
+    a0 += __bfloat162float(wp[j]) * x.x;
+    a1 += __bfloat162float(wp[4 + j]) * x.y;
+  }
+  a0 = a0 / (1.f + __expf(-a0));
+  a1 = a1 / (1.f + __expf(-a1));
+  *reinterpret_cast<uint32_t*>(p.out + static_cast<long long>(t) * p.C + c) = pack_bf16x2(a0, a1);
+}
+
+__global__ void __launch_bounds__(128) conv1d_state_kernel(const ConvParams p) {
+  pdl_launch_next();
+  pdl_wait_prior();
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 2;
+  const int seq = blockIdx.x;
+  if (c >= p.C) return;
+  const int start = p.cu_seqlens[seq], end = p.cu_seqlens[seq + 1];
+  if (end <= start) return;
+  const int slot = p.state_slot[seq];
+  float2 v[3];
+#pragma unroll
+  for (int j = 0; j < 3; ++j) v[j] = tap(p, end - 3 + j, start, slot, c);
+#pragma unroll
+  for (int j = 0; j < 3; ++j)
+    *reinterpret_cast<uint32_t*>(p.conv_state + (static_cast<long long>(slot) * 3 + j) * p.C + c) =
+        pack_bf16x2(v[j].x, v[j].y);
+}
+
+}  // namespace
+
+const char* causal_conv1d_silu(const ConvParams& p, cudaStream_t stream, bool pdl) {
+  if (p.T <= 0) return nullptr;
+  if (p.C % 2 || p.c_off % 2 || p.ld_x % 2) return "causal_conv1d_silu: channel counts/offsets must be even";
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(128); cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+  cfg.gridDim = dim3(p.T, (p.C / 2 + 127) / 128);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, conv1d_silu_kernel, p);
+  if (e != cudaSuccess) return cudaGetErrorString(e);
+  if (p.update_state) {
+    cfg.gridDim = dim3(p.n_seq, (p.C / 2 + 127) / 128);
+    e = cudaLaunchKernelEx(&cfg, conv1d_state_kernel, p);
+    if (e != cudaSuccess) return cudaGetErrorString(e);
+  }
+  return nullptr;
+}
+
+}  // namespace nfb

@@ -1,0 +1,51 @@
+// Host entry points of the Gated-DeltaNet family (plain C++ ABI).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace nfb {
+
+// Depthwise causal conv (kernel 4) + SiLU over C channels of a fused projection
+// row, for ragged batches.  Conv history lives per sequence slot as [slot, 3, C]
+// bf16, oldest -> newest.  `update_state` also rolls the history forward.
+struct ConvParams {
+  const __nv_bfloat16* x;   // [T, ld_x], channels start at c_off
+  long long ld_x;
+  int c_off, C, T, n_seq;
+  const __nv_bfloat16* w;   // [C, 4], tap 3 multiplies the newest input
+  const int* cu_seqlens;    // [n_seq + 1]
+  const int* token_seq;     // [T]
+  const int* state_slot;    // [n_seq]
+  __nv_bfloat16* conv_state;  // [slots, 3, C]
+  __nv_bfloat16* out;       // [T, C]
+  int update_state;
+};
+const char* causal_conv1d_silu(const ConvParams& p, cudaStream_t stream, bool pdl);
+
+// Gated delta rule over ragged sequences, state [slot, Hv, 128, 128] fp32 (dv-major):
+//   alpha = exp(-exp(A_log) * softplus(a + dt_bias)), beta = sigmoid(b)
+//   S = alpha * S;  u = beta * (v - S k);  S += u (x) k;  o = S q / sqrt(128)
+// with q, k L2-normalised per head, then per-head gated RMSNorm:
+//   y = o * rsqrt(mean(o^2) + eps) * norm_w * silu(z)
+struct GdnParams {
+  const __nv_bfloat16* qkv;  // [T, ld_qkv] conv output: q heads | k heads | v heads
+  long long ld_qkv;
+  int q_off, k_off, v_off;
+  const __nv_bfloat16* proj; // [T, ld_proj] raw projection (z, a, b columns)
+  long long ld_proj;
+  int z_off, a_off, b_off;
+  int T, n_seq, n_qk_heads, n_v_heads;
+  const float* A_log;        // [Hv]
+  const float* dt_bias;      // [Hv]
+  const __nv_bfloat16* norm_w;  // [128]
+  float eps;
+  const int* cu_seqlens;     // [n_seq + 1]
+  const int* state_slot;     // [n_seq]
+  float* state;              // [slots, Hv, 128, 128]
+  int write_state;           // 0: verify pass, state untouched
+  __nv_bfloat16* out;        // [T, Hv * 128]
+};
+const char* gdn_recurrent(const GdnParams& p, cudaStream_t stream, bool pdl);
+
+}  // namespace nfb

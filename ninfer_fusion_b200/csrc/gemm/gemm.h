@@ -1,0 +1,41 @@
+// Host entry points of the tcgen05 GEMM family (plain C++ ABI, no torch types).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace nfb {
+
+enum GemmEpilogue : int {
+  kEpiStore = 0,     // out = acc (+ bias[n])
+  kEpiResidual = 1,  // out = resid + acc
+  kEpiSwiglu = 2,    // W = [gate; up] (N rows), out[T, N/2] = silu(gate) * up
+  kEpiPartial = 3,   // partial[z, T, N] = acc over this split's K range (fp32)
+};
+
+struct GemmArgs {
+  const void* w = nullptr;  // [N, K] bf16 row-major, leading dimension ldw
+  int64_t N = 0, K = 0, ldw = 0;
+  const void* x = nullptr;  // [T, K] bf16 row-major, leading dimension ldx
+  int64_t T = 0, ldx = 0;
+  void* out = nullptr;      // bf16 [T, N] (or [T, N/2] for SwiGLU), leading dimension ldo
+  int64_t ldo = 0;
+  const void* resid = nullptr;
+  int64_t ldr = 0;
+  const float* bias = nullptr;
+  float* partial = nullptr;
+  int splits = 1;
+  int epi = kEpiStore;
+  int* status = nullptr;    // device status word (see common/ptx.cuh)
+  cudaStream_t stream = nullptr;
+  bool pdl = false;         // launch with programmatic stream serialization
+};
+
+// Returns nullptr on success, else a static error string.
+const char* gemm_bf16(const GemmArgs& args);
+
+// Token-tile width the kernel will use for T tokens (16, 32, 64, 128 or 256).
+int gemm_tile_tokens(int T);
+// Split-K factor that fills `sm_count` SMs for a decode-shaped problem.
+int gemm_pick_splits(int T, int N, int K, int epi, int sm_count);
+
+}  // namespace nfb

@@ -1,0 +1,410 @@
+// Weight-stationary bf16 GEMM for sm_100a:  out[T, N] = x[T, K] * W[N, K]^T.
+//
+// The weight matrix is the UMMA "A" operand (M = 128 weight rows per CTA), the
+// activations are the "B" operand (UMMA N = TN tokens, 16..256), so one kernel
+// template covers decode (T = 1..64: pure weight streaming) and prefill
+// (T tiles of 256).  Operands arrive by TMA into 128-byte-swizzled shared
+// memory, tcgen05.mma accumulates in TMEM, and the epilogue reads TMEM with
+// tcgen05.ld and fuses: plain store (+bias), residual add, SwiGLU (gate and up
+// rows of the fused [gate; up] parent are loaded as two 64-row boxes of one
+// 128-row tile), or fp32 split-K partials.
+//
+// Covers the reference's linear / linear_add / linear_swiglu bf16 routes
+// (include/ninfer/ops/linear.h, src/ops/linear/bf16/bf16_gemm_mma.cuh,
+// src/ops/linear_swiglu/*, src/ops/linear_add/*), which are mma.sync kernels.
+#include "gemm.h"
+
+#include <mutex>
+#include <unordered_map>
+
+#include "../common/ptx.cuh"
+#include "../common/tensor_map.h"
+
+namespace nfb {
+
+namespace {
+
+constexpr int kBlockK = 64;           // bf16 elements per k-block = one 128-byte swizzle row
+constexpr int kTileN = 128;           // weight rows per CTA (UMMA M)
+constexpr int kWTileBytes = kTileN * 128;
+
+template <int TN>
+struct GemmCfg {
+  static constexpr int kStages = TN <= 64 ? 4 : (TN == 128 ? 6 : 4);
+  static constexpr int kXTileBytes = TN * 128;
+  static constexpr int kStageBytes = kWTileBytes + kXTileBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // +1024: manual alignment
+  static constexpr int kTmemCols = TN < 32 ? 32 : TN;
+};
+
+struct KernelParams {
+  int T, N, K;
+  int kb_per_split;    // k-blocks handled by one blockIdx.z
+  int num_kb;          // ceil(K / 64)
+  int swiglu_half;     // N/2 for the SwiGLU epilogue, else 0
+  __nv_bfloat16* out;
+  long long ldo;
+  const __nv_bfloat16* resid;
+  long long ldr;
+  const float* bias;
+  float* partial;      // [splits, T, N] fp32
+  int* status;
+};
+
+template <int TN, int EPI>
+__global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                                                       const __grid_constant__ CUtensorMap tmap_x,
+                                                       const KernelParams p) {
+  using Cfg = GemmCfg<TN>;
+  constexpr int kStages = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kStages];
+  __shared__ __align__(8) uint64_t bar_empty[kStages];
+  __shared__ __align__(8) uint64_t bar_accum;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+  const int t0 = blockIdx.y * TN;
+  const int n0 = (EPI == kEpiSwiglu) ? blockIdx.x * 64 : blockIdx.x * kTileN;
+  const int kb_begin = blockIdx.z * p.kb_per_split;
+  const int kb_end = min(p.num_kb, kb_begin + p.kb_per_split);
+  const int num_it = kb_end - kb_begin;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&bar_accum), 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(&tmem_base_slot), Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  // Let the next kernel in the stream begin its own prologue / weight prefetch.
+  pdl_launch_next();
+
+  if (warp == 0) {
+    if (elect_one()) {
+      // ---------------- TMA producer ----------------
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_x = l2_policy_evict_last();
+      const int row_a = n0;
+      const int row_b = (EPI == kEpiSwiglu) ? p.swiglu_half + n0 : n0 + 64;
+      bool waited_prior = false;
+      int it = 0;
+      for (; it < num_it; ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1;
+        if (it >= kStages &&
+            !mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, &abort_flag, p.status, kStatusEmptyWaitTimeout))
+          break;
+        const uint32_t full = smem_u32(&bar_full[s]);
+        const uint32_t dst = smem_base + s * Cfg::kStageBytes;
+        const int kx = (kb_begin + it) * kBlockK;
+        mbar_expect_tx(full, Cfg::kStageBytes);
+        // Weights do not depend on the previous kernel: stream them first.
+        tma_load_2d(dst, &tmap_w, full, kx, row_a, pol_w);
+        tma_load_2d(dst + 64 * 128, &tmap_w, full, kx, row_b, pol_w);
+        if (!waited_prior) {
+          pdl_wait_prior();  // activations are produced by the previous kernel
+          waited_prior = true;
+        }
+        tma_load_2d(dst + kWTileBytes, &tmap_x, full, kx, t0, pol_x);
+      }
+      if (abort_flag) {
+        // Unwinding: let copies that were already issued land before the CTA exits.
+        const int first = it > kStages ? it - kStages : 0;
+        for (int j = first; j < it; ++j) {
+          const uint32_t bar = smem_u32(&bar_full[j % kStages]);
+          const uint32_t ph = (j / kStages) & 1;
+          for (uint32_t spin = 0; spin < (1u << 20); ++spin)
+            if (mbar_try_wait(bar, ph)) break;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      // ---------------- MMA issuer ----------------
+      constexpr uint32_t idesc = umma_idesc(kTileN, TN, 1, 1);
+      bool ok = true;
+      for (int it = 0; it < num_it; ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1;
+        if (!mbar_wait(smem_u32(&bar_full[s]), ph, &abort_flag, p.status, kStatusTmaWaitTimeout)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t a_addr = smem_base + s * Cfg::kStageBytes;
+        const uint64_t a_desc = umma_desc_k_sw128(a_addr);
+        const uint64_t b_desc = umma_desc_k_sw128(a_addr + kWTileBytes);
+#pragma unroll
+        for (int k = 0; k < kBlockK / 16; ++k) {
+          // advance 16 elements (32 bytes) along K inside the swizzle atom: +2 in 16-byte units
+          tc_mma_f16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (it > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&bar_empty[s]));
+      }
+      if (ok) tc_commit(smem_u32(&bar_accum));
+    }
+    __syncwarp();
+  }
+
+  // ---------------- epilogue: all four warps, warp w owns TMEM lanes 32w..32w+31 ----------------
+  pdl_wait_prior();
+  bool have_acc = true;
+  if (num_it > 0) {
+    have_acc = mbar_wait(smem_u32(&bar_accum), 0, &abort_flag, p.status, kStatusAccumWaitTimeout);
+  }
+  tc_fence_after();
+  // One CTA-wide verdict, so the barriers inside the epilogue are never divergent.
+  const int epilogue_ok = __syncthreads_and(have_acc && !abort_flag);
+
+  if (epilogue_ok) {
+    const uint32_t lane_taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    constexpr int kChunk = 16;
+    if constexpr (EPI == kEpiSwiglu) {
+      // lanes 0..63 hold gate rows, lanes 64..127 the matching up rows.
+      float* up_s = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));  // [TN][64]
+      if (warp >= 2) {
+        const int r = (warp - 2) * 32 + lane;
+        for (int c = 0; c < TN; c += kChunk) {
+          uint32_t v[kChunk];
+          tmem_ld_x16(lane_taddr + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < kChunk; ++j) up_s[(c + j) * 64 + r] = __uint_as_float(num_it > 0 ? v[j] : 0u);
+        }
+      }
+      __syncthreads();
+      if (warp < 2) {
+        const int r = warp * 32 + lane;
+        const int n = n0 + r;
+        for (int c = 0; c < TN; c += kChunk) {
+          uint32_t v[kChunk];
+          tmem_ld_x16(lane_taddr + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int m = 0; m < kChunk / 2; ++m) {
+            float a[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int j = 2 * m + h;
+              const float g = num_it > 0 ? __uint_as_float(v[j]) : 0.f;
+              const float u = up_s[(c + j) * 64 + r];
+              a[h] = g / (1.f + __expf(-g)) * u;
+            }
+            const float send = (lane & 1) ? a[0] : a[1];
+            const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+            const int t = t0 + c + 2 * m + (lane & 1);
+            const int ne = n & ~1;
+            if (t < p.T && ne < p.swiglu_half) {
+              const uint32_t packed = (lane & 1) ? pack_bf16x2(recv, a[1]) : pack_bf16x2(a[0], recv);
+              *reinterpret_cast<uint32_t*>(p.out + static_cast<long long>(t) * p.ldo + ne) = packed;
+            }
+          }
+        }
+      }
+    } else {
+      const int n = n0 + warp * 32 + lane;
+      const float bias = (EPI == kEpiStore && p.bias != nullptr && n < p.N) ? p.bias[n] : 0.f;
+      for (int c = 0; c < TN; c += kChunk) {
+        if (t0 + c >= p.T) break;
+        uint32_t v[kChunk];
+        tmem_ld_x16(lane_taddr + c, v);
+        tmem_ld_wait();
+        if (num_it == 0) {
+#pragma unroll
+          for (int j = 0; j < kChunk; ++j) v[j] = 0u;
+        }
+        if constexpr (EPI == kEpiPartial) {
+#pragma unroll
+          for (int j = 0; j < kChunk; ++j) {
+            const int t = t0 + c + j;
+            if (t < p.T && n < p.N)
+              p.partial[(static_cast<long long>(blockIdx.z) * p.T + t) * p.N + n] = __uint_as_float(v[j]);
+          }
+        } else {
+#pragma unroll
+          for (int m = 0; m < kChunk / 2; ++m) {
+            const float a0 = __uint_as_float(v[2 * m]) + bias;
+            const float a1 = __uint_as_float(v[2 * m + 1]) + bias;
+            const float send = (lane & 1) ? a0 : a1;
+            const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+            const int t = t0 + c + 2 * m + (lane & 1);
+            const int ne = n & ~1;
+            if (t < p.T && ne < p.N) {
+              float lo = (lane & 1) ? recv : a0;
+              float hi = (lane & 1) ? a1 : recv;
+              if constexpr (EPI == kEpiResidual) {
+                const __nv_bfloat162 r2 = *reinterpret_cast<const __nv_bfloat162*>(
+                    p.resid + static_cast<long long>(t) * p.ldr + ne);
+                lo += __bfloat162float(r2.x);
+                hi += __bfloat162float(r2.y);
+              }
+              *reinterpret_cast<uint32_t*>(p.out + static_cast<long long>(t) * p.ldo + ne) =
+                  pack_bf16x2(lo, hi);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+template <int TN, int EPI>
+cudaError_t launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const KernelParams& kp, dim3 grid,
+                       cudaStream_t stream, bool pdl) {
+  using Cfg = GemmCfg<TN>;
+  auto kern = gemm_ws_kernel<TN, EPI>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, tw, tx, kp);
+}
+
+template <int EPI>
+cudaError_t launch_tn(int TN, const CUtensorMap& tw, const CUtensorMap& tx, const KernelParams& kp,
+                      dim3 grid, cudaStream_t stream, bool pdl) {
+  switch (TN) {
+    case 16: return launch_one<16, EPI>(tw, tx, kp, grid, stream, pdl);
+    case 32: return launch_one<32, EPI>(tw, tx, kp, grid, stream, pdl);
+    case 64: return launch_one<64, EPI>(tw, tx, kp, grid, stream, pdl);
+    case 128: return launch_one<128, EPI>(tw, tx, kp, grid, stream, pdl);
+    default: return launch_one<256, EPI>(tw, tx, kp, grid, stream, pdl);
+  }
+}
+
+// Tensor maps are pure functions of (pointer, shape, box): cache them so the
+// eager path does not re-encode on every call.
+struct TmapKey {
+  const void* base; uint64_t rows, cols, ld; uint32_t box_rows;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.base);
+    h = h * 1000003u ^ k.rows; h = h * 1000003u ^ k.cols; h = h * 1000003u ^ k.ld;
+    return h * 1000003u ^ k.box_rows;
+  }
+};
+bool cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                 uint32_t box_rows) {
+  static std::mutex mu;
+  static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  TmapKey key{base, rows, cols, ld, box_rows};
+  std::lock_guard<std::mutex> g(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return true; }
+  CUtensorMap m;
+  if (!make_tmap_2d(&m, TmapDtype::BF16, base, rows, cols, ld, box_rows, kBlockK, true)) return false;
+  if (cache.size() > 65536) cache.clear();
+  cache.emplace(key, m);
+  *out = m;
+  return true;
+}
+
+}  // namespace
+
+int gemm_tile_tokens(int T) {
+  if (T <= 16) return 16;
+  if (T <= 32) return 32;
+  if (T <= 64) return 64;
+  if (T <= 128) return 128;
+  return 256;
+}
+
+int gemm_pick_splits(int T, int N, int K, int epi, int sm_count) {
+  if (epi == kEpiSwiglu) return 1;
+  const int tn = gemm_tile_tokens(T);
+  const int tiles = ((N + kTileN - 1) / kTileN) * ((T + tn - 1) / tn);
+  const int num_kb = (K + kBlockK - 1) / kBlockK;
+  const int slots = sm_count * (tn <= 64 ? 2 : 1);
+  if (tiles >= slots || T > 256) return 1;
+  int s = slots / tiles;
+  if (s > 8) s = 8;
+  while (s > 1 && num_kb / s < 8) --s;  // keep at least 8 k-blocks per split
+  if (s < 1) s = 1;
+  const int per = (num_kb + s - 1) / s;
+  return (num_kb + per - 1) / per;  // no empty trailing split
+}
+
+const char* gemm_bf16(const GemmArgs& a) {
+  if (a.T <= 0 || a.N <= 0 || a.K <= 0) return "gemm_bf16: empty problem";
+  if ((a.K % 8) || (a.ldw % 8) || (a.ldx % 8)) return "gemm_bf16: K and leading dims must be multiples of 8";
+  if ((reinterpret_cast<uintptr_t>(a.w) | reinterpret_cast<uintptr_t>(a.x)) & 15)
+    return "gemm_bf16: operands must be 16-byte aligned";
+  if ((a.N & 1) || (a.ldo & 1)) return "gemm_bf16: N and ldo must be even";
+  const int tn = gemm_tile_tokens(static_cast<int>(a.T));
+  KernelParams kp = {};
+  kp.T = static_cast<int>(a.T); kp.N = static_cast<int>(a.N); kp.K = static_cast<int>(a.K);
+  kp.num_kb = (kp.K + kBlockK - 1) / kBlockK;
+  int splits = a.splits < 1 ? 1 : a.splits;
+  if (a.epi != kEpiPartial) splits = 1;
+  if (splits > kp.num_kb) splits = kp.num_kb;
+  kp.kb_per_split = (kp.num_kb + splits - 1) / splits;
+  splits = (kp.num_kb + kp.kb_per_split - 1) / kp.kb_per_split;  // no empty split
+  if (a.epi == kEpiPartial && splits != a.splits) return "gemm_bf16: split count leaves an empty split";
+  kp.swiglu_half = a.epi == kEpiSwiglu ? kp.N / 2 : 0;
+  if (a.epi == kEpiSwiglu && (kp.N % 4)) return "gemm_bf16: SwiGLU needs N % 4 == 0";
+  kp.out = static_cast<__nv_bfloat16*>(a.out); kp.ldo = a.ldo;
+  kp.resid = static_cast<const __nv_bfloat16*>(a.resid); kp.ldr = a.ldr;
+  kp.bias = a.bias; kp.partial = a.partial; kp.status = a.status;
+  if (a.epi == kEpiResidual && a.resid == nullptr) return "gemm_bf16: residual epilogue without residual";
+  if (a.epi == kEpiPartial && a.partial == nullptr) return "gemm_bf16: split-K without workspace";
+  if (a.epi != kEpiPartial && a.out == nullptr) return "gemm_bf16: no output";
+
+  CUtensorMap tw, tx;
+  if (!cached_tmap(&tw, a.w, a.N, a.K, a.ldw, 64)) return "gemm_bf16: weight tensor map rejected";
+  if (!cached_tmap(&tx, a.x, a.T, a.K, a.ldx, tn)) return "gemm_bf16: activation tensor map rejected";
+
+  dim3 grid;
+  grid.x = a.epi == kEpiSwiglu ? (kp.swiglu_half + 63) / 64 : (kp.N + kTileN - 1) / kTileN;
+  grid.y = (kp.T + tn - 1) / tn;
+  grid.z = splits;
+  cudaError_t e;
+  switch (a.epi) {
+    case kEpiStore: e = launch_tn<kEpiStore>(tn, tw, tx, kp, grid, a.stream, a.pdl); break;
+    case kEpiResidual: e = launch_tn<kEpiResidual>(tn, tw, tx, kp, grid, a.stream, a.pdl); break;
+    case kEpiSwiglu: e = launch_tn<kEpiSwiglu>(tn, tw, tx, kp, grid, a.stream, a.pdl); break;
+    case kEpiPartial: e = launch_tn<kEpiPartial>(tn, tw, tx, kp, grid, a.stream, a.pdl); break;
+    default: return "gemm_bf16: unknown epilogue";
+  }
+  return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
+
+}  // namespace nfb

@@ -1,0 +1,38 @@
+// Host entry points of the token-selection kernels (plain C++ ABI).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace nfb {
+
+constexpr int kMaxTopK = 32;
+
+const char* argmax_rows(const void* logits, long long ld, int T, int V, int* out, cudaStream_t stream, bool pdl);
+
+struct SampleParams {
+  const __nv_bfloat16* logits;  // [T, ld]
+  long long ld;
+  int T, V;
+  const float* temperature;     // per row; <= 0 means greedy.  Null = 1
+  const int* top_k;             // per row; <= 0 or > 32 means 32.  Null = 32
+  const float* top_p;           // null = 1
+  const float* min_p;           // null = 0
+  const float* presence;        // null = 0
+  const float* frequency;       // null = 0
+  const int* token_counts;      // [T, V] occurrences so far, or null
+  const unsigned long long* seeds;  // per row
+  const int* positions;         // logical position of the token being drawn, per row
+  unsigned int purpose;         // stream id: 0 = sample, 1 = spec accept, 2 = residual resample, ...
+  int* out;                     // [T]
+  float* out_prob;              // optional: probability of the drawn token under the final distribution
+};
+const char* sample_rows(const SampleParams& p, cudaStream_t stream);
+
+const char* accept_greedy_chain(const int* target_ids, const int* draft_ids, int B, int K, int* n_accepted,
+                                int* out_tokens, cudaStream_t stream);
+const char* accept_greedy_tree(const int* target_ids, const int* node_tok, const int* parent, int B, int N,
+                               int max_depth, int* n_accepted, int* out_tokens, int* out_nodes,
+                               cudaStream_t stream);
+
+}  // namespace nfb

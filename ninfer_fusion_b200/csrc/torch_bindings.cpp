@@ -1,0 +1,361 @@
+// torch.ops.nfb200.* : thin, checked adapters from torch tensors to the plain
+// C++ launchers.  No kernel code lives here.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+#include <ATen/ATen.h>
+
+#include "attention/attention.h"
+#include "gdn/gdn.h"
+#include "gemm/gemm.h"
+#include "pointwise/pointwise.h"
+#include "sampling/sampling.h"
+
+namespace {
+
+using at::Tensor;
+using OptT = const std::optional<Tensor>&;
+
+inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+inline void chk(const char* err) { TORCH_CHECK(err == nullptr, err ? err : ""); }
+
+inline void need_cuda(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+}
+inline void need(const Tensor& t, at::ScalarType dt, const char* name) {
+  need_cuda(t, name);
+  TORCH_CHECK(t.scalar_type() == dt, name, " has the wrong dtype");
+}
+inline void need_rows(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.dim() == 2 && t.stride(1) == 1, name, " must be 2-D with unit inner stride");
+}
+template <typename T>
+inline T* ptr_or_null(OptT t) {
+  return t.has_value() && t->defined() ? static_cast<T*>(t->data_ptr()) : nullptr;
+}
+
+int64_t sm_count() {
+  static int n = 0;
+  if (n == 0) n = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  return n;
+}
+
+// out = epilogue(x @ w^T).  epi: 0 store(+bias), 1 residual add, 2 swiglu, 3 split-K partials.
+void gemm_bf16(const Tensor& x, const Tensor& w, OptT out, int64_t epi, OptT resid, OptT bias, OptT partial,
+               int64_t splits, OptT status, bool pdl) {
+  need(x, at::kBFloat16, "x"); need(w, at::kBFloat16, "w");
+  need_rows(x, "x"); need_rows(w, "w");
+  TORCH_CHECK(x.size(1) == w.size(1), "gemm_bf16: K mismatch");
+  c10::cuda::CUDAGuard guard(x.device());
+  nfb::GemmArgs a;
+  a.w = w.data_ptr(); a.N = w.size(0); a.K = w.size(1); a.ldw = w.stride(0);
+  a.x = x.data_ptr(); a.T = x.size(0); a.ldx = x.stride(0);
+  const int64_t out_cols = epi == nfb::kEpiSwiglu ? a.N / 2 : a.N;
+  if (epi != nfb::kEpiPartial) {
+    TORCH_CHECK(out.has_value(), "gemm_bf16: out required");
+    need(*out, at::kBFloat16, "out"); need_rows(*out, "out");
+    TORCH_CHECK(out->size(0) == a.T && out->size(1) == out_cols, "gemm_bf16: out shape");
+    a.out = out->data_ptr(); a.ldo = out->stride(0);
+  }
+  if (epi == nfb::kEpiResidual) {
+    TORCH_CHECK(resid.has_value(), "gemm_bf16: resid required");
+    need(*resid, at::kBFloat16, "resid"); need_rows(*resid, "resid");
+    TORCH_CHECK(resid->size(0) == a.T && resid->size(1) == a.N, "gemm_bf16: resid shape");
+    a.resid = resid->data_ptr(); a.ldr = resid->stride(0);
+  }
+  if (bias.has_value() && bias->defined()) {
+    need(*bias, at::kFloat, "bias");
+    TORCH_CHECK(bias->numel() == a.N && bias->is_contiguous(), "gemm_bf16: bias shape");
+    a.bias = static_cast<const float*>(bias->data_ptr());
+  }
+  if (epi == nfb::kEpiPartial) {
+    TORCH_CHECK(partial.has_value(), "gemm_bf16: partial workspace required");
+    need(*partial, at::kFloat, "partial");
+    TORCH_CHECK(partial->is_contiguous() && partial->numel() >= splits * a.T * a.N, "gemm_bf16: workspace too small");
+    a.partial = static_cast<float*>(partial->data_ptr());
+  }
+  a.splits = static_cast<int>(splits); a.epi = static_cast<int>(epi);
+  a.status = ptr_or_null<int>(status);
+  a.stream = cur_stream(); a.pdl = pdl;
+  chk(nfb::gemm_bf16(a));
+}
+
+int64_t gemm_pick_splits(int64_t T, int64_t N, int64_t K, int64_t epi) {
+  return nfb::gemm_pick_splits(static_cast<int>(T), static_cast<int>(N), static_cast<int>(K), static_cast<int>(epi),
+                               static_cast<int>(sm_count()));
+}
+
+void add_rmsnorm(OptT partial, int64_t splits, OptT delta, OptT resid_in, OptT resid_out, OptT norm_w, OptT normed,
+                 int64_t T, int64_t N, double eps, bool unit_offset, bool pdl) {
+  auto dev_of = [&]() -> const Tensor& {
+    if (resid_in.has_value() && resid_in->defined()) return *resid_in;
+    if (delta.has_value() && delta->defined()) return *delta;
+    TORCH_CHECK(partial.has_value() && partial->defined(), "add_rmsnorm: no input");
+    return *partial;
+  };
+  c10::cuda::CUDAGuard guard(dev_of().device());
+  for (OptT t : {delta, resid_in, resid_out, normed}) {
+    if (t.has_value() && t->defined()) {
+      need(*t, at::kBFloat16, "add_rmsnorm tensor");
+      TORCH_CHECK(t->is_contiguous() && t->numel() == T * N, "add_rmsnorm: tensors must be contiguous [T, N]");
+    }
+  }
+  if (partial.has_value() && partial->defined()) {
+    need(*partial, at::kFloat, "partial");
+    TORCH_CHECK(partial->is_contiguous() && partial->numel() >= splits * T * N, "add_rmsnorm: partial too small");
+  }
+  if (norm_w.has_value() && norm_w->defined()) {
+    need(*norm_w, at::kBFloat16, "norm_w");
+    TORCH_CHECK(norm_w->numel() == N, "add_rmsnorm: norm_w shape");
+  }
+  chk(nfb::add_rmsnorm(ptr_or_null<float>(partial), static_cast<int>(splits), ptr_or_null<void>(delta),
+                       ptr_or_null<void>(resid_in), ptr_or_null<void>(resid_out), ptr_or_null<void>(norm_w),
+                       ptr_or_null<void>(normed), static_cast<int>(T), static_cast<int>(N), static_cast<float>(eps),
+                       unit_offset ? 1 : 0, cur_stream(), pdl));
+}
+
+void embed_gather(const Tensor& ids, const Tensor& table, const Tensor& out, bool pdl) {
+  need(ids, at::kInt, "ids"); need(table, at::kBFloat16, "table"); need(out, at::kBFloat16, "out");
+  TORCH_CHECK(table.is_contiguous() && out.is_contiguous() && ids.is_contiguous());
+  TORCH_CHECK(out.size(0) == ids.numel() && out.size(1) == table.size(1));
+  c10::cuda::CUDAGuard guard(ids.device());
+  chk(nfb::embed_gather(static_cast<const int*>(ids.data_ptr()), table.data_ptr(), out.data_ptr(),
+                        static_cast<int>(ids.numel()), static_cast<int>(table.size(1)),
+                        static_cast<int>(table.size(0)), cur_stream(), pdl));
+}
+
+nfb::KvLayer make_kv(const Tensor& k_codes, const Tensor& v_codes, OptT k_scales, OptT v_scales, int64_t page_size,
+                     int64_t n_kv_heads, int64_t head_dim, int64_t format, int64_t group) {
+  need(k_codes, at::kByte, "k_codes"); need(v_codes, at::kByte, "v_codes");
+  TORCH_CHECK(k_codes.is_contiguous() && v_codes.is_contiguous());
+  nfb::KvLayer kv;
+  kv.k_codes = static_cast<uint8_t*>(k_codes.data_ptr());
+  kv.v_codes = static_cast<uint8_t*>(v_codes.data_ptr());
+  kv.k_scales = ptr_or_null<uint8_t>(k_scales);
+  kv.v_scales = ptr_or_null<uint8_t>(v_scales);
+  kv.page_size = static_cast<int>(page_size);
+  kv.n_kv_heads = static_cast<int>(n_kv_heads);
+  kv.head_dim = static_cast<int>(head_dim);
+  kv.format = static_cast<int>(format);
+  kv.group = static_cast<int>(group);
+  const int64_t rb = nfb::kv_row_bytes(kv.format, kv.head_dim);
+  TORCH_CHECK(k_codes.numel() % (n_kv_heads * page_size * rb) == 0, "kv codes size is not a whole number of pages");
+  if (nfb::kv_scale_bytes(kv.format, kv.head_dim, kv.group) > 0)
+    TORCH_CHECK(kv.k_scales != nullptr && kv.v_scales != nullptr, "this KV format needs scale planes");
+  return kv;
+}
+
+void attn_prep(const Tensor& proj, int64_t q_off, int64_t k_off, int64_t v_off, int64_t n_q_heads,
+               int64_t n_kv_heads, int64_t head_dim, OptT q_norm_w, OptT k_norm_w, double eps, bool unit_offset,
+               int64_t rot_dim, const Tensor& inv_freq, double attn_factor, const Tensor& rope_pos,
+               const Tensor& token_seq, const Tensor& cache_pos, const Tensor& block_table, const Tensor& q_out,
+               const Tensor& k_codes, const Tensor& v_codes, OptT k_scales, OptT v_scales, int64_t page_size,
+               int64_t format, int64_t group, bool pdl) {
+  need(proj, at::kBFloat16, "proj"); need_rows(proj, "proj");
+  need(inv_freq, at::kFloat, "inv_freq"); need(rope_pos, at::kInt, "rope_pos");
+  need(token_seq, at::kInt, "token_seq"); need(cache_pos, at::kInt, "cache_pos");
+  need(block_table, at::kInt, "block_table"); need(q_out, at::kBFloat16, "q_out");
+  TORCH_CHECK(block_table.dim() == 2 && block_table.is_contiguous() && q_out.is_contiguous() && rope_pos.is_contiguous());
+  c10::cuda::CUDAGuard guard(proj.device());
+  nfb::AttnPrepParams p = {};
+  p.proj = static_cast<const __nv_bfloat16*>(proj.data_ptr());
+  p.ld_proj = proj.stride(0);
+  p.q_off = static_cast<int>(q_off); p.k_off = static_cast<int>(k_off); p.v_off = static_cast<int>(v_off);
+  p.T = static_cast<int>(proj.size(0));
+  p.n_q_heads = static_cast<int>(n_q_heads); p.n_kv_heads = static_cast<int>(n_kv_heads);
+  p.head_dim = static_cast<int>(head_dim);
+  p.q_norm_w = ptr_or_null<const __nv_bfloat16>(q_norm_w);
+  p.k_norm_w = ptr_or_null<const __nv_bfloat16>(k_norm_w);
+  p.eps = static_cast<float>(eps); p.unit_offset = unit_offset ? 1 : 0;
+  p.rot_dim = static_cast<int>(rot_dim);
+  TORCH_CHECK(inv_freq.numel() >= rot_dim / 2, "inv_freq too short");
+  p.inv_freq = static_cast<const float*>(inv_freq.data_ptr());
+  p.rope_attn_factor = static_cast<float>(attn_factor);
+  p.rope_pos = static_cast<const int*>(rope_pos.data_ptr());
+  p.pos_axes = rope_pos.dim() == 2 ? static_cast<int>(rope_pos.size(1)) : 1;
+  TORCH_CHECK(p.pos_axes == 1 || p.pos_axes == 3, "rope_pos must be [T] or [T, 3]");
+  TORCH_CHECK(rope_pos.numel() == static_cast<int64_t>(p.T) * p.pos_axes && token_seq.numel() == p.T &&
+              cache_pos.numel() == p.T, "per-token arrays must have T entries");
+  p.token_seq = static_cast<const int*>(token_seq.data_ptr());
+  p.cache_pos = static_cast<const int*>(cache_pos.data_ptr());
+  p.block_table = static_cast<const int*>(block_table.data_ptr());
+  p.table_stride = static_cast<int>(block_table.size(1));
+  TORCH_CHECK(q_out.numel() == static_cast<int64_t>(p.T) * n_q_heads * head_dim, "q_out shape");
+  p.q_out = static_cast<__nv_bfloat16*>(q_out.data_ptr());
+  p.kv = make_kv(k_codes, v_codes, k_scales, v_scales, page_size, n_kv_heads, head_dim, format, group);
+  chk(nfb::attn_prep(p, cur_stream(), pdl));
+}
+
+void paged_attention(const Tensor& q, int64_t n_q_heads, int64_t n_kv_heads, int64_t head_dim, const Tensor& q_seq,
+                     const Tensor& q_kv_len, const Tensor& block_table, const Tensor& k_codes, const Tensor& v_codes,
+                     OptT k_scales, OptT v_scales, int64_t page_size, int64_t format, int64_t group, double sm_scale,
+                     int64_t split_keys, int64_t n_splits, const Tensor& part_o, const Tensor& part_ml, OptT gate,
+                     const Tensor& out, OptT tree_mask, OptT tree_base, bool pdl) {
+  need(q, at::kBFloat16, "q"); need(q_seq, at::kInt, "q_seq"); need(q_kv_len, at::kInt, "q_kv_len");
+  need(block_table, at::kInt, "block_table"); need(part_o, at::kFloat, "part_o"); need(part_ml, at::kFloat, "part_ml");
+  need(out, at::kBFloat16, "out");
+  TORCH_CHECK(q.is_contiguous() && out.is_contiguous() && block_table.dim() == 2 && block_table.is_contiguous());
+  c10::cuda::CUDAGuard guard(q.device());
+  nfb::PagedAttnParams p = {};
+  p.q = static_cast<const __nv_bfloat16*>(q.data_ptr());
+  p.Tq = static_cast<int>(q.numel() / (n_q_heads * head_dim));
+  p.n_q_heads = static_cast<int>(n_q_heads); p.n_kv_heads = static_cast<int>(n_kv_heads);
+  p.head_dim = static_cast<int>(head_dim);
+  TORCH_CHECK(q_seq.numel() == p.Tq && q_kv_len.numel() == p.Tq, "per-query arrays must have Tq entries");
+  p.q_seq = static_cast<const int*>(q_seq.data_ptr());
+  p.q_kv_len = static_cast<const int*>(q_kv_len.data_ptr());
+  p.block_table = static_cast<const int*>(block_table.data_ptr());
+  p.table_stride = static_cast<int>(block_table.size(1));
+  p.kv = make_kv(k_codes, v_codes, k_scales, v_scales, page_size, n_kv_heads, head_dim, format, group);
+  p.sm_scale = static_cast<float>(sm_scale);
+  p.split_keys = static_cast<int>(split_keys); p.n_splits = static_cast<int>(n_splits);
+  TORCH_CHECK(part_o.numel() >= static_cast<int64_t>(p.Tq) * n_q_heads * n_splits * head_dim, "part_o too small");
+  TORCH_CHECK(part_ml.numel() >= static_cast<int64_t>(p.Tq) * n_q_heads * n_splits * 2, "part_ml too small");
+  p.part_o = static_cast<float*>(part_o.data_ptr());
+  p.part_ml = static_cast<float*>(part_ml.data_ptr());
+  if (gate.has_value() && gate->defined()) {
+    need(*gate, at::kBFloat16, "gate"); need_rows(*gate, "gate");
+    p.gate = static_cast<const __nv_bfloat16*>(gate->data_ptr());
+    p.ld_gate = gate->stride(0);
+  }
+  TORCH_CHECK(out.numel() == static_cast<int64_t>(p.Tq) * n_q_heads * head_dim, "out shape");
+  p.out = static_cast<__nv_bfloat16*>(out.data_ptr());
+  if (tree_mask.has_value() && tree_mask->defined()) {
+    need(*tree_mask, at::kLong, "tree_mask");
+    TORCH_CHECK(tree_base.has_value(), "tree_base required with tree_mask");
+    need(*tree_base, at::kInt, "tree_base");
+    p.tree_mask = static_cast<const unsigned long long*>(tree_mask->data_ptr());
+    p.tree_base = static_cast<const int*>(tree_base->data_ptr());
+  }
+  chk(nfb::paged_attention(p, cur_stream(), pdl));
+}
+
+void causal_conv1d_silu(const Tensor& x, int64_t c_off, int64_t C, const Tensor& w, const Tensor& cu_seqlens,
+                        const Tensor& token_seq, const Tensor& state_slot, const Tensor& conv_state,
+                        const Tensor& out, bool update_state, bool pdl) {
+  need(x, at::kBFloat16, "x"); need_rows(x, "x"); need(w, at::kBFloat16, "w");
+  need(cu_seqlens, at::kInt, "cu_seqlens"); need(token_seq, at::kInt, "token_seq");
+  need(state_slot, at::kInt, "state_slot"); need(conv_state, at::kBFloat16, "conv_state");
+  need(out, at::kBFloat16, "out");
+  TORCH_CHECK(w.is_contiguous() && w.numel() == C * 4 && conv_state.is_contiguous() && out.is_contiguous());
+  TORCH_CHECK(conv_state.dim() == 3 && conv_state.size(1) == 3 && conv_state.size(2) == C, "conv_state [slots,3,C]");
+  c10::cuda::CUDAGuard guard(x.device());
+  nfb::ConvParams p = {};
+  p.x = static_cast<const __nv_bfloat16*>(x.data_ptr()); p.ld_x = x.stride(0);
+  p.c_off = static_cast<int>(c_off); p.C = static_cast<int>(C); p.T = static_cast<int>(x.size(0));
+  p.n_seq = static_cast<int>(state_slot.numel());
+  TORCH_CHECK(cu_seqlens.numel() == p.n_seq + 1 && token_seq.numel() == p.T);
+  TORCH_CHECK(out.numel() == static_cast<int64_t>(p.T) * C, "conv out shape");
+  p.w = static_cast<const __nv_bfloat16*>(w.data_ptr());
+  p.cu_seqlens = static_cast<const int*>(cu_seqlens.data_ptr());
+  p.token_seq = static_cast<const int*>(token_seq.data_ptr());
+  p.state_slot = static_cast<const int*>(state_slot.data_ptr());
+  p.conv_state = static_cast<__nv_bfloat16*>(conv_state.data_ptr());
+  p.out = static_cast<__nv_bfloat16*>(out.data_ptr());
+  p.update_state = update_state ? 1 : 0;
+  chk(nfb::causal_conv1d_silu(p, cur_stream(), pdl));
+}
+
+void gdn_recurrent(const Tensor& qkv, int64_t q_off, int64_t k_off, int64_t v_off, const Tensor& proj, int64_t z_off,
+                   int64_t a_off, int64_t b_off, int64_t n_qk_heads, int64_t n_v_heads, const Tensor& A_log,
+                   const Tensor& dt_bias, const Tensor& norm_w, double eps, const Tensor& cu_seqlens,
+                   const Tensor& state_slot, const Tensor& state, bool write_state, const Tensor& out, bool pdl) {
+  need(qkv, at::kBFloat16, "qkv"); need_rows(qkv, "qkv"); need(proj, at::kBFloat16, "proj"); need_rows(proj, "proj");
+  need(A_log, at::kFloat, "A_log"); need(dt_bias, at::kFloat, "dt_bias"); need(norm_w, at::kBFloat16, "norm_w");
+  need(cu_seqlens, at::kInt, "cu_seqlens"); need(state_slot, at::kInt, "state_slot");
+  need(state, at::kFloat, "state"); need(out, at::kBFloat16, "out");
+  TORCH_CHECK(state.is_contiguous() && state.dim() == 4 && state.size(1) == n_v_heads && state.size(2) == 128 &&
+              state.size(3) == 128, "state must be [slots, Hv, 128, 128]");
+  TORCH_CHECK(out.is_contiguous() && out.numel() == qkv.size(0) * n_v_heads * 128, "gdn out shape");
+  TORCH_CHECK(A_log.numel() == n_v_heads && dt_bias.numel() == n_v_heads && norm_w.numel() == 128);
+  c10::cuda::CUDAGuard guard(qkv.device());
+  nfb::GdnParams p = {};
+  p.qkv = static_cast<const __nv_bfloat16*>(qkv.data_ptr()); p.ld_qkv = qkv.stride(0);
+  p.q_off = static_cast<int>(q_off); p.k_off = static_cast<int>(k_off); p.v_off = static_cast<int>(v_off);
+  p.proj = static_cast<const __nv_bfloat16*>(proj.data_ptr()); p.ld_proj = proj.stride(0);
+  p.z_off = static_cast<int>(z_off); p.a_off = static_cast<int>(a_off); p.b_off = static_cast<int>(b_off);
+  p.T = static_cast<int>(qkv.size(0)); p.n_seq = static_cast<int>(state_slot.numel());
+  TORCH_CHECK(cu_seqlens.numel() == p.n_seq + 1);
+  p.n_qk_heads = static_cast<int>(n_qk_heads); p.n_v_heads = static_cast<int>(n_v_heads);
+  p.A_log = static_cast<const float*>(A_log.data_ptr()); p.dt_bias = static_cast<const float*>(dt_bias.data_ptr());
+  p.norm_w = static_cast<const __nv_bfloat16*>(norm_w.data_ptr()); p.eps = static_cast<float>(eps);
+  p.cu_seqlens = static_cast<const int*>(cu_seqlens.data_ptr());
+  p.state_slot = static_cast<const int*>(state_slot.data_ptr());
+  p.state = static_cast<float*>(state.data_ptr());
+  p.write_state = write_state ? 1 : 0;
+  p.out = static_cast<__nv_bfloat16*>(out.data_ptr());
+  chk(nfb::gdn_recurrent(p, cur_stream(), pdl));
+}
+
+void argmax_rows(const Tensor& logits, const Tensor& out, bool pdl) {
+  need(logits, at::kBFloat16, "logits"); need_rows(logits, "logits"); need(out, at::kInt, "out");
+  TORCH_CHECK(out.numel() == logits.size(0));
+  c10::cuda::CUDAGuard guard(logits.device());
+  chk(nfb::argmax_rows(logits.data_ptr(), logits.stride(0), static_cast<int>(logits.size(0)),
+                       static_cast<int>(logits.size(1)), static_cast<int*>(out.data_ptr()), cur_stream(), pdl));
+}
+
+void sample_rows(const Tensor& logits, OptT temperature, OptT top_k, OptT top_p, OptT min_p, OptT presence,
+                 OptT frequency, OptT token_counts, OptT seeds, OptT positions, int64_t purpose, const Tensor& out,
+                 OptT out_prob) {
+  need(logits, at::kBFloat16, "logits"); need_rows(logits, "logits"); need(out, at::kInt, "out");
+  c10::cuda::CUDAGuard guard(logits.device());
+  nfb::SampleParams p = {};
+  p.logits = static_cast<const __nv_bfloat16*>(logits.data_ptr()); p.ld = logits.stride(0);
+  p.T = static_cast<int>(logits.size(0)); p.V = static_cast<int>(logits.size(1));
+  p.temperature = ptr_or_null<const float>(temperature); p.top_k = ptr_or_null<const int>(top_k);
+  p.top_p = ptr_or_null<const float>(top_p); p.min_p = ptr_or_null<const float>(min_p);
+  p.presence = ptr_or_null<const float>(presence); p.frequency = ptr_or_null<const float>(frequency);
+  p.token_counts = ptr_or_null<const int>(token_counts);
+  p.seeds = ptr_or_null<const unsigned long long>(seeds); p.positions = ptr_or_null<const int>(positions);
+  p.purpose = static_cast<unsigned int>(purpose);
+  p.out = static_cast<int*>(out.data_ptr()); p.out_prob = ptr_or_null<float>(out_prob);
+  chk(nfb::sample_rows(p, cur_stream()));
+}
+
+void accept_greedy_chain(const Tensor& target_ids, const Tensor& draft_ids, const Tensor& n_accepted,
+                         const Tensor& out_tokens) {
+  need(target_ids, at::kInt, "target_ids"); need(draft_ids, at::kInt, "draft_ids");
+  need(n_accepted, at::kInt, "n_accepted"); need(out_tokens, at::kInt, "out_tokens");
+  const int B = static_cast<int>(draft_ids.size(0)), K = static_cast<int>(draft_ids.size(1));
+  TORCH_CHECK(target_ids.is_contiguous() && draft_ids.is_contiguous() && target_ids.numel() == B * (K + 1) &&
+              out_tokens.numel() == B * (K + 1) && n_accepted.numel() == B);
+  c10::cuda::CUDAGuard guard(target_ids.device());
+  chk(nfb::accept_greedy_chain(static_cast<const int*>(target_ids.data_ptr()),
+                               static_cast<const int*>(draft_ids.data_ptr()), B, K,
+                               static_cast<int*>(n_accepted.data_ptr()), static_cast<int*>(out_tokens.data_ptr()),
+                               cur_stream()));
+}
+
+void accept_greedy_tree(const Tensor& target_ids, const Tensor& node_tok, const Tensor& parent, int64_t max_depth,
+                        const Tensor& n_accepted, const Tensor& out_tokens, const Tensor& out_nodes) {
+  need(target_ids, at::kInt, "target_ids"); need(node_tok, at::kInt, "node_tok"); need(parent, at::kInt, "parent");
+  need(n_accepted, at::kInt, "n_accepted"); need(out_tokens, at::kInt, "out_tokens"); need(out_nodes, at::kInt, "out_nodes");
+  const int B = static_cast<int>(node_tok.size(0)), N = static_cast<int>(node_tok.size(1));
+  TORCH_CHECK(target_ids.numel() == B * N && parent.numel() == B * N && n_accepted.numel() == B &&
+              out_tokens.numel() == B * (max_depth + 1) && out_nodes.numel() == B * (max_depth + 1));
+  c10::cuda::CUDAGuard guard(target_ids.device());
+  chk(nfb::accept_greedy_tree(static_cast<const int*>(target_ids.data_ptr()),
+                              static_cast<const int*>(node_tok.data_ptr()), static_cast<const int*>(parent.data_ptr()),
+                              B, N, static_cast<int>(max_depth), static_cast<int*>(n_accepted.data_ptr()),
+                              static_cast<int*>(out_tokens.data_ptr()), static_cast<int*>(out_nodes.data_ptr()),
+                              cur_stream()));
+}
+
+}  // namespace
+
+TORCH_LIBRARY(nfb200, m) {
+  m.def("gemm_bf16(Tensor x, Tensor w, Tensor? out, int epi, Tensor? resid, Tensor? bias, Tensor? partial, int splits, Tensor? status, bool pdl) -> ()", &gemm_bf16);
+  m.def("gemm_pick_splits(int T, int N, int K, int epi) -> int", &gemm_pick_splits);
+  m.def("add_rmsnorm(Tensor? partial, int splits, Tensor? delta, Tensor? resid_in, Tensor? resid_out, Tensor? norm_w, Tensor? normed, int T, int N, float eps, bool unit_offset, bool pdl) -> ()", &add_rmsnorm);
+  m.def("embed_gather(Tensor ids, Tensor table, Tensor out, bool pdl) -> ()", &embed_gather);
+  m.def("attn_prep(Tensor proj, int q_off, int k_off, int v_off, int n_q_heads, int n_kv_heads, int head_dim, Tensor? q_norm_w, Tensor? k_norm_w, float eps, bool unit_offset, int rot_dim, Tensor inv_freq, float attn_factor, Tensor rope_pos, Tensor token_seq, Tensor cache_pos, Tensor block_table, Tensor q_out, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, bool pdl) -> ()", &attn_prep);
+  m.def("paged_attention(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, int split_keys, int n_splits, Tensor part_o, Tensor part_ml, Tensor? gate, Tensor out, Tensor? tree_mask, Tensor? tree_base, bool pdl) -> ()", &paged_attention);
+  m.def("causal_conv1d_silu(Tensor x, int c_off, int C, Tensor w, Tensor cu_seqlens, Tensor token_seq, Tensor state_slot, Tensor conv_state, Tensor out, bool update_state, bool pdl) -> ()", &causal_conv1d_silu);
+  m.def("gdn_recurrent(Tensor qkv, int q_off, int k_off, int v_off, Tensor proj, int z_off, int a_off, int b_off, int n_qk_heads, int n_v_heads, Tensor A_log, Tensor dt_bias, Tensor norm_w, float eps, Tensor cu_seqlens, Tensor state_slot, Tensor state, bool write_state, Tensor out, bool pdl) -> ()", &gdn_recurrent);
+  m.def("argmax_rows(Tensor logits, Tensor out, bool pdl) -> ()", &argmax_rows);
+  m.def("sample_rows(Tensor logits, Tensor? temperature, Tensor? top_k, Tensor? top_p, Tensor? min_p, Tensor? presence, Tensor? frequency, Tensor? token_counts, Tensor? seeds, Tensor? positions, int purpose, Tensor out, Tensor? out_prob) -> ()", &sample_rows);
+  m.def("accept_greedy_chain(Tensor target_ids, Tensor draft_ids, Tensor n_accepted, Tensor out_tokens) -> ()", &accept_greedy_chain);
+  m.def("accept_greedy_tree(Tensor target_ids, Tensor node_tok, Tensor parent, int max_depth, Tensor n_accepted, Tensor out_tokens, Tensor out_nodes) -> ()", &accept_greedy_tree);
+}

@@ -1,0 +1,305 @@
+"""Hybrid GDN / gated-GQA decoder forward pass on the native kernels.
+
+The math is the reference's layer schedule
+(src/targets/qwen3_6/impl/runtime/text_context_impl.h: attn_mix :1283-1468,
+gdn_mix :1470-1607, mlp_tail :1609-1618, run_layers :1830-2031) but the
+structure is B200-first: one ragged token batch per step (prefill chunks and
+decode rows use the same kernels), every GEMM is the tcgen05 weight-stationary
+kernel with a fused epilogue, the residual add + split-K reduction + next
+RMSNorm is one row kernel, and all buffers are preallocated so a decode step
+can be captured once in a CUDA graph.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import torch
+
+from .._lib import StatusWord, load_native
+from ..ops.reference import rope_inv_freq
+from ..runtime.kv_cache import GdnStatePool, PagedKvCache
+from .config import ModelConfig
+
+EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU, EPI_PARTIAL = 0, 1, 2, 3
+MAX_SPLITS = 8
+
+
+@dataclass
+class StepBatch:
+    """Device-side description of one ragged step (all int32)."""
+    ids: torch.Tensor          # [T]
+    token_seq: torch.Tensor    # [T] sequence index inside this step (row of cu_seqlens / state_slot)
+    table_row: torch.Tensor    # [T] row of the KV block table for each token
+    cache_pos: torch.Tensor    # [T] position in the sequence's KV cache
+    rope_pos: torch.Tensor     # [T] or [T, 3]
+    kv_len: torch.Tensor       # [T] visible keys per token (cache_pos + 1)
+    cu_seqlens: torch.Tensor   # [B + 1]
+    state_slot: torch.Tensor   # [B] GDN state slot per sequence
+    logit_rows: torch.Tensor   # [R] token indices whose logits are needed
+    max_kv_len: int            # host copy, picks the attention split geometry
+    n_tokens: int
+    n_seqs: int
+
+
+class Workspace:
+    """Activation buffers for up to `max_tokens` tokens; addresses are stable across steps."""
+
+    def __init__(self, cfg: ModelConfig, max_tokens: int, max_logit_rows: int, device, max_splits_attn: int = 64,
+                 shard: Optional["ShardGeometry"] = None):
+        g = shard or ShardGeometry.full(cfg)
+        bf, dev = torch.bfloat16, device
+        T, h = max_tokens, cfg.hidden
+        self.max_tokens = T
+        self.x = torch.empty((T, h), dtype=bf, device=dev)         # residual stream
+        self.normed = torch.empty((T, h), dtype=bf, device=dev)
+        wide = max(g.attn_in_dim, g.gdn_in_dim)
+        self.proj = torch.empty((T, wide), dtype=bf, device=dev)
+        self.q = torch.empty((T, g.n_q_heads * cfg.head_dim), dtype=bf, device=dev)
+        self.mix_attn = torch.empty((T, g.n_q_heads * cfg.head_dim), dtype=bf, device=dev)
+        self.mix_gdn = torch.empty((T, g.gdn_v_dim), dtype=bf, device=dev)
+        self.conv = torch.empty((T, g.gdn_conv_dim), dtype=bf, device=dev)
+        inter = g.ffn_inter if cfg.moe is None else max(cfg.moe.expert_inter, cfg.moe.shared_inter)
+        self.act = torch.empty((T, max(inter, 8)), dtype=bf, device=dev)
+        self.delta = torch.empty((T, h), dtype=bf, device=dev)
+        self.partial = torch.empty((MAX_SPLITS * min(T, 256) * h,), dtype=torch.float32, device=dev)
+        self.max_splits_attn = max_splits_attn
+        # split-KV partials: capacity in (query token x split) rows
+        self.part_rows = max(min(T, 256) * max_splits_attn, min(T, 4096))
+        self.part_o = torch.empty((self.part_rows * g.n_q_heads * cfg.head_dim,), dtype=torch.float32, device=dev)
+        self.part_ml = torch.empty((self.part_rows * g.n_q_heads * 2,), dtype=torch.float32, device=dev)
+        self.logits = torch.empty((max_logit_rows, g.vocab_rows), dtype=bf, device=dev)
+        self.head_in = torch.empty((max_logit_rows, h), dtype=bf, device=dev)
+        self.next_ids = torch.empty((max_logit_rows,), dtype=torch.int32, device=dev)
+
+
+@dataclass
+class ShardGeometry:
+    """Per-rank sizes of a tensor-parallel shard (world 1 = the whole model)."""
+    world: int
+    rank: int
+    n_q_heads: int
+    n_kv_heads: int
+    gdn_qk_heads: int
+    gdn_v_heads: int
+    ffn_inter: int
+    vocab_rows: int
+    head_dim: int
+    gdn_head_dim: int
+
+    @staticmethod
+    def full(cfg: ModelConfig) -> "ShardGeometry":
+        return ShardGeometry(1, 0, cfg.n_q_heads, cfg.n_kv_heads, cfg.gdn_qk_heads, cfg.gdn_v_heads, cfg.ffn_inter,
+                             cfg.vocab, cfg.head_dim, cfg.gdn_head_dim)
+
+    @property
+    def attn_in_dim(self) -> int:
+        return (2 * self.n_q_heads + 2 * self.n_kv_heads) * self.head_dim
+
+    @property
+    def gdn_qk_dim(self) -> int:
+        return self.gdn_qk_heads * self.gdn_head_dim
+
+    @property
+    def gdn_v_dim(self) -> int:
+        return self.gdn_v_heads * self.gdn_head_dim
+
+    @property
+    def gdn_conv_dim(self) -> int:
+        return 2 * self.gdn_qk_dim + self.gdn_v_dim
+
+    @property
+    def gdn_in_dim(self) -> int:
+        return self.gdn_conv_dim + self.gdn_v_dim + 2 * self.gdn_v_heads
+
+
+def pick_attention_split(max_kv_len: int, n_work: int, sm_count: int = 148, max_splits: int = 64) -> tuple[int, int]:
+    """Keys per split (multiple of 128) and split count for `n_work` (query, kv-head) items.
+
+    Aim for about two waves of CTAs; the split size only depends on the context
+    bucket, so decode and verify of the same position use the same ranges."""
+    bucket = 128
+    while bucket < max_kv_len:
+        bucket *= 2
+    want = max(1, (2 * sm_count + n_work - 1) // n_work)
+    split = max(128, bucket // want)
+    split = 1 << (split.bit_length() - 1)          # power of two >= 128
+    while (bucket + split - 1) // split > max_splits:
+        split *= 2
+    n_splits = (max_kv_len + split - 1) // split
+    return split, max(1, n_splits)
+
+
+class LaunchCounter:
+    """Proxy over torch.ops.nfb200 that counts the CUDA kernels each call launches."""
+
+    KERNELS = {"paged_attention": 2}
+
+    def __init__(self, ops):
+        self._ops = ops
+        self.count = 0
+        self.launches_last_forward = 0
+        self._cache = {}
+
+    def __getattr__(self, name):
+        fn = self._cache.get(name)
+        if fn is None:
+            raw = getattr(self._ops, name)
+            if name in ("gemm_pick_splits",):
+                fn = raw
+            elif name == "causal_conv1d_silu":
+                def fn(*a, _raw=raw):
+                    self.count += 2 if a[9] else 1  # + history roll when update_state
+                    return _raw(*a)
+            else:
+                k = self.KERNELS.get(name, 1)
+
+                def fn(*a, _raw=raw, _k=k):
+                    self.count += _k
+                    return _raw(*a)
+            self._cache[name] = fn
+        return fn
+
+
+class HybridModel:
+    def __init__(self, cfg: ModelConfig, weights: Dict[str, torch.Tensor], device, pdl: bool = False,
+                 shard: Optional[ShardGeometry] = None, prefix: str = "text"):
+        self.cfg = cfg
+        self.w = weights
+        self.device = torch.device(device)
+        self.ops = LaunchCounter(load_native())
+        self.status = StatusWord(self.device)
+        self.pdl = pdl
+        self.g = shard or ShardGeometry.full(cfg)
+        self.prefix = prefix
+        self.inv_freq = rope_inv_freq(cfg.rot_dim, cfg.rope_theta).to(self.device)
+        self.sm_scale = 1.0 / math.sqrt(cfg.head_dim)
+        self.comm = None  # tensor-parallel communicator (parallel.tp), None on one GPU
+        # layer index -> index among attention / GDN layers
+        self._attn_idx = {l: i for i, l in enumerate(cfg.attn_layers)}
+        self._gdn_idx = {l: i for i, l in enumerate(cfg.gdn_layers)}
+
+    # ------------------------------------------------------------------ GEMM helpers
+    def _gemm(self, x, w, out, epi=EPI_STORE, resid=None):
+        self.ops.gemm_bf16(x, w, out, epi, resid, None, None, 1, self.status.tensor, self.pdl)
+
+    def _gemm_to_residual(self, ws: Workspace, a, w, T: int, norm_w, normed_out):
+        """x += a @ w^T ; normed_out = rmsnorm(x) * (1 + norm_w).  x is ws.x[:T] (in place)."""
+        cfg, ops = self.cfg, self.ops
+        x = ws.x[:T]
+        N, K = w.shape
+        splits = int(ops.gemm_pick_splits(T, N, K, EPI_PARTIAL)) if T <= 256 else 1
+        if self.comm is not None:
+            # row-parallel: partial sums live on every rank; the communicator reduces them
+            self.comm.gemm_reduce_residual(self, ws, a, w, T, norm_w, normed_out, splits)
+            return
+        if splits > 1:
+            ops.gemm_bf16(a, w, None, EPI_PARTIAL, None, None, ws.partial, splits, self.status.tensor, self.pdl)
+            ops.add_rmsnorm(ws.partial, splits, None, x, x, norm_w, normed_out, T, N, cfg.rms_eps, True, self.pdl)
+        else:
+            ops.gemm_bf16(a, w, x, EPI_RESIDUAL, x, None, None, 1, self.status.tensor, self.pdl)
+            ops.add_rmsnorm(None, 0, None, x, None, norm_w, normed_out, T, N, cfg.rms_eps, True, self.pdl)
+
+    # ------------------------------------------------------------------ layers
+    def _attn_layer(self, ws: Workspace, b: StepBatch, kv: PagedKvCache, layer: int, T: int, prefix: str,
+                    kv_index: int):
+        cfg, g, ops = self.cfg, self.g, self.ops
+        D = cfg.head_dim
+        w_in = self.w[f"{prefix}/attn/in_proj"]
+        proj = ws.proj[:T, : w_in.shape[0]]
+        self._gemm(ws.normed[:T], w_in, proj)
+        q_dim, kv_dim = g.n_q_heads * D, g.n_kv_heads * D
+        planes = kv.layers[kv_index]
+        q = ws.q[:T]
+        ops.attn_prep(proj, 0, q_dim, q_dim + kv_dim + q_dim, g.n_q_heads, g.n_kv_heads, D,
+                      self.w[f"{prefix}/attn/q_norm"], self.w[f"{prefix}/attn/k_norm"], cfg.rms_eps, True,
+                      cfg.rot_dim, self.inv_freq, 1.0, b.rope_pos, b.table_row, b.cache_pos, kv.table, q,
+                      planes.k_codes, planes.v_codes, planes.k_scales, planes.v_scales, kv.page_size, planes.fmt,
+                      planes.group, self.pdl)
+        gate = proj[:, q_dim + kv_dim: q_dim + kv_dim + q_dim]
+        out = ws.mix_attn[:T]
+        split, n_splits = pick_attention_split(b.max_kv_len, T * g.n_kv_heads, max_splits=ws.max_splits_attn)
+        chunk = max(1, ws.part_rows // n_splits)
+        for t0 in range(0, T, chunk):
+            t1 = min(T, t0 + chunk)
+            ops.paged_attention(q[t0:t1], g.n_q_heads, g.n_kv_heads, D, b.table_row[t0:t1], b.kv_len[t0:t1], kv.table,
+                                planes.k_codes, planes.v_codes, planes.k_scales, planes.v_scales, kv.page_size,
+                                planes.fmt, planes.group, self.sm_scale, split, n_splits, ws.part_o, ws.part_ml,
+                                gate[t0:t1], out[t0:t1], None, None, self.pdl)
+        return out, self.w[f"{prefix}/attn/o_proj"]
+
+    def _gdn_layer(self, ws: Workspace, b: StepBatch, st: GdnStatePool, layer: int, T: int, prefix: str,
+                   write_state: bool = True):
+        cfg, g, ops = self.cfg, self.g, self.ops
+        gi = self._gdn_idx[layer]
+        w_in = self.w[f"{prefix}/gdn/in_proj"]
+        proj = ws.proj[:T, : w_in.shape[0]]
+        self._gemm(ws.normed[:T], w_in, proj)
+        C = g.gdn_conv_dim
+        conv = ws.conv[:T]
+        ops.causal_conv1d_silu(proj, 0, C, self.w[f"{prefix}/gdn/conv_w"], b.cu_seqlens, b.token_seq, b.state_slot,
+                               st.conv[gi], conv, write_state, self.pdl)
+        qk = g.gdn_qk_dim
+        out = ws.mix_gdn[:T]
+        ops.gdn_recurrent(conv, 0, qk, 2 * qk, proj, C, C + g.gdn_v_dim, C + g.gdn_v_dim + g.gdn_v_heads,
+                          g.gdn_qk_heads, g.gdn_v_heads, self.w[f"{prefix}/gdn/A_log"], self.w[f"{prefix}/gdn/dt_bias"],
+                          self.w[f"{prefix}/gdn/norm"], cfg.rms_eps, b.cu_seqlens, b.state_slot, st.ssm[gi],
+                          write_state, out, self.pdl)
+        return out, self.w[f"{prefix}/gdn/out_proj"]
+
+    def _mlp(self, ws: Workspace, T: int, prefix: str, next_norm_w, normed_out):
+        w_gu = self.w[f"{prefix}/mlp/gate_up"]
+        act = ws.act[:T, : w_gu.shape[0] // 2]
+        self._gemm(ws.normed[:T], w_gu, act, EPI_SWIGLU)
+        self._gemm_to_residual(ws, act, self.w[f"{prefix}/mlp/down"], T, next_norm_w, normed_out)
+
+    # ------------------------------------------------------------------ forward
+    def forward_hidden(self, ws: Workspace, b: StepBatch, kv: PagedKvCache, st: GdnStatePool,
+                       write_state: bool = True) -> torch.Tensor:
+        """Runs all layers; returns the final-normed hidden states [T, hidden] (ws.normed)."""
+        cfg, ops = self.cfg, self.ops
+        T = b.n_tokens
+        if T > ws.max_tokens:
+            raise ValueError(f"step of {T} tokens exceeds the workspace ({ws.max_tokens})")
+        x = ws.x[:T]
+        ops.embed_gather(b.ids, self.w[f"{self.prefix}/embed"], x, self.pdl)
+        first = f"{self.prefix}/layers/0/input_norm"
+        ops.add_rmsnorm(None, 0, None, x, None, self.w[first], ws.normed[:T], T, cfg.hidden, cfg.rms_eps, True, self.pdl)
+        for layer in range(cfg.n_layers):
+            p = f"{self.prefix}/layers/{layer}"
+            if cfg.is_full_attn(layer):
+                mix, w_out = self._attn_layer(ws, b, kv, layer, T, p, self._attn_idx[layer])
+            else:
+                mix, w_out = self._gdn_layer(ws, b, st, layer, T, p, write_state)
+            self._gemm_to_residual(ws, mix, w_out, T, self.w[f"{p}/post_norm"], ws.normed[:T])
+            nxt = (self.w[f"{self.prefix}/layers/{layer + 1}/input_norm"] if layer + 1 < cfg.n_layers
+                   else self.w[f"{self.prefix}/final_norm"])
+            if cfg.moe is None:
+                self._mlp(ws, T, p, nxt, ws.normed[:T])
+            else:
+                self.moe.forward(self, ws, T, p, nxt, ws.normed[:T])
+        return ws.normed[:T]
+
+    def logits(self, ws: Workspace, b: StepBatch, hidden: torch.Tensor) -> torch.Tensor:
+        R = b.logit_rows.numel()
+        head_in = ws.head_in[:R]
+        if R == hidden.shape[0]:
+            head_in = hidden  # decode: every row is a logit row, in order
+        else:
+            torch.index_select(hidden, 0, b.logit_rows.long(), out=head_in)
+        out = ws.logits[:R]
+        self._gemm(head_in, self.w[f"{self.prefix}/lm_head"], out)
+        return out
+
+    def forward_greedy(self, ws: Workspace, b: StepBatch, kv: PagedKvCache, st: GdnStatePool) -> torch.Tensor:
+        """One step ending in arg-max token ids for `b.logit_rows` (int32 [R], ws.next_ids)."""
+        start = self.ops.count
+        hidden = self.forward_hidden(ws, b, kv, st)
+        if b.logit_rows.numel() == 0:
+            return ws.next_ids[:0]
+        lg = self.logits(ws, b, hidden)
+        out = ws.next_ids[: lg.shape[0]]
+        self.ops.argmax_rows(lg, out, self.pdl)
+        self.ops.launches_last_forward = self.ops.count - start
+        return out

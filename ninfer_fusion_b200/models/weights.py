@@ -1,0 +1,87 @@
+"""Weight inventory of a hybrid decoder and random initialisation.
+
+Tensor names and fused row orders follow the reference's artifact inventory
+(docs/maintainer/qwen3.8-27b-artifact.md:71-127,194-284): the attention input
+projection is one parent with rows ``[query, key, output_gate, value]``, the GDN
+input projection ``[q, k, v, z]`` followed by the ``[A, B]`` gating rows, the MLP
+parent ``[gate, up]``.  Fusing the tiny A/B projection into the GDN parent is a
+load-time concatenation (the container keeps them as separate objects).
+"""
+from __future__ import annotations
+
+from typing import Dict, Iterator, Tuple
+
+import torch
+
+from .config import ModelConfig
+
+
+def weight_shapes(cfg: ModelConfig, with_mtp: bool = False) -> Iterator[Tuple[str, tuple, torch.dtype]]:
+    h = cfg.hidden
+    yield "text/embed", (cfg.vocab, h), torch.bfloat16
+    yield "text/lm_head", (cfg.vocab, h), torch.bfloat16
+    yield "text/final_norm", (h,), torch.bfloat16
+    layer_sets = [("text/layers", cfg.n_layers, None)]
+    if with_mtp:
+        layer_sets.append(("mtp/layers", cfg.mtp_layers, "attn"))
+        yield "mtp/fc", (h, 2 * h), torch.bfloat16          # [hidden ; embedding] -> hidden
+        yield "mtp/pre_fc_norm_hidden", (h,), torch.bfloat16
+        yield "mtp/pre_fc_norm_embedding", (h,), torch.bfloat16
+        yield "mtp/final_norm", (h,), torch.bfloat16
+    for prefix, n, force in layer_sets:
+        for i in range(n):
+            p = f"{prefix}/{i}"
+            yield f"{p}/input_norm", (h,), torch.bfloat16
+            yield f"{p}/post_norm", (h,), torch.bfloat16
+            if force == "attn" or (force is None and cfg.is_full_attn(i)):
+                yield f"{p}/attn/in_proj", (cfg.attn_in_dim, h), torch.bfloat16
+                yield f"{p}/attn/q_norm", (cfg.head_dim,), torch.bfloat16
+                yield f"{p}/attn/k_norm", (cfg.head_dim,), torch.bfloat16
+                yield f"{p}/attn/o_proj", (h, cfg.q_dim), torch.bfloat16
+            else:
+                yield f"{p}/gdn/in_proj", (cfg.gdn_in_dim, h), torch.bfloat16
+                yield f"{p}/gdn/conv_w", (cfg.gdn_conv_dim, cfg.conv_kernel), torch.bfloat16
+                yield f"{p}/gdn/A_log", (cfg.gdn_v_heads,), torch.float32
+                yield f"{p}/gdn/dt_bias", (cfg.gdn_v_heads,), torch.float32
+                yield f"{p}/gdn/norm", (cfg.gdn_head_dim,), torch.bfloat16
+                yield f"{p}/gdn/out_proj", (h, cfg.gdn_v_dim), torch.bfloat16
+            if cfg.moe is None:
+                yield f"{p}/mlp/gate_up", (2 * cfg.ffn_inter, h), torch.bfloat16
+                yield f"{p}/mlp/down", (h, cfg.ffn_inter), torch.bfloat16
+            else:
+                m = cfg.moe
+                yield f"{p}/moe/router", (m.n_experts + 1, h), torch.bfloat16  # last row: shared-expert gate
+                yield f"{p}/moe/experts_gate_up", (m.n_experts, 2 * m.expert_inter, h), torch.bfloat16
+                yield f"{p}/moe/experts_down", (m.n_experts, h, m.expert_inter), torch.bfloat16
+                yield f"{p}/moe/shared_gate_up", (2 * m.shared_inter, h), torch.bfloat16
+                yield f"{p}/moe/shared_down", (h, m.shared_inter), torch.bfloat16
+
+
+def random_weights(cfg: ModelConfig, device, seed: int = 0, with_mtp: bool = False,
+                   std: float = 0.02) -> Dict[str, torch.Tensor]:
+    """Random-init weights of the architecture (there are no checkpoints on the box)."""
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    out: Dict[str, torch.Tensor] = {}
+    for name, shape, dt in weight_shapes(cfg, with_mtp):
+        t = torch.empty(shape, dtype=dt, device=device)
+        leaf = name.rsplit("/", 1)[-1]
+        if leaf.endswith("norm") or leaf in ("q_norm", "k_norm", "pre_fc_norm_hidden", "pre_fc_norm_embedding"):
+            # unit-offset norms store w - 1; the GDN head norm stores w
+            t.normal_(0.0, 0.02, generator=gen)
+            if name.endswith("gdn/norm"):
+                t.add_(1.0)
+        elif leaf == "A_log":
+            t.uniform_(-1.0, 1.5, generator=gen)
+        elif leaf == "dt_bias":
+            t.uniform_(-2.0, 1.0, generator=gen)
+        elif leaf == "conv_w":
+            t.normal_(0.0, 0.3, generator=gen)
+        else:
+            t.normal_(0.0, std, generator=gen)
+        out[name] = t
+    return out
+
+
+def total_bytes(weights: Dict[str, torch.Tensor]) -> int:
+    return sum(t.numel() * t.element_size() for t in weights.values())

@@ -1,0 +1,233 @@
+"""Paged KV cache and GDN state pools.
+
+One page id addresses the same token range in every full-attention layer; each
+layer owns its planes and may use its own codec (bf16 / fp8-row / int8-group /
+nvfp4), which is what per-layer KV policies select.  Page size and the int8
+group are parameters (the reference fixes P = 64 and G = 64,
+src/core/paged_kv_cache.h:17).  Block tables are an int32 matrix
+``[rows, max_pages]`` mirrored in pinned host memory so a decode round uploads
+only what changed.
+
+The GDN pools hold, per linear-attention layer, the 3-column conv history and
+the fp32 recurrent state per sequence slot (reference:
+src/core/linear_attention_state.{h,cpp}; 2C slots = current + turn checkpoint).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..models.config import ModelConfig
+from ..ops.reference import KV_BF16, KV_FORMAT_NAMES, KV_FP8_ROW, KV_INT8_GROUP, KV_NVFP4
+
+
+def kv_row_bytes(fmt: int, head_dim: int) -> int:
+    return 2 * head_dim if fmt == KV_BF16 else (head_dim // 2 if fmt == KV_NVFP4 else head_dim)
+
+
+def kv_scale_bytes(fmt: int, head_dim: int, group: int) -> int:
+    if fmt == KV_FP8_ROW:
+        return 2
+    if fmt == KV_INT8_GROUP:
+        return 2 * (head_dim // group)
+    if fmt == KV_NVFP4:
+        return head_dim // 16
+    return 0
+
+
+@dataclass
+class KvLayerPlanes:
+    fmt: int
+    group: int
+    k_codes: torch.Tensor
+    v_codes: torch.Tensor
+    k_scales: Optional[torch.Tensor]
+    v_scales: Optional[torch.Tensor]
+
+    def bytes(self) -> int:
+        n = self.k_codes.numel() + self.v_codes.numel()
+        if self.k_scales is not None:
+            n += self.k_scales.numel() + self.v_scales.numel()
+        return n
+
+
+class PagePool:
+    """Free-list page allocator with per-row page lists (host side)."""
+
+    def __init__(self, n_pages: int):
+        self.n_pages = n_pages
+        self._free: List[int] = list(range(n_pages - 1, -1, -1))
+        self.refcount = [0] * n_pages
+
+    @property
+    def free_pages(self) -> int:
+        return len(self._free)
+
+    def alloc(self) -> int:
+        if not self._free:
+            raise MemoryError("KV page pool exhausted")
+        p = self._free.pop()
+        self.refcount[p] = 1
+        return p
+
+    def retain(self, page: int) -> None:
+        self.refcount[page] += 1
+
+    def release(self, page: int) -> None:
+        self.refcount[page] -= 1
+        if self.refcount[page] == 0:
+            self._free.append(page)
+        elif self.refcount[page] < 0:
+            raise RuntimeError(f"page {page} released twice")
+
+
+class PagedKvCache:
+    def __init__(self, cfg: ModelConfig, n_pages: int, page_size: int, max_rows: int, max_pages_per_row: int,
+                 device, formats: Sequence[str] | str = "bf16", int8_group: int = 64,
+                 n_kv_heads: Optional[int] = None, n_layers: Optional[int] = None):
+        self.cfg = cfg
+        self.page_size = page_size
+        self.n_pages = n_pages
+        self.device = torch.device(device)
+        self.n_kv_heads = n_kv_heads if n_kv_heads is not None else cfg.n_kv_heads
+        n_attn = n_layers if n_layers is not None else len(cfg.attn_layers)
+        if isinstance(formats, str):
+            formats = [formats] * n_attn
+        if len(formats) != n_attn:
+            raise ValueError(f"need one KV format per full-attention layer ({n_attn}), got {len(formats)}")
+        D = cfg.head_dim
+        self.layers: List[KvLayerPlanes] = []
+        for name in formats:
+            fmt = KV_FORMAT_NAMES[name]
+            group = int8_group if fmt == KV_INT8_GROUP else (16 if fmt == KV_NVFP4 else D)
+            rb, sb = kv_row_bytes(fmt, D), kv_scale_bytes(fmt, D, group)
+            shape = (n_pages, self.n_kv_heads, page_size, rb)
+            k = torch.zeros(shape, dtype=torch.uint8, device=self.device)
+            v = torch.zeros(shape, dtype=torch.uint8, device=self.device)
+            ks = vs = None
+            if sb:
+                ks = torch.zeros((n_pages, self.n_kv_heads, page_size, sb), dtype=torch.uint8, device=self.device)
+                vs = torch.zeros_like(ks)
+            self.layers.append(KvLayerPlanes(fmt, group, k, v, ks, vs))
+        self.pool = PagePool(n_pages)
+        self.max_rows = max_rows
+        self.max_pages_per_row = max_pages_per_row
+        pin = self.device.type == "cuda"
+        self.table_host = torch.full((max_rows, max_pages_per_row), -1, dtype=torch.int32, pin_memory=pin)
+        self.table = torch.full((max_rows, max_pages_per_row), -1, dtype=torch.int32, device=self.device)
+        self.row_pages: Dict[int, List[int]] = {}
+        self._dirty_rows: set[int] = set()
+
+    # ---- capacity ----
+    def bytes_per_token(self) -> float:
+        return sum(l.bytes() for l in self.layers) / (self.n_pages * self.page_size)
+
+    def total_bytes(self) -> int:
+        return sum(l.bytes() for l in self.layers)
+
+    # ---- mapping ----
+    def ensure(self, row: int, n_tokens: int) -> None:
+        """Make sure `row` has pages for positions [0, n_tokens)."""
+        pages = self.row_pages.setdefault(row, [])
+        need = (n_tokens + self.page_size - 1) // self.page_size
+        if need > self.max_pages_per_row:
+            raise MemoryError(f"row {row}: {n_tokens} tokens exceed the block-table width")
+        while len(pages) < need:
+            p = self.pool.alloc()
+            self.table_host[row, len(pages)] = p
+            pages.append(p)
+            self._dirty_rows.add(row)
+
+    def trim(self, row: int, n_tokens: int) -> None:
+        """Drop pages that lie wholly beyond n_tokens (speculative rollback)."""
+        pages = self.row_pages.get(row, [])
+        keep = (n_tokens + self.page_size - 1) // self.page_size
+        while len(pages) > keep:
+            p = pages.pop()
+            self.table_host[row, len(pages)] = -1
+            self.pool.release(p)
+            self._dirty_rows.add(row)
+
+    def free_row(self, row: int) -> None:
+        for p in self.row_pages.pop(row, []):
+            self.pool.release(p)
+        self.table_host[row].fill_(-1)
+        self._dirty_rows.add(row)
+
+    def fork_row(self, src: int, dst: int, n_tokens: int) -> None:
+        """Share src's full pages with dst (prefix reuse); a partial tail page is copied."""
+        self.free_row(dst)
+        full = n_tokens // self.page_size
+        pages = self.row_pages.setdefault(dst, [])
+        for i in range(full):
+            p = self.row_pages[src][i]
+            self.pool.retain(p)
+            pages.append(p)
+            self.table_host[dst, i] = p
+        if n_tokens % self.page_size:
+            p_src = self.row_pages[src][full]
+            p_new = self.pool.alloc()
+            for l in self.layers:
+                l.k_codes[p_new].copy_(l.k_codes[p_src])
+                l.v_codes[p_new].copy_(l.v_codes[p_src])
+                if l.k_scales is not None:
+                    l.k_scales[p_new].copy_(l.k_scales[p_src])
+                    l.v_scales[p_new].copy_(l.v_scales[p_src])
+            pages.append(p_new)
+            self.table_host[dst, full] = p_new
+        self._dirty_rows.add(dst)
+
+    def publish(self) -> None:
+        """Upload dirty block-table rows to the device."""
+        if not self._dirty_rows:
+            return
+        if len(self._dirty_rows) > 8:
+            self.table.copy_(self.table_host, non_blocking=True)
+        else:
+            for r in self._dirty_rows:
+                self.table[r].copy_(self.table_host[r], non_blocking=True)
+        self._dirty_rows.clear()
+
+
+class GdnStatePool:
+    """Conv history + fp32 recurrent state for every GDN layer, `n_slots` sequence slots."""
+
+    def __init__(self, cfg: ModelConfig, n_slots: int, device, n_qk_heads: Optional[int] = None,
+                 n_v_heads: Optional[int] = None, n_layers: Optional[int] = None):
+        self.cfg = cfg
+        self.n_slots = n_slots
+        hk = n_qk_heads if n_qk_heads is not None else cfg.gdn_qk_heads
+        hv = n_v_heads if n_v_heads is not None else cfg.gdn_v_heads
+        n_gdn = n_layers if n_layers is not None else len(cfg.gdn_layers)
+        d = cfg.gdn_head_dim
+        self.conv_dim = (2 * hk + hv) * d
+        self.conv = [torch.zeros((n_slots, 3, self.conv_dim), dtype=torch.bfloat16, device=device)
+                     for _ in range(n_gdn)]
+        self.ssm = [torch.zeros((n_slots, hv, d, d), dtype=torch.float32, device=device) for _ in range(n_gdn)]
+        self._free = list(range(n_slots - 1, -1, -1))
+
+    def alloc(self) -> int:
+        if not self._free:
+            raise MemoryError("GDN state slots exhausted")
+        s = self._free.pop()
+        self.reset(s)
+        return s
+
+    def release(self, slot: int) -> None:
+        self._free.append(slot)
+
+    def reset(self, slot: int) -> None:
+        for c, s in zip(self.conv, self.ssm):
+            c[slot].zero_()
+            s[slot].zero_()
+
+    def copy_slot(self, src: int, dst: int) -> None:
+        """Checkpoint / fork a sequence's recurrent state."""
+        for c, s in zip(self.conv, self.ssm):
+            c[dst].copy_(c[src])
+            s[dst].copy_(s[src])
+
+    def total_bytes(self) -> int:
+        return sum(c.numel() * 2 + s.numel() * 4 for c, s in zip(self.conv, self.ssm))

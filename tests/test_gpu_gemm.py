@@ -1,0 +1,109 @@
+"""tcgen05 GEMM vs an fp32 torch matmul of the same bf16 inputs."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU, EPI_PARTIAL = 0, 1, 2, 3
+
+
+def _mk(T, N, K, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(T, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    return x, w
+
+
+def _check(out, ref, tol=2e-2):
+    err = (out.float() - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    assert err / scale < tol, f"max err {err} vs scale {scale}"
+
+
+@pytest.mark.parametrize("T", [1, 7, 16, 32, 48, 64, 100, 128, 300, 513])
+@pytest.mark.parametrize("N,K", [(256, 512), (384, 192), (5120, 1024)])
+def test_gemm_store(ops, status, T, N, K):
+    x, w = _mk(T, N, K)
+    out = torch.full((T, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.gemm_bf16(x, w, out, EPI_STORE, None, None, None, 1, status.tensor, False)
+    _check(out, x.float() @ w.float().t())
+
+
+def test_gemm_store_ragged_n_and_k(ops, status):
+    # N not a multiple of 128, K not a multiple of 64: TMA zero-fills the tails
+    x, w = _mk(20, 16480 // 8, 200)
+    out = torch.empty((20, w.shape[0]), device="cuda", dtype=torch.bfloat16)
+    ops.gemm_bf16(x, w, out, EPI_STORE, None, None, None, 1, status.tensor, False)
+    _check(out, x.float() @ w.float().t())
+
+
+def test_gemm_strided_views_and_bias(ops, status):
+    x_full, w = _mk(33, 256, 1024)
+    x = x_full[:, :512]
+    w = w[:, :512]
+    out_full = torch.zeros((33, 512), device="cuda", dtype=torch.bfloat16)
+    out = out_full[:, 128:384]
+    bias = torch.randn(256, device="cuda")
+    ops.gemm_bf16(x, w, out, EPI_STORE, None, bias, None, 1, status.tensor, False)
+    _check(out, x.float() @ w.float().t() + bias)
+    assert out_full[:, :128].abs().max().item() == 0 and out_full[:, 384:].abs().max().item() == 0
+
+
+@pytest.mark.parametrize("T", [1, 32, 130])
+def test_gemm_residual(ops, status, T):
+    x, w = _mk(T, 512, 768)
+    resid = torch.randn(T, 512, device="cuda").to(torch.bfloat16)
+    out = resid.clone()
+    ops.gemm_bf16(x, w, out, EPI_RESIDUAL, out, None, None, 1, status.tensor, False)
+    _check(out, resid.float() + x.float() @ w.float().t())
+
+
+@pytest.mark.parametrize("T", [1, 32, 64, 257])
+@pytest.mark.parametrize("inter", [64, 192, 1024])
+def test_gemm_swiglu(ops, status, T, inter):
+    x, w = _mk(T, 2 * inter, 512)
+    out = torch.empty((T, inter), device="cuda", dtype=torch.bfloat16)
+    ops.gemm_bf16(x, w, out, EPI_SWIGLU, None, None, None, 1, status.tensor, False)
+    gu = x.float() @ w.float().t()
+    _check(out, torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:])
+
+
+@pytest.mark.parametrize("T,splits", [(1, 4), (32, 7), (64, 3)])
+def test_gemm_splitk_and_reduce(ops, status, T, splits):
+    N, K = 640, 64 * 40
+    x, w = _mk(T, N, K)
+    part = torch.full((splits * T * N,), float("nan"), device="cuda")
+    ops.gemm_bf16(x, w, None, EPI_PARTIAL, None, None, part, splits, status.tensor, False)
+    ref = x.float() @ w.float().t()
+    _check(part.view(splits, T, N).sum(0), ref, 1e-3)
+    # fused reduce + residual + rmsnorm
+    resid = torch.randn(T, N, device="cuda").to(torch.bfloat16)
+    nw = (torch.randn(N, device="cuda") * 0.1).to(torch.bfloat16)
+    r_out = torch.empty_like(resid)
+    normed = torch.empty_like(resid)
+    ops.add_rmsnorm(part, splits, None, resid, r_out, nw, normed, T, N, 1e-6, True, False)
+    xr = (resid.float() + ref).to(torch.bfloat16).float()
+    _check(r_out, xr, 1e-2)
+    nr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-6) * (1 + nw.float())
+    _check(normed, nr, 2e-2)
+
+
+def test_pick_splits_covers_k(ops):
+    for T, N, K in [(32, 5120, 17408), (32, 5120, 6144), (1, 5120, 6144), (64, 248320, 5120), (300, 5120, 6144)]:
+        s = int(ops.gemm_pick_splits(T, N, K, EPI_PARTIAL))
+        nkb = (K + 63) // 64
+        per = (nkb + s - 1) // s
+        assert 1 <= s <= 8 and (nkb + per - 1) // per == s
+
+
+def test_gemm_pdl_chain(ops, status):
+    """Back-to-back launches with programmatic dependent launch read each other's output."""
+    x, w1 = _mk(32, 512, 512)
+    _, w2 = _mk(32, 256, 512, seed=1)
+    h = torch.empty((32, 512), device="cuda", dtype=torch.bfloat16)
+    out = torch.empty((32, 256), device="cuda", dtype=torch.bfloat16)
+    for _ in range(3):
+        ops.gemm_bf16(x, w1, h, EPI_STORE, None, None, None, 1, status.tensor, True)
+        ops.gemm_bf16(h, w2, out, EPI_STORE, None, None, None, 1, status.tensor, True)
+    ref_h = (x.float() @ w1.float().t()).to(torch.bfloat16).float()
+    _check(out, ref_h @ w2.float().t())

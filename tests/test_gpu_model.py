@@ -1,0 +1,88 @@
+"""End-to-end parity of the native engine against the pure-torch reference model."""
+import pytest
+import torch
+
+from ninfer_fusion_b200.models.config import TINY_DENSE
+from ninfer_fusion_b200.models.reference_model import ReferenceModel, ReferenceSequence
+from ninfer_fusion_b200.models.weights import random_weights
+from ninfer_fusion_b200.ops import reference as R
+from ninfer_fusion_b200.runtime.batch import SeqChunk
+from ninfer_fusion_b200.runtime.generator import Generator
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(kv_format, use_graph, page_size=16, prefill_chunk=64, max_batch=4):
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cuda", seed=7, std=0.05)
+    gen = Generator(cfg, w, "cuda", max_batch=max_batch, max_context=512, kv_format=kv_format, page_size=page_size,
+                    prefill_chunk=prefill_chunk, use_graph=use_graph)
+    return cfg, w, gen
+
+
+@pytest.mark.parametrize("kv_format", ["bf16", "fp8", "int8", "nvfp4"])
+def test_prefill_hidden_matches_reference(kv_format):
+    cfg, w, gen = _setup(kv_format, use_graph=False)
+    ref = ReferenceModel(cfg, w)
+    torch.manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (37, 90)]
+    # engine: ragged chunked prefill (chunk 64 splits the second prompt)
+    gen.prefill(prompts)
+    # hidden of the last step is still in the workspace: rerun the reference and compare logits of last tokens
+    fmt = R.KV_FORMAT_NAMES[kv_format]
+    for b, p in enumerate(prompts):
+        seq = ReferenceSequence(cfg, fmt)
+        h = ref.forward(seq, torch.tensor(p))
+        ref_logits = ref.logits(h[-1:])[0]
+        # engine decode of one more token gives logits for position len(p); compare first-token choice instead
+        tok_ref = int(R.argmax_lowest(ref_logits[None])[0])
+        top2 = ref_logits.topk(2).values
+        if (top2[0] - top2[1]).item() > 0.05:  # skip near-ties
+            assert gen.last_tokens[b] == tok_ref
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_greedy_generation_matches_reference(use_graph):
+    cfg, w, gen = _setup("bf16", use_graph)
+    ref = ReferenceModel(cfg, w)
+    torch.manual_seed(1)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (21, 70, 5)]
+    n_new = 12
+    out = gen.generate(prompts, n_new)
+    agree = total = 0
+    for b, p in enumerate(prompts):
+        # teacher-forced comparison: feed the ENGINE's tokens to the reference and compare each choice
+        seq = ReferenceSequence(cfg, R.KV_BF16)
+        h = ref.forward(seq, torch.tensor(p))
+        for j in range(n_new):
+            lg = ref.logits(h[-1:])[0]
+            top2 = lg.topk(2).values
+            if (top2[0] - top2[1]).item() > 0.05:
+                total += 1
+                agree += int(int(R.argmax_lowest(lg[None])[0]) == out[b][j])
+            h = ref.forward(seq, torch.tensor([out[b][j]]))
+    assert total > 10 and agree / total >= 0.95, f"{agree}/{total}"
+
+
+def test_graph_and_eager_decode_agree():
+    cfg, w, gen_e = _setup("fp8", use_graph=False)
+    torch.manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (30, 64)]
+    a = gen_e.generate(prompts, 10)
+    gen_g = Generator(cfg, w, "cuda", max_batch=4, max_context=512, kv_format="fp8", page_size=16, prefill_chunk=64,
+                      use_graph=True)
+    b = gen_g.generate(prompts, 10)
+    assert a == b
+
+
+def test_device_loop_matches_stepwise():
+    cfg, w, gen = _setup("bf16", use_graph=True)
+    torch.manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (20, 33)]
+    ref_out = gen.generate(prompts, 9)
+    gen.prefill(prompts)
+    graph, finish = gen.decode_device_loop(8)
+    for _ in range(8):
+        graph.replay()
+    finish()
+    assert gen.last_tokens == [o[-1] for o in ref_out]

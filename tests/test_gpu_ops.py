@@ -1,0 +1,276 @@
+"""Attention / KV codec / GDN / sampling kernels vs the fp32 torch oracles."""
+import math
+
+import pytest
+import torch
+
+from ninfer_fusion_b200.ops import reference as R
+
+pytestmark = pytest.mark.gpu
+
+FORMATS = [("bf16", R.KV_BF16, 256), ("fp8", R.KV_FP8_ROW, 256), ("int8", R.KV_INT8_GROUP, 32),
+           ("int8", R.KV_INT8_GROUP, 64), ("nvfp4", R.KV_NVFP4, 16)]
+
+
+def _planes(n_pages, hkv, P, D, fmt, group):
+    rb = 2 * D if fmt == R.KV_BF16 else (D // 2 if fmt == R.KV_NVFP4 else D)
+    sb = {R.KV_BF16: 0, R.KV_FP8_ROW: 2, R.KV_INT8_GROUP: 2 * (D // group), R.KV_NVFP4: D // 16}[fmt]
+    k = torch.zeros((n_pages, hkv, P, rb), dtype=torch.uint8, device="cuda")
+    v = torch.zeros_like(k)
+    ks = vs = None
+    if sb:
+        ks = torch.zeros((n_pages, hkv, P, sb), dtype=torch.uint8, device="cuda")
+        vs = torch.zeros_like(ks)
+    return k, v, ks, vs
+
+
+@pytest.mark.parametrize("name,fmt,group", FORMATS)
+@pytest.mark.parametrize("hq,hkv,D,P", [(6, 1, 256, 16), (24, 4, 256, 64), (16, 2, 256, 64), (8, 2, 128, 32),
+                                        (3, 1, 256, 64)])
+def test_prep_append_and_paged_attention(ops, name, fmt, group, hq, hkv, D, P):
+    torch.manual_seed(1)
+    lens = [37, 256, 1000, 300]
+    B = len(lens)
+    max_pages = (max(lens) + P - 1) // P
+    n_pages = B * max_pages + 3
+    perm = torch.randperm(n_pages)[: B * max_pages].int().view(B, max_pages).cuda()  # scattered pages
+    k_codes, v_codes, k_sc, v_sc = _planes(n_pages, hkv, P, D, fmt, group)
+    theta, rot = 1e7, 64
+    inv_freq = R.rope_inv_freq(rot, theta).cuda()
+    qw = (torch.randn(D) * 0.1).to(torch.bfloat16).cuda()
+    kw = (torch.randn(D) * 0.1).to(torch.bfloat16).cuda()
+    ld = (2 * hq + 2 * hkv) * D
+    T = sum(lens)
+    proj = torch.randn(T, ld).to(torch.bfloat16)
+    # a few K outlier channels, as in the codec comparison workload
+    k_off = hq * D
+    for c in torch.randperm(D)[:4]:
+        proj[:, k_off + c] *= 8
+    proj = proj.cuda()
+    tok_seq = torch.cat([torch.full((n,), b) for b, n in enumerate(lens)]).int().cuda()
+    pos = torch.cat([torch.arange(n) for n in lens]).int().cuda()
+    q_out = torch.empty((T, hq, D), dtype=torch.bfloat16, device="cuda")
+    v_off = k_off + hkv * D + hq * D
+    ops.attn_prep(proj, 0, k_off, v_off, hq, hkv, D, qw, kw, 1e-6, True, rot, inv_freq, 1.0, pos, tok_seq, pos, perm,
+                  q_out, k_codes, v_codes, k_sc, v_sc, P, fmt, group, False)
+
+    # ---- oracle for q / k / v ----
+    pf = proj.float().cpu()
+    qr = pf[:, : hq * D].view(T, hq, D)
+    kr = pf[:, k_off:k_off + hkv * D].view(T, hkv, D)
+    vr = pf[:, v_off:v_off + hkv * D].view(T, hkv, D)
+    qn = R.bf16_round(R.rmsnorm(qr, qw.cpu(), 1e-6, True))
+    kn = R.bf16_round(R.rmsnorm(kr, kw.cpu(), 1e-6, True))
+    q_ref = R.bf16_round(R.rope_partial(qn, pos.cpu(), rot, theta))
+    k_ref = R.kv_quant_dequant(R.rope_partial(kn, pos.cpu(), rot, theta), fmt, group)
+    v_ref = R.kv_quant_dequant(vr, fmt, group)
+    assert (q_out.float().cpu() - q_ref).abs().max().item() < 0.07
+
+    # ---- decode-style attention: last token of each sequence + a mid-sequence query ----
+    q_rows, q_seq, q_len = [], [], []
+    start = 0
+    for b, n in enumerate(lens):
+        for p in {n - 1, n // 2}:
+            q_rows.append(start + p)
+            q_seq.append(b)
+            q_len.append(p + 1)
+        start += n
+    q_rows_t = torch.tensor(q_rows).cuda()
+    q = q_out[q_rows_t].contiguous()
+    Tq = q.shape[0]
+    gate = torch.randn(Tq, hq * D).to(torch.bfloat16).cuda()
+    for split_keys in (128, 512):
+        n_splits = (max(lens) + split_keys - 1) // split_keys
+        part_o = torch.empty(Tq * hq * n_splits * D, device="cuda")
+        part_ml = torch.empty(Tq * hq * n_splits * 2, device="cuda")
+        out = torch.empty((Tq, hq * D), dtype=torch.bfloat16, device="cuda")
+        ops.paged_attention(q, hq, hkv, D, torch.tensor(q_seq).int().cuda(), torch.tensor(q_len).int().cuda(), perm,
+                            k_codes, v_codes, k_sc, v_sc, P, fmt, group, 1 / math.sqrt(D), split_keys, n_splits,
+                            part_o, part_ml, gate, out, None, None, False)
+        start = 0
+        seq_start = [0]
+        for n in lens:
+            seq_start.append(seq_start[-1] + n)
+        for i in range(Tq):
+            b = q_seq[i]
+            ks_, vs_ = k_ref[seq_start[b]:seq_start[b + 1]], v_ref[seq_start[b]:seq_start[b + 1]]
+            o = R.gqa_attention(q[i:i + 1].float().cpu(), ks_, vs_, torch.tensor([q_len[i]]))
+            o = R.bf16_round(o).view(-1) * torch.sigmoid(gate[i].float().cpu())
+            err = (out[i].float().cpu() - o).abs().max().item()
+            assert err < 0.03, f"{name} split {split_keys} query {i}: err {err}"
+
+
+def test_paged_attention_tree_mask(ops):
+    """Verify-style masks: query j sees the prefix plus the masked tree positions."""
+    torch.manual_seed(3)
+    hq, hkv, D, P = 6, 1, 256, 16
+    L, W = 70, 5
+    n_pages = 8
+    table = torch.arange(n_pages).int().view(1, -1).cuda()
+    k = torch.randn(L + W, hkv, D)
+    v = torch.randn(L + W, hkv, D)
+    k_codes, v_codes, _, _ = _planes(n_pages, hkv, P, D, R.KV_BF16, D)
+    kb = k.to(torch.bfloat16).view(-1, hkv, D)
+    for t in range(L + W):
+        k_codes[t // P, 0, t % P] = kb[t, 0].view(torch.uint8).cuda()
+        v_codes[t // P, 0, t % P] = v.to(torch.bfloat16)[t, 0].view(torch.uint8).cuda()
+    q = torch.randn(W, hq, D).to(torch.bfloat16).cuda()
+    # tree: node j sees nodes in anc[j]
+    anc = [[0], [0, 1], [0, 2], [0, 1, 3], [0, 2, 4]]
+    masks = torch.tensor([sum(1 << a for a in row) for row in anc], dtype=torch.long).cuda()
+    base = torch.full((W,), L, dtype=torch.int32).cuda()
+    out = torch.empty((W, hq * D), dtype=torch.bfloat16, device="cuda")
+    part_o = torch.empty(W * hq * D, device="cuda")
+    part_ml = torch.empty(W * hq * 2, device="cuda")
+    ops.paged_attention(q, hq, hkv, D, torch.zeros(W).int().cuda(), torch.full((W,), L + W).int().cuda(), table,
+                        k_codes, v_codes, None, None, P, R.KV_BF16, D, 1 / 16, 128, 1, part_o, part_ml, None, out,
+                        masks, base, False)
+    vis = torch.zeros(W, L + W, dtype=torch.bool)
+    vis[:, :L] = True
+    for j, row in enumerate(anc):
+        for a in row:
+            vis[j, L + a] = True
+    ref = R.gqa_attention(q.float().cpu(), R.bf16_round(k), R.bf16_round(v), None, 1 / 16, vis).view(W, -1)
+    assert (out.float().cpu() - ref).abs().max().item() < 0.02
+
+
+@pytest.mark.parametrize("lens", [[1, 1, 1], [5, 1, 17], [64, 3]])
+def test_conv_and_gdn_recurrent(ops, lens):
+    torch.manual_seed(2)
+    hk, hv, d = 2, 6, 128
+    qk, vd = hk * d, hv * d
+    C = 2 * qk + vd
+    ld = C + vd + 2 * hv
+    T, B = sum(lens), len(lens)
+    proj = (torch.randn(T, ld) * 0.7).to(torch.bfloat16)
+    conv_w = (torch.randn(C, 4) * 0.3).to(torch.bfloat16)
+    A_log = torch.rand(hv) * 2 - 1
+    dt_bias = torch.rand(hv) * 2 - 1.5
+    nw = (1 + 0.1 * torch.randn(d)).to(torch.bfloat16)
+    slots = [3, 0, 2][:B]
+    n_slots = 4
+    conv_state = (torch.randn(n_slots, 3, C) * 0.5).to(torch.bfloat16)
+    ssm = torch.randn(n_slots, hv, d, d) * 0.1
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    tok_seq = torch.cat([torch.full((n,), b) for b, n in enumerate(lens)]).int()
+
+    conv_state_g, ssm_g = conv_state.clone().cuda(), ssm.clone().cuda()
+    conv_out = torch.empty((T, C), dtype=torch.bfloat16, device="cuda")
+    ops.causal_conv1d_silu(proj.cuda(), 0, C, conv_w.cuda(), cu.cuda(), tok_seq.cuda(), torch.tensor(slots).int().cuda(),
+                           conv_state_g, conv_out, True, False)
+    out = torch.empty((T, vd), dtype=torch.bfloat16, device="cuda")
+    ops.gdn_recurrent(conv_out, 0, qk, 2 * qk, proj.cuda(), C, C + vd, C + vd + hv, hk, hv, A_log.cuda(),
+                      dt_bias.cuda(), nw.cuda(), 1e-6, cu.cuda(), torch.tensor(slots).int().cuda(), ssm_g, True, out,
+                      False)
+    # verify pass must leave the state untouched
+    ssm_v = ssm.clone().cuda()
+    out_v = torch.empty_like(out)
+    ops.gdn_recurrent(conv_out, 0, qk, 2 * qk, proj.cuda(), C, C + vd, C + vd + hv, hk, hv, A_log.cuda(),
+                      dt_bias.cuda(), nw.cuda(), 1e-6, cu.cuda(), torch.tensor(slots).int().cuda(), ssm_v, False,
+                      out_v, False)
+    assert torch.equal(ssm_v.cpu(), ssm) and torch.equal(out_v, out)
+
+    for b, n in enumerate(lens):
+        s, e = int(cu[b]), int(cu[b + 1])
+        pj = proj[s:e].float()
+        cref, new_conv = R.causal_conv1d_silu(pj[:, :C], conv_w, conv_state[slots[b]])
+        cref = R.bf16_round(cref)
+        assert (conv_out[s:e].float().cpu() - cref).abs().max().item() < 0.02
+        assert torch.equal(conv_state_g[slots[b]].cpu(), new_conv.to(torch.bfloat16))
+        q = cref[:, :qk].view(n, hk, d)
+        k = cref[:, qk:2 * qk].view(n, hk, d)
+        v = cref[:, 2 * qk:].view(n, hv, d)
+        z = pj[:, C:C + vd].view(n, hv, d)
+        g, beta = R.gdn_gating(pj[:, C + vd:C + vd + hv], pj[:, C + vd + hv:], A_log, dt_bias)
+        o, new_s = R.gdn_recurrent(q, k, v, g, beta, ssm[slots[b]])
+        y = R.gated_rmsnorm(R.bf16_round(o), z, nw).view(n, vd)
+        err = (out[s:e].float().cpu() - y).abs().max().item()
+        assert err < 0.05 * max(1.0, y.abs().max().item()), f"seq {b} err {err}"
+        assert (ssm_g[slots[b]].cpu() - new_s).abs().max().item() < 2e-3 * max(1.0, new_s.abs().max().item())
+    untouched = [s for s in range(n_slots) if s not in slots]
+    for s in untouched:
+        assert torch.equal(ssm_g[s].cpu(), ssm[s])
+
+
+def test_embed_rmsnorm(ops):
+    torch.manual_seed(0)
+    V, N, T = 1000, 5120, 9
+    table = torch.randn(V, N).to(torch.bfloat16).cuda()
+    ids = torch.randint(0, V, (T,)).int().cuda()
+    x = torch.empty((T, N), dtype=torch.bfloat16, device="cuda")
+    ops.embed_gather(ids, table, x, False)
+    assert torch.equal(x, table[ids.long()])
+    w = (torch.randn(N) * 0.1).to(torch.bfloat16).cuda()
+    delta = torch.randn(T, N).to(torch.bfloat16).cuda()
+    r_out = torch.empty_like(x)
+    normed = torch.empty_like(x)
+    ops.add_rmsnorm(None, 0, delta, x, r_out, w, normed, T, N, 1e-6, True, False)
+    xr = (x.float() + delta.float()).to(torch.bfloat16)
+    assert torch.equal(r_out, xr)
+    ref = R.rmsnorm(xr.float().cpu(), w.cpu(), 1e-6, True)
+    assert (normed.float().cpu() - ref).abs().max().item() < 0.05
+
+
+def test_argmax_and_sampling(ops):
+    torch.manual_seed(0)
+    T, V = 5, 248320
+    logits = torch.randn(T, V).to(torch.bfloat16).cuda()
+    logits[1, 77] = 50.0
+    logits[1, 99999] = 50.0  # tie -> lowest id
+    out = torch.empty(T, dtype=torch.int32, device="cuda")
+    ops.argmax_rows(logits, out, False)
+    assert torch.equal(out.cpu(), R.argmax_lowest(logits.cpu()))
+    assert int(out[1]) == 77
+    # greedy through the sampler (temperature 0) must agree with arg-max
+    temp = torch.zeros(T, device="cuda")
+    out2 = torch.empty_like(out)
+    ops.sample_rows(logits, temp, None, None, None, None, None, None, None, None, 0, out2, None)
+    assert torch.equal(out, out2)
+    # stochastic: draws stay inside the top-k set, are reproducible per (seed, position), vary with position
+    temp = torch.ones(T, device="cuda")
+    top_k = torch.full((T,), 5, dtype=torch.int32, device="cuda")
+    seeds = torch.arange(T, dtype=torch.int64, device="cuda") + 11
+    posn = torch.arange(T, dtype=torch.int32, device="cuda")
+    a = torch.empty_like(out)
+    b = torch.empty_like(out)
+    ops.sample_rows(logits, temp, top_k, None, None, None, None, None, seeds, posn, 0, a, None)
+    ops.sample_rows(logits, temp, top_k, None, None, None, None, None, seeds, posn, 0, b, None)
+    assert torch.equal(a, b)
+    top5 = logits.float().topk(5, dim=-1).indices
+    for t in range(T):
+        assert int(a[t]) in top5[t].tolist()
+    # top_p tiny -> always the arg-max
+    top_p = torch.full((T,), 1e-4, device="cuda")
+    ops.sample_rows(logits, temp, top_k, top_p, None, None, None, None, seeds, posn, 0, b, None)
+    assert torch.equal(b, out)
+    # distribution check on a 3-way row
+    row = torch.full((1, 64), -30.0)
+    row[0, 3], row[0, 10], row[0, 20] = 2.0, 1.0, 0.0
+    row = row.to(torch.bfloat16).cuda().repeat(4096, 1)
+    seeds = torch.arange(4096, dtype=torch.int64, device="cuda")
+    draws = torch.empty(4096, dtype=torch.int32, device="cuda")
+    ops.sample_rows(row, torch.ones(4096, device="cuda"), None, None, None, None, None, None, seeds, None, 0, draws, None)
+    p = torch.softmax(torch.tensor([2.0, 1.0, 0.0]), 0)
+    freq = torch.tensor([(draws == i).float().mean().item() for i in (3, 10, 20)])
+    assert (freq - p).abs().max().item() < 0.03
+
+
+def test_speculative_accept(ops):
+    target = torch.tensor([[5, 6, 7, 8], [5, 6, 7, 8], [1, 2, 3, 4]], dtype=torch.int32)
+    draft = torch.tensor([[5, 6, 7], [5, 9, 7], [0, 2, 3]], dtype=torch.int32)
+    n_ref, out_ref = R.accept_greedy_chain(target, draft)
+    n = torch.empty(3, dtype=torch.int32, device="cuda")
+    out = torch.empty((3, 4), dtype=torch.int32, device="cuda")
+    ops.accept_greedy_chain(target.cuda(), draft.cuda(), n, out)
+    assert torch.equal(n.cpu(), n_ref) and torch.equal(out.cpu(), out_ref)
+    # tree: 0 -> {1, 2}; 1 -> {3}; 2 -> {4}; 3 -> {5}
+    parent = torch.tensor([[-1, 0, 0, 1, 2, 3]], dtype=torch.int32)
+    tok = torch.tensor([[0, 11, 12, 13, 14, 15]], dtype=torch.int32)
+    tgt = torch.tensor([[12, 13, 14, 15, 99, 98]], dtype=torch.int32)  # accepts 2 then 4
+    nr, tr, nodes_r = R.accept_greedy_tree(tgt, tok, parent, 4)
+    n1 = torch.empty(1, dtype=torch.int32, device="cuda")
+    t1 = torch.empty((1, 5), dtype=torch.int32, device="cuda")
+    nd = torch.empty((1, 5), dtype=torch.int32, device="cuda")
+    ops.accept_greedy_tree(tgt.cuda(), tok.cuda(), parent.cuda(), 4, n1, t1, nd)
+    assert torch.equal(n1.cpu(), nr) and torch.equal(t1.cpu(), tr) and torch.equal(nd.cpu(), nodes_r)
+    assert int(nr[0]) == 2 and tr[0, :3].tolist() == [12, 14, 99]
