@@ -10,7 +10,12 @@ enum GemmEpilogue : int {
   kEpiResidual = 1,  // out = resid + acc
   kEpiSwiglu = 2,    // W = [gate; up] (N rows), out[T, N/2] = silu(gate) * up
   kEpiPartial = 3,   // partial[z, T, N] = acc over this split's K range (fp32)
+  kEpiPushPartial = 4,  // tensor parallel: fp32 partial tiles are stored into the OWNER rank's receive
+                        // buffer [src_rank][split][T][N/world] over NVLink, then the owner's arrival
+                        // counter is incremented (GEMM -> reduce-scatter in one kernel)
 };
+
+constexpr int kMaxRanks = 8;
 
 struct GemmArgs {
   const void* w = nullptr;  // [N, K] bf16 row-major, leading dimension ldw
@@ -28,6 +33,10 @@ struct GemmArgs {
   int* status = nullptr;    // device status word (see common/ptx.cuh)
   cudaStream_t stream = nullptr;
   bool pdl = false;         // launch with programmatic stream serialization
+  // kEpiPushPartial only
+  int world = 1, rank = 0;
+  float* peer_recv[kMaxRanks] = {};
+  unsigned int* peer_flag[kMaxRanks] = {};
 };
 
 // Returns nullptr on success, else a static error string.

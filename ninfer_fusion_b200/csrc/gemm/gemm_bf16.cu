@@ -49,6 +49,10 @@ struct KernelParams {
   const float* bias;
   float* partial;      // [splits, T, N] fp32
   int* status;
+  // kEpiPushPartial: tensor-parallel reduce-scatter by peer stores
+  float* peer_recv[kMaxRanks];
+  unsigned int* peer_flag[kMaxRanks];
+  int rank, slice_cols;
 };
 
 template <int TN, int EPI>
@@ -239,6 +243,18 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
             if (t < p.T && n < p.N)
               p.partial[(static_cast<long long>(blockIdx.z) * p.T + t) * p.N + n] = __uint_as_float(v[j]);
           }
+        } else if constexpr (EPI == kEpiPushPartial) {
+          // reduce-scatter by push: this tile's columns belong to one owner rank; write the fp32
+          // partial straight into the owner's receive buffer [src_rank][split][T][slice_cols].
+          const int owner = n0 / p.slice_cols;
+          float* dst = p.peer_recv[owner] +
+                       (static_cast<long long>(p.rank) * gridDim.z + blockIdx.z) * p.T * p.slice_cols +
+                       (n - owner * p.slice_cols);
+#pragma unroll
+          for (int j = 0; j < kChunk; ++j) {
+            const int t = t0 + c + j;
+            if (t < p.T && n < p.N) dst[static_cast<long long>(t) * p.slice_cols] = __uint_as_float(v[j]);
+          }
         } else {
 #pragma unroll
           for (int m = 0; m < kChunk / 2; ++m) {
@@ -261,6 +277,15 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
                   pack_bf16x2(lo, hi);
             }
           }
+        }
+      }
+      if constexpr (EPI == kEpiPushPartial) {
+        // publish: every thread's peer stores are ordered before the owner's arrival counter
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          unsigned int* flag = p.peer_flag[n0 / p.slice_cols];
+          asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(flag) : "memory");
         }
       }
     }
@@ -374,11 +399,23 @@ const char* gemm_bf16(const GemmArgs& a) {
   kp.T = static_cast<int>(a.T); kp.N = static_cast<int>(a.N); kp.K = static_cast<int>(a.K);
   kp.num_kb = (kp.K + kBlockK - 1) / kBlockK;
   int splits = a.splits < 1 ? 1 : a.splits;
-  if (a.epi != kEpiPartial) splits = 1;
+  if (a.epi != kEpiPartial && a.epi != kEpiPushPartial) splits = 1;
   if (splits > kp.num_kb) splits = kp.num_kb;
   kp.kb_per_split = (kp.num_kb + splits - 1) / splits;
   splits = (kp.num_kb + kp.kb_per_split - 1) / kp.kb_per_split;  // no empty split
-  if (a.epi == kEpiPartial && splits != a.splits) return "gemm_bf16: split count leaves an empty split";
+  if ((a.epi == kEpiPartial || a.epi == kEpiPushPartial) && splits != a.splits)
+    return "gemm_bf16: split count leaves an empty split";
+  if (a.epi == kEpiPushPartial) {
+    if (a.world < 1 || a.world > kMaxRanks || a.rank < 0 || a.rank >= a.world) return "gemm_bf16: bad rank/world";
+    if (kp.N % a.world || (kp.N / a.world) % kTileN) return "gemm_bf16: N / world must be a multiple of 128";
+    kp.rank = a.rank;
+    kp.slice_cols = kp.N / a.world;
+    for (int r = 0; r < a.world; ++r) {
+      if (a.peer_recv[r] == nullptr || a.peer_flag[r] == nullptr) return "gemm_bf16: missing peer pointer";
+      kp.peer_recv[r] = a.peer_recv[r];
+      kp.peer_flag[r] = a.peer_flag[r];
+    }
+  }
   kp.swiglu_half = a.epi == kEpiSwiglu ? kp.N / 2 : 0;
   if (a.epi == kEpiSwiglu && (kp.N % 4)) return "gemm_bf16: SwiGLU needs N % 4 == 0";
   kp.out = static_cast<__nv_bfloat16*>(a.out); kp.ldo = a.ldo;
@@ -386,7 +423,7 @@ const char* gemm_bf16(const GemmArgs& a) {
   kp.bias = a.bias; kp.partial = a.partial; kp.status = a.status;
   if (a.epi == kEpiResidual && a.resid == nullptr) return "gemm_bf16: residual epilogue without residual";
   if (a.epi == kEpiPartial && a.partial == nullptr) return "gemm_bf16: split-K without workspace";
-  if (a.epi != kEpiPartial && a.out == nullptr) return "gemm_bf16: no output";
+  if (a.epi != kEpiPartial && a.epi != kEpiPushPartial && a.out == nullptr) return "gemm_bf16: no output";
 
   CUtensorMap tw, tx;
   if (!cached_tmap(&tw, a.w, a.N, a.K, a.ldw, 64)) return "gemm_bf16: weight tensor map rejected";
@@ -402,6 +439,7 @@ const char* gemm_bf16(const GemmArgs& a) {
     case kEpiResidual: e = launch_tn<kEpiResidual>(tn, tw, tx, kp, grid, a.stream, a.pdl); break;
     case kEpiSwiglu: e = launch_tn<kEpiSwiglu>(tn, tw, tx, kp, grid, a.stream, a.pdl); break;
     case kEpiPartial: e = launch_tn<kEpiPartial>(tn, tw, tx, kp, grid, a.stream, a.pdl); break;
+    case kEpiPushPartial: e = launch_tn<kEpiPushPartial>(tn, tw, tx, kp, grid, a.stream, a.pdl); break;
     default: return "gemm_bf16: unknown epilogue";
   }
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);

@@ -6,6 +6,7 @@
 #include <ATen/ATen.h>
 
 #include "attention/attention.h"
+#include "comm/comm.h"
 #include "gdn/gdn.h"
 #include "gemm/gemm.h"
 #include "pointwise/pointwise.h"
@@ -343,9 +344,119 @@ void accept_greedy_tree(const Tensor& target_ids, const Tensor& node_tok, const 
                               cur_stream()));
 }
 
+// ---------------------------------------------------------------- tensor parallel
+// One symmetric allocation per rank; `peer_bases[r]` is rank r's allocation as mapped here.
+std::tuple<Tensor, Tensor> symm_alloc(int64_t bytes) {
+  void* ptr = nullptr;
+  Tensor handle = at::empty({64}, at::TensorOptions().dtype(at::kByte));
+  chk(nfb::symm_alloc(static_cast<size_t>(bytes), &ptr, handle.data_ptr<uint8_t>()));
+  int dev = 0;
+  cudaGetDevice(&dev);
+  Tensor view = at::from_blob(ptr, {bytes}, [](void*) {}, at::TensorOptions().dtype(at::kByte).device(at::kCUDA, dev));
+  return {view, handle};
+}
+
+int64_t symm_open(const Tensor& handle) {
+  TORCH_CHECK(!handle.is_cuda() && handle.scalar_type() == at::kByte && handle.numel() == 64, "handle must be 64 CPU bytes");
+  void* ptr = nullptr;
+  chk(nfb::symm_open(handle.data_ptr<uint8_t>(), &ptr));
+  return reinterpret_cast<int64_t>(ptr);
+}
+
+void gemm_bf16_push(const Tensor& x, const Tensor& w, int64_t splits, int64_t world, int64_t rank,
+                    at::IntArrayRef peer_bases, int64_t recv_off, int64_t flag_off, OptT status, bool pdl) {
+  need(x, at::kBFloat16, "x"); need(w, at::kBFloat16, "w"); need_rows(x, "x"); need_rows(w, "w");
+  TORCH_CHECK(x.size(1) == w.size(1), "gemm_bf16_push: K mismatch");
+  TORCH_CHECK(static_cast<int64_t>(peer_bases.size()) == world && world <= nfb::kMaxRanks, "peer_bases size");
+  c10::cuda::CUDAGuard guard(x.device());
+  nfb::GemmArgs a;
+  a.w = w.data_ptr(); a.N = w.size(0); a.K = w.size(1); a.ldw = w.stride(0);
+  a.x = x.data_ptr(); a.T = x.size(0); a.ldx = x.stride(0);
+  a.splits = static_cast<int>(splits); a.epi = nfb::kEpiPushPartial;
+  a.world = static_cast<int>(world); a.rank = static_cast<int>(rank);
+  for (int r = 0; r < world; ++r) {
+    a.peer_recv[r] = reinterpret_cast<float*>(peer_bases[r] + recv_off);
+    a.peer_flag[r] = reinterpret_cast<unsigned int*>(peer_bases[r] + flag_off);
+  }
+  a.ldo = 2;
+  a.status = ptr_or_null<int>(status); a.stream = cur_stream(); a.pdl = pdl;
+  chk(nfb::gemm_bf16(a));
+}
+
+void tp_reduce_ag_norm(int64_t world, int64_t rank, int64_t T, int64_t T_cap, int64_t N, int64_t splits,
+                       int64_t arrivals, at::IntArrayRef peer_bases, int64_t recv_off, int64_t flag_off,
+                       int64_t x_off, int64_t ss_off, int64_t row_flag_off, OptT norm_w, OptT normed, double eps,
+                       bool unit_offset, const Tensor& state, OptT status, bool pdl) {
+  TORCH_CHECK(static_cast<int64_t>(peer_bases.size()) == world && world <= nfb::kMaxTpRanks, "peer_bases size");
+  need(state, at::kByte, "state");
+  TORCH_CHECK(state.numel() >= static_cast<int64_t>(sizeof(nfb::TpState)), "state too small");
+  c10::cuda::CUDAGuard guard(state.device());
+  nfb::TpReduceParams p = {};
+  p.world = static_cast<int>(world); p.rank = static_cast<int>(rank); p.T = static_cast<int>(T);
+  p.T_cap = static_cast<int>(T_cap); p.N = static_cast<int>(N); p.splits = static_cast<int>(splits);
+  p.arrivals_this_call = static_cast<unsigned int>(arrivals);
+  const int64_t me = peer_bases[rank];
+  p.my_recv = reinterpret_cast<const float*>(me + recv_off);
+  p.my_arrival_flag = reinterpret_cast<const unsigned int*>(me + flag_off);
+  p.my_x = reinterpret_cast<__nv_bfloat16*>(me + x_off);
+  p.my_ss = reinterpret_cast<float*>(me + ss_off);
+  p.my_row_flag = reinterpret_cast<unsigned int*>(me + row_flag_off);
+  for (int r = 0; r < world; ++r) {
+    p.peer_x[r] = reinterpret_cast<__nv_bfloat16*>(peer_bases[r] + x_off);
+    p.peer_ss[r] = reinterpret_cast<float*>(peer_bases[r] + ss_off);
+    p.peer_row_flag[r] = reinterpret_cast<unsigned int*>(peer_bases[r] + row_flag_off);
+  }
+  if (norm_w.has_value() && norm_w->defined()) {
+    need(*norm_w, at::kBFloat16, "norm_w");
+    TORCH_CHECK(norm_w->numel() == N);
+    p.norm_w = static_cast<const __nv_bfloat16*>(norm_w->data_ptr());
+  }
+  if (normed.has_value() && normed->defined()) {
+    need(*normed, at::kBFloat16, "normed");
+    TORCH_CHECK(normed->is_contiguous() && normed->numel() == T * N && p.norm_w != nullptr);
+    p.normed = static_cast<__nv_bfloat16*>(normed->data_ptr());
+  }
+  p.eps = static_cast<float>(eps); p.unit_offset = unit_offset ? 1 : 0;
+  p.state = reinterpret_cast<nfb::TpState*>(state.data_ptr());
+  p.status = ptr_or_null<int>(status);
+  chk(nfb::tp_reduce_ag_norm(p, cur_stream(), pdl));
+}
+
+void tp_argmax(int64_t world, int64_t rank, int64_t T_cap, const Tensor& logits, at::IntArrayRef peer_bases,
+               int64_t cand_off, int64_t flag_off, const Tensor& out, const Tensor& state, OptT status, bool pdl) {
+  need(logits, at::kBFloat16, "logits"); need_rows(logits, "logits"); need(out, at::kInt, "out");
+  need(state, at::kByte, "state");
+  TORCH_CHECK(static_cast<int64_t>(peer_bases.size()) == world && world <= nfb::kMaxTpRanks, "peer_bases size");
+  TORCH_CHECK(out.numel() >= logits.size(0));
+  c10::cuda::CUDAGuard guard(logits.device());
+  nfb::TpArgmaxParams p = {};
+  p.world = static_cast<int>(world); p.rank = static_cast<int>(rank); p.T = static_cast<int>(logits.size(0));
+  p.T_cap = static_cast<int>(T_cap); p.V_local = static_cast<int>(logits.size(1));
+  p.logits = static_cast<const __nv_bfloat16*>(logits.data_ptr()); p.ld = logits.stride(0);
+  const int64_t me = peer_bases[rank];
+  p.my_cand = reinterpret_cast<float2*>(me + cand_off);
+  p.my_flag = reinterpret_cast<unsigned int*>(me + flag_off);
+  for (int r = 0; r < world; ++r) {
+    p.peer_cand[r] = reinterpret_cast<float2*>(peer_bases[r] + cand_off);
+    p.peer_flag[r] = reinterpret_cast<unsigned int*>(peer_bases[r] + flag_off);
+  }
+  p.out = static_cast<int*>(out.data_ptr());
+  p.state = reinterpret_cast<nfb::TpState*>(state.data_ptr());
+  p.status = ptr_or_null<int>(status);
+  chk(nfb::tp_argmax(p, cur_stream(), pdl));
+}
+
+int64_t tp_state_bytes() { return static_cast<int64_t>(sizeof(nfb::TpState)); }
+
 }  // namespace
 
 TORCH_LIBRARY(nfb200, m) {
+  m.def("symm_alloc(int bytes) -> (Tensor, Tensor)", &symm_alloc);
+  m.def("symm_open(Tensor handle) -> int", &symm_open);
+  m.def("gemm_bf16_push(Tensor x, Tensor w, int splits, int world, int rank, int[] peer_bases, int recv_off, int flag_off, Tensor? status, bool pdl) -> ()", &gemm_bf16_push);
+  m.def("tp_reduce_ag_norm(int world, int rank, int T, int T_cap, int N, int splits, int arrivals, int[] peer_bases, int recv_off, int flag_off, int x_off, int ss_off, int row_flag_off, Tensor? norm_w, Tensor? normed, float eps, bool unit_offset, Tensor state, Tensor? status, bool pdl) -> ()", &tp_reduce_ag_norm);
+  m.def("tp_argmax(int world, int rank, int T_cap, Tensor logits, int[] peer_bases, int cand_off, int flag_off, Tensor out, Tensor state, Tensor? status, bool pdl) -> ()", &tp_argmax);
+  m.def("tp_state_bytes() -> int", &tp_state_bytes);
   m.def("gemm_bf16(Tensor x, Tensor w, Tensor? out, int epi, Tensor? resid, Tensor? bias, Tensor? partial, int splits, Tensor? status, bool pdl) -> ()", &gemm_bf16);
   m.def("gemm_pick_splits(int T, int N, int K, int epi) -> int", &gemm_pick_splits);
   m.def("add_rmsnorm(Tensor? partial, int splits, Tensor? delta, Tensor? resid_in, Tensor? resid_out, Tensor? norm_w, Tensor? normed, int T, int N, float eps, bool unit_offset, bool pdl) -> ()", &add_rmsnorm);

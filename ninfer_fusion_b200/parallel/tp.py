@@ -1,0 +1,231 @@
+"""Tensor parallelism over one NVSwitch box: shard plan, symmetric buffers, fused collectives.
+
+Shard rules (the reference only specifies them as host arithmetic,
+src/core/shard_plan.h:56-251, docs/gfx906/TP2-SLICES.md:42-61): column-parallel
+input projections (attention heads, GDN heads and the FFN intermediate are split;
+a KV head is replicated when there are fewer KV heads than ranks), row-parallel
+output projections, vocabulary-parallel head, replicated embedding / norms /
+residual stream.  Every row-parallel GEMM is followed by a sum over ranks: here
+the GEMM epilogue itself pushes its partial tiles into the owning rank over
+NVLink (`gemm_bf16_push`), and one more kernel reduces, adds the residual,
+all-gathers the new residual by peer stores and RMS-normalises it for the next
+column-parallel GEMM (`tp_reduce_ag_norm`).  `mode="nccl"` keeps a plain
+NCCL all-reduce as the baseline for the same math.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .._lib import load_native
+from ..models.config import ModelConfig
+from ..models.hybrid import EPI_PARTIAL, MAX_SPLITS, ShardGeometry
+from ..models.weights import random_weights, weight_shapes
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+def shard_geometry(cfg: ModelConfig, rank: int, world: int) -> ShardGeometry:
+    if cfg.n_q_heads % world or cfg.gdn_qk_heads % world or cfg.gdn_v_heads % world:
+        raise ValueError(f"head counts of {cfg.name} do not divide over {world} ranks")
+    if cfg.n_kv_heads % world and world % cfg.n_kv_heads:
+        raise ValueError(f"{cfg.n_kv_heads} KV heads cannot be split or replicated over {world} ranks")
+    if cfg.hidden % (128 * world):
+        raise ValueError(f"hidden {cfg.hidden} / {world} ranks must be a multiple of 128 (reduce-scatter tile)")
+    if cfg.moe is None and (cfg.ffn_inter % (64 * world)):
+        raise ValueError("FFN intermediate / world must be a multiple of 64")
+    if cfg.vocab % (2 * world):
+        raise ValueError("vocabulary must divide over the ranks")
+    n_kv = max(1, cfg.n_kv_heads // world)
+    q_l = cfg.n_q_heads // world
+    if q_l % n_kv:
+        raise ValueError("non-integer GQA group on a rank")
+    return ShardGeometry(world, rank, q_l, n_kv, cfg.gdn_qk_heads // world, cfg.gdn_v_heads // world,
+                         cfg.ffn_inter // world if cfg.moe is None else 0, cfg.vocab // world, cfg.head_dim,
+                         cfg.gdn_head_dim)
+
+
+def kv_head_range(cfg: ModelConfig, rank: int, world: int) -> range:
+    if cfg.n_kv_heads >= world:
+        per = cfg.n_kv_heads // world
+        return range(rank * per, (rank + 1) * per)
+    h = rank * cfg.n_kv_heads // world
+    return range(h, h + 1)
+
+
+def shard_weights(full: Dict[str, torch.Tensor], cfg: ModelConfig, rank: int, world: int) -> Dict[str, torch.Tensor]:
+    """Slice a full weight set into rank `rank`'s shard (same names, smaller tensors)."""
+    g = shard_geometry(cfg, rank, world)
+    D, d = cfg.head_dim, cfg.gdn_head_dim
+    out: Dict[str, torch.Tensor] = {}
+
+    def rows(t, start, n):
+        return t[start:start + n]
+
+    q_rows = range(rank * g.n_q_heads * D, (rank + 1) * g.n_q_heads * D)
+    kvh = kv_head_range(cfg, rank, world)
+    for name, t in full.items():
+        leaf = name.rsplit("/", 2)[-2:] if "/" in name else [name]
+        key = "/".join(leaf)
+        if key == "attn/in_proj":
+            qd, kd = cfg.q_dim, cfg.kv_dim
+            q = t[q_rows.start:q_rows.stop]
+            k = t[qd + kvh.start * D: qd + kvh.stop * D]
+            gate = t[qd + kd + q_rows.start: qd + kd + q_rows.stop]
+            v = t[2 * qd + kd + kvh.start * D: 2 * qd + kd + kvh.stop * D]
+            out[name] = torch.cat([q, k, gate, v], 0).contiguous()
+        elif key == "attn/o_proj":
+            out[name] = t[:, q_rows.start:q_rows.stop].contiguous()
+        elif key == "gdn/in_proj":
+            qk, vd, hv = cfg.gdn_qk_dim, cfg.gdn_v_dim, cfg.gdn_v_heads
+            qk_l, v_l, hv_l = g.gdn_qk_dim, g.gdn_v_dim, g.gdn_v_heads
+            parts = [rows(t, rank * qk_l, qk_l), rows(t, qk + rank * qk_l, qk_l),
+                     rows(t, 2 * qk + rank * v_l, v_l), rows(t, 2 * qk + vd + rank * v_l, v_l),
+                     rows(t, 2 * qk + 2 * vd + rank * hv_l, hv_l), rows(t, 2 * qk + 2 * vd + hv + rank * hv_l, hv_l)]
+            out[name] = torch.cat(parts, 0).contiguous()
+        elif key == "gdn/conv_w":
+            qk, qk_l, v_l = cfg.gdn_qk_dim, g.gdn_qk_dim, g.gdn_v_dim
+            out[name] = torch.cat([rows(t, rank * qk_l, qk_l), rows(t, qk + rank * qk_l, qk_l),
+                                   rows(t, 2 * qk + rank * v_l, v_l)], 0).contiguous()
+        elif key in ("gdn/A_log", "gdn/dt_bias"):
+            out[name] = rows(t, rank * g.gdn_v_heads, g.gdn_v_heads).contiguous()
+        elif key == "gdn/out_proj":
+            out[name] = t[:, rank * g.gdn_v_dim:(rank + 1) * g.gdn_v_dim].contiguous()
+        elif key == "mlp/gate_up":
+            i, il = cfg.ffn_inter, g.ffn_inter
+            out[name] = torch.cat([rows(t, rank * il, il), rows(t, i + rank * il, il)], 0).contiguous()
+        elif key == "mlp/down":
+            out[name] = t[:, rank * g.ffn_inter:(rank + 1) * g.ffn_inter].contiguous()
+        elif name.endswith("lm_head"):
+            out[name] = rows(t, rank * g.vocab_rows, g.vocab_rows).contiguous()
+        else:
+            out[name] = t
+    return out
+
+
+class TensorParallel:
+    def __init__(self, cfg: ModelConfig, rank: int, world: int, device, max_tokens: int, mode: str = "fused",
+                 group=None):
+        self.cfg, self.rank, self.world = cfg, rank, world
+        self.device = torch.device(device)
+        self.mode = mode
+        self.group = group
+        self.geometry = shard_geometry(cfg, rank, world)
+        self.ops = load_native()
+        self.T_cap = min(max_tokens, 4096)
+        N = cfg.hidden
+        self.slice = N // world
+        # ---- one symmetric allocation, identical layout on every rank ----
+        off = 0
+        self.off: Dict[str, int] = {}
+        for name, nbytes in [("recv", world * MAX_SPLITS * min(self.T_cap, 256) * self.slice * 4),
+                             ("x", self.T_cap * N * 2), ("ss", 2 * self.T_cap * world * 4),
+                             ("row_flag", self.T_cap * 4), ("arrival_flag", 256),
+                             ("cand", 2 * self.T_cap * world * 8), ("argmax_flag", self.T_cap * 4)]:
+            self.off[name] = off
+            off += _align(nbytes)
+        # large-T calls use one split; make sure that layout fits too
+        recv_need = world * self.T_cap * self.slice * 4
+        if recv_need > self.off["x"] - self.off["recv"]:
+            grow = _align(recv_need) - (self.off["x"] - self.off["recv"])
+            for k in self.off:
+                if k != "recv":
+                    self.off[k] += grow
+            off += grow
+        self.total_bytes = off
+        self.local, handle = self.ops.symm_alloc(off)
+        handles: List[Optional[torch.Tensor]] = [None] * world
+        dist.all_gather_object(handles, handle, group=group)
+        self.peer_bases: List[int] = []
+        for r in range(world):
+            self.peer_bases.append(self.local.data_ptr() if r == rank else int(self.ops.symm_open(handles[r])))
+        self.state = torch.zeros(int(self.ops.tp_state_bytes()), dtype=torch.uint8, device=self.device)
+        x_bytes = self.local[self.off["x"]: self.off["x"] + self.T_cap * N * 2]
+        self.x = x_bytes.view(torch.bfloat16).view(self.T_cap, N)
+        self.delta = torch.empty((self.T_cap, N), dtype=torch.bfloat16, device=self.device)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=group)
+
+    # ------------------------------------------------------------------ weights
+    def shard(self, full: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        return shard_weights(full, self.cfg, self.rank, self.world)
+
+    def random_shard_weights(self, seed: int = 0) -> Dict[str, torch.Tensor]:
+        """Random-init weights generated directly at shard shapes (replicated tensors use a shared seed)."""
+        g = self.geometry
+        gen_shared = torch.Generator(device=self.device).manual_seed(seed)
+        gen_rank = torch.Generator(device=self.device).manual_seed(seed * 1000 + 17 + self.rank)
+        cfg = self.cfg
+        shapes = {
+            "attn/in_proj": (g.attn_in_dim, cfg.hidden), "attn/o_proj": (cfg.hidden, g.n_q_heads * cfg.head_dim),
+            "gdn/in_proj": (g.gdn_in_dim, cfg.hidden), "gdn/conv_w": (g.gdn_conv_dim, cfg.conv_kernel),
+            "gdn/A_log": (g.gdn_v_heads,), "gdn/dt_bias": (g.gdn_v_heads,),
+            "gdn/out_proj": (cfg.hidden, g.gdn_v_dim), "mlp/gate_up": (2 * g.ffn_inter, cfg.hidden),
+            "mlp/down": (cfg.hidden, g.ffn_inter),
+        }
+        out = {}
+        for name, shape, dt in weight_shapes(cfg):
+            key = "/".join(name.rsplit("/", 2)[-2:])
+            sharded = key in shapes or name.endswith("lm_head")
+            shp = shapes.get(key, (g.vocab_rows, cfg.hidden) if name.endswith("lm_head") else shape)
+            gen = gen_rank if sharded else gen_shared
+            t = torch.empty(shp, dtype=dt, device=self.device)
+            leaf = name.rsplit("/", 1)[-1]
+            if leaf.endswith("norm"):
+                t.normal_(0.0, 0.02, generator=gen)
+                if name.endswith("gdn/norm"):
+                    t.add_(1.0)
+            elif leaf == "A_log":
+                t.uniform_(-1.0, 1.5, generator=gen)
+            elif leaf == "dt_bias":
+                t.uniform_(-2.0, 1.0, generator=gen)
+            elif leaf == "conv_w":
+                t.normal_(0.0, 0.3, generator=gen)
+            else:
+                t.normal_(0.0, 0.02, generator=gen)
+            out[name] = t
+        return out
+
+    # ------------------------------------------------------------------ collectives
+    def gemm_reduce_residual(self, model, ws, a, w, T: int, norm_w, normed_out, splits: int) -> None:
+        """x += sum_ranks(a_r @ w_r^T); normed_out = rmsnorm(x) * (1 + norm_w).  x is the symmetric residual."""
+        cfg, ops = self.cfg, model.ops
+        N = cfg.hidden
+        if self.mode == "nccl" or T > self.T_cap:
+            delta = self.delta[:T] if T <= self.T_cap else torch.empty((T, N), dtype=torch.bfloat16, device=self.device)
+            ops.gemm_bf16(a, w, delta, 0, None, None, None, 1, model.status.tensor, model.pdl)
+            dist.all_reduce(delta, group=self.group)
+            ops.add_rmsnorm(None, 0, delta, ws.x[:T], ws.x[:T], norm_w, normed_out, T, N, cfg.rms_eps, True, model.pdl)
+            return
+        if T > 256:
+            splits = 1
+        tn = 16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else 128 if T <= 128 else 256
+        arrivals = self.world * (self.slice // 128) * ((T + tn - 1) // tn) * splits
+        ops.gemm_bf16_push(a, w, splits, self.world, self.rank, self.peer_bases, self.off["recv"],
+                           self.off["arrival_flag"], model.status.tensor, model.pdl)
+        ops.tp_reduce_ag_norm(self.world, self.rank, T, self.T_cap, N, splits, arrivals, self.peer_bases,
+                              self.off["recv"], self.off["arrival_flag"], self.off["x"], self.off["ss"],
+                              self.off["row_flag"], norm_w, normed_out, cfg.rms_eps, True, self.state,
+                              model.status.tensor, model.pdl)
+
+    def argmax(self, model, logits: torch.Tensor, out: torch.Tensor) -> None:
+        if self.mode == "nccl":
+            local = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
+            model.ops.argmax_rows(logits, local, model.pdl)
+            vals = logits.float().gather(1, local.long()[:, None])[:, 0]
+            allv = [torch.empty_like(vals) for _ in range(self.world)]
+            alli = [torch.empty_like(local) for _ in range(self.world)]
+            dist.all_gather(allv, vals, group=self.group)
+            dist.all_gather(alli, local, group=self.group)
+            v = torch.stack(allv, 1)
+            i = torch.stack(alli, 1) + torch.arange(self.world, device=self.device, dtype=torch.int32)[None] * logits.shape[1]
+            best = v.amax(1, keepdim=True)
+            cand = torch.where(v == best, i, torch.full_like(i, 2 ** 31 - 1))
+            out.copy_(cand.amin(1))
+            return
+        model.ops.tp_argmax(self.world, self.rank, self.T_cap, logits, self.peer_bases, self.off["cand"],
+                            self.off["argmax_flag"], out, self.state, model.status.tensor, model.pdl)

@@ -112,8 +112,8 @@ def test_paged_attention_tree_mask(ops):
     k_codes, v_codes, _, _ = _planes(n_pages, hkv, P, D, R.KV_BF16, D)
     kb = k.to(torch.bfloat16).view(-1, hkv, D)
     for t in range(L + W):
-        k_codes[t // P, 0, t % P] = kb[t, 0].view(torch.uint8).cuda()
-        v_codes[t // P, 0, t % P] = v.to(torch.bfloat16)[t, 0].view(torch.uint8).cuda()
+        k_codes[t // P, 0, t % P] = kb[t, 0].contiguous().view(torch.uint8).cuda()
+        v_codes[t // P, 0, t % P] = v.to(torch.bfloat16)[t, 0].contiguous().view(torch.uint8).cuda()
     q = torch.randn(W, hq, D).to(torch.bfloat16).cuda()
     # tree: node j sees nodes in anc[j]
     anc = [[0], [0, 1], [0, 2], [0, 1, 3], [0, 2, 4]]
