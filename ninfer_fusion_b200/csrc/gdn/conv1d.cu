@@ -67,6 +67,38 @@ __global__ void __launch_bounds__(128) conv1d_state_kernel(const ConvParams p) {
         pack_bf16x2(v[j].x, v[j].y);
 }
 
+// Decode fast path (exactly one token per sequence): conv, SiLU and the history roll in one
+// launch.  The thread that owns (sequence, channel pair) is the only reader and writer of that
+// history column, so there is no ordering problem.
+__global__ void __launch_bounds__(128) conv1d_silu_decode_kernel(const ConvParams p) {
+  pdl_launch_next();
+  pdl_wait_prior();
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 2;
+  const int t = blockIdx.x;  // token index == sequence index
+  if (c >= p.C) return;
+  const int slot = p.state_slot[t];
+  __nv_bfloat16* st = p.conv_state + static_cast<long long>(slot) * 3 * p.C + c;
+  const uint4 wv = *reinterpret_cast<const uint4*>(p.w + static_cast<long long>(c) * 4);
+  const __nv_bfloat16* wp = reinterpret_cast<const __nv_bfloat16*>(&wv);
+  float2 x[4];
+  x[0] = ld2(st);
+  x[1] = ld2(st + p.C);
+  x[2] = ld2(st + 2 * p.C);
+  x[3] = ld2(p.x + static_cast<long long>(t) * p.ld_x + p.c_off + c);
+  float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    a0 += __bfloat162float(wp[j]) * x[j].x;
+    a1 += __bfloat162float(wp[4 + j]) * x[j].y;
+  }
+  a0 = a0 / (1.f + __expf(-a0));
+  a1 = a1 / (1.f + __expf(-a1));
+  *reinterpret_cast<uint32_t*>(p.out + static_cast<long long>(t) * p.C + c) = pack_bf16x2(a0, a1);
+#pragma unroll
+  for (int j = 0; j < 3; ++j)
+    *reinterpret_cast<uint32_t*>(st + j * p.C) = pack_bf16x2(x[j + 1].x, x[j + 1].y);
+}
+
 }  // namespace
 
 const char* causal_conv1d_silu(const ConvParams& p, cudaStream_t stream, bool pdl) {
@@ -79,6 +111,11 @@ const char* causal_conv1d_silu(const ConvParams& p, cudaStream_t stream, bool pd
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
   cfg.gridDim = dim3(p.T, (p.C / 2 + 127) / 128);
+  if (p.update_state && p.one_token_per_seq) {
+    if (p.T != p.n_seq) return "causal_conv1d_silu: one_token_per_seq needs T == n_seq";
+    cudaError_t e1 = cudaLaunchKernelEx(&cfg, conv1d_silu_decode_kernel, p);
+    return e1 == cudaSuccess ? nullptr : cudaGetErrorString(e1);
+  }
   cudaError_t e = cudaLaunchKernelEx(&cfg, conv1d_silu_kernel, p);
   if (e != cudaSuccess) return cudaGetErrorString(e);
   if (p.update_state) {

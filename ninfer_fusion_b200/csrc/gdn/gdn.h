@@ -20,6 +20,7 @@ struct ConvParams {
   __nv_bfloat16* conv_state;  // [slots, 3, C]
   __nv_bfloat16* out;       // [T, C]
   int update_state;
+  int one_token_per_seq;     // decode: token i belongs to sequence i; conv + history roll in one launch
 };
 const char* causal_conv1d_silu(const ConvParams& p, cudaStream_t stream, bool pdl);
 

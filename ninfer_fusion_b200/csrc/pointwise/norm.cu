@@ -146,6 +146,118 @@ __global__ void head_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, long lo
   }
 }
 
+// Decode-sized variant (few rows): a thread-block cluster of kClusterRow CTAs shares one row, each
+// CTA reduces and normalises N / kClusterRow columns and the row's sum of squares is combined
+// through distributed shared memory.  32 rows then occupy 256 CTAs instead of 32.
+constexpr int kClusterRow = 8;
+constexpr int kClThreads = 128;
+
+template <bool kHasPartial>
+__global__ void __launch_bounds__(kClThreads) add_rmsnorm_cluster_kernel(
+    const float* __restrict__ partial, int splits, long long split_stride,
+    const __nv_bfloat16* __restrict__ delta, const __nv_bfloat16* __restrict__ resid_in,
+    __nv_bfloat16* __restrict__ resid_out, const __nv_bfloat16* __restrict__ norm_w,
+    __nv_bfloat16* __restrict__ normed, int N, float eps, int unit_offset) {
+  __shared__ float red[kClThreads / 32];
+  __shared__ float cta_ss;
+  pdl_launch_next();
+  pdl_wait_prior();
+  const long long row = blockIdx.x / kClusterRow;
+  uint32_t crank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
+  const int cols = N / kClusterRow;           // columns of this CTA
+  const int c_begin = crank * cols;
+  const int c = c_begin + threadIdx.x * 8;    // one 8-wide vector per thread (cols <= 1024)
+  const bool active = threadIdx.x * 8 < cols;
+  float v[8];
+  float ss = 0.f;
+  if (active) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    if (resid_in != nullptr) {
+      const uint4 r = *reinterpret_cast<const uint4*>(resid_in + row * N + c);
+      const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { acc[2 * j] = __bfloat162float(rp[j].x); acc[2 * j + 1] = __bfloat162float(rp[j].y); }
+    }
+    if (delta != nullptr) {
+      const uint4 r = *reinterpret_cast<const uint4*>(delta + row * N + c);
+      const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { acc[2 * j] += __bfloat162float(rp[j].x); acc[2 * j + 1] += __bfloat162float(rp[j].y); }
+    }
+    if (kHasPartial) {
+#pragma unroll 8
+      for (int z = 0; z < splits; ++z) {
+        const float4* pp = reinterpret_cast<const float4*>(partial + z * split_stride + row * N + c);
+        const float4 a = __ldcs(pp), b = __ldcs(pp + 1);
+        acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+        acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+      }
+    }
+    uint4 o;
+    uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      op[j] = pack_bf16x2(acc[2 * j], acc[2 * j + 1]);
+      const __nv_bfloat162 b2 = *reinterpret_cast<__nv_bfloat162*>(&op[j]);
+      v[2 * j] = __bfloat162float(b2.x);
+      v[2 * j + 1] = __bfloat162float(b2.y);
+      ss += v[2 * j] * v[2 * j] + v[2 * j + 1] * v[2 * j + 1];
+    }
+    if (resid_out != nullptr) *reinterpret_cast<uint4*>(resid_out + row * N + c) = o;
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < kClThreads / 32; ++w) t += red[w];
+    cta_ss = t;
+  }
+  // every CTA of the cluster publishes its partial sum, then reads all eight in rank order
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  float tot = 0.f;
+  const uint32_t local = smem_u32(&cta_ss);
+#pragma unroll
+  for (uint32_t r = 0; r < kClusterRow; ++r) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(r));
+    float f;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(f) : "r"(remote));
+    tot += f;
+  }
+  // nobody may exit (and release its shared memory) before all peers have read it
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (normed == nullptr || !active) return;
+  const float inv = rsqrtf(tot / static_cast<float>(N) + eps);
+  const uint4 wv = *reinterpret_cast<const uint4*>(norm_w + c);
+  const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
+  uint4 o;
+  uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float w0 = __bfloat162float(wp[j].x), w1 = __bfloat162float(wp[j].y);
+    if (unit_offset) { w0 += 1.f; w1 += 1.f; }
+    op[j] = pack_bf16x2(v[2 * j] * inv * w0, v[2 * j + 1] * inv * w1);
+  }
+  *reinterpret_cast<uint4*>(normed + row * N + c) = o;
+}
+
+template <typename K, typename... Args>
+cudaError_t launch_cluster(K kern, dim3 grid, dim3 block, cudaStream_t stream, bool pdl, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = 0; cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kClusterRow; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 template <typename K, typename... Args>
 cudaError_t launch_pdl(K kern, dim3 grid, dim3 block, cudaStream_t stream, bool pdl, Args... args) {
   cudaLaunchConfig_t cfg = {};
@@ -172,6 +284,16 @@ const char* add_rmsnorm(const float* partial, int splits, const void* delta, con
   auto* ro = static_cast<__nv_bfloat16*>(resid_out);
   auto* w = static_cast<const __nv_bfloat16*>(norm_w);
   auto* no = static_cast<__nv_bfloat16*>(normed);
+  if (T <= 128 && N % (8 * kClusterRow) == 0 && N / kClusterRow <= kClThreads * 8) {
+    const dim3 grid(T * kClusterRow);
+    if (partial != nullptr && splits > 0)
+      e = launch_cluster(add_rmsnorm_cluster_kernel<true>, grid, dim3(kClThreads), stream, pdl, partial, splits,
+                         stride, d, ri, ro, w, no, N, eps, unit_offset);
+    else
+      e = launch_cluster(add_rmsnorm_cluster_kernel<false>, grid, dim3(kClThreads), stream, pdl, partial, 0, stride,
+                         d, ri, ro, w, no, N, eps, unit_offset);
+    return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+  }
   if (partial != nullptr && splits > 0)
     e = launch_pdl(add_rmsnorm_kernel<true>, dim3(T), dim3(kThreads), stream, pdl, partial, splits, stride,
                    d, ri, ro, w, no, N, eps, unit_offset);

@@ -234,7 +234,7 @@ void paged_attention(const Tensor& q, int64_t n_q_heads, int64_t n_kv_heads, int
 
 void causal_conv1d_silu(const Tensor& x, int64_t c_off, int64_t C, const Tensor& w, const Tensor& cu_seqlens,
                         const Tensor& token_seq, const Tensor& state_slot, const Tensor& conv_state,
-                        const Tensor& out, bool update_state, bool pdl) {
+                        const Tensor& out, bool update_state, bool one_token_per_seq, bool pdl) {
   need(x, at::kBFloat16, "x"); need_rows(x, "x"); need(w, at::kBFloat16, "w");
   need(cu_seqlens, at::kInt, "cu_seqlens"); need(token_seq, at::kInt, "token_seq");
   need(state_slot, at::kInt, "state_slot"); need(conv_state, at::kBFloat16, "conv_state");
@@ -255,6 +255,7 @@ void causal_conv1d_silu(const Tensor& x, int64_t c_off, int64_t C, const Tensor&
   p.conv_state = static_cast<__nv_bfloat16*>(conv_state.data_ptr());
   p.out = static_cast<__nv_bfloat16*>(out.data_ptr());
   p.update_state = update_state ? 1 : 0;
+  p.one_token_per_seq = one_token_per_seq ? 1 : 0;
   chk(nfb::causal_conv1d_silu(p, cur_stream(), pdl));
 }
 
@@ -463,7 +464,7 @@ TORCH_LIBRARY(nfb200, m) {
   m.def("embed_gather(Tensor ids, Tensor table, Tensor out, bool pdl) -> ()", &embed_gather);
   m.def("attn_prep(Tensor proj, int q_off, int k_off, int v_off, int n_q_heads, int n_kv_heads, int head_dim, Tensor? q_norm_w, Tensor? k_norm_w, float eps, bool unit_offset, int rot_dim, Tensor inv_freq, float attn_factor, Tensor rope_pos, Tensor token_seq, Tensor cache_pos, Tensor block_table, Tensor q_out, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, bool pdl) -> ()", &attn_prep);
   m.def("paged_attention(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, int split_keys, int n_splits, Tensor part_o, Tensor part_ml, Tensor? gate, Tensor out, Tensor? tree_mask, Tensor? tree_base, bool pdl) -> ()", &paged_attention);
-  m.def("causal_conv1d_silu(Tensor x, int c_off, int C, Tensor w, Tensor cu_seqlens, Tensor token_seq, Tensor state_slot, Tensor conv_state, Tensor out, bool update_state, bool pdl) -> ()", &causal_conv1d_silu);
+  m.def("causal_conv1d_silu(Tensor x, int c_off, int C, Tensor w, Tensor cu_seqlens, Tensor token_seq, Tensor state_slot, Tensor conv_state, Tensor out, bool update_state, bool one_token_per_seq, bool pdl) -> ()", &causal_conv1d_silu);
   m.def("gdn_recurrent(Tensor qkv, int q_off, int k_off, int v_off, Tensor proj, int z_off, int a_off, int b_off, int n_qk_heads, int n_v_heads, Tensor A_log, Tensor dt_bias, Tensor norm_w, float eps, Tensor cu_seqlens, Tensor state_slot, Tensor state, bool write_state, Tensor out, bool pdl) -> ()", &gdn_recurrent);
   m.def("argmax_rows(Tensor logits, Tensor out, bool pdl) -> ()", &argmax_rows);
   m.def("sample_rows(Tensor logits, Tensor? temperature, Tensor? top_k, Tensor? top_p, Tensor? min_p, Tensor? presence, Tensor? frequency, Tensor? token_counts, Tensor? seeds, Tensor? positions, int purpose, Tensor out, Tensor? out_prob) -> ()", &sample_rows);

@@ -41,18 +41,22 @@ class StepBatch:
     max_kv_len: int            # host copy, picks the attention split geometry
     n_tokens: int
     n_seqs: int
+    one_token_per_seq: bool = False
 
 
 class Workspace:
     """Activation buffers for up to `max_tokens` tokens; addresses are stable across steps."""
 
     def __init__(self, cfg: ModelConfig, max_tokens: int, max_logit_rows: int, device, max_splits_attn: int = 64,
-                 shard: Optional["ShardGeometry"] = None):
+                 shard: Optional["ShardGeometry"] = None, x_buffer: Optional[torch.Tensor] = None):
         g = shard or ShardGeometry.full(cfg)
         bf, dev = torch.bfloat16, device
         T, h = max_tokens, cfg.hidden
         self.max_tokens = T
-        self.x = torch.empty((T, h), dtype=bf, device=dev)         # residual stream
+        # residual stream; under tensor parallelism it lives in the symmetric buffer peers store into
+        self.x = x_buffer if x_buffer is not None else torch.empty((T, h), dtype=bf, device=dev)
+        if self.x.shape[0] < T or self.x.shape[1] != h:
+            raise ValueError("residual buffer is too small for the workspace")
         self.normed = torch.empty((T, h), dtype=bf, device=dev)
         wide = max(g.attn_in_dim, g.gdn_in_dim)
         self.proj = torch.empty((T, wide), dtype=bf, device=dev)
@@ -150,7 +154,7 @@ class LaunchCounter:
                 fn = raw
             elif name == "causal_conv1d_silu":
                 def fn(*a, _raw=raw):
-                    self.count += 2 if a[9] else 1  # + history roll when update_state
+                    self.count += 2 if (a[9] and not a[10]) else 1  # + history roll unless the decode fast path
                     return _raw(*a)
             else:
                 k = self.KERNELS.get(name, 1)
@@ -239,7 +243,7 @@ class HybridModel:
         C = g.gdn_conv_dim
         conv = ws.conv[:T]
         ops.causal_conv1d_silu(proj, 0, C, self.w[f"{prefix}/gdn/conv_w"], b.cu_seqlens, b.token_seq, b.state_slot,
-                               st.conv[gi], conv, write_state, self.pdl)
+                               st.conv[gi], conv, write_state, b.n_tokens == b.n_seqs and b.one_token_per_seq, self.pdl)
         qk = g.gdn_qk_dim
         out = ws.mix_gdn[:T]
         ops.gdn_recurrent(conv, 0, qk, 2 * qk, proj, C, C + g.gdn_v_dim, C + g.gdn_v_dim + g.gdn_v_heads,
@@ -300,6 +304,10 @@ class HybridModel:
             return ws.next_ids[:0]
         lg = self.logits(ws, b, hidden)
         out = ws.next_ids[: lg.shape[0]]
-        self.ops.argmax_rows(lg, out, self.pdl)
+        if self.comm is not None:
+            self.comm.argmax(self, lg, out)
+            self.ops.count += 1
+        else:
+            self.ops.argmax_rows(lg, out, self.pdl)
         self.ops.launches_last_forward = self.ops.count - start
         return out

@@ -100,4 +100,5 @@ class StepBuffers:
                          table_row=self._dview("table_row", T), cache_pos=self._dview("cache_pos", T), rope_pos=rp,
                          kv_len=self._dview("kv_len", T), cu_seqlens=self._dview("cu_seqlens", B + 1),
                          state_slot=self._dview("state_slot", B), logit_rows=self._dview("logit_rows", n_logit),
-                         max_kv_len=max_kv, n_tokens=T, n_seqs=B)
+                         max_kv_len=max_kv, n_tokens=T, n_seqs=B,
+                         one_token_per_seq=all(len(c.tokens) == 1 for c in chunks))

@@ -45,7 +45,7 @@ class Generator:
                                formats=kv_format, int8_group=int8_group, n_kv_heads=g.n_kv_heads)
         self.states = GdnStatePool(cfg, max_batch, device, n_qk_heads=g.gdn_qk_heads, n_v_heads=g.gdn_v_heads)
         cap = max(prefill_chunk, max_batch)
-        self.ws = Workspace(cfg, cap, max_batch, device, shard=shard)
+        self.ws = Workspace(cfg, cap, max_batch, device, shard=shard, x_buffer=None if comm is None else comm.x)
         self.bufs_prefill = StepBuffers(cap, max_batch, device)
         self.bufs_decode = StepBuffers(max_batch, max_batch, device)
         pin = self.device.type == "cuda"

@@ -147,7 +147,7 @@ def bench_gdn(ops, batch, hk=16, hv=48, iters=20):
     nw = torch.ones(d, dtype=torch.bfloat16, device="cuda")
 
     def fn():
-        ops.causal_conv1d_silu(proj, 0, C, conv_w, cu, seq, seq, conv_state, conv_out, True, False)
+        ops.causal_conv1d_silu(proj, 0, C, conv_w, cu, seq, seq, conv_state, conv_out, True, True, False)
         ops.gdn_recurrent(conv_out, 0, qk, 2 * qk, proj, C, C + vd, C + vd + hv, hk, hv, A, A, nw, 1e-6, cu, seq, ssm,
                           True, out, False)
     med, best = time_op(fn, iters=iters, flush=L2Flusher())

@@ -1,0 +1,71 @@
+"""Worker for the multi-GPU tensor-parallel tests (launched by torch.distributed.run).
+
+Every rank builds the same full random weights, takes its shard, generates greedily with the
+fused peer-memory collectives (and with the NCCL baseline), and rank 0 compares both against a
+single-GPU run of the same weights.  Prints one line starting with TP_OK or TP_FAIL.
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from ninfer_fusion_b200.models.config import TINY_DENSE  # noqa: E402
+from ninfer_fusion_b200.models.weights import random_weights  # noqa: E402
+from ninfer_fusion_b200.parallel.tp import TensorParallel  # noqa: E402
+from ninfer_fusion_b200.runtime.generator import Generator  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    cfg = TINY_DENSE
+    full = random_weights(cfg, dev, seed=7, std=0.05)
+    torch.manual_seed(5)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (21, 70, 5)]
+    n_new = 10
+    results = {}
+    for mode in ("fused", "nccl"):
+        for use_graph in (False, True):
+            comm = TensorParallel(cfg, rank, world, dev, max_tokens=64, mode=mode)
+            gen = Generator(cfg, comm.shard(full), dev, max_batch=4, max_context=256, kv_format="bf16", page_size=16,
+                            prefill_chunk=64, use_graph=use_graph, shard=comm.geometry, comm=comm)
+            results[(mode, use_graph)] = gen.generate(prompts, n_new)
+            torch.cuda.synchronize()
+            dist.barrier()
+    ok = True
+    msg = ""
+    if rank == 0:
+        single = Generator(cfg, full, dev, max_batch=4, max_context=256, kv_format="bf16", page_size=16,
+                           prefill_chunk=64, use_graph=False).generate(prompts, n_new)
+        for key, out in results.items():
+            same = sum(int(a == b) for o, s in zip(out, single) for a, b in zip(o, s))
+            total = sum(len(s) for s in single)
+            # partial sums are reduced in a different order than on one GPU: allow rare near-tie flips
+            if same < 0.8 * total:
+                ok = False
+            msg += f" {key}:{same}/{total}"
+        if results[("fused", False)] != results[("fused", True)]:
+            ok = False
+            msg += " fused graph!=eager"
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.broadcast(flag, 0)
+    # all ranks must produce the same tokens
+    mine = torch.tensor(results[("fused", True)], device=dev)
+    ref = mine.clone()
+    dist.broadcast(ref, 0)
+    if not torch.equal(mine, ref):
+        print(f"TP_FAIL rank {rank} tokens differ from rank 0", flush=True)
+    if rank == 0:
+        print(("TP_OK" if ok else "TP_FAIL") + msg, flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
