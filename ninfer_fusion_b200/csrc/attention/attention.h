@@ -52,9 +52,12 @@ struct PagedAttnParams {
   // position (tree_base[t] + j); keys below tree_base[t] are always visible.
   const unsigned long long* tree_mask;
   const int* tree_base;
+  int impl;  // 0 = pick, 1 = SIMT kernel, 2 = tensor-core (mma.sync) kernel
 };
 // Split-KV paged attention over quantised pages with in-register dequantisation,
 // followed by the (m, l, o) merge fused with the output sigmoid gate.
 const char* paged_attention(const PagedAttnParams& p, cudaStream_t stream, bool pdl);
+// Tensor-core split kernel; cudaErrorNotSupported when the geometry is outside its envelope.
+cudaError_t paged_attention_mma_split(const PagedAttnParams& p, cudaStream_t stream, bool pdl);
 
 }  // namespace nfb

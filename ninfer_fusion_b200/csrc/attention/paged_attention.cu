@@ -290,7 +290,13 @@ const char* paged_attention(const PagedAttnParams& p, cudaStream_t stream, bool 
   if (p.n_splits < 1) return "paged_attention: need at least one split";
   const int G = p.n_q_heads / p.n_kv_heads;
   const dim3 grid(p.Tq, p.n_kv_heads, p.n_splits);
-  cudaError_t e = p.head_dim == 256 ? launch_f<256>(G, grid, p, stream, pdl) : launch_f<128>(G, grid, p, stream, pdl);
+  cudaError_t e = cudaErrorNotSupported;
+  if (p.impl != 1) {
+    e = paged_attention_mma_split(p, stream, pdl);
+    if (e == cudaErrorNotSupported && p.impl == 2) return "paged_attention: geometry not supported by the tensor-core kernel";
+  }
+  if (e == cudaErrorNotSupported)
+    e = p.head_dim == 256 ? launch_f<256>(G, grid, p, stream, pdl) : launch_f<128>(G, grid, p, stream, pdl);
   if (e == cudaErrorInvalidValue) return "paged_attention: unsupported GQA group size or KV format";
   if (e != cudaSuccess) return cudaGetErrorString(e);
   const dim3 mgrid(p.Tq, p.n_q_heads);

@@ -1,0 +1,419 @@
+// Tensor-core split-KV paged attention for decode / small-T verify, head_dim 256.
+//
+// Work item = (query token, kv head, key split), 4 warps.  The GQA group's query
+// heads are the M rows of a 16-row MMA tile.  Per 64-key tile:
+//   1. all threads gather the tile's raw K / V rows from their pages (16-byte
+//      coalesced loads), dequantise (bf16 / fp8-row / int8-group / nvfp4) and
+//      store fp16 into shared memory: K as [key][d], V transposed as [d][key]
+//      (XOR-swizzled) so that both are plain ldmatrix B operands;
+//   2. warp w computes S = Q K^T for keys 16w..16w+15 (mma.sync m16n8k16 f16),
+//      applies the per-row K scale, masks, and publishes its row maxima;
+//   3. a tile-wide running max gives P = exp2(S - m); P (times the per-row V
+//      scale) goes to shared memory as fp16;
+//   4. warp w accumulates O[:, 64w..64w+63] += P V over the tile's 64 keys.
+// Splits cover absolute key ranges and tiles start at split boundaries, so the
+// reduction order for a query depends only on key positions.  Output partials
+// (m, l, un-normalised O) use the same layout as the SIMT kernel and are
+// finished by the same merge kernel.
+//
+// mma.sync is the right tensor path here: the M dimension is the 3..8 query heads
+// of one GQA group, far below the 64/128 rows a tcgen05 tile needs.
+#include "attention.h"
+
+#include <math_constants.h>
+
+#include "../common/ptx.cuh"
+#include "../kv/codec.cuh"
+
+namespace nfb {
+
+namespace {
+
+constexpr int D = 256;
+constexpr int kTileKeys = 64;
+constexpr int kLdK = D + 8;          // halves per K-tile row
+constexpr int kLdV = kTileKeys + 8;  // halves per V^T-tile row
+constexpr int kLdP = kTileKeys + 8;
+constexpr int kLdQ = D + 8;
+
+struct Smem {
+  __half k[kTileKeys][kLdK];   // 33,792 B
+  __half vt[D][kLdV];          // 36,864 B
+  __half q[16][kLdQ];          //  8,448 B
+  __half p[16][kLdP];          //  2,304 B
+  float kscale[kTileKeys];
+  float vscale[kTileKeys];
+  float rowmax[4][16];
+  float rowsum[4][16];
+  long long rowidx[kTileKeys];
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_f16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// One "unit" = 16 consecutive values [16*part, 16*part+16) of a cache row.  Loading (raw bytes into
+// registers) and converting (to 8 packed fp16 pairs) are separate so that a thread can put all of a
+// tile's loads in flight before it converts the first one.  The fp8-row scale is NOT applied here (it
+// multiplies scores / probabilities instead).
+template <int FORMAT>
+struct RawUnit {
+  uint4 a;
+  uint4 b;      // second half of a bf16 unit only
+  float scale;  // int8-group / nvfp4 block scale
+
+  __device__ __forceinline__ void clear() {
+    a = make_uint4(0, 0, 0, 0);
+    b = make_uint4(0, 0, 0, 0);
+    scale = 0.f;
+  }
+  __device__ __forceinline__ void load(const KvLayer& kv, const uint8_t* codes, const uint8_t* scales, long long r,
+                                       int part) {
+    if constexpr (FORMAT == kKvFp8Row) {
+      a = *reinterpret_cast<const uint4*>(codes + r * D + part * 16);
+    } else if constexpr (FORMAT == kKvBf16) {
+      const uint4* src = reinterpret_cast<const uint4*>(codes + r * (2 * D) + part * 32);
+      a = src[0];
+      b = src[1];
+    } else if constexpr (FORMAT == kKvInt8Group) {
+      a = *reinterpret_cast<const uint4*>(codes + r * D + part * 16);
+      scale = __half2float(reinterpret_cast<const __half*>(scales + r * (2 * (D / kv.group)))[part * 16 / kv.group]);
+    } else {
+      const uint2 c = *reinterpret_cast<const uint2*>(codes + r * (D / 2) + part * 8);
+      a = make_uint4(c.x, c.y, 0, 0);
+      scale = e4m3_to_float(scales[r * (D / 16) + part]);
+    }
+  }
+  __device__ __forceinline__ void convert(uint32_t* out) const {
+    if constexpr (FORMAT == kKvFp8Row) {
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w[i] & 0xffff), __NV_E4M3);
+        const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w[i] >> 16), __NV_E4M3);
+        out[2 * i] = *reinterpret_cast<const uint32_t*>(&lo);
+        out[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+      }
+    } else if constexpr (FORMAT == kKvBf16) {
+      const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
+        out[i] = pack_half2(__bfloat162float(v.x), __bfloat162float(v.y));
+      }
+    } else if constexpr (FORMAT == kKvInt8Group) {
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int c0 = static_cast<int8_t>((w[i / 2] >> (16 * (i % 2))) & 0xff);
+        const int c1 = static_cast<int8_t>((w[i / 2] >> (16 * (i % 2) + 8)) & 0xff);
+        out[i] = pack_half2(static_cast<float>(c0) * scale, static_cast<float>(c1) * scale);
+      }
+    } else {
+      const uint32_t w[2] = {a.x, a.y};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint32_t nib2 = (w[i / 4] >> (8 * (i % 4))) & 0xff;
+        out[i] = pack_half2(e2m1_to_float(nib2 & 0xf) * scale, e2m1_to_float(nib2 >> 4) * scale);
+      }
+    }
+  }
+};
+
+template <int FORMAT>
+__global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnParams p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
+
+  pdl_launch_next();
+  pdl_wait_prior();
+  const int t = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = p.n_q_heads / p.n_kv_heads;
+  const int kv_len = p.q_kv_len[t];
+  const int seq = p.q_seq[t];
+  const int k_begin = split * p.split_keys;
+  const int k_end = min(kv_len, k_begin + p.split_keys);
+  const long long part_base = (static_cast<long long>(t) * p.n_q_heads + kvh * G) * p.n_splits + split;
+
+  if (seq < 0 || k_begin >= k_end) {
+    for (int g = threadIdx.x; g < G; g += blockDim.x) {
+      float* ml = p.part_ml + (part_base + static_cast<long long>(g) * p.n_splits) * 2;
+      ml[0] = -CUDART_INF_F;
+      ml[1] = 0.f;
+    }
+    return;
+  }
+
+  // Q rows (g < G valid, rest zero), pre-scaled so that softmax runs on exp2
+  const float qscale = p.sm_scale * 1.4426950408889634f;
+  for (int i = threadIdx.x; i < 16 * (D / 2); i += blockDim.x) {
+    const int g = i / (D / 2), d2 = i % (D / 2);
+    float2 f = make_float2(0.f, 0.f);
+    if (g < G) {
+      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(
+          p.q + (static_cast<long long>(t) * p.n_q_heads + kvh * G + g) * D + 2 * d2);
+      f = make_float2(__bfloat162float(v.x) * qscale, __bfloat162float(v.y) * qscale);
+    }
+    *reinterpret_cast<uint32_t*>(&sm.q[g][2 * d2]) = pack_half2(f.x, f.y);
+  }
+
+  const unsigned long long tmask = p.tree_mask ? p.tree_mask[t] : ~0ull;
+  const int tbase = p.tree_mask ? p.tree_base[t] : 0x7fffffff;
+  const int* table = p.block_table + static_cast<long long>(seq) * p.table_stride;
+  const int P = p.kv.page_size;
+  const int row0 = lane >> 2, cq = lane & 3;  // accumulator rows row0 / row0+8, column pair 2*cq
+
+  float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F};
+  float l_run[2] = {0.f, 0.f};
+  float o[8][4];
+#pragma unroll
+  for (int n = 0; n < 8; ++n)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[n][j] = 0.f;
+
+  for (int kb = k_begin; kb < k_end; kb += kTileKeys) {
+    __syncthreads();  // previous tile fully consumed (also orders the Q stores on the first pass)
+    // ---- 1. gather + dequantise the tile ----
+    if (threadIdx.x < kTileKeys) {
+      const int key = kb + threadIdx.x;
+      long long r = -1;
+      float ks = 0.f, vs = 0.f;
+      if (key < k_end) {
+        const int page = table[key / P];
+        r = (static_cast<long long>(page) * p.kv.n_kv_heads + kvh) * P + key % P;
+        if constexpr (FORMAT == kKvFp8Row) {
+          ks = __half2float(reinterpret_cast<const __half*>(p.kv.k_scales)[r]);
+          vs = __half2float(reinterpret_cast<const __half*>(p.kv.v_scales)[r]);
+        } else {
+          ks = 1.f;
+          vs = 1.f;
+        }
+      }
+      sm.rowidx[threadIdx.x] = r;
+      sm.kscale[threadIdx.x] = ks;
+      sm.vscale[threadIdx.x] = vs;
+    }
+    __syncthreads();
+    // K: unit = (key, part), 1024 units, 8 per thread; consecutive lanes read consecutive 16 values of a row.
+    // All eight loads are issued before the first conversion.
+    {
+      RawUnit<FORMAT> raw[8];
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int u = it * 128 + threadIdx.x;
+        const long long r = sm.rowidx[u >> 4];
+        raw[it].clear();
+        if (r >= 0) raw[it].load(p.kv, p.kv.k_codes, p.kv.k_scales, r, u & 15);
+      }
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int u = it * 128 + threadIdx.x;
+        uint32_t h[8];
+        raw[it].convert(h);
+        uint4* dst = reinterpret_cast<uint4*>(&sm.k[u >> 4][(u & 15) * 16]);
+        dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
+        dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
+      }
+    }
+    // V: unit = (key pair, part), 512 units, 4 per thread; stored transposed, two keys per 32-bit word,
+    // column index XOR-swizzled by the row's 16-row group to spread the transposed stores over banks
+    {
+      RawUnit<FORMAT> raw[8];
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const int u = it * 128 + threadIdx.x;
+        const int jp = u >> 4, part = u & 15;
+        const long long r0 = sm.rowidx[2 * jp], r1 = sm.rowidx[2 * jp + 1];
+        raw[2 * it].clear();
+        raw[2 * it + 1].clear();
+        if (r0 >= 0) raw[2 * it].load(p.kv, p.kv.v_codes, p.kv.v_scales, r0, part);
+        if (r1 >= 0) raw[2 * it + 1].load(p.kv, p.kv.v_codes, p.kv.v_scales, r1, part);
+      }
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const int u = it * 128 + threadIdx.x;
+        const int jp = u >> 4, part = u & 15;
+        uint32_t h0[8], h1[8];
+        raw[2 * it].convert(h0);
+        raw[2 * it + 1].convert(h1);
+        const int col = (2 * jp) ^ ((part & 7) * 8);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          // h0[i] = (v[key0][d], v[key0][d+1]), h1[i] likewise for key1 -> rows d and d+1 get (key0, key1)
+          *reinterpret_cast<uint32_t*>(&sm.vt[part * 16 + 2 * i][col]) = __byte_perm(h0[i], h1[i], 0x5410);
+          *reinterpret_cast<uint32_t*>(&sm.vt[part * 16 + 2 * i + 1][col]) = __byte_perm(h0[i], h1[i], 0x7632);
+        }
+      }
+    }
+    __syncthreads();
+
+    // ---- 2. S = Q K^T for this warp's 16 keys ----
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    {
+      const uint32_t q_addr = smem_u32(&sm.q[(lane & 7) + 8 * ((lane >> 3) & 1)][8 * (lane >> 4)]);
+      const uint32_t k_addr = smem_u32(&sm.k[warp * 16 + (lane & 7) + 8 * (lane >> 4)][8 * ((lane >> 3) & 1)]);
+#pragma unroll 4
+      for (int ks = 0; ks < D / 16; ++ks) {
+        uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+        ldmatrix_x4(q_addr + ks * 32, a0, a1, a2, a3);
+        ldmatrix_x4(k_addr + ks * 32, b0, b1, b2, b3);
+        mma_f16(s[0], a0, a1, a2, a3, b0, b1);
+        mma_f16(s[1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+    float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int kl = warp * 16 + n * 8 + 2 * cq + (j & 1);  // key inside the tile
+        const int key = kb + kl;
+        bool valid = key < k_end;
+        if (valid && key >= tbase) valid = (tmask >> (key - tbase)) & 1ull;
+        const float v = valid ? s[n][j] * sm.kscale[kl] : -CUDART_INF_F;
+        s[n][j] = v;
+        mx[j >> 1] = fmaxf(mx[j >> 1], v);
+      }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+    }
+    if (cq == 0) {
+      sm.rowmax[warp][row0] = mx[0];
+      sm.rowmax[warp][row0 + 8] = mx[1];
+    }
+    __syncthreads();
+
+    // ---- 3. tile-wide running max, P to shared memory ----
+    float corr[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = row0 + 8 * h;
+      const float mt = fmaxf(fmaxf(sm.rowmax[0][r], sm.rowmax[1][r]), fmaxf(sm.rowmax[2][r], sm.rowmax[3][r]));
+      const float mn = fmaxf(m_run[h], mt);
+      corr[h] = (mn == -CUDART_INF_F) ? 1.f : exp2f(m_run[h] - mn);
+      m_run[h] = mn;
+      l_run[h] *= corr[h];
+    }
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+      const int kl = warp * 16 + n * 8 + 2 * cq;
+      float pv[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float mn = m_run[j >> 1];
+        pv[j] = (s[n][j] == -CUDART_INF_F) ? 0.f : exp2f(s[n][j] - mn);
+        l_run[j >> 1] += pv[j];
+        pv[j] *= sm.vscale[kl + (j & 1)];
+      }
+      *reinterpret_cast<uint32_t*>(&sm.p[row0][kl]) = pack_half2(pv[0], pv[1]);
+      *reinterpret_cast<uint32_t*>(&sm.p[row0 + 8][kl]) = pack_half2(pv[2], pv[3]);
+    }
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      o[n][0] *= corr[0]; o[n][1] *= corr[0];
+      o[n][2] *= corr[1]; o[n][3] *= corr[1];
+    }
+    __syncthreads();
+
+    // ---- 4. O[:, 64*warp .. +63] += P V ----
+    {
+      const uint32_t p_addr = smem_u32(&sm.p[(lane & 7) + 8 * ((lane >> 3) & 1)][8 * (lane >> 4)]);
+#pragma unroll
+      for (int kk = 0; kk < kTileKeys / 16; ++kk) {
+        uint32_t a0, a1, a2, a3;
+        ldmatrix_x4(p_addr + kk * 32, a0, a1, a2, a3);
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+          const int d = warp * 64 + np * 16 + (lane & 7) + 8 * (lane >> 4);  // V^T row
+          const int col = (kk * 16 + 8 * ((lane >> 3) & 1)) ^ (((d >> 4) & 7) * 8);
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4(smem_u32(&sm.vt[d][col]), b0, b1, b2, b3);
+          mma_f16(o[2 * np], a0, a1, a2, a3, b0, b1);
+          mma_f16(o[2 * np + 1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+    }
+  }
+
+  // ---- row sums: quad reduce, then across warps ----
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+  __syncthreads();
+  if (cq == 0) {
+    sm.rowsum[warp][row0] = l_run[0];
+    sm.rowsum[warp][row0 + 8] = l_run[1];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int g = row0 + 8 * h;
+    if (g < G) {
+      const long long pb = part_base + static_cast<long long>(g) * p.n_splits;
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        const int d = warp * 64 + n * 8 + 2 * cq;
+        *reinterpret_cast<float2*>(p.part_o + pb * D + d) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
+      }
+      if (warp == 0 && cq == 0) {
+        p.part_ml[pb * 2] = m_run[h];
+        p.part_ml[pb * 2 + 1] = sm.rowsum[0][g] + sm.rowsum[1][g] + sm.rowsum[2][g] + sm.rowsum[3][g];
+      }
+    }
+  }
+}
+
+template <int FORMAT>
+cudaError_t launch_fmt(const PagedAttnParams& p, cudaStream_t stream, bool pdl) {
+  auto kern = paged_attn_mma_kernel<FORMAT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, sizeof(Smem));
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.Tq, p.n_kv_heads, p.n_splits);
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = sizeof(Smem);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
+}  // namespace
+
+// Returns cudaErrorNotSupported when the geometry is outside this kernel (caller falls back to SIMT).
+cudaError_t paged_attention_mma_split(const PagedAttnParams& p, cudaStream_t stream, bool pdl) {
+  const int G = p.n_q_heads / p.n_kv_heads;
+  if (p.head_dim != D || G > 16 || p.split_keys % kTileKeys) return cudaErrorNotSupported;
+  if (p.kv.format == kKvInt8Group && (p.kv.group % 16)) return cudaErrorNotSupported;
+  switch (p.kv.format) {
+    case kKvBf16: return launch_fmt<kKvBf16>(p, stream, pdl);
+    case kKvFp8Row: return launch_fmt<kKvFp8Row>(p, stream, pdl);
+    case kKvInt8Group: return launch_fmt<kKvInt8Group>(p, stream, pdl);
+    case kKvNvfp4: return launch_fmt<kKvNvfp4>(p, stream, pdl);
+    default: return cudaErrorNotSupported;
+  }
+}
+
+}  // namespace nfb

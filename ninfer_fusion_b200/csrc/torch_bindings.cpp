@@ -192,7 +192,7 @@ void paged_attention(const Tensor& q, int64_t n_q_heads, int64_t n_kv_heads, int
                      const Tensor& q_kv_len, const Tensor& block_table, const Tensor& k_codes, const Tensor& v_codes,
                      OptT k_scales, OptT v_scales, int64_t page_size, int64_t format, int64_t group, double sm_scale,
                      int64_t split_keys, int64_t n_splits, const Tensor& part_o, const Tensor& part_ml, OptT gate,
-                     const Tensor& out, OptT tree_mask, OptT tree_base, bool pdl) {
+                     const Tensor& out, OptT tree_mask, OptT tree_base, int64_t impl, bool pdl) {
   need(q, at::kBFloat16, "q"); need(q_seq, at::kInt, "q_seq"); need(q_kv_len, at::kInt, "q_kv_len");
   need(block_table, at::kInt, "block_table"); need(part_o, at::kFloat, "part_o"); need(part_ml, at::kFloat, "part_ml");
   need(out, at::kBFloat16, "out");
@@ -229,6 +229,7 @@ void paged_attention(const Tensor& q, int64_t n_q_heads, int64_t n_kv_heads, int
     p.tree_mask = static_cast<const unsigned long long*>(tree_mask->data_ptr());
     p.tree_base = static_cast<const int*>(tree_base->data_ptr());
   }
+  p.impl = static_cast<int>(impl);
   chk(nfb::paged_attention(p, cur_stream(), pdl));
 }
 
@@ -463,7 +464,7 @@ TORCH_LIBRARY(nfb200, m) {
   m.def("add_rmsnorm(Tensor? partial, int splits, Tensor? delta, Tensor? resid_in, Tensor? resid_out, Tensor? norm_w, Tensor? normed, int T, int N, float eps, bool unit_offset, bool pdl) -> ()", &add_rmsnorm);
   m.def("embed_gather(Tensor ids, Tensor table, Tensor out, bool pdl) -> ()", &embed_gather);
   m.def("attn_prep(Tensor proj, int q_off, int k_off, int v_off, int n_q_heads, int n_kv_heads, int head_dim, Tensor? q_norm_w, Tensor? k_norm_w, float eps, bool unit_offset, int rot_dim, Tensor inv_freq, float attn_factor, Tensor rope_pos, Tensor token_seq, Tensor cache_pos, Tensor block_table, Tensor q_out, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, bool pdl) -> ()", &attn_prep);
-  m.def("paged_attention(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, int split_keys, int n_splits, Tensor part_o, Tensor part_ml, Tensor? gate, Tensor out, Tensor? tree_mask, Tensor? tree_base, bool pdl) -> ()", &paged_attention);
+  m.def("paged_attention(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, int split_keys, int n_splits, Tensor part_o, Tensor part_ml, Tensor? gate, Tensor out, Tensor? tree_mask, Tensor? tree_base, int impl, bool pdl) -> ()", &paged_attention);
   m.def("causal_conv1d_silu(Tensor x, int c_off, int C, Tensor w, Tensor cu_seqlens, Tensor token_seq, Tensor state_slot, Tensor conv_state, Tensor out, bool update_state, bool one_token_per_seq, bool pdl) -> ()", &causal_conv1d_silu);
   m.def("gdn_recurrent(Tensor qkv, int q_off, int k_off, int v_off, Tensor proj, int z_off, int a_off, int b_off, int n_qk_heads, int n_v_heads, Tensor A_log, Tensor dt_bias, Tensor norm_w, float eps, Tensor cu_seqlens, Tensor state_slot, Tensor state, bool write_state, Tensor out, bool pdl) -> ()", &gdn_recurrent);
   m.def("argmax_rows(Tensor logits, Tensor out, bool pdl) -> ()", &argmax_rows);

@@ -179,6 +179,7 @@ class HybridModel:
         self.prefix = prefix
         self.inv_freq = rope_inv_freq(cfg.rot_dim, cfg.rope_theta).to(self.device)
         self.sm_scale = 1.0 / math.sqrt(cfg.head_dim)
+        self.attn_impl = 0  # 0 = pick, 1 = SIMT, 2 = tensor-core split-KV attention
         self.comm = None  # tensor-parallel communicator (parallel.tp), None on one GPU
         # layer index -> index among attention / GDN layers
         self._attn_idx = {l: i for i, l in enumerate(cfg.attn_layers)}
@@ -230,7 +231,7 @@ class HybridModel:
             ops.paged_attention(q[t0:t1], g.n_q_heads, g.n_kv_heads, D, b.table_row[t0:t1], b.kv_len[t0:t1], kv.table,
                                 planes.k_codes, planes.v_codes, planes.k_scales, planes.v_scales, kv.page_size,
                                 planes.fmt, planes.group, self.sm_scale, split, n_splits, ws.part_o, ws.part_ml,
-                                gate[t0:t1], out[t0:t1], None, None, self.pdl)
+                                gate[t0:t1], out[t0:t1], None, None, self.attn_impl, self.pdl)
         return out, self.w[f"{prefix}/attn/o_proj"]
 
     def _gdn_layer(self, ws: Workspace, b: StepBatch, st: GdnStatePool, layer: int, T: int, prefix: str,

@@ -97,7 +97,7 @@ DECODE_27B = [("attn_in", 14336, 5120, "store"), ("gdn_in", 16480, 5120, "store"
               ("o_proj", 5120, 6144, "partial"), ("down", 5120, 17408, "partial"), ("lm_head", 248320, 5120, "store")]
 
 
-def bench_attn(ops, batch, ctx, kv, hq=24, hkv=4, D=256, P=64, iters=20):
+def bench_attn(ops, batch, ctx, kv, hq=24, hkv=4, D=256, P=64, iters=20, impl=0):
     fmt = R.KV_FORMAT_NAMES[kv]
     group = 64 if fmt == R.KV_INT8_GROUP else (16 if fmt == R.KV_NVFP4 else D)
     rb = 2 * D if fmt == R.KV_BF16 else (D // 2 if fmt == R.KV_NVFP4 else D)
@@ -122,11 +122,11 @@ def bench_attn(ops, batch, ctx, kv, hq=24, hkv=4, D=256, P=64, iters=20):
 
     def fn():
         ops.paged_attention(q, hq, hkv, D, seq, lens, table, k, v, ks, vs, P, fmt, group, D ** -0.5, split, n_splits,
-                            part_o, part_ml, None, out, None, None, False)
+                            part_o, part_ml, None, out, None, None, impl, False)
     med, best = time_op(fn, iters=iters, flush=L2Flusher())
     byts = 2 * batch * ctx * hkv * (rb + sb)
     bw, _, how = measured_peaks()
-    return {"op": "paged_attention", "batch": batch, "ctx": ctx, "kv": kv, "split_keys": split, "n_splits": n_splits,
+    return {"op": "paged_attention", "impl": impl, "batch": batch, "ctx": ctx, "kv": kv, "split_keys": split, "n_splits": n_splits,
             "us": round(med * 1e6, 2), "GBps": round(byts / med / 1e9, 1), "frac_hbm": round(byts / med / bw, 3), "peaks": how}
 
 
@@ -188,7 +188,8 @@ def main(argv=None):
             rows.append(r)
     if a.what in ("attn", "all"):
         for kv in (["bf16", "fp8", "int8", "nvfp4"] if a.what == "all" else [a.kv]):
-            rows.append(bench_attn(ops, a.batch, a.ctx, kv, iters=a.iters))
+            for impl in (1, 2):
+                rows.append(bench_attn(ops, a.batch, a.ctx, kv, iters=a.iters, impl=impl))
     if a.what in ("gdn", "all"):
         rows.append(bench_gdn(ops, a.batch, iters=a.iters))
     for r in rows:

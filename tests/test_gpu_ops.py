@@ -79,14 +79,16 @@ def test_prep_append_and_paged_attention(ops, name, fmt, group, hq, hkv, D, P):
     q = q_out[q_rows_t].contiguous()
     Tq = q.shape[0]
     gate = torch.randn(Tq, hq * D).to(torch.bfloat16).cuda()
-    for split_keys in (128, 512):
+    for split_keys, impl in ((128, 1), (512, 1), (128, 2), (512, 2)):
+        if impl == 2 and D != 256:
+            continue
         n_splits = (max(lens) + split_keys - 1) // split_keys
         part_o = torch.empty(Tq * hq * n_splits * D, device="cuda")
         part_ml = torch.empty(Tq * hq * n_splits * 2, device="cuda")
         out = torch.empty((Tq, hq * D), dtype=torch.bfloat16, device="cuda")
         ops.paged_attention(q, hq, hkv, D, torch.tensor(q_seq).int().cuda(), torch.tensor(q_len).int().cuda(), perm,
                             k_codes, v_codes, k_sc, v_sc, P, fmt, group, 1 / math.sqrt(D), split_keys, n_splits,
-                            part_o, part_ml, gate, out, None, None, False)
+                            part_o, part_ml, gate, out, None, None, impl, False)
         start = 0
         seq_start = [0]
         for n in lens:
@@ -97,7 +99,7 @@ def test_prep_append_and_paged_attention(ops, name, fmt, group, hq, hkv, D, P):
             o = R.gqa_attention(q[i:i + 1].float().cpu(), ks_, vs_, torch.tensor([q_len[i]]))
             o = R.bf16_round(o).view(-1) * torch.sigmoid(gate[i].float().cpu())
             err = (out[i].float().cpu() - o).abs().max().item()
-            assert err < 0.03, f"{name} split {split_keys} query {i}: err {err}"
+            assert err < 0.03, f"{name} split {split_keys} impl {impl} query {i}: err {err}"
 
 
 def test_paged_attention_tree_mask(ops):
@@ -122,9 +124,18 @@ def test_paged_attention_tree_mask(ops):
     out = torch.empty((W, hq * D), dtype=torch.bfloat16, device="cuda")
     part_o = torch.empty(W * hq * D, device="cuda")
     part_ml = torch.empty(W * hq * 2, device="cuda")
-    ops.paged_attention(q, hq, hkv, D, torch.zeros(W).int().cuda(), torch.full((W,), L + W).int().cuda(), table,
-                        k_codes, v_codes, None, None, P, R.KV_BF16, D, 1 / 16, 128, 1, part_o, part_ml, None, out,
-                        masks, base, False)
+    vis = torch.zeros(W, L + W, dtype=torch.bool)
+    vis[:, :L] = True
+    for j, row in enumerate(anc):
+        for a in row:
+            vis[j, L + a] = True
+    ref = R.gqa_attention(q.float().cpu(), R.bf16_round(k), R.bf16_round(v), None, 1 / 16, vis).reshape(W, -1)
+    for impl in (1, 2):
+        out.zero_()
+        ops.paged_attention(q, hq, hkv, D, torch.zeros(W).int().cuda(), torch.full((W,), L + W).int().cuda(), table,
+                            k_codes, v_codes, None, None, P, R.KV_BF16, D, 1 / 16, 128, 1, part_o, part_ml, None, out,
+                            masks, base, impl, False)
+        assert (out.float().cpu() - ref).abs().max().item() < 0.02, f"impl {impl}"
     vis = torch.zeros(W, L + W, dtype=torch.bool)
     vis[:, :L] = True
     for j, row in enumerate(anc):
