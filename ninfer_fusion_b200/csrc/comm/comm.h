@@ -16,7 +16,28 @@ struct TpState {
   unsigned int ctas_done;
   unsigned int row_calls[kTpMaxRows];     // finished reduce calls per token row
   unsigned int argmax_calls[kTpMaxRows];  // finished arg-max exchanges per token row
+  unsigned int call_idx;                  // finished one-shot (push-all) reductions; parity = receive buffer
+  unsigned int expected_all;              // cumulative push-all arrivals consumed so far
+  unsigned int ctas_done_all;
 };
+
+// Decode-sized all-reduce finish: the GEMMs of all ranks pushed fp32 tiles into this rank's buffer
+// [parity][src_rank][T_cap][N] (gemm kEpiPushAll); sum the `world` sources in rank order, add the residual,
+// round to bf16 and RMS-normalise.  Every rank computes the identical full row, so nothing is gathered.
+struct TpSumNormParams {
+  int world, T, T_cap, N;
+  unsigned int arrivals_this_call;   // world * (column tiles) * (token tiles)
+  const float* my_recv;
+  const unsigned int* my_flag;
+  __nv_bfloat16* x;                  // [T, N] residual stream, updated in place (local memory)
+  const __nv_bfloat16* norm_w;
+  __nv_bfloat16* normed;             // [T, N], may be null
+  float eps;
+  int unit_offset;
+  TpState* state;
+  int* status;
+};
+const char* tp_sum_norm(const TpSumNormParams& p, cudaStream_t stream, bool pdl);
 
 struct TpReduceParams {
   int world, rank, T, T_cap, N, splits;

@@ -204,7 +204,117 @@ __global__ void __launch_bounds__(1024) tp_argmax_kernel(const TpArgmaxParams p)
   st->argmax_calls[t] = epoch + 1u;
 }
 
+// ---- one-shot all-reduce finish (decode sizes): 8-CTA cluster per row ----
+constexpr int kRowCluster = 8;
+constexpr int kRowThreads = 128;
+
+__global__ void __launch_bounds__(kRowThreads) tp_sum_norm_kernel(const TpSumNormParams p) {
+  __shared__ float red[kRowThreads / 32];
+  __shared__ float cta_ss;
+  __shared__ int ok_s;
+  pdl_launch_next();
+  pdl_wait_prior();
+  TpState* st = p.state;
+  const long long row = blockIdx.x / kRowCluster;
+  uint32_t crank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
+  const int cols = p.N / kRowCluster;
+  const int c = crank * cols + threadIdx.x * 8;
+  const bool active = threadIdx.x * 8 < cols;
+  const uint32_t target = st->expected_all + p.arrivals_this_call;
+  const uint32_t par = st->call_idx & 1u;
+  if (threadIdx.x == 0) ok_s = wait_counter(p.my_flag, target, p.status) ? 1 : 0;
+  __syncthreads();
+  float v[8];
+  float ss = 0.f;
+  if (active && ok_s) {
+    float acc[8];
+    const uint4 r = *reinterpret_cast<const uint4*>(p.x + row * p.N + c);
+    const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { acc[2 * j] = __bfloat162float(rp[j].x); acc[2 * j + 1] = __bfloat162float(rp[j].y); }
+    for (int src = 0; src < p.world; ++src) {
+      const float4* pp = reinterpret_cast<const float4*>(
+          p.my_recv + ((static_cast<long long>(par) * p.world + src) * p.T_cap + row) * p.N + c);
+      const float4 a = __ldcg(pp), b = __ldcg(pp + 1);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+      acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    uint4 o;
+    uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      op[j] = pack_bf16x2(acc[2 * j], acc[2 * j + 1]);
+      const __nv_bfloat162 b2 = *reinterpret_cast<__nv_bfloat162*>(&op[j]);
+      v[2 * j] = __bfloat162float(b2.x);
+      v[2 * j + 1] = __bfloat162float(b2.y);
+      ss += v[2 * j] * v[2 * j] + v[2 * j + 1] * v[2 * j + 1];
+    }
+    *reinterpret_cast<uint4*>(p.x + row * p.N + c) = o;
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < kRowThreads / 32; ++w) t += red[w];
+    cta_ss = t;
+  }
+  cluster_sync_all();
+  float tot = 0.f;
+  const uint32_t local = smem_u32(&cta_ss);
+#pragma unroll
+  for (uint32_t r = 0; r < kRowCluster; ++r) {
+    float f;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(f) : "r"(mapa_shared(local, r)));
+    tot += f;
+  }
+  cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
+  if (p.normed != nullptr && active && ok_s) {
+    const float inv = rsqrtf(tot / static_cast<float>(p.N) + p.eps);
+    const uint4 wv = *reinterpret_cast<const uint4*>(p.norm_w + c);
+    const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
+    uint4 o;
+    uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float w0 = __bfloat162float(wp[j].x), w1 = __bfloat162float(wp[j].y);
+      if (p.unit_offset) { w0 += 1.f; w1 += 1.f; }
+      op[j] = pack_bf16x2(v[2 * j] * inv * w0, v[2 * j + 1] * inv * w1);
+    }
+    *reinterpret_cast<uint4*>(p.normed + row * p.N + c) = o;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int done = atomicAdd(&st->ctas_done_all, 1u);
+    if (done == gridDim.x - 1) {
+      st->expected_all = target;
+      st->call_idx = st->call_idx + 1u;
+      st->ctas_done_all = 0;
+      __threadfence();
+    }
+  }
+}
+
 }  // namespace
+
+const char* tp_sum_norm(const TpSumNormParams& p, cudaStream_t stream, bool pdl) {
+  if (p.T <= 0) return nullptr;
+  if (p.T > p.T_cap) return "tp_sum_norm: too many rows for the receive buffer";
+  if (p.N % (8 * kRowCluster) || p.N / kRowCluster > kRowThreads * 8) return "tp_sum_norm: unsupported row width";
+  if (p.normed != nullptr && p.norm_w == nullptr) return "tp_sum_norm: normed output without weight";
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.T * kRowCluster); cfg.blockDim = dim3(kRowThreads); cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kRowCluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl ? 2 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, tp_sum_norm_kernel, p);
+  return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
 
 const char* tp_reduce_ag_norm(const TpReduceParams& p, cudaStream_t stream, bool pdl) {
   if (p.T <= 0) return nullptr;

@@ -13,6 +13,9 @@ enum GemmEpilogue : int {
   kEpiPushPartial = 4,  // tensor parallel: fp32 partial tiles are stored into the OWNER rank's receive
                         // buffer [src_rank][split][T][N/world] over NVLink, then the owner's arrival
                         // counter is incremented (GEMM -> reduce-scatter in one kernel)
+  kEpiPushAll = 5,      // tensor parallel, decode sizes: the fp32 tile is stored into EVERY rank's receive
+                        // buffer [parity][src_rank][T_cap][N] (one-shot all-reduce by push) and every
+                        // rank's arrival counter is incremented (GEMM -> all-reduce in one kernel)
 };
 
 constexpr int kMaxRanks = 8;
@@ -33,8 +36,12 @@ struct GemmArgs {
   int* status = nullptr;    // device status word (see common/ptx.cuh)
   cudaStream_t stream = nullptr;
   bool pdl = false;         // launch with programmatic stream serialization
-  // kEpiPushPartial only
+  // `splits` > 1 with kEpiStore / kEpiResidual / kEpiSwiglu / kEpiPushAll = in-cluster split-K: that many
+  // CTAs (a power of two, see gemm_max_cluster) share one output tile and reduce through DSMEM.
+  // kEpiPushPartial / kEpiPushAll only
   int world = 1, rank = 0;
+  int T_cap = 0;                          // rows of the receive buffer (kEpiPushAll)
+  const unsigned int* call_idx = nullptr; // device counter whose parity selects the receive buffer
   float* peer_recv[kMaxRanks] = {};
   unsigned int* peer_flag[kMaxRanks] = {};
 };
@@ -44,6 +51,7 @@ const char* gemm_bf16(const GemmArgs& args);
 
 // Token-tile width the kernel will use for T tokens (16, 32, 64, 128 or 256).
 int gemm_tile_tokens(int T);
+int gemm_max_cluster(int tile_tokens);
 // Split-K factor that fills `sm_count` SMs for a decode-shaped problem.
 int gemm_pick_splits(int T, int N, int K, int epi, int sm_count);
 

@@ -53,6 +53,11 @@ struct KernelParams {
   float* peer_recv[kMaxRanks];
   unsigned int* peer_flag[kMaxRanks];
   int rank, slice_cols;
+  // in-cluster split-K: `cluster` CTAs along z share one output tile and reduce through DSMEM
+  int cluster;
+  // kEpiPushAll: one-shot all-reduce by push into [parity][src_rank][T_cap][N] on every rank
+  int world, T_cap;
+  const unsigned int* call_idx;  // device counter of finished reduce calls; its parity picks the buffer
 };
 
 template <int TN, int EPI>
@@ -67,6 +72,7 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
   __shared__ __align__(8) uint64_t bar_accum;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ int peer_ok[kMaxRanks];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -80,6 +86,7 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
+    for (int r = 0; r < kMaxRanks; ++r) peer_ok[r] = 0;
     for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
@@ -177,22 +184,65 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
   }
   tc_fence_after();
   // One CTA-wide verdict, so the barriers inside the epilogue are never divergent.
-  const int epilogue_ok = __syncthreads_and(have_acc && !abort_flag);
+  int epilogue_ok = __syncthreads_and(have_acc && !abort_flag);
+  const uint32_t lane_taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+  constexpr int kChunk = 16;
 
-  if (epilogue_ok) {
-    const uint32_t lane_taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    constexpr int kChunk = 16;
-    if constexpr (EPI == kEpiSwiglu) {
-      // lanes 0..63 hold gate rows, lanes 64..127 the matching up rows.
-      float* up_s = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));  // [TN][64]
-      if (warp >= 2) {
-        const int r = (warp - 2) * 32 + lane;
+  // ---------------- in-cluster split-K: peers hand their fp32 tiles to the leader through DSMEM ----------------
+  const int S = p.cluster;
+  const uint32_t crank = S > 1 ? blockIdx.z : 0;
+  // leader-side landing zone in the (now idle) pipeline stages: [S-1][TN][128] floats
+  const float* peer_s = reinterpret_cast<const float*>(smem_raw + (smem_base - smem_u32(smem_raw)));
+  if (S > 1) {
+    // #1: every CTA of the cluster has retired its MMAs, so the leader's stages may be overwritten
+    cluster_sync_all();
+    if (crank != 0) {
+      if (epilogue_ok) {
+        const uint32_t local = smem_base + ((crank - 1) * TN * 128 + warp * 32 + lane) * 4;
+        const uint32_t remote = mapa_shared(local, 0);
         for (int c = 0; c < TN; c += kChunk) {
           uint32_t v[kChunk];
           tmem_ld_x16(lane_taddr + c, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < kChunk; ++j) up_s[(c + j) * 64 + r] = __uint_as_float(num_it > 0 ? v[j] : 0u);
+          for (int j = 0; j < kChunk; ++j) st_shared_cluster_u32(remote + (c + j) * 512, num_it > 0 ? v[j] : 0u);
+        }
+      }
+      if (threadIdx.x == 0) st_shared_cluster_u32(mapa_shared(smem_u32(&peer_ok[crank]), 0), epilogue_ok ? 1u : 0u);
+    }
+    // #2: peers' tiles (release) are visible to the leader (acquire)
+    cluster_sync_all();
+    if (crank != 0) {
+      epilogue_ok = 0;  // only the leader writes the output
+    } else {
+      for (int r = 1; r < S; ++r) epilogue_ok &= peer_ok[r];
+    }
+  }
+  // accumulator chunk = own TMEM columns + the peers' contributions, summed in rank order
+  auto load_acc = [&](int c, float* acc) {
+    uint32_t v[kChunk];
+    tmem_ld_x16(lane_taddr + c, v);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < kChunk; ++j) acc[j] = num_it > 0 ? __uint_as_float(v[j]) : 0.f;
+    for (int r = 1; r < S; ++r) {
+#pragma unroll
+      for (int j = 0; j < kChunk; ++j) acc[j] += peer_s[((r - 1) * TN + c + j) * 128 + warp * 32 + lane];
+    }
+  };
+
+  if (epilogue_ok) {
+    if constexpr (EPI == kEpiSwiglu) {
+      // lanes 0..63 hold gate rows, lanes 64..127 the matching up rows.
+      float* up_s = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw))) +
+                    (S - 1) * TN * 128;  // [TN][64], behind the peers' landing zone
+      if (warp >= 2) {
+        const int r = (warp - 2) * 32 + lane;
+        for (int c = 0; c < TN; c += kChunk) {
+          float v[kChunk];
+          load_acc(c, v);
+#pragma unroll
+          for (int j = 0; j < kChunk; ++j) up_s[(c + j) * 64 + r] = v[j];
         }
       }
       __syncthreads();
@@ -200,16 +250,15 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
         const int r = warp * 32 + lane;
         const int n = n0 + r;
         for (int c = 0; c < TN; c += kChunk) {
-          uint32_t v[kChunk];
-          tmem_ld_x16(lane_taddr + c, v);
-          tmem_ld_wait();
+          float v[kChunk];
+          load_acc(c, v);
 #pragma unroll
           for (int m = 0; m < kChunk / 2; ++m) {
             float a[2];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               const int j = 2 * m + h;
-              const float g = num_it > 0 ? __uint_as_float(v[j]) : 0.f;
+              const float g = v[j];
               const float u = up_s[(c + j) * 64 + r];
               a[h] = g / (1.f + __expf(-g)) * u;
             }
@@ -229,19 +278,14 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
       const float bias = (EPI == kEpiStore && p.bias != nullptr && n < p.N) ? p.bias[n] : 0.f;
       for (int c = 0; c < TN; c += kChunk) {
         if (t0 + c >= p.T) break;
-        uint32_t v[kChunk];
-        tmem_ld_x16(lane_taddr + c, v);
-        tmem_ld_wait();
-        if (num_it == 0) {
-#pragma unroll
-          for (int j = 0; j < kChunk; ++j) v[j] = 0u;
-        }
+        float v[kChunk];
+        load_acc(c, v);
         if constexpr (EPI == kEpiPartial) {
 #pragma unroll
           for (int j = 0; j < kChunk; ++j) {
             const int t = t0 + c + j;
             if (t < p.T && n < p.N)
-              p.partial[(static_cast<long long>(blockIdx.z) * p.T + t) * p.N + n] = __uint_as_float(v[j]);
+              p.partial[(static_cast<long long>(blockIdx.z) * p.T + t) * p.N + n] = v[j];
           }
         } else if constexpr (EPI == kEpiPushPartial) {
           // reduce-scatter by push: this tile's columns belong to one owner rank; write the fp32
@@ -253,13 +297,26 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
 #pragma unroll
           for (int j = 0; j < kChunk; ++j) {
             const int t = t0 + c + j;
-            if (t < p.T && n < p.N) dst[static_cast<long long>(t) * p.slice_cols] = __uint_as_float(v[j]);
+            if (t < p.T && n < p.N) dst[static_cast<long long>(t) * p.slice_cols] = v[j];
+          }
+        } else if constexpr (EPI == kEpiPushAll) {
+          // one-shot all-reduce by push: the fp32 tile goes to EVERY rank's receive buffer
+          // [parity][src_rank][T_cap][N]; the reader sums the W sources in rank order.
+          const unsigned int par = *p.call_idx & 1u;
+          const long long base = ((static_cast<long long>(par) * p.world + p.rank) * p.T_cap) * p.N + n;
+          for (int r = 0; r < p.world; ++r) {
+            float* dst = p.peer_recv[r] + base;
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) {
+              const int t = t0 + c + j;
+              if (t < p.T && n < p.N) dst[static_cast<long long>(t) * p.N] = v[j];
+            }
           }
         } else {
 #pragma unroll
           for (int m = 0; m < kChunk / 2; ++m) {
-            const float a0 = __uint_as_float(v[2 * m]) + bias;
-            const float a1 = __uint_as_float(v[2 * m + 1]) + bias;
+            const float a0 = v[2 * m] + bias;
+            const float a1 = v[2 * m + 1] + bias;
             const float send = (lane & 1) ? a0 : a1;
             const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
             const int t = t0 + c + 2 * m + (lane & 1);
@@ -288,6 +345,14 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
           asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(flag) : "memory");
         }
       }
+      if constexpr (EPI == kEpiPushAll) {
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x < p.world) {
+          unsigned int* flag = p.peer_flag[threadIdx.x];
+          asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(flag) : "memory");
+        }
+      }
     }
   }
 
@@ -312,11 +377,22 @@ cudaError_t launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const Kerne
   cfg.blockDim = dim3(128);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
+  if (kp.cluster > 1) {
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = 1;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = kp.cluster;
+    ++n_attr;
+  }
+  if (pdl) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  cfg.numAttrs = n_attr;
   return cudaLaunchKernelEx(&cfg, kern, tw, tx, kp);
 }
 
@@ -373,17 +449,37 @@ int gemm_tile_tokens(int T) {
   return 256;
 }
 
+// Largest in-cluster split for a token tile: the leader needs (S-1) * TN * 512 bytes for the peers'
+// fp32 tiles plus TN * 256 bytes for the SwiGLU exchange inside its idle pipeline stages.
+int gemm_max_cluster(int tn) {
+  switch (tn) {
+    case 16: return 8;
+    case 32: return 4;
+    case 64: return 2;
+    case 128: return 2;
+    default: return 1;
+  }
+}
+
 int gemm_pick_splits(int T, int N, int K, int epi, int sm_count) {
-  if (epi == kEpiSwiglu) return 1;
   const int tn = gemm_tile_tokens(T);
-  const int tiles = ((N + kTileN - 1) / kTileN) * ((T + tn - 1) / tn);
+  const int rows = epi == kEpiSwiglu ? N / 2 : N;
+  const int tile_rows = epi == kEpiSwiglu ? 64 : kTileN;
+  const int tiles = ((rows + tile_rows - 1) / tile_rows) * ((T + tn - 1) / tn);
   const int num_kb = (K + kBlockK - 1) / kBlockK;
   const int slots = sm_count * (tn <= 64 ? 2 : 1);
+  const bool in_cluster = epi != kEpiPartial && epi != kEpiPushPartial;
+  const int cap = in_cluster ? gemm_max_cluster(tn) : 8;
   if (tiles >= slots || T > 256) return 1;
   int s = slots / tiles;
-  if (s > 8) s = 8;
+  if (s > cap) s = cap;
   while (s > 1 && num_kb / s < 8) --s;  // keep at least 8 k-blocks per split
   if (s < 1) s = 1;
+  if (in_cluster) {
+    while (s & (s - 1)) --s;              // cluster sizes are powers of two
+    while (s > 1 && (num_kb + s - 1) / s * (s - 1) >= num_kb) s >>= 1;
+    return s;
+  }
   const int per = (num_kb + s - 1) / s;
   return (num_kb + per - 1) / per;  // no empty trailing split
 }
@@ -395,26 +491,39 @@ const char* gemm_bf16(const GemmArgs& a) {
     return "gemm_bf16: operands must be 16-byte aligned";
   if ((a.N & 1) || (a.ldo & 1)) return "gemm_bf16: N and ldo must be even";
   const int tn = gemm_tile_tokens(static_cast<int>(a.T));
+  const bool global_split = a.epi == kEpiPartial || a.epi == kEpiPushPartial;
   KernelParams kp = {};
   kp.T = static_cast<int>(a.T); kp.N = static_cast<int>(a.N); kp.K = static_cast<int>(a.K);
   kp.num_kb = (kp.K + kBlockK - 1) / kBlockK;
   int splits = a.splits < 1 ? 1 : a.splits;
-  if (a.epi != kEpiPartial && a.epi != kEpiPushPartial) splits = 1;
   if (splits > kp.num_kb) splits = kp.num_kb;
   kp.kb_per_split = (kp.num_kb + splits - 1) / splits;
-  splits = (kp.num_kb + kp.kb_per_split - 1) / kp.kb_per_split;  // no empty split
-  if ((a.epi == kEpiPartial || a.epi == kEpiPushPartial) && splits != a.splits)
+  if ((kp.num_kb + kp.kb_per_split - 1) / kp.kb_per_split != splits || splits != (a.splits < 1 ? 1 : a.splits))
     return "gemm_bf16: split count leaves an empty split";
-  if (a.epi == kEpiPushPartial) {
+  kp.cluster = 1;
+  if (!global_split && splits > 1) {
+    if (splits > gemm_max_cluster(tn) || (splits & (splits - 1)))
+      return "gemm_bf16: in-cluster split must be a power of two within the tile's limit";
+    kp.cluster = splits;
+  }
+  if (a.epi == kEpiPushPartial || a.epi == kEpiPushAll) {
     if (a.world < 1 || a.world > kMaxRanks || a.rank < 0 || a.rank >= a.world) return "gemm_bf16: bad rank/world";
-    if (kp.N % a.world || (kp.N / a.world) % kTileN) return "gemm_bf16: N / world must be a multiple of 128";
     kp.rank = a.rank;
-    kp.slice_cols = kp.N / a.world;
+    kp.world = a.world;
     for (int r = 0; r < a.world; ++r) {
       if (a.peer_recv[r] == nullptr || a.peer_flag[r] == nullptr) return "gemm_bf16: missing peer pointer";
       kp.peer_recv[r] = a.peer_recv[r];
       kp.peer_flag[r] = a.peer_flag[r];
     }
+  }
+  if (a.epi == kEpiPushPartial) {
+    if (kp.N % a.world || (kp.N / a.world) % kTileN) return "gemm_bf16: N / world must be a multiple of 128";
+    kp.slice_cols = kp.N / a.world;
+  }
+  if (a.epi == kEpiPushAll) {
+    if (a.call_idx == nullptr || a.T_cap < kp.T) return "gemm_bf16: push-all needs the call counter and T <= T_cap";
+    kp.call_idx = a.call_idx;
+    kp.T_cap = a.T_cap;
   }
   kp.swiglu_half = a.epi == kEpiSwiglu ? kp.N / 2 : 0;
   if (a.epi == kEpiSwiglu && (kp.N % 4)) return "gemm_bf16: SwiGLU needs N % 4 == 0";
@@ -423,7 +532,8 @@ const char* gemm_bf16(const GemmArgs& a) {
   kp.bias = a.bias; kp.partial = a.partial; kp.status = a.status;
   if (a.epi == kEpiResidual && a.resid == nullptr) return "gemm_bf16: residual epilogue without residual";
   if (a.epi == kEpiPartial && a.partial == nullptr) return "gemm_bf16: split-K without workspace";
-  if (a.epi != kEpiPartial && a.epi != kEpiPushPartial && a.out == nullptr) return "gemm_bf16: no output";
+  const bool needs_out = a.epi == kEpiStore || a.epi == kEpiResidual || a.epi == kEpiSwiglu;
+  if (needs_out && a.out == nullptr) return "gemm_bf16: no output";
 
   CUtensorMap tw, tx;
   if (!cached_tmap(&tw, a.w, a.N, a.K, a.ldw, 64)) return "gemm_bf16: weight tensor map rejected";
@@ -440,6 +550,7 @@ const char* gemm_bf16(const GemmArgs& a) {
     case kEpiSwiglu: e = launch_tn<kEpiSwiglu>(tn, tw, tx, kp, grid, a.stream, a.pdl); break;
     case kEpiPartial: e = launch_tn<kEpiPartial>(tn, tw, tx, kp, grid, a.stream, a.pdl); break;
     case kEpiPushPartial: e = launch_tn<kEpiPushPartial>(tn, tw, tx, kp, grid, a.stream, a.pdl); break;
+    case kEpiPushAll: e = launch_tn<kEpiPushAll>(tn, tw, tx, kp, grid, a.stream, a.pdl); break;
     default: return "gemm_bf16: unknown epilogue";
   }
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);

@@ -448,6 +448,60 @@ void tp_argmax(int64_t world, int64_t rank, int64_t T_cap, const Tensor& logits,
   chk(nfb::tp_argmax(p, cur_stream(), pdl));
 }
 
+void gemm_bf16_push_all(const Tensor& x, const Tensor& w, int64_t splits, int64_t world, int64_t rank,
+                        at::IntArrayRef peer_bases, int64_t recv_off, int64_t flag_off, int64_t T_cap,
+                        const Tensor& state, OptT status, bool pdl) {
+  need(x, at::kBFloat16, "x"); need(w, at::kBFloat16, "w"); need_rows(x, "x"); need_rows(w, "w");
+  need(state, at::kByte, "state");
+  TORCH_CHECK(x.size(1) == w.size(1), "gemm_bf16_push_all: K mismatch");
+  TORCH_CHECK(static_cast<int64_t>(peer_bases.size()) == world && world <= nfb::kMaxRanks, "peer_bases size");
+  TORCH_CHECK(state.numel() >= static_cast<int64_t>(sizeof(nfb::TpState)), "state too small");
+  c10::cuda::CUDAGuard guard(x.device());
+  nfb::GemmArgs a;
+  a.w = w.data_ptr(); a.N = w.size(0); a.K = w.size(1); a.ldw = w.stride(0);
+  a.x = x.data_ptr(); a.T = x.size(0); a.ldx = x.stride(0);
+  a.splits = static_cast<int>(splits); a.epi = nfb::kEpiPushAll;
+  a.world = static_cast<int>(world); a.rank = static_cast<int>(rank);
+  a.T_cap = static_cast<int>(T_cap);
+  a.call_idx = &reinterpret_cast<const nfb::TpState*>(state.data_ptr())->call_idx;
+  for (int r = 0; r < world; ++r) {
+    a.peer_recv[r] = reinterpret_cast<float*>(peer_bases[r] + recv_off);
+    a.peer_flag[r] = reinterpret_cast<unsigned int*>(peer_bases[r] + flag_off);
+  }
+  a.ldo = 2;
+  a.status = ptr_or_null<int>(status); a.stream = cur_stream(); a.pdl = pdl;
+  chk(nfb::gemm_bf16(a));
+}
+
+void tp_sum_norm(int64_t world, int64_t T_cap, int64_t arrivals, int64_t my_base, int64_t recv_off, int64_t flag_off,
+                 const Tensor& x, OptT norm_w, OptT normed, double eps, bool unit_offset, const Tensor& state,
+                 OptT status, bool pdl) {
+  need(x, at::kBFloat16, "x"); need(state, at::kByte, "state");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous(), "x must be contiguous [T, N]");
+  c10::cuda::CUDAGuard guard(x.device());
+  nfb::TpSumNormParams p = {};
+  p.world = static_cast<int>(world); p.T = static_cast<int>(x.size(0)); p.T_cap = static_cast<int>(T_cap);
+  p.N = static_cast<int>(x.size(1));
+  p.arrivals_this_call = static_cast<unsigned int>(arrivals);
+  p.my_recv = reinterpret_cast<const float*>(my_base + recv_off);
+  p.my_flag = reinterpret_cast<const unsigned int*>(my_base + flag_off);
+  p.x = static_cast<__nv_bfloat16*>(x.data_ptr());
+  if (norm_w.has_value() && norm_w->defined()) {
+    need(*norm_w, at::kBFloat16, "norm_w");
+    TORCH_CHECK(norm_w->numel() == p.N);
+    p.norm_w = static_cast<const __nv_bfloat16*>(norm_w->data_ptr());
+  }
+  if (normed.has_value() && normed->defined()) {
+    need(*normed, at::kBFloat16, "normed");
+    TORCH_CHECK(normed->is_contiguous() && normed->numel() == x.numel());
+    p.normed = static_cast<__nv_bfloat16*>(normed->data_ptr());
+  }
+  p.eps = static_cast<float>(eps); p.unit_offset = unit_offset ? 1 : 0;
+  p.state = reinterpret_cast<nfb::TpState*>(state.data_ptr());
+  p.status = ptr_or_null<int>(status);
+  chk(nfb::tp_sum_norm(p, cur_stream(), pdl));
+}
+
 int64_t tp_state_bytes() { return static_cast<int64_t>(sizeof(nfb::TpState)); }
 
 }  // namespace
@@ -459,6 +513,8 @@ TORCH_LIBRARY(nfb200, m) {
   m.def("tp_reduce_ag_norm(int world, int rank, int T, int T_cap, int N, int splits, int arrivals, int[] peer_bases, int recv_off, int flag_off, int x_off, int ss_off, int row_flag_off, Tensor? norm_w, Tensor? normed, float eps, bool unit_offset, Tensor state, Tensor? status, bool pdl) -> ()", &tp_reduce_ag_norm);
   m.def("tp_argmax(int world, int rank, int T_cap, Tensor logits, int[] peer_bases, int cand_off, int flag_off, Tensor out, Tensor state, Tensor? status, bool pdl) -> ()", &tp_argmax);
   m.def("tp_state_bytes() -> int", &tp_state_bytes);
+  m.def("gemm_bf16_push_all(Tensor x, Tensor w, int splits, int world, int rank, int[] peer_bases, int recv_off, int flag_off, int T_cap, Tensor state, Tensor? status, bool pdl) -> ()", &gemm_bf16_push_all);
+  m.def("tp_sum_norm(int world, int T_cap, int arrivals, int my_base, int recv_off, int flag_off, Tensor x, Tensor? norm_w, Tensor? normed, float eps, bool unit_offset, Tensor state, Tensor? status, bool pdl) -> ()", &tp_sum_norm);
   m.def("gemm_bf16(Tensor x, Tensor w, Tensor? out, int epi, Tensor? resid, Tensor? bias, Tensor? partial, int splits, Tensor? status, bool pdl) -> ()", &gemm_bf16);
   m.def("gemm_pick_splits(int T, int N, int K, int epi) -> int", &gemm_pick_splits);
   m.def("add_rmsnorm(Tensor? partial, int splits, Tensor? delta, Tensor? resid_in, Tensor? resid_out, Tensor? norm_w, Tensor? normed, int T, int N, float eps, bool unit_offset, bool pdl) -> ()", &add_rmsnorm);

@@ -179,6 +179,7 @@ class HybridModel:
         self.prefix = prefix
         self.inv_freq = rope_inv_freq(cfg.rot_dim, cfg.rope_theta).to(self.device)
         self.sm_scale = 1.0 / math.sqrt(cfg.head_dim)
+        self.cluster_splitk = True  # False: split-K through an fp32 workspace + reduce kernel
         self.attn_impl = 0  # 0 = pick, 1 = SIMT, 2 = tensor-core split-KV attention
         self.comm = None  # tensor-parallel communicator (parallel.tp), None on one GPU
         # layer index -> index among attention / GDN layers
@@ -187,18 +188,25 @@ class HybridModel:
 
     # ------------------------------------------------------------------ GEMM helpers
     def _gemm(self, x, w, out, epi=EPI_STORE, resid=None):
-        self.ops.gemm_bf16(x, w, out, epi, resid, None, None, 1, self.status.tensor, self.pdl)
+        # in-cluster split-K when the output tiles alone cannot fill the GPU (decode, sharded weights)
+        splits = int(self.ops.gemm_pick_splits(x.shape[0], w.shape[0], w.shape[1], epi)) if self.cluster_splitk else 1
+        self.ops.gemm_bf16(x, w, out, epi, resid, None, None, splits, self.status.tensor, self.pdl)
 
     def _gemm_to_residual(self, ws: Workspace, a, w, T: int, norm_w, normed_out):
         """x += a @ w^T ; normed_out = rmsnorm(x) * (1 + norm_w).  x is ws.x[:T] (in place)."""
         cfg, ops = self.cfg, self.ops
         x = ws.x[:T]
         N, K = w.shape
-        splits = int(ops.gemm_pick_splits(T, N, K, EPI_PARTIAL)) if T <= 256 else 1
         if self.comm is not None:
             # row-parallel: partial sums live on every rank; the communicator reduces them
-            self.comm.gemm_reduce_residual(self, ws, a, w, T, norm_w, normed_out, splits)
+            self.comm.gemm_reduce_residual(self, ws, a, w, T, norm_w, normed_out)
             return
+        if self.cluster_splitk:
+            # split-K inside a thread-block cluster (DSMEM reduction), residual add in the epilogue
+            self._gemm(a, w, x, EPI_RESIDUAL, x)
+            ops.add_rmsnorm(None, 0, None, x, None, norm_w, normed_out, T, N, cfg.rms_eps, True, self.pdl)
+            return
+        splits = int(ops.gemm_pick_splits(T, N, K, EPI_PARTIAL)) if T <= 256 else 1
         if splits > 1:
             ops.gemm_bf16(a, w, None, EPI_PARTIAL, None, None, ws.partial, splits, self.status.tensor, self.pdl)
             ops.add_rmsnorm(ws.partial, splits, None, x, x, norm_w, normed_out, T, N, cfg.rms_eps, True, self.pdl)

@@ -122,20 +122,14 @@ class TensorParallel:
         # ---- one symmetric allocation, identical layout on every rank ----
         off = 0
         self.off: Dict[str, int] = {}
-        for name, nbytes in [("recv", world * MAX_SPLITS * min(self.T_cap, 256) * self.slice * 4),
+        self.one_shot_rows = min(self.T_cap, 128)   # rows handled by the one-shot (push-all) path
+        for name, nbytes in [("recv", world * self.T_cap * self.slice * 4),          # [src][T][N/W] fp32
+                             ("recv_all", 2 * world * self.one_shot_rows * N * 4),   # [parity][src][rows][N] fp32
                              ("x", self.T_cap * N * 2), ("ss", 2 * self.T_cap * world * 4),
-                             ("row_flag", self.T_cap * 4), ("arrival_flag", 256),
+                             ("row_flag", self.T_cap * 4), ("arrival_flag", 256), ("all_flag", 256),
                              ("cand", 2 * self.T_cap * world * 8), ("argmax_flag", self.T_cap * 4)]:
             self.off[name] = off
             off += _align(nbytes)
-        # large-T calls use one split; make sure that layout fits too
-        recv_need = world * self.T_cap * self.slice * 4
-        if recv_need > self.off["x"] - self.off["recv"]:
-            grow = _align(recv_need) - (self.off["x"] - self.off["recv"])
-            for k in self.off:
-                if k != "recv":
-                    self.off[k] += grow
-            off += grow
         self.total_bytes = off
         self.local, handle = self.ops.symm_alloc(off)
         handles: List[Optional[torch.Tensor]] = [None] * world
@@ -191,23 +185,34 @@ class TensorParallel:
         return out
 
     # ------------------------------------------------------------------ collectives
-    def gemm_reduce_residual(self, model, ws, a, w, T: int, norm_w, normed_out, splits: int) -> None:
-        """x += sum_ranks(a_r @ w_r^T); normed_out = rmsnorm(x) * (1 + norm_w).  x is the symmetric residual."""
+    def gemm_reduce_residual(self, model, ws, a, w, T: int, norm_w, normed_out) -> None:
+        """x += sum_ranks(a_r @ w_r^T); normed_out = rmsnorm(x) * (1 + norm_w)."""
         cfg, ops = self.cfg, model.ops
         N = cfg.hidden
+        x = ws.x[:T]
         if self.mode == "nccl" or T > self.T_cap:
             delta = self.delta[:T] if T <= self.T_cap else torch.empty((T, N), dtype=torch.bfloat16, device=self.device)
             ops.gemm_bf16(a, w, delta, 0, None, None, None, 1, model.status.tensor, model.pdl)
             dist.all_reduce(delta, group=self.group)
-            ops.add_rmsnorm(None, 0, delta, ws.x[:T], ws.x[:T], norm_w, normed_out, T, N, cfg.rms_eps, True, model.pdl)
+            ops.add_rmsnorm(None, 0, delta, x, x, norm_w, normed_out, T, N, cfg.rms_eps, True, model.pdl)
             return
-        if T > 256:
-            splits = 1
         tn = 16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else 128 if T <= 128 else 256
-        arrivals = self.world * (self.slice // 128) * ((T + tn - 1) // tn) * splits
-        ops.gemm_bf16_push(a, w, splits, self.world, self.rank, self.peer_bases, self.off["recv"],
+        t_tiles = (T + tn - 1) // tn
+        if T <= self.one_shot_rows:
+            # decode sizes: GEMM (in-cluster split-K) pushes its fp32 tile to every rank, one kernel sums + norms
+            splits = int(ops.gemm_pick_splits(T, N, w.shape[1], 5))
+            arrivals = self.world * (N // 128) * t_tiles
+            ops.gemm_bf16_push_all(a, w, splits, self.world, self.rank, self.peer_bases, self.off["recv_all"],
+                                   self.off["all_flag"], self.one_shot_rows, self.state, model.status.tensor, model.pdl)
+            ops.tp_sum_norm(self.world, self.one_shot_rows, arrivals, self.peer_bases[self.rank], self.off["recv_all"],
+                            self.off["all_flag"], x, norm_w, normed_out, cfg.rms_eps, True, self.state,
+                            model.status.tensor, model.pdl)
+            return
+        # prefill sizes: reduce-scatter by push into the owner, then reduce + all-gather + norm
+        arrivals = self.world * (self.slice // 128) * t_tiles
+        ops.gemm_bf16_push(a, w, 1, self.world, self.rank, self.peer_bases, self.off["recv"],
                            self.off["arrival_flag"], model.status.tensor, model.pdl)
-        ops.tp_reduce_ag_norm(self.world, self.rank, T, self.T_cap, N, splits, arrivals, self.peer_bases,
+        ops.tp_reduce_ag_norm(self.world, self.rank, T, self.T_cap, N, 1, arrivals, self.peer_bases,
                               self.off["recv"], self.off["arrival_flag"], self.off["x"], self.off["ss"],
                               self.off["row_flag"], norm_w, normed_out, cfg.rms_eps, True, self.state,
                               model.status.tensor, model.pdl)

@@ -94,6 +94,9 @@ def test_pick_splits_covers_k(ops):
         nkb = (K + 63) // 64
         per = (nkb + s - 1) // s
         assert 1 <= s <= 8 and (nkb + per - 1) // per == s
+    for T, N, K, epi in [(32, 5120, 17408, EPI_RESIDUAL), (32, 2060, 5120, EPI_STORE), (1, 34816, 5120, EPI_SWIGLU)]:
+        s = int(ops.gemm_pick_splits(T, N, K, epi))
+        assert s in (1, 2, 4, 8)
 
 
 def test_gemm_pdl_chain(ops, status):
@@ -107,3 +110,36 @@ def test_gemm_pdl_chain(ops, status):
         ops.gemm_bf16(h, w2, out, EPI_STORE, None, None, None, 1, status.tensor, True)
     ref_h = (x.float() @ w1.float().t()).to(torch.bfloat16).float()
     _check(out, ref_h @ w2.float().t())
+
+
+@pytest.mark.parametrize("T,splits", [(1, 8), (16, 4), (32, 2), (32, 4), (64, 2), (100, 2)])
+@pytest.mark.parametrize("epi", [EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU])
+def test_gemm_cluster_splitk(ops, status, T, splits, epi):
+    """Split-K inside a thread-block cluster: peers hand fp32 tiles to the leader through DSMEM."""
+    N, K = 512, 64 * 36 + 8
+    x, w = _mk(T, N, K, seed=3)
+    ref = x.float() @ w.float().t()
+    if epi == EPI_SWIGLU:
+        out = torch.full((T, N // 2), float("nan"), device="cuda", dtype=torch.bfloat16)
+        ops.gemm_bf16(x, w, out, epi, None, None, None, splits, status.tensor, False)
+        _check(out, torch.nn.functional.silu(ref[:, : N // 2]) * ref[:, N // 2:])
+    elif epi == EPI_RESIDUAL:
+        resid = torch.randn(T, N, device="cuda").to(torch.bfloat16)
+        out = resid.clone()
+        ops.gemm_bf16(x, w, out, epi, out, None, None, splits, status.tensor, False)
+        _check(out, resid.float() + ref)
+    else:
+        out = torch.full((T, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+        ops.gemm_bf16(x, w, out, epi, None, None, None, splits, status.tensor, True)
+        _check(out, ref)
+
+
+def test_gemm_cluster_splitk_is_deterministic(ops, status):
+    x, w = _mk(32, 5120, 6144, seed=4)
+    outs = []
+    for _ in range(3):
+        out = torch.empty((32, 5120), device="cuda", dtype=torch.bfloat16)
+        ops.gemm_bf16(x, w, out, EPI_STORE, None, None, None, 4, status.tensor, False)
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    _check(outs[0], x.float() @ w.float().t())

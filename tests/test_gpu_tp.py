@@ -15,7 +15,7 @@ def test_tp2_matches_single_gpu():
     worker = os.path.join(os.path.dirname(__file__), "tp_worker.py")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                         "--master-addr", "127.0.0.1", "--master-port", "29533", worker],
-                       capture_output=True, text=True, timeout=600, env=env)
+                       capture_output=True, text=True, timeout=300, env=env)
     out = r.stdout + r.stderr
     assert r.returncode == 0, out[-3000:]
     assert "TP_OK" in out and "TP_FAIL" not in out, out[-3000:]

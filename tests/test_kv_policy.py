@@ -1,0 +1,87 @@
+"""KV storage policy planners (CPU): grammars, bit-budget DP, block descent."""
+import pytest
+
+from ninfer_fusion_b200.kv.descent import CellMap, DescentConfig, apply_moves, plan_descent_pass
+from ninfer_fusion_b200.kv.policy import (build_ladder, format_layer_storage, parse_layer_storage, parse_tier_formats,
+                                          solve_bit_budget)
+
+
+def test_layer_storage_grammar_round_trip():
+    t = parse_layer_storage("all:fp8|0-3:bf16|7:nvfp4", 16)
+    assert t[:4] == ["bf16"] * 4 and t[7] == "nvfp4" and t[8] == "fp8"
+    assert parse_layer_storage(format_layer_storage(t), 16) == t
+    assert format_layer_storage(["fp8"] * 5) == "all:fp8"
+    for bad in ("all", "0-99:fp8", "3-1:fp8", "all:fp7", "|", "x:bf16"):
+        with pytest.raises(ValueError):
+            parse_layer_storage(bad, 16)
+    tf = parse_tier_formats("hot=bf16,cold=nvfp4")
+    assert (tf.hot, tf.tail, tf.cold) == ("bf16", "fp8", "nvfp4")
+    with pytest.raises(ValueError):
+        parse_tier_formats("warm=fp8")
+
+
+def test_ladder_bits_follow_page_geometry():
+    lad = build_ladder(256, 64)
+    assert lad["bf16"].bits_centi == 1600 and lad["int8"].bits_centi == 825
+    assert lad["fp8"].bits_centi == 806 and lad["nvfp4"].bits_centi == 450
+
+
+def test_bit_budget_is_exact_and_monotone():
+    n = 16
+    plan16 = solve_bit_budget(n, 16.0)
+    assert plan16.tiers == ["bf16"] * n and plan16.penalty_milli_total == 0
+    prev_pen = 0
+    for target in (12.0, 9.0, 8.3, 6.0, 4.5):
+        p = solve_bit_budget(n, target)
+        assert p.avg_bits <= target + 1e-9
+        assert p.penalty_milli_total >= prev_pen
+        prev_pen = p.penalty_milli_total
+        assert parse_layer_storage(p.spec, n) == p.tiers
+        # packing: precision never decreases with depth
+        order = {"nvfp4": 0, "fp8": 1, "int8": 2, "bf16": 3}
+        ranks = [order[t] for t in p.tiers]
+        assert ranks == sorted(ranks)
+    p = solve_bit_budget(n, 8.3)
+    # brute-force check on a small instance: 4 layers
+    lad = build_ladder()
+    import itertools
+    best = None
+    for combo in itertools.product(lad.values(), repeat=4):
+        bits = sum(t.bits_centi for t in combo)
+        if bits <= 830 * 4:
+            pen = sum(t.penalty_milli for t in combo)
+            best = pen if best is None else min(best, pen)
+    assert solve_bit_budget(4, 8.3).penalty_milli_total == best
+    with pytest.raises(ValueError):
+        solve_bit_budget(n, 4.0)
+    cold = solve_bit_budget(n, 4.0, cold_cap=4, cold_bits_centi=100)
+    assert len(cold.cold_layers) >= 2 and cold.cold_layers == list(range(len(cold.cold_layers)))
+
+
+def test_block_descent_one_rung_per_pass_oldest_first():
+    cfg = DescentConfig(min_age_tokens=128, max_cells_per_pass=3, sink_blocks=1)
+    cells = CellMap(page_tokens=64, n_layers=2)
+    cells.touch(0, 640)   # 10 blocks
+    moves = plan_descent_pass(cells, cfg, n_kv_heads=4, head_dim=256)
+    assert len(moves) == 3 and all(m.src == "bf16" and m.dst == "fp8" for m in moves)
+    assert [m.block for m in moves] == [1, 1, 2] and moves[0].layer == 0 and moves[1].layer == 1
+    assert all(m.bytes_freed == 2 * 64 * 4 * 256 * 1600 // 800 - 2 * 64 * 4 * 256 * 806 // 800 for m in moves)
+    apply_moves(cells, cfg, moves)
+    # young blocks (within 128 tokens of the frontier) and the sink block never move
+    for _ in range(50):
+        mv = plan_descent_pass(cells, cfg, 4, 256)
+        if not mv:
+            break
+        assert all(m.block >= 1 and (m.block + 1) * 64 + 128 <= 640 for m in mv)
+        apply_moves(cells, cfg, mv)
+    assert cells.rungs[(0, 0, 0)] == 0 and cells.rungs[(0, 0, 9)] == 0 and cells.rungs[(0, 1, 3)] == 2
+    # last rung + allow_cold -> cold moves; trimming forgets cells beyond the frontier
+    mv = plan_descent_pass(cells, cfg, 4, 256, allow_cold=True)
+    assert mv and all(m.dst == "cold" for m in mv)
+    cells.trim(0, 130)
+    assert (0, 0, 3) not in cells.rungs and (0, 0, 2) in cells.rungs
+    # resident-byte target stops the pass early
+    cells2 = CellMap(64, 1)
+    cells2.touch(1, 6400)
+    tight = DescentConfig(min_age_tokens=0, max_cells_per_pass=1000, target_resident_bytes=10**12)
+    assert plan_descent_pass(cells2, tight, 4, 256) == []

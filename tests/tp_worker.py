@@ -1,11 +1,13 @@
 """Worker for the multi-GPU tensor-parallel tests (launched by torch.distributed.run).
 
 Every rank builds the same full random weights, takes its shard, generates greedily with the
-fused peer-memory collectives (and with the NCCL baseline), and rank 0 compares both against a
-single-GPU run of the same weights.  Prints one line starting with TP_OK or TP_FAIL.
+fused peer-memory collectives (eager and CUDA graph) and with the NCCL baseline (eager), and
+rank 0 compares against a single-GPU run of the same weights.  Progress lines are flushed so a
+stall can be located; the last line starts with TP_OK or TP_FAIL.
 """
 import os
 import sys
+import time
 
 import torch
 import torch.distributed as dist
@@ -17,6 +19,10 @@ from ninfer_fusion_b200.models.config import TINY_DENSE  # noqa: E402
 from ninfer_fusion_b200.models.weights import random_weights  # noqa: E402
 from ninfer_fusion_b200.parallel.tp import TensorParallel  # noqa: E402
 from ninfer_fusion_b200.runtime.generator import Generator  # noqa: E402
+
+
+def log(rank, msg):
+    print(f"[rank {rank} {time.strftime('%H:%M:%S')}] {msg}", flush=True)
 
 
 def main():
@@ -31,14 +37,15 @@ def main():
     prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (21, 70, 5)]
     n_new = 10
     results = {}
-    for mode in ("fused", "nccl"):
-        for use_graph in (False, True):
-            comm = TensorParallel(cfg, rank, world, dev, max_tokens=64, mode=mode)
-            gen = Generator(cfg, comm.shard(full), dev, max_batch=4, max_context=256, kv_format="bf16", page_size=16,
-                            prefill_chunk=64, use_graph=use_graph, shard=comm.geometry, comm=comm)
-            results[(mode, use_graph)] = gen.generate(prompts, n_new)
-            torch.cuda.synchronize()
-            dist.barrier()
+    for mode, use_graph in (("fused", False), ("fused", True), ("nccl", False)):
+        log(rank, f"start {mode} graph={use_graph}")
+        comm = TensorParallel(cfg, rank, world, dev, max_tokens=64, mode=mode)
+        gen = Generator(cfg, comm.shard(full), dev, max_batch=4, max_context=256, kv_format="bf16", page_size=16,
+                        prefill_chunk=64, use_graph=use_graph, shard=comm.geometry, comm=comm)
+        results[(mode, use_graph)] = gen.generate(prompts, n_new)
+        torch.cuda.synchronize()
+        dist.barrier()
+        log(rank, f"done {mode} graph={use_graph}: {results[(mode, use_graph)][0][:5]}")
     ok = True
     msg = ""
     if rank == 0:
@@ -54,14 +61,12 @@ def main():
         if results[("fused", False)] != results[("fused", True)]:
             ok = False
             msg += " fused graph!=eager"
-    flag = torch.tensor([1 if ok else 0], device=dev)
-    dist.broadcast(flag, 0)
-    # all ranks must produce the same tokens
     mine = torch.tensor(results[("fused", True)], device=dev)
     ref = mine.clone()
     dist.broadcast(ref, 0)
     if not torch.equal(mine, ref):
         print(f"TP_FAIL rank {rank} tokens differ from rank 0", flush=True)
+    dist.barrier()
     if rank == 0:
         print(("TP_OK" if ok else "TP_FAIL") + msg, flush=True)
     dist.destroy_process_group()
