@@ -60,4 +60,25 @@ const char* paged_attention(const PagedAttnParams& p, cudaStream_t stream, bool 
 // Tensor-core split kernel; cudaErrorNotSupported when the geometry is outside its envelope.
 cudaError_t paged_attention_mma_split(const PagedAttnParams& p, cudaStream_t stream, bool pdl);
 
+// Causal prefill / wide-verify attention over blocks of consecutive query tokens of one sequence.
+struct PrefillAttnParams {
+  const __nv_bfloat16* q;     // [T, n_q_heads, head_dim]
+  int n_q_heads, n_kv_heads, head_dim;
+  const int* q_seq;           // [T] block-table row per token
+  const int* q_kv_len;        // [T] visible keys per token (cache_pos + 1), increasing inside a block
+  const int* blk_start;       // [n_blocks] first token of each query block
+  const int* blk_count;       // [n_blocks] tokens in the block (<= prefill_attn_block_tokens)
+  int n_blocks;
+  const int* block_table;
+  int table_stride;
+  KvLayer kv;
+  float sm_scale;
+  const __nv_bfloat16* gate;  // optional sigmoid gate [T, ld_gate]
+  long long ld_gate;
+  __nv_bfloat16* out;         // [T, n_q_heads * head_dim]
+};
+const char* paged_attention_prefill(const PrefillAttnParams& p, cudaStream_t stream, bool pdl);
+// Query tokens per block for a GQA geometry (128 MMA rows / group size).
+int prefill_attn_block_tokens(int n_q_heads, int n_kv_heads);
+
 }  // namespace nfb

@@ -30,7 +30,7 @@ constexpr int kWTileBytes = kTileN * 128;
 
 template <int TN>
 struct GemmCfg {
-  static constexpr int kStages = TN <= 64 ? 4 : (TN == 128 ? 6 : 4);
+  static constexpr int kStages = TN <= 32 ? 5 : (TN == 64 ? 4 : (TN == 128 ? 6 : 4));
   static constexpr int kXTileBytes = TN * 128;
   static constexpr int kStageBytes = kWTileBytes + kXTileBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // +1024: manual alignment
@@ -454,7 +454,7 @@ int gemm_tile_tokens(int T) {
 int gemm_max_cluster(int tn) {
   switch (tn) {
     case 16: return 8;
-    case 32: return 4;
+    case 32: return 6;   // 5 stages x 20.5 KB hold 5 peer tiles of 16 KB plus the 8 KB SwiGLU exchange
     case 64: return 2;
     case 128: return 2;
     default: return 1;
@@ -476,8 +476,7 @@ int gemm_pick_splits(int T, int N, int K, int epi, int sm_count) {
   while (s > 1 && num_kb / s < 8) --s;  // keep at least 8 k-blocks per split
   if (s < 1) s = 1;
   if (in_cluster) {
-    while (s & (s - 1)) --s;              // cluster sizes are powers of two
-    while (s > 1 && (num_kb + s - 1) / s * (s - 1) >= num_kb) s >>= 1;
+    while (s > 1 && (num_kb + s - 1) / s * (s - 1) >= num_kb) --s;  // no empty trailing split
     return s;
   }
   const int per = (num_kb + s - 1) / s;
@@ -502,8 +501,7 @@ const char* gemm_bf16(const GemmArgs& a) {
     return "gemm_bf16: split count leaves an empty split";
   kp.cluster = 1;
   if (!global_split && splits > 1) {
-    if (splits > gemm_max_cluster(tn) || (splits & (splits - 1)))
-      return "gemm_bf16: in-cluster split must be a power of two within the tile's limit";
+    if (splits > gemm_max_cluster(tn)) return "gemm_bf16: in-cluster split exceeds the tile's limit";
     kp.cluster = splits;
   }
   if (a.epi == kEpiPushPartial || a.epi == kEpiPushAll) {

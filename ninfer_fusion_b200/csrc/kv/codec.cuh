@@ -111,19 +111,18 @@ __device__ __forceinline__ void kv_store_row_warp(int format, int group, const f
     const __half sh = __float2half_rn(sf);
     sf = __half2float(sh);
     if (lane == 0) *reinterpret_cast<__half*>(scales) = sh;
-    const float inv = 1.f / sf;
+    // true division (not a reciprocal multiply): the codec contract is code = e4m3(x / scale)
 #pragma unroll
-    for (int j = 0; j < VPL; ++j) codes[d0 + j] = float_to_e4m3(vals[j] * inv);
+    for (int j = 0; j < VPL; ++j) codes[d0 + j] = float_to_e4m3(__fdiv_rn(vals[j], sf));
   } else if (format == kKvInt8Group) {
     const int lanes_per_group = group / VPL;  // 32/8=4, 64/8=8, 32/4=8, 64/4=16
     for (int o = lanes_per_group / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     const __half sh = __float2half_rn(amax / 127.f);
     const float sf = __half2float(sh);
     if ((lane % lanes_per_group) == 0) reinterpret_cast<__half*>(scales)[d0 / group] = sh;
-    const float inv = sf > 0.f ? 1.f / sf : 0.f;
 #pragma unroll
     for (int j = 0; j < VPL; ++j) {
-      float q = rintf(vals[j] * inv);
+      float q = sf > 0.f ? rintf(__fdiv_rn(vals[j], sf)) : 0.f;
       q = fminf(fmaxf(q, -127.f), 127.f);
       reinterpret_cast<int8_t*>(codes)[d0 + j] = static_cast<int8_t>(q);
     }
@@ -133,10 +132,9 @@ __device__ __forceinline__ void kv_store_row_warp(int format, int group, const f
     const uint8_t sc = float_to_e4m3(amax / 6.f);
     const float sf = e4m3_to_float(sc);
     if ((lane % lanes_per_group) == 0) scales[d0 / 16] = sc;
-    const float inv = sf > 0.f ? 1.f / sf : 0.f;
     uint32_t packed = 0;
 #pragma unroll
-    for (int j = 0; j < VPL; ++j) packed |= float_to_e2m1(vals[j] * inv) << (4 * j);
+    for (int j = 0; j < VPL; ++j) packed |= float_to_e2m1(sf > 0.f ? __fdiv_rn(vals[j], sf) : 0.f) << (4 * j);
     if (VPL == 8) *reinterpret_cast<uint32_t*>(codes + d0 / 2) = packed;
     else *reinterpret_cast<uint16_t*>(codes + d0 / 2) = static_cast<uint16_t>(packed);
   }

@@ -233,6 +233,45 @@ void paged_attention(const Tensor& q, int64_t n_q_heads, int64_t n_kv_heads, int
   chk(nfb::paged_attention(p, cur_stream(), pdl));
 }
 
+void paged_attention_prefill(const Tensor& q, int64_t n_q_heads, int64_t n_kv_heads, int64_t head_dim,
+                             const Tensor& q_seq, const Tensor& q_kv_len, const Tensor& blk_start,
+                             const Tensor& blk_count, const Tensor& block_table, const Tensor& k_codes,
+                             const Tensor& v_codes, OptT k_scales, OptT v_scales, int64_t page_size, int64_t format,
+                             int64_t group, double sm_scale, OptT gate, const Tensor& out, bool pdl) {
+  need(q, at::kBFloat16, "q"); need(q_seq, at::kInt, "q_seq"); need(q_kv_len, at::kInt, "q_kv_len");
+  need(blk_start, at::kInt, "blk_start"); need(blk_count, at::kInt, "blk_count");
+  need(block_table, at::kInt, "block_table"); need(out, at::kBFloat16, "out");
+  TORCH_CHECK(q.is_contiguous() && out.is_contiguous() && block_table.dim() == 2 && block_table.is_contiguous());
+  TORCH_CHECK(blk_start.numel() == blk_count.numel(), "block descriptor sizes");
+  c10::cuda::CUDAGuard guard(q.device());
+  nfb::PrefillAttnParams p = {};
+  p.q = static_cast<const __nv_bfloat16*>(q.data_ptr());
+  p.n_q_heads = static_cast<int>(n_q_heads); p.n_kv_heads = static_cast<int>(n_kv_heads);
+  p.head_dim = static_cast<int>(head_dim);
+  const int64_t T = q.numel() / (n_q_heads * head_dim);
+  TORCH_CHECK(q_seq.numel() == T && q_kv_len.numel() == T && out.numel() == q.numel(), "per-token array sizes");
+  p.q_seq = static_cast<const int*>(q_seq.data_ptr());
+  p.q_kv_len = static_cast<const int*>(q_kv_len.data_ptr());
+  p.blk_start = static_cast<const int*>(blk_start.data_ptr());
+  p.blk_count = static_cast<const int*>(blk_count.data_ptr());
+  p.n_blocks = static_cast<int>(blk_start.numel());
+  p.block_table = static_cast<const int*>(block_table.data_ptr());
+  p.table_stride = static_cast<int>(block_table.size(1));
+  p.kv = make_kv(k_codes, v_codes, k_scales, v_scales, page_size, n_kv_heads, head_dim, format, group);
+  p.sm_scale = static_cast<float>(sm_scale);
+  if (gate.has_value() && gate->defined()) {
+    need(*gate, at::kBFloat16, "gate"); need_rows(*gate, "gate");
+    p.gate = static_cast<const __nv_bfloat16*>(gate->data_ptr());
+    p.ld_gate = gate->stride(0);
+  }
+  p.out = static_cast<__nv_bfloat16*>(out.data_ptr());
+  chk(nfb::paged_attention_prefill(p, cur_stream(), pdl));
+}
+
+int64_t prefill_attn_block_tokens(int64_t n_q_heads, int64_t n_kv_heads) {
+  return nfb::prefill_attn_block_tokens(static_cast<int>(n_q_heads), static_cast<int>(n_kv_heads));
+}
+
 void causal_conv1d_silu(const Tensor& x, int64_t c_off, int64_t C, const Tensor& w, const Tensor& cu_seqlens,
                         const Tensor& token_seq, const Tensor& state_slot, const Tensor& conv_state,
                         const Tensor& out, bool update_state, bool one_token_per_seq, bool pdl) {
@@ -521,6 +560,8 @@ TORCH_LIBRARY(nfb200, m) {
   m.def("embed_gather(Tensor ids, Tensor table, Tensor out, bool pdl) -> ()", &embed_gather);
   m.def("attn_prep(Tensor proj, int q_off, int k_off, int v_off, int n_q_heads, int n_kv_heads, int head_dim, Tensor? q_norm_w, Tensor? k_norm_w, float eps, bool unit_offset, int rot_dim, Tensor inv_freq, float attn_factor, Tensor rope_pos, Tensor token_seq, Tensor cache_pos, Tensor block_table, Tensor q_out, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, bool pdl) -> ()", &attn_prep);
   m.def("paged_attention(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, int split_keys, int n_splits, Tensor part_o, Tensor part_ml, Tensor? gate, Tensor out, Tensor? tree_mask, Tensor? tree_base, int impl, bool pdl) -> ()", &paged_attention);
+  m.def("paged_attention_prefill(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor blk_start, Tensor blk_count, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, Tensor? gate, Tensor out, bool pdl) -> ()", &paged_attention_prefill);
+  m.def("prefill_attn_block_tokens(int n_q_heads, int n_kv_heads) -> int", &prefill_attn_block_tokens);
   m.def("causal_conv1d_silu(Tensor x, int c_off, int C, Tensor w, Tensor cu_seqlens, Tensor token_seq, Tensor state_slot, Tensor conv_state, Tensor out, bool update_state, bool one_token_per_seq, bool pdl) -> ()", &causal_conv1d_silu);
   m.def("gdn_recurrent(Tensor qkv, int q_off, int k_off, int v_off, Tensor proj, int z_off, int a_off, int b_off, int n_qk_heads, int n_v_heads, Tensor A_log, Tensor dt_bias, Tensor norm_w, float eps, Tensor cu_seqlens, Tensor state_slot, Tensor state, bool write_state, Tensor out, bool pdl) -> ()", &gdn_recurrent);
   m.def("argmax_rows(Tensor logits, Tensor out, bool pdl) -> ()", &argmax_rows);

@@ -42,6 +42,8 @@ class StepBatch:
     n_tokens: int
     n_seqs: int
     one_token_per_seq: bool = False
+    qblk_start: Optional[torch.Tensor] = None   # [NB] first token of each attention query block
+    qblk_count: Optional[torch.Tensor] = None   # [NB] tokens per query block
 
 
 class Workspace:
@@ -150,7 +152,7 @@ class LaunchCounter:
         fn = self._cache.get(name)
         if fn is None:
             raw = getattr(self._ops, name)
-            if name in ("gemm_pick_splits",):
+            if name in ("gemm_pick_splits", "prefill_attn_block_tokens"):
                 fn = raw
             elif name == "causal_conv1d_silu":
                 def fn(*a, _raw=raw):
@@ -232,6 +234,14 @@ class HybridModel:
                       planes.group, self.pdl)
         gate = proj[:, q_dim + kv_dim: q_dim + kv_dim + q_dim]
         out = ws.mix_attn[:T]
+        if (not b.one_token_per_seq and b.qblk_start is not None and D == 256 and self.attn_impl != 1
+                and T > b.n_seqs):
+            # prefill / wide verify: one CTA per (query block, kv head), K/V tiles dequantised once per block
+            ops.paged_attention_prefill(q, g.n_q_heads, g.n_kv_heads, D, b.table_row, b.kv_len, b.qblk_start,
+                                        b.qblk_count, kv.table, planes.k_codes, planes.v_codes, planes.k_scales,
+                                        planes.v_scales, kv.page_size, planes.fmt, planes.group, self.sm_scale, gate,
+                                        out, self.pdl)
+            return out, self.w[f"{prefix}/attn/o_proj"]
         split, n_splits = pick_attention_split(b.max_kv_len, T * g.n_kv_heads, max_splits=ws.max_splits_attn)
         chunk = max(1, ws.part_rows // n_splits)
         for t0 in range(0, T, chunk):

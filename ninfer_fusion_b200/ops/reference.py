@@ -86,14 +86,14 @@ def kv_quant_dequant(x: torch.Tensor, fmt: int, group: int = 64) -> torch.Tensor
     if fmt == KV_INT8_GROUP:
         g = x.reshape(*x.shape[:-1], -1, group)
         s = (g.abs().amax(-1, keepdim=True) / 127.0).to(torch.float16).float()
-        inv = torch.where(s > 0, 1.0 / s, torch.zeros_like(s))
-        q = torch.round(g * inv).clamp(-127, 127)
+        q = torch.where(s > 0, torch.round(g / torch.where(s > 0, s, torch.ones_like(s))), torch.zeros_like(g))
+        q = q.clamp(-127, 127)
         return (q * s).reshape(x.shape)
     if fmt == KV_NVFP4:
         g = x.reshape(*x.shape[:-1], -1, 16)
         s = e4m3_round(g.abs().amax(-1, keepdim=True) / 6.0)
-        inv = torch.where(s > 0, 1.0 / s, torch.zeros_like(s))
-        return (e2m1_round(g * inv) * s).reshape(x.shape)
+        q = torch.where(s > 0, g / torch.where(s > 0, s, torch.ones_like(s)), torch.zeros_like(g))
+        return (e2m1_round(q) * s).reshape(x.shape)
     raise ValueError(f"unknown KV format {fmt}")
 
 

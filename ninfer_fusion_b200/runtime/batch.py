@@ -27,13 +27,15 @@ class SeqChunk:
 
 
 class StepBuffers:
-    def __init__(self, max_tokens: int, max_seqs: int, device, mrope: bool = False):
+    def __init__(self, max_tokens: int, max_seqs: int, device, mrope: bool = False, attn_block_tokens: int = 16):
         self.max_tokens, self.max_seqs = max_tokens, max_seqs
         self.device = torch.device(device)
         self.pos_axes = 3 if mrope else 1
         T, B = max_tokens, max_seqs
+        self.attn_block_tokens = max(1, attn_block_tokens)
+        NB = (T + self.attn_block_tokens - 1) // self.attn_block_tokens + B
         sizes = [("ids", T), ("token_seq", T), ("table_row", T), ("cache_pos", T), ("rope_pos", T * self.pos_axes),
-                 ("kv_len", T), ("cu_seqlens", B + 1), ("state_slot", B), ("logit_rows", B)]
+                 ("kv_len", T), ("cu_seqlens", B + 1), ("state_slot", B), ("logit_rows", B), ("qblk_start", NB), ("qblk_count", NB)]
         self.offsets = {}
         off = 0
         for name, n in sizes:
@@ -68,6 +70,8 @@ class StepBuffers:
         cu, slot, lrows = self._hview("cu_seqlens", B + 1), self._hview("state_slot", B), self._hview("logit_rows", B)
         t = 0
         n_logit = 0
+        qt = self.attn_block_tokens
+        blk_s, blk_c = [], []
         max_kv = 1
         cu[0] = 0
         for b, c in enumerate(chunks):
@@ -85,12 +89,18 @@ class StepBuffers:
                 for a in range(3):
                     rpos[3 * t + a:3 * (t + n):3] = range(c.start_pos + d, c.start_pos + d + n)
             slot[b] = c.state_slot
+            for o in range(0, n, qt):
+                blk_s.append(t + o)
+                blk_c.append(min(qt, n - o))
             t += n
             cu[b + 1] = t
             if c.want_logits:
                 lrows[n_logit] = t - 1
                 n_logit += 1
             max_kv = max(max_kv, c.start_pos + n)
+        nb = len(blk_s)
+        self._hview("qblk_start", nb)[:] = blk_s
+        self._hview("qblk_count", nb)[:] = blk_c
         if upload:
             self.dev.copy_(self.host, non_blocking=True)
         rp = self._dview("rope_pos", T * self.pos_axes)
@@ -101,4 +111,5 @@ class StepBuffers:
                          kv_len=self._dview("kv_len", T), cu_seqlens=self._dview("cu_seqlens", B + 1),
                          state_slot=self._dview("state_slot", B), logit_rows=self._dview("logit_rows", n_logit),
                          max_kv_len=max_kv, n_tokens=T, n_seqs=B,
-                         one_token_per_seq=all(len(c.tokens) == 1 for c in chunks))
+                         one_token_per_seq=all(len(c.tokens) == 1 for c in chunks),
+                         qblk_start=self._dview("qblk_start", nb), qblk_count=self._dview("qblk_count", nb))

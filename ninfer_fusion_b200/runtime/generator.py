@@ -46,8 +46,9 @@ class Generator:
         self.states = GdnStatePool(cfg, max_batch, device, n_qk_heads=g.gdn_qk_heads, n_v_heads=g.gdn_v_heads)
         cap = max(prefill_chunk, max_batch)
         self.ws = Workspace(cfg, cap, max_batch, device, shard=shard, x_buffer=None if comm is None else comm.x)
-        self.bufs_prefill = StepBuffers(cap, max_batch, device)
-        self.bufs_decode = StepBuffers(max_batch, max_batch, device)
+        qt = int(self.model.ops.prefill_attn_block_tokens(g.n_q_heads, g.n_kv_heads)) if self.device.type == "cuda" else 16
+        self.bufs_prefill = StepBuffers(cap, max_batch, device, attn_block_tokens=qt)
+        self.bufs_decode = StepBuffers(max_batch, max_batch, device, attn_block_tokens=qt)
         pin = self.device.type == "cuda"
         self.out_host = torch.zeros(max_batch, dtype=torch.int32, pin_memory=pin)
         self._graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}

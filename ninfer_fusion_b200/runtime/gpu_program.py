@@ -1,0 +1,197 @@
+"""GPU program: lanes on the native kernels, CUDA graph per (batch size, context bucket, sampler kind).
+
+Decode round = fill the pinned step descriptor (+ per-row sampling parameters), one H2D copy, one graph
+launch (forward + arg-max or sampler + penalty-count update), one D2H copy of the token ids.  Prefill
+advances one lane by a chunk through the same ragged forward.  See `program.ProgramBase` for the verbs.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..models.config import ModelConfig
+from ..models.hybrid import HybridModel, ShardGeometry, StepBatch, Workspace
+from .batch import SeqChunk, StepBuffers
+from .generator import context_bucket
+from .kv_cache import GdnStatePool, PagedKvCache
+from .program import Lane, ProgramBase, SamplingParams
+
+
+class GpuProgram(ProgramBase):
+    def __init__(self, cfg: ModelConfig, weights: Dict[str, torch.Tensor], device, max_lanes: int = 32,
+                 max_context: int = 8192, kv_format="bf16", page_size: int = 64, prefill_chunk: int = 2048,
+                 use_graph: bool = True, pdl: bool = True, int8_group: int = 64, kv_pages: Optional[int] = None,
+                 shard: Optional[ShardGeometry] = None, comm=None, penalties: bool = False):
+        super().__init__(cfg, max_lanes, max_context)
+        self.device = torch.device(device)
+        self.prefill_chunk = prefill_chunk
+        self.use_graph = use_graph
+        self.model = HybridModel(cfg, weights, device, pdl=pdl, shard=shard)
+        self.model.comm = comm
+        g = self.model.g
+        pages_per_row = (max_context + page_size - 1) // page_size
+        n_pages = kv_pages if kv_pages is not None else max_lanes * pages_per_row
+        self.kv = PagedKvCache(cfg, n_pages, page_size, max_lanes, pages_per_row, device, formats=kv_format,
+                               int8_group=int8_group, n_kv_heads=g.n_kv_heads)
+        self.states = GdnStatePool(cfg, max_lanes, device, n_qk_heads=g.gdn_qk_heads, n_v_heads=g.gdn_v_heads)
+        cap = max(prefill_chunk, max_lanes)
+        self.ws = Workspace(cfg, cap, max_lanes, device, shard=shard, x_buffer=None if comm is None else comm.x)
+        qt = int(self.model.ops.prefill_attn_block_tokens(g.n_q_heads, g.n_kv_heads))
+        self.bufs_prefill = StepBuffers(cap, max_lanes, device, attn_block_tokens=qt)
+        self.bufs_decode = StepBuffers(max_lanes, max_lanes, device, attn_block_tokens=qt)
+        self.out_host = torch.zeros(max_lanes, dtype=torch.int32, pin_memory=True)
+        # per-row sampling parameters (pinned host + device twins), filled every sampled round
+        B = max_lanes
+        self.sp_host = {"temperature": torch.zeros(B, pin_memory=True), "top_p": torch.ones(B, pin_memory=True),
+                        "min_p": torch.zeros(B, pin_memory=True), "presence": torch.zeros(B, pin_memory=True),
+                        "frequency": torch.zeros(B, pin_memory=True),
+                        "top_k": torch.zeros(B, dtype=torch.int32, pin_memory=True),
+                        "seeds": torch.zeros(B, dtype=torch.int64, pin_memory=True),
+                        "positions": torch.zeros(B, dtype=torch.int32, pin_memory=True)}
+        self.sp_dev = {k: v.to(self.device) for k, v in self.sp_host.items()}
+        self.penalties = penalties
+        self.token_counts = (torch.zeros((B, g.vocab_rows), dtype=torch.int32, device=self.device)
+                             if penalties and comm is None else None)
+        self._graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
+
+    # ------------------------------------------------------------------ lanes
+    def _alloc_slot(self) -> int:
+        return self.states.alloc()
+
+    def _release(self, lane: Lane) -> None:
+        self.kv.free_row(lane.row)
+        self.states.release(lane.slot)
+        if self.token_counts is not None:
+            self.token_counts[lane.row].zero_()
+
+    def _kv_room(self, n_tokens: int) -> bool:
+        return self.kv.pool.free_pages >= (n_tokens + self.kv.page_size - 1) // self.kv.page_size
+
+    # ------------------------------------------------------------------ sampling
+    def _fill_sampling(self, lanes: Sequence[Lane]) -> bool:
+        """Returns True when every lane is greedy (arg-max graph)."""
+        if all(l.sampling.greedy for l in lanes):
+            return True
+        h = self.sp_host
+        for i, l in enumerate(lanes):
+            s = l.sampling
+            h["temperature"][i] = s.temperature
+            h["top_k"][i] = s.top_k
+            h["top_p"][i] = s.top_p
+            h["min_p"][i] = s.min_p
+            h["presence"][i] = s.presence_penalty
+            h["frequency"][i] = s.frequency_penalty
+            h["seeds"][i] = s.seed
+            h["positions"][i] = len(l.tokens)
+        for k in h:
+            self.sp_dev[k].copy_(h[k], non_blocking=True)
+        return False
+
+    def _select(self, logits: torch.Tensor, rows: torch.Tensor, greedy: bool, out: torch.Tensor) -> None:
+        ops = self.model.ops
+        n = logits.shape[0]
+        if greedy:
+            if self.model.comm is not None:
+                self.model.comm.argmax(self.model, logits, out)
+            else:
+                ops.argmax_rows(logits, out, self.model.pdl)
+            return
+        if self.model.comm is not None:
+            raise NotImplementedError("stochastic sampling under tensor parallelism needs gathered logits")
+        d = self.sp_dev
+        counts = None
+        if self.token_counts is not None:
+            counts = self.token_counts.index_select(0, rows.long())
+        ops.sample_rows(logits, d["temperature"][:n], d["top_k"][:n], d["top_p"][:n], d["min_p"][:n],
+                        d["presence"][:n] if counts is not None else None,
+                        d["frequency"][:n] if counts is not None else None, counts, d["seeds"][:n],
+                        d["positions"][:n], 0, out, None)
+
+    def _forward_select(self, batch: StepBatch, greedy: bool, rows: torch.Tensor) -> torch.Tensor:
+        hidden = self.model.forward_hidden(self.ws, batch, self.kv, self.states)
+        if batch.logit_rows.numel() == 0:
+            return self.ws.next_ids[:0]
+        lg = self.model.logits(self.ws, batch, hidden)
+        out = self.ws.next_ids[: lg.shape[0]]
+        self._select(lg, rows, greedy, out)
+        return out
+
+    # ------------------------------------------------------------------ prefill
+    def prefill_step(self, lane: Lane, budget: int) -> Optional[int]:
+        n = min(budget, self.prefill_chunk, len(lane.tokens) - lane.n_cached)
+        done = lane.n_cached + n == len(lane.tokens)
+        self.kv.ensure(lane.row, lane.n_cached + n + 1)
+        self.kv.publish()
+        chunk = SeqChunk(lane.row, lane.slot, lane.n_cached, lane.tokens[lane.n_cached:lane.n_cached + n], done)
+        batch = self.bufs_prefill.build([chunk])
+        greedy = self._fill_sampling([lane]) if done else True
+        rows = torch.tensor([lane.row], device=self.device)
+        ids = self._forward_select(batch, greedy, rows)
+        lane.n_cached += n
+        if not done:
+            return None
+        self.out_host[:1].copy_(ids[:1], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.model.status.check("after prefill")
+        lane.last_token = int(self.out_host[0])
+        return lane.last_token
+
+    # ------------------------------------------------------------------ decode
+    def _chunks(self, lanes: Sequence[Lane]) -> List[SeqChunk]:
+        return [SeqChunk(l.row, l.slot, l.n_cached, [l.last_token], True) for l in lanes]
+
+    def _graph_for(self, lanes: Sequence[Lane], bucket: int, greedy: bool) -> torch.cuda.CUDAGraph:
+        key = (len(lanes), bucket, greedy)
+        g = self._graphs.get(key)
+        if g is not None:
+            return g
+        batch = self.bufs_decode.build(self._chunks(lanes), upload=True)
+        batch.max_kv_len = bucket
+        rows = batch.table_row
+        saved = [(c.clone(), s.clone()) for c, s in zip(self.states.conv, self.states.ssm)]
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                self._forward_select(batch, greedy, rows)
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._forward_select(batch, greedy, rows)
+        torch.cuda.synchronize(self.device)
+        for (c0, s0), c, s in zip(saved, self.states.conv, self.states.ssm):
+            c.copy_(c0)
+            s.copy_(s0)
+        self._graphs[key] = g
+        return g
+
+    def decode_round(self, lanes: Sequence[Lane]) -> List[int]:
+        B = len(lanes)
+        if B == 0:
+            return []
+        for l in lanes:
+            l.tokens.append(l.last_token)
+            self.kv.ensure(l.row, l.n_cached + 2)
+        self.kv.publish()
+        greedy = self._fill_sampling(lanes)
+        if self.use_graph:
+            bucket = context_bucket(max(l.n_cached for l in lanes) + 1)
+            graph = self._graph_for(lanes, bucket, greedy)
+            self.bufs_decode.build(self._chunks(lanes), upload=True)
+            graph.replay()
+            ids = self.ws.next_ids[:B]
+        else:
+            batch = self.bufs_decode.build(self._chunks(lanes), upload=True)
+            ids = self._forward_select(batch, greedy, batch.table_row)
+        self.out_host[:B].copy_(ids, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        toks = [int(v) for v in self.out_host[:B]]
+        if self.token_counts is not None:
+            r = torch.tensor([l.row for l in lanes], device=self.device)
+            self.token_counts[r, torch.tensor(toks, device=self.device)] += 1
+        for l, t in zip(lanes, toks):
+            l.n_cached += 1
+            l.last_token = t
+        return toks

@@ -1,0 +1,166 @@
+"""Program: the physical layer under the engine (lanes, KV rows, GDN slots, graphs, sampling).
+
+A *lane* is one live sequence: a KV block-table row, a GDN state slot, its token history and its
+sampling state.  The engine drives three verbs -- `prefill_step` (advance one lane by a chunk),
+`decode_round` (one token for every listed lane, exact batch size, CUDA graph per (B, context bucket,
+sampler kind)) and `close` -- plus `fork` / `snapshot` for prefix reuse.  This is the counterpart of the
+reference's `Program<Variant>` surface (src/targets/qwen3_6/export/ninfer/targets/qwen3_6/runtime.h:739-905:
+plan_request / advance_prefill / decode / commit / finish) with one deliberate difference: batch sizes
+are not capped at 16 lanes, because the B200 configurations ask for 32..128 concurrent sequences.
+
+`ReferenceProgram` implements the same verbs on the pure-PyTorch CPU oracle, so the engine, the
+scheduler and the gateways can be tested end to end without a GPU.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..models.config import ModelConfig
+from ..ops import reference as R
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 0.0          # <= 0: greedy
+    top_k: int = 20
+    top_p: float = 1.0
+    min_p: float = 0.0
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    seed: int = 0
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature <= 0.0 or self.top_k == 1
+
+
+@dataclass
+class Lane:
+    lane_id: int
+    row: int                 # KV block-table row
+    slot: int                # GDN state slot
+    tokens: List[int] = field(default_factory=list)   # every token whose KV/state is (or will be) materialised
+    n_cached: int = 0        # tokens already run through the model
+    sampling: SamplingParams = field(default_factory=SamplingParams)
+    last_token: int = -1     # sampled but not yet fed
+
+
+class ProgramBase:
+    """Lane bookkeeping shared by the GPU and the CPU-reference programs."""
+
+    def __init__(self, cfg: ModelConfig, max_lanes: int, max_context: int):
+        self.cfg = cfg
+        self.max_lanes = max_lanes
+        self.max_context = max_context
+        self.lanes: Dict[int, Lane] = {}
+        self._free_rows = list(range(max_lanes - 1, -1, -1))
+        self._next_id = 0
+
+    # ---- capacity ----
+    def free_lanes(self) -> int:
+        return len(self._free_rows)
+
+    def can_admit(self, n_prompt: int, max_new: int) -> bool:
+        return bool(self._free_rows) and n_prompt + max_new <= self.max_context and self._kv_room(n_prompt + max_new)
+
+    def _kv_room(self, n_tokens: int) -> bool:
+        return True
+
+    def open(self, prompt: Sequence[int], sampling: Optional[SamplingParams] = None) -> Lane:
+        if not self._free_rows:
+            raise MemoryError("no free lane")
+        if len(prompt) == 0:
+            raise ValueError("empty prompt")
+        row = self._free_rows.pop()
+        lane = Lane(self._next_id, row, self._alloc_slot(), list(prompt), 0, sampling or SamplingParams())
+        self._next_id += 1
+        self.lanes[lane.lane_id] = lane
+        return lane
+
+    def close(self, lane: Lane) -> None:
+        if self.lanes.pop(lane.lane_id, None) is None:
+            return
+        self._release(lane)
+        self._free_rows.append(lane.row)
+
+    # ---- to be provided ----
+    def _alloc_slot(self) -> int:
+        raise NotImplementedError
+
+    def _release(self, lane: Lane) -> None:
+        raise NotImplementedError
+
+    def prefill_step(self, lane: Lane, budget: int) -> Optional[int]:
+        """Run up to `budget` not-yet-cached prompt tokens; returns the first sampled token when the prompt is done."""
+        raise NotImplementedError
+
+    def decode_round(self, lanes: Sequence[Lane]) -> List[int]:
+        raise NotImplementedError
+
+
+class ReferenceProgram(ProgramBase):
+    """CPU program on the fp32 oracle model (tiny configurations only)."""
+
+    def __init__(self, cfg: ModelConfig, weights, max_lanes: int = 8, max_context: int = 4096, kv_format: str = "bf16"):
+        super().__init__(cfg, max_lanes, max_context)
+        from ..models.reference_model import ReferenceModel, ReferenceSequence
+
+        self._Seq = ReferenceSequence
+        self.model = ReferenceModel(cfg, weights)
+        self.kv_fmt = R.KV_FORMAT_NAMES[kv_format]
+        self._seqs: Dict[int, object] = {}
+        self._slots = 0
+
+    def _alloc_slot(self) -> int:
+        self._slots += 1
+        return self._slots
+
+    def _release(self, lane: Lane) -> None:
+        self._seqs.pop(lane.lane_id, None)
+
+    def _sample(self, lane: Lane, logits: torch.Tensor) -> int:
+        sp = lane.sampling
+        lg = logits.float().clone()
+        if sp.presence_penalty or sp.frequency_penalty:
+            counts = torch.bincount(torch.tensor(lane.tokens), minlength=lg.numel()).float()
+            lg -= (counts > 0).float() * sp.presence_penalty + counts * sp.frequency_penalty
+        if sp.greedy:
+            return int(R.argmax_lowest(lg[None])[0])
+        k = sp.top_k if 0 < sp.top_k <= 32 else 32
+        vals, idx = torch.sort(lg, descending=True, stable=True)
+        vals, idx = vals[:k], idx[:k]
+        p = torch.softmax((vals - vals[0]) / sp.temperature, 0)
+        keep = (p >= sp.min_p * p[0]) if sp.min_p > 0 else torch.ones_like(p, dtype=torch.bool)
+        p = p * keep
+        p = p / p.sum()
+        if sp.top_p < 1.0:
+            c = torch.cumsum(p, 0)
+            m = int((c < sp.top_p).sum().item()) + 1
+            p[m:] = 0
+            p = p / p.sum()
+        g = torch.Generator().manual_seed((sp.seed * 1000003 + len(lane.tokens)) & 0x7FFFFFFF)
+        return int(idx[int(torch.multinomial(p, 1, generator=g))])
+
+    def prefill_step(self, lane: Lane, budget: int) -> Optional[int]:
+        seq = self._seqs.setdefault(lane.lane_id, self._Seq(self.cfg, self.kv_fmt))
+        n = min(budget, len(lane.tokens) - lane.n_cached)
+        h = self.model.forward(seq, torch.tensor(lane.tokens[lane.n_cached:lane.n_cached + n]))
+        lane.n_cached += n
+        if lane.n_cached < len(lane.tokens):
+            return None
+        lane.last_token = self._sample(lane, self.model.logits(h[-1:])[0])
+        return lane.last_token
+
+    def decode_round(self, lanes: Sequence[Lane]) -> List[int]:
+        out = []
+        for lane in lanes:
+            seq = self._seqs[lane.lane_id]
+            lane.tokens.append(lane.last_token)
+            h = self.model.forward(seq, torch.tensor([lane.last_token]))
+            lane.n_cached += 1
+            lane.last_token = self._sample(lane, self.model.logits(h)[0])
+            out.append(lane.last_token)
+        return out

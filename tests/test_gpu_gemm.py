@@ -96,7 +96,7 @@ def test_pick_splits_covers_k(ops):
         assert 1 <= s <= 8 and (nkb + per - 1) // per == s
     for T, N, K, epi in [(32, 5120, 17408, EPI_RESIDUAL), (32, 2060, 5120, EPI_STORE), (1, 34816, 5120, EPI_SWIGLU)]:
         s = int(ops.gemm_pick_splits(T, N, K, epi))
-        assert s in (1, 2, 4, 8)
+        assert 1 <= s <= 8
 
 
 def test_gemm_pdl_chain(ops, status):
@@ -112,7 +112,7 @@ def test_gemm_pdl_chain(ops, status):
     _check(out, ref_h @ w2.float().t())
 
 
-@pytest.mark.parametrize("T,splits", [(1, 8), (16, 4), (32, 2), (32, 4), (64, 2), (100, 2)])
+@pytest.mark.parametrize("T,splits", [(1, 8), (16, 5), (32, 2), (32, 6), (32, 3), (64, 2), (100, 2)])
 @pytest.mark.parametrize("epi", [EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU])
 def test_gemm_cluster_splitk(ops, status, T, splits, epi):
     """Split-K inside a thread-block cluster: peers hand fp32 tiles to the leader through DSMEM."""

@@ -286,3 +286,60 @@ def test_speculative_accept(ops):
     ops.accept_greedy_tree(tgt.cuda(), tok.cuda(), parent.cuda(), 4, n1, t1, nd)
     assert torch.equal(n1.cpu(), nr) and torch.equal(t1.cpu(), tr) and torch.equal(nd.cpu(), nodes_r)
     assert int(nr[0]) == 2 and tr[0, :3].tolist() == [12, 14, 99]
+
+
+@pytest.mark.parametrize("name,fmt,group", FORMATS)
+@pytest.mark.parametrize("hq,hkv", [(6, 1), (24, 4), (16, 2), (3, 1)])
+def test_prefill_attention(ops, name, fmt, group, hq, hkv):
+    """Causal block attention over a ragged chunk (one sequence continues mid-way) vs the fp32 oracle."""
+    torch.manual_seed(4)
+    D, P = 256, 16
+    lens = [150, 37]
+    chunk_from = [60, 0]            # tokens [60, 150) of sequence 0 and all of sequence 1 are the "chunk"
+    B = len(lens)
+    max_pages = (max(lens) + P - 1) // P
+    n_pages = B * max_pages + 2
+    table = torch.randperm(n_pages)[: B * max_pages].int().view(B, max_pages).cuda()
+    k_codes, v_codes, k_sc, v_sc = _planes(n_pages, hkv, P, D, fmt, group)
+    inv_freq = R.rope_inv_freq(64, 1e7).cuda()
+    ld = (2 * hq + 2 * hkv) * D
+    T = sum(lens)
+    proj = torch.randn(T, ld).to(torch.bfloat16).cuda()
+    tok_seq = torch.cat([torch.full((n,), b) for b, n in enumerate(lens)]).int().cuda()
+    pos = torch.cat([torch.arange(n) for n in lens]).int().cuda()
+    q_all = torch.empty((T, hq, D), dtype=torch.bfloat16, device="cuda")
+    k_off, v_off = hq * D, hq * D + hkv * D + hq * D
+    ops.attn_prep(proj, 0, k_off, v_off, hq, hkv, D, None, None, 1e-6, True, 0, inv_freq, 1.0, pos, tok_seq, pos, table,
+                  q_all, k_codes, v_codes, k_sc, v_sc, P, fmt, group, False)
+    # the chunk's tokens
+    rows, starts = [], [0, lens[0]]
+    for b in range(B):
+        rows += list(range(starts[b] + chunk_from[b], starts[b] + lens[b]))
+    rows_t = torch.tensor(rows).cuda()
+    q = q_all[rows_t].contiguous()
+    q_seq = tok_seq[rows_t].contiguous()
+    kv_len = (pos[rows_t] + 1).contiguous()
+    gate = torch.randn(len(rows), hq * D).to(torch.bfloat16).cuda()
+    qt = int(ops.prefill_attn_block_tokens(hq, hkv))
+    blk_s, blk_c, t = [], [], 0
+    for b in range(B):
+        n = lens[b] - chunk_from[b]
+        for o in range(0, n, qt):
+            blk_s.append(t + o)
+            blk_c.append(min(qt, n - o))
+        t += n
+    out = torch.full((len(rows), hq * D), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.paged_attention_prefill(q, hq, hkv, D, q_seq, kv_len, torch.tensor(blk_s).int().cuda(),
+                                torch.tensor(blk_c).int().cuda(), table, k_codes, v_codes, k_sc, v_sc, P, fmt, group,
+                                1 / 16, gate, out, False)
+    pf = proj.float().cpu()
+    k_ref = R.kv_quant_dequant(pf[:, k_off:k_off + hkv * D].view(T, hkv, D), fmt, group)
+    v_ref = R.kv_quant_dequant(pf[:, v_off:v_off + hkv * D].view(T, hkv, D), fmt, group)
+    worst = 0.0
+    for i, r in enumerate(rows):
+        b = int(tok_seq[r])
+        ks_, vs_ = k_ref[starts[b]:starts[b] + lens[b]], v_ref[starts[b]:starts[b] + lens[b]]
+        o = R.gqa_attention(q[i:i + 1].float().cpu(), ks_, vs_, torch.tensor([int(kv_len[i])]), 1 / 16)
+        o = R.bf16_round(o).reshape(-1) * torch.sigmoid(gate[i].float().cpu())
+        worst = max(worst, (out[i].float().cpu() - o).abs().max().item())
+    assert worst < 0.03, f"{name}: err {worst}"

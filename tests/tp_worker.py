@@ -52,12 +52,17 @@ def main():
         single = Generator(cfg, full, dev, max_batch=4, max_context=256, kv_format="bf16", page_size=16,
                            prefill_chunk=64, use_graph=False).generate(prompts, n_new)
         for key, out in results.items():
-            same = sum(int(a == b) for o, s in zip(out, single) for a, b in zip(o, s))
-            total = sum(len(s) for s in single)
-            # partial sums are reduced in a different order than on one GPU: allow rare near-tie flips
-            if same < 0.8 * total:
+            # greedy decoding diverges for good after one near-tie flip (partial sums are reduced in a different
+            # order than on one GPU), so compare the agreeing PREFIX of every sequence and the first token
+            prefix = []
+            for o, s in zip(out, single):
+                n = 0
+                while n < len(s) and o[n] == s[n]:
+                    n += 1
+                prefix.append(n)
+            if min(prefix) < 1 or sum(prefix) < 0.5 * sum(len(s) for s in single):
                 ok = False
-            msg += f" {key}:{same}/{total}"
+            msg += f" {key}:prefix{prefix}"
         if results[("fused", False)] != results[("fused", True)]:
             ok = False
             msg += " fused graph!=eager"
