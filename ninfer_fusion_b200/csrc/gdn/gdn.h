@@ -48,5 +48,7 @@ struct GdnParams {
   __nv_bfloat16* out;        // [T, Hv * 128]
 };
 const char* gdn_recurrent(const GdnParams& p, cudaStream_t stream, bool pdl);
+// Multi-token variant (token groups staged in shared memory); gdn_recurrent dispatches to it when T > n_seq.
+const char* gdn_prefill(const GdnParams& p, cudaStream_t stream, bool pdl);
 
 }  // namespace nfb

@@ -152,6 +152,7 @@ const char* gdn_recurrent(const GdnParams& p, cudaStream_t stream, bool pdl) {
   if (p.T <= 0 || p.n_seq <= 0) return nullptr;
   if (p.n_v_heads % p.n_qk_heads) return "gdn_recurrent: value heads must be a multiple of qk heads";
   if ((p.q_off | p.k_off | p.ld_qkv) % 4) return "gdn_recurrent: q/k offsets must be multiples of 4";
+  if (p.T > p.n_seq && (p.v_off | p.z_off | p.ld_proj) % 4 == 0) return gdn_prefill(p, stream, pdl);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.n_v_heads, p.n_seq); cfg.blockDim = dim3(kThreads); cfg.stream = stream;
   cudaLaunchAttribute attr[1];

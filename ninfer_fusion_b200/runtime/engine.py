@@ -1,0 +1,361 @@
+"""Engine: the request control plane over a Program.
+
+One worker thread owns every mutation (admission, prefill steps, decode rounds, commits); callers
+submit requests and consume events from per-request queues.  Loop order per iteration: expire
+deadlines -> settle cancellations -> admit FIFO heads while lanes / KV room allow -> advance ONE
+prefill chunk (governed chunk size) -> one decode round over every decode-ready lane -> commit
+(stop rules, budgets) -> publish.  Failures are classified Request / Resource / Invariant: a
+request-domain failure fails only that lane, anything else poisons the engine until `recover()`
+rebuilds the Program.  This keeps the reference's engine contract
+(include/ninfer/engine.h:78-163, src/runtime/engine/engine_core.h: worker_loop :2248-2479,
+commit ordering :1164, failure classification :454-496, lane failure :2148-2196, fault injection
+:2118-2142, bandwidth governor src/runtime/engine/bandwidth_governor.h) with a batch envelope sized
+for B200 (tens of lanes instead of 16).
+"""
+from __future__ import annotations
+
+import os
+import queue
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence
+
+from .program import Lane, ProgramBase, SamplingParams
+
+
+class RequestError(Exception):
+    """The request itself is at fault (bad arguments, too long, cancelled)."""
+
+
+class ResourceError(Exception):
+    """The engine ran out of something (lanes, KV pages, a device wait ran out)."""
+
+
+class InvariantError(Exception):
+    """Internal state is inconsistent; the engine must be rebuilt."""
+
+
+@dataclass
+class RequestOptions:
+    max_tokens: int = 256
+    sampling: SamplingParams = field(default_factory=SamplingParams)
+    stop_token_ids: Sequence[int] = ()
+    deadline_s: Optional[float] = None       # wall-clock budget for the whole request
+    pending_timeout_s: Optional[float] = None  # how long it may wait for admission
+    session: Optional[str] = None            # continuation key for prefix reuse
+
+
+@dataclass
+class Event:
+    kind: str                 # "token" | "done" | "error"
+    token: int = -1
+    finish_reason: str = ""   # "stop" | "length" | "cancelled" | "error" | "timeout"
+    message: str = ""
+
+
+@dataclass
+class RuntimeStats:
+    requests_submitted: int = 0
+    requests_done: int = 0
+    requests_failed: int = 0
+    requests_rejected: int = 0
+    prompt_tokens: int = 0
+    completion_tokens: int = 0
+    prefill_s: float = 0.0
+    decode_s: float = 0.0
+    decode_rounds: int = 0
+    prefix_hits: int = 0
+    prefix_tokens_reused: int = 0
+
+    def as_dict(self) -> dict:
+        d = dict(self.__dict__)
+        d["decode_tok_s"] = self.completion_tokens / self.decode_s if self.decode_s > 0 else 0.0
+        d["prefill_tok_s"] = self.prompt_tokens / self.prefill_s if self.prefill_s > 0 else 0.0
+        return d
+
+
+class GenerationHandle:
+    def __init__(self, request_id: int):
+        self.request_id = request_id
+        self.events: "queue.Queue[Event]" = queue.Queue()
+        self.tokens: List[int] = []
+        self.finish_reason: str = ""
+        self.error: str = ""
+        self.t_submit = time.perf_counter()
+        self.t_first: Optional[float] = None
+        self.t_done: Optional[float] = None
+        self._cancel = threading.Event()
+
+    def cancel(self) -> None:
+        self._cancel.set()
+
+    @property
+    def cancelled(self) -> bool:
+        return self._cancel.is_set()
+
+    def wait(self, sink: Optional[Callable[[Event], None]] = None, timeout: Optional[float] = None) -> List[int]:
+        """Block until the request finishes; `sink` sees every event in publication order."""
+        end = None if timeout is None else time.perf_counter() + timeout
+        while True:
+            left = None if end is None else max(0.0, end - time.perf_counter())
+            try:
+                ev = self.events.get(timeout=left)
+            except queue.Empty:
+                raise TimeoutError("generation did not finish in time") from None
+            if sink is not None:
+                sink(ev)
+            if ev.kind in ("done", "error"):
+                return self.tokens
+
+    @property
+    def ttft_ms(self) -> Optional[float]:
+        return None if self.t_first is None else (self.t_first - self.t_submit) * 1e3
+
+
+@dataclass
+class _Request:
+    handle: GenerationHandle
+    prompt: List[int]
+    opts: RequestOptions
+    lane: Optional[Lane] = None
+    state: str = "pending"     # pending | prefill | decode | finished
+    n_generated: int = 0
+
+
+class BandwidthGovernor:
+    """Shrinks the prefill chunk when decode rounds slow down, restores it when they recover.
+
+    Decode latency is compared with its own running floor (fastest recent rounds); when a round that
+    shared the loop with a prefill step exceeds floor * tolerance the prefill unit halves (not below
+    `min_unit`), and it doubles back after `recover_rounds` clean rounds."""
+
+    def __init__(self, max_unit: int, min_unit: int = 128, tolerance: float = 1.5, recover_rounds: int = 8,
+                 enabled: bool = True):
+        self.max_unit, self.min_unit = max_unit, min(min_unit, max_unit)
+        self.unit = max_unit
+        self.tolerance, self.recover_rounds = tolerance, recover_rounds
+        self.enabled = enabled
+        self.floor_ms: Optional[float] = None
+        self._clean = 0
+
+    def observe(self, decode_ms: float, shared_with_prefill: bool) -> None:
+        if not self.enabled:
+            return
+        if not shared_with_prefill:
+            self.floor_ms = decode_ms if self.floor_ms is None else min(self.floor_ms * 1.02, decode_ms) \
+                if decode_ms < self.floor_ms * 1.02 else self.floor_ms
+        if self.floor_ms is None:
+            return
+        if shared_with_prefill and decode_ms > self.floor_ms * self.tolerance:
+            self.unit = max(self.min_unit, self.unit // 2)
+            self._clean = 0
+        else:
+            self._clean += 1
+            if self._clean >= self.recover_rounds and self.unit < self.max_unit:
+                self.unit = min(self.max_unit, self.unit * 2)
+                self._clean = 0
+
+
+class Engine:
+    """Opaque engine facade: `submit()` from any thread, one worker thread does the rest."""
+
+    def __init__(self, program_factory: Callable[[], ProgramBase], max_pending: int = 256,
+                 prefill_chunk: int = 2048, governor: bool = True):
+        self._factory = program_factory
+        self.program = program_factory()
+        self.max_pending = max_pending
+        self.governor = BandwidthGovernor(prefill_chunk, enabled=governor)
+        self.stats = RuntimeStats()
+        self._pending: List[_Request] = []
+        self._active: List[_Request] = []
+        self._lock = threading.Lock()
+        self._wake = threading.Condition(self._lock)
+        self._next_id = 0
+        self._failed: Optional[str] = None
+        self._stop = False
+        self._fault = os.environ.get("NINFER_FAULT_INJECT", "")
+        self._fault_min_id = int(os.environ.get("NINFER_FAULT_INJECT_MIN_ID", "0"))
+        self._worker = threading.Thread(target=self._worker_loop, name="engine-worker", daemon=True)
+        self._worker.start()
+
+    # ------------------------------------------------------------------ public surface
+    def submit(self, prompt: Sequence[int], opts: Optional[RequestOptions] = None) -> GenerationHandle:
+        opts = opts or RequestOptions()
+        with self._wake:
+            if self._failed is not None:
+                raise ResourceError(f"engine failed: {self._failed}; call recover()")
+            if len(self._pending) >= self.max_pending:
+                self.stats.requests_rejected += 1
+                raise ResourceError("server_overloaded: pending queue is full")
+            if len(prompt) == 0:
+                raise RequestError("empty prompt")
+            if len(prompt) + opts.max_tokens > self.program.max_context:
+                self.stats.requests_rejected += 1
+                raise RequestError(f"prompt ({len(prompt)}) + max_tokens ({opts.max_tokens}) exceeds the "
+                                   f"context window ({self.program.max_context})")
+            h = GenerationHandle(self._next_id)
+            self._next_id += 1
+            self._pending.append(_Request(h, list(prompt), opts))
+            self.stats.requests_submitted += 1
+            self._wake.notify_all()
+            return h
+
+    def generate(self, prompt: Sequence[int], opts: Optional[RequestOptions] = None) -> List[int]:
+        return self.submit(prompt, opts).wait()
+
+    def health(self) -> dict:
+        with self._lock:
+            return {"status": "failed" if self._failed else "ok", "pending": len(self._pending),
+                    "active": len(self._active), "free_lanes": self.program.free_lanes()}
+
+    def recover(self) -> None:
+        """Rebuild the Program after an engine-wide failure; in-flight requests were already failed."""
+        with self._wake:
+            if self._failed is None:
+                return
+            self.program = self._factory()
+            self._failed = None
+            self._wake.notify_all()
+
+    def shutdown(self) -> None:
+        with self._wake:
+            self._stop = True
+            self._wake.notify_all()
+        self._worker.join(timeout=10)
+
+    # ------------------------------------------------------------------ worker
+    def _publish(self, req: _Request, ev: Event) -> None:
+        h = req.handle
+        if ev.kind == "token":
+            if h.t_first is None:
+                h.t_first = time.perf_counter()
+            h.tokens.append(ev.token)
+        else:
+            h.finish_reason = ev.finish_reason
+            h.error = ev.message
+            h.t_done = time.perf_counter()
+        h.events.put(ev)
+
+    def _finish(self, req: _Request, reason: str, message: str = "") -> None:
+        if req.state == "finished":
+            return
+        req.state = "finished"
+        if req.lane is not None:
+            self.program.close(req.lane)
+            req.lane = None
+        if reason == "error":
+            self.stats.requests_failed += 1
+            self._publish(req, Event("error", finish_reason="error", message=message))
+        else:
+            self.stats.requests_done += 1
+            self._publish(req, Event("done", finish_reason=reason))
+
+    def _commit_token(self, req: _Request, tok: int) -> None:
+        """Commit-before-publish: budget and stop rules are applied before the token becomes visible."""
+        req.n_generated += 1
+        self.stats.completion_tokens += 1
+        if tok in req.opts.stop_token_ids:
+            self._finish(req, "stop")
+            return
+        self._publish(req, Event("token", token=tok))
+        if req.n_generated >= req.opts.max_tokens:
+            self._finish(req, "length")
+
+    def _maybe_inject(self, req: _Request) -> None:
+        if self._fault and req.handle.request_id >= self._fault_min_id:
+            kind, self._fault = self._fault, ""
+            if kind == "request_once":
+                raise RequestError("injected request fault")
+            if kind == "invariant_once":
+                raise InvariantError("injected invariant fault")
+
+    def _admit(self) -> None:
+        now = time.perf_counter()
+        with self._lock:
+            pend = list(self._pending)
+        for req in pend:
+            if req.handle.cancelled:
+                with self._lock:
+                    self._pending.remove(req)
+                self._finish(req, "cancelled")
+                continue
+            t_wait = req.opts.pending_timeout_s
+            if t_wait is not None and now - req.handle.t_submit > t_wait:
+                with self._lock:
+                    self._pending.remove(req)
+                self._finish(req, "error", "request_queue_timeout")
+                continue
+            if not self.program.can_admit(len(req.prompt), req.opts.max_tokens):
+                break  # FIFO: do not let later requests overtake the head
+            with self._lock:
+                self._pending.remove(req)
+            try:
+                self._maybe_inject(req)
+                req.lane = self.program.open(req.prompt, req.opts.sampling)
+                req.state = "prefill"
+                self._active.append(req)
+            except RequestError as e:
+                self._finish(req, "error", str(e))
+            except Exception:
+                self._active.append(req)  # it must be among the victims of the engine-wide failure
+                raise
+
+    def _worker_loop(self) -> None:
+        while True:
+            with self._wake:
+                while not self._stop and (self._failed is not None or (not self._pending and not self._active)):
+                    self._wake.wait(timeout=0.5)
+                if self._stop:
+                    break
+            try:
+                self._iteration()
+            except (InvariantError, ResourceError, RuntimeError, MemoryError) as e:
+                # engine-wide failure: fail every in-flight request, refuse new ones until recover()
+                with self._lock:
+                    self._failed = f"{type(e).__name__}: {e}"
+                    victims = self._active + self._pending
+                    self._active, self._pending = [], []
+                for req in victims:
+                    req.lane = None  # the Program is discarded as a whole
+                    self._finish(req, "error", self._failed)
+
+    def _iteration(self) -> None:
+        now = time.perf_counter()
+        for req in list(self._active):
+            if req.handle.cancelled:
+                self._active.remove(req)
+                self._finish(req, "cancelled")
+            elif req.opts.deadline_s is not None and now - req.handle.t_submit > req.opts.deadline_s:
+                self._active.remove(req)
+                self._finish(req, "timeout")
+        self._admit()
+        did_prefill = False
+        for req in self._active:
+            if req.state == "prefill":
+                t0 = time.perf_counter()
+                try:
+                    n_before = req.lane.n_cached
+                    first = self.program.prefill_step(req.lane, self.governor.unit)
+                    self.stats.prompt_tokens += req.lane.n_cached - n_before
+                except RequestError as e:
+                    self._active.remove(req)
+                    self._finish(req, "error", str(e))
+                    break
+                self.stats.prefill_s += time.perf_counter() - t0
+                did_prefill = True
+                if first is not None:
+                    req.state = "decode"
+                    self._commit_token(req, first)
+                break  # one prefill chunk per iteration, then give the decode lanes a round
+        ready = [r for r in self._active if r.state == "decode"]
+        if ready:
+            t0 = time.perf_counter()
+            toks = self.program.decode_round([r.lane for r in ready])
+            dt = time.perf_counter() - t0
+            self.stats.decode_s += dt
+            self.stats.decode_rounds += 1
+            self.governor.observe(dt * 1e3, did_prefill)
+            for r, t in zip(ready, toks):
+                self._commit_token(r, t)
+        self._active = [r for r in self._active if r.state != "finished"]

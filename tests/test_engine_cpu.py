@@ -1,0 +1,111 @@
+"""Engine control plane on the CPU reference program: batching, stop rules, cancellation, failure domains."""
+import os
+import threading
+import time
+
+import pytest
+import torch
+
+from ninfer_fusion_b200.models.config import TINY_DENSE
+from ninfer_fusion_b200.models.reference_model import ReferenceModel
+from ninfer_fusion_b200.models.weights import random_weights
+from ninfer_fusion_b200.runtime.engine import (BandwidthGovernor, Engine, RequestError, RequestOptions, ResourceError)
+from ninfer_fusion_b200.runtime.program import ReferenceProgram, SamplingParams
+
+CFG = TINY_DENSE.shrink(2)
+W = random_weights(CFG, "cpu", seed=11, std=0.05)
+
+
+def make_engine(lanes=3, **kw):
+    return Engine(lambda: ReferenceProgram(CFG, W, max_lanes=lanes, max_context=256), **kw)
+
+
+def test_concurrent_requests_match_isolated_greedy():
+    eng = make_engine(prefill_chunk=8)
+    torch.manual_seed(0)
+    prompts = [torch.randint(0, CFG.vocab, (n,)).tolist() for n in (5, 19, 11, 7)]
+    handles = [eng.submit(p, RequestOptions(max_tokens=6)) for p in prompts]  # 4 requests, 3 lanes
+    outs = [h.wait(timeout=120) for h in handles]
+    ref = ReferenceModel(CFG, W)
+    for p, o in zip(prompts, outs):
+        assert o == ref.generate_greedy(torch.tensor(p), 6)
+    assert all(h.finish_reason == "length" and h.ttft_ms is not None for h in handles)
+    s = eng.stats.as_dict()
+    assert s["requests_done"] == 4 and s["completion_tokens"] == 24 and s["prompt_tokens"] == sum(map(len, prompts))
+    assert eng.health()["free_lanes"] == 3
+    eng.shutdown()
+
+
+def test_stop_token_cancel_and_limits():
+    eng = make_engine()
+    p = list(range(1, 9))
+    ref = ReferenceModel(CFG, W).generate_greedy(torch.tensor(p), 5)
+    h = eng.submit(p, RequestOptions(max_tokens=5, stop_token_ids=(ref[2],)))
+    assert h.wait(timeout=60) == ref[:2] and h.finish_reason == "stop"
+    with pytest.raises(RequestError):
+        eng.submit(p, RequestOptions(max_tokens=10_000))
+    with pytest.raises(RequestError):
+        eng.submit([], RequestOptions())
+    slow = eng.submit(p, RequestOptions(max_tokens=200))
+    time.sleep(0.2)
+    slow.cancel()
+    slow.wait(timeout=60)
+    assert slow.finish_reason == "cancelled" and len(slow.tokens) < 200
+    sampled = eng.submit(p, RequestOptions(max_tokens=4, sampling=SamplingParams(temperature=0.8, top_k=5, seed=3)))
+    again = eng.submit(p, RequestOptions(max_tokens=4, sampling=SamplingParams(temperature=0.8, top_k=5, seed=3)))
+    assert sampled.wait(timeout=60) == again.wait(timeout=60)
+    eng.shutdown()
+
+
+def test_fault_injection_domains(monkeypatch):
+    monkeypatch.setenv("NINFER_FAULT_INJECT", "request_once")
+    eng = make_engine()
+    bad = eng.submit([1, 2, 3], RequestOptions(max_tokens=2))
+    bad.wait(timeout=60)
+    assert bad.finish_reason == "error" and "injected request fault" in bad.error
+    ok = eng.submit([1, 2, 3], RequestOptions(max_tokens=2))   # only that lane failed
+    assert len(ok.wait(timeout=60)) == 2 and eng.health()["status"] == "ok"
+    eng.shutdown()
+    monkeypatch.setenv("NINFER_FAULT_INJECT", "invariant_once")
+    eng = make_engine()
+    h = eng.submit([1, 2, 3], RequestOptions(max_tokens=2))
+    h.wait(timeout=60)
+    assert h.finish_reason == "error" and eng.health()["status"] == "failed"
+    with pytest.raises(ResourceError):
+        eng.submit([1, 2, 3])
+    eng.recover()
+    assert len(eng.submit([1, 2, 3], RequestOptions(max_tokens=2)).wait(timeout=60)) == 2
+    eng.shutdown()
+
+
+def test_pending_queue_limit_and_timeout():
+    eng = make_engine(lanes=1, max_pending=2)
+    a = eng.submit([1, 2, 3, 4], RequestOptions(max_tokens=60))
+    while eng.health()["pending"]:
+        time.sleep(0.01)
+    b = eng.submit([1, 2], RequestOptions(max_tokens=2, pending_timeout_s=0.05))
+    c = eng.submit([1, 2], RequestOptions(max_tokens=2))
+    with pytest.raises(ResourceError):
+        for _ in range(4):
+            eng.submit([5], RequestOptions(max_tokens=1))
+    b.wait(timeout=120)
+    assert b.finish_reason == "error" and b.error == "request_queue_timeout"
+    a.wait(timeout=120)
+    assert len(c.wait(timeout=120)) == 2
+    eng.shutdown()
+
+
+def test_bandwidth_governor_shrinks_and_recovers():
+    g = BandwidthGovernor(2048, min_unit=128, tolerance=1.5, recover_rounds=3)
+    for _ in range(5):
+        g.observe(10.0, False)
+    assert g.unit == 2048
+    g.observe(30.0, True)
+    g.observe(30.0, True)
+    assert g.unit == 512
+    for _ in range(6):
+        g.observe(10.5, True)
+    assert g.unit == 2048
+    for _ in range(20):
+        g.observe(100.0, True)
+    assert g.unit == 128
