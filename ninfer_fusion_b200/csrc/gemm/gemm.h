@@ -50,6 +50,10 @@ struct GemmArgs {
 const char* gemm_bf16(const GemmArgs& args);
 
 // Token-tile width the kernel will use for T tokens (16, 32, 64, 128 or 256).
+// Performance debugging: per-CTA phase timeline (ns, globaltimer): 0 start, 1 set-up done, 2 main loop done,
+// 3 peer tile sent, 4 cluster exchange done, 5 epilogue done, 6 exit.
+void gemm_trace_enable(bool on);
+int gemm_trace_read(unsigned long long* host, int n_ctas);
 int gemm_tile_tokens(int T);
 int gemm_max_cluster(int tile_tokens);
 // Split-K factor that fills `sm_count` SMs for a decode-shaped problem.

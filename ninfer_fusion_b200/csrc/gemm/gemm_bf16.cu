@@ -28,16 +28,32 @@ constexpr int kBlockK = 64;           // bf16 elements per k-block = one 128-byt
 constexpr int kTileN = 128;           // weight rows per CTA (UMMA M)
 constexpr int kWTileBytes = kTileN * 128;
 
-template <int TN>
+// DEEP = one CTA per SM with a pipeline twice as deep: used when the whole grid fits in one wave, so that a
+// grid of ~100 CTAs still keeps ~200 KB per SM in flight (the memory system needs ~30 MB in flight overall).
+template <int TN, bool DEEP = false>
 struct GemmCfg {
-  static constexpr int kStages = TN <= 32 ? 5 : (TN == 64 ? 4 : (TN == 128 ? 6 : 4));
+  static constexpr int kStages =
+      DEEP ? (TN <= 32 ? 10 : 8) : (TN <= 32 ? 5 : (TN == 64 ? 4 : (TN == 128 ? 6 : 4)));
   static constexpr int kXTileBytes = TN * 128;
   static constexpr int kStageBytes = kWTileBytes + kXTileBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // +1024: manual alignment
   static constexpr int kTmemCols = TN < 32 ? 32 : TN;
 };
 
+// Optional phase timeline (globaltimer, ns) of every CTA, for performance debugging: 8 stamps per CTA.
+constexpr int kTraceStamps = 8;
+constexpr int kTraceCtas = 4096;
+__device__ unsigned long long g_gemm_trace[kTraceCtas * kTraceStamps];
+bool g_trace_enabled = false;
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
 struct KernelParams {
+  int trace;
   int T, N, K;
   int kb_per_split;    // k-blocks handled by one blockIdx.z
   int num_kb;          // ceil(K / 64)
@@ -60,11 +76,11 @@ struct KernelParams {
   const unsigned int* call_idx;  // device counter of finished reduce calls; its parity picks the buffer
 };
 
-template <int TN, int EPI>
+template <int TN, int EPI, bool DEEP>
 __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CUtensorMap tmap_w,
                                                        const __grid_constant__ CUtensorMap tmap_x,
                                                        const KernelParams p) {
-  using Cfg = GemmCfg<TN>;
+  using Cfg = GemmCfg<TN, DEEP>;
   constexpr int kStages = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kStages];
@@ -77,6 +93,11 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int cta_linear = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  auto stamp = [&](int i) {
+    if (p.trace && threadIdx.x == 0 && cta_linear < kTraceCtas) g_gemm_trace[cta_linear * kTraceStamps + i] = globaltimer_ns();
+  };
+  stamp(0);
 
   const int t0 = blockIdx.y * TN;
   const int n0 = (EPI == kEpiSwiglu) ? blockIdx.x * 64 : blockIdx.x * kTileN;
@@ -104,6 +125,7 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
+  stamp(1);
 
   // Let the next kernel in the stream begin its own prologue / weight prefetch.
   pdl_launch_next();
@@ -185,6 +207,7 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
   tc_fence_after();
   // One CTA-wide verdict, so the barriers inside the epilogue are never divergent.
   int epilogue_ok = __syncthreads_and(have_acc && !abort_flag);
+  stamp(2);
   const uint32_t lane_taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
   constexpr int kChunk = 16;
 
@@ -210,8 +233,10 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
       }
       if (threadIdx.x == 0) st_shared_cluster_u32(mapa_shared(smem_u32(&peer_ok[crank]), 0), epilogue_ok ? 1u : 0u);
     }
+    stamp(3);
     // #2: peers' tiles (release) are visible to the leader (acquire)
     cluster_sync_all();
+    stamp(4);
     if (crank != 0) {
       epilogue_ok = 0;  // only the leader writes the output
     } else {
@@ -313,6 +338,19 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
             }
           }
         } else {
+          // The residual may alias the output (in-place update): fetch the whole chunk's residual values
+          // before the first store, otherwise every load would have to wait for the previous store.
+          __nv_bfloat162 r2[kChunk / 2];
+          if constexpr (EPI == kEpiResidual) {
+#pragma unroll
+            for (int m = 0; m < kChunk / 2; ++m) {
+              const int t = t0 + c + 2 * m + (lane & 1);
+              const int ne = n & ~1;
+              r2[m] = (t < p.T && ne < p.N)
+                          ? *reinterpret_cast<const __nv_bfloat162*>(p.resid + static_cast<long long>(t) * p.ldr + ne)
+                          : __nv_bfloat162();
+            }
+          }
 #pragma unroll
           for (int m = 0; m < kChunk / 2; ++m) {
             const float a0 = v[2 * m] + bias;
@@ -325,10 +363,8 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
               float lo = (lane & 1) ? recv : a0;
               float hi = (lane & 1) ? a1 : recv;
               if constexpr (EPI == kEpiResidual) {
-                const __nv_bfloat162 r2 = *reinterpret_cast<const __nv_bfloat162*>(
-                    p.resid + static_cast<long long>(t) * p.ldr + ne);
-                lo += __bfloat162float(r2.x);
-                hi += __bfloat162float(r2.y);
+                lo += __bfloat162float(r2[m].x);
+                hi += __bfloat162float(r2[m].y);
               }
               *reinterpret_cast<uint32_t*>(p.out + static_cast<long long>(t) * p.ldo + ne) =
                   pack_bf16x2(lo, hi);
@@ -356,16 +392,18 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
     }
   }
 
+  stamp(5);
   tc_fence_before();
   __syncthreads();
   if (warp == 2) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  stamp(6);
 }
 
-template <int TN, int EPI>
+template <int TN, int EPI, bool DEEP>
 cudaError_t launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const KernelParams& kp, dim3 grid,
                        cudaStream_t stream, bool pdl) {
-  using Cfg = GemmCfg<TN>;
-  auto kern = gemm_ws_kernel<TN, EPI>;
+  using Cfg = GemmCfg<TN, DEEP>;
+  auto kern = gemm_ws_kernel<TN, EPI, DEEP>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
@@ -396,15 +434,29 @@ cudaError_t launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const Kerne
   return cudaLaunchKernelEx(&cfg, kern, tw, tx, kp);
 }
 
+int device_sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+
 template <int EPI>
 cudaError_t launch_tn(int TN, const CUtensorMap& tw, const CUtensorMap& tx, const KernelParams& kp,
                       dim3 grid, cudaStream_t stream, bool pdl) {
+  const bool deep = TN <= 64 && static_cast<long long>(grid.x) * grid.y * grid.z <= device_sm_count();
   switch (TN) {
-    case 16: return launch_one<16, EPI>(tw, tx, kp, grid, stream, pdl);
-    case 32: return launch_one<32, EPI>(tw, tx, kp, grid, stream, pdl);
-    case 64: return launch_one<64, EPI>(tw, tx, kp, grid, stream, pdl);
-    case 128: return launch_one<128, EPI>(tw, tx, kp, grid, stream, pdl);
-    default: return launch_one<256, EPI>(tw, tx, kp, grid, stream, pdl);
+    case 16: return deep ? launch_one<16, EPI, true>(tw, tx, kp, grid, stream, pdl)
+                         : launch_one<16, EPI, false>(tw, tx, kp, grid, stream, pdl);
+    case 32: return deep ? launch_one<32, EPI, true>(tw, tx, kp, grid, stream, pdl)
+                         : launch_one<32, EPI, false>(tw, tx, kp, grid, stream, pdl);
+    case 64: return deep ? launch_one<64, EPI, true>(tw, tx, kp, grid, stream, pdl)
+                         : launch_one<64, EPI, false>(tw, tx, kp, grid, stream, pdl);
+    case 128: return launch_one<128, EPI, false>(tw, tx, kp, grid, stream, pdl);
+    default: return launch_one<256, EPI, false>(tw, tx, kp, grid, stream, pdl);
   }
 }
 
@@ -441,6 +493,13 @@ bool cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t col
 
 }  // namespace
 
+void gemm_trace_enable(bool on) { g_trace_enabled = on; }
+int gemm_trace_read(unsigned long long* host, int n_ctas) {
+  if (n_ctas > kTraceCtas) n_ctas = kTraceCtas;
+  cudaMemcpyFromSymbol(host, g_gemm_trace, sizeof(unsigned long long) * n_ctas * kTraceStamps);
+  return kTraceStamps;
+}
+
 int gemm_tile_tokens(int T) {
   if (T <= 16) return 16;
   if (T <= 32) return 32;
@@ -467,20 +526,25 @@ int gemm_pick_splits(int T, int N, int K, int epi, int sm_count) {
   const int tile_rows = epi == kEpiSwiglu ? 64 : kTileN;
   const int tiles = ((rows + tile_rows - 1) / tile_rows) * ((T + tn - 1) / tn);
   const int num_kb = (K + kBlockK - 1) / kBlockK;
-  const int slots = sm_count * (tn <= 64 ? 2 : 1);
   const bool in_cluster = epi != kEpiPartial && epi != kEpiPushPartial;
-  const int cap = in_cluster ? gemm_max_cluster(tn) : 8;
-  if (tiles >= slots || T > 256) return 1;
-  int s = slots / tiles;
-  if (s > cap) s = cap;
-  while (s > 1 && num_kb / s < 8) --s;  // keep at least 8 k-blocks per split
-  if (s < 1) s = 1;
-  if (in_cluster) {
-    while (s > 1 && (num_kb + s - 1) / s * (s - 1) >= num_kb) --s;  // no empty trailing split
-    return s;
+  if (T > 256) return 1;
+  if (!in_cluster) {
+    const int slots = sm_count * (tn <= 64 ? 2 : 1);
+    if (tiles >= slots) return 1;
+    int s = slots / tiles;
+    if (s > 8) s = 8;
+    while (s > 1 && num_kb / s < 8) --s;
+    const int per = (num_kb + s - 1) / s;
+    return (num_kb + per - 1) / per;
   }
-  const int per = (num_kb + s - 1) / s;
-  return (num_kb + per - 1) / per;  // no empty trailing split
+  // in-cluster split: aim for ONE wave of deep-pipeline CTAs (<= sm_count CTAs, one per SM)
+  if (tiles >= sm_count || tn > 64) return 1;
+  int s = sm_count / tiles;
+  if (s > 8) s = 8;
+  if (tn == 64 && s > 6) s = 6;
+  while (s > 1 && num_kb / s < 8) --s;
+  while (s > 1 && (num_kb + s - 1) / s * (s - 1) >= num_kb) --s;  // no empty trailing split
+  return s < 1 ? 1 : s;
 }
 
 const char* gemm_bf16(const GemmArgs& a) {
@@ -492,6 +556,7 @@ const char* gemm_bf16(const GemmArgs& a) {
   const int tn = gemm_tile_tokens(static_cast<int>(a.T));
   const bool global_split = a.epi == kEpiPartial || a.epi == kEpiPushPartial;
   KernelParams kp = {};
+  kp.trace = g_trace_enabled ? 1 : 0;
   kp.T = static_cast<int>(a.T); kp.N = static_cast<int>(a.N); kp.K = static_cast<int>(a.K);
   kp.num_kb = (kp.K + kBlockK - 1) / kBlockK;
   int splits = a.splits < 1 ? 1 : a.splits;
@@ -501,7 +566,10 @@ const char* gemm_bf16(const GemmArgs& a) {
     return "gemm_bf16: split count leaves an empty split";
   kp.cluster = 1;
   if (!global_split && splits > 1) {
-    if (splits > gemm_max_cluster(tn)) return "gemm_bf16: in-cluster split exceeds the tile's limit";
+    const long long ctas = static_cast<long long>((kp.N + kTileN - 1) / kTileN) * ((kp.T + tn - 1) / tn) * splits;
+    const bool deep = tn <= 64 && ctas <= device_sm_count();  // (SwiGLU has more tiles: checked against the shallow limit)
+    const int cap = (deep && a.epi != kEpiSwiglu) ? (tn == 64 ? 6 : 8) : gemm_max_cluster(tn);
+    if (splits > cap) return "gemm_bf16: in-cluster split exceeds the tile's limit";
     kp.cluster = splits;
   }
   if (a.epi == kEpiPushPartial || a.epi == kEpiPushAll) {

@@ -82,6 +82,13 @@ void gemm_bf16(const Tensor& x, const Tensor& w, OptT out, int64_t epi, OptT res
   chk(nfb::gemm_bf16(a));
 }
 
+Tensor gemm_trace(bool enable, int64_t n_ctas) {
+  nfb::gemm_trace_enable(enable);
+  Tensor out = at::zeros({n_ctas, 8}, at::TensorOptions().dtype(at::kLong));
+  if (n_ctas > 0) nfb::gemm_trace_read(reinterpret_cast<unsigned long long*>(out.data_ptr()), static_cast<int>(n_ctas));
+  return out;
+}
+
 int64_t gemm_pick_splits(int64_t T, int64_t N, int64_t K, int64_t epi) {
   return nfb::gemm_pick_splits(static_cast<int>(T), static_cast<int>(N), static_cast<int>(K), static_cast<int>(epi),
                                static_cast<int>(sm_count()));
@@ -555,6 +562,7 @@ TORCH_LIBRARY(nfb200, m) {
   m.def("gemm_bf16_push_all(Tensor x, Tensor w, int splits, int world, int rank, int[] peer_bases, int recv_off, int flag_off, int T_cap, Tensor state, Tensor? status, bool pdl) -> ()", &gemm_bf16_push_all);
   m.def("tp_sum_norm(int world, int T_cap, int arrivals, int my_base, int recv_off, int flag_off, Tensor x, Tensor? norm_w, Tensor? normed, float eps, bool unit_offset, Tensor state, Tensor? status, bool pdl) -> ()", &tp_sum_norm);
   m.def("gemm_bf16(Tensor x, Tensor w, Tensor? out, int epi, Tensor? resid, Tensor? bias, Tensor? partial, int splits, Tensor? status, bool pdl) -> ()", &gemm_bf16);
+  m.def("gemm_trace(bool enable, int n_ctas) -> Tensor", &gemm_trace);
   m.def("gemm_pick_splits(int T, int N, int K, int epi) -> int", &gemm_pick_splits);
   m.def("add_rmsnorm(Tensor? partial, int splits, Tensor? delta, Tensor? resid_in, Tensor? resid_out, Tensor? norm_w, Tensor? normed, int T, int N, float eps, bool unit_offset, bool pdl) -> ()", &add_rmsnorm);
   m.def("embed_gather(Tensor ids, Tensor table, Tensor out, bool pdl) -> ()", &embed_gather);

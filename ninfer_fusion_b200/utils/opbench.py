@@ -81,8 +81,10 @@ def bench_gemm(ops, T, N, K, epi, splits=0, iters=20, pdl=False):
             ops.gemm_bf16(x, w, None, e, None, None, part, splits, status, pdl)
             ops.add_rmsnorm(part, splits, None, xres, xres, nw, normed, T, N, 1e-6, True, pdl)
     else:
+        cl = splits if splits else int(ops.gemm_pick_splits(T, N, K, e))
+
         def fn():
-            ops.gemm_bf16(x, w, out if e != 1 else resid, e, resid, None, None, 1, status, pdl)
+            ops.gemm_bf16(x, w, out if e != 1 else resid, e, resid, None, None, cl, status, pdl)
     med, best = time_op(fn, iters=iters, flush=L2Flusher())
     assert int(status.item()) == 0, "kernel reported a bounded-wait failure"
     byts = N * K * 2 + T * K * 2 + T * out_cols * 2
