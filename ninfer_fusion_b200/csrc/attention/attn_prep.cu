@@ -118,6 +118,10 @@ const char* attn_prep(const AttnPrepParams& p, cudaStream_t stream, bool pdl) {
   if (p.T <= 0) return nullptr;
   if (p.head_dim != 256 && p.head_dim != 128) return "attn_prep: head_dim must be 128 or 256";
   const int vpl = p.head_dim / 32;
+  // each lane loads its vpl values with one vector load: rows and column offsets must keep that alignment
+  if (p.ld_proj % vpl || p.q_off % vpl || p.k_off % vpl || p.v_off % vpl ||
+      (reinterpret_cast<uintptr_t>(p.proj) % (2 * vpl)))
+    return "attn_prep: projection rows must be aligned to head_dim/32 elements";
   if (p.rot_dim % (2 * vpl)) return "attn_prep: rot_dim/2 must be a multiple of head_dim/32";
   if (p.kv.format == kKvInt8Group && (p.kv.group % vpl || p.head_dim % p.kv.group)) return "attn_prep: bad int8 group";
   const int rows = p.T * (p.n_q_heads + 2 * p.n_kv_heads);

@@ -288,6 +288,8 @@ const char* paged_attention(const PagedAttnParams& p, cudaStream_t stream, bool 
   if (p.n_q_heads % p.n_kv_heads) return "paged_attention: q heads must be a multiple of kv heads";
   if (p.split_keys <= 0 || p.split_keys % 128) return "paged_attention: split_keys must be a positive multiple of 128";
   if (p.n_splits < 1) return "paged_attention: need at least one split";
+  if (p.gate != nullptr && (p.ld_gate % 4 || reinterpret_cast<uintptr_t>(p.gate) % 8))
+    return "paged_attention: gate rows must be 8-byte aligned";
   const int G = p.n_q_heads / p.n_kv_heads;
   const dim3 grid(p.Tq, p.n_kv_heads, p.n_splits);
   cudaError_t e = cudaErrorNotSupported;

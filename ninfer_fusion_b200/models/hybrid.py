@@ -60,7 +60,8 @@ class Workspace:
         if self.x.shape[0] < T or self.x.shape[1] != h:
             raise ValueError("residual buffer is too small for the workspace")
         self.normed = torch.empty((T, h), dtype=bf, device=dev)
-        wide = max(g.attn_in_dim, g.gdn_in_dim)
+        # rows are read with 16-byte vector loads: keep the leading dimension a multiple of 64 elements
+        wide = (max(g.attn_in_dim, g.gdn_in_dim) + 63) // 64 * 64
         self.proj = torch.empty((T, wide), dtype=bf, device=dev)
         self.q = torch.empty((T, g.n_q_heads * cfg.head_dim), dtype=bf, device=dev)
         self.mix_attn = torch.empty((T, g.n_q_heads * cfg.head_dim), dtype=bf, device=dev)
