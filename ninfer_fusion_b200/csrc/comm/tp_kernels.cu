@@ -25,31 +25,11 @@
 #include <math_constants.h>
 
 #include "../common/ptx.cuh"
+#include "peer_sync.cuh"
 
 namespace nfb {
 
 namespace {
-
-constexpr uint32_t kPeerPollLimit = 1u << 22;
-
-__device__ __forceinline__ uint32_t ld_acquire_sys(const unsigned int* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void red_release_sys_add(unsigned int* p, uint32_t v) {
-  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-// Wait until *flag - target >= 0 in wrap-around arithmetic.  Returns false on time-out.
-__device__ __forceinline__ bool wait_counter(const unsigned int* flag, uint32_t target, int* status) {
-  for (uint32_t i = 0; i < kPeerPollLimit; ++i) {
-    if (static_cast<int32_t>(ld_acquire_sys(flag) - target) >= 0) return true;
-    __nanosleep(i < 64 ? 20 : 200);
-  }
-  report_status(status, kStatusPeerWaitTimeout);
-  return false;
-}
 
 constexpr int kThreads = 256;
 

@@ -171,7 +171,8 @@ class LaunchCounter:
 
 class HybridModel:
     def __init__(self, cfg: ModelConfig, weights: Dict[str, torch.Tensor], device, pdl: bool = False,
-                 shard: Optional[ShardGeometry] = None, prefix: str = "text"):
+                 shard: Optional[ShardGeometry] = None, prefix: str = "text", ep_rank: int = 0, ep_world: int = 1,
+                 ep_group=None):
         self.cfg = cfg
         self.w = weights
         self.device = torch.device(device)
@@ -185,6 +186,9 @@ class HybridModel:
         self.cluster_splitk = True  # False: split-K through an fp32 workspace + reduce kernel
         self.attn_impl = 0  # 0 = pick, 1 = SIMT, 2 = tensor-core split-KV attention
         self.comm = None  # tensor-parallel communicator (parallel.tp), None on one GPU
+        self.moe = None   # models.moe.MoeBlock, created with the first workspace that runs a MoE layer
+        self.ep = (ep_rank, ep_world, ep_group)  # expert parallelism: experts split, the rest data-parallel
+        self.moe_global_tokens: Optional[int] = None  # bound on the tokens of all ranks in a step (default world * T)
         # layer index -> index among attention / GDN layers
         self._attn_idx = {l: i for i, l in enumerate(cfg.attn_layers)}
         self._gdn_idx = {l: i for i, l in enumerate(cfg.gdn_layers)}
@@ -302,7 +306,10 @@ class HybridModel:
             if cfg.moe is None:
                 self._mlp(ws, T, p, nxt, ws.normed[:T])
             else:
-                self.moe.forward(self, ws, T, p, nxt, ws.normed[:T])
+                if self.moe is None or self.moe.max_tokens < ws.max_tokens:
+                    from .moe import MoeBlock
+                    self.moe = MoeBlock(cfg, self.device, ws.max_tokens, *self.ep)
+                self.moe.forward(self, ws, T, p, nxt, ws.normed[:T], self.moe_global_tokens)
         return ws.normed[:T]
 
     def logits(self, ws: Workspace, b: StepBatch, hidden: torch.Tensor) -> torch.Tensor:

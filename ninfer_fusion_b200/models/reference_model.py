@@ -92,7 +92,7 @@ class ReferenceModel:
             act = R.bf16_round(torch.nn.functional.silu(gu[:, :i]) * gu[:, i:])
             return _lin(act, self.w[f"{p}/mlp/down"])
         m = cfg.moe
-        router = _lin(normed, self.w[f"{p}/moe/router"])
+        router = R.bf16_round(_lin(normed, self.w[f"{p}/moe/router"]))  # logits are a bf16 op boundary
         wts, ids = R.moe_route(router[:, : m.n_experts], m.top_k, m.norm_topk)
         out = torch.zeros(normed.shape[0], cfg.hidden)
         gu_all, dn_all = self.w[f"{p}/moe/experts_gate_up"], self.w[f"{p}/moe/experts_down"]
