@@ -109,6 +109,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="debug only: shrink the layer count (result is marked invalid)")
     ap.add_argument("--no-ttft", action="store_true")
     ap.add_argument("--pdl", type=int, default=1)
+    ap.add_argument("--parallel", default="", choices=["", "tp", "ep"],
+                    help="multi-GPU plan: tp = tensor parallel (dense default), ep = data parallel + expert parallel (MoE default)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -137,9 +139,18 @@ def main() -> int:
     if args.layers:
         cfg = cfg.shrink(args.layers)
     comm = shard = None
+    parallel = args.parallel or ("ep" if cfg.moe is not None else "tp")
+    ep = world > 1 and parallel == "ep"
+    if ep and (cfg.moe is None or args.batch % world):
+        print("bench.py: --parallel ep needs a MoE model and a batch divisible by the GPU count", file=sys.stderr)
+        return 2
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
+    if ep:
+        # attention / GDN / router / shared expert replicated (same seed), routed experts: this rank's range only
+        weights = random_weights(cfg, device, seed=0, expert_rank=rank, expert_world=world)
+    elif world > 1:
         from ninfer_fusion_b200.parallel.tp import TensorParallel
 
         comm = TensorParallel(cfg, rank, world, device, max_tokens=max(args.batch, 2048))
@@ -149,11 +160,14 @@ def main() -> int:
         weights = random_weights(cfg, device, seed=0)
 
     B, L, K, W = args.batch, args.prompt_len, args.steps, args.warmup
+    B_local = B // world if ep else B  # expert parallel: every rank decodes its own share of the sequences
     max_ctx = L + 2 * (K + W) + 64
-    gen = Generator(cfg, weights, device, max_batch=B, max_context=max_ctx, kv_format=args.kv_format, page_size=64,
-                    prefill_chunk=2048, use_graph=True, pdl=bool(args.pdl), shard=shard, comm=comm)
-    g = torch.Generator().manual_seed(1234)
-    prompts = [torch.randint(0, cfg.vocab, (L,), generator=g).tolist() for _ in range(B)]
+    gen = Generator(cfg, weights, device, max_batch=B_local, max_context=max_ctx, kv_format=args.kv_format,
+                    page_size=64, prefill_chunk=2048, use_graph=True, pdl=bool(args.pdl), shard=shard, comm=comm)
+    if ep:
+        gen.model.ep = (rank, world, None)
+    g = torch.Generator().manual_seed(1234 + (rank if ep else 0))
+    prompts = [torch.randint(0, cfg.vocab, (L,), generator=g).tolist() for _ in range(B_local)]
 
     def barrier():
         if world > 1:
@@ -218,23 +232,25 @@ def main() -> int:
         value = B * K / (dev_ms / 1e3)
         e2e_value = B * K / (e2e_ms / 1e3)
         launches = gen.model.ops.launches_last_forward * K
+        # single-request decode tok/s of the reference on one RTX 5090 (docs/performance.md:537 and :318)
+        baseline_tok_s = 271.1 if cfg.moe is not None else BASELINE_DECODE_TOK_S
         out = {
             "metric": "decode tokens/sec/box + p50 TTFT at 1/2/4/8 B200, 27B hybrid fp8-KV",
             "value": round(value, 2), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": round(value / BASELINE_DECODE_TOK_S, 3), "dtype": "bf16",
+            "vs_baseline": round(value / baseline_tok_s, 3), "dtype": "bf16",
             "data": "synthetic uniform-random token prompts, random-init weights",
             "config": {"model": cfg.name + ("" if not args.layers else " (SHRUNK: INVALID)"), "global_batch": B,
-                       "seq_len": L, "parallelism": f"tp{world}", "kv": args.kv_format + "-e4m3-row" if args.kv_format == "fp8" else args.kv_format,
+                       "seq_len": L, "parallelism": f"{parallel}{world}" if world > 1 else "single", "kv": args.kv_format + "-e4m3-row" if args.kv_format == "fp8" else args.kv_format,
                        "weights": "bf16", "decode": "greedy, CUDA graph per round",
-                       "l2": "inputs larger than L2 (weights 54 GB streamed every round), no flush",
-                       "baseline_note": "vs_baseline divides by the reference's single-request decode tok/s (86.4, 27B nvfp4, RTX 5090)"},
+                       "l2": "inputs larger than L2 (all weights streamed every round), no flush",
+                       "baseline_note": f"vs_baseline divides by the reference's single-request decode tok/s ({baseline_tok_s}, one RTX 5090)"},
             "ttft_ms_p50": round(ttft_max, 2) if ttft_ms is not None else None,
             "ttft_config": {"prompt_tokens": L, "batch": 1, "prefill_chunk": 2048},
             "batch_prefill_s": round(prefill_s, 3),
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s", "ms_per_step": round(e2e_ms / K, 4),
-                    "h2d_bytes_per_step": gen.bufs_decode.h2d_bytes(), "d2h_bytes_per_step": 4 * B},
+                    "h2d_bytes_per_step": gen.bufs_decode.h2d_bytes(), "d2h_bytes_per_step": 4 * B_local},
             "gpu_launches": launches,
         }
         print(json.dumps(out), flush=True)

@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(128) conv1d_state_kernel(const ConvParams p) {
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 2;
   const int seq = blockIdx.x;
   if (c >= p.C) return;
-  const int start = p.cu_seqlens[seq], end = p.cu_seqlens[seq + 1];
+  const int start = p.cu_seqlens[seq], end = p.seq_end != nullptr ? p.seq_end[seq] : p.cu_seqlens[seq + 1];
   if (end <= start) return;
   const int slot = p.state_slot[seq];
   float2 v[3];
@@ -116,7 +116,8 @@ const char* causal_conv1d_silu(const ConvParams& p, cudaStream_t stream, bool pd
     cudaError_t e1 = cudaLaunchKernelEx(&cfg, conv1d_silu_decode_kernel, p);
     return e1 == cudaSuccess ? nullptr : cudaGetErrorString(e1);
   }
-  cudaError_t e = cudaLaunchKernelEx(&cfg, conv1d_silu_kernel, p);
+  cudaError_t e = cudaSuccess;
+  if (!p.state_only) e = cudaLaunchKernelEx(&cfg, conv1d_silu_kernel, p);
   if (e != cudaSuccess) return cudaGetErrorString(e);
   if (p.update_state) {
     cfg.gridDim = dim3(p.n_seq, (p.C / 2 + 127) / 128);

@@ -21,6 +21,8 @@ struct ConvParams {
   __nv_bfloat16* out;       // [T, C]
   int update_state;
   int one_token_per_seq;     // decode: token i belongs to sequence i; conv + history roll in one launch
+  const int* seq_end = nullptr;  // optional [n_seq]: sequence s covers [cu_seqlens[s], seq_end[s]) (accepted prefix of a verify)
+  int state_only = 0;        // only roll the history forward (replay of an accepted prefix), no output
 };
 const char* causal_conv1d_silu(const ConvParams& p, cudaStream_t stream, bool pdl);
 
@@ -46,6 +48,7 @@ struct GdnParams {
   float* state;              // [slots, Hv, 128, 128]
   int write_state;           // 0: verify pass, state untouched
   __nv_bfloat16* out;        // [T, Hv * 128]
+  const int* seq_end = nullptr;  // optional [n_seq]: sequence s covers [cu_seqlens[s], seq_end[s])
 };
 const char* gdn_recurrent(const GdnParams& p, cudaStream_t stream, bool pdl);
 // Multi-token variant (token groups staged in shared memory); gdn_recurrent dispatches to it when T > n_seq.

@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(kThreads, 1) gdn_prefill_kernel(const GdnParam
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane >> 3, q8 = lane & 7;
   const int hk = hv / (p.n_v_heads / p.n_qk_heads);
-  const int t_begin = p.cu_seqlens[seq], t_end = p.cu_seqlens[seq + 1];
+  const int t_begin = p.cu_seqlens[seq], t_end = p.seq_end != nullptr ? p.seq_end[seq] : p.cu_seqlens[seq + 1];
   if (t_end <= t_begin) return;
   const int slot = p.state_slot[seq];
   const int n_groups = (t_end - t_begin + kTG - 1) / kTG;

@@ -79,6 +79,14 @@ class Workspace:
         self.logits = torch.empty((max_logit_rows, g.vocab_rows), dtype=bf, device=dev)
         self.head_in = torch.empty((max_logit_rows, h), dtype=bf, device=dev)
         self.next_ids = torch.empty((max_logit_rows,), dtype=torch.int32, device=dev)
+        self._mtp = None
+        self._dev = dev
+
+    def mtp_scratch(self):
+        """[3, max_tokens, hidden] bf16 scratch of the draft module (embedding, two normalised inputs), made on first use."""
+        if self._mtp is None:
+            self._mtp = torch.empty((3, self.max_tokens, self.x.shape[1]), dtype=torch.bfloat16, device=self._dev)
+        return self._mtp
 
 
 @dataclass
@@ -167,6 +175,20 @@ class LaunchCounter:
                     return _raw(*a)
             self._cache[name] = fn
         return fn
+
+
+class GdnRecords:
+    """Per-layer projection and convolution outputs of a verify pass, kept so that the accepted prefix can be
+    replayed into the recurrent state and the conv history without recomputing the projections
+    (the reference's replay records: include/ninfer/ops/gdn_replay.h:13-49, src/core/gdn_replay_records.h)."""
+
+    def __init__(self, cfg: ModelConfig, max_tokens: int, device, shard: Optional[ShardGeometry] = None):
+        g = shard or ShardGeometry.full(cfg)
+        wide = (g.gdn_in_dim + 63) // 64 * 64
+        n = len(cfg.gdn_layers)
+        self.max_tokens = max_tokens
+        self.proj = torch.empty((n, max_tokens, wide), dtype=torch.bfloat16, device=device)
+        self.conv = torch.empty((n, max_tokens, g.gdn_conv_dim), dtype=torch.bfloat16, device=device)
 
 
 class HybridModel:
@@ -258,14 +280,15 @@ class HybridModel:
         return out, self.w[f"{prefix}/attn/o_proj"]
 
     def _gdn_layer(self, ws: Workspace, b: StepBatch, st: GdnStatePool, layer: int, T: int, prefix: str,
-                   write_state: bool = True):
+                   write_state: bool = True, rec: Optional[GdnRecords] = None):
         cfg, g, ops = self.cfg, self.g, self.ops
         gi = self._gdn_idx[layer]
         w_in = self.w[f"{prefix}/gdn/in_proj"]
-        proj = ws.proj[:T, : w_in.shape[0]]
+        # a verify pass writes its projections into the layer's record instead of the shared scratch
+        proj = (ws.proj if rec is None else rec.proj[gi])[:T, : w_in.shape[0]]
         self._gemm(ws.normed[:T], w_in, proj)
         C = g.gdn_conv_dim
-        conv = ws.conv[:T]
+        conv = (ws.conv if rec is None else rec.conv[gi])[:T]
         ops.causal_conv1d_silu(proj, 0, C, self.w[f"{prefix}/gdn/conv_w"], b.cu_seqlens, b.token_seq, b.state_slot,
                                st.conv[gi], conv, write_state, b.n_tokens == b.n_seqs and b.one_token_per_seq, self.pdl)
         qk = g.gdn_qk_dim
@@ -283,8 +306,58 @@ class HybridModel:
         self._gemm_to_residual(ws, act, self.w[f"{prefix}/mlp/down"], T, next_norm_w, normed_out)
 
     # ------------------------------------------------------------------ forward
+    def fold_gdn(self, ws: Workspace, b: StepBatch, st: GdnStatePool, rec: GdnRecords, seq_end: torch.Tensor) -> None:
+        """Replays tokens [cu_seqlens[s], seq_end[s]) of the recorded verify pass `b` into the conv history and the
+        recurrent state of every GDN layer (the accepted prefix of a speculative round)."""
+        cfg, g, ops = self.cfg, self.g, self.ops
+        T = b.n_tokens
+        C, qk = g.gdn_conv_dim, g.gdn_qk_dim
+        for layer in cfg.gdn_layers:
+            gi = self._gdn_idx[layer]
+            p = f"{self.prefix}/layers/{layer}"
+            proj = rec.proj[gi][:T, : g.gdn_in_dim]
+            conv = rec.conv[gi][:T]
+            ops.causal_conv1d_silu(proj, 0, C, self.w[f"{p}/gdn/conv_w"], b.cu_seqlens, b.token_seq, b.state_slot,
+                                   st.conv[gi], ws.conv[:T], True, False, self.pdl, seq_end, True)
+            ops.gdn_recurrent(conv, 0, qk, 2 * qk, proj, C, C + g.gdn_v_dim, C + g.gdn_v_dim + g.gdn_v_heads,
+                              g.gdn_qk_heads, g.gdn_v_heads, self.w[f"{p}/gdn/A_log"], self.w[f"{p}/gdn/dt_bias"],
+                              self.w[f"{p}/gdn/norm"], cfg.rms_eps, b.cu_seqlens, b.state_slot, st.ssm[gi], True,
+                              ws.mix_gdn[:T], self.pdl, seq_end)
+
+    def forward_mtp(self, ws: Workspace, b: StepBatch, kv_mtp: PagedKvCache, hidden_in: torch.Tensor,
+                    next_ids: torch.Tensor) -> torch.Tensor:
+        """Draft module (one full-attention decoder layer sharing the embedding and the LM head): position p
+        consumes the final-normed hidden state of position p and the embedding of token p + 1 and predicts
+        token p + 2.  `hidden_in` [T, hidden] must not alias ws.normed.  Returns the module's final-normed
+        hidden states (ws.normed[:T]), which feed the shared head and the next draft step.
+        Reference: src/targets/qwen3_6/impl/runtime/mtp_impl.h, text_context_impl.h:732-1090,
+        docs/maintainer/qwen3.6-35b-a3b-model.md:416-470."""
+        cfg, ops, w = self.cfg, self.ops, self.w
+        T, h = b.n_tokens, cfg.hidden
+        scratch = ws.mtp_scratch()
+        e, a_n, e_n = scratch[0, :T], scratch[1, :T], scratch[2, :T]
+        ops.embed_gather(next_ids, w[f"{self.prefix}/embed"], e, self.pdl)
+        ops.add_rmsnorm(None, 0, None, hidden_in, None, w["mtp/pre_fc_norm_hidden"], a_n, T, h, cfg.rms_eps, True, self.pdl)
+        ops.add_rmsnorm(None, 0, None, e, None, w["mtp/pre_fc_norm_embedding"], e_n, T, h, cfg.rms_eps, True, self.pdl)
+        fc = w["mtp/fc"]  # [hidden, 2 * hidden]: columns [hidden state ; embedding]
+        x = ws.x[:T]
+        self._gemm(a_n, fc[:, :h], x)
+        self._gemm(e_n, fc[:, h:], x, EPI_RESIDUAL, x)
+        p = "mtp/layers/0"
+        ops.add_rmsnorm(None, 0, None, x, None, w[f"{p}/input_norm"], ws.normed[:T], T, h, cfg.rms_eps, True, self.pdl)
+        mix, w_out = self._attn_layer(ws, b, kv_mtp, 0, T, p, 0)
+        self._gemm_to_residual(ws, mix, w_out, T, w[f"{p}/post_norm"], ws.normed[:T])
+        if cfg.moe is None:
+            self._mlp(ws, T, p, w["mtp/final_norm"], ws.normed[:T])
+        else:
+            if self.moe is None or self.moe.max_tokens < ws.max_tokens:
+                from .moe import MoeBlock
+                self.moe = MoeBlock(cfg, self.device, ws.max_tokens, *self.ep)
+            self.moe.forward(self, ws, T, p, w["mtp/final_norm"], ws.normed[:T], self.moe_global_tokens)
+        return ws.normed[:T]
+
     def forward_hidden(self, ws: Workspace, b: StepBatch, kv: PagedKvCache, st: GdnStatePool,
-                       write_state: bool = True) -> torch.Tensor:
+                       write_state: bool = True, rec: Optional[GdnRecords] = None) -> torch.Tensor:
         """Runs all layers; returns the final-normed hidden states [T, hidden] (ws.normed)."""
         cfg, ops = self.cfg, self.ops
         T = b.n_tokens
@@ -299,7 +372,7 @@ class HybridModel:
             if cfg.is_full_attn(layer):
                 mix, w_out = self._attn_layer(ws, b, kv, layer, T, p, self._attn_idx[layer])
             else:
-                mix, w_out = self._gdn_layer(ws, b, st, layer, T, p, write_state)
+                mix, w_out = self._gdn_layer(ws, b, st, layer, T, p, write_state, rec)
             self._gemm_to_residual(ws, mix, w_out, T, self.w[f"{p}/post_norm"], ws.normed[:T])
             nxt = (self.w[f"{self.prefix}/layers/{layer + 1}/input_norm"] if layer + 1 < cfg.n_layers
                    else self.w[f"{self.prefix}/final_norm"])

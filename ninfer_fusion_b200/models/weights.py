@@ -58,12 +58,23 @@ def weight_shapes(cfg: ModelConfig, with_mtp: bool = False) -> Iterator[Tuple[st
 
 
 def random_weights(cfg: ModelConfig, device, seed: int = 0, with_mtp: bool = False,
-                   std: float = 0.02) -> Dict[str, torch.Tensor]:
-    """Random-init weights of the architecture (there are no checkpoints on the box)."""
+                   std: float = 0.02, expert_rank: int = 0, expert_world: int = 1) -> Dict[str, torch.Tensor]:
+    """Random-init weights of the architecture (there are no checkpoints on the box).
+
+    With `expert_world` > 1 the routed expert banks hold only this rank's contiguous range of experts
+    (drawn from a rank-specific stream); every other tensor is identical on all ranks.
+    """
     gen = torch.Generator(device=device)
     gen.manual_seed(seed)
+    gen_experts = torch.Generator(device=device)
+    gen_experts.manual_seed(seed * 1000 + 31 + expert_rank)
     out: Dict[str, torch.Tensor] = {}
     for name, shape, dt in weight_shapes(cfg, with_mtp):
+        if expert_world > 1 and name.rsplit("/", 1)[-1] in ("experts_gate_up", "experts_down"):
+            t = torch.empty((shape[0] // expert_world,) + tuple(shape[1:]), dtype=dt, device=device)
+            t.normal_(0.0, std, generator=gen_experts)
+            out[name] = t
+            continue
         t = torch.empty(shape, dtype=dt, device=device)
         leaf = name.rsplit("/", 1)[-1]
         if leaf.endswith("norm") or leaf in ("q_norm", "k_norm", "pre_fc_norm_hidden", "pre_fc_norm_embedding"):

@@ -24,18 +24,21 @@ class SeqChunk:
     start_pos: int       # cache position of the first token
     tokens: Sequence[int]
     want_logits: bool = True   # logits for the chunk's last token
+    all_logits: bool = False   # logits for every token of the chunk (speculative verify)
 
 
 class StepBuffers:
-    def __init__(self, max_tokens: int, max_seqs: int, device, mrope: bool = False, attn_block_tokens: int = 16):
+    def __init__(self, max_tokens: int, max_seqs: int, device, mrope: bool = False, attn_block_tokens: int = 16,
+                 max_logit_rows: int = 0):
         self.max_tokens, self.max_seqs = max_tokens, max_seqs
+        n_logit_rows = max(max_seqs, max_logit_rows)
         self.device = torch.device(device)
         self.pos_axes = 3 if mrope else 1
         T, B = max_tokens, max_seqs
         self.attn_block_tokens = max(1, attn_block_tokens)
         NB = (T + self.attn_block_tokens - 1) // self.attn_block_tokens + B
         sizes = [("ids", T), ("token_seq", T), ("table_row", T), ("cache_pos", T), ("rope_pos", T * self.pos_axes),
-                 ("kv_len", T), ("cu_seqlens", B + 1), ("state_slot", B), ("logit_rows", B), ("qblk_start", NB), ("qblk_count", NB)]
+                 ("kv_len", T), ("cu_seqlens", B + 1), ("state_slot", B), ("logit_rows", n_logit_rows), ("qblk_start", NB), ("qblk_count", NB)]
         self.offsets = {}
         off = 0
         for name, n in sizes:
@@ -67,7 +70,8 @@ class StepBuffers:
         ids, tseq, trow = self._hview("ids", T), self._hview("token_seq", T), self._hview("table_row", T)
         cpos, kvl = self._hview("cache_pos", T), self._hview("kv_len", T)
         rpos = self._hview("rope_pos", T * self.pos_axes)
-        cu, slot, lrows = self._hview("cu_seqlens", B + 1), self._hview("state_slot", B), self._hview("logit_rows", B)
+        cu, slot = self._hview("cu_seqlens", B + 1), self._hview("state_slot", B)
+        lrows = self._hview("logit_rows", sum(len(c.tokens) if c.all_logits else 1 for c in chunks))
         t = 0
         n_logit = 0
         qt = self.attn_block_tokens
@@ -94,7 +98,10 @@ class StepBuffers:
                 blk_c.append(min(qt, n - o))
             t += n
             cu[b + 1] = t
-            if c.want_logits:
+            if c.all_logits:
+                lrows[n_logit:n_logit + n] = range(t - n, t)
+                n_logit += n
+            elif c.want_logits:
                 lrows[n_logit] = t - 1
                 n_logit += 1
             max_kv = max(max_kv, c.start_pos + n)

@@ -30,7 +30,7 @@ class Generator:
     def __init__(self, cfg: ModelConfig, weights: Dict[str, torch.Tensor], device, max_batch: int, max_context: int,
                  kv_format: str | Sequence[str] = "bf16", page_size: int = 64, prefill_chunk: int = 2048,
                  use_graph: bool = True, pdl: bool = False, int8_group: int = 64,
-                 shard: Optional[ShardGeometry] = None, comm=None):
+                 shard: Optional[ShardGeometry] = None, comm=None, max_logit_rows: int = 0):
         self.cfg = cfg
         self.device = torch.device(device)
         self.max_batch, self.max_context = max_batch, max_context
@@ -45,7 +45,8 @@ class Generator:
                                formats=kv_format, int8_group=int8_group, n_kv_heads=g.n_kv_heads)
         self.states = GdnStatePool(cfg, max_batch, device, n_qk_heads=g.gdn_qk_heads, n_v_heads=g.gdn_v_heads)
         cap = max(prefill_chunk, max_batch)
-        self.ws = Workspace(cfg, cap, max_batch, device, shard=shard, x_buffer=None if comm is None else comm.x)
+        self.ws = Workspace(cfg, cap, max(max_batch, max_logit_rows), device, shard=shard,
+                            x_buffer=None if comm is None else comm.x)
         qt = int(self.model.ops.prefill_attn_block_tokens(g.n_q_heads, g.n_kv_heads)) if self.device.type == "cuda" else 16
         self.bufs_prefill = StepBuffers(cap, max_batch, device, attn_block_tokens=qt)
         self.bufs_decode = StepBuffers(max_batch, max_batch, device, attn_block_tokens=qt)

@@ -1,0 +1,274 @@
+"""Draft-and-verify speculative decoding: MTP draft module (or a host n-gram drafter), chain verify in
+one target pass, greedy acceptance on the device, and replay of the accepted prefix into the GDN state.
+
+One round for every sequence (frontier n = tokens in the target's KV cache, t = last sampled token):
+
+  1. draft      d_1 is already known from the previous round's catch-up; K - 1 single-token steps of
+                the draft module (its own hidden state fed back) give d_2..d_K
+  2. verify     the target runs [t, d_1..d_K] at positions n..n+K in ONE ragged pass; full-attention
+                layers append K/V for all K + 1 positions (rejected ones are simply overwritten later),
+                GDN layers leave their state untouched and record their projections
+  3. accept     longest prefix with d_{j+1} == argmax_j, plus the target's own next token
+  4. fold       the accepted m + 1 tokens are replayed into conv history + recurrent state
+  5. catch-up   the draft module re-reads the accepted positions with the TARGET's hidden states
+                (overwriting its speculative K/V there) and predicts the next d_1
+
+Reference: src/targets/qwen3_6/impl/runtime/mtp_impl.h, speculative_target_impl.h,
+include/ninfer/ops/speculative_round.h:40-151, include/ninfer/ops/gdn_replay.h:13-49
+(replay-record + fold), include/ninfer/ops/suffix_lookup.h (n-gram lookup drafts).
+"""
+from __future__ import annotations
+
+from typing import Callable, Dict, List, Optional, Sequence
+
+import torch
+
+from ..models.config import ModelConfig
+from ..models.hybrid import GdnRecords
+from .batch import SeqChunk, StepBuffers
+from .generator import Generator
+from .kv_cache import PagedKvCache
+
+
+def ngram_drafter(history: Sequence[int], k: int, max_n: int = 4) -> Optional[List[int]]:
+    """Suffix lookup: find the most recent earlier occurrence of the longest suffix (up to `max_n` tokens) of
+    `history` and propose the k tokens that followed it.  Returns None when nothing matches."""
+    L = len(history)
+    for n in range(min(max_n, L - 1), 0, -1):
+        suffix = list(history[L - n:])
+        for start in range(L - n - 1, -1, -1):
+            if list(history[start:start + n]) == suffix:
+                cont = list(history[start + n:start + n + k])
+                if cont:
+                    return cont + [cont[-1]] * (k - len(cont))
+    return None
+
+
+class SpeculativeGenerator(Generator):
+    """Static-batch greedy generation with K chained draft tokens per round."""
+
+    def __init__(self, cfg: ModelConfig, weights: Dict[str, torch.Tensor], device, max_batch: int, max_context: int,
+                 draft_tokens: int = 3, drafter: str = "mtp", **kw):
+        K = draft_tokens
+        if K < 1:
+            raise ValueError("draft_tokens must be >= 1")
+        kw.setdefault("use_graph", False)
+        super().__init__(cfg, weights, device, max_batch, max_context, max_logit_rows=max_batch * (K + 1), **kw)
+        self.K = K
+        self.drafter = drafter  # "mtp" | "ngram" | "hook"
+        self.draft_hook: Optional[Callable[[int, List[int], int], Optional[List[int]]]] = None
+        dev, g = self.device, self.model.g
+        Tv = max_batch * (K + 1)
+        qt = self.bufs_decode.attn_block_tokens
+        self.bufs_verify = StepBuffers(Tv, max_batch, dev, attn_block_tokens=qt, max_logit_rows=Tv)
+        self.bufs_catch = StepBuffers(Tv, max_batch, dev, attn_block_tokens=qt)
+        self.bufs_draft = StepBuffers(max_batch, max_batch, dev, attn_block_tokens=qt)
+        self.rec = GdnRecords(cfg, Tv, dev, shard=self.model.g)
+        h = cfg.hidden
+        self.h_keep = torch.empty((max(self.ws.max_tokens, Tv), h), dtype=torch.bfloat16, device=dev)
+        self.h_in = torch.empty((max(self.ws.max_tokens, Tv), h), dtype=torch.bfloat16, device=dev)
+        self.mtp_h = torch.empty((max_batch, h), dtype=torch.bfloat16, device=dev)
+        pin = dev.type == "cuda"
+        self.next_host = torch.zeros(max(self.ws.max_tokens, Tv), dtype=torch.int32, pin_memory=pin)
+        self.next_dev = torch.zeros(max(self.ws.max_tokens, Tv), dtype=torch.int32, device=dev)
+        self.drafts = torch.zeros((max_batch, K), dtype=torch.int32, device=dev)
+        self.draft_host = torch.zeros((max_batch, K), dtype=torch.int32, pin_memory=pin)
+        self.n_acc = torch.zeros(max_batch, dtype=torch.int32, device=dev)
+        self.out_tok = torch.zeros((max_batch, K + 1), dtype=torch.int32, device=dev)
+        self.acc_host = torch.zeros(max_batch, dtype=torch.int32, pin_memory=pin)
+        self.tok_host = torch.zeros((max_batch, K + 1), dtype=torch.int32, pin_memory=pin)
+        self.kv_mtp = None
+        if drafter == "mtp":
+            if "mtp/fc" not in weights:
+                raise ValueError("weights have no draft module (random_weights(..., with_mtp=True))")
+            pages_per_row = (max_context + self.page_size - 1) // self.page_size
+            one_attn = cfg.shrink(cfg.full_attn_interval)  # geometry of a cache with a single attention layer
+            self.kv_mtp = PagedKvCache(one_attn, max_batch * pages_per_row, self.page_size, max_batch, pages_per_row,
+                                       dev, formats="bf16", n_kv_heads=g.n_kv_heads)
+        self.history: List[List[int]] = []
+        self.rounds = 0
+        self.accepted = 0
+        self.emitted = 0
+
+    # ------------------------------------------------------------------ helpers
+    def _upload_next(self, toks: Sequence[int]) -> torch.Tensor:
+        n = len(toks)
+        self.next_host[:n] = torch.tensor(list(toks), dtype=torch.int32)
+        self.next_dev[:n].copy_(self.next_host[:n], non_blocking=True)
+        return self.next_dev[:n]
+
+    def _mtp_pass(self, batch, hidden_in: torch.Tensor, next_ids: torch.Tensor, seqs: Sequence[int]) -> None:
+        """Draft module over `batch`; for the sequences `seqs` (whose last token is a logit row, in order) store
+        the first draft token and the module's hidden state."""
+        hid = self.model.forward_mtp(self.ws, batch, self.kv_mtp, hidden_in, next_ids)
+        if not seqs:
+            return
+        lg = self.model.logits(self.ws, batch, hid)
+        ids = self.ws.next_ids[: lg.shape[0]]
+        self.model.ops.argmax_rows(lg, ids, self.model.pdl)
+        idx = torch.tensor(list(seqs), dtype=torch.long, device=self.device)
+        self.drafts[idx, 0] = ids
+        self.mtp_h[idx] = hid.index_select(0, batch.logit_rows.long())
+
+    # ------------------------------------------------------------------ prefill
+    def prefill(self, prompts: Sequence[Sequence[int]]) -> List[int]:
+        if self.drafter != "mtp":
+            first = super().prefill(prompts)
+            self.history = [list(p) + [t] for p, t in zip(prompts, first)]
+            return first
+        if len(prompts) > self.max_batch:
+            raise ValueError("too many sequences")
+        self.reset()
+        for r in range(self.max_batch):
+            self.kv_mtp.free_row(r)
+        B = len(prompts)
+        for b in range(B):
+            self.rows.append(b)
+            self.slots.append(self.states.alloc())
+            self.lengths.append(0)
+            self.kv.ensure(b, len(prompts[b]) + self.K + 2)
+            self.kv_mtp.ensure(b, len(prompts[b]) + self.K + 2)
+        self.kv.publish()
+        self.kv_mtp.publish()
+        first = [0] * B
+        cursor = [0] * B
+        pending = list(range(B))
+        while pending:
+            budget = self.prefill_chunk
+            chunks, owners = [], []
+            for b in list(pending):
+                if budget == 0 or len(chunks) == self.max_batch:
+                    break
+                n = min(budget, len(prompts[b]) - cursor[b])
+                done = cursor[b] + n == len(prompts[b])
+                chunks.append(SeqChunk(self.rows[b], self.slots[b], cursor[b], prompts[b][cursor[b]:cursor[b] + n], done))
+                owners.append((b, cursor[b], n, done))
+                cursor[b] += n
+                budget -= n
+                if done:
+                    pending.remove(b)
+            batch = self.bufs_prefill.build(chunks)
+            T = batch.n_tokens
+            ids = self.model.forward_greedy(self.ws, batch, self.kv, self.states)
+            self.h_keep[:T].copy_(self.ws.normed[:T])
+            if ids.numel():
+                self.out_host[: ids.numel()].copy_(ids, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            j = 0
+            nxt: List[int] = []
+            done_seqs = []
+            for b, start, n, done in owners:
+                if done:
+                    first[b] = int(self.out_host[j])
+                    j += 1
+                    done_seqs.append(b)
+                    nxt.extend(list(prompts[b][start + 1:start + n]) + [first[b]])
+                else:
+                    nxt.extend(prompts[b][start + 1:start + n + 1])
+            # the draft module reads the same positions: hidden state of p + token p + 1
+            self._mtp_pass(batch, self.h_keep[:T], self._upload_next(nxt), done_seqs)
+        for b in range(B):
+            self.lengths[b] = len(prompts[b])
+        self.last_tokens = list(first)
+        self.history = [list(p) + [t] for p, t in zip(prompts, first)]
+        self.model.status.check("after speculative prefill")
+        return first
+
+    # ------------------------------------------------------------------ one round
+    def _draft(self, B: int) -> None:
+        """Fills self.drafts[:B] (device)."""
+        K = self.K
+        if self.drafter == "mtp":
+            for j in range(1, K):
+                # position n + j - 1 of the draft module: its own hidden state + the previous draft token
+                chunks = [SeqChunk(self.rows[b], self.slots[b], self.lengths[b] + j - 1, [0], True) for b in range(B)]
+                batch = self.bufs_draft.build(chunks)
+                self.h_in[:B].copy_(self.mtp_h[:B])
+                hid = self.model.forward_mtp(self.ws, batch, self.kv_mtp, self.h_in[:B], self.drafts[:B, j - 1].contiguous())
+                lg = self.model.logits(self.ws, batch, hid)
+                ids = self.ws.next_ids[:B]
+                self.model.ops.argmax_rows(lg, ids, self.model.pdl)
+                self.drafts[:B, j] = ids
+                self.mtp_h[:B].copy_(hid)
+            return
+        for b in range(B):
+            d = None
+            if self.draft_hook is not None:
+                d = self.draft_hook(b, self.history[b], K)
+            elif self.drafter == "ngram":
+                d = ngram_drafter(self.history[b], K)
+            if d is None:
+                d = [self.last_tokens[b]] * K
+            self.draft_host[b] = torch.tensor(list(d)[:K], dtype=torch.int32)
+        self.drafts[:B].copy_(self.draft_host[:B], non_blocking=True)
+
+    def decode_round(self) -> List[List[int]]:
+        """One draft-verify round; returns the tokens emitted for every sequence (1..K+1 each)."""
+        B, K = len(self.rows), self.K
+        ops = self.model.ops
+        for b, r in enumerate(self.rows):
+            self.kv.ensure(r, self.lengths[b] + K + 2)
+            if self.kv_mtp is not None:
+                self.kv_mtp.ensure(r, self.lengths[b] + K + 2)
+        self.kv.publish()
+        if self.kv_mtp is not None:
+            self.kv_mtp.publish()
+        self._draft(B)
+        # ---- verify: [t, d_1..d_K] per sequence in one ragged target pass ----
+        chunks = [SeqChunk(self.rows[b], self.slots[b], self.lengths[b], [self.last_tokens[b]] + [0] * K, True, True)
+                  for b in range(B)]
+        batch = self.bufs_verify.build(chunks)
+        T = B * (K + 1)
+        batch.ids.view(B, K + 1)[:, 1:] = self.drafts[:B]
+        hidden = self.model.forward_hidden(self.ws, batch, self.kv, self.states, write_state=False, rec=self.rec)
+        self.h_keep[:T].copy_(hidden)
+        lg = self.model.logits(self.ws, batch, hidden)
+        target = self.ws.next_ids[:T]
+        ops.argmax_rows(lg, target, self.model.pdl)
+        # ---- accept + fold ----
+        ops.accept_greedy_chain(target.view(B, K + 1), self.drafts[:B], self.n_acc[:B], self.out_tok[:B])
+        seq_end = (batch.cu_seqlens[:B] + self.n_acc[:B] + 1).to(torch.int32)
+        self.model.fold_gdn(self.ws, batch, self.states, self.rec, seq_end)
+        self.acc_host[:B].copy_(self.n_acc[:B], non_blocking=True)
+        self.tok_host[:B].copy_(self.out_tok[:B], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        emitted: List[List[int]] = []
+        for b in range(B):
+            m = int(self.acc_host[b])
+            toks = [int(v) for v in self.tok_host[b, : m + 1]]
+            emitted.append(toks)
+            self.accepted += m
+            self.emitted += m + 1
+        self.rounds += 1
+        # ---- draft-module catch-up over the accepted positions with the target's hidden states ----
+        if self.drafter == "mtp":
+            chunks, rows, nxt = [], [], []
+            for b in range(B):
+                m1 = len(emitted[b])
+                chunks.append(SeqChunk(self.rows[b], self.slots[b], self.lengths[b], [0] * m1, True))
+                rows.extend(range(b * (K + 1), b * (K + 1) + m1))
+                nxt.extend(emitted[b])
+            cb = self.bufs_catch.build(chunks)
+            idx = torch.tensor(rows, dtype=torch.long, device=self.device)
+            Tc = len(rows)
+            torch.index_select(self.h_keep[:T], 0, idx, out=self.h_in[:Tc])
+            self._mtp_pass(cb, self.h_in[:Tc], self._upload_next(nxt), list(range(B)))
+        for b in range(B):
+            self.lengths[b] += len(emitted[b])
+            self.last_tokens[b] = emitted[b][-1]
+            self.history[b].extend(emitted[b])
+        return emitted
+
+    def generate(self, prompts: Sequence[Sequence[int]], n_new: int) -> List[List[int]]:
+        first = self.prefill(prompts)
+        out = [[t] for t in first]
+        while min(len(o) for o in out) < n_new:
+            for b, toks in enumerate(self.decode_round()):
+                out[b].extend(toks)
+        self.model.status.check("after speculative decode")
+        return [o[:n_new] for o in out]
+
+    @property
+    def tokens_per_round(self) -> float:
+        B = max(1, len(self.rows))
+        return self.emitted / max(1, self.rounds * B)

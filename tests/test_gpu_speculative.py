@@ -1,0 +1,91 @@
+"""Draft-and-verify decoding: the emitted stream must be the target's own greedy stream whatever the drafts are."""
+import pytest
+import torch
+
+from ninfer_fusion_b200.models.config import TINY_DENSE, TINY_MOE
+from ninfer_fusion_b200.models.reference_model import ReferenceModel, ReferenceSequence
+from ninfer_fusion_b200.models.weights import random_weights
+from ninfer_fusion_b200.ops import reference as R
+from ninfer_fusion_b200.runtime.generator import Generator
+from ninfer_fusion_b200.runtime.speculative import SpeculativeGenerator, ngram_drafter
+
+pytestmark = pytest.mark.gpu
+
+
+def _teacher_forced_agreement(cfg, w, prompts, out):
+    ref = ReferenceModel(cfg, {k: v.cpu() for k, v in w.items() if not k.startswith("mtp/")})
+    agree = total = 0
+    for b, p in enumerate(prompts):
+        seq = ReferenceSequence(cfg, R.KV_BF16)
+        hid = ref.forward(seq, torch.tensor(p))
+        for tok in out[b]:
+            lg = ref.logits(hid[-1:])[0]
+            top2 = lg.topk(2).values
+            if (top2[0] - top2[1]).item() > 0.05:
+                total += 1
+                agree += int(int(R.argmax_lowest(lg[None])[0]) == tok)
+            hid = ref.forward(seq, torch.tensor([tok]))
+    return agree, total
+
+
+@pytest.mark.parametrize("quality", ["perfect", "mixed", "garbage"])
+def test_hook_drafts_keep_the_greedy_stream(quality):
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cuda", seed=7, std=0.05)
+    torch.manual_seed(1)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (21, 70, 5)]
+    n_new = 24
+    plain = Generator(cfg, w, "cuda", max_batch=4, max_context=512, kv_format="bf16", page_size=16, prefill_chunk=64,
+                      use_graph=False).generate(prompts, n_new + 8)
+    K = 3
+    gen = SpeculativeGenerator(cfg, w, "cuda", max_batch=4, max_context=512, draft_tokens=K, drafter="hook",
+                               kv_format="bf16", page_size=16, prefill_chunk=64)
+    plen = [len(p) for p in prompts]
+
+    def hook(b, history, k):
+        done = len(history) - plen[b]           # tokens already emitted for b (plain[b][:done] if streams agree)
+        truth = plain[b][done:done + k]
+        truth = truth + [0] * (k - len(truth))
+        if quality == "perfect":
+            return truth
+        if quality == "garbage":
+            return [(t + 1) % cfg.vocab for t in truth]
+        cut = (done + b) % (k + 1)              # first `cut` drafts right, the rest wrong
+        return [t if i < cut else (t + 1) % cfg.vocab for i, t in enumerate(truth)]
+
+    gen.draft_hook = hook
+    out = gen.generate(prompts, n_new)
+    agree, total = _teacher_forced_agreement(cfg, w, prompts, out)
+    assert total > 30 and agree / total >= 0.95, f"{agree}/{total}"
+    if quality == "perfect":
+        assert gen.tokens_per_round > K  # nearly every draft accepted
+    if quality == "garbage":
+        assert gen.tokens_per_round == 1.0
+    if quality == "mixed":
+        assert 1.0 < gen.tokens_per_round < K + 1
+
+
+@pytest.mark.parametrize("cfg", [TINY_DENSE, TINY_MOE], ids=lambda c: c.name)
+def test_mtp_drafter_keeps_the_greedy_stream(cfg):
+    w = random_weights(cfg, "cuda", seed=9, std=0.05, with_mtp=True)
+    torch.manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (33, 90)]
+    gen = SpeculativeGenerator(cfg, w, "cuda", max_batch=2, max_context=512, draft_tokens=3, drafter="mtp",
+                               kv_format="bf16", page_size=16, prefill_chunk=64)
+    out = gen.generate(prompts, 16)
+    agree, total = _teacher_forced_agreement(cfg, w, prompts, out)
+    assert total > 12 and agree / total >= 0.9, f"{agree}/{total}"
+    assert gen.rounds > 0 and gen.tokens_per_round >= 1.0
+
+
+def test_ngram_drafter_on_repetitive_text():
+    assert ngram_drafter([1, 2, 3, 4, 1, 2, 3], 3) == [4, 1, 2]
+    assert ngram_drafter([5, 6, 7], 2) is None
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cuda", seed=7, std=0.05)
+    prompts = [[3, 9, 27, 81] * 8]
+    gen = SpeculativeGenerator(cfg, w, "cuda", max_batch=1, max_context=512, draft_tokens=3, drafter="ngram",
+                               kv_format="bf16", page_size=16, prefill_chunk=64)
+    out = gen.generate(prompts, 12)
+    agree, total = _teacher_forced_agreement(cfg, w, prompts, out)
+    assert total > 6 and agree / total >= 0.9
