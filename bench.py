@@ -109,6 +109,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="debug only: shrink the layer count (result is marked invalid)")
     ap.add_argument("--no-ttft", action="store_true")
     ap.add_argument("--pdl", type=int, default=1)
+    ap.add_argument("--weights", default="bf16", choices=["bf16", "fp8", "nvfp4"],
+                    help="matmul weight format (fp8 = e4m3 row-scale W8A8, nvfp4 = e2m1 block-scaled W4A4); one GPU only")
     ap.add_argument("--parallel", default="", choices=["", "tp", "ep"],
                     help="multi-GPU plan: tp = tensor parallel (dense default), ep = data parallel + expert parallel (MoE default)")
     args = ap.parse_args()
@@ -157,7 +159,10 @@ def main() -> int:
         shard = comm.geometry
         weights = comm.random_shard_weights(seed=0)
     else:
-        weights = random_weights(cfg, device, seed=0)
+        weights = random_weights(cfg, device, seed=0, weight_format=args.weights)
+    if args.weights != "bf16" and world > 1:
+        print("bench.py: quantised weights run on one GPU only", file=sys.stderr)
+        return 2
 
     B, L, K, W = args.batch, args.prompt_len, args.steps, args.warmup
     B_local = B // world if ep else B  # expert parallel: every rank decodes its own share of the sequences
@@ -238,11 +243,13 @@ def main() -> int:
             "metric": "decode tokens/sec/box + p50 TTFT at 1/2/4/8 B200, 27B hybrid fp8-KV",
             "value": round(value, 2), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": round(value / baseline_tok_s, 3), "dtype": "bf16",
+            "vs_baseline": round(value / baseline_tok_s, 3),
+            "dtype": {"bf16": "bf16", "fp8": "fp8 e4m3 weights and activations, fp32 accumulate, bf16 residual",
+                      "nvfp4": "nvfp4 weights and activations (block-scaled e2m1), fp32 accumulate, bf16 residual"}[args.weights],
             "data": "synthetic uniform-random token prompts, random-init weights",
             "config": {"model": cfg.name + ("" if not args.layers else " (SHRUNK: INVALID)"), "global_batch": B,
                        "seq_len": L, "parallelism": f"{parallel}{world}" if world > 1 else "single", "kv": args.kv_format + "-e4m3-row" if args.kv_format == "fp8" else args.kv_format,
-                       "weights": "bf16", "decode": "greedy, CUDA graph per round",
+                       "weights": args.weights, "decode": "greedy, CUDA graph per round",
                        "l2": "inputs larger than L2 (all weights streamed every round), no flush",
                        "baseline_note": f"vs_baseline divides by the reference's single-request decode tok/s ({baseline_tok_s}, one RTX 5090)"},
             "ttft_ms_p50": round(ttft_max, 2) if ttft_ms is not None else None,

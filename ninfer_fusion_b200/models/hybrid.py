@@ -177,6 +177,17 @@ class LaunchCounter:
         return fn
 
 
+class QuantWeight:
+    """A matmul weight held as quantised planes (ops.quant): fp8 row-scale or nvfp4 block-scaled."""
+    __slots__ = ("qtype", "codes", "scale", "divisor", "shape")
+
+    def __init__(self, qtype: int, codes: torch.Tensor, scale: torch.Tensor, divisor: float, shape):
+        self.qtype, self.codes, self.scale, self.divisor, self.shape = qtype, codes, scale, float(divisor), tuple(shape)
+
+    def nbytes(self) -> int:
+        return self.codes.numel() + self.scale.numel() * self.scale.element_size()
+
+
 class GdnRecords:
     """Per-layer projection and convolution outputs of a verify pass, kept so that the accepted prefix can be
     replayed into the recurrent state and the conv history without recomputing the projections
@@ -208,6 +219,8 @@ class HybridModel:
         self.cluster_splitk = True  # False: split-K through an fp32 workspace + reduce kernel
         self.attn_impl = 0  # 0 = pick, 1 = SIMT, 2 = tensor-core split-KV attention
         self.comm = None  # tensor-parallel communicator (parallel.tp), None on one GPU
+        self._qbuf: Dict[int, tuple] = {}
+        self._qkeep: List[tuple] = []
         self.moe = None   # models.moe.MoeBlock, created with the first workspace that runs a MoE layer
         self.ep = (ep_rank, ep_world, ep_group)  # expert parallelism: experts split, the rest data-parallel
         self.moe_global_tokens: Optional[int] = None  # bound on the tokens of all ranks in a step (default world * T)
@@ -216,7 +229,40 @@ class HybridModel:
         self._gdn_idx = {l: i for i, l in enumerate(cfg.gdn_layers)}
 
     # ------------------------------------------------------------------ GEMM helpers
+    def _quant_scratch(self, T: int, K: int):
+        """Activation code / scale buffers for a quantised GEMM with K input features (grown on demand; earlier
+        buffers stay alive because captured graphs may still point at them)."""
+        cur = self._qbuf.get(K)
+        if cur is None or cur[0] < T:
+            cap = max(T, 64 if cur is None else 2 * cur[0])
+            dev = self.device
+            cur = (cap, torch.empty(cap * K, dtype=torch.uint8, device=dev),
+                   torch.empty(cap, dtype=torch.float32, device=dev),
+                   torch.zeros(int(self.ops.nvfp4_act_scale_bytes(cap, K)) if K % 64 == 0 else 16, dtype=torch.uint8, device=dev))
+            self._qkeep.append(cur)
+            self._qbuf[K] = cur
+        return cur
+
+    def _gemm_quant(self, x, w: QuantWeight, out, epi, resid):
+        T, (N, K) = x.shape[0], w.shape
+        _, codes, scale, plane = self._quant_scratch(T, K)
+        splits = 1
+        if self.cluster_splitk:
+            kb_equiv = (K // 2 if w.qtype == 2 else K) // 2   # so that K/64 equals the kernel's 128-byte k-blocks
+            splits = int(self.ops.gemm_pick_splits(T, N, kb_equiv, EPI_STORE if epi == EPI_SWIGLU else epi))
+        if w.qtype == 2:
+            xc = codes[: T * K // 2].view(T, K // 2)
+            self.ops.quant_act_nvfp4(x, xc, plane)
+            self.ops.gemm_quant(2, xc, plane, w.codes, w.scale, w.divisor, out, epi, resid, splits, self.status.tensor, self.pdl)
+        else:
+            xc = codes[: T * K].view(T, K)
+            self.ops.quant_act_fp8(x, xc, scale)
+            self.ops.gemm_quant(1, xc, scale, w.codes, w.scale, 1.0, out, epi, resid, splits, self.status.tensor, self.pdl)
+
     def _gemm(self, x, w, out, epi=EPI_STORE, resid=None):
+        if isinstance(w, QuantWeight):
+            self._gemm_quant(x, w, out, epi, resid)
+            return
         # in-cluster split-K when the output tiles alone cannot fill the GPU (decode, sharded weights)
         splits = int(self.ops.gemm_pick_splits(x.shape[0], w.shape[0], w.shape[1], epi)) if self.cluster_splitk else 1
         self.ops.gemm_bf16(x, w, out, epi, resid, None, None, splits, self.status.tensor, self.pdl)

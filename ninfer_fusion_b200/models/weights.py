@@ -58,7 +58,8 @@ def weight_shapes(cfg: ModelConfig, with_mtp: bool = False) -> Iterator[Tuple[st
 
 
 def random_weights(cfg: ModelConfig, device, seed: int = 0, with_mtp: bool = False,
-                   std: float = 0.02, expert_rank: int = 0, expert_world: int = 1) -> Dict[str, torch.Tensor]:
+                   std: float = 0.02, expert_rank: int = 0, expert_world: int = 1,
+                   weight_format: str = "bf16") -> Dict[str, torch.Tensor]:
     """Random-init weights of the architecture (there are no checkpoints on the box).
 
     With `expert_world` > 1 the routed expert banks hold only this rank's contiguous range of experts
@@ -90,9 +91,53 @@ def random_weights(cfg: ModelConfig, device, seed: int = 0, with_mtp: bool = Fal
             t.normal_(0.0, 0.3, generator=gen)
         else:
             t.normal_(0.0, std, generator=gen)
-        out[name] = t
+        out[name] = quantize_tensor(name, t, weight_format)  # quantised right away: the bf16 copy is dropped
     return out
 
 
-def total_bytes(weights: Dict[str, torch.Tensor]) -> int:
-    return sum(t.numel() * t.element_size() for t in weights.values())
+QUANT_LEAVES = ("in_proj", "o_proj", "out_proj", "gate_up", "down", "lm_head")
+
+
+def quantize_tensor(name: str, t: torch.Tensor, weight_format: str):
+    """bf16 matmul weight -> QuantWeight for the tcgen05 quantised GEMMs ('fp8' row-scale or 'nvfp4' block-scaled).
+    The fused [gate; up] parent is stored tile-interleaved, as the quantised SwiGLU epilogue expects."""
+    from ..ops import quant as Q
+    from .hybrid import QuantWeight
+    leaf = name.rsplit("/", 1)[-1]
+    if weight_format == "bf16" or t.dim() != 2 or leaf not in QUANT_LEAVES or "/moe/" in name:
+        return t
+    N, K = t.shape
+    w = Q.interleave_gate_up(t) if leaf == "gate_up" else t
+    if weight_format == "fp8":
+        codes, scale = Q.quantize_fp8_row(w)
+        return QuantWeight(Q.QT_FP8_ROW, codes, scale, 1.0, (N, K))
+    if weight_format == "nvfp4":
+        if K % 256:
+            raise ValueError(f"{name}: nvfp4 needs K % 256 == 0, got {K}")
+        chunks = [Q.quantize_nvfp4_prepare(w)]
+        codes, plane, d_w = chunks[0]
+        return QuantWeight(Q.QT_NVFP4, codes, plane, d_w, (N, K))
+    raise ValueError(f"unknown weight format '{weight_format}'")
+
+
+def quantize_weights(weights: Dict[str, torch.Tensor], weight_format: str) -> Dict[str, object]:
+    """Quantise every eligible matmul weight in place of its bf16 tensor (embedding, norms, conv, router stay bf16)."""
+    return {k: quantize_tensor(k, v, weight_format) for k, v in weights.items()}
+
+
+def dequantize_weights(weights: Dict[str, object]) -> Dict[str, torch.Tensor]:
+    """The represented values of every tensor (fp32 for quantised ones, original row order): the oracle's weights."""
+    from ..ops import quant as Q
+    out = {}
+    for name, t in weights.items():
+        if not hasattr(t, "qtype"):
+            out[name] = t
+            continue
+        N, K = t.shape
+        w = Q.dequant_nvfp4(t.codes, t.scale, t.divisor, N, K) if t.qtype == Q.QT_NVFP4 else Q.dequant_fp8_row(t.codes, t.scale)
+        out[name] = Q.deinterleave_gate_up(w) if name.endswith("gate_up") else w
+    return out
+
+
+def total_bytes(weights: Dict[str, object]) -> int:
+    return sum(t.nbytes() if hasattr(t, "qtype") else t.numel() * t.element_size() for t in weights.values())

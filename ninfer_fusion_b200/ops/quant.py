@@ -55,6 +55,29 @@ def quantize_nvfp4(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, float]:
     return packed.contiguous(), plane, d_w
 
 
+def quantize_nvfp4_prepare(w: torch.Tensor, rows_per_step: int = 16384) -> Tuple[torch.Tensor, torch.Tensor, float]:
+    """quantize_nvfp4 for large matrices: the global divisor comes from one pass over the matrix, then the
+    rows are encoded in slabs (multiples of 128 rows) to bound the temporary memory."""
+    N, K = w.shape
+    gmax = float(w.abs().amax())
+    d_w = 448.0 * 6.0 / gmax if gmax > 0 else 1.0
+    packed = torch.empty((N, K // 2), dtype=torch.uint8, device=w.device)
+    plane = torch.zeros(((N + 127) // 128) * (K // 64) * 512, dtype=torch.uint8, device=w.device)
+    tile_bytes = (K // 64) * 512
+    for r0 in range(0, N, rows_per_step):
+        r1 = min(N, r0 + rows_per_step)
+        g = w[r0:r1].float().reshape(r1 - r0, K // 16, 16)
+        amax = g.abs().amax(-1)
+        sf = (amax * d_w / 6.0).clamp(max=448.0).to(torch.float8_e4m3fn)
+        s = sf.float()
+        inv = torch.where(s > 0, d_w / torch.where(s > 0, s, torch.ones_like(s)), torch.zeros_like(s))
+        codes = e2m1_codes(g * inv[..., None]).reshape(r1 - r0, K)
+        packed[r0:r1] = codes[:, 0::2] | (codes[:, 1::2] << 4)
+        off = sf_tile_offsets(r1 - r0, K, w.device).reshape(-1) + (r0 // 128) * tile_bytes
+        plane[off] = sf.view(torch.uint8).reshape(-1)
+    return packed, plane, d_w
+
+
 def dequant_nvfp4(packed: torch.Tensor, plane: torch.Tensor, divisor: float, rows: int, K: int) -> torch.Tensor:
     codes = torch.stack([packed & 0xF, packed >> 4], dim=-1).reshape(rows, K)
     sf = plane[sf_tile_offsets(rows, K, packed.device).reshape(-1)].view(torch.float8_e4m3fn).float().reshape(rows, K // 16)
@@ -81,3 +104,10 @@ def interleave_gate_up(w: torch.Tensor) -> torch.Tensor:
         raise ValueError("intermediate size must be a multiple of 64")
     gate, up = w[:i].reshape(i // 64, 64, K), w[i:].reshape(i // 64, 64, K)
     return torch.cat([gate, up], dim=1).reshape(two_i, K).contiguous()
+
+
+def deinterleave_gate_up(w: torch.Tensor) -> torch.Tensor:
+    """Inverse of interleave_gate_up."""
+    two_i, K = w.shape
+    t = w.reshape(two_i // 128, 2, 64, K)
+    return torch.cat([t[:, 0].reshape(two_i // 2, K), t[:, 1].reshape(two_i // 2, K)], dim=0).contiguous()
