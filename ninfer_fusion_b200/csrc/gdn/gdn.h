@@ -53,5 +53,8 @@ struct GdnParams {
 const char* gdn_recurrent(const GdnParams& p, cudaStream_t stream, bool pdl);
 // Multi-token variant (token groups staged in shared memory); gdn_recurrent dispatches to it when T > n_seq.
 const char* gdn_prefill(const GdnParams& p, cudaStream_t stream, bool pdl);
+// Performance debugging of the row-split variant: switches the phase profile on/off and reads the last profile
+// (cycles of CTA (0,0): operand wait, prologue, serial steps, partial sums + cluster barrier, epilogue).
+void gdn_prefill_trace(bool enable, long long* host5);
 
 }  // namespace nfb

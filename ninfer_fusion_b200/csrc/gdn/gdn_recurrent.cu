@@ -89,10 +89,12 @@ __global__ void __launch_bounds__(kThreads, 2) gdn_recurrent_kernel(const GdnPar
     for (int j = 0; j < kRowsPerThread; ++j) {
       const int r = warp * 16 + j * 4 + sub;
       const float v = __bfloat162float(row[p.v_off + hv * kDv + r]);
-      float ks = 0.f;
+      // same summation tree as the prefill kernels, so decode, prefill and replay stay bit-consistent
+      float kp4[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i)
-        ks += S[j][i].x * k4[i].x + S[j][i].y * k4[i].y + S[j][i].z * k4[i].z + S[j][i].w * k4[i].w;
+        kp4[i] = S[j][i].x * k4[i].x + S[j][i].y * k4[i].y + S[j][i].z * k4[i].z + S[j][i].w * k4[i].w;
+      float ks = (kp4[0] + kp4[1]) + (kp4[2] + kp4[3]);
       ks += __shfl_xor_sync(0xffffffffu, ks, 1);
       ks += __shfl_xor_sync(0xffffffffu, ks, 2);
       ks += __shfl_xor_sync(0xffffffffu, ks, 4);

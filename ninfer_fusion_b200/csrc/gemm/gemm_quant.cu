@@ -39,14 +39,16 @@ constexpr int kKBytes = 128;  // bytes of K per k-block = one swizzle row
 constexpr int kWTileBytes = kTileN * kKBytes;
 constexpr int kSfTileBytes = 512;  // 128 rows x 4 scales
 
-template <int TN, int QT>
+// DEEP = the whole grid fits in one wave: one CTA per SM with a deep pipeline.  Otherwise the pipeline is shallow
+// enough for two CTAs per SM, so that a grid of up to two waves is resident at once.
+template <int TN, int QT, bool DEEP>
 struct QCfg {
   static constexpr bool kBlockScaled = QT == kQNvfp4;
   static constexpr int kXTileBytes = TN * kKBytes;
   static constexpr int kSfaBytes = kBlockScaled ? 4 * kSfTileBytes : 0;                     // 4 MMA-K steps per k-block
   static constexpr int kSfbBytes = kBlockScaled ? (TN <= 128 ? 4 : 8) * kSfTileBytes : 0;  // 1 or 2 token tiles
   static constexpr int kStageBytes = kWTileBytes + kXTileBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kStages = TN <= 32 ? 8 : (TN == 64 ? 6 : (TN == 128 ? 5 : 3));
+  static constexpr int kStages = TN <= 32 ? (DEEP ? 8 : 4) : (TN == 64 ? (DEEP ? 6 : 3) : (TN == 128 ? 5 : 3));
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
   static constexpr int kSfaCol = TN;           // TMEM columns: [0, TN) accumulator, then SFA, then SFB
   static constexpr int kSfbCol = TN + 16;
@@ -100,10 +102,10 @@ struct QParams {
   int* status;
 };
 
-template <int TN, int QT, int EPI>
+template <int TN, int QT, int EPI, bool DEEP>
 __global__ void __launch_bounds__(128) gemm_q_kernel(const __grid_constant__ CUtensorMap tmap_w,
                                                       const __grid_constant__ CUtensorMap tmap_x, const QParams p) {
-  using Cfg = QCfg<TN, QT>;
+  using Cfg = QCfg<TN, QT, DEEP>;
   constexpr int kStages = Cfg::kStages;
   constexpr bool kBS = Cfg::kBlockScaled;
   extern __shared__ uint8_t smem_raw[];
@@ -383,6 +385,8 @@ __global__ void __launch_bounds__(128) gemm_q_kernel(const __grid_constant__ CUt
 __global__ void __launch_bounds__(256) quant_act_fp8_kernel(const __nv_bfloat16* x, long long ldx, int K, uint8_t* codes,
                                                             float* scale) {
   __shared__ float red[8];
+  pdl_launch_next();
+  pdl_wait_prior();
   const int t = blockIdx.x;
   const __nv_bfloat16* row = x + static_cast<long long>(t) * ldx;
   const int nvec = K / 8;
@@ -418,6 +422,8 @@ __global__ void __launch_bounds__(256) quant_act_fp8_kernel(const __nv_bfloat16*
 
 __global__ void __launch_bounds__(256) quant_act_nvfp4_kernel(const __nv_bfloat16* x, long long ldx, int K, uint8_t* codes,
                                                               uint8_t* sf_plane) {
+  pdl_launch_next();
+  pdl_wait_prior();
   const int t = blockIdx.x;
   const int g = blockIdx.y * 256 + threadIdx.x;  // 16-value block index
   if (g * 16 >= K) return;
@@ -450,11 +456,11 @@ __global__ void __launch_bounds__(256) quant_act_nvfp4_kernel(const __nv_bfloat1
   sf_plane[off] = sc;
 }
 
-template <int TN, int QT, int EPI>
+template <int TN, int QT, int EPI, bool DEEP>
 cudaError_t launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const QParams& kp, dim3 grid, cudaStream_t stream,
                        bool pdl) {
-  using Cfg = QCfg<TN, QT>;
-  auto kern = gemm_q_kernel<TN, QT, EPI>;
+  using Cfg = QCfg<TN, QT, DEEP>;
+  auto kern = gemm_q_kernel<TN, QT, EPI, DEEP>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
@@ -485,14 +491,30 @@ cudaError_t launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const QPara
   return cudaLaunchKernelEx(&cfg, kern, tw, tx, kp);
 }
 
+int q_sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+bool q_is_deep(int tn, dim3 grid) {
+  return tn <= 64 && static_cast<long long>(grid.x) * grid.y * grid.z <= q_sm_count();
+}
+
 template <int QT, int EPI>
 cudaError_t launch_tn(int tn, const CUtensorMap& tw, const CUtensorMap& tx, const QParams& kp, dim3 grid,
                       cudaStream_t stream, bool pdl) {
+  const bool deep = q_is_deep(tn, grid);
   switch (tn) {
-    case 32: return launch_one<32, QT, EPI>(tw, tx, kp, grid, stream, pdl);
-    case 64: return launch_one<64, QT, EPI>(tw, tx, kp, grid, stream, pdl);
-    case 128: return launch_one<128, QT, EPI>(tw, tx, kp, grid, stream, pdl);
-    default: return launch_one<256, QT, EPI>(tw, tx, kp, grid, stream, pdl);
+    case 32: return deep ? launch_one<32, QT, EPI, true>(tw, tx, kp, grid, stream, pdl)
+                         : launch_one<32, QT, EPI, false>(tw, tx, kp, grid, stream, pdl);
+    case 64: return deep ? launch_one<64, QT, EPI, true>(tw, tx, kp, grid, stream, pdl)
+                         : launch_one<64, QT, EPI, false>(tw, tx, kp, grid, stream, pdl);
+    case 128: return launch_one<128, QT, EPI, false>(tw, tx, kp, grid, stream, pdl);
+    default: return launch_one<256, QT, EPI, false>(tw, tx, kp, grid, stream, pdl);
   }
 }
 
@@ -538,24 +560,35 @@ int q_tile_tokens(int T) { return T <= 32 ? 32 : (T <= 64 ? 64 : (T <= 128 ? 128
 
 int64_t nvfp4_act_scale_bytes(int64_t T, int64_t K) { return ((T + 255) / 256) * 2 * (K / 64) * kSfTileBytes; }
 
+template <typename Kern, typename... Args>
+cudaError_t launch_pdl(Kern kern, dim3 grid, cudaStream_t stream, bool pdl, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = dim3(256); cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 const char* quant_act_fp8(const __nv_bfloat16* x, int64_t ldx, int64_t T, int64_t K, uint8_t* codes, float* scale,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, bool pdl) {
   if (T <= 0) return nullptr;
   if (K % 8 || ldx % 8 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(codes) & 7))
     return "quant_act_fp8: K and the row stride must be multiples of 8, pointers aligned";
-  quant_act_fp8_kernel<<<static_cast<unsigned>(T), 256, 0, stream>>>(x, ldx, static_cast<int>(K), codes, scale);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_pdl(quant_act_fp8_kernel, dim3(static_cast<unsigned>(T)), stream, pdl, x,
+                             static_cast<long long>(ldx), static_cast<int>(K), codes, scale);
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 
 const char* quant_act_nvfp4(const __nv_bfloat16* x, int64_t ldx, int64_t T, int64_t K, uint8_t* codes, uint8_t* sf_plane,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, bool pdl) {
   if (T <= 0) return nullptr;
   if (K % 64 || ldx % 8 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(codes) & 7))
     return "quant_act_nvfp4: K must be a multiple of 64, the row stride of 8, pointers aligned";
   dim3 grid(static_cast<unsigned>(T), static_cast<unsigned>((K / 16 + 255) / 256));
-  quant_act_nvfp4_kernel<<<grid, 256, 0, stream>>>(x, ldx, static_cast<int>(K), codes, sf_plane);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_pdl(quant_act_nvfp4_kernel, grid, stream, pdl, x, static_cast<long long>(ldx),
+                             static_cast<int>(K), codes, sf_plane);
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 
@@ -582,7 +615,8 @@ const char* gemm_quant(const QGemmArgs& a) {
   splits = (kp.num_kb + kp.kb_per_split - 1) / kp.kb_per_split;
   // leader's idle stages hold (S-1) peer tiles of TN*512 bytes (+ TN*256 for the SwiGLU exchange)
   const int stage_bytes = kWTileBytes + tn * kKBytes + (bs ? (tn <= 128 ? 8 : 12) * kSfTileBytes : 0);
-  const int stages = tn <= 32 ? 8 : (tn == 64 ? 6 : (tn == 128 ? 5 : 3));
+  // (sized for the shallow pipeline: a split grid may or may not fit in one wave)
+  const int stages = tn <= 32 ? 4 : (tn == 64 ? 3 : (tn == 128 ? 5 : 3));
   while (splits > 1 && ((splits - 1) * tn * 512 + tn * 256 > stages * stage_bytes || splits > 8 ||
                         (kp.num_kb + splits - 1) / splits * (splits - 1) >= kp.num_kb))
     --splits;

@@ -39,8 +39,8 @@ int64_t nvfp4_act_scale_bytes(int64_t T, int64_t K);
 // Activation quantisers.  fp8: scale[t] = amax/448 (fp32), code = e4m3(x / scale).  nvfp4: per 16 values
 // scale = e4m3(amax/6), code = e2m1(x / scale), scales written in the 128x4 tile order.
 const char* quant_act_fp8(const __nv_bfloat16* x, int64_t ldx, int64_t T, int64_t K, uint8_t* codes, float* scale,
-                          cudaStream_t stream);
+                          cudaStream_t stream, bool pdl = false);
 const char* quant_act_nvfp4(const __nv_bfloat16* x, int64_t ldx, int64_t T, int64_t K, uint8_t* codes, uint8_t* sf_plane,
-                            cudaStream_t stream);
+                            cudaStream_t stream, bool pdl = false);
 
 }  // namespace nfb

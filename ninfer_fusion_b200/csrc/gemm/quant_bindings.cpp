@@ -18,23 +18,23 @@ inline void need(const Tensor& t, at::ScalarType dt, const char* name) {
   TORCH_CHECK(t.scalar_type() == dt, name, " has the wrong dtype");
 }
 
-void quant_act_fp8(const Tensor& x, const Tensor& codes, const Tensor& scale) {
+void quant_act_fp8(const Tensor& x, const Tensor& codes, const Tensor& scale, bool pdl) {
   need(x, at::kBFloat16, "x"); need(codes, at::kByte, "codes"); need(scale, at::kFloat, "scale");
   TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && codes.is_contiguous() && codes.numel() >= x.numel() &&
               scale.numel() >= x.size(0), "quant_act_fp8: shapes");
   c10::cuda::CUDAGuard guard(x.device());
   chk(nfb::quant_act_fp8(static_cast<const __nv_bfloat16*>(x.data_ptr()), x.stride(0), x.size(0), x.size(1),
-                         static_cast<uint8_t*>(codes.data_ptr()), static_cast<float*>(scale.data_ptr()), cur_stream()));
+                         static_cast<uint8_t*>(codes.data_ptr()), static_cast<float*>(scale.data_ptr()), cur_stream(), pdl));
 }
 
-void quant_act_nvfp4(const Tensor& x, const Tensor& codes, const Tensor& sf_plane) {
+void quant_act_nvfp4(const Tensor& x, const Tensor& codes, const Tensor& sf_plane, bool pdl) {
   need(x, at::kBFloat16, "x"); need(codes, at::kByte, "codes"); need(sf_plane, at::kByte, "sf_plane");
   TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && codes.is_contiguous() && codes.numel() >= x.numel() / 2 &&
               sf_plane.numel() >= nfb::nvfp4_act_scale_bytes(x.size(0), x.size(1)), "quant_act_nvfp4: shapes");
   c10::cuda::CUDAGuard guard(x.device());
   chk(nfb::quant_act_nvfp4(static_cast<const __nv_bfloat16*>(x.data_ptr()), x.stride(0), x.size(0), x.size(1),
                            static_cast<uint8_t*>(codes.data_ptr()), static_cast<uint8_t*>(sf_plane.data_ptr()),
-                           cur_stream()));
+                           cur_stream(), pdl));
 }
 
 // x_codes: [T, K] (fp8) or [T, K/2] (nvfp4) bytes; w_codes likewise with N rows.
@@ -78,8 +78,8 @@ int64_t nvfp4_act_scale_bytes(int64_t T, int64_t K) { return nfb::nvfp4_act_scal
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(nfb200, m) {
-  m.def("quant_act_fp8(Tensor x, Tensor codes, Tensor scale) -> ()", &quant_act_fp8);
-  m.def("quant_act_nvfp4(Tensor x, Tensor codes, Tensor sf_plane) -> ()", &quant_act_nvfp4);
+  m.def("quant_act_fp8(Tensor x, Tensor codes, Tensor scale, bool pdl=False) -> ()", &quant_act_fp8);
+  m.def("quant_act_nvfp4(Tensor x, Tensor codes, Tensor sf_plane, bool pdl=False) -> ()", &quant_act_nvfp4);
   m.def("gemm_quant(int qtype, Tensor x_codes, Tensor x_scale, Tensor w_codes, Tensor w_scale, float w_divisor, Tensor out, int epi, Tensor? resid, int splits, Tensor? status, bool pdl) -> ()", &gemm_quant);
   m.def("nvfp4_act_scale_bytes(int T, int K) -> int", &nvfp4_act_scale_bytes);
 }

@@ -8,6 +8,9 @@
 //   y = x * rsqrt(mean(x^2) + eps) * (unit_offset ? 1 + w : w)
 #include "pointwise.h"
 
+#include "../gemm/gemm_quant.h"
+#include "../kv/codec.cuh"
+
 #include "../common/ptx.cuh"
 
 namespace nfb {
@@ -157,7 +160,8 @@ __global__ void __launch_bounds__(kClThreads) add_rmsnorm_cluster_kernel(
     const float* __restrict__ partial, int splits, long long split_stride,
     const __nv_bfloat16* __restrict__ delta, const __nv_bfloat16* __restrict__ resid_in,
     __nv_bfloat16* __restrict__ resid_out, const __nv_bfloat16* __restrict__ norm_w,
-    __nv_bfloat16* __restrict__ normed, int N, float eps, int unit_offset) {
+    __nv_bfloat16* __restrict__ normed, int N, float eps, int unit_offset, uint8_t* __restrict__ q_codes,
+    uint8_t* __restrict__ q_sf) {
   __shared__ float red[kClThreads / 32];
   __shared__ float cta_ss;
   pdl_launch_next();
@@ -230,19 +234,42 @@ __global__ void __launch_bounds__(kClThreads) add_rmsnorm_cluster_kernel(
   }
   // nobody may exit (and release its shared memory) before all peers have read it
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-  if (normed == nullptr || !active) return;
+  if (normed == nullptr) return;
   const float inv = rsqrtf(tot / static_cast<float>(N) + eps);
-  const uint4 wv = *reinterpret_cast<const uint4*>(norm_w + c);
-  const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
-  uint4 o;
-  uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+  float nv[8];
+  float amax = 0.f;
+  if (active) {
+    const uint4 wv = *reinterpret_cast<const uint4*>(norm_w + c);
+    const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
+    uint4 o;
+    uint32_t* op = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    float w0 = __bfloat162float(wp[j].x), w1 = __bfloat162float(wp[j].y);
-    if (unit_offset) { w0 += 1.f; w1 += 1.f; }
-    op[j] = pack_bf16x2(v[2 * j] * inv * w0, v[2 * j + 1] * inv * w1);
+    for (int j = 0; j < 4; ++j) {
+      float w0 = __bfloat162float(wp[j].x), w1 = __bfloat162float(wp[j].y);
+      if (unit_offset) { w0 += 1.f; w1 += 1.f; }
+      op[j] = pack_bf16x2(v[2 * j] * inv * w0, v[2 * j + 1] * inv * w1);
+      const __nv_bfloat162 b2 = *reinterpret_cast<__nv_bfloat162*>(&op[j]);
+      nv[2 * j] = __bfloat162float(b2.x);
+      nv[2 * j + 1] = __bfloat162float(b2.y);
+      amax = fmaxf(amax, fmaxf(fabsf(nv[2 * j]), fabsf(nv[2 * j + 1])));
+    }
+    *reinterpret_cast<uint4*>(normed + row * N + c) = o;
   }
-  *reinterpret_cast<uint4*>(normed + row * N + c) = o;
+  if (q_codes == nullptr) return;
+  // nvfp4 copy of the normalised row for a block-scaled GEMM: two neighbouring threads share a 16-value block
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  if (!active) return;
+  const uint8_t sc = float_to_e4m3(amax / 6.f);
+  const float sf = e4m3_to_float(sc);
+  uint32_t packed = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) packed |= float_to_e2m1(sf > 0.f ? __fdiv_rn(nv[j], sf) : 0.f) << (4 * j);
+  *reinterpret_cast<uint32_t*>(q_codes + row * (N / 2) + c / 2) = packed;
+  if ((threadIdx.x & 1) == 0) {
+    const int g = c / 16;
+    const int t = static_cast<int>(row);
+    q_sf[(static_cast<long long>(t / 128) * (N / 64) + g / 4) * 512 + (t % 32) * 16 + ((t % 128) / 32) * 4 + (g % 4)] = sc;
+  }
 }
 
 template <typename K, typename... Args>
@@ -273,8 +300,10 @@ cudaError_t launch_pdl(K kern, dim3 grid, dim3 block, cudaStream_t stream, bool 
 
 const char* add_rmsnorm(const float* partial, int splits, const void* delta, const void* resid_in,
                         void* resid_out, const void* norm_w, void* normed, int T, int N, float eps,
-                        int unit_offset, cudaStream_t stream, bool pdl) {
+                        int unit_offset, cudaStream_t stream, bool pdl, uint8_t* q_codes, uint8_t* q_sf) {
   if (T <= 0) return nullptr;
+  if (q_codes != nullptr && (q_sf == nullptr || normed == nullptr || N % 64))
+    return "add_rmsnorm: the nvfp4 copy needs the scale plane, the bf16 output and N % 64 == 0";
   if (N % 8 || N > kThreads * kMaxVec * 8) return "add_rmsnorm: N must be a multiple of 8 and <= 8192";
   if (normed != nullptr && norm_w == nullptr) return "add_rmsnorm: normed output without weight";
   cudaError_t e;
@@ -284,14 +313,14 @@ const char* add_rmsnorm(const float* partial, int splits, const void* delta, con
   auto* ro = static_cast<__nv_bfloat16*>(resid_out);
   auto* w = static_cast<const __nv_bfloat16*>(norm_w);
   auto* no = static_cast<__nv_bfloat16*>(normed);
-  if (T <= 128 && N % (8 * kClusterRow) == 0 && N / kClusterRow <= kClThreads * 8) {
+  if (T <= 128 && N % (16 * kClusterRow) == 0 && N / kClusterRow <= kClThreads * 8) {
     const dim3 grid(T * kClusterRow);
     if (partial != nullptr && splits > 0)
       e = launch_cluster(add_rmsnorm_cluster_kernel<true>, grid, dim3(kClThreads), stream, pdl, partial, splits,
-                         stride, d, ri, ro, w, no, N, eps, unit_offset);
+                         stride, d, ri, ro, w, no, N, eps, unit_offset, q_codes, q_sf);
     else
       e = launch_cluster(add_rmsnorm_cluster_kernel<false>, grid, dim3(kClThreads), stream, pdl, partial, 0, stride,
-                         d, ri, ro, w, no, N, eps, unit_offset);
+                         d, ri, ro, w, no, N, eps, unit_offset, q_codes, q_sf);
     return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
   }
   if (partial != nullptr && splits > 0)
@@ -300,7 +329,9 @@ const char* add_rmsnorm(const float* partial, int splits, const void* delta, con
   else
     e = launch_pdl(add_rmsnorm_kernel<false>, dim3(T), dim3(kThreads), stream, pdl, partial, 0, stride, d,
                    ri, ro, w, no, N, eps, unit_offset);
-  return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+  if (e != cudaSuccess) return cudaGetErrorString(e);
+  if (q_codes != nullptr) return quant_act_nvfp4(no, N, T, N, q_codes, q_sf, stream, pdl);
+  return nullptr;
 }
 
 const char* embed_gather(const int* ids, const void* table, void* out, int T, int N, int vocab,

@@ -95,7 +95,7 @@ int64_t gemm_pick_splits(int64_t T, int64_t N, int64_t K, int64_t epi) {
 }
 
 void add_rmsnorm(OptT partial, int64_t splits, OptT delta, OptT resid_in, OptT resid_out, OptT norm_w, OptT normed,
-                 int64_t T, int64_t N, double eps, bool unit_offset, bool pdl) {
+                 int64_t T, int64_t N, double eps, bool unit_offset, bool pdl, OptT q_codes, OptT q_sf) {
   auto dev_of = [&]() -> const Tensor& {
     if (resid_in.has_value() && resid_in->defined()) return *resid_in;
     if (delta.has_value() && delta->defined()) return *delta;
@@ -117,10 +117,23 @@ void add_rmsnorm(OptT partial, int64_t splits, OptT delta, OptT resid_in, OptT r
     need(*norm_w, at::kBFloat16, "norm_w");
     TORCH_CHECK(norm_w->numel() == N, "add_rmsnorm: norm_w shape");
   }
+  if (q_codes.has_value() && q_codes->defined()) {
+    TORCH_CHECK(q_sf.has_value() && q_sf->defined(), "add_rmsnorm: q_codes without q_sf");
+    need(*q_codes, at::kByte, "q_codes"); need(*q_sf, at::kByte, "q_sf");
+    TORCH_CHECK(q_codes->is_contiguous() && q_codes->numel() >= T * N / 2, "add_rmsnorm: q_codes too small");
+    TORCH_CHECK(q_sf->numel() >= ((T + 255) / 256) * 2 * (N / 64) * 512, "add_rmsnorm: q_sf too small");
+  }
   chk(nfb::add_rmsnorm(ptr_or_null<float>(partial), static_cast<int>(splits), ptr_or_null<void>(delta),
                        ptr_or_null<void>(resid_in), ptr_or_null<void>(resid_out), ptr_or_null<void>(norm_w),
                        ptr_or_null<void>(normed), static_cast<int>(T), static_cast<int>(N), static_cast<float>(eps),
-                       unit_offset ? 1 : 0, cur_stream(), pdl));
+                       unit_offset ? 1 : 0, cur_stream(), pdl, ptr_or_null<uint8_t>(q_codes), ptr_or_null<uint8_t>(q_sf)));
+}
+
+Tensor gdn_prefill_trace(bool enable) {
+  Tensor t = at::zeros({5}, at::kLong);
+  c10::cuda::CUDAGuard guard(c10::Device(c10::kCUDA, at::cuda::current_device()));
+  nfb::gdn_prefill_trace(enable, reinterpret_cast<long long*>(t.data_ptr<int64_t>()));
+  return t;
 }
 
 void embed_gather(const Tensor& ids, const Tensor& table, const Tensor& out, bool pdl) {
@@ -577,7 +590,7 @@ TORCH_LIBRARY(nfb200, m) {
   m.def("gemm_bf16(Tensor x, Tensor w, Tensor? out, int epi, Tensor? resid, Tensor? bias, Tensor? partial, int splits, Tensor? status, bool pdl) -> ()", &gemm_bf16);
   m.def("gemm_trace(bool enable, int n_ctas) -> Tensor", &gemm_trace);
   m.def("gemm_pick_splits(int T, int N, int K, int epi) -> int", &gemm_pick_splits);
-  m.def("add_rmsnorm(Tensor? partial, int splits, Tensor? delta, Tensor? resid_in, Tensor? resid_out, Tensor? norm_w, Tensor? normed, int T, int N, float eps, bool unit_offset, bool pdl) -> ()", &add_rmsnorm);
+  m.def("add_rmsnorm(Tensor? partial, int splits, Tensor? delta, Tensor? resid_in, Tensor? resid_out, Tensor? norm_w, Tensor? normed, int T, int N, float eps, bool unit_offset, bool pdl, Tensor? q_codes=None, Tensor? q_sf=None) -> ()", &add_rmsnorm);
   m.def("embed_gather(Tensor ids, Tensor table, Tensor out, bool pdl) -> ()", &embed_gather);
   m.def("attn_prep(Tensor proj, int q_off, int k_off, int v_off, int n_q_heads, int n_kv_heads, int head_dim, Tensor? q_norm_w, Tensor? k_norm_w, float eps, bool unit_offset, int rot_dim, Tensor inv_freq, float attn_factor, Tensor rope_pos, Tensor token_seq, Tensor cache_pos, Tensor block_table, Tensor q_out, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, bool pdl) -> ()", &attn_prep);
   m.def("paged_attention(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, int split_keys, int n_splits, Tensor part_o, Tensor part_ml, Tensor? gate, Tensor out, Tensor? tree_mask, Tensor? tree_base, int impl, bool pdl) -> ()", &paged_attention);
@@ -585,6 +598,7 @@ TORCH_LIBRARY(nfb200, m) {
   m.def("prefill_attn_block_tokens(int n_q_heads, int n_kv_heads) -> int", &prefill_attn_block_tokens);
   m.def("causal_conv1d_silu(Tensor x, int c_off, int C, Tensor w, Tensor cu_seqlens, Tensor token_seq, Tensor state_slot, Tensor conv_state, Tensor out, bool update_state, bool one_token_per_seq, bool pdl, Tensor? seq_end=None, bool state_only=False) -> ()", &causal_conv1d_silu);
   m.def("gdn_recurrent(Tensor qkv, int q_off, int k_off, int v_off, Tensor proj, int z_off, int a_off, int b_off, int n_qk_heads, int n_v_heads, Tensor A_log, Tensor dt_bias, Tensor norm_w, float eps, Tensor cu_seqlens, Tensor state_slot, Tensor state, bool write_state, Tensor out, bool pdl, Tensor? seq_end=None) -> ()", &gdn_recurrent);
+  m.def("gdn_prefill_trace(bool enable) -> Tensor", &gdn_prefill_trace);
   m.def("argmax_rows(Tensor logits, Tensor out, bool pdl) -> ()", &argmax_rows);
   m.def("sample_rows(Tensor logits, Tensor? temperature, Tensor? top_k, Tensor? top_p, Tensor? min_p, Tensor? presence, Tensor? frequency, Tensor? token_counts, Tensor? seeds, Tensor? positions, int purpose, Tensor out, Tensor? out_prob) -> ()", &sample_rows);
   m.def("accept_greedy_chain(Tensor target_ids, Tensor draft_ids, Tensor n_accepted, Tensor out_tokens) -> ()", &accept_greedy_chain);

@@ -219,6 +219,8 @@ class HybridModel:
         self.cluster_splitk = True  # False: split-K through an fp32 workspace + reduce kernel
         self.attn_impl = 0  # 0 = pick, 1 = SIMT, 2 = tensor-core split-KV attention
         self.comm = None  # tensor-parallel communicator (parallel.tp), None on one GPU
+        self.act_nvfp4 = any(isinstance(t, QuantWeight) and t.qtype == 2 for t in weights.values())
+        self._prequant = None
         self._qbuf: Dict[int, tuple] = {}
         self._qkeep: List[tuple] = []
         self.moe = None   # models.moe.MoeBlock, created with the first workspace that runs a MoE layer
@@ -243,6 +245,18 @@ class HybridModel:
             self._qbuf[K] = cur
         return cur
 
+    def _add_rmsnorm(self, partial, splits, delta, resid_in, resid_out, norm_w, normed, T, N):
+        """resid_out = resid_in + delta + sum(partial); normed = rmsnorm(resid_out) * (1 + norm_w).  With nvfp4
+        weights the decode-sized kernel also emits the block-scaled copy of `normed` that the next GEMM consumes."""
+        eps = self.cfg.rms_eps
+        if self.act_nvfp4 and normed is not None and N % 256 == 0:
+            _, codes, _, plane = self._quant_scratch(T, N)
+            self.ops.add_rmsnorm(partial, splits, delta, resid_in, resid_out, norm_w, normed, T, N, eps, True, self.pdl,
+                                 codes[: T * N // 2], plane)
+            self._prequant = (normed.data_ptr(), T, N)
+            return
+        self.ops.add_rmsnorm(partial, splits, delta, resid_in, resid_out, norm_w, normed, T, N, eps, True, self.pdl)
+
     def _gemm_quant(self, x, w: QuantWeight, out, epi, resid):
         T, (N, K) = x.shape[0], w.shape
         _, codes, scale, plane = self._quant_scratch(T, K)
@@ -252,11 +266,13 @@ class HybridModel:
             splits = int(self.ops.gemm_pick_splits(T, N, kb_equiv, EPI_STORE if epi == EPI_SWIGLU else epi))
         if w.qtype == 2:
             xc = codes[: T * K // 2].view(T, K // 2)
-            self.ops.quant_act_nvfp4(x, xc, plane)
+            if self._prequant != (x.data_ptr(), T, K):
+                self.ops.quant_act_nvfp4(x, xc, plane, self.pdl)
+            self._prequant = None
             self.ops.gemm_quant(2, xc, plane, w.codes, w.scale, w.divisor, out, epi, resid, splits, self.status.tensor, self.pdl)
         else:
             xc = codes[: T * K].view(T, K)
-            self.ops.quant_act_fp8(x, xc, scale)
+            self.ops.quant_act_fp8(x, xc, scale, self.pdl)
             self.ops.gemm_quant(1, xc, scale, w.codes, w.scale, 1.0, out, epi, resid, splits, self.status.tensor, self.pdl)
 
     def _gemm(self, x, w, out, epi=EPI_STORE, resid=None):
@@ -279,15 +295,15 @@ class HybridModel:
         if self.cluster_splitk:
             # split-K inside a thread-block cluster (DSMEM reduction), residual add in the epilogue
             self._gemm(a, w, x, EPI_RESIDUAL, x)
-            ops.add_rmsnorm(None, 0, None, x, None, norm_w, normed_out, T, N, cfg.rms_eps, True, self.pdl)
+            self._add_rmsnorm(None, 0, None, x, None, norm_w, normed_out, T, N)
             return
         splits = int(ops.gemm_pick_splits(T, N, K, EPI_PARTIAL)) if T <= 256 else 1
         if splits > 1:
             ops.gemm_bf16(a, w, None, EPI_PARTIAL, None, None, ws.partial, splits, self.status.tensor, self.pdl)
-            ops.add_rmsnorm(ws.partial, splits, None, x, x, norm_w, normed_out, T, N, cfg.rms_eps, True, self.pdl)
+            self._add_rmsnorm(ws.partial, splits, None, x, x, norm_w, normed_out, T, N)
         else:
             ops.gemm_bf16(a, w, x, EPI_RESIDUAL, x, None, None, 1, self.status.tensor, self.pdl)
-            ops.add_rmsnorm(None, 0, None, x, None, norm_w, normed_out, T, N, cfg.rms_eps, True, self.pdl)
+            self._add_rmsnorm(None, 0, None, x, None, norm_w, normed_out, T, N)
 
     # ------------------------------------------------------------------ layers
     def _attn_layer(self, ws: Workspace, b: StepBatch, kv: PagedKvCache, layer: int, T: int, prefix: str,
@@ -383,14 +399,14 @@ class HybridModel:
         scratch = ws.mtp_scratch()
         e, a_n, e_n = scratch[0, :T], scratch[1, :T], scratch[2, :T]
         ops.embed_gather(next_ids, w[f"{self.prefix}/embed"], e, self.pdl)
-        ops.add_rmsnorm(None, 0, None, hidden_in, None, w["mtp/pre_fc_norm_hidden"], a_n, T, h, cfg.rms_eps, True, self.pdl)
-        ops.add_rmsnorm(None, 0, None, e, None, w["mtp/pre_fc_norm_embedding"], e_n, T, h, cfg.rms_eps, True, self.pdl)
+        self._add_rmsnorm(None, 0, None, hidden_in, None, w["mtp/pre_fc_norm_hidden"], a_n, T, h)
+        self._add_rmsnorm(None, 0, None, e, None, w["mtp/pre_fc_norm_embedding"], e_n, T, h)
         fc = w["mtp/fc"]  # [hidden, 2 * hidden]: columns [hidden state ; embedding]
         x = ws.x[:T]
         self._gemm(a_n, fc[:, :h], x)
         self._gemm(e_n, fc[:, h:], x, EPI_RESIDUAL, x)
         p = "mtp/layers/0"
-        ops.add_rmsnorm(None, 0, None, x, None, w[f"{p}/input_norm"], ws.normed[:T], T, h, cfg.rms_eps, True, self.pdl)
+        self._add_rmsnorm(None, 0, None, x, None, w[f"{p}/input_norm"], ws.normed[:T], T, h)
         mix, w_out = self._attn_layer(ws, b, kv_mtp, 0, T, p, 0)
         self._gemm_to_residual(ws, mix, w_out, T, w[f"{p}/post_norm"], ws.normed[:T])
         if cfg.moe is None:
@@ -412,7 +428,7 @@ class HybridModel:
         x = ws.x[:T]
         ops.embed_gather(b.ids, self.w[f"{self.prefix}/embed"], x, self.pdl)
         first = f"{self.prefix}/layers/0/input_norm"
-        ops.add_rmsnorm(None, 0, None, x, None, self.w[first], ws.normed[:T], T, cfg.hidden, cfg.rms_eps, True, self.pdl)
+        self._add_rmsnorm(None, 0, None, x, None, self.w[first], ws.normed[:T], T, cfg.hidden)
         for layer in range(cfg.n_layers):
             p = f"{self.prefix}/layers/{layer}"
             if cfg.is_full_attn(layer):

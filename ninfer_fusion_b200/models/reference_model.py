@@ -40,12 +40,14 @@ class ReferenceModel:
         self.cfg = cfg
         self.w = {k: v.detach().cpu() for k, v in weights.items()}
         self.prefix = prefix
+        # W8A8 / W4A4 engines quantise the GEMM inputs on the fly; set to ops.quant.fake_quant_* to mirror that
+        self.act_quant = lambda x: x
 
     # ---- pieces ----
     def _attn(self, seq: ReferenceSequence, ai: int, p: str, normed: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
         cfg = self.cfg
         T, D = normed.shape[0], cfg.head_dim
-        proj = R.bf16_round(_lin(normed, self.w[f"{p}/attn/in_proj"]))
+        proj = R.bf16_round(_lin(self.act_quant(normed), self.w[f"{p}/attn/in_proj"]))
         qd, kd = cfg.q_dim, cfg.kv_dim
         q = proj[:, :qd].reshape(T, cfg.n_q_heads, D)
         k = proj[:, qd:qd + kd].reshape(T, cfg.n_kv_heads, D)
@@ -68,7 +70,7 @@ class ReferenceModel:
     def _gdn(self, seq: ReferenceSequence, gi: int, p: str, normed: torch.Tensor) -> torch.Tensor:
         cfg = self.cfg
         T, d = normed.shape[0], cfg.gdn_head_dim
-        proj = R.bf16_round(_lin(normed, self.w[f"{p}/gdn/in_proj"]))
+        proj = R.bf16_round(_lin(self.act_quant(normed), self.w[f"{p}/gdn/in_proj"]))
         C, vd, hv = cfg.gdn_conv_dim, cfg.gdn_v_dim, cfg.gdn_v_heads
         conv, seq.conv[gi] = R.causal_conv1d_silu(proj[:, :C], self.w[f"{p}/gdn/conv_w"], seq.conv[gi])
         conv = R.bf16_round(conv)
@@ -87,10 +89,10 @@ class ReferenceModel:
     def _ffn(self, p: str, normed: torch.Tensor) -> torch.Tensor:
         cfg = self.cfg
         if cfg.moe is None:
-            gu = _lin(normed, self.w[f"{p}/mlp/gate_up"])
+            gu = _lin(self.act_quant(normed), self.w[f"{p}/mlp/gate_up"])
             i = gu.shape[1] // 2
             act = R.bf16_round(torch.nn.functional.silu(gu[:, :i]) * gu[:, i:])
-            return _lin(act, self.w[f"{p}/mlp/down"])
+            return _lin(self.act_quant(act), self.w[f"{p}/mlp/down"])
         m = cfg.moe
         router = R.bf16_round(_lin(normed, self.w[f"{p}/moe/router"]))  # logits are a bf16 op boundary
         wts, ids = R.moe_route(router[:, : m.n_experts], m.top_k, m.norm_topk)
@@ -122,7 +124,7 @@ class ReferenceModel:
             else:
                 mix = self._gdn(seq, cfg.gdn_layers.index(layer), p, normed)
                 w_out = self.w[f"{p}/gdn/out_proj"]
-            x = R.bf16_round(x + _lin(mix, w_out))
+            x = R.bf16_round(x + _lin(self.act_quant(mix), w_out))
             normed = R.bf16_round(R.rmsnorm(x, self.w[f"{p}/post_norm"], cfg.rms_eps, True))
             x = R.bf16_round(x + self._ffn(p, normed))
             if trace is not None:
@@ -134,7 +136,7 @@ class ReferenceModel:
         return hidden
 
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
-        return R.bf16_round(_lin(hidden, self.w[f"{self.prefix}/lm_head"]))
+        return R.bf16_round(_lin(self.act_quant(hidden), self.w[f"{self.prefix}/lm_head"]))
 
     def generate_greedy(self, prompt: torch.Tensor, n_new: int, kv_format: int = R.KV_BF16) -> List[int]:
         seq = ReferenceSequence(self.cfg, kv_format)

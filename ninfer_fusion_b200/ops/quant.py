@@ -111,3 +111,24 @@ def deinterleave_gate_up(w: torch.Tensor) -> torch.Tensor:
     two_i, K = w.shape
     t = w.reshape(two_i // 128, 2, 64, K)
     return torch.cat([t[:, 0].reshape(two_i // 2, K), t[:, 1].reshape(two_i // 2, K)], dim=0).contiguous()
+
+
+def fake_quant_nvfp4(x: torch.Tensor) -> torch.Tensor:
+    """Activation quantisation of the W4A4 path as a value map: per 16 values scale = e4m3(amax / 6), e2m1 codes."""
+    T, K = x.shape
+    g = bf16(x).reshape(T, K // 16, 16)
+    sf = (g.abs().amax(-1) / 6.0).clamp(max=448.0).to(torch.float8_e4m3fn).float()
+    safe = torch.where(sf > 0, sf, torch.ones_like(sf))
+    q = e2m1_values(e2m1_codes(torch.where(sf[..., None] > 0, g / safe[..., None], torch.zeros_like(g))))
+    return (q * sf[..., None]).reshape(T, K)
+
+
+def fake_quant_fp8(x: torch.Tensor) -> torch.Tensor:
+    """Activation quantisation of the W8A8 path as a value map: per token scale = amax / 448, e4m3 codes."""
+    xb = bf16(x)
+    scale = (xb.abs().amax(-1, keepdim=True) / 448.0).clamp(min=1e-12)
+    return (xb / scale).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).float() * scale
+
+
+def bf16(x: torch.Tensor) -> torch.Tensor:
+    return x.to(torch.bfloat16).float()

@@ -132,6 +132,40 @@ def bench_attn(ops, batch, ctx, kv, hq=24, hkv=4, D=256, P=64, iters=20, impl=0)
             "us": round(med * 1e6, 2), "GBps": round(byts / med / 1e9, 1), "frac_hbm": round(byts / med / bw, 3), "peaks": how}
 
 
+def bench_gdn_prefill(ops, batch, tokens, hk=16, hv=48, iters=10):
+    """conv1d + multi-token GDN recurrence over `tokens` tokens of `batch` sequences (the TTFT path)."""
+    d = 128
+    qk, vd = hk * d, hv * d
+    C = 2 * qk + vd
+    ld = C + vd + 2 * hv
+    T = batch * tokens
+    proj = (torch.randn(T, ld, device="cuda") * 0.5).to(torch.bfloat16)
+    conv_w = (torch.randn(C, 4, device="cuda") * 0.3).to(torch.bfloat16)
+    conv_state = torch.zeros((batch, 3, C), dtype=torch.bfloat16, device="cuda")
+    ssm = torch.zeros((batch, hv, d, d), device="cuda")
+    cu = (torch.arange(batch + 1, device="cuda") * tokens).to(torch.int32)
+    tseq = torch.arange(batch, device="cuda").repeat_interleave(tokens).to(torch.int32)
+    slot = torch.arange(batch, dtype=torch.int32, device="cuda")
+    conv_out = torch.empty((T, C), dtype=torch.bfloat16, device="cuda")
+    out = torch.empty((T, vd), dtype=torch.bfloat16, device="cuda")
+    A = torch.zeros(hv, device="cuda")
+    nw = torch.ones(d, dtype=torch.bfloat16, device="cuda")
+    res = {}
+    for name, fn in (("conv1d", lambda: ops.causal_conv1d_silu(proj, 0, C, conv_w, cu, tseq, slot, conv_state, conv_out, True, False, False)),
+                     ("gdn", lambda: ops.gdn_recurrent(conv_out, 0, qk, 2 * qk, proj, C, C + vd, C + vd + hv, hk, hv, A, A, nw, 1e-6,
+                                                       cu, slot, ssm, True, out, False))):
+        med, best = time_op(fn, iters=iters, flush=L2Flusher())
+        res[name + "_us"] = round(med * 1e6, 1)
+    ops.gdn_prefill_trace(True)
+    ops.gdn_recurrent(conv_out, 0, qk, 2 * qk, proj, C, C + vd, C + vd + hv, hk, hv, A, A, nw, 1e-6, cu, slot, ssm, True, out, False)
+    torch.cuda.synchronize()
+    ph = ops.gdn_prefill_trace(False).tolist()
+    res["phase_cycles(wait,prologue,serial,partial+barrier,epilogue)"] = ph
+    res.update({"op": "gdn_prefill(conv, recurrence)", "batch": batch, "tokens": tokens, "heads": hv,
+                "us_per_token": round(res["gdn_us"] / tokens, 4)})
+    return res
+
+
 def bench_gdn(ops, batch, hk=16, hv=48, iters=20):
     d = 128
     qk, vd = hk * d, hv * d
@@ -161,7 +195,7 @@ def bench_gdn(ops, batch, hk=16, hv=48, iters=20):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "decode27b", "prefill27b", "attn", "gdn", "all"])
+    ap.add_argument("what", choices=["gemm", "decode27b", "prefill27b", "attn", "gdn", "gdn_prefill", "all"])
     ap.add_argument("--T", type=int, default=32)
     ap.add_argument("--N", type=int, default=34816)
     ap.add_argument("--K", type=int, default=5120)
@@ -194,6 +228,9 @@ def main(argv=None):
                 rows.append(bench_attn(ops, a.batch, a.ctx, kv, iters=a.iters, impl=impl))
     if a.what in ("gdn", "all"):
         rows.append(bench_gdn(ops, a.batch, iters=a.iters))
+    if a.what == "gdn_prefill":
+        rows.append(bench_gdn_prefill(ops, a.batch, a.T, iters=a.iters))
+        rows.append(bench_gdn_prefill(ops, a.batch, a.T, hk=2, hv=6, iters=a.iters))
     for r in rows:
         print(json.dumps(r), flush=True)
 

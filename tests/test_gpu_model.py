@@ -91,14 +91,16 @@ def test_device_loop_matches_stepwise():
 @pytest.mark.parametrize("weight_format", ["fp8", "nvfp4"])
 def test_quantised_weights_logits_close_to_dequantised_oracle(weight_format):
     """fp8 / nvfp4 weights through the quantised tcgen05 GEMMs.  The oracle uses the de-quantised weights with
-    bf16 activations; the engine also quantises activations on the fly, so the logits agree in direction, not bit
-    for bit (the GEMM itself is checked exactly in test_gpu_gemm_quant.py)."""
+    the same on-the-fly activation quantisation as a value map (rounding-boundary flips of single codes keep the
+    agreement from being bit exact; the GEMM itself is checked exactly in test_gpu_gemm_quant.py)."""
     from ninfer_fusion_b200.models.weights import dequantize_weights
     cfg = TINY_DENSE
     w = random_weights(cfg, "cuda", seed=7, std=0.05, weight_format=weight_format)
     gen = Generator(cfg, w, "cuda", max_batch=4, max_context=512, kv_format="bf16", page_size=16, prefill_chunk=64,
                     use_graph=True)
+    from ninfer_fusion_b200.ops import quant as Q
     ref = ReferenceModel(cfg, {k: v.cpu() for k, v in dequantize_weights(w).items()})
+    ref.act_quant = Q.fake_quant_fp8 if weight_format == "fp8" else Q.fake_quant_nvfp4  # the engine quantises GEMM inputs too
     torch.manual_seed(1)
     prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (21, 40)]
     gen.prefill(prompts)
@@ -108,6 +110,6 @@ def test_quantised_weights_logits_close_to_dequantised_oracle(weight_format):
         h = ref.forward(ReferenceSequence(cfg, R.KV_BF16), torch.tensor(p))
         want = ref.logits(h[-1:])[0]
         cos.append(torch.nn.functional.cosine_similarity(got[b], want, dim=0).item())
-    assert min(cos) > (0.97 if weight_format == "fp8" else 0.85), cos
+    assert min(cos) > (0.99 if weight_format == "fp8" else 0.97), cos
     out = gen.generate(prompts, 6)   # decode path (graph) runs and reports no kernel error
     assert all(len(o) == 6 for o in out)

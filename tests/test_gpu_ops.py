@@ -145,10 +145,11 @@ def test_paged_attention_tree_mask(ops):
     assert (out.float().cpu() - ref).abs().max().item() < 0.02
 
 
-@pytest.mark.parametrize("lens", [[1, 1, 1], [5, 1, 17], [64, 3]])
-def test_conv_and_gdn_recurrent(ops, lens):
+@pytest.mark.parametrize("heads", [(2, 6), (4, 16), (8, 32), (16, 48)])  # row-split over 8 / 4 / 2 / 1 CTAs per head
+@pytest.mark.parametrize("lens", [[1, 1, 1], [5, 1, 17], [64, 3], [300, 40]])
+def test_conv_and_gdn_recurrent(ops, lens, heads):
     torch.manual_seed(2)
-    hk, hv, d = 2, 6, 128
+    (hk, hv), d = heads, 128
     qk, vd = hk * d, hv * d
     C = 2 * qk + vd
     ld = C + vd + 2 * hv
