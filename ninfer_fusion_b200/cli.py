@@ -1,0 +1,272 @@
+"""Command line front ends: `python -m ninfer_fusion_b200.cli {generate,serve,inspect,make-artifact,perplexity}`.
+
+One loader builds the engine for every front end: weights come from a `.ninfer` artifact (tensors are
+materialised onto the device, quantised formats are decoded or re-encoded for the tcgen05 quantised GEMMs) or
+are random-initialised for a registered geometry; the tokenizer comes from the artifact's embedded
+`tokenizer.json`, from a file, or is a small byte-level BPE when neither exists.
+
+Reference: apps/cli/main.cpp + options.cpp (usage block README.md:391-429), apps/serve/main.cpp,
+apps/perplexity (corpus scoring), src/serve/serve_options.cpp (docs/serving.md:658-705).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import sys
+import time
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .artifact.container import ArtifactReader, ArtifactWriter
+from .frontend.chat import BUILTIN_TEMPLATE, renderer_for
+from .frontend.tokenizer import Tokenizer
+from .models.config import ModelConfig, get_config
+from .models.weights import quantize_weights, random_weights, total_bytes
+from .runtime.engine import Engine, RequestOptions
+from .runtime.program import ReferenceProgram, SamplingParams
+
+DEFAULT_CORPUS = ("The quick brown fox jumps over the lazy dog. Hello world! def main(): return 0\n"
+                  "<|im_start|>user\nWhat is 2 + 2?<|im_end|>\n<|im_start|>assistant\n4<|im_end|>\n") * 8
+SPECIAL_TOKENS = ["<|endoftext|>", "<|im_start|>", "<|im_end|>", "<think>", "</think>", "<tool_call>", "</tool_call>",
+                  "<tool_response>", "</tool_response>", "<|vision_start|>", "<|vision_end|>", "<|image_pad|>", "<|video_pad|>"]
+
+
+def add_model_args(ap: argparse.ArgumentParser) -> None:
+    ap.add_argument("--artifact", help=".ninfer artifact (weights + embedded tokenizer / chat template)")
+    ap.add_argument("--model", default="tiny-dense", help="registered geometry for --random-init (see models/config.py)")
+    ap.add_argument("--random-init", action="store_true", help="random weights of --model instead of an artifact")
+    ap.add_argument("--layers", type=int, default=0, help="shrink the geometry to this many layers (debug)")
+    ap.add_argument("--tokenizer", help="tokenizer.json (overrides the artifact's embedded one)")
+    ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    ap.add_argument("--weights", default="bf16", choices=["bf16", "fp8", "nvfp4"], help="matmul weight format on the device")
+    ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8", "int8", "nvfp4"])
+    ap.add_argument("--kv-layer-spec", default="", help="per-layer KV storage, e.g. 'all:fp8' or '0-3:bf16,4-15:nvfp4'")
+    ap.add_argument("--max-context", type=int, default=4096)
+    ap.add_argument("--max-lanes", type=int, default=8, help="concurrent sequences")
+    ap.add_argument("--prefill-chunk", type=int, default=2048)
+    ap.add_argument("--page-size", type=int, default=64)
+    ap.add_argument("--no-graphs", action="store_true", help="eager decode instead of CUDA graphs")
+    ap.add_argument("--allow-unknown-template", action="store_true")
+    ap.add_argument("--seed", type=int, default=0)
+
+
+def load_model(args) -> Tuple[ModelConfig, Dict[str, object], Tokenizer, str]:
+    tok: Optional[Tokenizer] = None
+    template: Optional[str] = None
+    if args.artifact and not args.random_init:
+        with ArtifactReader(args.artifact) as rd:
+            model_id, weights_id = rd.identity
+            cfg = get_config(model_id)
+            weights = {name: rd.tensor(name) for name in rd.tensors()}
+            if "tokenizer.json" in rd.by_name:
+                tok = Tokenizer.from_json(rd.resource("tokenizer.json"))
+            if "chat_template.jinja" in rd.by_name:
+                template = rd.resource("chat_template.jinja").decode("utf-8")
+        weights = {k: (v.to(torch.bfloat16) if v.dtype == torch.float32 and not k.endswith(("A_log", "dt_bias")) else v)
+                   for k, v in weights.items()}
+        weights = {k: v.to(args.device) for k, v in weights.items()}
+        name = f"{model_id}:{weights_id}"
+    else:
+        cfg = get_config(args.model)
+        if args.layers:
+            cfg = cfg.shrink(args.layers)
+        weights = random_weights(cfg, args.device, seed=args.seed, std=0.05 if cfg.hidden <= 512 else 0.02)
+        name = f"{cfg.name}:random-init"
+    renderer_for(template, allow_unknown=args.allow_unknown_template)  # refuses an unknown template early
+    if args.weights != "bf16":
+        if args.device == "cpu":
+            raise SystemExit("--weights fp8/nvfp4 needs a GPU (the CPU program runs the fp32 oracle)")
+        weights = quantize_weights(weights, args.weights)
+    if args.tokenizer:
+        tok = Tokenizer.from_file(args.tokenizer)
+    if tok is None:
+        tok = Tokenizer.train_toy(DEFAULT_CORPUS, n_merges=min(200, max(0, cfg.vocab - 256 - len(SPECIAL_TOKENS))),
+                                  added_tokens=SPECIAL_TOKENS)
+    if tok.vocab_size > cfg.vocab:
+        raise SystemExit(f"tokenizer has {tok.vocab_size} ids but the model's vocabulary is {cfg.vocab}")
+    return cfg, weights, tok, name
+
+
+def build_engine(args, cfg: ModelConfig, weights) -> Engine:
+    kv = args.kv_dtype
+    if args.kv_layer_spec:
+        from .kv.policy import parse_layer_storage
+        kv = parse_layer_storage(args.kv_layer_spec, len(cfg.attn_layers))
+    if str(args.device).startswith("cuda"):
+        from .runtime.gpu_program import GpuProgram
+
+        def factory():
+            return GpuProgram(cfg, weights, args.device, max_lanes=args.max_lanes, max_context=args.max_context,
+                              kv_format=kv, page_size=args.page_size, prefill_chunk=args.prefill_chunk,
+                              use_graph=not args.no_graphs)
+    else:
+        def factory():
+            return ReferenceProgram(cfg, weights, max_lanes=args.max_lanes, max_context=args.max_context,
+                                    kv_format=kv if isinstance(kv, str) else "bf16")
+    return Engine(factory, prefill_chunk=args.prefill_chunk)
+
+
+# ---------------------------------------------------------------------------------------------------------
+def cmd_generate(args) -> int:
+    from .serve.service import GenerationService, GenRequest
+    cfg, weights, tok, name = load_model(args)
+    engine = build_engine(args, cfg, weights)
+    svc = GenerationService(engine, tok, name)
+    req = GenRequest(max_tokens=args.max_tokens, temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
+                     seed=args.seed, enable_thinking=not args.no_think, stop=args.stop or ())
+    if args.prompt_ids:
+        req.prompt_ids = [int(v) for v in args.prompt_ids.split(",")]
+    elif args.messages_json:
+        with open(args.messages_json, encoding="utf-8") as f:
+            req.messages = json.load(f)
+    elif args.raw:
+        req.prompt = args.prompt
+    else:
+        req.messages = ([{"role": "system", "content": args.system}] if args.system else []) + \
+                       [{"role": "user", "content": args.prompt}]
+    t0 = time.perf_counter()
+    result = None
+    for kind, item in svc.stream(req):
+        if kind == "delta":
+            if item.reasoning and args.show_thinking:
+                sys.stdout.write(item.reasoning)
+            if item.content:
+                sys.stdout.write(item.content)
+            sys.stdout.flush()
+        else:
+            result = item
+    sys.stdout.write("\n")
+    dt = time.perf_counter() - t0
+    stats = {"model": name, "prompt_tokens": result.prompt_tokens, "completion_tokens": result.completion_tokens,
+             "finish_reason": result.finish_reason, "ttft_ms": result.ttft_ms, "total_s": round(dt, 3),
+             "decode_tok_s": round((result.completion_tokens - 1) / max(1e-9, dt - (result.ttft_ms or 0) / 1e3), 2),
+             "weights_bytes": total_bytes(weights)}
+    print(json.dumps(stats), file=sys.stderr)
+    engine.shutdown()
+    return 0 if result.finish_reason != "error" else 1
+
+
+def cmd_serve(args) -> int:
+    from .serve.server import serve
+    from .serve.service import GenerationService
+    cfg, weights, tok, name = load_model(args)
+    engine = build_engine(args, cfg, weights)
+    svc = GenerationService(engine, tok, args.served_model_name or name, max_concurrent=args.max_concurrent,
+                            queue_timeout_s=args.queue_timeout)
+    httpd = serve(svc, args.host, args.port, args.api_key, args.request_log)
+    print(f"ninfer-serve: {name} on http://{args.host}:{httpd.server_address[1]}", file=sys.stderr, flush=True)
+    try:
+        httpd.serve_forever()
+    except KeyboardInterrupt:
+        pass
+    finally:
+        httpd.server_close()
+        engine.shutdown()
+    return 0
+
+
+def cmd_inspect(args) -> int:
+    with ArtifactReader(args.path) as rd:
+        print(json.dumps({"identity": {"model_id": rd.identity[0], "weights_id": rd.identity[1]},
+                          "objects": [{"name": o.name, "kind": o.kind, "shape": getattr(o, "shape", None),
+                                       "format": getattr(o, "format", None), "layout": getattr(o, "layout", None),
+                                       "bytes": o.bytes} for o in rd.objects]}, indent=1))
+    return 0
+
+
+def cmd_make_artifact(args) -> int:
+    """Random-init artifact of a registered geometry with an embedded tokenizer and chat template."""
+    cfg = get_config(args.model)
+    if args.layers:
+        cfg = cfg.shrink(args.layers)
+    weights = random_weights(cfg, "cpu", seed=args.seed, std=0.05 if cfg.hidden <= 512 else 0.02, with_mtp=args.with_mtp)
+    w = ArtifactWriter(f"{args.model}@{args.layers}" if args.layers else args.model, args.weights_id)
+    for name, t in weights.items():
+        leaf = name.rsplit("/", 1)[-1]
+        fmt = "FP32" if t.dtype == torch.float32 else "BF16"
+        if args.format != "BF16" and t.dim() == 2 and leaf in ("in_proj", "o_proj", "out_proj", "gate_up", "down", "lm_head"):
+            fmt = args.format
+        w.add_tensor(name, t, fmt)
+    tok = Tokenizer.from_file(args.tokenizer) if args.tokenizer else Tokenizer.train_toy(
+        DEFAULT_CORPUS, n_merges=min(200, max(0, cfg.vocab - 256 - len(SPECIAL_TOKENS))), added_tokens=SPECIAL_TOKENS)
+    w.add_resource("tokenizer.json", tok.to_json().encode("utf-8"))
+    w.add_resource("chat_template.jinja", BUILTIN_TEMPLATE.encode("utf-8"))
+    w.add_resource("generation_config.json", json.dumps({"eos_token": "<|im_end|>"}).encode("utf-8"))
+    w.write(args.out)
+    print(f"wrote {args.out}", file=sys.stderr)
+    return 0
+
+
+def cmd_perplexity(args) -> int:
+    """Corpus scoring on the oracle model: mean negative log-likelihood per token and its exponential."""
+    from .models.reference_model import ReferenceModel, ReferenceSequence
+    from .models.weights import dequantize_weights
+    args.device = "cpu"
+    cfg, weights, tok, name = load_model(args)
+    with open(args.corpus, encoding="utf-8") as f:
+        ids = tok.encode(f.read())[: args.max_tokens]
+    if len(ids) < 2:
+        raise SystemExit("corpus is too short")
+    ref = ReferenceModel(cfg, dequantize_weights(weights))
+    seq = ReferenceSequence(cfg)
+    hidden = ref.forward(seq, torch.tensor(ids[:-1]))
+    logp = torch.log_softmax(ref.logits(hidden).float(), dim=-1)
+    nll = -logp[torch.arange(len(ids) - 1), torch.tensor(ids[1:])].mean().item()
+    print(json.dumps({"model": name, "tokens": len(ids) - 1, "nll": round(nll, 5), "perplexity": round(math.exp(nll), 4)}))
+    return 0
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="ninfer", description=__doc__.split("\n")[0])
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("generate", help="one prompt -> text on stdout, stats JSON on stderr")
+    add_model_args(g)
+    g.add_argument("--prompt", default="Hello")
+    g.add_argument("--system", default="")
+    g.add_argument("--raw", action="store_true", help="feed --prompt as is, without the chat template")
+    g.add_argument("--prompt-ids", help="comma separated token ids")
+    g.add_argument("--messages-json", help="file with an OpenAI-style messages array")
+    g.add_argument("--max-tokens", type=int, default=64)
+    g.add_argument("--temperature", type=float, default=None)
+    g.add_argument("--top-p", type=float, default=None)
+    g.add_argument("--top-k", type=int, default=None)
+    g.add_argument("--stop", action="append")
+    g.add_argument("--no-think", action="store_true")
+    g.add_argument("--show-thinking", action="store_true")
+    g.set_defaults(fn=cmd_generate)
+    s = sub.add_parser("serve", help="OpenAI / Anthropic compatible HTTP server")
+    add_model_args(s)
+    s.add_argument("--host", default="127.0.0.1")
+    s.add_argument("--port", type=int, default=8080)
+    s.add_argument("--api-key", default=None)
+    s.add_argument("--served-model-name", default=None)
+    s.add_argument("--max-concurrent", type=int, default=64)
+    s.add_argument("--queue-timeout", type=float, default=30.0)
+    s.add_argument("--request-log", default=None, help="JSONL request log path")
+    s.set_defaults(fn=cmd_serve)
+    i = sub.add_parser("inspect", help="print an artifact's directory")
+    i.add_argument("path")
+    i.set_defaults(fn=cmd_inspect)
+    m = sub.add_parser("make-artifact", help="write a random-init artifact with embedded frontend resources")
+    m.add_argument("--model", default="tiny-dense")
+    m.add_argument("--layers", type=int, default=0)
+    m.add_argument("--weights-id", default="random-init-bf16")
+    m.add_argument("--format", default="BF16", help="matmul weight format, e.g. BF16, NVFP4, FP8_E4M3FN_ROW_BF16S, W8G32_F16S")
+    m.add_argument("--with-mtp", action="store_true")
+    m.add_argument("--tokenizer")
+    m.add_argument("--seed", type=int, default=0)
+    m.add_argument("--out", required=True)
+    m.set_defaults(fn=cmd_make_artifact)
+    p = sub.add_parser("perplexity", help="score a text corpus on the oracle model")
+    add_model_args(p)
+    p.add_argument("--corpus", required=True)
+    p.add_argument("--max-tokens", type=int, default=512)
+    p.set_defaults(fn=cmd_perplexity)
+    args = ap.parse_args(argv)
+    return args.fn(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

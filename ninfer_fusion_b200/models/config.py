@@ -137,6 +137,10 @@ REGISTRY["qwen3.8-27b"] = replace(QWEN36_27B, name="qwen3.8-27b")
 
 
 def get_config(name: str) -> ModelConfig:
+    """Registered geometry by name; `name@N` is the same geometry shrunk to N layers (debug artifacts)."""
+    if "@" in name:
+        base, _, n = name.partition("@")
+        return replace(get_config(base), n_layers=int(n), name=name)
     try:
         return REGISTRY[name]
     except KeyError:

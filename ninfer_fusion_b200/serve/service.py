@@ -1,0 +1,171 @@
+"""Generation service: owns the engine, the tokenizer and the chat frontend; protocol gateways talk to it.
+
+Counterpart of the reference's src/serve/generation_service.cpp (engine ownership, warm-up, request
+admission) plus the family frontend session (prompt preparation, stop handling, output parsing).
+"""
+from __future__ import annotations
+
+import threading
+import time
+import uuid
+from dataclasses import dataclass, field
+from typing import Callable, Dict, Iterator, List, Optional, Sequence
+
+from ..frontend.chat import OutputParser, ParsedDelta, ToolCall, render_chat
+from ..frontend.tokenizer import StreamDecoder, Tokenizer
+from ..runtime.engine import Engine, Event, RequestError, RequestOptions, ResourceError
+from ..runtime.program import SamplingParams
+
+# Sampling defaults per mode (docs/serving.md:711-716 of the reference): thinking / non-thinking.
+DEFAULT_SAMPLING = {
+    True: dict(temperature=1.0, top_p=0.95, top_k=20, presence_penalty=0.0),
+    False: dict(temperature=0.7, top_p=0.80, top_k=20, presence_penalty=1.5),
+}
+
+
+@dataclass
+class GenRequest:
+    messages: Optional[List[dict]] = None      # chat form
+    prompt: Optional[str] = None               # raw text form
+    prompt_ids: Optional[List[int]] = None     # pre-tokenised form
+    tools: Optional[List[dict]] = None
+    max_tokens: int = 512
+    temperature: Optional[float] = None
+    top_p: Optional[float] = None
+    top_k: Optional[int] = None
+    min_p: Optional[float] = None
+    presence_penalty: Optional[float] = None
+    frequency_penalty: Optional[float] = None
+    seed: Optional[int] = None
+    stop: Sequence[str] = ()
+    enable_thinking: bool = True
+    queue_timeout_s: Optional[float] = None
+    deadline_s: Optional[float] = None
+    session: Optional[str] = None
+
+
+@dataclass
+class GenResult:
+    request_id: str
+    content: str = ""
+    reasoning: str = ""
+    tool_calls: List[ToolCall] = field(default_factory=list)
+    finish_reason: str = "stop"       # stop | length | tool_calls | stop_sequence | cancelled | error | timeout
+    prompt_tokens: int = 0
+    completion_tokens: int = 0
+    ttft_ms: Optional[float] = None
+    total_s: float = 0.0
+    error: str = ""
+
+
+class GenerationService:
+    def __init__(self, engine: Engine, tokenizer: Tokenizer, model_id: str, max_concurrent: int = 64,
+                 queue_timeout_s: float = 30.0, eos_tokens: Sequence[str] = ("<|im_end|>", "<|endoftext|>")):
+        self.engine, self.tok, self.model_id = engine, tokenizer, model_id
+        self.queue_timeout_s = queue_timeout_s
+        self.eos_ids = [i for i in (tokenizer.token_id(t) for t in eos_tokens) if i is not None]
+        self._permits = threading.Semaphore(max_concurrent)
+        self.max_concurrent = max_concurrent
+        self.started = time.time()
+
+    # ------------------------------------------------------------------ prompt side
+    def prepare(self, req: GenRequest) -> List[int]:
+        if req.prompt_ids is not None:
+            return list(req.prompt_ids)
+        if req.messages is not None:
+            text = render_chat(req.messages, req.tools, add_generation_prompt=True, enable_thinking=req.enable_thinking)
+        elif req.prompt is not None:
+            text = req.prompt
+        else:
+            raise RequestError("request has neither messages nor prompt")
+        return self.tok.encode(text)
+
+    def count_tokens(self, req: GenRequest) -> int:
+        return len(self.prepare(req))
+
+    def _options(self, req: GenRequest) -> RequestOptions:
+        d = dict(DEFAULT_SAMPLING[bool(req.enable_thinking)])
+        for k in ("temperature", "top_p", "top_k", "min_p", "presence_penalty", "frequency_penalty", "seed"):
+            v = getattr(req, k)
+            if v is not None:
+                d[k] = v
+        sp = SamplingParams(temperature=float(d.get("temperature", 0.0)), top_k=int(d.get("top_k", 20)),
+                            top_p=float(d.get("top_p", 1.0)), min_p=float(d.get("min_p", 0.0)),
+                            presence_penalty=float(d.get("presence_penalty", 0.0)),
+                            frequency_penalty=float(d.get("frequency_penalty", 0.0)), seed=int(d.get("seed", 0)))
+        return RequestOptions(max_tokens=max(1, int(req.max_tokens)), sampling=sp, stop_token_ids=tuple(self.eos_ids),
+                              deadline_s=req.deadline_s,
+                              pending_timeout_s=req.queue_timeout_s if req.queue_timeout_s is not None else self.queue_timeout_s,
+                              session=req.session)
+
+    # ------------------------------------------------------------------ generation
+    def stream(self, req: GenRequest, on_start: Optional[Callable[[str, int], None]] = None,
+               cancelled: Optional[Callable[[], bool]] = None) -> Iterator[tuple]:
+        """Yields ("delta", ParsedDelta) items and finally ("done", GenResult)."""
+        rid = uuid.uuid4().hex[:24]
+        if not self._permits.acquire(blocking=False):
+            raise ResourceError("server_overloaded: too many requests in flight")
+        t0 = time.perf_counter()
+        res = GenResult(rid)
+        try:
+            ids = self.prepare(req)
+            res.prompt_tokens = len(ids)
+            if on_start is not None:
+                on_start(rid, len(ids))
+            handle = self.engine.submit(ids, self._options(req))
+            dec = StreamDecoder(self.tok, skip_special=True)
+            # a chat prompt with thinking enabled continues inside an open reasoning frame only if the template
+            # opened one; this template leaves the frame to the model, so parsing starts in content mode
+            parser = OutputParser(thinking=False, stop=req.stop)
+            eos = set(self.eos_ids)
+            while True:
+                try:
+                    ev: Event = handle.events.get(timeout=0.25)
+                except Exception:
+                    if cancelled is not None and cancelled():
+                        handle.cancel()
+                    continue
+                if ev.kind == "token":
+                    res.completion_tokens += 1
+                    if ev.token in eos:
+                        continue
+                    piece = dec.feed(ev.token)
+                    d = parser.feed(piece) if piece else ParsedDelta()
+                    if d.content or d.reasoning or d.tool_calls:
+                        yield ("delta", d)
+                    if parser.stopped:
+                        handle.cancel()
+                        res.finish_reason = "stop_sequence"
+                elif ev.kind in ("done", "error"):
+                    tail = parser.feed(dec.flush())
+                    end = parser.finish()
+                    tail.content += end.content
+                    tail.reasoning += end.reasoning
+                    if tail.content or tail.reasoning or tail.tool_calls:
+                        yield ("delta", tail)
+                    if ev.kind == "error":
+                        res.finish_reason, res.error = "error", ev.message
+                    elif res.finish_reason != "stop_sequence":
+                        res.finish_reason = ev.finish_reason or "stop"
+                    break
+            res.content, res.reasoning, res.tool_calls = parser.content, parser.reasoning, list(parser.tool_calls)
+            if res.tool_calls and res.finish_reason == "stop":
+                res.finish_reason = "tool_calls"
+            res.ttft_ms = handle.ttft_ms
+            res.total_s = time.perf_counter() - t0
+            yield ("done", res)
+        finally:
+            self._permits.release()
+
+    def generate(self, req: GenRequest) -> GenResult:
+        last = None
+        for kind, item in self.stream(req):
+            if kind == "done":
+                last = item
+        return last
+
+    def health(self) -> dict:
+        h = self.engine.health()
+        h.update({"model": self.model_id, "uptime_s": round(time.time() - self.started, 1),
+                  "stats": self.engine.stats.as_dict()})
+        return h

@@ -1,0 +1,120 @@
+"""Tokenizer (native BPE core vs Python twin), chat template, streaming output parser."""
+import json
+
+import pytest
+
+from ninfer_fusion_b200.frontend.chat import (BUILTIN_TEMPLATE, OutputParser, TemplateRefused, render_chat, renderer_for)
+from ninfer_fusion_b200.frontend.tokenizer import FRAME_CONTROL, FRAME_THINK, FRAME_TOOL, StreamDecoder, Tokenizer
+
+CORPUS = ("the quick brown fox jumps over the lazy dog. " * 30 + "hello world, hello tokens! 你好世界 naïve café 🙂 " * 10
+          + "def f(x):\n    return x + 1\n" * 10)
+SPECIALS = ["<|im_start|>", "<|im_end|>", "<think>", "</think>", "<tool_call>", "</tool_call>"]
+
+
+@pytest.fixture(scope="module")
+def tok():
+    return Tokenizer.train_toy(CORPUS, 300, SPECIALS)
+
+
+def test_roundtrip_and_specials(tok):
+    text = "<|im_start|>user\nhello world 你好 🙂 café\tx = f(3)<|im_end|>\n"
+    ids = tok.encode(text)
+    assert tok.decode(ids) == text
+    assert ids[0] == tok.token_id("<|im_start|>") and tok.token_id("<|im_end|>") in ids
+    assert len(ids) < len(text.encode("utf-8"))  # merges happened
+    assert tok.decode(ids, skip_special=True) == "user\nhello world 你好 🙂 café\tx = f(3)\n"
+    # special literals are plain text when not allowed
+    assert tok.token_id("<|im_start|>") not in tok.encode("<|im_start|>", allow_special=False)
+    assert tok.frame_class[tok.token_id("<think>")] == FRAME_THINK
+    assert tok.frame_class[tok.token_id("<tool_call>")] == FRAME_TOOL
+    assert tok.frame_class[tok.token_id("<|im_end|>")] == FRAME_CONTROL
+
+
+def test_native_merge_loop_equals_python(tok):
+    py = Tokenizer.from_json(tok.to_json(), use_native=False)
+    samples = [CORPUS[:500], "zzzz the thethe   quick\n\n\nbrown", "你好你好世界世界", "a" * 100, ""]
+    for s in samples:
+        assert tok.encode(s) == py.encode(s)
+    if tok._handle is None:
+        pytest.skip("native library not built")
+
+
+def test_json_roundtrip(tok):
+    t2 = Tokenizer.from_json(tok.to_json())
+    s = "the lazy dog says hello <think> hmm </think>"
+    assert t2.encode(s) == tok.encode(s) and t2.vocab_size == tok.vocab_size
+
+
+def test_stream_decoder_holds_back_split_characters(tok):
+    text = "héllo 🙂 世界!"
+    ids = tok.encode(text)
+    dec = StreamDecoder(tok)
+    out = ""
+    for i in ids:
+        piece = dec.feed(i)
+        assert "�" not in piece
+        out += piece
+    assert out + dec.flush() == text
+
+
+def test_chat_template():
+    msgs = [{"role": "system", "content": "Be brief."}, {"role": "user", "content": "Hi"},
+            {"role": "assistant", "content": "Hello!", "reasoning_content": "greet"}, {"role": "user", "content": [
+                {"type": "text", "text": "What is "}, {"type": "text", "text": "2+2?"}]}]
+    s = render_chat(msgs)
+    assert s == ("<|im_start|>system\nBe brief.<|im_end|>\n<|im_start|>user\nHi<|im_end|>\n"
+                 "<|im_start|>assistant\nHello!<|im_end|>\n<|im_start|>user\nWhat is 2+2?<|im_end|>\n<|im_start|>assistant\n")
+    assert render_chat(msgs, enable_thinking=False).endswith("<|im_start|>assistant\n<think>\n\n</think>\n\n")
+    # reasoning after the last user turn is kept, tool calls and tool results are framed
+    tools = [{"type": "function", "function": {"name": "add", "parameters": {"type": "object"}}}]
+    msgs2 = [{"role": "user", "content": "add 1 2"},
+             {"role": "assistant", "content": "", "reasoning_content": "call it",
+              "tool_calls": [{"type": "function", "function": {"name": "add", "arguments": "{\"a\": 1, \"b\": 2}"}}]},
+             {"role": "tool", "content": "3"}, {"role": "tool", "content": "ok"}]
+    s2 = render_chat(msgs2, tools=tools)
+    assert "# Tools" in s2 and json.dumps(tools[0]) in s2
+    assert "<think>\ncall it\n</think>\n\n<tool_call>\n{\"name\": \"add\", \"arguments\": {\"a\": 1, \"b\": 2}}\n</tool_call><|im_end|>" in s2
+    assert "<|im_start|>user\n<tool_response>\n3\n</tool_response>\n<tool_response>\nok\n</tool_response><|im_end|>" in s2
+    with pytest.raises(ValueError):
+        render_chat([{"role": "wizard", "content": "x"}])
+
+
+def test_template_identity():
+    assert renderer_for(BUILTIN_TEMPLATE) == "qwen3" and renderer_for(None) == "qwen3"
+    with pytest.raises(TemplateRefused):
+        renderer_for("{{ messages }}")
+    assert renderer_for("{{ messages }}", allow_unknown=True) == "qwen3"
+
+
+@pytest.mark.parametrize("chunk", [1, 2, 3, 7, 1000])
+def test_output_parser_streams_frames(chunk):
+    text = ("<think>\nlet me think</think>\n\nThe answer is 4.\n<tool_call>\n{\"name\": \"add\", \"arguments\": {\"a\": 1}}\n"
+            "</tool_call> done < not a tag")
+    p = OutputParser()
+    reasoning = content = ""
+    calls = []
+    for i in range(0, len(text), chunk):
+        d = p.feed(text[i:i + chunk])
+        reasoning += d.reasoning
+        content += d.content
+        calls += d.tool_calls
+        assert "<thi" not in d.content and "<tool" not in d.content
+    end = p.finish()
+    content += end.content
+    assert reasoning == "\nlet me think"
+    assert content == "The answer is 4.\n done < not a tag"
+    assert len(calls) == 1 and calls[0].name == "add" and json.loads(calls[0].arguments) == {"a": 1}
+    assert p.content == content and p.reasoning == reasoning
+
+
+def test_output_parser_stop_strings_and_unterminated_tool():
+    p = OutputParser(stop=["STOP"])
+    d = p.feed("hello ST")
+    assert d.content == "hello "
+    d = p.feed("OP trailing")
+    assert p.stopped and d.content == "" and p.content == "hello "
+    q = OutputParser()
+    q.feed("x <tool_call>{\"name\": ")
+    assert q.finish().content == "<tool_call>{\"name\": "
+    r = OutputParser(thinking=True)
+    assert r.feed("deep thought</think>answer").reasoning == "deep thought" and r.content == "answer"

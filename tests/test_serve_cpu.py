@@ -1,0 +1,196 @@
+"""`ninfer-serve` over the CPU oracle program: OpenAI chat / responses, Anthropic messages, SSE, auth, logs, CLI."""
+import http.client
+import json
+import os
+import threading
+
+import pytest
+import torch
+
+from ninfer_fusion_b200 import cli
+from ninfer_fusion_b200.frontend.tokenizer import Tokenizer
+from ninfer_fusion_b200.models.config import TINY_DENSE
+from ninfer_fusion_b200.models.weights import random_weights
+from ninfer_fusion_b200.runtime.engine import Engine
+from ninfer_fusion_b200.runtime.program import ReferenceProgram
+from ninfer_fusion_b200.serve.server import serve
+from ninfer_fusion_b200.serve.service import GenerationService, GenRequest
+
+
+@pytest.fixture(scope="module")
+def server(tmp_path_factory):
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cpu", seed=3, std=0.05)
+    tok = Tokenizer.train_toy(cli.DEFAULT_CORPUS, 200, cli.SPECIAL_TOKENS)
+    engine = Engine(lambda: ReferenceProgram(cfg, w, max_lanes=4, max_context=512), prefill_chunk=64)
+    svc = GenerationService(engine, tok, "tiny-dense:test", max_concurrent=4, queue_timeout_s=20.0)
+    log = str(tmp_path_factory.mktemp("log") / "requests.jsonl")
+    httpd = serve(svc, "127.0.0.1", 0, api_key="sekret", log_path=log)
+    t = threading.Thread(target=httpd.serve_forever, daemon=True)
+    t.start()
+    yield httpd.server_address[1], svc, log
+    httpd.shutdown()
+    httpd.server_close()
+    engine.shutdown()
+
+
+def call(port, method, path, body=None, key="sekret", header="Authorization"):
+    c = http.client.HTTPConnection("127.0.0.1", port, timeout=60)
+    headers = {"Content-Type": "application/json"}
+    if key:
+        headers[header] = f"Bearer {key}" if header == "Authorization" else key
+    c.request(method, path, json.dumps(body) if body is not None else None, headers)
+    r = c.getresponse()
+    data = r.read()
+    c.close()
+    return r.status, r.getheader("Content-Type", ""), data
+
+
+def sse_events(data: bytes):
+    out = []
+    for block in data.decode("utf-8").split("\n\n"):
+        ev, payload = None, None
+        for line in block.split("\n"):
+            if line.startswith("event: "):
+                ev = line[7:]
+            elif line.startswith("data: "):
+                payload = line[6:]
+        if payload is not None:
+            out.append((ev, payload if payload == "[DONE]" else json.loads(payload)))
+    return out
+
+
+def test_health_models_auth(server):
+    port, svc, _ = server
+    st, _, data = call(port, "GET", "/health", key=None)
+    assert st == 200 and json.loads(data)["status"] == "ok"
+    assert call(port, "GET", "/v1/models", key=None)[0] == 401
+    assert call(port, "GET", "/v1/models", key="wrong")[0] == 401
+    st, _, data = call(port, "GET", "/v1/models", key="sekret", header="x-api-key")
+    assert st == 200 and json.loads(data)["data"][0]["id"] == "tiny-dense:test"
+    assert call(port, "GET", "/v1/models/tiny-dense:test")[0] == 200
+    assert call(port, "GET", "/v1/models/other")[0] == 404
+    assert call(port, "GET", "/nope")[0] == 404
+
+
+def test_openai_chat_blocking_and_streaming_agree(server):
+    port, svc, _ = server
+    body = {"model": "x", "messages": [{"role": "user", "content": "Hello there"}], "max_tokens": 12, "temperature": 0}
+    st, ct, data = call(port, "POST", "/v1/chat/completions", body)
+    assert st == 200 and ct.startswith("application/json")
+    obj = json.loads(data)
+    assert obj["object"] == "chat.completion" and obj["choices"][0]["finish_reason"] in ("stop", "length")
+    assert obj["usage"]["completion_tokens"] <= 12 and obj["usage"]["prompt_tokens"] > 3
+    text = obj["choices"][0]["message"]["content"] or ""
+    st, ct, data = call(port, "POST", "/v1/chat/completions", dict(body, stream=True, stream_options={"include_usage": True}))
+    assert st == 200 and ct.startswith("text/event-stream")
+    evs = sse_events(data)
+    assert evs[-1][1] == "[DONE]"
+    chunks = [e for _, e in evs[:-1]]
+    assert chunks[0]["choices"][0]["delta"]["role"] == "assistant"
+    streamed = "".join(c["choices"][0]["delta"].get("content", "") for c in chunks if c["choices"])
+    assert streamed == text  # greedy: same tokens
+    assert any(c.get("usage") for c in chunks)
+    assert [c for c in chunks if c["choices"] and c["choices"][0]["finish_reason"]]
+
+
+def test_openai_chat_rejects_bad_requests(server):
+    port, _, _ = server
+    assert call(port, "POST", "/v1/chat/completions", {"messages": []})[0] == 400
+    assert call(port, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}], "n": 2})[0] == 400
+    st, _, data = call(port, "POST", "/v1/chat/completions",
+                       {"messages": [{"role": "user", "content": "x"}], "response_format": {"type": "json_schema"}})
+    assert st == 400 and json.loads(data)["error"]["code"] == "unsupported_parameter"
+    st, _, data = call(port, "POST", "/v1/chat/completions",
+                       {"messages": [{"role": "user", "content": "x"}], "max_tokens": 100000})
+    assert st == 400 and "context window" in json.loads(data)["error"]["message"]
+    c = http.client.HTTPConnection("127.0.0.1", port, timeout=10)
+    c.request("POST", "/v1/chat/completions", "{not json", {"Authorization": "Bearer sekret", "Content-Type": "application/json"})
+    assert c.getresponse().status == 400
+
+
+def test_openai_responses_store_and_continuation(server):
+    port, _, _ = server
+    st, _, data = call(port, "POST", "/v1/responses", {"input": "Say hi", "max_output_tokens": 8, "temperature": 0})
+    assert st == 200
+    obj = json.loads(data)
+    assert obj["object"] == "response" and obj["status"] in ("completed", "incomplete")
+    assert obj["usage"]["output_tokens"] <= 8 and obj["output"][-1]["type"] in ("message", "function_call")
+    rid = obj["id"]
+    st, _, data = call(port, "GET", f"/v1/responses/{rid}")
+    assert st == 200 and json.loads(data)["id"] == rid
+    st, _, data = call(port, "GET", f"/v1/responses/{rid}/input_items")
+    assert st == 200 and json.loads(data)["data"][0]["content"] == "Say hi"
+    st, _, data = call(port, "POST", "/v1/responses", {"input": "And again", "previous_response_id": rid,
+                                                       "max_output_tokens": 4, "temperature": 0, "stream": True})
+    evs = sse_events(data)
+    names = [e for e, _ in evs]
+    assert names[0] == "response.created" and names[-1] in ("response.completed", "response.incomplete")
+    st, _, data = call(port, "POST", "/v1/responses/input_tokens", {"input": "count me"})
+    assert st == 200 and json.loads(data)["input_tokens"] > 2
+    st, _, data = call(port, "POST", "/v1/responses/compact", {"input": [{"type": "message", "role": "user", "content": "a " * 50},
+                                                                        {"type": "message", "role": "user", "content": "b"}],
+                                                              "max_input_tokens": 12})
+    assert st == 200 and json.loads(data)["output"][-1]["content"] == "b" and len(json.loads(data)["output"]) == 1
+    assert call(port, "DELETE", f"/v1/responses/{rid}")[0] == 200
+    assert call(port, "GET", f"/v1/responses/{rid}")[0] == 404
+    assert call(port, "POST", "/v1/responses", {"input": "x", "previous_response_id": "resp_missing"})[0] == 404
+
+
+def test_anthropic_messages(server):
+    port, _, _ = server
+    body = {"model": "x", "max_tokens": 10, "temperature": 0, "system": "Be brief.",
+            "messages": [{"role": "user", "content": [{"type": "text", "text": "Hello"}]}]}
+    st, _, data = call(port, "POST", "/v1/messages", body, header="x-api-key")
+    assert st == 200
+    obj = json.loads(data)
+    assert obj["type"] == "message" and obj["role"] == "assistant" and obj["stop_reason"] in ("end_turn", "max_tokens")
+    assert obj["usage"]["output_tokens"] <= 10 and obj["content"][-1]["type"] == "text"
+    st, ct, data = call(port, "POST", "/v1/messages", dict(body, stream=True), header="x-api-key")
+    names = [e for e, _ in sse_events(data)]
+    assert names[0] == "message_start" and names[-1] == "message_stop" and "message_delta" in names
+    st, _, data = call(port, "POST", "/v1/messages/count_tokens", {"messages": body["messages"]}, header="x-api-key")
+    assert st == 200 and json.loads(data)["input_tokens"] > 2
+    st, _, data = call(port, "POST", "/v1/messages", {"messages": body["messages"]}, header="x-api-key")
+    assert st == 400 and json.loads(data)["type"] == "error"
+
+
+def test_request_log_lines(server):
+    port, _, log = server
+    call(port, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "log me"}], "max_tokens": 3})
+    recs = [json.loads(line) for line in open(log, encoding="utf-8")]
+    kinds = {r["event"] for r in recs}
+    assert {"server_start", "request_start", "request_done"} <= kinds and "request_rejected" in kinds
+    done = [r for r in recs if r["event"] == "request_done"][-1]
+    assert done["schema"] == 1 and done["completion_tokens"] <= 3 and done["api"] == "openai_chat"
+
+
+def test_overload_is_429(server):
+    port, svc, _ = server
+    held = [svc._permits.acquire(blocking=False) for _ in range(svc.max_concurrent)]
+    try:
+        st, _, data = call(port, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}]})
+        assert st == 429 and json.loads(data)["error"]["code"] == "server_overloaded"
+    finally:
+        for h in held:
+            if h:
+                svc._permits.release()
+
+
+def test_cli_artifact_roundtrip(tmp_path, capsys):
+    art = str(tmp_path / "tiny.ninfer")
+    assert cli.main(["make-artifact", "--model", "tiny-dense", "--out", art]) == 0
+    assert cli.main(["inspect", art]) == 0
+    listing = json.loads(capsys.readouterr().out)
+    names = {o["name"] for o in listing["objects"]}
+    assert {"tokenizer.json", "chat_template.jinja", "text/embed"} <= names
+    assert cli.main(["generate", "--artifact", art, "--device", "cpu", "--prompt", "Hello", "--max-tokens", "5",
+                     "--temperature", "0"]) == 0
+    out = capsys.readouterr()
+    stats = json.loads(out.err.strip().splitlines()[-1])
+    assert stats["completion_tokens"] <= 5 and stats["model"].startswith("tiny-dense")
+    corpus = tmp_path / "c.txt"
+    corpus.write_text("the quick brown fox jumps over the lazy dog " * 4)
+    assert cli.main(["perplexity", "--artifact", art, "--corpus", str(corpus), "--max-tokens", "40"]) == 0
+    ppl = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert ppl["perplexity"] > 1.0
