@@ -1,0 +1,70 @@
+"""Engine + lane-based GPU program: concurrent requests, graph decode, sampling determinism, the text service."""
+import pytest
+import torch
+
+from ninfer_fusion_b200 import cli
+from ninfer_fusion_b200.frontend.tokenizer import Tokenizer
+from ninfer_fusion_b200.models.config import TINY_DENSE
+from ninfer_fusion_b200.models.reference_model import ReferenceModel, ReferenceSequence
+from ninfer_fusion_b200.models.weights import random_weights
+from ninfer_fusion_b200.ops import reference as R
+from ninfer_fusion_b200.runtime.engine import Engine, RequestOptions
+from ninfer_fusion_b200.runtime.gpu_program import GpuProgram
+from ninfer_fusion_b200.runtime.program import SamplingParams
+from ninfer_fusion_b200.serve.service import GenerationService, GenRequest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def setup():
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cuda", seed=7, std=0.05)
+    engine = Engine(lambda: GpuProgram(cfg, w, "cuda", max_lanes=4, max_context=512, kv_format="fp8", page_size=16,
+                                       prefill_chunk=64, use_graph=True), prefill_chunk=64)
+    yield cfg, w, engine
+    engine.shutdown()
+
+
+def test_concurrent_greedy_requests_match_the_oracle(setup):
+    cfg, w, engine = setup
+    torch.manual_seed(4)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (9, 70, 33, 130, 5)]   # more requests than lanes
+    handles = [engine.submit(p, RequestOptions(max_tokens=10)) for p in prompts]
+    outs = [h.wait(timeout=120) for h in handles]
+    assert all(h.finish_reason == "length" and len(o) == 10 for h, o in zip(handles, outs))
+    ref = ReferenceModel(cfg, {k: v.cpu() for k, v in w.items()})
+    agree = total = 0
+    for p, out in zip(prompts, outs):
+        seq = ReferenceSequence(cfg, R.KV_FP8_ROW)
+        hid = ref.forward(seq, torch.tensor(p))
+        for tok in out:
+            lg = ref.logits(hid[-1:])[0]
+            top2 = lg.topk(2).values
+            if (top2[0] - top2[1]).item() > 0.05:
+                total += 1
+                agree += int(int(R.argmax_lowest(lg[None])[0]) == tok)
+            hid = ref.forward(seq, torch.tensor([tok]))
+    assert total > 20 and agree / total >= 0.9, f"{agree}/{total}"
+    st = engine.stats.as_dict()
+    assert st["requests_done"] >= 5 and st["completion_tokens"] >= 50
+
+
+def test_sampling_is_reproducible_per_seed(setup):
+    cfg, _, engine = setup
+    prompt = list(range(3, 40))
+    sp = SamplingParams(temperature=1.0, top_k=20, top_p=0.95, seed=1234)
+    a = engine.generate(prompt, RequestOptions(max_tokens=12, sampling=sp))
+    b = engine.generate(prompt, RequestOptions(max_tokens=12, sampling=sp))
+    c = engine.generate(prompt, RequestOptions(max_tokens=12, sampling=SamplingParams(temperature=1.0, top_k=20, top_p=0.95, seed=99)))
+    assert a == b and len(a) == 12
+    assert a != c  # a different seed walks a different path (top-20 over a near-flat random-init distribution)
+
+
+def test_text_service_on_gpu(setup):
+    cfg, _, engine = setup
+    tok = Tokenizer.train_toy(cli.DEFAULT_CORPUS, 200, cli.SPECIAL_TOKENS)
+    svc = GenerationService(engine, tok, "tiny-dense:gpu")
+    res = svc.generate(GenRequest(messages=[{"role": "user", "content": "Hello world"}], max_tokens=8, temperature=0.0))
+    assert res.finish_reason in ("stop", "length", "tool_calls") and res.completion_tokens <= 8 and res.prompt_tokens > 4
+    assert isinstance(res.content, str)
