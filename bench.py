@@ -110,7 +110,7 @@ def main() -> int:
     ap.add_argument("--no-ttft", action="store_true")
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--weights", default="bf16", choices=["bf16", "fp8", "nvfp4"],
-                    help="matmul weight format (fp8 = e4m3 row-scale W8A8, nvfp4 = e2m1 block-scaled W4A4); one GPU only")
+                    help="matmul weight format (fp8 = e4m3 row-scale W8A8, nvfp4 = e2m1 block-scaled W4A4)")
     ap.add_argument("--parallel", default="", choices=["", "tp", "ep"],
                     help="multi-GPU plan: tp = tensor parallel (dense default), ep = data parallel + expert parallel (MoE default)")
     args = ap.parse_args()
@@ -158,10 +158,13 @@ def main() -> int:
         comm = TensorParallel(cfg, rank, world, device, max_tokens=max(args.batch, 2048))
         shard = comm.geometry
         weights = comm.random_shard_weights(seed=0)
+        if args.weights != "bf16":
+            from ninfer_fusion_b200.models.weights import quantize_weights
+            weights = quantize_weights(weights, args.weights)  # every rank quantises its own shard
     else:
         weights = random_weights(cfg, device, seed=0, weight_format=args.weights)
-    if args.weights != "bf16" and world > 1:
-        print("bench.py: quantised weights run on one GPU only", file=sys.stderr)
+    if args.weights != "bf16" and ep:
+        print("bench.py: quantised weights are not wired for the expert-parallel plan", file=sys.stderr)
         return 2
 
     B, L, K, W = args.batch, args.prompt_len, args.steps, args.warmup

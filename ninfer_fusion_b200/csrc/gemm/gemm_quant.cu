@@ -100,6 +100,11 @@ struct QParams {
   const __nv_bfloat16* resid;
   long long ldr;
   int* status;
+  // tensor-parallel epilogues (see gemm.h: kEpiPushPartial, kEpiPushAll)
+  float* peer_recv[kMaxRanks];
+  unsigned int* peer_flag[kMaxRanks];
+  int rank, world, slice_cols, T_cap;
+  const unsigned int* call_idx;
 };
 
 template <int TN, int QT, int EPI, bool DEEP>
@@ -337,6 +342,43 @@ __global__ void __launch_bounds__(128) gemm_q_kernel(const __grid_constant__ CUt
           }
         }
       }
+    } else if constexpr (EPI == kEpiPushAll || EPI == kEpiPushPartial) {
+      // the scaled fp32 tile goes to peer memory: to EVERY rank's [parity][src][T_cap][N] buffer (one-shot
+      // all-reduce) or to the OWNER of this column slice [src][T][N/world] (reduce-scatter)
+      for (int c = 0; c < TN; c += kChunk) {
+        if (t0 + c >= p.T) break;
+        float v[kChunk];
+        load_acc(c, v);
+        if constexpr (EPI == kEpiPushAll) {
+          const unsigned int par = *p.call_idx & 1u;
+          const long long base = ((static_cast<long long>(par) * p.world + p.rank) * p.T_cap) * p.N + n;
+          for (int r = 0; r < p.world; ++r) {
+            float* dst = p.peer_recv[r] + base;
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) {
+              const int t = t0 + c + j;
+              if (t < p.T && n < p.N) dst[static_cast<long long>(t) * p.N] = v[j];
+            }
+          }
+        } else {
+          const int owner = n0 / p.slice_cols;
+          float* dst = p.peer_recv[owner] + static_cast<long long>(p.rank) * p.T * p.slice_cols + (n - owner * p.slice_cols);
+#pragma unroll
+          for (int j = 0; j < kChunk; ++j) {
+            const int t = t0 + c + j;
+            if (t < p.T && n < p.N) dst[static_cast<long long>(t) * p.slice_cols] = v[j];
+          }
+        }
+      }
+      __threadfence_system();
+      __syncthreads();
+      if constexpr (EPI == kEpiPushAll) {
+        if (threadIdx.x < p.world)
+          asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.peer_flag[threadIdx.x]) : "memory");
+      } else {
+        if (threadIdx.x == 0)
+          asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.peer_flag[n0 / p.slice_cols]) : "memory");
+      }
     } else {
       for (int c = 0; c < TN; c += kChunk) {
         if (t0 + c >= p.T) break;
@@ -524,6 +566,8 @@ cudaError_t launch_epi(int epi, int tn, const CUtensorMap& tw, const CUtensorMap
   switch (epi) {
     case kEpiResidual: return launch_tn<QT, kEpiResidual>(tn, tw, tx, kp, grid, stream, pdl);
     case kEpiSwiglu: return launch_tn<QT, kEpiSwiglu>(tn, tw, tx, kp, grid, stream, pdl);
+    case kEpiPushAll: return launch_tn<QT, kEpiPushAll>(tn, tw, tx, kp, grid, stream, pdl);
+    case kEpiPushPartial: return launch_tn<QT, kEpiPushPartial>(tn, tw, tx, kp, grid, stream, pdl);
     default: return launch_tn<QT, kEpiStore>(tn, tw, tx, kp, grid, stream, pdl);
   }
 }
@@ -596,12 +640,13 @@ const char* gemm_quant(const QGemmArgs& a) {
   if (a.T <= 0 || a.N <= 0 || a.K <= 0) return "gemm_quant: empty problem";
   const bool bs = a.qtype == kQNvfp4;
   if (a.qtype != kQFp8Row && !bs) return "gemm_quant: unknown weight format";
-  if (a.epi != kEpiStore && a.epi != kEpiResidual && a.epi != kEpiSwiglu) return "gemm_quant: unsupported epilogue";
+  const bool push = a.epi == kEpiPushAll || a.epi == kEpiPushPartial;
+  if (a.epi != kEpiStore && a.epi != kEpiResidual && a.epi != kEpiSwiglu && !push) return "gemm_quant: unsupported epilogue";
   const int64_t k_bytes = bs ? a.K / 2 : a.K;
   if (bs ? (a.K % 256) : (a.K % 16)) return "gemm_quant: K must be a multiple of 256 (nvfp4) / 16 (fp8)";
   if ((a.ldw % 16) || (a.ldx % 16) || ((reinterpret_cast<uintptr_t>(a.w) | reinterpret_cast<uintptr_t>(a.x)) & 15))
     return "gemm_quant: operands and leading dimensions must be 16-byte aligned";
-  if (a.w_scale == nullptr || a.x_scale == nullptr || a.out == nullptr) return "gemm_quant: missing scale or output";
+  if (a.w_scale == nullptr || a.x_scale == nullptr || (a.out == nullptr && !push)) return "gemm_quant: missing scale or output";
   if ((a.N & 1) || (a.ldo & 1)) return "gemm_quant: N and ldo must be even";
   if (a.epi == kEpiSwiglu && a.N % 128) return "gemm_quant: SwiGLU needs tile-interleaved rows (N multiple of 128)";
   if (a.epi == kEpiResidual && a.resid == nullptr) return "gemm_quant: residual epilogue without residual";
@@ -635,6 +680,22 @@ const char* gemm_quant(const QGemmArgs& a) {
   kp.out = static_cast<__nv_bfloat16*>(a.out); kp.ldo = a.ldo;
   kp.resid = static_cast<const __nv_bfloat16*>(a.resid); kp.ldr = a.ldr;
   kp.status = a.status;
+  if (push) {
+    if (a.world < 1 || a.world > kMaxRanks || a.rank < 0 || a.rank >= a.world) return "gemm_quant: bad rank/world";
+    kp.rank = a.rank; kp.world = a.world;
+    for (int r = 0; r < a.world; ++r) {
+      if (a.peer_recv[r] == nullptr || a.peer_flag[r] == nullptr) return "gemm_quant: missing peer pointer";
+      kp.peer_recv[r] = a.peer_recv[r]; kp.peer_flag[r] = a.peer_flag[r];
+    }
+    if (a.epi == kEpiPushAll) {
+      if (a.call_idx == nullptr || a.T_cap < kp.T) return "gemm_quant: push-all needs the call counter and T <= T_cap";
+      kp.call_idx = a.call_idx; kp.T_cap = a.T_cap;
+    } else {
+      if (kp.N % a.world || (kp.N / a.world) % kTileN) return "gemm_quant: N / world must be a multiple of 128";
+      if (splits != 1) return "gemm_quant: the reduce-scatter epilogue takes no split-K";
+      kp.slice_cols = kp.N / a.world;
+    }
+  }
   CUtensorMap tw, tx;
   if (!cached_tmap(&tw, a.w, a.N, k_bytes, a.ldw, 64)) return "gemm_quant: weight tensor map rejected";
   if (!cached_tmap(&tx, a.x, a.T, k_bytes, a.ldx, tn)) return "gemm_quant: activation tensor map rejected";

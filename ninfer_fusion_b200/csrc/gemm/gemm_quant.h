@@ -25,7 +25,12 @@ struct QGemmArgs {
   int64_t ldo = 0;
   const void* resid = nullptr;
   int64_t ldr = 0;
-  int epi = kEpiStore;            // kEpiStore, kEpiResidual or kEpiSwiglu
+  int epi = kEpiStore;            // kEpiStore, kEpiResidual, kEpiSwiglu, kEpiPushAll or kEpiPushPartial
+  // tensor-parallel epilogues (same protocol as the bf16 kernel, gemm.h)
+  int world = 1, rank = 0, T_cap = 0;
+  const unsigned int* call_idx = nullptr;
+  float* peer_recv[kMaxRanks] = {};
+  unsigned int* peer_flag[kMaxRanks] = {};
   int splits = 1;                 // in-cluster split-K
   int* status = nullptr;
   cudaStream_t stream = nullptr;

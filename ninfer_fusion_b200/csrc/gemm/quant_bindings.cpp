@@ -4,9 +4,14 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
 
+#include <cstddef>
+
+#include "../comm/comm.h"
 #include "gemm_quant.h"
 
 namespace {
+
+inline size_t nfb_tp_call_idx_offset() { return offsetof(nfb::TpState, call_idx); }
 
 using at::Tensor;
 using OptT = const std::optional<Tensor>&;
@@ -73,6 +78,39 @@ void gemm_quant(int64_t qtype, const Tensor& x_codes, const Tensor& x_scale, con
   chk(nfb::gemm_quant(a));
 }
 
+// Row-parallel GEMM whose epilogue pushes the scaled fp32 tile into peer memory.  all = true: one-shot all-reduce
+// (every rank's [parity][src][T_cap][N] buffer, call counter from `state`); all = false: reduce-scatter into the owner.
+void gemm_quant_push(int64_t qtype, const Tensor& x_codes, const Tensor& x_scale, const Tensor& w_codes,
+                     const Tensor& w_scale, double w_divisor, bool all, int64_t splits, int64_t world, int64_t rank,
+                     at::IntArrayRef peer_bases, int64_t recv_off, int64_t flag_off, int64_t T_cap, const Tensor& state,
+                     OptT status, bool pdl) {
+  need(x_codes, at::kByte, "x_codes"); need(w_codes, at::kByte, "w_codes"); need(state, at::kByte, "state");
+  TORCH_CHECK(x_codes.dim() == 2 && w_codes.dim() == 2 && x_codes.size(1) == w_codes.size(1), "gemm_quant_push: code shapes");
+  TORCH_CHECK(static_cast<int64_t>(peer_bases.size()) == world && world <= nfb::kMaxRanks, "peer_bases size");
+  c10::cuda::CUDAGuard guard(x_codes.device());
+  nfb::QGemmArgs a;
+  a.qtype = static_cast<int>(qtype);
+  const bool bs = qtype == nfb::kQNvfp4;
+  a.N = w_codes.size(0); a.T = x_codes.size(0); a.K = bs ? w_codes.size(1) * 2 : w_codes.size(1);
+  a.w = w_codes.data_ptr(); a.ldw = w_codes.stride(0);
+  a.x = x_codes.data_ptr(); a.ldx = x_codes.stride(0);
+  a.x_scale = x_scale.data_ptr(); a.w_scale = w_scale.data_ptr();
+  a.w_divisor = static_cast<float>(w_divisor);
+  a.ldo = 2;
+  a.epi = all ? nfb::kEpiPushAll : nfb::kEpiPushPartial;
+  a.splits = static_cast<int>(splits);
+  a.world = static_cast<int>(world); a.rank = static_cast<int>(rank); a.T_cap = static_cast<int>(T_cap);
+  // the call counter is the field `call_idx` of the tensor-parallel state block (comm/comm.h: TpState)
+  a.call_idx = reinterpret_cast<const unsigned int*>(static_cast<const char*>(state.data_ptr()) + nfb_tp_call_idx_offset());
+  for (int r = 0; r < world; ++r) {
+    a.peer_recv[r] = reinterpret_cast<float*>(peer_bases[r] + recv_off);
+    a.peer_flag[r] = reinterpret_cast<unsigned int*>(peer_bases[r] + flag_off);
+  }
+  a.status = status.has_value() && status->defined() ? static_cast<int*>(status->data_ptr()) : nullptr;
+  a.stream = cur_stream(); a.pdl = pdl;
+  chk(nfb::gemm_quant(a));
+}
+
 int64_t nvfp4_act_scale_bytes(int64_t T, int64_t K) { return nfb::nvfp4_act_scale_bytes(T, K); }
 
 }  // namespace
@@ -82,4 +120,5 @@ TORCH_LIBRARY_FRAGMENT(nfb200, m) {
   m.def("quant_act_nvfp4(Tensor x, Tensor codes, Tensor sf_plane, bool pdl=False) -> ()", &quant_act_nvfp4);
   m.def("gemm_quant(int qtype, Tensor x_codes, Tensor x_scale, Tensor w_codes, Tensor w_scale, float w_divisor, Tensor out, int epi, Tensor? resid, int splits, Tensor? status, bool pdl) -> ()", &gemm_quant);
   m.def("nvfp4_act_scale_bytes(int T, int K) -> int", &nvfp4_act_scale_bytes);
+  m.def("gemm_quant_push(int qtype, Tensor x_codes, Tensor x_scale, Tensor w_codes, Tensor w_scale, float w_divisor, bool all, int splits, int world, int rank, int[] peer_bases, int recv_off, int flag_off, int T_cap, Tensor state, Tensor? status, bool pdl) -> ()", &gemm_quant_push);
 }

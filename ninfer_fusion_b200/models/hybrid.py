@@ -68,7 +68,9 @@ class Workspace:
         self.mix_gdn = torch.empty((T, g.gdn_v_dim), dtype=bf, device=dev)
         self.conv = torch.empty((T, g.gdn_conv_dim), dtype=bf, device=dev)
         inter = g.ffn_inter if cfg.moe is None else max(cfg.moe.expert_inter, cfg.moe.shared_inter)
-        self.act = torch.empty((T, max(inter, 8)), dtype=bf, device=dev)
+        # zero-filled and padded to a multiple of 256 columns: a block-scaled down projection whose shard width is
+        # not a multiple of its 256-value k-block reads the zero tail
+        self.act = torch.zeros((T, (max(inter, 8) + 255) // 256 * 256), dtype=bf, device=dev)
         self.delta = torch.empty((T, h), dtype=bf, device=dev)
         self.partial = torch.empty((MAX_SPLITS * min(T, 256) * h,), dtype=torch.float32, device=dev)
         self.max_splits_attn = max_splits_attn
@@ -222,6 +224,7 @@ class HybridModel:
         self.act_nvfp4 = any(isinstance(t, QuantWeight) and t.qtype == 2 for t in weights.values())
         self._prequant = None
         self._qbuf: Dict[int, tuple] = {}
+        self._padbuf: Dict[int, torch.Tensor] = {}
         self._qkeep: List[tuple] = []
         self.moe = None   # models.moe.MoeBlock, created with the first workspace that runs a MoE layer
         self.ep = (ep_rank, ep_world, ep_group)  # expert parallelism: experts split, the rest data-parallel
@@ -257,7 +260,21 @@ class HybridModel:
             return
         self.ops.add_rmsnorm(partial, splits, delta, resid_in, resid_out, norm_w, normed, T, N, eps, True, self.pdl)
 
+    def _pad_k(self, x, K: int):
+        """Activation widened with zero columns to a weight whose K was padded to the kernel's k-block."""
+        if x.shape[1] == K:
+            return x
+        buf = self._padbuf.get(K)
+        if buf is None or buf.shape[0] < x.shape[0]:
+            buf = torch.zeros((max(64, 2 * x.shape[0]), K), dtype=x.dtype, device=x.device)
+            self._qkeep.append(buf)
+            self._padbuf[K] = buf
+        out = buf[: x.shape[0]]
+        out[:, : x.shape[1]].copy_(x)
+        return out
+
     def _gemm_quant(self, x, w: QuantWeight, out, epi, resid):
+        x = self._pad_k(x, w.shape[1])
         T, (N, K) = x.shape[0], w.shape
         _, codes, scale, plane = self._quant_scratch(T, K)
         splits = 1
@@ -365,7 +382,8 @@ class HybridModel:
         w_gu = self.w[f"{prefix}/mlp/gate_up"]
         act = ws.act[:T, : w_gu.shape[0] // 2]
         self._gemm(ws.normed[:T], w_gu, act, EPI_SWIGLU)
-        self._gemm_to_residual(ws, act, self.w[f"{prefix}/mlp/down"], T, next_norm_w, normed_out)
+        w_down = self.w[f"{prefix}/mlp/down"]
+        self._gemm_to_residual(ws, ws.act[:T, : w_down.shape[1]], w_down, T, next_norm_w, normed_out)
 
     # ------------------------------------------------------------------ forward
     def fold_gdn(self, ws: Workspace, b: StepBatch, st: GdnStatePool, rec: GdnRecords, seq_end: torch.Tensor) -> None:

@@ -113,9 +113,12 @@ def quantize_tensor(name: str, t: torch.Tensor, weight_format: str):
         return QuantWeight(Q.QT_FP8_ROW, codes, scale, 1.0, (N, K))
     if weight_format == "nvfp4":
         if K % 256:
-            raise ValueError(f"{name}: nvfp4 needs K % 256 == 0, got {K}")
-        chunks = [Q.quantize_nvfp4_prepare(w)]
-        codes, plane, d_w = chunks[0]
+            # zero columns up to the kernel's 256-value k-block (sharded down projections); the consumer reads a
+            # zero-padded activation of the same width
+            Kp = (K + 255) // 256 * 256
+            w = torch.cat([w, torch.zeros((N, Kp - K), dtype=w.dtype, device=w.device)], dim=1)
+            K = Kp
+        codes, plane, d_w = Q.quantize_nvfp4_prepare(w)
         return QuantWeight(Q.QT_NVFP4, codes, plane, d_w, (N, K))
     raise ValueError(f"unknown weight format '{weight_format}'")
 

@@ -190,6 +190,8 @@ class TensorParallel:
         cfg, ops = self.cfg, model.ops
         N = cfg.hidden
         x = ws.x[:T]
+        if hasattr(w, "qtype"):
+            return self._quant_reduce_residual(model, ws, a, w, T, norm_w, normed_out)
         if self.mode == "nccl" or T > self.T_cap:
             delta = self.delta[:T] if T <= self.T_cap else torch.empty((T, N), dtype=torch.bfloat16, device=self.device)
             ops.gemm_bf16(a, w, delta, 0, None, None, None, 1, model.status.tensor, model.pdl)
@@ -212,6 +214,47 @@ class TensorParallel:
         arrivals = self.world * (self.slice // 128) * t_tiles
         ops.gemm_bf16_push(a, w, 1, self.world, self.rank, self.peer_bases, self.off["recv"],
                            self.off["arrival_flag"], model.status.tensor, model.pdl)
+        ops.tp_reduce_ag_norm(self.world, self.rank, T, self.T_cap, N, 1, arrivals, self.peer_bases,
+                              self.off["recv"], self.off["arrival_flag"], self.off["x"], self.off["ss"],
+                              self.off["row_flag"], norm_w, normed_out, cfg.rms_eps, True, self.state,
+                              model.status.tensor, model.pdl)
+
+    def _quant_reduce_residual(self, model, ws, a, w, T: int, norm_w, normed_out) -> None:
+        """Row-parallel GEMM over quantised weights (fp8 / nvfp4): same peer-memory protocols, quantised operands."""
+        cfg, ops = self.cfg, model.ops
+        N, K = w.shape
+        a = model._pad_k(a, K)
+        x = ws.x[:T]
+        _, codes, scale, plane = model._quant_scratch(T, K)
+        if w.qtype == 2:
+            xc, xs, div = codes[: T * K // 2].view(T, K // 2), plane, w.divisor
+            ops.quant_act_nvfp4(a, xc, plane, model.pdl)
+        else:
+            xc, xs, div = codes[: T * K].view(T, K), scale, 1.0
+            ops.quant_act_fp8(a, xc, scale, model.pdl)
+        model._prequant = None
+        if self.mode == "nccl" or T > self.T_cap:
+            delta = self.delta[:T] if T <= self.T_cap else torch.empty((T, N), dtype=torch.bfloat16, device=self.device)
+            ops.gemm_quant(w.qtype, xc, xs, w.codes, w.scale, div, delta, 0, None, 1, model.status.tensor, model.pdl)
+            dist.all_reduce(delta, group=self.group)
+            ops.add_rmsnorm(None, 0, delta, x, x, norm_w, normed_out, T, N, cfg.rms_eps, True, model.pdl)
+            return
+        tn = 32 if T <= 32 else 64 if T <= 64 else 128 if T <= 128 else 256   # token tile of the quantised kernel
+        t_tiles = (T + tn - 1) // tn
+        if T <= self.one_shot_rows:
+            kb_equiv = (K // 2 if w.qtype == 2 else K) // 2
+            splits = int(ops.gemm_pick_splits(T, N, kb_equiv, 0))
+            arrivals = self.world * (N // 128) * t_tiles
+            ops.gemm_quant_push(w.qtype, xc, xs, w.codes, w.scale, div, True, splits, self.world, self.rank, self.peer_bases,
+                                self.off["recv_all"], self.off["all_flag"], self.one_shot_rows, self.state,
+                                model.status.tensor, model.pdl)
+            ops.tp_sum_norm(self.world, self.one_shot_rows, arrivals, self.peer_bases[self.rank], self.off["recv_all"],
+                            self.off["all_flag"], x, norm_w, normed_out, cfg.rms_eps, True, self.state,
+                            model.status.tensor, model.pdl)
+            return
+        arrivals = self.world * (self.slice // 128) * t_tiles
+        ops.gemm_quant_push(w.qtype, xc, xs, w.codes, w.scale, div, False, 1, self.world, self.rank, self.peer_bases,
+                            self.off["recv"], self.off["arrival_flag"], self.T_cap, self.state, model.status.tensor, model.pdl)
         ops.tp_reduce_ag_norm(self.world, self.rank, T, self.T_cap, N, 1, arrivals, self.peer_bases,
                               self.off["recv"], self.off["arrival_flag"], self.off["x"], self.off["ss"],
                               self.off["row_flag"], norm_w, normed_out, cfg.rms_eps, True, self.state,

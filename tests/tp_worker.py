@@ -46,8 +46,45 @@ def main():
         torch.cuda.synchronize()
         dist.barrier()
         log(rank, f"done {mode} graph={use_graph}: {results[(mode, use_graph)][0][:5]}")
+    # quantised weights: shard first, quantise each shard; fused (peer-memory) and NCCL reductions must tell the same story
+    from ninfer_fusion_b200.models.weights import quantize_weights
+    qres, qlogits = {}, {}
+    for fmt in ("nvfp4", "fp8"):
+        for mode, use_graph in (("fused", True), ("nccl", False)):
+            log(rank, f"start {fmt} {mode} graph={use_graph}")
+            comm = TensorParallel(cfg, rank, world, dev, max_tokens=64, mode=mode)
+            wq = quantize_weights(comm.shard(full), fmt)
+            gen = Generator(cfg, wq, dev, max_batch=4, max_context=256, kv_format="bf16", page_size=16,
+                            prefill_chunk=64, use_graph=use_graph, shard=comm.geometry, comm=comm)
+            gen.prefill([prompts[0], prompts[2]])   # one ragged step (26 tokens): the logits of both last tokens stay in the workspace
+            qlogits[(fmt, mode)] = gen.ws.logits[:2].float().clone()
+            qres[(fmt, mode)] = gen.generate(prompts, n_new)
+            torch.cuda.synchronize()
+            gen.model.status.check()
+            dist.barrier()
+            log(rank, f"done {fmt} {mode}: {qres[(fmt, mode)][0][:5]}")
     ok = True
     msg = ""
+    for fmt in ("nvfp4", "fp8"):
+        # the two reductions differ only in rounding (fp32 partial tiles vs bf16 deltas); with 4-bit activations a
+        # rounding difference can flip single codes downstream, so the logits are compared by direction and the
+        # tokens only for fp8
+        la, lb = qlogits[(fmt, "fused")], qlogits[(fmt, "nccl")]
+        cos = torch.nn.functional.cosine_similarity(la, lb, dim=-1).min().item()
+        msg += f" {fmt}: cos(fused, nccl) {cos:.4f};"
+        if cos < (0.85 if fmt == "nvfp4" else 0.98):
+            ok = False
+        a, b = qres[(fmt, "fused")], qres[(fmt, "nccl")]
+        if fmt == "fp8" and sum(int(x[0] == y[0]) for x, y in zip(a, b)) < len(a) - 1:
+            ok = False
+            msg += f" {fmt}: fused {a} vs nccl {b};"
+        # every rank must hold the same tokens (the reductions are replicated, not approximate per rank)
+        mine = torch.tensor(a, device=dev)
+        ref0 = mine.clone()
+        dist.broadcast(ref0, 0)
+        if not torch.equal(mine, ref0):
+            ok = False
+            msg += f" {fmt}: rank {rank} diverged from rank 0;"
     if rank == 0:
         single = Generator(cfg, full, dev, max_batch=4, max_context=256, kv_format="bf16", page_size=16,
                            prefill_chunk=64, use_graph=False).generate(prompts, n_new)
@@ -71,6 +108,11 @@ def main():
     dist.broadcast(ref, 0)
     if not torch.equal(mine, ref):
         print(f"TP_FAIL rank {rank} tokens differ from rank 0", flush=True)
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if not ok and rank != 0:
+        print(f"TP_FAIL rank {rank}:{msg}", flush=True)
+    ok = bool(int(flag.item()))
     dist.barrier()
     if rank == 0:
         print(("TP_OK" if ok else "TP_FAIL") + msg, flush=True)
