@@ -242,6 +242,8 @@ class Engine:
             return
         req.state = "finished"
         if req.lane is not None:
+            if req.opts.session and reason in ("stop", "length"):
+                self.program.checkpoint(req.lane, req.opts.session, "endpoint")   # where this turn's generation ended
             self.program.close(req.lane)
             req.lane = None
         if reason == "error":
@@ -292,7 +294,10 @@ class Engine:
                 self._pending.remove(req)
             try:
                 self._maybe_inject(req)
-                req.lane = self.program.open(req.prompt, req.opts.sampling)
+                req.lane = self.program.open(req.prompt, req.opts.sampling, session=req.opts.session)
+                if req.lane.reused:
+                    self.stats.prefix_hits += 1
+                    self.stats.prefix_tokens_reused += req.lane.reused
                 req.state = "prefill"
                 self._active.append(req)
             except RequestError as e:
@@ -345,6 +350,8 @@ class Engine:
                 self.stats.prefill_s += time.perf_counter() - t0
                 did_prefill = True
                 if first is not None:
+                    if req.opts.session:
+                        self.program.checkpoint(req.lane, req.opts.session, "turn")   # the prompt boundary
                     req.state = "decode"
                     self._commit_token(req, first)
                 break  # one prefill chunk per iteration, then give the decode lanes a round

@@ -22,8 +22,12 @@ class GpuProgram(ProgramBase):
     def __init__(self, cfg: ModelConfig, weights: Dict[str, torch.Tensor], device, max_lanes: int = 32,
                  max_context: int = 8192, kv_format="bf16", page_size: int = 64, prefill_chunk: int = 2048,
                  use_graph: bool = True, pdl: bool = True, int8_group: int = 64, kv_pages: Optional[int] = None,
-                 shard: Optional[ShardGeometry] = None, comm=None, penalties: bool = False):
+                 shard: Optional[ShardGeometry] = None, comm=None, penalties: bool = False,
+                 checkpoint_slots: Optional[int] = None):
         super().__init__(cfg, max_lanes, max_context)
+        # recurrent-state slots beyond the lanes hold the state images of session checkpoints (the reference keeps 2C)
+        self.checkpoint_slots = max_lanes if checkpoint_slots is None else checkpoint_slots
+        self.max_checkpoints = self.checkpoint_slots
         self.device = torch.device(device)
         self.prefill_chunk = prefill_chunk
         self.use_graph = use_graph
@@ -34,7 +38,9 @@ class GpuProgram(ProgramBase):
         n_pages = kv_pages if kv_pages is not None else max_lanes * pages_per_row
         self.kv = PagedKvCache(cfg, n_pages, page_size, max_lanes, pages_per_row, device, formats=kv_format,
                                int8_group=int8_group, n_kv_heads=g.n_kv_heads)
-        self.states = GdnStatePool(cfg, max_lanes, device, n_qk_heads=g.gdn_qk_heads, n_v_heads=g.gdn_v_heads)
+        self.states = GdnStatePool(cfg, max_lanes + self.checkpoint_slots, device, n_qk_heads=g.gdn_qk_heads,
+                                   n_v_heads=g.gdn_v_heads)
+        self._ckpt_slots_free = self.checkpoint_slots
         cap = max(prefill_chunk, max_lanes)
         self.ws = Workspace(cfg, cap, max_lanes, device, shard=shard, x_buffer=None if comm is None else comm.x)
         qt = int(self.model.ops.prefill_attn_block_tokens(g.n_q_heads, g.n_kv_heads))
@@ -64,6 +70,29 @@ class GpuProgram(ProgramBase):
         self.states.release(lane.slot)
         if self.token_counts is not None:
             self.token_counts[lane.row].zero_()
+
+    # ------------------------------------------------------------------ session checkpoints
+    def _snapshot(self, lane: Lane, n_tokens: int):
+        if self._ckpt_slots_free <= 0:
+            return None
+        pages = self.kv.detach_prefix(lane.row, n_tokens)
+        if pages is None:
+            return None
+        self._ckpt_slots_free -= 1
+        slot = self.states.alloc()
+        self.states.copy_slot(lane.slot, slot)
+        return (pages, slot)
+
+    def _restore(self, handle, lane: Lane, n_tokens: int) -> None:
+        pages, slot = handle
+        self.kv.attach_prefix(pages, lane.row, n_tokens)
+        self.states.copy_slot(slot, lane.slot)
+
+    def _drop(self, handle) -> None:
+        pages, slot = handle
+        self.kv.drop_pages(pages)
+        self.states.release(slot)
+        self._ckpt_slots_free += 1
 
     def _kv_room(self, n_tokens: int) -> bool:
         return self.kv.pool.free_pages >= (n_tokens + self.kv.page_size - 1) // self.kv.page_size

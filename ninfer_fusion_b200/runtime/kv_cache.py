@@ -179,6 +179,53 @@ class PagedKvCache:
             self.table_host[dst, full] = p_new
         self._dirty_rows.add(dst)
 
+    # ---- detached page lists (session checkpoints): they hold page references but own no block-table row ----
+    def detach_prefix(self, src_row: int, n_tokens: int) -> Optional[List[int]]:
+        """Page list covering positions [0, n_tokens) of `src_row`: full pages are shared (retained), a partial tail
+        page is copied so that the source may keep appending into its own.  None if the pool is exhausted."""
+        full = n_tokens // self.page_size
+        tail = n_tokens % self.page_size
+        if tail and self.pool.free_pages < 1:
+            return None
+        src = self.row_pages[src_row]
+        pages = []
+        for i in range(full):
+            self.pool.retain(src[i])
+            pages.append(src[i])
+        if tail:
+            p_new = self.pool.alloc()
+            self._copy_page(src[full], p_new)
+            pages.append(p_new)
+        return pages
+
+    def attach_prefix(self, pages: List[int], dst_row: int, n_tokens: int) -> None:
+        """Make `dst_row` start from a detached page list (full pages shared, partial tail page copied)."""
+        self.free_row(dst_row)
+        full = n_tokens // self.page_size
+        mine = self.row_pages.setdefault(dst_row, [])
+        for i in range(full):
+            self.pool.retain(pages[i])
+            mine.append(pages[i])
+            self.table_host[dst_row, i] = pages[i]
+        if n_tokens % self.page_size:
+            p_new = self.pool.alloc()
+            self._copy_page(pages[full], p_new)
+            mine.append(p_new)
+            self.table_host[dst_row, full] = p_new
+        self._dirty_rows.add(dst_row)
+
+    def drop_pages(self, pages: List[int]) -> None:
+        for p in pages:
+            self.pool.release(p)
+
+    def _copy_page(self, p_src: int, p_dst: int) -> None:
+        for l in self.layers:
+            l.k_codes[p_dst].copy_(l.k_codes[p_src])
+            l.v_codes[p_dst].copy_(l.v_codes[p_src])
+            if l.k_scales is not None:
+                l.k_scales[p_dst].copy_(l.k_scales[p_src])
+                l.v_scales[p_dst].copy_(l.v_scales[p_src])
+
     def publish(self) -> None:
         """Upload dirty block-table rows to the device."""
         if not self._dirty_rows:

@@ -46,6 +46,20 @@ class Lane:
     n_cached: int = 0        # tokens already run through the model
     sampling: SamplingParams = field(default_factory=SamplingParams)
     last_token: int = -1     # sampled but not yet fed
+    reused: int = 0          # prompt tokens restored from a session checkpoint instead of being prefilled
+
+
+@dataclass
+class Checkpoint:
+    """A reusable frontier of a session: exact token history + KV coverage + recurrent state image.
+    Kinds follow the reference's catalogue (docs/maintainer/resource-scheduling-and-context-cache.md:266-284):
+    'turn' = the prompt boundary of a request (TurnClosure), 'endpoint' = where its generation stopped
+    (SessionEndpoint).  A frontier is reusable only for a prompt that starts with exactly these tokens."""
+    session: str
+    kind: str
+    tokens: List[int]
+    handle: object
+    last_used: float = 0.0
 
 
 class ProgramBase:
@@ -58,18 +72,74 @@ class ProgramBase:
         self.lanes: Dict[int, Lane] = {}
         self._free_rows = list(range(max_lanes - 1, -1, -1))
         self._next_id = 0
+        self.checkpoints: List[Checkpoint] = []
+        self.max_checkpoints = 2 * max_lanes
+        self._clock = 0
 
     # ---- capacity ----
     def free_lanes(self) -> int:
         return len(self._free_rows)
 
     def can_admit(self, n_prompt: int, max_new: int) -> bool:
-        return bool(self._free_rows) and n_prompt + max_new <= self.max_context and self._kv_room(n_prompt + max_new)
+        if not self._free_rows or n_prompt + max_new > self.max_context:
+            return False
+        while not self._kv_room(n_prompt + max_new):
+            if not self._evict_checkpoint():   # cached frontiers give way to live requests, oldest first
+                return False
+        return True
+
+    # ---- session checkpoints (prefix reuse) ----
+    def _evict_checkpoint(self) -> bool:
+        if not self.checkpoints:
+            return False
+        victim = min(self.checkpoints, key=lambda c: c.last_used)
+        self.checkpoints.remove(victim)
+        self._drop(victim.handle)
+        return True
+
+    def checkpoint(self, lane: Lane, session: str, kind: str) -> bool:
+        """Remember the lane's materialised frontier (lane.tokens[:n_cached]) for `session`."""
+        n = lane.n_cached
+        if not session or n <= 0:
+            return False
+        for c in [c for c in self.checkpoints if c.session == session and c.kind == kind]:
+            self.checkpoints.remove(c)       # one frontier per (session, kind)
+            self._drop(c.handle)
+        while len(self.checkpoints) >= self.max_checkpoints:
+            self._evict_checkpoint()
+        handle = None
+        while handle is None:
+            handle = self._snapshot(lane, n)
+            if handle is None and not self._evict_checkpoint():
+                return False
+        self._clock += 1
+        self.checkpoints.append(Checkpoint(session, kind, list(lane.tokens[:n]), handle, self._clock))
+        return True
+
+    def _match(self, session: Optional[str], prompt: Sequence[int]) -> Optional[Checkpoint]:
+        best = None
+        if session:
+            for c in self.checkpoints:
+                n = len(c.tokens)
+                if c.session == session and n < len(prompt) and (best is None or n > len(best.tokens)) \
+                        and list(prompt[:n]) == c.tokens:
+                    best = c
+        return best
+
+    def _snapshot(self, lane: Lane, n_tokens: int):
+        return None   # programs without checkpoint support simply never reuse
+
+    def _restore(self, handle, lane: Lane, n_tokens: int) -> None:
+        raise NotImplementedError
+
+    def _drop(self, handle) -> None:
+        pass
 
     def _kv_room(self, n_tokens: int) -> bool:
         return True
 
-    def open(self, prompt: Sequence[int], sampling: Optional[SamplingParams] = None) -> Lane:
+    def open(self, prompt: Sequence[int], sampling: Optional[SamplingParams] = None,
+             session: Optional[str] = None) -> Lane:
         if not self._free_rows:
             raise MemoryError("no free lane")
         if len(prompt) == 0:
@@ -78,6 +148,12 @@ class ProgramBase:
         lane = Lane(self._next_id, row, self._alloc_slot(), list(prompt), 0, sampling or SamplingParams())
         self._next_id += 1
         self.lanes[lane.lane_id] = lane
+        ck = self._match(session, prompt)
+        if ck is not None:
+            self._restore(ck.handle, lane, len(ck.tokens))
+            lane.n_cached = lane.reused = len(ck.tokens)
+            self._clock += 1
+            ck.last_used = self._clock
         return lane
 
     def close(self, lane: Lane) -> None:
@@ -120,6 +196,14 @@ class ReferenceProgram(ProgramBase):
 
     def _release(self, lane: Lane) -> None:
         self._seqs.pop(lane.lane_id, None)
+
+    def _snapshot(self, lane: Lane, n_tokens: int):
+        import copy
+        return copy.deepcopy(self._seqs[lane.lane_id])
+
+    def _restore(self, handle, lane: Lane, n_tokens: int) -> None:
+        import copy
+        self._seqs[lane.lane_id] = copy.deepcopy(handle)
 
     def _sample(self, lane: Lane, logits: torch.Tensor) -> int:
         sp = lane.sampling

@@ -109,3 +109,31 @@ def test_bandwidth_governor_shrinks_and_recovers():
     for _ in range(20):
         g.observe(100.0, True)
     assert g.unit == 128
+
+
+def test_session_checkpoints_reuse_the_prefix_and_keep_the_stream():
+    """A follow-up turn of a session restores the longest stored frontier (prompt boundary or end of generation) and
+    produces exactly the tokens a cold run produces."""
+    from ninfer_fusion_b200.models.config import TINY_DENSE
+    from ninfer_fusion_b200.models.weights import random_weights
+    from ninfer_fusion_b200.runtime.program import ReferenceProgram
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cpu", seed=5, std=0.05)
+    eng = Engine(lambda: ReferenceProgram(cfg, w, max_lanes=2, max_context=256), prefill_chunk=16)
+    try:
+        turn1 = list(range(10, 40))
+        out1 = eng.generate(turn1, RequestOptions(max_tokens=6, session="s1"))
+        turn2 = turn1 + out1 + [7, 8, 9, 11]                  # the client echoes the reply and adds a new user turn
+        cold = eng.generate(turn2, RequestOptions(max_tokens=6))
+        hits0 = eng.stats.prefix_hits
+        warm = eng.generate(turn2, RequestOptions(max_tokens=6, session="s1"))
+        assert warm == cold
+        assert eng.stats.prefix_hits == hits0 + 1
+        assert eng.stats.prefix_tokens_reused >= len(turn1)       # at least the prompt boundary was reused
+        # a prompt that diverges inside the stored history must not reuse it
+        turn3 = turn1[:20] + [999 % cfg.vocab] + turn1[21:] + [3, 4]
+        hits1 = eng.stats.prefix_hits
+        assert eng.generate(turn3, RequestOptions(max_tokens=3, session="s1")) == eng.generate(turn3, RequestOptions(max_tokens=3))
+        assert eng.stats.prefix_hits == hits1
+    finally:
+        eng.shutdown()

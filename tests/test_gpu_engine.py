@@ -68,3 +68,25 @@ def test_text_service_on_gpu(setup):
     res = svc.generate(GenRequest(messages=[{"role": "user", "content": "Hello world"}], max_tokens=8, temperature=0.0))
     assert res.finish_reason in ("stop", "length", "tool_calls") and res.completion_tokens <= 8 and res.prompt_tokens > 4
     assert isinstance(res.content, str)
+
+
+def test_session_checkpoint_reuse_on_gpu(setup):
+    """Follow-up turn restores KV pages (shared full pages + copied tail page) and the GDN state image."""
+    cfg, _, engine = setup
+    turn1 = list(range(10, 63))          # 53 tokens: three full 16-token pages + a partial one
+    out1 = engine.generate(turn1, RequestOptions(max_tokens=9, session="chat-1"))
+    turn2 = turn1 + out1 + [7, 8, 9, 11, 12]
+    cold = engine.generate(turn2, RequestOptions(max_tokens=8))
+    hits, reused = engine.stats.prefix_hits, engine.stats.prefix_tokens_reused
+    warm = engine.generate(turn2, RequestOptions(max_tokens=8, session="chat-1"))
+    assert engine.stats.prefix_hits == hits + 1
+    assert engine.stats.prefix_tokens_reused - reused >= len(turn1)
+    n = 0
+    while n < len(cold) and warm[n] == cold[n]:
+        n += 1
+    assert n >= 4, (warm, cold)   # restored vs recomputed state differ only by kernel-shape rounding
+    # the pool gets its pages back when the checkpoints are evicted
+    prog = engine.program
+    while prog._evict_checkpoint():
+        pass
+    assert prog.kv.pool.free_pages == prog.kv.n_pages and prog._ckpt_slots_free == prog.checkpoint_slots
