@@ -173,6 +173,7 @@ class Engine:
         self._wake = threading.Condition(self._lock)
         self._next_id = 0
         self._failed: Optional[str] = None
+        self._draining = False   # reload_kv_storage in progress: admission is paused
         self._stop = False
         self._fault = os.environ.get("NINFER_FAULT_INJECT", "")
         self._fault_min_id = int(os.environ.get("NINFER_FAULT_INJECT_MIN_ID", "0"))
@@ -208,6 +209,32 @@ class Engine:
         with self._lock:
             return {"status": "failed" if self._failed else "ok", "pending": len(self._pending),
                     "active": len(self._active), "free_lanes": self.program.free_lanes()}
+
+    def reload_kv_storage(self, program_factory: Callable[[], ProgramBase], timeout_s: float = 60.0) -> None:
+        """Swap the KV storage plan (per-layer formats, page geometry) by rebuilding the Program once the engine has
+        drained: new requests keep queueing, in-flight ones finish first.  Session checkpoints are dropped with the
+        old Program.  (Reference: Engine::reload_kv_storage, src/runtime/engine/engine.cpp:764, used by the
+        serve-side KV auto-relayout.)"""
+        end = time.perf_counter() + timeout_s
+        with self._wake:
+            self._draining = True
+        try:
+            while True:
+                with self._lock:
+                    if not self._active:
+                        old = self.program
+                        self._factory = program_factory
+                        self.program = None
+                        del old
+                        self.program = program_factory()
+                        return
+                if time.perf_counter() > end:
+                    raise TimeoutError("engine did not drain in time")
+                time.sleep(0.005)
+        finally:
+            with self._wake:
+                self._draining = False
+                self._wake.notify_all()
 
     def recover(self) -> None:
         """Rebuild the Program after an engine-wide failure; in-flight requests were already failed."""
@@ -273,6 +300,9 @@ class Engine:
                 raise InvariantError("injected invariant fault")
 
     def _admit(self) -> None:
+        if self._draining or self.program is None:
+            time.sleep(0.002)   # a storage reload is waiting for the lanes to drain
+            return
         now = time.perf_counter()
         with self._lock:
             pend = list(self._pending)
