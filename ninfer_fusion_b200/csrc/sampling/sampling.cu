@@ -121,7 +121,12 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const SampleParams p) 
   }
   __syncthreads();
   if (threadIdx.x != 0) return;
-  if (greedy) { p.out[row_id] = top_i[0]; return; }
+  const int draft = p.draft_ids != nullptr ? p.draft_ids[row_id] : -1;
+  if (greedy) {
+    p.out[row_id] = top_i[0];
+    if (p.accepted != nullptr) p.accepted[row_id] = (draft >= 0 && draft == top_i[0]) ? 1 : 0;
+    return;
+  }
 
   // softmax over the K candidates at the given temperature, then min-p / top-p cuts
   const float inv_t = 1.f / temp;
@@ -158,15 +163,42 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const SampleParams p) 
   }
   const uint64_t seed = p.seeds ? p.seeds[row_id] : 0ull;
   const uint32_t pos = p.positions ? static_cast<uint32_t>(p.positions[row_id]) : 0u;
-  const uint4 rnd = philox(make_uint4(pos, p.purpose, 0u, 0u),
-                           make_uint2(static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32)));
-  const float u = (static_cast<float>(rnd.x >> 8) + 0.5f) * (1.f / 16777216.f);
-  float acc = 0.f;
-  int pick = keep - 1;
-  for (int k = 0; k < keep; ++k) {
-    acc += prob[k] / ksum;
-    if (u < acc) { pick = k; break; }
+  const uint2 key = make_uint2(static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32));
+  auto uniform = [&](unsigned int purpose) {
+    const uint4 r = philox(make_uint4(pos, purpose, 0u, 0u), key);
+    return (static_cast<float>(r.x >> 8) + 0.5f) * (1.f / 16777216.f);
+  };
+  unsigned int purpose = p.purpose;
+  if (draft >= 0) {
+    int kd = -1;
+    for (int k = 0; k < keep; ++k)
+      if (top_i[k] == draft) kd = k;
+    const float pd = kd >= 0 ? prob[kd] / ksum : 0.f;
+    const bool ok = kd >= 0 && (keep == 1 || uniform(1u) < pd);
+    if (p.accepted != nullptr) p.accepted[row_id] = ok ? 1 : 0;
+    if (ok) {
+      p.out[row_id] = draft;
+      if (p.out_prob != nullptr) p.out_prob[row_id] = pd;
+      return;
+    }
+    if (kd >= 0) {   // residual distribution: the draft's mass is removed, the rest renormalised
+      ksum -= prob[kd];
+      prob[kd] = 0.f;
+    }
+    purpose = 2u;
+  } else if (p.accepted != nullptr) {
+    p.accepted[row_id] = 0;
   }
+  const float u = uniform(purpose);
+  float acc = 0.f;
+  int pick = -1;
+  for (int k = 0; k < keep; ++k) {
+    if (prob[k] <= 0.f) continue;
+    pick = k;                      // the last candidate with mass absorbs the rounding tail
+    acc += prob[k] / ksum;
+    if (u < acc) break;
+  }
+  if (pick < 0) pick = 0;
   p.out[row_id] = top_i[pick];
   if (p.out_prob != nullptr) p.out_prob[row_id] = prob[pick] / ksum;
 }

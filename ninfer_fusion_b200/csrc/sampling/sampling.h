@@ -26,6 +26,12 @@ struct SampleParams {
   unsigned int purpose;         // stream id: 0 = sample, 1 = spec accept, 2 = residual resample, ...
   int* out;                     // [T]
   float* out_prob;              // optional: probability of the drawn token under the final distribution
+  // Speculative verification of deterministic drafts (optional): row r checks draft_ids[r] (< 0: no draft, plain
+  // sampling).  The draft is accepted with probability p(draft) under the row's final distribution (random stream
+  // `purpose` = 1); on rejection the token is drawn from that distribution with the draft removed and renormalised
+  // (stream 2), so the emitted token is distributed exactly as p.  Greedy rows accept iff the draft is the arg-max.
+  const int* draft_ids = nullptr;
+  int* accepted = nullptr;      // [T] 1 = draft accepted (out = draft), 0 = rejected (out = replacement)
 };
 const char* sample_rows(const SampleParams& p, cudaStream_t stream);
 

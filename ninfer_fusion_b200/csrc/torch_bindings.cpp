@@ -373,7 +373,7 @@ void argmax_rows(const Tensor& logits, const Tensor& out, bool pdl) {
 
 void sample_rows(const Tensor& logits, OptT temperature, OptT top_k, OptT top_p, OptT min_p, OptT presence,
                  OptT frequency, OptT token_counts, OptT seeds, OptT positions, int64_t purpose, const Tensor& out,
-                 OptT out_prob) {
+                 OptT out_prob, OptT draft_ids, OptT accepted) {
   need(logits, at::kBFloat16, "logits"); need_rows(logits, "logits"); need(out, at::kInt, "out");
   c10::cuda::CUDAGuard guard(logits.device());
   nfb::SampleParams p = {};
@@ -386,6 +386,16 @@ void sample_rows(const Tensor& logits, OptT temperature, OptT top_k, OptT top_p,
   p.seeds = ptr_or_null<const unsigned long long>(seeds); p.positions = ptr_or_null<const int>(positions);
   p.purpose = static_cast<unsigned int>(purpose);
   p.out = static_cast<int*>(out.data_ptr()); p.out_prob = ptr_or_null<float>(out_prob);
+  if (draft_ids.has_value() && draft_ids->defined()) {
+    need(*draft_ids, at::kInt, "draft_ids");
+    TORCH_CHECK(draft_ids->numel() >= p.T, "draft_ids: one entry per row");
+    p.draft_ids = static_cast<const int*>(draft_ids->data_ptr());
+  }
+  if (accepted.has_value() && accepted->defined()) {
+    need(*accepted, at::kInt, "accepted");
+    TORCH_CHECK(accepted->numel() >= p.T, "accepted: one entry per row");
+    p.accepted = static_cast<int*>(accepted->data_ptr());
+  }
   chk(nfb::sample_rows(p, cur_stream()));
 }
 
@@ -600,7 +610,7 @@ TORCH_LIBRARY(nfb200, m) {
   m.def("gdn_recurrent(Tensor qkv, int q_off, int k_off, int v_off, Tensor proj, int z_off, int a_off, int b_off, int n_qk_heads, int n_v_heads, Tensor A_log, Tensor dt_bias, Tensor norm_w, float eps, Tensor cu_seqlens, Tensor state_slot, Tensor state, bool write_state, Tensor out, bool pdl, Tensor? seq_end=None) -> ()", &gdn_recurrent);
   m.def("gdn_prefill_trace(bool enable) -> Tensor", &gdn_prefill_trace);
   m.def("argmax_rows(Tensor logits, Tensor out, bool pdl) -> ()", &argmax_rows);
-  m.def("sample_rows(Tensor logits, Tensor? temperature, Tensor? top_k, Tensor? top_p, Tensor? min_p, Tensor? presence, Tensor? frequency, Tensor? token_counts, Tensor? seeds, Tensor? positions, int purpose, Tensor out, Tensor? out_prob) -> ()", &sample_rows);
+  m.def("sample_rows(Tensor logits, Tensor? temperature, Tensor? top_k, Tensor? top_p, Tensor? min_p, Tensor? presence, Tensor? frequency, Tensor? token_counts, Tensor? seeds, Tensor? positions, int purpose, Tensor out, Tensor? out_prob, Tensor? draft_ids=None, Tensor? accepted=None) -> ()", &sample_rows);
   m.def("accept_greedy_chain(Tensor target_ids, Tensor draft_ids, Tensor n_accepted, Tensor out_tokens) -> ()", &accept_greedy_chain);
   m.def("accept_greedy_tree(Tensor target_ids, Tensor node_tok, Tensor parent, int max_depth, Tensor n_accepted, Tensor out_tokens, Tensor out_nodes) -> ()", &accept_greedy_tree);
 }

@@ -46,6 +46,7 @@ class ModelConfig:
     mrope_sections: tuple = (11, 11, 10)
     mtp_layers: int = 1
     max_context: int = 262144
+    rope_yarn_factor: float = 0.0   # > 1: YaRN context extension by this factor over max_context (yarn4 = 4.0)
 
     # ---- derived geometry ----
     def is_full_attn(self, layer: int) -> bool:

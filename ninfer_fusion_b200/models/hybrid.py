@@ -18,7 +18,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .._lib import StatusWord, load_native
-from ..ops.reference import rope_inv_freq
+from ..ops.reference import rope_inv_freq, rope_inv_freq_yarn
 from ..runtime.kv_cache import GdnStatePool, PagedKvCache
 from .config import ModelConfig
 
@@ -216,7 +216,12 @@ class HybridModel:
         self.pdl = pdl
         self.g = shard or ShardGeometry.full(cfg)
         self.prefix = prefix
-        self.inv_freq = rope_inv_freq(cfg.rot_dim, cfg.rope_theta).to(self.device)
+        self.rope_factor = 1.0
+        if cfg.rope_yarn_factor > 1.0:
+            inv, self.rope_factor = rope_inv_freq_yarn(cfg.rot_dim, cfg.rope_theta, cfg.rope_yarn_factor, cfg.max_context)
+            self.inv_freq = inv.to(self.device)
+        else:
+            self.inv_freq = rope_inv_freq(cfg.rot_dim, cfg.rope_theta).to(self.device)
         self.sm_scale = 1.0 / math.sqrt(cfg.head_dim)
         self.cluster_splitk = True  # False: split-K through an fp32 workspace + reduce kernel
         self.attn_impl = 0  # 0 = pick, 1 = SIMT, 2 = tensor-core split-KV attention
@@ -335,7 +340,7 @@ class HybridModel:
         q = ws.q[:T]
         ops.attn_prep(proj, 0, q_dim, q_dim + kv_dim + q_dim, g.n_q_heads, g.n_kv_heads, D,
                       self.w[f"{prefix}/attn/q_norm"], self.w[f"{prefix}/attn/k_norm"], cfg.rms_eps, True,
-                      cfg.rot_dim, self.inv_freq, 1.0, b.rope_pos, b.table_row, b.cache_pos, kv.table, q,
+                      cfg.rot_dim, self.inv_freq, self.rope_factor, b.rope_pos, b.table_row, b.cache_pos, kv.table, q,
                       planes.k_codes, planes.v_codes, planes.k_scales, planes.v_scales, kv.page_size, planes.fmt,
                       planes.group, self.pdl)
         gate = proj[:, q_dim + kv_dim: q_dim + kv_dim + q_dim]

@@ -42,6 +42,10 @@ class ReferenceModel:
         self.prefix = prefix
         # W8A8 / W4A4 engines quantise the GEMM inputs on the fly; set to ops.quant.fake_quant_* to mirror that
         self.act_quant = lambda x: x
+        self.rope_inv, self.rope_factor = None, 1.0
+        if cfg.rope_yarn_factor > 1.0:
+            self.rope_inv, self.rope_factor = R.rope_inv_freq_yarn(cfg.rot_dim, cfg.rope_theta, cfg.rope_yarn_factor,
+                                                                   cfg.max_context)
 
     # ---- pieces ----
     def _attn(self, seq: ReferenceSequence, ai: int, p: str, normed: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
@@ -55,8 +59,8 @@ class ReferenceModel:
         v = proj[:, 2 * qd + kd:].reshape(T, cfg.n_kv_heads, D)
         q = R.bf16_round(R.rmsnorm(q, self.w[f"{p}/attn/q_norm"], cfg.rms_eps, True))
         k = R.bf16_round(R.rmsnorm(k, self.w[f"{p}/attn/k_norm"], cfg.rms_eps, True))
-        q = R.bf16_round(R.rope_partial(q, pos, cfg.rot_dim, cfg.rope_theta))
-        k = R.rope_partial(k, pos, cfg.rot_dim, cfg.rope_theta)
+        q = R.bf16_round(R.rope_partial(q, pos, cfg.rot_dim, cfg.rope_theta, self.rope_factor, self.rope_inv))
+        k = R.rope_partial(k, pos, cfg.rot_dim, cfg.rope_theta, self.rope_factor, self.rope_inv)
         k = R.kv_quant_dequant(k, seq.kv_format, seq.int8_group)
         v = R.kv_quant_dequant(v, seq.kv_format, seq.int8_group)
         base = seq.k[ai].shape[0]

@@ -9,6 +9,7 @@ are placed where an operator boundary stores bf16.
 from __future__ import annotations
 
 import math
+from typing import Optional
 
 import torch
 
@@ -33,14 +34,35 @@ def rope_inv_freq(rot_dim: int, theta: float) -> torch.Tensor:
     return (theta ** (-torch.arange(half, dtype=torch.float64) / half)).float()
 
 
+def rope_inv_freq_yarn(rot_dim: int, theta: float, factor: float = 4.0, original_context: int = 262144,
+                       beta_fast: float = 32.0, beta_slow: float = 1.0):
+    """YaRN frequency table and attention factor (reference: yarn4, include/ninfer/ops/rope.h:110-117).
+
+    Pairs that rotate more than `beta_fast` times over the original context keep their frequency, pairs that
+    rotate less than `beta_slow` times are interpolated by `factor`, the band in between is blended linearly.
+    The returned factor 0.1 * ln(factor) + 1 (1.1386 for x4) multiplies cos and sin."""
+    half = rot_dim // 2
+    inv = theta ** (-torch.arange(half, dtype=torch.float64) / half)
+
+    def dim_of(rotations: float) -> float:
+        return (rot_dim * math.log(original_context / (rotations * 2 * math.pi))) / (2 * math.log(theta))
+
+    low = max(math.floor(dim_of(beta_fast)), 0)
+    high = min(math.ceil(dim_of(beta_slow)), half - 1)
+    ramp = ((torch.arange(half, dtype=torch.float64) - low) / max(high - low, 1e-3)).clamp(0, 1)
+    keep = 1.0 - ramp                       # 1 = extrapolate (original frequency), 0 = interpolate
+    out = inv / factor * (1 - keep) + inv * keep
+    return out.float(), 0.1 * math.log(factor) + 1.0
+
+
 def rope_partial(x: torch.Tensor, pos: torch.Tensor, rot_dim: int, theta: float,
-                 attn_factor: float = 1.0) -> torch.Tensor:
+                 attn_factor: float = 1.0, inv_freq: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x [T, H, D]; NeoX split-half rotation on the first rot_dim dims.
 
     pos is [T] or [T, 3] (MRoPE: rotary pair i uses axis i % 3)."""
     x = x.float()
     half = rot_dim // 2
-    inv = rope_inv_freq(rot_dim, theta).to(x.device)
+    inv = (rope_inv_freq(rot_dim, theta) if inv_freq is None else inv_freq).to(x.device)
     if pos.dim() == 1:
         p = pos.float()[:, None].expand(-1, half)
     else:

@@ -113,3 +113,28 @@ def test_quantised_weights_logits_close_to_dequantised_oracle(weight_format):
     assert min(cos) > (0.99 if weight_format == "fp8" else 0.97), cos
     out = gen.generate(prompts, 6)   # decode path (graph) runs and reports no kernel error
     assert all(len(o) == 6 for o in out)
+
+
+def test_yarn_rope_matches_reference():
+    """YaRN x4 frequency table + attention factor on the engine against the oracle with the same table."""
+    from dataclasses import replace
+    cfg = replace(TINY_DENSE, name="tiny-dense-yarn4", rope_yarn_factor=4.0, max_context=64)
+    w = random_weights(cfg, "cuda", seed=7, std=0.05)
+    gen = Generator(cfg, w, "cuda", max_batch=2, max_context=512, kv_format="bf16", page_size=16, prefill_chunk=64,
+                    use_graph=False)
+    ref = ReferenceModel(cfg, w)
+    torch.manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (150, 40)]   # well past the original context
+    out = gen.generate(prompts, 8)
+    agree = total = 0
+    for b, p in enumerate(prompts):
+        seq = ReferenceSequence(cfg, R.KV_BF16)
+        h = ref.forward(seq, torch.tensor(p))
+        for tok in out[b]:
+            lg = ref.logits(h[-1:])[0]
+            top2 = lg.topk(2).values
+            if (top2[0] - top2[1]).item() > 0.05:
+                total += 1
+                agree += int(int(R.argmax_lowest(lg[None])[0]) == tok)
+            h = ref.forward(seq, torch.tensor([tok]))
+    assert total >= 8 and agree / total >= 0.9, f"{agree}/{total}"

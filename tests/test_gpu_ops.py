@@ -344,3 +344,56 @@ def test_prefill_attention(ops, name, fmt, group, hq, hkv):
         o = R.bf16_round(o).reshape(-1) * torch.sigmoid(gate[i].float().cpu())
         worst = max(worst, (out[i].float().cpu() - o).abs().max().item())
     assert worst < 0.03, f"{name}: err {worst}"
+
+
+def test_stochastic_draft_verification_preserves_the_target_distribution(ops):
+    """Deterministic drafts verified by speculative sampling: accept w.p. p(draft), else draw from p without the
+    draft.  Over many seeds the emitted token must follow p itself and the acceptance rate must be p(draft)."""
+    torch.manual_seed(0)
+    V, n = 64, 6000
+    base = torch.randn(V) * 1.5
+    logits = base.to(torch.bfloat16)[None].repeat(n, 1).contiguous().cuda()
+    k = 8
+    vals, idx = torch.sort(logits[0].float().cpu(), descending=True, stable=True)
+    p = torch.softmax(vals[:k], 0)                    # temperature 1, top-k 8, no top-p
+    draft_tok = int(idx[2])                           # third most likely token, p ~ p[2]
+    temp = torch.ones(n, device="cuda")
+    topk = torch.full((n,), k, dtype=torch.int32, device="cuda")
+    seeds = torch.arange(n, dtype=torch.int64, device="cuda")
+    pos = torch.full((n,), 17, dtype=torch.int32, device="cuda")
+    out = torch.empty(n, dtype=torch.int32, device="cuda")
+    acc = torch.empty(n, dtype=torch.int32, device="cuda")
+    drafts = torch.full((n,), draft_tok, dtype=torch.int32, device="cuda")
+    ops.sample_rows(logits, temp, topk, None, None, None, None, None, seeds, pos, 0, out, None, drafts, acc)
+    rate = acc.float().mean().item()
+    assert abs(rate - p[2].item()) < 0.02
+    assert bool((out[acc.bool()] == draft_tok).all()) and bool((out[~acc.bool()] != draft_tok).all())
+    emp = torch.bincount(out.cpu().long(), minlength=V).float() / n
+    want = torch.zeros(V)
+    want[idx[:k]] = p
+    assert (emp - want).abs().max().item() < 0.025
+    # a draft outside the candidate set is always rejected; a greedy row accepts only the arg-max
+    drafts.fill_(int(idx[-1]))
+    ops.sample_rows(logits, temp, topk, None, None, None, None, None, seeds, pos, 0, out, None, drafts, acc)
+    assert acc.sum().item() == 0
+    temp.zero_()
+    drafts.fill_(int(idx[0]))
+    ops.sample_rows(logits, temp, topk, None, None, None, None, None, seeds, pos, 0, out, None, drafts, acc)
+    assert acc.sum().item() == n and bool((out == int(idx[0])).all())
+    # chain acceptance on top: rows of one sequence are columns of the verify window
+    B, K = 4, 3
+    lg = logits[: B * (K + 1)]
+    temp = torch.ones(B * (K + 1), device="cuda")
+    d = torch.full((B, K + 1), -1, dtype=torch.int32, device="cuda")
+    d[:, :K] = draft_tok
+    tok = torch.empty(B * (K + 1), dtype=torch.int32, device="cuda")
+    ok = torch.empty(B * (K + 1), dtype=torch.int32, device="cuda")
+    ops.sample_rows(lg, temp, topk[: B * (K + 1)], None, None, None, None, None, seeds[: B * (K + 1)], pos[: B * (K + 1)], 0,
+                    tok, None, d.view(-1).contiguous(), ok)
+    n_acc = torch.empty(B, dtype=torch.int32, device="cuda")
+    out_tok = torch.empty((B, K + 1), dtype=torch.int32, device="cuda")
+    ops.accept_greedy_chain(tok.view(B, K + 1), d[:, :K].contiguous(), n_acc, out_tok)
+    okm = ok.view(B, K + 1).cpu()
+    for b in range(B):
+        first_rej = next((j for j in range(K) if okm[b, j] == 0), K)
+        assert int(n_acc[b]) == first_rej and int(out_tok[b, first_rej]) == int(tok.view(B, K + 1)[b, first_rej])
