@@ -48,13 +48,14 @@ class SpeculativeGenerator(Generator):
     """Static-batch greedy generation with K chained draft tokens per round."""
 
     def __init__(self, cfg: ModelConfig, weights: Dict[str, torch.Tensor], device, max_batch: int, max_context: int,
-                 draft_tokens: int = 3, drafter: str = "mtp", **kw):
+                 draft_tokens: int = 3, drafter: str = "mtp", sampling=None, **kw):
         K = draft_tokens
         if K < 1:
             raise ValueError("draft_tokens must be >= 1")
         kw.setdefault("use_graph", False)
         super().__init__(cfg, weights, device, max_batch, max_context, max_logit_rows=max_batch * (K + 1), **kw)
         self.K = K
+        self.sampling = sampling  # runtime.program.SamplingParams for stochastic verification; None / greedy = arg-max
         self.drafter = drafter  # "mtp" | "ngram" | "hook"
         self.draft_hook: Optional[Callable[[int, List[int], int], Optional[List[int]]]] = None
         dev, g = self.device, self.model.g
@@ -224,7 +225,21 @@ class SpeculativeGenerator(Generator):
         self.h_keep[:T].copy_(hidden)
         lg = self.model.logits(self.ws, batch, hidden)
         target = self.ws.next_ids[:T]
-        ops.argmax_rows(lg, target, self.model.pdl)
+        if self.sampling is None or self.sampling.greedy:
+            ops.argmax_rows(lg, target, self.model.pdl)
+        else:
+            # speculative sampling: column j draws against draft j + 1 (the last column has no draft: bonus token);
+            # a rejected column already holds its replacement, so the chain rule below applies unchanged
+            sp = self.sampling
+            dev = self.device
+            d = torch.full((B, K + 1), -1, dtype=torch.int32, device=dev)
+            d[:, :K] = self.drafts[:B]
+            pos = torch.tensor([self.lengths[b] + j + 1 for b in range(B) for j in range(K + 1)], dtype=torch.int32, device=dev)
+            ops.sample_rows(lg, torch.full((T,), sp.temperature, device=dev),
+                            torch.full((T,), sp.top_k, dtype=torch.int32, device=dev),
+                            torch.full((T,), sp.top_p, device=dev), torch.full((T,), sp.min_p, device=dev), None, None, None,
+                            torch.full((T,), sp.seed, dtype=torch.int64, device=dev), pos, 0, target, None,
+                            d.view(-1), torch.empty(T, dtype=torch.int32, device=dev))
         # ---- accept + fold ----
         ops.accept_greedy_chain(target.view(B, K + 1), self.drafts[:B], self.n_acc[:B], self.out_tok[:B])
         seq_end = (batch.cu_seqlens[:B] + self.n_acc[:B] + 1).to(torch.int32)

@@ -89,3 +89,20 @@ def test_ngram_drafter_on_repetitive_text():
     out = gen.generate(prompts, 12)
     agree, total = _teacher_forced_agreement(cfg, w, prompts, out)
     assert total > 6 and agree / total >= 0.9
+
+
+def test_sampled_speculation_runs_and_is_seed_reproducible():
+    from ninfer_fusion_b200.runtime.program import SamplingParams
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cuda", seed=9, std=0.05, with_mtp=True)
+    prompts = [list(range(5, 45)), list(range(100, 118))]
+
+    def run(seed):
+        gen = SpeculativeGenerator(cfg, w, "cuda", max_batch=2, max_context=512, draft_tokens=3, drafter="mtp",
+                                   sampling=SamplingParams(temperature=0.8, top_k=8, top_p=0.95, seed=seed),
+                                   kv_format="bf16", page_size=16, prefill_chunk=64)
+        return gen.generate(prompts, 14), gen.tokens_per_round
+    a, tpr = run(11)
+    b, _ = run(11)
+    c, _ = run(12)
+    assert a == b and a != c and all(len(o) == 14 for o in a) and tpr >= 1.0
