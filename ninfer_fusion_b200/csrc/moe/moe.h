@@ -112,8 +112,16 @@ struct MoeGemmArgs {
   unsigned int* peer_ret_flag[kMoeMaxRanks] = {};
   int* status = nullptr;
   cudaStream_t stream = nullptr;
+  // fp8 block-scaled experts (moe_gemm_fp8): w / x are e4m3 codes, scales are fp32
+  const float* w_scale = nullptr;   // [experts, rows_per_expert / 128, K / 128]
+  const float* x_scale = nullptr;   // [cap, K / 128]
 };
 const char* moe_gemm(const MoeGemmArgs& a);
+// Same tile walk over e4m3 weights with 128 x 128 block scales and activations quantised per row and 128-wide k-block.
+const char* moe_gemm_fp8(const MoeGemmArgs& a);
+// Quantises the first min(max_rows, state->total_rows) rows of x [max_rows, K] (state may be null: all rows).
+const char* moe_quant_rows_block128(const __nv_bfloat16* x, long long ldx, int max_rows, int K, const MoeState* state,
+                                    uint8_t* codes, float* scales, cudaStream_t stream);
 // Token-tile width for an expected number of rows per expert.
 int moe_tile_tokens(double rows_per_expert);
 

@@ -144,6 +144,61 @@ void moe_gemm(const Tensor& x, const Tensor& w, int64_t epi, int64_t tile_tokens
   chk(nfb::moe_gemm(a));
 }
 
+// fp8 block-scaled variant: x [cap, K] and w [experts, rows, K] are uint8 e4m3 codes.
+void moe_gemm_fp8(const Tensor& x, const Tensor& x_scale, const Tensor& w, const Tensor& w_scale, int64_t epi,
+                  int64_t tile_tokens, int64_t max_tiles, const Tensor& tiles, const Tensor& state, OptT out, int64_t world,
+                  OptT recv_meta, at::IntArrayRef peer_bases, int64_t ret_off, int64_t ret_flag_off, OptT status) {
+  need(x, at::kByte, "x"); need(w, at::kByte, "w"); need(tiles, at::kInt, "tiles");
+  need(x_scale, at::kFloat, "x_scale"); need(w_scale, at::kFloat, "w_scale");
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 3 && w.is_contiguous() && x.size(1) == w.size(2), "moe_gemm_fp8: shapes");
+  TORCH_CHECK(tiles.dim() == 2 && tiles.size(0) == 3 && tiles.is_contiguous() && max_tiles <= tiles.size(1));
+  const int64_t nkb = w.size(2) / 128;
+  TORCH_CHECK(w_scale.is_contiguous() && w_scale.numel() == w.size(0) * (w.size(1) / 128) * nkb, "moe_gemm_fp8: w_scale shape");
+  TORCH_CHECK(x_scale.is_contiguous() && x_scale.numel() >= x.size(0) * nkb, "moe_gemm_fp8: x_scale shape");
+  c10::cuda::CUDAGuard guard(x.device());
+  nfb::MoeGemmArgs a;
+  a.w = w.data_ptr(); a.n_local_experts = static_cast<int>(w.size(0)); a.rows_per_expert = w.size(1);
+  a.K = w.size(2); a.ldw = w.size(2);
+  a.x = x.data_ptr(); a.cap = x.size(0); a.ldx = x.stride(0);
+  a.w_scale = static_cast<const float*>(w_scale.data_ptr()); a.x_scale = static_cast<const float*>(x_scale.data_ptr());
+  a.tile_tokens = static_cast<int>(tile_tokens); a.max_tiles = static_cast<int>(max_tiles);
+  const int* t = static_cast<const int*>(tiles.data_ptr());
+  const int64_t stride = tiles.size(1);
+  a.tile_expert = t; a.tile_row0 = t + stride; a.tile_rows = t + 2 * stride;
+  a.state = state_ptr(state);
+  a.epi = static_cast<int>(epi);
+  if (epi == nfb::kMoeEpiSwiglu) {
+    TORCH_CHECK(out.has_value() && out->defined(), "moe_gemm_fp8: out required");
+    need(*out, at::kBFloat16, "out");
+    TORCH_CHECK(out->dim() == 2 && out->size(0) >= x.size(0) && out->size(1) == w.size(1) / 2, "moe_gemm_fp8: out shape");
+    a.out = out->data_ptr(); a.ldo = out->stride(0);
+  } else {
+    TORCH_CHECK(recv_meta.has_value() && recv_meta->defined(), "moe_gemm_fp8: recv_meta required");
+    need(*recv_meta, at::kInt, "recv_meta");
+    TORCH_CHECK(static_cast<int64_t>(peer_bases.size()) == world && world <= nfb::kMoeMaxRanks, "peer_bases size");
+    a.world = static_cast<int>(world);
+    a.recv_meta = static_cast<const int*>(recv_meta->data_ptr());
+    for (int r = 0; r < world; ++r) {
+      a.peer_ret[r] = reinterpret_cast<__nv_bfloat16*>(peer_bases[r] + ret_off);
+      a.peer_ret_flag[r] = reinterpret_cast<unsigned int*>(peer_bases[r] + ret_flag_off);
+    }
+  }
+  a.status = ptr_or_null<int>(status);
+  a.stream = cur_stream();
+  chk(nfb::moe_gemm_fp8(a));
+}
+
+void moe_quant_rows_block128(const Tensor& x, const Tensor& codes, const Tensor& scales, OptT state) {
+  need(x, at::kBFloat16, "x"); need(codes, at::kByte, "codes"); need(scales, at::kFloat, "scales");
+  TORCH_CHECK(x.dim() == 2 && codes.is_contiguous() && codes.numel() >= x.numel() && scales.is_contiguous() &&
+              scales.numel() >= x.size(0) * (x.size(1) / 128), "moe_quant_rows_block128: shapes");
+  c10::cuda::CUDAGuard guard(x.device());
+  const nfb::MoeState* st = state.has_value() && state->defined() ? state_ptr(*state) : nullptr;
+  chk(nfb::moe_quant_rows_block128(static_cast<const __nv_bfloat16*>(x.data_ptr()), x.stride(0), static_cast<int>(x.size(0)),
+                                   static_cast<int>(x.size(1)), st, static_cast<uint8_t*>(codes.data_ptr()),
+                                   static_cast<float*>(scales.data_ptr()), cur_stream()));
+}
+
 void moe_combine(const Tensor& x, const Tensor& weights, const Tensor& ret, int64_t my_base, int64_t ret_flag_off,
                  OptT shared, OptT shared_gate, OptT norm_w, OptT normed, double eps, const Tensor& state, OptT status) {
   need(x, at::kBFloat16, "x"); need(weights, at::kFloat, "weights"); need(ret, at::kBFloat16, "ret");
@@ -188,6 +243,8 @@ TORCH_LIBRARY_FRAGMENT(nfb200, m) {
   m.def("moe_plan(int world, int rank, int E, int tile_tokens, int cap, Tensor hist, int[] peer_bases, int counts_off, int count_flag_off, Tensor send_base, Tensor tiles, Tensor state, Tensor? status) -> ()", &moe_plan);
   m.def("moe_push(int world, int rank, int E, int cap, Tensor x, Tensor ids, Tensor pos, Tensor send_base, int[] peer_bases, int recv_x_off, int recv_meta_off, int arrive_flag_off, Tensor state, Tensor? status) -> ()", &moe_push);
   m.def("moe_gemm(Tensor x, Tensor w, int epi, int tile_tokens, int max_tiles, Tensor tiles, Tensor state, Tensor? out, int world, Tensor? recv_meta, int[] peer_bases, int ret_off, int ret_flag_off, Tensor? status) -> ()", &moe_gemm);
+  m.def("moe_gemm_fp8(Tensor x, Tensor x_scale, Tensor w, Tensor w_scale, int epi, int tile_tokens, int max_tiles, Tensor tiles, Tensor state, Tensor? out, int world, Tensor? recv_meta, int[] peer_bases, int ret_off, int ret_flag_off, Tensor? status) -> ()", &moe_gemm_fp8);
+  m.def("moe_quant_rows_block128(Tensor x, Tensor codes, Tensor scales, Tensor? state) -> ()", &moe_quant_rows_block128);
   m.def("moe_combine(Tensor x, Tensor weights, Tensor ret, int my_base, int ret_flag_off, Tensor? shared, Tensor? shared_gate, Tensor? norm_w, Tensor? normed, float eps, Tensor state, Tensor? status) -> ()", &moe_combine);
   m.def("moe_state_bytes() -> int", &moe_state_bytes);
   m.def("moe_tile_tokens(float rows_per_expert) -> int", &moe_tile_tokens);

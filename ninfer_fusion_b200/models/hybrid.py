@@ -233,6 +233,7 @@ class HybridModel:
         self._qkeep: List[tuple] = []
         self.moe = None   # models.moe.MoeBlock, created with the first workspace that runs a MoE layer
         self.ep = (ep_rank, ep_world, ep_group)  # expert parallelism: experts split, the rest data-parallel
+        self.expert_format = "bf16"   # "fp8_block": routed experts as e4m3 with 128 x 128 block scales
         self.moe_global_tokens: Optional[int] = None  # bound on the tokens of all ranks in a step (default world * T)
         # layer index -> index among attention / GDN layers
         self._attn_idx = {l: i for i, l in enumerate(cfg.attn_layers)}
@@ -437,7 +438,7 @@ class HybridModel:
         else:
             if self.moe is None or self.moe.max_tokens < ws.max_tokens:
                 from .moe import MoeBlock
-                self.moe = MoeBlock(cfg, self.device, ws.max_tokens, *self.ep)
+                self.moe = MoeBlock(cfg, self.device, ws.max_tokens, *self.ep, expert_format=self.expert_format)
             self.moe.forward(self, ws, T, p, w["mtp/final_norm"], ws.normed[:T], self.moe_global_tokens)
         return ws.normed[:T]
 
@@ -466,7 +467,7 @@ class HybridModel:
             else:
                 if self.moe is None or self.moe.max_tokens < ws.max_tokens:
                     from .moe import MoeBlock
-                    self.moe = MoeBlock(cfg, self.device, ws.max_tokens, *self.ep)
+                    self.moe = MoeBlock(cfg, self.device, ws.max_tokens, *self.ep, expert_format=self.expert_format)
                 self.moe.forward(self, ws, T, p, nxt, ws.normed[:T], self.moe_global_tokens)
         return ws.normed[:T]
 

@@ -37,12 +37,18 @@ def _align(n: int, a: int = 256) -> int:
 class MoeBlock:
     """Buffers and launch sequence of the MoE block, shared by all layers of a model."""
 
-    def __init__(self, cfg: ModelConfig, device, max_tokens: int, rank: int = 0, world: int = 1, group=None):
+    def __init__(self, cfg: ModelConfig, device, max_tokens: int, rank: int = 0, world: int = 1, group=None,
+                 expert_format: str = "bf16"):
         if cfg.moe is None:
             raise ValueError("model has no MoE configuration")
         m = cfg.moe
         if m.n_experts % world:
             raise ValueError(f"{m.n_experts} experts do not divide over {world} ranks")
+        if expert_format not in ("bf16", "fp8_block"):
+            raise ValueError("expert_format must be 'bf16' or 'fp8_block'")
+        if expert_format == "fp8_block" and (cfg.hidden % 128 or m.expert_inter % 128):
+            raise ValueError("fp8 128x128 block-scaled experts need hidden and expert_inter in multiples of 128")
+        self.expert_format = expert_format
         self.cfg, self.rank, self.world, self.group = cfg, rank, world, group
         self.device = torch.device(device)
         self.ops = load_native()
@@ -86,6 +92,12 @@ class MoeBlock:
         self.tiles = torch.zeros((3, self.max_tiles_cap), dtype=i32, device=dev)
         self.state = torch.zeros(int(self.ops.moe_state_bytes()), dtype=torch.uint8, device=dev)
         self.act = torch.empty((self.cap, m.expert_inter), dtype=torch.bfloat16, device=dev)
+        if expert_format == "fp8_block":
+            u8, f32 = torch.uint8, torch.float32
+            self.recv_q = torch.empty((self.cap, H), dtype=u8, device=dev)
+            self.recv_qs = torch.empty((self.cap, H // 128), dtype=f32, device=dev)
+            self.act_q = torch.empty((self.cap, m.expert_inter), dtype=u8, device=dev)
+            self.act_qs = torch.empty((self.cap, m.expert_inter // 128), dtype=f32, device=dev)
         self.router_cols = (E + 1 + 7) // 8 * 8
         self.logits = torch.empty((max_tokens, self.router_cols), dtype=torch.bfloat16, device=dev)
         self.shared_act = torch.empty((max_tokens, m.shared_inter), dtype=torch.bfloat16, device=dev)
@@ -117,6 +129,9 @@ class MoeBlock:
                 lo = self.rank * self.n_local
                 gu, dn = gu[lo: lo + self.n_local].contiguous(), dn[lo: lo + self.n_local].contiguous()
             t = (gu, dn)
+            if self.expert_format == "fp8_block" and gu.dtype != torch.uint8:
+                from ..ops import quant as Q
+                t = Q.quantize_fp8_block128(gu) + Q.quantize_fp8_block128(dn)   # (gu codes, gu scales, dn codes, dn scales)
             self._local_experts[prefix] = t
         return t
 
@@ -138,17 +153,28 @@ class MoeBlock:
         ops.moe_route(logits, E, k, m.norm_topk, True, self.hist, ids, wts, pos, sgate)
         g_tokens = W * T if global_tokens is None else global_tokens
         tn = int(ops.moe_tile_tokens(g_tokens * k / E))
+        if self.expert_format == "fp8_block":
+            tn = min(tn, 128)   # the two-level accumulation keeps one fp32 register per token of the tile
         rows_bound = min(self.cap, g_tokens * self.k_per_rank)
         max_tiles = min(self.max_tiles_cap, self.n_local + (rows_bound + tn - 1) // tn)
         ops.moe_plan(W, self.rank, E, tn, self.cap, self.hist, self.peer_bases, self.off["counts"],
                      self.off["count_flag"], self.send_base, self.tiles, self.state, status)
         ops.moe_push(W, self.rank, E, self.cap, normed, ids, pos, self.send_base, self.peer_bases,
                      self.off["recv_x"], self.off["recv_meta"], self.off["arrive_flag"], self.state, status)
-        gate_up, down = self._experts(model.w, prefix)
-        ops.moe_gemm(self.recv_x, gate_up, MOE_EPI_SWIGLU, tn, max_tiles, self.tiles, self.state, self.act, W, None,
-                     self.peer_bases, 0, 0, status)
-        ops.moe_gemm(self.act, down, MOE_EPI_RETURN, tn, max_tiles, self.tiles, self.state, None, W, self.recv_meta,
-                     self.peer_bases, self.off["ret"], self.off["ret_flag"], status)
+        if self.expert_format == "fp8_block":
+            gu_q, gu_s, dn_q, dn_s = self._experts(model.w, prefix)
+            ops.moe_quant_rows_block128(self.recv_x, self.recv_q, self.recv_qs, self.state)
+            ops.moe_gemm_fp8(self.recv_q, self.recv_qs, gu_q, gu_s, MOE_EPI_SWIGLU, tn, max_tiles, self.tiles, self.state,
+                             self.act, W, None, self.peer_bases, 0, 0, status)
+            ops.moe_quant_rows_block128(self.act, self.act_q, self.act_qs, self.state)
+            ops.moe_gemm_fp8(self.act_q, self.act_qs, dn_q, dn_s, MOE_EPI_RETURN, tn, max_tiles, self.tiles, self.state,
+                             None, W, self.recv_meta, self.peer_bases, self.off["ret"], self.off["ret_flag"], status)
+        else:
+            gate_up, down = self._experts(model.w, prefix)
+            ops.moe_gemm(self.recv_x, gate_up, MOE_EPI_SWIGLU, tn, max_tiles, self.tiles, self.state, self.act, W, None,
+                         self.peer_bases, 0, 0, status)
+            ops.moe_gemm(self.act, down, MOE_EPI_RETURN, tn, max_tiles, self.tiles, self.state, None, W, self.recv_meta,
+                         self.peer_bases, self.off["ret"], self.off["ret_flag"], status)
         # shared expert (replicated): dense SwiGLU MLP on the local tokens
         sact, sout = self.shared_act[:T], self.shared_out[:T]
         model._gemm(normed, model.w[f"{prefix}/moe/shared_gate_up"], sact, EPI_SWIGLU)

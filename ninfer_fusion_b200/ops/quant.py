@@ -132,3 +132,26 @@ def fake_quant_fp8(x: torch.Tensor) -> torch.Tensor:
 
 def bf16(x: torch.Tensor) -> torch.Tensor:
     return x.to(torch.bfloat16).float()
+
+
+def quantize_fp8_block128(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """w [..., N, K] (N, K multiples of 128) -> (e4m3 codes uint8 [..., N, K], fp32 scales [..., N/128, K/128])."""
+    *lead, N, K = w.shape
+    blocks = w.float().reshape(*lead, N // 128, 128, K // 128, 128)
+    scale = (blocks.abs().amax(dim=(-3, -1)) / 448.0).clamp(min=1e-12)
+    codes = (blocks / scale[..., :, None, :, None]).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+    return codes.reshape(*lead, N, K).contiguous(), scale.float().contiguous()
+
+
+def dequant_fp8_block128(codes: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    *lead, N, K = codes.shape
+    v = codes.view(torch.float8_e4m3fn).float().reshape(*lead, N // 128, 128, K // 128, 128)
+    return (v * scale[..., :, None, :, None]).reshape(*lead, N, K)
+
+
+def fake_quant_fp8_block128_rows(x: torch.Tensor) -> torch.Tensor:
+    """Activation quantisation of the fp8 block-scaled expert path as a value map: per row and 128-wide k-block."""
+    T, K = x.shape
+    g = bf16(x).reshape(T, K // 128, 128)
+    scale = (g.abs().amax(-1, keepdim=True) / 448.0).clamp(min=1e-12)
+    return ((g / scale).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).float() * scale).reshape(T, K)

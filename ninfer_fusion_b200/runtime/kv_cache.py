@@ -53,34 +53,87 @@ class KvLayerPlanes:
         return n
 
 
-class PagePool:
-    """Free-list page allocator with per-row page lists (host side)."""
+def _load_pool_lib():
+    import ctypes
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "_C.so")
+    if not os.path.exists(path):
+        return None
+    try:
+        lib = ctypes.CDLL(path)
+        lib.nfb200_pool_create.restype = ctypes.c_void_p
+        lib.nfb200_pool_create.argtypes = [ctypes.c_int32]
+        lib.nfb200_pool_destroy.argtypes = [ctypes.c_void_p]
+        for name in ("free_pages", "alloc"):
+            getattr(lib, f"nfb200_pool_{name}").restype = ctypes.c_int32
+            getattr(lib, f"nfb200_pool_{name}").argtypes = [ctypes.c_void_p]
+        for name in ("retain", "release", "refcount"):
+            getattr(lib, f"nfb200_pool_{name}").restype = ctypes.c_int32
+            getattr(lib, f"nfb200_pool_{name}").argtypes = [ctypes.c_void_p, ctypes.c_int32]
+        return lib
+    except (OSError, AttributeError):
+        return None
 
-    def __init__(self, n_pages: int):
+
+class PagePool:
+    """Reference-counted page allocator.  The bookkeeping runs in native code (csrc/runtime/page_pool.cpp) when the
+    library is built; the pure-Python twin has the same semantics."""
+
+    def __init__(self, n_pages: int, use_native: bool = True):
         self.n_pages = n_pages
-        self._free: List[int] = list(range(n_pages - 1, -1, -1))
-        self.refcount = [0] * n_pages
+        self._lib = _load_pool_lib() if use_native else None
+        self._h = self._lib.nfb200_pool_create(n_pages) if self._lib is not None else None
+        if self._h is None:
+            self._free: List[int] = list(range(n_pages - 1, -1, -1))
+            self._ref = [0] * n_pages
+
+    def __del__(self):
+        if getattr(self, "_h", None) is not None:
+            self._lib.nfb200_pool_destroy(self._h)
+            self._h = None
+
+    @property
+    def native(self) -> bool:
+        return self._h is not None
 
     @property
     def free_pages(self) -> int:
-        return len(self._free)
+        return int(self._lib.nfb200_pool_free_pages(self._h)) if self._h is not None else len(self._free)
+
+    def refcount_of(self, page: int) -> int:
+        return int(self._lib.nfb200_pool_refcount(self._h, page)) if self._h is not None else self._ref[page]
 
     def alloc(self) -> int:
+        if self._h is not None:
+            p = int(self._lib.nfb200_pool_alloc(self._h))
+            if p < 0:
+                raise MemoryError("KV page pool exhausted")
+            return p
         if not self._free:
             raise MemoryError("KV page pool exhausted")
         p = self._free.pop()
-        self.refcount[p] = 1
+        self._ref[p] = 1
         return p
 
     def retain(self, page: int) -> None:
-        self.refcount[page] += 1
+        if self._h is not None:
+            if self._lib.nfb200_pool_retain(self._h, page) < 0:
+                raise RuntimeError(f"page {page} is not allocated")
+            return
+        if self._ref[page] <= 0:
+            raise RuntimeError(f"page {page} is not allocated")
+        self._ref[page] += 1
 
     def release(self, page: int) -> None:
-        self.refcount[page] -= 1
-        if self.refcount[page] == 0:
-            self._free.append(page)
-        elif self.refcount[page] < 0:
+        if self._h is not None:
+            if self._lib.nfb200_pool_release(self._h, page) < 0:
+                raise RuntimeError(f"page {page} released twice")
+            return
+        if self._ref[page] <= 0:
             raise RuntimeError(f"page {page} released twice")
+        self._ref[page] -= 1
+        if self._ref[page] == 0:
+            self._free.append(page)
 
 
 class PagedKvCache:

@@ -78,3 +78,50 @@ def test_moe_greedy_generation_matches_reference():
                 agree += int(int(R.argmax_lowest(lg[None])[0]) == out[b][j])
             hid = ref.forward(seq, torch.tensor([out[b][j]]))
     assert total > 8 and agree / total >= 0.9, f"{agree}/{total}"
+
+
+@pytest.mark.parametrize("cfg", [TINY_MOE, MID_MOE], ids=lambda c: c.name)
+@pytest.mark.parametrize("T", [3, 40, 300])
+def test_moe_block_fp8_block_scaled_experts(cfg, T):
+    """Routed experts as e4m3 with 128x128 block scales (two-level accumulation kernel) against an oracle that uses
+    the de-quantised expert weights and the same per-row / per-128 activation quantisation."""
+    from ninfer_fusion_b200.ops import quant as Q
+    torch.manual_seed(T)
+    w = random_weights(cfg, "cuda", seed=3, std=0.05)
+    model = HybridModel(cfg, w, "cuda")
+    ws = Workspace(cfg, 512, 8, "cuda")
+    p = "text/layers/1"
+    m = cfg.moe
+    x0 = (torch.randn(T, cfg.hidden, device="cuda") * 0.5).bfloat16()
+    h = torch.randn(T, cfg.hidden, device="cuda").bfloat16()
+    nxt = w["text/layers/2/input_norm"]
+    model.moe = MoeBlock(cfg, "cuda", ws.max_tokens, expert_format="fp8_block")
+    for rep in range(2):
+        ws.x[:T].copy_(x0)
+        ws.normed[:T].copy_(h)
+        model.moe.forward(model, ws, T, p, nxt, ws.normed[:T])
+        torch.cuda.synchronize()
+        model.status.check()
+    # oracle
+    hf = h.float().cpu()
+    router = R.bf16_round(hf @ w[f"{p}/moe/router"].float().cpu().t())
+    wts, ids = R.moe_route(router[:, : m.n_experts], m.top_k, True)
+    gu = Q.dequant_fp8_block128(*Q.quantize_fp8_block128(w[f"{p}/moe/experts_gate_up"])).cpu()
+    dn = Q.dequant_fp8_block128(*Q.quantize_fp8_block128(w[f"{p}/moe/experts_down"])).cpu()
+    hq = Q.fake_quant_fp8_block128_rows(hf)
+    out = torch.zeros(T, cfg.hidden)
+    for t in range(T):
+        for j in range(m.top_k):
+            e = int(ids[t, j])
+            g = hq[t] @ gu[e].t()
+            act = R.bf16_round(torch.nn.functional.silu(g[: m.expert_inter]) * g[m.expert_inter:])
+            y = R.bf16_round(Q.fake_quant_fp8_block128_rows(act[None])[0] @ dn[e].t())
+            out[t] += wts[t, j] * y
+    sg = hf @ w[f"{p}/moe/shared_gate_up"].float().cpu().t()
+    sact = R.bf16_round(torch.nn.functional.silu(sg[:, : m.shared_inter]) * sg[:, m.shared_inter:])
+    shared = R.bf16_round(sact @ w[f"{p}/moe/shared_down"].float().cpu().t())
+    want = R.bf16_round(x0.float().cpu() + out + torch.sigmoid(router[:, m.n_experts:]) * shared)
+    same = (model.moe.ids[:T].cpu().long() == ids).all(-1)
+    assert same.float().mean().item() >= 0.97
+    err = (ws.x[:T].float().cpu() - want)[same].abs().max().item()
+    assert err <= 0.02 * want.abs().max().item() + 0.02, err
