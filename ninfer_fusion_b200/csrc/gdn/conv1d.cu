@@ -25,6 +25,21 @@ __device__ __forceinline__ float2 tap(const ConvParams& p, int tau, int seq_star
   return ld2(p.conv_state + (static_cast<long long>(slot) * 3 + j) * p.C + c);
 }
 
+// Token index `back` steps before t: along the draft tree's parent links while inside the window, then into the
+// history (indices below seq_start).
+__device__ __forceinline__ int ancestor(const ConvParams& p, int t, int back, int seq_start) {
+  int cur = t;
+  for (int i = 0; i < back; ++i) {
+    if (p.parent != nullptr && cur >= seq_start) {
+      const int par = p.parent[cur];
+      cur = par >= 0 ? par : seq_start - 1;
+    } else {
+      cur -= 1;
+    }
+  }
+  return cur;
+}
+
 __global__ void __launch_bounds__(128) conv1d_silu_kernel(const ConvParams p) {
   pdl_launch_next();
   pdl_wait_prior();
@@ -40,7 +55,7 @@ __global__ void __launch_bounds__(128) conv1d_silu_kernel(const ConvParams p) {
   float a0 = 0.f, a1 = 0.f;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const float2 x = tap(p, t - 3 + j, start, slot, c);
+    const float2 x = tap(p, ancestor(p, t, 3 - j, start), start, slot, c);
     a0 += __bfloat162float(wp[j]) * x.x;
     a1 += __bfloat162float(wp[4 + j]) * x.y;
   }
@@ -58,9 +73,11 @@ __global__ void __launch_bounds__(128) conv1d_state_kernel(const ConvParams p) {
   const int start = p.cu_seqlens[seq], end = p.seq_end != nullptr ? p.seq_end[seq] : p.cu_seqlens[seq + 1];
   if (end <= start) return;
   const int slot = p.state_slot[seq];
+  // the new history = the last three inputs along the (accepted) path that ends at `last`
+  const int last = p.last_token != nullptr ? p.last_token[seq] : end - 1;
   float2 v[3];
 #pragma unroll
-  for (int j = 0; j < 3; ++j) v[j] = tap(p, end - 3 + j, start, slot, c);
+  for (int j = 0; j < 3; ++j) v[j] = tap(p, ancestor(p, last, 2 - j, start), start, slot, c);
 #pragma unroll
   for (int j = 0; j < 3; ++j)
     *reinterpret_cast<uint32_t*>(p.conv_state + (static_cast<long long>(slot) * 3 + j) * p.C + c) =

@@ -23,6 +23,11 @@ struct ConvParams {
   int one_token_per_seq;     // decode: token i belongs to sequence i; conv + history roll in one launch
   const int* seq_end = nullptr;  // optional [n_seq]: sequence s covers [cu_seqlens[s], seq_end[s]) (accepted prefix of a verify)
   int state_only = 0;        // only roll the history forward (replay of an accepted prefix), no output
+  // Tree verification (optional): parent[t] = token index of t's parent in the draft tree, or -1 for the first
+  // token of the window (its predecessors are the sequence's history).  The taps of a token follow its ancestors
+  // instead of the preceding buffer rows.  With `last_token` (per sequence) the history roll ends at that token.
+  const int* parent = nullptr;
+  const int* last_token = nullptr;
 };
 const char* causal_conv1d_silu(const ConvParams& p, cudaStream_t stream, bool pdl);
 
@@ -49,6 +54,10 @@ struct GdnParams {
   int write_state;           // 0: verify pass, state untouched
   __nv_bfloat16* out;        // [T, Hv * 128]
   const int* seq_end = nullptr;  // optional [n_seq]: sequence s covers [cu_seqlens[s], seq_end[s])
+  // Tree verification / selective replay (optional, per token): commit[t] = 0 means "side branch": the token sees
+  // the current state, produces its output, and leaves the state as it was.  Tokens are visited in buffer order, so
+  // a side branch must directly follow the state it hangs off.
+  const unsigned char* commit = nullptr;
 };
 const char* gdn_recurrent(const GdnParams& p, cudaStream_t stream, bool pdl);
 // Multi-token variant (token groups staged in shared memory); gdn_recurrent dispatches to it when T > n_seq.

@@ -30,6 +30,8 @@ struct PrefillSmem {
   float qn[kTG][kD];
   float o[kTG][kD];
   float alpha[kTG], beta[kTG];
+  float kdq[kTG];  // k . q of the normalised vectors (side-branch tokens)
+  int cm[kTG];     // commit flag per token
 };
 
 __device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
@@ -134,6 +136,15 @@ __global__ void __launch_bounds__(kThreads, 1) gdn_prefill_kernel(const GdnParam
           sm.qn[tok][part * 8 + i] = qf[i] * iq;
         }
       }
+      {
+        // k . q over the token's 16 lanes (raw dot, scaled by both normalisers)
+        float d = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d += kf[i] * qf[i];
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        if (valid && part == 0) sm.kdq[tok] = d * rsqrtf(ssk + 1e-6f) * rsqrtf(ssq + 1e-6f) * qscale;
+      }
       if (threadIdx.x < n_tok) {
         const __nv_bfloat16* prow = p.proj + static_cast<long long>(t0 + threadIdx.x) * p.ld_proj;
         const float a = __bfloat162float(prow[p.a_off + hv]);
@@ -142,6 +153,7 @@ __global__ void __launch_bounds__(kThreads, 1) gdn_prefill_kernel(const GdnParam
         const float sp_x = x > 20.f ? x : log1pf(__expf(x));
         sm.alpha[threadIdx.x] = __expf(neg_a * sp_x);
         sm.beta[threadIdx.x] = 1.f / (1.f + __expf(-b));
+        sm.cm[threadIdx.x] = (p.commit == nullptr || p.commit[t0 + threadIdx.x] != 0) ? 1 : 0;
       }
     }
     __syncthreads();
@@ -155,6 +167,8 @@ __global__ void __launch_bounds__(kThreads, 1) gdn_prefill_kernel(const GdnParam
         q4[i] = reinterpret_cast<const float4*>(sm.qn[tk])[q8 + 8 * i];
       }
       const float alpha = sm.alpha[tk], beta = sm.beta[tk];
+      const bool cm = sm.cm[tk] != 0;
+      const float kqv = sm.kdq[tk];
       float o[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -171,17 +185,25 @@ __global__ void __launch_bounds__(kThreads, 1) gdn_prefill_kernel(const GdnParam
         ks += __shfl_xor_sync(0xffffffffu, ks, 4);
         const float u = beta * (v - alpha * ks);
         float oj = 0.f;
+        if (cm) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          S[j][i].x = alpha * S[j][i].x + u * k4[i].x;
-          S[j][i].y = alpha * S[j][i].y + u * k4[i].y;
-          S[j][i].z = alpha * S[j][i].z + u * k4[i].z;
-          S[j][i].w = alpha * S[j][i].w + u * k4[i].w;
-          oj += S[j][i].x * q4[i].x + S[j][i].y * q4[i].y + S[j][i].z * q4[i].z + S[j][i].w * q4[i].w;
+          for (int i = 0; i < 4; ++i) {
+            S[j][i].x = alpha * S[j][i].x + u * k4[i].x;
+            S[j][i].y = alpha * S[j][i].y + u * k4[i].y;
+            S[j][i].z = alpha * S[j][i].z + u * k4[i].z;
+            S[j][i].w = alpha * S[j][i].w + u * k4[i].w;
+            oj += S[j][i].x * q4[i].x + S[j][i].y * q4[i].y + S[j][i].z * q4[i].z + S[j][i].w * q4[i].w;
+          }
+        } else {   // side branch: the state stays, o = alpha * (S q) + u * (k . q)
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            oj += S[j][i].x * q4[i].x + S[j][i].y * q4[i].y + S[j][i].z * q4[i].z + S[j][i].w * q4[i].w;
+          oj *= alpha;
         }
         oj += __shfl_xor_sync(0xffffffffu, oj, 1);
         oj += __shfl_xor_sync(0xffffffffu, oj, 2);
         oj += __shfl_xor_sync(0xffffffffu, oj, 4);
+        if (!cm) oj += u * kqv;
         o[j] = oj;
       }
       if (q8 < 4) {
@@ -255,6 +277,8 @@ struct SplitSmem {
   float qn[kTGS][kD];
   float o[kTGS][ROWS];
   float alpha[kTGS], beta[kTGS];
+  float kdq[kTGS];                       // k . q of the normalised vectors (side-branch tokens)
+  int cm[kTGS];                          // commit flag per token
   float part[2][kTGS];                   // partial sum of squares per token, by group parity
 };
 
@@ -393,6 +417,15 @@ __global__ void __launch_bounds__(THREADS, 2) gdn_prefill_split_kernel(const Gdn
           sm.qn[tok][part * 8 + i] = qf[i] * iq;
         }
       }
+      {
+        // k . q over the token's 16 lanes (raw dot, scaled by both normalisers)
+        float d = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d += kf[i] * qf[i];
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        if (valid && part == 0) sm.kdq[tok] = d * rsqrtf(ssk + 1e-6f) * rsqrtf(ssq + 1e-6f) * qscale;
+      }
     }
     if (threadIdx.x < n_tok) {
       const float a = ga, b = gb;
@@ -400,6 +433,7 @@ __global__ void __launch_bounds__(THREADS, 2) gdn_prefill_split_kernel(const Gdn
       const float sp_x = x > 20.f ? x : log1pf(__expf(x));
       sm.alpha[threadIdx.x] = __expf(neg_a * sp_x);
       sm.beta[threadIdx.x] = 1.f / (1.f + __expf(-b));
+      sm.cm[threadIdx.x] = (p.commit == nullptr || p.commit[t0 + threadIdx.x] != 0) ? 1 : 0;
     }
     if (g + 1 < n_groups) load_gates(g + 1);  // lands while the serial steps run
     __syncthreads();
@@ -411,7 +445,9 @@ __global__ void __launch_bounds__(THREADS, 2) gdn_prefill_split_kernel(const Gdn
     {
       float4 k4[4], q4[4];
       float vv[RPT], alpha, beta;
-      auto load_tok = [&](int tk, float4* kk, float4* qq, float* vr, float& al, float& be) {
+      auto load_tok = [&](int tk, float4* kk, float4* qq, float* vr, float& al, float& be, float& kqo, int& cmo) {
+        kqo = sm.kdq[tk];
+        cmo = sm.cm[tk];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           kk[i] = reinterpret_cast<const float4*>(sm.kn[tk])[q8 + 8 * i];
@@ -422,15 +458,18 @@ __global__ void __launch_bounds__(THREADS, 2) gdn_prefill_split_kernel(const Gdn
         al = sm.alpha[tk];
         be = sm.beta[tk];
       };
-      load_tok(0, k4, q4, vv, alpha, beta);
+      float kqv = 0.f;
+      int cmv = 1;
+      load_tok(0, k4, q4, vv, alpha, beta, kqv, cmv);
       float o_pend[RPT];
 #pragma unroll
       for (int j = 0; j < RPT; ++j) o_pend[j] = 0.f;
       // one token: `c*` = operands of this token, `n*` = registers that receive the next token's operands
       auto step = [&](int tk, const float4* ck4, const float4* cq4, const float* cv, float calpha, float cbeta,
-                      float4* nk4, float4* nq4, float* nv, float& nalpha, float& nbeta) {
+                      float ckq, int ccm, float4* nk4, float4* nq4, float* nv, float& nalpha, float& nbeta,
+                      float& nkq, int& ncm) {
         const int tn = tk + 1 < n_tok ? tk + 1 : tk;
-        load_tok(tn, nk4, nq4, nv, nalpha, nbeta);
+        load_tok(tn, nk4, nq4, nv, nalpha, nbeta, nkq, ncm);
         float ks[RPT];
 #pragma unroll
         for (int j = 0; j < RPT; ++j) {
@@ -460,23 +499,33 @@ __global__ void __launch_bounds__(THREADS, 2) gdn_prefill_split_kernel(const Gdn
         for (int j = 0; j < RPT; ++j) {
           const float u = cbeta * (cv[j] - calpha * ks[j]);
           float oj = 0.f;
+          if (ccm) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            S[j][i].x = calpha * S[j][i].x + u * ck4[i].x;
-            S[j][i].y = calpha * S[j][i].y + u * ck4[i].y;
-            S[j][i].z = calpha * S[j][i].z + u * ck4[i].z;
-            S[j][i].w = calpha * S[j][i].w + u * ck4[i].w;
-            oj += S[j][i].x * cq4[i].x + S[j][i].y * cq4[i].y + S[j][i].z * cq4[i].z + S[j][i].w * cq4[i].w;
+            for (int i = 0; i < 4; ++i) {
+              S[j][i].x = calpha * S[j][i].x + u * ck4[i].x;
+              S[j][i].y = calpha * S[j][i].y + u * ck4[i].y;
+              S[j][i].z = calpha * S[j][i].z + u * ck4[i].z;
+              S[j][i].w = calpha * S[j][i].w + u * ck4[i].w;
+              oj += S[j][i].x * cq4[i].x + S[j][i].y * cq4[i].y + S[j][i].z * cq4[i].z + S[j][i].w * cq4[i].w;
+            }
+          } else {
+            // side branch: o = alpha * (S q) + u * (k . q); the (k . q) term belongs to one lane of the row only,
+            // because the eight lanes' partial sums are added up afterwards
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              oj += S[j][i].x * cq4[i].x + S[j][i].y * cq4[i].y + S[j][i].z * cq4[i].z + S[j][i].w * cq4[i].w;
+            oj = calpha * oj + (q8 == 0 ? u * ckq : 0.f);
           }
           o_pend[j] = oj;
         }
       };
       // two tokens per trip with ping-pong operand registers (no register-to-register copies)
       float4 k4b[4], q4b[4];
-      float vvb[RPT], alphab = 0.f, betab = 0.f;
+      float vvb[RPT], alphab = 0.f, betab = 0.f, kqb = 0.f;
+      int cmb = 1;
       for (int tk = 0; tk < n_tok; tk += 2) {
-        step(tk, k4, q4, vv, alpha, beta, k4b, q4b, vvb, alphab, betab);
-        if (tk + 1 < n_tok) step(tk + 1, k4b, q4b, vvb, alphab, betab, k4, q4, vv, alpha, beta);
+        step(tk, k4, q4, vv, alpha, beta, kqv, cmv, k4b, q4b, vvb, alphab, betab, kqb, cmb);
+        if (tk + 1 < n_tok) step(tk + 1, k4b, q4b, vvb, alphab, betab, kqb, cmb, k4, q4, vv, alpha, beta, kqv, cmv);
       }
 #pragma unroll
       for (int j = 0; j < RPT; ++j) {

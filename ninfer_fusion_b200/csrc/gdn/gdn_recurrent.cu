@@ -83,6 +83,16 @@ __global__ void __launch_bounds__(kThreads, 2) gdn_recurrent_kernel(const GdnPar
     const float alpha = __expf(neg_a * sp_x);
     const float beta = 1.f / (1.f + __expf(-b));
 
+    // side-branch tokens (commit[t] == 0) read the state but do not change it:  o = alpha * (S q) + u * (k . q)
+    const bool cm = p.commit == nullptr || p.commit[t] != 0;
+    float kq = 0.f;
+    if (!cm) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) kq += k4[i].x * q4[i].x + k4[i].y * q4[i].y + k4[i].z * q4[i].z + k4[i].w * q4[i].w;
+      kq += __shfl_xor_sync(0xffffffffu, kq, 1);
+      kq += __shfl_xor_sync(0xffffffffu, kq, 2);
+      kq += __shfl_xor_sync(0xffffffffu, kq, 4);
+    }
     float o[kRowsPerThread];
     float sq = 0.f;
 #pragma unroll
@@ -100,17 +110,25 @@ __global__ void __launch_bounds__(kThreads, 2) gdn_recurrent_kernel(const GdnPar
       ks += __shfl_xor_sync(0xffffffffu, ks, 4);
       const float u = beta * (v - alpha * ks);
       float oj = 0.f;
+      if (cm) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        S[j][i].x = alpha * S[j][i].x + u * k4[i].x;
-        S[j][i].y = alpha * S[j][i].y + u * k4[i].y;
-        S[j][i].z = alpha * S[j][i].z + u * k4[i].z;
-        S[j][i].w = alpha * S[j][i].w + u * k4[i].w;
-        oj += S[j][i].x * q4[i].x + S[j][i].y * q4[i].y + S[j][i].z * q4[i].z + S[j][i].w * q4[i].w;
+        for (int i = 0; i < 4; ++i) {
+          S[j][i].x = alpha * S[j][i].x + u * k4[i].x;
+          S[j][i].y = alpha * S[j][i].y + u * k4[i].y;
+          S[j][i].z = alpha * S[j][i].z + u * k4[i].z;
+          S[j][i].w = alpha * S[j][i].w + u * k4[i].w;
+          oj += S[j][i].x * q4[i].x + S[j][i].y * q4[i].y + S[j][i].z * q4[i].z + S[j][i].w * q4[i].w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          oj += S[j][i].x * q4[i].x + S[j][i].y * q4[i].y + S[j][i].z * q4[i].z + S[j][i].w * q4[i].w;
+        oj *= alpha;
       }
       oj += __shfl_xor_sync(0xffffffffu, oj, 1);
       oj += __shfl_xor_sync(0xffffffffu, oj, 2);
       oj += __shfl_xor_sync(0xffffffffu, oj, 4);
+      if (!cm) oj += u * kq;
       oj = __bfloat162float(__float2bfloat16(oj));  // bf16 boundary before the head norm
       o[j] = oj;
       if (q8 == 0) sq += oj * oj;

@@ -295,7 +295,7 @@ int64_t prefill_attn_block_tokens(int64_t n_q_heads, int64_t n_kv_heads) {
 void causal_conv1d_silu(const Tensor& x, int64_t c_off, int64_t C, const Tensor& w, const Tensor& cu_seqlens,
                         const Tensor& token_seq, const Tensor& state_slot, const Tensor& conv_state,
                         const Tensor& out, bool update_state, bool one_token_per_seq, bool pdl, OptT seq_end,
-                        bool state_only) {
+                        bool state_only, OptT parent, OptT last_token) {
   need(x, at::kBFloat16, "x"); need_rows(x, "x"); need(w, at::kBFloat16, "w");
   need(cu_seqlens, at::kInt, "cu_seqlens"); need(token_seq, at::kInt, "token_seq");
   need(state_slot, at::kInt, "state_slot"); need(conv_state, at::kBFloat16, "conv_state");
@@ -323,6 +323,16 @@ void causal_conv1d_silu(const Tensor& x, int64_t c_off, int64_t C, const Tensor&
     p.seq_end = static_cast<const int*>(seq_end->data_ptr());
   }
   p.state_only = state_only ? 1 : 0;
+  if (parent.has_value() && parent->defined()) {
+    need(*parent, at::kInt, "parent");
+    TORCH_CHECK(parent->numel() == p.T && !one_token_per_seq, "parent [T], not with the decode fast path");
+    p.parent = static_cast<const int*>(parent->data_ptr());
+  }
+  if (last_token.has_value() && last_token->defined()) {
+    need(*last_token, at::kInt, "last_token");
+    TORCH_CHECK(last_token->numel() == p.n_seq, "last_token [n_seq]");
+    p.last_token = static_cast<const int*>(last_token->data_ptr());
+  }
   chk(nfb::causal_conv1d_silu(p, cur_stream(), pdl));
 }
 
@@ -330,7 +340,7 @@ void gdn_recurrent(const Tensor& qkv, int64_t q_off, int64_t k_off, int64_t v_of
                    int64_t a_off, int64_t b_off, int64_t n_qk_heads, int64_t n_v_heads, const Tensor& A_log,
                    const Tensor& dt_bias, const Tensor& norm_w, double eps, const Tensor& cu_seqlens,
                    const Tensor& state_slot, const Tensor& state, bool write_state, const Tensor& out, bool pdl,
-                   OptT seq_end) {
+                   OptT seq_end, OptT commit) {
   need(qkv, at::kBFloat16, "qkv"); need_rows(qkv, "qkv"); need(proj, at::kBFloat16, "proj"); need_rows(proj, "proj");
   need(A_log, at::kFloat, "A_log"); need(dt_bias, at::kFloat, "dt_bias"); need(norm_w, at::kBFloat16, "norm_w");
   need(cu_seqlens, at::kInt, "cu_seqlens"); need(state_slot, at::kInt, "state_slot");
@@ -359,6 +369,11 @@ void gdn_recurrent(const Tensor& qkv, int64_t q_off, int64_t k_off, int64_t v_of
     need(*seq_end, at::kInt, "seq_end");
     TORCH_CHECK(seq_end->numel() == p.n_seq, "seq_end [n_seq]");
     p.seq_end = static_cast<const int*>(seq_end->data_ptr());
+  }
+  if (commit.has_value() && commit->defined()) {
+    need(*commit, at::kByte, "commit");
+    TORCH_CHECK(commit->numel() == p.T, "commit [T]");
+    p.commit = static_cast<const unsigned char*>(commit->data_ptr());
   }
   chk(nfb::gdn_recurrent(p, cur_stream(), pdl));
 }
@@ -606,8 +621,8 @@ TORCH_LIBRARY(nfb200, m) {
   m.def("paged_attention(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, int split_keys, int n_splits, Tensor part_o, Tensor part_ml, Tensor? gate, Tensor out, Tensor? tree_mask, Tensor? tree_base, int impl, bool pdl) -> ()", &paged_attention);
   m.def("paged_attention_prefill(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor blk_start, Tensor blk_count, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, Tensor? gate, Tensor out, bool pdl) -> ()", &paged_attention_prefill);
   m.def("prefill_attn_block_tokens(int n_q_heads, int n_kv_heads) -> int", &prefill_attn_block_tokens);
-  m.def("causal_conv1d_silu(Tensor x, int c_off, int C, Tensor w, Tensor cu_seqlens, Tensor token_seq, Tensor state_slot, Tensor conv_state, Tensor out, bool update_state, bool one_token_per_seq, bool pdl, Tensor? seq_end=None, bool state_only=False) -> ()", &causal_conv1d_silu);
-  m.def("gdn_recurrent(Tensor qkv, int q_off, int k_off, int v_off, Tensor proj, int z_off, int a_off, int b_off, int n_qk_heads, int n_v_heads, Tensor A_log, Tensor dt_bias, Tensor norm_w, float eps, Tensor cu_seqlens, Tensor state_slot, Tensor state, bool write_state, Tensor out, bool pdl, Tensor? seq_end=None) -> ()", &gdn_recurrent);
+  m.def("causal_conv1d_silu(Tensor x, int c_off, int C, Tensor w, Tensor cu_seqlens, Tensor token_seq, Tensor state_slot, Tensor conv_state, Tensor out, bool update_state, bool one_token_per_seq, bool pdl, Tensor? seq_end=None, bool state_only=False, Tensor? parent=None, Tensor? last_token=None) -> ()", &causal_conv1d_silu);
+  m.def("gdn_recurrent(Tensor qkv, int q_off, int k_off, int v_off, Tensor proj, int z_off, int a_off, int b_off, int n_qk_heads, int n_v_heads, Tensor A_log, Tensor dt_bias, Tensor norm_w, float eps, Tensor cu_seqlens, Tensor state_slot, Tensor state, bool write_state, Tensor out, bool pdl, Tensor? seq_end=None, Tensor? commit=None) -> ()", &gdn_recurrent);
   m.def("gdn_prefill_trace(bool enable) -> Tensor", &gdn_prefill_trace);
   m.def("argmax_rows(Tensor logits, Tensor out, bool pdl) -> ()", &argmax_rows);
   m.def("sample_rows(Tensor logits, Tensor? temperature, Tensor? top_k, Tensor? top_p, Tensor? min_p, Tensor? presence, Tensor? frequency, Tensor? token_counts, Tensor? seeds, Tensor? positions, int purpose, Tensor out, Tensor? out_prob, Tensor? draft_ids=None, Tensor? accepted=None) -> ()", &sample_rows);
