@@ -81,4 +81,9 @@ const char* paged_attention_prefill(const PrefillAttnParams& p, cudaStream_t str
 // Query tokens per block for a GQA geometry (128 MMA rows / group size).
 int prefill_attn_block_tokens(int n_q_heads, int n_kv_heads);
 
+// Moves K/V rows of each sequence from cache positions src_pos[b, m] to dst_pos[b, m], in order m = 0.. (a negative
+// entry skips the move): accepted tree nodes go from frontier + node index to frontier + depth (kv/kv_move.cu).
+const char* kv_move_rows(const KvLayer& L, const int* table, int table_cols, const int* table_row, const int* src_pos,
+                         const int* dst_pos, int n_seq, int max_moves, cudaStream_t stream);
+
 }  // namespace nfb

@@ -167,6 +167,22 @@ nfb::KvLayer make_kv(const Tensor& k_codes, const Tensor& v_codes, OptT k_scales
   return kv;
 }
 
+// Moves K/V rows of each sequence from cache positions src_pos[b, m] to dst_pos[b, m] (in order m = 0.., -1 = skip).
+void kv_move_rows(const Tensor& block_table, const Tensor& table_row, const Tensor& src_pos, const Tensor& dst_pos,
+                  const Tensor& k_codes, const Tensor& v_codes, OptT k_scales, OptT v_scales, int64_t page_size,
+                  int64_t n_kv_heads, int64_t head_dim, int64_t format, int64_t group) {
+  need(block_table, at::kInt, "block_table"); need(table_row, at::kInt, "table_row");
+  need(src_pos, at::kInt, "src_pos"); need(dst_pos, at::kInt, "dst_pos");
+  TORCH_CHECK(src_pos.dim() == 2 && src_pos.is_contiguous() && dst_pos.is_contiguous() && src_pos.sizes() == dst_pos.sizes() &&
+              src_pos.size(0) == table_row.numel() && block_table.dim() == 2 && block_table.is_contiguous(), "kv_move_rows: shapes");
+  c10::cuda::CUDAGuard guard(k_codes.device());
+  nfb::KvLayer kv = make_kv(k_codes, v_codes, k_scales, v_scales, page_size, n_kv_heads, head_dim, format, group);
+  chk(nfb::kv_move_rows(kv, static_cast<const int*>(block_table.data_ptr()), static_cast<int>(block_table.size(1)),
+                        static_cast<const int*>(table_row.data_ptr()), static_cast<const int*>(src_pos.data_ptr()),
+                        static_cast<const int*>(dst_pos.data_ptr()), static_cast<int>(src_pos.size(0)),
+                        static_cast<int>(src_pos.size(1)), cur_stream()));
+}
+
 void attn_prep(const Tensor& proj, int64_t q_off, int64_t k_off, int64_t v_off, int64_t n_q_heads,
                int64_t n_kv_heads, int64_t head_dim, OptT q_norm_w, OptT k_norm_w, double eps, bool unit_offset,
                int64_t rot_dim, const Tensor& inv_freq, double attn_factor, const Tensor& rope_pos,
@@ -624,6 +640,7 @@ TORCH_LIBRARY(nfb200, m) {
   m.def("causal_conv1d_silu(Tensor x, int c_off, int C, Tensor w, Tensor cu_seqlens, Tensor token_seq, Tensor state_slot, Tensor conv_state, Tensor out, bool update_state, bool one_token_per_seq, bool pdl, Tensor? seq_end=None, bool state_only=False, Tensor? parent=None, Tensor? last_token=None) -> ()", &causal_conv1d_silu);
   m.def("gdn_recurrent(Tensor qkv, int q_off, int k_off, int v_off, Tensor proj, int z_off, int a_off, int b_off, int n_qk_heads, int n_v_heads, Tensor A_log, Tensor dt_bias, Tensor norm_w, float eps, Tensor cu_seqlens, Tensor state_slot, Tensor state, bool write_state, Tensor out, bool pdl, Tensor? seq_end=None, Tensor? commit=None) -> ()", &gdn_recurrent);
   m.def("gdn_prefill_trace(bool enable) -> Tensor", &gdn_prefill_trace);
+  m.def("kv_move_rows(Tensor block_table, Tensor table_row, Tensor src_pos, Tensor dst_pos, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int n_kv_heads, int head_dim, int format, int group) -> ()", &kv_move_rows);
   m.def("argmax_rows(Tensor logits, Tensor out, bool pdl) -> ()", &argmax_rows);
   m.def("sample_rows(Tensor logits, Tensor? temperature, Tensor? top_k, Tensor? top_p, Tensor? min_p, Tensor? presence, Tensor? frequency, Tensor? token_counts, Tensor? seeds, Tensor? positions, int purpose, Tensor out, Tensor? out_prob, Tensor? draft_ids=None, Tensor? accepted=None) -> ()", &sample_rows);
   m.def("accept_greedy_chain(Tensor target_ids, Tensor draft_ids, Tensor n_accepted, Tensor out_tokens) -> ()", &accept_greedy_chain);

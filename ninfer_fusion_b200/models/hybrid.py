@@ -44,6 +44,13 @@ class StepBatch:
     one_token_per_seq: bool = False
     qblk_start: Optional[torch.Tensor] = None   # [NB] first token of each attention query block
     qblk_count: Optional[torch.Tensor] = None   # [NB] tokens per query block
+    # draft-tree verification (all optional): per token, the parent's token index (-1 = root of its window), whether
+    # the token extends the state it saw (0 = side branch), the visibility bit mask over the window's cache
+    # positions and the window's first cache position
+    tree_parent: Optional[torch.Tensor] = None  # int32 [T]
+    tree_commit: Optional[torch.Tensor] = None  # uint8 [T]
+    tree_mask: Optional[torch.Tensor] = None    # int64 [T]
+    tree_base: Optional[torch.Tensor] = None    # int32 [T]
 
 
 class Workspace:
@@ -347,7 +354,7 @@ class HybridModel:
         gate = proj[:, q_dim + kv_dim: q_dim + kv_dim + q_dim]
         out = ws.mix_attn[:T]
         if (not b.one_token_per_seq and b.qblk_start is not None and D == 256 and self.attn_impl != 1
-                and T > b.n_seqs):
+                and T > b.n_seqs and b.tree_mask is None):
             # prefill / wide verify: one CTA per (query block, kv head), K/V tiles dequantised once per block
             ops.paged_attention_prefill(q, g.n_q_heads, g.n_kv_heads, D, b.table_row, b.kv_len, b.qblk_start,
                                         b.qblk_count, kv.table, planes.k_codes, planes.v_codes, planes.k_scales,
@@ -361,7 +368,8 @@ class HybridModel:
             ops.paged_attention(q[t0:t1], g.n_q_heads, g.n_kv_heads, D, b.table_row[t0:t1], b.kv_len[t0:t1], kv.table,
                                 planes.k_codes, planes.v_codes, planes.k_scales, planes.v_scales, kv.page_size,
                                 planes.fmt, planes.group, self.sm_scale, split, n_splits, ws.part_o, ws.part_ml,
-                                gate[t0:t1], out[t0:t1], None, None, self.attn_impl, self.pdl)
+                                gate[t0:t1], out[t0:t1], None if b.tree_mask is None else b.tree_mask[t0:t1],
+                                None if b.tree_base is None else b.tree_base[t0:t1], self.attn_impl, self.pdl)
         return out, self.w[f"{prefix}/attn/o_proj"]
 
     def _gdn_layer(self, ws: Workspace, b: StepBatch, st: GdnStatePool, layer: int, T: int, prefix: str,
@@ -375,13 +383,14 @@ class HybridModel:
         C = g.gdn_conv_dim
         conv = (ws.conv if rec is None else rec.conv[gi])[:T]
         ops.causal_conv1d_silu(proj, 0, C, self.w[f"{prefix}/gdn/conv_w"], b.cu_seqlens, b.token_seq, b.state_slot,
-                               st.conv[gi], conv, write_state, b.n_tokens == b.n_seqs and b.one_token_per_seq, self.pdl)
+                               st.conv[gi], conv, write_state, b.n_tokens == b.n_seqs and b.one_token_per_seq, self.pdl,
+                               None, False, b.tree_parent, None)
         qk = g.gdn_qk_dim
         out = ws.mix_gdn[:T]
         ops.gdn_recurrent(conv, 0, qk, 2 * qk, proj, C, C + g.gdn_v_dim, C + g.gdn_v_dim + g.gdn_v_heads,
                           g.gdn_qk_heads, g.gdn_v_heads, self.w[f"{prefix}/gdn/A_log"], self.w[f"{prefix}/gdn/dt_bias"],
                           self.w[f"{prefix}/gdn/norm"], cfg.rms_eps, b.cu_seqlens, b.state_slot, st.ssm[gi],
-                          write_state, out, self.pdl)
+                          write_state, out, self.pdl, None, b.tree_commit)
         return out, self.w[f"{prefix}/gdn/out_proj"]
 
     def _mlp(self, ws: Workspace, T: int, prefix: str, next_norm_w, normed_out):
@@ -392,6 +401,27 @@ class HybridModel:
         self._gemm_to_residual(ws, ws.act[:T, : w_down.shape[1]], w_down, T, next_norm_w, normed_out)
 
     # ------------------------------------------------------------------ forward
+    def fold_gdn_tree(self, ws: Workspace, b: StepBatch, st: GdnStatePool, rec: GdnRecords, accepted: torch.Tensor,
+                      last_token: torch.Tensor) -> None:
+        """Tree variant of fold_gdn: `accepted` (uint8 [T]) marks the nodes of the accepted path, `last_token`
+        (int32 [n_seq]) its last node.  The whole recorded window is replayed with the accepted nodes as the only
+        committing tokens, so the state ends exactly after the accepted path; the conv history is rebuilt from the
+        path's last three inputs."""
+        cfg, g, ops = self.cfg, self.g, self.ops
+        T = b.n_tokens
+        C, qk = g.gdn_conv_dim, g.gdn_qk_dim
+        for layer in cfg.gdn_layers:
+            gi = self._gdn_idx[layer]
+            p = f"{self.prefix}/layers/{layer}"
+            proj = rec.proj[gi][:T, : g.gdn_in_dim]
+            conv = rec.conv[gi][:T]
+            ops.causal_conv1d_silu(proj, 0, C, self.w[f"{p}/gdn/conv_w"], b.cu_seqlens, b.token_seq, b.state_slot,
+                                   st.conv[gi], ws.conv[:T], True, False, self.pdl, None, True, b.tree_parent, last_token)
+            ops.gdn_recurrent(conv, 0, qk, 2 * qk, proj, C, C + g.gdn_v_dim, C + g.gdn_v_dim + g.gdn_v_heads,
+                              g.gdn_qk_heads, g.gdn_v_heads, self.w[f"{p}/gdn/A_log"], self.w[f"{p}/gdn/dt_bias"],
+                              self.w[f"{p}/gdn/norm"], cfg.rms_eps, b.cu_seqlens, b.state_slot, st.ssm[gi], True,
+                              ws.mix_gdn[:T], self.pdl, None, accepted)
+
     def fold_gdn(self, ws: Workspace, b: StepBatch, st: GdnStatePool, rec: GdnRecords, seq_end: torch.Tensor) -> None:
         """Replays tokens [cu_seqlens[s], seq_end[s]) of the recorded verify pass `b` into the conv history and the
         recurrent state of every GDN layer (the accepted prefix of a speculative round)."""

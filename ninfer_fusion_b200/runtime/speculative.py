@@ -48,18 +48,22 @@ class SpeculativeGenerator(Generator):
     """Static-batch greedy generation with K chained draft tokens per round."""
 
     def __init__(self, cfg: ModelConfig, weights: Dict[str, torch.Tensor], device, max_batch: int, max_context: int,
-                 draft_tokens: int = 3, drafter: str = "mtp", sampling=None, **kw):
+                 draft_tokens: int = 3, drafter: str = "mtp", sampling=None, tree_ranks: int = 1, **kw):
         K = draft_tokens
         if K < 1:
             raise ValueError("draft_tokens must be >= 1")
         kw.setdefault("use_graph", False)
-        super().__init__(cfg, weights, device, max_batch, max_context, max_logit_rows=max_batch * (K + 1), **kw)
+        R_ = max(1, tree_ranks)
+        if 1 + R_ * K > 64:
+            raise ValueError("a verify window holds at most 64 nodes (one visibility bit each)")
+        super().__init__(cfg, weights, device, max_batch, max_context, max_logit_rows=max_batch * (1 + R_ * K), **kw)
         self.K = K
+        self.R = R_   # candidates per depth of the draft tree: rank 0 extends the chain, ranks 1.. are side branches
         self.sampling = sampling  # runtime.program.SamplingParams for stochastic verification; None / greedy = arg-max
         self.drafter = drafter  # "mtp" | "ngram" | "hook"
         self.draft_hook: Optional[Callable[[int, List[int], int], Optional[List[int]]]] = None
         dev, g = self.device, self.model.g
-        Tv = max_batch * (K + 1)
+        Tv = max_batch * (1 + self.R * K)
         qt = self.bufs_decode.attn_block_tokens
         self.bufs_verify = StepBuffers(Tv, max_batch, dev, attn_block_tokens=qt, max_logit_rows=Tv)
         self.bufs_catch = StepBuffers(Tv, max_batch, dev, attn_block_tokens=qt)
@@ -73,6 +77,8 @@ class SpeculativeGenerator(Generator):
         self.next_host = torch.zeros(max(self.ws.max_tokens, Tv), dtype=torch.int32, pin_memory=pin)
         self.next_dev = torch.zeros(max(self.ws.max_tokens, Tv), dtype=torch.int32, device=dev)
         self.drafts = torch.zeros((max_batch, K), dtype=torch.int32, device=dev)
+        self.drafts_r = torch.zeros((max_batch, K, self.R), dtype=torch.int32, device=dev)   # [b, depth, rank]
+        self.tree_hook: Optional[Callable[[int, List[int], int, int], Optional[List[List[int]]]]] = None
         self.draft_host = torch.zeros((max_batch, K), dtype=torch.int32, pin_memory=pin)
         self.n_acc = torch.zeros(max_batch, dtype=torch.int32, device=dev)
         self.out_tok = torch.zeros((max_batch, K + 1), dtype=torch.int32, device=dev)
@@ -109,6 +115,8 @@ class SpeculativeGenerator(Generator):
         self.model.ops.argmax_rows(lg, ids, self.model.pdl)
         idx = torch.tensor(list(seqs), dtype=torch.long, device=self.device)
         self.drafts[idx, 0] = ids
+        if self.R > 1:
+            self.drafts_r[idx, 0] = torch.topk(lg.float(), self.R, dim=-1).indices.to(torch.int32)
         self.mtp_h[idx] = hid.index_select(0, batch.logit_rows.long())
 
     # ------------------------------------------------------------------ prefill
@@ -190,7 +198,19 @@ class SpeculativeGenerator(Generator):
                 ids = self.ws.next_ids[:B]
                 self.model.ops.argmax_rows(lg, ids, self.model.pdl)
                 self.drafts[:B, j] = ids
+                if self.R > 1:
+                    self.drafts_r[:B, j] = torch.topk(lg.float(), self.R, dim=-1).indices.to(torch.int32)
                 self.mtp_h[:B].copy_(hid)
+            return
+        if self.R > 1:
+            host = torch.zeros((B, K, self.R), dtype=torch.int32)
+            for b in range(B):
+                cand = self.tree_hook(b, self.history[b], K, self.R) if self.tree_hook is not None else None
+                if cand is None:
+                    cand = [[self.last_tokens[b]] * self.R for _ in range(K)]
+                host[b] = torch.tensor(cand, dtype=torch.int32)
+            self.drafts_r[:B].copy_(host.to(self.device))
+            self.drafts[:B].copy_(self.drafts_r[:B, :, 0])
             return
         for b in range(B):
             d = None
@@ -203,8 +223,115 @@ class SpeculativeGenerator(Generator):
             self.draft_host[b] = torch.tensor(list(d)[:K], dtype=torch.int32)
         self.drafts[:B].copy_(self.draft_host[:B], non_blocking=True)
 
+    # ------------------------------------------------------------------ tree round
+    def _tree_layout(self):
+        """Node order of one verify window: root, then per depth the side branches (ranks 1..R-1) followed by the chain
+        node (rank 0), so that every side branch directly follows the state it hangs off."""
+        K, R_ = self.K, self.R
+        W = 1 + R_ * K
+        parent, depth, rank, commit, mask = [-1], [0], [0], [1], [1]
+        for d in range(1, K + 1):
+            base = 1 + R_ * (d - 1)
+            par = R_ * (d - 1)          # chain node of depth d - 1 (0 = root)
+            anc = 1
+            for dd in range(1, d):
+                anc |= 1 << (R_ * dd)
+            for j in range(R_):
+                r = j + 1 if j < R_ - 1 else 0
+                parent.append(par); depth.append(d); rank.append(r); commit.append(1 if r == 0 else 0)
+                mask.append(anc | (1 << (base + j)))
+        return W, parent, depth, rank, commit, mask
+
+    def decode_round_tree(self) -> List[List[int]]:
+        """One round with a draft tree of K depths x R ranks verified in one target pass."""
+        B, K, R_ = len(self.rows), self.K, self.R
+        ops, dev = self.model.ops, self.device
+        W, parent, depth, rank, commit, mask = self._tree_layout()
+        for b, r in enumerate(self.rows):
+            self.kv.ensure(r, self.lengths[b] + W + 1)
+            if self.kv_mtp is not None:
+                self.kv_mtp.ensure(r, self.lengths[b] + K + 2)
+        self.kv.publish()
+        if self.kv_mtp is not None:
+            self.kv_mtp.publish()
+        self._draft(B)
+        chunks = [SeqChunk(self.rows[b], self.slots[b], self.lengths[b], [self.last_tokens[b]] + [0] * (W - 1), True, True)
+                  for b in range(B)]
+        batch = self.bufs_verify.build(chunks)
+        T = B * W
+        # node tokens: drafts_r[b, depth - 1, rank]
+        d_idx = torch.tensor(depth[1:], device=dev) - 1
+        r_idx = torch.tensor(rank[1:], device=dev)
+        batch.ids.view(B, W)[:, 1:] = self.drafts_r[:B][:, d_idx, r_idx]
+        n0 = torch.tensor(self.lengths[:B], dtype=torch.int32, device=dev)[:, None]
+        batch.rope_pos.view(B, W).copy_(n0 + torch.tensor(depth, dtype=torch.int32, device=dev)[None])
+        batch.kv_len.view(B, W).copy_((n0 + W).expand(B, W))
+        offs = (torch.arange(B, dtype=torch.int32, device=dev) * W)[:, None]
+        par = torch.tensor(parent, dtype=torch.int32, device=dev)[None].expand(B, W)
+        batch.tree_parent = torch.where(par >= 0, par + offs, par).reshape(-1).contiguous()
+        batch.tree_commit = torch.tensor(commit, dtype=torch.uint8, device=dev).repeat(B)
+        batch.tree_mask = torch.tensor(mask, dtype=torch.int64, device=dev).repeat(B)
+        batch.tree_base = n0.expand(B, W).reshape(-1).contiguous()
+        hidden = self.model.forward_hidden(self.ws, batch, self.kv, self.states, write_state=False, rec=self.rec)
+        self.h_keep[:T].copy_(hidden)
+        lg = self.model.logits(self.ws, batch, hidden)
+        target = self.ws.next_ids[:T]
+        ops.argmax_rows(lg, target, self.model.pdl)
+        n_acc = torch.empty(B, dtype=torch.int32, device=dev)
+        out_tok = torch.empty((B, K + 1), dtype=torch.int32, device=dev)
+        out_node = torch.empty((B, K + 1), dtype=torch.int32, device=dev)
+        ops.accept_greedy_tree(target.view(B, W), batch.ids.view(B, W), par.contiguous(), K, n_acc, out_tok, out_node)
+        acc_h, tok_h, node_h = n_acc.cpu(), out_tok.cpu(), out_node.cpu()   # (synchronises)
+        emitted: List[List[int]] = []
+        accepted = torch.zeros((B, W), dtype=torch.uint8)
+        last = torch.zeros(B, dtype=torch.int32)
+        src = torch.full((B, K), -1, dtype=torch.int32)
+        dst = torch.full((B, K), -1, dtype=torch.int32)
+        path_rows: List[int] = []
+        for b in range(B):
+            m = int(acc_h[b])
+            emitted.append([int(v) for v in tok_h[b, : m + 1]])
+            accepted[b, 0] = 1
+            last[b] = b * W
+            path_rows.append(b * W)
+            for d in range(m):
+                node = int(node_h[b, d])
+                accepted[b, node] = 1
+                last[b] = b * W + node
+                path_rows.append(b * W + node)
+                src[b, d] = self.lengths[b] + node
+                dst[b, d] = self.lengths[b] + d + 1
+            self.accepted += m
+            self.emitted += m + 1
+        self.rounds += 1
+        # state: replay with the accepted path as the only committing tokens; KV: accepted rows to their final places
+        self.model.fold_gdn_tree(self.ws, batch, self.states, self.rec, accepted.view(-1).to(dev), last.to(dev))
+        src_d, dst_d = src.to(dev), dst.to(dev)
+        trow = torch.tensor(self.rows[:B], dtype=torch.int32, device=dev)
+        g = self.model.g
+        for planes in self.kv.layers:
+            ops.kv_move_rows(self.kv.table, trow, src_d, dst_d, planes.k_codes, planes.v_codes, planes.k_scales,
+                             planes.v_scales, self.kv.page_size, g.n_kv_heads, self.cfg.head_dim, planes.fmt, planes.group)
+        if self.drafter == "mtp":
+            chunks, nxt = [], []
+            for b in range(B):
+                chunks.append(SeqChunk(self.rows[b], self.slots[b], self.lengths[b], [0] * len(emitted[b]), True))
+                nxt.extend(emitted[b])
+            cb = self.bufs_catch.build(chunks)
+            idx = torch.tensor(path_rows, dtype=torch.long, device=dev)
+            Tc = len(path_rows)
+            torch.index_select(self.h_keep[:T], 0, idx, out=self.h_in[:Tc])
+            self._mtp_pass(cb, self.h_in[:Tc], self._upload_next(nxt), list(range(B)))
+        for b in range(B):
+            self.lengths[b] += len(emitted[b])
+            self.last_tokens[b] = emitted[b][-1]
+            self.history[b].extend(emitted[b])
+        return emitted
+
     def decode_round(self) -> List[List[int]]:
         """One draft-verify round; returns the tokens emitted for every sequence (1..K+1 each)."""
+        if self.R > 1:
+            return self.decode_round_tree()
         B, K = len(self.rows), self.K
         ops = self.model.ops
         for b, r in enumerate(self.rows):

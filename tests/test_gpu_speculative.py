@@ -12,11 +12,11 @@ from ninfer_fusion_b200.runtime.speculative import SpeculativeGenerator, ngram_d
 pytestmark = pytest.mark.gpu
 
 
-def _teacher_forced_agreement(cfg, w, prompts, out):
+def _teacher_forced_agreement(cfg, w, prompts, out, kv=R.KV_BF16):
     ref = ReferenceModel(cfg, {k: v.cpu() for k, v in w.items() if not k.startswith("mtp/")})
     agree = total = 0
     for b, p in enumerate(prompts):
-        seq = ReferenceSequence(cfg, R.KV_BF16)
+        seq = ReferenceSequence(cfg, kv)
         hid = ref.forward(seq, torch.tensor(p))
         for tok in out[b]:
             lg = ref.logits(hid[-1:])[0]
@@ -106,3 +106,65 @@ def test_sampled_speculation_runs_and_is_seed_reproducible():
     b, _ = run(11)
     c, _ = run(12)
     assert a == b and a != c and all(len(o) == 14 for o in a) and tpr >= 1.0
+
+
+@pytest.mark.parametrize("pattern", ["chain", "side", "miss"])
+@pytest.mark.parametrize("kv_format", ["bf16", "fp8"])
+def test_tree_verification_keeps_the_greedy_stream(pattern, kv_format):
+    """Draft tree (4 depths x 3 ranks, 13 nodes) verified in one pass: tree-masked attention, side-branch GDN tokens,
+    replay of the accepted path, relocation of its KV rows.  Whatever the tree holds, the stream is the target's."""
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cuda", seed=7, std=0.05)
+    torch.manual_seed(1)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (21, 70, 5)]
+    n_new = 26
+    plain = Generator(cfg, w, "cuda", max_batch=4, max_context=512, kv_format=kv_format, page_size=16, prefill_chunk=64,
+                      use_graph=False).generate(prompts, n_new + 8)
+    K, RK = 4, 3
+    gen = SpeculativeGenerator(cfg, w, "cuda", max_batch=4, max_context=512, draft_tokens=K, drafter="hook",
+                               tree_ranks=RK, kv_format=kv_format, page_size=16, prefill_chunk=64)
+    plen = [len(p) for p in prompts]
+
+    def tree_hook(b, history, k, r):
+        done = len(history) - plen[b]
+        truth = plain[b][done:done + k]
+        truth = truth + [0] * (k - len(truth))
+        rows = []
+        for d, t in enumerate(truth):
+            wrong = [(t + 1 + j) % cfg.vocab for j in range(r)]
+            if pattern == "chain":
+                where = 0                      # truth is always the chain candidate
+            elif pattern == "side":
+                where = (done + d + b) % r     # truth wanders over the ranks: a side-branch hit ends the walk
+            else:
+                where = -1                     # truth is nowhere in the tree
+            row = wrong[:]
+            if where >= 0:
+                row[where] = t
+            rows.append(row)
+        return rows
+
+    gen.tree_hook = tree_hook
+    out = gen.generate(prompts, n_new)
+    agree, total = _teacher_forced_agreement(cfg, w, prompts, out, R.KV_FORMAT_NAMES[kv_format])
+    assert total > 30 and agree / total >= 0.93, f"{agree}/{total}"
+    if kv_format != "bf16":
+        return   # the hook's "truth" comes from a separate run; with a lossy cache the two streams part after a few tokens
+    if pattern == "chain":
+        assert gen.tokens_per_round > K
+    if pattern == "miss":
+        assert gen.tokens_per_round == 1.0
+    if pattern == "side":
+        assert 1.0 < gen.tokens_per_round < K + 1
+
+
+def test_tree_with_mtp_drafts_runs():
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cuda", seed=9, std=0.05, with_mtp=True)
+    torch.manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (33, 90)]
+    gen = SpeculativeGenerator(cfg, w, "cuda", max_batch=2, max_context=512, draft_tokens=4, drafter="mtp", tree_ranks=3,
+                               kv_format="bf16", page_size=16, prefill_chunk=64)
+    out = gen.generate(prompts, 16)
+    agree, total = _teacher_forced_agreement(cfg, w, prompts, out)
+    assert total > 12 and agree / total >= 0.9, f"{agree}/{total}"
