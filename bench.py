@@ -111,6 +111,8 @@ def main() -> int:
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--weights", default="bf16", choices=["bf16", "fp8", "nvfp4"],
                     help="matmul weight format (fp8 = e4m3 row-scale W8A8, nvfp4 = e2m1 block-scaled W4A4)")
+    ap.add_argument("--experts", default="bf16", choices=["bf16", "fp8_block"],
+                    help="routed expert format of MoE models (fp8_block = e4m3 with 128x128 block scales)")
     ap.add_argument("--parallel", default="", choices=["", "tp", "ep"],
                     help="multi-GPU plan: tp = tensor parallel (dense default), ep = data parallel + expert parallel (MoE default)")
     args = ap.parse_args()
@@ -172,6 +174,7 @@ def main() -> int:
     max_ctx = L + 2 * (K + W) + 64
     gen = Generator(cfg, weights, device, max_batch=B_local, max_context=max_ctx, kv_format=args.kv_format,
                     page_size=64, prefill_chunk=2048, use_graph=True, pdl=bool(args.pdl), shard=shard, comm=comm)
+    gen.model.expert_format = args.experts
     if ep:
         gen.model.ep = (rank, world, None)
     g = torch.Generator().manual_seed(1234 + (rank if ep else 0))
@@ -252,7 +255,8 @@ def main() -> int:
             "data": "synthetic uniform-random token prompts, random-init weights",
             "config": {"model": cfg.name + ("" if not args.layers else " (SHRUNK: INVALID)"), "global_batch": B,
                        "seq_len": L, "parallelism": f"{parallel}{world}" if world > 1 else "single", "kv": args.kv_format + "-e4m3-row" if args.kv_format == "fp8" else args.kv_format,
-                       "weights": args.weights, "decode": "greedy, CUDA graph per round",
+                       "weights": args.weights if cfg.moe is None or args.experts == "bf16" else f"{args.weights} (routed experts {args.experts})",
+                       "decode": "greedy, CUDA graph per round",
                        "l2": "inputs larger than L2 (all weights streamed every round), no flush",
                        "baseline_note": f"vs_baseline divides by the reference's single-request decode tok/s ({baseline_tok_s}, one RTX 5090)"},
             "ttft_ms_p50": round(ttft_max, 2) if ttft_ms is not None else None,
