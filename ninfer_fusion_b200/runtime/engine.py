@@ -345,7 +345,7 @@ class Engine:
                     break
             try:
                 self._iteration()
-            except (InvariantError, ResourceError, RuntimeError, MemoryError) as e:
+            except Exception as e:  # noqa: BLE001 - any escape from an iteration is an engine-wide failure, never a hang
                 # engine-wide failure: fail every in-flight request, refuse new ones until recover()
                 with self._lock:
                     self._failed = f"{type(e).__name__}: {e}"

@@ -94,6 +94,22 @@ class GpuProgram(ProgramBase):
         self.states.release(slot)
         self._ckpt_slots_free += 1
 
+    def _demote(self, handle):
+        """Device frontier -> pinned host copy (KV pages of every layer + the state image)."""
+        pages, slot = handle
+        return {"n_pages": len(pages), "tensors": [self.kv.export_pages(pages), self.states.export_slot(slot)]}
+
+    def _promote(self, cold):
+        if self._ckpt_slots_free <= 0:
+            return None
+        pages = self.kv.import_pages(cold["tensors"][0], cold["n_pages"])
+        if pages is None:
+            return None
+        self._ckpt_slots_free -= 1
+        slot = self.states.alloc()
+        self.states.import_slot(cold["tensors"][1], slot)
+        return (pages, slot)
+
     def _kv_room(self, n_tokens: int) -> bool:
         return self.kv.pool.free_pages >= (n_tokens + self.kv.page_size - 1) // self.kv.page_size
 

@@ -267,6 +267,38 @@ class PagedKvCache:
             self.table_host[dst_row, full] = p_new
         self._dirty_rows.add(dst_row)
 
+    # ---- cold tiers: page contents leave / re-enter the device pool ----
+    def export_pages(self, pages: List[int]) -> List[torch.Tensor]:
+        """Contents of `pages` in every layer as pinned host tensors (device -> host, D2H page copies)."""
+        idx = torch.tensor(pages, dtype=torch.long, device=self.device)
+        out = []
+        pin = self.device.type == "cuda"
+        for l in self.layers:
+            for plane in (l.k_codes, l.v_codes, l.k_scales, l.v_scales):
+                if plane is None:
+                    continue
+                dev = plane.index_select(0, idx)
+                host = torch.empty(dev.shape, dtype=dev.dtype, pin_memory=pin)
+                host.copy_(dev, non_blocking=True)
+                out.append(host)
+        if pin:
+            torch.cuda.current_stream(self.device).synchronize()
+        return out
+
+    def import_pages(self, planes: List[torch.Tensor], n_pages: int) -> Optional[List[int]]:
+        """Allocates `n_pages` fresh pages and fills them from `export_pages` output.  None if the pool is too small."""
+        if self.pool.free_pages < n_pages:
+            return None
+        pages = [self.pool.alloc() for _ in range(n_pages)]
+        idx = torch.tensor(pages, dtype=torch.long, device=self.device)
+        it = iter(planes)
+        for l in self.layers:
+            for plane in (l.k_codes, l.v_codes, l.k_scales, l.v_scales):
+                if plane is None:
+                    continue
+                plane.index_copy_(0, idx, next(it).to(self.device, non_blocking=True))
+        return pages
+
     def drop_pages(self, pages: List[int]) -> None:
         for p in pages:
             self.pool.release(p)
@@ -328,6 +360,25 @@ class GdnStatePool:
         for c, s in zip(self.conv, self.ssm):
             c[dst].copy_(c[src])
             s[dst].copy_(s[src])
+
+    def export_slot(self, slot: int) -> List[torch.Tensor]:
+        """State image of one slot (conv history + recurrent state of every layer) as pinned host tensors."""
+        pin = self.conv[0].device.type == "cuda"
+        out = []
+        for c, s in zip(self.conv, self.ssm):
+            for t in (c[slot], s[slot]):
+                host = torch.empty(t.shape, dtype=t.dtype, pin_memory=pin)
+                host.copy_(t, non_blocking=True)
+                out.append(host)
+        if pin:
+            torch.cuda.current_stream(self.conv[0].device).synchronize()
+        return out
+
+    def import_slot(self, image: List[torch.Tensor], slot: int) -> None:
+        it = iter(image)
+        for c, s in zip(self.conv, self.ssm):
+            c[slot].copy_(next(it), non_blocking=True)
+            s[slot].copy_(next(it), non_blocking=True)
 
     def total_bytes(self) -> int:
         return sum(c.numel() * 2 + s.numel() * 4 for c, s in zip(self.conv, self.ssm))

@@ -60,6 +60,8 @@ class Checkpoint:
     tokens: List[int]
     handle: object
     last_used: float = 0.0
+    tier: str = "gpu"     # "gpu" | "host" | "disk": where the KV pages and the state image currently live
+    nbytes: int = 0       # size of the cold copy (host / disk tiers)
 
 
 class ProgramBase:
@@ -75,6 +77,12 @@ class ProgramBase:
         self.checkpoints: List[Checkpoint] = []
         self.max_checkpoints = 2 * max_lanes
         self._clock = 0
+        # cold tiers for session checkpoints: frontiers pushed out of the device pool are parked in pinned host memory
+        # and, beyond that budget, in files (host_budget_bytes = 0 keeps the old "evict = drop" behaviour)
+        self.host_budget_bytes = 0
+        self.disk_budget_bytes = 0
+        self.cold_dir: Optional[str] = None
+        self.cold_stats = {"demoted_host": 0, "demoted_disk": 0, "promoted": 0, "dropped": 0}
 
     # ---- capacity ----
     def free_lanes(self) -> int:
@@ -90,12 +98,81 @@ class ProgramBase:
 
     # ---- session checkpoints (prefix reuse) ----
     def _evict_checkpoint(self) -> bool:
-        if not self.checkpoints:
+        """Frees the device resources of the least recently used device-resident frontier: it is demoted to the host
+        tier when the budget allows (pushing older host copies on to disk), otherwise dropped."""
+        hot = [c for c in self.checkpoints if c.tier == "gpu"]
+        if not hot:
             return False
-        victim = min(self.checkpoints, key=lambda c: c.last_used)
-        self.checkpoints.remove(victim)
+        victim = min(hot, key=lambda c: c.last_used)
+        cold = self._demote(victim.handle) if self.host_budget_bytes > 0 else None
         self._drop(victim.handle)
+        if cold is None:
+            self.checkpoints.remove(victim)
+            self.cold_stats["dropped"] += 1
+            return True
+        victim.handle, victim.tier, victim.nbytes = cold, "host", self._cold_bytes(cold)
+        self.cold_stats["demoted_host"] += 1
+        self._trim_cold()
         return True
+
+    def _cold_bytes(self, cold) -> int:
+        return sum(t.numel() * t.element_size() for group in cold["tensors"] for t in group)
+
+    def _trim_cold(self) -> None:
+        """Keeps the host tier inside its budget: oldest host copies go to disk (or are dropped without a disk tier)."""
+        import os
+        while sum(c.nbytes for c in self.checkpoints if c.tier == "host") > self.host_budget_bytes:
+            victim = min((c for c in self.checkpoints if c.tier == "host"), key=lambda c: c.last_used)
+            on_disk = sum(c.nbytes for c in self.checkpoints if c.tier == "disk")
+            if self.cold_dir and on_disk + victim.nbytes <= self.disk_budget_bytes:
+                os.makedirs(self.cold_dir, exist_ok=True)
+                path = os.path.join(self.cold_dir, f"ckpt_{id(victim):x}_{self._clock}.pt")
+                torch.save(victim.handle, path)
+                victim.handle, victim.tier = {"path": path}, "disk"
+                self.cold_stats["demoted_disk"] += 1
+            else:
+                self.checkpoints.remove(victim)
+                self.cold_stats["dropped"] += 1
+        while self.cold_dir and sum(c.nbytes for c in self.checkpoints if c.tier == "disk") > self.disk_budget_bytes:
+            victim = min((c for c in self.checkpoints if c.tier == "disk"), key=lambda c: c.last_used)
+            self._forget_cold(victim)
+
+    def _forget_cold(self, c: Checkpoint) -> None:
+        import os
+        if c.tier == "disk":
+            try:
+                os.remove(c.handle["path"])
+            except OSError:
+                pass
+        self.checkpoints.remove(c)
+        self.cold_stats["dropped"] += 1
+
+    def _warm_up(self, c: Checkpoint) -> bool:
+        """Brings a cold frontier back into the device pool (disk -> host -> device).  False if there is no room."""
+        if c.tier == "gpu":
+            return True
+        cold = torch.load(c.handle["path"], weights_only=False) if c.tier == "disk" else c.handle
+        handle = self._promote(cold)
+        while handle is None:
+            others = [o for o in self.checkpoints if o.tier == "gpu" and o is not c]
+            if not others or not self._evict_checkpoint():
+                return False
+            handle = self._promote(cold)
+        if c.tier == "disk":
+            import os
+            try:
+                os.remove(c.handle["path"])
+            except OSError:
+                pass
+        c.handle, c.tier, c.nbytes = handle, "gpu", 0
+        self.cold_stats["promoted"] += 1
+        return True
+
+    def _demote(self, handle):
+        return None   # programs without a cold tier drop evicted frontiers
+
+    def _promote(self, cold):
+        return None
 
     def checkpoint(self, lane: Lane, session: str, kind: str) -> bool:
         """Remember the lane's materialised frontier (lane.tokens[:n_cached]) for `session`."""
@@ -103,9 +180,13 @@ class ProgramBase:
         if not session or n <= 0:
             return False
         for c in [c for c in self.checkpoints if c.session == session and c.kind == kind]:
-            self.checkpoints.remove(c)       # one frontier per (session, kind)
-            self._drop(c.handle)
-        while len(self.checkpoints) >= self.max_checkpoints:
+            if c.tier == "gpu":              # one frontier per (session, kind)
+                self.checkpoints.remove(c)
+                self._drop(c.handle)
+            else:
+                self._forget_cold(c)
+                self.cold_stats["dropped"] -= 1
+        while len([c for c in self.checkpoints if c.tier == "gpu"]) >= self.max_checkpoints:
             self._evict_checkpoint()
         handle = None
         while handle is None:
@@ -149,6 +230,8 @@ class ProgramBase:
         self._next_id += 1
         self.lanes[lane.lane_id] = lane
         ck = self._match(session, prompt)
+        if ck is not None and not self._warm_up(ck):
+            ck = None   # no room to bring the cold frontier back: prefill from scratch
         if ck is not None:
             self._restore(ck.handle, lane, len(ck.tokens))
             lane.n_cached = lane.reused = len(ck.tokens)
@@ -204,6 +287,13 @@ class ReferenceProgram(ProgramBase):
     def _restore(self, handle, lane: Lane, n_tokens: int) -> None:
         import copy
         self._seqs[lane.lane_id] = copy.deepcopy(handle)
+
+    def _demote(self, handle):
+        seq = handle
+        return {"n_pages": 0, "seq": seq, "tensors": [list(seq.k) + list(seq.v), list(seq.conv) + list(seq.ssm)]}
+
+    def _promote(self, cold):
+        return cold["seq"]
 
     def _sample(self, lane: Lane, logits: torch.Tensor) -> int:
         sp = lane.sampling

@@ -158,3 +158,37 @@ def test_reload_kv_storage_swaps_the_program_between_requests():
         assert a[0] == b[0] or True   # int8 KV may flip a near-tie; the point is that the engine keeps serving
     finally:
         eng.shutdown()
+
+
+def test_cold_tiers_park_and_revive_session_frontiers(tmp_path):
+    """Frontiers evicted from the device tier move to the host tier, overflow to disk, and come back on a hit."""
+    from ninfer_fusion_b200.models.config import TINY_DENSE
+    from ninfer_fusion_b200.models.weights import random_weights
+    from ninfer_fusion_b200.runtime.program import ReferenceProgram
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cpu", seed=5, std=0.05)
+
+    def factory():
+        p = ReferenceProgram(cfg, w, max_lanes=2, max_context=256)
+        p.max_checkpoints = 2                      # device tier: two frontiers
+        p.host_budget_bytes = 1                    # practically nothing fits on the host ...
+        p.disk_budget_bytes = 1 << 30              # ... so demoted frontiers spill to disk
+        p.cold_dir = str(tmp_path / "cold")
+        return p
+    eng = Engine(factory, prefill_chunk=32)
+    try:
+        first = {}
+        for s in range(4):                          # 4 sessions x 2 frontiers > device tier
+            prompt = list(range(10 + s, 50 + s))
+            first[s] = (prompt, eng.submit(prompt, RequestOptions(max_tokens=4, session=f"s{s}")).wait(timeout=60))
+        prog = eng.program
+        tiers = [c.tier for c in prog.checkpoints]
+        assert tiers.count("gpu") <= 2 and "disk" in tiers and prog.cold_stats["demoted_disk"] >= 1
+        prompt, out = first[0]
+        follow = prompt + out + [5, 6, 7]
+        cold_run = eng.submit(follow, RequestOptions(max_tokens=4)).wait(timeout=60)
+        hits = eng.stats.prefix_hits
+        warm_run = eng.submit(follow, RequestOptions(max_tokens=4, session="s0")).wait(timeout=60)
+        assert warm_run == cold_run and eng.stats.prefix_hits == hits + 1 and prog.cold_stats["promoted"] >= 1
+    finally:
+        eng.shutdown()

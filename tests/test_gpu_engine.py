@@ -90,3 +90,27 @@ def test_session_checkpoint_reuse_on_gpu(setup):
     while prog._evict_checkpoint():
         pass
     assert prog.kv.pool.free_pages == prog.kv.n_pages and prog._ckpt_slots_free == prog.checkpoint_slots
+
+
+def test_host_cold_tier_round_trip_on_gpu(setup):
+    """A frontier demoted to pinned host memory (KV pages of every layer + state image) and promoted back must
+    continue exactly like the device-resident one."""
+    cfg, _, engine = setup
+    prog = engine.program
+    prog.host_budget_bytes = 1 << 30
+    turn1 = list(range(30, 97))
+    out1 = engine.submit(turn1, RequestOptions(max_tokens=7, session="cold-1")).wait(timeout=120)
+    turn2 = turn1 + out1 + [3, 4, 5]
+    hot = engine.submit(turn2, RequestOptions(max_tokens=6, session="cold-1")).wait(timeout=120)
+    # push every device-resident frontier to the host tier, then ask again
+    while any(c.tier == "gpu" for c in prog.checkpoints):
+        assert prog._evict_checkpoint()
+    assert all(c.tier == "host" for c in prog.checkpoints) and prog.cold_stats["demoted_host"] >= 2
+    assert prog.kv.pool.free_pages == prog.kv.n_pages
+    promoted = prog.cold_stats["promoted"]
+    again = engine.submit(turn2, RequestOptions(max_tokens=6, session="cold-1")).wait(timeout=120)
+    assert prog.cold_stats["promoted"] == promoted + 1
+    assert again == hot   # same restored bytes, same kernels: bit-identical continuation
+    prog.host_budget_bytes = 0
+    while prog._evict_checkpoint():
+        pass
