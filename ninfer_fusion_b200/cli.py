@@ -48,6 +48,8 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--prefill-chunk", type=int, default=2048)
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--no-graphs", action="store_true", help="eager decode instead of CUDA graphs")
+    ap.add_argument("--spec", default="none", choices=["none", "mtp"], help="speculative decoding with the MTP draft module")
+    ap.add_argument("--draft-tokens", type=int, default=3)
     ap.add_argument("--allow-unknown-template", action="store_true")
     ap.add_argument("--seed", type=int, default=0)
 
@@ -72,7 +74,8 @@ def load_model(args) -> Tuple[ModelConfig, Dict[str, object], Tokenizer, str]:
         cfg = get_config(args.model)
         if args.layers:
             cfg = cfg.shrink(args.layers)
-        weights = random_weights(cfg, args.device, seed=args.seed, std=0.05 if cfg.hidden <= 512 else 0.02)
+        weights = random_weights(cfg, args.device, seed=args.seed, std=0.05 if cfg.hidden <= 512 else 0.02,
+                                 with_mtp=getattr(args, "spec", "none") == "mtp")
         name = f"{cfg.name}:random-init"
     renderer_for(template, allow_unknown=args.allow_unknown_template)  # refuses an unknown template early
     if args.weights != "bf16":
@@ -94,6 +97,18 @@ def build_engine(args, cfg: ModelConfig, weights) -> Engine:
     if args.kv_layer_spec:
         from .kv.policy import parse_layer_storage
         kv = parse_layer_storage(args.kv_layer_spec, len(cfg.attn_layers))
+    if getattr(args, "spec", "none") == "mtp":
+        if not str(args.device).startswith("cuda"):
+            raise SystemExit("--spec mtp needs a GPU")
+        if "mtp/fc" not in weights:
+            raise SystemExit("--spec mtp: the weights have no draft module (make-artifact --with-mtp)")
+        from .runtime.speculative import SpeculativeProgram
+
+        def factory():
+            return SpeculativeProgram(cfg, weights, args.device, max_lanes=args.max_lanes, max_context=args.max_context,
+                                      draft_tokens=args.draft_tokens, kv_format=kv, page_size=args.page_size,
+                                      prefill_chunk=args.prefill_chunk)
+        return Engine(factory, prefill_chunk=args.prefill_chunk)
     if str(args.device).startswith("cuda"):
         from .runtime.gpu_program import GpuProgram
 

@@ -394,5 +394,10 @@ class Engine:
             self.stats.decode_rounds += 1
             self.governor.observe(dt * 1e3, did_prefill)
             for r, t in zip(ready, toks):
-                self._commit_token(r, t)
+                # a speculative program returns several tokens per lane and round; each one goes through the
+                # same commit-before-publish gate, and nothing after a stop / budget hit becomes visible
+                for tok in (t if isinstance(t, (list, tuple)) else (t,)):
+                    if r.state == "finished":
+                        break
+                    self._commit_token(r, tok)
         self._active = [r for r in self._active if r.state != "finished"]

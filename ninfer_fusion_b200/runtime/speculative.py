@@ -352,20 +352,25 @@ class SpeculativeGenerator(Generator):
         self.h_keep[:T].copy_(hidden)
         lg = self.model.logits(self.ws, batch, hidden)
         target = self.ws.next_ids[:T]
-        if self.sampling is None or self.sampling.greedy:
+        sps = self.sampling if isinstance(self.sampling, (list, tuple)) else [self.sampling] * B
+        if all(sp is None or sp.greedy for sp in sps):
             ops.argmax_rows(lg, target, self.model.pdl)
         else:
             # speculative sampling: column j draws against draft j + 1 (the last column has no draft: bonus token);
-            # a rejected column already holds its replacement, so the chain rule below applies unchanged
-            sp = self.sampling
+            # a rejected column already holds its replacement, so the chain rule below applies unchanged.  Rows of a
+            # greedy sequence carry temperature 0 and fall back to arg-max acceptance inside the same kernel.
             dev = self.device
             d = torch.full((B, K + 1), -1, dtype=torch.int32, device=dev)
             d[:, :K] = self.drafts[:B]
             pos = torch.tensor([self.lengths[b] + j + 1 for b in range(B) for j in range(K + 1)], dtype=torch.int32, device=dev)
-            ops.sample_rows(lg, torch.full((T,), sp.temperature, device=dev),
-                            torch.full((T,), sp.top_k, dtype=torch.int32, device=dev),
-                            torch.full((T,), sp.top_p, device=dev), torch.full((T,), sp.min_p, device=dev), None, None, None,
-                            torch.full((T,), sp.seed, dtype=torch.int64, device=dev), pos, 0, target, None,
+
+            def rows(get, dtype):
+                return torch.tensor([get(sps[b]) for b in range(B) for _ in range(K + 1)], dtype=dtype, device=dev)
+            ops.sample_rows(lg, rows(lambda sp: 0.0 if sp is None else sp.temperature, torch.float32),
+                            rows(lambda sp: 1 if sp is None else sp.top_k, torch.int32),
+                            rows(lambda sp: 1.0 if sp is None else sp.top_p, torch.float32),
+                            rows(lambda sp: 0.0 if sp is None else sp.min_p, torch.float32), None, None, None,
+                            rows(lambda sp: 0 if sp is None else sp.seed, torch.int64), pos, 0, target, None,
                             d.view(-1), torch.empty(T, dtype=torch.int32, device=dev))
         # ---- accept + fold ----
         ops.accept_greedy_chain(target.view(B, K + 1), self.drafts[:B], self.n_acc[:B], self.out_tok[:B])
@@ -414,3 +419,111 @@ class SpeculativeGenerator(Generator):
     def tokens_per_round(self) -> float:
         B = max(1, len(self.rows))
         return self.emitted / max(1, self.rounds * B)
+
+
+class SpeculativeProgram:
+    """Lane-based Program (the Engine's interface) on top of the speculative generator: MTP chain drafts, one verify
+    pass per round, several committed tokens per lane and round.  Lanes join and leave between rounds; the
+    generator's per-sequence arrays are rebuilt from the lanes before every round, and the two pieces of draft state
+    that persist between rounds (first draft token, draft-module hidden state) are kept per block-table row.
+
+    Reference: ProgramImpl's speculative decode rounds (src/targets/qwen3_6/impl/runtime/mtp_impl.h,
+    speculative_target_impl.h) behind the same Program API as ordinary decode."""
+
+    def __init__(self, cfg: ModelConfig, weights: Dict[str, torch.Tensor], device, max_lanes: int = 8,
+                 max_context: int = 4096, draft_tokens: int = 3, **kw):
+        from .program import Lane, ProgramBase, SamplingParams  # noqa: F401
+        self.gen = SpeculativeGenerator(cfg, weights, device, max_lanes, max_context, draft_tokens=draft_tokens,
+                                        drafter="mtp", **kw)
+        self.cfg, self.max_lanes, self.max_context = cfg, max_lanes, max_context
+        self.K = draft_tokens
+        self._base = ProgramBase(cfg, max_lanes, max_context)
+        self.lanes = self._base.lanes
+        self.checkpoints: list = []
+        h = cfg.hidden
+        self.row_draft = torch.zeros(max_lanes, dtype=torch.int32, device=self.gen.device)
+        self.row_mtp_h = torch.zeros((max_lanes, h), dtype=torch.bfloat16, device=self.gen.device)
+
+    # ---- Program API ----
+    def free_lanes(self) -> int:
+        return len(self._base._free_rows)
+
+    def can_admit(self, n_prompt: int, max_new: int) -> bool:
+        g = self.gen
+        need = (n_prompt + max_new + self.K + 2 + g.page_size - 1) // g.page_size
+        return bool(self._base._free_rows) and n_prompt + max_new + self.K + 2 <= self.max_context and \
+            g.kv.pool.free_pages >= need and g.kv_mtp.pool.free_pages >= need
+
+    def open(self, prompt, sampling=None, session=None):
+        from .program import Lane, SamplingParams
+        if not self._base._free_rows:
+            raise MemoryError("no free lane")
+        row = self._base._free_rows.pop()
+        lane = Lane(self._base._next_id, row, self.gen.states.alloc(), list(prompt), 0, sampling or SamplingParams())
+        self._base._next_id += 1
+        self.lanes[lane.lane_id] = lane
+        return lane
+
+    def close(self, lane) -> None:
+        if self.lanes.pop(lane.lane_id, None) is None:
+            return
+        self.gen.kv.free_row(lane.row)
+        self.gen.kv_mtp.free_row(lane.row)
+        self.gen.states.release(lane.slot)
+        self._base._free_rows.append(lane.row)
+
+    def checkpoint(self, lane, session, kind) -> bool:
+        return False   # the draft module's cache is not part of a frontier yet: no prefix reuse in speculative mode
+
+    def prefill_step(self, lane, budget: int):
+        g = self.gen
+        n = min(budget, g.prefill_chunk, len(lane.tokens) - lane.n_cached)
+        done = lane.n_cached + n == len(lane.tokens)
+        for cache in (g.kv, g.kv_mtp):
+            cache.ensure(lane.row, lane.n_cached + n + self.K + 2)
+            cache.publish()
+        chunk = SeqChunk(lane.row, lane.slot, lane.n_cached, lane.tokens[lane.n_cached:lane.n_cached + n], done)
+        batch = g.bufs_prefill.build([chunk])
+        ids = g.model.forward_greedy(g.ws, batch, g.kv, g.states)
+        g.h_keep[:n].copy_(g.ws.normed[:n])
+        first = None
+        nxt = list(lane.tokens[lane.n_cached + 1:lane.n_cached + n + 1])
+        if done:
+            g.out_host[:1].copy_(ids[:1], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            first = int(g.out_host[0])
+            nxt = nxt + [first]
+        # the draft module reads the same positions (hidden state of p + token p + 1)
+        g._mtp_pass(batch, g.h_keep[:n], g._upload_next(nxt), [0] if done else [])
+        if done:
+            self.row_draft[lane.row] = g.drafts[0, 0]
+            self.row_mtp_h[lane.row].copy_(g.mtp_h[0])
+        lane.n_cached += n
+        g.model.status.check("after speculative prefill")
+        if done:
+            lane.last_token = first
+        return first
+
+    def decode_round(self, lanes):
+        g = self.gen
+        B = len(lanes)
+        if B == 0:
+            return []
+        rows = torch.tensor([l.row for l in lanes], dtype=torch.long, device=g.device)
+        g.rows = [l.row for l in lanes]
+        g.slots = [l.slot for l in lanes]
+        g.lengths = [l.n_cached for l in lanes]
+        g.last_tokens = [l.last_token for l in lanes]
+        g.history = [list(l.tokens) + [l.last_token] for l in lanes]
+        g.sampling = [l.sampling for l in lanes]
+        g.drafts[:B, 0] = self.row_draft[rows]
+        g.mtp_h[:B] = self.row_mtp_h[rows]
+        emitted = g.decode_round()
+        self.row_draft[rows] = g.drafts[:B, 0]
+        self.row_mtp_h[rows] = g.mtp_h[:B]
+        for l, toks in zip(lanes, emitted):
+            l.tokens.append(l.last_token)
+            l.tokens.extend(toks[:-1])
+            l.n_cached += len(toks)
+            l.last_token = toks[-1]
+        return emitted

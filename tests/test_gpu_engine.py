@@ -94,23 +94,59 @@ def test_session_checkpoint_reuse_on_gpu(setup):
 
 def test_host_cold_tier_round_trip_on_gpu(setup):
     """A frontier demoted to pinned host memory (KV pages of every layer + state image) and promoted back must
-    continue exactly like the device-resident one."""
+    continue exactly like a device-resident one."""
     cfg, _, engine = setup
     prog = engine.program
     prog.host_budget_bytes = 1 << 30
     turn1 = list(range(30, 97))
-    out1 = engine.submit(turn1, RequestOptions(max_tokens=7, session="cold-1")).wait(timeout=120)
-    turn2 = turn1 + out1 + [3, 4, 5]
-    hot = engine.submit(turn2, RequestOptions(max_tokens=6, session="cold-1")).wait(timeout=120)
-    # push every device-resident frontier to the host tier, then ask again
+    out_a = engine.submit(turn1, RequestOptions(max_tokens=7, session="tier-a")).wait(timeout=120)
+    out_b = engine.submit(turn1, RequestOptions(max_tokens=7, session="tier-b")).wait(timeout=120)
+    assert out_a == out_b
+    turn2 = turn1 + out_a + [3, 4, 5]
+    hot = engine.submit(turn2, RequestOptions(max_tokens=6, session="tier-a")).wait(timeout=120)   # device tier
+    # push every device-resident frontier to the host tier, then continue session b
     while any(c.tier == "gpu" for c in prog.checkpoints):
         assert prog._evict_checkpoint()
     assert all(c.tier == "host" for c in prog.checkpoints) and prog.cold_stats["demoted_host"] >= 2
     assert prog.kv.pool.free_pages == prog.kv.n_pages
-    promoted = prog.cold_stats["promoted"]
-    again = engine.submit(turn2, RequestOptions(max_tokens=6, session="cold-1")).wait(timeout=120)
-    assert prog.cold_stats["promoted"] == promoted + 1
-    assert again == hot   # same restored bytes, same kernels: bit-identical continuation
+    promoted, hits = prog.cold_stats["promoted"], engine.stats.prefix_hits
+    warm = engine.submit(turn2, RequestOptions(max_tokens=6, session="tier-b")).wait(timeout=120)  # host tier
+    assert prog.cold_stats["promoted"] == promoted + 1 and engine.stats.prefix_hits == hits + 1
+    assert warm == hot   # same restored bytes, same kernels: bit-identical continuation
     prog.host_budget_bytes = 0
     while prog._evict_checkpoint():
         pass
+
+
+def test_engine_with_speculative_program():
+    """MTP speculation behind the ordinary Engine API: several tokens committed per lane and round, lanes joining and
+    leaving between rounds, greedy and sampled lanes side by side."""
+    from ninfer_fusion_b200.runtime.speculative import SpeculativeProgram
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cuda", seed=9, std=0.05, with_mtp=True)
+    eng = Engine(lambda: SpeculativeProgram(cfg, w, "cuda", max_lanes=3, max_context=512, draft_tokens=3,
+                                            kv_format="bf16", page_size=16, prefill_chunk=64), prefill_chunk=64)
+    try:
+        torch.manual_seed(6)
+        prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (12, 80, 33, 7)]   # one more request than lanes
+        handles = [eng.submit(p, RequestOptions(max_tokens=11)) for p in prompts]
+        sampled = eng.submit(prompts[0], RequestOptions(max_tokens=9, sampling=SamplingParams(temperature=0.9, top_k=8, seed=5)))
+        outs = [h.wait(timeout=180) for h in handles]
+        s_out = sampled.wait(timeout=180)
+        assert all(len(o) == 11 and h.finish_reason == "length" for o, h in zip(outs, handles)) and len(s_out) == 9
+        ref = ReferenceModel(cfg, {k: v.cpu() for k, v in w.items() if not k.startswith("mtp/")})
+        agree = total = 0
+        for p, out in zip(prompts, outs):
+            seq = ReferenceSequence(cfg, R.KV_BF16)
+            hid = ref.forward(seq, torch.tensor(p))
+            for tok in out:
+                lg = ref.logits(hid[-1:])[0]
+                top2 = lg.topk(2).values
+                if (top2[0] - top2[1]).item() > 0.05:
+                    total += 1
+                    agree += int(int(R.argmax_lowest(lg[None])[0]) == tok)
+                hid = ref.forward(seq, torch.tensor([tok]))
+        assert total > 20 and agree / total >= 0.9, f"{agree}/{total}"
+        assert eng.program.gen.rounds > 0 and eng.health()["status"] == "ok"
+    finally:
+        eng.shutdown()
