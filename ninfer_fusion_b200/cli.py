@@ -41,7 +41,8 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--tokenizer", help="tokenizer.json (overrides the artifact's embedded one)")
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     ap.add_argument("--weights", default="bf16", choices=["bf16", "fp8", "nvfp4"], help="matmul weight format on the device")
-    ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8", "int8", "nvfp4"])
+    ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8", "fp8h", "int8", "nvfp4"],
+                    help="KV cache codec (fp8h = fp8 per-row with K in the Hadamard frame)")
     ap.add_argument("--kv-layer-spec", default="", help="per-layer KV storage, e.g. 'all:fp8' or '0-3:bf16,4-15:nvfp4'")
     ap.add_argument("--max-context", type=int, default=4096)
     ap.add_argument("--max-lanes", type=int, default=8, help="concurrent sequences")

@@ -28,6 +28,10 @@ struct AttnPrepParams {
   int table_stride;
   __nv_bfloat16* q_out;       // [T, n_q_heads, head_dim]
   KvLayer kv;
+  // K frame: 1 = q and k are rotated by the normalised Hadamard matrix of the head dimension before q is written
+  // and k is quantised (q . k is unchanged; outlier channels of k are spread over the row, which is what a per-row
+  // fp8 scale needs).  V is stored from its source values.
+  int k_hadamard = 0;
 };
 const char* attn_prep(const AttnPrepParams& p, cudaStream_t stream, bool pdl);
 

@@ -86,6 +86,32 @@ __global__ void __launch_bounds__(128) attn_prep_kernel(const AttnPrepParams p) 
     }
   }
 
+  if (kind != 2 && p.k_hadamard) {
+    // fast Walsh-Hadamard transform over the head: index = lane * VPL + j, one butterfly per index bit
+#pragma unroll
+    for (int s = 1; s < VPL; s <<= 1) {
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) {
+        if ((j & s) == 0) {
+          const float a = v[j], b = v[j | s];
+          v[j] = a + b;
+          v[j | s] = a - b;
+        }
+      }
+    }
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) {
+        const float o = __shfl_xor_sync(0xffffffffu, v[j], m);
+        v[j] = (lane & m) ? o - v[j] : v[j] + o;
+      }
+    }
+    const float norm = rsqrtf(static_cast<float>(D));
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) v[j] *= norm;
+  }
+
   if (kind == 0) {
     __nv_bfloat16* dst = p.q_out + (static_cast<long long>(t) * p.n_q_heads + h) * D + d0;
     uint32_t packed[VPL / 2];

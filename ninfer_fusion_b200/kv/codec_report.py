@@ -34,8 +34,11 @@ def run(seed: int = 0, n_q_heads: int = 8, n_kv_heads: int = 2, head_dim: int = 
     g = torch.Generator().manual_seed(seed)
     D = head_dim
     outliers = torch.randperm(D, generator=g)[:4]
-    formats = [("bf16", R.KV_BF16, D), ("fp8-e4m3-row", R.KV_FP8_ROW, D), (f"int8-g{int8_group}", R.KV_INT8_GROUP, int8_group),
-               ("nvfp4-g16", R.KV_NVFP4, 16)]
+    # "+hadamard": K (and the query) rotated by the normalised Hadamard matrix before K is quantised, which spreads
+    # the outlier channels over the row (the reference's fixed orthogonal K frame, src/ops/kv_cache/hadamard_d256.cuh)
+    formats = [("bf16", R.KV_BF16, D), ("fp8-e4m3-row", R.KV_FP8_ROW, D), ("fp8-e4m3-row+hadamard", R.KV_FP8_ROW, D),
+               (f"int8-g{int8_group}", R.KV_INT8_GROUP, int8_group), ("nvfp4-g16", R.KV_NVFP4, 16)]
+    Hn = R.hadamard_matrix(D)
     seqs = []
     n_pages_total = sum((n + page_size - 1) // page_size for n in lengths)
     perm = torch.randperm(n_pages_total, generator=g).tolist()
@@ -55,7 +58,10 @@ def run(seed: int = 0, n_q_heads: int = 8, n_kv_heads: int = 2, head_dim: int = 
         k_pages = torch.zeros(n_pages_total, n_kv_heads, page_size, D)
         v_pages = torch.zeros_like(k_pages)
         res = []
+        rotate = name.endswith("+hadamard")
         for q, k, v, table in seqs:
+            if rotate:
+                q, k = R.bf16_round(q @ Hn), R.bf16_round(k @ Hn)
             kq, vq = R.kv_quant_dequant(k, fmt, group), R.kv_quant_dequant(v, fmt, group)
             for t in range(k.shape[0]):
                 k_pages[table[t // page_size], :, t % page_size] = kq[t]

@@ -350,7 +350,7 @@ class HybridModel:
                       self.w[f"{prefix}/attn/q_norm"], self.w[f"{prefix}/attn/k_norm"], cfg.rms_eps, True,
                       cfg.rot_dim, self.inv_freq, self.rope_factor, b.rope_pos, b.table_row, b.cache_pos, kv.table, q,
                       planes.k_codes, planes.v_codes, planes.k_scales, planes.v_scales, kv.page_size, planes.fmt,
-                      planes.group, self.pdl)
+                      planes.group, self.pdl, planes.hadamard)
         gate = proj[:, q_dim + kv_dim: q_dim + kv_dim + q_dim]
         out = ws.mix_attn[:T]
         if (not b.one_token_per_seq and b.qblk_start is not None and D == 256 and self.attn_impl != 1

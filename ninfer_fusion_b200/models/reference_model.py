@@ -24,8 +24,9 @@ def _lin(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 class ReferenceSequence:
     """Holds one sequence's caches: dense K/V per attention layer, conv + ssm state per GDN layer."""
 
-    def __init__(self, cfg: ModelConfig, kv_format: int = R.KV_BF16, int8_group: int = 64):
+    def __init__(self, cfg: ModelConfig, kv_format: int = R.KV_BF16, int8_group: int = 64, k_hadamard: bool = False):
         self.cfg = cfg
+        self.k_hadamard = k_hadamard   # q and k rotated by the normalised Hadamard matrix before k is quantised
         self.kv_format = kv_format
         self.int8_group = int8_group
         self.k: List[torch.Tensor] = [torch.zeros(0, cfg.n_kv_heads, cfg.head_dim) for _ in cfg.attn_layers]
@@ -61,6 +62,10 @@ class ReferenceModel:
         k = R.bf16_round(R.rmsnorm(k, self.w[f"{p}/attn/k_norm"], cfg.rms_eps, True))
         q = R.bf16_round(R.rope_partial(q, pos, cfg.rot_dim, cfg.rope_theta, self.rope_factor, self.rope_inv))
         k = R.rope_partial(k, pos, cfg.rot_dim, cfg.rope_theta, self.rope_factor, self.rope_inv)
+        if seq.k_hadamard:
+            Hn = R.hadamard_matrix(D)
+            q = R.bf16_round(q @ Hn)
+            k = k @ Hn
         k = R.kv_quant_dequant(k, seq.kv_format, seq.int8_group)
         v = R.kv_quant_dequant(v, seq.kv_format, seq.int8_group)
         base = seq.k[ai].shape[0]

@@ -55,6 +55,14 @@ def rope_inv_freq_yarn(rot_dim: int, theta: float, factor: float = 4.0, original
     return out.float(), 0.1 * math.log(factor) + 1.0
 
 
+def hadamard_matrix(n: int) -> torch.Tensor:
+    """Normalised Sylvester-Hadamard matrix (symmetric, orthogonal): H_n / sqrt(n), n a power of two."""
+    H = torch.ones(1, 1)
+    while H.shape[0] < n:
+        H = torch.cat([torch.cat([H, H], 1), torch.cat([H, -H], 1)], 0)
+    return H / math.sqrt(n)
+
+
 def rope_partial(x: torch.Tensor, pos: torch.Tensor, rot_dim: int, theta: float,
                  attn_factor: float = 1.0, inv_freq: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x [T, H, D]; NeoX split-half rotation on the first rot_dim dims.

@@ -45,6 +45,7 @@ class KvLayerPlanes:
     v_codes: torch.Tensor
     k_scales: Optional[torch.Tensor]
     v_scales: Optional[torch.Tensor]
+    hadamard: bool = False   # K (and the matching Q) live in the normalised Hadamard frame ("fp8h")
 
     def bytes(self) -> int:
         n = self.k_codes.numel() + self.v_codes.numel()
@@ -153,7 +154,8 @@ class PagedKvCache:
         D = cfg.head_dim
         self.layers: List[KvLayerPlanes] = []
         for name in formats:
-            fmt = KV_FORMAT_NAMES[name]
+            hadamard = name == "fp8h"   # fp8 per-row codec with K stored in the Hadamard frame
+            fmt = KV_FORMAT_NAMES["fp8" if hadamard else name]
             group = int8_group if fmt == KV_INT8_GROUP else (16 if fmt == KV_NVFP4 else D)
             rb, sb = kv_row_bytes(fmt, D), kv_scale_bytes(fmt, D, group)
             shape = (n_pages, self.n_kv_heads, page_size, rb)
@@ -163,7 +165,7 @@ class PagedKvCache:
             if sb:
                 ks = torch.zeros((n_pages, self.n_kv_heads, page_size, sb), dtype=torch.uint8, device=self.device)
                 vs = torch.zeros_like(ks)
-            self.layers.append(KvLayerPlanes(fmt, group, k, v, ks, vs))
+            self.layers.append(KvLayerPlanes(fmt, group, k, v, ks, vs, hadamard))
         self.pool = PagePool(n_pages)
         self.max_rows = max_rows
         self.max_pages_per_row = max_pages_per_row

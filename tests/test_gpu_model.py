@@ -138,3 +138,28 @@ def test_yarn_rope_matches_reference():
                 agree += int(int(R.argmax_lowest(lg[None])[0]) == tok)
             h = ref.forward(seq, torch.tensor([tok]))
     assert total >= 8 and agree / total >= 0.9, f"{agree}/{total}"
+
+
+def test_fp8_hadamard_kv_matches_reference():
+    """fp8 per-row KV with K stored in the Hadamard frame ("fp8h"): engine vs the oracle with the same rotation."""
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cuda", seed=7, std=0.05)
+    gen = Generator(cfg, w, "cuda", max_batch=2, max_context=512, kv_format="fp8h", page_size=16, prefill_chunk=64,
+                    use_graph=True)
+    assert gen.kv.layers[0].hadamard and gen.kv.layers[0].fmt == R.KV_FP8_ROW
+    ref = ReferenceModel(cfg, w)
+    torch.manual_seed(4)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (60, 25)]
+    out = gen.generate(prompts, 10)
+    agree = total = 0
+    for b, p in enumerate(prompts):
+        seq = ReferenceSequence(cfg, R.KV_FP8_ROW, k_hadamard=True)
+        h = ref.forward(seq, torch.tensor(p))
+        for tok in out[b]:
+            lg = ref.logits(h[-1:])[0]
+            top2 = lg.topk(2).values
+            if (top2[0] - top2[1]).item() > 0.05:
+                total += 1
+                agree += int(int(R.argmax_lowest(lg[None])[0]) == tok)
+            h = ref.forward(seq, torch.tensor([tok]))
+    assert total >= 10 and agree / total >= 0.9, f"{agree}/{total}"

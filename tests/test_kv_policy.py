@@ -85,3 +85,16 @@ def test_block_descent_one_rung_per_pass_oldest_first():
     cells2.touch(1, 6400)
     tight = DescentConfig(min_age_tokens=0, max_cells_per_pass=1000, target_resident_bytes=10**12)
     assert plan_descent_pass(cells2, tight, 4, 256) == []
+
+
+def test_hadamard_frame_is_an_equivalent_k_frame():
+    from ninfer_fusion_b200.kv.codec_report import run
+    from ninfer_fusion_b200.ops import reference as R
+    import torch
+    c = run()["codecs"]
+    # a floating-point codec keeps relative precision per value, so the rotation neither helps nor hurts much (it
+    # matters for fixed-point codecs); what must hold is that q.k is preserved and the error stays in the same range
+    a, b = c["fp8-e4m3-row+hadamard"], c["fp8-e4m3-row"]
+    assert a["mean_abs_err"] < 1.3 * b["mean_abs_err"] and a["max_abs_err"] < 1.3 * b["max_abs_err"]
+    H = R.hadamard_matrix(256)
+    assert torch.allclose(H @ H.t(), torch.eye(256), atol=1e-5) and torch.equal(H, H.t())
