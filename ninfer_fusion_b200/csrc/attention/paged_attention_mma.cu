@@ -37,11 +37,11 @@ struct Smem {
   __half vt[D][kLdV];          // 36,864 B
   __half q[16][kLdQ];          //  8,448 B
   __half p[16][kLdP];          //  2,304 B
-  float kscale[kTileKeys];
-  float vscale[kTileKeys];
+  float kscale[2][kTileKeys];   // per-tile buffers, double-buffered with the row indices
+  float vscale[2][kTileKeys];
   float rowmax[4][16];
   float rowsum[4][16];
-  long long rowidx[kTileKeys];
+  long long rowidx[2][kTileKeys];
 };
 
 template <int FORMAT>
@@ -96,9 +96,14 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
 #pragma unroll
     for (int j = 0; j < 4; ++j) o[n][j] = 0.f;
 
-  for (int kb = k_begin; kb < k_end; kb += kTileKeys) {
-    __syncthreads();  // previous tile fully consumed (also orders the Q stores on the first pass)
-    // ---- 1. gather + dequantise the tile ----
+  // Raw (still quantised) K / V units of one tile, held in registers between their global loads and
+  // their conversion into shared memory.  With a narrow KV format the next tile's loads are issued
+  // before the current tile's math, so that their latency hides behind the MMAs; bf16 rows would
+  // need twice the registers and keep the load-then-convert order.
+  constexpr bool kPrefetch = FORMAT != kKvBf16;
+  RawUnit<FORMAT> rawk[8], rawv[8];
+
+  auto gather_idx = [&](int kb, int buf) {
     if (threadIdx.x < kTileKeys) {
       const int key = kb + threadIdx.x;
       long long r = -1;
@@ -114,63 +119,85 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
           vs = 1.f;
         }
       }
-      sm.rowidx[threadIdx.x] = r;
-      sm.kscale[threadIdx.x] = ks;
-      sm.vscale[threadIdx.x] = vs;
+      sm.rowidx[buf][threadIdx.x] = r;
+      sm.kscale[buf][threadIdx.x] = ks;
+      sm.vscale[buf][threadIdx.x] = vs;
     }
+  };
+  // K: unit = (key, part), 1024 units, 8 per thread; consecutive lanes read consecutive 16 values of a row.
+  // V: unit = (key pair, part), 512 units, 4 per thread, two rows each.  All sixteen loads are in flight together.
+  auto load_raw = [&](int buf) {
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int u = it * 128 + threadIdx.x;
+      const long long r = sm.rowidx[buf][u >> 4];
+      rawk[it].clear();
+      if (r >= 0) rawk[it].load(p.kv, p.kv.k_codes, p.kv.k_scales, r, u & 15);
+    }
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int u = it * 128 + threadIdx.x;
+      const int jp = u >> 4, part = u & 15;
+      const long long r0 = sm.rowidx[buf][2 * jp], r1 = sm.rowidx[buf][2 * jp + 1];
+      rawv[2 * it].clear();
+      rawv[2 * it + 1].clear();
+      if (r0 >= 0) rawv[2 * it].load(p.kv, p.kv.v_codes, p.kv.v_scales, r0, part);
+      if (r1 >= 0) rawv[2 * it + 1].load(p.kv, p.kv.v_codes, p.kv.v_scales, r1, part);
+    }
+  };
+  // Dequantise to fp16: K as [key][d]; V transposed, two keys per 32-bit word, column index XOR-swizzled by
+  // the row's 16-row group to spread the transposed stores over banks.
+  auto store_tile = [&]() {
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int u = it * 128 + threadIdx.x;
+      uint32_t h[8];
+      rawk[it].convert(h);
+      uint4* dst = reinterpret_cast<uint4*>(&sm.k[u >> 4][(u & 15) * 16]);
+      dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
+      dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
+    }
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int u = it * 128 + threadIdx.x;
+      const int jp = u >> 4, part = u & 15;
+      uint32_t h0[8], h1[8];
+      rawv[2 * it].convert(h0);
+      rawv[2 * it + 1].convert(h1);
+      const int col = (2 * jp) ^ ((part & 7) * 8);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        // h0[i] = (v[key0][d], v[key0][d+1]), h1[i] likewise for key1 -> rows d and d+1 get (key0, key1)
+        *reinterpret_cast<uint32_t*>(&sm.vt[part * 16 + 2 * i][col]) = __byte_perm(h0[i], h1[i], 0x5410);
+        *reinterpret_cast<uint32_t*>(&sm.vt[part * 16 + 2 * i + 1][col]) = __byte_perm(h0[i], h1[i], 0x7632);
+      }
+    }
+  };
+
+  if constexpr (kPrefetch) {
+    gather_idx(k_begin, 0);
     __syncthreads();
-    // K: unit = (key, part), 1024 units, 8 per thread; consecutive lanes read consecutive 16 values of a row.
-    // All eight loads are issued before the first conversion.
-    {
-      RawUnit<FORMAT> raw[8];
-#pragma unroll
-      for (int it = 0; it < 8; ++it) {
-        const int u = it * 128 + threadIdx.x;
-        const long long r = sm.rowidx[u >> 4];
-        raw[it].clear();
-        if (r >= 0) raw[it].load(p.kv, p.kv.k_codes, p.kv.k_scales, r, u & 15);
-      }
-#pragma unroll
-      for (int it = 0; it < 8; ++it) {
-        const int u = it * 128 + threadIdx.x;
-        uint32_t h[8];
-        raw[it].convert(h);
-        uint4* dst = reinterpret_cast<uint4*>(&sm.k[u >> 4][(u & 15) * 16]);
-        dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
-        dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
-      }
+    load_raw(0);
+  }
+  int buf = 0;
+  for (int kb = k_begin; kb < k_end; kb += kTileKeys, buf ^= 1) {
+    // ---- 1. gather + dequantise the tile ----
+    const bool has_next = kb + kTileKeys < k_end;
+    if constexpr (kPrefetch) {
+      __syncthreads();  // previous tile fully consumed (also orders the Q stores on the first pass)
+      store_tile();
+      if (has_next) gather_idx(kb + kTileKeys, buf ^ 1);
+      __syncthreads();
+      if (has_next) load_raw(buf ^ 1);  // in flight during this tile's math
+    } else {
+      gather_idx(kb, buf);
+      __syncthreads();  // previous tile fully consumed, this tile's row indices visible
+      load_raw(buf);
+      store_tile();
+      __syncthreads();
     }
-    // V: unit = (key pair, part), 512 units, 4 per thread; stored transposed, two keys per 32-bit word,
-    // column index XOR-swizzled by the row's 16-row group to spread the transposed stores over banks
-    {
-      RawUnit<FORMAT> raw[8];
-#pragma unroll
-      for (int it = 0; it < 4; ++it) {
-        const int u = it * 128 + threadIdx.x;
-        const int jp = u >> 4, part = u & 15;
-        const long long r0 = sm.rowidx[2 * jp], r1 = sm.rowidx[2 * jp + 1];
-        raw[2 * it].clear();
-        raw[2 * it + 1].clear();
-        if (r0 >= 0) raw[2 * it].load(p.kv, p.kv.v_codes, p.kv.v_scales, r0, part);
-        if (r1 >= 0) raw[2 * it + 1].load(p.kv, p.kv.v_codes, p.kv.v_scales, r1, part);
-      }
-#pragma unroll
-      for (int it = 0; it < 4; ++it) {
-        const int u = it * 128 + threadIdx.x;
-        const int jp = u >> 4, part = u & 15;
-        uint32_t h0[8], h1[8];
-        raw[2 * it].convert(h0);
-        raw[2 * it + 1].convert(h1);
-        const int col = (2 * jp) ^ ((part & 7) * 8);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          // h0[i] = (v[key0][d], v[key0][d+1]), h1[i] likewise for key1 -> rows d and d+1 get (key0, key1)
-          *reinterpret_cast<uint32_t*>(&sm.vt[part * 16 + 2 * i][col]) = __byte_perm(h0[i], h1[i], 0x5410);
-          *reinterpret_cast<uint32_t*>(&sm.vt[part * 16 + 2 * i + 1][col]) = __byte_perm(h0[i], h1[i], 0x7632);
-        }
-      }
-    }
-    __syncthreads();
+    const float* kscale = sm.kscale[buf];
+    const float* vscale = sm.vscale[buf];
 
     // ---- 2. S = Q K^T for this warp's 16 keys ----
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -195,7 +222,7 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
         const int key = kb + kl;
         bool valid = key < k_end;
         if (valid && key >= tbase) valid = (tmask >> (key - tbase)) & 1ull;
-        const float v = valid ? s[n][j] * sm.kscale[kl] : -CUDART_INF_F;
+        const float v = valid ? s[n][j] * kscale[kl] : -CUDART_INF_F;
         s[n][j] = v;
         mx[j >> 1] = fmaxf(mx[j >> 1], v);
       }
@@ -230,7 +257,7 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
         const float mn = m_run[j >> 1];
         pv[j] = (s[n][j] == -CUDART_INF_F) ? 0.f : exp2f(s[n][j] - mn);
         l_run[j >> 1] += pv[j];
-        pv[j] *= sm.vscale[kl + (j & 1)];
+        pv[j] *= vscale[kl + (j & 1)];
       }
       *reinterpret_cast<uint32_t*>(&sm.p[row0][kl]) = pack_half2(pv[0], pv[1]);
       *reinterpret_cast<uint32_t*>(&sm.p[row0 + 8][kl]) = pack_half2(pv[2], pv[3]);

@@ -6,8 +6,8 @@
 namespace nfb {
 
 enum GemmEpilogue : int {
-  kEpiStore = 0,     // out = acc (+ bias[n])
-  kEpiResidual = 1,  // out = resid + acc
+  kEpiStore = 0,     // out = act(acc (+ bias[n]))
+  kEpiResidual = 1,  // out = resid + acc (+ bias[n])
   kEpiSwiglu = 2,    // W = [gate; up] (N rows), out[T, N/2] = silu(gate) * up
   kEpiPartial = 3,   // partial[z, T, N] = acc over this split's K range (fp32)
   kEpiPushPartial = 4,  // tensor parallel: fp32 partial tiles are stored into the OWNER rank's receive
@@ -17,6 +17,8 @@ enum GemmEpilogue : int {
                         // buffer [parity][src_rank][T_cap][N] (one-shot all-reduce by push) and every
                         // rank's arrival counter is incremented (GEMM -> all-reduce in one kernel)
 };
+
+enum GemmActivation : int { kActNone = 0, kActGeluTanh = 1, kActGeluErf = 2 };
 
 constexpr int kMaxRanks = 8;
 
@@ -29,7 +31,8 @@ struct GemmArgs {
   int64_t ldo = 0;
   const void* resid = nullptr;
   int64_t ldr = 0;
-  const float* bias = nullptr;
+  const float* bias = nullptr;   // [N] fp32, added by kEpiStore and kEpiResidual
+  int act = kActNone;            // kEpiStore: out = act(acc + bias)
   float* partial = nullptr;
   int splits = 1;
   int epi = kEpiStore;

@@ -63,6 +63,7 @@ struct KernelParams {
   const __nv_bfloat16* resid;
   long long ldr;
   const float* bias;
+  int act;  // kActNone / kActGeluTanh / kActGeluErf, applied after the bias (kEpiStore only)
   float* partial;      // [splits, T, N] fp32
   int* status;
   // kEpiPushPartial: tensor-parallel reduce-scatter by peer stores
@@ -75,6 +76,15 @@ struct KernelParams {
   int world, T_cap;
   const unsigned int* call_idx;  // device counter of finished reduce calls; its parity picks the buffer
 };
+
+// GELU in the two forms vision towers use: tanh approximation (transformer blocks) and exact erf (merger).
+__device__ __forceinline__ float gelu(float x, int mode) {
+  if (mode == kActGeluTanh) {
+    const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    return 0.5f * x * (1.f + tanhf(u));
+  }
+  return 0.5f * x * (1.f + erff(x * 0.7071067811865476f));
+}
 
 template <int TN, int EPI, bool DEEP>
 __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CUtensorMap tmap_w,
@@ -300,7 +310,7 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
       }
     } else {
       const int n = n0 + warp * 32 + lane;
-      const float bias = (EPI == kEpiStore && p.bias != nullptr && n < p.N) ? p.bias[n] : 0.f;
+      const float bias = ((EPI == kEpiStore || EPI == kEpiResidual) && p.bias != nullptr && n < p.N) ? p.bias[n] : 0.f;
       for (int c = 0; c < TN; c += kChunk) {
         if (t0 + c >= p.T) break;
         float v[kChunk];
@@ -353,8 +363,14 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
           }
 #pragma unroll
           for (int m = 0; m < kChunk / 2; ++m) {
-            const float a0 = v[2 * m] + bias;
-            const float a1 = v[2 * m + 1] + bias;
+            float a0 = v[2 * m] + bias;
+            float a1 = v[2 * m + 1] + bias;
+            if constexpr (EPI == kEpiStore) {
+              if (p.act != kActNone) {
+                a0 = gelu(a0, p.act);
+                a1 = gelu(a1, p.act);
+              }
+            }
             const float send = (lane & 1) ? a0 : a1;
             const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
             const int t = t0 + c + 2 * m + (lane & 1);
@@ -595,7 +611,7 @@ const char* gemm_bf16(const GemmArgs& a) {
   if (a.epi == kEpiSwiglu && (kp.N % 4)) return "gemm_bf16: SwiGLU needs N % 4 == 0";
   kp.out = static_cast<__nv_bfloat16*>(a.out); kp.ldo = a.ldo;
   kp.resid = static_cast<const __nv_bfloat16*>(a.resid); kp.ldr = a.ldr;
-  kp.bias = a.bias; kp.partial = a.partial; kp.status = a.status;
+  kp.bias = a.bias; kp.act = a.epi == kEpiStore ? a.act : kActNone; kp.partial = a.partial; kp.status = a.status;
   if (a.epi == kEpiResidual && a.resid == nullptr) return "gemm_bf16: residual epilogue without residual";
   if (a.epi == kEpiPartial && a.partial == nullptr) return "gemm_bf16: split-K without workspace";
   const bool needs_out = a.epi == kEpiStore || a.epi == kEpiResidual || a.epi == kEpiSwiglu;

@@ -44,10 +44,11 @@ int64_t sm_count() {
 
 // out = epilogue(x @ w^T).  epi: 0 store(+bias), 1 residual add, 2 swiglu, 3 split-K partials.
 void gemm_bf16(const Tensor& x, const Tensor& w, OptT out, int64_t epi, OptT resid, OptT bias, OptT partial,
-               int64_t splits, OptT status, bool pdl) {
+               int64_t splits, OptT status, bool pdl, int64_t act) {
   need(x, at::kBFloat16, "x"); need(w, at::kBFloat16, "w");
   need_rows(x, "x"); need_rows(w, "w");
   TORCH_CHECK(x.size(1) == w.size(1), "gemm_bf16: K mismatch");
+  TORCH_CHECK(act >= 0 && act <= 2 && (act == 0 || epi == nfb::kEpiStore), "gemm_bf16: activation needs the store epilogue");
   c10::cuda::CUDAGuard guard(x.device());
   nfb::GemmArgs a;
   a.w = w.data_ptr(); a.N = w.size(0); a.K = w.size(1); a.ldw = w.stride(0);
@@ -76,7 +77,7 @@ void gemm_bf16(const Tensor& x, const Tensor& w, OptT out, int64_t epi, OptT res
     TORCH_CHECK(partial->is_contiguous() && partial->numel() >= splits * a.T * a.N, "gemm_bf16: workspace too small");
     a.partial = static_cast<float*>(partial->data_ptr());
   }
-  a.splits = static_cast<int>(splits); a.epi = static_cast<int>(epi);
+  a.splits = static_cast<int>(splits); a.epi = static_cast<int>(epi); a.act = static_cast<int>(act);
   a.status = ptr_or_null<int>(status);
   a.stream = cur_stream(); a.pdl = pdl;
   chk(nfb::gemm_bf16(a));
@@ -629,7 +630,7 @@ TORCH_LIBRARY(nfb200, m) {
   m.def("tp_state_bytes() -> int", &tp_state_bytes);
   m.def("gemm_bf16_push_all(Tensor x, Tensor w, int splits, int world, int rank, int[] peer_bases, int recv_off, int flag_off, int T_cap, Tensor state, Tensor? status, bool pdl) -> ()", &gemm_bf16_push_all);
   m.def("tp_sum_norm(int world, int T_cap, int arrivals, int my_base, int recv_off, int flag_off, Tensor x, Tensor? norm_w, Tensor? normed, float eps, bool unit_offset, Tensor state, Tensor? status, bool pdl) -> ()", &tp_sum_norm);
-  m.def("gemm_bf16(Tensor x, Tensor w, Tensor? out, int epi, Tensor? resid, Tensor? bias, Tensor? partial, int splits, Tensor? status, bool pdl) -> ()", &gemm_bf16);
+  m.def("gemm_bf16(Tensor x, Tensor w, Tensor? out, int epi, Tensor? resid, Tensor? bias, Tensor? partial, int splits, Tensor? status, bool pdl, int act=0) -> ()", &gemm_bf16);
   m.def("gemm_trace(bool enable, int n_ctas) -> Tensor", &gemm_trace);
   m.def("gemm_pick_splits(int T, int N, int K, int epi) -> int", &gemm_pick_splits);
   m.def("add_rmsnorm(Tensor? partial, int splits, Tensor? delta, Tensor? resid_in, Tensor? resid_out, Tensor? norm_w, Tensor? normed, int T, int N, float eps, bool unit_offset, bool pdl, Tensor? q_codes=None, Tensor? q_sf=None) -> ()", &add_rmsnorm);

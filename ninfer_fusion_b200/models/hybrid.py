@@ -51,6 +51,9 @@ class StepBatch:
     tree_commit: Optional[torch.Tensor] = None  # uint8 [T]
     tree_mask: Optional[torch.Tensor] = None    # int64 [T]
     tree_base: Optional[torch.Tensor] = None    # int32 [T]
+    # multimodal prefill: rows of the step whose embedding is replaced by a vision-tower output row
+    embed_rows: Optional[torch.Tensor] = None   # int64 [V]
+    embed_vals: Optional[torch.Tensor] = None   # bf16 [V, hidden]
 
 
 class Workspace:
@@ -170,7 +173,7 @@ class LaunchCounter:
         fn = self._cache.get(name)
         if fn is None:
             raw = getattr(self._ops, name)
-            if name in ("gemm_pick_splits", "prefill_attn_block_tokens"):
+            if name in ("gemm_pick_splits", "prefill_attn_block_tokens", "packed_attention_tile"):
                 fn = raw
             elif name == "causal_conv1d_silu":
                 def fn(*a, _raw=raw):
@@ -481,6 +484,8 @@ class HybridModel:
             raise ValueError(f"step of {T} tokens exceeds the workspace ({ws.max_tokens})")
         x = ws.x[:T]
         ops.embed_gather(b.ids, self.w[f"{self.prefix}/embed"], x, self.pdl)
+        if b.embed_rows is not None and b.embed_rows.numel():
+            x.index_copy_(0, b.embed_rows, b.embed_vals)   # visual tokens replace their placeholder embeddings
         first = f"{self.prefix}/layers/0/input_norm"
         self._add_rmsnorm(None, 0, None, x, None, self.w[first], ws.normed[:T], T, cfg.hidden)
         for layer in range(cfg.n_layers):

@@ -119,11 +119,17 @@ class ReferenceModel:
         return out + torch.sigmoid(router[:, m.n_experts:]) * shared
 
     # ---- forward over T new tokens of one sequence ----
-    def forward(self, seq: ReferenceSequence, ids: torch.Tensor, trace: Optional[dict] = None) -> torch.Tensor:
+    def forward(self, seq: ReferenceSequence, ids: torch.Tensor, trace: Optional[dict] = None,
+                positions: Optional[torch.Tensor] = None, embed_rows: Optional[torch.Tensor] = None,
+                embed_vals: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """`positions` ([T] or [T, 3]) overrides the default cache positions for the rope; `embed_vals` rows replace the
+        token embeddings at `embed_rows` (visual tokens of a multimodal prompt)."""
         cfg, pf = self.cfg, self.prefix
         T = ids.shape[0]
-        pos = seq.n_tokens + torch.arange(T)
+        pos = seq.n_tokens + torch.arange(T) if positions is None else positions
         x = self.w[f"{pf}/embed"][ids.long()].float()
+        if embed_rows is not None:
+            x[embed_rows.long()] = embed_vals.float()
         for layer in range(cfg.n_layers):
             p = f"{pf}/layers/{layer}"
             normed = R.bf16_round(R.rmsnorm(x, self.w[f"{p}/input_norm"], cfg.rms_eps, True))

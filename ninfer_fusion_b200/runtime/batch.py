@@ -11,6 +11,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import List, Sequence
 
+import numpy as np
 import torch
 
 from ..models.hybrid import StepBatch
@@ -25,6 +26,7 @@ class SeqChunk:
     tokens: Sequence[int]
     want_logits: bool = True   # logits for the chunk's last token
     all_logits: bool = False   # logits for every token of the chunk (speculative verify)
+    positions: object = None   # optional int [n, 3] rope positions (multimodal prefill); default = cache positions
 
 
 class StepBuffers:
@@ -86,8 +88,12 @@ class StepBuffers:
             pos = range(c.start_pos, c.start_pos + n)
             cpos[t:t + n] = pos
             kvl[t:t + n] = range(c.start_pos + 1, c.start_pos + n + 1)
-            d = rope_delta[b] if rope_delta is not None else 0
-            if self.pos_axes == 1:
+            d = rope_delta[b] if rope_delta is not None and b < len(rope_delta) else 0
+            if c.positions is not None:
+                if self.pos_axes != 3:
+                    raise ValueError("explicit positions need three-axis step buffers")
+                rpos[3 * t:3 * (t + n)] = np.asarray(c.positions, dtype=np.int32).reshape(-1)
+            elif self.pos_axes == 1:
                 rpos[t:t + n] = range(c.start_pos + d, c.start_pos + d + n)
             else:
                 for a in range(3):

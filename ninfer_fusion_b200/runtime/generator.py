@@ -11,6 +11,7 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..models.config import ModelConfig
@@ -59,6 +60,9 @@ class Generator:
         self.slots: List[int] = []
         self.lengths: List[int] = []
         self.last_tokens: List[int] = []
+        self.rope_delta: List[int] = []   # per sequence: rope position - cache position after a multimodal prompt
+        self.vision = None                # VisionTower, attached by the caller for multimodal prompts
+        self._bufs_prefill_mm = None
         self.launches_per_step = 0
 
     # ------------------------------------------------------------------ sequences
@@ -67,14 +71,45 @@ class Generator:
             self.kv.free_row(r)
         for s in self.slots:
             self.states.release(s)
-        self.rows, self.slots, self.lengths, self.last_tokens = [], [], [], []
+        self.rows, self.slots, self.lengths, self.last_tokens, self.rope_delta = [], [], [], [], []
 
-    def prefill(self, prompts: Sequence[Sequence[int]]) -> List[int]:
-        """Prefill all prompts (chunked, ragged-packed); returns each sequence's first new token."""
+    def _encode_media(self, media) -> List[Optional[torch.Tensor]]:
+        """Runs the vision tower over every prompt's media; one [V, hidden] tensor per prompt (None = text only)."""
+        from ..models.vision import build_control
+        if self.vision is None:
+            raise ValueError("prompt carries media but no vision tower is attached")
+        out: List[Optional[torch.Tensor]] = []
+        for pm in media:
+            if pm is None or not pm.items:
+                out.append(None)
+                continue
+            control = build_control(pm.grids, self.vision.cfg.merge)
+            if control.n_tokens != len(pm.embed_rows):
+                raise ValueError("pad-token count does not match the media grids")
+            out.append(self.vision.encode(pm.patches(), control))
+        return out
+
+    def prefill(self, prompts: Sequence[Sequence[int]], media: Optional[Sequence] = None) -> List[int]:
+        """Prefill all prompts (chunked, ragged-packed); returns each sequence's first new token.
+
+        `media[b]` (optional) is the prepared multimodal prompt of sequence b (frontend.media.PreparedPrompt whose
+        ids equal prompts[b]): its visual tokens replace the pad-token embeddings and its three-axis positions
+        drive the rope; later decode positions are shifted by its rope_delta."""
         if len(prompts) > self.max_batch:
             raise ValueError("too many sequences")
         self.reset()
         B = len(prompts)
+        bufs = self.bufs_prefill
+        visual: List[Optional[torch.Tensor]] = [None] * B
+        if media is not None and any(m is not None for m in media):
+            if len(media) != B or any(m is not None and list(m.ids) != list(prompts[b]) for b, m in enumerate(media)):
+                raise ValueError("media must hold one prepared prompt (or None) per sequence, with the same ids")
+            visual = self._encode_media(media)
+            if self._bufs_prefill_mm is None:
+                self._bufs_prefill_mm = StepBuffers(bufs.max_tokens, bufs.max_seqs, self.device, mrope=True,
+                                                    attn_block_tokens=bufs.attn_block_tokens)
+            bufs = self._bufs_prefill_mm
+        self.rope_delta = [0 if (media is None or media[b] is None) else int(media[b].rope_delta) for b in range(B)]
         for b in range(B):
             self.rows.append(b)
             self.slots.append(self.states.alloc())
@@ -87,18 +122,31 @@ class Generator:
         while pending:
             budget = self.prefill_chunk
             chunks, owners = [], []
+            e_rows, e_vals = [], []
             for b in list(pending):
                 if budget == 0 or len(chunks) == self.max_batch:
                     break
                 n = min(budget, len(prompts[b]) - cursor[b])
                 done = cursor[b] + n == len(prompts[b])
-                chunks.append(SeqChunk(self.rows[b], self.slots[b], cursor[b], prompts[b][cursor[b]:cursor[b] + n], done))
+                chunk = SeqChunk(self.rows[b], self.slots[b], cursor[b], prompts[b][cursor[b]:cursor[b] + n], done)
+                if visual[b] is not None:
+                    pm = media[b]
+                    chunk.positions = pm.positions[cursor[b]:cursor[b] + n]
+                    lo, hi = np.searchsorted(pm.embed_rows, [cursor[b], cursor[b] + n])
+                    if hi > lo:
+                        step_row0 = self.prefill_chunk - budget
+                        e_rows.append(torch.from_numpy(pm.embed_rows[lo:hi].astype(np.int64) - cursor[b] + step_row0))
+                        e_vals.append(visual[b][lo:hi])
+                chunks.append(chunk)
                 owners.append((b, done))
                 cursor[b] += n
                 budget -= n
                 if done:
                     pending.remove(b)
-            batch = self.bufs_prefill.build(chunks)
+            batch = bufs.build(chunks)
+            if e_rows:
+                batch.embed_rows = torch.cat(e_rows).to(self.device, non_blocking=True)
+                batch.embed_vals = torch.cat(e_vals)
             ids = self.model.forward_greedy(self.ws, batch, self.kv, self.states)
             if ids.numel():
                 self.out_host[: ids.numel()].copy_(ids, non_blocking=True)
@@ -128,7 +176,7 @@ class Generator:
         key = (B, bucket, advance)
         if key in self._graphs:
             return self._graphs[key], self._graph_batches[key]
-        batch = self.bufs_decode.build(self._decode_chunks(), upload=True)
+        batch = self.bufs_decode.build(self._decode_chunks(), upload=True, rope_delta=self.rope_delta)
         batch.max_kv_len = bucket  # bake the bucket's split geometry, not this step's
         stream = torch.cuda.Stream(device=self.device)
         stream.wait_stream(torch.cuda.current_stream())
@@ -171,11 +219,11 @@ class Generator:
         if self.use_graph:
             bucket = context_bucket(max(self.lengths) + 1)
             graph, _ = self._graph_for(B, bucket, advance=False)
-            self.bufs_decode.build(self._decode_chunks(), upload=True)
+            self.bufs_decode.build(self._decode_chunks(), upload=True, rope_delta=self.rope_delta)
             graph.replay()
             ids = self.ws.next_ids[:B]
         else:
-            batch = self.bufs_decode.build(self._decode_chunks(), upload=True)
+            batch = self.bufs_decode.build(self._decode_chunks(), upload=True, rope_delta=self.rope_delta)
             ids = self.model.forward_greedy(self.ws, batch, self.kv, self.states)
         self.out_host[:B].copy_(ids, non_blocking=True)
         if self.device.type == "cuda":
@@ -194,7 +242,7 @@ class Generator:
         self._ensure_pages(n_steps + 1)
         bucket = context_bucket(max(self.lengths) + n_steps + 1)
         graph, batch = self._graph_for(B, bucket, advance=True)
-        self.bufs_decode.build(self._decode_chunks(), upload=True)
+        self.bufs_decode.build(self._decode_chunks(), upload=True, rope_delta=self.rope_delta)
 
         def finish():
             self.out_host[:B].copy_(self.ws.next_ids[:B])

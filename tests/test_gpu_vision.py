@@ -1,0 +1,181 @@
+"""Vision kernels and the tower against plain PyTorch fp32 references; multimodal prefill against the oracle model."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from ninfer_fusion_b200.models import vision as V
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from ninfer_fusion_b200._lib import load_native
+    return load_native()
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp(min=1e-9)).item()
+
+
+@pytest.mark.parametrize("T,D", [(5, 1152), (130, 1152), (33, 256)])
+def test_layer_norm(ops, T, D):
+    torch.manual_seed(0)
+    x = (torch.randn(T, D) * 2 + 0.3).to(torch.bfloat16).cuda()
+    w = (1 + 0.1 * torch.randn(D)).to(torch.bfloat16).cuda()
+    b = (0.1 * torch.randn(D)).to(torch.bfloat16).cuda()
+    out = torch.empty_like(x)
+    ops.layer_norm(x, w, b, out, 1e-6)
+    ref = torch.nn.functional.layer_norm(x.float(), (D,), w.float(), b.float(), 1e-6)
+    assert (out.float() - ref).abs().max().item() < 0.03
+    assert _rel(out, ref) < 4e-3
+    ops.layer_norm(x, w, None, out, 1e-6)
+    ref = torch.nn.functional.layer_norm(x.float(), (D,), w.float(), None, 1e-6)
+    assert _rel(out, ref) < 4e-3
+
+
+@pytest.mark.parametrize("act", [0, 1, 2])
+def test_gemm_bias_activation_and_bias_residual(ops, act):
+    torch.manual_seed(1)
+    T, N, K = 70, 4304, 1152
+    x = (torch.randn(T, K) / 4).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K) / math.sqrt(K)).to(torch.bfloat16).cuda()
+    bias = torch.randn(N).cuda()
+    out = torch.empty((T, N), dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ops.gemm_bf16(x, w, out, 0, None, bias, None, 1, status, False, act)
+    ref = x.float() @ w.float().t() + bias
+    if act == 1:
+        ref = torch.nn.functional.gelu(ref, approximate="tanh")
+    elif act == 2:
+        ref = torch.nn.functional.gelu(ref)
+    assert _rel(out, ref) < 5e-3
+    if act == 0:
+        # K = 4304 is not a multiple of the 64-wide k block; bias joins the residual epilogue
+        x2 = (torch.randn(T, N) / 4).to(torch.bfloat16).cuda()
+        w2 = (torch.randn(K, N) / math.sqrt(N)).to(torch.bfloat16).cuda()
+        b2 = torch.randn(K).cuda()
+        resid = torch.randn(T, K).to(torch.bfloat16).cuda()
+        ref2 = resid.float() + x2.float() @ w2.float().t() + b2
+        ops.gemm_bf16(x2, w2, resid, 1, resid, b2, None, 1, status, False, 0)
+        assert _rel(resid, ref2) < 5e-3
+    assert int(status[0]) == 0
+
+
+def test_pos_embed_and_rope(ops):
+    torch.manual_seed(2)
+    cfg = V.VisionConfig()
+    ctl = V.build_control([(1, 6, 10), (2, 4, 4)])
+    P = ctl.n_patches
+    table = (0.5 * torch.randn(cfg.pos_side ** 2, cfg.hidden)).to(torch.bfloat16)
+    x = torch.randn(P, cfg.hidden).to(torch.bfloat16)
+    ref = x.float() + V.pos_embed_reference(table, ctl, cfg.pos_side)
+    xd = x.cuda()
+    pos = torch.from_numpy(ctl.pos_yx).cuda()
+    ghw = torch.from_numpy(ctl.grid_hw).cuda()
+    ops.vision_pos_embed_add(xd, table.cuda(), pos, ghw, cfg.pos_side)
+    assert (xd.float().cpu() - ref).abs().max().item() < 0.03
+
+    qkv = torch.randn(P, 3 * cfg.hidden).to(torch.bfloat16)
+    v4 = qkv.view(P, 3, cfg.heads, cfg.head_dim)
+    pos_t = torch.from_numpy(ctl.pos_yx)
+    rq = V.rope_2d_reference(v4[:, 0], pos_t, cfg.rope_theta)
+    rk = V.rope_2d_reference(v4[:, 1], pos_t, cfg.rope_theta)
+    qd = qkv.cuda()
+    ops.vision_rope(qd, pos, cfg.heads, cfg.head_dim, cfg.rope_theta)
+    got = qd.float().cpu().view(P, 3, cfg.heads, cfg.head_dim)
+    assert (got[:, 0] - rq).abs().max().item() < 0.04
+    assert (got[:, 1] - rk).abs().max().item() < 0.04
+    assert torch.equal(got[:, 2], v4[:, 2].float())   # v untouched
+
+
+@pytest.mark.parametrize("grids", [[(1, 2, 2)], [(1, 6, 10), (2, 4, 4)], [(1, 16, 18)], [(1, 34, 30)]])
+def test_packed_attention(ops, grids):
+    torch.manual_seed(3)
+    cfg = V.VisionConfig()
+    ctl = V.build_control(grids)
+    P, H, D = ctl.n_patches, cfg.heads, cfg.head_dim
+    qkv = torch.randn(P, 3 * cfg.hidden).to(torch.bfloat16)
+    v4 = qkv.float().view(P, 3, H, D)
+    scale = 1 / math.sqrt(D)
+    ref = V.packed_attention_reference(v4[:, 0], v4[:, 1], v4[:, 2], ctl.segments, scale).reshape(P, H * D)
+    tiles = torch.from_numpy(V.attention_tiles(ctl.segments, int(ops.packed_attention_tile()))).cuda()
+    out = torch.full((P, H * D), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.packed_attention(qkv.cuda(), out, tiles, H, scale)
+    torch.cuda.synchronize()
+    assert not torch.isnan(out).any()
+    assert (out.float().cpu() - ref).abs().max().item() < 0.03
+    assert _rel(out.cpu(), ref) < 1e-2
+
+
+def test_tower_matches_reference():
+    cfg = V.VisionConfig().scaled(layers=3, out_hidden=256)
+    w = V.random_vision_weights(cfg, seed=5)
+    torch.manual_seed(4)
+    ctl = V.build_control([(1, 6, 10), (2, 4, 4)])
+    patches = (0.5 * torch.randn(ctl.n_patches, cfg.patch_dim)).to(torch.bfloat16)
+    ref = V.vision_reference(cfg, w, patches, ctl)
+    tower = V.VisionTower(cfg, w, "cuda")
+    out = tower.encode(patches, ctl)
+    torch.cuda.synchronize()
+    assert out.shape == (ctl.n_tokens, 256)
+    assert int(tower.status[0]) == 0
+    assert tower.launches == 2 + 8 * cfg.layers + 3
+    cos = torch.nn.functional.cosine_similarity(out.float().cpu().flatten(), ref.flatten(), dim=0).item()
+    assert cos > 0.995
+    assert _rel(out.cpu(), ref) < 0.06
+
+
+def test_multimodal_prefill_matches_reference():
+    from ninfer_fusion_b200.frontend import media as M
+    from ninfer_fusion_b200.models.config import TINY_DENSE
+    from ninfer_fusion_b200.models.reference_model import ReferenceModel, ReferenceSequence
+    from ninfer_fusion_b200.models.weights import random_weights
+    from ninfer_fusion_b200.ops import reference as R
+    from ninfer_fusion_b200.runtime.generator import Generator
+
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cuda", seed=7, std=0.05)
+    vcfg = V.VisionConfig().scaled(layers=2, out_hidden=cfg.hidden)
+    vw = V.random_vision_weights(vcfg, seed=6)
+    gen = Generator(cfg, w, "cuda", max_batch=2, max_context=512, kv_format="bf16", page_size=16, prefill_chunk=32,
+                    use_graph=False)
+    gen.vision = V.VisionTower(vcfg, vw, "cuda")
+    rng = np.random.default_rng(0)
+    proc = M.MediaProcessor(M.MediaOptions(image_min_pixels=32 * 32, image_max_pixels=128 * 128))
+    item = proc.image(rng.integers(0, 256, (96, 128, 3), dtype=np.uint8))   # 6 x 8 patches -> 12 visual tokens
+    IMG = cfg.vocab - 1
+    torch.manual_seed(5)
+    head = torch.randint(0, cfg.vocab - 2, (27,)).tolist()    # the run of pad tokens straddles the 32-token chunk edge
+    tail = torch.randint(0, cfg.vocab - 2, (9,)).tolist()
+    ids = head + [IMG] * item.n_tokens + tail
+    pos, delta, rows = M.build_positions(ids, [item], IMG, IMG - 1)
+    pm = M.PreparedPrompt(ids, pos, delta, [item], rows)
+    text_only = torch.randint(0, cfg.vocab - 2, (40,)).tolist()
+    first = gen.prefill([ids, text_only], media=[pm, None])
+    nxt = gen.decode_step()
+
+    ref = ReferenceModel(cfg, w)
+    vis = V.vision_reference(vcfg, vw, pm.patches(), V.build_control(pm.grids))
+    seq = ReferenceSequence(cfg, R.KV_BF16)
+    h = ref.forward(seq, torch.tensor(ids), positions=torch.from_numpy(pos), embed_rows=torch.from_numpy(rows), embed_vals=vis)
+    lg = ref.logits(h[-1:])[0]
+    top2 = lg.topk(2).values
+    if (top2[0] - top2[1]).item() > 0.05:
+        assert first[0] == int(R.argmax_lowest(lg[None])[0])
+    # decode position of the multimodal sequence is shifted by rope_delta
+    h2 = ref.forward(seq, torch.tensor([first[0]]), positions=torch.tensor([len(ids) + delta]))
+    lg2 = ref.logits(h2)[0]
+    top2 = lg2.topk(2).values
+    if (top2[0] - top2[1]).item() > 0.05:
+        assert nxt[0] == int(R.argmax_lowest(lg2[None])[0])
+    # the text-only neighbour is unaffected by the three-axis buffers
+    seq_t = ReferenceSequence(cfg, R.KV_BF16)
+    ht = ref.forward(seq_t, torch.tensor(text_only))
+    lgt = ref.logits(ht[-1:])[0]
+    top2 = lgt.topk(2).values
+    if (top2[0] - top2[1]).item() > 0.05:
+        assert first[1] == int(R.argmax_lowest(lgt[None])[0])
+    assert delta < 0
