@@ -52,6 +52,9 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--spec", default="none", choices=["none", "mtp"], help="speculative decoding with the MTP draft module")
     ap.add_argument("--draft-tokens", type=int, default=3)
     ap.add_argument("--allow-unknown-template", action="store_true")
+    ap.add_argument("--vision", action="store_true",
+                    help="attach the vision tower (the artifact's vision/ tensors, or random ones with --random-init)")
+    ap.add_argument("--vision-layers", type=int, default=0, help="shrink the vision tower to this many blocks (debug)")
     ap.add_argument("--seed", type=int, default=0)
 
 
@@ -90,7 +93,34 @@ def load_model(args) -> Tuple[ModelConfig, Dict[str, object], Tokenizer, str]:
                                   added_tokens=SPECIAL_TOKENS)
     if tok.vocab_size > cfg.vocab:
         raise SystemExit(f"tokenizer has {tok.vocab_size} ids but the model's vocabulary is {cfg.vocab}")
+    if getattr(args, "vision", False) and not any(k.startswith("vision/") for k in weights):
+        if not args.random_init:
+            raise SystemExit("--vision: the artifact has no vision/ tensors")
+        from .models.vision import random_vision_weights
+        weights.update(random_vision_weights(vision_config(args, cfg), args.device, seed=args.seed + 1))
     return cfg, weights, tok, name
+
+
+def vision_config(args, cfg: ModelConfig):
+    from .models.vision import VisionConfig
+    base = VisionConfig()
+    return base.scaled(args.vision_layers or base.layers, cfg.hidden)
+
+
+def attach_vision(args, cfg: ModelConfig, weights, program):
+    """Gives `program` the vision tower when --vision is set (device tower on a GPU program, fp32 oracle on the CPU)."""
+    if not getattr(args, "vision", False):
+        return program
+    vcfg = vision_config(args, cfg)
+    vw = {k: v for k, v in weights.items() if k.startswith("vision/")}
+    if isinstance(program, ReferenceProgram):
+        program.attach_vision(vcfg, vw)
+    elif hasattr(program, "attach_vision"):
+        from .models.vision import VisionTower
+        program.attach_vision(VisionTower(vcfg, vw, args.device))
+    else:
+        raise SystemExit("--vision is not available with this program (speculative decoding)")
+    return program
 
 
 def build_engine(args, cfg: ModelConfig, weights) -> Engine:
@@ -114,13 +144,16 @@ def build_engine(args, cfg: ModelConfig, weights) -> Engine:
         from .runtime.gpu_program import GpuProgram
 
         def factory():
-            return GpuProgram(cfg, weights, args.device, max_lanes=args.max_lanes, max_context=args.max_context,
+            text = {k: v for k, v in weights.items() if not k.startswith("vision/")}
+            prog = GpuProgram(cfg, text, args.device, max_lanes=args.max_lanes, max_context=args.max_context,
                               kv_format=kv, page_size=args.page_size, prefill_chunk=args.prefill_chunk,
                               use_graph=not args.no_graphs)
+            return attach_vision(args, cfg, weights, prog)
     else:
         def factory():
-            return ReferenceProgram(cfg, weights, max_lanes=args.max_lanes, max_context=args.max_context,
+            prog = ReferenceProgram(cfg, weights, max_lanes=args.max_lanes, max_context=args.max_context,
                                     kv_format=kv if isinstance(kv, str) else "bf16")
+            return attach_vision(args, cfg, weights, prog)
     return Engine(factory, prefill_chunk=args.prefill_chunk)
 
 
@@ -140,8 +173,16 @@ def cmd_generate(args) -> int:
     elif args.raw:
         req.prompt = args.prompt
     else:
+        content = args.prompt
+        if args.image or args.video:
+            if not args.vision:
+                raise SystemExit("--image / --video need --vision")
+            svc.allow_media_files = True
+            content = ([{"type": "image_url", "image_url": {"url": p}} for p in args.image] +
+                       [{"type": "video_url", "video_url": {"url": p}} for p in args.video] +
+                       [{"type": "text", "text": args.prompt}])
         req.messages = ([{"role": "system", "content": args.system}] if args.system else []) + \
-                       [{"role": "user", "content": args.prompt}]
+                       [{"role": "user", "content": content}]
     t0 = time.perf_counter()
     result = None
     for kind, item in svc.stream(req):
@@ -241,6 +282,8 @@ def main(argv=None) -> int:
     add_model_args(g)
     g.add_argument("--prompt", default="Hello")
     g.add_argument("--system", default="")
+    g.add_argument("--image", action="append", default=[], help="image file for the user turn (repeatable; needs --vision)")
+    g.add_argument("--video", action="append", default=[], help="multi-frame image file as a video (repeatable; needs --vision)")
     g.add_argument("--raw", action="store_true", help="feed --prompt as is, without the chat template")
     g.add_argument("--prompt-ids", help="comma separated token ids")
     g.add_argument("--messages-json", help="file with an OpenAI-style messages array")

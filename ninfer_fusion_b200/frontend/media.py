@@ -286,3 +286,61 @@ def prepare_prompt(tokenizer, rendered_text: str, items: Sequence[MediaItem]) ->
     vid = VIDEO_TOKEN_ID if vid is None else vid
     pos, delta, rows = build_positions(ids, items, img, vid)
     return PreparedPrompt(ids, pos, delta, list(items), rows)
+
+
+# ---------------------------------------------------------------------------------------- chat messages
+def collect_media(messages: Sequence[dict]) -> List[Tuple[str, object]]:
+    """(modality, source) of every image / video part of OpenAI-style messages, in rendering order (the system
+    message first when it leads, as the chat template renders it)."""
+    out: List[Tuple[str, object]] = []
+    for m in messages:
+        content = m.get("content")
+        if not isinstance(content, (list, tuple)):
+            continue
+        for part in content:
+            if not isinstance(part, dict):
+                continue
+            kind = part.get("type")
+            if kind in ("image_url", "image", "input_image"):
+                src = part.get("image_url", part.get("image"))
+                out.append(("image", src.get("url") if isinstance(src, dict) else src))
+            elif kind in ("video_url", "video"):
+                src = part.get("video_url", part.get("video"))
+                out.append(("video", src.get("url") if isinstance(src, dict) else src))
+    return out
+
+
+def acquire_source(source, allow_files: bool = False, max_bytes: int = 256 * 1024 * 1024):
+    """Turns a message's media reference into something `decode_media` accepts.  `data:` URIs and in-memory
+    objects always pass; `file://` / plain paths only when the gateway allows local files; remote URLs are refused
+    (this build has no network fetcher)."""
+    if source is None:
+        raise ValueError("media part has no source")
+    if not isinstance(source, str):
+        return source
+    if source.startswith("data:"):
+        if len(source) > max_bytes * 4 // 3 + 64:
+            raise ValueError("media source exceeds the byte limit")
+        return source
+    if source.startswith(("http://", "https://")):
+        raise ValueError("remote media URLs are not fetched by this server; send a data: URI")
+    path = source[len("file://"):] if source.startswith("file://") else source
+    if not allow_files:
+        raise ValueError("local media files are disabled on this gateway")
+    import os
+    if os.path.getsize(path) > max_bytes:
+        raise ValueError("media source exceeds the byte limit")
+    return path
+
+
+def prepare_messages(tokenizer, rendered_text: str, messages: Sequence[dict], processor: "MediaProcessor",
+                     allow_files: bool = False, video_fps: float = 24.0) -> Optional[PreparedPrompt]:
+    """PreparedPrompt for chat messages with media parts, or None when there are none."""
+    refs = collect_media(messages)
+    if not refs:
+        return None
+    items = []
+    for modality, src in refs:
+        src = acquire_source(src, allow_files, processor.opt.max_source_bytes)
+        items.append(processor.image(src) if modality == "image" else processor.video(src, fps=video_fps))
+    return prepare_prompt(tokenizer, rendered_text, items)

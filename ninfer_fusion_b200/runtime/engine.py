@@ -44,6 +44,7 @@ class RequestOptions:
     deadline_s: Optional[float] = None       # wall-clock budget for the whole request
     pending_timeout_s: Optional[float] = None  # how long it may wait for admission
     session: Optional[str] = None            # continuation key for prefix reuse
+    media: object = None                     # frontend.media.PreparedPrompt for a request with images / videos
 
 
 @dataclass
@@ -191,6 +192,11 @@ class Engine:
                 raise ResourceError("server_overloaded: pending queue is full")
             if len(prompt) == 0:
                 raise RequestError("empty prompt")
+            if opts.media is not None and getattr(opts.media, "items", None):
+                if not getattr(self.program, "supports_media", False):
+                    raise RequestError("this engine has no vision tower: media prompts are not supported")
+                if list(opts.media.ids) != list(prompt):
+                    raise RequestError("the prepared media prompt does not match the request's token ids")
             if len(prompt) + opts.max_tokens > self.program.max_context:
                 self.stats.requests_rejected += 1
                 raise RequestError(f"prompt ({len(prompt)}) + max_tokens ({opts.max_tokens}) exceeds the "
@@ -324,7 +330,9 @@ class Engine:
                 self._pending.remove(req)
             try:
                 self._maybe_inject(req)
-                req.lane = self.program.open(req.prompt, req.opts.sampling, session=req.opts.session)
+                req.lane = (self.program.open(req.prompt, req.opts.sampling, session=req.opts.session)
+                            if req.opts.media is None else
+                            self.program.open(req.prompt, req.opts.sampling, session=req.opts.session, media=req.opts.media))
                 if req.lane.reused:
                     self.stats.prefix_hits += 1
                     self.stats.prefix_tokens_reused += req.lane.reused

@@ -8,6 +8,7 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..models.config import ModelConfig
@@ -60,6 +61,8 @@ class GpuProgram(ProgramBase):
         self.token_counts = (torch.zeros((B, g.vocab_rows), dtype=torch.int32, device=self.device)
                              if penalties and comm is None else None)
         self._graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
+        self.vision = None
+        self._bufs_prefill_mm = None
 
     # ------------------------------------------------------------------ lanes
     def _alloc_slot(self) -> int:
@@ -169,7 +172,10 @@ class GpuProgram(ProgramBase):
         self.kv.ensure(lane.row, lane.n_cached + n + 1)
         self.kv.publish()
         chunk = SeqChunk(lane.row, lane.slot, lane.n_cached, lane.tokens[lane.n_cached:lane.n_cached + n], done)
-        batch = self.bufs_prefill.build([chunk])
+        if lane.media is not None:
+            batch = self._build_media_chunk(lane, chunk, n)
+        else:
+            batch = self.bufs_prefill.build([chunk])
         greedy = self._fill_sampling([lane]) if done else True
         rows = torch.tensor([lane.row], device=self.device)
         ids = self._forward_select(batch, greedy, rows)
@@ -182,6 +188,37 @@ class GpuProgram(ProgramBase):
         lane.last_token = int(self.out_host[0])
         return lane.last_token
 
+    def attach_vision(self, tower) -> None:
+        """Enables multimodal requests: `tower` is a models.vision.VisionTower whose output width is the text hidden."""
+        if tower.cfg.out_hidden != self.cfg.hidden:
+            raise ValueError("vision tower output width differs from the text hidden size")
+        self.vision = tower
+        self.supports_media = True
+
+    def _build_media_chunk(self, lane: Lane, chunk: SeqChunk, n: int) -> StepBatch:
+        """Step descriptor of a multimodal prompt chunk: three-axis positions, visual rows over the pad embeddings."""
+        from ..models.vision import build_control
+        pm = lane.media
+        if lane.visual is None:
+            control = build_control(pm.grids, self.vision.cfg.merge)
+            if control.n_tokens != len(pm.embed_rows):
+                raise ValueError("pad-token count does not match the media grids")
+            lane.visual = self.vision.encode(pm.patches(), control)
+        if self._bufs_prefill_mm is None:
+            b = self.bufs_prefill
+            self._bufs_prefill_mm = StepBuffers(b.max_tokens, b.max_seqs, self.device, mrope=True,
+                                                attn_block_tokens=b.attn_block_tokens)
+        c0 = lane.n_cached
+        chunk.positions = pm.positions[c0:c0 + n]
+        batch = self._bufs_prefill_mm.build([chunk])
+        lo, hi = np.searchsorted(pm.embed_rows, [c0, c0 + n])
+        if hi > lo:
+            batch.embed_rows = torch.from_numpy(pm.embed_rows[lo:hi].astype(np.int64) - c0).to(self.device, non_blocking=True)
+            batch.embed_vals = lane.visual[lo:hi]
+        if c0 + n == len(lane.tokens):
+            lane.visual = None   # the tower's output is not needed after the prompt
+        return batch
+
     # ------------------------------------------------------------------ decode
     def _chunks(self, lanes: Sequence[Lane]) -> List[SeqChunk]:
         return [SeqChunk(l.row, l.slot, l.n_cached, [l.last_token], True) for l in lanes]
@@ -191,7 +228,7 @@ class GpuProgram(ProgramBase):
         g = self._graphs.get(key)
         if g is not None:
             return g
-        batch = self.bufs_decode.build(self._chunks(lanes), upload=True)
+        batch = self.bufs_decode.build(self._chunks(lanes), upload=True, rope_delta=[l.rope_delta for l in lanes])
         batch.max_kv_len = bucket
         rows = batch.table_row
         saved = [(c.clone(), s.clone()) for c, s in zip(self.states.conv, self.states.ssm)]
@@ -224,11 +261,11 @@ class GpuProgram(ProgramBase):
         if self.use_graph:
             bucket = context_bucket(max(l.n_cached for l in lanes) + 1)
             graph = self._graph_for(lanes, bucket, greedy)
-            self.bufs_decode.build(self._chunks(lanes), upload=True)
+            self.bufs_decode.build(self._chunks(lanes), upload=True, rope_delta=[l.rope_delta for l in lanes])
             graph.replay()
             ids = self.ws.next_ids[:B]
         else:
-            batch = self.bufs_decode.build(self._chunks(lanes), upload=True)
+            batch = self.bufs_decode.build(self._chunks(lanes), upload=True, rope_delta=[l.rope_delta for l in lanes])
             ids = self._forward_select(batch, greedy, batch.table_row)
         self.out_host[:B].copy_(ids, non_blocking=True)
         torch.cuda.current_stream().synchronize()

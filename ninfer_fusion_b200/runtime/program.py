@@ -47,6 +47,9 @@ class Lane:
     sampling: SamplingParams = field(default_factory=SamplingParams)
     last_token: int = -1     # sampled but not yet fed
     reused: int = 0          # prompt tokens restored from a session checkpoint instead of being prefilled
+    media: object = None     # frontend.media.PreparedPrompt of a multimodal request
+    visual: object = None    # [V, hidden] vision-tower output of `media` (filled at the first prefill step)
+    rope_delta: int = 0      # rope position - cache position once the prompt is in (multimodal prompts)
 
 
 @dataclass
@@ -175,6 +178,8 @@ class ProgramBase:
         return None
 
     def checkpoint(self, lane: Lane, session: str, kind: str) -> bool:
+        if lane.media is not None:
+            return False   # see open(): multimodal histories are not reusable by token ids alone
         """Remember the lane's materialised frontier (lane.tokens[:n_cached]) for `session`."""
         n = lane.n_cached
         if not session or n <= 0:
@@ -219,14 +224,26 @@ class ProgramBase:
     def _kv_room(self, n_tokens: int) -> bool:
         return True
 
+    supports_media = False
+
     def open(self, prompt: Sequence[int], sampling: Optional[SamplingParams] = None,
-             session: Optional[str] = None) -> Lane:
+             session: Optional[str] = None, media=None) -> Lane:
         if not self._free_rows:
             raise MemoryError("no free lane")
         if len(prompt) == 0:
             raise ValueError("empty prompt")
+        if media is not None and getattr(media, "items", None):
+            if not self.supports_media:
+                raise ValueError("this program has no vision tower: media prompts are not supported")
+            if list(media.ids) != list(prompt):
+                raise ValueError("the prepared media prompt does not match the request's token ids")
+            session = None   # frontiers are keyed by token ids only; visual content is not part of that identity
+        else:
+            media = None
         row = self._free_rows.pop()
         lane = Lane(self._next_id, row, self._alloc_slot(), list(prompt), 0, sampling or SamplingParams())
+        if media is not None:
+            lane.media, lane.rope_delta = media, int(media.rope_delta)
         self._next_id += 1
         self.lanes[lane.lane_id] = lane
         ck = self._match(session, prompt)
@@ -318,10 +335,30 @@ class ReferenceProgram(ProgramBase):
         g = torch.Generator().manual_seed((sp.seed * 1000003 + len(lane.tokens)) & 0x7FFFFFFF)
         return int(idx[int(torch.multinomial(p, 1, generator=g))])
 
+    def attach_vision(self, vision_cfg, vision_weights) -> None:
+        """Enables multimodal requests on the oracle program (fp32 vision tower on the CPU)."""
+        if vision_cfg.out_hidden != self.cfg.hidden:
+            raise ValueError("vision tower output width differs from the text hidden size")
+        self._vision = (vision_cfg, vision_weights)
+        self.supports_media = True
+
     def prefill_step(self, lane: Lane, budget: int) -> Optional[int]:
         seq = self._seqs.setdefault(lane.lane_id, self._Seq(self.cfg, self.kv_fmt))
         n = min(budget, len(lane.tokens) - lane.n_cached)
-        h = self.model.forward(seq, torch.tensor(lane.tokens[lane.n_cached:lane.n_cached + n]))
+        ids = torch.tensor(lane.tokens[lane.n_cached:lane.n_cached + n])
+        if lane.media is not None:
+            import numpy as np
+            from ..models.vision import build_control, vision_reference
+            pm, c0 = lane.media, lane.n_cached
+            if lane.visual is None:
+                vcfg, vw = self._vision
+                lane.visual = vision_reference(vcfg, vw, pm.patches(), build_control(pm.grids, vcfg.merge))
+            lo, hi = np.searchsorted(pm.embed_rows, [c0, c0 + n])
+            h = self.model.forward(seq, ids, positions=torch.from_numpy(pm.positions[c0:c0 + n]),
+                                   embed_rows=torch.from_numpy(pm.embed_rows[lo:hi].astype(np.int64) - c0),
+                                   embed_vals=lane.visual[lo:hi])
+        else:
+            h = self.model.forward(seq, ids)
         lane.n_cached += n
         if lane.n_cached < len(lane.tokens):
             return None
@@ -333,7 +370,8 @@ class ReferenceProgram(ProgramBase):
         for lane in lanes:
             seq = self._seqs[lane.lane_id]
             lane.tokens.append(lane.last_token)
-            h = self.model.forward(seq, torch.tensor([lane.last_token]))
+            pos = torch.tensor([lane.n_cached + lane.rope_delta]) if lane.rope_delta else None
+            h = self.model.forward(seq, torch.tensor([lane.last_token]), positions=pos)
             lane.n_cached += 1
             lane.last_token = self._sample(lane, self.model.logits(h)[0])
             out.append(lane.last_token)

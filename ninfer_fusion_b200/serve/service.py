@@ -67,18 +67,36 @@ class GenerationService:
         self._permits = threading.Semaphore(max_concurrent)
         self.max_concurrent = max_concurrent
         self.started = time.time()
+        self.media = None                 # frontend.media.MediaProcessor, created on the first media request
+        self.allow_media_files = False    # local paths in media parts (CLI use); gateways leave this off
 
     # ------------------------------------------------------------------ prompt side
     def prepare(self, req: GenRequest) -> List[int]:
+        return self.prepare_full(req)[0]
+
+    def prepare_full(self, req: GenRequest):
+        """(token ids, prepared media prompt or None).  Image / video parts of chat messages go through the media
+        processor: placeholders expand to one pad token per visual token and positions become three-axis."""
         if req.prompt_ids is not None:
-            return list(req.prompt_ids)
+            return list(req.prompt_ids), None
         if req.messages is not None:
             text = render_chat(req.messages, req.tools, add_generation_prompt=True, enable_thinking=req.enable_thinking)
+            from ..frontend import media as M
+            if M.collect_media(req.messages):
+                if not getattr(self.engine.program, "supports_media", False):
+                    raise RequestError("this deployment has no vision tower: image and video parts are not supported")
+                if self.media is None:
+                    self.media = M.MediaProcessor()
+                try:
+                    pm = M.prepare_messages(self.tok, text, req.messages, self.media, allow_files=self.allow_media_files)
+                except (ValueError, OSError) as e:
+                    raise RequestError(f"invalid media: {e}")
+                return list(pm.ids), pm
         elif req.prompt is not None:
             text = req.prompt
         else:
             raise RequestError("request has neither messages nor prompt")
-        return self.tok.encode(text)
+        return self.tok.encode(text), None
 
     def count_tokens(self, req: GenRequest) -> int:
         return len(self.prepare(req))
@@ -108,11 +126,13 @@ class GenerationService:
         t0 = time.perf_counter()
         res = GenResult(rid)
         try:
-            ids = self.prepare(req)
+            ids, media = self.prepare_full(req)
             res.prompt_tokens = len(ids)
             if on_start is not None:
                 on_start(rid, len(ids))
-            handle = self.engine.submit(ids, self._options(req))
+            opts = self._options(req)
+            opts.media = media
+            handle = self.engine.submit(ids, opts)
             dec = StreamDecoder(self.tok, skip_special=True)
             # a chat prompt with thinking enabled continues inside an open reasoning frame only if the template
             # opened one; this template leaves the frame to the model, so parsing starts in content mode

@@ -193,9 +193,36 @@ def bench_gdn(ops, batch, hk=16, hv=48, iters=20):
             "GBps": round(byts / med / 1e9, 1), "frac_hbm": round(byts / med / bw, 3), "peaks": how}
 
 
+def bench_vision(side_patches: int, layers: int, iters=5):
+    """Full-geometry vision tower on one square image of side_patches x side_patches patches; also times the
+    packed attention kernel alone and reports its FLOP rate."""
+    import math
+    from ..models import vision as V
+    cfg = V.VisionConfig().scaled(layers, 5120)
+    w = V.random_vision_weights(cfg, "cuda", seed=0)
+    tower = V.VisionTower(cfg, w, "cuda")
+    ctl = V.build_control([(1, side_patches, side_patches)])
+    P = ctl.n_patches
+    patches = (0.5 * torch.randn(P, cfg.patch_dim, device="cuda")).to(torch.bfloat16)
+    med, best = time_op(lambda: tower.encode(patches, ctl), iters=iters, warmup=2)
+    H = cfg.hidden
+    gemm_flops = 2.0 * P * (cfg.patch_dim * H + layers * (3 * H * H + H * H + 2 * H * cfg.intermediate)) + \
+        2.0 * (P / 4) * (cfg.merger_hidden ** 2 + cfg.merger_hidden * cfg.out_hidden)
+    attn_flops = layers * 4.0 * P * P * H
+    tiles = torch.from_numpy(V.attention_tiles(ctl.segments, tower.tile)).cuda()
+    qkv = torch.randn(P, 3 * H, device="cuda").to(torch.bfloat16)
+    out = torch.empty(P, H, device="cuda", dtype=torch.bfloat16)
+    a_med, _ = time_op(lambda: tower.ops.packed_attention(qkv, out, tiles, cfg.heads, 1 / math.sqrt(cfg.head_dim)), iters=10)
+    return {"op": "vision_tower", "patches": P, "layers": layers, "launches": tower.launches, "ms": round(med * 1e3, 3),
+            "ms_best": round(best * 1e3, 3), "tflops": round((gemm_flops + attn_flops) / med / 1e12, 1),
+            "attn_us": round(a_med * 1e6, 1), "attn_tflops": round(4.0 * P * P * H / a_med / 1e12, 1)}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "decode27b", "prefill27b", "attn", "gdn", "gdn_prefill", "all"])
+    ap.add_argument("what", choices=["gemm", "decode27b", "prefill27b", "attn", "gdn", "gdn_prefill", "vision", "all"])
+    ap.add_argument("--side", type=int, default=64, help="vision: patches per image side (64 = a 1024 x 1024 image)")
+    ap.add_argument("--layers", type=int, default=27, help="vision: transformer blocks")
     ap.add_argument("--T", type=int, default=32)
     ap.add_argument("--N", type=int, default=34816)
     ap.add_argument("--K", type=int, default=5120)
@@ -231,6 +258,8 @@ def main(argv=None):
     if a.what == "gdn_prefill":
         rows.append(bench_gdn_prefill(ops, a.batch, a.T, iters=a.iters))
         rows.append(bench_gdn_prefill(ops, a.batch, a.T, hk=2, hv=6, iters=a.iters))
+    if a.what == "vision":
+        rows.append(bench_vision(a.side, a.layers, max(3, a.iters // 4)))
     for r in rows:
         print(json.dumps(r), flush=True)
 

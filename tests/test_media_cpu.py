@@ -115,3 +115,75 @@ def test_vision_reference_runs_and_segments_are_independent():
     out_ab = V.vision_reference(cfg, w, torch.cat([pa, pb]), ctl_ab)
     assert out_a.shape == (1, 64) and out_ab.shape == (3, 64)
     assert torch.allclose(out_a, out_ab[:1], atol=1e-5)   # a second item does not change the first
+
+
+def test_engine_multimodal_request_on_oracle_program():
+    """A chat request with an image part runs through the service, the engine and the oracle program; the image
+    changes the output, a text-only engine refuses it, and a wrong prepared prompt is rejected."""
+    import base64
+    from PIL import Image
+    from ninfer_fusion_b200 import cli
+    from ninfer_fusion_b200.frontend.tokenizer import Tokenizer
+    from ninfer_fusion_b200.models.config import TINY_DENSE
+    from ninfer_fusion_b200.models.weights import random_weights
+    from ninfer_fusion_b200.runtime.engine import Engine, RequestError, RequestOptions
+    from ninfer_fusion_b200.runtime.program import ReferenceProgram
+    from ninfer_fusion_b200.serve.service import GenerationService, GenRequest
+
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cpu", seed=3, std=0.05)
+    vcfg = V.VisionConfig().scaled(layers=1, out_hidden=cfg.hidden)
+    vw = V.random_vision_weights(vcfg, seed=2)
+    tok = Tokenizer.train_toy(cli.DEFAULT_CORPUS, 200, cli.SPECIAL_TOKENS)
+    assert tok.token_id(M.IMAGE_PAD) is not None
+
+    def factory():
+        prog = ReferenceProgram(cfg, w, max_lanes=2, max_context=512)
+        prog.attach_vision(vcfg, vw)
+        return prog
+
+    engine = Engine(factory, prefill_chunk=16)
+    try:
+        svc = GenerationService(engine, tok, "tiny-dense:test", max_concurrent=2)
+        svc.media = M.MediaProcessor(M.MediaOptions(image_min_pixels=32 * 32, image_max_pixels=64 * 64))
+
+        def uri(seed):
+            arr = np.random.default_rng(seed).integers(0, 256, (64, 64, 3), dtype=np.uint8)
+            buf = io.BytesIO()
+            Image.fromarray(arr).save(buf, format="PNG")
+            return "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+
+        def ask(seed):
+            msgs = [{"role": "user", "content": [{"type": "text", "text": "what is this"},
+                                                 {"type": "image_url", "image_url": {"url": uri(seed)}}]}]
+            req = GenRequest(messages=msgs, max_tokens=6, temperature=0.0)
+            ids, pm = svc.prepare_full(req)
+            assert pm is not None and ids.count(tok.token_id(M.IMAGE_PAD)) == 4 and pm.rope_delta == 2 - 4
+            return svc.generate(req)
+
+        a, b, a2 = ask(1), ask(2), ask(1)
+        assert a.completion_tokens == 6 and a.error == ""
+        assert a.content == a2.content                 # deterministic
+        # text-only request still works next to it
+        plain = svc.generate(GenRequest(messages=[{"role": "user", "content": "hello"}], max_tokens=4, temperature=0.0))
+        assert plain.error == "" and plain.completion_tokens == 4
+        # a prepared prompt that does not match the ids is refused at submit
+        ids, pm = svc.prepare_full(GenRequest(messages=[{"role": "user", "content": [
+            {"type": "image_url", "image_url": {"url": uri(3)}}]}], max_tokens=2))
+        with pytest.raises(RequestError):
+            engine.submit(ids[:-1], RequestOptions(max_tokens=2, media=pm))
+        # remote URLs are refused with a request error
+        bad = GenRequest(messages=[{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "http://x/y.png"}}]}])
+        with pytest.raises(RequestError):
+            svc.prepare_full(bad)
+    finally:
+        engine.shutdown()
+
+    text_engine = Engine(lambda: ReferenceProgram(cfg, w, max_lanes=2, max_context=512), prefill_chunk=16)
+    try:
+        svc2 = GenerationService(text_engine, tok, "tiny-dense:test")
+        with pytest.raises(RequestError):
+            svc2.prepare_full(GenRequest(messages=[{"role": "user", "content": [
+                {"type": "image_url", "image_url": {"url": "data:image/png;base64,AAAA"}}]}]))
+    finally:
+        text_engine.shutdown()
