@@ -2,6 +2,7 @@
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <stddef.h>
 #include <stdint.h>
 
 namespace nfb {
@@ -62,6 +63,12 @@ struct GdnParams {
 const char* gdn_recurrent(const GdnParams& p, cudaStream_t stream, bool pdl);
 // Multi-token variant (token groups staged in shared memory); gdn_recurrent dispatches to it when T > n_seq.
 const char* gdn_prefill(const GdnParams& p, cudaStream_t stream, bool pdl);
+// Chunked (WY) tensor-core formulation for long prefill chunks: 64-token chunks, all chunks prepared in parallel,
+// then one pass per (sequence, head) over the chunks.  Needs a workspace of gdn_chunked_workspace_bytes(
+// gdn_chunked_max_chunks(T, n_seq), n_v_heads) bytes; seq_end / commit passes are not supported (they are short).
+size_t gdn_chunked_workspace_bytes(int max_chunks, int n_v_heads);
+int gdn_chunked_max_chunks(int T, int n_seq);
+const char* gdn_chunked(const GdnParams& p, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 // Performance debugging of the row-split variant: switches the phase profile on/off and reads the last profile
 // (cycles of CTA (0,0): operand wait, prologue, serial steps, partial sums + cluster barrier, epilogue).
 void gdn_prefill_trace(bool enable, long long* host5);

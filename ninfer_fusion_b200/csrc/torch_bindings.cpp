@@ -358,7 +358,7 @@ void gdn_recurrent(const Tensor& qkv, int64_t q_off, int64_t k_off, int64_t v_of
                    int64_t a_off, int64_t b_off, int64_t n_qk_heads, int64_t n_v_heads, const Tensor& A_log,
                    const Tensor& dt_bias, const Tensor& norm_w, double eps, const Tensor& cu_seqlens,
                    const Tensor& state_slot, const Tensor& state, bool write_state, const Tensor& out, bool pdl,
-                   OptT seq_end, OptT commit) {
+                   OptT seq_end, OptT commit, OptT chunk_ws) {
   need(qkv, at::kBFloat16, "qkv"); need_rows(qkv, "qkv"); need(proj, at::kBFloat16, "proj"); need_rows(proj, "proj");
   need(A_log, at::kFloat, "A_log"); need(dt_bias, at::kFloat, "dt_bias"); need(norm_w, at::kBFloat16, "norm_w");
   need(cu_seqlens, at::kInt, "cu_seqlens"); need(state_slot, at::kInt, "state_slot");
@@ -393,7 +393,19 @@ void gdn_recurrent(const Tensor& qkv, int64_t q_off, int64_t k_off, int64_t v_of
     TORCH_CHECK(commit->numel() == p.T, "commit [T]");
     p.commit = static_cast<const unsigned char*>(commit->data_ptr());
   }
+  if (chunk_ws.has_value() && chunk_ws->defined()) {
+    // chunked tensor-core formulation (long prefill chunks)
+    need(*chunk_ws, at::kByte, "chunk_ws");
+    TORCH_CHECK(chunk_ws->is_contiguous(), "chunk_ws must be contiguous");
+    chk(nfb::gdn_chunked(p, chunk_ws->data_ptr(), static_cast<size_t>(chunk_ws->numel()), cur_stream()));
+    return;
+  }
   chk(nfb::gdn_recurrent(p, cur_stream(), pdl));
+}
+
+int64_t gdn_chunked_workspace_bytes(int64_t T, int64_t n_seq, int64_t n_v_heads) {
+  return static_cast<int64_t>(nfb::gdn_chunked_workspace_bytes(
+      nfb::gdn_chunked_max_chunks(static_cast<int>(T), static_cast<int>(n_seq)), static_cast<int>(n_v_heads)));
 }
 
 void argmax_rows(const Tensor& logits, const Tensor& out, bool pdl) {
@@ -640,7 +652,8 @@ TORCH_LIBRARY(nfb200, m) {
   m.def("paged_attention_prefill(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor blk_start, Tensor blk_count, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, Tensor? gate, Tensor out, bool pdl) -> ()", &paged_attention_prefill);
   m.def("prefill_attn_block_tokens(int n_q_heads, int n_kv_heads) -> int", &prefill_attn_block_tokens);
   m.def("causal_conv1d_silu(Tensor x, int c_off, int C, Tensor w, Tensor cu_seqlens, Tensor token_seq, Tensor state_slot, Tensor conv_state, Tensor out, bool update_state, bool one_token_per_seq, bool pdl, Tensor? seq_end=None, bool state_only=False, Tensor? parent=None, Tensor? last_token=None) -> ()", &causal_conv1d_silu);
-  m.def("gdn_recurrent(Tensor qkv, int q_off, int k_off, int v_off, Tensor proj, int z_off, int a_off, int b_off, int n_qk_heads, int n_v_heads, Tensor A_log, Tensor dt_bias, Tensor norm_w, float eps, Tensor cu_seqlens, Tensor state_slot, Tensor state, bool write_state, Tensor out, bool pdl, Tensor? seq_end=None, Tensor? commit=None) -> ()", &gdn_recurrent);
+  m.def("gdn_recurrent(Tensor qkv, int q_off, int k_off, int v_off, Tensor proj, int z_off, int a_off, int b_off, int n_qk_heads, int n_v_heads, Tensor A_log, Tensor dt_bias, Tensor norm_w, float eps, Tensor cu_seqlens, Tensor state_slot, Tensor state, bool write_state, Tensor out, bool pdl, Tensor? seq_end=None, Tensor? commit=None, Tensor? chunk_ws=None) -> ()", &gdn_recurrent);
+  m.def("gdn_chunked_workspace_bytes(int T, int n_seq, int n_v_heads) -> int", &gdn_chunked_workspace_bytes);
   m.def("gdn_prefill_trace(bool enable) -> Tensor", &gdn_prefill_trace);
   m.def("kv_move_rows(Tensor block_table, Tensor table_row, Tensor src_pos, Tensor dst_pos, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int n_kv_heads, int head_dim, int format, int group) -> ()", &kv_move_rows);
   m.def("argmax_rows(Tensor logits, Tensor out, bool pdl) -> ()", &argmax_rows);

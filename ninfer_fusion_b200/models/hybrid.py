@@ -11,6 +11,8 @@ can be captured once in a CUDA graph.
 """
 from __future__ import annotations
 
+import os
+
 import math
 from dataclasses import dataclass
 from typing import Dict, List, Optional
@@ -221,7 +223,10 @@ class HybridModel:
         self.cfg = cfg
         self.w = weights
         self.device = torch.device(device)
-        self.ops = LaunchCounter(load_native())
+        self._raw_ops = load_native()
+        self.ops = LaunchCounter(self._raw_ops)
+        self.gdn_chunked = os.environ.get("NFB_GDN_CHUNKED", "1") != "0"   # chunked tensor-core GDN for long prefill chunks
+        self._gdn_ws = None
         self.status = StatusWord(self.device)
         self.pdl = pdl
         self.g = shard or ShardGeometry.full(cfg)
@@ -390,10 +395,20 @@ class HybridModel:
                                None, False, b.tree_parent, None)
         qk = g.gdn_qk_dim
         out = ws.mix_gdn[:T]
+        # long prefill chunks take the chunked tensor-core formulation (three launches), everything else the
+        # token-by-token kernels
+        chunk_ws = None
+        if (self.gdn_chunked and b.tree_commit is None and T >= 256 and T >= 64 * b.n_seqs and qk % 8 == 0
+                and proj.stride(0) % 8 == 0 and C % 8 == 0):
+            need = int(self._raw_ops.gdn_chunked_workspace_bytes(T, b.n_seqs, g.gdn_v_heads))
+            if self._gdn_ws is None or self._gdn_ws.numel() < need:
+                self._gdn_ws = torch.empty(need, dtype=torch.uint8, device=self.device)
+            chunk_ws = self._gdn_ws
+            ops.count += 2
         ops.gdn_recurrent(conv, 0, qk, 2 * qk, proj, C, C + g.gdn_v_dim, C + g.gdn_v_dim + g.gdn_v_heads,
                           g.gdn_qk_heads, g.gdn_v_heads, self.w[f"{prefix}/gdn/A_log"], self.w[f"{prefix}/gdn/dt_bias"],
                           self.w[f"{prefix}/gdn/norm"], cfg.rms_eps, b.cu_seqlens, b.state_slot, st.ssm[gi],
-                          write_state, out, self.pdl, None, b.tree_commit)
+                          write_state, out, self.pdl, None, b.tree_commit, chunk_ws)
         return out, self.w[f"{prefix}/gdn/out_proj"]
 
     def _mlp(self, ws: Workspace, T: int, prefix: str, next_norm_w, normed_out):

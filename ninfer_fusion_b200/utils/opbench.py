@@ -151,9 +151,12 @@ def bench_gdn_prefill(ops, batch, tokens, hk=16, hv=48, iters=10):
     A = torch.zeros(hv, device="cuda")
     nw = torch.ones(d, dtype=torch.bfloat16, device="cuda")
     res = {}
+    chunk_ws = torch.empty(int(ops.gdn_chunked_workspace_bytes(T, batch, hv)), dtype=torch.uint8, device="cuda")
     for name, fn in (("conv1d", lambda: ops.causal_conv1d_silu(proj, 0, C, conv_w, cu, tseq, slot, conv_state, conv_out, True, False, False)),
                      ("gdn", lambda: ops.gdn_recurrent(conv_out, 0, qk, 2 * qk, proj, C, C + vd, C + vd + hv, hk, hv, A, A, nw, 1e-6,
-                                                       cu, slot, ssm, True, out, False))):
+                                                       cu, slot, ssm, True, out, False)),
+                     ("gdn_chunked", lambda: ops.gdn_recurrent(conv_out, 0, qk, 2 * qk, proj, C, C + vd, C + vd + hv, hk, hv, A, A, nw,
+                                                               1e-6, cu, slot, ssm, True, out, False, None, None, chunk_ws))):
         med, best = time_op(fn, iters=iters, flush=L2Flusher())
         res[name + "_us"] = round(med * 1e6, 1)
     ops.gdn_prefill_trace(True)
