@@ -256,6 +256,58 @@ def cmd_make_artifact(args) -> int:
     return 0
 
 
+def cmd_convert(args) -> int:
+    """Hugging Face safetensors checkpoint -> .ninfer artifact (leaf by leaf, so host memory stays at one tensor),
+    or the inverse with --to-hf."""
+    import os
+    from .convert.hf import config_from_hf, hf_to_weights, weights_to_hf
+    from .convert.safetensors_io import SafetensorsSource, write_safetensors
+    from .models.vision import VisionConfig
+    if args.to_hf:
+        with ArtifactReader(args.src) as rd:
+            model_id, _ = rd.identity
+            cfg = get_config(model_id)
+            weights = {n: rd.tensor(n) for n in rd.tensors()}
+        vision = None
+        if any(k.startswith("vision/") for k in weights):
+            n_blocks = 1 + max(int(k.split("/")[2]) for k in weights if k.startswith("vision/blocks/"))
+            vision = VisionConfig().scaled(n_blocks, cfg.hidden)
+        write_safetensors(args.out, weights_to_hf(cfg, weights, vision), {"format": "pt"})
+        print(f"wrote {args.out}", file=sys.stderr)
+        return 0
+    if args.model:
+        cfg = get_config(args.model)
+    else:
+        with open(os.path.join(args.src, "config.json"), encoding="utf-8") as f:
+            cfg = config_from_hf(json.load(f), name=os.path.basename(os.path.normpath(args.src)))
+    src = SafetensorsSource(args.src)
+    vision = None
+    if args.vision or (args.vision is None and "model.visual.pos_embed.weight" in src):
+        n_blocks = 1 + max(int(n.split(".")[3]) for n in src.names() if n.startswith("model.visual.blocks."))
+        vision = VisionConfig().scaled(n_blocks, cfg.hidden)
+    with_mtp = "mtp.fc.weight" in src and not args.no_mtp
+    w = ArtifactWriter(args.model or cfg.name, args.weights_id)
+    n = 0
+    for name, t in hf_to_weights(cfg, src, with_mtp=with_mtp, vision=vision):
+        leaf = name.rsplit("/", 1)[-1]
+        fmt = "FP32" if t.dtype == torch.float32 else "BF16"
+        if args.format != "BF16" and t.dim() == 2 and leaf in ("in_proj", "o_proj", "out_proj", "gate_up", "down", "lm_head") \
+                and not name.startswith("vision/"):
+            fmt = args.format
+        w.add_tensor(name, t, fmt)
+        n += 1
+    for res in ("tokenizer.json", "chat_template.jinja", "generation_config.json"):
+        path = os.path.join(args.src, res) if os.path.isdir(args.src) else ""
+        if path and os.path.exists(path):
+            with open(path, "rb") as f:
+                w.add_resource(res, f.read())
+    src.close()
+    w.write(args.out)
+    print(f"wrote {args.out}: {n} tensors, draft module {'yes' if with_mtp else 'no'}, vision {'yes' if vision else 'no'}",
+          file=sys.stderr)
+    return 0
+
+
 def cmd_perplexity(args) -> int:
     """Corpus scoring on the oracle model: mean negative log-likelihood per token and its exponential."""
     from .models.reference_model import ReferenceModel, ReferenceSequence
@@ -318,6 +370,16 @@ def main(argv=None) -> int:
     m.add_argument("--seed", type=int, default=0)
     m.add_argument("--out", required=True)
     m.set_defaults(fn=cmd_make_artifact)
+    c = sub.add_parser("convert", help="Hugging Face safetensors checkpoint -> .ninfer artifact (or back with --to-hf)")
+    c.add_argument("src", help="checkpoint directory / .safetensors file (or an artifact with --to-hf)")
+    c.add_argument("--out", required=True)
+    c.add_argument("--model", default="", help="registered geometry; default: derived from the checkpoint's config.json")
+    c.add_argument("--weights-id", default="hf-import")
+    c.add_argument("--format", default="BF16", help="storage format of the matmul weights in the artifact")
+    c.add_argument("--vision", action=argparse.BooleanOptionalAction, default=None, help="import the vision tower (default: if present)")
+    c.add_argument("--no-mtp", action="store_true", help="skip the draft module")
+    c.add_argument("--to-hf", action="store_true", help="artifact -> safetensors with Hugging Face names")
+    c.set_defaults(fn=cmd_convert)
     p = sub.add_parser("perplexity", help="score a text corpus on the oracle model")
     add_model_args(p)
     p.add_argument("--corpus", required=True)

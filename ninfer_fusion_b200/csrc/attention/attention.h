@@ -57,6 +57,7 @@ struct PagedAttnParams {
   const unsigned long long* tree_mask;
   const int* tree_base;
   int impl;  // 0 = pick, 1 = SIMT kernel, 2 = tensor-core (mma.sync) kernel
+  int window = 0;  // sliding window: a query sees only its last `window` keys (0 = all of them)
 };
 // Split-KV paged attention over quantised pages with in-register dequantisation,
 // followed by the (m, l, o) merge fused with the output sigmoid gate.
@@ -80,6 +81,7 @@ struct PrefillAttnParams {
   const __nv_bfloat16* gate;  // optional sigmoid gate [T, ld_gate]
   long long ld_gate;
   __nv_bfloat16* out;         // [T, n_q_heads * head_dim]
+  int window = 0;             // sliding window (0 = full causal attention)
 };
 const char* paged_attention_prefill(const PrefillAttnParams& p, cudaStream_t stream, bool pdl);
 // Query tokens per block for a GQA geometry (128 MMA rows / group size).

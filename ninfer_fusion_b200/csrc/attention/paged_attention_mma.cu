@@ -56,8 +56,9 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
   const int G = p.n_q_heads / p.n_kv_heads;
   const int kv_len = p.q_kv_len[t];
   const int seq = p.q_seq[t];
-  const int k_begin = split * p.split_keys;
-  const int k_end = min(kv_len, k_begin + p.split_keys);
+  // a sliding window drops the keys before kv_len - window; the split then starts at the window's edge
+  const int k_begin = max(split * p.split_keys, p.window > 0 ? kv_len - p.window : 0);
+  const int k_end = min(kv_len, (split + 1) * p.split_keys);
   const long long part_base = (static_cast<long long>(t) * p.n_q_heads + kvh * G) * p.n_splits + split;
 
   if (seq < 0 || k_begin >= k_end) {

@@ -79,6 +79,14 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_prefill_kernel(const P
     const int r = warp * 16 + row0 + 8 * h;
     lim[h] = r < n_rows ? p.q_kv_len[t0 + r / G] : 0;
   }
+  // sliding window: row r sees keys [lim - window, lim); tiles entirely before the first token's window are skipped
+  int lo[2] = {0, 0};
+  int k_first = 0;
+  if (p.window > 0) {
+    lo[0] = max(0, lim[0] - p.window);
+    lo[1] = max(0, lim[1] - p.window);
+    k_first = max(0, p.q_kv_len[t0] - p.window) / kTileKeys * kTileKeys;
+  }
   // keys this warp needs at all (rows of a warp are consecutive tokens): skip tiles beyond it
   const int warp_last_row = min(n_rows - 1, warp * 16 + 15);
   const int warp_k_end = warp * 16 < n_rows ? p.q_kv_len[t0 + warp_last_row / G] : 0;
@@ -91,7 +99,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_prefill_kernel(const P
 #pragma unroll
     for (int j = 0; j < 4; ++j) o[n][j] = 0.f;
 
-  for (int kb = 0; kb < k_end; kb += kTileKeys) {
+  for (int kb = k_first; kb < k_end; kb += kTileKeys) {
     __syncthreads();  // previous tile consumed; Q stores ordered on the first pass
     if (threadIdx.x < kTileKeys) {
       const int key = kb + threadIdx.x;
@@ -190,7 +198,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_prefill_kernel(const P
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int kl = n * 8 + 2 * cq + (j & 1);
-        const bool valid = kb + kl < lim[j >> 1];
+        const bool valid = kb + kl < lim[j >> 1] && kb + kl >= lo[j >> 1];
         const float v = valid ? s[n][j] * sm.kscale[kl] : -CUDART_INF_F;
         s[n][j] = v;
         mx[j >> 1] = fmaxf(mx[j >> 1], v);

@@ -118,6 +118,14 @@ QWEN36_35B_A3B = ModelConfig(
     gdn_qk_heads=16, gdn_v_heads=32, ffn_inter=0, moe=MoEConfig(),
 )
 
+# The 3.5-generation 9B GDN hybrid (src/targets/qwen3_5_9b/impl/config.h:12-30: 32 layers, hidden 4096, 16 / 4 heads of
+# 256, GDN 16 key / 32 value heads of 128, MLP 12288, one draft layer).
+QWEN35_9B = ModelConfig(
+    name="qwen3.5-9b", n_layers=32, hidden=4096, vocab=248320,
+    n_q_heads=16, n_kv_heads=4, head_dim=256, rot_dim=64, rope_theta=1e7,
+    gdn_qk_heads=16, gdn_v_heads=32, ffn_inter=12288,
+)
+
 # Small geometries with the same structure, for CPU oracles and GPU smoke runs.
 TINY_DENSE = ModelConfig(
     name="tiny-dense", n_layers=4, hidden=256, vocab=1024,
@@ -132,7 +140,7 @@ TINY_MOE = ModelConfig(
     moe=MoEConfig(n_experts=16, top_k=4, expert_inter=128, shared_inter=128), max_context=4096,
 )
 
-REGISTRY = {c.name: c for c in (QWEN36_27B, QWEN36_35B_A3B, TINY_DENSE, TINY_MOE)}
+REGISTRY = {c.name: c for c in (QWEN36_27B, QWEN36_35B_A3B, QWEN35_9B, TINY_DENSE, TINY_MOE)}
 # The 3.8 generation shares the 27B geometry (docs/maintainer/qwen3.8-27b-artifact.md).
 REGISTRY["qwen3.8-27b"] = replace(QWEN36_27B, name="qwen3.8-27b")
 
