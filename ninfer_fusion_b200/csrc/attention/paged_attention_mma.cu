@@ -4,8 +4,8 @@
 // heads are the M rows of a 16-row MMA tile.  Per 64-key tile:
 //   1. all threads gather the tile's raw K / V rows from their pages (16-byte
 //      coalesced loads), dequantise (bf16 / fp8-row / int8-group / nvfp4) and
-//      store fp16 into shared memory: K as [key][d], V transposed as [d][key]
-//      (XOR-swizzled) so that both are plain ldmatrix B operands;
+//      store fp16 into shared memory, K and V both as [key][d] rows (16-byte
+//      stores): K is a plain ldmatrix B operand, V goes through ldmatrix.trans;
 //   2. warp w computes S = Q K^T for keys 16w..16w+15 (mma.sync m16n8k16 f16),
 //      applies the per-row K scale, masks, and publishes its row maxima;
 //   3. a tile-wide running max gives P = exp2(S - m); P (times the per-row V
@@ -34,7 +34,7 @@ using namespace attn_mma;
 
 struct Smem {
   __half k[kTileKeys][kLdK];   // 33,792 B
-  __half vt[D][kLdV];          // 36,864 B
+  __half v[kTileKeys][kLdK];   // 33,792 B, row-major like K: the PV product reads it through ldmatrix.trans
   __half q[16][kLdQ];          //  8,448 B
   __half p[16][kLdP];          //  2,304 B
   float kscale[2][kTileKeys];   // per-tile buffers, double-buffered with the row indices
@@ -125,8 +125,8 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
       sm.vscale[buf][threadIdx.x] = vs;
     }
   };
-  // K: unit = (key, part), 1024 units, 8 per thread; consecutive lanes read consecutive 16 values of a row.
-  // V: unit = (key pair, part), 512 units, 4 per thread, two rows each.  All sixteen loads are in flight together.
+  // K and V: unit = (key, part), 1024 units each, 8 per thread; consecutive lanes read consecutive 16 values of a
+  // row.  All sixteen loads are in flight together.
   auto load_raw = [&](int buf) {
 #pragma unroll
     for (int it = 0; it < 8; ++it) {
@@ -136,18 +136,14 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
       if (r >= 0) rawk[it].load(p.kv, p.kv.k_codes, p.kv.k_scales, r, u & 15);
     }
 #pragma unroll
-    for (int it = 0; it < 4; ++it) {
+    for (int it = 0; it < 8; ++it) {
       const int u = it * 128 + threadIdx.x;
-      const int jp = u >> 4, part = u & 15;
-      const long long r0 = sm.rowidx[buf][2 * jp], r1 = sm.rowidx[buf][2 * jp + 1];
-      rawv[2 * it].clear();
-      rawv[2 * it + 1].clear();
-      if (r0 >= 0) rawv[2 * it].load(p.kv, p.kv.v_codes, p.kv.v_scales, r0, part);
-      if (r1 >= 0) rawv[2 * it + 1].load(p.kv, p.kv.v_codes, p.kv.v_scales, r1, part);
+      const long long r = sm.rowidx[buf][u >> 4];
+      rawv[it].clear();
+      if (r >= 0) rawv[it].load(p.kv, p.kv.v_codes, p.kv.v_scales, r, u & 15);
     }
   };
-  // Dequantise to fp16: K as [key][d]; V transposed, two keys per 32-bit word, column index XOR-swizzled by
-  // the row's 16-row group to spread the transposed stores over banks.
+  // Dequantise to fp16, K and V both as [key][d] rows (16-byte stores, conflict-free with the 8-half row padding).
   auto store_tile = [&]() {
 #pragma unroll
     for (int it = 0; it < 8; ++it) {
@@ -159,19 +155,13 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
       dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
     }
 #pragma unroll
-    for (int it = 0; it < 4; ++it) {
+    for (int it = 0; it < 8; ++it) {
       const int u = it * 128 + threadIdx.x;
-      const int jp = u >> 4, part = u & 15;
-      uint32_t h0[8], h1[8];
-      rawv[2 * it].convert(h0);
-      rawv[2 * it + 1].convert(h1);
-      const int col = (2 * jp) ^ ((part & 7) * 8);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        // h0[i] = (v[key0][d], v[key0][d+1]), h1[i] likewise for key1 -> rows d and d+1 get (key0, key1)
-        *reinterpret_cast<uint32_t*>(&sm.vt[part * 16 + 2 * i][col]) = __byte_perm(h0[i], h1[i], 0x5410);
-        *reinterpret_cast<uint32_t*>(&sm.vt[part * 16 + 2 * i + 1][col]) = __byte_perm(h0[i], h1[i], 0x7632);
-      }
+      uint32_t h[8];
+      rawv[it].convert(h);
+      uint4* dst = reinterpret_cast<uint4*>(&sm.v[u >> 4][(u & 15) * 16]);
+      dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
+      dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
     }
   };
 
@@ -279,10 +269,10 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
         ldmatrix_x4(p_addr + kk * 32, a0, a1, a2, a3);
 #pragma unroll
         for (int np = 0; np < 4; ++np) {
-          const int d = warp * 64 + np * 16 + (lane & 7) + 8 * (lane >> 4);  // V^T row
-          const int col = (kk * 16 + 8 * ((lane >> 3) & 1)) ^ (((d >> 4) & 7) * 8);
+          // V[key][d] is k x n row-major: the transposing ldmatrix yields the col-major B fragments
           uint32_t b0, b1, b2, b3;
-          ldmatrix_x4(smem_u32(&sm.vt[d][col]), b0, b1, b2, b3);
+          ldmatrix_x4_trans(smem_u32(&sm.v[kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)][warp * 64 + np * 16 + 8 * (lane >> 4)]),
+                            b0, b1, b2, b3);
           mma_f16(o[2 * np], a0, a1, a2, a3, b0, b1);
           mma_f16(o[2 * np + 1], a0, a1, a2, a3, b2, b3);
         }
