@@ -194,3 +194,14 @@ def test_cli_artifact_roundtrip(tmp_path, capsys):
     assert cli.main(["perplexity", "--artifact", art, "--corpus", str(corpus), "--max-tokens", "40"]) == 0
     ppl = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert ppl["perplexity"] > 1.0
+
+
+def test_loadgen_against_the_server(server):
+    from ninfer_fusion_b200.serve.loadgen import run_level
+    port, _, _ = server
+    res = run_level(f"http://127.0.0.1:{port}/v1", "tiny-dense:test", ["hello there", "count to three"], concurrency=2,
+                    n_requests=4, max_tokens=5, api_key="sekret")
+    assert res["ok"] == 4 and res["errors"] == 0
+    assert res["output_tokens"] >= 4 and res["ttft_ms_p50"] is not None and res["output_tok_s"] > 0
+    bad = run_level(f"http://127.0.0.1:{port}/v1", "tiny-dense:test", ["x"], 1, 1, 2, api_key="wrong")
+    assert bad["ok"] == 0 and bad["errors"] == 1
