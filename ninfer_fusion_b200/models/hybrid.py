@@ -491,27 +491,38 @@ class HybridModel:
         return ws.normed[:T]
 
     def forward_hidden(self, ws: Workspace, b: StepBatch, kv: PagedKvCache, st: GdnStatePool,
-                       write_state: bool = True, rec: Optional[GdnRecords] = None) -> torch.Tensor:
-        """Runs all layers; returns the final-normed hidden states [T, hidden] (ws.normed)."""
+                       write_state: bool = True, rec: Optional[GdnRecords] = None,
+                       layers: Optional[tuple] = None) -> torch.Tensor:
+        """Runs all layers; returns the final-normed hidden states [T, hidden] (ws.normed).
+
+        `layers = (first, end)` runs one pipeline stage: a stage that does not start at layer 0 finds the residual
+        stream of the previous stage in ws.x[:T]; a stage that does not end at the last layer leaves its residual
+        stream there (the returned tensor is then ws.x[:T])."""
         cfg, ops = self.cfg, self.ops
         T = b.n_tokens
         if T > ws.max_tokens:
             raise ValueError(f"step of {T} tokens exceeds the workspace ({ws.max_tokens})")
+        first_layer, end_layer = layers if layers is not None else (0, cfg.n_layers)
         x = ws.x[:T]
-        ops.embed_gather(b.ids, self.w[f"{self.prefix}/embed"], x, self.pdl)
-        if b.embed_rows is not None and b.embed_rows.numel():
-            x.index_copy_(0, b.embed_rows, b.embed_vals)   # visual tokens replace their placeholder embeddings
-        first = f"{self.prefix}/layers/0/input_norm"
+        if first_layer == 0:
+            ops.embed_gather(b.ids, self.w[f"{self.prefix}/embed"], x, self.pdl)
+            if b.embed_rows is not None and b.embed_rows.numel():
+                x.index_copy_(0, b.embed_rows, b.embed_vals)   # visual tokens replace their placeholder embeddings
+        first = f"{self.prefix}/layers/{first_layer}/input_norm"
         self._add_rmsnorm(None, 0, None, x, None, self.w[first], ws.normed[:T], T, cfg.hidden)
-        for layer in range(cfg.n_layers):
+        for layer in range(first_layer, end_layer):
             p = f"{self.prefix}/layers/{layer}"
             if cfg.is_full_attn(layer):
                 mix, w_out = self._attn_layer(ws, b, kv, layer, T, p, self._attn_idx[layer])
             else:
                 mix, w_out = self._gdn_layer(ws, b, st, layer, T, p, write_state, rec)
             self._gemm_to_residual(ws, mix, w_out, T, self.w[f"{p}/post_norm"], ws.normed[:T])
-            nxt = (self.w[f"{self.prefix}/layers/{layer + 1}/input_norm"] if layer + 1 < cfg.n_layers
-                   else self.w[f"{self.prefix}/final_norm"])
+            if layer + 1 < cfg.n_layers:
+                # at a stage boundary the next layer's norm lives on the next rank, which recomputes it from the
+                # residual stream: any norm weight of this rank keeps the fused kernel's shape
+                nxt = self.w.get(f"{self.prefix}/layers/{layer + 1}/input_norm", self.w[f"{p}/input_norm"])
+            else:
+                nxt = self.w[f"{self.prefix}/final_norm"]
             if cfg.moe is None:
                 self._mlp(ws, T, p, nxt, ws.normed[:T])
             else:
@@ -519,7 +530,7 @@ class HybridModel:
                     from .moe import MoeBlock
                     self.moe = MoeBlock(cfg, self.device, ws.max_tokens, *self.ep, expert_format=self.expert_format)
                 self.moe.forward(self, ws, T, p, nxt, ws.normed[:T], self.moe_global_tokens)
-        return ws.normed[:T]
+        return ws.normed[:T] if end_layer == cfg.n_layers else x
 
     def logits(self, ws: Workspace, b: StepBatch, hidden: torch.Tensor) -> torch.Tensor:
         R = b.logit_rows.numel()

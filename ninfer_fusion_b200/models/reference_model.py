@@ -121,16 +121,26 @@ class ReferenceModel:
     # ---- forward over T new tokens of one sequence ----
     def forward(self, seq: ReferenceSequence, ids: torch.Tensor, trace: Optional[dict] = None,
                 positions: Optional[torch.Tensor] = None, embed_rows: Optional[torch.Tensor] = None,
-                embed_vals: Optional[torch.Tensor] = None) -> torch.Tensor:
+                embed_vals: Optional[torch.Tensor] = None, layers: Optional[tuple] = None,
+                hidden_in: Optional[torch.Tensor] = None) -> torch.Tensor:
         """`positions` ([T] or [T, 3]) overrides the default cache positions for the rope; `embed_vals` rows replace the
-        token embeddings at `embed_rows` (visual tokens of a multimodal prompt)."""
+        token embeddings at `embed_rows` (visual tokens of a multimodal prompt).
+
+        Pipeline stages: `layers = (first, end)` runs only that half-open range of layers; a stage that does not start
+        at layer 0 takes the residual stream of the previous stage as `hidden_in` [T, hidden], and a stage that does
+        not end at the last layer returns the residual stream instead of the final-normed hidden states.  The token
+        count of the sequence advances on the last stage only."""
         cfg, pf = self.cfg, self.prefix
         T = ids.shape[0]
+        first, end = layers if layers is not None else (0, cfg.n_layers)
         pos = seq.n_tokens + torch.arange(T) if positions is None else positions
-        x = self.w[f"{pf}/embed"][ids.long()].float()
-        if embed_rows is not None:
-            x[embed_rows.long()] = embed_vals.float()
-        for layer in range(cfg.n_layers):
+        if first == 0:
+            x = self.w[f"{pf}/embed"][ids.long()].float()
+            if embed_rows is not None:
+                x[embed_rows.long()] = embed_vals.float()
+        else:
+            x = R.bf16_round(hidden_in.float())
+        for layer in range(first, end):
             p = f"{pf}/layers/{layer}"
             normed = R.bf16_round(R.rmsnorm(x, self.w[f"{p}/input_norm"], cfg.rms_eps, True))
             if cfg.is_full_attn(layer):
@@ -144,6 +154,8 @@ class ReferenceModel:
             x = R.bf16_round(x + self._ffn(p, normed))
             if trace is not None:
                 trace[f"layer{layer}"] = x.clone()
+        if end < cfg.n_layers:
+            return x
         seq.n_tokens += T
         hidden = R.bf16_round(R.rmsnorm(x, self.w[f"{pf}/final_norm"], cfg.rms_eps, True))
         if trace is not None:
