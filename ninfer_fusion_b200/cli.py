@@ -52,6 +52,8 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--spec", default="none", choices=["none", "mtp"], help="speculative decoding with the MTP draft module")
     ap.add_argument("--draft-tokens", type=int, default=3)
     ap.add_argument("--allow-unknown-template", action="store_true")
+    ap.add_argument("--weight-budget-gib", type=float, default=0.0,
+                    help="device bytes for weights; layers beyond it rotate in from pinned host memory (eager decode)")
     ap.add_argument("--vision", action="store_true",
                     help="attach the vision tower (the artifact's vision/ tensors, or random ones with --random-init)")
     ap.add_argument("--vision-layers", type=int, default=0, help="shrink the vision tower to this many blocks (debug)")
@@ -147,7 +149,8 @@ def build_engine(args, cfg: ModelConfig, weights) -> Engine:
             text = {k: v for k, v in weights.items() if not k.startswith("vision/")}
             prog = GpuProgram(cfg, text, args.device, max_lanes=args.max_lanes, max_context=args.max_context,
                               kv_format=kv, page_size=args.page_size, prefill_chunk=args.prefill_chunk,
-                              use_graph=not args.no_graphs)
+                              use_graph=not args.no_graphs,
+                              weight_budget_bytes=int(args.weight_budget_gib * (1 << 30)) if args.weight_budget_gib > 0 else None)
             return attach_vision(args, cfg, weights, prog)
     else:
         def factory():

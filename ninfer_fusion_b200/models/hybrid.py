@@ -510,8 +510,11 @@ class HybridModel:
                 x.index_copy_(0, b.embed_rows, b.embed_vals)   # visual tokens replace their placeholder embeddings
         first = f"{self.prefix}/layers/{first_layer}/input_norm"
         self._add_rmsnorm(None, 0, None, x, None, self.w[first], ws.normed[:T], T, cfg.hidden)
+        note_layer = getattr(self.w, "note_layer", None)   # offloaded weights rotate through a device arena
         for layer in range(first_layer, end_layer):
             p = f"{self.prefix}/layers/{layer}"
+            if note_layer is not None:
+                note_layer(layer)
             if cfg.is_full_attn(layer):
                 mix, w_out = self._attn_layer(ws, b, kv, layer, T, p, self._attn_idx[layer])
             else:

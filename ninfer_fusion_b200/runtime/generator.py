@@ -31,9 +31,17 @@ class Generator:
     def __init__(self, cfg: ModelConfig, weights: Dict[str, torch.Tensor], device, max_batch: int, max_context: int,
                  kv_format: str | Sequence[str] = "bf16", page_size: int = 64, prefill_chunk: int = 2048,
                  use_graph: bool = True, pdl: bool = False, int8_group: int = 64,
-                 shard: Optional[ShardGeometry] = None, comm=None, max_logit_rows: int = 0):
+                 shard: Optional[ShardGeometry] = None, comm=None, max_logit_rows: int = 0,
+                 weight_budget_bytes: Optional[int] = None):
         self.cfg = cfg
         self.device = torch.device(device)
+        if weight_budget_bytes is not None:
+            # layers beyond the budget live in pinned host memory and rotate through a device arena; the host copies
+            # cannot be baked into a decode graph, so such a model runs eagerly
+            from .weight_offload import OffloadedWeights
+            weights = OffloadedWeights(weights, self.device, int(weight_budget_bytes))
+            if weights.plan.offloaded_layers:
+                use_graph = False
         self.max_batch, self.max_context = max_batch, max_context
         self.page_size = page_size
         self.prefill_chunk = prefill_chunk

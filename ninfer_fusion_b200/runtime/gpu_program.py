@@ -24,8 +24,13 @@ class GpuProgram(ProgramBase):
                  max_context: int = 8192, kv_format="bf16", page_size: int = 64, prefill_chunk: int = 2048,
                  use_graph: bool = True, pdl: bool = True, int8_group: int = 64, kv_pages: Optional[int] = None,
                  shard: Optional[ShardGeometry] = None, comm=None, penalties: bool = False,
-                 checkpoint_slots: Optional[int] = None):
+                 checkpoint_slots: Optional[int] = None, weight_budget_bytes: Optional[int] = None):
         super().__init__(cfg, max_lanes, max_context)
+        if weight_budget_bytes is not None:
+            from .weight_offload import OffloadedWeights
+            weights = OffloadedWeights(weights, device, int(weight_budget_bytes))
+            if weights.plan.offloaded_layers:
+                use_graph = False   # host copies cannot be baked into a decode graph
         # recurrent-state slots beyond the lanes hold the state images of session checkpoints (the reference keeps 2C)
         self.checkpoint_slots = max_lanes if checkpoint_slots is None else checkpoint_slots
         self.max_checkpoints = self.checkpoint_slots

@@ -163,3 +163,22 @@ def test_fp8_hadamard_kv_matches_reference():
                 agree += int(int(R.argmax_lowest(lg[None])[0]) == tok)
             h = ref.forward(seq, torch.tensor([tok]))
     assert total >= 10 and agree / total >= 0.9, f"{agree}/{total}"
+
+
+def test_weight_offload_generates_the_same_tokens():
+    """Three of the four layers rotate in from pinned host memory through a two-slot arena."""
+    from ninfer_fusion_b200.runtime.weight_offload import plan_residency
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cuda", seed=7, std=0.05)
+    torch.manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (33, 9)]
+    ref = Generator(cfg, w, "cuda", max_batch=2, max_context=256, kv_format="bf16", page_size=16, prefill_chunk=64,
+                    use_graph=False).generate(prompts, 10)
+    plan = plan_residency(w, 1 << 40)
+    budget = plan.fixed_bytes + 2 * max(plan.layer_bytes.values()) + plan.layer_bytes[0]
+    gen = Generator(cfg, w, "cuda", max_batch=2, max_context=256, kv_format="bf16", page_size=16, prefill_chunk=64,
+                    use_graph=True, weight_budget_bytes=budget)
+    assert gen.model.w.plan.offloaded_layers == [1, 2, 3] and not gen.use_graph
+    out = gen.generate(prompts, 10)
+    assert out == ref
+    assert gen.model.w.fetches >= 3 * 10
