@@ -167,6 +167,7 @@ class PagedKvCache:
                 vs = torch.zeros_like(ks)
             self.layers.append(KvLayerPlanes(fmt, group, k, v, ks, vs, hadamard))
         self.pool = PagePool(n_pages)
+        self.host_arena = None   # optional runtime.host_arena.HostKvArena for the cold copies of exported pages
         self.max_rows = max_rows
         self.max_pages_per_row = max_pages_per_row
         pin = self.device.type == "cuda"
@@ -280,7 +281,9 @@ class PagedKvCache:
                 if plane is None:
                     continue
                 dev = plane.index_select(0, idx)
-                host = torch.empty(dev.shape, dtype=dev.dtype, pin_memory=pin)
+                host = self.host_arena.alloc_like(dev) if self.host_arena is not None else None
+                if host is None:   # no arena, or no free run large enough: a private pinned allocation
+                    host = torch.empty(dev.shape, dtype=dev.dtype, pin_memory=pin)
                 host.copy_(dev, non_blocking=True)
                 out.append(host)
         if pin:
