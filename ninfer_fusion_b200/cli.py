@@ -142,6 +142,11 @@ def build_engine(args, cfg: ModelConfig, weights) -> Engine:
                                       draft_tokens=args.draft_tokens, kv_format=kv, page_size=args.page_size,
                                       prefill_chunk=args.prefill_chunk)
         return Engine(factory, prefill_chunk=args.prefill_chunk)
+    return Engine(program_factory(args, cfg, weights, kv), prefill_chunk=args.prefill_chunk)
+
+
+def program_factory(args, cfg: ModelConfig, weights, kv):
+    """Factory of the ordinary (non-speculative) Program for a KV storage plan (`kv`: one format or one per layer)."""
     if str(args.device).startswith("cuda"):
         from .runtime.gpu_program import GpuProgram
 
@@ -157,7 +162,7 @@ def build_engine(args, cfg: ModelConfig, weights) -> Engine:
             prog = ReferenceProgram(cfg, weights, max_lanes=args.max_lanes, max_context=args.max_context,
                                     kv_format=kv if isinstance(kv, str) else "bf16")
             return attach_vision(args, cfg, weights, prog)
-    return Engine(factory, prefill_chunk=args.prefill_chunk)
+    return factory
 
 
 # ---------------------------------------------------------------------------------------------------------
@@ -215,6 +220,16 @@ def cmd_serve(args) -> int:
     engine = build_engine(args, cfg, weights)
     svc = GenerationService(engine, tok, args.served_model_name or name, max_concurrent=args.max_concurrent,
                             queue_timeout_s=args.queue_timeout)
+    relayout = None
+    if args.kv_auto_relayout > 0:
+        if not str(args.device).startswith("cuda") or args.spec != "none":
+            raise SystemExit("--kv-auto-relayout needs the GPU program without speculative decoding")
+        from .serve.kv_auto_relayout import KvAutoRelayout, RelayoutConfig, kv_scale_energy
+        relayout = KvAutoRelayout(engine, len(cfg.attn_layers), lambda: kv_scale_energy(engine.program.kv),
+                                  lambda tiers: program_factory(args, cfg, weights, list(tiers)),
+                                  RelayoutConfig(target_bits=args.kv_auto_relayout, period_s=args.kv_relayout_period),
+                                  log=lambda rec: print(json.dumps(rec), file=sys.stderr, flush=True))
+        relayout.start()
     httpd = serve(svc, args.host, args.port, args.api_key, args.request_log)
     print(f"ninfer-serve: {name} on http://{args.host}:{httpd.server_address[1]}", file=sys.stderr, flush=True)
     try:
@@ -351,6 +366,9 @@ def main(argv=None) -> int:
     g.add_argument("--show-thinking", action="store_true")
     g.set_defaults(fn=cmd_generate)
     s = sub.add_parser("serve", help="OpenAI / Anthropic compatible HTTP server")
+    s.add_argument("--kv-auto-relayout", type=float, default=0.0,
+                   help="average KV bits per element to hold: per-layer tiers follow the layers' key energy (0 = off)")
+    s.add_argument("--kv-relayout-period", type=float, default=300.0, help="seconds between relayout decisions")
     add_model_args(s)
     s.add_argument("--host", default="127.0.0.1")
     s.add_argument("--port", type=int, default=8080)

@@ -203,12 +203,35 @@ class PagedKvCache:
         while len(pages) > keep:
             p = pages.pop()
             self.table_host[row, len(pages)] = -1
-            self.pool.release(p)
+            if p >= 0:
+                self.pool.release(p)
             self._dirty_rows.add(row)
+
+    def release_before(self, row: int, n_tokens: int, window: int, slack: int = 64) -> int:
+        """Sliding-window layers never look further back than `window` keys: pages that lie wholly before
+        n_tokens + 1 - window - slack go back to the pool (the row behaves like a ring over a bounded number of
+        pages; `slack` covers the prefill kernel's tile rounding).  The freed positions keep their place in the
+        block table as -1.  Returns the number of pages released.  Only valid when EVERY layer sharing this table
+        is windowed."""
+        if window <= 0:
+            return 0
+        pages = self.row_pages.get(row, [])
+        first_needed = max(0, n_tokens + 1 - window - slack)
+        n = 0
+        for i in range(min(len(pages), first_needed // self.page_size)):
+            if pages[i] >= 0:
+                self.pool.release(pages[i])
+                pages[i] = -1
+                self.table_host[row, i] = -1
+                n += 1
+        if n:
+            self._dirty_rows.add(row)
+        return n
 
     def free_row(self, row: int) -> None:
         for p in self.row_pages.pop(row, []):
-            self.pool.release(p)
+            if p >= 0:
+                self.pool.release(p)
         self.table_host[row].fill_(-1)
         self._dirty_rows.add(row)
 
@@ -217,6 +240,8 @@ class PagedKvCache:
         self.free_row(dst)
         full = n_tokens // self.page_size
         pages = self.row_pages.setdefault(dst, [])
+        if any(p < 0 for p in self.row_pages[src][: full + 1]):
+            raise ValueError("a row whose early pages were released (sliding window) cannot be forked")
         for i in range(full):
             p = self.row_pages[src][i]
             self.pool.retain(p)
@@ -244,6 +269,8 @@ class PagedKvCache:
         if tail and self.pool.free_pages < 1:
             return None
         src = self.row_pages[src_row]
+        if any(p < 0 for p in src[: full + (1 if tail else 0)]):
+            return None   # early pages were released (sliding window): this history cannot become a frontier
         pages = []
         for i in range(full):
             self.pool.retain(src[i])

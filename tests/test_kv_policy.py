@@ -98,3 +98,73 @@ def test_hadamard_frame_is_an_equivalent_k_frame():
     assert a["mean_abs_err"] < 1.3 * b["mean_abs_err"] and a["max_abs_err"] < 1.3 * b["max_abs_err"]
     H = R.hadamard_matrix(256)
     assert torch.allclose(H @ H.t(), torch.eye(256), atol=1e-5) and torch.equal(H, H.t())
+
+
+def test_sliding_window_rows_release_their_early_pages():
+    """A windowed row keeps a bounded number of pages: the cache behaves like a ring."""
+    import torch
+    from ninfer_fusion_b200.models.config import TINY_DENSE
+    from ninfer_fusion_b200.runtime.kv_cache import PagedKvCache
+    P, window = 16, 100
+    kv = PagedKvCache(TINY_DENSE, 32, P, 2, 64, "cpu", formats="bf16")
+    free0 = kv.pool.free_pages
+    peak = 0
+    for n in range(1, 900):
+        kv.ensure(0, n + 1)
+        kv.release_before(0, n, window)
+        peak = max(peak, free0 - kv.pool.free_pages)
+    assert peak <= (window + 64) // P + 3            # bounded, although 900 tokens need 57 pages
+    pages = kv.row_pages[0]
+    first_live = next(i for i, p in enumerate(pages) if p >= 0)
+    assert first_live * P <= 900 - window and (first_live + 1) * P > 900 + 1 - window - 64 - P
+    assert all(int(kv.table_host[0, i]) == -1 for i in range(first_live))
+    assert kv.detach_prefix(0, 200) is None           # not a reusable frontier any more
+    kv.free_row(0)
+    assert kv.pool.free_pages == free0
+    assert kv.release_before(1, 500, 0) == 0
+
+
+def test_kv_auto_relayout_policy_and_loop():
+    from ninfer_fusion_b200.serve.kv_auto_relayout import ColdPolicy, KvAutoRelayout, RelayoutConfig
+    from ninfer_fusion_b200.kv.policy import build_ladder
+    n = 8
+    cfg = RelayoutConfig(target_bits=8.5, min_observations=2, ewma=0.5, hysteresis=0.05)
+    pol = ColdPolicy(n, cfg)
+    energy = [1.0, 5.0, 0.2, 3.0, 0.1, 4.0, 0.3, 2.0]
+    pol.observe(energy)
+    assert not pol.decide().changed                       # one observation is not enough
+    pol.observe(energy)
+    d = pol.decide()
+    assert d.changed and len(d.tiers) == n
+    ladder = build_ladder()
+    bits = [ladder[t].bits_centi for t in d.tiers]
+    assert sum(bits) <= 850 * n
+    # the most energetic layers hold the most precise tiers
+    order = sorted(range(n), key=lambda i: -energy[i])
+    assert [bits[i] for i in order] == sorted(bits, reverse=True)
+    # small fluctuations inside the hysteresis do not reshuffle the layers
+    pol.current = list(d.tiers)
+    pol.observe([e * (1.02 if i % 2 else 0.98) for i, e in enumerate(energy)])
+    assert not pol.decide().changed
+
+    class FakeEngine:
+        def __init__(self):
+            self.reloads, self.fail = [], False
+
+        def reload_kv_storage(self, factory, timeout_s=60.0):
+            if self.fail:
+                raise TimeoutError("busy")
+            self.reloads.append(factory())
+
+    eng = FakeEngine()
+    samples = iter([None, energy, energy, energy])
+    loop = KvAutoRelayout(eng, n, lambda: next(samples), lambda tiers: (lambda: tuple(tiers)), cfg)
+    assert not loop.tick().changed and not loop.tick().changed
+    d = loop.tick()
+    assert d.changed and d.applied and eng.reloads == [tuple(d.tiers)] and loop.policy.current == d.tiers
+    assert not loop.tick().changed                        # same statistics, same layout: nothing to do
+    eng.fail = True
+    loop.policy.current = ["bf16"] * n
+    samples = iter([energy])
+    d = loop.tick()
+    assert d.changed and not d.applied and "drain" in d.reason and loop.policy.current == ["bf16"] * n
