@@ -32,16 +32,20 @@ namespace {
 
 using namespace attn_mma;
 
+// Page-table look-ups and row-scale loads are a chain of dependent global loads; doing them for 512 keys at once
+// (four keys per thread, all in flight together) takes that chain out of the per-tile critical path.
+constexpr int kSuperKeys = 512;
+
 struct Smem {
   __half k[kTileKeys][kLdK];   // 33,792 B
   __half v[kTileKeys][kLdK];   // 33,792 B, row-major like K: the PV product reads it through ldmatrix.trans
   __half q[16][kLdQ];          //  8,448 B
   __half p[16][kLdP];          //  2,304 B
-  float kscale[2][kTileKeys];   // per-tile buffers, double-buffered with the row indices
-  float vscale[2][kTileKeys];
+  float kscale[kSuperKeys];    // row scales and row indices of one super-tile of keys, looked up in one go
+  float vscale[kSuperKeys];
   float rowmax[4][16];
   float rowsum[4][16];
-  long long rowidx[2][kTileKeys];
+  long long rowidx[kSuperKeys];
 };
 
 template <int FORMAT>
@@ -104,9 +108,9 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
   constexpr bool kPrefetch = FORMAT != kKvBf16;
   RawUnit<FORMAT> rawk[8], rawv[8];
 
-  auto gather_idx = [&](int kb, int buf) {
-    if (threadIdx.x < kTileKeys) {
-      const int key = kb + threadIdx.x;
+  auto gather_super = [&](int sb) {
+    for (int i = threadIdx.x; i < kSuperKeys; i += blockDim.x) {
+      const int key = sb + i;
       long long r = -1;
       float ks = 0.f, vs = 0.f;
       if (key < k_end) {
@@ -120,25 +124,25 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
           vs = 1.f;
         }
       }
-      sm.rowidx[buf][threadIdx.x] = r;
-      sm.kscale[buf][threadIdx.x] = ks;
-      sm.vscale[buf][threadIdx.x] = vs;
+      sm.rowidx[i] = r;
+      sm.kscale[i] = ks;
+      sm.vscale[i] = vs;
     }
   };
   // K and V: unit = (key, part), 1024 units each, 8 per thread; consecutive lanes read consecutive 16 values of a
   // row.  All sixteen loads are in flight together.
-  auto load_raw = [&](int buf) {
+  auto load_raw = [&](int off) {
 #pragma unroll
     for (int it = 0; it < 8; ++it) {
       const int u = it * 128 + threadIdx.x;
-      const long long r = sm.rowidx[buf][u >> 4];
+      const long long r = sm.rowidx[off + (u >> 4)];
       rawk[it].clear();
       if (r >= 0) rawk[it].load(p.kv, p.kv.k_codes, p.kv.k_scales, r, u & 15);
     }
 #pragma unroll
     for (int it = 0; it < 8; ++it) {
       const int u = it * 128 + threadIdx.x;
-      const long long r = sm.rowidx[buf][u >> 4];
+      const long long r = sm.rowidx[off + (u >> 4)];
       rawv[it].clear();
       if (r >= 0) rawv[it].load(p.kv, p.kv.v_codes, p.kv.v_scales, r, u & 15);
     }
@@ -165,30 +169,28 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
     }
   };
 
-  if constexpr (kPrefetch) {
-    gather_idx(k_begin, 0);
-    __syncthreads();
-    load_raw(0);
-  }
-  int buf = 0;
-  for (int kb = k_begin; kb < k_end; kb += kTileKeys, buf ^= 1) {
-    // ---- 1. gather + dequantise the tile ----
-    const bool has_next = kb + kTileKeys < k_end;
+  for (int sb = k_begin; sb < k_end; sb += kSuperKeys) {
+  __syncthreads();  // the previous super-tile's index readers are done (also orders the Q stores on the first pass)
+  gather_super(sb);
+  __syncthreads();
+  const int s_end = min(k_end, sb + kSuperKeys);
+  if constexpr (kPrefetch) load_raw(0);
+  for (int kb = sb; kb < s_end; kb += kTileKeys) {
+    // ---- 1. dequantise the tile ----
+    const int off = kb - sb;
+    const bool has_next = kb + kTileKeys < s_end;
+    __syncthreads();  // previous tile fully consumed
     if constexpr (kPrefetch) {
-      __syncthreads();  // previous tile fully consumed (also orders the Q stores on the first pass)
       store_tile();
-      if (has_next) gather_idx(kb + kTileKeys, buf ^ 1);
       __syncthreads();
-      if (has_next) load_raw(buf ^ 1);  // in flight during this tile's math
+      if (has_next) load_raw(off + kTileKeys);  // in flight during this tile's math
     } else {
-      gather_idx(kb, buf);
-      __syncthreads();  // previous tile fully consumed, this tile's row indices visible
-      load_raw(buf);
+      load_raw(off);
       store_tile();
       __syncthreads();
     }
-    const float* kscale = sm.kscale[buf];
-    const float* vscale = sm.vscale[buf];
+    const float* kscale = sm.kscale + off;
+    const float* vscale = sm.vscale + off;
 
     // ---- 2. S = Q K^T for this warp's 16 keys ----
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -278,6 +280,7 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
         }
       }
     }
+  }
   }
 
   // ---- row sums: quad reduce, then across warps ----

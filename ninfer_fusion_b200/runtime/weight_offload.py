@@ -149,6 +149,16 @@ class OffloadedWeights:
     def items(self):
         return ((k, self[k]) for k in self.keys())
 
+    def values(self):
+        """Resident objects as they are; offloaded tensors as views of their pinned host image (no fetch)."""
+        yield from self._resident.values()
+        for l, lay in self._layout.items():
+            for off, shape, dt in lay.values():
+                n = 1
+                for s_ in shape:
+                    n *= s_
+                yield self._host[l][off:off + n * torch.empty(0, dtype=dt).element_size()].view(dt).view(shape)
+
     # ---------------------------------------------------------------- rotation
     def _fetch(self, layer: int) -> None:
         slot = self._slot_of[layer]

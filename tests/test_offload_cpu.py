@@ -39,3 +39,13 @@ def test_offloaded_weights_serve_the_same_tensors():
     assert torch.equal(ow["text/layers/3/input_norm"], w["text/layers/3/input_norm"])   # vectors stay resident
     assert ow.fetches >= 6          # three offloaded layers rotate through two slots, every step
     assert set(ow.keys()) == set(w)
+
+
+def test_values_do_not_fetch():
+    w = random_weights(TINY_DENSE, "cpu", seed=1)
+    plan = plan_residency(w, 1 << 40)
+    ow = OffloadedWeights(w, "cpu", plan.fixed_bytes + 2 * max(plan.layer_bytes.values()) + plan.layer_bytes[0])
+    before = ow.fetches
+    vals = list(ow.values())
+    assert len(vals) == len(w) and ow.fetches == before
+    assert all(isinstance(v, torch.Tensor) for v in vals)
