@@ -1,16 +1,18 @@
 // Tensor-core split-KV paged attention for decode / small-T verify, head_dim 256.
 //
-// Work item = (query token, kv head, key split), 4 warps.  The GQA group's query
+// Work item = (query token, kv head, key split), 8 warps.  The GQA group's query
 // heads are the M rows of a 16-row MMA tile.  Per 64-key tile:
 //   1. all threads gather the tile's raw K / V rows from their pages (16-byte
 //      coalesced loads), dequantise (bf16 / fp8-row / int8-group / nvfp4) and
 //      store fp16 into shared memory, K and V both as [key][d] rows (16-byte
 //      stores): K is a plain ldmatrix B operand, V goes through ldmatrix.trans;
-//   2. warp w computes S = Q K^T for keys 16w..16w+15 (mma.sync m16n8k16 f16),
+//   2. warp w computes S = Q K^T for keys 8w..8w+7 (mma.sync m16n8k16 f16),
 //      applies the per-row K scale, masks, and publishes its row maxima;
 //   3. a tile-wide running max gives P = exp2(S - m); P (times the per-row V
 //      scale) goes to shared memory as fp16;
-//   4. warp w accumulates O[:, 64w..64w+63] += P V over the tile's 64 keys.
+//   4. warp w accumulates O[:, 32w..32w+31] += P V over the tile's 64 keys.
+// Eight warps on a 64-key tile (rather than four) halve each thread's serial dequantisation work and double the
+// warps per SM that cover shared-memory latency: the kernel is bound by that latency, not by bandwidth.
 // Splits cover absolute key ranges and tiles start at split boundaries, so the
 // reduction order for a query depends only on key positions.  Output partials
 // (m, l, un-normalised O) use the same layout as the SIMT kernel and are
@@ -35,6 +37,9 @@ using namespace attn_mma;
 // Page-table look-ups and row-scale loads are a chain of dependent global loads; doing them for 512 keys at once
 // (four keys per thread, all in flight together) takes that chain out of the per-tile critical path.
 constexpr int kSuperKeys = 512;
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kUnits = kTileKeys * 16 / kThreads;   // 16-value units of a K (or V) tile per thread
 
 struct Smem {
   __half k[kTileKeys][kLdK];   // 33,792 B
@@ -43,13 +48,13 @@ struct Smem {
   __half p[16][kLdP];          //  2,304 B
   float kscale[kSuperKeys];    // row scales and row indices of one super-tile of keys, looked up in one go
   float vscale[kSuperKeys];
-  float rowmax[4][16];
-  float rowsum[4][16];
+  float rowmax[kWarps][16];
+  float rowsum[kWarps][16];
   long long rowidx[kSuperKeys];
 };
 
 template <int FORMAT>
-__global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnParams p) {
+__global__ void __launch_bounds__(kThreads, 2) paged_attn_mma_kernel(const PagedAttnParams p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
 
@@ -95,9 +100,9 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
 
   float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F};
   float l_run[2] = {0.f, 0.f};
-  float o[8][4];
+  float o[4][4];
 #pragma unroll
-  for (int n = 0; n < 8; ++n)
+  for (int n = 0; n < 4; ++n)
 #pragma unroll
     for (int j = 0; j < 4; ++j) o[n][j] = 0.f;
 
@@ -106,7 +111,7 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
   // before the current tile's math, so that their latency hides behind the MMAs; bf16 rows would
   // need twice the registers and keep the load-then-convert order.
   constexpr bool kPrefetch = FORMAT != kKvBf16;
-  RawUnit<FORMAT> rawk[8], rawv[8];
+  RawUnit<FORMAT> rawk[kUnits], rawv[kUnits];
 
   auto gather_super = [&](int sb) {
     for (int i = threadIdx.x; i < kSuperKeys; i += blockDim.x) {
@@ -129,19 +134,19 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
       sm.vscale[i] = vs;
     }
   };
-  // K and V: unit = (key, part), 1024 units each, 8 per thread; consecutive lanes read consecutive 16 values of a
-  // row.  All sixteen loads are in flight together.
+  // K and V: unit = (key, part), 1024 units each, kUnits per thread; consecutive lanes read consecutive 16 values of a
+  // row.  All of a thread's loads are in flight together.
   auto load_raw = [&](int off) {
 #pragma unroll
-    for (int it = 0; it < 8; ++it) {
-      const int u = it * 128 + threadIdx.x;
+    for (int it = 0; it < kUnits; ++it) {
+      const int u = it * kThreads + threadIdx.x;
       const long long r = sm.rowidx[off + (u >> 4)];
       rawk[it].clear();
       if (r >= 0) rawk[it].load(p.kv, p.kv.k_codes, p.kv.k_scales, r, u & 15);
     }
 #pragma unroll
-    for (int it = 0; it < 8; ++it) {
-      const int u = it * 128 + threadIdx.x;
+    for (int it = 0; it < kUnits; ++it) {
+      const int u = it * kThreads + threadIdx.x;
       const long long r = sm.rowidx[off + (u >> 4)];
       rawv[it].clear();
       if (r >= 0) rawv[it].load(p.kv, p.kv.v_codes, p.kv.v_scales, r, u & 15);
@@ -150,8 +155,8 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
   // Dequantise to fp16, K and V both as [key][d] rows (16-byte stores, conflict-free with the 8-half row padding).
   auto store_tile = [&]() {
 #pragma unroll
-    for (int it = 0; it < 8; ++it) {
-      const int u = it * 128 + threadIdx.x;
+    for (int it = 0; it < kUnits; ++it) {
+      const int u = it * kThreads + threadIdx.x;
       uint32_t h[8];
       rawk[it].convert(h);
       uint4* dst = reinterpret_cast<uint4*>(&sm.k[u >> 4][(u & 15) * 16]);
@@ -159,8 +164,8 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
       dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
     }
 #pragma unroll
-    for (int it = 0; it < 8; ++it) {
-      const int u = it * 128 + threadIdx.x;
+    for (int it = 0; it < kUnits; ++it) {
+      const int u = it * kThreads + threadIdx.x;
       uint32_t h[8];
       rawv[it].convert(h);
       uint4* dst = reinterpret_cast<uint4*>(&sm.v[u >> 4][(u & 15) * 16]);
@@ -193,32 +198,32 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
     const float* vscale = sm.vscale + off;
 
     // ---- 2. S = Q K^T for this warp's 16 keys ----
-    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
     {
       const uint32_t q_addr = smem_u32(&sm.q[(lane & 7) + 8 * ((lane >> 3) & 1)][8 * (lane >> 4)]);
-      const uint32_t k_addr = smem_u32(&sm.k[warp * 16 + (lane & 7) + 8 * (lane >> 4)][8 * ((lane >> 3) & 1)]);
+      // one ldmatrix.x4 brings this warp's 8 keys for two k-steps: d columns 0-7, 8-15, 16-23, 24-31 of the pair
+      const uint32_t k_addr = smem_u32(&sm.k[warp * 8 + (lane & 7)][8 * (lane >> 3)]);
 #pragma unroll 4
-      for (int ks = 0; ks < D / 16; ++ks) {
-        uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
-        ldmatrix_x4(q_addr + ks * 32, a0, a1, a2, a3);
-        ldmatrix_x4(k_addr + ks * 32, b0, b1, b2, b3);
-        mma_f16(s[0], a0, a1, a2, a3, b0, b1);
-        mma_f16(s[1], a0, a1, a2, a3, b2, b3);
+      for (int ks2 = 0; ks2 < D / 32; ++ks2) {
+        uint32_t a0, a1, a2, a3, c0, c1, c2, c3, b0, b1, b2, b3;
+        ldmatrix_x4(k_addr + ks2 * 64, b0, b1, b2, b3);
+        ldmatrix_x4(q_addr + ks2 * 64, a0, a1, a2, a3);
+        ldmatrix_x4(q_addr + ks2 * 64 + 32, c0, c1, c2, c3);
+        mma_f16(s, a0, a1, a2, a3, b0, b1);
+        mma_f16(s, c0, c1, c2, c3, b2, b3);
       }
     }
     float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-    for (int n = 0; n < 2; ++n)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int kl = warp * 16 + n * 8 + 2 * cq + (j & 1);  // key inside the tile
-        const int key = kb + kl;
-        bool valid = key < k_end;
-        if (valid && key >= tbase) valid = (tmask >> (key - tbase)) & 1ull;
-        const float v = valid ? s[n][j] * kscale[kl] : -CUDART_INF_F;
-        s[n][j] = v;
-        mx[j >> 1] = fmaxf(mx[j >> 1], v);
-      }
+    for (int j = 0; j < 4; ++j) {
+      const int kl = warp * 8 + 2 * cq + (j & 1);  // key inside the tile
+      const int key = kb + kl;
+      bool valid = key < k_end;
+      if (valid && key >= tbase) valid = (tmask >> (key - tbase)) & 1ull;
+      const float v = valid ? s[j] * kscale[kl] : -CUDART_INF_F;
+      s[j] = v;
+      mx[j >> 1] = fmaxf(mx[j >> 1], v);
+    }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
@@ -235,20 +240,21 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int r = row0 + 8 * h;
-      const float mt = fmaxf(fmaxf(sm.rowmax[0][r], sm.rowmax[1][r]), fmaxf(sm.rowmax[2][r], sm.rowmax[3][r]));
+      float mt = sm.rowmax[0][r];
+#pragma unroll
+      for (int w = 1; w < kWarps; ++w) mt = fmaxf(mt, sm.rowmax[w][r]);
       const float mn = fmaxf(m_run[h], mt);
       corr[h] = (mn == -CUDART_INF_F) ? 1.f : exp2f(m_run[h] - mn);
       m_run[h] = mn;
       l_run[h] *= corr[h];
     }
-#pragma unroll
-    for (int n = 0; n < 2; ++n) {
-      const int kl = warp * 16 + n * 8 + 2 * cq;
+    {
+      const int kl = warp * 8 + 2 * cq;
       float pv[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float mn = m_run[j >> 1];
-        pv[j] = (s[n][j] == -CUDART_INF_F) ? 0.f : exp2f(s[n][j] - mn);
+        pv[j] = (s[j] == -CUDART_INF_F) ? 0.f : exp2f(s[j] - mn);
         l_run[j >> 1] += pv[j];
         pv[j] *= vscale[kl + (j & 1)];
       }
@@ -256,13 +262,13 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
       *reinterpret_cast<uint32_t*>(&sm.p[row0 + 8][kl]) = pack_half2(pv[2], pv[3]);
     }
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
+    for (int n = 0; n < 4; ++n) {
       o[n][0] *= corr[0]; o[n][1] *= corr[0];
       o[n][2] *= corr[1]; o[n][3] *= corr[1];
     }
     __syncthreads();
 
-    // ---- 4. O[:, 64*warp .. +63] += P V ----
+    // ---- 4. O[:, 32*warp .. +31] += P V ----
     {
       const uint32_t p_addr = smem_u32(&sm.p[(lane & 7) + 8 * ((lane >> 3) & 1)][8 * (lane >> 4)]);
 #pragma unroll
@@ -270,10 +276,10 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
         uint32_t a0, a1, a2, a3;
         ldmatrix_x4(p_addr + kk * 32, a0, a1, a2, a3);
 #pragma unroll
-        for (int np = 0; np < 4; ++np) {
+        for (int np = 0; np < 2; ++np) {
           // V[key][d] is k x n row-major: the transposing ldmatrix yields the col-major B fragments
           uint32_t b0, b1, b2, b3;
-          ldmatrix_x4_trans(smem_u32(&sm.v[kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)][warp * 64 + np * 16 + 8 * (lane >> 4)]),
+          ldmatrix_x4_trans(smem_u32(&sm.v[kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)][warp * 32 + np * 16 + 8 * (lane >> 4)]),
                             b0, b1, b2, b3);
           mma_f16(o[2 * np], a0, a1, a2, a3, b0, b1);
           mma_f16(o[2 * np + 1], a0, a1, a2, a3, b2, b3);
@@ -301,13 +307,16 @@ __global__ void __launch_bounds__(128) paged_attn_mma_kernel(const PagedAttnPara
     if (g < G) {
       const long long pb = part_base + static_cast<long long>(g) * p.n_splits;
 #pragma unroll
-      for (int n = 0; n < 8; ++n) {
-        const int d = warp * 64 + n * 8 + 2 * cq;
+      for (int n = 0; n < 4; ++n) {
+        const int d = warp * 32 + n * 8 + 2 * cq;
         *reinterpret_cast<float2*>(p.part_o + pb * D + d) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
       }
       if (warp == 0 && cq == 0) {
         p.part_ml[pb * 2] = m_run[h];
-        p.part_ml[pb * 2 + 1] = sm.rowsum[0][g] + sm.rowsum[1][g] + sm.rowsum[2][g] + sm.rowsum[3][g];
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) tot += sm.rowsum[w][g];
+        p.part_ml[pb * 2 + 1] = tot;
       }
     }
   }
@@ -324,7 +333,7 @@ cudaError_t launch_fmt(const PagedAttnParams& p, cudaStream_t stream, bool pdl) 
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.Tq, p.n_kv_heads, p.n_splits);
-  cfg.blockDim = dim3(128);
+  cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = sizeof(Smem);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
