@@ -17,6 +17,8 @@
 #include <mutex>
 #include <unordered_map>
 
+#include <cstdlib>
+
 #include "../common/ptx.cuh"
 #include "../common/tensor_map.h"
 
@@ -32,8 +34,12 @@ constexpr int kWTileBytes = kTileN * 128;
 // grid of ~100 CTAs still keeps ~200 KB per SM in flight (the memory system needs ~30 MB in flight overall).
 template <int TN, bool DEEP = false>
 struct GemmCfg {
+  // TN = 256 (prefill): the main loop already runs at the tensor rate, so what matters is hiding the epilogue
+  // (9-24 us per tile against a 33 us main loop at K = 5120).  Two stages = 96 KB let two CTAs share an SM (and its
+  // 512 TMEM columns): one drains its accumulator while the other feeds the tensor core.  A grid that fits in one
+  // wave keeps the four-stage pipeline (DEEP).
   static constexpr int kStages =
-      DEEP ? (TN <= 32 ? 10 : 8) : (TN <= 32 ? 5 : (TN == 64 ? 4 : (TN == 128 ? 6 : 4)));
+      DEEP ? (TN <= 32 ? 10 : (TN == 256 ? 4 : 8)) : (TN <= 32 ? 5 : (TN == 64 ? 4 : (TN == 128 ? 6 : 2)));
   static constexpr int kXTileBytes = TN * 128;
   static constexpr int kStageBytes = kWTileBytes + kXTileBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // +1024: manual alignment
@@ -415,6 +421,297 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
   stamp(6);
 }
 
+int device_sm_count();
+
+// ------------------------------------------------------------------------------------------------------------
+// Persistent prefill kernel (TN = 256): one CTA per SM walks output tiles, with the roles split over six warps so
+// that the epilogue of tile i overlaps the main loop of tile i + 1:
+//   warp 0  TMA producer (4 stages of 16 KB weights + 32 KB tokens, one running stage counter across tiles)
+//   warp 1  MMA issuer; the fp32 accumulator alternates between TMEM columns [0, 256) and [256, 512)
+//   warps 2..5  epilogue: warp w drains TMEM lanes 32 (w % 4) ..; tcgen05.ld -> bias / GELU / residual / SwiGLU -> bf16
+// The non-persistent kernel spends 9-24 us per tile in an epilogue that nothing overlaps (main loop 33 us at
+// K = 5120); here the tensor core only waits for the first tile's pipeline fill.  Tiles are numbered token-tile
+// fastest, so the CTAs running at one time share a few weight tiles and all token tiles through L2.
+constexpr int kPersistTN = 256;
+constexpr int kPersistStages = 4;
+constexpr int kPersistThreads = 192;
+constexpr int kPersistStageBytes = kWTileBytes + kPersistTN * 128;
+constexpr int kPersistExchangeBytes = 2 * 16 * 64 * 4;   // SwiGLU: two 16-column chunks of up values
+constexpr int kPersistSmemBytes = kPersistStages * kPersistStageBytes + kPersistExchangeBytes + 1024;
+
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int EPI>
+__global__ void __launch_bounds__(kPersistThreads, 1) gemm_persist_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                                                                           const __grid_constant__ CUtensorMap tmap_x,
+                                                                           const KernelParams p) {
+  static_assert(EPI == kEpiStore || EPI == kEpiResidual || EPI == kEpiSwiglu, "persistent kernel: plain epilogues only");
+  constexpr int TN = kPersistTN;
+  constexpr int kStages = kPersistStages;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kStages];
+  __shared__ __align__(8) uint64_t bar_empty[kStages];
+  __shared__ __align__(8) uint64_t bar_acc_full[2];
+  __shared__ __align__(8) uint64_t bar_acc_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  __shared__ int epi_verdict[4];
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int w_rows = (EPI == kEpiSwiglu) ? 64 : kTileN;                 // output rows per tile
+  const int n_w_tiles = (EPI == kEpiSwiglu) ? (p.swiglu_half + 63) / 64 : (p.N + kTileN - 1) / kTileN;
+  const int n_t_tiles = (p.T + TN - 1) / TN;
+  const int n_tiles = n_w_tiles * n_t_tiles;
+  const int num_kb = p.num_kb;
+  volatile int* abortp = &abort_flag;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&bar_acc_full[a]), 1);
+      mbar_init(smem_u32(&bar_acc_empty[a]), 4);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  pdl_launch_next();
+
+  if (warp == 0) {
+    if (elect_one()) {
+      // ---------------- TMA producer ----------------
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_x = l2_policy_evict_last();
+      bool waited_prior = false;
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < n_tiles && !*abortp; tile += gridDim.x) {
+        const int n0 = (tile / n_t_tiles) * w_rows;
+        const int t0 = (tile % n_t_tiles) * TN;
+        const int row_a = n0;
+        const int row_b = (EPI == kEpiSwiglu) ? p.swiglu_half + n0 : n0 + 64;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (it >= kStages &&
+              !mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, &abort_flag, p.status, kStatusEmptyWaitTimeout)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = smem_u32(&bar_full[s]);
+          const uint32_t dst = smem_base + s * kPersistStageBytes;
+          const int kx = kb * kBlockK;
+          mbar_expect_tx(full, kPersistStageBytes);
+          tma_load_2d(dst, &tmap_w, full, kx, row_a, pol_w);
+          tma_load_2d(dst + 64 * 128, &tmap_w, full, kx, row_b, pol_w);
+          if (!waited_prior) {
+            pdl_wait_prior();  // activations are produced by the previous kernel
+            waited_prior = true;
+          }
+          tma_load_2d(dst + kWTileBytes, &tmap_x, full, kx, t0, pol_x);
+        }
+        if (!ok) break;
+      }
+      if (*abortp) {
+        // Unwinding: let copies that were already issued land before the CTA exits.
+        const uint32_t first = it > kStages ? it - kStages : 0;
+        for (uint32_t j = first; j < it; ++j) {
+          const uint32_t bar = smem_u32(&bar_full[j % kStages]);
+          const uint32_t ph = (j / kStages) & 1;
+          for (uint32_t spin = 0; spin < (1u << 20); ++spin)
+            if (mbar_try_wait(bar, ph)) break;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      // ---------------- MMA issuer ----------------
+      constexpr uint32_t idesc = umma_idesc(kTileN, TN, 1, 1);
+      uint32_t it = 0;
+      int tile_i = 0;
+      for (int tile = blockIdx.x; tile < n_tiles && !*abortp; tile += gridDim.x, ++tile_i) {
+        const int a = tile_i & 1;
+        const uint32_t aph = (tile_i >> 1) & 1;
+        // the epilogue has drained this accumulator's previous tile
+        if (tile_i >= 2 &&
+            !mbar_wait(smem_u32(&bar_acc_empty[a]), aph ^ 1, &abort_flag, p.status, kStatusAccumWaitTimeout))
+          break;
+        tc_fence_after();
+        const uint32_t acc = tmem_base + a * TN;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(smem_u32(&bar_full[s]), ph, &abort_flag, p.status, kStatusTmaWaitTimeout)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + s * kPersistStageBytes;
+          const uint64_t a_desc = umma_desc_k_sw128(a_addr);
+          const uint64_t b_desc = umma_desc_k_sw128(a_addr + kWTileBytes);
+#pragma unroll
+          for (int k = 0; k < kBlockK / 16; ++k)
+            tc_mma_f16(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          tc_commit(smem_u32(&bar_empty[s]));
+        }
+        if (!ok) break;
+        tc_commit(smem_u32(&bar_acc_full[a]));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue warps ----------------
+    pdl_wait_prior();   // the residual may be written by the previous kernel
+    const int lg = warp & 3;   // TMEM lane group this warp may read
+    constexpr int kChunk = 16;
+    float* up_s = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)) + kStages * kPersistStageBytes);
+    int tile_i = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_i) {
+      const int a = tile_i & 1;
+      const uint32_t ph = (tile_i >> 1) & 1;
+      const bool have = mbar_wait(smem_u32(&bar_acc_full[a]), ph, &abort_flag, p.status, kStatusAccumWaitTimeout);
+      // one verdict for the four warps, so that the chunk barriers below are never divergent
+      if (lane == 0) epi_verdict[warp - 2] = (have && !*abortp) ? 1 : 0;
+      epi_bar_sync();
+      const bool go = epi_verdict[0] && epi_verdict[1] && epi_verdict[2] && epi_verdict[3];
+      epi_bar_sync();   // everybody has read the verdict before the next tile overwrites it
+      if (!go) break;
+      tc_fence_after();
+      const int n0 = (tile / n_t_tiles) * w_rows;
+      const int t0 = (tile % n_t_tiles) * TN;
+      const uint32_t lane_taddr = tmem_base + a * TN + (static_cast<uint32_t>(lg * 32) << 16);
+      if constexpr (EPI == kEpiSwiglu) {
+        // lane groups 0, 1 hold gate rows, 2, 3 the matching up rows; up values cross in 16-column chunks
+        const bool is_up = lg >= 2;
+        const int r = (lg & 1) * 32 + lane;
+        const int n = n0 + r;
+        for (int c = 0, ci = 0; c < TN; c += kChunk, ++ci) {
+          float* buf = up_s + (ci & 1) * (kChunk * 64);
+          uint32_t v[kChunk];
+          tmem_ld_x16(lane_taddr + c, v);
+          tmem_ld_wait();
+          if (is_up) {
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) buf[j * 64 + r] = __uint_as_float(v[j]);
+          }
+          epi_bar_sync();
+          if (!is_up && t0 + c < p.T) {
+#pragma unroll
+            for (int m = 0; m < kChunk / 2; ++m) {
+              float o2[2];
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const int j = 2 * m + h;
+                const float g = __uint_as_float(v[j]);
+                o2[h] = g / (1.f + __expf(-g)) * buf[j * 64 + r];
+              }
+              const float send = (lane & 1) ? o2[0] : o2[1];
+              const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+              const int t = t0 + c + 2 * m + (lane & 1);
+              const int ne = n & ~1;
+              if (t < p.T && ne < p.swiglu_half) {
+                const uint32_t packed = (lane & 1) ? pack_bf16x2(recv, o2[1]) : pack_bf16x2(o2[0], recv);
+                *reinterpret_cast<uint32_t*>(p.out + static_cast<long long>(t) * p.ldo + ne) = packed;
+              }
+            }
+          }
+        }
+      } else {
+        const int n = n0 + lg * 32 + lane;
+        const float bias = (p.bias != nullptr && n < p.N) ? p.bias[n] : 0.f;
+        for (int c = 0; c < TN; c += kChunk) {
+          if (t0 + c >= p.T) break;
+          uint32_t v[kChunk];
+          tmem_ld_x16(lane_taddr + c, v);
+          tmem_ld_wait();
+          __nv_bfloat162 r2[kChunk / 2];
+          if constexpr (EPI == kEpiResidual) {
+#pragma unroll
+            for (int m = 0; m < kChunk / 2; ++m) {
+              const int t = t0 + c + 2 * m + (lane & 1);
+              const int ne = n & ~1;
+              r2[m] = (t < p.T && ne < p.N)
+                          ? *reinterpret_cast<const __nv_bfloat162*>(p.resid + static_cast<long long>(t) * p.ldr + ne)
+                          : __nv_bfloat162();
+            }
+          }
+#pragma unroll
+          for (int m = 0; m < kChunk / 2; ++m) {
+            float a0 = __uint_as_float(v[2 * m]) + bias;
+            float a1 = __uint_as_float(v[2 * m + 1]) + bias;
+            if constexpr (EPI == kEpiStore) {
+              if (p.act != kActNone) {
+                a0 = gelu(a0, p.act);
+                a1 = gelu(a1, p.act);
+              }
+            }
+            const float send = (lane & 1) ? a0 : a1;
+            const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+            const int t = t0 + c + 2 * m + (lane & 1);
+            const int ne = n & ~1;
+            if (t < p.T && ne < p.N) {
+              float lo = (lane & 1) ? recv : a0;
+              float hi = (lane & 1) ? a1 : recv;
+              if constexpr (EPI == kEpiResidual) {
+                lo += __bfloat162float(r2[m].x);
+                hi += __bfloat162float(r2[m].y);
+              }
+              *reinterpret_cast<uint32_t*>(p.out + static_cast<long long>(t) * p.ldo + ne) = pack_bf16x2(lo, hi);
+            }
+          }
+        }
+      }
+      // this warp is done with the accumulator: hand it back to the MMA issuer
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[a]));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+template <int EPI>
+cudaError_t launch_persist(const CUtensorMap& tw, const CUtensorMap& tx, const KernelParams& kp, int n_tiles,
+                           cudaStream_t stream, bool pdl) {
+  auto kern = gemm_persist_kernel<EPI>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPersistSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_tiles < device_sm_count() ? n_tiles : device_sm_count());
+  cfg.blockDim = dim3(kPersistThreads);
+  cfg.dynamicSmemBytes = kPersistSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, tw, tx, kp);
+}
+
 template <int TN, int EPI, bool DEEP>
 cudaError_t launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const KernelParams& kp, dim3 grid,
                        cudaStream_t stream, bool pdl) {
@@ -472,7 +769,10 @@ cudaError_t launch_tn(int TN, const CUtensorMap& tw, const CUtensorMap& tx, cons
     case 64: return deep ? launch_one<64, EPI, true>(tw, tx, kp, grid, stream, pdl)
                          : launch_one<64, EPI, false>(tw, tx, kp, grid, stream, pdl);
     case 128: return launch_one<128, EPI, false>(tw, tx, kp, grid, stream, pdl);
-    default: return launch_one<256, EPI, false>(tw, tx, kp, grid, stream, pdl);
+    default:
+      return static_cast<long long>(grid.x) * grid.y * grid.z <= device_sm_count()
+                 ? launch_one<256, EPI, true>(tw, tx, kp, grid, stream, pdl)
+                 : launch_one<256, EPI, false>(tw, tx, kp, grid, stream, pdl);
   }
 }
 
@@ -626,6 +926,23 @@ const char* gemm_bf16(const GemmArgs& a) {
   grid.y = (kp.T + tn - 1) / tn;
   grid.z = splits;
   cudaError_t e;
+  // prefill-sized problems with more tiles than SMs: persistent kernel, epilogue overlapped with the next main loop
+  // (NFB_GEMM_PERSISTENT=0 keeps the one-tile-per-CTA kernel for every size)
+  static const bool persistent_enabled = [] {
+    const char* e = getenv("NFB_GEMM_PERSISTENT");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  if (tn == kPersistTN && splits == 1 && persistent_enabled && !g_trace_enabled &&
+      (a.epi == kEpiStore || a.epi == kEpiResidual || a.epi == kEpiSwiglu) &&
+      static_cast<long long>(grid.x) * grid.y > device_sm_count()) {
+    const int n_tiles = static_cast<int>(grid.x * grid.y);
+    switch (a.epi) {
+      case kEpiStore: e = launch_persist<kEpiStore>(tw, tx, kp, n_tiles, a.stream, a.pdl); break;
+      case kEpiResidual: e = launch_persist<kEpiResidual>(tw, tx, kp, n_tiles, a.stream, a.pdl); break;
+      default: e = launch_persist<kEpiSwiglu>(tw, tx, kp, n_tiles, a.stream, a.pdl); break;
+    }
+    return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+  }
   switch (a.epi) {
     case kEpiStore: e = launch_tn<kEpiStore>(tn, tw, tx, kp, grid, a.stream, a.pdl); break;
     case kEpiResidual: e = launch_tn<kEpiResidual>(tn, tw, tx, kp, grid, a.stream, a.pdl); break;

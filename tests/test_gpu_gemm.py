@@ -143,3 +143,36 @@ def test_gemm_cluster_splitk_is_deterministic(ops, status):
         outs.append(out)
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
     _check(outs[0], x.float() @ w.float().t())
+
+
+@pytest.mark.parametrize("T", [300, 777, 2048])
+def test_gemm_persistent_prefill_kernel(ops, status, T):
+    """More output tiles than SMs at TN = 256: the persistent kernel (epilogue overlapped with the next main loop)
+    with every plain epilogue, ragged T / N / K, bias + GELU, in-place residual; checked tile by tile."""
+    # store + bias + GELU(tanh), N and K not multiples of the tile
+    x, w = _mk(T, 20040, 1096, seed=1)
+    bias = torch.randn(20040, device="cuda")
+    out = torch.full((T, 20040), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.gemm_bf16(x, w, out, EPI_STORE, None, bias, None, 1, status.tensor, False, 1)
+    ref = torch.nn.functional.gelu(x.float() @ w.float().t() + bias, approximate="tanh")
+    _check(out, ref)
+    assert not torch.isnan(out).any()
+    # in-place residual
+    x, w = _mk(T, 19200, 512, seed=2)
+    resid = torch.randn(T, 19200, device="cuda").to(torch.bfloat16)
+    out = resid.clone()
+    ops.gemm_bf16(x, w, out, EPI_RESIDUAL, out, None, None, 1, status.tensor, False)
+    _check(out, resid.float() + x.float() @ w.float().t())
+    # SwiGLU with [gate; up] parent
+    inter = 9792
+    x, w = _mk(T, 2 * inter, 640, seed=3)
+    out = torch.full((T, inter), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.gemm_bf16(x, w, out, EPI_SWIGLU, None, None, None, 1, status.tensor, False)
+    gu = x.float() @ w.float().t()
+    _check(out, torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:])
+    assert not torch.isnan(out).any()
+    # twice in a row on the same stream (barrier phases restart per launch), PDL attribute set
+    out2 = torch.empty_like(out)
+    ops.gemm_bf16(x, w, out2, EPI_SWIGLU, None, None, None, 1, status.tensor, True)
+    assert torch.equal(out, out2)
+    status.check("persistent gemm")
