@@ -45,6 +45,7 @@ class RequestOptions:
     pending_timeout_s: Optional[float] = None  # how long it may wait for admission
     session: Optional[str] = None            # continuation key for prefix reuse
     media: object = None                     # frontend.media.PreparedPrompt for a request with images / videos
+    shared_prefix_tokens: int = 0            # publish the first N prompt tokens (system prompt) in the shared catalogue
 
 
 @dataclass
@@ -379,8 +380,14 @@ class Engine:
                 t0 = time.perf_counter()
                 try:
                     n_before = req.lane.n_cached
-                    first = self.program.prefill_step(req.lane, self.governor.unit)
+                    budget = self.governor.unit
+                    edge = req.opts.shared_prefix_tokens
+                    if 0 < edge < len(req.prompt) and n_before < edge:
+                        budget = min(budget, edge - n_before)      # stop exactly at the shared boundary
+                    first = self.program.prefill_step(req.lane, budget)
                     self.stats.prompt_tokens += req.lane.n_cached - n_before
+                    if first is None and req.lane.n_cached == edge and n_before < edge:
+                        self.program.checkpoint(req.lane, "shared", "shared")   # any session may start from here
                 except RequestError as e:
                     self._active.remove(req)
                     self._finish(req, "error", str(e))

@@ -67,6 +67,9 @@ class Checkpoint:
     nbytes: int = 0       # size of the cold copy (host / disk tiers)
 
 
+SHARED_SESSION = "__shared__"
+
+
 class ProgramBase:
     """Lane bookkeeping shared by the GPU and the CPU-reference programs."""
 
@@ -86,6 +89,9 @@ class ProgramBase:
         self.disk_budget_bytes = 0
         self.cold_dir: Optional[str] = None
         self.cold_stats = {"demoted_host": 0, "demoted_disk": 0, "promoted": 0, "dropped": 0}
+        # shared-prefix catalogue: frontiers of prompt prefixes that any request may start from (system prompts)
+        self.max_shared_prefixes = 8
+        self.shared_stats = {"published": 0, "hits": 0}
 
     # ---- capacity ----
     def free_lanes(self) -> int:
@@ -178,13 +184,34 @@ class ProgramBase:
         return None
 
     def checkpoint(self, lane: Lane, session: str, kind: str) -> bool:
+        """Remember the lane's materialised frontier (lane.tokens[:n_cached]) for `session`.
+
+        kind 'shared' publishes the frontier in the shared-prefix catalogue (session SHARED_SESSION): any later request
+        whose prompt starts with exactly these tokens may start from it, whatever its session.  The catalogue keeps
+        `max_shared_prefixes` entries, least recently used first out; an identical prefix is only refreshed."""
         if lane.media is not None:
             return False   # see open(): multimodal histories are not reusable by token ids alone
-        """Remember the lane's materialised frontier (lane.tokens[:n_cached]) for `session`."""
         n = lane.n_cached
         if not session or n <= 0:
             return False
-        for c in [c for c in self.checkpoints if c.session == session and c.kind == kind]:
+        if kind == "shared":
+            session = SHARED_SESSION
+            toks = list(lane.tokens[:n])
+            shared = [c for c in self.checkpoints if c.kind == "shared"]
+            for c in shared:
+                if c.tokens == toks:
+                    self._clock += 1
+                    c.last_used = self._clock
+                    return True
+            while len(shared) >= self.max_shared_prefixes:
+                victim = min(shared, key=lambda c: c.last_used)
+                shared.remove(victim)
+                if victim.tier == "gpu":
+                    self.checkpoints.remove(victim)
+                    self._drop(victim.handle)
+                else:
+                    self._forget_cold(victim)
+        for c in [c for c in self.checkpoints if c.session == session and c.kind == kind and kind != "shared"]:
             if c.tier == "gpu":              # one frontier per (session, kind)
                 self.checkpoints.remove(c)
                 self._drop(c.handle)
@@ -200,16 +227,20 @@ class ProgramBase:
                 return False
         self._clock += 1
         self.checkpoints.append(Checkpoint(session, kind, list(lane.tokens[:n]), handle, self._clock))
+        if kind == "shared":
+            self.shared_stats["published"] += 1
         return True
 
     def _match(self, session: Optional[str], prompt: Sequence[int]) -> Optional[Checkpoint]:
         best = None
-        if session:
-            for c in self.checkpoints:
-                n = len(c.tokens)
-                if c.session == session and n < len(prompt) and (best is None or n > len(best.tokens)) \
-                        and list(prompt[:n]) == c.tokens:
-                    best = c
+        for c in self.checkpoints:
+            n = len(c.tokens)
+            mine = bool(session) and c.session == session
+            if (mine or c.kind == "shared") and n < len(prompt) and (best is None or n > len(best.tokens)) \
+                    and list(prompt[:n]) == c.tokens:
+                best = c
+        if best is not None and best.kind == "shared":
+            self.shared_stats["hits"] += 1
         return best
 
     def _snapshot(self, lane: Lane, n_tokens: int):

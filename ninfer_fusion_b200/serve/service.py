@@ -68,6 +68,8 @@ class GenerationService:
         self.max_concurrent = max_concurrent
         self.started = time.time()
         self.media = None                 # frontend.media.MediaProcessor, created on the first media request
+        self.auto_shared_prefix = True    # publish the leading system block of chat prompts in the shared-prefix catalogue
+        self.min_shared_prefix_tokens = 32
         self.allow_media_files = False    # local paths in media parts (CLI use); gateways leave this off
 
     # ------------------------------------------------------------------ prompt side
@@ -97,6 +99,23 @@ class GenerationService:
         else:
             raise RequestError("request has neither messages nor prompt")
         return self.tok.encode(text), None
+
+    def shared_prefix_tokens(self, req: GenRequest, ids: Sequence[int]) -> int:
+        """Length in tokens of the prompt's leading system block (system / developer message with the tool
+        declarations the template renders into it), when it is long enough to be worth sharing across sessions."""
+        if not self.auto_shared_prefix or req.messages is None or not req.messages:
+            return 0
+        if req.messages[0].get("role") not in ("system", "developer") and not req.tools:
+            return 0
+        text = render_chat(req.messages, req.tools, add_generation_prompt=True, enable_thinking=req.enable_thinking)
+        end = text.find("<|im_end|>\n")
+        if end < 0:
+            return 0
+        head = self.tok.encode(text[: end + len("<|im_end|>\n")])
+        n = len(head)
+        if n < self.min_shared_prefix_tokens or n >= len(ids) or list(ids[:n]) != head:
+            return 0
+        return n
 
     def count_tokens(self, req: GenRequest) -> int:
         return len(self.prepare(req))
@@ -132,6 +151,8 @@ class GenerationService:
                 on_start(rid, len(ids))
             opts = self._options(req)
             opts.media = media
+            if media is None:
+                opts.shared_prefix_tokens = self.shared_prefix_tokens(req, ids)
             handle = self.engine.submit(ids, opts)
             dec = StreamDecoder(self.tok, skip_special=True)
             # a chat prompt with thinking enabled continues inside an open reasoning frame only if the template

@@ -192,3 +192,43 @@ def test_cold_tiers_park_and_revive_session_frontiers(tmp_path):
         assert warm_run == cold_run and eng.stats.prefix_hits == hits + 1 and prog.cold_stats["promoted"] >= 1
     finally:
         eng.shutdown()
+
+
+def test_shared_prefix_catalogue_across_sessions():
+    """The system block of one request becomes a frontier that requests of OTHER sessions start from; outputs equal a
+    cold run; the catalogue is bounded and least-recently-used entries leave first."""
+    from ninfer_fusion_b200.runtime.engine import Engine, RequestOptions
+    from ninfer_fusion_b200.runtime.program import ReferenceProgram
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cpu", seed=11, std=0.05)
+    torch.manual_seed(3)
+    system = torch.randint(0, cfg.vocab, (40,)).tolist()
+    users = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (9, 14, 5)]
+
+    def run(engine, prompt, session, edge):
+        return engine.submit(prompt, RequestOptions(max_tokens=6, session=session, shared_prefix_tokens=edge)).wait(timeout=60)
+
+    cold = Engine(lambda: ReferenceProgram(cfg, w, max_lanes=2, max_context=256), prefill_chunk=16)
+    warm = Engine(lambda: ReferenceProgram(cfg, w, max_lanes=2, max_context=256), prefill_chunk=16)
+    try:
+        want = [run(cold, system + u, None, 0) for u in users]
+        got = [run(warm, system + u, f"s{i}", len(system)) for i, u in enumerate(users)]
+        assert got == want
+        prog = warm.program
+        assert prog.shared_stats["published"] == 1 and prog.shared_stats["hits"] == 2
+        assert warm.stats.prefix_hits == 2 and warm.stats.prefix_tokens_reused == 2 * len(system)
+        # a different system prompt is a different entry; the catalogue keeps at most max_shared_prefixes of them
+        prog.max_shared_prefixes = 2
+        for k in range(3):
+            other = torch.randint(0, cfg.vocab, (33 + k,)).tolist()
+            run(warm, other + users[0], None, len(other))
+        shared = [c for c in prog.checkpoints if c.kind == "shared"]
+        assert len(shared) == 2 and all(len(c.tokens) in (34, 35) for c in shared)
+        # no boundary inside the prompt -> nothing published
+        n_pub = prog.shared_stats["published"]
+        run(warm, users[1], None, 0)
+        run(warm, users[1], None, len(users[1]))
+        assert prog.shared_stats["published"] == n_pub
+    finally:
+        cold.shutdown()
+        warm.shutdown()

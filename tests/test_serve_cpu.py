@@ -205,3 +205,23 @@ def test_loadgen_against_the_server(server):
     assert res["output_tokens"] >= 4 and res["ttft_ms_p50"] is not None and res["output_tok_s"] > 0
     bad = run_level(f"http://127.0.0.1:{port}/v1", "tiny-dense:test", ["x"], 1, 1, 2, api_key="wrong")
     assert bad["ok"] == 0 and bad["errors"] == 1
+
+
+def test_service_finds_the_shared_system_prefix(server):
+    _, svc, _ = server
+    long_system = "You are a careful assistant. " * 12
+    req = GenRequest(messages=[{"role": "system", "content": long_system}, {"role": "user", "content": "hi"}], max_tokens=2)
+    ids = svc.prepare(req)
+    n = svc.shared_prefix_tokens(req, ids)
+    assert 32 <= n < len(ids)
+    assert svc.tok.decode(ids[:n]).endswith("<|im_end|>\n") or svc.tok.decode(ids[:n], skip_special=False).endswith("<|im_end|>\n")
+    short = GenRequest(messages=[{"role": "system", "content": "Be brief."}, {"role": "user", "content": "hi"}], max_tokens=2)
+    assert svc.shared_prefix_tokens(short, svc.prepare(short)) == 0
+    none = GenRequest(messages=[{"role": "user", "content": "hi"}], max_tokens=2)
+    assert svc.shared_prefix_tokens(none, svc.prepare(none)) == 0
+    before = svc.engine.program.shared_stats["published"]
+    a = svc.generate(GenRequest(messages=req.messages, max_tokens=3, temperature=0.0, session="u1"))
+    b = svc.generate(GenRequest(messages=[req.messages[0], {"role": "user", "content": "other question"}], max_tokens=3,
+                                temperature=0.0, session="u2"))
+    assert a.error == "" and b.error == ""
+    assert svc.engine.program.shared_stats["published"] == before + 1 and svc.engine.program.shared_stats["hits"] >= 1
