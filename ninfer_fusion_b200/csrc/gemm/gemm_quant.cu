@@ -23,6 +23,7 @@
 // sm_100a), src/ops/linear/fp8/fp8_a8_mma.cuh (mma.sync f8f6f4 with row-scale epilogue).
 #include "gemm_quant.h"
 
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -498,6 +499,336 @@ __global__ void __launch_bounds__(256) quant_act_nvfp4_kernel(const __nv_bfloat1
   sf_plane[off] = sc;
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// Persistent prefill kernel for quantised weights: the same role split as the bf16 one (gemm_bf16.cu) -- warp 0 TMA,
+// warp 1 MMA with the accumulator alternating between two TMEM column ranges, warps 2..5 epilogue -- so the epilogue
+// of tile i overlaps the main loop of tile i + 1.  With fp8 / nvfp4 the main loop is 2-4 x shorter than in bf16 while
+// the epilogue is the same size, so the one-tile-per-CTA kernel spends most of its time in epilogues.
+//   fp8 row-scale: 256-token tiles, accumulators at TMEM columns [0, 256) and [256, 512)
+//   nvfp4:         128-token tiles, accumulators at [0, 128) and [128, 256), scale factors at [256, 288)
+template <int QT>
+struct QPersist {
+  static constexpr bool kBS = QT == kQNvfp4;
+  static constexpr int TN = kBS ? 128 : 256;
+  static constexpr int kXTileBytes = TN * kKBytes;
+  static constexpr int kSfaBytes = kBS ? 4 * kSfTileBytes : 0;
+  static constexpr int kSfbBytes = kBS ? 4 * kSfTileBytes : 0;
+  static constexpr int kStageBytes = kWTileBytes + kXTileBytes + kSfaBytes + kSfbBytes;
+  static constexpr int kStages = kBS ? 5 : 4;
+  static constexpr int kExchangeBytes = 2 * 16 * 64 * 4;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kExchangeBytes + 1024;
+  static constexpr int kSfaCol = 2 * TN;
+  static constexpr int kSfbCol = 2 * TN + 16;
+};
+constexpr int kQPersistThreads = 192;
+
+__device__ __forceinline__ void q_epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int QT, int EPI>
+__global__ void __launch_bounds__(kQPersistThreads, 1) gemm_q_persist_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                                                                              const __grid_constant__ CUtensorMap tmap_x,
+                                                                              const QParams p) {
+  static_assert(EPI == kEpiStore || EPI == kEpiResidual || EPI == kEpiSwiglu, "persistent kernel: plain epilogues only");
+  using Cfg = QPersist<QT>;
+  constexpr int TN = Cfg::TN;
+  constexpr int kStages = Cfg::kStages;
+  constexpr bool kBS = Cfg::kBS;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kStages];
+  __shared__ __align__(8) uint64_t bar_empty[kStages];
+  __shared__ __align__(8) uint64_t bar_acc_full[2];
+  __shared__ __align__(8) uint64_t bar_acc_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  __shared__ int epi_verdict[4];
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int n_w_tiles = (p.N + kTileN - 1) / kTileN;
+  const int n_t_tiles = (p.T + TN - 1) / TN;
+  const int n_tiles = n_w_tiles * n_t_tiles;
+  const int num_kb = p.num_kb;
+  volatile int* abortp = &abort_flag;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&bar_acc_full[a]), 1);
+      mbar_init(smem_u32(&bar_acc_empty[a]), 4);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  pdl_launch_next();
+
+  if (warp == 0) {
+    if (elect_one()) {
+      // ---------------- TMA producer ----------------
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_x = l2_policy_evict_last();
+      bool waited_prior = false;
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < n_tiles && !*abortp; tile += gridDim.x) {
+        const int w_tile = tile / n_t_tiles;
+        const int n0 = w_tile * kTileN;
+        const int t0 = (tile % n_t_tiles) * TN;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (it >= kStages &&
+              !mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, &abort_flag, p.status, kStatusEmptyWaitTimeout)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = smem_u32(&bar_full[s]);
+          const uint32_t dst = smem_base + s * Cfg::kStageBytes;
+          const int kx = kb * kKBytes;
+          mbar_expect_tx(full, Cfg::kStageBytes);
+          tma_load_2d(dst, &tmap_w, full, kx, n0, pol_w);
+          tma_load_2d(dst + 64 * 128, &tmap_w, full, kx, n0 + 64, pol_w);
+          if constexpr (kBS) {
+            const uint8_t* sfa = p.w_sf + (static_cast<long long>(w_tile) * p.k_tiles + 4 * kb) * kSfTileBytes;
+            bulk_load(dst + kWTileBytes + Cfg::kXTileBytes, sfa, Cfg::kSfaBytes, full);
+          }
+          if (!waited_prior) {
+            pdl_wait_prior();  // activations (and their scales) come from the previous kernel
+            waited_prior = true;
+          }
+          tma_load_2d(dst + kWTileBytes, &tmap_x, full, kx, t0, pol_x);
+          if constexpr (kBS) {
+            const uint32_t sfb_dst = dst + kWTileBytes + Cfg::kXTileBytes + Cfg::kSfaBytes;
+            const long long tile0 = t0 / 128;
+            bulk_load(sfb_dst, p.x_sf + (tile0 * p.k_tiles + 4 * kb) * kSfTileBytes, 4 * kSfTileBytes, full);
+          }
+        }
+        if (!ok) break;
+      }
+      if (*abortp) {
+        const uint32_t first = it > kStages ? it - kStages : 0;
+        for (uint32_t j = first; j < it; ++j) {
+          const uint32_t bar = smem_u32(&bar_full[j % kStages]);
+          const uint32_t ph = (j / kStages) & 1;
+          for (uint32_t spin = 0; spin < (1u << 20); ++spin)
+            if (mbar_try_wait(bar, ph)) break;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      // ---------------- MMA issuer ----------------
+      constexpr uint32_t idesc = kBS ? idesc_nvfp4(kTileN, TN) : umma_idesc(kTileN, TN, 0, 0);
+      uint32_t it = 0;
+      int tile_i = 0;
+      for (int tile = blockIdx.x; tile < n_tiles && !*abortp; tile += gridDim.x, ++tile_i) {
+        const int a = tile_i & 1;
+        const uint32_t aph = (tile_i >> 1) & 1;
+        if (tile_i >= 2 &&
+            !mbar_wait(smem_u32(&bar_acc_empty[a]), aph ^ 1, &abort_flag, p.status, kStatusAccumWaitTimeout))
+          break;
+        tc_fence_after();
+        const uint32_t acc = tmem_base + a * TN;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(smem_u32(&bar_full[s]), ph, &abort_flag, p.status, kStatusTmaWaitTimeout)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + s * Cfg::kStageBytes;
+          const uint64_t a_desc = umma_desc_k_sw128(a_addr);
+          const uint64_t b_desc = umma_desc_k_sw128(a_addr + kWTileBytes);
+          if constexpr (kBS) {
+            const uint32_t sfa_s = a_addr + kWTileBytes + Cfg::kXTileBytes;
+            const uint32_t sfb_s = sfa_s + Cfg::kSfaBytes;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              tc_cp_sf(tmem_base + Cfg::kSfaCol + 4 * k, sf_desc(sfa_s + k * kSfTileBytes));
+              tc_cp_sf(tmem_base + Cfg::kSfbCol + 4 * k, sf_desc(sfb_s + k * kSfTileBytes));
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              tc_mma_nvfp4(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_base + Cfg::kSfaCol + 4 * k,
+                           tmem_base + Cfg::kSfbCol + 4 * k, (kb > 0 || k > 0) ? 1u : 0u);
+          } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              tc_mma_f8f6f4(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(smem_u32(&bar_empty[s]));
+        }
+        if (!ok) break;
+        tc_commit(smem_u32(&bar_acc_full[a]));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue warps ----------------
+    pdl_wait_prior();
+    const int lg = warp & 3;
+    constexpr int kChunk = 16;
+    float* up_s = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)) + kStages * Cfg::kStageBytes);
+    int tile_i = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_i) {
+      const int a = tile_i & 1;
+      const uint32_t ph = (tile_i >> 1) & 1;
+      const bool have = mbar_wait(smem_u32(&bar_acc_full[a]), ph, &abort_flag, p.status, kStatusAccumWaitTimeout);
+      if (lane == 0) epi_verdict[warp - 2] = (have && !*abortp) ? 1 : 0;
+      q_epi_bar_sync();
+      const bool go = epi_verdict[0] && epi_verdict[1] && epi_verdict[2] && epi_verdict[3];
+      q_epi_bar_sync();
+      if (!go) break;
+      tc_fence_after();
+      const int w_tile = tile / n_t_tiles;
+      const int n0 = w_tile * kTileN;
+      const int t0 = (tile % n_t_tiles) * TN;
+      const uint32_t lane_taddr = tmem_base + a * TN + (static_cast<uint32_t>(lg * 32) << 16);
+      const int n = n0 + lg * 32 + lane;
+      const float row_scale = kBS ? p.out_scale : ((n < p.N) ? p.w_scale[n] : 0.f);
+      auto load_acc = [&](int c, float* acc) {
+        uint32_t v[kChunk];
+        tmem_ld_x16(lane_taddr + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < kChunk; ++j) {
+          float sc = row_scale;
+          if constexpr (!kBS) sc *= (t0 + c + j < p.T) ? p.x_scale[t0 + c + j] : 0.f;
+          acc[j] = __uint_as_float(v[j]) * sc;
+        }
+      };
+      if constexpr (EPI == kEpiSwiglu) {
+        // rows are tile-interleaved: lane groups 0, 1 = gate rows, 2, 3 = the matching up rows
+        const bool is_up = lg >= 2;
+        const int r = (lg & 1) * 32 + lane;
+        const int col = w_tile * 64 + r;
+        for (int c = 0, ci = 0; c < TN; c += kChunk, ++ci) {
+          float* buf = up_s + (ci & 1) * (kChunk * 64);
+          float v[kChunk];
+          load_acc(c, v);
+          if (is_up) {
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) buf[j * 64 + r] = v[j];
+          }
+          q_epi_bar_sync();
+          if (!is_up && t0 + c < p.T) {
+#pragma unroll
+            for (int m = 0; m < kChunk / 2; ++m) {
+              float o2[2];
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const int j = 2 * m + h;
+                const float g = v[j];
+                o2[h] = g / (1.f + __expf(-g)) * buf[j * 64 + r];
+              }
+              const float send = (lane & 1) ? o2[0] : o2[1];
+              const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+              const int t = t0 + c + 2 * m + (lane & 1);
+              const int ce = col & ~1;
+              if (t < p.T && ce < p.N / 2) {
+                const uint32_t packed = (lane & 1) ? pack_bf16x2(recv, o2[1]) : pack_bf16x2(o2[0], recv);
+                *reinterpret_cast<uint32_t*>(p.out + static_cast<long long>(t) * p.ldo + ce) = packed;
+              }
+            }
+          }
+        }
+      } else {
+        for (int c = 0; c < TN; c += kChunk) {
+          if (t0 + c >= p.T) break;
+          float v[kChunk];
+          load_acc(c, v);
+          __nv_bfloat162 r2[kChunk / 2];
+          if constexpr (EPI == kEpiResidual) {
+#pragma unroll
+            for (int m = 0; m < kChunk / 2; ++m) {
+              const int t = t0 + c + 2 * m + (lane & 1);
+              const int ne = n & ~1;
+              r2[m] = (t < p.T && ne < p.N)
+                          ? *reinterpret_cast<const __nv_bfloat162*>(p.resid + static_cast<long long>(t) * p.ldr + ne)
+                          : __nv_bfloat162();
+            }
+          }
+#pragma unroll
+          for (int m = 0; m < kChunk / 2; ++m) {
+            const float a0 = v[2 * m], a1 = v[2 * m + 1];
+            const float send = (lane & 1) ? a0 : a1;
+            const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+            const int t = t0 + c + 2 * m + (lane & 1);
+            const int ne = n & ~1;
+            if (t < p.T && ne < p.N) {
+              float lo = (lane & 1) ? recv : a0;
+              float hi = (lane & 1) ? a1 : recv;
+              if constexpr (EPI == kEpiResidual) {
+                lo += __bfloat162float(r2[m].x);
+                hi += __bfloat162float(r2[m].y);
+              }
+              *reinterpret_cast<uint32_t*>(p.out + static_cast<long long>(t) * p.ldo + ne) = pack_bf16x2(lo, hi);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[a]));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+int q_sm_count();
+
+template <int QT, int EPI>
+cudaError_t launch_q_persist(const CUtensorMap& tw, const CUtensorMap& tx, const QParams& kp, int n_tiles,
+                             cudaStream_t stream, bool pdl) {
+  auto kern = gemm_q_persist_kernel<QT, EPI>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, QPersist<QT>::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_tiles < q_sm_count() ? n_tiles : q_sm_count());
+  cfg.blockDim = dim3(kQPersistThreads);
+  cfg.dynamicSmemBytes = QPersist<QT>::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, tw, tx, kp);
+}
+
+template <int QT>
+cudaError_t launch_q_persist_epi(int epi, const CUtensorMap& tw, const CUtensorMap& tx, const QParams& kp, int n_tiles,
+                                 cudaStream_t stream, bool pdl) {
+  switch (epi) {
+    case kEpiResidual: return launch_q_persist<QT, kEpiResidual>(tw, tx, kp, n_tiles, stream, pdl);
+    case kEpiSwiglu: return launch_q_persist<QT, kEpiSwiglu>(tw, tx, kp, n_tiles, stream, pdl);
+    default: return launch_q_persist<QT, kEpiStore>(tw, tx, kp, n_tiles, stream, pdl);
+  }
+}
+
 template <int TN, int QT, int EPI, bool DEEP>
 cudaError_t launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const QParams& kp, dim3 grid, cudaStream_t stream,
                        bool pdl) {
@@ -698,6 +1029,21 @@ const char* gemm_quant(const QGemmArgs& a) {
   }
   CUtensorMap tw, tx;
   if (!cached_tmap(&tw, a.w, a.N, k_bytes, a.ldw, 64)) return "gemm_quant: weight tensor map rejected";
+  // prefill-sized problems with more tiles than SMs: persistent kernel (NFB_GEMM_PERSISTENT=0 switches it off)
+  static const bool persistent_enabled = [] {
+    const char* e = getenv("NFB_GEMM_PERSISTENT");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  if (persistent_enabled && tn == 256 && splits == 1 && !push) {
+    const int ptn = bs ? 128 : 256;
+    const long long n_tiles = static_cast<long long>((kp.N + kTileN - 1) / kTileN) * ((kp.T + ptn - 1) / ptn);
+    if (n_tiles > q_sm_count()) {
+      if (!cached_tmap(&tx, a.x, a.T, k_bytes, a.ldx, ptn)) return "gemm_quant: activation tensor map rejected";
+      cudaError_t e = bs ? launch_q_persist_epi<kQNvfp4>(a.epi, tw, tx, kp, static_cast<int>(n_tiles), a.stream, a.pdl)
+                         : launch_q_persist_epi<kQFp8Row>(a.epi, tw, tx, kp, static_cast<int>(n_tiles), a.stream, a.pdl);
+      return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+    }
+  }
   if (!cached_tmap(&tx, a.x, a.T, k_bytes, a.ldx, tn)) return "gemm_quant: activation tensor map rejected";
   dim3 grid((kp.N + kTileN - 1) / kTileN, (kp.T + tn - 1) / tn, splits);
   cudaError_t e = bs ? launch_epi<kQNvfp4>(a.epi, tn, tw, tx, kp, grid, a.stream, a.pdl)

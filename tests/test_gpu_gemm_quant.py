@@ -47,7 +47,9 @@ def test_activation_quantisers(T):
 @pytest.mark.parametrize("T,N,K,epi,splits", [
     (1, 256, 512, EPI_STORE, 1), (20, 384, 1024, EPI_RESIDUAL, 1), (32, 512, 2048, EPI_SWIGLU, 1),
     (64, 256, 2048, EPI_STORE, 4), (100, 640, 768, EPI_RESIDUAL, 1), (130, 256, 512, EPI_SWIGLU, 1),
-    (300, 384, 1024, EPI_STORE, 1), (16, 5120, 5120, EPI_RESIDUAL, 3)])
+    (300, 384, 1024, EPI_STORE, 1), (16, 5120, 5120, EPI_RESIDUAL, 3),
+    # more tiles than SMs at prefill size: the persistent kernel (overlapped epilogue), ragged T
+    (600, 8192, 768, EPI_STORE, 1), (777, 8192, 512, EPI_RESIDUAL, 1), (1000, 9984, 512, EPI_SWIGLU, 1)])
 def test_gemm_quant_matches_oracle(qt, T, N, K, epi, splits):
     ops = load_native()
     status = StatusWord("cuda")
