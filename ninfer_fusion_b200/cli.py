@@ -293,12 +293,21 @@ def cmd_convert(args) -> int:
         write_safetensors(args.out, weights_to_hf(cfg, weights, vision), {"format": "pt"})
         print(f"wrote {args.out}", file=sys.stderr)
         return 0
-    if args.model:
+    is_gguf = os.path.isfile(args.src) and args.src.lower().endswith(".gguf")
+    if is_gguf:
+        from .convert.gguf import GgufSource, config_from_gguf
+        src = GgufSource(args.src)
+        cfg = get_config(args.model) if args.model else config_from_gguf(
+            src.file.kv, name=os.path.splitext(os.path.basename(args.src))[0])
+        if src.unmapped:
+            print(f"convert: {len(src.unmapped)} GGUF tensors have no role in this family, e.g. {src.unmapped[:3]}", file=sys.stderr)
+    elif args.model:
         cfg = get_config(args.model)
     else:
         with open(os.path.join(args.src, "config.json"), encoding="utf-8") as f:
             cfg = config_from_hf(json.load(f), name=os.path.basename(os.path.normpath(args.src)))
-    src = SafetensorsSource(args.src)
+    if not is_gguf:
+        src = SafetensorsSource(args.src)
     vision = None
     if args.vision or (args.vision is None and "model.visual.pos_embed.weight" in src):
         n_blocks = 1 + max(int(n.split(".")[3]) for n in src.names() if n.startswith("model.visual.blocks."))
@@ -391,7 +400,7 @@ def main(argv=None) -> int:
     m.add_argument("--seed", type=int, default=0)
     m.add_argument("--out", required=True)
     m.set_defaults(fn=cmd_make_artifact)
-    c = sub.add_parser("convert", help="Hugging Face safetensors checkpoint -> .ninfer artifact (or back with --to-hf)")
+    c = sub.add_parser("convert", help="Hugging Face safetensors checkpoint or GGUF file -> .ninfer artifact (or back with --to-hf)")
     c.add_argument("src", help="checkpoint directory / .safetensors file (or an artifact with --to-hf)")
     c.add_argument("--out", required=True)
     c.add_argument("--model", default="", help="registered geometry; default: derived from the checkpoint's config.json")
