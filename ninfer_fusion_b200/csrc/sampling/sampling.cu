@@ -168,20 +168,52 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const SampleParams p) 
     const uint4 r = philox(make_uint4(pos, purpose, 0u, 0u), key);
     return (static_cast<float>(r.x >> 8) + 0.5f) * (1.f / 16777216.f);
   };
+  if (p.out_dist_ids != nullptr && p.out_dist_probs != nullptr) {
+    for (int k = 0; k < p.dist_out_k; ++k) {
+      p.out_dist_ids[static_cast<long long>(row_id) * p.dist_out_k + k] = k < keep ? top_i[k] : -1;
+      p.out_dist_probs[static_cast<long long>(row_id) * p.dist_out_k + k] = k < keep ? prob[k] / ksum : 0.f;
+    }
+  }
   unsigned int purpose = p.purpose;
   if (draft >= 0) {
     int kd = -1;
     for (int k = 0; k < keep; ++k)
       if (top_i[k] == draft) kd = k;
     const float pd = kd >= 0 ? prob[kd] / ksum : 0.f;
-    const bool ok = kd >= 0 && (keep == 1 || uniform(1u) < pd);
+    const bool have_q = p.draft_dist_ids != nullptr && p.draft_dist_probs != nullptr && p.dist_k > 0;
+    const int* q_ids = have_q ? p.draft_dist_ids + static_cast<long long>(row_id) * p.dist_k : nullptr;
+    const float* q_pr = have_q ? p.draft_dist_probs + static_cast<long long>(row_id) * p.dist_k : nullptr;
+    auto q_of = [&](int token) {
+      float q = 0.f;
+      for (int j = 0; j < p.dist_k; ++j)
+        if (q_ids[j] == token) q = q_pr[j];
+      return q;
+    };
+    float accept_p = pd;                        // deterministic draft: q(d) = 1
+    if (have_q) {
+      const float qd = q_of(draft);
+      accept_p = qd > 0.f ? fminf(1.f, pd / qd) : (pd > 0.f ? 1.f : 0.f);
+    }
+    const bool ok = kd >= 0 && ((!have_q && keep == 1) || uniform(1u) < accept_p);
     if (p.accepted != nullptr) p.accepted[row_id] = ok ? 1 : 0;
     if (ok) {
       p.out[row_id] = draft;
       if (p.out_prob != nullptr) p.out_prob[row_id] = pd;
       return;
     }
-    if (kd >= 0) {   // residual distribution: the draft's mass is removed, the rest renormalised
+    if (have_q) {
+      // residual max(p - q, 0), renormalised; if p <= q everywhere (p == q) the residual is empty and p itself is used
+      float rsum = 0.f;
+      float res[kMaxTopK];
+      for (int k = 0; k < keep; ++k) {
+        res[k] = fmaxf(prob[k] / ksum - q_of(top_i[k]), 0.f);
+        rsum += res[k];
+      }
+      if (rsum > 1e-9f) {
+        for (int k = 0; k < keep; ++k) prob[k] = res[k];
+        ksum = rsum;
+      }
+    } else if (kd >= 0) {   // residual distribution: the draft's mass is removed, the rest renormalised
       ksum -= prob[kd];
       prob[kd] = 0.f;
     }

@@ -32,6 +32,18 @@ struct SampleParams {
   // (stream 2), so the emitted token is distributed exactly as p.  Greedy rows accept iff the draft is the arg-max.
   const int* draft_ids = nullptr;
   int* accepted = nullptr;      // [T] 1 = draft accepted (out = draft), 0 = rejected (out = replacement)
+  // Stochastic drafts (optional, with draft_ids): the drafter's own processed distribution q of each row as
+  // dist_k (id, probability) pairs, probabilities summing to 1 over the ids with id >= 0.  The draft is then accepted
+  // with probability min(1, p(d) / q(d)) and a rejection resamples from max(p - q, 0) renormalised -- speculative
+  // sampling in its general form; without q the draft counts as deterministic (q = 1 at the draft).
+  const int* draft_dist_ids = nullptr;     // [T, dist_k]
+  const float* draft_dist_probs = nullptr; // [T, dist_k]
+  int dist_k = 0;
+  // Optional outputs: the row's final distribution (kept candidates, renormalised) as dist_out_k (id, prob) pairs,
+  // padded with id = -1: what a drafter hands to the verifier as its q.
+  int* out_dist_ids = nullptr;             // [T, dist_out_k]
+  float* out_dist_probs = nullptr;         // [T, dist_out_k]
+  int dist_out_k = 0;
 };
 const char* sample_rows(const SampleParams& p, cudaStream_t stream);
 

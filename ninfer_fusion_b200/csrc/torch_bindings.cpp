@@ -422,7 +422,8 @@ void argmax_rows(const Tensor& logits, const Tensor& out, bool pdl) {
 
 void sample_rows(const Tensor& logits, OptT temperature, OptT top_k, OptT top_p, OptT min_p, OptT presence,
                  OptT frequency, OptT token_counts, OptT seeds, OptT positions, int64_t purpose, const Tensor& out,
-                 OptT out_prob, OptT draft_ids, OptT accepted) {
+                 OptT out_prob, OptT draft_ids, OptT accepted, OptT draft_dist_ids, OptT draft_dist_probs,
+                 OptT out_dist_ids, OptT out_dist_probs) {
   need(logits, at::kBFloat16, "logits"); need_rows(logits, "logits"); need(out, at::kInt, "out");
   c10::cuda::CUDAGuard guard(logits.device());
   nfb::SampleParams p = {};
@@ -444,6 +445,25 @@ void sample_rows(const Tensor& logits, OptT temperature, OptT top_k, OptT top_p,
     need(*accepted, at::kInt, "accepted");
     TORCH_CHECK(accepted->numel() >= p.T, "accepted: one entry per row");
     p.accepted = static_cast<int*>(accepted->data_ptr());
+  }
+  if (draft_dist_ids.has_value() && draft_dist_ids->defined()) {
+    TORCH_CHECK(draft_dist_probs.has_value() && draft_dist_probs->defined() && p.draft_ids != nullptr,
+                "draft distribution needs ids, probabilities and draft_ids");
+    need(*draft_dist_ids, at::kInt, "draft_dist_ids"); need(*draft_dist_probs, at::kFloat, "draft_dist_probs");
+    TORCH_CHECK(draft_dist_ids->is_contiguous() && draft_dist_probs->is_contiguous() && draft_dist_ids->dim() == 2 &&
+                draft_dist_ids->size(0) >= p.T && draft_dist_probs->sizes() == draft_dist_ids->sizes(), "draft distribution shapes");
+    p.draft_dist_ids = static_cast<const int*>(draft_dist_ids->data_ptr());
+    p.draft_dist_probs = static_cast<const float*>(draft_dist_probs->data_ptr());
+    p.dist_k = static_cast<int>(draft_dist_ids->size(1));
+  }
+  if (out_dist_ids.has_value() && out_dist_ids->defined()) {
+    TORCH_CHECK(out_dist_probs.has_value() && out_dist_probs->defined(), "out_dist needs ids and probabilities");
+    need(*out_dist_ids, at::kInt, "out_dist_ids"); need(*out_dist_probs, at::kFloat, "out_dist_probs");
+    TORCH_CHECK(out_dist_ids->is_contiguous() && out_dist_probs->is_contiguous() && out_dist_ids->dim() == 2 &&
+                out_dist_ids->size(0) >= p.T && out_dist_probs->sizes() == out_dist_ids->sizes(), "out distribution shapes");
+    p.out_dist_ids = static_cast<int*>(out_dist_ids->data_ptr());
+    p.out_dist_probs = static_cast<float*>(out_dist_probs->data_ptr());
+    p.dist_out_k = static_cast<int>(out_dist_ids->size(1));
   }
   chk(nfb::sample_rows(p, cur_stream()));
 }
@@ -661,7 +681,7 @@ TORCH_LIBRARY(nfb200, m) {
   m.def("gdn_prefill_trace(bool enable) -> Tensor", &gdn_prefill_trace);
   m.def("kv_move_rows(Tensor block_table, Tensor table_row, Tensor src_pos, Tensor dst_pos, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int n_kv_heads, int head_dim, int format, int group) -> ()", &kv_move_rows);
   m.def("argmax_rows(Tensor logits, Tensor out, bool pdl) -> ()", &argmax_rows);
-  m.def("sample_rows(Tensor logits, Tensor? temperature, Tensor? top_k, Tensor? top_p, Tensor? min_p, Tensor? presence, Tensor? frequency, Tensor? token_counts, Tensor? seeds, Tensor? positions, int purpose, Tensor out, Tensor? out_prob, Tensor? draft_ids=None, Tensor? accepted=None) -> ()", &sample_rows);
+  m.def("sample_rows(Tensor logits, Tensor? temperature, Tensor? top_k, Tensor? top_p, Tensor? min_p, Tensor? presence, Tensor? frequency, Tensor? token_counts, Tensor? seeds, Tensor? positions, int purpose, Tensor out, Tensor? out_prob, Tensor? draft_ids=None, Tensor? accepted=None, Tensor? draft_dist_ids=None, Tensor? draft_dist_probs=None, Tensor? out_dist_ids=None, Tensor? out_dist_probs=None) -> ()", &sample_rows);
   m.def("accept_greedy_chain(Tensor target_ids, Tensor draft_ids, Tensor n_accepted, Tensor out_tokens) -> ()", &accept_greedy_chain);
   m.def("accept_greedy_tree(Tensor target_ids, Tensor node_tok, Tensor parent, int max_depth, Tensor n_accepted, Tensor out_tokens, Tensor out_nodes) -> ()", &accept_greedy_tree);
 }

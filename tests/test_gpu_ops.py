@@ -397,3 +397,45 @@ def test_stochastic_draft_verification_preserves_the_target_distribution(ops):
     for b in range(B):
         first_rej = next((j for j in range(K) if okm[b, j] == 0), K)
         assert int(n_acc[b]) == first_rej and int(out_tok[b, first_rej]) == int(tok.view(B, K + 1)[b, first_rej])
+
+
+def test_speculative_sampling_with_a_stochastic_drafter(ops):
+    """General speculative sampling: the drafter samples d ~ q and hands over q; the verifier accepts with
+    min(1, p(d) / q(d)) and resamples from max(p - q, 0).  The emitted token must follow p, the acceptance rate must be
+    sum(min(p, q))."""
+    torch.manual_seed(1)
+    V, n, k = 64, 8000, 8
+    t_logits = (torch.randn(V) * 1.5).to(torch.bfloat16)
+    d_logits = (t_logits.float() + torch.randn(V) * 1.0).to(torch.bfloat16)     # a drafter that is close, not equal
+    tl = t_logits[None].repeat(n, 1).contiguous().cuda()
+    dl = d_logits[None].repeat(n, 1).contiguous().cuda()
+    temp = torch.ones(n, device="cuda")
+    topk = torch.full((n,), k, dtype=torch.int32, device="cuda")
+    seeds = torch.arange(n, dtype=torch.int64, device="cuda")
+    pos = torch.full((n,), 5, dtype=torch.int32, device="cuda")
+    # drafter: sample d ~ q (random stream 3) and export q
+    d_tok = torch.empty(n, dtype=torch.int32, device="cuda")
+    q_ids = torch.empty((n, 32), dtype=torch.int32, device="cuda")
+    q_pr = torch.empty((n, 32), dtype=torch.float32, device="cuda")
+    ops.sample_rows(dl, temp, topk, None, None, None, None, None, seeds, pos, 3, d_tok, None, None, None, None, None, q_ids, q_pr)
+    assert bool((q_ids[:, :k] >= 0).all()) and bool((q_ids[:, k:] == -1).all())
+    assert torch.allclose(q_pr.sum(1), torch.ones(n, device="cuda"), atol=1e-5)
+    # verifier
+    out = torch.empty(n, dtype=torch.int32, device="cuda")
+    acc = torch.empty(n, dtype=torch.int32, device="cuda")
+    ops.sample_rows(tl, temp, topk, None, None, None, None, None, seeds, pos, 0, out, None, d_tok, acc, q_ids, q_pr)
+    tv, ti = torch.sort(t_logits.float(), descending=True, stable=True)
+    dv, di = torch.sort(d_logits.float(), descending=True, stable=True)
+    p = torch.zeros(V)
+    q = torch.zeros(V)
+    p[ti[:k]] = torch.softmax(tv[:k], 0)
+    q[di[:k]] = torch.softmax(dv[:k], 0)
+    want_rate = torch.minimum(p, q).sum().item()
+    assert abs(acc.float().mean().item() - want_rate) < 0.02
+    emp = torch.bincount(out.cpu().long(), minlength=V).float() / n
+    assert (emp - p).abs().max().item() < 0.02
+    assert bool((out[acc.bool()] == d_tok[acc.bool()]).all())
+    # q == p: every draft is accepted
+    ops.sample_rows(tl, temp, topk, None, None, None, None, None, seeds, pos, 3, d_tok, None, None, None, None, None, q_ids, q_pr)
+    ops.sample_rows(tl, temp, topk, None, None, None, None, None, seeds, pos, 0, out, None, d_tok, acc, q_ids, q_pr)
+    assert acc.sum().item() == n and torch.equal(out, d_tok)
