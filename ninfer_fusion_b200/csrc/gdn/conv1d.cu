@@ -64,6 +64,79 @@ __global__ void __launch_bounds__(128) conv1d_silu_kernel(const ConvParams p) {
   *reinterpret_cast<uint32_t*>(p.out + static_cast<long long>(t) * p.C + c) = pack_bf16x2(a0, a1);
 }
 
+// Prefill variant: one thread owns 8 channels of a run of 16 consecutive tokens and slides the three previous
+// inputs through registers, so every input row is read once (16-byte loads) instead of four times, and the grid is
+// T / 16 x C / 1024 CTAs instead of T x C / 256.  Sequence boundaries inside a run reload the window from the new
+// sequence's history.  (2048 tokens x 10240 channels: 97 us with the per-token kernel against 13 us of traffic.)
+constexpr int kConvRun = 16;
+
+__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float* v) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __bfloat162float(h[i].x);
+    v[2 * i + 1] = __bfloat162float(h[i].y);
+  }
+}
+
+__global__ void __launch_bounds__(128) conv1d_silu_rows_kernel(const ConvParams p) {
+  pdl_launch_next();
+  pdl_wait_prior();
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (c >= p.C) return;
+  const int t0 = blockIdx.x * kConvRun, t1 = min(p.T, t0 + kConvRun);
+  float w[8][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {   // 8 channels x 4 taps = 64 bytes
+    float v[8];
+    ld8(p.w + static_cast<long long>(c) * 4 + i * 8, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) w[(i * 8 + j) >> 2][(i * 8 + j) & 3] = v[j];
+  }
+  float win[3][8];
+  int seq = -2;
+  for (int t = t0; t < t1; ++t) {
+    const int s = p.token_seq[t];
+    if (s < 0) {
+      seq = -2;
+      continue;
+    }
+    if (s != seq) {   // first token of this run, or a new sequence starts here
+      seq = s;
+      const int start = p.cu_seqlens[s];
+      const int slot = p.state_slot[s];
+#pragma unroll
+      for (int j = 0; j < 3; ++j) {
+        const int tau = t - 3 + j;
+        if (tau >= start) ld8(p.x + static_cast<long long>(tau) * p.ld_x + p.c_off + c, win[j]);
+        else ld8(p.conv_state + (static_cast<long long>(slot) * 3 + (tau - start + 3)) * p.C + c, win[j]);
+      }
+    }
+    float cur[8];
+    ld8(p.x + static_cast<long long>(t) * p.ld_x + p.c_off + c, cur);
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float a[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int ch = 2 * i + h;
+        const float v = w[ch][0] * win[0][ch] + w[ch][1] * win[1][ch] + w[ch][2] * win[2][ch] + w[ch][3] * cur[ch];
+        a[h] = v / (1.f + __expf(-v));
+      }
+      o[i] = pack_bf16x2(a[0], a[1]);
+    }
+    *reinterpret_cast<uint4*>(p.out + static_cast<long long>(t) * p.C + c) = make_uint4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) {
+      win[0][ch] = win[1][ch];
+      win[1][ch] = win[2][ch];
+      win[2][ch] = cur[ch];
+    }
+  }
+}
+
 __global__ void __launch_bounds__(128) conv1d_state_kernel(const ConvParams p) {
   pdl_launch_next();
   pdl_wait_prior();
@@ -134,7 +207,16 @@ const char* causal_conv1d_silu(const ConvParams& p, cudaStream_t stream, bool pd
     return e1 == cudaSuccess ? nullptr : cudaGetErrorString(e1);
   }
   cudaError_t e = cudaSuccess;
-  if (!p.state_only) e = cudaLaunchKernelEx(&cfg, conv1d_silu_kernel, p);
+  const bool rows_ok = p.parent == nullptr && p.T >= 64 && p.C % 8 == 0 && p.c_off % 8 == 0 && p.ld_x % 8 == 0 &&
+                       ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.out) |
+                         reinterpret_cast<uintptr_t>(p.conv_state) | reinterpret_cast<uintptr_t>(p.w)) & 15) == 0;
+  if (!p.state_only && rows_ok) {
+    cfg.gridDim = dim3((p.T + kConvRun - 1) / kConvRun, (p.C / 8 + 127) / 128);
+    e = cudaLaunchKernelEx(&cfg, conv1d_silu_rows_kernel, p);
+    cfg.gridDim = dim3(p.T, (p.C / 2 + 127) / 128);
+  } else if (!p.state_only) {
+    e = cudaLaunchKernelEx(&cfg, conv1d_silu_kernel, p);
+  }
   if (e != cudaSuccess) return cudaGetErrorString(e);
   if (p.update_state) {
     cfg.gridDim = dim3(p.n_seq, (p.C / 2 + 127) / 128);
