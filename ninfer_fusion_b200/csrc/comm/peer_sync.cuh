@@ -18,6 +18,12 @@ __device__ __forceinline__ void red_release_sys_add(unsigned int* p, uint32_t v)
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// Same counter when producer and consumer are known to be on one GPU: device scope is enough and far cheaper when
+// thousands of CTAs signal one word.
+__device__ __forceinline__ void red_release_gpu_add(unsigned int* p, uint32_t v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 // Wait until *flag - target >= 0 in wrap-around arithmetic.  Returns false on time-out.
 __device__ __forceinline__ bool wait_counter(const unsigned int* flag, uint32_t target, int* status) {
   for (uint32_t i = 0; i < kPeerPollLimit; ++i) {

@@ -268,9 +268,12 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_fp8_kernel(const __grid_con
         }
         const int t = threadIdx.x - 64;   // 0..127 over the four epilogue warps
         if (t < rows) atomicAdd(&src_cnt[meta_s[t] >> 24], 1);
-        __threadfence_system();
+        if (p.world == 1) __threadfence(); else __threadfence_system();
         epi_bar_sync();
-        if (t < p.world && src_cnt[t] > 0) red_release_sys_add(p.peer_ret_flag[t], static_cast<uint32_t>(src_cnt[t]));
+        if (t < p.world && src_cnt[t] > 0) {
+          if (p.world == 1) red_release_gpu_add(p.peer_ret_flag[t], static_cast<uint32_t>(src_cnt[t]));
+          else red_release_sys_add(p.peer_ret_flag[t], static_cast<uint32_t>(src_cnt[t]));
+        }
       }
     }
   }

@@ -93,9 +93,12 @@ __global__ void __launch_bounds__(kPlanThreads) moe_plan_kernel(const MoePlanPar
     const int h = p.hist[e];
     for (int r = 0; r < W; ++r) p.peer_counts[r][p.rank * E + e] = h;
   }
-  __threadfence_system();
+  if (W == 1) __threadfence(); else __threadfence_system();   // one GPU: device scope is enough (and much cheaper)
   __syncthreads();
-  if (tid < W) red_release_sys_add(p.peer_count_flag[tid], 1u);
+  if (tid < W) {
+    if (W == 1) red_release_gpu_add(p.peer_count_flag[tid], 1u);
+    else red_release_sys_add(p.peer_count_flag[tid], 1u);
+  }
   if (tid == 0) ok_s = wait_counter(p.my_count_flag, (c + 1u) * static_cast<uint32_t>(W), p.status) ? 1 : 0;
   __syncthreads();
   const bool ok = ok_s != 0;
@@ -192,9 +195,12 @@ __global__ void __launch_bounds__(kPushThreads) moe_push_kernel(const MoePushPar
       if (lane == 0) p.peer_recv_meta[dest][slot] = (p.rank << 24) | a;
     }
   }
-  __threadfence_system();
+  if (p.world == 1) __threadfence(); else __threadfence_system();
   __syncthreads();
-  if (threadIdx.x < p.world) red_release_sys_add(p.peer_arrive_flag[threadIdx.x], 1u);
+  if (threadIdx.x < p.world) {
+    if (p.world == 1) red_release_gpu_add(p.peer_arrive_flag[threadIdx.x], 1u);
+    else red_release_sys_add(p.peer_arrive_flag[threadIdx.x], 1u);
+  }
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     const uint32_t target = p.state->call_idx * static_cast<uint32_t>(p.world) * gridDim.x;
     wait_counter(p.my_arrive_flag, target, p.status);
