@@ -395,18 +395,19 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
         }
       }
       if constexpr (EPI == kEpiPushPartial) {
-        // publish: every thread's peer stores are ordered before the owner's arrival counter
-        __threadfence_system();
+        // publish: the block barrier orders every thread's peer stores before the signalling thread, whose
+        // system-scope fence + release is cumulative over them (one fence instead of 128)
         __syncthreads();
         if (threadIdx.x == 0) {
+          __threadfence_system();
           unsigned int* flag = p.peer_flag[n0 / p.slice_cols];
           asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(flag) : "memory");
         }
       }
       if constexpr (EPI == kEpiPushAll) {
-        __threadfence_system();
         __syncthreads();
         if (threadIdx.x < p.world) {
+          __threadfence_system();
           unsigned int* flag = p.peer_flag[threadIdx.x];
           asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(flag) : "memory");
         }

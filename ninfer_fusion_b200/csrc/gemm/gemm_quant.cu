@@ -371,14 +371,19 @@ __global__ void __launch_bounds__(128) gemm_q_kernel(const __grid_constant__ CUt
           }
         }
       }
-      __threadfence_system();
+      // the block barrier orders every thread's peer stores before the signalling threads, whose system-scope
+      // fence + release is cumulative over them
       __syncthreads();
       if constexpr (EPI == kEpiPushAll) {
-        if (threadIdx.x < p.world)
+        if (threadIdx.x < p.world) {
+          __threadfence_system();
           asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.peer_flag[threadIdx.x]) : "memory");
+        }
       } else {
-        if (threadIdx.x == 0)
+        if (threadIdx.x == 0) {
+          __threadfence_system();
           asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.peer_flag[n0 / p.slice_cols]) : "memory");
+        }
       }
     } else {
       for (int c = 0; c < TN; c += kChunk) {

@@ -251,11 +251,17 @@ __global__ void __launch_bounds__(128) moe_gemm_kernel(const __grid_constant__ C
       if (threadIdx.x < rows) atomicAdd(&src_cnt[meta_s[threadIdx.x] >> 24], 1);
       if (TN > 128 && threadIdx.x + 128 < rows) atomicAdd(&src_cnt[meta_s[threadIdx.x + 128] >> 24], 1);
       // one GPU: device-scope fence and counter (a prefill chunk has thousands of tiles signalling one word)
-      if (p.world == 1) __threadfence(); else __threadfence_system();
+      // (several ranks: the block barrier orders all stores before the signalling threads, whose system-scope fence +
+      // release is cumulative over them)
+      if (p.world == 1) __threadfence();
       __syncthreads();
       if (threadIdx.x < p.world && src_cnt[threadIdx.x] > 0) {
-        if (p.world == 1) red_release_gpu_add(p.peer_ret_flag[threadIdx.x], static_cast<uint32_t>(src_cnt[threadIdx.x]));
-        else red_release_sys_add(p.peer_ret_flag[threadIdx.x], static_cast<uint32_t>(src_cnt[threadIdx.x]));
+        if (p.world == 1) {
+          red_release_gpu_add(p.peer_ret_flag[threadIdx.x], static_cast<uint32_t>(src_cnt[threadIdx.x]));
+        } else {
+          __threadfence_system();
+          red_release_sys_add(p.peer_ret_flag[threadIdx.x], static_cast<uint32_t>(src_cnt[threadIdx.x]));
+        }
       }
     }
   }

@@ -195,11 +195,15 @@ __global__ void __launch_bounds__(kPushThreads) moe_push_kernel(const MoePushPar
       if (lane == 0) p.peer_recv_meta[dest][slot] = (p.rank << 24) | a;
     }
   }
-  if (p.world == 1) __threadfence(); else __threadfence_system();
+  if (p.world == 1) __threadfence();
   __syncthreads();
   if (threadIdx.x < p.world) {
-    if (p.world == 1) red_release_gpu_add(p.peer_arrive_flag[threadIdx.x], 1u);
-    else red_release_sys_add(p.peer_arrive_flag[threadIdx.x], 1u);
+    if (p.world == 1) {
+      red_release_gpu_add(p.peer_arrive_flag[threadIdx.x], 1u);
+    } else {
+      __threadfence_system();   // cumulative over the stores the block barrier ordered before this thread
+      red_release_sys_add(p.peer_arrive_flag[threadIdx.x], 1u);
+    }
   }
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     const uint32_t target = p.state->call_idx * static_cast<uint32_t>(p.world) * gridDim.x;
