@@ -19,11 +19,13 @@ from typing import Dict, Optional, Tuple
 
 import torch
 
+from .artifact import layouts as L
 from .artifact.container import ArtifactReader, ArtifactWriter
 from .frontend.chat import BUILTIN_TEMPLATE, renderer_for
 from .frontend.tokenizer import Tokenizer
 from .models.config import ModelConfig, get_config
-from .models.weights import quantize_weights, random_weights, total_bytes
+from .models.weights import QUANT_LEAVES, quantize_weights, random_weights, total_bytes
+from .ops.groupint import GroupIntWeight
 from .runtime.engine import Engine, RequestOptions
 from .runtime.program import ReferenceProgram, SamplingParams
 
@@ -40,7 +42,9 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--layers", type=int, default=0, help="shrink the geometry to this many layers (debug)")
     ap.add_argument("--tokenizer", help="tokenizer.json (overrides the artifact's embedded one)")
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
-    ap.add_argument("--weights", default="bf16", choices=["bf16", "fp8", "nvfp4"], help="matmul weight format on the device")
+    ap.add_argument("--weights", default="bf16", choices=["bf16", "fp8", "nvfp4", "q4", "q5", "q6", "w8", "stored"],
+                    help="matmul weight format on the device; q4/q5/q6/w8 keep groupwise-int codes and dequantise in the "
+                         "decode kernels; 'stored' keeps an artifact's groupwise-int tensors exactly as encoded")
     ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8", "fp8h", "int8", "nvfp4"],
                     help="KV cache codec (fp8h = fp8 per-row with K in the Hadamard frame)")
     ap.add_argument("--kv-layer-spec", default="", help="per-layer KV storage, e.g. 'all:fp8' or '0-3:bf16,4-15:nvfp4'")
@@ -67,14 +71,23 @@ def load_model(args) -> Tuple[ModelConfig, Dict[str, object], Tokenizer, str]:
         with ArtifactReader(args.artifact) as rd:
             model_id, weights_id = rd.identity
             cfg = get_config(model_id)
-            weights = {name: rd.tensor(name) for name in rd.tensors()}
+            weights = {}
+            for name in rd.tensors():
+                o = rd.by_name[name]
+                if (args.weights == "stored" and args.device != "cpu" and o.format in L.GROUP_FORMATS and len(o.shape) == 2
+                        and name.rsplit("/", 1)[-1] in QUANT_LEAVES and "/moe/" not in name):
+                    # zero-copy in format: the encoded object goes to the device as it is
+                    raw = torch.frombuffer(bytearray(rd.payload(name)), dtype=torch.uint8)
+                    weights[name] = GroupIntWeight(o.format, raw.to(args.device), o.shape)
+                else:
+                    weights[name] = rd.tensor(name)
             if "tokenizer.json" in rd.by_name:
                 tok = Tokenizer.from_json(rd.resource("tokenizer.json"))
             if "chat_template.jinja" in rd.by_name:
                 template = rd.resource("chat_template.jinja").decode("utf-8")
-        weights = {k: (v.to(torch.bfloat16) if v.dtype == torch.float32 and not k.endswith(("A_log", "dt_bias")) else v)
-                   for k, v in weights.items()}
-        weights = {k: v.to(args.device) for k, v in weights.items()}
+        weights = {k: (v.to(torch.bfloat16) if torch.is_tensor(v) and v.dtype == torch.float32
+                       and not k.endswith(("A_log", "dt_bias")) else v) for k, v in weights.items()}
+        weights = {k: (v.to(args.device) if torch.is_tensor(v) else v) for k, v in weights.items()}
         name = f"{model_id}:{weights_id}"
     else:
         cfg = get_config(args.model)
@@ -84,7 +97,7 @@ def load_model(args) -> Tuple[ModelConfig, Dict[str, object], Tokenizer, str]:
                                  with_mtp=getattr(args, "spec", "none") == "mtp")
         name = f"{cfg.name}:random-init"
     renderer_for(template, allow_unknown=args.allow_unknown_template)  # refuses an unknown template early
-    if args.weights != "bf16":
+    if args.weights not in ("bf16", "stored"):
         if args.device == "cpu":
             raise SystemExit("--weights fp8/nvfp4 needs a GPU (the CPU program runs the fp32 oracle)")
         weights = quantize_weights(weights, args.weights)

@@ -191,6 +191,9 @@ class LaunchCounter:
         return fn
 
 
+from ..ops.groupint import GroupIntWeight  # noqa: E402  (encoded Q4/Q5/Q6/W8 weight, streamed as stored)
+
+
 class QuantWeight:
     """A matmul weight held as quantised planes (ops.quant): fp8 row-scale or nvfp4 block-scaled."""
     __slots__ = ("qtype", "codes", "scale", "divisor", "shape")
@@ -317,6 +320,14 @@ class HybridModel:
         if isinstance(w, QuantWeight):
             self._gemm_quant(x, w, out, epi, resid)
             return
+        if isinstance(w, GroupIntWeight):
+            # groupwise-int codes are streamed as stored for decode-sized token counts (in-register dequant);
+            # prefill chunks and the SwiGLU epilogue take the tcgen05 GEMM on a bf16 copy decoded once
+            if x.shape[0] <= 32 and epi in (EPI_STORE, EPI_RESIDUAL) and w.usable_by_kernel():
+                self.ops.groupint_linear(x, w.payload, w.fmt_id, w.shape[0], w.shape[1], out,
+                                         resid if epi == EPI_RESIDUAL else None)
+                return
+            w = w.dense()
         # in-cluster split-K when the output tiles alone cannot fill the GPU (decode, sharded weights)
         splits = int(self.ops.gemm_pick_splits(x.shape[0], w.shape[0], w.shape[1], epi)) if self.cluster_splitk else 1
         self.ops.gemm_bf16(x, w, out, epi, resid, None, None, splits, self.status.tensor, self.pdl)

@@ -96,6 +96,7 @@ def random_weights(cfg: ModelConfig, device, seed: int = 0, with_mtp: bool = Fal
 
 
 QUANT_LEAVES = ("in_proj", "o_proj", "out_proj", "gate_up", "down", "lm_head")
+GROUPINT_FORMATS = ("q4", "q5", "q6", "w8")   # groupwise-int codes kept as the artifact stores them (ops.groupint)
 
 
 def quantize_tensor(name: str, t: torch.Tensor, weight_format: str):
@@ -107,6 +108,9 @@ def quantize_tensor(name: str, t: torch.Tensor, weight_format: str):
     if weight_format == "bf16" or t.dim() != 2 or leaf not in QUANT_LEAVES or "/moe/" in name:
         return t
     N, K = t.shape
+    if weight_format in GROUPINT_FORMATS:
+        from ..ops.groupint import GroupIntWeight
+        return GroupIntWeight.from_dense(t, weight_format)
     w = Q.interleave_gate_up(t) if leaf == "gate_up" else t
     if weight_format == "fp8":
         codes, scale = Q.quantize_fp8_row(w)
@@ -137,6 +141,9 @@ def dequantize_weights(weights: Dict[str, object]) -> Dict[str, torch.Tensor]:
             out[name] = t
             continue
         N, K = t.shape
+        if t.qtype == 3:   # ops.groupint.GroupIntWeight
+            out[name] = t.dequant().to(t.payload.device)
+            continue
         w = Q.dequant_nvfp4(t.codes, t.scale, t.divisor, N, K) if t.qtype == Q.QT_NVFP4 else Q.dequant_fp8_row(t.codes, t.scale)
         out[name] = Q.deinterleave_gate_up(w) if name.endswith("gate_up") else w
     return out

@@ -88,6 +88,7 @@ class ProgramBase:
         self.host_budget_bytes = 0
         self.disk_budget_bytes = 0
         self.cold_dir: Optional[str] = None
+        self.cold_entropy = False   # entropy-code frontiers written to the disk tier (kv/cold_codec.py)
         self.cold_stats = {"demoted_host": 0, "demoted_disk": 0, "promoted": 0, "dropped": 0}
         # shared-prefix catalogue: frontiers of prompt prefixes that any request may start from (system prompts)
         self.max_shared_prefixes = 8
@@ -136,7 +137,14 @@ class ProgramBase:
             if self.cold_dir and on_disk + victim.nbytes <= self.disk_budget_bytes:
                 os.makedirs(self.cold_dir, exist_ok=True)
                 path = os.path.join(self.cold_dir, f"ckpt_{id(victim):x}_{self._clock}.pt")
-                torch.save(victim.handle, path)
+                if self.cold_entropy and set(victim.handle) == {"n_pages", "tensors"}:
+                    # lossless entropy stage (rANS per tensor, raw when it does not pay): fewer bytes on disk
+                    from ..kv.cold_codec import save_cold
+                    st = save_cold(victim.handle, path)
+                    self.cold_stats["disk_raw_bytes"] = self.cold_stats.get("disk_raw_bytes", 0) + st["raw"]
+                    self.cold_stats["disk_stored_bytes"] = self.cold_stats.get("disk_stored_bytes", 0) + st["stored"]
+                else:
+                    torch.save(victim.handle, path)
                 victim.handle, victim.tier = {"path": path}, "disk"
                 self.cold_stats["demoted_disk"] += 1
             else:
@@ -160,7 +168,7 @@ class ProgramBase:
         """Brings a cold frontier back into the device pool (disk -> host -> device).  False if there is no room."""
         if c.tier == "gpu":
             return True
-        cold = torch.load(c.handle["path"], weights_only=False) if c.tier == "disk" else c.handle
+        cold = self._read_cold_file(c.handle["path"]) if c.tier == "disk" else c.handle
         handle = self._promote(cold)
         while handle is None:
             others = [o for o in self.checkpoints if o.tier == "gpu" and o is not c]
@@ -176,6 +184,13 @@ class ProgramBase:
         c.handle, c.tier, c.nbytes = handle, "gpu", 0
         self.cold_stats["promoted"] += 1
         return True
+
+    @staticmethod
+    def _read_cold_file(path: str):
+        from ..kv.cold_codec import FILE_MAGIC, load_cold
+        with open(path, "rb") as f:
+            coded = f.read(len(FILE_MAGIC)) == FILE_MAGIC
+        return load_cold(path) if coded else torch.load(path, weights_only=False)
 
     def _demote(self, handle):
         return None   # programs without a cold tier drop evicted frontiers

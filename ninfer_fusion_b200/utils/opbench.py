@@ -95,6 +95,27 @@ def bench_gemm(ops, T, N, K, epi, splits=0, iters=20, pdl=False):
             "frac_hbm": round(byts / med / bw, 3), "frac_bf16": round(flops / med / fl, 3), "peaks": how}
 
 
+def bench_groupint(ops, T, N, K, fmt, iters=20):
+    """Streaming linear over groupwise-int codes (random codes, constant scales: timing only)."""
+    from ..artifact import layouts as L
+    from ..ops import groupint as G
+    long_name = G.SHORT_NAMES[fmt]
+    size = L.encoded_size(long_name, "row-split-k128-v1", (N, K))
+    payload = torch.randint(0, 256, (size,), dtype=torch.uint8, device="cuda")
+    group = L.GROUP_FORMATS[long_name][1]
+    n_scale = N * (L.align_up(K, 128) // group)
+    payload[size - 2 * n_scale:].copy_(torch.full((n_scale,), 0.01, dtype=torch.float16, device="cuda").view(torch.uint8))
+    w = G.GroupIntWeight(long_name, payload, (N, K))
+    x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
+    out = torch.empty((T, N), dtype=torch.bfloat16, device="cuda")
+    med, best = time_op(lambda: G.linear(ops, x, w, out=out), iters=iters, flush=L2Flusher())
+    byts = size + T * K * 2 + T * N * 2
+    bw, _, how = measured_peaks()
+    return {"op": f"groupint_{fmt}", "T": T, "N": N, "K": K, "us": round(med * 1e6, 2), "best_us": round(best * 1e6, 2),
+            "GBps": round(byts / med / 1e9, 1), "frac_hbm": round(byts / med / bw, 3), "weight_MB": round(size / 1e6, 1),
+            "peaks": how}
+
+
 DECODE_27B = [("attn_in", 14336, 5120, "store"), ("gdn_in", 16480, 5120, "store"), ("gate_up", 34816, 5120, "swiglu"),
               ("o_proj", 5120, 6144, "partial"), ("down", 5120, 17408, "partial"), ("lm_head", 248320, 5120, "store")]
 
@@ -223,7 +244,7 @@ def bench_vision(side_patches: int, layers: int, iters=5):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "decode27b", "prefill27b", "attn", "gdn", "gdn_prefill", "vision", "all"])
+    ap.add_argument("what", choices=["gemm", "decode27b", "prefill27b", "attn", "gdn", "gdn_prefill", "vision", "groupint", "all"])
     ap.add_argument("--side", type=int, default=64, help="vision: patches per image side (64 = a 1024 x 1024 image)")
     ap.add_argument("--layers", type=int, default=27, help="vision: transformer blocks")
     ap.add_argument("--T", type=int, default=32)
@@ -261,6 +282,13 @@ def main(argv=None):
     if a.what == "gdn_prefill":
         rows.append(bench_gdn_prefill(ops, a.batch, a.T, iters=a.iters))
         rows.append(bench_gdn_prefill(ops, a.batch, a.T, hk=2, hv=6, iters=a.iters))
+    if a.what == "groupint":
+        for fmt in ("q4", "q6", "w8"):
+            for T in (1, 8, 32):
+                for name, N, K, _ in DECODE_27B[2:5]:
+                    r = bench_groupint(ops, T, N, K, fmt, a.iters)
+                    r["name"] = name
+                    rows.append(r)
     if a.what == "vision":
         rows.append(bench_vision(a.side, a.layers, max(3, a.iters // 4)))
     for r in rows:
