@@ -61,6 +61,13 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--vision", action="store_true",
                     help="attach the vision tower (the artifact's vision/ tensors, or random ones with --random-init)")
     ap.add_argument("--vision-layers", type=int, default=0, help="shrink the vision tower to this many blocks (debug)")
+    ap.add_argument("--kv-capacity", default="full", help="main KV pool: 'full', 'auto' or a token count >= --max-context")
+    ap.add_argument("--kv-headroom-gib", type=float, default=2.0, help="device memory left free by --kv-capacity auto")
+    ap.add_argument("--planner", default="lru", choices=["lru", "b200", "h100", "rtx5090"],
+                    help="which cached frontier is given up under memory pressure: least recently used, or the "
+                         "materialisation planner with that machine's cost preset")
+    ap.add_argument("--kv-rowscale", default=None,
+                    help="K row-scale table (default: NINFER_KV_ROWSCALE, else <artifact>.kvrowscale.bin when present)")
     ap.add_argument("--seed", type=int, default=0)
 
 
@@ -167,8 +174,12 @@ def program_factory(args, cfg: ModelConfig, weights, kv):
             text = {k: v for k, v in weights.items() if not k.startswith("vision/")}
             prog = GpuProgram(cfg, text, args.device, max_lanes=args.max_lanes, max_context=args.max_context,
                               kv_format=kv, page_size=args.page_size, prefill_chunk=args.prefill_chunk,
-                              use_graph=not args.no_graphs,
+                              use_graph=not args.no_graphs, kv_pages=resolve_kv_pages(args, cfg, kv),
                               weight_budget_bytes=int(args.weight_budget_gib * (1 << 30)) if args.weight_budget_gib > 0 else None)
+            load_row_scale(args, cfg, prog.model)
+            if getattr(args, "planner", "lru") != "lru":
+                from .runtime.planner import PRESETS, MaterializationPlanner
+                prog.planner = MaterializationPlanner(PRESETS[args.planner])
             return attach_vision(args, cfg, weights, prog)
     else:
         def factory():
@@ -176,6 +187,59 @@ def program_factory(args, cfg: ModelConfig, weights, kv):
                                     kv_format=kv if isinstance(kv, str) else "bf16")
             return attach_vision(args, cfg, weights, prog)
     return factory
+
+
+def resolve_kv_pages(args, cfg: ModelConfig, kv) -> Optional[int]:
+    """--kv-capacity: 'full' (every lane can reach max_context), a token count, or 'auto' (what the free device memory
+    holds after the weights, less --kv-headroom-gib, along the layout's affine capacity curve)."""
+    from .runtime import capacity as CAP
+    spec = str(getattr(args, "kv_capacity", "full"))
+    if spec == "full":
+        return None
+    curve = CAP.build_curve(cfg, kv, args.page_size, args.max_context, args.max_lanes)
+    if spec == "auto":
+        free, _ = torch.cuda.mem_get_info(torch.device(args.device))
+        plan = CAP.resolve(curve, args.page_size, args.max_context, free_bytes=int(free),
+                           headroom_bytes=int(args.kv_headroom_gib * (1 << 30)))
+    else:
+        plan = CAP.resolve(curve, args.page_size, args.max_context, explicit_tokens=int(spec))
+    print(json.dumps({"kv_capacity": {"policy": plan.policy, "pages": plan.pages, "tokens": plan.tokens,
+                                      "reserved_bytes": plan.reserved_bytes}}), file=sys.stderr)
+    return plan.pages
+
+
+def load_row_scale(args, cfg: ModelConfig, model) -> int:
+    """K row-scale table from --kv-rowscale, NINFER_KV_ROWSCALE or the artifact's side file; none of them: feature off."""
+    import os
+    from .kv import rowscale as RS
+    path = getattr(args, "kv_rowscale", None) or os.environ.get("NINFER_KV_ROWSCALE")
+    if not path and getattr(args, "artifact", None) and os.path.exists(RS.side_file(args.artifact)):
+        path = RS.side_file(args.artifact)
+    if not path:
+        return 0
+    table = RS.read_table(path)
+    RS.validate(table, len(cfg.attn_layers), cfg.n_kv_heads, cfg.head_dim)
+    return RS.load_into(model, table, cfg.attn_layers)
+
+
+def cmd_kv_rowscale(args) -> int:
+    """Side-file tool: write an identity table, or validate a table against a model geometry."""
+    from .kv import rowscale as RS
+    cfg = get_config(args.model)
+    L, H, D = len(cfg.attn_layers), cfg.n_kv_heads, cfg.head_dim
+    if args.identity:
+        RS.write_table(args.identity, torch.ones((L, H, D)), tag=args.tag, identity=True)
+        print(json.dumps({"wrote": args.identity, "layers": L, "kv_heads": H, "head_dim": D, "identity": True}))
+        return 0
+    try:
+        t = RS.read_table(args.validate)
+        RS.validate(t, L, H, D)
+    except RS.RowScaleError as e:
+        print(json.dumps({"valid": False, "error": str(e)}))
+        return 1
+    print(json.dumps({"valid": True, "geometry": list(t.geometry), "identity": t.identity, "tag": t.tag,
+                      "min": float(t.scales.float().min()), "max": float(t.scales.float().max())}))
+    return 0
 
 
 # ---------------------------------------------------------------------------------------------------------
@@ -423,6 +487,12 @@ def main(argv=None) -> int:
     c.add_argument("--no-mtp", action="store_true", help="skip the draft module")
     c.add_argument("--to-hf", action="store_true", help="artifact -> safetensors with Hugging Face names")
     c.set_defaults(fn=cmd_convert)
+    r = sub.add_parser("kv-rowscale", help="K row-scale side file: write an identity table or validate one")
+    r.add_argument("--model", default="qwen3.6-27b")
+    r.add_argument("--identity", metavar="OUT", help="write an identity table for the model's geometry")
+    r.add_argument("--validate", metavar="TABLE", help="check a table against the model's geometry")
+    r.add_argument("--tag", default="")
+    r.set_defaults(fn=cmd_kv_rowscale)
     p = sub.add_parser("perplexity", help="score a text corpus on the oracle model")
     add_model_args(p)
     p.add_argument("--corpus", required=True)

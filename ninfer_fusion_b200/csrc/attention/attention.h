@@ -32,6 +32,11 @@ struct AttnPrepParams {
   // and k is quantised (q . k is unchanged; outlier channels of k are spread over the row, which is what a per-row
   // fp8 scale needs).  V is stored from its source values.
   int k_hadamard = 0;
+  // Per-channel row scale of the stored K frame, [n_kv_heads, head_dim] bf16 for this layer or nullptr: k is
+  // multiplied by s_d before it is quantised and q (of the heads that read that kv head) by 1 / s_d, so q . k is
+  // unchanged while the channel magnitudes of k are balanced for the group / row scales of the codec
+  // (the reference's Sinkhorn row scale, s_d in [0.5, 2]: src/ops/kernel/gqa_isoquant_row_scale.cuh).
+  const __nv_bfloat16* k_row_scale = nullptr;
 };
 const char* attn_prep(const AttnPrepParams& p, cudaStream_t stream, bool pdl);
 

@@ -112,6 +112,17 @@ __global__ void __launch_bounds__(128) attn_prep_kernel(const AttnPrepParams p) 
     for (int j = 0; j < VPL; ++j) v[j] *= norm;
   }
 
+  if (kind != 2 && p.k_row_scale != nullptr) {
+    // balance the channels of the stored K frame; q takes the inverse so that q . k does not change
+    const int kvh = kind == 1 ? h : h / (p.n_q_heads / p.n_kv_heads);
+    const __nv_bfloat16* s = p.k_row_scale + static_cast<long long>(kvh) * D + d0;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const float sd = __bfloat162float(s[j]);
+      v[j] = kind == 1 ? v[j] * sd : v[j] / sd;
+    }
+  }
+
   if (kind == 0) {
     __nv_bfloat16* dst = p.q_out + (static_cast<long long>(t) * p.n_q_heads + h) * D + d0;
     uint32_t packed[VPL / 2];

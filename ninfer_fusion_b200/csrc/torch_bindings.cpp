@@ -189,7 +189,7 @@ void attn_prep(const Tensor& proj, int64_t q_off, int64_t k_off, int64_t v_off, 
                int64_t rot_dim, const Tensor& inv_freq, double attn_factor, const Tensor& rope_pos,
                const Tensor& token_seq, const Tensor& cache_pos, const Tensor& block_table, const Tensor& q_out,
                const Tensor& k_codes, const Tensor& v_codes, OptT k_scales, OptT v_scales, int64_t page_size,
-               int64_t format, int64_t group, bool pdl, bool k_hadamard) {
+               int64_t format, int64_t group, bool pdl, bool k_hadamard, OptT k_row_scale) {
   need(proj, at::kBFloat16, "proj"); need_rows(proj, "proj");
   need(inv_freq, at::kFloat, "inv_freq"); need(rope_pos, at::kInt, "rope_pos");
   need(token_seq, at::kInt, "token_seq"); need(cache_pos, at::kInt, "cache_pos");
@@ -223,6 +223,12 @@ void attn_prep(const Tensor& proj, int64_t q_off, int64_t k_off, int64_t v_off, 
   p.q_out = static_cast<__nv_bfloat16*>(q_out.data_ptr());
   p.kv = make_kv(k_codes, v_codes, k_scales, v_scales, page_size, n_kv_heads, head_dim, format, group);
   p.k_hadamard = k_hadamard ? 1 : 0;
+  if (k_row_scale.has_value() && k_row_scale->defined()) {
+    need(*k_row_scale, at::kBFloat16, "k_row_scale");
+    TORCH_CHECK(k_row_scale->is_contiguous() && k_row_scale->numel() == n_kv_heads * head_dim,
+                "k_row_scale must be a contiguous [n_kv_heads, head_dim] table");
+    p.k_row_scale = static_cast<const __nv_bfloat16*>(k_row_scale->data_ptr());
+  }
   chk(nfb::attn_prep(p, cur_stream(), pdl));
 }
 
@@ -671,7 +677,7 @@ TORCH_LIBRARY(nfb200, m) {
   m.def("gemm_pick_splits(int T, int N, int K, int epi) -> int", &gemm_pick_splits);
   m.def("add_rmsnorm(Tensor? partial, int splits, Tensor? delta, Tensor? resid_in, Tensor? resid_out, Tensor? norm_w, Tensor? normed, int T, int N, float eps, bool unit_offset, bool pdl, Tensor? q_codes=None, Tensor? q_sf=None) -> ()", &add_rmsnorm);
   m.def("embed_gather(Tensor ids, Tensor table, Tensor out, bool pdl) -> ()", &embed_gather);
-  m.def("attn_prep(Tensor proj, int q_off, int k_off, int v_off, int n_q_heads, int n_kv_heads, int head_dim, Tensor? q_norm_w, Tensor? k_norm_w, float eps, bool unit_offset, int rot_dim, Tensor inv_freq, float attn_factor, Tensor rope_pos, Tensor token_seq, Tensor cache_pos, Tensor block_table, Tensor q_out, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, bool pdl, bool k_hadamard=False) -> ()", &attn_prep);
+  m.def("attn_prep(Tensor proj, int q_off, int k_off, int v_off, int n_q_heads, int n_kv_heads, int head_dim, Tensor? q_norm_w, Tensor? k_norm_w, float eps, bool unit_offset, int rot_dim, Tensor inv_freq, float attn_factor, Tensor rope_pos, Tensor token_seq, Tensor cache_pos, Tensor block_table, Tensor q_out, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, bool pdl, bool k_hadamard=False, Tensor? k_row_scale=None) -> ()", &attn_prep);
   m.def("paged_attention(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, int split_keys, int n_splits, Tensor part_o, Tensor part_ml, Tensor? gate, Tensor out, Tensor? tree_mask, Tensor? tree_base, int impl, bool pdl, int window=0) -> ()", &paged_attention);
   m.def("paged_attention_prefill(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor blk_start, Tensor blk_count, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, Tensor? gate, Tensor out, bool pdl, int window=0) -> ()", &paged_attention_prefill);
   m.def("prefill_attn_block_tokens(int n_q_heads, int n_kv_heads) -> int", &prefill_attn_block_tokens);

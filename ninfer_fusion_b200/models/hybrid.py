@@ -241,6 +241,8 @@ class HybridModel:
         else:
             self.inv_freq = rope_inv_freq(cfg.rot_dim, cfg.rope_theta).to(self.device)
         self.sm_scale = 1.0 / math.sqrt(cfg.head_dim)
+        # per-layer K row-scale tables ([n_kv_heads, head_dim] bf16), set by load_k_row_scale (kv/rowscale.py)
+        self.k_row_scale: Dict[int, torch.Tensor] = {}
         self.cluster_splitk = True  # False: split-K through an fp32 workspace + reduce kernel
         self.attn_impl = 0  # 0 = pick, 1 = SIMT, 2 = tensor-core split-KV attention
         self.comm = None  # tensor-parallel communicator (parallel.tp), None on one GPU
@@ -369,7 +371,7 @@ class HybridModel:
                       self.w[f"{prefix}/attn/q_norm"], self.w[f"{prefix}/attn/k_norm"], cfg.rms_eps, True,
                       cfg.rot_dim, self.inv_freq, self.rope_factor, b.rope_pos, b.table_row, b.cache_pos, kv.table, q,
                       planes.k_codes, planes.v_codes, planes.k_scales, planes.v_scales, kv.page_size, planes.fmt,
-                      planes.group, self.pdl, planes.hadamard)
+                      planes.group, self.pdl, planes.hadamard, self.k_row_scale.get(layer))
         gate = proj[:, q_dim + kv_dim: q_dim + kv_dim + q_dim]
         out = ws.mix_attn[:T]
         if (not b.one_token_per_seq and b.qblk_start is not None and D == 256 and self.attn_impl != 1

@@ -34,6 +34,9 @@ class ReferenceSequence:
         self.conv = [torch.zeros(3, cfg.gdn_conv_dim) for _ in cfg.gdn_layers]
         self.ssm = [torch.zeros(cfg.gdn_v_heads, cfg.gdn_head_dim, cfg.gdn_head_dim) for _ in cfg.gdn_layers]
         self.n_tokens = 0
+        # per attention layer (index into cfg.attn_layers): [n_kv_heads, head_dim] channel multipliers of the stored K
+        # frame; k is multiplied and q divided, so scores only change through the codec's rounding
+        self.k_row_scale: Dict[int, torch.Tensor] = {}
 
 
 class ReferenceModel:
@@ -66,6 +69,11 @@ class ReferenceModel:
             Hn = R.hadamard_matrix(D)
             q = R.bf16_round(q @ Hn)
             k = k @ Hn
+        rs = seq.k_row_scale.get(ai)
+        if rs is not None:
+            rs = R.bf16_round(rs.float())
+            k = k * rs[None]
+            q = R.bf16_round(q / rs.repeat_interleave(cfg.n_q_heads // cfg.n_kv_heads, dim=0)[None])
         k = R.kv_quant_dequant(k, seq.kv_format, seq.int8_group)
         v = R.kv_quant_dequant(v, seq.kv_format, seq.int8_group)
         base = seq.k[ai].shape[0]

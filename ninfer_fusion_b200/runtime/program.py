@@ -65,6 +65,7 @@ class Checkpoint:
     last_used: float = 0.0
     tier: str = "gpu"     # "gpu" | "host" | "disk": where the KV pages and the state image currently live
     nbytes: int = 0       # size of the cold copy (host / disk tiers)
+    hits: int = 0         # times a request started from this frontier (the planner's demand signal)
 
 
 SHARED_SESSION = "__shared__"
@@ -113,7 +114,7 @@ class ProgramBase:
         hot = [c for c in self.checkpoints if c.tier == "gpu"]
         if not hot:
             return False
-        victim = min(hot, key=lambda c: c.last_used)
+        victim = self._choose_victim(hot)
         cold = self._demote(victim.handle) if self.host_budget_bytes > 0 else None
         self._drop(victim.handle)
         if cold is None:
@@ -124,6 +125,23 @@ class ProgramBase:
         self.cold_stats["demoted_host"] += 1
         self._trim_cold()
         return True
+
+    def _choose_victim(self, hot: List[Checkpoint]) -> Checkpoint:
+        """Least recently used without a planner; with one (`self.planner`, runtime/planner.py) the frontier whose loss
+        costs least per token of context it holds: demand (hits, recency, shared credit) times the cost of getting
+        it back from the tier it would fall to."""
+        planner = getattr(self, "planner", None)
+        if planner is None:
+            return min(hot, key=lambda c: c.last_used)
+        from .planner import DROP, TO_HOST, Owner
+        action = TO_HOST if self.host_budget_bytes > 0 else DROP
+
+        def loss(c: Checkpoint) -> float:
+            n = max(1, len(c.tokens))
+            o = Owner(key=id(c), pages=n, tokens=n, nbytes=n * getattr(self, "bytes_per_token_estimate", 65536),
+                      hits=c.hits, last_hit_epoch=int(c.last_used), shared=c.session == SHARED_SESSION)
+            return planner.action_cost(o, action, self._clock) / n
+        return min(hot, key=lambda c: (loss(c), c.last_used))
 
     def _cold_bytes(self, cold) -> int:
         return sum(t.numel() * t.element_size() for group in cold["tensors"] for t in group)
@@ -300,6 +318,7 @@ class ProgramBase:
             lane.n_cached = lane.reused = len(ck.tokens)
             self._clock += 1
             ck.last_used = self._clock
+            ck.hits += 1
         return lane
 
     def close(self, lane: Lane) -> None:

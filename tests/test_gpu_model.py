@@ -182,3 +182,40 @@ def test_weight_offload_generates_the_same_tokens():
     out = gen.generate(prompts, 10)
     assert out == ref
     assert gen.model.w.fetches >= 3 * 10
+
+
+def test_k_row_scale_matches_reference_and_changes_the_stored_k():
+    """K row-scale tables on the engine: logits follow the oracle with the same tables (nvfp4 and bf16 KV), and the
+    bf16 K planes hold k * s (the table is really applied on the write path, q takes 1 / s)."""
+    from ninfer_fusion_b200.kv import rowscale as RS
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cuda", seed=7, std=0.05)
+    g = torch.Generator().manual_seed(5)
+    table = (torch.rand((len(cfg.attn_layers), cfg.n_kv_heads, cfg.head_dim), generator=g) * 1.5 + 0.5)
+    table = table.to(torch.bfloat16)
+    rs = RS.RowScaleTable(table)
+    torch.manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (37, 20)]
+    ref = ReferenceModel(cfg, w)
+    planes = {}
+    for kv_format, fmt in (("bf16", R.KV_BF16), ("nvfp4", R.KV_NVFP4)):
+        for scaled in (False, True):
+            gen = Generator(cfg, w, "cuda", max_batch=2, max_context=512, kv_format=kv_format, page_size=16,
+                            prefill_chunk=64, use_graph=False)
+            if scaled:
+                assert RS.load_into(gen.model, rs, cfg.attn_layers) == len(cfg.attn_layers)
+            gen.prefill(prompts)
+            got = gen.ws.logits[:2].float().cpu()
+            if kv_format == "bf16":
+                planes[scaled] = gen.kv.layers[0].k_codes.clone()
+            for b, p in enumerate(prompts):
+                seq = ReferenceSequence(cfg, fmt)
+                if scaled:
+                    seq.k_row_scale = {ai: table[ai].float() for ai in range(len(cfg.attn_layers))}
+                want = ref.logits(ref.forward(seq, torch.tensor(p))[-1:])[0]
+                cos = torch.nn.functional.cosine_similarity(got[b], want, dim=0).item()
+                assert cos > (0.999 if kv_format == "bf16" else 0.98), (kv_format, scaled, cos)
+    a, b = planes[False].view(torch.bfloat16).float(), planes[True].view(torch.bfloat16).float()
+    used = a.abs() > 1e-3
+    ratio = (b[used] / a[used])
+    assert used.sum() > 1000 and float(ratio.min()) > 0.45 and float(ratio.max()) < 2.2 and float(ratio.std()) > 0.2
