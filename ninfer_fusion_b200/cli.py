@@ -222,6 +222,15 @@ def load_row_scale(args, cfg: ModelConfig, model) -> int:
     return RS.load_into(model, table, cfg.attn_layers)
 
 
+def cmd_packages(args) -> int:
+    """The closed package table: what each registered model needs and whether this engine serves it."""
+    from .models import packages as PK
+    ids = [args.model] if args.model else sorted(PK.PACKAGES)
+    for mid in ids:
+        print(json.dumps(PK.describe(mid)))
+    return 0
+
+
 def cmd_kv_rowscale(args) -> int:
     """Side-file tool: write an identity table, or validate a table against a model geometry."""
     from .kv import rowscale as RS
@@ -487,6 +496,9 @@ def main(argv=None) -> int:
     c.add_argument("--no-mtp", action="store_true", help="skip the draft module")
     c.add_argument("--to-hf", action="store_true", help="artifact -> safetensors with Hugging Face names")
     c.set_defaults(fn=cmd_convert)
+    k = sub.add_parser("packages", help="list the registered model packages and the capability gate's verdict")
+    k.add_argument("--model", default=None)
+    k.set_defaults(fn=cmd_packages)
     r = sub.add_parser("kv-rowscale", help="K row-scale side file: write an identity table or validate one")
     r.add_argument("--model", default="qwen3.6-27b")
     r.add_argument("--identity", metavar="OUT", help="write an identity table for the model's geometry")

@@ -14,6 +14,10 @@
 #include "gemm_groupint.h"
 
 #include <cstdint>
+#include <cstdlib>
+
+#include "../common/ptx.cuh"
+#include "../common/tensor_map.h"
 
 namespace nfb {
 namespace {
@@ -86,13 +90,32 @@ struct Frag {
   float s[MT][2][H];
 };
 
-template <int FMT, int MT, int NT>
-__global__ void __launch_bounds__(kThreads) groupint_linear_kernel(const GroupIntLinearParams p) {
+constexpr int kStages = 4;        // TMA ring depth per warp
+constexpr int kBoxBytes = 32;     // bytes of one weight row in a TMA box: 64 four-bit codes or 32 eight-bit codes
+
+// dynamic shared memory of the TMA variant: per-warp rings (the cross-warp reduction reuses them), the CTA's scale
+// rows, the ring barriers
+__host__ __device__ constexpr int ring_bytes(int rows, int boxes) { return kWarps * kStages * boxes * rows * kBoxBytes; }
+__host__ __device__ constexpr int red_bytes(int rows, int cols) { return kWarps * rows * (cols + 1) * 4; }
+__host__ __device__ constexpr int max_i(int a, int b) { return a > b ? a : b; }
+
+// TMA = true (Q4 and W8): every warp keeps its own ring of kStages k blocks in shared memory, filled by 2-D bulk
+// tensor copies of [ROWS x 32 bytes] boxes that one lane issues and an mbarrier per slot completes; the fragments are
+// then read from shared memory without bank conflicts (a box is 32 bytes wide, so the eight rows of a fragment load
+// are 256 consecutive bytes).  This takes the weight stream off the load/store unit, which the register variant
+// saturates with one 128-byte line per row and load.  No cluster multicast: every CTA loads its own rows.
+template <int FMT, int MT, int NT, bool TMA>
+__global__ void __launch_bounds__(kThreads) groupint_linear_kernel(const GroupIntLinearParams p,
+                                                                   const __grid_constant__ CUtensorMap tm0,
+                                                                   const __grid_constant__ CUtensorMap tm1) {
   constexpr int ROWS = 16 * MT;
   constexpr int COLS = 8 * NT;
   constexpr int BITS = FMT == kQ4G64 ? 4 : FMT == kQ5G64 ? 5 : FMT == kQ6G64 ? 6 : 8;
   constexpr int hb = BITS == 8 ? 0 : BITS - 4;
-  __shared__ float red[kWarps][ROWS][COLS + 1];
+  static_assert(!TMA || hb == 0, "the TMA variant covers the formats without a high-bit plane");
+  __shared__ float red_static[TMA ? 1 : kWarps * ROWS * (COLS + 1)];
+  extern __shared__ __align__(128) uint8_t dyn[];
+  float (*red)[ROWS][COLS + 1] = reinterpret_cast<float (*)[ROWS][COLS + 1]>(TMA ? reinterpret_cast<float*>(dyn) : red_static);
 
   const GroupIntWeight& W = p.w[blockIdx.y];
   const int r0 = blockIdx.x * ROWS;
@@ -142,15 +165,25 @@ __global__ void __launch_bounds__(kThreads) groupint_linear_kernel(const GroupIn
 #pragma unroll
       for (int c = 0; c < 4; ++c) acc[mt][nt][c] = 0.f;
 
-  auto compute = [&](const Frag<FMT, MT>& f, int blk) {
+  // the lane's activations of one k block: [half][token tile] x 8 consecutive k (see the fragment order above)
+  auto load_x = [&](int blk, uint4 (&xq)[2][NT]) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int k0 = BITS == 8 ? 64 * blk + 32 * h + 8 * t : 64 * blk + 16 * t + 8 * h;
+        xq[h][nt] = __ldg(reinterpret_cast<const uint4*>(xrow[nt] + k0));
+      }
+  };
+
+  auto compute = [&](const Frag<FMT, MT>& f, const uint4 (&xq)[2][NT]) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {       // Q formats: h = 32-bit word of the lane's 16 codes; W8: h = group of 32
       // B fragments of both MMA steps of this half, per token tile
       uint32_t b[NT][2][2];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        const int k0 = BITS == 8 ? 64 * blk + 32 * h + 8 * t : 64 * blk + 16 * t + 8 * h;
-        const uint4 xv = __ldg(reinterpret_cast<const uint4*>(xrow[nt] + k0));
+        const uint4 xv = xq[h][nt];
         if constexpr (BITS == 8) {
           b[nt][0][0] = xv.x; b[nt][0][1] = xv.y; b[nt][1][0] = xv.z; b[nt][1][1] = xv.w;
         } else {
@@ -209,14 +242,80 @@ __global__ void __launch_bounds__(kThreads) groupint_linear_kernel(const GroupIn
   // One k block requested ahead of the one being multiplied.  Requesting four ahead did not help (measured): the
   // kernel is held by the load/store unit (8 distinct 128-byte lines per warp-wide load: one per weight row) and by
   // the 1.5-2 integer operations per dequantised weight, not by the depth of its DRAM queue.
-  Frag<FMT, MT> cur, nxt;
-  int blk = warp;
-  if (blk < nblk) load(cur, blk);
-  for (; blk < nblk; blk += kWarps) {
-    const int nb = blk + kWarps;
-    if (nb < nblk) load(nxt, nb);
-    compute(cur, blk);
-    cur = nxt;
+  if constexpr (!TMA) {
+    Frag<FMT, MT> cur, nxt;
+    int blk = warp;
+    if (blk < nblk) load(cur, blk);
+    for (; blk < nblk; blk += kWarps) {
+      const int nb = blk + kWarps;
+      if (nb < nblk) load(nxt, nb);
+      uint4 xq[2][NT];
+      load_x(blk, xq);
+      compute(cur, xq);
+      cur = nxt;
+    }
+  } else {
+    constexpr int NB = Frag<FMT, MT>::H;                 // boxes per k block: W8 has two groups of 32 codes
+    constexpr int BOX = ROWS * kBoxBytes;
+    constexpr int RING = ring_bytes(ROWS, NB);
+    constexpr int FRONT = max_i(RING, red_bytes(ROWS, COLS));
+    __shared__ int abort_flag;
+    const int spitch = scale_pitch + 2;                  // halves; two spare so that rows start in different banks
+    __half* sc = reinterpret_cast<__half*>(dyn + FRONT);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(dyn + FRONT + ((ROWS * spitch * 2 + 15) / 16) * 16);
+    uint8_t* my_ring = dyn + warp * (kStages * NB * BOX);
+    for (int i = threadIdx.x; i < ROWS * scale_pitch; i += kThreads) {
+      const int r = i / scale_pitch, c = i - r * scale_pitch;
+      sc[r * spitch + c] = r0 + r < W.N ? __ldg(W.scale + static_cast<int64_t>(r0 + r) * scale_pitch + c) : __float2half(0.f);
+    }
+    if (threadIdx.x == 0) abort_flag = 0;
+    if (lane == 0) {
+#pragma unroll
+      for (int st = 0; st < kStages; ++st) mbar_init(smem_u32(&bars[warp * kStages + st]), 1);
+      mbar_fence_init();
+    }
+    __syncthreads();
+    const CUtensorMap* tm = blockIdx.y == 0 ? &tm0 : &tm1;
+    const uint64_t policy = l2_policy_evict_first();     // weights are read once per launch
+    auto issue = [&](int slot, int blk) {                // one lane
+      const uint32_t bar = smem_u32(&bars[warp * kStages + slot]);
+      mbar_expect_tx(bar, NB * BOX);
+#pragma unroll
+      for (int b = 0; b < NB; ++b)
+        tma_load_2d(smem_u32(my_ring + (slot * NB + b) * BOX), tm, bar, BITS == 8 ? 64 * blk + 32 * b : 32 * blk, r0, policy);
+    };
+    const int n_my = warp < nblk ? (nblk - warp + kWarps - 1) / kWarps : 0;
+    if (lane == 0)
+      for (int st = 0; st < kStages && st < n_my; ++st) issue(st, warp + st * kWarps);
+    __syncwarp();
+    for (int i = 0; i < n_my; ++i) {
+      const int slot = i % kStages, blk = warp + i * kWarps;
+      // bounded: a copy that never lands sets the status word and the CTA unwinds instead of spinning
+      if (!mbar_wait(smem_u32(&bars[warp * kStages + slot]), (i / kStages) & 1, &abort_flag, p.status, kStatusTmaWaitTimeout)) break;
+      Frag<FMT, MT> f;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const int row = mt * 16 + g + 8 * r;
+#pragma unroll
+          for (int h = 0; h < NB; ++h) {
+            f.a[mt][r][h] = *reinterpret_cast<const uint2*>(my_ring + (slot * NB + h) * BOX + row * kBoxBytes + 8 * t);
+            f.s[mt][r][h] = __half2float(sc[row * spitch + (BITS == 8 ? 2 * blk + h : blk)]);
+          }
+        }
+      __syncwarp();
+      if (lane == 0 && i + kStages < n_my) {
+        fence_proxy_async_smem();                        // the slot's reads above are ordered before the refill
+        issue(slot, warp + (i + kStages) * kWarps);
+      }
+      // (fetching the next block's activations a block ahead was tried: no gain up to 16 tokens, a loss at 32 from
+      // the 32 extra registers)
+      uint4 xq[2][NT];
+      load_x(blk, xq);
+      compute(f, xq);
+    }
+    __syncthreads();                                     // every ring is drained before the reduction reuses the space
   }
 
 #pragma unroll
@@ -237,12 +336,38 @@ __global__ void __launch_bounds__(kThreads) groupint_linear_kernel(const GroupIn
   }
 }
 
-template <int FMT, int MT>
-const char* launch_nt(const GroupIntLinearParams& p, dim3 grid, cudaStream_t stream) {
-  if (p.T <= 8) groupint_linear_kernel<FMT, MT, 1><<<grid, kThreads, 0, stream>>>(p);
-  else if (p.T <= 16) groupint_linear_kernel<FMT, MT, 2><<<grid, kThreads, 0, stream>>>(p);
-  else groupint_linear_kernel<FMT, MT, 4><<<grid, kThreads, 0, stream>>>(p);
+bool tma_enabled() {
+  static const bool on = [] { const char* e = std::getenv("NFB_GROUPINT_TMA"); return !(e && e[0] == '0'); }();
+  return on;
+}
+
+template <int FMT, int MT, int NT, bool TMA>
+const char* launch_one(const GroupIntLinearParams& p, dim3 grid, cudaStream_t stream, const CUtensorMap& tm0, const CUtensorMap& tm1) {
+  auto kernel = groupint_linear_kernel<FMT, MT, NT, TMA>;
+  int dyn_bytes = 0;
+  if (TMA) {
+    constexpr int ROWS = 16 * MT;
+    constexpr int NB = FMT == kW8G32 ? 2 : 1;
+    const int scale_pitch = FMT == kW8G32 ? p.Kp / 32 : p.Kp / 64;
+    dyn_bytes = max_i(ring_bytes(ROWS, NB), red_bytes(ROWS, 8 * NT)) + ((ROWS * (scale_pitch + 2) * 2 + 15) / 16) * 16 +
+                kWarps * kStages * 8;
+    if (dyn_bytes > 200 * 1024) return "groupint_linear: K is too large for the shared-memory scale rows";
+    static int configured = 0;   // per instantiation: the largest size the attribute was raised to
+    if (dyn_bytes > configured) {
+      if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn_bytes) != cudaSuccess)
+        return "groupint_linear: cannot raise the dynamic shared memory limit";
+      configured = dyn_bytes;
+    }
+  }
+  kernel<<<grid, kThreads, dyn_bytes, stream>>>(p, tm0, tm1);
   return cudaGetLastError() == cudaSuccess ? nullptr : "groupint_linear: launch failed";
+}
+
+template <int FMT, int MT, bool TMA>
+const char* launch_nt(const GroupIntLinearParams& p, dim3 grid, cudaStream_t stream, const CUtensorMap& tm0, const CUtensorMap& tm1) {
+  if (p.T <= 8) return launch_one<FMT, MT, 1, TMA>(p, grid, stream, tm0, tm1);
+  if (p.T <= 16) return launch_one<FMT, MT, 2, TMA>(p, grid, stream, tm0, tm1);
+  return launch_one<FMT, MT, 4, TMA>(p, grid, stream, tm0, tm1);
 }
 
 template <int FMT>
@@ -251,8 +376,21 @@ const char* launch_mt(const GroupIntLinearParams& p, cudaStream_t stream) {
   if (p.n_weights == 2 && p.w[1].N > n_max) n_max = p.w[1].N;
   // 32-row tiles reuse each activation fragment twice; 16-row tiles double the CTA count when rows are scarce
   const bool wide = n_max % 32 == 0 && (n_max / 32) * p.n_weights >= 2 * 148;
-  if (wide) return launch_nt<FMT, 2>(p, dim3(n_max / 32, p.n_weights), stream);
-  return launch_nt<FMT, 1>(p, dim3(n_max / 16, p.n_weights), stream);
+  const dim3 grid(wide ? n_max / 32 : n_max / 16, p.n_weights);
+  CUtensorMap tm[2] = {};
+  if constexpr (FMT == kQ4G64 || FMT == kW8G32) {
+    bool ok = tma_enabled();
+    const uint64_t pitch = FMT == kW8G32 ? p.Kp : p.Kp / 2;
+    for (int i = 0; ok && i < p.n_weights; ++i)
+      ok = (reinterpret_cast<uintptr_t>(p.w[i].base) & 15) == 0 &&
+           make_tmap_2d(&tm[i], TmapDtype::U8, p.w[i].base, static_cast<uint64_t>(p.w[i].N), pitch, pitch, wide ? 32 : 16,
+                        kBoxBytes, false);
+    if (ok) {
+      if (p.n_weights == 1) tm[1] = tm[0];
+      return wide ? launch_nt<FMT, 2, true>(p, grid, stream, tm[0], tm[1]) : launch_nt<FMT, 1, true>(p, grid, stream, tm[0], tm[1]);
+    }
+  }
+  return wide ? launch_nt<FMT, 2, false>(p, grid, stream, tm[0], tm[1]) : launch_nt<FMT, 1, false>(p, grid, stream, tm[0], tm[1]);
 }
 
 }  // namespace

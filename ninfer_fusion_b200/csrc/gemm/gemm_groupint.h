@@ -35,6 +35,7 @@ struct GroupIntLinearParams {
   int64_t ldx = 0;
   const __nv_bfloat16* resid = nullptr;  // optional [T, N] added to out of weight 0 (may alias out)
   int64_t ldr = 0;
+  int* status = nullptr;                 // optional device status word: a bounded wait that ran out is recorded here
 };
 
 // out[t, n] = sum_k x[t, k] * code[n, k] * scale[n, k / group] (+ resid[t, n]); fp32 accumulation, group sums of the

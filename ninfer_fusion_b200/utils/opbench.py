@@ -244,7 +244,7 @@ def bench_vision(side_patches: int, layers: int, iters=5):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "decode27b", "prefill27b", "attn", "gdn", "gdn_prefill", "vision", "groupint", "all"])
+    ap.add_argument("what", choices=["gemm", "decode27b", "prefill27b", "attn", "gdn", "gdn_prefill", "vision", "groupint", "groupint1", "all"])
     ap.add_argument("--side", type=int, default=64, help="vision: patches per image side (64 = a 1024 x 1024 image)")
     ap.add_argument("--layers", type=int, default=27, help="vision: transformer blocks")
     ap.add_argument("--T", type=int, default=32)
@@ -282,6 +282,8 @@ def main(argv=None):
     if a.what == "gdn_prefill":
         rows.append(bench_gdn_prefill(ops, a.batch, a.T, iters=a.iters))
         rows.append(bench_gdn_prefill(ops, a.batch, a.T, hk=2, hv=6, iters=a.iters))
+    if a.what == "groupint1":
+        rows.append(bench_groupint(ops, a.T, a.N, a.K, a.kv if a.kv in ("q4", "q5", "q6", "w8") else "q4", a.iters))
     if a.what == "groupint":
         for fmt in ("q4", "q6", "w8"):
             for T in (1, 8, 32):
