@@ -55,6 +55,9 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--no-graphs", action="store_true", help="eager decode instead of CUDA graphs")
     ap.add_argument("--spec", default="none", choices=["none", "mtp"], help="speculative decoding with the MTP draft module")
     ap.add_argument("--draft-tokens", type=int, default=3)
+    ap.add_argument("--spec-stochastic", action="store_true",
+                    help="with --spec mtp and sampled requests: the draft module samples its proposals and the verifier "
+                         "accepts with min(1, p / q) (general speculative sampling) instead of arg-max proposals")
     ap.add_argument("--allow-unknown-template", action="store_true")
     ap.add_argument("--weight-budget-gib", type=float, default=0.0,
                     help="device bytes for weights; layers beyond it rotate in from pinned host memory (eager decode)")
@@ -160,7 +163,8 @@ def build_engine(args, cfg: ModelConfig, weights) -> Engine:
         def factory():
             return SpeculativeProgram(cfg, weights, args.device, max_lanes=args.max_lanes, max_context=args.max_context,
                                       draft_tokens=args.draft_tokens, kv_format=kv, page_size=args.page_size,
-                                      prefill_chunk=args.prefill_chunk)
+                                      prefill_chunk=args.prefill_chunk,
+                                      stochastic_drafts=getattr(args, "spec_stochastic", False))
         return Engine(factory, prefill_chunk=args.prefill_chunk)
     return Engine(program_factory(args, cfg, weights, kv), prefill_chunk=args.prefill_chunk)
 

@@ -48,7 +48,8 @@ class SpeculativeGenerator(Generator):
     """Static-batch greedy generation with K chained draft tokens per round."""
 
     def __init__(self, cfg: ModelConfig, weights: Dict[str, torch.Tensor], device, max_batch: int, max_context: int,
-                 draft_tokens: int = 3, drafter: str = "mtp", sampling=None, tree_ranks: int = 1, **kw):
+                 draft_tokens: int = 3, drafter: str = "mtp", sampling=None, tree_ranks: int = 1,
+                 stochastic_drafts: bool = False, **kw):
         K = draft_tokens
         if K < 1:
             raise ValueError("draft_tokens must be >= 1")
@@ -84,6 +85,14 @@ class SpeculativeGenerator(Generator):
         self.out_tok = torch.zeros((max_batch, K + 1), dtype=torch.int32, device=dev)
         self.acc_host = torch.zeros(max_batch, dtype=torch.int32, pin_memory=pin)
         self.tok_host = torch.zeros((max_batch, K + 1), dtype=torch.int32, pin_memory=pin)
+        # Stochastic drafts (chain mode, MTP drafter, sampled requests): the draft module SAMPLES its proposals from
+        # its own processed distribution q and hands q to the verifier, which accepts with min(1, p / q) and resamples
+        # a rejection from max(p - q, 0): speculative sampling in its general form.  Off: proposals are arg-max tokens
+        # verified with q = 1 at the draft.  Either way the emitted tokens are distributed as the target's p.
+        self.stochastic_drafts = bool(stochastic_drafts) and drafter == "mtp" and self.R == 1
+        DK = 32   # pairs per exported distribution: the sampler keeps at most its top-k cap (32) candidates
+        self.q_ids = torch.full((max_batch, K + 1, DK), -1, dtype=torch.int32, device=dev)
+        self.q_probs = torch.zeros((max_batch, K + 1, DK), dtype=torch.float32, device=dev)
         self.kv_mtp = None
         if drafter == "mtp":
             if "mtp/fc" not in weights:
@@ -104,6 +113,43 @@ class SpeculativeGenerator(Generator):
         self.next_dev[:n].copy_(self.next_host[:n], non_blocking=True)
         return self.next_dev[:n]
 
+    def _sampling_of(self, b: int):
+        sp = self.sampling[b] if isinstance(self.sampling, (list, tuple)) else self.sampling
+        return sp
+
+    def _draft_stochastically(self) -> bool:
+        if not self.stochastic_drafts or self.sampling is None:
+            return False
+        sps = self.sampling if isinstance(self.sampling, (list, tuple)) else [self.sampling]
+        return any(sp is not None and not sp.greedy for sp in sps)
+
+    def _sample_draft(self, lg: torch.Tensor, ids: torch.Tensor, seqs: Sequence[int], col: int) -> None:
+        """Draws draft column `col` of the sequences `seqs` (one logit row each, in order) from the draft module's
+        distribution under each sequence's own sampling parameters and keeps that distribution as q.  Random stream
+        3, so that the proposals are independent of the verifier's accept / resample draws (streams 1 and 2)."""
+        dev, n = self.device, len(seqs)
+
+        def rows(get, dtype):
+            return torch.tensor([get(self._sampling_of(b)) for b in seqs], dtype=dtype, device=dev)
+        pos = torch.tensor([self.lengths[b] + col + 1 for b in seqs], dtype=torch.int32, device=dev)
+        q_i = torch.empty((n, self.q_ids.shape[2]), dtype=torch.int32, device=dev)
+        q_p = torch.empty((n, self.q_ids.shape[2]), dtype=torch.float32, device=dev)
+        q_i.fill_(-1); q_p.zero_()
+        self.model.ops.sample_rows(lg, rows(lambda sp: 0.0 if sp is None else sp.temperature, torch.float32),
+                                   rows(lambda sp: 1 if sp is None else sp.top_k, torch.int32),
+                                   rows(lambda sp: 1.0 if sp is None else sp.top_p, torch.float32),
+                                   rows(lambda sp: 0.0 if sp is None else sp.min_p, torch.float32), None, None, None,
+                                   rows(lambda sp: 0 if sp is None else sp.seed, torch.int64), pos, 3, ids, None,
+                                   None, None, None, None, q_i, q_p)
+        # a greedy sequence proposes its arg-max: q is one at that token (the sampler writes no distribution for it)
+        greedy = torch.tensor([self._sampling_of(b) is None or self._sampling_of(b).greedy for b in seqs], device=dev)
+        if bool(greedy.any()):
+            q_i[:, 0] = torch.where(greedy, ids[:n], q_i[:, 0])
+            q_p[:, 0] = torch.where(greedy, torch.ones_like(q_p[:, 0]), q_p[:, 0])
+        idx = torch.tensor(list(seqs), dtype=torch.long, device=dev)
+        self.q_ids[idx, col] = q_i
+        self.q_probs[idx, col] = q_p
+
     def _mtp_pass(self, batch, hidden_in: torch.Tensor, next_ids: torch.Tensor, seqs: Sequence[int]) -> None:
         """Draft module over `batch`; for the sequences `seqs` (whose last token is a logit row, in order) store
         the first draft token and the module's hidden state."""
@@ -112,7 +158,10 @@ class SpeculativeGenerator(Generator):
             return
         lg = self.model.logits(self.ws, batch, hid)
         ids = self.ws.next_ids[: lg.shape[0]]
-        self.model.ops.argmax_rows(lg, ids, self.model.pdl)
+        if self._draft_stochastically() and len(self.lengths) > max(seqs):
+            self._sample_draft(lg, ids, list(seqs), 0)
+        else:
+            self.model.ops.argmax_rows(lg, ids, self.model.pdl)
         idx = torch.tensor(list(seqs), dtype=torch.long, device=self.device)
         self.drafts[idx, 0] = ids
         if self.R > 1:
@@ -196,7 +245,10 @@ class SpeculativeGenerator(Generator):
                 hid = self.model.forward_mtp(self.ws, batch, self.kv_mtp, self.h_in[:B], self.drafts[:B, j - 1].contiguous())
                 lg = self.model.logits(self.ws, batch, hid)
                 ids = self.ws.next_ids[:B]
-                self.model.ops.argmax_rows(lg, ids, self.model.pdl)
+                if self._draft_stochastically():
+                    self._sample_draft(lg, ids, list(range(B)), j)
+                else:
+                    self.model.ops.argmax_rows(lg, ids, self.model.pdl)
                 self.drafts[:B, j] = ids
                 if self.R > 1:
                     self.drafts_r[:B, j] = torch.topk(lg.float(), self.R, dim=-1).indices.to(torch.int32)
@@ -371,7 +423,9 @@ class SpeculativeGenerator(Generator):
                             rows(lambda sp: 1.0 if sp is None else sp.top_p, torch.float32),
                             rows(lambda sp: 0.0 if sp is None else sp.min_p, torch.float32), None, None, None,
                             rows(lambda sp: 0 if sp is None else sp.seed, torch.int64), pos, 0, target, None,
-                            d.view(-1), torch.empty(T, dtype=torch.int32, device=dev))
+                            d.view(-1), torch.empty(T, dtype=torch.int32, device=dev),
+                            *((self.q_ids[:B].reshape(T, -1), self.q_probs[:B].reshape(T, -1))
+                              if self._draft_stochastically() else ()))
         # ---- accept + fold ----
         ops.accept_greedy_chain(target.view(B, K + 1), self.drafts[:B], self.n_acc[:B], self.out_tok[:B])
         seq_end = (batch.cu_seqlens[:B] + self.n_acc[:B] + 1).to(torch.int32)
@@ -443,6 +497,9 @@ class SpeculativeProgram:
         h = cfg.hidden
         self.row_draft = torch.zeros(max_lanes, dtype=torch.int32, device=self.gen.device)
         self.row_mtp_h = torch.zeros((max_lanes, h), dtype=torch.bfloat16, device=self.gen.device)
+        # the first draft token's distribution q (stochastic drafts) belongs to the row as well
+        self.row_q_ids = torch.full((max_lanes, self.gen.q_ids.shape[2]), -1, dtype=torch.int32, device=self.gen.device)
+        self.row_q_probs = torch.zeros((max_lanes, self.gen.q_ids.shape[2]), dtype=torch.float32, device=self.gen.device)
 
     # ---- Program API ----
     def free_lanes(self) -> int:
@@ -493,11 +550,16 @@ class SpeculativeProgram:
             torch.cuda.current_stream().synchronize()
             first = int(g.out_host[0])
             nxt = nxt + [first]
-        # the draft module reads the same positions (hidden state of p + token p + 1)
+        # the draft module reads the same positions (hidden state of p + token p + 1); the first draft of a finished
+        # prompt is drawn under this lane's own sampling parameters
+        if done:
+            g.sampling, g.lengths = [lane.sampling], [lane.n_cached + n]
         g._mtp_pass(batch, g.h_keep[:n], g._upload_next(nxt), [0] if done else [])
         if done:
             self.row_draft[lane.row] = g.drafts[0, 0]
             self.row_mtp_h[lane.row].copy_(g.mtp_h[0])
+            self.row_q_ids[lane.row].copy_(g.q_ids[0, 0])
+            self.row_q_probs[lane.row].copy_(g.q_probs[0, 0])
         lane.n_cached += n
         g.model.status.check("after speculative prefill")
         if done:
@@ -518,9 +580,13 @@ class SpeculativeProgram:
         g.sampling = [l.sampling for l in lanes]
         g.drafts[:B, 0] = self.row_draft[rows]
         g.mtp_h[:B] = self.row_mtp_h[rows]
+        g.q_ids[:B, 0] = self.row_q_ids[rows]
+        g.q_probs[:B, 0] = self.row_q_probs[rows]
         emitted = g.decode_round()
         self.row_draft[rows] = g.drafts[:B, 0]
         self.row_mtp_h[rows] = g.mtp_h[:B]
+        self.row_q_ids[rows] = g.q_ids[:B, 0]
+        self.row_q_probs[rows] = g.q_probs[:B, 0]
         for l, toks in zip(lanes, emitted):
             l.tokens.append(l.last_token)
             l.tokens.extend(toks[:-1])

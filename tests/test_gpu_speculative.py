@@ -168,3 +168,37 @@ def test_tree_with_mtp_drafts_runs():
     out = gen.generate(prompts, 16)
     agree, total = _teacher_forced_agreement(cfg, w, prompts, out)
     assert total > 12 and agree / total >= 0.9, f"{agree}/{total}"
+
+
+def test_stochastic_mtp_drafts_run_reproducibly_and_keep_the_greedy_stream():
+    """The draft module samples its proposals and hands its distribution q to the verifier (min(1, p / q) acceptance,
+    residual max(p - q, 0)).  Same seed -> same text; a greedy request in the same generator still produces the
+    plain greedy stream (its proposals and its acceptance stay arg-max); the kernel-level distribution test is
+    in test_gpu_ops.py."""
+    from ninfer_fusion_b200.runtime.program import SamplingParams
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cuda", seed=9, std=0.05, with_mtp=True)
+    prompts = [list(range(5, 45)), list(range(100, 118))]
+    plain = Generator(cfg, w, "cuda", max_batch=2, max_context=512, kv_format="bf16", page_size=16, prefill_chunk=64,
+                      use_graph=False).generate(prompts, 12)
+
+    def run(seed, stochastic, sampling=None):
+        sp = sampling or [SamplingParams(temperature=0.9, top_k=12, top_p=0.95, seed=seed), SamplingParams()]
+        gen = SpeculativeGenerator(cfg, w, "cuda", max_batch=2, max_context=512, draft_tokens=3, drafter="mtp",
+                                   sampling=sp, stochastic_drafts=stochastic, kv_format="bf16", page_size=16,
+                                   prefill_chunk=64)
+        assert gen.stochastic_drafts == stochastic
+        out = gen.generate(prompts, 12)
+        return out, gen
+    a, gen = run(21, True)
+    b, _ = run(21, True)
+    c, _ = run(22, True)
+    assert a == b and a[0] != c[0] and all(len(o) == 12 for o in a)
+    assert a[1] == plain[1] and c[1] == plain[1]            # the greedy request is untouched by its sampled neighbour
+    assert all(0 <= t < cfg.vocab for o in a for t in o) and gen.tokens_per_round >= 1.0
+    q = gen.q_probs[0, :3].sum(-1)                           # the kept distributions of the sampled sequence are normalised
+    assert torch.allclose(q, torch.ones_like(q), atol=1e-3)
+    # top_k = 1 under a non-zero temperature: the sampled machinery runs (q and p are both one at the arg-max, a wrong
+    # proposal is rejected and the residual is p), and the text must be the greedy text exactly
+    one, _ = run(5, True, [SamplingParams(temperature=0.9, top_k=1, seed=5), SamplingParams()])
+    assert one == plain
