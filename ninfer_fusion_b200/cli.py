@@ -42,9 +42,9 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--layers", type=int, default=0, help="shrink the geometry to this many layers (debug)")
     ap.add_argument("--tokenizer", help="tokenizer.json (overrides the artifact's embedded one)")
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
-    ap.add_argument("--weights", default="bf16", choices=["bf16", "fp8", "nvfp4", "q4", "q5", "q6", "w8", "stored"],
+    ap.add_argument("--weights", default="bf16", choices=["bf16", "fp8", "nvfp4", "q4", "q5", "q6", "w8", "q4+h64", "q4+h128", "q5+h64", "q6+h64", "w8+h64", "stored"],
                     help="matmul weight format on the device; q4/q5/q6/w8 keep groupwise-int codes and dequantise in the "
-                         "decode kernels; 'stored' keeps an artifact's groupwise-int tensors exactly as encoded")
+                         "decode kernels ('+h64': input dimension rotated by a block Hadamard first); 'stored' keeps an artifact's groupwise-int tensors exactly as encoded")
     ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8", "fp8h", "int8", "nvfp4"],
                     help="KV cache codec (fp8h = fp8 per-row with K in the Hadamard frame)")
     ap.add_argument("--kv-layer-spec", default="", help="per-layer KV storage, e.g. 'all:fp8' or '0-3:bf16,4-15:nvfp4'")

@@ -6,6 +6,7 @@
 #include <torch/library.h>
 
 #include "gemm_groupint.h"
+#include "../pointwise/hadamard.h"
 
 namespace {
 
@@ -96,9 +97,22 @@ void groupint_linear_pair(const Tensor& x, const Tensor& payload0, int64_t N0, c
   if (x.size(0) > 0) run_chunks(p, x, nullptr);
 }
 
+void hadamard_blocks(const Tensor& x, const Tensor& out, int64_t block) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "hadamard_blocks: x must be row-major bf16");
+  TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kBFloat16 && out.dim() == 2 && out.stride(1) == 1 &&
+              out.sizes() == x.sizes(), "hadamard_blocks: out must match x");
+  c10::cuda::CUDAGuard guard(x.device());
+  const char* err = nfb::hadamard_blocks(static_cast<const __nv_bfloat16*>(x.data_ptr()), x.stride(0),
+                                         static_cast<__nv_bfloat16*>(out.data_ptr()), out.stride(0),
+                                         static_cast<int>(x.size(0)), static_cast<int>(x.size(1)), static_cast<int>(block),
+                                         at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(err == nullptr, err ? err : "");
+}
+
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(nfb200, m) {
+  m.def("hadamard_blocks(Tensor x, Tensor out, int block) -> ()", &hadamard_blocks);
   m.def("groupint_linear(Tensor x, Tensor payload, int fmt, int N, int K, Tensor out, Tensor? resid) -> ()", &groupint_linear);
   m.def("groupint_linear_pair(Tensor x, Tensor payload0, int N0, Tensor payload1, int N1, int fmt, int K, Tensor out0, "
         "Tensor out1) -> ()", &groupint_linear_pair);

@@ -243,6 +243,7 @@ class HybridModel:
         self.sm_scale = 1.0 / math.sqrt(cfg.head_dim)
         # per-layer K row-scale tables ([n_kv_heads, head_dim] bf16), set by load_k_row_scale (kv/rowscale.py)
         self.k_row_scale: Dict[int, torch.Tensor] = {}
+        self._rot_scratch: Dict[tuple, torch.Tensor] = {}   # rotated activations of rotated groupwise-int weights
         self.cluster_splitk = True  # False: split-K through an fp32 workspace + reduce kernel
         self.attn_impl = 0  # 0 = pick, 1 = SIMT, 2 = tensor-core split-KV attention
         self.comm = None  # tensor-parallel communicator (parallel.tp), None on one GPU
@@ -326,6 +327,12 @@ class HybridModel:
             # groupwise-int codes are streamed as stored for decode-sized token counts (in-register dequant);
             # prefill chunks and the SwiGLU epilogue take the tcgen05 GEMM on a bf16 copy decoded once
             if x.shape[0] <= 32 and epi in (EPI_STORE, EPI_RESIDUAL) and w.usable_by_kernel():
+                if w.rot_block:   # codes hold W H: rotate the activations the same way (ops/rotation.py)
+                    key = (x.shape[0], x.shape[1])
+                    if key not in self._rot_scratch:
+                        self._rot_scratch[key] = torch.empty((x.shape[0], x.shape[1]), dtype=x.dtype, device=x.device)
+                    self.ops.hadamard_blocks(x, self._rot_scratch[key], w.rot_block)
+                    x = self._rot_scratch[key]
                 self.ops.groupint_linear(x, w.payload, w.fmt_id, w.shape[0], w.shape[1], out,
                                          resid if epi == EPI_RESIDUAL else None)
                 return

@@ -108,9 +108,13 @@ def quantize_tensor(name: str, t: torch.Tensor, weight_format: str):
     if weight_format == "bf16" or t.dim() != 2 or leaf not in QUANT_LEAVES or "/moe/" in name:
         return t
     N, K = t.shape
-    if weight_format in GROUPINT_FORMATS:
+    fmt, _, rot = weight_format.partition("+h")       # "q4+h64": Q4 codes of the weight with its input rotated
+    if fmt in GROUPINT_FORMATS:
         from ..ops.groupint import GroupIntWeight
-        return GroupIntWeight.from_dense(t, weight_format)
+        rot_block = int(rot) if rot else 0
+        if rot_block and K % rot_block:
+            rot_block = 0                                 # widths the block does not divide stay unrotated
+        return GroupIntWeight.from_dense(t, fmt, rot_block=rot_block)
     w = Q.interleave_gate_up(t) if leaf == "gate_up" else t
     if weight_format == "fp8":
         codes, scale = Q.quantize_fp8_row(w)

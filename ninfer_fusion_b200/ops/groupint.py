@@ -21,9 +21,9 @@ QT_GROUPINT = 3   # qtype tag beside ops.quant.QT_FP8_ROW (1) and QT_NVFP4 (2)
 
 class GroupIntWeight:
     """One [N, K] matmul weight as an encoded row-split object on the device."""
-    __slots__ = ("fmt", "payload", "shape", "qtype", "_dense")
+    __slots__ = ("fmt", "payload", "shape", "qtype", "_dense", "rot_block")
 
-    def __init__(self, fmt: str, payload: torch.Tensor, shape):
+    def __init__(self, fmt: str, payload: torch.Tensor, shape, rot_block: int = 0):
         if fmt not in FORMAT_IDS:
             raise ValueError(f"not a groupwise-int format: {fmt}")
         N, K = (int(s) for s in shape)
@@ -31,15 +31,21 @@ class GroupIntWeight:
         if payload.dtype != torch.uint8 or payload.numel() < need:
             raise ValueError(f"payload of {payload.numel()} bytes cannot hold a {fmt} [{N}, {K}] object ({need} bytes)")
         self.fmt, self.payload, self.shape, self.qtype, self._dense = fmt, payload, (N, K), QT_GROUPINT, None
+        # > 0: the codes hold W H (input dimension rotated block-wise, ops/rotation.py); consumers rotate x the same way
+        self.rot_block = int(rot_block)
 
     @classmethod
-    def from_dense(cls, w: torch.Tensor, fmt: str, device=None) -> "GroupIntWeight":
+    def from_dense(cls, w: torch.Tensor, fmt: str, device=None, rot_block: int = 0) -> "GroupIntWeight":
         fmt = SHORT_NAMES.get(fmt, fmt)
+        dev = device if device is not None else w.device
+        if rot_block:
+            from .rotation import fold
+            w = fold(w.detach().to("cpu", torch.float32), rot_block)
         w32 = w.detach().to("cpu", torch.float32).numpy()
         codes, scale = L.quantize_group_int(w32, fmt)
         raw = L.encode_row_split(codes, scale, fmt, w32.shape[1])
         payload = torch.from_numpy(np.frombuffer(raw, dtype=np.uint8).copy())
-        return cls(fmt, payload.to(device if device is not None else w.device), w.shape)
+        return cls(fmt, payload.to(dev), w.shape, rot_block)
 
     @property
     def fmt_id(self) -> int:
@@ -52,11 +58,20 @@ class GroupIntWeight:
         N, K = self.shape
         return N % 16 == 0 and K % 64 == 0
 
-    def dequant(self) -> torch.Tensor:
-        """Represented values, fp32 [N, K] on the CPU (the oracle's weight)."""
+    def dequant_stored(self) -> torch.Tensor:
+        """Values of the stored codes, fp32 [N, K] on the CPU (W H when the weight is rotated)."""
         raw = self.payload.cpu().numpy().tobytes()
         codes, scale = L.decode_row_split(raw, self.fmt, self.shape)
         return torch.from_numpy(L.dequant_row_split(codes, scale, self.fmt, self.shape[1]).astype(np.float32))
+
+    def dequant(self) -> torch.Tensor:
+        """Represented weight, fp32 [N, K] on the CPU (the oracle's weight): a rotated weight is rotated back,
+        H being its own inverse."""
+        w = self.dequant_stored()
+        if self.rot_block:
+            from .rotation import fold
+            w = fold(w, self.rot_block)
+        return w
 
     def dense(self) -> torch.Tensor:
         """bf16 copy on the device for token counts the streaming kernel is not meant for (made once, kept)."""
@@ -71,6 +86,9 @@ def linear(ops, x: torch.Tensor, w: GroupIntWeight, out: Optional[torch.Tensor] 
     N, K = w.shape
     if out is None:
         out = torch.empty((x.shape[0], N), dtype=torch.bfloat16, device=x.device)
+    if w.rot_block:
+        from .rotation import rotate
+        x = rotate(ops, x, w.rot_block)
     ops.groupint_linear(x, w.payload, w.fmt_id, N, K, out, resid)
     return out
 
@@ -79,6 +97,11 @@ def linear_pair(ops, x: torch.Tensor, w0: GroupIntWeight, w1: GroupIntWeight) ->
     """Two projections of one input in one launch (the reference's linear_pair: MTP K / V projections)."""
     if w0.fmt != w1.fmt or w0.shape[1] != w1.shape[1]:
         raise ValueError("linear_pair: both weights must share the format and the input width")
+    if w0.rot_block != w1.rot_block:
+        raise ValueError("linear_pair: both weights must share the input rotation")
+    if w0.rot_block:
+        from .rotation import rotate
+        x = rotate(ops, x, w0.rot_block)
     T = x.shape[0]
     o0 = torch.empty((T, w0.shape[0]), dtype=torch.bfloat16, device=x.device)
     o1 = torch.empty((T, w1.shape[0]), dtype=torch.bfloat16, device=x.device)
