@@ -205,6 +205,17 @@ def make_handler(state: ServeState):
             path = self.path.split("?", 1)[0].rstrip("/") or "/"
             if path == "/health":
                 return self._send_json(200, svc.health())
+            if path in ("/", "/console"):
+                # the browser console: a static page without data of its own, so it needs no key (its calls do)
+                from .console import page_bytes
+                data = page_bytes()
+                self.send_response(200)
+                self.send_header("Content-Type", "text/html; charset=utf-8")
+                self.send_header("Content-Length", str(len(data)))
+                self.send_header("Cache-Control", "no-store")
+                self.end_headers()
+                self.wfile.write(data)
+                return
             if not self._authorized():
                 return self._error(401, "invalid API key", "authentication_error")
             model_obj = {"id": svc.model_id, "object": "model", "created": int(svc.started), "owned_by": "ninfer-fusion-b200"}

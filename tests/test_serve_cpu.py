@@ -225,3 +225,20 @@ def test_service_finds_the_shared_system_prefix(server):
                                 temperature=0.0, session="u2"))
     assert a.error == "" and b.error == ""
     assert svc.engine.program.shared_stats["published"] == before + 1 and svc.engine.program.shared_stats["hits"] >= 1
+
+
+def test_browser_console_is_served_without_a_key_and_uses_public_routes(server):
+    port, _, _ = server
+    for path in ("/", "/console"):
+        status, ctype, data = call(port, "GET", path, key=None)
+        assert status == 200 and ctype.startswith("text/html")
+        page = data.decode("utf-8")
+        assert "<title>ninfer-fusion-b200 console</title>" in page
+        # it only ever calls routes any client can call, and sends the typed key as a bearer header
+        assert "/v1/chat/completions" in page and "/v1/models" in page and "/health" in page and "Bearer" in page
+    assert call(port, "GET", "/v1/models", key=None)[0] == 401          # the API itself still wants the key
+    # what the page sends is accepted by the chat route
+    body = {"model": "tiny-dense:test", "messages": [{"role": "user", "content": "hi"}], "stream": True, "max_tokens": 4,
+            "temperature": 0.7, "enable_thinking": False}
+    status, ctype, data = call(port, "POST", "/v1/chat/completions", body)
+    assert status == 200 and ctype.startswith("text/event-stream") and sse_events(data)[-1][1] == "[DONE]"
