@@ -44,7 +44,10 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_prefill_kernel(const P
 
   pdl_launch_next();
   pdl_wait_prior();
-  const int blk = blockIdx.x, kvh = blockIdx.y;
+  // Longest first: a later query block of a causal prompt sees more keys, and CTAs are handed out in grid order, so
+  // the grid runs the blocks from the last to the first (all KV heads of a block side by side); the short blocks
+  // then fill the tail of the last wave instead of one long block running alone.
+  const int kvh = blockIdx.x, blk = static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = p.n_q_heads / p.n_kv_heads;
   const int t0 = p.blk_start[blk];
@@ -283,7 +286,7 @@ cudaError_t launch_fmt(const PrefillAttnParams& p, cudaStream_t stream, bool pdl
     attr_set = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(p.n_blocks, p.n_kv_heads);
+  cfg.gridDim = dim3(p.n_kv_heads, p.n_blocks);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = sizeof(PrefillSmem);
   cfg.stream = stream;
