@@ -63,6 +63,14 @@ struct PagedAttnParams {
   const int* tree_base;
   int impl;  // 0 = pick, 1 = SIMT kernel, 2 = tensor-core (mma.sync) kernel
   int window = 0;  // sliding window: a query sees only its last `window` keys (0 = all of them)
+  // Selected-block attention (optional, decode only): query t attends to sel_count[t] blocks of four consecutive
+  // tokens, block ids in sel_blocks[t * sel_stride ..] (each below the number of complete blocks, kv_len / 4), plus
+  // the tokens of the last incomplete block [4 * (kv_len / 4), kv_len).  The splits then cover ordinals of that
+  // gathered key list instead of absolute positions.  Not combined with a window or a tree mask.
+  // (Reference: include/ninfer/ops/selected_block_attention.h, query-selected sparse attention of the FlashNext target.)
+  const int* sel_blocks = nullptr;
+  const int* sel_count = nullptr;
+  int sel_stride = 0;
 };
 // Split-KV paged attention over quantised pages with in-register dequantisation,
 // followed by the (m, l, o) merge fused with the output sigmoid gate.

@@ -61,8 +61,14 @@ __global__ void __launch_bounds__(kWarps * 32) paged_attn_split_kernel(const Pag
   pdl_wait_prior();
   const int t = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kv_len = p.q_kv_len[t];
   const int seq = p.q_seq[t];
+  // selected-block mode: the key list is sel_count blocks of four tokens + the incomplete last block, addressed by ordinal
+  const bool selected = p.sel_blocks != nullptr;
+  const int real_len = p.q_kv_len[t];
+  const int sel_keys = selected ? 4 * p.sel_count[t] : 0;
+  const int sel_tail0 = (real_len / 4) * 4;                       // first token of the incomplete block
+  const int kv_len = selected ? sel_keys + (real_len - sel_tail0) : real_len;
+  const int* sel = selected ? p.sel_blocks + static_cast<long long>(t) * p.sel_stride : nullptr;
   // a sliding window drops the keys before kv_len - window; the split then starts at the window's edge
   const int k_begin = max(split * p.split_keys, p.window > 0 ? kv_len - p.window : 0);
   const int k_end = min(kv_len, (split + 1) * p.split_keys);
@@ -109,8 +115,9 @@ __global__ void __launch_bounds__(kWarps * 32) paged_attn_split_kernel(const Pag
 #pragma unroll
     for (int g = 0; g < G; ++g) s[g] = 0.f;
     if (valid) {
-      const int page = table[key / P];
-      r = (static_cast<long long>(page) * p.kv.n_kv_heads + kvh) * P + key % P;
+      const int pos = !selected ? key : key < sel_keys ? sel[key >> 2] * 4 + (key & 3) : sel_tail0 + key - sel_keys;
+      const int page = table[pos / P];
+      r = (static_cast<long long>(page) * p.kv.n_kv_heads + kvh) * P + pos % P;
 #pragma unroll 4
       for (int c = 0; c < D / 8; ++c) {
         float kf[8];
@@ -289,12 +296,16 @@ const char* paged_attention(const PagedAttnParams& p, cudaStream_t stream, bool 
   if (p.n_q_heads % p.n_kv_heads) return "paged_attention: q heads must be a multiple of kv heads";
   if (p.split_keys <= 0 || p.split_keys % 128) return "paged_attention: split_keys must be a positive multiple of 128";
   if (p.n_splits < 1) return "paged_attention: need at least one split";
+  if (p.sel_blocks != nullptr) {
+    if (p.sel_count == nullptr || p.sel_stride <= 0) return "paged_attention: selection needs counts and a row stride";
+    if (p.window > 0 || p.tree_mask != nullptr) return "paged_attention: selection excludes a window or a tree mask";
+  }
   if (p.gate != nullptr && (p.ld_gate % 4 || reinterpret_cast<uintptr_t>(p.gate) % 8))
     return "paged_attention: gate rows must be 8-byte aligned";
   const int G = p.n_q_heads / p.n_kv_heads;
   const dim3 grid(p.Tq, p.n_kv_heads, p.n_splits);
   cudaError_t e = cudaErrorNotSupported;
-  if (p.impl != 1) {
+  if (p.impl != 1 && p.sel_blocks == nullptr) {   // the gathered key list runs on the SIMT kernel
     e = paged_attention_mma_split(p, stream, pdl);
     if (e == cudaErrorNotSupported && p.impl == 2) return "paged_attention: geometry not supported by the tensor-core kernel";
   }

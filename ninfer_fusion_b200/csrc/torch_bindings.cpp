@@ -236,7 +236,8 @@ void paged_attention(const Tensor& q, int64_t n_q_heads, int64_t n_kv_heads, int
                      const Tensor& q_kv_len, const Tensor& block_table, const Tensor& k_codes, const Tensor& v_codes,
                      OptT k_scales, OptT v_scales, int64_t page_size, int64_t format, int64_t group, double sm_scale,
                      int64_t split_keys, int64_t n_splits, const Tensor& part_o, const Tensor& part_ml, OptT gate,
-                     const Tensor& out, OptT tree_mask, OptT tree_base, int64_t impl, bool pdl, int64_t window) {
+                     const Tensor& out, OptT tree_mask, OptT tree_base, int64_t impl, bool pdl, int64_t window,
+                     OptT sel_blocks, OptT sel_count) {
   need(q, at::kBFloat16, "q"); need(q_seq, at::kInt, "q_seq"); need(q_kv_len, at::kInt, "q_kv_len");
   need(block_table, at::kInt, "block_table"); need(part_o, at::kFloat, "part_o"); need(part_ml, at::kFloat, "part_ml");
   need(out, at::kBFloat16, "out");
@@ -276,6 +277,15 @@ void paged_attention(const Tensor& q, int64_t n_q_heads, int64_t n_kv_heads, int
   p.impl = static_cast<int>(impl);
   TORCH_CHECK(window >= 0, "window must be >= 0");
   p.window = static_cast<int>(window);
+  if (sel_blocks.has_value() && sel_blocks->defined()) {
+    TORCH_CHECK(sel_count.has_value() && sel_count->defined(), "sel_count required with sel_blocks");
+    need(*sel_blocks, at::kInt, "sel_blocks"); need(*sel_count, at::kInt, "sel_count");
+    TORCH_CHECK(sel_blocks->dim() == 2 && sel_blocks->is_contiguous() && sel_blocks->size(0) == p.Tq &&
+                sel_count->numel() == p.Tq, "selection: sel_blocks [Tq, max_blocks], sel_count [Tq]");
+    p.sel_blocks = static_cast<const int*>(sel_blocks->data_ptr());
+    p.sel_count = static_cast<const int*>(sel_count->data_ptr());
+    p.sel_stride = static_cast<int>(sel_blocks->size(1));
+  }
   chk(nfb::paged_attention(p, cur_stream(), pdl));
 }
 
@@ -678,7 +688,7 @@ TORCH_LIBRARY(nfb200, m) {
   m.def("add_rmsnorm(Tensor? partial, int splits, Tensor? delta, Tensor? resid_in, Tensor? resid_out, Tensor? norm_w, Tensor? normed, int T, int N, float eps, bool unit_offset, bool pdl, Tensor? q_codes=None, Tensor? q_sf=None) -> ()", &add_rmsnorm);
   m.def("embed_gather(Tensor ids, Tensor table, Tensor out, bool pdl) -> ()", &embed_gather);
   m.def("attn_prep(Tensor proj, int q_off, int k_off, int v_off, int n_q_heads, int n_kv_heads, int head_dim, Tensor? q_norm_w, Tensor? k_norm_w, float eps, bool unit_offset, int rot_dim, Tensor inv_freq, float attn_factor, Tensor rope_pos, Tensor token_seq, Tensor cache_pos, Tensor block_table, Tensor q_out, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, bool pdl, bool k_hadamard=False, Tensor? k_row_scale=None) -> ()", &attn_prep);
-  m.def("paged_attention(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, int split_keys, int n_splits, Tensor part_o, Tensor part_ml, Tensor? gate, Tensor out, Tensor? tree_mask, Tensor? tree_base, int impl, bool pdl, int window=0) -> ()", &paged_attention);
+  m.def("paged_attention(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, int split_keys, int n_splits, Tensor part_o, Tensor part_ml, Tensor? gate, Tensor out, Tensor? tree_mask, Tensor? tree_base, int impl, bool pdl, int window=0, Tensor? sel_blocks=None, Tensor? sel_count=None) -> ()", &paged_attention);
   m.def("paged_attention_prefill(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor blk_start, Tensor blk_count, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, Tensor? gate, Tensor out, bool pdl, int window=0) -> ()", &paged_attention_prefill);
   m.def("prefill_attn_block_tokens(int n_q_heads, int n_kv_heads) -> int", &prefill_attn_block_tokens);
   m.def("causal_conv1d_silu(Tensor x, int c_off, int C, Tensor w, Tensor cu_seqlens, Tensor token_seq, Tensor state_slot, Tensor conv_state, Tensor out, bool update_state, bool one_token_per_seq, bool pdl, Tensor? seq_end=None, bool state_only=False, Tensor? parent=None, Tensor? last_token=None) -> ()", &causal_conv1d_silu);

@@ -159,6 +159,19 @@ def gqa_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_len: tor
     return torch.einsum("hqk,khd->qhd", p, vv)
 
 
+def selected_block_mask(kv_len: torch.Tensor, sel_blocks: torch.Tensor, sel_count: torch.Tensor, n_keys: int) -> torch.Tensor:
+    """Visibility of selected-block attention: query i sees the 4-token blocks sel_blocks[i, :sel_count[i]] and the
+    tokens of its incomplete last block [4 * (kv_len // 4), kv_len).  Returns bool [Tq, n_keys] for gqa_attention."""
+    Tq = kv_len.numel()
+    vis = torch.zeros((Tq, n_keys), dtype=torch.bool)
+    for i in range(Tq):
+        n = int(kv_len[i])
+        for b in sel_blocks[i, : int(sel_count[i])].tolist():
+            vis[i, 4 * b: 4 * b + 4] = True
+        vis[i, (n // 4) * 4: n] = True
+    return vis
+
+
 # ----------------------------------------------------------------------------
 # Gated DeltaNet
 # ----------------------------------------------------------------------------

@@ -439,3 +439,65 @@ def test_speculative_sampling_with_a_stochastic_drafter(ops):
     ops.sample_rows(tl, temp, topk, None, None, None, None, None, seeds, pos, 3, d_tok, None, None, None, None, None, q_ids, q_pr)
     ops.sample_rows(tl, temp, topk, None, None, None, None, None, seeds, pos, 0, out, None, d_tok, acc, q_ids, q_pr)
     assert acc.sum().item() == n and torch.equal(out, d_tok)
+
+
+@pytest.mark.parametrize("fmt_name", ["bf16", "fp8"])
+def test_selected_block_attention(ops, fmt_name):
+    """Decode attention over a query-selected list of 4-token blocks plus the incomplete last block, against the
+    dense oracle with the matching visibility mask; two splits of the gathered key list, scattered pages."""
+    torch.manual_seed(5)
+    hq, hkv, D, P = 12, 2, 256, 16
+    lens = [203, 64, 1030]                        # tails of 3, 0 and 2 tokens
+    B = len(lens)
+    max_pages = (max(lens) + P - 1) // P
+    n_pages = B * max_pages + 2
+    table = torch.randperm(n_pages)[: B * max_pages].int().view(B, max_pages).cuda()
+    fmt = R.KV_BF16 if fmt_name == "bf16" else R.KV_FP8_ROW
+    k_codes, v_codes, k_sc, v_sc = _planes(n_pages, hkv, P, D, fmt, D)
+    ks, vs = [], []
+    for b, n in enumerate(lens):
+        k, v = torch.randn(n, hkv, D), torch.randn(n, hkv, D)
+        kq, vq = R.kv_quant_dequant(k, fmt, 64), R.kv_quant_dequant(v, fmt, 64)
+        ks.append(kq); vs.append(vq)
+        for t in range(n):
+            page = int(table[b, t // P])
+            for h in range(hkv):
+                if fmt == R.KV_BF16:
+                    k_codes[page, h, t % P] = k[t, h].to(torch.bfloat16).view(torch.uint8).cuda()
+                    v_codes[page, h, t % P] = v[t, h].to(torch.bfloat16).view(torch.uint8).cuda()
+                else:
+                    for src, codes, sc in ((k[t, h], k_codes, k_sc), (v[t, h], v_codes, v_sc)):
+                        x = R.bf16_round(src.float())
+                        s_ = (x.abs().amax() / 448.0).clamp(2.0 ** -24, 65504.0).to(torch.float16)
+                        c = (x / s_.float()).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+                        codes[page, h, t % P] = c.view(torch.uint8).cuda()
+                        sc[page, h, t % P] = s_.reshape(1).view(torch.uint8).cuda()
+    max_sel = 160
+    sel = torch.zeros((B, max_sel), dtype=torch.int32)
+    cnt = torch.zeros(B, dtype=torch.int32)
+    for b, n in enumerate(lens):
+        complete = n // 4
+        c = min(max_sel, max(1, complete // 2))
+        pick = torch.randperm(complete)[:c].sort().values if b != 1 else torch.randperm(complete)[:c]   # order is free
+        sel[b, :c] = pick.int()
+        cnt[b] = c
+    q = torch.randn(B, hq, D).to(torch.bfloat16).cuda()
+    kv_len = torch.tensor(lens, dtype=torch.int32)
+    split_keys = 384
+    n_splits = (4 * max_sel + 3 + split_keys - 1) // split_keys
+    part_o = torch.empty(B * hq * n_splits * D, device="cuda")
+    part_ml = torch.empty(B * hq * n_splits * 2, device="cuda")
+    out = torch.empty((B, hq * D), dtype=torch.bfloat16, device="cuda")
+    ops.paged_attention(q, hq, hkv, D, torch.arange(B).int().cuda(), kv_len.cuda(), table, k_codes, v_codes, k_sc, v_sc, P,
+                        fmt, D, 1 / 16, split_keys, n_splits, part_o, part_ml, None, out, None, None, 0, False, 0,
+                        sel.cuda(), cnt.cuda())
+    torch.cuda.synchronize()
+    for b, n in enumerate(lens):
+        vis = R.selected_block_mask(kv_len[b:b + 1], sel[b:b + 1], cnt[b:b + 1], n)
+        ref = R.gqa_attention(q[b:b + 1].float().cpu(), ks[b], vs[b], None, 1 / 16, vis).reshape(-1)
+        err = (out[b].float().cpu() - ref).abs().max().item()
+        assert err < 0.02, (fmt_name, b, err)
+    with pytest.raises(RuntimeError, match="excludes a window"):
+        ops.paged_attention(q, hq, hkv, D, torch.arange(B).int().cuda(), kv_len.cuda(), table, k_codes, v_codes, k_sc, v_sc,
+                            P, fmt, D, 1 / 16, split_keys, n_splits, part_o, part_ml, None, out, None, None, 0, False, 128,
+                            sel.cuda(), cnt.cuda())
