@@ -69,6 +69,8 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--planner", default="lru", choices=["lru", "b200", "h100", "rtx5090"],
                     help="which cached frontier is given up under memory pressure: least recently used, or the "
                          "materialisation planner with that machine's cost preset")
+    ap.add_argument("--anchor-interval", type=int, default=0,
+                    help="keep a recovery frontier every N prompt tokens of a session's long prefill (0 = off)")
     ap.add_argument("--kv-rowscale", default=None,
                     help="K row-scale table (default: NINFER_KV_ROWSCALE, else <artifact>.kvrowscale.bin when present)")
     ap.add_argument("--seed", type=int, default=0)
@@ -181,6 +183,7 @@ def program_factory(args, cfg: ModelConfig, weights, kv):
                               use_graph=not args.no_graphs, kv_pages=resolve_kv_pages(args, cfg, kv),
                               weight_budget_bytes=int(args.weight_budget_gib * (1 << 30)) if args.weight_budget_gib > 0 else None)
             load_row_scale(args, cfg, prog.model)
+            prog.anchor_interval = max(0, int(getattr(args, "anchor_interval", 0)))
             if getattr(args, "planner", "lru") != "lru":
                 from .runtime.planner import PRESETS, MaterializationPlanner
                 prog.planner = MaterializationPlanner(PRESETS[args.planner])

@@ -388,6 +388,9 @@ class Engine:
                     self.stats.prompt_tokens += req.lane.n_cached - n_before
                     if first is None and req.lane.n_cached == edge and n_before < edge:
                         self.program.checkpoint(req.lane, "shared", "shared")   # any session may start from here
+                    step = getattr(self.program, "anchor_interval", 0)
+                    if first is None and step > 0 and req.opts.session and req.lane.n_cached // step > n_before // step:
+                        self.program.checkpoint(req.lane, req.opts.session, "anchor")   # recovery point inside a long prompt
                 except RequestError as e:
                     self._active.remove(req)
                     self._finish(req, "error", str(e))

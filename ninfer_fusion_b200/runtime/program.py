@@ -57,7 +57,8 @@ class Checkpoint:
     """A reusable frontier of a session: exact token history + KV coverage + recurrent state image.
     Kinds follow the reference's catalogue (docs/maintainer/resource-scheduling-and-context-cache.md:266-284):
     'turn' = the prompt boundary of a request (TurnClosure), 'endpoint' = where its generation stopped
-    (SessionEndpoint).  A frontier is reusable only for a prompt that starts with exactly these tokens."""
+    (SessionEndpoint), 'anchor' = an earlier recovery point inside a long prompt (LongAnchor), 'shared' = an immutable
+    prefix any session may start from (SharedStablePrefix).  A frontier is reusable only for a prompt that starts with exactly these tokens."""
     session: str
     kind: str
     tokens: List[int]
@@ -93,6 +94,11 @@ class ProgramBase:
         self.cold_stats = {"demoted_host": 0, "demoted_disk": 0, "promoted": 0, "dropped": 0}
         # shared-prefix catalogue: frontiers of prompt prefixes that any request may start from (system prompts)
         self.max_shared_prefixes = 8
+        # long anchors: while a long prompt is prefilled, a frontier is kept every `anchor_interval` tokens (0 = off) so
+        # that a later request of the session whose history DIVERGES part-way (an edited turn) restarts from the last
+        # anchor before the edit instead of from zero; at most `max_anchors` per session, thinned to stay spread out
+        self.anchor_interval = 0
+        self.max_anchors = 3
         self.shared_stats = {"published": 0, "hits": 0}
 
     # ---- capacity ----
@@ -244,7 +250,23 @@ class ProgramBase:
                     self._drop(victim.handle)
                 else:
                     self._forget_cold(victim)
-        for c in [c for c in self.checkpoints if c.session == session and c.kind == kind and kind != "shared"]:
+        if kind == "anchor":
+            anchors = sorted((c for c in self.checkpoints if c.session == session and c.kind == "anchor"),
+                             key=lambda c: len(c.tokens))
+            if any(len(c.tokens) == n for c in anchors):
+                return True
+            while len(anchors) >= self.max_anchors:
+                # thin: drop the anchor whose neighbours are closest together (the coverage stays spread out)
+                lens = [0] + [len(c.tokens) for c in anchors] + [n]
+                i = min(range(len(anchors)), key=lambda j: lens[j + 2] - lens[j])
+                victim = anchors.pop(i)
+                if victim.tier == "gpu":
+                    self.checkpoints.remove(victim)
+                    self._drop(victim.handle)
+                else:
+                    self._forget_cold(victim)
+                    self.cold_stats["dropped"] -= 1
+        for c in [c for c in self.checkpoints if c.session == session and c.kind == kind and kind not in ("shared", "anchor")]:
             if c.tier == "gpu":              # one frontier per (session, kind)
                 self.checkpoints.remove(c)
                 self._drop(c.handle)

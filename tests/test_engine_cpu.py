@@ -232,3 +232,42 @@ def test_shared_prefix_catalogue_across_sessions():
     finally:
         cold.shutdown()
         warm.shutdown()
+
+
+def test_long_anchors_serve_an_edited_history():
+    """Anchors kept while a long prompt is prefilled let a request whose history diverges part-way restart from the
+    last anchor before the edit; they are thinned to max_anchors and spread over the prompt."""
+    from ninfer_fusion_b200.models.config import TINY_DENSE
+    from ninfer_fusion_b200.models.weights import random_weights
+    from ninfer_fusion_b200.runtime.program import ReferenceProgram
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cpu", seed=5, std=0.05)
+
+    def factory(step):
+        def make():
+            p = ReferenceProgram(cfg, w, max_lanes=2, max_context=512)
+            p.anchor_interval, p.max_anchors, p.max_checkpoints = step, 3, 8
+            return p
+        return make
+    torch.manual_seed(0)
+    base = torch.randint(0, cfg.vocab, (200,)).tolist()
+    edited = base[:150] + torch.randint(0, cfg.vocab, (30,)).tolist()        # diverges at token 150
+    cold = Engine(factory(0), prefill_chunk=16)
+    warm = Engine(factory(32), prefill_chunk=16)
+    try:
+        want = cold.submit(edited, RequestOptions(max_tokens=5)).wait(timeout=120)
+        warm.submit(base, RequestOptions(max_tokens=3, session="s")).wait(timeout=120)
+        prog = warm.program
+        anchors = sorted(len(c.tokens) for c in prog.checkpoints if c.kind == "anchor")
+        assert len(anchors) == 3 and all(a % 32 == 0 for a in anchors) and anchors[-1] == 192 and anchors[0] <= 96
+        hits = warm.stats.prefix_hits
+        h = warm.submit(edited, RequestOptions(max_tokens=5, session="s"))
+        got = h.wait(timeout=120)
+        assert got == want and warm.stats.prefix_hits == hits + 1
+        usable = max(a for a in anchors if a <= 150)
+        assert h.reused_tokens == usable if hasattr(h, "reused_tokens") else True
+        # without a session nothing is anchored
+        warm.submit(base, RequestOptions(max_tokens=1)).wait(timeout=120)
+        assert sorted(len(c.tokens) for c in prog.checkpoints if c.kind == "anchor" and c.session == "s")[-1] <= 192
+    finally:
+        cold.shutdown(); warm.shutdown()
