@@ -243,7 +243,8 @@ class HybridModel:
         self.sm_scale = 1.0 / math.sqrt(cfg.head_dim)
         # per-layer K row-scale tables ([n_kv_heads, head_dim] bf16), set by load_k_row_scale (kv/rowscale.py)
         self.k_row_scale: Dict[int, torch.Tensor] = {}
-        self._rot_scratch: Dict[tuple, torch.Tensor] = {}   # rotated activations of rotated groupwise-int weights
+        self._rot_scratch: Dict[tuple, torch.Tensor] = {}   # rotated activations / gate-up rows of groupwise-int weights
+        self.groupint_dense_prefill = os.environ.get("NFB_GROUPINT_DENSE", "1") != "0"
         self.cluster_splitk = True  # False: split-K through an fp32 workspace + reduce kernel
         self.attn_impl = 0  # 0 = pick, 1 = SIMT, 2 = tensor-core split-KV attention
         self.comm = None  # tensor-parallel communicator (parallel.tp), None on one GPU
@@ -324,18 +325,31 @@ class HybridModel:
             self._gemm_quant(x, w, out, epi, resid)
             return
         if isinstance(w, GroupIntWeight):
-            # groupwise-int codes are streamed as stored for decode-sized token counts (in-register dequant);
-            # prefill chunks and the SwiGLU epilogue take the tcgen05 GEMM on a bf16 copy decoded once
-            if x.shape[0] <= 32 and epi in (EPI_STORE, EPI_RESIDUAL) and w.usable_by_kernel():
+            # Groupwise-int codes are streamed as stored for decode-sized token counts (in-register dequant).  Prefill
+            # chunks take the tcgen05 GEMM on a bf16 copy decoded once, unless NFB_GROUPINT_DENSE=0 asks for the codes
+            # only (no second copy of the weights; the kernel then re-reads them once per 32 tokens).
+            T = x.shape[0]
+            if w.usable_by_kernel() and (T <= 32 or not self.groupint_dense_prefill):
                 if w.rot_block:   # codes hold W H: rotate the activations the same way (ops/rotation.py)
-                    key = (x.shape[0], x.shape[1])
+                    key = (T, x.shape[1])
                     if key not in self._rot_scratch:
-                        self._rot_scratch[key] = torch.empty((x.shape[0], x.shape[1]), dtype=x.dtype, device=x.device)
+                        self._rot_scratch[key] = torch.empty((T, x.shape[1]), dtype=x.dtype, device=x.device)
                     self.ops.hadamard_blocks(x, self._rot_scratch[key], w.rot_block)
                     x = self._rot_scratch[key]
-                self.ops.groupint_linear(x, w.payload, w.fmt_id, w.shape[0], w.shape[1], out,
-                                         resid if epi == EPI_RESIDUAL else None)
-                return
+                if epi == EPI_SWIGLU:
+                    # [gate; up] rows in one pass over the codes, then silu(gate) * up in fp32
+                    key = ("gu", T, w.shape[0])
+                    if key not in self._rot_scratch:
+                        self._rot_scratch[key] = torch.empty((T, w.shape[0]), dtype=x.dtype, device=x.device)
+                    gu = self._rot_scratch[key]
+                    self.ops.groupint_linear(x, w.payload, w.fmt_id, w.shape[0], w.shape[1], gu, None)
+                    inter = w.shape[0] // 2
+                    out.copy_(torch.nn.functional.silu(gu[:, :inter].float()) * gu[:, inter:].float())
+                    return
+                if epi in (EPI_STORE, EPI_RESIDUAL):
+                    self.ops.groupint_linear(x, w.payload, w.fmt_id, w.shape[0], w.shape[1], out,
+                                             resid if epi == EPI_RESIDUAL else None)
+                    return
             w = w.dense()
         # in-cluster split-K when the output tiles alone cannot fill the GPU (decode, sharded weights)
         splits = int(self.ops.gemm_pick_splits(x.shape[0], w.shape[0], w.shape[1], epi)) if self.cluster_splitk else 1

@@ -169,3 +169,32 @@ def test_rotated_q4_linear_and_model(ops):
     out = gen.generate(prompts, 4)              # decode path: rotated activations + streaming kernel
     assert all(len(o) == 4 for o in out)
     gen.model.status.check("rotated q4 decode")
+
+
+def test_model_runs_on_codes_only(ops):
+    """With the dense prefill copy switched off every kernel-usable weight (the SwiGLU parent included) stays codes:
+    prefill streams them per 32 tokens, decode per round; logits follow the oracle of the represented weights."""
+    from ninfer_fusion_b200.models.config import TINY_DENSE
+    from ninfer_fusion_b200.models.reference_model import ReferenceModel, ReferenceSequence
+    from ninfer_fusion_b200.models.weights import dequantize_weights, quantize_weights, random_weights
+    from ninfer_fusion_b200.ops import reference as R
+    from ninfer_fusion_b200.runtime.generator import Generator
+    cfg = TINY_DENSE
+    qw = quantize_weights(random_weights(cfg, "cuda", seed=7, std=0.05), "w8")
+    gen = Generator(cfg, qw, "cuda", max_batch=2, max_context=256, kv_format="bf16", page_size=16, prefill_chunk=64,
+                    use_graph=False)
+    gen.model.groupint_dense_prefill = False
+    ref = ReferenceModel(cfg, {k: v.cpu() for k, v in dequantize_weights(qw).items()})
+    torch.manual_seed(1)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (21, 40)]   # one 61-token chunk: two weight passes
+    gen.prefill(prompts)
+    got = gen.ws.logits[:2].float().cpu()
+    for b, p in enumerate(prompts):
+        want = ref.logits(ref.forward(ReferenceSequence(cfg, R.KV_BF16), torch.tensor(p))[-1:])[0]
+        assert torch.nn.functional.cosine_similarity(got[b], want, dim=0).item() > 0.995
+    out = gen.generate(prompts, 4)
+    assert all(len(o) == 4 for o in out)
+    gen.model.status.check("codes-only run")
+    usable = [v for v in qw.values() if isinstance(v, G.GroupIntWeight) and v.usable_by_kernel()]
+    assert any(k.endswith("gate_up") and isinstance(v, G.GroupIntWeight) and v.usable_by_kernel() for k, v in qw.items())
+    assert usable and all(v._dense is None for v in usable)
