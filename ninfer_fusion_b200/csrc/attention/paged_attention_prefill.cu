@@ -32,9 +32,10 @@ struct PrefillSmem {
   __half k[kTileKeys][kLdK];
   __half vt[D][kLdV];
   __half q[kRows][kLdQ];
-  float kscale[kTileKeys];
-  float vscale[kTileKeys];
-  long long rowidx[kTileKeys];
+  // double buffered: while a tile is gathered and multiplied, the page rows and scales of the next one are looked up
+  float kscale[2][kTileKeys];
+  float vscale[2][kTileKeys];
+  long long rowidx[2][kTileKeys];
 };
 
 template <int FORMAT>
@@ -102,65 +103,76 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_prefill_kernel(const P
 #pragma unroll
     for (int j = 0; j < 4; ++j) o[n][j] = 0.f;
 
-  for (int kb = k_first; kb < k_end; kb += kTileKeys) {
-    __syncthreads();  // previous tile consumed; Q stores ordered on the first pass
-    if (threadIdx.x < kTileKeys) {
-      const int key = kb + threadIdx.x;
-      long long r = -1;
-      float ks = 0.f, vs = 0.f;
-      if (key < k_end) {
-        const int page = table[key / P];
-        r = (static_cast<long long>(page) * p.kv.n_kv_heads + kvh) * P + key % P;
-        ks = 1.f;
-        vs = 1.f;
-        if constexpr (FORMAT == kKvFp8Row) {
-          ks = __half2float(reinterpret_cast<const __half*>(p.kv.k_scales)[r]);
-          vs = __half2float(reinterpret_cast<const __half*>(p.kv.v_scales)[r]);
-        }
+  // page row and scales of one key of the tile starting at `kb`, written to buffer `b` (threads 0..63)
+  auto lookup = [&](int kb, int b) {
+    const int key = kb + threadIdx.x;
+    long long r = -1;
+    float ks = 0.f, vs = 0.f;
+    if (key < k_end) {
+      const int page = table[key / P];
+      r = (static_cast<long long>(page) * p.kv.n_kv_heads + kvh) * P + key % P;
+      ks = 1.f;
+      vs = 1.f;
+      if constexpr (FORMAT == kKvFp8Row) {
+        ks = __half2float(reinterpret_cast<const __half*>(p.kv.k_scales)[r]);
+        vs = __half2float(reinterpret_cast<const __half*>(p.kv.v_scales)[r]);
       }
-      sm.rowidx[threadIdx.x] = r;
-      sm.kscale[threadIdx.x] = ks;
-      sm.vscale[threadIdx.x] = vs;
     }
-    __syncthreads();
-    {  // K: 1024 units of 16 values, 4 per thread
-      RawUnit<FORMAT> raw[4];
+    sm.rowidx[b][threadIdx.x] = r;
+    sm.kscale[b][threadIdx.x] = ks;
+    sm.vscale[b][threadIdx.x] = vs;
+  };
+  if (threadIdx.x < kTileKeys && k_first < k_end) lookup(k_first, 0);
+  int buf = 0;
+  for (int kb = k_first; kb < k_end; kb += kTileKeys, buf ^= 1) {
+    __syncthreads();  // previous tile consumed; Q stores and this tile's look-up ordered
+    {
+      // K: 1024 units of 16 values, 4 per thread; V: 512 (key pair, part) units, 2 per thread.  All eight gathers
+      // of a thread are issued before the first conversion, so a tile pays one L2 round trip instead of two (the
+      // kernel is latency bound: 8 warps per SM, long scoreboard the top stall).  bf16 units are 32 bytes each, too
+      // many registers to hold eight at once beside the 128 accumulator registers: that format loads K, then V.
+      constexpr bool kTogether = FORMAT != kKvBf16;
+      RawUnit<FORMAT> rk[4], rv[4];
 #pragma unroll
       for (int it = 0; it < 4; ++it) {
         const int u = it * kThreads + threadIdx.x;
-        const long long r = sm.rowidx[u >> 4];
-        raw[it].clear();
-        if (r >= 0) raw[it].load(p.kv, p.kv.k_codes, p.kv.k_scales, r, u & 15);
+        const long long r = sm.rowidx[buf][u >> 4];
+        rk[it].clear();
+        if (r >= 0) rk[it].load(p.kv, p.kv.k_codes, p.kv.k_scales, r, u & 15);
       }
+      auto load_v = [&]() {
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+          const int u = it * kThreads + threadIdx.x;
+          const int jp = u >> 4, part = u & 15;
+          const long long r0 = sm.rowidx[buf][2 * jp], r1 = sm.rowidx[buf][2 * jp + 1];
+          rv[2 * it].clear();
+          rv[2 * it + 1].clear();
+          if (r0 >= 0) rv[2 * it].load(p.kv, p.kv.v_codes, p.kv.v_scales, r0, part);
+          if (r1 >= 0) rv[2 * it + 1].load(p.kv, p.kv.v_codes, p.kv.v_scales, r1, part);
+        }
+      };
+      if constexpr (kTogether) load_v();
+      // the next tile's look-up (two dependent global reads) is issued behind this tile's gathers, so that it runs
+      // beside them instead of in front of them
+      if (threadIdx.x < kTileKeys && kb + kTileKeys < k_end) lookup(kb + kTileKeys, buf ^ 1);
 #pragma unroll
       for (int it = 0; it < 4; ++it) {
         const int u = it * kThreads + threadIdx.x;
         uint32_t h[8];
-        raw[it].convert(h);
+        rk[it].convert(h);
         uint4* dst = reinterpret_cast<uint4*>(&sm.k[u >> 4][(u & 15) * 16]);
         dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
         dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
       }
-    }
-    {  // V: 512 (key pair, part) units, 2 per thread, transposed + swizzled
-      RawUnit<FORMAT> raw[4];
-#pragma unroll
-      for (int it = 0; it < 2; ++it) {
-        const int u = it * kThreads + threadIdx.x;
-        const int jp = u >> 4, part = u & 15;
-        const long long r0 = sm.rowidx[2 * jp], r1 = sm.rowidx[2 * jp + 1];
-        raw[2 * it].clear();
-        raw[2 * it + 1].clear();
-        if (r0 >= 0) raw[2 * it].load(p.kv, p.kv.v_codes, p.kv.v_scales, r0, part);
-        if (r1 >= 0) raw[2 * it + 1].load(p.kv, p.kv.v_codes, p.kv.v_scales, r1, part);
-      }
+      if constexpr (!kTogether) load_v();
 #pragma unroll
       for (int it = 0; it < 2; ++it) {
         const int u = it * kThreads + threadIdx.x;
         const int jp = u >> 4, part = u & 15;
         uint32_t h0[8], h1[8];
-        raw[2 * it].convert(h0);
-        raw[2 * it + 1].convert(h1);
+        rv[2 * it].convert(h0);
+        rv[2 * it + 1].convert(h1);
         const int col = (2 * jp) ^ ((part & 7) * 8);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -202,7 +214,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_prefill_kernel(const P
       for (int j = 0; j < 4; ++j) {
         const int kl = n * 8 + 2 * cq + (j & 1);
         const bool valid = kb + kl < lim[j >> 1] && kb + kl >= lo[j >> 1];
-        const float v = valid ? s[n][j] * sm.kscale[kl] : -CUDART_INF_F;
+        const float v = valid ? s[n][j] * sm.kscale[buf][kl] : -CUDART_INF_F;
         s[n][j] = v;
         mx[j >> 1] = fmaxf(mx[j >> 1], v);
       }
@@ -224,7 +236,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_prefill_kernel(const P
       for (int j = 0; j < 4; ++j) {
         pv[j] = (s[n][j] == -CUDART_INF_F) ? 0.f : exp2f(s[n][j] - m_run[j >> 1]);
         l_run[j >> 1] += pv[j];
-        pv[j] *= sm.vscale[n * 8 + 2 * cq + (j & 1)];
+        pv[j] *= sm.vscale[buf][n * 8 + 2 * cq + (j & 1)];
       }
       pa[n][0] = pack_half2(pv[0], pv[1]);
       pa[n][1] = pack_half2(pv[2], pv[3]);
