@@ -37,6 +37,13 @@ int64_t bind_planes(const Tensor& payload, int64_t fmt, int64_t N, int64_t K, nf
   return total;
 }
 
+// optional device status word (int32[1]) that a bounded wait which ran out is recorded in
+int* status_ptr(OptT status) {
+  if (!status.has_value() || !status->defined()) return nullptr;
+  TORCH_CHECK(status->is_cuda() && status->scalar_type() == at::kInt && status->numel() >= 1, "groupint: status must be a CUDA int32 tensor");
+  return static_cast<int*>(status->data_ptr());
+}
+
 void check_act(const Tensor& x, int64_t K) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1 && x.size(1) == K,
               "groupint: x must be a row-major bf16 [T, K] matrix");
@@ -64,7 +71,8 @@ void run_chunks(nfb::GroupIntLinearParams p, const Tensor& x, const Tensor* resi
   }
 }
 
-void groupint_linear(const Tensor& x, const Tensor& payload, int64_t fmt, int64_t N, int64_t K, const Tensor& out, OptT resid) {
+void groupint_linear(const Tensor& x, const Tensor& payload, int64_t fmt, int64_t N, int64_t K, const Tensor& out, OptT resid,
+                     OptT status) {
   check_act(x, K);
   check_out(out, x.size(0), N, "out");
   c10::cuda::CUDAGuard guard(x.device());
@@ -73,6 +81,7 @@ void groupint_linear(const Tensor& x, const Tensor& payload, int64_t fmt, int64_
   bind_planes(payload, fmt, N, K, p.w[0]);
   p.w[0].out = static_cast<__nv_bfloat16*>(out.data_ptr()); p.w[0].ldo = out.stride(0);
   p.ldx = x.stride(0);
+  p.status = status_ptr(status);
   const Tensor* r = nullptr;
   if (resid.has_value() && resid->defined()) {
     check_out(*resid, x.size(0), N, "resid");
@@ -82,7 +91,7 @@ void groupint_linear(const Tensor& x, const Tensor& payload, int64_t fmt, int64_
 }
 
 void groupint_linear_pair(const Tensor& x, const Tensor& payload0, int64_t N0, const Tensor& payload1, int64_t N1, int64_t fmt,
-                          int64_t K, const Tensor& out0, const Tensor& out1) {
+                          int64_t K, const Tensor& out0, const Tensor& out1, OptT status) {
   check_act(x, K);
   check_out(out0, x.size(0), N0, "out0");
   check_out(out1, x.size(0), N1, "out1");
@@ -94,6 +103,7 @@ void groupint_linear_pair(const Tensor& x, const Tensor& payload0, int64_t N0, c
   p.w[0].out = static_cast<__nv_bfloat16*>(out0.data_ptr()); p.w[0].ldo = out0.stride(0);
   p.w[1].out = static_cast<__nv_bfloat16*>(out1.data_ptr()); p.w[1].ldo = out1.stride(0);
   p.ldx = x.stride(0);
+  p.status = status_ptr(status);
   if (x.size(0) > 0) run_chunks(p, x, nullptr);
 }
 
@@ -113,7 +123,7 @@ void hadamard_blocks(const Tensor& x, const Tensor& out, int64_t block) {
 
 TORCH_LIBRARY_FRAGMENT(nfb200, m) {
   m.def("hadamard_blocks(Tensor x, Tensor out, int block) -> ()", &hadamard_blocks);
-  m.def("groupint_linear(Tensor x, Tensor payload, int fmt, int N, int K, Tensor out, Tensor? resid) -> ()", &groupint_linear);
+  m.def("groupint_linear(Tensor x, Tensor payload, int fmt, int N, int K, Tensor out, Tensor? resid, Tensor? status=None) -> ()", &groupint_linear);
   m.def("groupint_linear_pair(Tensor x, Tensor payload0, int N0, Tensor payload1, int N1, int fmt, int K, Tensor out0, "
-        "Tensor out1) -> ()", &groupint_linear_pair);
+        "Tensor out1, Tensor? status=None) -> ()", &groupint_linear_pair);
 }

@@ -342,13 +342,13 @@ class HybridModel:
                     if key not in self._rot_scratch:
                         self._rot_scratch[key] = torch.empty((T, w.shape[0]), dtype=x.dtype, device=x.device)
                     gu = self._rot_scratch[key]
-                    self.ops.groupint_linear(x, w.payload, w.fmt_id, w.shape[0], w.shape[1], gu, None)
+                    self.ops.groupint_linear(x, w.payload, w.fmt_id, w.shape[0], w.shape[1], gu, None, self.status.tensor)
                     inter = w.shape[0] // 2
                     out.copy_(torch.nn.functional.silu(gu[:, :inter].float()) * gu[:, inter:].float())
                     return
                 if epi in (EPI_STORE, EPI_RESIDUAL):
                     self.ops.groupint_linear(x, w.payload, w.fmt_id, w.shape[0], w.shape[1], out,
-                                             resid if epi == EPI_RESIDUAL else None)
+                                             resid if epi == EPI_RESIDUAL else None, self.status.tensor)
                     return
             w = w.dense()
         # in-cluster split-K when the output tiles alone cannot fill the GPU (decode, sharded weights)
