@@ -69,6 +69,8 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--planner", default="lru", choices=["lru", "b200", "h100", "rtx5090"],
                     help="which cached frontier is given up under memory pressure: least recently used, or the "
                          "materialisation planner with that machine's cost preset")
+    ap.add_argument("--cold-slots", action="store_true",
+                    help="int8 KV pages leave the device as requantised cold slots (lossy, 0.55 of the bytes)")
     ap.add_argument("--anchor-interval", type=int, default=0,
                     help="keep a recovery frontier every N prompt tokens of a session's long prefill (0 = off)")
     ap.add_argument("--kv-rowscale", default=None,
@@ -184,6 +186,7 @@ def program_factory(args, cfg: ModelConfig, weights, kv):
                               weight_budget_bytes=int(args.weight_budget_gib * (1 << 30)) if args.weight_budget_gib > 0 else None)
             load_row_scale(args, cfg, prog.model)
             prog.anchor_interval = max(0, int(getattr(args, "anchor_interval", 0)))
+            prog.kv.cold_slots = bool(getattr(args, "cold_slots", False))
             if getattr(args, "planner", "lru") != "lru":
                 from .runtime.planner import PRESETS, MaterializationPlanner
                 prog.planner = MaterializationPlanner(PRESETS[args.planner])

@@ -168,6 +168,10 @@ class PagedKvCache:
             self.layers.append(KvLayerPlanes(fmt, group, k, v, ks, vs, hadamard))
         self.pool = PagePool(n_pages)
         self.host_arena = None   # optional runtime.host_arena.HostKvArena for the cold copies of exported pages
+        # Lossy cold copies: int8 group-64 layers leave the device as requantised cold slots (E2M1 codes + E4M3 scales
+        # per 16 values, 9232 bytes per 64 x 256 page plane instead of 16896) packed by a device kernel before the
+        # D2H copy; a page warmed from its slot is close to, not identical with, the page that was retired.
+        self.cold_slots = False
         self.max_rows = max_rows
         self.max_pages_per_row = max_pages_per_row
         pin = self.device.type == "cuda"
@@ -304,6 +308,18 @@ class PagedKvCache:
         out = []
         pin = self.device.type == "cuda"
         for l in self.layers:
+            if self._slot_layer(l):
+                from .._lib import load_native
+                ops = load_native()
+                D = self.cfg.head_dim
+                for codes, scales in ((l.k_codes, l.k_scales), (l.v_codes, l.v_scales)):
+                    c = codes.index_select(0, idx).view(torch.int8).reshape(-1, D)
+                    sc = scales.index_select(0, idx).view(torch.float16).reshape(-1, D // 64)
+                    dev = ops.cold_slot_pack_int8(c, sc, self.page_size)      # [pages * heads, slot bytes]
+                    host = torch.empty(dev.shape, dtype=dev.dtype, pin_memory=pin)
+                    host.copy_(dev, non_blocking=True)
+                    out.append(host)
+                continue
             for plane in (l.k_codes, l.v_codes, l.k_scales, l.v_scales):
                 if plane is None:
                     continue
@@ -325,11 +341,26 @@ class PagedKvCache:
         idx = torch.tensor(pages, dtype=torch.long, device=self.device)
         it = iter(planes)
         for l in self.layers:
+            if self._slot_layer(l):
+                from .._lib import load_native
+                ops = load_native()
+                D = self.cfg.head_dim
+                for codes, scales in ((l.k_codes, l.k_scales), (l.v_codes, l.v_scales)):
+                    slots = next(it).to(self.device, non_blocking=True)
+                    c, sc = ops.cold_slot_restore_int8(slots, self.page_size, D)
+                    codes.index_copy_(0, idx, c.view(torch.uint8).reshape(n_pages, self.n_kv_heads, self.page_size, D))
+                    scales.index_copy_(0, idx, sc.view(torch.uint8).reshape(n_pages, self.n_kv_heads, self.page_size, -1))
+                continue
             for plane in (l.k_codes, l.v_codes, l.k_scales, l.v_scales):
                 if plane is None:
                     continue
                 plane.index_copy_(0, idx, next(it).to(self.device, non_blocking=True))
         return pages
+
+    def _slot_layer(self, l: "KvLayerPlanes") -> bool:
+        """A layer whose cold copies are requantised slots: lossy copies switched on, int8 with 64-value groups, on a GPU."""
+        return (self.cold_slots and l.fmt == KV_INT8_GROUP and l.group == 64 and self.cfg.head_dim % 64 == 0
+                and self.device.type == "cuda")
 
     def drop_pages(self, pages: List[int]) -> None:
         for p in pages:
