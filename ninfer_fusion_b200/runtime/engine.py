@@ -46,6 +46,7 @@ class RequestOptions:
     session: Optional[str] = None            # continuation key for prefix reuse
     media: object = None                     # frontend.media.PreparedPrompt for a request with images / videos
     shared_prefix_tokens: int = 0            # publish the first N prompt tokens (system prompt) in the shared catalogue
+    replay_edge_tokens: int = 0              # session frontier before the generation opener (regenerate-this-response point)
 
 
 @dataclass
@@ -382,12 +383,18 @@ class Engine:
                     n_before = req.lane.n_cached
                     budget = self.governor.unit
                     edge = req.opts.shared_prefix_tokens
-                    if 0 < edge < len(req.prompt) and n_before < edge:
-                        budget = min(budget, edge - n_before)      # stop exactly at the shared boundary
+                    replay = req.opts.replay_edge_tokens if req.opts.session else 0
+                    for e in (edge, replay):
+                        if 0 < e < len(req.prompt) and n_before < e:
+                            budget = min(budget, e - n_before)     # stop exactly at the boundary
                     first = self.program.prefill_step(req.lane, budget)
                     self.stats.prompt_tokens += req.lane.n_cached - n_before
                     if first is None and req.lane.n_cached == edge and n_before < edge:
                         self.program.checkpoint(req.lane, "shared", "shared")   # any session may start from here
+                    if first is None and req.lane.n_cached == replay and n_before < replay:
+                        # the history up to, not including, the generation opener: a request that asks for this
+                        # response again (other sampling, other opener) starts here
+                        self.program.checkpoint(req.lane, req.opts.session, "replay")
                     step = getattr(self.program, "anchor_interval", 0)
                     if first is None and step > 0 and req.opts.session and req.lane.n_cached // step > n_before // step:
                         self.program.checkpoint(req.lane, req.opts.session, "anchor")   # recovery point inside a long prompt

@@ -57,7 +57,8 @@ class Checkpoint:
     """A reusable frontier of a session: exact token history + KV coverage + recurrent state image.
     Kinds follow the reference's catalogue (docs/maintainer/resource-scheduling-and-context-cache.md:266-284):
     'turn' = the prompt boundary of a request (TurnClosure), 'endpoint' = where its generation stopped
-    (SessionEndpoint), 'anchor' = an earlier recovery point inside a long prompt (LongAnchor), 'shared' = an immutable
+    (SessionEndpoint), 'replay' = the history before the generation opener (ResponseReplay), 'anchor' = an earlier
+    recovery point inside a long prompt (LongAnchor), 'shared' = an immutable
     prefix any session may start from (SharedStablePrefix).  A frontier is reusable only for a prompt that starts with exactly these tokens."""
     session: str
     kind: str

@@ -117,6 +117,19 @@ class GenerationService:
             return 0
         return n
 
+    def replay_edge_tokens(self, req: GenRequest, ids: Sequence[int]) -> int:
+        """Tokens of the rendered history without the generation opener (what the template appends to make the model
+        answer): the frontier a regenerated response restarts from.  0 when the prompt is not a chat or the opener
+        is not a clean token suffix."""
+        if req.messages is None or not req.messages or not req.session:
+            return 0
+        text = render_chat(req.messages, req.tools, add_generation_prompt=False, enable_thinking=req.enable_thinking)
+        head = self.tok.encode(text)
+        n = len(head)
+        if n == 0 or n >= len(ids) or list(ids[:n]) != head:
+            return 0
+        return n
+
     def count_tokens(self, req: GenRequest) -> int:
         return len(self.prepare(req))
 
@@ -153,6 +166,7 @@ class GenerationService:
             opts.media = media
             if media is None:
                 opts.shared_prefix_tokens = self.shared_prefix_tokens(req, ids)
+                opts.replay_edge_tokens = self.replay_edge_tokens(req, ids)
             handle = self.engine.submit(ids, opts)
             dec = StreamDecoder(self.tok, skip_special=True)
             # a chat prompt with thinking enabled continues inside an open reasoning frame only if the template

@@ -242,3 +242,21 @@ def test_browser_console_is_served_without_a_key_and_uses_public_routes(server):
             "temperature": 0.7, "enable_thinking": False}
     status, ctype, data = call(port, "POST", "/v1/chat/completions", body)
     assert status == 200 and ctype.startswith("text/event-stream") and sse_events(data)[-1][1] == "[DONE]"
+
+
+def test_response_replay_frontier(server):
+    """A chat request of a session leaves a frontier before the generation opener; asking for the same response again
+    (same history, thinking switched the other way, so another opener) starts from it."""
+    port, svc, _ = server
+    msgs = [{"role": "user", "content": "tell me about pages and frontiers " * 3}]
+    body = {"model": "tiny-dense:test", "messages": msgs, "max_tokens": 4, "user": "replay-session", "enable_thinking": True}
+    assert call(port, "POST", "/v1/chat/completions", body)[0] == 200
+    prog = svc.engine.program
+    kinds = {c.kind for c in prog.checkpoints if c.session == "replay-session"}
+    assert "replay" in kinds and "turn" in kinds
+    replay = next(c for c in prog.checkpoints if c.session == "replay-session" and c.kind == "replay")
+    turn = next(c for c in prog.checkpoints if c.session == "replay-session" and c.kind == "turn")
+    assert 0 < len(replay.tokens) < len(turn.tokens) and turn.tokens[:len(replay.tokens)] == replay.tokens
+    hits = svc.engine.stats.prefix_hits
+    assert call(port, "POST", "/v1/chat/completions", dict(body, enable_thinking=False))[0] == 200
+    assert svc.engine.stats.prefix_hits == hits + 1
