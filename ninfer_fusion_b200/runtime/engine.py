@@ -21,6 +21,7 @@ import time
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence
 
+from ..utils import trace
 from .program import Lane, ProgramBase, SamplingParams
 
 
@@ -387,7 +388,8 @@ class Engine:
                     for e in (edge, replay):
                         if 0 < e < len(req.prompt) and n_before < e:
                             budget = min(budget, e - n_before)     # stop exactly at the boundary
-                    first = self.program.prefill_step(req.lane, budget)
+                    with trace.span("engine", "prefill_chunk", budget=int(budget), cached=int(n_before)):
+                        first = self.program.prefill_step(req.lane, budget)
                     self.stats.prompt_tokens += req.lane.n_cached - n_before
                     if first is None and req.lane.n_cached == edge and n_before < edge:
                         self.program.checkpoint(req.lane, "shared", "shared")   # any session may start from here
@@ -413,7 +415,8 @@ class Engine:
         ready = [r for r in self._active if r.state == "decode"]
         if ready:
             t0 = time.perf_counter()
-            toks = self.program.decode_round([r.lane for r in ready])
+            with trace.span("engine", "decode_round", lanes=len(ready)):
+                toks = self.program.decode_round([r.lane for r in ready])
             dt = time.perf_counter() - t0
             self.stats.decode_s += dt
             self.stats.decode_rounds += 1

@@ -11,6 +11,8 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 import torch
 
+from ..utils import trace
+
 from ..models.config import ModelConfig
 from ..models.hybrid import HybridModel, ShardGeometry, StepBatch, Workspace
 from .batch import SeqChunk, StepBuffers
@@ -267,7 +269,8 @@ class GpuProgram(ProgramBase):
             bucket = context_bucket(max(l.n_cached for l in lanes) + 1)
             graph = self._graph_for(lanes, bucket, greedy)
             self.bufs_decode.build(self._chunks(lanes), upload=True, rope_delta=[l.rope_delta for l in lanes])
-            graph.replay()
+            with trace.span("graph", "replay", lanes=B):
+                graph.replay()
             ids = self.ws.next_ids[:B]
         else:
             batch = self.bufs_decode.build(self._chunks(lanes), upload=True, rope_delta=[l.rope_delta for l in lanes])
