@@ -86,10 +86,10 @@ class ClockSampler:
 
 
 def reference_arm(args) -> int:
-    # The reference is a CMake/C++ project without setup.py or pyproject.toml, so
-    # `pip install --target baseline/_ref /root/reference` fails ("not installable"); its CMake
+    # The reference is a CMake/C++ project without setup.py or pyproject.toml, so a
+    # `pip install --target baseline/_ref <reference tree>` fails ("not installable"); its CMake
     # build needs FFmpeg and libcurl development packages and CUDA >= 13.1 for sm_100a, none
-    # of which exist offline here.
+    # of which are available offline.
     print(json.dumps({"impl": "reference",
                       "unavailable": "reference is a CMake C++/CUDA project (no setup.py/pyproject: pip install "
                                      "refused; needs FFmpeg+libcurl dev libs and CUDA>=13.1 for sm_100a)"}))
