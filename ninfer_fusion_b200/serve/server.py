@@ -10,6 +10,7 @@ Reference: src/serve/http_server.cpp:408-500, docs/serving.md:66-73, :658-705, :
 from __future__ import annotations
 
 import json
+import socket
 import threading
 import time
 from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
@@ -21,6 +22,7 @@ from .request_log import RequestLog
 from .service import GenerationService, GenRequest, GenResult
 
 KEEPALIVE_S = 5.0
+DEAD_PEER_MS = 15000   # TCP_USER_TIMEOUT on accepted connections (0 = leave the kernel default)
 
 
 class _Keepalive:
@@ -75,6 +77,18 @@ def make_handler(state: ServeState):
 
         def log_message(self, fmt, *args):  # the JSONL log replaces the default stderr access log
             pass
+
+        def setup(self):
+            super().setup()
+            # Dead-peer detection: unacknowledged stream bytes (the 5-second keep-alive comments included) fail the
+            # connection after DEAD_PEER_MS instead of after the kernel's retransmission schedule (minutes), so a
+            # client that vanished stops costing decode rounds.  Linux only; elsewhere the write error comes later.
+            opt = getattr(socket, "TCP_USER_TIMEOUT", None)
+            if opt is not None and DEAD_PEER_MS > 0:
+                try:
+                    self.connection.setsockopt(socket.IPPROTO_TCP, opt, DEAD_PEER_MS)
+                except OSError:
+                    pass
 
         # ---------------------------------------------------------------- helpers
         def _send_json(self, code: int, obj: dict, headers: Optional[dict] = None) -> None:

@@ -3,6 +3,7 @@ import http.client
 import json
 import os
 import threading
+import time
 
 import pytest
 import torch
@@ -260,3 +261,27 @@ def test_response_replay_frontier(server):
     hits = svc.engine.stats.prefix_hits
     assert call(port, "POST", "/v1/chat/completions", dict(body, enable_thinking=False))[0] == 200
     assert svc.engine.stats.prefix_hits == hits + 1
+
+
+def test_dead_peer_timeout_is_set_on_accepted_connections(server):
+    import socket
+    from ninfer_fusion_b200.serve import server as S
+    if not hasattr(socket, "TCP_USER_TIMEOUT"):
+        pytest.skip("no TCP_USER_TIMEOUT on this platform")
+    port, _, _ = server
+    seen = {}
+    orig = S.BaseHTTPRequestHandler.finish
+
+    def spy(self):                                    # runs on the server thread while the connection is still open
+        seen["ms"] = self.connection.getsockopt(socket.IPPROTO_TCP, socket.TCP_USER_TIMEOUT)
+        orig(self)
+    S.BaseHTTPRequestHandler.finish = spy
+    try:
+        assert call(port, "GET", "/health", key=None)[0] == 200
+        for _ in range(100):
+            if "ms" in seen:
+                break
+            time.sleep(0.01)
+    finally:
+        S.BaseHTTPRequestHandler.finish = orig
+    assert seen.get("ms") == S.DEAD_PEER_MS == 15000
