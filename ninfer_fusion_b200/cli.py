@@ -326,6 +326,12 @@ def cmd_serve(args) -> int:
                                   RelayoutConfig(target_bits=args.kv_auto_relayout, period_s=args.kv_relayout_period),
                                   log=lambda rec: print(json.dumps(rec), file=sys.stderr, flush=True))
         relayout.start()
+    if getattr(args, "warmup", 0) > 0:
+        # one short generation before the port opens: kernels are loaded, decode graphs captured, pools touched
+        from .serve.service import GenRequest
+        t0 = time.perf_counter()
+        svc.generate(GenRequest(prompt="warm-up", max_tokens=int(args.warmup), temperature=0.0))
+        print(json.dumps({"warmup_s": round(time.perf_counter() - t0, 3)}), file=sys.stderr, flush=True)
     httpd = serve(svc, args.host, args.port, args.api_key, args.request_log)
     print(f"ninfer-serve: {name} on http://{args.host}:{httpd.server_address[1]}", file=sys.stderr, flush=True)
     try:
@@ -345,6 +351,49 @@ def cmd_inspect(args) -> int:
                                        "format": getattr(o, "format", None), "layout": getattr(o, "layout", None),
                                        "bytes": o.bytes} for o in rd.objects]}, indent=1))
     return 0
+
+
+def cmd_diff(args) -> int:
+    """Compares two artifacts object by object: presence, shape / format / layout, and for tensors the largest absolute
+    difference of the represented values (a re-quantised artifact against its source, two conversions of one model)."""
+    rows, worst = [], 0.0
+    with ArtifactReader(args.a) as ra, ArtifactReader(args.b) as rb:
+        names = sorted(set(ra.by_name) | set(rb.by_name))
+        for n in names:
+            oa, ob = ra.by_name.get(n), rb.by_name.get(n)
+            if oa is None or ob is None:
+                rows.append({"name": n, "status": "only_in_b" if oa is None else "only_in_a"})
+                continue
+            rec = {"name": n, "status": "same"}
+            if oa.kind != ob.kind:
+                rec["status"] = "kind_differs"
+            elif oa.kind == "resource":
+                if ra.resource(n) != rb.resource(n):
+                    rec["status"] = "bytes_differ"
+            else:
+                if tuple(oa.shape) != tuple(ob.shape):
+                    rec["status"] = "shape_differs"
+                    rec["shapes"] = [list(oa.shape), list(ob.shape)]
+                else:
+                    ta, tb = ra.tensor(n).float(), rb.tensor(n).float()
+                    d = float((ta - tb).abs().max()) if ta.numel() else 0.0
+                    scale = float(ta.abs().max()) if ta.numel() else 0.0
+                    worst = max(worst, d / scale if scale > 0 else d)
+                    if oa.format != ob.format or oa.layout != ob.layout:
+                        rec["status"] = "format_differs"
+                        rec["formats"] = [oa.format, ob.format]
+                    if d > 0:
+                        rec["max_abs_diff"] = d
+                        rec["relative"] = round(d / scale, 6) if scale > 0 else None
+                        if rec["status"] == "same":
+                            rec["status"] = "values_differ"
+            if rec["status"] != "same" or args.all:
+                rows.append(rec)
+    for r in rows:
+        print(json.dumps(r))
+    print(json.dumps({"objects": len(names), "reported": len(rows), "worst_relative_diff": round(worst, 6)}))
+    structural = any(r["status"] in ("only_in_a", "only_in_b", "kind_differs", "shape_differs", "bytes_differ") for r in rows)
+    return 1 if structural or worst > args.tolerance else 0
 
 
 def cmd_make_artifact(args) -> int:
@@ -482,6 +531,7 @@ def main(argv=None) -> int:
     s.add_argument("--max-concurrent", type=int, default=64)
     s.add_argument("--queue-timeout", type=float, default=30.0)
     s.add_argument("--request-log", default=None, help="JSONL request log path")
+    s.add_argument("--warmup", type=int, default=8, help="tokens of one warm-up generation before the port opens (0 = none)")
     s.set_defaults(fn=cmd_serve)
     i = sub.add_parser("inspect", help="print an artifact's directory")
     i.add_argument("path")
@@ -506,6 +556,11 @@ def main(argv=None) -> int:
     c.add_argument("--no-mtp", action="store_true", help="skip the draft module")
     c.add_argument("--to-hf", action="store_true", help="artifact -> safetensors with Hugging Face names")
     c.set_defaults(fn=cmd_convert)
+    d = sub.add_parser("diff", help="compare two artifacts (objects, formats, represented values)")
+    d.add_argument("a"); d.add_argument("b")
+    d.add_argument("--tolerance", type=float, default=0.0, help="largest accepted relative difference of a tensor")
+    d.add_argument("--all", action="store_true", help="list identical objects too")
+    d.set_defaults(fn=cmd_diff)
     k = sub.add_parser("packages", help="list the registered model packages and the capability gate's verdict")
     k.add_argument("--model", default=None)
     k.set_defaults(fn=cmd_packages)

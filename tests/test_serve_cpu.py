@@ -285,3 +285,20 @@ def test_dead_peer_timeout_is_set_on_accepted_connections(server):
     finally:
         S.BaseHTTPRequestHandler.finish = orig
     assert seen.get("ms") == S.DEAD_PEER_MS == 15000
+
+
+def test_artifact_diff(tmp_path, capsys):
+    a, b, c = (str(tmp_path / n) for n in ("a.ninfer", "b.ninfer", "c.ninfer"))
+    assert cli.main(["make-artifact", "--model", "tiny-dense", "--out", a]) == 0
+    assert cli.main(["make-artifact", "--model", "tiny-dense", "--out", b]) == 0
+    assert cli.main(["make-artifact", "--model", "tiny-dense", "--format", "W8G32_F16S", "--out", c]) == 0
+    capsys.readouterr()
+    assert cli.main(["diff", a, b]) == 0                                   # same seed, same bytes
+    summary = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert summary["reported"] == 0 and summary["worst_relative_diff"] == 0
+    assert cli.main(["diff", a, c]) == 1                                   # quantised copy: values differ, beyond tolerance 0
+    lines = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
+    changed = [l for l in lines[:-1] if l["status"] == "format_differs"]
+    assert changed and all(l["formats"] == ["BF16", "W8G32_F16S"] and 0 < l["relative"] < 0.02 for l in changed)
+    assert cli.main(["diff", a, c, "--tolerance", "0.02"]) == 0            # within the int8 envelope
+    capsys.readouterr()
