@@ -3,8 +3,8 @@
 Workload: 1 layer, 8 query heads / 2 KV heads, head_dim 128, 4 sequences of
 length 37 / 256 / 1000 / 2048, page size 16; Q/K/V bf16 drawn N(0,1) from a
 seed with 4 random K channels scaled x8 as outliers.  KV is stored as bf16,
-fp8-E4M3 with a per-row scale and int8 with group-32 scales (nvfp4 is reported
-too); the report gives the attention-output max / mean absolute error of each
+fp8-E4M3 with a per-row scale and int8 with group-32 scales (nvfp4, nvfp4 with the K
+row scale and the E8-lattice K tier are reported too); the report gives the attention-output max / mean absolute error of each
 codec against bf16 storage and the bytes per token.
 
 Run: ``python -m ninfer_fusion_b200.kv.codec_report``
@@ -37,7 +37,11 @@ def run(seed: int = 0, n_q_heads: int = 8, n_kv_heads: int = 2, head_dim: int = 
     # "+hadamard": K (and the query) rotated by the normalised Hadamard matrix before K is quantised, which spreads
     # the outlier channels over the row (the reference's fixed orthogonal K frame, src/ops/kv_cache/hadamard_d256.cuh)
     formats = [("bf16", R.KV_BF16, D), ("fp8-e4m3-row", R.KV_FP8_ROW, D), ("fp8-e4m3-row+hadamard", R.KV_FP8_ROW, D),
-               (f"int8-g{int8_group}", R.KV_INT8_GROUP, int8_group), ("nvfp4-g16", R.KV_NVFP4, 16)]
+               (f"int8-g{int8_group}", R.KV_INT8_GROUP, int8_group), ("nvfp4-g16", R.KV_NVFP4, 16),
+               # nvfp4 with the K row scale (per-channel multipliers solved from the sequence's own keys, K x s stored,
+               # q / s applied: kv/rowscale.py) and the E8-lattice K tier beside an nvfp4 V (kv/e8_lattice.py)
+               ("nvfp4-g16+rowscale", R.KV_NVFP4, 16), ("e8-rk4v4", R.KV_NVFP4, 16),
+               ("e8-rk4v4+hadamard", R.KV_NVFP4, 16)]
     Hn = R.hadamard_matrix(D)
     seqs = []
     n_pages_total = sum((n + page_size - 1) // page_size for n in lengths)
@@ -62,13 +66,25 @@ def run(seed: int = 0, n_q_heads: int = 8, n_kv_heads: int = 2, head_dim: int = 
         for q, k, v, table in seqs:
             if rotate:
                 q, k = R.bf16_round(q @ Hn), R.bf16_round(k @ Hn)
-            kq, vq = R.kv_quant_dequant(k, fmt, group), R.kv_quant_dequant(v, fmt, group)
+            if name.endswith("+rowscale"):
+                from . import rowscale as RS
+                sc = torch.stack([RS.solve_row_scale(k[:, h]) for h in range(n_kv_heads)])          # [Hkv, D]
+                k = R.bf16_round(k * sc[None])
+                q = R.bf16_round(q / sc.repeat_interleave(n_q_heads // n_kv_heads, dim=0))
+            if name.startswith("e8-"):
+                from . import e8_lattice as E8
+                kq, vq = E8.quant_dequant(k, "rk4v4"), R.kv_quant_dequant(v, fmt, group)
+            else:
+                kq, vq = R.kv_quant_dequant(k, fmt, group), R.kv_quant_dequant(v, fmt, group)
             for t in range(k.shape[0]):
                 k_pages[table[t // page_size], :, t % page_size] = kq[t]
                 v_pages[table[t // page_size], :, t % page_size] = vq[t]
             res.append(paged_decode_reference(q, k_pages, v_pages, table, page_size, k.shape[0]))
         outs[name] = res
         bits = R.kv_bits_per_value(fmt, D, group)
+        if name.startswith("e8-"):
+            from . import e8_lattice as E8
+            bits = (E8.bits_per_value("rk4v4") + bits) / 2          # K on the lattice, V nvfp4
         report["codecs"][name] = {"bits_per_value": bits, "bytes_per_token": 2 * n_kv_heads * D * bits / 8}
     for name in outs:
         errs = [(a - b).abs() for a, b in zip(outs[name], outs["bf16"])]

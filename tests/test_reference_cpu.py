@@ -48,6 +48,10 @@ def test_codec_report_config():
     assert c["fp8-e4m3-row"]["bytes_per_token"] == 2 * 2 * (128 + 2)
     assert c["int8-g32"]["bytes_per_token"] == 2 * 2 * (128 + 2 * 4)
     assert c["int8-g32"]["mean_abs_err"] < c["fp8-e4m3-row"]["mean_abs_err"] < c["nvfp4-g16"]["mean_abs_err"] < 0.2
+    # the K row scale helps nvfp4 on keys with loud channels; the lattice tier needs the rotated frame for them
+    assert c["nvfp4-g16+rowscale"]["mean_abs_err"] < 0.9 * c["nvfp4-g16"]["mean_abs_err"]
+    assert c["e8-rk4v4+hadamard"]["mean_abs_err"] < 0.6 * c["e8-rk4v4"]["mean_abs_err"]
+    assert c["e8-rk4v4"]["bytes_per_token"] < c["nvfp4-g16"]["bytes_per_token"]
 
 
 def test_gdn_chunk_invariance():
