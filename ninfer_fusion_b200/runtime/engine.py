@@ -216,8 +216,15 @@ class Engine:
 
     def health(self) -> dict:
         with self._lock:
-            return {"status": "failed" if self._failed else "ok", "pending": len(self._pending),
-                    "active": len(self._active), "free_lanes": self.program.free_lanes()}
+            out = {"status": "failed" if self._failed else "ok", "pending": len(self._pending),
+                   "active": len(self._active), "free_lanes": self.program.free_lanes()}
+        census = getattr(self.program, "census", None)
+        if census is not None:
+            try:   # counts only (no tokens, no session names); the worker may be changing the catalogue meanwhile
+                out["census"] = census()
+            except Exception:
+                pass
+        return out
 
     def reload_kv_storage(self, program_factory: Callable[[], ProgramBase], timeout_s: float = 60.0) -> None:
         """Swap the KV storage plan (per-layer formats, page geometry) by rebuilding the Program once the engine has

@@ -114,6 +114,34 @@ class ProgramBase:
                 return False
         return True
 
+    # ---- census ----
+    def census(self) -> dict:
+        """Where the reusable state lives right now: frontiers per tier and kind, bytes of the cold copies, page pool
+        occupancy and bytes per KV plane format when the program has a paged cache (residency / plane census of the
+        reference: src/product/kv_residency_census.h, kv_plane_census.h)."""
+        tiers = {"gpu": 0, "host": 0, "disk": 0}
+        kinds: dict = {}
+        cold_bytes = {"host": 0, "disk": 0}
+        for c in self.checkpoints:
+            tiers[c.tier] = tiers.get(c.tier, 0) + 1
+            kinds[c.kind] = kinds.get(c.kind, 0) + 1
+            if c.tier in cold_bytes:
+                cold_bytes[c.tier] += c.nbytes
+        out = {"lanes": {"active": len(self.lanes), "max": self.max_lanes}, "frontiers": tiers, "kinds": kinds,
+               "cold_bytes": cold_bytes, "budgets": {"host": self.host_budget_bytes, "disk": self.disk_budget_bytes},
+               "cold_stats": dict(self.cold_stats), "shared_stats": dict(self.shared_stats)}
+        kv = getattr(self, "kv", None)
+        pool = getattr(kv, "pool", None)
+        if pool is not None:
+            free = int(getattr(pool, "free_pages", 0))
+            out["pages"] = {"total": int(kv.n_pages), "free": free, "used": int(kv.n_pages) - free,
+                            "page_tokens": int(kv.page_size)}
+            planes: dict = {}
+            for l in kv.layers:
+                planes[l.fmt] = planes.get(l.fmt, 0) + int(l.bytes())
+            out["plane_bytes_by_format"] = planes
+        return out
+
     # ---- session checkpoints (prefix reuse) ----
     def _evict_checkpoint(self) -> bool:
         """Frees the device resources of the least recently used device-resident frontier: it is demoted to the host

@@ -271,3 +271,26 @@ def test_long_anchors_serve_an_edited_history():
         assert sorted(len(c.tokens) for c in prog.checkpoints if c.kind == "anchor" and c.session == "s")[-1] <= 192
     finally:
         cold.shutdown(); warm.shutdown()
+
+
+def test_health_carries_a_residency_census(tmp_path):
+    from ninfer_fusion_b200.models.config import TINY_DENSE
+    from ninfer_fusion_b200.models.weights import random_weights
+    from ninfer_fusion_b200.runtime.program import ReferenceProgram
+    w = random_weights(TINY_DENSE, "cpu", seed=5, std=0.05)
+
+    def factory():
+        p = ReferenceProgram(TINY_DENSE, w, max_lanes=2, max_context=256)
+        p.max_checkpoints, p.host_budget_bytes = 2, 1 << 30
+        return p
+    eng = Engine(factory, prefill_chunk=32)
+    try:
+        for s in range(3):
+            eng.submit(list(range(10 + s, 40 + s)), RequestOptions(max_tokens=2, session=f"s{s}")).wait(timeout=60)
+        c = eng.health()["census"]
+        assert c["lanes"] == {"active": 0, "max": 2}
+        assert c["frontiers"]["gpu"] <= 2 and c["frontiers"]["host"] >= 1 and c["cold_bytes"]["host"] > 0
+        assert c["kinds"].get("turn", 0) + c["kinds"].get("endpoint", 0) == sum(c["frontiers"].values())
+        assert c["cold_stats"]["demoted_host"] >= 1 and "pages" not in c          # the oracle program has no page pool
+    finally:
+        eng.shutdown()
