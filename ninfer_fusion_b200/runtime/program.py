@@ -188,16 +188,28 @@ class ProgramBase:
             victim = min((c for c in self.checkpoints if c.tier == "host"), key=lambda c: c.last_used)
             on_disk = sum(c.nbytes for c in self.checkpoints if c.tier == "disk")
             if self.cold_dir and on_disk + victim.nbytes <= self.disk_budget_bytes:
-                os.makedirs(self.cold_dir, exist_ok=True)
                 path = os.path.join(self.cold_dir, f"ckpt_{id(victim):x}_{self._clock}.pt")
-                if self.cold_entropy and set(victim.handle) == {"n_pages", "tensors"}:
-                    # lossless entropy stage (rANS per tensor, raw when it does not pay): fewer bytes on disk
-                    from ..kv.cold_codec import save_cold
-                    st = save_cold(victim.handle, path)
-                    self.cold_stats["disk_raw_bytes"] = self.cold_stats.get("disk_raw_bytes", 0) + st["raw"]
-                    self.cold_stats["disk_stored_bytes"] = self.cold_stats.get("disk_stored_bytes", 0) + st["stored"]
-                else:
-                    torch.save(victim.handle, path)
+                try:
+                    os.makedirs(self.cold_dir, exist_ok=True)
+                    if self.cold_entropy and set(victim.handle) == {"n_pages", "tensors"}:
+                        # lossless entropy stage (rANS per tensor, raw when it does not pay): fewer bytes on disk
+                        from ..kv.cold_codec import save_cold
+                        st = save_cold(victim.handle, path)
+                        self.cold_stats["disk_raw_bytes"] = self.cold_stats.get("disk_raw_bytes", 0) + st["raw"]
+                        self.cold_stats["disk_stored_bytes"] = self.cold_stats.get("disk_stored_bytes", 0) + st["stored"]
+                    else:
+                        torch.save(victim.handle, path)
+                except OSError:
+                    # a spill that cannot be written (full or read-only disk) costs this frontier, not the engine:
+                    # it is counted and the copy is dropped (the reference counts cold-spill write failures the same way)
+                    self.cold_stats["spill_write_failed"] = self.cold_stats.get("spill_write_failed", 0) + 1
+                    try:
+                        os.remove(path)
+                    except OSError:
+                        pass
+                    self.checkpoints.remove(victim)
+                    self.cold_stats["dropped"] += 1
+                    continue
                 victim.handle, victim.tier = {"path": path}, "disk"
                 self.cold_stats["demoted_disk"] += 1
             else:

@@ -129,3 +129,27 @@ def test_disk_tier_writes_coded_frontiers(tmp_path):
     got = p.revived["tensors"]
     assert torch.equal(got[0][0], planes[0]) and torch.equal(got[0][1], planes[1]) and got[0][1].dtype == torch.float16
     assert torch.equal(got[1][0], torch.arange(12.0).reshape(3, 4))
+
+
+def test_a_failed_spill_is_counted_not_fatal(tmp_path):
+    """The disk tier's directory cannot be created (a file sits where it should be): the frontier is dropped and
+    counted, nothing raises."""
+    from ninfer_fusion_b200.models.config import TINY_DENSE
+    from ninfer_fusion_b200.runtime.program import Checkpoint, ProgramBase
+
+    class Stub(ProgramBase):
+        def _demote(self, handle):
+            return {"n_pages": 1, "tensors": [[torch.zeros(64)]]}
+
+        def _drop(self, handle):
+            pass
+
+    blocker = tmp_path / "not-a-dir"
+    blocker.write_text("x")
+    p = Stub(TINY_DENSE, max_lanes=2, max_context=64)
+    p.host_budget_bytes, p.disk_budget_bytes, p.cold_dir = 1, 1 << 30, str(blocker / "cold")
+    ck = Checkpoint("s", "turn", [1, 2, 3], object(), last_used=1)
+    p.checkpoints.append(ck)
+    assert p._evict_checkpoint()
+    assert ck not in p.checkpoints
+    assert p.cold_stats["spill_write_failed"] == 1 and p.cold_stats["dropped"] == 1 and p.cold_stats["demoted_disk"] == 0
