@@ -14,6 +14,7 @@ from __future__ import annotations
 import ctypes
 import json
 import os
+import unicodedata
 from typing import Dict, Iterable, List, Optional, Sequence, Tuple
 
 try:  # `regex` understands \\p{L} / \\p{N}; the stdlib module does not
@@ -65,7 +66,12 @@ def _load_native():
 
 class Tokenizer:
     def __init__(self, vocab: Dict[str, int], merges: Sequence[Tuple[str, str]], added_tokens: Sequence[dict] = (),
-                 split_pattern: str = QWEN_SPLIT, use_native: bool = True):
+                 split_pattern: str = QWEN_SPLIT, use_native: bool = True, normalizer: str = ""):
+        if normalizer not in ("", "NFC", "NFKC", "NFD", "NFKD"):
+            raise ValueError(f"unsupported normalizer '{normalizer}'")
+        # Unicode normal form applied to ordinary text before it is split (added tokens pass through untouched);
+        # the Qwen tokenizer declares NFC, so that 'e' + combining acute and the precomposed letter give the same ids
+        self.normalizer = normalizer
         self.vocab = dict(vocab)
         self.added: Dict[str, int] = {}
         self.special_ids = set()
@@ -123,6 +129,10 @@ class Tokenizer:
         for p in ([pre] if pre.get("type") != "Sequence" else pre.get("pretokenizers", [])):
             if p.get("type") == "Split" and isinstance(p.get("pattern"), dict) and "Regex" in p["pattern"]:
                 pattern = p["pattern"]["Regex"]
+        norm = cfg.get("normalizer") or {}
+        forms = [n.get("type", "") for n in ([norm] if norm.get("type") != "Sequence" else norm.get("normalizers", []))]
+        form = next((f for f in forms if f in ("NFC", "NFKC", "NFD", "NFKD")), "")
+        kw.setdefault("normalizer", form)
         return cls(model["vocab"], merges, cfg.get("added_tokens", []), split_pattern=pattern, **kw)
 
     @classmethod
@@ -170,6 +180,7 @@ class Tokenizer:
         merges = [f"{id_to_str[a]} {id_to_str[b]}" for (a, b), _ in inv]
         added = [{"id": i, "content": s, "special": i in self.special_ids} for s, i in self.added.items()]
         return json.dumps({"version": "1.0", "added_tokens": added,
+                           "normalizer": {"type": self.normalizer} if self.normalizer else None,
                            "pre_tokenizer": {"type": "Sequence", "pretokenizers": [
                                {"type": "Split", "pattern": {"Regex": self._split.pattern}, "behavior": "Isolated"},
                                {"type": "ByteLevel", "add_prefix_space": False, "use_regex": False}]},
@@ -225,6 +236,8 @@ class Tokenizer:
             if allow_special and part in self.added:
                 ids.append(self.added[part])
                 continue
+            if self.normalizer:
+                part = unicodedata.normalize(self.normalizer, part)
             for piece in self._split.findall(part):
                 ids.extend(self._bpe(piece))
         return ids

@@ -118,3 +118,24 @@ def test_output_parser_stop_strings_and_unterminated_tool():
     assert q.finish().content == "<tool_call>{\"name\": "
     r = OutputParser(thinking=True)
     assert r.feed("deep thought</think>answer").reasoning == "deep thought" and r.content == "answer"
+
+
+def test_unicode_normal_form_from_tokenizer_json():
+    """A tokenizer.json that declares NFC: decomposed and precomposed spellings encode to the same ids; without the
+    declaration they differ; the setting survives to_json / from_json; added tokens are not normalised."""
+    from ninfer_fusion_b200.frontend.tokenizer import Tokenizer
+    base = Tokenizer.train_toy("café café café naïve " * 20, n_merges=40, added_tokens=["<|im_start|>"])
+    cfg = json.loads(base.to_json())
+    assert cfg["normalizer"] is None
+    cfg["normalizer"] = {"type": "Sequence", "normalizers": [{"type": "NFC"}]}
+    nfc = Tokenizer.from_json(json.dumps(cfg))
+    assert nfc.normalizer == "NFC" and base.normalizer == ""
+    a, b = "café time", "café time"
+    assert nfc.encode(a) == nfc.encode(b)
+    assert base.encode(a) != base.encode(b)
+    assert nfc.decode(nfc.encode(a)) == b
+    again = Tokenizer.from_json(nfc.to_json())
+    assert again.normalizer == "NFC" and again.encode(a) == nfc.encode(a)
+    assert nfc.encode("<|im_start|>x")[0] == nfc.added["<|im_start|>"]
+    with pytest.raises(ValueError):
+        Tokenizer(base.vocab, [], normalizer="lowercase")
