@@ -86,8 +86,12 @@ def load_model(args) -> Tuple[ModelConfig, Dict[str, object], Tokenizer, str]:
             model_id, weights_id = rd.identity
             cfg = get_config(model_id)
             weights = {}
-            for name in rd.tensors():
+            from .utils.progress import Progress
+            names = list(rd.tensors())
+            bar = Progress(sum(rd.by_name[n].bytes for n in names), "loading")
+            for name in names:
                 o = rd.by_name[name]
+                bar.advance(o.bytes, name)
                 if (args.weights == "stored" and args.device != "cpu" and o.format in L.GROUP_FORMATS and len(o.shape) == 2
                         and name.rsplit("/", 1)[-1] in QUANT_LEAVES and "/moe/" not in name):
                     # zero-copy in format: the encoded object goes to the device as it is
@@ -95,6 +99,7 @@ def load_model(args) -> Tuple[ModelConfig, Dict[str, object], Tokenizer, str]:
                     weights[name] = GroupIntWeight(o.format, raw.to(args.device), o.shape)
                 else:
                     weights[name] = rd.tensor(name)
+            bar.close()
             if "tokenizer.json" in rd.by_name:
                 tok = Tokenizer.from_json(rd.resource("tokenizer.json"))
             if "chat_template.jinja" in rd.by_name:

@@ -42,3 +42,17 @@ def test_engine_emits_prefill_and_decode_spans(tmp_path):
         trace.configure(log_path="")
     names = [json.loads(l)["name"] for l in log.read_text().splitlines()]
     assert names.count("prefill_chunk") == 3 and names.count("decode_round") >= 2
+
+
+def test_progress_bar_is_silent_off_a_terminal_and_draws_on_one():
+    import io
+    from ninfer_fusion_b200.utils.progress import Progress
+    quiet = io.StringIO()
+    p = Progress(100, "loading", stream=quiet)
+    p.advance(50, "a"); p.advance(50, "b"); p.close()
+    assert quiet.getvalue() == "" and p.done == 100
+    loud = io.StringIO()
+    p = Progress(4 << 20, "loading", stream=loud, force=True)
+    p.advance(1 << 20, "text/embed"); p.advance(10 << 20, "text/lm_head"); p.close()
+    out = loud.getvalue()
+    assert "100.0%" in out and "text/lm_head" in out and out.endswith("\n") and p.done == 4 << 20
