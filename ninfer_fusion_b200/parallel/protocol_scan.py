@@ -86,3 +86,82 @@ def scan(world: int = 2, calls: int = 3, depth: int = 2, max_states: int = 2_000
             r = blocked[0]
             return Violation("deadlock", r, progs[r][pcs[r]][2], f"ranks {blocked} wait for arrivals that never come"), len(seen)
     return None, len(seen)
+
+
+# ------------------------------------------------------------------------------------------------ generic engine
+def scan_programs(progs: List[List[Tuple]], max_states: int = 2_000_000) -> Tuple[Optional[Violation], int]:
+    """Every interleaving of per-rank step lists over shared cells.  Steps:
+    ("store", cell, value) | ("add", counter) | ("wait", counter, threshold) | ("read", [cells], expected, rank, call)."""
+    cells = sorted({s[1] for p in progs for s in p if s[0] == "store"} | {c for p in progs for s in p if s[0] == "read" for c in s[1]})
+    counters = sorted({s[1] for p in progs for s in p if s[0] in ("add", "wait")})
+    ci = {c: i for i, c in enumerate(cells)}
+    ki = {c: i for i, c in enumerate(counters)}
+    start = (tuple(0 for _ in progs), tuple(-1 for _ in cells), tuple(0 for _ in counters))
+    seen, stack = {start}, [start]
+    while stack:
+        pcs, mem, cnt = stack.pop()
+        if len(seen) > max_states:
+            raise RuntimeError("state space larger than max_states")
+        moved, finished = False, True
+        for r, prog in enumerate(progs):
+            if pcs[r] >= len(prog):
+                continue
+            finished = False
+            s = prog[pcs[r]]
+            n_mem, n_cnt = mem, cnt
+            if s[0] == "store":
+                m = list(mem); m[ci[s[1]]] = s[2]; n_mem = tuple(m)
+            elif s[0] == "add":
+                k = list(cnt); k[ki[s[1]]] += 1; n_cnt = tuple(k)
+            elif s[0] == "wait":
+                if cnt[ki[s[1]]] < s[2]:
+                    continue
+            else:
+                got = [mem[ci[c]] for c in s[1]]
+                if any(v != s[2] for v in got):
+                    return Violation("stale_read", s[3], s[4], f"rank {s[3]} call {s[4]} read {got}, expected {s[2]}"), len(seen)
+            moved = True
+            n_pcs = list(pcs); n_pcs[r] += 1
+            nxt = (tuple(n_pcs), n_mem, n_cnt)
+            if nxt not in seen:
+                seen.add(nxt)
+                stack.append(nxt)
+        if not moved and not finished:
+            blocked = [r for r in range(len(progs)) if pcs[r] < len(progs[r])]
+            return Violation("deadlock", blocked[0], -1, f"ranks {blocked} wait for counters that never advance"), len(seen)
+    return None, len(seen)
+
+
+def expert_parallel_programs(world: int, calls: int, rows: List[List[bool]], unconditional_arrive: bool = True) -> List[List[Tuple]]:
+    """The expert-parallel layer protocol (csrc/moe/moe_route.cu): a histogram exchange that doubles as a barrier, then
+    rows pushed into SINGLE receive buffers.  rows[s][d]: does rank s route any token to rank d in a call.
+
+        plan:  store counts[d][r] for every d; add count_flag[d]; wait count_flag[r] >= (e + 1) W; read counts[r][*]
+        push:  store recv[d][r] where rows[r][d]; add arrive_flag[d] (for EVERY d when `unconditional_arrive`, as the
+               kernel does; only where rows were sent otherwise); wait arrive_flag[r]; read recv[r][s] for senders s
+
+    The receive and count buffers have no parity: what keeps call e + 1 from overwriting call e is that a rank cannot
+    leave call e before every rank's push kernel of call e ran, which follows that rank's plan in stream order."""
+    progs = []
+    for r in range(world):
+        p: List[Tuple] = []
+        for e in range(calls):
+            for d in range(world):
+                p.append(("store", ("counts", d, r), e))
+            for d in range(world):
+                p.append(("add", ("count_flag", d)))
+            p.append(("wait", ("count_flag", r), (e + 1) * world))
+            p.append(("read", [("counts", r, s) for s in range(world)], e, r, e))
+            for d in range(world):
+                if rows[r][d]:
+                    p.append(("store", ("recv", d, r), e))
+            senders = [s for s in range(world) if rows[s][r]]
+            for d in range(world):
+                if unconditional_arrive or rows[r][d]:
+                    p.append(("add", ("arrive_flag", d)))
+            expect = world if unconditional_arrive else len(senders)
+            p.append(("wait", ("arrive_flag", r), (e + 1) * expect))
+            if senders:
+                p.append(("read", [("recv", r, s) for s in senders], e, r, e))
+        progs.append(p)
+    return progs

@@ -30,3 +30,20 @@ def test_missing_arrival_is_reported_as_deadlock():
     finally:
         P._program = orig
     assert violation is not None and violation.kind == "deadlock" and violation.rank == 0
+
+
+def test_expert_parallel_protocol_needs_the_unconditional_arrival():
+    """Single-buffered counts and receive rows are safe because every push signals every rank, rows or not; if a rank
+    only signalled the ranks it sent rows to, a rank with no traffic to a slow peer could lap it and overwrite its
+    counts."""
+    from ninfer_fusion_b200.parallel.protocol_scan import expert_parallel_programs, scan_programs
+    local_only = [[True, False], [False, True]]                       # every token stays on its own rank
+    dense = [[True, True], [True, True]]
+    mixed = [[True, True, False], [False, True, True], [True, False, True]]
+    for rows, world in ((local_only, 2), (dense, 2), (mixed, 3)):
+        v, states = scan_programs(expert_parallel_programs(world, 3 if world == 2 else 2, rows, unconditional_arrive=True))
+        assert v is None and states > 50, (rows, v)
+    v, _ = scan_programs(expert_parallel_programs(2, 2, local_only, unconditional_arrive=False))
+    assert v is not None and v.kind == "stale_read"
+    v, _ = scan_programs(expert_parallel_programs(2, 3, dense, unconditional_arrive=False))
+    assert v is None                                                   # with traffic between every pair the waits chain anyway
