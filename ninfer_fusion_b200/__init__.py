@@ -5,8 +5,8 @@ runtime), ``ops`` (checked Python entry points + fp32 torch oracles),
 ``models`` (hybrid GDN/GQA decoders, dense and MoE, MTP draft head),
 ``parallel`` (rank runtime, shard plan, fused collectives), ``runtime``
 (paged KV pool, state pools, CUDA-graph families, engine/scheduler),
-``kv`` (codec policy: bit budget, block descent, tiers), ``spec``
-(speculative decoding), ``artifact`` (.ninfer v2 container), ``serve`` /
+``kv`` (codec policy: bit budget, block descent, tiers; speculative
+decoding lives in ``runtime.speculative``), ``artifact`` (.ninfer v2 container), ``serve`` /
 ``cli`` (gateways).
 """
 

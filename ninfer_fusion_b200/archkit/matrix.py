@@ -6,7 +6,7 @@ from typing import Dict, List
 from ..models.config import ModelConfig
 
 GPUS: Dict[str, Dict[str, float]] = {
-    # memory in GiB usable by one process, copy bandwidth in TB/s (B200: measured on this pool's parts)
+    # memory in GiB usable by one process, copy bandwidth in TB/s (B200: a measured copy rate, not the nominal 7.7)
     "b200": {"mem_gib": 178.0, "tbps": 6.5},
     "h200": {"mem_gib": 139.0, "tbps": 4.0},
     "h100": {"mem_gib": 79.0, "tbps": 2.9},

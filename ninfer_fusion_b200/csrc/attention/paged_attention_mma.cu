@@ -120,11 +120,12 @@ __global__ void __launch_bounds__(kThreads, 2) paged_attn_mma_kernel(const Paged
       float ks = 0.f, vs = 0.f;
       if (key < k_end) {
         const int page = table[key / P];
-        r = (static_cast<long long>(page) * p.kv.n_kv_heads + kvh) * P + key % P;
-        if constexpr (FORMAT == kKvFp8Row) {
+        // a released or unpublished page (-1) contributes nothing: no row, no scale read
+        if (page >= 0) r = (static_cast<long long>(page) * p.kv.n_kv_heads + kvh) * P + key % P;
+        if (FORMAT == kKvFp8Row && r >= 0) {
           ks = __half2float(reinterpret_cast<const __half*>(p.kv.k_scales)[r]);
           vs = __half2float(reinterpret_cast<const __half*>(p.kv.v_scales)[r]);
-        } else {
+        } else if (r >= 0) {
           ks = 1.f;
           vs = 1.f;
         }

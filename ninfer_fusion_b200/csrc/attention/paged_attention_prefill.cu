@@ -110,10 +110,11 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_prefill_kernel(const P
     float ks = 0.f, vs = 0.f;
     if (key < k_end) {
       const int page = table[key / P];
-      r = (static_cast<long long>(page) * p.kv.n_kv_heads + kvh) * P + key % P;
-      ks = 1.f;
-      vs = 1.f;
-      if constexpr (FORMAT == kKvFp8Row) {
+      // a released or unpublished page (-1) contributes nothing: no row, no scale read
+      if (page >= 0) r = (static_cast<long long>(page) * p.kv.n_kv_heads + kvh) * P + key % P;
+      ks = r >= 0 ? 1.f : 0.f;
+      vs = ks;
+      if (FORMAT == kKvFp8Row && r >= 0) {
         ks = __half2float(reinterpret_cast<const __half*>(p.kv.k_scales)[r]);
         vs = __half2float(reinterpret_cast<const __half*>(p.kv.v_scales)[r]);
       }

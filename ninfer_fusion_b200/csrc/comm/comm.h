@@ -56,6 +56,10 @@ struct TpReduceParams {
   int unit_offset;
   TpState* state;
   int* status;
+  // bit 0: phase A (reduce my slice, push it to every rank), bit 1: phase B (wait for all slices, normalise).
+  // 3 = both in one launch (production); the halves are launched separately only to walk several ranks through on
+  // one GPU, where a kernel must never wait for a later launch
+  int phases = 3;
 };
 const char* tp_reduce_ag_norm(const TpReduceParams& p, cudaStream_t stream, bool pdl);
 
@@ -70,8 +74,28 @@ struct TpArgmaxParams {
   int* out;                          // [T] global token ids
   TpState* state;
   int* status;
+  int phases = 3;                    // bit 0: scan + push the candidate, bit 1: wait for all candidates + pick
 };
 const char* tp_argmax(const TpArgmaxParams& p, cudaStream_t stream, bool pdl);
+
+// Materialises the RMS-normalised residual stream after a GEMM whose epilogue reduce-scattered and all-gathered
+// it (gemm kEpiRsAg): waits (bounded) until `*flag - *target >= 0`, i.e. every residual tile of every owner has
+// landed in this rank's buffer, then writes normed[t] = x[t] * rsqrt(mean(x[t]^2) + eps) * (unit_offset + w).
+// Used where the consumer is not a column-parallel GEMM that can wait and scale by itself (the final norm before
+// the vocabulary head, a draft module, a router).
+struct TpGatherNormParams {
+  int T, N;
+  const unsigned int* flag;      // this rank's residual arrival counter
+  const unsigned int* target;    // cumulative arrivals to wait for (device word written by the producing GEMM)
+  const __nv_bfloat16* x;        // [T, ldx]
+  long long ldx;
+  const __nv_bfloat16* norm_w;   // [N]
+  __nv_bfloat16* normed;         // [T, N] contiguous
+  float eps;
+  int unit_offset;
+  int* status;
+};
+const char* tp_gather_norm(const TpGatherNormParams& p, cudaStream_t stream, bool pdl);
 
 // ---- symmetric buffers over CUDA IPC (one process per GPU, one node) ----
 // Allocates `bytes` with cudaMalloc (zero-filled) and exports a 64-byte IPC handle.

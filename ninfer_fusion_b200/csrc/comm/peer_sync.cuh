@@ -24,10 +24,13 @@ __device__ __forceinline__ void red_release_gpu_add(unsigned int* p, uint32_t v)
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// Wait until *flag - target >= 0 in wrap-around arithmetic.  Returns false on time-out.
+// Wait until *flag - target >= 0 in wrap-around arithmetic.  Returns false on time-out, and at once (after one
+// look at the counter) when the status word already holds a failure: after the first wait that ran out, the
+// kernels that follow it in the stream would otherwise each spend their own full limit.
 __device__ __forceinline__ bool wait_counter(const unsigned int* flag, uint32_t target, int* status) {
   for (uint32_t i = 0; i < kPeerPollLimit; ++i) {
     if (static_cast<int32_t>(ld_acquire_sys(flag) - target) >= 0) return true;
+    if ((i & 1023u) == 0 && status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return false;
     __nanosleep(i < 64 ? 20 : 200);
   }
   report_status(status, kStatusPeerWaitTimeout);

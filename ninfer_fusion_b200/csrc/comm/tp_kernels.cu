@@ -45,13 +45,14 @@ __global__ void __launch_bounds__(kThreads) tp_reduce_ag_norm_kernel(const TpRed
   TpState* st = p.state;
 
   // ---- phase A: reduce my column slice of row t ----
+  const bool do_a = (p.phases & 1) != 0, do_b = (p.phases & 2) != 0;
   const uint32_t target1 = st->expected_arrivals + p.arrivals_this_call;
-  if (threadIdx.x == 0) ok_s = wait_counter(p.my_arrival_flag, target1, p.status) ? 1 : 0;
+  if (threadIdx.x == 0) ok_s = (!do_a || wait_counter(p.my_arrival_flag, target1, p.status)) ? 1 : 0;
   __syncthreads();
   const bool ok = ok_s != 0;
   float ss = 0.f;
   const int nvec = slice / 4;
-  if (ok) {
+  if (ok && do_a) {
     for (int v = threadIdx.x; v < nvec; v += kThreads) {
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int src = 0; src < W * p.splits; ++src) {
@@ -77,7 +78,7 @@ __global__ void __launch_bounds__(kThreads) tp_reduce_ag_norm_kernel(const TpRed
   __threadfence_system();
   __syncthreads();
   const uint32_t row_epoch = st->row_calls[t];
-  if (threadIdx.x == 0 && ok) {
+  if (threadIdx.x == 0 && ok && do_a) {
     float tot = 0.f;
     for (int w = 0; w < kThreads / 32; ++w) tot += red[w];
     // the sum of squares travels in a double-buffered slot so a fast peer's next call cannot overwrite it
@@ -89,7 +90,7 @@ __global__ void __launch_bounds__(kThreads) tp_reduce_ag_norm_kernel(const TpRed
 
   // ---- phase B: the whole row is here once all W slices have arrived ----
   if (threadIdx.x == 0) {
-    ok_s = ok && wait_counter(p.my_row_flag + t, (row_epoch + 1u) * static_cast<uint32_t>(W), p.status) ? 1 : 0;
+    ok_s = ok && do_b && wait_counter(p.my_row_flag + t, (row_epoch + 1u) * static_cast<uint32_t>(W), p.status) ? 1 : 0;
   }
   __syncthreads();
   if (ok_s && p.normed != nullptr) {
@@ -117,13 +118,15 @@ __global__ void __launch_bounds__(kThreads) tp_reduce_ag_norm_kernel(const TpRed
   // ---- bookkeeping: the last CTA to finish advances the call-level expectations ----
   __syncthreads();
   if (threadIdx.x == 0) {
-    st->row_calls[t] = row_epoch + 1u;
-    __threadfence();
-    const unsigned int done = atomicAdd(&st->ctas_done, 1u);
-    if (done == gridDim.x - 1) {
-      st->expected_arrivals = target1;
-      st->ctas_done = 0;
+    if (do_b) st->row_calls[t] = row_epoch + 1u;
+    if (do_a) {
       __threadfence();
+      const unsigned int done = atomicAdd(&st->ctas_done, 1u);
+      if (done == gridDim.x - 1) {
+        st->expected_arrivals = target1;
+        st->ctas_done = 0;
+        __threadfence();
+      }
     }
   }
 }
@@ -137,9 +140,10 @@ __global__ void __launch_bounds__(1024) tp_argmax_kernel(const TpArgmaxParams p)
   pdl_wait_prior();
   const int t = blockIdx.x;
   const __nv_bfloat16* row = p.logits + static_cast<long long>(t) * p.ld;
+  const bool do_push = (p.phases & 1) != 0, do_pick = (p.phases & 2) != 0;
   float best = -CUDART_INF_F;
   int idx = 0x7fffffff;
-  for (int i = threadIdx.x; i < p.V_local; i += blockDim.x) {
+  for (int i = threadIdx.x; do_push && i < p.V_local; i += blockDim.x) {
     const float f = __bfloat162float(row[i]);
     if (f > best || (f == best && i < idx)) { best = f; idx = i; }
   }
@@ -165,12 +169,15 @@ __global__ void __launch_bounds__(1024) tp_argmax_kernel(const TpArgmaxParams p)
   const uint32_t epoch = st->argmax_calls[t];
   const int par = epoch & 1;
   const int W = p.world;
-  for (int r = 0; r < W; ++r) {
-    float2* slot = p.peer_cand[r] + (static_cast<long long>(par) * p.T_cap + t) * W + p.rank;
-    *slot = make_float2(best, __int_as_float(idx + p.rank * p.V_local));
+  if (do_push) {
+    for (int r = 0; r < W; ++r) {
+      float2* slot = p.peer_cand[r] + (static_cast<long long>(par) * p.T_cap + t) * W + p.rank;
+      *slot = make_float2(best, __int_as_float(idx + p.rank * p.V_local));
+    }
+    __threadfence_system();
+    for (int r = 0; r < W; ++r) red_release_sys_add(p.peer_flag[r] + t, 1u);
   }
-  __threadfence_system();
-  for (int r = 0; r < W; ++r) red_release_sys_add(p.peer_flag[r] + t, 1u);
+  if (!do_pick) return;
   if (wait_counter(p.my_flag + t, (epoch + 1u) * static_cast<uint32_t>(W), p.status)) {
     float gb = -CUDART_INF_F;
     int gi = 0x7fffffff;
@@ -277,7 +284,68 @@ __global__ void __launch_bounds__(kRowThreads) tp_sum_norm_kernel(const TpSumNor
   }
 }
 
+// Wait for the all-gathered residual stream, then RMS-normalise it: one CTA per token row.
+__global__ void __launch_bounds__(kThreads) tp_gather_norm_kernel(const TpGatherNormParams p) {
+  __shared__ float red[kThreads / 32];
+  __shared__ int ok_s;
+  pdl_launch_next();
+  pdl_wait_prior();
+  const int t = blockIdx.x;
+  if (threadIdx.x == 0) ok_s = wait_counter(p.flag, __ldcg(p.target), p.status) ? 1 : 0;
+  __syncthreads();
+  if (!ok_s) return;
+  const __nv_bfloat16* row = p.x + static_cast<long long>(t) * p.ldx;
+  float ss = 0.f;
+  for (int v = threadIdx.x; v < p.N / 8; v += kThreads) {
+    const uint4 xv = __ldcg(reinterpret_cast<const uint4*>(row + v * 8));
+    const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = __bfloat162float(xp[j].x), b = __bfloat162float(xp[j].y);
+      ss += a * a + b * b;
+    }
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < kThreads / 32; ++w) tot += red[w];
+  const float inv = rsqrtf(tot / static_cast<float>(p.N) + p.eps);
+  for (int v = threadIdx.x; v < p.N / 8; v += kThreads) {
+    const uint4 xv = __ldcg(reinterpret_cast<const uint4*>(row + v * 8));
+    const uint4 wv = *reinterpret_cast<const uint4*>(p.norm_w + v * 8);
+    const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+    const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
+    uint4 o;
+    uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float w0 = __bfloat162float(wp[j].x), w1 = __bfloat162float(wp[j].y);
+      if (p.unit_offset) { w0 += 1.f; w1 += 1.f; }
+      op[j] = pack_bf16x2(__bfloat162float(xp[j].x) * inv * w0, __bfloat162float(xp[j].y) * inv * w1);
+    }
+    *reinterpret_cast<uint4*>(p.normed + static_cast<long long>(t) * p.N + v * 8) = o;
+  }
+}
+
 }  // namespace
+
+const char* tp_gather_norm(const TpGatherNormParams& p, cudaStream_t stream, bool pdl) {
+  if (p.T <= 0) return nullptr;
+  if (p.N % 8 || p.ldx % 8 || p.N > 65536) return "tp_gather_norm: row width must be a multiple of 8";
+  if ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.normed) | reinterpret_cast<uintptr_t>(p.norm_w)) & 15)
+    return "tp_gather_norm: operands must be 16-byte aligned";
+  if (p.flag == nullptr || p.target == nullptr || p.norm_w == nullptr || p.normed == nullptr)
+    return "tp_gather_norm: missing pointer";
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.T); cfg.blockDim = dim3(kThreads); cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, tp_gather_norm_kernel, p);
+  return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
 
 const char* tp_sum_norm(const TpSumNormParams& p, cudaStream_t stream, bool pdl) {
   if (p.T <= 0) return nullptr;

@@ -16,11 +16,54 @@ enum GemmEpilogue : int {
   kEpiPushAll = 5,      // tensor parallel, decode sizes: the fp32 tile is stored into EVERY rank's receive
                         // buffer [parity][src_rank][T_cap][N] (one-shot all-reduce by push) and every
                         // rank's arrival counter is incremented (GEMM -> all-reduce in one kernel)
+  kEpiRsAg = 6,         // tensor parallel, decode sizes, two hops inside one kernel: every CTA whose column
+                        // tile belongs to another rank stores its fp32 tile into that owner's receive buffer
+                        // [src_rank][T_cap][N/world] and bumps the owner's per-tile counter; the CTA that owns
+                        // its tile waits for the world-1 peer tiles, adds them and the residual, rounds to
+                        // bf16, stores the new residual tile and the tile's per-token sums of squares into
+                        // EVERY rank's residual buffer and bumps every rank's residual counter
+                        // (GEMM -> reduce-scatter -> all-gather in one kernel).  The next column-parallel
+                        // GEMM waits on that counter itself (GemmGather below).
+};
+
+// Rank-local bookkeeping of kEpiRsAg and of the gathered consumer (ordinary device memory, zero-initialised).
+constexpr int kRsMaxOwnTiles = 64;   // column tiles of 128 a rank can own (N / world <= 8192)
+constexpr int kRsMaxTokenTiles = 16;
+constexpr int kRsSsStride = 64;      // column tiles per row of the sums-of-squares table (N <= 8192)
+struct RsState {
+  unsigned int tile_expected[kRsMaxOwnTiles * kRsMaxTokenTiles];  // cumulative peer arrivals consumed per owned tile
+  unsigned int x_expected;   // cumulative residual-tile arrivals the next consumer has to see
+};
+
+// A column-parallel GEMM that consumes the residual stream straight from the all-gather of kEpiRsAg: its TMA
+// producer first streams weights into every pipeline stage, then waits until `*flag - *target >= 0` (all residual
+// tiles of all owners have landed in this rank's buffer) and only then loads activations; the epilogue multiplies
+// token t by rsqrt(sum_j ss[t][j] / n_features + eps), i.e. applies the RMS norm as a row scale (the norm's
+// column weights must have been folded into the GEMM weight).
+struct GemmGather {
+  const unsigned int* flag = nullptr;    // this rank's residual arrival counter (symmetric buffer)
+  const unsigned int* target = nullptr;  // RsState::x_expected
+  const float* ss = nullptr;             // [T_cap][kRsSsStride] per-tile sums of squares (symmetric buffer)
+  int ss_tiles = 0;                      // tiles per row that hold data (n_features / 128)
+  int n_features = 0;
+  float eps = 0.f;
 };
 
 enum GemmActivation : int { kActNone = 0, kActGeluTanh = 1, kActGeluErf = 2 };
 
 constexpr int kMaxRanks = 8;
+
+// kEpiStore at decode (token t is sequence t): output columns [0, C) are the inputs of a depthwise causal
+// conv (4 taps) + SiLU with a 3-column history per sequence slot.  The epilogue thread that holds (token, channel)
+// applies the taps, rolls the history forward and writes the activation to `out` [T, C]; columns >= C go to the
+// GEMM's ordinary output.  Same arithmetic as the stand-alone decode kernel (gdn/conv1d.cu); C % 128 == 0.
+struct GemmConv {
+  const void* w = nullptr;      // bf16 [C, 4], tap 3 multiplies the newest input
+  void* state = nullptr;        // bf16 [slots, 3, C], oldest -> newest
+  const int* slot = nullptr;    // [T] history slot of each token's sequence
+  void* out = nullptr;          // bf16 [T, C]
+  int C = 0;
+};
 
 struct GemmArgs {
   const void* w = nullptr;  // [N, K] bf16 row-major, leading dimension ldw
@@ -47,6 +90,19 @@ struct GemmArgs {
   const unsigned int* call_idx = nullptr; // device counter whose parity selects the receive buffer
   float* peer_recv[kMaxRanks] = {};
   unsigned int* peer_flag[kMaxRanks] = {};
+  // kEpiRsAg only: every rank's residual buffer [T_cap][N] bf16, sums-of-squares table, residual counter; this
+  // rank's bookkeeping; `rs_phase` 0 = fused (production), 1 = push tiles only (owned tiles are pushed to this
+  // rank's own receive buffer too), 2 = no GEMM, owners reduce the `world` tiles that phase 1 left.  Phases 1 and
+  // 2 exist so that several ranks can be walked through on ONE GPU without any kernel waiting on another.
+  void* peer_x[kMaxRanks] = {};            // bf16 [T_cap][ldx_resid]
+  int64_t ld_resid = 0;                    // leading dimension of the residual buffers (elements)
+  float* peer_ss[kMaxRanks] = {};          // [T_cap][kRsSsStride]
+  unsigned int* peer_xflag[kMaxRanks] = {};
+  RsState* rs_state = nullptr;
+  int rs_phase = 0;
+  // kEpiStore / kEpiSwiglu: consume the gathered residual stream (see GemmGather); flag == nullptr = off
+  GemmGather gather;
+  GemmConv conv;   // kEpiStore only; state == nullptr = off
 };
 
 // Returns nullptr on success, else a static error string.

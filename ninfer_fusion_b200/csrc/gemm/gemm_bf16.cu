@@ -19,6 +19,7 @@
 
 #include <cstdlib>
 
+#include "../comm/peer_sync.cuh"
 #include "../common/ptx.cuh"
 #include "../common/tensor_map.h"
 
@@ -81,6 +82,25 @@ struct KernelParams {
   // kEpiPushAll: one-shot all-reduce by push into [parity][src_rank][T_cap][N] on every rank
   int world, T_cap;
   const unsigned int* call_idx;  // device counter of finished reduce calls; its parity picks the buffer
+  // kEpiRsAg: reduce-scatter into the owner, owner-side reduction, all-gather of the new residual tile
+  __nv_bfloat16* peer_x[kMaxRanks];
+  long long ld_resid;
+  float* peer_ss[kMaxRanks];
+  unsigned int* peer_xflag[kMaxRanks];
+  RsState* rs_state;
+  int rs_phase;
+  // gathered consumer (kEpiStore / kEpiSwiglu): wait for the residual tiles, RMS norm as an epilogue row scale
+  const unsigned int* g_flag;
+  const unsigned int* g_target;
+  const float* g_ss;
+  int g_tiles;
+  float g_inv_n, g_eps;
+  // kEpiStore: decode conv + SiLU + history roll on columns [0, conv_C)
+  const __nv_bfloat16* conv_w;
+  __nv_bfloat16* conv_state;
+  const int* conv_slot;
+  __nv_bfloat16* conv_out;
+  int conv_C;
 };
 
 // GELU in the two forms vision towers use: tanh approximation (transformer blocks) and exact erf (merger).
@@ -105,6 +125,8 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ int peer_ok[kMaxRanks];
+  __shared__ float row_s[TN];   // per token: RMS factor (gathered consumer) or the tile's sum of squares (kEpiRsAg)
+  __shared__ int rs_ok;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -119,7 +141,9 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
   const int n0 = (EPI == kEpiSwiglu) ? blockIdx.x * 64 : blockIdx.x * kTileN;
   const int kb_begin = blockIdx.z * p.kb_per_split;
   const int kb_end = min(p.num_kb, kb_begin + p.kb_per_split);
-  const int num_it = kb_end - kb_begin;
+  // (phase 2 of kEpiRsAg runs no GEMM: the tiles were left in the receive buffers by phase 1)
+  const int num_it = (EPI == kEpiRsAg && p.rs_phase == 2) ? 0 : kb_end - kb_begin;
+  const bool gathered = (EPI == kEpiStore || EPI == kEpiSwiglu) && p.g_flag != nullptr;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -155,6 +179,30 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
       const int row_b = (EPI == kEpiSwiglu) ? p.swiglu_half + n0 : n0 + 64;
       bool waited_prior = false;
       int it = 0;
+      if (gathered) {
+        // Weights first, into every stage; the activations are the residual tiles that the owner ranks push into
+        // this rank's buffer, so wait for all of them (bounded) before the first activation load.
+        const int pre = num_it < kStages ? num_it : kStages;
+        for (int j = 0; j < pre; ++j) {
+          const uint32_t full = smem_u32(&bar_full[j]);
+          const uint32_t dst = smem_base + j * Cfg::kStageBytes;
+          const int kx = (kb_begin + j) * kBlockK;
+          mbar_expect_tx(full, Cfg::kStageBytes);
+          tma_load_2d(dst, &tmap_w, full, kx, row_a, pol_w);
+          tma_load_2d(dst + 64 * 128, &tmap_w, full, kx, row_b, pol_w);
+        }
+        pdl_wait_prior();
+        waited_prior = true;
+        const uint32_t target = __ldcg(p.g_target);
+        // on a time-out the loads below are still issued (the data is stale, the status word says so): every
+        // barrier that was armed above must complete before the CTA may leave
+        if (!wait_counter(p.g_flag, target, p.status)) abort_flag = 1;
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        for (int j = 0; j < pre; ++j)
+          tma_load_2d(smem_base + j * Cfg::kStageBytes + kWTileBytes, &tmap_x, smem_u32(&bar_full[j]),
+                      (kb_begin + j) * kBlockK, t0, pol_x);
+        it = pre;
+      }
       for (; it < num_it; ++it) {
         const int s = it % kStages;
         const uint32_t ph = (it / kStages) & 1;
@@ -259,6 +307,25 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
       for (int r = 1; r < S; ++r) epilogue_ok &= peer_ok[r];
     }
   }
+  if (gathered) {
+    // RMS factor of every token of the tile from the per-tile sums of squares that travelled with the residual
+    if (threadIdx.x == 0) (void)ld_acquire_sys(p.g_flag);
+    __syncthreads();
+    for (int t = threadIdx.x; t < TN; t += 128) {
+      // the whole table row in independent 16-byte loads (entries past the last tile are never written: zero)
+      float ss = 0.f;
+      if (t0 + t < p.T) {
+        const float4* rowp = reinterpret_cast<const float4*>(p.g_ss + static_cast<long long>(t0 + t) * kRsSsStride);
+        float4 q[kRsSsStride / 4];
+#pragma unroll
+        for (int j = 0; j < kRsSsStride / 4; ++j) q[j] = __ldcg(rowp + j);
+#pragma unroll
+        for (int j = 0; j < kRsSsStride / 4; ++j) ss += (q[j].x + q[j].y) + (q[j].z + q[j].w);
+      }
+      row_s[t] = rsqrtf(ss * p.g_inv_n + p.g_eps);
+    }
+    __syncthreads();
+  }
   // accumulator chunk = own TMEM columns + the peers' contributions, summed in rank order
   auto load_acc = [&](int c, float* acc) {
     uint32_t v[kChunk];
@@ -269,6 +336,10 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
     for (int r = 1; r < S; ++r) {
 #pragma unroll
       for (int j = 0; j < kChunk; ++j) acc[j] += peer_s[((r - 1) * TN + c + j) * 128 + warp * 32 + lane];
+    }
+    if (gathered) {
+#pragma unroll
+      for (int j = 0; j < kChunk; ++j) acc[j] *= row_s[c + j];
     }
   };
 
@@ -314,13 +385,182 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
           }
         }
       }
+    } else if constexpr (EPI == kEpiRsAg) {
+      const int n = n0 + warp * 32 + lane;
+      const int owner = n0 / p.slice_cols;
+      const int tile_local = (n0 - owner * p.slice_cols) / kTileN;
+      const int flag_idx = tile_local * kRsMaxTokenTiles + blockIdx.y;
+      const bool mine = owner == p.rank;
+      const bool pushes = p.rs_phase != 2 && (!mine || p.rs_phase == 1);
+      const bool reduces = mine && p.rs_phase != 1;
+      // The fp32 tile goes through shared memory (behind the split-K landing zone of the idle pipeline stages) so
+      // that the second half works on token rows: a quarter row (32 columns) per thread, 16-byte accesses, runs of
+      // 512 contiguous bytes per token towards a peer instead of 128.
+      constexpr int kRowPad = kTileN + 4;   // floats per row: shifts consecutive rows by four banks
+      float* tile_s = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw))) + (S - 1) * TN * 128;
+      if (p.rs_phase != 2) {
+        for (int c = 0; c < TN; c += kChunk) {
+          if (t0 + c >= p.T) break;
+          float v[kChunk];
+          load_acc(c, v);
+#pragma unroll
+          for (int j = 0; j < kChunk; ++j) tile_s[(c + j) * kRowPad + warp * 32 + lane] = v[j];
+        }
+      }
+      unsigned int* expected = &p.rs_state->tile_expected[flag_idx];
+      uint32_t target = 0;
+      if (reduces) {
+        // owner of the tile: the peers' tiles have to be here before the rows can be reduced
+        target = *expected + static_cast<uint32_t>(p.rs_phase == 0 ? p.world - 1 : p.world);
+        if (threadIdx.x == 0) rs_ok = wait_counter(p.peer_flag[p.rank] + flag_idx, target, p.status) ? 1 : 0;
+      }
+      __syncthreads();
+      const int seg = threadIdx.x & 3;            // quarter of the tile's 128 columns
+      const int col = seg * 32;                   // first column of this thread inside the tile
+      const int n_first = n0 + col;               // ... in the output
+      const int n_local = n_first - owner * p.slice_cols;
+      (void)n;
+      if (pushes) {
+        // hop 1: rows of the fp32 tile into the owner's receive buffer [src][T_cap][slice]
+        float* dst = p.peer_recv[owner] + static_cast<long long>(p.rank) * p.T_cap * p.slice_cols + n_local;
+        for (int r = threadIdx.x >> 2; r < TN; r += 32) {
+          const int t = t0 + r;
+          if (t >= p.T) continue;
+          const float4* src4 = reinterpret_cast<const float4*>(tile_s + r * kRowPad + col);
+          float4* dst4 = reinterpret_cast<float4*>(dst + static_cast<long long>(t) * p.slice_cols);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) dst4[q] = src4[q];
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          __threadfence_system();
+          red_release_sys_add(p.peer_flag[owner] + flag_idx, 1u);
+        }
+      }
+      if (reduces) {
+        const bool ok = rs_ok != 0;
+        __nv_bfloat16* my_x = p.peer_x[p.rank];
+        const float* recv = p.peer_recv[p.rank] + n_local;
+        for (int r0 = 0; r0 < TN; r0 += 32) {      // uniform trip count: the shuffles below need whole warps
+          const int r = r0 + (threadIdx.x >> 2);
+          const int t = t0 + r;
+          const bool live = ok && r < TN && t < p.T;
+          float ss = 0.f;
+          if (live) {
+            float4 a[8];
+            if (p.rs_phase == 0) {
+              const float4* own = reinterpret_cast<const float4*>(tile_s + r * kRowPad + col);
+#pragma unroll
+              for (int q = 0; q < 8; ++q) a[q] = own[q];
+            } else {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) a[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            for (int src = 0; src < p.world; ++src) {   // rank order, the same on every rank's owner
+              if (p.rs_phase == 0 && src == p.rank) continue;
+              const float4* sp = reinterpret_cast<const float4*>(
+                  recv + (static_cast<long long>(src) * p.T_cap + t) * p.slice_cols);
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const float4 b = __ldcg(sp + q);
+                a[q].x += b.x; a[q].y += b.y; a[q].z += b.z; a[q].w += b.w;
+              }
+            }
+            const long long at = static_cast<long long>(t) * p.ld_resid + n_first;
+            uint4 o[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint4 rv = *reinterpret_cast<const uint4*>(my_x + at + q * 8);
+              const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
+              const float4 lo = a[2 * q], hi = a[2 * q + 1];
+              uint32_t* op = reinterpret_cast<uint32_t*>(&o[q]);
+              op[0] = pack_bf16x2(lo.x + __bfloat162float(rp[0].x), lo.y + __bfloat162float(rp[0].y));
+              op[1] = pack_bf16x2(lo.z + __bfloat162float(rp[1].x), lo.w + __bfloat162float(rp[1].y));
+              op[2] = pack_bf16x2(hi.x + __bfloat162float(rp[2].x), hi.y + __bfloat162float(rp[2].y));
+              op[3] = pack_bf16x2(hi.z + __bfloat162float(rp[3].x), hi.w + __bfloat162float(rp[3].y));
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const __nv_bfloat162 ob = *reinterpret_cast<const __nv_bfloat162*>(&op[e]);
+                const float f0 = __bfloat162float(ob.x), f1 = __bfloat162float(ob.y);
+                ss += f0 * f0 + f1 * f1;
+              }
+            }
+            for (int rk = 0; rk < p.world; ++rk) {   // hop 2: all-gather by push (own copy included)
+              uint4* dst = reinterpret_cast<uint4*>(p.peer_x[rk] + at);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) dst[q] = o[q];
+            }
+          }
+          // the four threads of a token row: sum of squares of the tile's 128 columns
+          ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+          ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+          if (live && seg == 0) {
+            const int tile_global = n0 / kTileN;
+            for (int rk = 0; rk < p.world; ++rk)
+              p.peer_ss[rk][static_cast<long long>(t) * kRsSsStride + tile_global] = ss;
+          }
+        }
+        __syncthreads();
+        if (ok && threadIdx.x < p.world) {
+          __threadfence_system();
+          red_release_sys_add(p.peer_xflag[threadIdx.x], 1u);
+        }
+        if (threadIdx.x == 0) *expected = target;
+      }
+      // what the next consumer of the residual stream has to wait for: one arrival per (column tile, token tile)
+      if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && p.rs_phase != 1)
+        p.rs_state->x_expected += static_cast<unsigned int>((p.N / kTileN) * gridDim.y);
     } else {
       const int n = n0 + warp * 32 + lane;
       const float bias = ((EPI == kEpiStore || EPI == kEpiResidual) && p.bias != nullptr && n < p.N) ? p.bias[n] : 0.f;
+      // tiles of conv channels (kEpiStore at decode): taps + SiLU + history roll here, activation to conv_out
+      const bool conv_tile = EPI == kEpiStore && p.conv_state != nullptr && n0 < p.conv_C;
+      float cw[4] = {0.f, 0.f, 0.f, 0.f};
+      if (conv_tile) {
+        const uint2 wv = *reinterpret_cast<const uint2*>(p.conv_w + static_cast<long long>(n) * 4);
+        const __nv_bfloat16* wp = reinterpret_cast<const __nv_bfloat16*>(&wv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) cw[j] = __bfloat162float(wp[j]);
+      }
+      __nv_bfloat16* const outp = conv_tile ? p.conv_out : p.out;
+      const long long ldo = conv_tile ? p.conv_C : p.ldo;
       for (int c = 0; c < TN; c += kChunk) {
         if (t0 + c >= p.T) break;
         float v[kChunk];
         load_acc(c, v);
+        if (conv_tile) {
+          // all history columns of the chunk's tokens first (48 independent loads), then taps and the roll
+          long long at[kChunk];
+          __nv_bfloat16 h[kChunk][3];
+#pragma unroll
+          for (int j = 0; j < kChunk; ++j) {
+            const int t = t0 + c + j;
+            at[j] = t < p.T ? static_cast<long long>(p.conv_slot[t]) * 3 * p.conv_C + n : -1;
+          }
+#pragma unroll
+          for (int j = 0; j < kChunk; ++j) {
+            if (at[j] >= 0) {
+              h[j][0] = p.conv_state[at[j]];
+              h[j][1] = p.conv_state[at[j] + p.conv_C];
+              h[j][2] = p.conv_state[at[j] + 2 * p.conv_C];
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < kChunk; ++j) {
+            if (at[j] >= 0) {
+              const __nv_bfloat16 xb = __float2bfloat16(v[j] + bias);   // the projection's bf16 value
+              float a = 0.f;
+              a += cw[0] * __bfloat162float(h[j][0]);
+              a += cw[1] * __bfloat162float(h[j][1]);
+              a += cw[2] * __bfloat162float(h[j][2]);
+              a += cw[3] * __bfloat162float(xb);
+              p.conv_state[at[j]] = h[j][1];
+              p.conv_state[at[j] + p.conv_C] = h[j][2];
+              p.conv_state[at[j] + 2 * p.conv_C] = xb;
+              v[j] = a / (1.f + __expf(-a)) - bias;   // (the bias is added back below; it is zero for these tiles)
+            }
+          }
+        }
         if constexpr (EPI == kEpiPartial) {
 #pragma unroll
           for (int j = 0; j < kChunk; ++j) {
@@ -388,8 +628,7 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
                 lo += __bfloat162float(r2[m].x);
                 hi += __bfloat162float(r2[m].y);
               }
-              *reinterpret_cast<uint32_t*>(p.out + static_cast<long long>(t) * p.ldo + ne) =
-                  pack_bf16x2(lo, hi);
+              *reinterpret_cast<uint32_t*>(outp + static_cast<long long>(t) * ldo + ne) = pack_bf16x2(lo, hi);
             }
           }
         }
@@ -859,6 +1098,7 @@ int gemm_pick_splits(int T, int N, int K, int epi, int sm_count) {
   int s = sm_count / tiles;
   if (s > 8) s = 8;
   if (tn == 64 && s > 6) s = 6;
+  if (tn == 64 && epi == kEpiRsAg && s > 5) s = 5;   // its row staging tile shares the pipeline stages
   while (s > 1 && num_kb / s < 8) --s;
   while (s > 1 && (num_kb + s - 1) / s * (s - 1) >= num_kb) --s;  // no empty trailing split
   return s < 1 ? 1 : s;
@@ -889,7 +1129,7 @@ const char* gemm_bf16(const GemmArgs& a) {
     if (splits > cap) return "gemm_bf16: in-cluster split exceeds the tile's limit";
     kp.cluster = splits;
   }
-  if (a.epi == kEpiPushPartial || a.epi == kEpiPushAll) {
+  if (a.epi == kEpiPushPartial || a.epi == kEpiPushAll || a.epi == kEpiRsAg) {
     if (a.world < 1 || a.world > kMaxRanks || a.rank < 0 || a.rank >= a.world) return "gemm_bf16: bad rank/world";
     kp.rank = a.rank;
     kp.world = a.world;
@@ -907,6 +1147,59 @@ const char* gemm_bf16(const GemmArgs& a) {
     if (a.call_idx == nullptr || a.T_cap < kp.T) return "gemm_bf16: push-all needs the call counter and T <= T_cap";
     kp.call_idx = a.call_idx;
     kp.T_cap = a.T_cap;
+  }
+  if (a.epi == kEpiRsAg) {
+    if (kp.N % a.world || (kp.N / a.world) % kTileN) return "gemm_bf16: N / world must be a multiple of 128";
+    if (kp.N / a.world / kTileN > kRsMaxOwnTiles || kp.N / kTileN > kRsSsStride)
+      return "gemm_bf16: too many column tiles for the reduce-scatter bookkeeping";
+    if ((kp.T + tn - 1) / tn > kRsMaxTokenTiles || a.T_cap < kp.T) return "gemm_bf16: too many rows for the receive buffer";
+    if (a.rs_state == nullptr || a.rs_phase < 0 || a.rs_phase > 2 || (a.ld_resid % 8))
+      return "gemm_bf16: reduce-scatter epilogue needs its state, a phase in 0..2 and a residual stride that is a multiple of 8";
+    if (kp.T > 128) return "gemm_bf16: reduce-scatter epilogue is for decode sizes (T <= 128)";
+    // the fp32 tile is staged behind the split-K landing zone inside the pipeline stages
+    if (tn == 64 && splits > 5) return "gemm_bf16: reduce-scatter epilogue with a 64-token tile allows at most 5 splits";
+    for (int r = 0; r < a.world; ++r)
+      if (reinterpret_cast<uintptr_t>(a.peer_x[r]) & 15) return "gemm_bf16: residual buffers must be 16-byte aligned";
+    // an owner CTA waits for peers while it holds its SM: every CTA of the grid has to be resident at once
+    if (a.rs_phase == 0 && static_cast<long long>(kp.N / kTileN) * ((kp.T + tn - 1) / tn) * splits > device_sm_count())
+      return "gemm_bf16: reduce-scatter epilogue needs a grid that is resident at once";
+    kp.slice_cols = kp.N / a.world;
+    kp.T_cap = a.T_cap;
+    kp.ld_resid = a.ld_resid;
+    kp.rs_state = a.rs_state;
+    kp.rs_phase = a.rs_phase;
+    for (int r = 0; r < a.world; ++r) {
+      if (a.peer_x[r] == nullptr || a.peer_ss[r] == nullptr || a.peer_xflag[r] == nullptr)
+        return "gemm_bf16: missing residual pointer of a rank";
+      kp.peer_x[r] = static_cast<__nv_bfloat16*>(a.peer_x[r]);
+      kp.peer_ss[r] = a.peer_ss[r];
+      kp.peer_xflag[r] = a.peer_xflag[r];
+    }
+  }
+  if (a.gather.flag != nullptr) {
+    if (a.epi != kEpiStore && a.epi != kEpiSwiglu) return "gemm_bf16: the gathered input needs the store or SwiGLU epilogue";
+    if (a.gather.target == nullptr || a.gather.ss == nullptr || a.gather.ss_tiles < 1 ||
+        a.gather.ss_tiles > kRsSsStride || a.gather.n_features < 1 || kp.T > 256)
+      return "gemm_bf16: bad gathered-input description";
+    kp.g_flag = a.gather.flag;
+    kp.g_target = a.gather.target;
+    kp.g_ss = a.gather.ss;
+    kp.g_tiles = a.gather.ss_tiles;
+    kp.g_inv_n = 1.f / static_cast<float>(a.gather.n_features);
+    kp.g_eps = a.gather.eps;
+  }
+  if (a.conv.state != nullptr) {
+    if (a.epi != kEpiStore || a.bias != nullptr || a.act != kActNone)
+      return "gemm_bf16: the conv epilogue needs the plain store epilogue";
+    if (a.conv.w == nullptr || a.conv.slot == nullptr || a.conv.out == nullptr || a.conv.C <= 0 ||
+        a.conv.C % kTileN || a.conv.C > kp.N || kp.T > 256)
+      return "gemm_bf16: bad conv description (C must be a multiple of 128 within N, decode sizes only)";
+    if (reinterpret_cast<uintptr_t>(a.conv.w) & 7) return "gemm_bf16: conv weights must be 8-byte aligned";
+    kp.conv_w = static_cast<const __nv_bfloat16*>(a.conv.w);
+    kp.conv_state = static_cast<__nv_bfloat16*>(a.conv.state);
+    kp.conv_slot = a.conv.slot;
+    kp.conv_out = static_cast<__nv_bfloat16*>(a.conv.out);
+    kp.conv_C = a.conv.C;
   }
   kp.swiglu_half = a.epi == kEpiSwiglu ? kp.N / 2 : 0;
   if (a.epi == kEpiSwiglu && (kp.N % 4)) return "gemm_bf16: SwiGLU needs N % 4 == 0";
@@ -933,7 +1226,8 @@ const char* gemm_bf16(const GemmArgs& a) {
     const char* e = getenv("NFB_GEMM_PERSISTENT");
     return !(e != nullptr && e[0] == '0');
   }();
-  if (tn == kPersistTN && splits == 1 && persistent_enabled && !g_trace_enabled &&
+  if (tn == kPersistTN && splits == 1 && persistent_enabled && !g_trace_enabled && a.gather.flag == nullptr &&
+      a.conv.state == nullptr &&
       (a.epi == kEpiStore || a.epi == kEpiResidual || a.epi == kEpiSwiglu) &&
       static_cast<long long>(grid.x) * grid.y > device_sm_count()) {
     const int n_tiles = static_cast<int>(grid.x * grid.y);
@@ -951,6 +1245,7 @@ const char* gemm_bf16(const GemmArgs& a) {
     case kEpiPartial: e = launch_tn<kEpiPartial>(tn, tw, tx, kp, grid, a.stream, a.pdl); break;
     case kEpiPushPartial: e = launch_tn<kEpiPushPartial>(tn, tw, tx, kp, grid, a.stream, a.pdl); break;
     case kEpiPushAll: e = launch_tn<kEpiPushAll>(tn, tw, tx, kp, grid, a.stream, a.pdl); break;
+    case kEpiRsAg: e = launch_tn<kEpiRsAg>(tn, tw, tx, kp, grid, a.stream, a.pdl); break;
     default: return "gemm_bf16: unknown epilogue";
   }
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);

@@ -16,8 +16,16 @@
 //
 // Rules for callers:
 //   * splits * T * N must not exceed kNoAllocScratchFloats (4 Mi floats); larger problems are refused.
+//   * T <= 256, N <= 8192 and N % 8 == 0; K, ldx and ldw multiples of 8; x, w and resid 16-byte aligned
+//     (the second kernel updates the residual with 16-byte accesses).  Anything else is refused before a
+//     kernel is launched, so a refused call leaves the scratch and the residual untouched.
+//   * The kernels' internal waits are bounded.  Should one ever run out, the call that hit it cannot know
+//     (it has returned already): the failure is recorded on the device, copied to the host at the end of that
+//     call's stream work, and the NEXT call on that device returns code 5 without launching anything.
 //   * The first call on a device looks up the scratch array's device address (cudaGetSymbolAddress with
-//     that device current).  Make that first call outside any stream capture.
+//     that device current).  Make that first call outside any stream capture, and early: when the CUDA
+//     runtime loads modules lazily, this look-up is also the moment the driver instantiates the library's
+//     static array on that device (free device memory drops by 16 MiB once, there and never again).
 //   * All calls share the one scratch array.  Nothing in it has to start at zero (each call overwrites
 //     every partial it later reads), but two calls that overlap on the GPU (different streams, or
 //     programmatic overlap) race on it: serialise them.

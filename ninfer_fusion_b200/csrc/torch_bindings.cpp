@@ -42,9 +42,28 @@ int64_t sm_count() {
   return n;
 }
 
+// Optional decode conv epilogue (nfb::GemmConv): all four tensors or none.
+void fill_conv(nfb::GemmArgs& a, OptT conv_w, OptT conv_state, OptT conv_slot, OptT conv_out) {
+  if (!(conv_state.has_value() && conv_state->defined())) return;
+  TORCH_CHECK(conv_w.has_value() && conv_slot.has_value() && conv_out.has_value(), "conv epilogue: all four tensors");
+  need(*conv_w, at::kBFloat16, "conv_w"); need(*conv_state, at::kBFloat16, "conv_state");
+  need(*conv_slot, at::kInt, "conv_slot"); need(*conv_out, at::kBFloat16, "conv_out");
+  TORCH_CHECK(conv_w->dim() == 2 && conv_w->size(1) == 4 && conv_w->is_contiguous(), "conv_w must be [C, 4]");
+  const int64_t C = conv_w->size(0);
+  TORCH_CHECK(conv_state->dim() == 3 && conv_state->size(1) == 3 && conv_state->size(2) == C && conv_state->is_contiguous(),
+              "conv_state must be [slots, 3, C]");
+  TORCH_CHECK(conv_out->dim() == 2 && conv_out->size(0) == a.T && conv_out->size(1) == C && conv_out->is_contiguous(),
+              "conv_out must be [T, C]");
+  TORCH_CHECK(conv_slot->numel() >= a.T && conv_slot->is_contiguous(), "conv_slot must hold one slot per token");
+  a.conv.w = conv_w->data_ptr(); a.conv.state = conv_state->data_ptr();
+  a.conv.slot = static_cast<const int*>(conv_slot->data_ptr()); a.conv.out = conv_out->data_ptr();
+  a.conv.C = static_cast<int>(C);
+}
+
 // out = epilogue(x @ w^T).  epi: 0 store(+bias), 1 residual add, 2 swiglu, 3 split-K partials.
 void gemm_bf16(const Tensor& x, const Tensor& w, OptT out, int64_t epi, OptT resid, OptT bias, OptT partial,
-               int64_t splits, OptT status, bool pdl, int64_t act) {
+               int64_t splits, OptT status, bool pdl, int64_t act, OptT conv_w, OptT conv_state, OptT conv_slot,
+               OptT conv_out) {
   need(x, at::kBFloat16, "x"); need(w, at::kBFloat16, "w");
   need_rows(x, "x"); need_rows(w, "w");
   TORCH_CHECK(x.size(1) == w.size(1), "gemm_bf16: K mismatch");
@@ -80,6 +99,7 @@ void gemm_bf16(const Tensor& x, const Tensor& w, OptT out, int64_t epi, OptT res
   a.splits = static_cast<int>(splits); a.epi = static_cast<int>(epi); a.act = static_cast<int>(act);
   a.status = ptr_or_null<int>(status);
   a.stream = cur_stream(); a.pdl = pdl;
+  fill_conv(a, conv_w, conv_state, conv_slot, conv_out);
   chk(nfb::gemm_bf16(a));
 }
 
@@ -555,12 +575,14 @@ void gemm_bf16_push(const Tensor& x, const Tensor& w, int64_t splits, int64_t wo
 void tp_reduce_ag_norm(int64_t world, int64_t rank, int64_t T, int64_t T_cap, int64_t N, int64_t splits,
                        int64_t arrivals, at::IntArrayRef peer_bases, int64_t recv_off, int64_t flag_off,
                        int64_t x_off, int64_t ss_off, int64_t row_flag_off, OptT norm_w, OptT normed, double eps,
-                       bool unit_offset, const Tensor& state, OptT status, bool pdl) {
+                       bool unit_offset, const Tensor& state, OptT status, bool pdl, int64_t phases) {
   TORCH_CHECK(static_cast<int64_t>(peer_bases.size()) == world && world <= nfb::kMaxTpRanks, "peer_bases size");
   need(state, at::kByte, "state");
   TORCH_CHECK(state.numel() >= static_cast<int64_t>(sizeof(nfb::TpState)), "state too small");
+  TORCH_CHECK(phases >= 1 && phases <= 3, "phases must be 1, 2 or 3");
   c10::cuda::CUDAGuard guard(state.device());
   nfb::TpReduceParams p = {};
+  p.phases = static_cast<int>(phases);
   p.world = static_cast<int>(world); p.rank = static_cast<int>(rank); p.T = static_cast<int>(T);
   p.T_cap = static_cast<int>(T_cap); p.N = static_cast<int>(N); p.splits = static_cast<int>(splits);
   p.arrivals_this_call = static_cast<unsigned int>(arrivals);
@@ -592,7 +614,9 @@ void tp_reduce_ag_norm(int64_t world, int64_t rank, int64_t T, int64_t T_cap, in
 }
 
 void tp_argmax(int64_t world, int64_t rank, int64_t T_cap, const Tensor& logits, at::IntArrayRef peer_bases,
-               int64_t cand_off, int64_t flag_off, const Tensor& out, const Tensor& state, OptT status, bool pdl) {
+               int64_t cand_off, int64_t flag_off, const Tensor& out, const Tensor& state, OptT status, bool pdl,
+               int64_t phases) {
+  TORCH_CHECK(phases >= 1 && phases <= 3, "phases must be 1, 2 or 3");
   need(logits, at::kBFloat16, "logits"); need_rows(logits, "logits"); need(out, at::kInt, "out");
   need(state, at::kByte, "state");
   TORCH_CHECK(static_cast<int64_t>(peer_bases.size()) == world && world <= nfb::kMaxTpRanks, "peer_bases size");
@@ -612,6 +636,7 @@ void tp_argmax(int64_t world, int64_t rank, int64_t T_cap, const Tensor& logits,
   p.out = static_cast<int*>(out.data_ptr());
   p.state = reinterpret_cast<nfb::TpState*>(state.data_ptr());
   p.status = ptr_or_null<int>(status);
+  p.phases = static_cast<int>(phases);
   chk(nfb::tp_argmax(p, cur_stream(), pdl));
 }
 
@@ -669,6 +694,93 @@ void tp_sum_norm(int64_t world, int64_t T_cap, int64_t arrivals, int64_t my_base
   chk(nfb::tp_sum_norm(p, cur_stream(), pdl));
 }
 
+// Row-parallel GEMM whose epilogue reduce-scatters into the owner rank, reduces there and all-gathers the new
+// residual tile (gemm kEpiRsAg).  All buffers are offsets into the ranks' symmetric allocations.
+void gemm_bf16_rs_ag(const Tensor& x, const Tensor& w, int64_t splits, int64_t world, int64_t rank,
+                     at::IntArrayRef peer_bases, int64_t recv_off, int64_t flag_off, int64_t x_off, int64_t ss_off,
+                     int64_t xflag_off, int64_t T_cap, int64_t ld_resid, const Tensor& state, int64_t phase,
+                     OptT status, bool pdl) {
+  need(x, at::kBFloat16, "x"); need(w, at::kBFloat16, "w"); need_rows(x, "x"); need_rows(w, "w");
+  need(state, at::kByte, "state");
+  TORCH_CHECK(x.size(1) == w.size(1), "gemm_bf16_rs_ag: K mismatch");
+  TORCH_CHECK(static_cast<int64_t>(peer_bases.size()) == world && world <= nfb::kMaxRanks, "peer_bases size");
+  TORCH_CHECK(state.numel() >= static_cast<int64_t>(sizeof(nfb::RsState)), "state too small");
+  c10::cuda::CUDAGuard guard(x.device());
+  nfb::GemmArgs a;
+  a.w = w.data_ptr(); a.N = w.size(0); a.K = w.size(1); a.ldw = w.stride(0);
+  a.x = x.data_ptr(); a.T = x.size(0); a.ldx = x.stride(0);
+  a.splits = static_cast<int>(splits); a.epi = nfb::kEpiRsAg;
+  a.world = static_cast<int>(world); a.rank = static_cast<int>(rank);
+  a.T_cap = static_cast<int>(T_cap); a.ld_resid = ld_resid;
+  a.rs_state = reinterpret_cast<nfb::RsState*>(state.data_ptr());
+  a.rs_phase = static_cast<int>(phase);
+  for (int r = 0; r < world; ++r) {
+    a.peer_recv[r] = reinterpret_cast<float*>(peer_bases[r] + recv_off);
+    a.peer_flag[r] = reinterpret_cast<unsigned int*>(peer_bases[r] + flag_off);
+    a.peer_x[r] = reinterpret_cast<void*>(peer_bases[r] + x_off);
+    a.peer_ss[r] = reinterpret_cast<float*>(peer_bases[r] + ss_off);
+    a.peer_xflag[r] = reinterpret_cast<unsigned int*>(peer_bases[r] + xflag_off);
+  }
+  a.ldo = 2;
+  a.status = ptr_or_null<int>(status); a.stream = cur_stream(); a.pdl = pdl;
+  chk(nfb::gemm_bf16(a));
+}
+
+// Column-parallel GEMM (store or SwiGLU epilogue) that waits for the all-gathered residual stream by itself and
+// applies the RMS norm as a row scale (see nfb::GemmGather).
+void gemm_bf16_gathered(const Tensor& x, const Tensor& w, const Tensor& out, int64_t epi, int64_t splits,
+                        int64_t my_base, int64_t ss_off, int64_t xflag_off, int64_t n_features, double eps,
+                        const Tensor& state, OptT status, bool pdl, OptT conv_w, OptT conv_state, OptT conv_slot,
+                        OptT conv_out) {
+  need(x, at::kBFloat16, "x"); need(w, at::kBFloat16, "w"); need(out, at::kBFloat16, "out");
+  need_rows(x, "x"); need_rows(w, "w"); need_rows(out, "out");
+  need(state, at::kByte, "state");
+  TORCH_CHECK(x.size(1) == w.size(1), "gemm_bf16_gathered: K mismatch");
+  TORCH_CHECK(epi == nfb::kEpiStore || epi == nfb::kEpiSwiglu, "gemm_bf16_gathered: store or SwiGLU epilogue");
+  TORCH_CHECK(state.numel() >= static_cast<int64_t>(sizeof(nfb::RsState)), "state too small");
+  TORCH_CHECK(n_features == x.size(1) && n_features % 128 == 0, "gemm_bf16_gathered: the GEMM's K must be the normalised width");
+  c10::cuda::CUDAGuard guard(x.device());
+  nfb::GemmArgs a;
+  a.w = w.data_ptr(); a.N = w.size(0); a.K = w.size(1); a.ldw = w.stride(0);
+  a.x = x.data_ptr(); a.T = x.size(0); a.ldx = x.stride(0);
+  const int64_t out_cols = epi == nfb::kEpiSwiglu ? a.N / 2 : a.N;
+  TORCH_CHECK(out.size(0) == a.T && out.size(1) == out_cols, "gemm_bf16_gathered: out shape");
+  a.out = out.data_ptr(); a.ldo = out.stride(0);
+  a.splits = static_cast<int>(splits); a.epi = static_cast<int>(epi);
+  a.gather.flag = reinterpret_cast<const unsigned int*>(my_base + xflag_off);
+  a.gather.target = &reinterpret_cast<const nfb::RsState*>(state.data_ptr())->x_expected;
+  a.gather.ss = reinterpret_cast<const float*>(my_base + ss_off);
+  a.gather.ss_tiles = static_cast<int>(n_features / 128);
+  a.gather.n_features = static_cast<int>(n_features);
+  a.gather.eps = static_cast<float>(eps);
+  a.status = ptr_or_null<int>(status); a.stream = cur_stream(); a.pdl = pdl;
+  fill_conv(a, conv_w, conv_state, conv_slot, conv_out);
+  chk(nfb::gemm_bf16(a));
+}
+
+void tp_gather_norm(const Tensor& x, const Tensor& norm_w, const Tensor& normed, int64_t my_base, int64_t xflag_off,
+                    double eps, bool unit_offset, const Tensor& state, OptT status, bool pdl) {
+  need(x, at::kBFloat16, "x"); need(norm_w, at::kBFloat16, "norm_w"); need(normed, at::kBFloat16, "normed");
+  need_rows(x, "x"); need(state, at::kByte, "state");
+  TORCH_CHECK(normed.is_contiguous() && normed.dim() == 2 && normed.size(0) == x.size(0) && normed.size(1) == x.size(1),
+              "tp_gather_norm: normed shape");
+  TORCH_CHECK(norm_w.numel() == x.size(1) && norm_w.is_contiguous(), "tp_gather_norm: norm weight shape");
+  TORCH_CHECK(state.numel() >= static_cast<int64_t>(sizeof(nfb::RsState)), "state too small");
+  c10::cuda::CUDAGuard guard(x.device());
+  nfb::TpGatherNormParams p = {};
+  p.T = static_cast<int>(x.size(0)); p.N = static_cast<int>(x.size(1));
+  p.flag = reinterpret_cast<const unsigned int*>(my_base + xflag_off);
+  p.target = &reinterpret_cast<const nfb::RsState*>(state.data_ptr())->x_expected;
+  p.x = static_cast<const __nv_bfloat16*>(x.data_ptr()); p.ldx = x.stride(0);
+  p.norm_w = static_cast<const __nv_bfloat16*>(norm_w.data_ptr());
+  p.normed = static_cast<__nv_bfloat16*>(normed.data_ptr());
+  p.eps = static_cast<float>(eps); p.unit_offset = unit_offset ? 1 : 0;
+  p.status = ptr_or_null<int>(status);
+  chk(nfb::tp_gather_norm(p, cur_stream(), pdl));
+}
+
+int64_t rs_state_bytes() { return static_cast<int64_t>(sizeof(nfb::RsState)); }
+
 int64_t tp_state_bytes() { return static_cast<int64_t>(sizeof(nfb::TpState)); }
 
 }  // namespace
@@ -677,12 +789,16 @@ TORCH_LIBRARY(nfb200, m) {
   m.def("symm_alloc(int bytes) -> (Tensor, Tensor)", &symm_alloc);
   m.def("symm_open(Tensor handle) -> int", &symm_open);
   m.def("gemm_bf16_push(Tensor x, Tensor w, int splits, int world, int rank, int[] peer_bases, int recv_off, int flag_off, Tensor? status, bool pdl) -> ()", &gemm_bf16_push);
-  m.def("tp_reduce_ag_norm(int world, int rank, int T, int T_cap, int N, int splits, int arrivals, int[] peer_bases, int recv_off, int flag_off, int x_off, int ss_off, int row_flag_off, Tensor? norm_w, Tensor? normed, float eps, bool unit_offset, Tensor state, Tensor? status, bool pdl) -> ()", &tp_reduce_ag_norm);
-  m.def("tp_argmax(int world, int rank, int T_cap, Tensor logits, int[] peer_bases, int cand_off, int flag_off, Tensor out, Tensor state, Tensor? status, bool pdl) -> ()", &tp_argmax);
+  m.def("tp_reduce_ag_norm(int world, int rank, int T, int T_cap, int N, int splits, int arrivals, int[] peer_bases, int recv_off, int flag_off, int x_off, int ss_off, int row_flag_off, Tensor? norm_w, Tensor? normed, float eps, bool unit_offset, Tensor state, Tensor? status, bool pdl, int phases=3) -> ()", &tp_reduce_ag_norm);
+  m.def("tp_argmax(int world, int rank, int T_cap, Tensor logits, int[] peer_bases, int cand_off, int flag_off, Tensor out, Tensor state, Tensor? status, bool pdl, int phases=3) -> ()", &tp_argmax);
   m.def("tp_state_bytes() -> int", &tp_state_bytes);
+  m.def("rs_state_bytes() -> int", &rs_state_bytes);
+  m.def("gemm_bf16_rs_ag(Tensor x, Tensor w, int splits, int world, int rank, int[] peer_bases, int recv_off, int flag_off, int x_off, int ss_off, int xflag_off, int T_cap, int ld_resid, Tensor state, int phase, Tensor? status, bool pdl) -> ()", &gemm_bf16_rs_ag);
+  m.def("gemm_bf16_gathered(Tensor x, Tensor w, Tensor out, int epi, int splits, int my_base, int ss_off, int xflag_off, int n_features, float eps, Tensor state, Tensor? status, bool pdl, Tensor? conv_w=None, Tensor? conv_state=None, Tensor? conv_slot=None, Tensor? conv_out=None) -> ()", &gemm_bf16_gathered);
+  m.def("tp_gather_norm(Tensor x, Tensor norm_w, Tensor normed, int my_base, int xflag_off, float eps, bool unit_offset, Tensor state, Tensor? status, bool pdl) -> ()", &tp_gather_norm);
   m.def("gemm_bf16_push_all(Tensor x, Tensor w, int splits, int world, int rank, int[] peer_bases, int recv_off, int flag_off, int T_cap, Tensor state, Tensor? status, bool pdl) -> ()", &gemm_bf16_push_all);
   m.def("tp_sum_norm(int world, int T_cap, int arrivals, int my_base, int recv_off, int flag_off, Tensor x, Tensor? norm_w, Tensor? normed, float eps, bool unit_offset, Tensor state, Tensor? status, bool pdl) -> ()", &tp_sum_norm);
-  m.def("gemm_bf16(Tensor x, Tensor w, Tensor? out, int epi, Tensor? resid, Tensor? bias, Tensor? partial, int splits, Tensor? status, bool pdl, int act=0) -> ()", &gemm_bf16);
+  m.def("gemm_bf16(Tensor x, Tensor w, Tensor? out, int epi, Tensor? resid, Tensor? bias, Tensor? partial, int splits, Tensor? status, bool pdl, int act=0, Tensor? conv_w=None, Tensor? conv_state=None, Tensor? conv_slot=None, Tensor? conv_out=None) -> ()", &gemm_bf16);
   m.def("gemm_trace(bool enable, int n_ctas) -> Tensor", &gemm_trace);
   m.def("gemm_pick_splits(int T, int N, int K, int epi) -> int", &gemm_pick_splits);
   m.def("add_rmsnorm(Tensor? partial, int splits, Tensor? delta, Tensor? resid_in, Tensor? resid_out, Tensor? norm_w, Tensor? normed, int T, int N, float eps, bool unit_offset, bool pdl, Tensor? q_codes=None, Tensor? q_sf=None) -> ()", &add_rmsnorm);

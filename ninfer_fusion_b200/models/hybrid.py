@@ -246,8 +246,12 @@ class HybridModel:
         self._rot_scratch: Dict[tuple, torch.Tensor] = {}   # rotated activations / gate-up rows of groupwise-int weights
         self.groupint_dense_prefill = os.environ.get("NFB_GROUPINT_DENSE", "1") != "0"
         self.cluster_splitk = True  # False: split-K through an fp32 workspace + reduce kernel
+        self.fuse_conv = os.environ.get("NFB_FUSE_CONV", "1") != "0"   # GDN decode conv inside the in_proj epilogue
         self.attn_impl = 0  # 0 = pick, 1 = SIMT, 2 = tensor-core split-KV attention
         self.comm = None  # tensor-parallel communicator (parallel.tp), None on one GPU
+        # (norm weight, normed buffer, T) while the residual stream of the last row-parallel GEMM is still being
+        # gathered from the owner ranks and ws.normed has not been written (tensor parallel, decode sizes)
+        self._gathered = None
         self.act_nvfp4 = any(isinstance(t, QuantWeight) and t.qtype == 2 for t in weights.values())
         self._prequant = None
         self._qbuf: Dict[int, tuple] = {}
@@ -320,7 +324,9 @@ class HybridModel:
             self.ops.quant_act_fp8(x, xc, scale, self.pdl)
             self.ops.gemm_quant(1, xc, scale, w.codes, w.scale, 1.0, out, epi, resid, splits, self.status.tensor, self.pdl)
 
-    def _gemm(self, x, w, out, epi=EPI_STORE, resid=None):
+    def _gemm(self, x, w, out, epi=EPI_STORE, resid=None, conv=None):
+        if conv is not None and not (isinstance(w, torch.Tensor) and epi == EPI_STORE):
+            raise ValueError("the conv epilogue exists for bf16 weights with the store epilogue only")
         if isinstance(w, QuantWeight):
             self._gemm_quant(x, w, out, epi, resid)
             return
@@ -353,7 +359,25 @@ class HybridModel:
             w = w.dense()
         # in-cluster split-K when the output tiles alone cannot fill the GPU (decode, sharded weights)
         splits = int(self.ops.gemm_pick_splits(x.shape[0], w.shape[0], w.shape[1], epi)) if self.cluster_splitk else 1
-        self.ops.gemm_bf16(x, w, out, epi, resid, None, None, splits, self.status.tensor, self.pdl)
+        self.ops.gemm_bf16(x, w, out, epi, resid, None, None, splits, self.status.tensor, self.pdl, 0,
+                           *(conv or (None, None, None, None)))
+
+    def _materialize_normed(self, ws: Workspace) -> None:
+        """Writes the normalised copy that a pending gather (see `_gathered`) has left out."""
+        if self._gathered is not None:
+            norm_w, normed_out, T = self._gathered
+            self._gathered = None
+            self.comm.gather_norm(self, ws, T, norm_w, normed_out)
+
+    def _gemm_normed(self, ws: Workspace, T: int, w, out, epi=EPI_STORE, conv=None):
+        """out = epilogue(normed residual @ w^T): the consumer of the last `_gemm_to_residual`.  `conv` (bf16
+        weights only) fuses the decode conv + SiLU + history roll of the leading output columns into the epilogue."""
+        if self._gathered is not None:
+            if self.comm.can_gather(w):
+                self.comm.gemm_gathered(self, ws, T, w, out, epi, conv)
+                return
+            self._materialize_normed(ws)
+        self._gemm(ws.normed[:T], w, out, epi, conv=conv)
 
     def _gemm_to_residual(self, ws: Workspace, a, w, T: int, norm_w, normed_out):
         """x += a @ w^T ; normed_out = rmsnorm(x) * (1 + norm_w).  x is ws.x[:T] (in place)."""
@@ -384,7 +408,7 @@ class HybridModel:
         D = cfg.head_dim
         w_in = self.w[f"{prefix}/attn/in_proj"]
         proj = ws.proj[:T, : w_in.shape[0]]
-        self._gemm(ws.normed[:T], w_in, proj)
+        self._gemm_normed(ws, T, w_in, proj)
         q_dim, kv_dim = g.n_q_heads * D, g.n_kv_heads * D
         planes = kv.layers[kv_index]
         q = ws.q[:T]
@@ -421,12 +445,18 @@ class HybridModel:
         w_in = self.w[f"{prefix}/gdn/in_proj"]
         # a verify pass writes its projections into the layer's record instead of the shared scratch
         proj = (ws.proj if rec is None else rec.proj[gi])[:T, : w_in.shape[0]]
-        self._gemm(ws.normed[:T], w_in, proj)
         C = g.gdn_conv_dim
         conv = (ws.conv if rec is None else rec.conv[gi])[:T]
-        ops.causal_conv1d_silu(proj, 0, C, self.w[f"{prefix}/gdn/conv_w"], b.cu_seqlens, b.token_seq, b.state_slot,
-                               st.conv[gi], conv, write_state, b.n_tokens == b.n_seqs and b.one_token_per_seq, self.pdl,
-                               None, False, b.tree_parent, None)
+        decode = b.n_tokens == b.n_seqs and b.one_token_per_seq
+        if (self.fuse_conv and decode and write_state and rec is None and b.tree_parent is None and C % 128 == 0
+                and isinstance(w_in, torch.Tensor) and w_in.dtype == torch.bfloat16):
+            # decode: conv taps + SiLU + history roll in the projection's epilogue (token i is sequence i)
+            self._gemm_normed(ws, T, w_in, proj, EPI_STORE,
+                              (self.w[f"{prefix}/gdn/conv_w"], st.conv[gi], b.state_slot, conv))
+        else:
+            self._gemm_normed(ws, T, w_in, proj)
+            ops.causal_conv1d_silu(proj, 0, C, self.w[f"{prefix}/gdn/conv_w"], b.cu_seqlens, b.token_seq, b.state_slot,
+                                   st.conv[gi], conv, write_state, decode, self.pdl, None, False, b.tree_parent, None)
         qk = g.gdn_qk_dim
         out = ws.mix_gdn[:T]
         # long prefill chunks take the chunked tensor-core formulation (three launches), everything else the
@@ -448,7 +478,7 @@ class HybridModel:
     def _mlp(self, ws: Workspace, T: int, prefix: str, next_norm_w, normed_out):
         w_gu = self.w[f"{prefix}/mlp/gate_up"]
         act = ws.act[:T, : w_gu.shape[0] // 2]
-        self._gemm(ws.normed[:T], w_gu, act, EPI_SWIGLU)
+        self._gemm_normed(ws, T, w_gu, act, EPI_SWIGLU)
         w_down = self.w[f"{prefix}/mlp/down"]
         self._gemm_to_residual(ws, ws.act[:T, : w_down.shape[1]], w_down, T, next_norm_w, normed_out)
 
@@ -518,6 +548,7 @@ class HybridModel:
         if cfg.moe is None:
             self._mlp(ws, T, p, w["mtp/final_norm"], ws.normed[:T])
         else:
+            self._materialize_normed(ws)
             if self.moe is None or self.moe.max_tokens < ws.max_tokens:
                 from .moe import MoeBlock
                 self.moe = MoeBlock(cfg, self.device, ws.max_tokens, *self.ep, expert_format=self.expert_format)
@@ -563,10 +594,12 @@ class HybridModel:
             if cfg.moe is None:
                 self._mlp(ws, T, p, nxt, ws.normed[:T])
             else:
+                self._materialize_normed(ws)
                 if self.moe is None or self.moe.max_tokens < ws.max_tokens:
                     from .moe import MoeBlock
                     self.moe = MoeBlock(cfg, self.device, ws.max_tokens, *self.ep, expert_format=self.expert_format)
                 self.moe.forward(self, ws, T, p, nxt, ws.normed[:T], self.moe_global_tokens)
+        self._materialize_normed(ws)
         return ws.normed[:T] if end_layer == cfg.n_layers else x
 
     def logits(self, ws: Workspace, b: StepBatch, hidden: torch.Tensor) -> torch.Tensor:

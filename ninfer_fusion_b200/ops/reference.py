@@ -1,8 +1,8 @@
 """Plain-PyTorch fp32 oracles of every kernel's math.
 
-These run on CPU and are the numerics baseline for the CUDA kernels (the pool
-this project is developed on has no compute-sanitizer, so independent oracles
-at small exhaustive shapes are the safety net).  Contracts follow the
+These run on CPU and are the numerics baseline for the CUDA kernels: independent
+oracles at small exhaustive shapes are the safety net where no memory checker
+runs.  Contracts follow the
 reference's operator headers (include/ninfer/ops/*.h); bf16 rounding points
 are placed where an operator boundary stores bf16.
 """

@@ -12,7 +12,7 @@ those steps between the ranks (stores and adds to different destinations are sep
 consumer always reads the payloads of its own call (nothing stale, nothing overwritten early) and that no schedule
 deadlocks.  With depth = 2 (the kernels' parity buffers) the protocol is safe; with depth = 1 the scan finds the
 overwrite, which is why the parity exists.  This is the host-side proof that stands in for a race detector on the
-device (compute-sanitizer is not available on the pool); the reference keeps the same kind of scan for its 2-rank
+device; the reference keeps the same kind of scan for its 2-rank
 transport (src/core/tp_transport.h: ordering scan of the slot protocol).
 """
 from __future__ import annotations

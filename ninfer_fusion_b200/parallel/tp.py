@@ -9,8 +9,15 @@ residual stream.  Every row-parallel GEMM is followed by a sum over ranks: here
 the GEMM epilogue itself pushes its partial tiles into the owning rank over
 NVLink (`gemm_bf16_push`), and one more kernel reduces, adds the residual,
 all-gathers the new residual by peer stores and RMS-normalises it for the next
-column-parallel GEMM (`tp_reduce_ag_norm`).  `mode="nccl"` keeps a plain
-NCCL all-reduce as the baseline for the same math.
+column-parallel GEMM (`tp_reduce_ag_norm`).  At decode sizes both hops happen
+inside the GEMM (`gemm_bf16_rs_ag`: the CTA that owns a column tile waits for
+the peers' tiles, reduces and pushes the new residual tile to every rank) and
+the next column-parallel GEMM waits for the gathered residual in its own TMA
+producer, with the RMS norm applied as a row scale in its epilogue
+(`gemm_bf16_gathered`; needs `fold_norms`).  `mode="oneshot"` keeps the older
+decode path (every rank receives every fp32 tile, one more kernel sums and
+normalises), `mode="nccl"` a plain NCCL all-reduce as the baseline for the
+same math.
 """
 from __future__ import annotations
 
@@ -110,6 +117,34 @@ def shard_weights(full: Dict[str, torch.Tensor], cfg: ModelConfig, rank: int, wo
 class TensorParallel:
     def __init__(self, cfg: ModelConfig, rank: int, world: int, device, max_tokens: int, mode: str = "fused",
                  group=None):
+        self._setup(cfg, rank, world, device, max_tokens, mode, group)
+        self.local, handle = self.ops.symm_alloc(self.total_bytes)
+        handles: List[Optional[torch.Tensor]] = [None] * world
+        dist.all_gather_object(handles, handle, group=group)
+        self._connect([self.local.data_ptr() if r == rank else int(self.ops.symm_open(handles[r]))
+                       for r in range(world)])
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=group)
+
+    @classmethod
+    def loopback(cls, cfg: ModelConfig, world: int, device, max_tokens: int, mode: str = "fused") -> List["TensorParallel"]:
+        """All `world` ranks inside one process on one GPU, each with its own symmetric allocation: the rank logic,
+        addressing and counters of the peer-memory kernels can then be walked through phase by phase (first every
+        rank's producing step, then every rank's consuming step, so that no kernel ever waits for a later launch).
+        The reference exercises its rank logic on one GPU the same way (src/core/virtual_device.h:137-145)."""
+        ranks = []
+        for r in range(world):
+            tp = cls.__new__(cls)
+            tp._setup(cfg, r, world, device, max_tokens, mode, None)
+            tp.local, _ = tp.ops.symm_alloc(tp.total_bytes)
+            ranks.append(tp)
+        bases = [tp.local.data_ptr() for tp in ranks]
+        for tp in ranks:
+            tp._connect(bases)
+        torch.cuda.synchronize(torch.device(device))
+        return ranks
+
+    def _setup(self, cfg: ModelConfig, rank: int, world: int, device, max_tokens: int, mode: str, group) -> None:
         self.cfg, self.rank, self.world = cfg, rank, world
         self.device = torch.device(device)
         self.mode = mode
@@ -122,27 +157,30 @@ class TensorParallel:
         # ---- one symmetric allocation, identical layout on every rank ----
         off = 0
         self.off: Dict[str, int] = {}
-        self.one_shot_rows = min(self.T_cap, 128)   # rows handled by the one-shot (push-all) path
+        self.one_shot_rows = min(self.T_cap, 128)   # rows handled by the decode-sized paths
         for name, nbytes in [("recv", world * self.T_cap * self.slice * 4),          # [src][T][N/W] fp32
                              ("recv_all", 2 * world * self.one_shot_rows * N * 4),   # [parity][src][rows][N] fp32
                              ("x", self.T_cap * N * 2), ("ss", 2 * self.T_cap * world * 4),
                              ("row_flag", self.T_cap * 4), ("arrival_flag", 256), ("all_flag", 256),
-                             ("cand", 2 * self.T_cap * world * 8), ("argmax_flag", self.T_cap * 4)]:
+                             ("cand", 2 * self.T_cap * world * 8), ("argmax_flag", self.T_cap * 4),
+                             # decode-sized reduce-scatter + all-gather inside the GEMM (gemm kEpiRsAg)
+                             ("rs_recv", self.one_shot_rows * N * 4),       # [src][rows][N/W] fp32
+                             ("rs_flag", 64 * 16 * 4),                      # per (owned tile, token tile)
+                             ("rs_ss", self.one_shot_rows * 64 * 4),        # [rows][64 column tiles] fp32
+                             ("x_flag", 256)]:
             self.off[name] = off
             off += _align(nbytes)
         self.total_bytes = off
-        self.local, handle = self.ops.symm_alloc(off)
-        handles: List[Optional[torch.Tensor]] = [None] * world
-        dist.all_gather_object(handles, handle, group=group)
-        self.peer_bases: List[int] = []
-        for r in range(world):
-            self.peer_bases.append(self.local.data_ptr() if r == rank else int(self.ops.symm_open(handles[r])))
         self.state = torch.zeros(int(self.ops.tp_state_bytes()), dtype=torch.uint8, device=self.device)
+        self.rs_state = torch.zeros(int(self.ops.rs_state_bytes()), dtype=torch.uint8, device=self.device)
+        self.fold = False   # set by fold_norms: layer norms are pure RMS scalings, their weights live in the GEMMs
+        self.delta = torch.empty((self.T_cap, N), dtype=torch.bfloat16, device=self.device)
+
+    def _connect(self, peer_bases: List[int]) -> None:
+        N = self.cfg.hidden
+        self.peer_bases = list(peer_bases)
         x_bytes = self.local[self.off["x"]: self.off["x"] + self.T_cap * N * 2]
         self.x = x_bytes.view(torch.bfloat16).view(self.T_cap, N)
-        self.delta = torch.empty((self.T_cap, N), dtype=torch.bfloat16, device=self.device)
-        torch.cuda.synchronize(self.device)
-        dist.barrier(group=group)
 
     # ------------------------------------------------------------------ weights
     def shard(self, full: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
@@ -184,7 +222,54 @@ class TensorParallel:
             out[name] = t
         return out
 
+    def fold_norms(self, weights: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        """Moves the column weights of every layer norm that feeds a column-parallel GEMM into that GEMM
+        (`W[n, k] *= 1 + norm[k]`) and zeroes the norm, so that the norm is a pure per-token scale which the
+        GEMM's epilogue can apply (`gemm_bf16_gathered`).  In place; the final norm keeps its weights."""
+        for name in list(weights):
+            if not name.endswith(("/input_norm", "/post_norm")):
+                continue
+            layer = name.rsplit("/", 1)[0]
+            if name.endswith("/input_norm"):
+                targets = [k for k in (f"{layer}/attn/in_proj", f"{layer}/gdn/in_proj") if k in weights]
+            else:
+                targets = [k for k in (f"{layer}/mlp/gate_up",) if k in weights]
+            if not targets:
+                continue      # e.g. a MoE block: its router and experts keep the separate norm
+            scale = (1.0 + weights[name].float())[None, :]
+            for k in targets:
+                if weights[k].dtype != torch.bfloat16 or weights[k].dim() != 2:
+                    raise ValueError(f"fold_norms: {k} must still be a bf16 matrix (fold before quantising)")
+                weights[k] = (weights[k].float() * scale).to(torch.bfloat16)
+            weights[name] = torch.zeros_like(weights[name])
+        self.fold = True
+        return weights
+
     # ------------------------------------------------------------------ collectives
+    def _rs_ag(self, model, a, w, T: int, phase: int = 0) -> None:
+        ops = model.ops
+        splits = int(ops.gemm_pick_splits(T, w.shape[0], w.shape[1], 6))
+        ops.gemm_bf16_rs_ag(a, w, splits, self.world, self.rank, self.peer_bases, self.off["rs_recv"],
+                            self.off["rs_flag"], self.off["x"], self.off["rs_ss"], self.off["x_flag"],
+                            self.one_shot_rows, self.cfg.hidden, self.rs_state, phase, model.status.tensor, model.pdl)
+
+    def gather_norm(self, model, ws, T: int, norm_w, normed_out) -> None:
+        """normed_out = rmsnorm(x) * (1 + norm_w) once every rank's residual tiles of the last `_rs_ag` are here."""
+        model.ops.tp_gather_norm(ws.x[:T], norm_w, normed_out, self.peer_bases[self.rank], self.off["x_flag"],
+                                 self.cfg.rms_eps, True, self.rs_state, model.status.tensor, model.pdl)
+
+    def can_gather(self, w) -> bool:
+        return self.fold and isinstance(w, torch.Tensor) and w.dtype == torch.bfloat16 and w.shape[1] == self.cfg.hidden
+
+    def gemm_gathered(self, model, ws, T: int, w, out, epi: int, conv=None) -> None:
+        """Column-parallel GEMM straight on the gathered residual stream (waits for it, RMS norm as a row scale).
+        `conv` = (conv_w, conv_state, slot per token, conv_out): decode conv + SiLU + history roll in the epilogue."""
+        ops = model.ops
+        splits = int(ops.gemm_pick_splits(T, w.shape[0], w.shape[1], epi))
+        ops.gemm_bf16_gathered(ws.x[:T], w, out, epi, splits, self.peer_bases[self.rank], self.off["rs_ss"],
+                               self.off["x_flag"], self.cfg.hidden, self.cfg.rms_eps, self.rs_state,
+                               model.status.tensor, model.pdl, *(conv or (None, None, None, None)))
+
     def gemm_reduce_residual(self, model, ws, a, w, T: int, norm_w, normed_out) -> None:
         """x += sum_ranks(a_r @ w_r^T); normed_out = rmsnorm(x) * (1 + norm_w)."""
         cfg, ops = self.cfg, model.ops
@@ -192,6 +277,15 @@ class TensorParallel:
         x = ws.x[:T]
         if hasattr(w, "qtype"):
             return self._quant_reduce_residual(model, ws, a, w, T, norm_w, normed_out)
+        if self.mode == "fused" and T <= self.one_shot_rows and isinstance(w, torch.Tensor):
+            # decode sizes: reduce-scatter, owner-side reduction and all-gather inside the GEMM; the norm is left to
+            # the consumer (a gathered GEMM when the norms are folded, else tp_gather_norm)
+            self._rs_ag(model, a, w, T)
+            if self.fold:
+                model._gathered = (norm_w, normed_out, T)
+            else:
+                self.gather_norm(model, ws, T, norm_w, normed_out)
+            return
         if self.mode == "nccl" or T > self.T_cap:
             delta = self.delta[:T] if T <= self.T_cap else torch.empty((T, N), dtype=torch.bfloat16, device=self.device)
             ops.gemm_bf16(a, w, delta, 0, None, None, None, 1, model.status.tensor, model.pdl)

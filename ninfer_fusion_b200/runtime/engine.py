@@ -168,6 +168,10 @@ class Engine:
                  prefill_chunk: int = 2048, governor: bool = True):
         self._factory = program_factory
         self.program = program_factory()
+        # limits that submit() checks, cached so that it never touches the Program while the worker swaps it
+        self._max_context = self.program.max_context
+        self._supports_media = bool(getattr(self.program, "supports_media", False))
+        self._reload = None      # (factory, done event, result box) posted by reload_kv_storage, served by the worker
         self.max_pending = max_pending
         self.governor = BandwidthGovernor(prefill_chunk, enabled=governor)
         self.stats = RuntimeStats()
@@ -196,14 +200,14 @@ class Engine:
             if len(prompt) == 0:
                 raise RequestError("empty prompt")
             if opts.media is not None and getattr(opts.media, "items", None):
-                if not getattr(self.program, "supports_media", False):
+                if not self._supports_media:
                     raise RequestError("this engine has no vision tower: media prompts are not supported")
                 if list(opts.media.ids) != list(prompt):
                     raise RequestError("the prepared media prompt does not match the request's token ids")
-            if len(prompt) + opts.max_tokens > self.program.max_context:
+            if len(prompt) + opts.max_tokens > self._max_context:
                 self.stats.requests_rejected += 1
                 raise RequestError(f"prompt ({len(prompt)}) + max_tokens ({opts.max_tokens}) exceeds the "
-                                   f"context window ({self.program.max_context})")
+                                   f"context window ({self._max_context})")
             h = GenerationHandle(self._next_id)
             self._next_id += 1
             self._pending.append(_Request(h, list(prompt), opts))
@@ -216,9 +220,10 @@ class Engine:
 
     def health(self) -> dict:
         with self._lock:
+            prog = self.program   # None for the moment in which the worker rebuilds it (storage reload)
             out = {"status": "failed" if self._failed else "ok", "pending": len(self._pending),
-                   "active": len(self._active), "free_lanes": self.program.free_lanes()}
-        census = getattr(self.program, "census", None)
+                   "active": len(self._active), "free_lanes": prog.free_lanes() if prog is not None else 0}
+        census = getattr(prog, "census", None)
         if census is not None:
             try:   # counts only (no tokens, no session names); the worker may be changing the catalogue meanwhile
                 out["census"] = census()
@@ -231,26 +236,54 @@ class Engine:
         drained: new requests keep queueing, in-flight ones finish first.  Session checkpoints are dropped with the
         old Program.  (Reference: Engine::reload_kv_storage, src/runtime/engine/engine.cpp:764, used by the
         serve-side KV auto-relayout.)"""
-        end = time.perf_counter() + timeout_s
+        # The swap itself happens on the worker thread, the only thread that opens lanes: it serves the request
+        # at the top of an iteration once no lane is active, so no admission can interleave with it, and it
+        # builds the new Program outside the lock (submit() and health() keep answering meanwhile).
+        done = threading.Event()
+        box: dict = {}
         with self._wake:
+            if self._reload is not None:
+                raise ResourceError("a storage reload is already in progress")
+            self._reload = (program_factory, done, box)
             self._draining = True
-        try:
-            while True:
-                with self._lock:
-                    if not self._active:
-                        old = self.program
-                        self._factory = program_factory
-                        self.program = None
-                        del old
-                        self.program = program_factory()
-                        return
-                if time.perf_counter() > end:
+            self._wake.notify_all()
+        if not done.wait(timeout_s):
+            with self._wake:
+                if self._reload is not None and not box.get("started"):
+                    self._reload = None
+                    self._draining = False
+                    self._wake.notify_all()
                     raise TimeoutError("engine did not drain in time")
-                time.sleep(0.005)
+            done.wait()   # the worker is already building the new Program: let it finish
+        if "error" in box:
+            raise box["error"]
+
+    def _serve_reload(self) -> None:
+        """Worker thread, no lane active: replace the Program by the one the posted factory builds."""
+        with self._lock:
+            if self._reload is None:
+                return
+            factory, done, box = self._reload
+            box["started"] = True
+            old, self.program = self.program, None
+        del old   # its device memory goes back before the new pools are allocated
+        try:
+            new = factory()
+            with self._wake:
+                self.program = new
+                self._factory = factory
+                self._max_context = new.max_context
+                self._supports_media = bool(getattr(new, "supports_media", False))
+        except Exception as e:  # noqa: BLE001 - the old Program is gone: engine-wide failure until recover()
+            box["error"] = e
+            with self._wake:
+                self._failed = f"storage reload failed: {type(e).__name__}: {e}"
         finally:
             with self._wake:
+                self._reload = None
                 self._draining = False
                 self._wake.notify_all()
+            done.set()
 
     def recover(self) -> None:
         """Rebuild the Program after an engine-wide failure; in-flight requests were already failed."""
@@ -258,6 +291,8 @@ class Engine:
             if self._failed is None:
                 return
             self.program = self._factory()
+            self._max_context = self.program.max_context
+            self._supports_media = bool(getattr(self.program, "supports_media", False))
             self._failed = None
             self._wake.notify_all()
 
@@ -357,7 +392,8 @@ class Engine:
     def _worker_loop(self) -> None:
         while True:
             with self._wake:
-                while not self._stop and (self._failed is not None or (not self._pending and not self._active)):
+                while not self._stop and (self._failed is not None or
+                                          (not self._pending and not self._active and self._reload is None)):
                     self._wake.wait(timeout=0.5)
                 if self._stop:
                     break
@@ -374,6 +410,10 @@ class Engine:
                     self._finish(req, "error", self._failed)
 
     def _iteration(self) -> None:
+        if self._reload is not None and not self._active:
+            self._serve_reload()
+            if self._failed is not None:
+                return
         now = time.perf_counter()
         for req in list(self._active):
             if req.handle.cancelled:

@@ -512,11 +512,18 @@ class SpeculativeProgram:
             g.kv.pool.free_pages >= need and g.kv_mtp.pool.free_pages >= need
 
     def open(self, prompt, sampling=None, session=None):
+        from .engine import RequestError
         from .program import Lane, SamplingParams
+        sampling = sampling or SamplingParams()
+        if getattr(sampling, "presence_penalty", 0.0) or getattr(sampling, "frequency_penalty", 0.0):
+            # verification samples without per-lane token counts, so a penalty would silently change the
+            # distribution between the speculative and the ordinary program: refuse instead
+            raise RequestError("presence / frequency penalties are not supported by the speculative program")
         if not self._base._free_rows:
             raise MemoryError("no free lane")
+        slot = self.gen.states.alloc()      # before the row is taken: a failure here must not leak the row
         row = self._base._free_rows.pop()
-        lane = Lane(self._base._next_id, row, self.gen.states.alloc(), list(prompt), 0, sampling or SamplingParams())
+        lane = Lane(self._base._next_id, row, slot, list(prompt), 0, sampling)
         self._base._next_id += 1
         self.lanes[lane.lane_id] = lane
         return lane

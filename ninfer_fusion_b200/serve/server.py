@@ -9,10 +9,12 @@ Reference: src/serve/http_server.cpp:408-500, docs/serving.md:66-73, :658-705, :
 """
 from __future__ import annotations
 
+import hmac
 import json
 import socket
 import threading
 import time
+from collections import OrderedDict
 from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 from typing import Dict, Iterator, Optional
 
@@ -60,10 +62,13 @@ class _Keepalive:
 
 class ServeState:
     def __init__(self, service: GenerationService, api_key: Optional[str] = None, log_path: Optional[str] = None,
-                 max_body_bytes: int = 32 << 20):
+                 max_body_bytes: int = 32 << 20, max_stored_responses: int = 512):
         self.service, self.api_key, self.max_body = service, api_key, max_body_bytes
         self.log = RequestLog(log_path)
-        self.responses: Dict[str, dict] = {}   # local response store
+        # local response store: bounded, the least recently used entry goes first (a stored response keeps its
+        # whole message history, so an unbounded store would grow with the server's life)
+        self.responses: "OrderedDict[str, dict]" = OrderedDict()
+        self.max_stored_responses = max(1, int(max_stored_responses))
         self.lock = threading.Lock()
         self.log.event("server_start", model=service.model_id, max_concurrent=service.max_concurrent)
 
@@ -111,13 +116,18 @@ def make_handler(state: ServeState):
         def _authorized(self) -> bool:
             if not state.api_key:
                 return True
+            want = state.api_key.encode()
             auth = self.headers.get("Authorization", "")
-            if auth.startswith("Bearer ") and auth[7:].strip() == state.api_key:
+            # constant-time comparisons: the time to a refusal must not depend on how much of the key matched
+            if auth.startswith("Bearer ") and hmac.compare_digest(auth[7:].strip().encode(), want):
                 return True
-            return self.headers.get("x-api-key", "") == state.api_key
+            return hmac.compare_digest(self.headers.get("x-api-key", "").encode(), want)
 
         def _body(self) -> dict:
-            n = int(self.headers.get("Content-Length", "0") or 0)
+            try:
+                n = int(self.headers.get("Content-Length", "0") or 0)
+            except ValueError:
+                raise P.BadRequest("Content-Length is not a number") from None
             if n <= 0:
                 raise P.BadRequest("request body is empty")
             if n > state.max_body:
@@ -244,6 +254,8 @@ def make_handler(state: ServeState):
                 rid, _, tail = rest.partition("/")
                 with state.lock:
                     obj = state.responses.get(rid)
+                    if obj is not None:
+                        state.responses.move_to_end(rid)   # recently read = recently used
                 if obj is None:
                     return self._error(404, f"response '{rid}' not found", "not_found_error")
                 if tail == "input_items":
@@ -289,6 +301,9 @@ def make_handler(state: ServeState):
                             rec["_messages"] = o["messages"] + [{"role": "assistant", "content": res.content}]
                             with state.lock:
                                 state.responses[obj["id"]] = rec
+                                state.responses.move_to_end(obj["id"])
+                                while len(state.responses) > state.max_stored_responses:
+                                    state.responses.popitem(last=False)
 
                     def build(res: GenResult):
                         obj = P.openai_responses_object(res, svc.model_id)
@@ -333,9 +348,9 @@ def make_handler(state: ServeState):
 
 
 def serve(service: GenerationService, host: str = "127.0.0.1", port: int = 8080, api_key: Optional[str] = None,
-          log_path: Optional[str] = None) -> ThreadingHTTPServer:
+          log_path: Optional[str] = None, max_stored_responses: int = 512) -> ThreadingHTTPServer:
     """Builds the server (not yet serving): call `.serve_forever()` or run it in a thread; `.shutdown()` stops it."""
-    state = ServeState(service, api_key, log_path)
+    state = ServeState(service, api_key, log_path, max_stored_responses=max_stored_responses)
     httpd = ThreadingHTTPServer((host, port), make_handler(state))
     httpd.daemon_threads = True
     httpd.state = state  # type: ignore[attr-defined]

@@ -18,7 +18,7 @@ KV_BITS = {"bf16": 16.0, "fp8": 8.0 + 16.0 / 256, "int8": 8.0 + 16.0 / 64, "nvfp
 
 
 def measured_peaks(path: Optional[str] = None) -> Dict[str, float]:
-    """Copy bandwidth (GB/s) and bf16 GEMM throughput (TFLOP/s) measured on this pool, else the stated fallback."""
+    """Copy bandwidth (GB/s) and bf16 GEMM throughput (TFLOP/s) as measured on the target GPU (MEASURED_PEAKS.json beside the package), else a stated fallback."""
     path = path or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
     try:
         with open(path) as f:

@@ -160,6 +160,61 @@ def test_reload_kv_storage_swaps_the_program_between_requests():
         eng.shutdown()
 
 
+def test_reload_kv_storage_while_requests_keep_arriving():
+    """Submitters race a storage reload: every request finishes on exactly one Program, none is lost, nothing
+    raises on the worker (the swap happens on the worker thread, between lanes)."""
+    lanes_seen = []
+
+    class Spy(ReferenceProgram):
+        def open(self, *a, **k):
+            lane = super().open(*a, **k)
+            lanes_seen.append(id(self))
+            return lane
+
+    built = []
+
+    def factory(fmt):
+        def make():
+            p = Spy(CFG, W, max_lanes=2, max_context=256, kv_format=fmt)
+            built.append(id(p))
+            return p
+        return make
+
+    eng = Engine(factory("bf16"), prefill_chunk=8)
+    handles, stop = [], threading.Event()
+
+    def submitter():
+        i = 0
+        while not stop.is_set() and i < 40:
+            handles.append(eng.submit([3 + (i % 7), 9, 4, 11, 2], RequestOptions(max_tokens=3)))
+            i += 1
+            time.sleep(0.002)
+
+    th = threading.Thread(target=submitter)
+    th.start()
+    try:
+        for fmt in ("int8", "bf16", "int8"):
+            time.sleep(0.02)
+            eng.reload_kv_storage(factory(fmt), timeout_s=120)
+            assert eng.health()["status"] == "ok"
+        stop.set()
+        th.join()
+        for h in handles:
+            assert len(h.wait(timeout=120)) == 3 and h.finish_reason == "length"
+        assert len(built) == 4 and set(lanes_seen) <= set(built)
+        assert eng.health()["status"] == "ok" and eng.stats.as_dict()["requests_failed"] == 0
+        with pytest.raises(ResourceError):
+            # a second reload while one is pending is refused, not queued
+            eng._reload = (None, threading.Event(), {})
+            try:
+                eng.reload_kv_storage(factory("bf16"), timeout_s=1)
+            finally:
+                eng._reload = None
+    finally:
+        stop.set()
+        eng.shutdown()
+
+
 def test_cold_tiers_park_and_revive_session_frontiers(tmp_path):
     """Frontiers evicted from the device tier move to the host tier, overflow to disk, and come back on a hit."""
     from ninfer_fusion_b200.models.config import TINY_DENSE

@@ -176,3 +176,36 @@ def test_gemm_persistent_prefill_kernel(ops, status, T):
     ops.gemm_bf16(x, w, out2, EPI_SWIGLU, None, None, None, 1, status.tensor, True)
     assert torch.equal(out, out2)
     status.check("persistent gemm")
+
+
+@pytest.mark.parametrize("T,N,K,C", [(32, 1024, 512, 512), (5, 640, 256, 384), (64, 2048, 1024, 1280)])
+def test_gemm_conv_epilogue_matches_separate_conv(ops, status, T, N, K, C):
+    """Decode conv + SiLU + history roll inside the store epilogue = GEMM followed by the stand-alone conv kernel."""
+    torch.manual_seed(T + N)
+    x = torch.randn(T, K, device="cuda").bfloat16()
+    w = torch.randn(N, K, device="cuda").mul_(0.05).bfloat16()
+    conv_w = torch.randn(C, 4, device="cuda").mul_(0.3).bfloat16()
+    n_slots = T + 3
+    slots = torch.randperm(n_slots, device="cuda")[:T].int()
+    state0 = torch.randn(n_slots, 3, C, device="cuda").bfloat16()
+    splits = int(ops.gemm_pick_splits(T, N, K, 0))
+    # separate kernels
+    proj = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_bf16(x, w, proj, 0, None, None, None, splits, status.tensor, False)
+    st_a, out_a = state0.clone(), torch.empty(T, C, device="cuda", dtype=torch.bfloat16)
+    cu = torch.arange(T + 1, device="cuda", dtype=torch.int32)
+    seq = torch.arange(T, device="cuda", dtype=torch.int32)
+    ops.causal_conv1d_silu(proj, 0, C, conv_w, cu, seq, slots, st_a, out_a, True, True, False)
+    # fused
+    proj_b = torch.zeros(T, N, device="cuda", dtype=torch.bfloat16)
+    st_b, out_b = state0.clone(), torch.empty(T, C, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_bf16(x, w, proj_b, 0, None, None, None, splits, status.tensor, False, 0, conv_w, st_b, slots, out_b)
+    torch.cuda.synchronize()
+    assert torch.equal(st_a, st_b)                                  # the history is a copy of bf16 values
+    assert torch.equal(proj[:, C:], proj_b[:, C:])                  # columns past the conv channels: plain output
+    torch.testing.assert_close(out_b.float(), out_a.float(), rtol=1e-2, atol=1e-2)
+    # and against the definition
+    hist = state0[slots.long()].float()                             # [T, 3, C]
+    taps = torch.cat([hist, proj[:, None, :C].float()], dim=1)      # [T, 4, C]
+    ref = torch.nn.functional.silu((taps * conv_w.float().T[None]).sum(1))
+    torch.testing.assert_close(out_b.float(), ref, rtol=2e-2, atol=2e-2)

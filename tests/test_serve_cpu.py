@@ -61,6 +61,31 @@ def sse_events(data: bytes):
     return out
 
 
+def test_response_store_is_bounded_and_bad_content_length_is_a_400(server):
+    port, svc, _ = server
+    import socket as _socket
+
+    from ninfer_fusion_b200.serve import server as S
+    # the store drops its least recently used entry once it is full
+    st = S.ServeState(svc, None, None, max_stored_responses=2)
+    handler = S.make_handler(st)
+    assert handler is not None
+    for i in range(3):
+        with st.lock:
+            st.responses[f"r{i}"] = {"id": f"r{i}"}
+            st.responses.move_to_end(f"r{i}")
+            while len(st.responses) > st.max_stored_responses:
+                st.responses.popitem(last=False)
+    assert list(st.responses) == ["r1", "r2"]
+    # a Content-Length that is not a number is the client's mistake, not a server error
+    c = _socket.create_connection(("127.0.0.1", port), timeout=30)
+    c.sendall(b"POST /v1/chat/completions HTTP/1.1\r\nHost: x\r\nAuthorization: Bearer sekret\r\n"
+              b"Content-Type: application/json\r\nContent-Length: banana\r\nConnection: close\r\n\r\n{}")
+    head = c.recv(4096).decode("latin1")
+    c.close()
+    assert head.startswith("HTTP/1.1 400"), head[:200]
+
+
 def test_health_models_auth(server):
     port, svc, _ = server
     st, _, data = call(port, "GET", "/health", key=None)

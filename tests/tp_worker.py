@@ -15,7 +15,7 @@ import torch.distributed as dist
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
-from ninfer_fusion_b200.models.config import TINY_DENSE  # noqa: E402
+from ninfer_fusion_b200.models.config import TINY_DENSE, ModelConfig  # noqa: E402
 from ninfer_fusion_b200.models.weights import random_weights  # noqa: E402
 from ninfer_fusion_b200.parallel.tp import TensorParallel  # noqa: E402
 from ninfer_fusion_b200.runtime.generator import Generator  # noqa: E402
@@ -31,19 +31,60 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
-    cfg = TINY_DENSE
-    full = random_weights(cfg, dev, seed=7, std=0.05)
+    # two ranks take the tiny geometry; four and eight need widths that still divide into 128-column tiles
+    cfg = TINY_DENSE if world <= 2 else ModelConfig(
+        name="tp-wide", n_layers=4, hidden=1024, vocab=2048, n_q_heads=8, n_kv_heads=2, head_dim=256, rot_dim=64,
+        rope_theta=1e7, gdn_qk_heads=8, gdn_v_heads=8, ffn_inter=1024, max_context=4096)
+    full = random_weights(cfg, dev, seed=7, std=0.05 if world <= 2 else 0.03)
     torch.manual_seed(5)
     prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (21, 70, 5)]
     n_new = 10
     results = {}
-    for mode, use_graph in (("fused", False), ("fused", True), ("nccl", False)):
-        log(rank, f"start {mode} graph={use_graph}")
-        comm = TensorParallel(cfg, rank, world, dev, max_tokens=64, mode=mode)
-        gen = Generator(cfg, comm.shard(full), dev, max_batch=4, max_context=256, kv_format="bf16", page_size=16,
-                        prefill_chunk=64, use_graph=use_graph, shard=comm.geometry, comm=comm)
+    logit_err = {}
+
+    def gathered_logits(gen, n_rows):
+        """Last-token logits of the whole vocabulary: every rank holds a slice of the columns."""
+        mine = gen.ws.logits[:n_rows].float().contiguous()
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)
+        return torch.cat(parts, dim=1)
+
+    # single-GPU oracle of the same weights: logits after the prefill and after three decode rounds
+    single_gen = Generator(cfg, full, dev, max_batch=4, max_context=512, kv_format="bf16", page_size=16,
+                           prefill_chunk=256, use_graph=False)
+    long_prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (150, 70)]
+    ref_logits = {}
+    for name, ps in (("short", prompts), ("long", long_prompts)):
+        single_gen.prefill(ps)
+        ref_logits[(name, "prefill")] = single_gen.ws.logits[: len(ps)].float().clone()
+        for _ in range(3):
+            single_gen.decode_step()
+        ref_logits[(name, "decode")] = single_gen.ws.logits[: len(ps)].float().clone()
+    single = single_gen.generate(prompts, n_new)
+
+    for mode, use_graph, fold in (("fused", False, False), ("fused", True, True), ("oneshot", True, False),
+                                  ("nccl", False, False)):
+        log(rank, f"start {mode} graph={use_graph} fold={fold}")
+        comm = TensorParallel(cfg, rank, world, dev, max_tokens=256, mode=mode)
+        shard = comm.shard(full)
+        if fold:
+            shard = comm.fold_norms(dict(shard))
+        gen = Generator(cfg, shard, dev, max_batch=4, max_context=512, kv_format="bf16", page_size=16,
+                        prefill_chunk=256, use_graph=use_graph, shard=comm.geometry, comm=comm)
+        # logits of the fused paths against the single-GPU run: decode-sized steps take the in-GEMM
+        # reduce-scatter / all-gather, the 220-token chunk of the long prompts the push + reduce kernel
+        for name, ps in (("short", prompts), ("long", long_prompts)):
+            gen.prefill(ps)
+            got = {"prefill": gathered_logits(gen, len(ps))}
+            for _ in range(3):
+                gen.decode_step()
+            got["decode"] = gathered_logits(gen, len(ps))
+            for when, lg in got.items():
+                ref = ref_logits[(name, when)]
+                logit_err[(mode, use_graph, fold, name, when)] = ((lg - ref).abs().max() / (ref.max() - ref.min())).item()
         results[(mode, use_graph)] = gen.generate(prompts, n_new)
         torch.cuda.synchronize()
+        gen.model.status.check()
         dist.barrier()
         log(rank, f"done {mode} graph={use_graph}: {results[(mode, use_graph)][0][:5]}")
     # quantised weights: shard first, quantise each shard; fused (peer-memory) and NCCL reductions must tell the same story
@@ -85,24 +126,26 @@ def main():
         if not torch.equal(mine, ref0):
             ok = False
             msg += f" {fmt}: rank {rank} diverged from rank 0;"
+    worst = max(logit_err.values())
+    msg += f" worst logit error / range {worst:.4f};"
+    for key, err in logit_err.items():
+        if err > 2e-2:
+            ok = False
+            msg += f" logits{key}={err:.4f};"
     if rank == 0:
-        single = Generator(cfg, full, dev, max_batch=4, max_context=256, kv_format="bf16", page_size=16,
-                           prefill_chunk=64, use_graph=False).generate(prompts, n_new)
         for key, out in results.items():
             # greedy decoding diverges for good after one near-tie flip (partial sums are reduced in a different
-            # order than on one GPU), so compare the agreeing PREFIX of every sequence and the first token
+            # order than on one GPU), so the tokens are only a coarse check: the first token of every sequence and
+            # half of all tokens must agree; the logits above carry the numerical comparison
             prefix = []
-            for o, s in zip(out, single):
+            for o, s_ in zip(out, single):
                 n = 0
-                while n < len(s) and o[n] == s[n]:
+                while n < len(s_) and o[n] == s_[n]:
                     n += 1
                 prefix.append(n)
-            if min(prefix) < 1 or sum(prefix) < 0.5 * sum(len(s) for s in single):
+            if min(prefix) < 1 or sum(prefix) < 0.5 * sum(len(s_) for s_ in single):
                 ok = False
             msg += f" {key}:prefix{prefix}"
-        if results[("fused", False)] != results[("fused", True)]:
-            ok = False
-            msg += " fused graph!=eager"
     mine = torch.tensor(results[("fused", True)], device=dev)
     ref = mine.clone()
     dist.broadcast(ref, 0)
