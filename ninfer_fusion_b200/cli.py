@@ -13,6 +13,7 @@ from __future__ import annotations
 import argparse
 import json
 import math
+import os
 import sys
 import time
 from typing import Dict, Optional, Tuple
@@ -76,6 +77,11 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--kv-rowscale", default=None,
                     help="K row-scale table (default: NINFER_KV_ROWSCALE, else <artifact>.kvrowscale.bin when present)")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--tp", type=int, default=1,
+                    help="tensor-parallel ranks; launch the command with `python -m torch.distributed.run --nproc-per-node N "
+                         "--master-addr 127.0.0.1 -m ninfer_fusion_b200.cli ...`: rank 0 serves, the others follow its steps")
+    ap.add_argument("--rank-timeout", type=float, default=60.0,
+                    help="seconds after which a silent rank fails the engine (control channel time-out)")
 
 
 def load_model(args) -> Tuple[ModelConfig, Dict[str, object], Tokenizer, str]:
@@ -116,7 +122,7 @@ def load_model(args) -> Tuple[ModelConfig, Dict[str, object], Tokenizer, str]:
                                  with_mtp=getattr(args, "spec", "none") == "mtp")
         name = f"{cfg.name}:random-init"
     renderer_for(template, allow_unknown=args.allow_unknown_template)  # refuses an unknown template early
-    if args.weights not in ("bf16", "stored"):
+    if args.weights not in ("bf16", "stored") and int(getattr(args, "tp", 1)) <= 1:   # (--tp: each rank quantises its shard)
         if args.device == "cpu":
             raise SystemExit("--weights fp8/nvfp4 needs a GPU (the CPU program runs the fp32 oracle)")
         weights = quantize_weights(weights, args.weights)
@@ -157,8 +163,55 @@ def attach_vision(args, cfg: ModelConfig, weights, program):
     return program
 
 
-def build_engine(args, cfg: ModelConfig, weights) -> Engine:
+def setup_ranks(args):
+    """Joins the rank group of a multi-GPU run: picks this rank's GPU, starts NCCL (bootstrap of the symmetric
+    buffers) and the gloo control channel of the replicated engine.  Returns None for a single rank, else
+    (rank, world, channel).  Must run before the model is loaded: it decides `args.device`."""
+    from .parallel.replicated import RankChannel, world_from_env
+    rank, world = world_from_env()
+    want = max(int(getattr(args, "tp", 1)), 1)
+    if world == 1 and want == 1:
+        return None
+    if world != want:
+        raise SystemExit(f"--tp {want} needs {want} ranks (python -m torch.distributed.run --nproc-per-node {want} "
+                         f"--master-addr 127.0.0.1 -m ninfer_fusion_b200.cli ...); found {world}")
+    import torch.distributed as dist
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    args.device = f"cuda:{local}"
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=torch.device(args.device))
+    return rank, world, RankChannel.create(rank, world, timeout_s=float(getattr(args, "rank_timeout", 60.0)))
+
+
+def build_engine(args, cfg: ModelConfig, weights, ranks=None) -> Optional[Engine]:
+    """The engine of this process.  With `ranks` (see setup_ranks) the model is tensor-parallel: rank 0 gets an
+    Engine whose Program mirrors every step to the followers; a follower runs its loop here until the leader
+    stops it and gets None."""
     kv = args.kv_dtype
+    if ranks is not None:
+        from .parallel.replicated import LeaderProgram, follower_loop
+        from .parallel.tp import TensorParallel
+        rank, world, channel = ranks
+        if getattr(args, "spec", "none") != "none" or getattr(args, "vision", False) or args.weight_budget_gib > 0:
+            raise SystemExit("--tp does not combine with --spec, --vision or --weight-budget-gib yet")
+        if args.kv_layer_spec:
+            from .kv.policy import parse_layer_storage
+            kv = parse_layer_storage(args.kv_layer_spec, len(cfg.attn_layers))
+        comm = TensorParallel(cfg, rank, world, args.device, max_tokens=max(args.prefill_chunk, args.max_lanes))
+        text = {k: v for k, v in weights.items() if not k.startswith("vision/")}
+        if any(hasattr(v, "qtype") for v in text.values()):
+            raise SystemExit("--tp: give bf16 weights (every rank quantises its own shard: --weights applies after the split)")
+        shard_w = comm.shard(text)
+        if args.weights == "bf16":
+            shard_w = comm.fold_norms(dict(shard_w))
+        elif args.weights != "stored":
+            shard_w = quantize_weights(shard_w, args.weights)
+        inner_factory = program_factory(args, cfg, shard_w, kv, shard=comm.geometry, comm=comm)
+        if rank != 0:
+            follower_loop(inner_factory(), channel)
+            return None
+        return Engine(lambda: LeaderProgram(inner_factory(), channel), prefill_chunk=args.prefill_chunk)
     if args.kv_layer_spec:
         from .kv.policy import parse_layer_storage
         kv = parse_layer_storage(args.kv_layer_spec, len(cfg.attn_layers))
@@ -178,8 +231,9 @@ def build_engine(args, cfg: ModelConfig, weights) -> Engine:
     return Engine(program_factory(args, cfg, weights, kv), prefill_chunk=args.prefill_chunk)
 
 
-def program_factory(args, cfg: ModelConfig, weights, kv):
-    """Factory of the ordinary (non-speculative) Program for a KV storage plan (`kv`: one format or one per layer)."""
+def program_factory(args, cfg: ModelConfig, weights, kv, shard=None, comm=None):
+    """Factory of the ordinary (non-speculative) Program for a KV storage plan (`kv`: one format or one per layer);
+    `shard` / `comm`: this rank's geometry and communicator under tensor parallelism."""
     if str(args.device).startswith("cuda"):
         from .runtime.gpu_program import GpuProgram
 
@@ -187,8 +241,8 @@ def program_factory(args, cfg: ModelConfig, weights, kv):
             text = {k: v for k, v in weights.items() if not k.startswith("vision/")}
             prog = GpuProgram(cfg, text, args.device, max_lanes=args.max_lanes, max_context=args.max_context,
                               kv_format=kv, page_size=args.page_size, prefill_chunk=args.prefill_chunk,
-                              use_graph=not args.no_graphs, kv_pages=resolve_kv_pages(args, cfg, kv),
-                              weight_budget_bytes=int(args.weight_budget_gib * (1 << 30)) if args.weight_budget_gib > 0 else None)
+                              use_graph=not args.no_graphs, kv_pages=resolve_kv_pages(args, cfg, kv), shard=shard,
+                              comm=comm, weight_budget_bytes=int(args.weight_budget_gib * (1 << 30)) if args.weight_budget_gib > 0 else None)
             load_row_scale(args, cfg, prog.model)
             prog.anchor_interval = max(0, int(getattr(args, "anchor_interval", 0)))
             prog.kv.cold_slots = bool(getattr(args, "cold_slots", False))
@@ -269,8 +323,11 @@ def cmd_kv_rowscale(args) -> int:
 # ---------------------------------------------------------------------------------------------------------
 def cmd_generate(args) -> int:
     from .serve.service import GenerationService, GenRequest
+    ranks = setup_ranks(args)
     cfg, weights, tok, name = load_model(args)
-    engine = build_engine(args, cfg, weights)
+    engine = build_engine(args, cfg, weights, ranks)
+    if engine is None:
+        return 0     # a follower rank: it executed the leader's steps until told to stop
     svc = GenerationService(engine, tok, name)
     req = GenRequest(max_tokens=args.max_tokens, temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
                      seed=args.seed, enable_thinking=not args.no_think, stop=args.stop or ())
@@ -309,16 +366,21 @@ def cmd_generate(args) -> int:
              "finish_reason": result.finish_reason, "ttft_ms": result.ttft_ms, "total_s": round(dt, 3),
              "decode_tok_s": round((result.completion_tokens - 1) / max(1e-9, dt - (result.ttft_ms or 0) / 1e3), 2),
              "weights_bytes": total_bytes(weights)}
+    if args.print_ids:
+        stats["completion_ids"] = list(result.token_ids)
     print(json.dumps(stats), file=sys.stderr)
-    engine.shutdown()
+    _shutdown(engine)
     return 0 if result.finish_reason != "error" else 1
 
 
 def cmd_serve(args) -> int:
     from .serve.server import serve
     from .serve.service import GenerationService
+    ranks = setup_ranks(args)
     cfg, weights, tok, name = load_model(args)
-    engine = build_engine(args, cfg, weights)
+    engine = build_engine(args, cfg, weights, ranks)
+    if engine is None:
+        return 0     # a follower rank
     svc = GenerationService(engine, tok, args.served_model_name or name, max_concurrent=args.max_concurrent,
                             queue_timeout_s=args.queue_timeout)
     relayout = None
@@ -345,8 +407,16 @@ def cmd_serve(args) -> int:
         pass
     finally:
         httpd.server_close()
-        engine.shutdown()
+        _shutdown(engine)
     return 0
+
+
+def _shutdown(engine: Engine) -> None:
+    """Stops the engine; a leader first lets the worker drain, then releases the follower ranks."""
+    program = engine.program
+    engine.shutdown()
+    if hasattr(program, "replicated_stats"):
+        program.shutdown()
 
 
 def cmd_inspect(args) -> int:
@@ -523,6 +593,7 @@ def main(argv=None) -> int:
     g.add_argument("--stop", action="append")
     g.add_argument("--no-think", action="store_true")
     g.add_argument("--show-thinking", action="store_true")
+    g.add_argument("--print-ids", action="store_true", help="add the completion's token ids to the stats line")
     g.set_defaults(fn=cmd_generate)
     s = sub.add_parser("serve", help="OpenAI / Anthropic compatible HTTP server")
     s.add_argument("--kv-auto-relayout", type=float, default=0.0,

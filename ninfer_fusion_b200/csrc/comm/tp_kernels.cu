@@ -143,7 +143,19 @@ __global__ void __launch_bounds__(1024) tp_argmax_kernel(const TpArgmaxParams p)
   const bool do_push = (p.phases & 1) != 0, do_pick = (p.phases & 2) != 0;
   float best = -CUDART_INF_F;
   int idx = 0x7fffffff;
-  for (int i = threadIdx.x; do_push && i < p.V_local; i += blockDim.x) {
+  // 16-byte loads when the row allows it (8 logits per load, ascending ids: strict > keeps the lowest id)
+  const bool vec = (p.ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.logits) & 15) == 0);
+  const int nvec = (do_push && vec) ? p.V_local / 8 : 0;
+  for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+    const uint4 r = *reinterpret_cast<const uint4*>(row + c * 8);
+    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&r);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float f = __bfloat162float(e[j]);
+      if (f > best) { best = f; idx = c * 8 + j; }
+    }
+  }
+  for (int i = nvec * 8 + threadIdx.x; do_push && i < p.V_local; i += blockDim.x) {
     const float f = __bfloat162float(row[i]);
     if (f > best || (f == best && i < idx)) { best = f; idx = i; }
   }

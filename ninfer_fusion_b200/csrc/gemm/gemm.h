@@ -110,9 +110,16 @@ const char* gemm_bf16(const GemmArgs& args);
 
 // Token-tile width the kernel will use for T tokens (16, 32, 64, 128 or 256).
 // Performance debugging: per-CTA phase timeline (ns, globaltimer): 0 start, 1 set-up done, 2 main loop done,
-// 3 peer tile sent, 4 cluster exchange done, 5 epilogue done, 6 exit.
+// 3 peer tile sent, 4 cluster exchange done, 5 epilogue done, 6 exit; kEpiRsAg also 7 tile pushed and signalled,
+// 8 owner: tile staged and peers' tiles here, 9 rows reduced and stored, 10 barrier, 11 residual counters signalled.
+// Twelve stamps per CTA.
 void gemm_trace_enable(bool on);
 int gemm_trace_read(unsigned long long* host, int n_ctas);
+// Timeline over several launches: between begin and end, GEMM launch i records the stamps of its first 256 CTAs in
+// slot i % 64 (a launch captured into a CUDA graph keeps its slot at every replay).  `end` copies
+// [64][256][12] stamps (ns, globaltimer; 0 = not written) to `host` and returns the number of launches seen.
+void gemm_timeline_begin();
+int gemm_timeline_end(unsigned long long* host, int* n_slots, int* n_ctas);
 int gemm_tile_tokens(int T);
 int gemm_max_cluster(int tile_tokens);
 // Split-K factor that fills `sm_count` SMs for a decode-shaped problem.

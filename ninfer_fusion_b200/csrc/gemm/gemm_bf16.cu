@@ -48,10 +48,17 @@ struct GemmCfg {
 };
 
 // Optional phase timeline (globaltimer, ns) of every CTA, for performance debugging: 8 stamps per CTA.
-constexpr int kTraceStamps = 8;
+constexpr int kTraceStamps = 12;
 constexpr int kTraceCtas = 4096;
 __device__ unsigned long long g_gemm_trace[kTraceCtas * kTraceStamps];
 bool g_trace_enabled = false;
+// Timeline over SEVERAL launches (a whole layer, a captured graph): launch i of a traced run writes the stamps of
+// its first kTimelineCtas CTAs into slot i % kTimelineSlots, so that the overlap of consecutive kernels under
+// programmatic dependent launch can be read off one clock (globaltimer).
+constexpr int kTimelineSlots = 64;
+constexpr int kTimelineCtas = 256;
+__device__ unsigned long long g_gemm_timeline[kTimelineSlots * kTimelineCtas * kTraceStamps];
+int g_timeline_next = -1;   // < 0: off; else the slot of the next launch
 
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
   unsigned long long t;
@@ -133,7 +140,12 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int cta_linear = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
   auto stamp = [&](int i) {
-    if (p.trace && threadIdx.x == 0 && cta_linear < kTraceCtas) g_gemm_trace[cta_linear * kTraceStamps + i] = globaltimer_ns();
+    if (p.trace && threadIdx.x == 0) {
+      const unsigned long long now = globaltimer_ns();
+      if (cta_linear < kTraceCtas) g_gemm_trace[cta_linear * kTraceStamps + i] = now;
+      if (p.trace > 1 && cta_linear < kTimelineCtas)
+        g_gemm_timeline[((p.trace - 2) * kTimelineCtas + cta_linear) * kTraceStamps + i] = now;
+    }
   };
   stamp(0);
 
@@ -264,6 +276,22 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
 
   // ---------------- epilogue: all four warps, warp w owns TMEM lanes 32w..32w+31 ----------------
   pdl_wait_prior();
+  // kEpiRsAg, CTA that owns its tile: what the reduction reads from global memory (its bookkeeping word and the
+  // residual of the first 32 token rows) is fetched now, so that the latency hides under the main loop
+  uint4 resid_pre[4] = {};
+  uint32_t expected_pre = 0;
+  if constexpr (EPI == kEpiRsAg) {
+    if (n0 / p.slice_cols == p.rank && p.rs_phase != 1 && (p.cluster <= 1 || blockIdx.z == 0)) {
+      expected_pre = p.rs_state->tile_expected[((n0 % p.slice_cols) / kTileN) * kRsMaxTokenTiles + blockIdx.y];
+      const int r = threadIdx.x >> 2, t = t0 + r;
+      if (r < TN && t < p.T) {
+        const uint4* src = reinterpret_cast<const uint4*>(p.peer_x[p.rank] + static_cast<long long>(t) * p.ld_resid + n0 +
+                                                          (threadIdx.x & 3) * 32);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) resid_pre[q] = src[q];
+      }
+    }
+  }
   bool have_acc = true;
   if (num_it > 0) {
     have_acc = mbar_wait(smem_u32(&bar_accum), 0, &abort_flag, p.status, kStatusAccumWaitTimeout);
@@ -411,7 +439,7 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
       uint32_t target = 0;
       if (reduces) {
         // owner of the tile: the peers' tiles have to be here before the rows can be reduced
-        target = *expected + static_cast<uint32_t>(p.rs_phase == 0 ? p.world - 1 : p.world);
+        target = expected_pre + static_cast<uint32_t>(p.rs_phase == 0 ? p.world - 1 : p.world);
         if (threadIdx.x == 0) rs_ok = wait_counter(p.peer_flag[p.rank] + flag_idx, target, p.status) ? 1 : 0;
       }
       __syncthreads();
@@ -432,12 +460,13 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
           for (int q = 0; q < 8; ++q) dst4[q] = src4[q];
         }
         __syncthreads();
-        if (threadIdx.x == 0) {
-          __threadfence_system();
-          red_release_sys_add(p.peer_flag[owner] + flag_idx, 1u);
-        }
+        // the block barrier orders every thread's peer stores before the signalling thread, whose release (system
+        // scope) is cumulative over them: no separate fence
+        if (threadIdx.x == 0) red_release_sys_add(p.peer_flag[owner] + flag_idx, 1u);
+        stamp(7);
       }
       if (reduces) {
+        stamp(8);
         const bool ok = rs_ok != 0;
         __nv_bfloat16* my_x = p.peer_x[p.rank];
         const float* recv = p.peer_recv[p.rank] + n_local;
@@ -470,7 +499,7 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
             uint4 o[4];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              const uint4 rv = *reinterpret_cast<const uint4*>(my_x + at + q * 8);
+              const uint4 rv = r0 == 0 ? resid_pre[q] : *reinterpret_cast<const uint4*>(my_x + at + q * 8);
               const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
               const float4 lo = a[2 * q], hi = a[2 * q + 1];
               uint32_t* op = reinterpret_cast<uint32_t*>(&o[q]);
@@ -500,11 +529,11 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
               p.peer_ss[rk][static_cast<long long>(t) * kRsSsStride + tile_global] = ss;
           }
         }
+        stamp(9);
         __syncthreads();
-        if (ok && threadIdx.x < p.world) {
-          __threadfence_system();
-          red_release_sys_add(p.peer_xflag[threadIdx.x], 1u);
-        }
+        stamp(10);
+        if (ok && threadIdx.x < p.world) red_release_sys_add(p.peer_xflag[threadIdx.x], 1u);   // (release: see above)
+        stamp(11);
         if (threadIdx.x == 0) *expected = target;
       }
       // what the next consumer of the residual stream has to wait for: one arrival per (column tile, token tile)
@@ -997,10 +1026,22 @@ int device_sm_count() {
   return n;
 }
 
+// One CTA per SM with the deep pipeline when the whole grid fits in one wave.  NFB_GEMM_DEEP=0 keeps the shallow
+// pipeline (about 100 KB per CTA) for every size, so that the CTAs of two consecutive kernels fit on one SM and the
+// next kernel's weight prefetch (programmatic dependent launch) can run under the current kernel.
+bool deep_enabled() {
+  static const bool enabled = [] {
+    const char* e = getenv("NFB_GEMM_DEEP");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return enabled;
+}
+bool use_deep(int tn, long long ctas) { return deep_enabled() && tn <= 64 && ctas <= device_sm_count(); }
+
 template <int EPI>
 cudaError_t launch_tn(int TN, const CUtensorMap& tw, const CUtensorMap& tx, const KernelParams& kp,
                       dim3 grid, cudaStream_t stream, bool pdl) {
-  const bool deep = TN <= 64 && static_cast<long long>(grid.x) * grid.y * grid.z <= device_sm_count();
+  const bool deep = use_deep(TN, static_cast<long long>(grid.x) * grid.y * grid.z);
   switch (TN) {
     case 16: return deep ? launch_one<16, EPI, true>(tw, tx, kp, grid, stream, pdl)
                          : launch_one<16, EPI, false>(tw, tx, kp, grid, stream, pdl);
@@ -1050,6 +1091,22 @@ bool cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t col
 }  // namespace
 
 void gemm_trace_enable(bool on) { g_trace_enabled = on; }
+void gemm_timeline_begin() {
+  g_trace_enabled = true;
+  g_timeline_next = 0;
+  void* p = nullptr;
+  if (cudaGetSymbolAddress(&p, g_gemm_timeline) == cudaSuccess) cudaMemset(p, 0, sizeof(unsigned long long) * kTimelineSlots * kTimelineCtas * kTraceStamps);
+}
+int gemm_timeline_end(unsigned long long* host, int* n_slots, int* n_ctas) {
+  g_trace_enabled = false;
+  const int used = g_timeline_next < 0 ? 0 : (g_timeline_next < kTimelineSlots ? g_timeline_next : kTimelineSlots);
+  g_timeline_next = -1;
+  *n_slots = kTimelineSlots;
+  *n_ctas = kTimelineCtas;
+  if (host != nullptr)
+    cudaMemcpyFromSymbol(host, g_gemm_timeline, sizeof(unsigned long long) * kTimelineSlots * kTimelineCtas * kTraceStamps);
+  return used;
+}
 int gemm_trace_read(unsigned long long* host, int n_ctas) {
   if (n_ctas > kTraceCtas) n_ctas = kTraceCtas;
   cudaMemcpyFromSymbol(host, g_gemm_trace, sizeof(unsigned long long) * n_ctas * kTraceStamps);
@@ -1076,6 +1133,64 @@ int gemm_max_cluster(int tn) {
   }
 }
 
+// How many clusters of `s` CTAs (along z) of one kernel instance can be resident at once.  A cluster lives inside
+// one GPC, so this is not sm_count / s: with one CTA per SM, 17 clusters of 8 or 34 clusters of 4 do not fit and
+// the grid runs in two waves.  Asked from the runtime once per (kernel, cluster size) and cached.
+template <int TN, int EPI, bool DEEP>
+int occupancy_clusters(int s) {
+  using Cfg = GemmCfg<TN, DEEP>;
+  auto kern = gemm_ws_kernel<TN, EPI, DEEP>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1, 1, s);
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = s;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+template <int EPI>
+int occupancy_clusters_tn(int tn, bool deep, int s) {
+  switch (tn) {
+    case 16: return deep ? occupancy_clusters<16, EPI, true>(s) : occupancy_clusters<16, EPI, false>(s);
+    case 32: return deep ? occupancy_clusters<32, EPI, true>(s) : occupancy_clusters<32, EPI, false>(s);
+    case 64: return deep ? occupancy_clusters<64, EPI, true>(s) : occupancy_clusters<64, EPI, false>(s);
+    default: return 0;
+  }
+}
+
+// 0 = unknown (no device, query failed): the caller then falls back to the SM-count estimate.
+int max_active_clusters(int tn, int epi, bool deep, int s) {
+  static std::mutex mu;
+  static std::unordered_map<int, int> cache;
+  const int key = ((tn * 16 + epi) * 2 + (deep ? 1 : 0)) * 16 + s;
+  std::lock_guard<std::mutex> g(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  int n = 0;
+  switch (epi) {
+    case kEpiStore: n = occupancy_clusters_tn<kEpiStore>(tn, deep, s); break;
+    case kEpiResidual: n = occupancy_clusters_tn<kEpiResidual>(tn, deep, s); break;
+    case kEpiSwiglu: n = occupancy_clusters_tn<kEpiSwiglu>(tn, deep, s); break;
+    case kEpiPushAll: n = occupancy_clusters_tn<kEpiPushAll>(tn, deep, s); break;
+    case kEpiRsAg: n = occupancy_clusters_tn<kEpiRsAg>(tn, deep, s); break;
+    default: n = 0;
+  }
+  cache.emplace(key, n);
+  return n;
+}
+
 int gemm_pick_splits(int T, int N, int K, int epi, int sm_count) {
   const int tn = gemm_tile_tokens(T);
   const int rows = epi == kEpiSwiglu ? N / 2 : N;
@@ -1099,8 +1214,18 @@ int gemm_pick_splits(int T, int N, int K, int epi, int sm_count) {
   if (s > 8) s = 8;
   if (tn == 64 && s > 6) s = 6;
   if (tn == 64 && epi == kEpiRsAg && s > 5) s = 5;   // its row staging tile shares the pipeline stages
-  while (s > 1 && num_kb / s < 8) --s;
-  while (s > 1 && (num_kb + s - 1) / s * (s - 1) >= num_kb) --s;  // no empty trailing split
+  if (!deep_enabled() && s > gemm_max_cluster(tn)) s = gemm_max_cluster(tn);
+  // the largest split whose clusters are all resident at once (one wave), that leaves every split at least eight
+  // k-blocks and no split empty
+  for (; s > 1; --s) {
+    if (num_kb / s < 8) continue;
+    if ((num_kb + s - 1) / s * (s - 1) >= num_kb) continue;
+    const bool deep = use_deep(tn, static_cast<long long>(tiles) * s);
+    if (!deep && s > gemm_max_cluster(tn)) continue;
+    const int fit = max_active_clusters(tn, epi, deep, s);
+    if (fit > 0 && fit < tiles) continue;
+    break;
+  }
   return s < 1 ? 1 : s;
 }
 
@@ -1114,6 +1239,7 @@ const char* gemm_bf16(const GemmArgs& a) {
   const bool global_split = a.epi == kEpiPartial || a.epi == kEpiPushPartial;
   KernelParams kp = {};
   kp.trace = g_trace_enabled ? 1 : 0;
+  if (g_trace_enabled && g_timeline_next >= 0) kp.trace = 2 + (g_timeline_next++ % kTimelineSlots);
   kp.T = static_cast<int>(a.T); kp.N = static_cast<int>(a.N); kp.K = static_cast<int>(a.K);
   kp.num_kb = (kp.K + kBlockK - 1) / kBlockK;
   int splits = a.splits < 1 ? 1 : a.splits;
@@ -1124,7 +1250,7 @@ const char* gemm_bf16(const GemmArgs& a) {
   kp.cluster = 1;
   if (!global_split && splits > 1) {
     const long long ctas = static_cast<long long>((kp.N + kTileN - 1) / kTileN) * ((kp.T + tn - 1) / tn) * splits;
-    const bool deep = tn <= 64 && ctas <= device_sm_count();  // (SwiGLU has more tiles: checked against the shallow limit)
+    const bool deep = use_deep(tn, ctas);  // (SwiGLU has more tiles: checked against the shallow limit)
     const int cap = (deep && a.epi != kEpiSwiglu) ? (tn == 64 ? 6 : 8) : gemm_max_cluster(tn);
     if (splits > cap) return "gemm_bf16: in-cluster split exceeds the tile's limit";
     kp.cluster = splits;

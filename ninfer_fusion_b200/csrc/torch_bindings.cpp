@@ -105,9 +105,22 @@ void gemm_bf16(const Tensor& x, const Tensor& w, OptT out, int64_t epi, OptT res
 
 Tensor gemm_trace(bool enable, int64_t n_ctas) {
   nfb::gemm_trace_enable(enable);
-  Tensor out = at::zeros({n_ctas, 8}, at::TensorOptions().dtype(at::kLong));
+  Tensor out = at::zeros({n_ctas, 12}, at::TensorOptions().dtype(at::kLong));
   if (n_ctas > 0) nfb::gemm_trace_read(reinterpret_cast<unsigned long long*>(out.data_ptr()), static_cast<int>(n_ctas));
   return out;
+}
+
+// mode 1: start a multi-launch timeline; mode 0: stop and return (launches seen, stamps [64, 256, 12] int64 ns)
+std::tuple<int64_t, Tensor> gemm_timeline(int64_t mode) {
+  if (mode == 1) {
+    nfb::gemm_timeline_begin();
+    return {0, at::zeros({0}, at::TensorOptions().dtype(at::kLong))};
+  }
+  Tensor out = at::zeros({64, 256, 12}, at::TensorOptions().dtype(at::kLong));
+  int slots = 0, ctas = 0;
+  const int used = nfb::gemm_timeline_end(reinterpret_cast<unsigned long long*>(out.data_ptr()), &slots, &ctas);
+  TORCH_CHECK(slots == 64 && ctas == 256, "timeline geometry changed");
+  return {used, out};
 }
 
 int64_t gemm_pick_splits(int64_t T, int64_t N, int64_t K, int64_t epi) {
@@ -800,6 +813,7 @@ TORCH_LIBRARY(nfb200, m) {
   m.def("tp_sum_norm(int world, int T_cap, int arrivals, int my_base, int recv_off, int flag_off, Tensor x, Tensor? norm_w, Tensor? normed, float eps, bool unit_offset, Tensor state, Tensor? status, bool pdl) -> ()", &tp_sum_norm);
   m.def("gemm_bf16(Tensor x, Tensor w, Tensor? out, int epi, Tensor? resid, Tensor? bias, Tensor? partial, int splits, Tensor? status, bool pdl, int act=0, Tensor? conv_w=None, Tensor? conv_state=None, Tensor? conv_slot=None, Tensor? conv_out=None) -> ()", &gemm_bf16);
   m.def("gemm_trace(bool enable, int n_ctas) -> Tensor", &gemm_trace);
+  m.def("gemm_timeline(int mode) -> (int, Tensor)", &gemm_timeline);
   m.def("gemm_pick_splits(int T, int N, int K, int epi) -> int", &gemm_pick_splits);
   m.def("add_rmsnorm(Tensor? partial, int splits, Tensor? delta, Tensor? resid_in, Tensor? resid_out, Tensor? norm_w, Tensor? normed, int T, int N, float eps, bool unit_offset, bool pdl, Tensor? q_codes=None, Tensor? q_sf=None) -> ()", &add_rmsnorm);
   m.def("embed_gather(Tensor ids, Tensor table, Tensor out, bool pdl) -> ()", &embed_gather);

@@ -367,8 +367,9 @@ class ProgramBase:
             session = None   # frontiers are keyed by token ids only; visual content is not part of that identity
         else:
             media = None
+        slot = self._alloc_slot()      # before the row is taken: a failure here must not leak the row
         row = self._free_rows.pop()
-        lane = Lane(self._next_id, row, self._alloc_slot(), list(prompt), 0, sampling or SamplingParams())
+        lane = Lane(self._next_id, row, slot, list(prompt), 0, sampling or SamplingParams())
         if media is not None:
             lane.media, lane.rope_delta = media, int(media.rope_delta)
         self._next_id += 1

@@ -56,6 +56,7 @@ class GenResult:
     ttft_ms: Optional[float] = None
     total_s: float = 0.0
     error: str = ""
+    token_ids: List[int] = field(default_factory=list)   # every committed completion token, in order
 
 
 class GenerationService:
@@ -182,6 +183,7 @@ class GenerationService:
                     continue
                 if ev.kind == "token":
                     res.completion_tokens += 1
+                    res.token_ids.append(int(ev.token))
                     if ev.token in eos:
                         continue
                     piece = dec.feed(ev.token)
