@@ -99,7 +99,10 @@ def build(verbose: bool = True, ptxas_info: bool = False) -> Path:
     changed = any(r[1] for r in res)
     if changed or not LIB.exists():
         tl = ce.library_paths()
-        link = ["g++", "-shared", "-o", str(LIB)] + [str(o) for o in objs]
+        # link beside the final name and rename: a reader (a process that loads the library, a copy of the tree) never
+        # sees a half-written file
+        tmp = LIB.with_suffix(".so.tmp")
+        link = ["g++", "-shared", "-o", str(tmp)] + [str(o) for o in objs]
         for p in tl:
             link += [f"-L{p}", f"-Wl,-rpath,{p}"]
         link += [f"-L{cuda}/lib64", "-lc10", "-ltorch_cpu", "-ltorch", "-lc10_cuda", "-ltorch_cuda", "-lcudart"]
@@ -108,6 +111,7 @@ def build(verbose: bool = True, ptxas_info: bool = False) -> Path:
         r = subprocess.run(link, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed: {' '.join(link)}\n{r.stdout}\n{r.stderr}")
+        os.replace(tmp, LIB)
     return LIB
 
 

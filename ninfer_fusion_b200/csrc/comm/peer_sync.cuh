@@ -18,6 +18,13 @@ __device__ __forceinline__ void red_release_sys_add(unsigned int* p, uint32_t v)
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// 16-byte load that is never served from a stale L1 line (polling of data another GPU writes).
+__device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
 // Same counter when producer and consumer are known to be on one GPU: device scope is enough and far cheaper when
 // thousands of CTAs signal one word.
 __device__ __forceinline__ void red_release_gpu_add(unsigned int* p, uint32_t v) {

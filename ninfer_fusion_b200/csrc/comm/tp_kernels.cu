@@ -75,17 +75,18 @@ __global__ void __launch_bounds__(kThreads) tp_reduce_ag_norm_kernel(const TpRed
   }
   ss = warp_sum(ss);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-  __threadfence_system();
-  __syncthreads();
+  __syncthreads();   // orders every thread's peer stores before the signalling threads below
   const uint32_t row_epoch = st->row_calls[t];
-  if (threadIdx.x == 0 && ok && do_a) {
+  if (threadIdx.x < W && ok && do_a) {
+    // thread r signals rank r: its release (system scope) is cumulative over the stores the barrier ordered, so
+    // neither the other 255 threads nor this one need a separate system fence
     float tot = 0.f;
     for (int w = 0; w < kThreads / 32; ++w) tot += red[w];
     // the sum of squares travels in a double-buffered slot so a fast peer's next call cannot overwrite it
     const int par = row_epoch & 1;
-    for (int r = 0; r < W; ++r) p.peer_ss[r][(static_cast<long long>(par) * p.T_cap + t) * W + me] = tot;
-    __threadfence_system();
-    for (int r = 0; r < W; ++r) red_release_sys_add(p.peer_row_flag[r] + t, 1u);
+    const int r = threadIdx.x;
+    p.peer_ss[r][(static_cast<long long>(par) * p.T_cap + t) * W + me] = tot;
+    red_release_sys_add(p.peer_row_flag[r] + t, 1u);
   }
 
   // ---- phase B: the whole row is here once all W slices have arrived ----

@@ -30,13 +30,20 @@ __global__ void __launch_bounds__(kThreads, 2) gdn_recurrent_kernel(const GdnPar
   __shared__ float red[2][kThreads / 32];
 
   pdl_launch_next();
-  pdl_wait_prior();
+  // The step description (sequence ranges, state slots) is uploaded before the step's first kernel and the state
+  // was last written by this kernel one step earlier, so neither depends on the kernel right before this one: the
+  // 64 KB state load is issued BEFORE waiting for that kernel and overlaps its tail.  A replay pass reads
+  // per-sequence ends that a kernel of this very step computed: it waits first.
+  if (p.seq_end != nullptr) pdl_wait_prior();
   const int hv = blockIdx.x, seq = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane >> 3, q8 = lane & 7;
   const int hk = hv / (p.n_v_heads / p.n_qk_heads);
   const int t_begin = p.cu_seqlens[seq], t_end = p.seq_end != nullptr ? p.seq_end[seq] : p.cu_seqlens[seq + 1];
-  if (t_end <= t_begin) return;
+  if (t_end <= t_begin) {
+    pdl_wait_prior();   // every CTA waits before it leaves: a later kernel's wait then still implies all earlier ones
+    return;
+  }
   const int slot = p.state_slot[seq];
 
   // thread's rows: r_j = warp*16 + j*4 + sub ; columns: float4 index q8 + 8*i
@@ -51,6 +58,7 @@ __global__ void __launch_bounds__(kThreads, 2) gdn_recurrent_kernel(const GdnPar
   const float neg_a = -__expf(p.A_log[hv]);
   const float dtb = p.dt_bias[hv];
   const float qscale = rsqrtf(static_cast<float>(kDk));
+  if (p.seq_end == nullptr) pdl_wait_prior();   // the projections of this step's tokens come from the previous kernel
 
   for (int t = t_begin; t < t_end; ++t) {
     // ---- per-warp copy of the normalised q, k of this token ----

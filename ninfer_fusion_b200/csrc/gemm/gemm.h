@@ -18,8 +18,9 @@ enum GemmEpilogue : int {
                         // rank's arrival counter is incremented (GEMM -> all-reduce in one kernel)
   kEpiRsAg = 6,         // tensor parallel, decode sizes, two hops inside one kernel: every CTA whose column
                         // tile belongs to another rank stores its fp32 tile into that owner's receive buffer
-                        // [src_rank][T_cap][N/world] and bumps the owner's per-tile counter; the CTA that owns
-                        // its tile waits for the world-1 peer tiles, adds them and the residual, rounds to
+                        // [src_rank][T_cap][N/world] as (value, epoch) pairs (the data says by itself when it is
+                        // complete: no fence, no counter); the CTA that owns its tile polls the world-1 peer
+                        // tiles until they carry this call's epoch, adds them and the residual, rounds to
                         // bf16, stores the new residual tile and the tile's per-token sums of squares into
                         // EVERY rank's residual buffer and bumps every rank's residual counter
                         // (GEMM -> reduce-scatter -> all-gather in one kernel).  The next column-parallel
@@ -27,11 +28,12 @@ enum GemmEpilogue : int {
 };
 
 // Rank-local bookkeeping of kEpiRsAg and of the gathered consumer (ordinary device memory, zero-initialised).
-constexpr int kRsMaxOwnTiles = 64;   // column tiles of 128 a rank can own (N / world <= 8192)
+constexpr int kRsMaxTiles = 64;      // column tiles of 128 (N <= 8192)
 constexpr int kRsMaxTokenTiles = 16;
 constexpr int kRsSsStride = 64;      // column tiles per row of the sums-of-squares table (N <= 8192)
 struct RsState {
-  unsigned int tile_expected[kRsMaxOwnTiles * kRsMaxTokenTiles];  // cumulative peer arrivals consumed per owned tile
+  unsigned int tile_epoch[kRsMaxTiles * kRsMaxTokenTiles];  // finished calls per (column tile, token tile); every
+                                                            // rank runs the same calls, so the words agree
   unsigned int x_expected;   // cumulative residual-tile arrivals the next consumer has to see
 };
 
@@ -90,7 +92,8 @@ struct GemmArgs {
   const unsigned int* call_idx = nullptr; // device counter whose parity selects the receive buffer
   float* peer_recv[kMaxRanks] = {};
   unsigned int* peer_flag[kMaxRanks] = {};
-  // kEpiRsAg only: every rank's residual buffer [T_cap][N] bf16, sums-of-squares table, residual counter; this
+  // kEpiRsAg only (peer_recv then holds (fp32 bits, epoch) pairs, 8 bytes per value; peer_flag is unused):
+  // every rank's residual buffer [T_cap][N] bf16, sums-of-squares table, residual counter; this
   // rank's bookkeeping; `rs_phase` 0 = fused (production), 1 = push tiles only (owned tiles are pushed to this
   // rank's own receive buffer too), 2 = no GEMM, owners reduce the `world` tiles that phase 1 left.  Phases 1 and
   // 2 exist so that several ranks can be walked through on ONE GPU without any kernel waiting on another.

@@ -94,6 +94,7 @@ struct KernelParams {
   long long ld_resid;
   float* peer_ss[kMaxRanks];
   unsigned int* peer_xflag[kMaxRanks];
+  uint2* peer_recv_ll[kMaxRanks];   // [src][T_cap][N / world] (fp32 bits, epoch)
   RsState* rs_state;
   int rs_phase;
   // gathered consumer (kEpiStore / kEpiSwiglu): wait for the residual tiles, RMS norm as an epilogue row scale
@@ -279,16 +280,30 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
   // kEpiRsAg, CTA that owns its tile: what the reduction reads from global memory (its bookkeeping word and the
   // residual of the first 32 token rows) is fetched now, so that the latency hides under the main loop
   uint4 resid_pre[4] = {};
-  uint32_t expected_pre = 0;
+  uint32_t epoch_pre = 0;
   if constexpr (EPI == kEpiRsAg) {
+    if (p.cluster <= 1 || blockIdx.z == 0) epoch_pre = p.rs_state->tile_epoch[blockIdx.x * kRsMaxTokenTiles + blockIdx.y];
     if (n0 / p.slice_cols == p.rank && p.rs_phase != 1 && (p.cluster <= 1 || blockIdx.z == 0)) {
-      expected_pre = p.rs_state->tile_expected[((n0 % p.slice_cols) / kTileN) * kRsMaxTokenTiles + blockIdx.y];
       const int r = threadIdx.x >> 2, t = t0 + r;
       if (r < TN && t < p.T) {
         const uint4* src = reinterpret_cast<const uint4*>(p.peer_x[p.rank] + static_cast<long long>(t) * p.ld_resid + n0 +
                                                           (threadIdx.x & 3) * 32);
 #pragma unroll
         for (int q = 0; q < 4; ++q) resid_pre[q] = src[q];
+      }
+    }
+  }
+  if constexpr (EPI == kEpiStore) {
+    // decode conv tiles: pull this thread's history columns towards L2 now (fire and forget), so that the
+    // dependent slot -> history loads of the epilogue do not each pay a trip to HBM after the main loop
+    if (p.conv_state != nullptr && n0 < p.conv_C && (p.cluster <= 1 || blockIdx.z == 0)) {
+      const int n = n0 + threadIdx.x;
+      for (int t = t0; t < min(p.T, t0 + TN); ++t) {
+        const __nv_bfloat16* st = p.conv_state + static_cast<long long>(p.conv_slot[t]) * 3 * p.conv_C + n;
+        if ((threadIdx.x & 31) == 0) {   // one request per 64-byte run of a warp's channels
+#pragma unroll
+          for (int j = 0; j < 3; ++j) asm volatile("prefetch.global.L2 [%0];" ::"l"(st + j * p.conv_C));
+        }
       }
     }
   }
@@ -413,17 +428,53 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
           }
         }
       }
-    } else if constexpr (EPI == kEpiRsAg) {
-      const int n = n0 + warp * 32 + lane;
+    } else if constexpr (EPI == kEpiPushPartial) {
+      // reduce-scatter by push: this tile's columns belong to one owner rank; the fp32 partial goes into the
+      // owner's receive buffer [src_rank][split][T][slice_cols].  The tile passes through shared memory (the idle
+      // pipeline stages), up to 128 token rows at a time, so that the stores are 16 bytes wide and every token row
+      // of the tile is one contiguous 512-byte run, instead of 4-byte stores in 128-byte runs.
       const int owner = n0 / p.slice_cols;
-      const int tile_local = (n0 - owner * p.slice_cols) / kTileN;
-      const int flag_idx = tile_local * kRsMaxTokenTiles + blockIdx.y;
+      constexpr int kRowPad = kTileN + 4;
+      constexpr int kRows = TN < 128 ? TN : 128;
+      float* tile_s = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));
+      const int col = (threadIdx.x & 3) * 32;
+      float* dst = p.peer_recv[owner] + (static_cast<long long>(p.rank) * gridDim.z + blockIdx.z) * p.T * p.slice_cols +
+                   (n0 + col - owner * p.slice_cols);
+      for (int h = 0; h < TN; h += kRows) {
+        if (t0 + h >= p.T) break;
+        for (int c = h; c < h + kRows; c += kChunk) {
+          if (t0 + c >= p.T) break;
+          float v[kChunk];
+          load_acc(c, v);
+#pragma unroll
+          for (int j = 0; j < kChunk; ++j) tile_s[(c - h + j) * kRowPad + warp * 32 + lane] = v[j];
+        }
+        __syncthreads();
+        for (int r = threadIdx.x >> 2; r < kRows; r += 32) {
+          const int t = t0 + h + r;
+          if (t >= p.T) continue;
+          const float4* src4 = reinterpret_cast<const float4*>(tile_s + r * kRowPad + col);
+          float4* dst4 = reinterpret_cast<float4*>(dst + static_cast<long long>(t) * p.slice_cols);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) dst4[q] = src4[q];
+        }
+        __syncthreads();   // (orders the peer stores before the signalling thread; frees the staging tile)
+      }
+      // publish: the signalling thread's release (system scope) is cumulative over the stores the barrier ordered
+      if (threadIdx.x == 0) red_release_sys_add(p.peer_flag[owner], 1u);
+    } else if constexpr (EPI == kEpiRsAg) {
+      const int owner = n0 / p.slice_cols;
       const bool mine = owner == p.rank;
       const bool pushes = p.rs_phase != 2 && (!mine || p.rs_phase == 1);
       const bool reduces = mine && p.rs_phase != 1;
+      // Every call of this tile carries the next epoch: the tile's fp32 values travel as (value, epoch) pairs, so
+      // the owner sees from the data itself when a peer's tile is complete.  No fence and no counter sit between
+      // the peer's stores and the owner's loads (16-byte stores are not torn).
+      unsigned int* epoch_word = &p.rs_state->tile_epoch[blockIdx.x * kRsMaxTokenTiles + blockIdx.y];
+      const uint32_t epoch = epoch_pre + 1u;
       // The fp32 tile goes through shared memory (behind the split-K landing zone of the idle pipeline stages) so
-      // that the second half works on token rows: a quarter row (32 columns) per thread, 16-byte accesses, runs of
-      // 512 contiguous bytes per token towards a peer instead of 128.
+      // that the second half works on token rows: a quarter row (32 columns) per thread, 16-byte accesses, long
+      // contiguous runs per token towards a peer.
       constexpr int kRowPad = kTileN + 4;   // floats per row: shifts consecutive rows by four banks
       float* tile_s = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw))) + (S - 1) * TN * 128;
       if (p.rs_phase != 2) {
@@ -435,48 +486,40 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
           for (int j = 0; j < kChunk; ++j) tile_s[(c + j) * kRowPad + warp * 32 + lane] = v[j];
         }
       }
-      unsigned int* expected = &p.rs_state->tile_expected[flag_idx];
-      uint32_t target = 0;
-      if (reduces) {
-        // owner of the tile: the peers' tiles have to be here before the rows can be reduced
-        target = expected_pre + static_cast<uint32_t>(p.rs_phase == 0 ? p.world - 1 : p.world);
-        if (threadIdx.x == 0) rs_ok = wait_counter(p.peer_flag[p.rank] + flag_idx, target, p.status) ? 1 : 0;
-      }
+      if (threadIdx.x == 0) rs_ok = 1;
       __syncthreads();
       const int seg = threadIdx.x & 3;            // quarter of the tile's 128 columns
       const int col = seg * 32;                   // first column of this thread inside the tile
       const int n_first = n0 + col;               // ... in the output
       const int n_local = n_first - owner * p.slice_cols;
-      (void)n;
       if (pushes) {
-        // hop 1: rows of the fp32 tile into the owner's receive buffer [src][T_cap][slice]
-        float* dst = p.peer_recv[owner] + static_cast<long long>(p.rank) * p.T_cap * p.slice_cols + n_local;
+        // hop 1: rows of the tile into the owner's receive buffer [src][T_cap][slice] of (value, epoch) pairs
+        uint2* dst = p.peer_recv_ll[owner] + static_cast<long long>(p.rank) * p.T_cap * p.slice_cols + n_local;
         for (int r = threadIdx.x >> 2; r < TN; r += 32) {
           const int t = t0 + r;
           if (t >= p.T) continue;
           const float4* src4 = reinterpret_cast<const float4*>(tile_s + r * kRowPad + col);
-          float4* dst4 = reinterpret_cast<float4*>(dst + static_cast<long long>(t) * p.slice_cols);
+          uint4* dst4 = reinterpret_cast<uint4*>(dst + static_cast<long long>(t) * p.slice_cols);
 #pragma unroll
-          for (int q = 0; q < 8; ++q) dst4[q] = src4[q];
+          for (int q = 0; q < 8; ++q) {
+            const float4 f = src4[q];
+            dst4[2 * q] = make_uint4(__float_as_uint(f.x), epoch, __float_as_uint(f.y), epoch);
+            dst4[2 * q + 1] = make_uint4(__float_as_uint(f.z), epoch, __float_as_uint(f.w), epoch);
+          }
         }
-        __syncthreads();
-        // the block barrier orders every thread's peer stores before the signalling thread, whose release (system
-        // scope) is cumulative over them: no separate fence
-        if (threadIdx.x == 0) red_release_sys_add(p.peer_flag[owner] + flag_idx, 1u);
         stamp(7);
       }
       if (reduces) {
         stamp(8);
-        const bool ok = rs_ok != 0;
         __nv_bfloat16* my_x = p.peer_x[p.rank];
-        const float* recv = p.peer_recv[p.rank] + n_local;
+        const uint2* recv = p.peer_recv_ll[p.rank] + n_local;
         for (int r0 = 0; r0 < TN; r0 += 32) {      // uniform trip count: the shuffles below need whole warps
           const int r = r0 + (threadIdx.x >> 2);
           const int t = t0 + r;
-          const bool live = ok && r < TN && t < p.T;
+          bool live = r < TN && t < p.T;
           float ss = 0.f;
+          float4 a[8];
           if (live) {
-            float4 a[8];
             if (p.rs_phase == 0) {
               const float4* own = reinterpret_cast<const float4*>(tile_s + r * kRowPad + col);
 #pragma unroll
@@ -485,16 +528,40 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
 #pragma unroll
               for (int q = 0; q < 8; ++q) a[q] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
-            for (int src = 0; src < p.world; ++src) {   // rank order, the same on every rank's owner
+            for (int src = 0; src < p.world && live; ++src) {   // rank order, the same on every rank's owner
               if (p.rs_phase == 0 && src == p.rank) continue;
-              const float4* sp = reinterpret_cast<const float4*>(
-                  recv + (static_cast<long long>(src) * p.T_cap + t) * p.slice_cols);
+              const uint4* sp = reinterpret_cast<const uint4*>(recv + (static_cast<long long>(src) * p.T_cap + t) * p.slice_cols);
 #pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                const float4 b = __ldcg(sp + q);
-                a[q].x += b.x; a[q].y += b.y; a[q].z += b.z; a[q].w += b.w;
+              for (int half = 0; half < 2; ++half) {
+                uint4 v[8];
+                bool here = false;
+                for (uint32_t spin = 0; spin < kPeerPollLimit && !here; ++spin) {
+                  here = true;
+#pragma unroll
+                  for (int q = 0; q < 8; ++q) {
+                    v[q] = ld_volatile_v4(sp + half * 8 + q);
+                    here = here && v[q].y == epoch && v[q].w == epoch;
+                  }
+                  if (!here) {
+                    if ((spin & 1023u) == 1023u && p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) break;
+                    if (spin > 64) __nanosleep(100);
+                  }
+                }
+                if (!here) {   // bounded: record it and let the step fail on the host instead of hanging
+                  report_status(p.status, kStatusPeerWaitTimeout);
+                  rs_ok = 0;
+                  live = false;
+                }
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  float4& acc = a[half * 4 + q / 2];
+                  if (q & 1) { acc.z += __uint_as_float(v[q].x); acc.w += __uint_as_float(v[q].z); }
+                  else { acc.x += __uint_as_float(v[q].x); acc.y += __uint_as_float(v[q].z); }
+                }
               }
             }
+          }
+          if (live) {
             const long long at = static_cast<long long>(t) * p.ld_resid + n_first;
             uint4 o[4];
 #pragma unroll
@@ -532,10 +599,12 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
         stamp(9);
         __syncthreads();
         stamp(10);
-        if (ok && threadIdx.x < p.world) red_release_sys_add(p.peer_xflag[threadIdx.x], 1u);   // (release: see above)
+        // the block barrier orders every thread's peer stores before the signalling threads, whose release (system
+        // scope) is cumulative over them: no separate fence
+        if (rs_ok && threadIdx.x < p.world) red_release_sys_add(p.peer_xflag[threadIdx.x], 1u);
         stamp(11);
-        if (threadIdx.x == 0) *expected = target;
       }
+      if (threadIdx.x == 0 && p.rs_phase != 1) *epoch_word = epoch;
       // what the next consumer of the residual stream has to wait for: one arrival per (column tile, token tile)
       if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && p.rs_phase != 1)
         p.rs_state->x_expected += static_cast<unsigned int>((p.N / kTileN) * gridDim.y);
@@ -597,18 +666,6 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
             if (t < p.T && n < p.N)
               p.partial[(static_cast<long long>(blockIdx.z) * p.T + t) * p.N + n] = v[j];
           }
-        } else if constexpr (EPI == kEpiPushPartial) {
-          // reduce-scatter by push: this tile's columns belong to one owner rank; write the fp32
-          // partial straight into the owner's receive buffer [src_rank][split][T][slice_cols].
-          const int owner = n0 / p.slice_cols;
-          float* dst = p.peer_recv[owner] +
-                       (static_cast<long long>(p.rank) * gridDim.z + blockIdx.z) * p.T * p.slice_cols +
-                       (n - owner * p.slice_cols);
-#pragma unroll
-          for (int j = 0; j < kChunk; ++j) {
-            const int t = t0 + c + j;
-            if (t < p.T && n < p.N) dst[static_cast<long long>(t) * p.slice_cols] = v[j];
-          }
         } else if constexpr (EPI == kEpiPushAll) {
           // one-shot all-reduce by push: the fp32 tile goes to EVERY rank's receive buffer
           // [parity][src_rank][T_cap][N]; the reader sums the W sources in rank order.
@@ -660,16 +717,6 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
               *reinterpret_cast<uint32_t*>(outp + static_cast<long long>(t) * ldo + ne) = pack_bf16x2(lo, hi);
             }
           }
-        }
-      }
-      if constexpr (EPI == kEpiPushPartial) {
-        // publish: the block barrier orders every thread's peer stores before the signalling thread, whose
-        // system-scope fence + release is cumulative over them (one fence instead of 128)
-        __syncthreads();
-        if (threadIdx.x == 0) {
-          __threadfence_system();
-          unsigned int* flag = p.peer_flag[n0 / p.slice_cols];
-          asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(flag) : "memory");
         }
       }
       if constexpr (EPI == kEpiPushAll) {
@@ -1260,7 +1307,8 @@ const char* gemm_bf16(const GemmArgs& a) {
     kp.rank = a.rank;
     kp.world = a.world;
     for (int r = 0; r < a.world; ++r) {
-      if (a.peer_recv[r] == nullptr || a.peer_flag[r] == nullptr) return "gemm_bf16: missing peer pointer";
+      if (a.peer_recv[r] == nullptr || (a.peer_flag[r] == nullptr && a.epi != kEpiRsAg))
+        return "gemm_bf16: missing peer pointer";
       kp.peer_recv[r] = a.peer_recv[r];
       kp.peer_flag[r] = a.peer_flag[r];
     }
@@ -1276,7 +1324,7 @@ const char* gemm_bf16(const GemmArgs& a) {
   }
   if (a.epi == kEpiRsAg) {
     if (kp.N % a.world || (kp.N / a.world) % kTileN) return "gemm_bf16: N / world must be a multiple of 128";
-    if (kp.N / a.world / kTileN > kRsMaxOwnTiles || kp.N / kTileN > kRsSsStride)
+    if (kp.N / kTileN > kRsMaxTiles || kp.N / kTileN > kRsSsStride)
       return "gemm_bf16: too many column tiles for the reduce-scatter bookkeeping";
     if ((kp.T + tn - 1) / tn > kRsMaxTokenTiles || a.T_cap < kp.T) return "gemm_bf16: too many rows for the receive buffer";
     if (a.rs_state == nullptr || a.rs_phase < 0 || a.rs_phase > 2 || (a.ld_resid % 8))
@@ -1298,6 +1346,7 @@ const char* gemm_bf16(const GemmArgs& a) {
       if (a.peer_x[r] == nullptr || a.peer_ss[r] == nullptr || a.peer_xflag[r] == nullptr)
         return "gemm_bf16: missing residual pointer of a rank";
       kp.peer_x[r] = static_cast<__nv_bfloat16*>(a.peer_x[r]);
+      kp.peer_recv_ll[r] = reinterpret_cast<uint2*>(a.peer_recv[r]);
       kp.peer_ss[r] = a.peer_ss[r];
       kp.peer_xflag[r] = a.peer_xflag[r];
     }

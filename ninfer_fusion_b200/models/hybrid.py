@@ -246,9 +246,10 @@ class HybridModel:
         self._rot_scratch: Dict[tuple, torch.Tensor] = {}   # rotated activations / gate-up rows of groupwise-int weights
         self.groupint_dense_prefill = os.environ.get("NFB_GROUPINT_DENSE", "1") != "0"
         self.cluster_splitk = True  # False: split-K through an fp32 workspace + reduce kernel
-        # GDN decode conv inside the in_proj epilogue: pays off for the small sharded projections of a tensor-parallel
-        # rank (one launch less per layer), costs a little on the whole-width projection of one GPU, whose epilogue
-        # is on the critical path of a multi-wave grid.  NFB_FUSE_CONV=0/1 forces it; default: on under `comm`.
+        # GDN decode conv inside the in_proj epilogue (NFB_FUSE_CONV=1): one launch less per GDN layer, but the taps
+        # and the history roll then sit on the critical path of the projection's leader CTAs; measured slower than
+        # the separate conv kernel both on one GPU (13.78 vs 13.56 ms per round) and on a 1/8 shard (4.73 vs 4.37 ms),
+        # so it is off unless asked for.
         self._fuse_conv_env = os.environ.get("NFB_FUSE_CONV")
         self.attn_impl = 0  # 0 = pick, 1 = SIMT, 2 = tensor-core split-KV attention
         self.comm = None  # tensor-parallel communicator (parallel.tp), None on one GPU
@@ -451,7 +452,7 @@ class HybridModel:
         C = g.gdn_conv_dim
         conv = (ws.conv if rec is None else rec.conv[gi])[:T]
         decode = b.n_tokens == b.n_seqs and b.one_token_per_seq
-        fuse_conv = self.comm is not None if self._fuse_conv_env is None else self._fuse_conv_env != "0"
+        fuse_conv = self._fuse_conv_env is not None and self._fuse_conv_env != "0"
         if (fuse_conv and decode and write_state and rec is None and b.tree_parent is None and C % 128 == 0
                 and isinstance(w_in, torch.Tensor) and w_in.dtype == torch.bfloat16):
             # decode: conv taps + SiLU + history roll in the projection's epilogue (token i is sequence i)

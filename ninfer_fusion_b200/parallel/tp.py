@@ -164,8 +164,8 @@ class TensorParallel:
                              ("row_flag", self.T_cap * 4), ("arrival_flag", 256), ("all_flag", 256),
                              ("cand", 2 * self.T_cap * world * 8), ("argmax_flag", self.T_cap * 4),
                              # decode-sized reduce-scatter + all-gather inside the GEMM (gemm kEpiRsAg)
-                             ("rs_recv", self.one_shot_rows * N * 4),       # [src][rows][N/W] fp32
-                             ("rs_flag", 64 * 16 * 4),                      # per (owned tile, token tile)
+                             ("rs_recv", self.one_shot_rows * N * 8),       # [src][rows][N/W] (fp32 bits, epoch) pairs
+                             ("rs_flag", 256),                              # (unused: the pairs carry their own flag)
                              ("rs_ss", self.one_shot_rows * 64 * 4),        # [rows][64 column tiles] fp32
                              ("x_flag", 256)]:
             self.off[name] = off

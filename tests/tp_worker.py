@@ -53,12 +53,12 @@ def main():
     single_gen = Generator(cfg, full, dev, max_batch=4, max_context=512, kv_format="bf16", page_size=16,
                            prefill_chunk=256, use_graph=False)
     long_prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (150, 70)]
-    ref_logits = {}
+    ref_logits, ref_tokens = {}, {}
     for name, ps in (("short", prompts), ("long", long_prompts)):
-        single_gen.prefill(ps)
+        ref_tokens[name] = [single_gen.prefill(ps)]
         ref_logits[(name, "prefill")] = single_gen.ws.logits[: len(ps)].float().clone()
         for _ in range(3):
-            single_gen.decode_step()
+            ref_tokens[name].append(single_gen.decode_step())
         ref_logits[(name, "decode")] = single_gen.ws.logits[: len(ps)].float().clone()
     single = single_gen.generate(prompts, n_new)
 
@@ -76,7 +76,10 @@ def main():
         for name, ps in (("short", prompts), ("long", long_prompts)):
             gen.prefill(ps)
             got = {"prefill": gathered_logits(gen, len(ps))}
-            for _ in range(3):
+            for step in range(3):
+                # teacher forcing: every run is fed the single-GPU run's tokens, so a near-tie that flips an
+                # arg-max on one side does not send the two runs down different sequences
+                gen.last_tokens = list(ref_tokens[name][step])
                 gen.decode_step()
             got["decode"] = gathered_logits(gen, len(ps))
             for when, lg in got.items():
@@ -129,7 +132,8 @@ def main():
     worst = max(logit_err.values())
     msg += f" worst logit error / range {worst:.4f};"
     for key, err in logit_err.items():
-        if err > 2e-2:
+        # folded norm weights are rounded to bf16 once more inside the GEMM weights: a little more slack
+        if err > (3e-2 if key[2] else 2e-2):
             ok = False
             msg += f" logits{key}={err:.4f};"
     if rank == 0:
