@@ -96,6 +96,106 @@ def reference_arm(args) -> int:
     return 0
 
 
+def speculative_run(args, cfg, device) -> int:
+    """Draft-verify decoding against plain greedy decoding of the same model and prompts on one GPU: decode tok/s of
+    both (device-timed, whole rounds, host round trips included: speculative rounds are eager), acceptance rate and
+    tokens per round.  Prints one JSON line with class "speculative"."""
+    import torch
+
+    from ninfer_fusion_b200.models.weights import random_weights
+    from ninfer_fusion_b200.runtime.generator import Generator
+    from ninfer_fusion_b200.runtime.speculative import SpeculativeGenerator
+
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        print("bench.py: --spec runs on one GPU", file=sys.stderr)
+        return 2
+    B, L, Kd, R_ = args.batch, args.prompt_len, args.draft_tokens, args.tree_ranks
+    n_rounds, warm = args.steps, max(3, args.warmup)
+    weights = random_weights(cfg, device, seed=0, with_mtp=True)
+    g = torch.Generator().manual_seed(1234)
+    prompts = [torch.randint(0, cfg.vocab, (L,), generator=g).tolist() for _ in range(B)]
+    n_plain = (n_rounds + warm + 2) * (Kd + 1)
+    max_ctx = L + n_plain + 64
+
+    def timed(fn, n):
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(device)
+        return e0.elapsed_time(e1)
+
+    plain = Generator(cfg, weights, device, max_batch=B, max_context=max_ctx, kv_format=args.kv_format, page_size=64,
+                      prefill_chunk=2048, use_graph=True, pdl=bool(args.pdl))
+    first = plain.prefill(prompts)
+    stream = [[t] for t in first]
+    for _ in range(warm):
+        for b, t in enumerate(plain.decode_step()):
+            stream[b].append(t)
+    steps_plain = n_plain - warm - 1
+
+    def plain_step():
+        for b, t in enumerate(plain.decode_step()):
+            stream[b].append(t)
+    plain_ms = timed(plain_step, steps_plain)
+    plain_tok_s = B * steps_plain / (plain_ms / 1e3)
+    del plain
+    torch.cuda.empty_cache()
+
+    spec = SpeculativeGenerator(cfg, weights, device, max_batch=B, max_context=max_ctx, draft_tokens=Kd,
+                                drafter="mtp" if args.spec == "mtp" else "hook", tree_ranks=R_, kv_format=args.kv_format,
+                                page_size=64, prefill_chunk=2048, pdl=bool(args.pdl))
+    if args.spec == "hook":
+        def hook(b, history, k):
+            done = len(history) - L
+            truth = stream[b][done:done + k]
+            truth = truth + [0] * (k - len(truth))
+            cut = (done + b) % (k + 1)
+            return [t if i < cut else (t + 1) % cfg.vocab for i, t in enumerate(truth)]
+        spec.draft_hook = hook
+        if R_ > 1:
+            def tree_hook(b, history, k, r):
+                # rank 0 = the chain's guess; when that guess is wrong, rank 1 holds the right token every other round,
+                # so a side branch can rescue the depth; further ranks are wrong
+                done = len(history) - L
+                chain = hook(b, history, k)
+                truth = stream[b][done:done + k] + [0] * k
+                out_ = []
+                for d in range(k):
+                    row = [chain[d]]
+                    for j in range(1, r):
+                        rescue = j == 1 and chain[d] != truth[d] and done % 2 == 0
+                        row.append(truth[d] if rescue else (truth[d] + 1 + j) % cfg.vocab)
+                    out_.append(row)
+                return out_
+            spec.tree_hook = tree_hook
+    spec.prefill(prompts)
+    for _ in range(warm):
+        spec.decode_round()
+    e0, r0 = spec.emitted, spec.rounds
+    spec_ms = timed(spec.decode_round, n_rounds)
+    emitted = spec.emitted - e0
+    spec.model.status.check("after speculative rounds")
+    out = {
+        "class": "speculative", "metric": "decode tokens/sec, draft-verify vs plain greedy (same model, prompts, GPU)",
+        "value": round(emitted / (spec_ms / 1e3), 2), "unit": "tokens/s", "n_gpus": 1, "steps": n_rounds, "warmup": warm,
+        "ms_per_step": round(spec_ms / n_rounds, 4), "higher_is_better": True, "dtype": "bf16",
+        "data": "synthetic uniform-random token prompts, random-init weights",
+        "config": {"model": cfg.name + ("" if not args.layers else " (SHRUNK: INVALID)"), "global_batch": B, "seq_len": L,
+                   "kv": args.kv_format, "drafter": args.spec, "draft_tokens": Kd, "tree_ranks": R_,
+                   "rounds": "eager (no CUDA graph), host round trip per round"},
+        "tokens_per_round": round(emitted / max(1, (spec.rounds - r0) * B), 3),
+        "acceptance": round((emitted / max(1, (spec.rounds - r0) * B) - 1.0) / Kd, 4),
+        "plain": {"tokens_per_s": round(plain_tok_s, 2), "ms_per_step": round(plain_ms / steps_plain, 4),
+                  "rounds": "CUDA graph per round"},
+        "speedup_vs_plain": round(emitted / (spec_ms / 1e3) / plain_tok_s, 3),
+    }
+    print(json.dumps(out), flush=True)
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -119,6 +219,12 @@ def main() -> int:
     ap.add_argument("--tp-mode", default="fused", choices=["fused", "oneshot", "nccl"],
                     help="tensor-parallel reduction: fused = reduce-scatter + all-gather inside the GEMMs, oneshot = "
                          "every rank receives every tile + one sum kernel, nccl = NCCL all-reduce baseline")
+    ap.add_argument("--spec", default="none", choices=["none", "mtp", "hook"],
+                    help="speculative decoding run (one GPU, eager rounds): mtp = the draft module proposes (random-init "
+                         "weights accept next to nothing), hook = synthetic drafts of mixed quality taken from the plain "
+                         "greedy stream (the first (round + b) mod (K + 1) drafts right, the rest wrong)")
+    ap.add_argument("--draft-tokens", type=int, default=4)
+    ap.add_argument("--tree-ranks", type=int, default=1, help="candidates per depth of the draft tree (1 = chain)")
     ap.add_argument("--parallel", default="", choices=["", "tp", "ep"],
                     help="multi-GPU plan: tp = tensor parallel (dense default), ep = data parallel + expert parallel (MoE default)")
     args = ap.parse_args()
@@ -192,6 +298,8 @@ def main() -> int:
         return 2
 
     B, L, K, W = args.batch, args.prompt_len, args.steps, args.warmup
+    if args.spec != "none":
+        return speculative_run(args, cfg, device)
     B_local = B // world if ep else B  # expert parallel: every rank decodes its own share of the sequences
     max_ctx = L + 2 * (K + W) + 64
     gen = Generator(cfg, weights, device, max_batch=B_local, max_context=max_ctx, kv_format=args.kv_format,

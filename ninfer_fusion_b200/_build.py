@@ -97,7 +97,9 @@ def build(verbose: bool = True, ptxas_info: bool = False) -> Path:
         res = list(ex.map(lambda j: _compile(j[0], j[1], j[2], hdr, verbose), jobs))
     objs = [r[0] for r in res]
     changed = any(r[1] for r in res)
-    if changed or not LIB.exists():
+    # (objects may also have been compiled by an earlier, link-less pass: compare against the library's age)
+    stale = LIB.exists() and any(o.stat().st_mtime > LIB.stat().st_mtime for o in objs)
+    if changed or stale or not LIB.exists():
         tl = ce.library_paths()
         # link beside the final name and rename: a reader (a process that loads the library, a copy of the tree) never
         # sees a half-written file

@@ -46,7 +46,12 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--weights", default="bf16", choices=["bf16", "fp8", "nvfp4", "q4", "q5", "q6", "w8", "q4+h64", "q4+h128", "q5+h64", "q6+h64", "w8+h64", "stored"],
                     help="matmul weight format on the device; q4/q5/q6/w8 keep groupwise-int codes and dequantise in the "
                          "decode kernels ('+h64': input dimension rotated by a block Hadamard first); 'stored' keeps an artifact's groupwise-int tensors exactly as encoded")
-    ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8", "fp8h", "int8", "nvfp4"],
+    ap.add_argument("--kv-descent-age", type=int, default=0,
+                    help="with --kv-dtype mixed: cells whose newest token is older than this many tokens descend one "
+                         "precision rung per pass (bf16 -> fp8 -> nvfp4); 0 = no automatic descent")
+    ap.add_argument("--kv-descent-target-mib", type=float, default=0.0,
+                    help="stop descending once the live KV cells of the mixed layers fit in this many MiB (0 = no target)")
+    ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8", "fp8h", "int8", "nvfp4", "mixed"],
                     help="KV cache codec (fp8h = fp8 per-row with K in the Hadamard frame)")
     ap.add_argument("--kv-layer-spec", default="", help="per-layer KV storage, e.g. 'all:fp8' or '0-3:bf16,4-15:nvfp4'")
     ap.add_argument("--max-context", type=int, default=4096)
@@ -237,9 +242,15 @@ def program_factory(args, cfg: ModelConfig, weights, kv, shard=None, comm=None):
     if str(args.device).startswith("cuda"):
         from .runtime.gpu_program import GpuProgram
 
+        descent = None
+        if getattr(args, "kv_descent_age", 0) > 0:
+            from .kv.descent import DescentConfig
+            descent = DescentConfig(min_age_tokens=int(args.kv_descent_age),
+                                    target_resident_bytes=int(getattr(args, "kv_descent_target_mib", 0.0) * (1 << 20)))
+
         def factory():
             text = {k: v for k, v in weights.items() if not k.startswith("vision/")}
-            prog = GpuProgram(cfg, text, args.device, max_lanes=args.max_lanes, max_context=args.max_context,
+            prog = GpuProgram(cfg, text, args.device, descent=descent, max_lanes=args.max_lanes, max_context=args.max_context,
                               kv_format=kv, page_size=args.page_size, prefill_chunk=args.prefill_chunk,
                               use_graph=not args.no_graphs, kv_pages=resolve_kv_pages(args, cfg, kv), shard=shard,
                               comm=comm, weight_budget_bytes=int(args.weight_budget_gib * (1 << 30)) if args.weight_budget_gib > 0 else None)

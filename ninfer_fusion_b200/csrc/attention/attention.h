@@ -102,6 +102,16 @@ int prefill_attn_block_tokens(int n_q_heads, int n_kv_heads);
 
 // Moves K/V rows of each sequence from cache positions src_pos[b, m] to dst_pos[b, m], in order m = 0.. (a negative
 // entry skips the move): accepted tree nodes go from frontier + node index to frontier + depth (kv/kv_move.cu).
+// Re-encodes cells of a mixed-precision layer into another tier (see kv/kv_requant.cu).  `src_cell` / `dst_cell`:
+// device arrays of n_cells entries, each tier << 28 | slot; the caller updates the layer's cell map afterwards.
+struct KvRequantParams {
+  KvLayer kv;             // format kKvMixed with all three tiers' planes
+  const int* src_cell;
+  const int* dst_cell;
+  int n_cells;
+};
+const char* kv_requant(const KvRequantParams& p, cudaStream_t stream);
+
 const char* kv_move_rows(const KvLayer& L, const int* table, int table_cols, const int* table_row, const int* src_pos,
                          const int* dst_pos, int n_seq, int max_moves, cudaStream_t stream);
 

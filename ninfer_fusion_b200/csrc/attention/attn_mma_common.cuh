@@ -46,11 +46,35 @@ struct RawUnit {
   uint4 a;
   uint4 b;      // second half of a bf16 unit only
   float scale;  // int8-group / nvfp4 block scale
+  int tier;     // mixed layers: the tier this unit was read from (decides how it is converted)
 
   __device__ __forceinline__ void clear() {
     a = make_uint4(0, 0, 0, 0);
     b = make_uint4(0, 0, 0, 0);
     scale = 0.f;
+    tier = 0;
+  }
+  // `which` 0 = K, 1 = V; `r` as returned by kv_row_of (mixed layers: tier in the top bits)
+  __device__ __forceinline__ void load_row(const KvLayer& kv, int which, long long r, int part) {
+    if constexpr (FORMAT == kKvMixed) {
+      tier = kv_row_tier(r);
+      const long long rr = kv_row_index(r);
+      const uint8_t* codes = which ? kv.tier_v_codes[tier] : kv.tier_k_codes[tier];
+      if (tier == 0) {
+        const uint4* src = reinterpret_cast<const uint4*>(codes + rr * (2 * D) + part * 32);
+        a = src[0];
+        b = src[1];
+      } else if (tier == 1) {
+        a = *reinterpret_cast<const uint4*>(codes + rr * D + part * 16);
+      } else {
+        const uint2 c = *reinterpret_cast<const uint2*>(codes + rr * (D / 2) + part * 8);
+        a = make_uint4(c.x, c.y, 0, 0);
+        const uint8_t* scales = which ? kv.tier_v_scales[2] : kv.tier_k_scales[2];
+        scale = e4m3_to_float(scales[rr * (D / 16) + part]);
+      }
+    } else {
+      load(kv, which ? kv.v_codes : kv.k_codes, which ? kv.v_scales : kv.k_scales, r, part);
+    }
   }
   __device__ __forceinline__ void load(const KvLayer& kv, const uint8_t* codes, const uint8_t* scales, long long r,
                                        int part) {
@@ -70,7 +94,22 @@ struct RawUnit {
     }
   }
   __device__ __forceinline__ void convert(uint32_t* out) const {
-    if constexpr (FORMAT == kKvFp8Row) {
+    if constexpr (FORMAT == kKvMixed) {
+      // one of the three tier codecs, chosen per unit
+      if (tier == 0) {
+        RawUnit<kKvBf16> u;
+        u.a = a; u.b = b; u.scale = 0.f; u.tier = 0;
+        u.convert(out);
+      } else if (tier == 1) {
+        RawUnit<kKvFp8Row> u;
+        u.a = a; u.b = b; u.scale = 0.f; u.tier = 0;
+        u.convert(out);
+      } else {
+        RawUnit<kKvNvfp4> u;
+        u.a = a; u.b = b; u.scale = scale; u.tier = 0;
+        u.convert(out);
+      }
+    } else if constexpr (FORMAT == kKvFp8Row) {
       const uint32_t w[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {

@@ -139,14 +139,24 @@ __global__ void __launch_bounds__(128) attn_prep_kernel(const AttnPrepParams p) 
   if (seq < 0 || pos < 0) return;  // padded token
   const int page = p.block_table[static_cast<long long>(seq) * p.table_stride + pos / p.kv.page_size];
   if (page < 0) return;
-  const long long r = (static_cast<long long>(page) * p.kv.n_kv_heads + h) * p.kv.page_size + pos % p.kv.page_size;
-  const int rb = kv_row_bytes(p.kv.format, D), sb = kv_scale_bytes(p.kv.format, D, p.kv.group);
-  uint8_t* codes = (kind == 1 ? p.kv.k_codes : p.kv.v_codes) + r * rb;
-  uint8_t* scales = sb ? (kind == 1 ? p.kv.k_scales : p.kv.v_scales) + r * sb : nullptr;
+  const long long rt = kv_row_of(p.kv, page, h, pos % p.kv.page_size);
+  if (rt < 0) return;
+  // a mixed layer appends into whatever tier the page's cell is in (new pages start in the hot tier)
+  const int tier = p.kv.format == kKvMixed ? kv_row_tier(rt) : 0;
+  const long long r = p.kv.format == kKvMixed ? kv_row_index(rt) : rt;
+  const int fmt = p.kv.format == kKvMixed ? kv_tier_format(tier) : p.kv.format;
+  const int group = p.kv.format == kKvMixed ? kv_tier_group(tier, D) : p.kv.group;
+  const int rb = kv_row_bytes(fmt, D), sb = kv_scale_bytes(fmt, D, group);
+  uint8_t* cbase = p.kv.format == kKvMixed ? (kind == 1 ? p.kv.tier_k_codes[tier] : p.kv.tier_v_codes[tier])
+                                           : (kind == 1 ? p.kv.k_codes : p.kv.v_codes);
+  uint8_t* sbase = p.kv.format == kKvMixed ? (kind == 1 ? p.kv.tier_k_scales[tier] : p.kv.tier_v_scales[tier])
+                                           : (kind == 1 ? p.kv.k_scales : p.kv.v_scales);
+  uint8_t* codes = cbase + r * rb;
+  uint8_t* scales = sb ? sbase + r * sb : nullptr;
   // K is stored from its bf16-rounded value so that bf16 KV is a bit copy of what attention would see.
 #pragma unroll
   for (int j = 0; j < VPL; ++j) v[j] = __bfloat162float(__float2bfloat16(v[j]));
-  kv_store_row_warp<VPL>(p.kv.format, p.kv.group, v, codes, scales, lane);
+  kv_store_row_warp<VPL>(fmt, group, v, codes, scales, lane);
 }
 
 }  // namespace

@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(kThreads, 2) paged_attn_mma_kernel(const Paged
   // their conversion into shared memory.  With a narrow KV format the next tile's loads are issued
   // before the current tile's math, so that their latency hides behind the MMAs; bf16 rows would
   // need twice the registers and keep the load-then-convert order.
-  constexpr bool kPrefetch = FORMAT != kKvBf16;
+  constexpr bool kPrefetch = FORMAT != kKvBf16 && FORMAT != kKvMixed;   // (a mixed unit may be a 32-byte bf16 one)
   RawUnit<FORMAT> rawk[kUnits], rawv[kUnits];
 
   auto gather_super = [&](int sb) {
@@ -121,10 +121,13 @@ __global__ void __launch_bounds__(kThreads, 2) paged_attn_mma_kernel(const Paged
       if (key < k_end) {
         const int page = table[key / P];
         // a released or unpublished page (-1) contributes nothing: no row, no scale read
-        if (page >= 0) r = (static_cast<long long>(page) * p.kv.n_kv_heads + kvh) * P + key % P;
+        r = kv_row_of(p.kv, page, kvh, key % P);   // (mixed layers: the cell's tier rides in the top bits)
         if (FORMAT == kKvFp8Row && r >= 0) {
           ks = __half2float(reinterpret_cast<const __half*>(p.kv.k_scales)[r]);
           vs = __half2float(reinterpret_cast<const __half*>(p.kv.v_scales)[r]);
+        } else if (FORMAT == kKvMixed && r >= 0 && kv_row_tier(r) == 1) {
+          ks = __half2float(reinterpret_cast<const __half*>(p.kv.tier_k_scales[1])[kv_row_index(r)]);
+          vs = __half2float(reinterpret_cast<const __half*>(p.kv.tier_v_scales[1])[kv_row_index(r)]);
         } else if (r >= 0) {
           ks = 1.f;
           vs = 1.f;
@@ -143,14 +146,14 @@ __global__ void __launch_bounds__(kThreads, 2) paged_attn_mma_kernel(const Paged
       const int u = it * kThreads + threadIdx.x;
       const long long r = sm.rowidx[off + (u >> 4)];
       rawk[it].clear();
-      if (r >= 0) rawk[it].load(p.kv, p.kv.k_codes, p.kv.k_scales, r, u & 15);
+      if (r >= 0) rawk[it].load_row(p.kv, 0, r, u & 15);
     }
 #pragma unroll
     for (int it = 0; it < kUnits; ++it) {
       const int u = it * kThreads + threadIdx.x;
       const long long r = sm.rowidx[off + (u >> 4)];
       rawv[it].clear();
-      if (r >= 0) rawv[it].load(p.kv, p.kv.v_codes, p.kv.v_scales, r, u & 15);
+      if (r >= 0) rawv[it].load_row(p.kv, 1, r, u & 15);
     }
   };
   // Dequantise to fp16, K and V both as [key][d] rows (16-byte stores, conflict-free with the 8-half row padding).
@@ -356,6 +359,7 @@ cudaError_t paged_attention_mma_split(const PagedAttnParams& p, cudaStream_t str
     case kKvFp8Row: return launch_fmt<kKvFp8Row>(p, stream, pdl);
     case kKvInt8Group: return launch_fmt<kKvInt8Group>(p, stream, pdl);
     case kKvNvfp4: return launch_fmt<kKvNvfp4>(p, stream, pdl);
+    case kKvMixed: return launch_fmt<kKvMixed>(p, stream, pdl);
     default: return cudaErrorNotSupported;
   }
 }

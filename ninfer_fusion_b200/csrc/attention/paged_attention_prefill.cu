@@ -111,12 +111,15 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_prefill_kernel(const P
     if (key < k_end) {
       const int page = table[key / P];
       // a released or unpublished page (-1) contributes nothing: no row, no scale read
-      if (page >= 0) r = (static_cast<long long>(page) * p.kv.n_kv_heads + kvh) * P + key % P;
+      r = kv_row_of(p.kv, page, kvh, key % P);   // (mixed layers: the cell's tier rides in the top bits)
       ks = r >= 0 ? 1.f : 0.f;
       vs = ks;
       if (FORMAT == kKvFp8Row && r >= 0) {
         ks = __half2float(reinterpret_cast<const __half*>(p.kv.k_scales)[r]);
         vs = __half2float(reinterpret_cast<const __half*>(p.kv.v_scales)[r]);
+      } else if (FORMAT == kKvMixed && r >= 0 && kv_row_tier(r) == 1) {
+        ks = __half2float(reinterpret_cast<const __half*>(p.kv.tier_k_scales[1])[kv_row_index(r)]);
+        vs = __half2float(reinterpret_cast<const __half*>(p.kv.tier_v_scales[1])[kv_row_index(r)]);
       }
     }
     sm.rowidx[b][threadIdx.x] = r;
@@ -132,14 +135,14 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_prefill_kernel(const P
       // of a thread are issued before the first conversion, so a tile pays one L2 round trip instead of two (the
       // kernel is latency bound: 8 warps per SM, long scoreboard the top stall).  bf16 units are 32 bytes each, too
       // many registers to hold eight at once beside the 128 accumulator registers: that format loads K, then V.
-      constexpr bool kTogether = FORMAT != kKvBf16;
+      constexpr bool kTogether = FORMAT != kKvBf16 && FORMAT != kKvMixed;
       RawUnit<FORMAT> rk[4], rv[4];
 #pragma unroll
       for (int it = 0; it < 4; ++it) {
         const int u = it * kThreads + threadIdx.x;
         const long long r = sm.rowidx[buf][u >> 4];
         rk[it].clear();
-        if (r >= 0) rk[it].load(p.kv, p.kv.k_codes, p.kv.k_scales, r, u & 15);
+        if (r >= 0) rk[it].load_row(p.kv, 0, r, u & 15);
       }
       auto load_v = [&]() {
 #pragma unroll
@@ -149,8 +152,8 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_prefill_kernel(const P
           const long long r0 = sm.rowidx[buf][2 * jp], r1 = sm.rowidx[buf][2 * jp + 1];
           rv[2 * it].clear();
           rv[2 * it + 1].clear();
-          if (r0 >= 0) rv[2 * it].load(p.kv, p.kv.v_codes, p.kv.v_scales, r0, part);
-          if (r1 >= 0) rv[2 * it + 1].load(p.kv, p.kv.v_codes, p.kv.v_scales, r1, part);
+          if (r0 >= 0) rv[2 * it].load_row(p.kv, 1, r0, part);
+          if (r1 >= 0) rv[2 * it + 1].load_row(p.kv, 1, r1, part);
         }
       };
       if constexpr (kTogether) load_v();
@@ -328,6 +331,7 @@ const char* paged_attention_prefill(const PrefillAttnParams& p, cudaStream_t str
     case kKvFp8Row: e = launch_fmt<kKvFp8Row>(p, stream, pdl); break;
     case kKvInt8Group: e = launch_fmt<kKvInt8Group>(p, stream, pdl); break;
     case kKvNvfp4: e = launch_fmt<kKvNvfp4>(p, stream, pdl); break;
+    case kKvMixed: e = launch_fmt<kKvMixed>(p, stream, pdl); break;
     default: return "paged_attention_prefill: unknown KV format";
   }
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);

@@ -106,6 +106,11 @@ struct GemmArgs {
   // kEpiStore / kEpiSwiglu: consume the gathered residual stream (see GemmGather); flag == nullptr = off
   GemmGather gather;
   GemmConv conv;   // kEpiStore only; state == nullptr = off
+  // Optional: memory the NEXT kernel will stream (its weights).  Once a CTA has issued its own last load it asks
+  // L2 to fetch its share of this range, so that HBM keeps working through this kernel's tail and epilogue and
+  // the next kernel's pipeline fills from L2.  A hint only: nothing waits for it.
+  const void* prefetch = nullptr;
+  int64_t prefetch_bytes = 0;
 };
 
 // Returns nullptr on success, else a static error string.

@@ -109,6 +109,10 @@ struct KernelParams {
   const int* conv_slot;
   __nv_bfloat16* conv_out;
   int conv_C;
+  // L2 prefetch hint for the next kernel's weights: each CTA asks for `pf_per_cta` bytes of [pf_ptr, pf_ptr + pf_bytes)
+  const uint8_t* pf_ptr;
+  long long pf_bytes;
+  int pf_per_cta;
 };
 
 // GELU in the two forms vision towers use: tanh approximation (transformer blocks) and exact erf (merger).
@@ -243,6 +247,15 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
           const uint32_t ph = (j / kStages) & 1;
           for (uint32_t spin = 0; spin < (1u << 20); ++spin)
             if (mbar_try_wait(bar, ph)) break;
+        }
+      } else if (p.pf_per_cta > 0) {
+        // own loads are all in flight: pull this CTA's share of the next kernel's weights into L2
+        const long long off = static_cast<long long>(cta_linear) * p.pf_per_cta;
+        if (off < p.pf_bytes) {
+          const long long n = min(static_cast<long long>(p.pf_per_cta), p.pf_bytes - off) & ~15LL;
+          if (n > 0)
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.pf_ptr + off), "r"(static_cast<uint32_t>(n))
+                         : "memory");
         }
       }
     }
@@ -1394,6 +1407,15 @@ const char* gemm_bf16(const GemmArgs& a) {
   grid.x = a.epi == kEpiSwiglu ? (kp.swiglu_half + 63) / 64 : (kp.N + kTileN - 1) / kTileN;
   grid.y = (kp.T + tn - 1) / tn;
   grid.z = splits;
+  if (a.prefetch != nullptr && a.prefetch_bytes > 0 && (reinterpret_cast<uintptr_t>(a.prefetch) & 15) == 0) {
+    const long long ctas = static_cast<long long>(grid.x) * grid.y * grid.z;
+    long long per = (a.prefetch_bytes + ctas - 1) / ctas;
+    per = (per + 4095) & ~4095LL;                 // whole 4 KB pieces per CTA
+    if (per > (1 << 20)) per = 1 << 20;           // at most 1 MB per CTA
+    kp.pf_ptr = static_cast<const uint8_t*>(a.prefetch);
+    kp.pf_bytes = a.prefetch_bytes;
+    kp.pf_per_cta = static_cast<int>(per);
+  }
   cudaError_t e;
   // prefill-sized problems with more tiles than SMs: persistent kernel, epilogue overlapped with the next main loop
   // (NFB_GEMM_PERSISTENT=0 keeps the one-tile-per-CTA kernel for every size)

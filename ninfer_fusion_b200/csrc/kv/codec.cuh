@@ -57,6 +57,23 @@ __device__ __forceinline__ uint32_t float_to_e2m1(float f) {
   return sign | m;
 }
 
+// ---- where the row of (logical page, kv head, token in page) lives ----
+// Uniform layers: the row index inside the layer's planes.  Mixed layers: the row index inside the cell's tier,
+// with the tier in bits 56.. (kv_row_tier / kv_row_index take it apart).  -1: no page / no cell.
+constexpr long long kRowIndexMask = (1LL << 56) - 1;
+__device__ __forceinline__ long long kv_row_of(const KvLayer& kv, int page, int kvh, int in_page) {
+  if (page < 0) return -1;
+  if (kv.format != kKvMixed)
+    return (static_cast<long long>(page) * kv.n_kv_heads + kvh) * kv.page_size + in_page;
+  const int cell = kv.cell_map[page];
+  if (cell < 0) return -1;
+  const long long slot = cell & ((1 << kCellTierShift) - 1);
+  return ((slot * kv.n_kv_heads + kvh) * kv.page_size + in_page) |
+         (static_cast<long long>(cell >> kCellTierShift) << 56);
+}
+__device__ __forceinline__ int kv_row_tier(long long r) { return static_cast<int>(r >> 56); }
+__device__ __forceinline__ long long kv_row_index(long long r) { return r & kRowIndexMask; }
+
 // ---- dequantise 8 consecutive values [d0, d0+8) of a row into floats ----
 template <int FORMAT>
 __device__ __forceinline__ void kv_load8(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales,

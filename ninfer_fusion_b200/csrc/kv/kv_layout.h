@@ -18,7 +18,14 @@
 
 namespace nfb {
 
-enum KvFormat : int { kKvBf16 = 0, kKvFp8Row = 1, kKvInt8Group = 2, kKvNvfp4 = 3 };
+// kKvMixed: the layer's (64-token block x layer) cells live in one of three tiers, each with its own planes and
+// codec (tier 0 bf16, tier 1 fp8-row, tier 2 nvfp4); `cell_map[page]` says where a logical page's cell is:
+// tier << 28 | slot inside that tier's planes, or -1.  This is the storage side of per-cell precision descent
+// (the reference's contract: src/product/kv_block_descent.h:1-58, narrow sentinels in its block-table entries,
+// src/core/paged_kv_cache.h).
+enum KvFormat : int { kKvBf16 = 0, kKvFp8Row = 1, kKvInt8Group = 2, kKvNvfp4 = 3, kKvMixed = 4 };
+constexpr int kKvTiers = 3;
+constexpr int kCellTierShift = 28;
 
 struct KvLayer {
   uint8_t* k_codes;   // [pages, Hkv, P, row_bytes]
@@ -30,7 +37,16 @@ struct KvLayer {
   int head_dim;
   int format;         // KvFormat
   int group;          // int8 group size (32 or 64); 16 for nvfp4; head_dim for fp8 row
+  // kKvMixed only
+  const int* cell_map = nullptr;             // [logical pages]
+  uint8_t* tier_k_codes[kKvTiers] = {};      // per tier: [slots, Hkv, P, row_bytes(tier format)]
+  uint8_t* tier_v_codes[kKvTiers] = {};
+  uint8_t* tier_k_scales[kKvTiers] = {};
+  uint8_t* tier_v_scales[kKvTiers] = {};
 };
+
+NFB_HD inline int kv_tier_format(int tier) { return tier == 0 ? kKvBf16 : (tier == 1 ? kKvFp8Row : kKvNvfp4); }
+NFB_HD inline int kv_tier_group(int tier, int D) { return tier == 2 ? 16 : D; }
 
 NFB_HD inline int kv_row_bytes(int format, int D) {
   return format == kKvBf16 ? 2 * D : (format == kKvNvfp4 ? D / 2 : D);

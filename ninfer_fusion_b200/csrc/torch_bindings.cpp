@@ -42,6 +42,14 @@ int64_t sm_count() {
   return n;
 }
 
+// Optional L2 prefetch hint: a (contiguous) tensor the next kernel will stream; at most the first 32 MB are asked for.
+void fill_prefetch(nfb::GemmArgs& a, OptT next) {
+  if (!(next.has_value() && next->defined() && next->is_cuda() && next->is_contiguous())) return;
+  a.prefetch = next->data_ptr();
+  const int64_t bytes = next->numel() * next->element_size();
+  a.prefetch_bytes = bytes < (32 << 20) ? bytes : (32 << 20);
+}
+
 // Optional decode conv epilogue (nfb::GemmConv): all four tensors or none.
 void fill_conv(nfb::GemmArgs& a, OptT conv_w, OptT conv_state, OptT conv_slot, OptT conv_out) {
   if (!(conv_state.has_value() && conv_state->defined())) return;
@@ -63,7 +71,7 @@ void fill_conv(nfb::GemmArgs& a, OptT conv_w, OptT conv_state, OptT conv_slot, O
 // out = epilogue(x @ w^T).  epi: 0 store(+bias), 1 residual add, 2 swiglu, 3 split-K partials.
 void gemm_bf16(const Tensor& x, const Tensor& w, OptT out, int64_t epi, OptT resid, OptT bias, OptT partial,
                int64_t splits, OptT status, bool pdl, int64_t act, OptT conv_w, OptT conv_state, OptT conv_slot,
-               OptT conv_out) {
+               OptT conv_out, OptT prefetch) {
   need(x, at::kBFloat16, "x"); need(w, at::kBFloat16, "w");
   need_rows(x, "x"); need_rows(w, "w");
   TORCH_CHECK(x.size(1) == w.size(1), "gemm_bf16: K mismatch");
@@ -100,6 +108,7 @@ void gemm_bf16(const Tensor& x, const Tensor& w, OptT out, int64_t epi, OptT res
   a.status = ptr_or_null<int>(status);
   a.stream = cur_stream(); a.pdl = pdl;
   fill_conv(a, conv_w, conv_state, conv_slot, conv_out);
+  fill_prefetch(a, prefetch);
   chk(nfb::gemm_bf16(a));
 }
 
@@ -180,11 +189,39 @@ void embed_gather(const Tensor& ids, const Tensor& table, const Tensor& out, boo
                         static_cast<int>(table.size(0)), cur_stream(), pdl));
 }
 
+// `tiers` (mixed layers, format 4): CPU int64 tensor of 13 device addresses
+// [cell_map, then per tier 0..2: k_codes, v_codes, k_scales, v_scales] (0 = none); the caller keeps the tensors alive.
 nfb::KvLayer make_kv(const Tensor& k_codes, const Tensor& v_codes, OptT k_scales, OptT v_scales, int64_t page_size,
-                     int64_t n_kv_heads, int64_t head_dim, int64_t format, int64_t group) {
+                     int64_t n_kv_heads, int64_t head_dim, int64_t format, int64_t group, OptT tiers = std::nullopt) {
   need(k_codes, at::kByte, "k_codes"); need(v_codes, at::kByte, "v_codes");
   TORCH_CHECK(k_codes.is_contiguous() && v_codes.is_contiguous());
   nfb::KvLayer kv;
+  if (format == nfb::kKvMixed) {
+    TORCH_CHECK(tiers.has_value() && tiers->defined() && !tiers->is_cuda() && tiers->scalar_type() == at::kLong &&
+                tiers->numel() == 1 + 4 * nfb::kKvTiers && tiers->is_contiguous(), "mixed KV layer needs its tier descriptor");
+    const int64_t* d = tiers->data_ptr<int64_t>();
+    TORCH_CHECK(d[0] != 0, "mixed KV layer without a cell map");
+    kv.cell_map = reinterpret_cast<const int*>(d[0]);
+    for (int t = 0; t < nfb::kKvTiers; ++t) {
+      kv.tier_k_codes[t] = reinterpret_cast<uint8_t*>(d[1 + 4 * t]);
+      kv.tier_v_codes[t] = reinterpret_cast<uint8_t*>(d[2 + 4 * t]);
+      kv.tier_k_scales[t] = reinterpret_cast<uint8_t*>(d[3 + 4 * t]);
+      kv.tier_v_scales[t] = reinterpret_cast<uint8_t*>(d[4 + 4 * t]);
+      TORCH_CHECK(kv.tier_k_codes[t] != nullptr && kv.tier_v_codes[t] != nullptr, "mixed KV layer: a tier has no planes");
+    }
+    TORCH_CHECK(kv.tier_k_scales[1] && kv.tier_v_scales[1] && kv.tier_k_scales[2] && kv.tier_v_scales[2],
+                "mixed KV layer: the fp8 and nvfp4 tiers need scale planes");
+    TORCH_CHECK(head_dim == 256, "mixed KV layers need head_dim 256");
+    kv.k_codes = static_cast<uint8_t*>(k_codes.data_ptr());
+    kv.v_codes = static_cast<uint8_t*>(v_codes.data_ptr());
+    kv.k_scales = kv.v_scales = nullptr;
+    kv.page_size = static_cast<int>(page_size);
+    kv.n_kv_heads = static_cast<int>(n_kv_heads);
+    kv.head_dim = static_cast<int>(head_dim);
+    kv.format = nfb::kKvMixed;
+    kv.group = static_cast<int>(head_dim);
+    return kv;
+  }
   kv.k_codes = static_cast<uint8_t*>(k_codes.data_ptr());
   kv.v_codes = static_cast<uint8_t*>(v_codes.data_ptr());
   kv.k_scales = ptr_or_null<uint8_t>(k_scales);
@@ -217,12 +254,27 @@ void kv_move_rows(const Tensor& block_table, const Tensor& table_row, const Tens
                         static_cast<int>(src_pos.size(1)), cur_stream()));
 }
 
+// Re-encodes cells of a mixed-precision KV layer into another tier.  `anchor`: any device tensor of the layer (device
+// guard); `src_cell` / `dst_cell`: int32 device arrays of tier << 28 | slot.
+void kv_requant(const Tensor& tiers, const Tensor& anchor, const Tensor& src_cell, const Tensor& dst_cell,
+                int64_t page_size, int64_t n_kv_heads, int64_t head_dim) {
+  need(anchor, at::kByte, "anchor"); need(src_cell, at::kInt, "src_cell"); need(dst_cell, at::kInt, "dst_cell");
+  TORCH_CHECK(src_cell.is_contiguous() && dst_cell.is_contiguous() && src_cell.numel() == dst_cell.numel(), "cell lists");
+  c10::cuda::CUDAGuard guard(anchor.device());
+  nfb::KvRequantParams p = {};
+  p.kv = make_kv(anchor, anchor, std::nullopt, std::nullopt, page_size, n_kv_heads, head_dim, nfb::kKvMixed, head_dim, tiers);
+  p.src_cell = static_cast<const int*>(src_cell.data_ptr());
+  p.dst_cell = static_cast<const int*>(dst_cell.data_ptr());
+  p.n_cells = static_cast<int>(src_cell.numel());
+  chk(nfb::kv_requant(p, cur_stream()));
+}
+
 void attn_prep(const Tensor& proj, int64_t q_off, int64_t k_off, int64_t v_off, int64_t n_q_heads,
                int64_t n_kv_heads, int64_t head_dim, OptT q_norm_w, OptT k_norm_w, double eps, bool unit_offset,
                int64_t rot_dim, const Tensor& inv_freq, double attn_factor, const Tensor& rope_pos,
                const Tensor& token_seq, const Tensor& cache_pos, const Tensor& block_table, const Tensor& q_out,
                const Tensor& k_codes, const Tensor& v_codes, OptT k_scales, OptT v_scales, int64_t page_size,
-               int64_t format, int64_t group, bool pdl, bool k_hadamard, OptT k_row_scale) {
+               int64_t format, int64_t group, bool pdl, bool k_hadamard, OptT k_row_scale, OptT tiers) {
   need(proj, at::kBFloat16, "proj"); need_rows(proj, "proj");
   need(inv_freq, at::kFloat, "inv_freq"); need(rope_pos, at::kInt, "rope_pos");
   need(token_seq, at::kInt, "token_seq"); need(cache_pos, at::kInt, "cache_pos");
@@ -254,7 +306,7 @@ void attn_prep(const Tensor& proj, int64_t q_off, int64_t k_off, int64_t v_off, 
   p.table_stride = static_cast<int>(block_table.size(1));
   TORCH_CHECK(q_out.numel() == static_cast<int64_t>(p.T) * n_q_heads * head_dim, "q_out shape");
   p.q_out = static_cast<__nv_bfloat16*>(q_out.data_ptr());
-  p.kv = make_kv(k_codes, v_codes, k_scales, v_scales, page_size, n_kv_heads, head_dim, format, group);
+  p.kv = make_kv(k_codes, v_codes, k_scales, v_scales, page_size, n_kv_heads, head_dim, format, group, tiers);
   p.k_hadamard = k_hadamard ? 1 : 0;
   if (k_row_scale.has_value() && k_row_scale->defined()) {
     need(*k_row_scale, at::kBFloat16, "k_row_scale");
@@ -270,7 +322,7 @@ void paged_attention(const Tensor& q, int64_t n_q_heads, int64_t n_kv_heads, int
                      OptT k_scales, OptT v_scales, int64_t page_size, int64_t format, int64_t group, double sm_scale,
                      int64_t split_keys, int64_t n_splits, const Tensor& part_o, const Tensor& part_ml, OptT gate,
                      const Tensor& out, OptT tree_mask, OptT tree_base, int64_t impl, bool pdl, int64_t window,
-                     OptT sel_blocks, OptT sel_count) {
+                     OptT sel_blocks, OptT sel_count, OptT tiers) {
   need(q, at::kBFloat16, "q"); need(q_seq, at::kInt, "q_seq"); need(q_kv_len, at::kInt, "q_kv_len");
   need(block_table, at::kInt, "block_table"); need(part_o, at::kFloat, "part_o"); need(part_ml, at::kFloat, "part_ml");
   need(out, at::kBFloat16, "out");
@@ -286,7 +338,7 @@ void paged_attention(const Tensor& q, int64_t n_q_heads, int64_t n_kv_heads, int
   p.q_kv_len = static_cast<const int*>(q_kv_len.data_ptr());
   p.block_table = static_cast<const int*>(block_table.data_ptr());
   p.table_stride = static_cast<int>(block_table.size(1));
-  p.kv = make_kv(k_codes, v_codes, k_scales, v_scales, page_size, n_kv_heads, head_dim, format, group);
+  p.kv = make_kv(k_codes, v_codes, k_scales, v_scales, page_size, n_kv_heads, head_dim, format, group, tiers);
   p.sm_scale = static_cast<float>(sm_scale);
   p.split_keys = static_cast<int>(split_keys); p.n_splits = static_cast<int>(n_splits);
   TORCH_CHECK(part_o.numel() >= static_cast<int64_t>(p.Tq) * n_q_heads * n_splits * head_dim, "part_o too small");
@@ -326,7 +378,8 @@ void paged_attention_prefill(const Tensor& q, int64_t n_q_heads, int64_t n_kv_he
                              const Tensor& q_seq, const Tensor& q_kv_len, const Tensor& blk_start,
                              const Tensor& blk_count, const Tensor& block_table, const Tensor& k_codes,
                              const Tensor& v_codes, OptT k_scales, OptT v_scales, int64_t page_size, int64_t format,
-                             int64_t group, double sm_scale, OptT gate, const Tensor& out, bool pdl, int64_t window) {
+                             int64_t group, double sm_scale, OptT gate, const Tensor& out, bool pdl, int64_t window,
+                             OptT tiers) {
   need(q, at::kBFloat16, "q"); need(q_seq, at::kInt, "q_seq"); need(q_kv_len, at::kInt, "q_kv_len");
   need(blk_start, at::kInt, "blk_start"); need(blk_count, at::kInt, "blk_count");
   need(block_table, at::kInt, "block_table"); need(out, at::kBFloat16, "out");
@@ -346,7 +399,7 @@ void paged_attention_prefill(const Tensor& q, int64_t n_q_heads, int64_t n_kv_he
   p.n_blocks = static_cast<int>(blk_start.numel());
   p.block_table = static_cast<const int*>(block_table.data_ptr());
   p.table_stride = static_cast<int>(block_table.size(1));
-  p.kv = make_kv(k_codes, v_codes, k_scales, v_scales, page_size, n_kv_heads, head_dim, format, group);
+  p.kv = make_kv(k_codes, v_codes, k_scales, v_scales, page_size, n_kv_heads, head_dim, format, group, tiers);
   p.sm_scale = static_cast<float>(sm_scale);
   if (gate.has_value() && gate->defined()) {
     need(*gate, at::kBFloat16, "gate"); need_rows(*gate, "gate");
@@ -712,7 +765,7 @@ void tp_sum_norm(int64_t world, int64_t T_cap, int64_t arrivals, int64_t my_base
 void gemm_bf16_rs_ag(const Tensor& x, const Tensor& w, int64_t splits, int64_t world, int64_t rank,
                      at::IntArrayRef peer_bases, int64_t recv_off, int64_t flag_off, int64_t x_off, int64_t ss_off,
                      int64_t xflag_off, int64_t T_cap, int64_t ld_resid, const Tensor& state, int64_t phase,
-                     OptT status, bool pdl) {
+                     OptT status, bool pdl, OptT prefetch) {
   need(x, at::kBFloat16, "x"); need(w, at::kBFloat16, "w"); need_rows(x, "x"); need_rows(w, "w");
   need(state, at::kByte, "state");
   TORCH_CHECK(x.size(1) == w.size(1), "gemm_bf16_rs_ag: K mismatch");
@@ -736,6 +789,7 @@ void gemm_bf16_rs_ag(const Tensor& x, const Tensor& w, int64_t splits, int64_t w
   }
   a.ldo = 2;
   a.status = ptr_or_null<int>(status); a.stream = cur_stream(); a.pdl = pdl;
+  fill_prefetch(a, prefetch);
   chk(nfb::gemm_bf16(a));
 }
 
@@ -744,7 +798,7 @@ void gemm_bf16_rs_ag(const Tensor& x, const Tensor& w, int64_t splits, int64_t w
 void gemm_bf16_gathered(const Tensor& x, const Tensor& w, const Tensor& out, int64_t epi, int64_t splits,
                         int64_t my_base, int64_t ss_off, int64_t xflag_off, int64_t n_features, double eps,
                         const Tensor& state, OptT status, bool pdl, OptT conv_w, OptT conv_state, OptT conv_slot,
-                        OptT conv_out) {
+                        OptT conv_out, OptT prefetch) {
   need(x, at::kBFloat16, "x"); need(w, at::kBFloat16, "w"); need(out, at::kBFloat16, "out");
   need_rows(x, "x"); need_rows(w, "w"); need_rows(out, "out");
   need(state, at::kByte, "state");
@@ -768,6 +822,7 @@ void gemm_bf16_gathered(const Tensor& x, const Tensor& w, const Tensor& out, int
   a.gather.eps = static_cast<float>(eps);
   a.status = ptr_or_null<int>(status); a.stream = cur_stream(); a.pdl = pdl;
   fill_conv(a, conv_w, conv_state, conv_slot, conv_out);
+  fill_prefetch(a, prefetch);
   chk(nfb::gemm_bf16(a));
 }
 
@@ -806,20 +861,21 @@ TORCH_LIBRARY(nfb200, m) {
   m.def("tp_argmax(int world, int rank, int T_cap, Tensor logits, int[] peer_bases, int cand_off, int flag_off, Tensor out, Tensor state, Tensor? status, bool pdl, int phases=3) -> ()", &tp_argmax);
   m.def("tp_state_bytes() -> int", &tp_state_bytes);
   m.def("rs_state_bytes() -> int", &rs_state_bytes);
-  m.def("gemm_bf16_rs_ag(Tensor x, Tensor w, int splits, int world, int rank, int[] peer_bases, int recv_off, int flag_off, int x_off, int ss_off, int xflag_off, int T_cap, int ld_resid, Tensor state, int phase, Tensor? status, bool pdl) -> ()", &gemm_bf16_rs_ag);
-  m.def("gemm_bf16_gathered(Tensor x, Tensor w, Tensor out, int epi, int splits, int my_base, int ss_off, int xflag_off, int n_features, float eps, Tensor state, Tensor? status, bool pdl, Tensor? conv_w=None, Tensor? conv_state=None, Tensor? conv_slot=None, Tensor? conv_out=None) -> ()", &gemm_bf16_gathered);
+  m.def("gemm_bf16_rs_ag(Tensor x, Tensor w, int splits, int world, int rank, int[] peer_bases, int recv_off, int flag_off, int x_off, int ss_off, int xflag_off, int T_cap, int ld_resid, Tensor state, int phase, Tensor? status, bool pdl, Tensor? prefetch=None) -> ()", &gemm_bf16_rs_ag);
+  m.def("gemm_bf16_gathered(Tensor x, Tensor w, Tensor out, int epi, int splits, int my_base, int ss_off, int xflag_off, int n_features, float eps, Tensor state, Tensor? status, bool pdl, Tensor? conv_w=None, Tensor? conv_state=None, Tensor? conv_slot=None, Tensor? conv_out=None, Tensor? prefetch=None) -> ()", &gemm_bf16_gathered);
   m.def("tp_gather_norm(Tensor x, Tensor norm_w, Tensor normed, int my_base, int xflag_off, float eps, bool unit_offset, Tensor state, Tensor? status, bool pdl) -> ()", &tp_gather_norm);
   m.def("gemm_bf16_push_all(Tensor x, Tensor w, int splits, int world, int rank, int[] peer_bases, int recv_off, int flag_off, int T_cap, Tensor state, Tensor? status, bool pdl) -> ()", &gemm_bf16_push_all);
   m.def("tp_sum_norm(int world, int T_cap, int arrivals, int my_base, int recv_off, int flag_off, Tensor x, Tensor? norm_w, Tensor? normed, float eps, bool unit_offset, Tensor state, Tensor? status, bool pdl) -> ()", &tp_sum_norm);
-  m.def("gemm_bf16(Tensor x, Tensor w, Tensor? out, int epi, Tensor? resid, Tensor? bias, Tensor? partial, int splits, Tensor? status, bool pdl, int act=0, Tensor? conv_w=None, Tensor? conv_state=None, Tensor? conv_slot=None, Tensor? conv_out=None) -> ()", &gemm_bf16);
+  m.def("gemm_bf16(Tensor x, Tensor w, Tensor? out, int epi, Tensor? resid, Tensor? bias, Tensor? partial, int splits, Tensor? status, bool pdl, int act=0, Tensor? conv_w=None, Tensor? conv_state=None, Tensor? conv_slot=None, Tensor? conv_out=None, Tensor? prefetch=None) -> ()", &gemm_bf16);
   m.def("gemm_trace(bool enable, int n_ctas) -> Tensor", &gemm_trace);
   m.def("gemm_timeline(int mode) -> (int, Tensor)", &gemm_timeline);
   m.def("gemm_pick_splits(int T, int N, int K, int epi) -> int", &gemm_pick_splits);
   m.def("add_rmsnorm(Tensor? partial, int splits, Tensor? delta, Tensor? resid_in, Tensor? resid_out, Tensor? norm_w, Tensor? normed, int T, int N, float eps, bool unit_offset, bool pdl, Tensor? q_codes=None, Tensor? q_sf=None) -> ()", &add_rmsnorm);
   m.def("embed_gather(Tensor ids, Tensor table, Tensor out, bool pdl) -> ()", &embed_gather);
-  m.def("attn_prep(Tensor proj, int q_off, int k_off, int v_off, int n_q_heads, int n_kv_heads, int head_dim, Tensor? q_norm_w, Tensor? k_norm_w, float eps, bool unit_offset, int rot_dim, Tensor inv_freq, float attn_factor, Tensor rope_pos, Tensor token_seq, Tensor cache_pos, Tensor block_table, Tensor q_out, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, bool pdl, bool k_hadamard=False, Tensor? k_row_scale=None) -> ()", &attn_prep);
-  m.def("paged_attention(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, int split_keys, int n_splits, Tensor part_o, Tensor part_ml, Tensor? gate, Tensor out, Tensor? tree_mask, Tensor? tree_base, int impl, bool pdl, int window=0, Tensor? sel_blocks=None, Tensor? sel_count=None) -> ()", &paged_attention);
-  m.def("paged_attention_prefill(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor blk_start, Tensor blk_count, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, Tensor? gate, Tensor out, bool pdl, int window=0) -> ()", &paged_attention_prefill);
+  m.def("attn_prep(Tensor proj, int q_off, int k_off, int v_off, int n_q_heads, int n_kv_heads, int head_dim, Tensor? q_norm_w, Tensor? k_norm_w, float eps, bool unit_offset, int rot_dim, Tensor inv_freq, float attn_factor, Tensor rope_pos, Tensor token_seq, Tensor cache_pos, Tensor block_table, Tensor q_out, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, bool pdl, bool k_hadamard=False, Tensor? k_row_scale=None, Tensor? tiers=None) -> ()", &attn_prep);
+  m.def("paged_attention(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, int split_keys, int n_splits, Tensor part_o, Tensor part_ml, Tensor? gate, Tensor out, Tensor? tree_mask, Tensor? tree_base, int impl, bool pdl, int window=0, Tensor? sel_blocks=None, Tensor? sel_count=None, Tensor? tiers=None) -> ()", &paged_attention);
+  m.def("paged_attention_prefill(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor blk_start, Tensor blk_count, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, Tensor? gate, Tensor out, bool pdl, int window=0, Tensor? tiers=None) -> ()", &paged_attention_prefill);
+  m.def("kv_requant(Tensor tiers, Tensor anchor, Tensor src_cell, Tensor dst_cell, int page_size, int n_kv_heads, int head_dim) -> ()", &kv_requant);
   m.def("prefill_attn_block_tokens(int n_q_heads, int n_kv_heads) -> int", &prefill_attn_block_tokens);
   m.def("causal_conv1d_silu(Tensor x, int c_off, int C, Tensor w, Tensor cu_seqlens, Tensor token_seq, Tensor state_slot, Tensor conv_state, Tensor out, bool update_state, bool one_token_per_seq, bool pdl, Tensor? seq_end=None, bool state_only=False, Tensor? parent=None, Tensor? last_token=None) -> ()", &causal_conv1d_silu);
   m.def("gdn_recurrent(Tensor qkv, int q_off, int k_off, int v_off, Tensor proj, int z_off, int a_off, int b_off, int n_qk_heads, int n_v_heads, Tensor A_log, Tensor dt_bias, Tensor norm_w, float eps, Tensor cu_seqlens, Tensor state_slot, Tensor state, bool write_state, Tensor out, bool pdl, Tensor? seq_end=None, Tensor? commit=None, Tensor? chunk_ws=None) -> ()", &gdn_recurrent);

@@ -334,13 +334,21 @@ def acquire_source(source, allow_files: bool = False, max_bytes: int = 256 * 102
 
 
 def prepare_messages(tokenizer, rendered_text: str, messages: Sequence[dict], processor: "MediaProcessor",
-                     allow_files: bool = False, video_fps: float = 24.0) -> Optional[PreparedPrompt]:
-    """PreparedPrompt for chat messages with media parts, or None when there are none."""
+                     allow_files: bool = False, video_fps: float = 24.0, pool=None,
+                     checkpoint=None) -> Optional[PreparedPrompt]:
+    """PreparedPrompt for chat messages with media parts, or None when there are none.  With a
+    runtime.worker_pool.HostWorkerPool the items are decoded and resized on its threads (bounded queue;
+    `checkpoint` lets a cancelled request stop waiting for a slot)."""
     refs = collect_media(messages)
     if not refs:
         return None
-    items = []
-    for modality, src in refs:
+
+    def one(modality, src):
         src = acquire_source(src, allow_files, processor.opt.max_source_bytes)
-        items.append(processor.image(src) if modality == "image" else processor.video(src, fps=video_fps))
+        return processor.image(src) if modality == "image" else processor.video(src, fps=video_fps)
+
+    if pool is not None and len(refs) > 1:
+        items = pool.map([(lambda m=m, s=s: one(m, s)) for m, s in refs], checkpoint)
+    else:
+        items = [one(m, s) for m, s in refs]
     return prepare_prompt(tokenizer, rendered_text, items)

@@ -251,6 +251,9 @@ class HybridModel:
         # the separate conv kernel both on one GPU (13.78 vs 13.56 ms per round) and on a 1/8 shard (4.73 vs 4.37 ms),
         # so it is off unless asked for.
         self._fuse_conv_env = os.environ.get("NFB_FUSE_CONV")
+        # decode: every GEMM asks L2 for the head of the NEXT GEMM's weights once its own loads are in flight
+        # (NFB_L2_PREFETCH=0 switches the hint off)
+        self.l2_prefetch = os.environ.get("NFB_L2_PREFETCH", "1") != "0"
         self.attn_impl = 0  # 0 = pick, 1 = SIMT, 2 = tensor-core split-KV attention
         self.comm = None  # tensor-parallel communicator (parallel.tp), None on one GPU
         # (norm weight, normed buffer, T) while the residual stream of the last row-parallel GEMM is still being
@@ -328,7 +331,13 @@ class HybridModel:
             self.ops.quant_act_fp8(x, xc, scale, self.pdl)
             self.ops.gemm_quant(1, xc, scale, w.codes, w.scale, 1.0, out, epi, resid, splits, self.status.tensor, self.pdl)
 
-    def _gemm(self, x, w, out, epi=EPI_STORE, resid=None, conv=None):
+    def _pf(self, T: int, w_next):
+        """The tensor a decode-sized GEMM should prefetch towards L2, or None."""
+        if self.l2_prefetch and T <= 64 and isinstance(w_next, torch.Tensor) and w_next.is_cuda and w_next.is_contiguous():
+            return w_next
+        return None
+
+    def _gemm(self, x, w, out, epi=EPI_STORE, resid=None, conv=None, prefetch=None):
         if conv is not None and not (isinstance(w, torch.Tensor) and epi == EPI_STORE):
             raise ValueError("the conv epilogue exists for bf16 weights with the store epilogue only")
         if isinstance(w, QuantWeight):
@@ -364,7 +373,7 @@ class HybridModel:
         # in-cluster split-K when the output tiles alone cannot fill the GPU (decode, sharded weights)
         splits = int(self.ops.gemm_pick_splits(x.shape[0], w.shape[0], w.shape[1], epi)) if self.cluster_splitk else 1
         self.ops.gemm_bf16(x, w, out, epi, resid, None, None, splits, self.status.tensor, self.pdl, 0,
-                           *(conv or (None, None, None, None)))
+                           *(conv or (None, None, None, None)), self._pf(x.shape[0], prefetch))
 
     def _materialize_normed(self, ws: Workspace) -> None:
         """Writes the normalised copy that a pending gather (see `_gathered`) has left out."""
@@ -373,28 +382,28 @@ class HybridModel:
             self._gathered = None
             self.comm.gather_norm(self, ws, T, norm_w, normed_out)
 
-    def _gemm_normed(self, ws: Workspace, T: int, w, out, epi=EPI_STORE, conv=None):
+    def _gemm_normed(self, ws: Workspace, T: int, w, out, epi=EPI_STORE, conv=None, prefetch=None):
         """out = epilogue(normed residual @ w^T): the consumer of the last `_gemm_to_residual`.  `conv` (bf16
         weights only) fuses the decode conv + SiLU + history roll of the leading output columns into the epilogue."""
         if self._gathered is not None:
             if self.comm.can_gather(w):
-                self.comm.gemm_gathered(self, ws, T, w, out, epi, conv)
+                self.comm.gemm_gathered(self, ws, T, w, out, epi, conv, self._pf(T, prefetch))
                 return
             self._materialize_normed(ws)
-        self._gemm(ws.normed[:T], w, out, epi, conv=conv)
+        self._gemm(ws.normed[:T], w, out, epi, conv=conv, prefetch=prefetch)
 
-    def _gemm_to_residual(self, ws: Workspace, a, w, T: int, norm_w, normed_out):
+    def _gemm_to_residual(self, ws: Workspace, a, w, T: int, norm_w, normed_out, prefetch=None):
         """x += a @ w^T ; normed_out = rmsnorm(x) * (1 + norm_w).  x is ws.x[:T] (in place)."""
         cfg, ops = self.cfg, self.ops
         x = ws.x[:T]
         N, K = w.shape
         if self.comm is not None:
             # row-parallel: partial sums live on every rank; the communicator reduces them
-            self.comm.gemm_reduce_residual(self, ws, a, w, T, norm_w, normed_out)
+            self.comm.gemm_reduce_residual(self, ws, a, w, T, norm_w, normed_out, self._pf(T, prefetch))
             return
         if self.cluster_splitk:
             # split-K inside a thread-block cluster (DSMEM reduction), residual add in the epilogue
-            self._gemm(a, w, x, EPI_RESIDUAL, x)
+            self._gemm(a, w, x, EPI_RESIDUAL, x, prefetch=prefetch)
             self._add_rmsnorm(None, 0, None, x, None, norm_w, normed_out, T, N)
             return
         splits = int(ops.gemm_pick_splits(T, N, K, EPI_PARTIAL)) if T <= 256 else 1
@@ -412,15 +421,16 @@ class HybridModel:
         D = cfg.head_dim
         w_in = self.w[f"{prefix}/attn/in_proj"]
         proj = ws.proj[:T, : w_in.shape[0]]
-        self._gemm_normed(ws, T, w_in, proj)
+        self._gemm_normed(ws, T, w_in, proj, prefetch=self.w[f"{prefix}/attn/o_proj"])
         q_dim, kv_dim = g.n_q_heads * D, g.n_kv_heads * D
         planes = kv.layers[kv_index]
+        tiers = getattr(planes, "desc", None)   # mixed-precision layer: addresses of its tiers and of its cell map
         q = ws.q[:T]
         ops.attn_prep(proj, 0, q_dim, q_dim + kv_dim + q_dim, g.n_q_heads, g.n_kv_heads, D,
                       self.w[f"{prefix}/attn/q_norm"], self.w[f"{prefix}/attn/k_norm"], cfg.rms_eps, True,
                       cfg.rot_dim, self.inv_freq, self.rope_factor, b.rope_pos, b.table_row, b.cache_pos, kv.table, q,
                       planes.k_codes, planes.v_codes, planes.k_scales, planes.v_scales, kv.page_size, planes.fmt,
-                      planes.group, self.pdl, planes.hadamard, self.k_row_scale.get(layer))
+                      planes.group, self.pdl, planes.hadamard, self.k_row_scale.get(layer), tiers)
         gate = proj[:, q_dim + kv_dim: q_dim + kv_dim + q_dim]
         out = ws.mix_attn[:T]
         if (not b.one_token_per_seq and b.qblk_start is not None and D == 256 and self.attn_impl != 1
@@ -429,7 +439,7 @@ class HybridModel:
             ops.paged_attention_prefill(q, g.n_q_heads, g.n_kv_heads, D, b.table_row, b.kv_len, b.qblk_start,
                                         b.qblk_count, kv.table, planes.k_codes, planes.v_codes, planes.k_scales,
                                         planes.v_scales, kv.page_size, planes.fmt, planes.group, self.sm_scale, gate,
-                                        out, self.pdl)
+                                        out, self.pdl, 0, tiers)
             return out, self.w[f"{prefix}/attn/o_proj"]
         split, n_splits = pick_attention_split(b.max_kv_len, T * g.n_kv_heads, max_splits=ws.max_splits_attn)
         chunk = max(1, ws.part_rows // n_splits)
@@ -439,7 +449,8 @@ class HybridModel:
                                 planes.k_codes, planes.v_codes, planes.k_scales, planes.v_scales, kv.page_size,
                                 planes.fmt, planes.group, self.sm_scale, split, n_splits, ws.part_o, ws.part_ml,
                                 gate[t0:t1], out[t0:t1], None if b.tree_mask is None else b.tree_mask[t0:t1],
-                                None if b.tree_base is None else b.tree_base[t0:t1], self.attn_impl, self.pdl)
+                                None if b.tree_base is None else b.tree_base[t0:t1], self.attn_impl, self.pdl, 0, None,
+                                None, tiers)
         return out, self.w[f"{prefix}/attn/o_proj"]
 
     def _gdn_layer(self, ws: Workspace, b: StepBatch, st: GdnStatePool, layer: int, T: int, prefix: str,
@@ -459,7 +470,7 @@ class HybridModel:
             self._gemm_normed(ws, T, w_in, proj, EPI_STORE,
                               (self.w[f"{prefix}/gdn/conv_w"], st.conv[gi], b.state_slot, conv))
         else:
-            self._gemm_normed(ws, T, w_in, proj)
+            self._gemm_normed(ws, T, w_in, proj, prefetch=self.w[f"{prefix}/gdn/out_proj"])
             ops.causal_conv1d_silu(proj, 0, C, self.w[f"{prefix}/gdn/conv_w"], b.cu_seqlens, b.token_seq, b.state_slot,
                                    st.conv[gi], conv, write_state, decode, self.pdl, None, False, b.tree_parent, None)
         qk = g.gdn_qk_dim
@@ -480,12 +491,12 @@ class HybridModel:
                           write_state, out, self.pdl, None, b.tree_commit, chunk_ws)
         return out, self.w[f"{prefix}/gdn/out_proj"]
 
-    def _mlp(self, ws: Workspace, T: int, prefix: str, next_norm_w, normed_out):
+    def _mlp(self, ws: Workspace, T: int, prefix: str, next_norm_w, normed_out, next_w=None):
         w_gu = self.w[f"{prefix}/mlp/gate_up"]
         act = ws.act[:T, : w_gu.shape[0] // 2]
-        self._gemm_normed(ws, T, w_gu, act, EPI_SWIGLU)
         w_down = self.w[f"{prefix}/mlp/down"]
-        self._gemm_to_residual(ws, ws.act[:T, : w_down.shape[1]], w_down, T, next_norm_w, normed_out)
+        self._gemm_normed(ws, T, w_gu, act, EPI_SWIGLU, prefetch=w_down)
+        self._gemm_to_residual(ws, ws.act[:T, : w_down.shape[1]], w_down, T, next_norm_w, normed_out, prefetch=next_w)
 
     # ------------------------------------------------------------------ forward
     def fold_gdn_tree(self, ws: Workspace, b: StepBatch, st: GdnStatePool, rec: GdnRecords, accepted: torch.Tensor,
@@ -589,7 +600,8 @@ class HybridModel:
                 mix, w_out = self._attn_layer(ws, b, kv, layer, T, p, self._attn_idx[layer])
             else:
                 mix, w_out = self._gdn_layer(ws, b, st, layer, T, p, write_state, rec)
-            self._gemm_to_residual(ws, mix, w_out, T, self.w[f"{p}/post_norm"], ws.normed[:T])
+            self._gemm_to_residual(ws, mix, w_out, T, self.w[f"{p}/post_norm"], ws.normed[:T],
+                                   prefetch=self.w.get(f"{p}/mlp/gate_up"))
             if layer + 1 < cfg.n_layers:
                 # at a stage boundary the next layer's norm lives on the next rank, which recomputes it from the
                 # residual stream: any norm weight of this rank keeps the fused kernel's shape
@@ -597,7 +609,12 @@ class HybridModel:
             else:
                 nxt = self.w[f"{self.prefix}/final_norm"]
             if cfg.moe is None:
-                self._mlp(ws, T, p, nxt, ws.normed[:T])
+                if layer + 1 < cfg.n_layers:
+                    kind = "attn" if cfg.is_full_attn(layer + 1) else "gdn"
+                    next_w = self.w.get(f"{self.prefix}/layers/{layer + 1}/{kind}/in_proj")
+                else:
+                    next_w = self.w.get(f"{self.prefix}/lm_head")
+                self._mlp(ws, T, p, nxt, ws.normed[:T], next_w)
             else:
                 self._materialize_normed(ws)
                 if self.moe is None or self.moe.max_tokens < ws.max_tokens:

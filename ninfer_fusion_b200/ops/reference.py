@@ -104,9 +104,10 @@ def e2m1_round(x: torch.Tensor) -> torch.Tensor:
     return torch.sign(x) * E2M1_GRID.to(x.device)[idx]
 
 
-def kv_quant_dequant(x: torch.Tensor, fmt: int, group: int = 64) -> torch.Tensor:
-    """What an attention kernel sees after a row [.., D] went through the cache codec."""
-    x = bf16_round(x.float())
+def kv_quant_dequant(x: torch.Tensor, fmt: int, group: int = 64, bf16_input: bool = True) -> torch.Tensor:
+    """What an attention kernel sees after a row [.., D] went through the cache codec.  `bf16_input=False`: the row
+    is already the fp32 decode of another codec (a cell re-encoded from one tier to the next) and is taken as is."""
+    x = bf16_round(x.float()) if bf16_input else x.float()
     if fmt == KV_BF16:
         return x
     if fmt == KV_FP8_ROW:

@@ -38,7 +38,7 @@ import torch.distributed as dist
 
 from ..runtime.engine import RequestError, ResourceError
 
-OP_STOP, OP_CAN_ADMIT, OP_OPEN, OP_CLOSE, OP_PREFILL, OP_DECODE, OP_CHECKPOINT, OP_PING = range(8)
+OP_STOP, OP_CAN_ADMIT, OP_OPEN, OP_CLOSE, OP_PREFILL, OP_DECODE, OP_CHECKPOINT, OP_PING, OP_DESCENT = range(9)
 _DESC_WORDS = 72   # op, count, then up to 64 lane ids / scalar arguments
 _KINDS = ("turn", "endpoint", "replay", "anchor", "shared")
 
@@ -189,6 +189,13 @@ class LeaderProgram:
         self.ch.bcast_object(session)
         return self.inner.checkpoint(lane, session, kind)
 
+    def kv_descent_step(self) -> int:
+        """Per-cell KV precision descent, on every rank in the same step (each rank re-encodes its own heads)."""
+        if getattr(self.inner, "descent", None) is None:
+            return 0     # not configured: nothing to mirror (every rank has the same configuration)
+        self.ch.send_desc(OP_DESCENT)
+        return self.inner.kv_descent_step()
+
     def ping(self) -> bool:
         """Round trip over the control channel: every rank is in its loop and answers."""
         self.ch.send_desc(OP_PING)
@@ -242,6 +249,8 @@ def follower_loop(inner, channel: RankChannel, on_step: Optional[Callable[[int],
                 pass   # the leader hit the same refusal and closes the lane with its next step
         elif op == OP_DECODE:
             inner.decode_round([inner.lanes[int(i)] for i in a])
+        elif op == OP_DESCENT:
+            inner.kv_descent_step()
         elif op == OP_CHECKPOINT:
             session = channel.bcast_object()
             inner.checkpoint(inner.lanes[int(a[0])], session, _KINDS[int(a[1])])

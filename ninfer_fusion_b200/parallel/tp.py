@@ -246,12 +246,13 @@ class TensorParallel:
         return weights
 
     # ------------------------------------------------------------------ collectives
-    def _rs_ag(self, model, a, w, T: int, phase: int = 0) -> None:
+    def _rs_ag(self, model, a, w, T: int, phase: int = 0, prefetch=None) -> None:
         ops = model.ops
         splits = int(ops.gemm_pick_splits(T, w.shape[0], w.shape[1], 6))
         ops.gemm_bf16_rs_ag(a, w, splits, self.world, self.rank, self.peer_bases, self.off["rs_recv"],
                             self.off["rs_flag"], self.off["x"], self.off["rs_ss"], self.off["x_flag"],
-                            self.one_shot_rows, self.cfg.hidden, self.rs_state, phase, model.status.tensor, model.pdl)
+                            self.one_shot_rows, self.cfg.hidden, self.rs_state, phase, model.status.tensor, model.pdl,
+                            prefetch)
 
     def gather_norm(self, model, ws, T: int, norm_w, normed_out) -> None:
         """normed_out = rmsnorm(x) * (1 + norm_w) once every rank's residual tiles of the last `_rs_ag` are here."""
@@ -261,16 +262,16 @@ class TensorParallel:
     def can_gather(self, w) -> bool:
         return self.fold and isinstance(w, torch.Tensor) and w.dtype == torch.bfloat16 and w.shape[1] == self.cfg.hidden
 
-    def gemm_gathered(self, model, ws, T: int, w, out, epi: int, conv=None) -> None:
+    def gemm_gathered(self, model, ws, T: int, w, out, epi: int, conv=None, prefetch=None) -> None:
         """Column-parallel GEMM straight on the gathered residual stream (waits for it, RMS norm as a row scale).
         `conv` = (conv_w, conv_state, slot per token, conv_out): decode conv + SiLU + history roll in the epilogue."""
         ops = model.ops
         splits = int(ops.gemm_pick_splits(T, w.shape[0], w.shape[1], epi))
         ops.gemm_bf16_gathered(ws.x[:T], w, out, epi, splits, self.peer_bases[self.rank], self.off["rs_ss"],
                                self.off["x_flag"], self.cfg.hidden, self.cfg.rms_eps, self.rs_state,
-                               model.status.tensor, model.pdl, *(conv or (None, None, None, None)))
+                               model.status.tensor, model.pdl, *(conv or (None, None, None, None)), prefetch)
 
-    def gemm_reduce_residual(self, model, ws, a, w, T: int, norm_w, normed_out) -> None:
+    def gemm_reduce_residual(self, model, ws, a, w, T: int, norm_w, normed_out, prefetch=None) -> None:
         """x += sum_ranks(a_r @ w_r^T); normed_out = rmsnorm(x) * (1 + norm_w)."""
         cfg, ops = self.cfg, model.ops
         N = cfg.hidden
@@ -280,7 +281,7 @@ class TensorParallel:
         if self.mode == "fused" and T <= self.one_shot_rows and isinstance(w, torch.Tensor):
             # decode sizes: reduce-scatter, owner-side reduction and all-gather inside the GEMM; the norm is left to
             # the consumer (a gathered GEMM when the norms are folded, else tp_gather_norm)
-            self._rs_ag(model, a, w, T)
+            self._rs_ag(model, a, w, T, prefetch=prefetch)
             if self.fold:
                 model._gathered = (norm_w, normed_out, T)
             else:

@@ -89,6 +89,12 @@ class GenerationHandle:
         self.t_submit = time.perf_counter()
         self.t_first: Optional[float] = None
         self.t_done: Optional[float] = None
+        # filled by the worker: when the request got its lane, what it reused, how it was served
+        self.t_admit: Optional[float] = None
+        self.cached_tokens = 0          # prompt tokens restored from a retained frontier
+        self.reuse_kind = ""            # kind of that frontier ("" = started at the root)
+        self.prefill_chunks = 0
+        self.decode_rounds = 0
         self._cancel = threading.Event()
 
     def cancel(self) -> None:
@@ -378,9 +384,12 @@ class Engine:
                 req.lane = (self.program.open(req.prompt, req.opts.sampling, session=req.opts.session)
                             if req.opts.media is None else
                             self.program.open(req.prompt, req.opts.sampling, session=req.opts.session, media=req.opts.media))
+                req.handle.t_admit = time.perf_counter()
                 if req.lane.reused:
                     self.stats.prefix_hits += 1
                     self.stats.prefix_tokens_reused += req.lane.reused
+                    req.handle.cached_tokens = int(req.lane.reused)
+                    req.handle.reuse_kind = getattr(req.lane, "reuse_kind", "") or "turn"
                 req.state = "prefill"
                 self._active.append(req)
             except RequestError as e:
@@ -437,6 +446,7 @@ class Engine:
                             budget = min(budget, e - n_before)     # stop exactly at the boundary
                     with trace.span("engine", "prefill_chunk", budget=int(budget), cached=int(n_before)):
                         first = self.program.prefill_step(req.lane, budget)
+                    req.handle.prefill_chunks += 1
                     self.stats.prompt_tokens += req.lane.n_cached - n_before
                     if first is None and req.lane.n_cached == edge and n_before < edge:
                         self.program.checkpoint(req.lane, "shared", "shared")   # any session may start from here
@@ -468,6 +478,11 @@ class Engine:
             self.stats.decode_s += dt
             self.stats.decode_rounds += 1
             self.governor.observe(dt * 1e3, did_prefill)
+            descend = getattr(self.program, "kv_descent_step", None)
+            if descend is not None:
+                descend()   # per-cell KV precision descent between rounds (a no-op unless the program is set up for it)
+            for r in ready:
+                r.handle.decode_rounds += 1
             for r, t in zip(ready, toks):
                 # a speculative program returns several tokens per lane and round; each one goes through the
                 # same commit-before-publish gate, and nothing after a stop / budget hit becomes visible

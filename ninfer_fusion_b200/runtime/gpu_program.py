@@ -26,7 +26,11 @@ class GpuProgram(ProgramBase):
                  max_context: int = 8192, kv_format="bf16", page_size: int = 64, prefill_chunk: int = 2048,
                  use_graph: bool = True, pdl: bool = True, int8_group: int = 64, kv_pages: Optional[int] = None,
                  shard: Optional[ShardGeometry] = None, comm=None, penalties: bool = False,
-                 checkpoint_slots: Optional[int] = None, weight_budget_bytes: Optional[int] = None):
+                 checkpoint_slots: Optional[int] = None, weight_budget_bytes: Optional[int] = None,
+                 mixed_capacity: Optional[Sequence[int]] = None, mixed_hot_tier: int = 0, descent=None):
+        """`kv_format` "mixed" (or a per-layer list with "mixed" entries): those layers keep their cells in three
+        precision tiers; `mixed_capacity` = cells per tier and layer, `descent` = a kv.descent.DescentConfig that
+        `kv_descent_step` applies between rounds (None = cells only move when `kv.descend` is called by hand)."""
         super().__init__(cfg, max_lanes, max_context)
         if weight_budget_bytes is not None:
             from .weight_offload import OffloadedWeights
@@ -45,7 +49,10 @@ class GpuProgram(ProgramBase):
         pages_per_row = (max_context + page_size - 1) // page_size
         n_pages = kv_pages if kv_pages is not None else max_lanes * pages_per_row
         self.kv = PagedKvCache(cfg, n_pages, page_size, max_lanes, pages_per_row, device, formats=kv_format,
-                               int8_group=int8_group, n_kv_heads=g.n_kv_heads)
+                               int8_group=int8_group, n_kv_heads=g.n_kv_heads, mixed_capacity=mixed_capacity,
+                               mixed_hot_tier=mixed_hot_tier)
+        self.descent = descent
+        self.descent_stats = {"passes": 0, "cells_moved": 0}
         self.states = GdnStatePool(cfg, max_lanes + self.checkpoint_slots, device, n_qk_heads=g.gdn_qk_heads,
                                    n_v_heads=g.gdn_v_heads)
         self._ckpt_slots_free = self.checkpoint_slots
@@ -121,7 +128,55 @@ class GpuProgram(ProgramBase):
         return (pages, slot)
 
     def _kv_room(self, n_tokens: int) -> bool:
-        return self.kv.pool.free_pages >= (n_tokens + self.kv.page_size - 1) // self.kv.page_size
+        need = (n_tokens + self.kv.page_size - 1) // self.kv.page_size
+        if self.kv.pool.free_pages < need:
+            return False
+        # mixed layers: every new page needs a cell in the hot tier of each of them
+        return all(len(l.free[l.hot_tier]) >= need for l in self.kv.mixed)
+
+    # ------------------------------------------------------------------ per-cell precision descent
+    def kv_descent_step(self) -> int:
+        """One descent pass over the live lanes' cells (kv/descent.py decides which, one rung per cell and pass,
+        oldest first, under the configured budgets); the re-encoding runs on the device.  Called by the engine
+        between rounds.  Returns the number of cells moved."""
+        if self.descent is None or not self.kv.mixed or not self.lanes:
+            return 0
+        from ..kv.descent import CellMap, plan_descent_pass
+        mixed_idx = [i for i, l in enumerate(self.kv.layers) if l in self.kv.mixed]
+        cells = CellMap(self.kv.page_size, len(mixed_idx))
+        page_of = {}
+        for lane in self.lanes.values():
+            pages = self.kv.row_pages.get(lane.row, [])
+            cells.frontier[lane.lane_id] = lane.n_cached
+            for b, pg in enumerate(pages[: (lane.n_cached + self.kv.page_size - 1) // self.kv.page_size]):
+                if pg < 0:
+                    continue
+                for j, li in enumerate(mixed_idx):
+                    t = self.kv.layers[li].tier_of(pg)
+                    if t >= 0:
+                        cells.rungs[(lane.lane_id, j, b)] = t
+                        page_of[(lane.lane_id, j, b)] = pg
+        moves = plan_descent_pass(cells, self.descent, self.model.g.n_kv_heads, self.cfg.head_dim)
+        by_target: Dict[tuple, List[int]] = {}
+        for m in moves:
+            if m.dst == "cold":
+                continue
+            by_target.setdefault((mixed_idx[m.layer], self.descent.ladder.index(m.dst)), []).append(page_of[(m.seq, m.layer, m.block)])
+        moved = 0
+        for (li, tier), pages in by_target.items():
+            moved += self.kv.descend(li, sorted(set(pages)), tier)
+        if moved:
+            self.descent_stats["passes"] += 1
+            self.descent_stats["cells_moved"] += moved
+        return moved
+
+    def census(self) -> dict:
+        c = super().census()
+        if self.kv.mixed:
+            c["kv_tiers"] = self.kv.tier_census()
+            c["kv_bytes_in_use"] = self.kv.bytes_in_use()
+            c["kv_descent"] = dict(self.descent_stats)
+        return c
 
     # ------------------------------------------------------------------ sampling
     def _fill_sampling(self, lanes: Sequence[Lane]) -> bool:

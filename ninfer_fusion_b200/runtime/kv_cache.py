@@ -54,6 +54,97 @@ class KvLayerPlanes:
         return n
 
 
+KV_MIXED = 4                                   # csrc/kv/kv_layout.h kKvMixed
+TIER_FORMATS = (KV_BF16, KV_FP8_ROW, KV_NVFP4)   # tier 0, 1, 2 of a mixed layer
+TIER_NAMES = ("bf16", "fp8", "nvfp4")
+CELL_TIER_SHIFT = 28
+
+
+class MixedKvPlanes(KvLayerPlanes):
+    """A full-attention layer whose (64-token block x layer) cells live in one of three tiers of falling precision:
+    tier 0 bf16, tier 1 fp8-row, tier 2 nvfp4.  Every tier has its own planes and slot allocator; `cell_map[page]`
+    (tier << 28 | slot, -1 = none) says where the cell of a logical page is.  New pages start in `hot_tier`; cells
+    descend one rung at a time (`PagedKvCache.descend`), which frees a wide slot for a narrow one: that is where
+    per-cell precision descent saves device memory.  The attention and append kernels follow the map (format 4).
+    Reference: the cell contract of src/product/kv_block_descent.h:1-58 and the narrow sentinels in the block-table
+    entries of src/core/paged_kv_cache.h."""
+
+    def __init__(self, n_pages: int, n_kv_heads: int, page_size: int, head_dim: int, device, capacity, hot_tier: int):
+        if head_dim != 256:
+            raise ValueError("mixed-precision KV layers need head_dim 256")
+        self.tiers: List[KvLayerPlanes] = []
+        for t, slots in enumerate(capacity):
+            fmt = TIER_FORMATS[t]
+            group = 16 if fmt == KV_NVFP4 else head_dim
+            rb, sb = kv_row_bytes(fmt, head_dim), kv_scale_bytes(fmt, head_dim, group)
+            n = max(1, int(slots))
+            k = torch.zeros((n, n_kv_heads, page_size, rb), dtype=torch.uint8, device=device)
+            v = torch.zeros_like(k)
+            ks = vs = None
+            if sb:
+                ks = torch.zeros((n, n_kv_heads, page_size, sb), dtype=torch.uint8, device=device)
+                vs = torch.zeros_like(ks)
+            self.tiers.append(KvLayerPlanes(fmt, group, k, v, ks, vs))
+        hot = self.tiers[0]
+        super().__init__(KV_MIXED, head_dim, hot.k_codes, hot.v_codes, None, None, False)
+        self.capacity = [int(c) for c in capacity]
+        self.free: List[List[int]] = [list(range(int(c) - 1, -1, -1)) for c in capacity]
+        self.hot_tier = hot_tier
+        pin = torch.device(device).type == "cuda"
+        self.cell_map_host = torch.full((n_pages,), -1, dtype=torch.int32, pin_memory=pin)
+        self.cell_map = torch.full((n_pages,), -1, dtype=torch.int32, device=device)
+        self.dirty = False
+        addr = [self.cell_map.data_ptr()]
+        for t in self.tiers:
+            addr += [t.k_codes.data_ptr(), t.v_codes.data_ptr(),
+                     0 if t.k_scales is None else t.k_scales.data_ptr(), 0 if t.v_scales is None else t.v_scales.data_ptr()]
+        self.desc = torch.tensor(addr, dtype=torch.int64)   # what the kernels' bindings read (CPU tensor of addresses)
+        self.cell_bytes = [2 * n_kv_heads * page_size * (kv_row_bytes(f, head_dim) +
+                                                         kv_scale_bytes(f, head_dim, 16 if f == KV_NVFP4 else head_dim))
+                           for f in TIER_FORMATS]
+
+    def bytes(self) -> int:
+        return sum(t.bytes() for t in self.tiers)
+
+    def bytes_in_use(self) -> int:
+        return sum((self.capacity[t] - len(self.free[t])) * self.cell_bytes[t] for t in range(3))
+
+    def tier_of(self, page: int) -> int:
+        c = int(self.cell_map_host[page])
+        return -1 if c < 0 else c >> CELL_TIER_SHIFT
+
+    def alloc_cell(self, page: int, tier: Optional[int] = None) -> None:
+        t = self.hot_tier if tier is None else tier
+        if not self.free[t]:
+            raise MemoryError(f"mixed KV layer: tier {TIER_NAMES[t]} has no free cell")
+        self.cell_map_host[page] = (t << CELL_TIER_SHIFT) | self.free[t].pop()
+        self.dirty = True
+
+    def free_cell(self, page: int) -> None:
+        c = int(self.cell_map_host[page])
+        if c >= 0:
+            self.free[c >> CELL_TIER_SHIFT].append(c & ((1 << CELL_TIER_SHIFT) - 1))
+            self.cell_map_host[page] = -1
+            self.dirty = True
+
+    def copy_cell(self, p_src: int, p_dst: int) -> None:
+        """Cell of `p_dst` := a copy of the cell of `p_src`, in the same tier."""
+        c = int(self.cell_map_host[p_src])
+        t, s_src = c >> CELL_TIER_SHIFT, c & ((1 << CELL_TIER_SHIFT) - 1)
+        self.free_cell(p_dst)
+        self.alloc_cell(p_dst, t)
+        s_dst = int(self.cell_map_host[p_dst]) & ((1 << CELL_TIER_SHIFT) - 1)
+        tp = self.tiers[t]
+        for plane in (tp.k_codes, tp.v_codes, tp.k_scales, tp.v_scales):
+            if plane is not None:
+                plane[s_dst].copy_(plane[s_src])
+
+    def publish(self) -> None:
+        if self.dirty:
+            self.cell_map.copy_(self.cell_map_host, non_blocking=True)
+            self.dirty = False
+
+
 def _load_pool_lib():
     import ctypes
     import os
@@ -140,7 +231,10 @@ class PagePool:
 class PagedKvCache:
     def __init__(self, cfg: ModelConfig, n_pages: int, page_size: int, max_rows: int, max_pages_per_row: int,
                  device, formats: Sequence[str] | str = "bf16", int8_group: int = 64,
-                 n_kv_heads: Optional[int] = None, n_layers: Optional[int] = None):
+                 n_kv_heads: Optional[int] = None, n_layers: Optional[int] = None,
+                 mixed_capacity: Optional[Sequence[int]] = None, mixed_hot_tier: int = 0):
+        """`formats` entry "mixed": that layer keeps its cells in three tiers (MixedKvPlanes); `mixed_capacity` =
+        cells per tier (default: every tier can hold every page), `mixed_hot_tier` = where new pages start."""
         self.cfg = cfg
         self.page_size = page_size
         self.n_pages = n_pages
@@ -154,6 +248,10 @@ class PagedKvCache:
         D = cfg.head_dim
         self.layers: List[KvLayerPlanes] = []
         for name in formats:
+            if name == "mixed":
+                cap = list(mixed_capacity) if mixed_capacity is not None else [n_pages, n_pages, n_pages]
+                self.layers.append(MixedKvPlanes(n_pages, self.n_kv_heads, page_size, D, self.device, cap, mixed_hot_tier))
+                continue
             hadamard = name == "fp8h"   # fp8 per-row codec with K stored in the Hadamard frame
             fmt = KV_FORMAT_NAMES["fp8" if hadamard else name]
             group = int8_group if fmt == KV_INT8_GROUP else (16 if fmt == KV_NVFP4 else D)
@@ -166,6 +264,7 @@ class PagedKvCache:
                 ks = torch.zeros((n_pages, self.n_kv_heads, page_size, sb), dtype=torch.uint8, device=self.device)
                 vs = torch.zeros_like(ks)
             self.layers.append(KvLayerPlanes(fmt, group, k, v, ks, vs, hadamard))
+        self.mixed = [l for l in self.layers if isinstance(l, MixedKvPlanes)]
         self.pool = PagePool(n_pages)
         self.host_arena = None   # optional runtime.host_arena.HostKvArena for the cold copies of exported pages
         # Lossy cold copies: int8 group-64 layers leave the device as requantised cold slots (E2M1 codes + E4M3 scales
@@ -187,6 +286,70 @@ class PagedKvCache:
     def total_bytes(self) -> int:
         return sum(l.bytes() for l in self.layers)
 
+    # ---- logical pages (and, for mixed layers, their cells) ----
+    def _page_alloc(self) -> int:
+        p = self.pool.alloc()
+        try:
+            for l in self.mixed:
+                l.alloc_cell(p)
+        except MemoryError:
+            for l in self.mixed:
+                l.free_cell(p)
+            self.pool.release(p)
+            raise
+        return p
+
+    def _page_release(self, p: int) -> None:
+        self.pool.release(p)
+        if self.mixed and self.pool.refcount_of(p) == 0:
+            for l in self.mixed:
+                l.free_cell(p)
+
+    def bytes_in_use(self) -> int:
+        """Device bytes of the cells that hold live pages (mixed layers: by each cell's tier)."""
+        used = self.n_pages - self.pool.free_pages
+        n = 0
+        for l in self.layers:
+            n += l.bytes_in_use() if isinstance(l, MixedKvPlanes) else l.bytes() // self.n_pages * used
+        return n
+
+    def tier_census(self) -> Dict[str, int]:
+        """Cells per tier over all mixed layers."""
+        out = {name: 0 for name in TIER_NAMES}
+        for l in self.mixed:
+            for t, name in enumerate(TIER_NAMES):
+                out[name] += l.capacity[t] - len(l.free[t])
+        return out
+
+    def descend(self, layer_index: int, pages: Sequence[int], to_tier: int) -> int:
+        """Re-encodes the cells of `pages` in mixed layer `layer_index` into `to_tier` (one launch) and frees their old
+        slots.  Cells already there, or without a free target slot, are skipped; returns the number moved.  Call
+        between steps: the kernel and the map update are ordered on the current stream."""
+        l = self.layers[layer_index]
+        if not isinstance(l, MixedKvPlanes):
+            raise ValueError(f"layer {layer_index} is not a mixed-precision layer")
+        src, dst, moved = [], [], []
+        for p in pages:
+            c = int(l.cell_map_host[p])
+            if c < 0 or (c >> CELL_TIER_SHIFT) == to_tier or not l.free[to_tier]:
+                continue
+            src.append(c)
+            dst.append((to_tier << CELL_TIER_SHIFT) | l.free[to_tier].pop())
+            moved.append(p)
+        if not moved:
+            return 0
+        from .._lib import load_native
+        ops = load_native()
+        s = torch.tensor(src, dtype=torch.int32).to(self.device, non_blocking=True)
+        d = torch.tensor(dst, dtype=torch.int32).to(self.device, non_blocking=True)
+        ops.kv_requant(l.desc, l.tiers[0].k_codes, s, d, self.page_size, self.n_kv_heads, self.cfg.head_dim)
+        for p, c_old, c_new in zip(moved, src, dst):
+            l.free[c_old >> CELL_TIER_SHIFT].append(c_old & ((1 << CELL_TIER_SHIFT) - 1))
+            l.cell_map_host[p] = c_new
+        l.dirty = True
+        l.publish()
+        return len(moved)
+
     # ---- mapping ----
     def ensure(self, row: int, n_tokens: int) -> None:
         """Make sure `row` has pages for positions [0, n_tokens)."""
@@ -195,7 +358,7 @@ class PagedKvCache:
         if need > self.max_pages_per_row:
             raise MemoryError(f"row {row}: {n_tokens} tokens exceed the block-table width")
         while len(pages) < need:
-            p = self.pool.alloc()
+            p = self._page_alloc()
             self.table_host[row, len(pages)] = p
             pages.append(p)
             self._dirty_rows.add(row)
@@ -208,7 +371,7 @@ class PagedKvCache:
             p = pages.pop()
             self.table_host[row, len(pages)] = -1
             if p >= 0:
-                self.pool.release(p)
+                self._page_release(p)
             self._dirty_rows.add(row)
 
     def release_before(self, row: int, n_tokens: int, window: int, slack: int = 64) -> int:
@@ -224,7 +387,7 @@ class PagedKvCache:
         n = 0
         for i in range(min(len(pages), first_needed // self.page_size)):
             if pages[i] >= 0:
-                self.pool.release(pages[i])
+                self._page_release(pages[i])
                 pages[i] = -1
                 self.table_host[row, i] = -1
                 n += 1
@@ -235,7 +398,7 @@ class PagedKvCache:
     def free_row(self, row: int) -> None:
         for p in self.row_pages.pop(row, []):
             if p >= 0:
-                self.pool.release(p)
+                self._page_release(p)
         self.table_host[row].fill_(-1)
         self._dirty_rows.add(row)
 
@@ -253,13 +416,8 @@ class PagedKvCache:
             self.table_host[dst, i] = p
         if n_tokens % self.page_size:
             p_src = self.row_pages[src][full]
-            p_new = self.pool.alloc()
-            for l in self.layers:
-                l.k_codes[p_new].copy_(l.k_codes[p_src])
-                l.v_codes[p_new].copy_(l.v_codes[p_src])
-                if l.k_scales is not None:
-                    l.k_scales[p_new].copy_(l.k_scales[p_src])
-                    l.v_scales[p_new].copy_(l.v_scales[p_src])
+            p_new = self._page_alloc()
+            self._copy_page(p_src, p_new)
             pages.append(p_new)
             self.table_host[dst, full] = p_new
         self._dirty_rows.add(dst)
@@ -280,7 +438,7 @@ class PagedKvCache:
             self.pool.retain(src[i])
             pages.append(src[i])
         if tail:
-            p_new = self.pool.alloc()
+            p_new = self._page_alloc()
             self._copy_page(src[full], p_new)
             pages.append(p_new)
         return pages
@@ -295,7 +453,7 @@ class PagedKvCache:
             mine.append(pages[i])
             self.table_host[dst_row, i] = pages[i]
         if n_tokens % self.page_size:
-            p_new = self.pool.alloc()
+            p_new = self._page_alloc()
             self._copy_page(pages[full], p_new)
             mine.append(p_new)
             self.table_host[dst_row, full] = p_new
@@ -304,6 +462,8 @@ class PagedKvCache:
     # ---- cold tiers: page contents leave / re-enter the device pool ----
     def export_pages(self, pages: List[int]) -> List[torch.Tensor]:
         """Contents of `pages` in every layer as pinned host tensors (device -> host, D2H page copies)."""
+        if self.mixed:
+            raise NotImplementedError("cold copies of mixed-precision layers are not built: their cells already descend")
         idx = torch.tensor(pages, dtype=torch.long, device=self.device)
         out = []
         pin = self.device.type == "cuda"
@@ -337,7 +497,7 @@ class PagedKvCache:
         """Allocates `n_pages` fresh pages and fills them from `export_pages` output.  None if the pool is too small."""
         if self.pool.free_pages < n_pages:
             return None
-        pages = [self.pool.alloc() for _ in range(n_pages)]
+        pages = [self._page_alloc() for _ in range(n_pages)]
         idx = torch.tensor(pages, dtype=torch.long, device=self.device)
         it = iter(planes)
         for l in self.layers:
@@ -364,10 +524,13 @@ class PagedKvCache:
 
     def drop_pages(self, pages: List[int]) -> None:
         for p in pages:
-            self.pool.release(p)
+            self._page_release(p)
 
     def _copy_page(self, p_src: int, p_dst: int) -> None:
         for l in self.layers:
+            if isinstance(l, MixedKvPlanes):
+                l.copy_cell(p_src, p_dst)
+                continue
             l.k_codes[p_dst].copy_(l.k_codes[p_src])
             l.v_codes[p_dst].copy_(l.v_codes[p_src])
             if l.k_scales is not None:
@@ -375,7 +538,9 @@ class PagedKvCache:
                 l.v_scales[p_dst].copy_(l.v_scales[p_src])
 
     def publish(self) -> None:
-        """Upload dirty block-table rows to the device."""
+        """Upload dirty block-table rows (and the cell maps of mixed layers) to the device."""
+        for l in self.mixed:
+            l.publish()
         if not self._dirty_rows:
             return
         if len(self._dirty_rows) > 8:

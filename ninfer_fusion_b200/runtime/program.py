@@ -47,6 +47,7 @@ class Lane:
     sampling: SamplingParams = field(default_factory=SamplingParams)
     last_token: int = -1     # sampled but not yet fed
     reused: int = 0          # prompt tokens restored from a session checkpoint instead of being prefilled
+    reuse_kind: str = ""     # kind of the frontier those tokens came from ("" = none: the request started at the root)
     media: object = None     # frontend.media.PreparedPrompt of a multimodal request
     visual: object = None    # [V, hidden] vision-tower output of `media` (filled at the first prefill step)
     rope_delta: int = 0      # rope position - cache position once the prompt is in (multimodal prompts)
@@ -380,6 +381,7 @@ class ProgramBase:
         if ck is not None:
             self._restore(ck.handle, lane, len(ck.tokens))
             lane.n_cached = lane.reused = len(ck.tokens)
+            lane.reuse_kind = ck.kind
             self._clock += 1
             ck.last_used = self._clock
             ck.hits += 1

@@ -70,7 +70,14 @@ class ServeState:
         self.responses: "OrderedDict[str, dict]" = OrderedDict()
         self.max_stored_responses = max(1, int(max_stored_responses))
         self.lock = threading.Lock()
-        self.log.event("server_start", model=service.model_id, max_concurrent=service.max_concurrent)
+        import sys as _sys
+
+        from .request_log import redact_argv
+        eng = service.engine
+        self.log.event("server_start", model=service.model_id, max_concurrent=service.max_concurrent,
+                       engine={"max_context": getattr(eng, "_max_context", None), "max_pending": getattr(eng, "max_pending", None),
+                               "free_lanes": eng.health().get("free_lanes")},
+                       argv=redact_argv(_sys.argv))
 
 
 def make_handler(state: ServeState):
@@ -163,15 +170,13 @@ def make_handler(state: ServeState):
 
             def on_start(rid, n_prompt):
                 info["rid"], info["prompt_tokens"] = rid, n_prompt
-                state.log.event("request_start", request_id=rid, api=api, stream=stream, prompt_tokens=n_prompt)
+                state.log.event("request_start", request_id=rid, protocol=api, stream=bool(stream), prompt_tokens=n_prompt,
+                                sampler={"temperature": req.temperature, "top_p": req.top_p, "top_k": req.top_k,
+                                         "seed": req.seed}, output_budget=req.max_tokens,
+                                thinking=bool(getattr(req, "enable_thinking", True)), session=bool(req.session))
 
             def finished(res: GenResult):
-                state.log.event("request_done" if res.finish_reason != "error" else "request_error", request_id=res.request_id,
-                                api=api, finish_reason=res.finish_reason, prompt_tokens=res.prompt_tokens,
-                                completion_tokens=res.completion_tokens, ttft_ms=res.ttft_ms,
-                                total_s=round(res.total_s, 4), error=res.error or None,
-                                decode_tok_s=round((res.completion_tokens - 1) / max(1e-9, res.total_s - (res.ttft_ms or 0) / 1e3), 2)
-                                if res.completion_tokens > 1 else None)
+                state.log.request_done(res, api, stream)
 
             try:
                 events = svc.stream(req, on_start=on_start, cancelled=gone.is_set)
@@ -210,19 +215,21 @@ def make_handler(state: ServeState):
 
                 if not self._stream(iter(_Keepalive(build_stream(tap(all_events()))))):
                     gone.set()
-                    state.log.event("request_error", request_id=info.get("rid"), api=api, error="client disconnected")
+                    state.log.event("request_error", request_id=info.get("rid"), protocol=api, error="client disconnected")
             except ResourceError as e:
-                state.log.event("request_rejected", api=api, reason=str(e))
+                state.log.event("request_rejected", protocol=api, phase="prepare", message=str(e))
                 if "timeout" in str(e):
                     self._error(503, str(e), "server_error", ecode="request_queue_timeout", anthropic=anthropic)
                 else:
                     self._error(429, str(e), "overloaded_error" if anthropic else "server_overloaded",
                                 ecode="server_overloaded", anthropic=anthropic)
             except (RequestError, P.BadRequest) as e:
-                state.log.event("request_rejected", api=api, reason=str(e))
+                state.log.event("request_rejected", protocol=api, phase="prepare", message=str(e))
                 self._error(400, str(e), "invalid_request_error", getattr(e, "param", None), anthropic=anthropic)
             finally:
-                state.log.throughput(svc.engine.stats.as_dict(), time.time() - t0)
+                h = svc.engine.health()
+                state.log.throughput(svc.engine.stats.as_dict(), {"running": h.get("active"), "waiting": h.get("pending"),
+                                                                  "free_lanes": h.get("free_lanes")})
 
         # ---------------------------------------------------------------- routes
         def do_GET(self):
@@ -340,7 +347,7 @@ def make_handler(state: ServeState):
                     return self._send_json(200, {"input_tokens": svc.count_tokens(req)})
                 return self._error(404, f"no route for POST {path}", "not_found_error", anthropic=anthropic)
             except P.BadRequest as e:
-                state.log.event("request_rejected", api=path, reason=str(e))
+                state.log.event("request_rejected", protocol=path, phase="prepare", message=str(e))
                 return self._error(404 if e.code == "not_found" else 400, str(e), "invalid_request_error", e.param,
                                    e.code, anthropic=anthropic)
 

@@ -57,6 +57,11 @@ class GenResult:
     total_s: float = 0.0
     error: str = ""
     token_ids: List[int] = field(default_factory=list)   # every committed completion token, in order
+    cached_tokens: int = 0        # prompt tokens served from a retained frontier
+    reuse_kind: str = ""          # engine name of that frontier's kind ("" = none)
+    queue_wait_s: float = 0.0     # submit -> lane
+    prefill_chunks: int = 0
+    decode_rounds: int = 0
 
 
 class GenerationService:
@@ -69,6 +74,7 @@ class GenerationService:
         self.max_concurrent = max_concurrent
         self.started = time.time()
         self.media = None                 # frontend.media.MediaProcessor, created on the first media request
+        self.media_pool = None            # runtime.worker_pool.HostWorkerPool for media decoding / resizing
         self.auto_shared_prefix = True    # publish the leading system block of chat prompts in the shared-prefix catalogue
         self.min_shared_prefix_tokens = 32
         self.allow_media_files = False    # local paths in media parts (CLI use); gateways leave this off
@@ -91,7 +97,11 @@ class GenerationService:
                 if self.media is None:
                     self.media = M.MediaProcessor()
                 try:
-                    pm = M.prepare_messages(self.tok, text, req.messages, self.media, allow_files=self.allow_media_files)
+                    if self.media_pool is None:
+                        from ..runtime.worker_pool import HostWorkerPool
+                        self.media_pool = HostWorkerPool(threads=4, queue_capacity=16)
+                    pm = M.prepare_messages(self.tok, text, req.messages, self.media, allow_files=self.allow_media_files,
+                                            pool=self.media_pool)
                 except (ValueError, OSError) as e:
                     raise RequestError(f"invalid media: {e}")
                 return list(pm.ids), pm
@@ -210,6 +220,9 @@ class GenerationService:
                 res.finish_reason = "tool_calls"
             res.ttft_ms = handle.ttft_ms
             res.total_s = time.perf_counter() - t0
+            res.cached_tokens, res.reuse_kind = handle.cached_tokens, handle.reuse_kind
+            res.queue_wait_s = (handle.t_admit - handle.t_submit) if handle.t_admit is not None else 0.0
+            res.prefill_chunks, res.decode_rounds = handle.prefill_chunks, handle.decode_rounds
             yield ("done", res)
         finally:
             self._permits.release()

@@ -168,3 +168,35 @@ def test_kv_auto_relayout_policy_and_loop():
     samples = iter([energy])
     d = loop.tick()
     assert d.changed and not d.applied and "drain" in d.reason and loop.policy.current == ["bf16"] * n
+
+
+def test_mixed_layer_cells_follow_logical_pages_on_cpu():
+    """Bookkeeping of a mixed-precision layer (no kernels involved): every logical page gets a hot-tier cell in
+    every mixed layer, shared pages keep theirs until the last reference goes, a copy lands in the source's tier,
+    and running out of hot cells is a MemoryError that leaves nothing half-allocated."""
+    from ninfer_fusion_b200.models.config import TINY_DENSE
+    from ninfer_fusion_b200.runtime.kv_cache import CELL_TIER_SHIFT, MixedKvPlanes, PagedKvCache
+    kv = PagedKvCache(TINY_DENSE, 16, 16, 3, 8, "cpu", formats="mixed", mixed_capacity=(6, 8, 8))
+    L = kv.layers[0]
+    assert isinstance(L, MixedKvPlanes) and L.desc.numel() == 13 and kv.mixed == [L]
+    kv.ensure(0, 70)                               # five pages
+    assert kv.tier_census() == {"bf16": 5, "fp8": 0, "nvfp4": 0}
+    assert [L.tier_of(p) for p in kv.row_pages[0]] == [0] * 5
+    assert kv.bytes_in_use() == 5 * L.cell_bytes[0]
+    kv.fork_row(0, 1, 40)                          # two full pages shared, the partial third one copied
+    assert kv.tier_census()["bf16"] == 6 and kv.row_pages[1][:2] == kv.row_pages[0][:2]
+    with pytest.raises(MemoryError):
+        kv.ensure(2, 16)                           # no hot cell left: the logical page must not leak either
+    assert kv.pool.free_pages == 16 - 6 and kv.tier_census()["bf16"] == 6
+    kv.free_row(0)                                 # the shared pages stay alive through row 1
+    assert kv.tier_census()["bf16"] == 3
+    kv.free_row(1)
+    assert kv.tier_census() == {"bf16": 0, "fp8": 0, "nvfp4": 0} and kv.pool.free_pages == 16
+    assert int(L.cell_map_host.max()) == -1
+    # a cell that sits in a colder tier is copied into the same tier
+    kv.ensure(0, 20)
+    p0 = kv.row_pages[0][0]
+    L.free_cell(p0)
+    L.alloc_cell(p0, 2)
+    kv.fork_row(0, 1, 8)                           # partial first page: copied
+    assert L.tier_of(kv.row_pages[1][0]) == 2 and (int(L.cell_map_host[kv.row_pages[1][0]]) >> CELL_TIER_SHIFT) == 2

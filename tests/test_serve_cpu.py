@@ -188,7 +188,22 @@ def test_request_log_lines(server):
     kinds = {r["event"] for r in recs}
     assert {"server_start", "request_start", "request_done"} <= kinds and "request_rejected" in kinds
     done = [r for r in recs if r["event"] == "request_done"][-1]
-    assert done["schema"] == 1 and done["completion_tokens"] <= 3 and done["api"] == "openai_chat"
+    # the reference's measurement-log contract: schema name and version, ids on every line, raw counts and seconds
+    assert done["schema"] == "ninfer_serve_request_log" and done["schema_version"] == 18
+    assert all("timestamp_unix_ms" in r and r["server_instance_id"] == done["server_instance_id"] for r in recs)
+    assert done["protocol"] == "openai_chat" and done["tokens"]["completion"] <= 3
+    assert done["tokens"]["prompt"] == done["tokens"]["cached"] + done["tokens"]["computed_prefill"]
+    assert done["reuse_path"] in ("root", "private_endpoint", "private_turn_closure", "private_response_replay",
+                                  "private_long_anchor", "shared_stable_prefix")
+    t = done["timings_seconds"]
+    assert set(t) == {"prepare", "ttft", "vision", "prefill", "decode", "total"} and t["total"] >= t["ttft"] > 0
+    assert done["engine_timing"]["queue_wait_seconds"] >= 0 and done["engine_timing"]["units"]["prefill"] >= 1
+    assert set(done["speculative"]) == {"backend", "draft_window", "rounds", "drafted_tokens", "accepted_tokens",
+                                        "fallback_steps", "accepted_per_position"}
+    start = [r for r in recs if r["event"] == "server_start"][-1]
+    assert "sekret" not in json.dumps(start) and "argv" in start
+    rs = [r for r in recs if r["event"] == "request_start"][-1]
+    assert rs["output_budget"] == 3 and "sampler" in rs
 
 
 def test_overload_is_429(server):
