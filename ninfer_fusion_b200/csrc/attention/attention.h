@@ -61,7 +61,9 @@ struct PagedAttnParams {
   // position (tree_base[t] + j); keys below tree_base[t] are always visible.
   const unsigned long long* tree_mask;
   const int* tree_base;
-  int impl;  // 0 = pick, 1 = SIMT kernel, 2 = tensor-core (mma.sync) kernel
+  int impl;  // 0 = pick, 1 = SIMT kernel, 2 = mma.sync tensor-core kernel, 3 = tcgen05 kernel (fp8-row pages)
+  long long kv_plane_rows = 0;  // rows (page x head x token) of the K / V code planes; 0 = unknown (no TMA path)
+  int* status = nullptr;        // optional device status word for the bounded waits of the tcgen05 kernel
   int window = 0;  // sliding window: a query sees only its last `window` keys (0 = all of them)
   // Selected-block attention (optional, decode only): query t attends to sel_count[t] blocks of four consecutive
   // tokens, block ids in sel_blocks[t * sel_stride ..] (each below the number of complete blocks, kv_len / 4), plus
@@ -75,8 +77,9 @@ struct PagedAttnParams {
 // Split-KV paged attention over quantised pages with in-register dequantisation,
 // followed by the (m, l, o) merge fused with the output sigmoid gate.
 const char* paged_attention(const PagedAttnParams& p, cudaStream_t stream, bool pdl);
-// Tensor-core split kernel; cudaErrorNotSupported when the geometry is outside its envelope.
+// Tensor-core split kernels; cudaErrorNotSupported when the problem is outside a kernel's envelope.
 cudaError_t paged_attention_mma_split(const PagedAttnParams& p, cudaStream_t stream, bool pdl);
+cudaError_t paged_attention_tc_split(const PagedAttnParams& p, cudaStream_t stream, bool pdl);   // tcgen05, fp8-row pages
 
 // Causal prefill / wide-verify attention over blocks of consecutive query tokens of one sequence.
 struct PrefillAttnParams {

@@ -14,6 +14,8 @@
 // launcher/gqa_attention_decode*.cu (mma.sync / FFMA routes for sm_120a).
 #include "attention.h"
 
+#include <cstdlib>
+
 #include <math_constants.h>
 
 #include "../common/ptx.cuh"
@@ -290,6 +292,15 @@ cudaError_t launch_f(int G, dim3 grid, const PagedAttnParams& p, cudaStream_t st
 
 }  // namespace
 
+// NFB_ATTN_TC=0 keeps the mma.sync kernel for fp8-row pages (comparison runs).
+static bool tc_attention_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("NFB_ATTN_TC");
+    return e == nullptr || e[0] != '0';
+  }();
+  return on;
+}
+
 const char* paged_attention(const PagedAttnParams& p, cudaStream_t stream, bool pdl) {
   if (p.Tq <= 0) return nullptr;
   if (p.head_dim != 256 && p.head_dim != 128) return "paged_attention: head_dim must be 128 or 256";
@@ -305,7 +316,11 @@ const char* paged_attention(const PagedAttnParams& p, cudaStream_t stream, bool 
   const int G = p.n_q_heads / p.n_kv_heads;
   const dim3 grid(p.Tq, p.n_kv_heads, p.n_splits);
   cudaError_t e = cudaErrorNotSupported;
-  if (p.impl != 1 && p.sel_blocks == nullptr) {   // the gathered key list runs on the SIMT kernel
+  if ((p.impl == 3 || (p.impl == 0 && tc_attention_enabled())) && p.sel_blocks == nullptr) {
+    e = paged_attention_tc_split(p, stream, pdl);   // fp8-row pages straight into tcgen05.mma
+    if (e == cudaErrorNotSupported && p.impl == 3) return "paged_attention: problem not supported by the tcgen05 kernel";
+  }
+  if (e == cudaErrorNotSupported && p.impl != 1 && p.sel_blocks == nullptr) {   // the gathered key list runs on the SIMT kernel
     e = paged_attention_mma_split(p, stream, pdl);
     if (e == cudaErrorNotSupported && p.impl == 2) return "paged_attention: geometry not supported by the tensor-core kernel";
   }

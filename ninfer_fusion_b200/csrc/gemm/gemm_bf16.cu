@@ -194,49 +194,41 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
       const uint64_t pol_x = l2_policy_evict_last();
       const int row_a = n0;
       const int row_b = (EPI == kEpiSwiglu) ? p.swiglu_half + n0 : n0 + 64;
-      bool waited_prior = false;
-      int it = 0;
+      // Weights do not depend on the previous kernel: fill EVERY stage with them before waiting for it, so that the
+      // whole pipeline (not one stage) is in flight while the previous kernel drains.  Only then the activations:
+      // after the previous kernel (plain input), or after the owner ranks have pushed their residual tiles into
+      // this rank's buffer (gathered input; bounded wait).
+      const int pre = num_it < kStages ? num_it : kStages;
+      for (int j = 0; j < pre; ++j) {
+        const uint32_t full = smem_u32(&bar_full[j]);
+        const uint32_t dst = smem_base + j * Cfg::kStageBytes;
+        const int kx = (kb_begin + j) * kBlockK;
+        mbar_expect_tx(full, Cfg::kStageBytes);
+        tma_load_2d(dst, &tmap_w, full, kx, row_a, pol_w);
+        tma_load_2d(dst + 64 * 128, &tmap_w, full, kx, row_b, pol_w);
+      }
+      pdl_wait_prior();
       if (gathered) {
-        // Weights first, into every stage; the activations are the residual tiles that the owner ranks push into
-        // this rank's buffer, so wait for all of them (bounded) before the first activation load.
-        const int pre = num_it < kStages ? num_it : kStages;
-        for (int j = 0; j < pre; ++j) {
-          const uint32_t full = smem_u32(&bar_full[j]);
-          const uint32_t dst = smem_base + j * Cfg::kStageBytes;
-          const int kx = (kb_begin + j) * kBlockK;
-          mbar_expect_tx(full, Cfg::kStageBytes);
-          tma_load_2d(dst, &tmap_w, full, kx, row_a, pol_w);
-          tma_load_2d(dst + 64 * 128, &tmap_w, full, kx, row_b, pol_w);
-        }
-        pdl_wait_prior();
-        waited_prior = true;
         const uint32_t target = __ldcg(p.g_target);
         // on a time-out the loads below are still issued (the data is stale, the status word says so): every
         // barrier that was armed above must complete before the CTA may leave
         if (!wait_counter(p.g_flag, target, p.status)) abort_flag = 1;
         asm volatile("fence.proxy.async.global;" ::: "memory");
-        for (int j = 0; j < pre; ++j)
-          tma_load_2d(smem_base + j * Cfg::kStageBytes + kWTileBytes, &tmap_x, smem_u32(&bar_full[j]),
-                      (kb_begin + j) * kBlockK, t0, pol_x);
-        it = pre;
       }
+      for (int j = 0; j < pre; ++j)
+        tma_load_2d(smem_base + j * Cfg::kStageBytes + kWTileBytes, &tmap_x, smem_u32(&bar_full[j]),
+                    (kb_begin + j) * kBlockK, t0, pol_x);
+      int it = pre;
       for (; it < num_it; ++it) {
         const int s = it % kStages;
         const uint32_t ph = (it / kStages) & 1;
-        if (it >= kStages &&
-            !mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, &abort_flag, p.status, kStatusEmptyWaitTimeout))
-          break;
+        if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, &abort_flag, p.status, kStatusEmptyWaitTimeout)) break;
         const uint32_t full = smem_u32(&bar_full[s]);
         const uint32_t dst = smem_base + s * Cfg::kStageBytes;
         const int kx = (kb_begin + it) * kBlockK;
         mbar_expect_tx(full, Cfg::kStageBytes);
-        // Weights do not depend on the previous kernel: stream them first.
         tma_load_2d(dst, &tmap_w, full, kx, row_a, pol_w);
         tma_load_2d(dst + 64 * 128, &tmap_w, full, kx, row_b, pol_w);
-        if (!waited_prior) {
-          pdl_wait_prior();  // activations are produced by the previous kernel
-          waited_prior = true;
-        }
         tma_load_2d(dst + kWTileBytes, &tmap_x, full, kx, t0, pol_x);
       }
       if (abort_flag) {

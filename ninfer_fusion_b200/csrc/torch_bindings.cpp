@@ -360,6 +360,7 @@ void paged_attention(const Tensor& q, int64_t n_q_heads, int64_t n_kv_heads, int
     p.tree_base = static_cast<const int*>(tree_base->data_ptr());
   }
   p.impl = static_cast<int>(impl);
+  if (format == nfb::kKvFp8Row) p.kv_plane_rows = k_codes.numel() / head_dim;
   TORCH_CHECK(window >= 0, "window must be >= 0");
   p.window = static_cast<int>(window);
   if (sel_blocks.has_value() && sel_blocks->defined()) {

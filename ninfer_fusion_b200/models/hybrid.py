@@ -143,15 +143,17 @@ class ShardGeometry:
         return self.gdn_conv_dim + self.gdn_v_dim + 2 * self.gdn_v_heads
 
 
-def pick_attention_split(max_kv_len: int, n_work: int, sm_count: int = 148, max_splits: int = 64) -> tuple[int, int]:
+def pick_attention_split(max_kv_len: int, n_work: int, sm_count: int = 148, max_splits: int = 64,
+                         waves: int = 2) -> tuple[int, int]:
     """Keys per split (multiple of 128) and split count for `n_work` (query, kv-head) items.
 
-    Aim for about two waves of CTAs; the split size only depends on the context
-    bucket, so decode and verify of the same position use the same ranges."""
+    Aim for about `waves` items per SM: two for the kernels that run one CTA per item, eight for the persistent
+    tcgen05 kernel (its CTAs walk a list of items, so many small items balance better than few large ones).  The
+    split size only depends on the context bucket, so decode and verify of the same position use the same ranges."""
     bucket = 128
     while bucket < max_kv_len:
         bucket *= 2
-    want = max(1, (2 * sm_count + n_work - 1) // n_work)
+    want = max(1, (waves * sm_count + n_work - 1) // n_work)
     split = max(128, bucket // want)
     split = 1 << (split.bit_length() - 1)          # power of two >= 128
     while (bucket + split - 1) // split > max_splits:
@@ -441,7 +443,10 @@ class HybridModel:
                                         planes.v_scales, kv.page_size, planes.fmt, planes.group, self.sm_scale, gate,
                                         out, self.pdl, 0, tiers)
             return out, self.w[f"{prefix}/attn/o_proj"]
-        split, n_splits = pick_attention_split(b.max_kv_len, T * g.n_kv_heads, max_splits=ws.max_splits_attn)
+        persistent = (planes.fmt == 1 and D == 256 and kv.page_size % 64 == 0 and self.attn_impl in (0, 3)
+                      and os.environ.get("NFB_ATTN_TC", "1") != "0")
+        split, n_splits = pick_attention_split(b.max_kv_len, T * g.n_kv_heads, max_splits=ws.max_splits_attn,
+                                               waves=8 if persistent else 2)
         chunk = max(1, ws.part_rows // n_splits)
         for t0 in range(0, T, chunk):
             t1 = min(T, t0 + chunk)
