@@ -24,30 +24,37 @@ N_GDN, N_ATTN, N_LAYERS = 48, 16, 64
 
 
 def commands(T: int, context: int):
-    """(key, count per decode round, argv, note).  `T` = tokens per step (the decode batch)."""
+    """(key, count per decode round, argv, note).  `T` = tokens per step (the decode batch).
+
+    The reference batches its stateful Ops (GDN step, decode convolution, cached attention) over at most 8
+    sequences (they exist for one request plus its draft tree), so a batch of T sequences is ceil(T / 8) calls of
+    those; its bf16 Linear only accepts the weight shapes of its own models, so the GDN input projection is the
+    three Linears it is made of there (z 6144, v 6144, q+k 4096 rows; the 96 gating rows have no bf16 bench shape and
+    are left out).  Its fp8 benches are not part of the sum: `fp8_linear_swiglu` ended with
+    "cudaErrorLaunchFailure: unspecified launch failure" on this GPU and is never started again."""
     t = str(T)
     lin = lambda n, k: ["linear", "--qtype", "BF16", "--n", str(n), "--k", str(k), "--t", t, "--warmup", "5", "--repeat", "30"]
-    gdn_batch = min(T, 8)
+    sb = min(T, 8)                       # sequences per call of a stateful Op
+    calls = (T + sb - 1) // sb
+    many = f"the Op takes at most 8 sequences: {calls} calls for {T}"
     return [
-        ("gdn_in_proj_bf16", N_GDN, lin(16384, 5120), "qkv 10240 + z 6144 rows, bf16 weights, generic Linear"),
-        ("gdn_ab_proj_bf16", N_GDN, lin(96, 5120), "a / b gating rows"),
+        ("gdn_in_proj_zv_bf16", 2 * N_GDN, lin(6144, 5120), "z and v rows of the GDN input projection (two Linears per layer)"),
+        ("gdn_in_proj_qk_bf16", N_GDN, lin(4096, 5120), "q + k rows of the GDN input projection"),
         ("attn_in_proj_bf16", N_ATTN, ["attn_input_proj", "--format", "bf16", "--tokens", t, "--cache", "cold", "--warmup", "5",
                                        "--repeat", "30"], "q + gate + k + v rows 14336 x 5120, fused input projection"),
         ("out_proj_bf16_add", N_LAYERS, ["bf16_linear_add", "--t-sweep", t, "--route", "production", "--warmup", "5", "--repeat", "30"],
          "5120 x 6144 + residual (GDN out_proj and attention o_proj)"),
-        ("mlp_gate_up_bf16", N_LAYERS, lin(34816, 5120), "gate and up rows, generic Linear (the SwiGLU product is a separate Op there)"),
-        ("mlp_down_bf16", N_LAYERS, lin(5120, 17408), "down projection, generic Linear"),
-        ("mlp_gate_up_fp8_swiglu", 0, ["fp8_linear_swiglu", "--t-sweep", t, "--warmup", "5", "--repeat", "30"],
-         "fp8 weights, fused SwiGLU (context: the reference's fused form exists for quantised weights only)"),
-        ("mlp_down_fp8_add", 0, ["fp8_linear_add", "--k", "17408", "--t-sweep", t, "--warmup", "5", "--repeat", "30"], "fp8 weights"),
-        ("conv1d_silu", N_GDN, ["causal_conv1d_silu", "--decode", "--batch", t, "--cache", "cold"], "decode step of the GDN convolution"),
-        ("gdn_step", N_GDN * ((T + gdn_batch - 1) // gdn_batch),
-         ["gated_delta_net", "--batch-update", "--batch", str(gdn_batch), "--warmup", "10", "--repeat", "40"],
-         f"recurrent update; the Op accepts batches up to 8, so a batch of {T} is {(T + gdn_batch - 1) // gdn_batch} calls"),
+        ("mlp_gate_up_bf16", N_LAYERS, lin(34816, 5120), "gate and up rows, generic Linear (the SwiGLU product is a separate Op there, not timed)"),
+        ("mlp_down_bf16", N_LAYERS, lin(5120, 17408), "down projection, generic Linear (the residual add is not timed)"),
+        ("conv1d_silu", N_GDN * calls, ["causal_conv1d_silu", "--snapshot", "--batch", str(sb), "--tokens", "1", "--cache", "cold"],
+         "decode step of the GDN convolution, batched snapshot form; " + many),
+        ("gdn_step", N_GDN * calls, ["gated_delta_net", "--batch-update", "--batch", str(sb), "--warmup", "10", "--repeat", "40"],
+         "recurrent update; " + many),
         ("rmsnorm_hidden", 2 * N_LAYERS + 1, ["rmsnorm", "--decode", "--kind", "hidden27", "--tokens", t], "input and post-attention norms"),
-        ("attention_fp8", N_ATTN, ["causal_softmax_attention", "--entry", "cached", "--geometry", "d256-h24-kv4", "--kv-dtype", "fp8",
-                                   "--batch", t, "--tokens", "1", "--context", str(context), "--execution", "eager", "--cache", "cold",
-                                   "--warmup", "5", "--repeat", "30"], "decode attention over an fp8 cache"),
+        ("attention_fp8", N_ATTN * calls, ["causal_softmax_attention", "--entry", "cached", "--geometry", "d256-h24-kv4", "--kv-dtype",
+                                           "fp8", "--batch", str(sb), "--tokens", "1", "--context", str(context), "--execution",
+                                           "eager", "--cache", "cold", "--warmup", "5", "--repeat", "30"],
+         "decode attention over an fp8 cache; " + many),
         ("lm_head_bf16", 1, lin(248320, 5120), "vocabulary projection, generic Linear"),
         ("argmax", 1, ["argmax", "--shape", "full", "--cols", str(min(T, 128))], "greedy token choice"),
     ]
@@ -57,9 +64,13 @@ _MEDIAN = re.compile(r"median[=\s:]+\s*([0-9]+(?:\.[0-9]+)?)\s*us", re.I)
 _US = re.compile(r"([0-9]+(?:\.[0-9]+)?)\s*us\b")
 
 
+_LINEAR_ROW = re.compile(r"^(?:explicit|sweep)\s+\S+\s+\S+\s+\d+\s+\d+\s+\d+\s+([0-9]+(?:\.[0-9]+)?)", re.M)
+
+
 def parse_median_us(text: str):
-    """The first `median=... us` of the output, else None (the raw text is kept beside it)."""
-    m = _MEDIAN.search(text)
+    """The first `median=... us` of the output, or the median_us column of the Linear bench's table row, else None
+    (the raw text is kept beside it)."""
+    m = _MEDIAN.search(text) or _LINEAR_ROW.search(text)
     return float(m.group(1)) if m else None
 
 

@@ -86,13 +86,56 @@ class ClockSampler:
 
 
 def reference_arm(args) -> int:
-    # The reference is a CMake/C++ project without setup.py or pyproject.toml, so a
-    # `pip install --target baseline/_ref <reference tree>` fails ("not installable"); its CMake
-    # build needs FFmpeg and libcurl development packages and CUDA >= 13.1 for sm_100a, none
-    # of which are available offline.
-    print(json.dumps({"impl": "reference",
-                      "unavailable": "reference is a CMake C++/CUDA project (no setup.py/pyproject: pip install "
-                                     "refused; needs FFmpeg+libcurl dev libs and CUDA>=13.1 for sm_100a)"}))
+    """The reference arm: the reference's own Op benchmarks (its sources compiled unmodified for plain sm_100, see
+    baseline/build_reference.sh) at the shapes of one 27B decode round, summed per round (baseline/reference_ops.py).
+
+    The reference has no multi-GPU engine and no batched serving loop, and its model programs only start from
+    artifact files that do not exist offline, so this is an Op sum, marked as such ("class": "op-sum").  On N GPUs
+    it is what the reference could do with them: N independent replicas, each decoding batch / N sequences; the
+    round time is the slowest replica's."""
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
+    import reference_ops
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ["CUDA_VISIBLE_DEVICES"] = str(local)   # the bench mains use device 0 of what they see
+    batch = max(1, args.batch // world)
+    raw = os.environ.get("NFB_REFERENCE_RAW_DIR")
+    res = reference_ops.run(T=batch, context=args.prompt_len, raw_dir=os.path.join(raw, f"rank{rank}") if raw else None)
+    if "unavailable" in res:
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": res["unavailable"]}))
+        return 0
+    sum_us = res["sum_us"]
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        dist.init_process_group("gloo")
+        t = torch.tensor([sum_us], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sum_us = float(t[0])
+        dist.destroy_process_group()
+    if rank != 0:
+        return 0
+    if sum_us <= 0:
+        print(json.dumps({"impl": "reference", "unavailable": "no reference Op benchmark produced a time on this device: "
+                          + "; ".join(f"{r['op']}: {r.get('refused', '?')}" for r in res["rows"][:4])}))
+        return 0
+    ms = sum_us / 1e3
+    print(json.dumps({
+        "impl": "reference", "class": "op-sum",
+        "metric": "decode tokens/sec/box + p50 TTFT at 1/2/4/8 B200, 27B hybrid fp8-KV",
+        "value": round(batch * world / (ms / 1e3), 2), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (the reference benches' own generated operands)",
+        "config": {"model": "qwen3.6-27b", "global_batch": batch * world, "seq_len": args.prompt_len,
+                   "parallelism": "single" if world == 1 else f"{world} independent replicas of batch {batch}",
+                   "kv": "fp8-e4m3-row", "weights": "bf16", "l2": "flushed between samples by the reference benches"},
+        "note": "sum over the Ops of one decode round of (count per round x the median the reference's bench main printed); "
+                "no launch gaps, no sampling loop, no host work: an optimistic round time for the reference",
+        "ops": res["rows"], "missing": res["missing"]}))
     return 0
 
 

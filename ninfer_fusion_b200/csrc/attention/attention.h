@@ -80,6 +80,7 @@ const char* paged_attention(const PagedAttnParams& p, cudaStream_t stream, bool 
 // Tensor-core split kernels; cudaErrorNotSupported when the problem is outside a kernel's envelope.
 cudaError_t paged_attention_mma_split(const PagedAttnParams& p, cudaStream_t stream, bool pdl);
 cudaError_t paged_attention_tc_split(const PagedAttnParams& p, cudaStream_t stream, bool pdl);   // tcgen05, fp8-row pages
+void paged_attention_tc_trace(bool enable, unsigned long long* host_out);   // event trace of CTA 0: [5][1024] words
 
 // Causal prefill / wide-verify attention over blocks of consecutive query tokens of one sequence.
 struct PrefillAttnParams {

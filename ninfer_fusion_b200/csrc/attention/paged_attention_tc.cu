@@ -23,9 +23,12 @@
 //   Moving a frame rescales the O^T columns in TMEM (tcgen05.ld / tcgen05.st) and needs the previous product to be
 //   complete; with lazy frames that happens in the first tile or two of an item, and every other tile's softmax
 //   overlaps the previous tile's P.V.
-// * S^T (2 x 16 columns), O_hi and O_lo (2 x 16 columns each) live in TMEM.
-// * Warps: 0-3 softmax (thread = key = TMEM lane), 4 TMA producer, 5 MMA issuer + TMEM owner, 6 query staging
-//   (bf16 -> two swizzled e4m3 operand tiles, one item ahead).
+// * S^T (2 buffers x 4 partial accumulators x 16 columns), O_hi and O_lo (2 x 16 columns each) live in TMEM.  The
+//   N = 16 instructions are latency bound, so no two consecutive ones share an accumulator: S^T is summed from four
+//   partials by the softmax threads, and P.V walks its four accumulators inside every key step.
+// * Warps: 0-7 softmax (two threads per key = TMEM lane, each with half of the query rows: one warp per scheduler
+//   could not hide its own latencies), 8 TMA producer, 9 issuer of S^T + TMEM owner, 10 query staging (bf16 -> two
+//   swizzled e4m3 operand tiles, one item ahead), 11 issuer of P.V.
 //
 // Every wait is bounded; after a time-out the roles run their loops to the end without blocking, the status word
 // says what gave up, and the CTA frees its TMEM.  Unwritten rows of a tile (pages past the sequence end) keep
@@ -63,23 +66,38 @@ constexpr int kQBytes = 2 * kQPartBytes;         // hi + lo
 constexpr int kPPartBytes = kTileKeys * kRows;   // one e4m3 term of P^T: [128 keys][16 rows]
 constexpr int kPBytes = 2 * kPPartBytes;
 constexpr int kSmemBytes = kStages * kStageBytes + 2 * kQBytes + 2 * kPBytes + 1024;
-constexpr int kThreads = 7 * 32;
-constexpr int kSoftmaxThreads = 128;
-constexpr int kTmemCols = 128;                   // S^T: 2 x 16, O_hi: 2 x 16, O_lo: 2 x 16 (power of two)
+constexpr int kSoftmaxWarps = 8;     // two threads per key: each owns half of the group's query rows
+constexpr int kSoftmaxThreads = kSoftmaxWarps * 32;
+constexpr int kWarpProducer = 8, kWarpS = 9, kWarpQ = 10, kWarpPV = 11;
+constexpr int kThreads = 12 * 32;
+constexpr int kTmemCols = 256;                   // S^T: 2 buffers x 4 partials x 16, O_hi and O_lo: 2 x 16 each
 constexpr float kPScale = 1.f;      // p' = kPScale * p * v_scale / R <= 16 * 2
 constexpr float kLoScale = 128.f;   // second term of P: 128 x the residual (<= half an e4m3 step of 32, i.e. <= 128)
 constexpr float kFrameSlack = 4.f;  // log2 units a score may exceed its row's frame before the frame moves
 constexpr int kMaxItems = 256;      // items one CTA may walk (their descriptors live in shared memory)
 constexpr int kMaxBoxes = 1024;     // 64-key boxes of those items (cache rows looked up once, in the prologue)
-constexpr int kColO = 2 * kRows;    // first O^T column: [hi d0-127][hi d128-255][lo d0-127][lo d128-255]
+constexpr int kColO = 8 * kRows;    // first O^T column: [hi d0-127][hi d128-255][lo d0-127][lo d128-255]
 
 enum : int { kStatusAttnWait = 6 };
+
+// Optional event trace of CTA 0 (development aid): five roles x 1024 (code << 56 | globaltimer ns) entries.
+constexpr int kTraceRoles = 5, kTraceLen = 1024;
+__device__ unsigned long long g_attn_trace[kTraceRoles * kTraceLen];
+bool g_attn_trace_on = false;
+__device__ __forceinline__ void trace_event(int on, int role, int& n, int code) {
+  if (on && blockIdx.x == 0 && n < kTraceLen) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_attn_trace[role * kTraceLen + n++] = (static_cast<unsigned long long>(code) << 56) | (t & 0x00ffffffffffffffull);
+  }
+}
 
 struct TcParams {
   PagedAttnParams a;
   int n_items;
   int G;
   int* status;
+  int trace;
 };
 
 struct Item {
@@ -146,7 +164,9 @@ constexpr uint32_t kIdescPV = umma_idesc(128, kRows, 0, 0) | (1u << 15) | (1u <<
 // ---- TMEM <-> registers, N columns of this thread's lane ----
 template <int N>
 __device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t* r) {
-  if constexpr (N == 4) {
+  if constexpr (N == 2) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(taddr));
+  } else if constexpr (N == 4) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr));
   } else if constexpr (N == 8) {
@@ -157,7 +177,9 @@ __device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t* r) {
 }
 template <int N>
 __device__ __forceinline__ void tmem_st(uint32_t taddr, const uint32_t* r) {
-  if constexpr (N == 4) {
+  if constexpr (N == 2) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1,%2};" ::"r"(taddr), "r"(r[0]), "r"(r[1]) : "memory");
+  } else if constexpr (N == 4) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};"
                  ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]) : "memory");
   } else if constexpr (N == 8) {
@@ -173,7 +195,18 @@ __device__ __forceinline__ void tmem_st(uint32_t taddr, const uint32_t* r) {
   }
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+// barrier of the softmax threads that also ORs a predicate over all of them
+__device__ __forceinline__ bool softmax_any(bool v) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.or.pred p, 1, 256, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(r) : "r"(static_cast<uint32_t>(v)) : "memory");
+  return r != 0;
+}
 
 // x ~ hi + lo, both e4m3; two values at a time.  Returns hi in the low 16 bits, lo in the high 16 bits.
 __device__ __forceinline__ uint32_t split_e4m3x2(float a, float b) {
@@ -207,6 +240,34 @@ struct Bars {
   uint64_t q_full[2], q_empty[2];
 };
 
+// A position in this CTA's stream of tiles: local item, its descriptor, tile inside the item, ordinal of the item
+// among the non-empty ones (selects the Q buffer).
+struct Cursor {
+  int li;
+  Item it;
+  int j;
+  uint32_t qn;
+  bool valid;
+};
+__device__ __forceinline__ void cursor_seek(Cursor& c, const ItemRec* recs, int n_local) {
+  c.valid = false;
+  for (; c.li < n_local; ++c.li) {
+    c.it = get_item(recs, c.li);
+    if (!c.it.empty) {
+      c.valid = true;
+      c.j = 0;
+      return;
+    }
+  }
+}
+__device__ __forceinline__ void cursor_next(Cursor& c, const ItemRec* recs, int n_local) {
+  if (++c.j >= c.it.nt) {
+    ++c.li;
+    ++c.qn;
+    cursor_seek(c, recs, n_local);
+  }
+}
+
 template <int NR>   // query rows of the group, padded to 4 / 8 / 16
 __global__ void __launch_bounds__(kThreads, 1) paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
                                                                     const __grid_constant__ CUtensorMap tmap_v,
@@ -216,9 +277,9 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_tc_kernel(const __grid
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ float q_scale[2][kRows];
-  __shared__ float red_m[2][4][kRows];
-  __shared__ float red_v[2][4];
-  __shared__ float red_l[4][kRows];
+  __shared__ float red_m[2][kSoftmaxWarps][kRows / 2];
+  __shared__ float red_v[2][kSoftmaxWarps];
+  __shared__ float red_l[kSoftmaxWarps][kRows / 2];
   __shared__ ItemRec item_recs[kMaxItems];
   __shared__ int box_rows[kMaxBoxes];   // [local item][box of its split]: first cache row of the box, or -1
 
@@ -230,12 +291,14 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_tc_kernel(const __grid
   const uint32_t p_base = q_base + 2 * kQBytes;
   uint8_t* const smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   volatile int* abortp = &abort_flag;
+  int tn = 0;   // this thread's trace cursor
+  if (threadIdx.x == 0) trace_event(tp.trace, 2, tn, 0);
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_u32(&bars.full[s]), 1);
-      mbar_init(smem_u32(&bars.empty[s]), 1);
+      mbar_init(smem_u32(&bars.empty[s]), 2);   // the S product and the P.V product each release their half
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&bars.s_full[b]), 1);
@@ -248,7 +311,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_tc_kernel(const __grid
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
   }
-  if (warp == 5) {
+  if (warp == kWarpS) {
     tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
     tmem_relinquish();
   }
@@ -259,8 +322,9 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_tc_kernel(const __grid
     const int st = i / (kOperandBytes / 16), o = i % (kOperandBytes / 16);
     reinterpret_cast<uint4*>(smem_gen + st * kStageBytes + kOperandBytes)[o] = make_uint4(0, 0, 0, 0);
   }
-  for (int i = threadIdx.x; i < 2 * kQBytes / 16; i += kThreads)
+  for (int i = threadIdx.x; i < (2 * kQBytes + 2 * kPBytes) / 16; i += kThreads)   // Q and P^T tiles (adjacent)
     reinterpret_cast<uint4*>(smem_gen + kStages * kStageBytes)[i] = make_uint4(0, 0, 0, 0);
+  if (threadIdx.x < 2 * kRows) (&q_scale[0][0])[threadIdx.x] = 1.f;   // rows past the group: a finite scale for their zero scores
   fence_proxy_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -288,8 +352,9 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_tc_kernel(const __grid
     box_rows[e] = row;
   }
   __syncthreads();
+  if (threadIdx.x == 0) trace_event(tp.trace, 2, tn, 1);
 
-  if (warp == 4) {
+  if (warp == kWarpProducer) {
     // =========================== TMA producer ===========================
     if (elect_one()) {
       const uint64_t pol = l2_policy_evict_first();
@@ -297,17 +362,20 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_tc_kernel(const __grid
       for (int li = 0; li < n_local; ++li) {
         const Item it = get_item(item_recs, li);
         if (it.empty) continue;
-        const int box0 = li * bpi + (it.k0 - it.split * p.split_keys) / kBoxKeys;
+        const int first_box = (it.k0 - it.split * p.split_keys) / kBoxKeys;
         for (int j = 0; j < it.nt; ++j, ++g) {
           const int stage = g % kStages;
+          trace_event(tp.trace, 0, tn, 10);
           if (g >= kStages)
             mbar_wait(smem_u32(&bars.empty[stage]), ((g / kStages) & 1) ^ 1, abortp, tp.status, kStatusEmptyWaitTimeout);
           if (*abortp) break;
+          trace_event(tp.trace, 0, tn, 11);
           int rows[2];
           uint32_t bytes = 0;
 #pragma unroll
           for (int b = 0; b < 2; ++b) {
-            rows[b] = (2 * j + b < bpi - (box0 - li * bpi)) ? box_rows[box0 + 2 * j + b] : -1;
+            const int box = first_box + 2 * j + b;
+            rows[b] = box < bpi ? box_rows[li * bpi + box] : -1;
             if (rows[b] >= 0) bytes += 4 * kBoxBytes;
           }
           const uint32_t full = smem_u32(&bars.full[stage]);
@@ -334,36 +402,27 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_tc_kernel(const __grid
       }
     }
     __syncwarp();
-  } else if (warp == 5) {
-    // =========================== MMA issuer ===========================
+  } else if (warp == kWarpS) {
+    // =========================== issuer of S^T = K . Q^T ===========================
+    // Sixteen k-steps (two e4m3 terms of Q x two d-halves x four 32-byte steps) go into FOUR partial accumulators,
+    // one per step inside the swizzle atom, so that consecutive instructions never depend on each other; the
+    // softmax threads add the four partials.  (Sixteen dependent N = 16 instructions would pay the tensor pipe's
+    // full latency sixteen times.)
     if (elect_one()) {
-      // two cursors over the same tile stream: S^T runs one tile ahead of P.V
-      struct Cursor {
-        int idx; Item it; int j; uint32_t qn; bool valid;
-      };
-      auto seek = [&](Cursor& c) {   // first non-empty item at or after local index c.idx
-        c.valid = false;
-        for (; c.idx < n_local; ++c.idx) {
-          c.it = get_item(item_recs, c.idx);
-          if (!c.it.empty) { c.valid = true; c.j = 0; return; }
-        }
-      };
-      auto advance = [&](Cursor& c) {
-        if (++c.j >= c.it.nt) { ++c.idx; ++c.qn; seek(c); }
-      };
-      Cursor cs{0, {}, 0, 0, false}, cp{0, {}, 0, 0, false};
-      seek(cs);
-      seek(cp);
-      uint32_t gs = 0, gp = 0;
-      auto issue_s = [&]() {
-        const uint32_t qb = cs.qn & 1;
-        if (cs.j == 0) mbar_wait(smem_u32(&bars.q_full[qb]), (cs.qn >> 1) & 1, abortp, tp.status, kStatusAttnWait);
+      Cursor c{0, {}, 0, 0, false};
+      cursor_seek(c, item_recs, n_local);
+      for (uint32_t gs = 0; c.valid && !*abortp; ++gs) {
+        const uint32_t qb = c.qn & 1;
+        if (c.j == 0) mbar_wait(smem_u32(&bars.q_full[qb]), (c.qn >> 1) & 1, abortp, tp.status, kStatusAttnWait);
+        // the S^T buffer of this parity was read by the softmax of two tiles ago (its P^T arrival says so)
+        if (gs >= 2) mbar_wait(smem_u32(&bars.p_full[gs & 1]), ((gs >> 1) - 1) & 1, abortp, tp.status, kStatusAttnWait);
+        trace_event(tp.trace, 1, tn, 20);
         mbar_wait(smem_u32(&bars.full[gs % kStages]), (gs / kStages) & 1, abortp, tp.status, kStatusTmaWaitTimeout);
+        trace_event(tp.trace, 1, tn, 21);
         tc_fence_after();
         const uint32_t kaddr = smem_base + (gs % kStages) * kStageBytes;
         const uint32_t qaddr = q_base + qb * kQBytes;
-        const uint32_t d = tmem_base + (gs & 1) * kRows;
-        uint32_t acc = 0;
+        const uint32_t d = tmem_base + (gs & 1) * (4 * kRows);
 #pragma unroll
         for (int part = 0; part < 2; ++part)
 #pragma unroll
@@ -371,56 +430,69 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_tc_kernel(const __grid
             const uint64_t a = umma_desc_k_sw128(kaddr + h * kHalfBytes);
             const uint64_t b = umma_desc_k_sw128(qaddr + part * kQPartBytes + h * (kRows * 128));
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-              tc_mma_f8f6f4(d, a + 2 * ks, b + 2 * ks, kIdescS, acc);
-              acc = 1;
-            }
+            for (int ks = 0; ks < 4; ++ks)
+              tc_mma_f8f6f4(d + ks * kRows, a + 2 * ks, b + 2 * ks, kIdescS, (part | h) ? 1u : 0u);
           }
         tc_commit(smem_u32(&bars.s_full[gs & 1]));
-        if (cs.j == cs.it.nt - 1) tc_commit(smem_u32(&bars.q_empty[qb]));
-        ++gs;
-        advance(cs);
-      };
-      if (cs.valid) issue_s();
-      while (cp.valid) {
-        if (cs.valid) issue_s();
-        mbar_wait(smem_u32(&bars.p_full[gp & 1]), (gp >> 1) & 1, abortp, tp.status, kStatusAttnWait);
-        tc_fence_after();
-        const uint32_t vaddr = smem_base + (gp % kStages) * kStageBytes + kOperandBytes;
-        const uint32_t paddr = p_base + (gp & 1) * kPBytes;
-#pragma unroll
-        for (int part = 0; part < 2; ++part)
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const uint32_t d = tmem_base + kColO + (2 * part + h) * kRows;
-            const uint64_t a = desc_mn_sw128(vaddr + h * kHalfBytes);
-            const uint64_t b = desc_mn_plain16(paddr + part * kPPartBytes);
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks)   // 32 keys per instruction: four 1024-byte groups of V, 512 bytes of P^T
-              tc_mma_f8f6f4(d, a + ks * (4096 >> 4), b + ks * (512 >> 4), kIdescPV, (cp.j == 0 && ks == 0) ? 0u : 1u);
-          }
-        tc_commit(smem_u32(&bars.empty[gp % kStages]));
-        tc_commit(smem_u32(&bars.pv_done[gp & 1]));
-        ++gp;
-        advance(cp);
-        if (*abortp) break;
+        tc_commit(smem_u32(&bars.empty[gs % kStages]));
+        if (c.j == c.it.nt - 1) tc_commit(smem_u32(&bars.q_empty[qb]));
+        trace_event(tp.trace, 1, tn, 22);
+        cursor_next(c, item_recs, n_local);
       }
     }
     __syncwarp();
-  } else if (warp == 6) {
+  } else if (warp == kWarpPV) {
+    // =========================== issuer of O^T += V^T . P^T ===========================
+    if (elect_one()) {
+      Cursor c{0, {}, 0, 0, false};
+      cursor_seek(c, item_recs, n_local);
+      for (uint32_t gp = 0; c.valid && !*abortp; ++gp) {
+        trace_event(tp.trace, 4, tn, 23);
+        mbar_wait(smem_u32(&bars.p_full[gp & 1]), (gp >> 1) & 1, abortp, tp.status, kStatusAttnWait);
+        trace_event(tp.trace, 4, tn, 24);
+        tc_fence_after();
+        const uint32_t vaddr = smem_base + (gp % kStages) * kStageBytes + kOperandBytes;
+        const uint32_t paddr = p_base + (gp & 1) * kPBytes;
+        // four accumulators (two terms of P x two d-halves); the key steps are the outer loop, so that consecutive
+        // instructions go to different accumulators
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)   // 32 keys per instruction: four 1024-byte groups of V, 512 bytes of P^T
+#pragma unroll
+          for (int part = 0; part < 2; ++part)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const uint64_t a = desc_mn_sw128(vaddr + h * kHalfBytes);
+              const uint64_t b = desc_mn_plain16(paddr + part * kPPartBytes);
+              tc_mma_f8f6f4(tmem_base + kColO + (2 * part + h) * kRows, a + ks * (4096 >> 4), b + ks * (512 >> 4),
+                            kIdescPV, (c.j == 0 && ks == 0) ? 0u : 1u);
+            }
+        tc_commit(smem_u32(&bars.empty[gp % kStages]));
+        tc_commit(smem_u32(&bars.pv_done[gp & 1]));
+        trace_event(tp.trace, 4, tn, 25);
+        cursor_next(c, item_recs, n_local);
+      }
+    }
+    __syncwarp();
+  } else if (warp == kWarpQ) {
     // =========================== query staging ===========================
     uint32_t qn = 0;
     for (int li = 0; li < n_local; ++li) {
       const Item it = get_item(item_recs, li);
       if (it.empty) continue;
       const uint32_t qb = qn & 1;
+      // lane owns d = 8 * lane .. + 7 of every row; all rows are requested before the first one is used
+      uint4 raw[NR];
+#pragma unroll
+      for (int r = 0; r < NR; ++r)
+        if (r < G)
+          raw[r] = *reinterpret_cast<const uint4*>(
+              p.q + (static_cast<long long>(it.t) * p.n_q_heads + it.kvh * G + r) * D + lane * 8);
       if (qn >= 2) mbar_wait(smem_u32(&bars.q_empty[qb]), ((qn >> 1) - 1) & 1, abortp, tp.status, kStatusAttnWait);
-      // lane owns d = 8 * lane .. + 7 of every row
       const int half = lane >> 4, chunk = (lane & 15) >> 1, sub = (lane & 1) * 8;
-      for (int r = 0; r < G; ++r) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(
-            p.q + (static_cast<long long>(it.t) * p.n_q_heads + it.kvh * G + r) * D + lane * 8);
-        const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        if (r >= G) continue;
+        const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&raw[r]);
         float f[8];
         float amax = 0.f;
 #pragma unroll
@@ -429,7 +501,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_tc_kernel(const __grid
           f[2 * i + 1] = __bfloat162float(v2[i].y);
           amax = fmaxf(amax, fmaxf(fabsf(f[2 * i]), fabsf(f[2 * i + 1])));
         }
-        amax = warp_max(amax);
+        amax = warp_max_fast(amax);
         const float sc = amax > 0.f ? amax / 448.f : 1.f;
         const float inv = 1.f / sc;
         uint32_t hi[2], lo[2];
@@ -450,73 +522,102 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_tc_kernel(const __grid
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars.q_full[qb]));
+      if (lane == 0) trace_event(tp.trace, 3, tn, 40);
       ++qn;
     }
   } else {
-    // =========================== softmax: thread = key = TMEM lane ===========================
-    const int tid = threadIdx.x;   // 0..127
-    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+    // =========================== softmax: two threads per key (= TMEM lane), half of the rows each ===========
+    constexpr int NH = NR / 2;                 // rows of this thread
+    const int tid = threadIdx.x;               // 0..255
+    const int key_lane = tid & 127;            // key inside the tile = TMEM lane
+    const int rh = warp >> 2;                  // which half of the rows
+    const int row0 = rh * NH;
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const float c_log2e = p.sm_scale * 1.4426950408889634f;
-    uint32_t g = 0, qn = 0;
+    const __half* kscales = reinterpret_cast<const __half*>(p.kv.k_scales);
+    const __half* vscales = reinterpret_cast<const __half*>(p.kv.v_scales);
+    // splits without keys still owe their (max, sum) pair
     for (int li = 0; li < n_local; ++li) {
       const Item it = get_item(item_recs, li);
-      const long long part_row0 = (static_cast<long long>(it.t) * p.n_q_heads + it.kvh * G) * p.n_splits + it.split;
-      if (it.empty) {
-        if (tid < G) {
-          float* ml = p.part_ml + (part_row0 + static_cast<long long>(tid) * p.n_splits) * 2;
-          ml[0] = -CUDART_INF_F;
-          ml[1] = 0.f;
-        }
-        continue;
+      if (it.empty && tid < G) {
+        float* ml = p.part_ml + ((static_cast<long long>(it.t) * p.n_q_heads + it.kvh * G + tid) * p.n_splits + it.split) * 2;
+        ml[0] = -CUDART_INF_F;
+        ml[1] = 0.f;
       }
-      const uint32_t qb = qn & 1;
-      mbar_wait(smem_u32(&bars.q_full[qb]), (qn >> 1) & 1, abortp, tp.status, kStatusAttnWait);
-      float qs[NR], m_run[NR], l_part[NR];
-#pragma unroll
-      for (int r = 0; r < NR; ++r) {
-        qs[r] = q_scale[qb][r] * c_log2e;
-        m_run[r] = -CUDART_INF_F;
-        l_part[r] = 0.f;
-      }
-      mbar_arrive(smem_u32(&bars.q_empty[qb]));
-      float r_run = 0.f;
-      const unsigned long long tmask = p.tree_mask ? p.tree_mask[it.t] : ~0ull;
-      const int tbase = p.tree_mask ? p.tree_base[it.t] : 0x7fffffff;
-      const int* my_boxes = box_rows + li * bpi;
-      const int split_base = it.split * p.split_keys;
-      const __half* kscales = reinterpret_cast<const __half*>(p.kv.k_scales);
-      const __half* vscales = reinterpret_cast<const __half*>(p.kv.v_scales);
-      // the key's scales, fetched one tile ahead of its scores
-      auto fetch = [&](int j, float& ks, float& vs, bool& ok) {
-        const int key = it.k0 + j * kTileKeys + tid;
-        ok = false; ks = 0.f; vs = 0.f;
-        if (key >= it.k_begin && key < it.k_end) {
-          const int box_row = my_boxes[(key - split_base) / kBoxKeys];
-          if (box_row >= 0) {
-            const long long row = box_row + key % kBoxKeys;
-            ks = __half2float(kscales[row]);
-            vs = __half2float(vscales[row]);
-            ok = key < tbase || ((tmask >> (key - tbase)) & 1ull);
+    }
+    // the scales of this thread's key in a tile, fetched one tile ahead of its scores (also across items)
+    auto fetch = [&](const Cursor& c, float& ks, float& vs, bool& ok) {
+      ok = false; ks = 0.f; vs = 0.f;
+      if (!c.valid) return;
+      const int key = c.it.k0 + c.j * kTileKeys + key_lane;
+      if (key >= c.it.k_begin && key < c.it.k_end) {
+        const int box_row = box_rows[c.li * bpi + (key - c.it.split * p.split_keys) / kBoxKeys];
+        if (box_row >= 0) {
+          const long long row = box_row + key % kBoxKeys;
+          ks = __half2float(kscales[row]);
+          vs = __half2float(vscales[row]);
+          if (p.tree_mask != nullptr) {
+            const int tbase = p.tree_base[c.it.t];
+            ok = key < tbase || ((p.tree_mask[c.it.t] >> (key - tbase)) & 1ull);
+          } else {
+            ok = true;
           }
         }
-      };
-      float ks_n, vs_n;
-      bool ok_n;
-      fetch(0, ks_n, vs_n, ok_n);
-      for (int j = 0; j < it.nt; ++j, ++g) {
-        const float ks = ks_n, vs = vs_n;
-        const bool ok = ok_n;
-        if (j + 1 < it.nt) fetch(j + 1, ks_n, vs_n, ok_n);
-        const uint32_t sb = g & 1;
-        mbar_wait(smem_u32(&bars.s_full[sb]), (g >> 1) & 1, abortp, tp.status, kStatusAccumWaitTimeout);
-        tc_fence_after();
-        uint32_t acc[NR];
-        tmem_ld<NR>(tmem_base + lane_sel + sb * kRows, acc);
-        tmem_ld_wait();
-        float s[NR];
+      }
+    };
+    Cursor c{0, {}, 0, 0, false};
+    cursor_seek(c, item_recs, n_local);
+    float ks_n, vs_n;
+    bool ok_n;
+    fetch(c, ks_n, vs_n, ok_n);
+    float qs[NH], m_run[NH], l_part[NH];
+    float r_run = 0.f;
+    for (uint32_t g = 0; c.valid; ++g) {
+      const uint32_t qb = c.qn & 1;
+      if (c.j == 0) {
+        mbar_wait(smem_u32(&bars.q_full[qb]), (c.qn >> 1) & 1, abortp, tp.status, kStatusAttnWait);
 #pragma unroll
-        for (int r = 0; r < NR; ++r) {
-          s[r] = ok ? __uint_as_float(acc[r]) * qs[r] * ks : -CUDART_INF_F;
+        for (int r = 0; r < NH; ++r) {
+          qs[r] = q_scale[qb][row0 + r] * c_log2e;
+          m_run[r] = -CUDART_INF_F;
+          l_part[r] = 0.f;
+        }
+        r_run = 0.f;
+        mbar_arrive(smem_u32(&bars.q_empty[qb]));
+      }
+      const Item it = c.it;
+      const int j = c.j;
+      const float ks = ks_n, vs = vs_n;
+      const bool ok = ok_n;
+      Cursor nx = c;
+      cursor_next(nx, item_recs, n_local);
+      fetch(nx, ks_n, vs_n, ok_n);
+      const uint32_t sb = g & 1;
+      if (tid == 0) trace_event(tp.trace, 2, tn, 30);
+      mbar_wait(smem_u32(&bars.s_full[sb]), (g >> 1) & 1, abortp, tp.status, kStatusAccumWaitTimeout);
+      if (tid == 0) trace_event(tp.trace, 2, tn, 31);
+      tc_fence_after();
+      uint32_t acc[4][NH];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) tmem_ld<NH>(tmem_base + lane_sel + (sb * 4 + q4) * kRows + row0, acc[q4]);
+      tmem_ld_wait();
+      float s[NH];
+      bool exceed = ok && vs > 2.f * r_run;
+#pragma unroll
+      for (int r = 0; r < NH; ++r) {
+        const float dot = (__uint_as_float(acc[0][r]) + __uint_as_float(acc[1][r])) +
+                          (__uint_as_float(acc[2][r]) + __uint_as_float(acc[3][r]));
+        s[r] = ok ? dot * qs[r] * ks : -CUDART_INF_F;
+        exceed |= s[r] > m_run[r] + kFrameSlack;   // (always true for a visible key while the row has no frame yet)
+      }
+      // Frames: a row's softmax frame m and the V-scale frame R only move when some key leaves the slack above them.
+      // One barrier-with-OR says whether any does; on most tiles none does and no maximum is computed at all.
+      bool moved = false;
+      float fcorr[NH];
+      float rr = 1.f;
+      if (softmax_any(exceed)) {
+#pragma unroll
+        for (int r = 0; r < NH; ++r) {
           const float wm = warp_max_fast(s[r]);
           if (lane == 0) red_m[sb][warp][r] = wm;
         }
@@ -525,12 +626,10 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_tc_kernel(const __grid
           if (lane == 0) red_v[sb][warp] = wv;
         }
         softmax_bar();
-        // Frames: a row's frame moves only when the tile's maximum leaves the slack above it (or it has none yet).
-        float fcorr[NR];
-        bool moved = false;
+        const int w0 = rh * 4;
 #pragma unroll
-        for (int r = 0; r < NR; ++r) {
-          const float tm = fmaxf(fmaxf(red_m[sb][0][r], red_m[sb][1][r]), fmaxf(red_m[sb][2][r], red_m[sb][3][r]));
+        for (int r = 0; r < NH; ++r) {
+          const float tm = fmaxf(fmaxf(red_m[sb][w0][r], red_m[sb][w0 + 1][r]), fmaxf(red_m[sb][w0 + 2][r], red_m[sb][w0 + 3][r]));
           fcorr[r] = 1.f;
           if (tm > m_run[r] + kFrameSlack || (m_run[r] == -CUDART_INF_F && tm > -CUDART_INF_F)) {
             fcorr[r] = m_run[r] == -CUDART_INF_F ? 0.f : exp2f(m_run[r] - tm);
@@ -538,91 +637,107 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_tc_kernel(const __grid
             moved = true;
           }
         }
-        const float tv = fmaxf(fmaxf(red_v[sb][0], red_v[sb][1]), fmaxf(red_v[sb][2], red_v[sb][3]));
-        float rr = 1.f;
+        const float tv = fmaxf(fmaxf(red_v[sb][w0], red_v[sb][w0 + 1]), fmaxf(red_v[sb][w0 + 2], red_v[sb][w0 + 3]));
         if (tv > 2.f * r_run) {
           rr = r_run / tv;   // (r_run == 0: nothing was accumulated in the old frame)
           r_run = tv;
           moved = true;
         }
-        // the P^T buffer of this parity was read by the product of two tiles ago
-        if (g >= 2) mbar_wait(smem_u32(&bars.pv_done[sb]), ((g >> 1) - 1) & 1, abortp, tp.status, kStatusAttnWait);
-        if (moved && j > 0) {
-          // O^T holds sums in the old frames: wait for the previous product, rescale this thread's 4 x NR columns
-          mbar_wait(smem_u32(&bars.pv_done[(g - 1) & 1]), ((g - 1) >> 1) & 1, abortp, tp.status, kStatusAttnWait);
-          tc_fence_after();
-#pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            uint32_t o[NR];
-            const uint32_t oaddr = tmem_base + lane_sel + kColO + h * kRows;
-            tmem_ld<NR>(oaddr, o);
-            tmem_ld_wait();
-#pragma unroll
-            for (int r = 0; r < NR; ++r) o[r] = __float_as_uint(__uint_as_float(o[r]) * fcorr[r] * rr);
-            tmem_st<NR>(oaddr, o);
-          }
-          tmem_st_wait();
-#pragma unroll
-          for (int r = 0; r < NR; ++r) l_part[r] *= fcorr[r];
-        }
-        const float vw = (ok && r_run > 0.f) ? vs / r_run * kPScale : 0.f;
-        uint32_t hi[kRows / 4] = {}, lo[kRows / 4] = {};
-#pragma unroll
-        for (int r = 0; r < NR; r += 2) {
-          const float p0 = ok ? exp2f(s[r] - m_run[r]) : 0.f;
-          const float p1 = ok ? exp2f(s[r + 1] - m_run[r + 1]) : 0.f;
-          l_part[r] += p0;
-          l_part[r + 1] += p1;
-          const uint32_t w = split_e4m3x2_scaled(p0 * vw, p1 * vw);
-          hi[r >> 2] |= (w & 0xffff) << (8 * (r & 3));
-          lo[r >> 2] |= (w >> 16) << (8 * (r & 3));
-        }
-        uint8_t* pdst = smem_gen + kStages * kStageBytes + 2 * kQBytes + sb * kPBytes + tid * kRows;
-        *reinterpret_cast<uint4*>(pdst) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-        *reinterpret_cast<uint4*>(pdst + kPPartBytes) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        fence_proxy_async_smem();
-        tc_fence_before();
-        mbar_arrive(smem_u32(&bars.p_full[sb]));
       }
-      // ---- the item's partial result ----
-      mbar_wait(smem_u32(&bars.pv_done[(g - 1) & 1]), ((g - 1) >> 1) & 1, abortp, tp.status, kStatusAttnWait);
-      tc_fence_after();
-      const float oscale = r_run / kPScale;
+      if (tid == 0) trace_event(tp.trace, 2, tn, 32);
+      // the P^T buffer of this parity was read by the product of two tiles ago
+      if (g >= 2) mbar_wait(smem_u32(&bars.pv_done[sb]), ((g >> 1) - 1) & 1, abortp, tp.status, kStatusAttnWait);
+      if (moved && j > 0) {
+        // O^T holds sums in the old frames: wait for the previous product, rescale this thread's 4 x NH columns
+        mbar_wait(smem_u32(&bars.pv_done[(g - 1) & 1]), ((g - 1) >> 1) & 1, abortp, tp.status, kStatusAttnWait);
+        tc_fence_after();
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t o[NR], ol[NR];
-        tmem_ld<NR>(tmem_base + lane_sel + kColO + h * kRows, o);
-        tmem_ld<NR>(tmem_base + lane_sel + kColO + (2 + h) * kRows, ol);
-        tmem_ld_wait();
+        for (int h = 0; h < 4; ++h) {
+          uint32_t o[NH];
+          const uint32_t oaddr = tmem_base + lane_sel + kColO + h * kRows + row0;
+          tmem_ld<NH>(oaddr, o);
+          tmem_ld_wait();
 #pragma unroll
-        for (int r = 0; r < NR; ++r)
-          if (r < G)
-            p.part_o[(part_row0 + static_cast<long long>(r) * p.n_splits) * D + h * 128 + tid] =
-                (__uint_as_float(o[r]) + __uint_as_float(ol[r]) * (1.f / kLoScale)) * oscale;
+          for (int r = 0; r < NH; ++r) o[r] = __float_as_uint(__uint_as_float(o[r]) * fcorr[r] * rr);
+          tmem_st<NH>(oaddr, o);
+        }
+        tmem_st_wait();
+#pragma unroll
+        for (int r = 0; r < NH; ++r) l_part[r] *= fcorr[r];
       }
+      if (tid == 0) trace_event(tp.trace, 2, tn, 33 + (moved && j > 0 ? 1 : 0));
+      const float vw = (ok && r_run > 0.f) ? vs / r_run * kPScale : 0.f;
+      uint32_t hi[NH / 4 + 1] = {}, lo[NH / 4 + 1] = {};
+#pragma unroll
+      for (int r = 0; r < NH; r += 2) {
+        const float p0 = ok ? exp2f(s[r] - m_run[r]) : 0.f;
+        const float p1 = ok ? exp2f(s[r + 1] - m_run[r + 1]) : 0.f;
+        l_part[r] += p0;
+        l_part[r + 1] += p1;
+        const uint32_t w = split_e4m3x2_scaled(p0 * vw, p1 * vw);
+        hi[r >> 2] |= (w & 0xffff) << (8 * (r & 3));
+        lo[r >> 2] |= (w >> 16) << (8 * (r & 3));
+      }
+      uint8_t* pdst = smem_gen + kStages * kStageBytes + 2 * kQBytes + sb * kPBytes + key_lane * kRows + row0;
+      if constexpr (NH == 2) {
+        *reinterpret_cast<uint16_t*>(pdst) = static_cast<uint16_t>(hi[0]);
+        *reinterpret_cast<uint16_t*>(pdst + kPPartBytes) = static_cast<uint16_t>(lo[0]);
+      } else if constexpr (NH == 4) {
+        *reinterpret_cast<uint32_t*>(pdst) = hi[0];
+        *reinterpret_cast<uint32_t*>(pdst + kPPartBytes) = lo[0];
+      } else {
+        *reinterpret_cast<uint2*>(pdst) = make_uint2(hi[0], hi[1]);
+        *reinterpret_cast<uint2*>(pdst + kPPartBytes) = make_uint2(lo[0], lo[1]);
+      }
+      fence_proxy_async_smem();
       tc_fence_before();
+      mbar_arrive(smem_u32(&bars.p_full[sb]));
+      if (tid == 0) trace_event(tp.trace, 2, tn, 35);
+
+      if (j == it.nt - 1) {
+        // ---- the item's partial result ----
+        const long long part_row0 = (static_cast<long long>(it.t) * p.n_q_heads + it.kvh * G) * p.n_splits + it.split;
 #pragma unroll
-      for (int r = 0; r < NR; ++r) {
-        const float ws = warp_sum(l_part[r]);
-        if (lane == 0) red_l[warp][r] = ws;
-      }
-      softmax_bar();
-      if (tid < G) {
-        float mine = -CUDART_INF_F;
+        for (int r = 0; r < NH; ++r) {
+          const float ws = warp_sum(l_part[r]);
+          if (lane == 0) red_l[warp][r] = ws;
+        }
+        mbar_wait(smem_u32(&bars.pv_done[sb]), (g >> 1) & 1, abortp, tp.status, kStatusAttnWait);
+        tc_fence_after();
+        const float oscale = r_run / kPScale;
 #pragma unroll
-        for (int r = 0; r < NR; ++r) mine = (r == tid) ? m_run[r] : mine;
-        float* ml = p.part_ml + (part_row0 + static_cast<long long>(tid) * p.n_splits) * 2;
-        ml[0] = mine;
-        ml[1] = red_l[0][tid] + red_l[1][tid] + red_l[2][tid] + red_l[3][tid];
+        for (int h = 0; h < 2; ++h) {
+          uint32_t o[NH], ol[NH];
+          tmem_ld<NH>(tmem_base + lane_sel + kColO + h * kRows + row0, o);
+          tmem_ld<NH>(tmem_base + lane_sel + kColO + (2 + h) * kRows + row0, ol);
+          tmem_ld_wait();
+#pragma unroll
+          for (int r = 0; r < NH; ++r)
+            if (row0 + r < G)
+              p.part_o[(part_row0 + static_cast<long long>(row0 + r) * p.n_splits) * D + h * 128 + key_lane] =
+                  (__uint_as_float(o[r]) + __uint_as_float(ol[r]) * (1.f / kLoScale)) * oscale;
+        }
+        tc_fence_before();
+        softmax_bar();
+        // row r is written by lane (r % NH) of the first warp of the half that owns it
+        if ((warp & 3) == 0 && lane < NH && row0 + lane < G) {
+          float mine = -CUDART_INF_F;
+#pragma unroll
+          for (int r = 0; r < NH; ++r) mine = (r == lane) ? m_run[r] : mine;
+          float* ml = p.part_ml + (part_row0 + static_cast<long long>(row0 + lane) * p.n_splits) * 2;
+          ml[0] = mine;
+          ml[1] = red_l[warp][lane] + red_l[warp + 1][lane] + red_l[warp + 2][lane] + red_l[warp + 3][lane];
+        }
+        softmax_bar();   // red_l is reused by the next item
+        if (tid == 0) trace_event(tp.trace, 2, tn, 36);
       }
-      softmax_bar();   // red_l is reused by the next item
-      ++qn;
+      c = nx;
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == kWarpS) tmem_dealloc(tmem_base, kTmemCols);
 }
 
 struct MapKey {
@@ -684,6 +799,14 @@ int sm_count() {
 
 }  // namespace
 
+// Development aid: switch the event trace of CTA 0 on / off and copy it out ([5 roles][1024] entries, 0 = unused).
+void paged_attention_tc_trace(bool enable, unsigned long long* host_out) {
+  if (host_out != nullptr) cudaMemcpyFromSymbol(host_out, g_attn_trace, sizeof(g_attn_trace));
+  static const unsigned long long zeros[kTraceRoles * kTraceLen] = {};
+  cudaMemcpyToSymbol(g_attn_trace, zeros, sizeof(zeros));
+  g_attn_trace_on = enable;
+}
+
 // Returns cudaErrorNotSupported when the problem is outside this kernel (the caller falls back to the mma.sync one).
 cudaError_t paged_attention_tc_split(const PagedAttnParams& p, cudaStream_t stream, bool pdl) {
   const int G = p.n_q_heads / p.n_kv_heads;
@@ -701,6 +824,7 @@ cudaError_t paged_attention_tc_split(const PagedAttnParams& p, cudaStream_t stre
   tp.a = p;
   tp.G = G;
   tp.status = p.status;
+  tp.trace = g_attn_trace_on ? 1 : 0;
   const long long items = static_cast<long long>(p.Tq) * p.n_kv_heads * p.n_splits;
   if (items > 0x7fffffffLL) return cudaErrorNotSupported;
   tp.n_items = static_cast<int>(items);

@@ -375,6 +375,13 @@ void paged_attention(const Tensor& q, int64_t n_q_heads, int64_t n_kv_heads, int
   chk(nfb::paged_attention(p, cur_stream(), pdl));
 }
 
+// Development aid: returns the event trace of CTA 0 of the tcgen05 attention kernel and switches tracing on / off.
+Tensor attn_tc_trace(bool enable) {
+  Tensor out = at::zeros({5, 1024}, at::TensorOptions().dtype(at::kLong));
+  nfb::paged_attention_tc_trace(enable, reinterpret_cast<unsigned long long*>(out.data_ptr()));
+  return out;
+}
+
 void paged_attention_prefill(const Tensor& q, int64_t n_q_heads, int64_t n_kv_heads, int64_t head_dim,
                              const Tensor& q_seq, const Tensor& q_kv_len, const Tensor& blk_start,
                              const Tensor& blk_count, const Tensor& block_table, const Tensor& k_codes,
@@ -870,6 +877,7 @@ TORCH_LIBRARY(nfb200, m) {
   m.def("gemm_bf16(Tensor x, Tensor w, Tensor? out, int epi, Tensor? resid, Tensor? bias, Tensor? partial, int splits, Tensor? status, bool pdl, int act=0, Tensor? conv_w=None, Tensor? conv_state=None, Tensor? conv_slot=None, Tensor? conv_out=None, Tensor? prefetch=None) -> ()", &gemm_bf16);
   m.def("gemm_trace(bool enable, int n_ctas) -> Tensor", &gemm_trace);
   m.def("gemm_timeline(int mode) -> (int, Tensor)", &gemm_timeline);
+  m.def("attn_tc_trace(bool enable) -> Tensor", &attn_tc_trace);
   m.def("gemm_pick_splits(int T, int N, int K, int epi) -> int", &gemm_pick_splits);
   m.def("add_rmsnorm(Tensor? partial, int splits, Tensor? delta, Tensor? resid_in, Tensor? resid_out, Tensor? norm_w, Tensor? normed, int T, int N, float eps, bool unit_offset, bool pdl, Tensor? q_codes=None, Tensor? q_sf=None) -> ()", &add_rmsnorm);
   m.def("embed_gather(Tensor ids, Tensor table, Tensor out, bool pdl) -> ()", &embed_gather);
