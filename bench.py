@@ -259,9 +259,10 @@ def main() -> int:
     ap.add_argument("--emulate-tp-shard", type=int, default=0,
                     help="debug only: run ONE rank's 1/W shard of the tensor-parallel model on one GPU (no peers, so no "
                          "NVLink latency): the per-rank kernel chain of a W-GPU round (result is marked invalid)")
-    ap.add_argument("--tp-mode", default="fused", choices=["fused", "oneshot", "nccl"],
+    ap.add_argument("--tp-mode", default="auto", choices=["auto", "fused", "oneshot", "nccl"],
                     help="tensor-parallel reduction: fused = reduce-scatter + all-gather inside the GEMMs, oneshot = "
-                         "every rank receives every tile + one sum kernel, nccl = NCCL all-reduce baseline")
+                         "every rank receives every tile + one sum kernel, nccl = NCCL all-reduce baseline, auto = the "
+                         "faster of fused / oneshot at this GPU count as measured (TensorParallel.best_mode)")
     ap.add_argument("--spec", default="none", choices=["none", "mtp", "hook"],
                     help="speculative decoding run (one GPU, eager rounds): mtp = the draft module proposes (random-init "
                          "weights accept next to nothing), hook = synthetic drafts of mixed quality taken from the plain "
@@ -312,6 +313,8 @@ def main() -> int:
     elif world > 1:
         from ninfer_fusion_b200.parallel.tp import TensorParallel
 
+        if args.tp_mode == "auto":
+            args.tp_mode = TensorParallel.best_mode(world)
         comm = TensorParallel(cfg, rank, world, device, max_tokens=max(args.batch, 2048), mode=args.tp_mode)
         shard = comm.geometry
         weights = comm.random_shard_weights(seed=0)
@@ -329,6 +332,8 @@ def main() -> int:
         cfg = replace(cfg, name=f"{cfg.name} (EMULATED 1/{Wd} SHARD: INVALID)", n_q_heads=cfg.n_q_heads // Wd,
                       n_kv_heads=max(1, cfg.n_kv_heads // Wd), gdn_qk_heads=cfg.gdn_qk_heads // Wd,
                       gdn_v_heads=cfg.gdn_v_heads // Wd, ffn_inter=cfg.ffn_inter // Wd, vocab=cfg.vocab // Wd)
+        if args.tp_mode == "auto":
+            args.tp_mode = "fused"
         comm = TensorParallel.loopback(cfg, 1, device, max_tokens=max(args.batch, 2048), mode=args.tp_mode)[0]
         shard = comm.geometry
         weights = random_weights(cfg, device, seed=0)

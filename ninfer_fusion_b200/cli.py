@@ -203,14 +203,15 @@ def build_engine(args, cfg: ModelConfig, weights, ranks=None) -> Optional[Engine
         if args.kv_layer_spec:
             from .kv.policy import parse_layer_storage
             kv = parse_layer_storage(args.kv_layer_spec, len(cfg.attn_layers))
-        comm = TensorParallel(cfg, rank, world, args.device, max_tokens=max(args.prefill_chunk, args.max_lanes))
+        comm = TensorParallel(cfg, rank, world, args.device, max_tokens=max(args.prefill_chunk, args.max_lanes),
+                              mode=TensorParallel.best_mode(world))
         text = {k: v for k, v in weights.items() if not k.startswith("vision/")}
         if any(hasattr(v, "qtype") for v in text.values()):
             raise SystemExit("--tp: give bf16 weights (every rank quantises its own shard: --weights applies after the split)")
         shard_w = comm.shard(text)
-        if args.weights == "bf16":
+        if args.weights == "bf16" and comm.mode == "fused":
             shard_w = comm.fold_norms(dict(shard_w))
-        elif args.weights != "stored":
+        elif args.weights not in ("stored", "bf16"):
             shard_w = quantize_weights(shard_w, args.weights)
         inner_factory = program_factory(args, cfg, shard_w, kv, shard=comm.geometry, comm=comm)
         if rank != 0:

@@ -1,7 +1,8 @@
 // Split-KV paged decode / verify attention on the 5th-generation tensor cores, fp8-row KV pages, head_dim 256.
 //
 // The e4m3 codes of the cache are the MMA operands as they lie in the pages: no dequantisation, no register
-// staging.  A persistent CTA (one per SM) walks its share of the (query token, kv head, key split) items and runs
+// staging.  A persistent CTA (one per SM) takes an equal share of the 128-key tiles of all (query token, kv head)
+// rows -- rows are cut where CTA boundaries fall, each piece fills one partial-result slot of its row -- and runs
 // the whole problem TRANSPOSED, so that the 128 MMA rows are keys instead of the handful of query rows of a GQA
 // group:
 //
@@ -41,6 +42,7 @@
 #include <cuda_fp8.h>
 #include <math_constants.h>
 
+#include <algorithm>
 #include <mutex>
 #include <unordered_map>
 
@@ -75,7 +77,7 @@ constexpr float kPScale = 1.f;      // p' = kPScale * p * v_scale / R <= 16 * 2
 constexpr float kLoScale = 128.f;   // second term of P: 128 x the residual (<= half an e4m3 step of 32, i.e. <= 128)
 constexpr float kFrameSlack = 4.f;  // log2 units a score may exceed its row's frame before the frame moves
 constexpr int kMaxItems = 256;      // items one CTA may walk (their descriptors live in shared memory)
-constexpr int kMaxBoxes = 1024;     // 64-key boxes of those items (cache rows looked up once, in the prologue)
+constexpr int kMaxBoxes = 512;      // 64-key boxes of those items (cache rows looked up once, in the prologue)
 constexpr int kColO = 8 * kRows;    // first O^T column: [hi d0-127][hi d128-255][lo d0-127][lo d128-255]
 
 enum : int { kStatusAttnWait = 6 };
@@ -94,33 +96,19 @@ __device__ __forceinline__ void trace_event(int on, int role, int& n, int code) 
 
 struct TcParams {
   PagedAttnParams a;
-  int n_items;
   int G;
   int* status;
   int trace;
 };
 
+// A piece of work: tiles [k0, k_end) of one (query token, kv head) row, visible keys [k_begin, k_end), partial result
+// slot `split` of that row.  Pieces are cut by the prologue so that every CTA gets the same number of 128-key tiles.
 struct Item {
-  int t, kvh, split, k_begin, k_end, k0, nt;
-  bool empty;
+  int t, kvh, split, k_begin, k_end, k0, nt, box0;
 };
-// What the prologue keeps per item; everything else is derived.
 struct ItemRec {
-  int t, kvh_split, k_begin, k_end;
+  int t, kvh_split, k_begin, k_end, k0, box0;
 };
-
-__device__ __forceinline__ ItemRec make_item(const PagedAttnParams& p, int idx) {
-  ItemRec r;
-  const int split = idx % p.n_splits;
-  const int q = idx / p.n_splits;
-  const int kvh = q % p.n_kv_heads;
-  r.t = q / p.n_kv_heads;
-  r.kvh_split = (kvh << 16) | split;
-  const int kv_len = p.q_kv_len[r.t];
-  r.k_begin = max(split * p.split_keys, p.window > 0 ? kv_len - p.window : 0);
-  r.k_end = p.q_seq[r.t] < 0 ? r.k_begin : min(kv_len, (split + 1) * p.split_keys);   // no table row: empty
-  return r;
-}
 __device__ __forceinline__ Item get_item(const ItemRec* recs, int i) {
   const ItemRec r = recs[i];
   Item it;
@@ -129,10 +117,17 @@ __device__ __forceinline__ Item get_item(const ItemRec* recs, int i) {
   it.split = r.kvh_split & 0xffff;
   it.k_begin = r.k_begin;
   it.k_end = r.k_end;
-  it.empty = r.k_begin >= r.k_end;
-  it.k0 = r.k_begin & ~(kTileKeys - 1);
-  it.nt = it.empty ? 0 : (r.k_end - it.k0 + kTileKeys - 1) / kTileKeys;
+  it.k0 = r.k0;
+  it.nt = (r.k_end - r.k0 + kTileKeys - 1) / kTileKeys;
+  it.box0 = r.box0;
   return it;
+}
+// tiles of a (token, head) row and where they start: a window drops the keys before kv_len - window
+__device__ __forceinline__ int row_tiles(const PagedAttnParams& p, int t, int& k_lo, int& kv_len) {
+  kv_len = p.q_kv_len[t];
+  k_lo = p.window > 0 ? max(0, kv_len - p.window) : 0;
+  if (p.q_seq[t] < 0 || kv_len <= k_lo) return 0;
+  return (kv_len - (k_lo & ~(kTileKeys - 1)) + kTileKeys - 1) / kTileKeys;
 }
 
 // ---- descriptors ----
@@ -250,14 +245,10 @@ struct Cursor {
   bool valid;
 };
 __device__ __forceinline__ void cursor_seek(Cursor& c, const ItemRec* recs, int n_local) {
-  c.valid = false;
-  for (; c.li < n_local; ++c.li) {
+  c.valid = c.li < n_local;
+  if (c.valid) {
     c.it = get_item(recs, c.li);
-    if (!c.it.empty) {
-      c.valid = true;
-      c.j = 0;
-      return;
-    }
+    c.j = 0;
   }
 }
 __device__ __forceinline__ void cursor_next(Cursor& c, const ItemRec* recs, int n_local) {
@@ -281,7 +272,8 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_tc_kernel(const __grid
   __shared__ float red_v[2][kSoftmaxWarps];
   __shared__ float red_l[kSoftmaxWarps][kRows / 2];
   __shared__ ItemRec item_recs[kMaxItems];
-  __shared__ int box_rows[kMaxBoxes];   // [local item][box of its split]: first cache row of the box, or -1
+  __shared__ int box_rows[kMaxBoxes];   // boxes of this CTA's pieces in order: first cache row of the box, or -1
+  __shared__ int part_sh[4];            // prologue: total tiles, longest row, pieces, boxes
 
   const PagedAttnParams& p = tp.a;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -335,22 +327,137 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_tc_kernel(const __grid
   pdl_wait_prior();   // q, the new token's cache rows and the step's tables come from earlier kernels
 
   const int H = p.n_kv_heads, P = p.kv.page_size;
-  // ---- this CTA's items and the cache rows of their boxes, looked up once: no role chases a table afterwards ----
-  const int n_local = (tp.n_items - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
-  const int bpi = p.split_keys / kBoxKeys;   // boxes per item
-  for (int i = threadIdx.x; i < n_local; i += kThreads) item_recs[i] = make_item(p, blockIdx.x + i * gridDim.x);
+  // ---- partition: every CTA takes the same number of consecutive 128-key tiles of the flattened (row, tile) list;
+  // a row cut by a CTA boundary yields one piece (and one partial-result slot) per CTA that touches it.  The tile
+  // counts and their prefix sums live in the K half of stage 0 until the first TMA load overwrites it. ----
+  const int R = p.Tq * H;
+  int* sc = reinterpret_cast<int*>(smem_gen);            // [R + 1] tile counts, then exclusive prefix sums
+  int* chunk_sum = sc + R + 1;                            // [kThreads]
+  if (threadIdx.x < 4) part_sh[threadIdx.x] = 0;
   __syncthreads();
-  for (int e = threadIdx.x; e < n_local * bpi; e += kThreads) {
-    const int i = e / bpi, b = e % bpi;
-    const ItemRec r = item_recs[i];
-    const int key0 = (r.kvh_split & 0xffff) * p.split_keys + b * kBoxKeys;
-    int row = -1;
-    if (key0 < r.k_end && key0 + kBoxKeys > r.k_begin) {
-      const int page = p.block_table[static_cast<long long>(p.q_seq[r.t]) * p.table_stride + key0 / P];
-      if (page >= 0) row = (page * H + (r.kvh_split >> 16)) * P + key0 % P;
+  {
+    int longest = 0;
+    for (int r = threadIdx.x; r < R; r += kThreads) {
+      int k_lo, kv_len;
+      const int nt = row_tiles(p, r / H, k_lo, kv_len);
+      sc[r] = nt;
+      longest = max(longest, nt);
     }
-    box_rows[e] = row;
+    longest = __reduce_max_sync(0xffffffffu, longest);
+    if (lane == 0) atomicMax(&part_sh[1], longest);
   }
+  __syncthreads();
+  const int chunk = (R + kThreads - 1) / kThreads;
+  {
+    int sum = 0;
+    for (int r = threadIdx.x * chunk; r < min(R, (threadIdx.x + 1) * chunk); ++r) sum += sc[r];
+    chunk_sum[threadIdx.x] = sum;
+  }
+  __syncthreads();
+  if (warp == 0) {   // exclusive scan of the kThreads chunk sums: 12 per lane, then across the warp
+    constexpr int kPer = kThreads / 32;
+    int loc[kPer], tot = 0;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) { loc[i] = tot; tot += chunk_sum[lane * kPer + i]; }
+    int inc = tot;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += v;
+    }
+    const int base = inc - tot;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) chunk_sum[lane * kPer + i] = base + loc[i];
+    if (lane == 31) part_sh[0] = inc;
+  }
+  __syncthreads();
+  {
+    int run = chunk_sum[threadIdx.x];
+    for (int r = threadIdx.x * chunk; r < min(R, (threadIdx.x + 1) * chunk); ++r) {
+      const int nt = sc[r];
+      sc[r] = run;
+      run += nt;
+    }
+    if (threadIdx.x == 0) sc[R] = part_sh[0];
+  }
+  __syncthreads();
+  const int total_tiles = part_sh[0];
+  // tiles per CTA: an equal share, but never so small that the longest row would need more slots than it has
+  const int share = max(1, max((total_tiles + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x),
+                               (part_sh[1] + max(1, p.n_splits - 1) - 1) / max(1, p.n_splits - 1)));
+  const int my_lo = min(total_tiles, static_cast<int>(blockIdx.x) * share);
+  const int my_hi = min(total_tiles, my_lo + share);
+  if (threadIdx.x == 0 && my_lo < my_hi) {
+    // first row that reaches past my_lo (binary search over the prefix sums), then walk
+    int lo = 0, hi = R;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (sc[mid + 1] <= my_lo) lo = mid + 1; else hi = mid;
+    }
+    int n = 0, boxes = 0, pos = my_lo;
+    for (int r = lo; r < R && pos < my_hi; ++r) {
+      const int nt = sc[r + 1] - sc[r];
+      if (nt == 0) continue;
+      const int a = pos - sc[r], b = min(nt, my_hi - sc[r]);
+      if (n < kMaxItems && boxes + 2 * (b - a) <= kMaxBoxes) {
+        int k_lo, kv_len;
+        row_tiles(p, r / H, k_lo, kv_len);
+        const int k0 = (k_lo & ~(kTileKeys - 1)) + a * kTileKeys;
+        ItemRec rec;
+        rec.t = r / H;
+        rec.kvh_split = ((r % H) << 16) | (static_cast<int>(blockIdx.x) - sc[r] / share);
+        rec.k_begin = max(k_lo, k0);
+        rec.k_end = min(kv_len, k0 + (b - a) * kTileKeys);
+        rec.k0 = k0;
+        rec.box0 = boxes;
+        item_recs[n++] = rec;
+        boxes += 2 * (b - a);
+      } else {
+        abort_flag = 1;   // (the host bounds the share; a violation means an argument lied about the lengths)
+        report_status(tp.status, kStatusBadArgument);
+      }
+      pos = sc[r] + b;
+    }
+    part_sh[2] = n;
+    part_sh[3] = boxes;
+  }
+  // partial-result slots that no piece fills: the CTA that holds a row's first tile closes the row's unused slots;
+  // rows without keys are closed round-robin
+  for (int r = threadIdx.x; r < R; r += kThreads) {
+    const int nt = sc[r + 1] - sc[r];
+    int first_empty = -1;
+    if (nt == 0) {
+      if (r % static_cast<int>(gridDim.x) == static_cast<int>(blockIdx.x)) first_empty = 0;
+    } else if (sc[r] / share == static_cast<int>(blockIdx.x)) {
+      first_empty = (sc[r] + nt - 1) / share - static_cast<int>(blockIdx.x) + 1;
+    }
+    if (first_empty >= 0) {
+      const long long row0 = (static_cast<long long>(r / H) * p.n_q_heads + (r % H) * G) * p.n_splits;
+      for (int g2 = 0; g2 < G; ++g2)
+        for (int sl = first_empty; sl < p.n_splits; ++sl) {
+          float* ml = p.part_ml + (row0 + static_cast<long long>(g2) * p.n_splits + sl) * 2;
+          ml[0] = -CUDART_INF_F;
+          ml[1] = 0.f;
+        }
+    }
+  }
+  __syncthreads();
+  const int n_local = part_sh[2];
+  // the cache rows of the pieces' boxes, looked up once: no role chases a table afterwards
+  for (int i = 0; i < n_local; ++i) {
+    const ItemRec r = item_recs[i];
+    const int nb = 2 * ((r.k_end - r.k0 + kTileKeys - 1) / kTileKeys);
+    for (int b2 = threadIdx.x; b2 < nb; b2 += kThreads) {
+      const int key0 = r.k0 + b2 * kBoxKeys;
+      int row = -1;
+      if (key0 < r.k_end && key0 + kBoxKeys > r.k_begin) {
+        const int page = p.block_table[static_cast<long long>(p.q_seq[r.t]) * p.table_stride + key0 / P];
+        if (page >= 0) row = (page * H + (r.kvh_split >> 16)) * P + key0 % P;
+      }
+      box_rows[r.box0 + b2] = row;
+    }
+  }
+  fence_proxy_async_smem();   // the scratch words above lie where the first TMA load lands
   __syncthreads();
   if (threadIdx.x == 0) trace_event(tp.trace, 2, tn, 1);
 
@@ -361,8 +468,6 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_tc_kernel(const __grid
       uint32_t g = 0;
       for (int li = 0; li < n_local; ++li) {
         const Item it = get_item(item_recs, li);
-        if (it.empty) continue;
-        const int first_box = (it.k0 - it.split * p.split_keys) / kBoxKeys;
         for (int j = 0; j < it.nt; ++j, ++g) {
           const int stage = g % kStages;
           trace_event(tp.trace, 0, tn, 10);
@@ -374,8 +479,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_tc_kernel(const __grid
           uint32_t bytes = 0;
 #pragma unroll
           for (int b = 0; b < 2; ++b) {
-            const int box = first_box + 2 * j + b;
-            rows[b] = box < bpi ? box_rows[li * bpi + box] : -1;
+            rows[b] = box_rows[it.box0 + 2 * j + b];
             if (rows[b] >= 0) bytes += 4 * kBoxBytes;
           }
           const uint32_t full = smem_u32(&bars.full[stage]);
@@ -478,7 +582,6 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_tc_kernel(const __grid
     uint32_t qn = 0;
     for (int li = 0; li < n_local; ++li) {
       const Item it = get_item(item_recs, li);
-      if (it.empty) continue;
       const uint32_t qb = qn & 1;
       // lane owns d = 8 * lane .. + 7 of every row; all rows are requested before the first one is used
       uint4 raw[NR];
@@ -536,22 +639,13 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attn_tc_kernel(const __grid
     const float c_log2e = p.sm_scale * 1.4426950408889634f;
     const __half* kscales = reinterpret_cast<const __half*>(p.kv.k_scales);
     const __half* vscales = reinterpret_cast<const __half*>(p.kv.v_scales);
-    // splits without keys still owe their (max, sum) pair
-    for (int li = 0; li < n_local; ++li) {
-      const Item it = get_item(item_recs, li);
-      if (it.empty && tid < G) {
-        float* ml = p.part_ml + ((static_cast<long long>(it.t) * p.n_q_heads + it.kvh * G + tid) * p.n_splits + it.split) * 2;
-        ml[0] = -CUDART_INF_F;
-        ml[1] = 0.f;
-      }
-    }
     // the scales of this thread's key in a tile, fetched one tile ahead of its scores (also across items)
     auto fetch = [&](const Cursor& c, float& ks, float& vs, bool& ok) {
       ok = false; ks = 0.f; vs = 0.f;
       if (!c.valid) return;
       const int key = c.it.k0 + c.j * kTileKeys + key_lane;
       if (key >= c.it.k_begin && key < c.it.k_end) {
-        const int box_row = box_rows[c.li * bpi + (key - c.it.split * p.split_keys) / kBoxKeys];
+        const int box_row = box_rows[c.it.box0 + (key - c.it.k0) / kBoxKeys];
         if (box_row >= 0) {
           const long long row = box_row + key % kBoxKeys;
           ks = __half2float(kscales[row]);
@@ -825,13 +919,17 @@ cudaError_t paged_attention_tc_split(const PagedAttnParams& p, cudaStream_t stre
   tp.G = G;
   tp.status = p.status;
   tp.trace = g_attn_trace_on ? 1 : 0;
-  const long long items = static_cast<long long>(p.Tq) * p.n_kv_heads * p.n_splits;
-  if (items > 0x7fffffffLL) return cudaErrorNotSupported;
-  tp.n_items = static_cast<int>(items);
-  const int grid = static_cast<int>(items < sm_count() ? items : sm_count());
-  // the per-CTA item and box tables are fixed-size shared arrays
-  const long long per_cta = (items + grid - 1) / grid;
-  if (per_cta > kMaxItems || per_cta * (p.split_keys / kBoxKeys) > kMaxBoxes || p.n_splits > 0xffff) return cudaErrorNotSupported;
+  // The kernel cuts the (token, kv head) rows into pieces itself (equal numbers of 128-key tiles per CTA); n_splits
+  // is the number of partial-result slots a row has, split_keys only bounds the context (kv_len <= n_splits x
+  // split_keys).  Rows are only cut when they have at least two slots.
+  const long long rows = static_cast<long long>(p.Tq) * p.n_kv_heads;
+  const long long row_tiles_max = (static_cast<long long>(p.n_splits) * p.split_keys + kTileKeys - 1) / kTileKeys;
+  if (p.n_splits < 2 || p.n_splits > 0xffff || rows + 1 + kThreads > kOperandBytes / 4) return cudaErrorNotSupported;
+  const long long work = rows * row_tiles_max;
+  const int grid = static_cast<int>(work < sm_count() ? work : sm_count());
+  // shared tables of one CTA: at most kMaxBoxes / 2 tiles and kMaxItems pieces (one piece has at least one tile)
+  const long long share_max = std::max((work + grid - 1) / grid, (row_tiles_max + p.n_splits - 2) / (p.n_splits - 1));
+  if (share_max > kMaxBoxes / 2 || share_max > kMaxItems) return cudaErrorNotSupported;
   if (G <= 4) return launch_tc<4>(tk, tv, tp, grid, stream, pdl);
   if (G <= 8) return launch_tc<8>(tk, tv, tp, grid, stream, pdl);
   return launch_tc<16>(tk, tv, tp, grid, stream, pdl);

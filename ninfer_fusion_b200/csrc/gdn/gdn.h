@@ -59,6 +59,15 @@ struct GdnParams {
   // the current state, produces its output, and leaves the state as it was.  Tokens are visited in buffer order, so
   // a side branch must directly follow the state it hangs off.
   const unsigned char* commit = nullptr;
+  // Decode with the causal convolution fused in (exactly one token per sequence, state written, no seq_end / commit):
+  // `qkv` is then the RAW input projection (conv channel c at column c), conv_w is [C, 4], conv_state [slots, 3, C]
+  // holds the last three inputs of every channel; q_off / k_off / v_off index conv channels.  The kernel applies the
+  // four taps and SiLU, rounds to bf16 like the separate conv kernel does, and rolls the history; the CTAs of the
+  // value heads that share a key head form a cluster, so that all of them have read the shared q / k history before
+  // one of them rewrites it.
+  const __nv_bfloat16* conv_w = nullptr;
+  __nv_bfloat16* conv_state = nullptr;
+  int conv_C = 0;
 };
 const char* gdn_recurrent(const GdnParams& p, cudaStream_t stream, bool pdl);
 // Multi-token variant (token groups staged in shared memory); gdn_recurrent dispatches to it when T > n_seq.

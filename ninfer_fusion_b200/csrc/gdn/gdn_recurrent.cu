@@ -28,6 +28,7 @@ __global__ void __launch_bounds__(kThreads, 2) gdn_recurrent_kernel(const GdnPar
   __shared__ __align__(16) float k_s[kThreads / 32][kDk];
   __shared__ __align__(16) float q_s[kThreads / 32][kDk];
   __shared__ float red[2][kThreads / 32];
+  __shared__ __align__(16) float conv_q[kDk], conv_k[kDk], conv_v[kDv];   // fused-conv decode: this CTA's q, k, v rows
 
   pdl_launch_next();
   // The step description (sequence ranges, state slots) is uploaded before the step's first kernel and the state
@@ -40,11 +41,31 @@ __global__ void __launch_bounds__(kThreads, 2) gdn_recurrent_kernel(const GdnPar
   const int sub = lane >> 3, q8 = lane & 7;
   const int hk = hv / (p.n_v_heads / p.n_qk_heads);
   const int t_begin = p.cu_seqlens[seq], t_end = p.seq_end != nullptr ? p.seq_end[seq] : p.cu_seqlens[seq + 1];
+  const int ratio = p.n_v_heads / p.n_qk_heads;
+  const bool fused = p.conv_w != nullptr;
   if (t_end <= t_begin) {
     pdl_wait_prior();   // every CTA waits before it leaves: a later kernel's wait then still implies all earlier ones
+    if (fused && ratio > 1) cluster_sync_all();   // (the cluster's CTAs share the sequence: all of them are here)
     return;
   }
   const int slot = p.state_slot[seq];
+  // fused conv: thread i < 128 owns q channel i and v channel i of this CTA's heads, thread 128 + i k channel i.  The
+  // history is as old as the state (written one step ago): it is requested before the dependency wait as well.
+  const int ci = threadIdx.x & 127;
+  const int ch_a = threadIdx.x < 128 ? p.q_off + hk * kDk + ci : p.k_off + hk * kDk + ci;
+  const int ch_v = p.v_off + hv * kDv + ci;
+  float hist_a[3] = {0.f, 0.f, 0.f}, hist_v[3] = {0.f, 0.f, 0.f};
+  __nv_bfloat16* st_a = nullptr;
+  __nv_bfloat16* st_v = nullptr;
+  if (fused) {
+    st_a = p.conv_state + static_cast<long long>(slot) * 3 * p.conv_C + ch_a;
+    st_v = p.conv_state + static_cast<long long>(slot) * 3 * p.conv_C + ch_v;
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      hist_a[j] = __bfloat162float(st_a[j * p.conv_C]);
+      if (threadIdx.x < 128) hist_v[j] = __bfloat162float(st_v[j * p.conv_C]);
+    }
+  }
 
   // thread's rows: r_j = warp*16 + j*4 + sub ; columns: float4 index q8 + 8*i
   float* sbase = p.state + (static_cast<long long>(slot) * p.n_v_heads + hv) * kDv * kDk;
@@ -60,15 +81,59 @@ __global__ void __launch_bounds__(kThreads, 2) gdn_recurrent_kernel(const GdnPar
   const float qscale = rsqrtf(static_cast<float>(kDk));
   if (p.seq_end == nullptr) pdl_wait_prior();   // the projections of this step's tokens come from the previous kernel
 
+  if (fused) {
+    // four taps + SiLU on this CTA's 384 channels, rounded to bf16 like the separate kernel's output; then the roll
+    const __nv_bfloat16* xrow = p.qkv + static_cast<long long>(t_begin) * p.ld_qkv;
+    auto conv1 = [&](int ch, const float* hist, float x) {
+      const uint2 wv = *reinterpret_cast<const uint2*>(p.conv_w + static_cast<long long>(ch) * 4);
+      const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
+      float a = __bfloat162float(wp[0].x) * hist[0];
+      a += __bfloat162float(wp[0].y) * hist[1];
+      a += __bfloat162float(wp[1].x) * hist[2];
+      a += __bfloat162float(wp[1].y) * x;
+      a = a / (1.f + __expf(-a));
+      return __bfloat162float(__float2bfloat16(a));
+    };
+    const float xa = __bfloat162float(xrow[ch_a]);
+    (threadIdx.x < 128 ? conv_q : conv_k)[ci] = conv1(ch_a, hist_a, xa);
+    float xv = 0.f;
+    if (threadIdx.x < 128) {
+      xv = __bfloat162float(xrow[ch_v]);
+      conv_v[ci] = conv1(ch_v, hist_v, xv);
+    }
+    if (ratio > 1) cluster_sync_all();   // every value head of this key head has read the shared q / k history
+    else __syncthreads();
+    if (hv % ratio == 0) {
+      st_a[0] = __float2bfloat16(hist_a[1]);
+      st_a[p.conv_C] = __float2bfloat16(hist_a[2]);
+      st_a[2 * p.conv_C] = __float2bfloat16(xa);
+    }
+    if (threadIdx.x < 128) {
+      st_v[0] = __float2bfloat16(hist_v[1]);
+      st_v[p.conv_C] = __float2bfloat16(hist_v[2]);
+      st_v[2 * p.conv_C] = __float2bfloat16(xv);
+    }
+  }
+
   for (int t = t_begin; t < t_end; ++t) {
     // ---- per-warp copy of the normalised q, k of this token ----
     const __nv_bfloat16* row = p.qkv + static_cast<long long>(t) * p.ld_qkv;
-    const uint2 kr = *reinterpret_cast<const uint2*>(row + p.k_off + hk * kDk + lane * 4);
-    const uint2 qr = *reinterpret_cast<const uint2*>(row + p.q_off + hk * kDk + lane * 4);
-    const __nv_bfloat162* kp = reinterpret_cast<const __nv_bfloat162*>(&kr);
-    const __nv_bfloat162* qp = reinterpret_cast<const __nv_bfloat162*>(&qr);
-    const float kf[4] = {__bfloat162float(kp[0].x), __bfloat162float(kp[0].y), __bfloat162float(kp[1].x), __bfloat162float(kp[1].y)};
-    const float qf[4] = {__bfloat162float(qp[0].x), __bfloat162float(qp[0].y), __bfloat162float(qp[1].x), __bfloat162float(qp[1].y)};
+    float kf[4], qf[4];
+    if (fused) {
+      const float4 k4f = *reinterpret_cast<const float4*>(&conv_k[lane * 4]);
+      const float4 q4f = *reinterpret_cast<const float4*>(&conv_q[lane * 4]);
+      kf[0] = k4f.x; kf[1] = k4f.y; kf[2] = k4f.z; kf[3] = k4f.w;
+      qf[0] = q4f.x; qf[1] = q4f.y; qf[2] = q4f.z; qf[3] = q4f.w;
+    } else {
+      const uint2 kr = *reinterpret_cast<const uint2*>(row + p.k_off + hk * kDk + lane * 4);
+      const uint2 qr = *reinterpret_cast<const uint2*>(row + p.q_off + hk * kDk + lane * 4);
+      const __nv_bfloat162* kp = reinterpret_cast<const __nv_bfloat162*>(&kr);
+      const __nv_bfloat162* qp = reinterpret_cast<const __nv_bfloat162*>(&qr);
+      kf[0] = __bfloat162float(kp[0].x); kf[1] = __bfloat162float(kp[0].y);
+      kf[2] = __bfloat162float(kp[1].x); kf[3] = __bfloat162float(kp[1].y);
+      qf[0] = __bfloat162float(qp[0].x); qf[1] = __bfloat162float(qp[0].y);
+      qf[2] = __bfloat162float(qp[1].x); qf[3] = __bfloat162float(qp[1].y);
+    }
     const float ssk = warp_sum(kf[0] * kf[0] + kf[1] * kf[1] + kf[2] * kf[2] + kf[3] * kf[3]);
     const float ssq = warp_sum(qf[0] * qf[0] + qf[1] * qf[1] + qf[2] * qf[2] + qf[3] * qf[3]);
     const float ik = rsqrtf(ssk + 1e-6f), iq = rsqrtf(ssq + 1e-6f) * qscale;
@@ -106,7 +171,7 @@ __global__ void __launch_bounds__(kThreads, 2) gdn_recurrent_kernel(const GdnPar
 #pragma unroll
     for (int j = 0; j < kRowsPerThread; ++j) {
       const int r = warp * 16 + j * 4 + sub;
-      const float v = __bfloat162float(row[p.v_off + hv * kDv + r]);
+      const float v = fused ? conv_v[r] : __bfloat162float(row[p.v_off + hv * kDv + r]);
       // same summation tree as the prefill kernels, so decode, prefill and replay stay bit-consistent
       float kp4[4];
 #pragma unroll
@@ -180,13 +245,31 @@ const char* gdn_recurrent(const GdnParams& p, cudaStream_t stream, bool pdl) {
   if (p.T <= 0 || p.n_seq <= 0) return nullptr;
   if (p.n_v_heads % p.n_qk_heads) return "gdn_recurrent: value heads must be a multiple of qk heads";
   if ((p.q_off | p.k_off | p.ld_qkv) % 4) return "gdn_recurrent: q/k offsets must be multiples of 4";
-  if (p.T > p.n_seq && (p.v_off | p.z_off | p.ld_proj) % 4 == 0) return gdn_prefill(p, stream, pdl);
+  const int ratio = p.n_v_heads / p.n_qk_heads;
+  if (p.conv_w != nullptr) {
+    if (p.T != p.n_seq || p.seq_end != nullptr || p.commit != nullptr || !p.write_state)
+      return "gdn_recurrent: the fused convolution is for plain decode steps (one token per sequence, state written)";
+    if (p.conv_state == nullptr || p.conv_C <= 0 || ratio > 8) return "gdn_recurrent: bad fused-convolution arguments";
+  } else if (p.T > p.n_seq && (p.v_off | p.z_off | p.ld_proj) % 4 == 0) {
+    return gdn_prefill(p, stream, pdl);
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.n_v_heads, p.n_seq); cfg.blockDim = dim3(kThreads); cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (p.conv_w != nullptr && ratio > 1) {   // the value heads of one key head share its q / k history: one cluster
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = ratio;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  cfg.attrs = attr; cfg.numAttrs = na;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gdn_recurrent_kernel, p);
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }

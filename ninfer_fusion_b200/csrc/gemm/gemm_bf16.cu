@@ -282,21 +282,11 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
 
   // ---------------- epilogue: all four warps, warp w owns TMEM lanes 32w..32w+31 ----------------
   pdl_wait_prior();
-  // kEpiRsAg, CTA that owns its tile: what the reduction reads from global memory (its bookkeeping word and the
-  // residual of the first 32 token rows) is fetched now, so that the latency hides under the main loop
-  uint4 resid_pre[4] = {};
+  // kEpiRsAg: the bookkeeping word of this CTA's tile (its epoch) is fetched now, so that the latency hides under
+  // the main loop
   uint32_t epoch_pre = 0;
   if constexpr (EPI == kEpiRsAg) {
     if (p.cluster <= 1 || blockIdx.z == 0) epoch_pre = p.rs_state->tile_epoch[blockIdx.x * kRsMaxTokenTiles + blockIdx.y];
-    if (n0 / p.slice_cols == p.rank && p.rs_phase != 1 && (p.cluster <= 1 || blockIdx.z == 0)) {
-      const int r = threadIdx.x >> 2, t = t0 + r;
-      if (r < TN && t < p.T) {
-        const uint4* src = reinterpret_cast<const uint4*>(p.peer_x[p.rank] + static_cast<long long>(t) * p.ld_resid + n0 +
-                                                          (threadIdx.x & 3) * 32);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) resid_pre[q] = src[q];
-      }
-    }
   }
   if constexpr (EPI == kEpiStore) {
     // decode conv tiles: pull this thread's history columns towards L2 now (fire and forget), so that the
@@ -469,20 +459,20 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
       if (threadIdx.x == 0) red_release_sys_add(p.peer_flag[owner], 1u);
     } else if constexpr (EPI == kEpiRsAg) {
       const int owner = n0 / p.slice_cols;
-      const bool mine = owner == p.rank;
-      const bool pushes = p.rs_phase != 2 && (!mine || p.rs_phase == 1);
-      const bool reduces = mine && p.rs_phase != 1;
+      const bool pushes = p.rs_phase != 2;
+      const bool reduces = p.rs_phase != 1;
       // Every call of this tile carries the next epoch: the tile's fp32 values travel as (value, epoch) pairs, so
-      // the owner sees from the data itself when a peer's tile is complete.  No fence and no counter sit between
-      // the peer's stores and the owner's loads (16-byte stores are not torn).
+      // the reader sees from the data itself when a tile is complete.  No fence and no counter sit between the
+      // writer's stores and the reader's loads (16-byte stores are not torn).  Every tile of one state object is
+      // written once per call, so all tiles carry the same epoch.
       unsigned int* epoch_word = &p.rs_state->tile_epoch[blockIdx.x * kRsMaxTokenTiles + blockIdx.y];
       const uint32_t epoch = epoch_pre + 1u;
       // The fp32 tile goes through shared memory (behind the split-K landing zone of the idle pipeline stages) so
-      // that the second half works on token rows: a quarter row (32 columns) per thread, 16-byte accesses, long
-      // contiguous runs per token towards a peer.
+      // that the push works on token rows: a quarter row (32 columns) per thread, 16-byte accesses, long
+      // contiguous runs per token towards the owner.
       constexpr int kRowPad = kTileN + 4;   // floats per row: shifts consecutive rows by four banks
       float* tile_s = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw))) + (S - 1) * TN * 128;
-      if (p.rs_phase != 2) {
+      if (pushes) {
         for (int c = 0; c < TN; c += kChunk) {
           if (t0 + c >= p.T) break;
           float v[kChunk];
@@ -493,12 +483,12 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
       }
       if (threadIdx.x == 0) rs_ok = 1;
       __syncthreads();
-      const int seg = threadIdx.x & 3;            // quarter of the tile's 128 columns
-      const int col = seg * 32;                   // first column of this thread inside the tile
-      const int n_first = n0 + col;               // ... in the output
-      const int n_local = n_first - owner * p.slice_cols;
       if (pushes) {
-        // hop 1: rows of the tile into the owner's receive buffer [src][T_cap][slice] of (value, epoch) pairs
+        // hop 1: rows of the tile into the owner's receive buffer [src][T_cap][slice] of (value, epoch) pairs --
+        // the owner's own tiles take the same road (into its own buffer), so that the reduction below reads every
+        // contribution the same way and can run on any CTA
+        const int col = (threadIdx.x & 3) * 32;
+        const int n_local = n0 + col - owner * p.slice_cols;
         uint2* dst = p.peer_recv_ll[owner] + static_cast<long long>(p.rank) * p.T_cap * p.slice_cols + n_local;
         for (int r = threadIdx.x >> 2; r < TN; r += 32) {
           const int t = t0 + r;
@@ -514,89 +504,85 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
         }
         stamp(7);
       }
-      if (reduces) {
+      // hop 2, spread over the grid: this rank owns T x slice_cols values; they are cut into units of one token x
+      // eight columns, one unit per thread, and dealt to the leading CTAs of the grid.  A thread has the 64 bytes
+      // of all `world` contributions in flight at once, so a unit costs one round of polling instead of one per
+      // contribution (a tile's owner CTA reducing its whole tile alone needed 2 x (world - 1) dependent rounds).
+      const int n_ctas = gridDim.x * gridDim.y;                       // (split-K helpers never get here)
+      const int cta = blockIdx.x + gridDim.x * blockIdx.y;
+      const int groups = p.slice_cols / 8;                            // 8-column groups per token
+      const int units = p.T * groups;
+      const int n_red = min(n_ctas, (units + 127) / 128);
+      if (reduces && cta < n_red) {
         stamp(8);
         __nv_bfloat16* my_x = p.peer_x[p.rank];
-        const uint2* recv = p.peer_recv_ll[p.rank] + n_local;
-        for (int r0 = 0; r0 < TN; r0 += 32) {      // uniform trip count: the shuffles below need whole warps
-          const int r = r0 + (threadIdx.x >> 2);
-          const int t = t0 + r;
-          bool live = r < TN && t < p.T;
+        const uint2* recv = p.peer_recv_ll[p.rank];
+        for (int u0 = cta * 128; u0 < units; u0 += n_red * 128) {    // uniform trip count per CTA
+          const int u = u0 + threadIdx.x;
+          const bool live0 = u < units;
+          const int t = live0 ? u / groups : 0;
+          const int cg = live0 ? u % groups : 0;
+          const int n_first = p.rank * p.slice_cols + cg * 8;         // first output column of the unit
+          bool live = live0;
+          float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          uint4 rv = make_uint4(0, 0, 0, 0);
+          if (live) {
+            rv = *reinterpret_cast<const uint4*>(my_x + static_cast<long long>(t) * p.ld_resid + n_first);
+            uint4 v[kMaxRanks][4];
+            bool here = false;
+            for (uint32_t spin = 0; spin < kPeerPollLimit && !here; ++spin) {
+              here = true;
+#pragma unroll
+              for (int src = 0; src < kMaxRanks; ++src) {
+                if (src >= p.world) break;
+                const uint4* sp = reinterpret_cast<const uint4*>(recv + (static_cast<long long>(src) * p.T_cap + t) * p.slice_cols + cg * 8);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  v[src][q] = ld_volatile_v4(sp + q);
+                  here = here && v[src][q].y == epoch && v[src][q].w == epoch;
+                }
+              }
+              if (!here) {
+                if ((spin & 1023u) == 1023u && p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) break;
+                if (spin > 64) __nanosleep(100);
+              }
+            }
+            if (!here) {   // bounded: record it and let the step fail on the host instead of hanging
+              report_status(p.status, kStatusPeerWaitTimeout);
+              rs_ok = 0;
+              live = false;
+            }
+#pragma unroll
+            for (int src = 0; src < kMaxRanks; ++src) {   // rank order, the same on every rank
+              if (src >= p.world) break;
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                a[2 * q] += __uint_as_float(v[src][q].x);
+                a[2 * q + 1] += __uint_as_float(v[src][q].z);
+              }
+            }
+          }
           float ss = 0.f;
-          float4 a[8];
           if (live) {
-            if (p.rs_phase == 0) {
-              const float4* own = reinterpret_cast<const float4*>(tile_s + r * kRowPad + col);
+            const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
+            uint4 o;
+            uint32_t* op = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
-              for (int q = 0; q < 8; ++q) a[q] = own[q];
-            } else {
-#pragma unroll
-              for (int q = 0; q < 8; ++q) a[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int e = 0; e < 4; ++e) {
+              op[e] = pack_bf16x2(a[2 * e] + __bfloat162float(rp[e].x), a[2 * e + 1] + __bfloat162float(rp[e].y));
+              const __nv_bfloat162 ob = *reinterpret_cast<const __nv_bfloat162*>(&op[e]);
+              const float f0 = __bfloat162float(ob.x), f1 = __bfloat162float(ob.y);
+              ss += f0 * f0 + f1 * f1;
             }
-            for (int src = 0; src < p.world && live; ++src) {   // rank order, the same on every rank's owner
-              if (p.rs_phase == 0 && src == p.rank) continue;
-              const uint4* sp = reinterpret_cast<const uint4*>(recv + (static_cast<long long>(src) * p.T_cap + t) * p.slice_cols);
-#pragma unroll
-              for (int half = 0; half < 2; ++half) {
-                uint4 v[8];
-                bool here = false;
-                for (uint32_t spin = 0; spin < kPeerPollLimit && !here; ++spin) {
-                  here = true;
-#pragma unroll
-                  for (int q = 0; q < 8; ++q) {
-                    v[q] = ld_volatile_v4(sp + half * 8 + q);
-                    here = here && v[q].y == epoch && v[q].w == epoch;
-                  }
-                  if (!here) {
-                    if ((spin & 1023u) == 1023u && p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) break;
-                    if (spin > 64) __nanosleep(100);
-                  }
-                }
-                if (!here) {   // bounded: record it and let the step fail on the host instead of hanging
-                  report_status(p.status, kStatusPeerWaitTimeout);
-                  rs_ok = 0;
-                  live = false;
-                }
-#pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                  float4& acc = a[half * 4 + q / 2];
-                  if (q & 1) { acc.z += __uint_as_float(v[q].x); acc.w += __uint_as_float(v[q].z); }
-                  else { acc.x += __uint_as_float(v[q].x); acc.y += __uint_as_float(v[q].z); }
-                }
-              }
-            }
-          }
-          if (live) {
             const long long at = static_cast<long long>(t) * p.ld_resid + n_first;
-            uint4 o[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint4 rv = r0 == 0 ? resid_pre[q] : *reinterpret_cast<const uint4*>(my_x + at + q * 8);
-              const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
-              const float4 lo = a[2 * q], hi = a[2 * q + 1];
-              uint32_t* op = reinterpret_cast<uint32_t*>(&o[q]);
-              op[0] = pack_bf16x2(lo.x + __bfloat162float(rp[0].x), lo.y + __bfloat162float(rp[0].y));
-              op[1] = pack_bf16x2(lo.z + __bfloat162float(rp[1].x), lo.w + __bfloat162float(rp[1].y));
-              op[2] = pack_bf16x2(hi.x + __bfloat162float(rp[2].x), hi.y + __bfloat162float(rp[2].y));
-              op[3] = pack_bf16x2(hi.z + __bfloat162float(rp[3].x), hi.w + __bfloat162float(rp[3].y));
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const __nv_bfloat162 ob = *reinterpret_cast<const __nv_bfloat162*>(&op[e]);
-                const float f0 = __bfloat162float(ob.x), f1 = __bfloat162float(ob.y);
-                ss += f0 * f0 + f1 * f1;
-              }
-            }
-            for (int rk = 0; rk < p.world; ++rk) {   // hop 2: all-gather by push (own copy included)
-              uint4* dst = reinterpret_cast<uint4*>(p.peer_x[rk] + at);
-#pragma unroll
-              for (int q = 0; q < 4; ++q) dst[q] = o[q];
-            }
+            for (int rk = 0; rk < p.world; ++rk)   // all-gather by push (own copy included)
+              *reinterpret_cast<uint4*>(p.peer_x[rk] + at) = o;
           }
-          // the four threads of a token row: sum of squares of the tile's 128 columns
-          ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-          ss += __shfl_xor_sync(0xffffffffu, ss, 2);
-          if (live && seg == 0) {
-            const int tile_global = n0 / kTileN;
+          // the sixteen threads of one (token, 128-column tile): its sum of squares (a dead unit adds zero)
+#pragma unroll
+          for (int o2 = 1; o2 < 16; o2 <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o2);
+          if (live && (threadIdx.x & 15) == 0) {
+            const int tile_global = n_first / kTileN;
             for (int rk = 0; rk < p.world; ++rk)
               p.peer_ss[rk][static_cast<long long>(t) * kRsSsStride + tile_global] = ss;
           }
@@ -610,9 +596,9 @@ __global__ void __launch_bounds__(128) gemm_ws_kernel(const __grid_constant__ CU
         stamp(11);
       }
       if (threadIdx.x == 0 && p.rs_phase != 1) *epoch_word = epoch;
-      // what the next consumer of the residual stream has to wait for: one arrival per (column tile, token tile)
+      // what the next consumer of the residual stream has to wait for: one arrival per reducing CTA of every rank
       if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && p.rs_phase != 1)
-        p.rs_state->x_expected += static_cast<unsigned int>((p.N / kTileN) * gridDim.y);
+        p.rs_state->x_expected += static_cast<unsigned int>(n_red * p.world);
     } else {
       const int n = n0 + warp * 32 + lane;
       const float bias = ((EPI == kEpiStore || EPI == kEpiResidual) && p.bias != nullptr && n < p.N) ? p.bias[n] : 0.f;

@@ -472,7 +472,7 @@ void gdn_recurrent(const Tensor& qkv, int64_t q_off, int64_t k_off, int64_t v_of
                    int64_t a_off, int64_t b_off, int64_t n_qk_heads, int64_t n_v_heads, const Tensor& A_log,
                    const Tensor& dt_bias, const Tensor& norm_w, double eps, const Tensor& cu_seqlens,
                    const Tensor& state_slot, const Tensor& state, bool write_state, const Tensor& out, bool pdl,
-                   OptT seq_end, OptT commit, OptT chunk_ws) {
+                   OptT seq_end, OptT commit, OptT chunk_ws, OptT conv_w, OptT conv_state) {
   need(qkv, at::kBFloat16, "qkv"); need_rows(qkv, "qkv"); need(proj, at::kBFloat16, "proj"); need_rows(proj, "proj");
   need(A_log, at::kFloat, "A_log"); need(dt_bias, at::kFloat, "dt_bias"); need(norm_w, at::kBFloat16, "norm_w");
   need(cu_seqlens, at::kInt, "cu_seqlens"); need(state_slot, at::kInt, "state_slot");
@@ -506,6 +506,18 @@ void gdn_recurrent(const Tensor& qkv, int64_t q_off, int64_t k_off, int64_t v_of
     need(*commit, at::kByte, "commit");
     TORCH_CHECK(commit->numel() == p.T, "commit [T]");
     p.commit = static_cast<const unsigned char*>(commit->data_ptr());
+  }
+  if (conv_w.has_value() && conv_w->defined()) {
+    // decode with the causal convolution fused in: `qkv` is the raw projection, channel c at column c
+    TORCH_CHECK(conv_state.has_value() && conv_state->defined(), "conv_state required with conv_w");
+    need(*conv_w, at::kBFloat16, "conv_w"); need(*conv_state, at::kBFloat16, "conv_state");
+    TORCH_CHECK(conv_w->is_contiguous() && conv_w->dim() == 2 && conv_w->size(1) == 4, "conv_w must be [C, 4]");
+    TORCH_CHECK(conv_state->is_contiguous() && conv_state->dim() == 3 && conv_state->size(1) == 3 &&
+                conv_state->size(2) == conv_w->size(0), "conv_state must be [slots, 3, C]");
+    TORCH_CHECK(conv_w->size(0) <= qkv.size(1) && reinterpret_cast<uintptr_t>(conv_w->data_ptr()) % 8 == 0, "conv_w layout");
+    p.conv_w = static_cast<const __nv_bfloat16*>(conv_w->data_ptr());
+    p.conv_state = static_cast<__nv_bfloat16*>(conv_state->data_ptr());
+    p.conv_C = static_cast<int>(conv_w->size(0));
   }
   if (chunk_ws.has_value() && chunk_ws->defined()) {
     // chunked tensor-core formulation (long prefill chunks)
@@ -887,7 +899,7 @@ TORCH_LIBRARY(nfb200, m) {
   m.def("kv_requant(Tensor tiers, Tensor anchor, Tensor src_cell, Tensor dst_cell, int page_size, int n_kv_heads, int head_dim) -> ()", &kv_requant);
   m.def("prefill_attn_block_tokens(int n_q_heads, int n_kv_heads) -> int", &prefill_attn_block_tokens);
   m.def("causal_conv1d_silu(Tensor x, int c_off, int C, Tensor w, Tensor cu_seqlens, Tensor token_seq, Tensor state_slot, Tensor conv_state, Tensor out, bool update_state, bool one_token_per_seq, bool pdl, Tensor? seq_end=None, bool state_only=False, Tensor? parent=None, Tensor? last_token=None) -> ()", &causal_conv1d_silu);
-  m.def("gdn_recurrent(Tensor qkv, int q_off, int k_off, int v_off, Tensor proj, int z_off, int a_off, int b_off, int n_qk_heads, int n_v_heads, Tensor A_log, Tensor dt_bias, Tensor norm_w, float eps, Tensor cu_seqlens, Tensor state_slot, Tensor state, bool write_state, Tensor out, bool pdl, Tensor? seq_end=None, Tensor? commit=None, Tensor? chunk_ws=None) -> ()", &gdn_recurrent);
+  m.def("gdn_recurrent(Tensor qkv, int q_off, int k_off, int v_off, Tensor proj, int z_off, int a_off, int b_off, int n_qk_heads, int n_v_heads, Tensor A_log, Tensor dt_bias, Tensor norm_w, float eps, Tensor cu_seqlens, Tensor state_slot, Tensor state, bool write_state, Tensor out, bool pdl, Tensor? seq_end=None, Tensor? commit=None, Tensor? chunk_ws=None, Tensor? conv_w=None, Tensor? conv_state=None) -> ()", &gdn_recurrent);
   m.def("gdn_chunked_workspace_bytes(int T, int n_seq, int n_v_heads) -> int", &gdn_chunked_workspace_bytes);
   m.def("gdn_prefill_trace(bool enable) -> Tensor", &gdn_prefill_trace);
   m.def("kv_move_rows(Tensor block_table, Tensor table_row, Tensor src_pos, Tensor dst_pos, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int n_kv_heads, int head_dim, int format, int group) -> ()", &kv_move_rows);

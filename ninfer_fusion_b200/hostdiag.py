@@ -30,6 +30,7 @@ TENSOR_KEYS = {"name", "kind", "shape", "format", "layout", "offset", "bytes"}
 RESOURCE_KEYS = {"name", "kind", "encoding", "offset", "bytes"}
 KNOWN_FORMATS = {"BF16", "FP32", "I32", "Q4G64_F16S", "Q5G64_F16S", "Q6G64_F16S", "W8G32_F16S", "NVFP4",
                  "FP8_E4M3FN_ROW_BF16S", "FP8_E4M3FN_BLOCK128_F32S"}
+TENSOR_ALIGNMENT = 256
 LIB_DIRS = ("/usr/lib/x86_64-linux-gnu", "/usr/lib64", "/usr/local/cuda/lib64", "/usr/local/cuda/targets/x86_64-linux/lib",
             "/usr/lib/wsl/lib")
 
@@ -97,8 +98,9 @@ def read_directory(path):
             raise ValueError(f"object '{o.get('name')}': member set is not the closed set of its kind")
         if o["kind"] == "tensor" and o["format"] not in KNOWN_FORMATS:
             raise ValueError(f"object '{o['name']}': unknown format '{o['format']}'")
-        if o["offset"] < end_prev or o["offset"] % 256:
-            raise ValueError(f"object '{o['name']}': payloads must be ordered, 256-byte aligned and non-overlapping")
+        if o["offset"] < end_prev or (o["kind"] == "tensor" and o["offset"] % TENSOR_ALIGNMENT):
+            raise ValueError(f"object '{o['name']}': payloads must be ordered and non-overlapping, tensors "
+                             f"{TENSOR_ALIGNMENT}-byte aligned")
         end_prev = o["offset"] + o["bytes"]
     if start + end_prev > size:
         raise ValueError("payloads run past the end of the file")

@@ -253,6 +253,8 @@ class HybridModel:
         # the separate conv kernel both on one GPU (13.78 vs 13.56 ms per round) and on a 1/8 shard (4.73 vs 4.37 ms),
         # so it is off unless asked for.
         self._fuse_conv_env = os.environ.get("NFB_FUSE_CONV")
+        # decode convolution inside the recurrent GDN step (NFB_FUSE_GDN_CONV=1 switches it on)
+        self._fuse_gdn_conv = os.environ.get("NFB_FUSE_GDN_CONV", "0") == "1"
         # decode: every GEMM asks L2 for the head of the NEXT GEMM's weights once its own loads are in flight
         # (NFB_L2_PREFETCH=0 switches the hint off)
         self.l2_prefetch = os.environ.get("NFB_L2_PREFETCH", "1") != "0"
@@ -476,6 +478,17 @@ class HybridModel:
                               (self.w[f"{prefix}/gdn/conv_w"], st.conv[gi], b.state_slot, conv))
         else:
             self._gemm_normed(ws, T, w_in, proj, prefetch=self.w[f"{prefix}/gdn/out_proj"])
+            if (self._fuse_gdn_conv and decode and write_state and rec is None and b.tree_parent is None
+                    and b.tree_commit is None):
+                # decode: the four taps, SiLU and the history roll run inside the recurrent step (one launch less)
+                qk = g.gdn_qk_dim
+                out = ws.mix_gdn[:T]
+                ops.gdn_recurrent(proj, 0, qk, 2 * qk, proj, C, C + g.gdn_v_dim, C + g.gdn_v_dim + g.gdn_v_heads,
+                                  g.gdn_qk_heads, g.gdn_v_heads, self.w[f"{prefix}/gdn/A_log"],
+                                  self.w[f"{prefix}/gdn/dt_bias"], self.w[f"{prefix}/gdn/norm"], cfg.rms_eps, b.cu_seqlens,
+                                  b.state_slot, st.ssm[gi], True, out, self.pdl, None, None, None,
+                                  self.w[f"{prefix}/gdn/conv_w"], st.conv[gi])
+                return out, self.w[f"{prefix}/gdn/out_proj"]
             ops.causal_conv1d_silu(proj, 0, C, self.w[f"{prefix}/gdn/conv_w"], b.cu_seqlens, b.token_seq, b.state_slot,
                                    st.conv[gi], conv, write_state, decode, self.pdl, None, False, b.tree_parent, None)
         qk = g.gdn_qk_dim

@@ -181,6 +181,15 @@ def test_conv_and_gdn_recurrent(ops, lens, heads):
                       dt_bias.cuda(), nw.cuda(), 1e-6, cu.cuda(), torch.tensor(slots).int().cuda(), ssm_v, False,
                       out_v, False)
     assert torch.equal(ssm_v.cpu(), ssm) and torch.equal(out_v, out)
+    if all(n == 1 for n in lens):
+        # decode: the same step with the convolution inside the recurrent kernel gives the same bits and the same
+        # history as the two launches above
+        conv_f, ssm_f = conv_state.clone().cuda(), ssm.clone().cuda()
+        out_f = torch.full_like(out, float("nan"))
+        ops.gdn_recurrent(proj.cuda(), 0, qk, 2 * qk, proj.cuda(), C, C + vd, C + vd + hv, hk, hv, A_log.cuda(),
+                          dt_bias.cuda(), nw.cuda(), 1e-6, cu.cuda(), torch.tensor(slots).int().cuda(), ssm_f, True, out_f,
+                          False, None, None, None, conv_w.cuda(), conv_f)
+        assert torch.equal(out_f, out) and torch.equal(ssm_f, ssm_g) and torch.equal(conv_f, conv_state_g)
 
     for b, n in enumerate(lens):
         s, e = int(cu[b]), int(cu[b + 1])
