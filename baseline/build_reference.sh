@@ -43,7 +43,7 @@ timeout "${REF_BUILD_SECONDS:-7200}" ninja -C "$BUILD" -k 0 ${JOBS:+-j$JOBS} $TA
 cd "$BUILD"
 MUX="$BUILD/mux"
 mkdir -p "$MUX"
-EXCL='/w8/.*\.cu\.o|w4a4|gqa_attention_decode_e8|gqa_attention_decode_i8|gqa_attention_decode_nvfp4|gqa_attention_decode_iso3|softmax_attention/dense'
+EXCL='/w8/.*\.cu\.o|w4a4|gqa_attention_decode_e8|gqa_attention_decode_i8|gqa_attention_prefill|gqa_attention_decode_nvfp4|gqa_attention_decode_iso3|softmax_attention/dense'
 OBJS=$(find src/CMakeFiles/ninfer_ops.dir -name "*.o" | grep -Ev "$EXCL" | sort | tr '\n' ' ')
 BOBJS=""
 for b in $BENCHES; do

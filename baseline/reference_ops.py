@@ -51,16 +51,11 @@ def commands(T: int, context: int):
         ("gdn_step", N_GDN * calls, ["gated_delta_net", "--batch-update", "--batch", str(sb), "--warmup", "10", "--repeat", "40"],
          "recurrent update; " + many),
         ("rmsnorm_hidden", 2 * N_LAYERS + 1, ["rmsnorm", "--decode", "--kind", "hidden27", "--tokens", t], "input and post-attention norms"),
-        ("attention_fp8", N_ATTN * calls, ["causal_softmax_attention", "--entry", "append", "--geometry", "d256-h24-kv4", "--kv-dtype",
-                                           "fp8", "--batch", str(sb), "--tokens", "1", "--context", str(context), "--execution",
-                                           "eager", "--cache", "cold", "--warmup", "5", "--repeat", "30"],
-         "decode attention over an fp8 cache, `append` entry (its batched form; it also writes the new token's K / V, "
-         "which this repository does in its attn_prep kernel); " + many),
-        # tried only when the batched entry above gives no time: the single-sequence entry, once per sequence
-        ("attention_fp8_single", N_ATTN * T, ["causal_softmax_attention", "--entry", "cached", "--geometry", "d256-h24-kv4",
-                                              "--kv-dtype", "fp8", "--batch", "1", "--tokens", "1", "--context", str(context),
-                                              "--execution", "eager", "--cache", "cold", "--warmup", "5", "--repeat", "30"],
-         "fallback for attention_fp8: the `cached` entry takes one sequence, so a batch of T is T calls"),
+        ("attention_fp8", N_ATTN * T, ["causal_softmax_attention", "--entry", "cached", "--geometry", "d256-h24-kv4",
+                                       "--kv-dtype", "fp8", "--batch", "1", "--tokens", "1", "--context", str(context),
+                                       "--execution", "eager", "--cache", "cold", "--warmup", "5", "--repeat", "30"],
+         f"decode attention over an fp8 cache: the `cached` entry takes one sequence, so a batch of {T} is {T} calls (the "
+         "batched `append` entry needs the prefill objects, which do not fit the snapshot that travels to the GPU box)"),
         ("lm_head_bf16", 1, lin(248320, 5120), "vocabulary projection, generic Linear"),
         ("argmax", 1, ["argmax", "--shape", "full", "--cols", str(min(T, 128))], "greedy token choice"),
     ]
@@ -84,10 +79,7 @@ def run(T: int = 32, context: int = 2048, raw_dir: str | None = None, timeout: i
     if not BIN.exists():
         return {"unavailable": f"{BIN.relative_to(HERE.parent)} is missing: run baseline/build_reference.sh"}
     rows, total, missing = [], 0.0, []
-    have = {}
     for key, count, argv, note in commands(T, context):
-        if key.endswith("_single") and have.get(key[:-len("_single")]) is not None:
-            continue   # the batched form of this Op gave a time
         try:
             r = subprocess.run([str(BIN)] + argv, capture_output=True, text=True, timeout=timeout)
             out, rc = r.stdout + r.stderr, r.returncode
@@ -97,9 +89,6 @@ def run(T: int = 32, context: int = 2048, raw_dir: str | None = None, timeout: i
             os.makedirs(raw_dir, exist_ok=True)
             Path(raw_dir, f"{key}_T{T}.txt").write_text("$ ninfer_ref_benches " + " ".join(argv) + f"\n[rc {rc}]\n" + out)
         us = parse_median_us(out) if rc == 0 else None
-        have[key] = us
-        if us is not None and key.endswith("_single") and key[:-len("_single")] in missing:
-            missing.remove(key[:-len("_single")])
         row = {"op": key, "per_round": count, "median_us": us, "note": note}
         if us is None:
             row["refused"] = (out.strip().splitlines() or ["no output"])[-1][:200]

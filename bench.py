@@ -155,6 +155,9 @@ def speculative_run(args, cfg, device) -> int:
     B, L, Kd, R_ = args.batch, args.prompt_len, args.draft_tokens, args.tree_ranks
     n_rounds, warm = args.steps, max(3, args.warmup)
     weights = random_weights(cfg, device, seed=0, with_mtp=True)
+    if args.spec == "dflash":
+        from ninfer_fusion_b200.models.dflash import DFlashConfig, random_dflash_weights
+        weights.update(random_dflash_weights(cfg, DFlashConfig(), weights, device))
     g = torch.Generator().manual_seed(1234)
     prompts = [torch.randint(0, cfg.vocab, (L,), generator=g).tolist() for _ in range(B)]
     n_plain = (n_rounds + warm + 2) * (Kd + 1)
@@ -188,7 +191,8 @@ def speculative_run(args, cfg, device) -> int:
     torch.cuda.empty_cache()
 
     spec = SpeculativeGenerator(cfg, weights, device, max_batch=B, max_context=max_ctx, draft_tokens=Kd,
-                                drafter="mtp" if args.spec == "mtp" else "hook", tree_ranks=R_, kv_format=args.kv_format,
+                                drafter=args.spec if args.spec in ("mtp", "dflash") else "hook", tree_ranks=R_,
+                                kv_format=args.kv_format,
                                 page_size=64, prefill_chunk=2048, pdl=bool(args.pdl))
     if args.spec == "hook":
         def hook(b, history, k):
@@ -263,8 +267,9 @@ def main() -> int:
                     help="tensor-parallel reduction: fused = reduce-scatter + all-gather inside the GEMMs, oneshot = "
                          "every rank receives every tile + one sum kernel, nccl = NCCL all-reduce baseline, auto = the "
                          "faster of fused / oneshot at this GPU count as measured (TensorParallel.best_mode)")
-    ap.add_argument("--spec", default="none", choices=["none", "mtp", "hook"],
-                    help="speculative decoding run (one GPU, eager rounds): mtp = the draft module proposes (random-init "
+    ap.add_argument("--spec", default="none", choices=["none", "mtp", "dflash", "hook"],
+                    help="speculative decoding run (one GPU, eager rounds): mtp = the draft module proposes, dflash = the "
+                         "block-diffusion draft model proposes the whole block in one pass (random-init "
                          "weights accept next to nothing), hook = synthetic drafts of mixed quality taken from the plain "
                          "greedy stream (the first (round + b) mod (K + 1) drafts right, the rest wrong)")
     ap.add_argument("--draft-tokens", type=int, default=4)

@@ -259,6 +259,12 @@ class HybridModel:
         # (NFB_L2_PREFETCH=0 switches the hint off)
         self.l2_prefetch = os.environ.get("NFB_L2_PREFETCH", "1") != "0"
         self.attn_impl = 0  # 0 = pick, 1 = SIMT, 2 = tensor-core split-KV attention
+        # Feature taps for a draft model that conditions on intermediate target states (DFlash): {layer: column
+        # block}; after that layer's MLP the residual stream of the step's tokens is copied into
+        # feature_buf[:, block * hidden : (block + 1) * hidden].  None: nothing is copied.
+        self.layer_window: Dict[int, int] = {}   # layer -> sliding window of its decode-style attention (absent: all keys)
+        self.feature_taps: Optional[Dict[int, int]] = None
+        self.feature_buf: Optional[torch.Tensor] = None
         self.comm = None  # tensor-parallel communicator (parallel.tp), None on one GPU
         # (norm weight, normed buffer, T) while the residual stream of the last row-parallel GEMM is still being
         # gathered from the owner ranks and ws.normed has not been written (tensor parallel, decode sizes)
@@ -456,8 +462,8 @@ class HybridModel:
                                 planes.k_codes, planes.v_codes, planes.k_scales, planes.v_scales, kv.page_size,
                                 planes.fmt, planes.group, self.sm_scale, split, n_splits, ws.part_o, ws.part_ml,
                                 gate[t0:t1], out[t0:t1], None if b.tree_mask is None else b.tree_mask[t0:t1],
-                                None if b.tree_base is None else b.tree_base[t0:t1], self.attn_impl, self.pdl, 0, None,
-                                None, tiers)
+                                None if b.tree_base is None else b.tree_base[t0:t1], self.attn_impl, self.pdl,
+                                self.layer_window.get(layer, 0), None, None, tiers)
         return out, self.w[f"{prefix}/attn/o_proj"]
 
     def _gdn_layer(self, ws: Workspace, b: StepBatch, st: GdnStatePool, layer: int, T: int, prefix: str,
@@ -639,6 +645,9 @@ class HybridModel:
                     from .moe import MoeBlock
                     self.moe = MoeBlock(cfg, self.device, ws.max_tokens, *self.ep, expert_format=self.expert_format)
                 self.moe.forward(self, ws, T, p, nxt, ws.normed[:T], self.moe_global_tokens)
+            if self.feature_taps is not None and layer in self.feature_taps:
+                blk, h = self.feature_taps[layer], cfg.hidden
+                self.feature_buf[:T, blk * h:(blk + 1) * h].copy_(ws.x[:T])
         self._materialize_normed(ws)
         return ws.normed[:T] if end_layer == cfg.n_layers else x
 

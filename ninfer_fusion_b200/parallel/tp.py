@@ -128,10 +128,10 @@ class TensorParallel:
 
     @staticmethod
     def best_mode(world: int) -> str:
-        """The faster decode mode at `world` GPUs as measured on one 8 x B200 box (27B, batch 32): at 2 GPUs the fused
-        reduce-scatter / all-gather epilogues win (8.99 vs 9.60 ms per round); at 4 and 8 the second hop through the
-        tile's owner costs more than the bytes it saves (8 GPUs: 8.48 ms fused, 6.53 ms one-shot)."""
-        return "fused" if world <= 2 else "oneshot"
+        """The faster decode mode at `world` GPUs as measured on one 8 x B200 box (27B, batch 32, ms per round, fused
+        vs one-shot): 2 GPUs 8.89 / 9.60, 4 GPUs 6.67 / 6.97, 8 GPUs 6.08 / 6.44.  (Before the reduction of the
+        reduce-scatter hop was spread over the grid the fused form lost at 4 and 8 GPUs: 7.56 and 8.48.)"""
+        return "fused"
 
     @classmethod
     def loopback(cls, cfg: ModelConfig, world: int, device, max_tokens: int, mode: str = "fused") -> List["TensorParallel"]:

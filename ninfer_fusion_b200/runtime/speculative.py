@@ -54,6 +54,7 @@ class SpeculativeGenerator(Generator):
         if K < 1:
             raise ValueError("draft_tokens must be >= 1")
         kw.setdefault("use_graph", False)
+        dflash_config = kw.pop("dflash_config", None)
         R_ = max(1, tree_ranks)
         if 1 + R_ * K > 64:
             raise ValueError("a verify window holds at most 64 nodes (one visibility bit each)")
@@ -61,7 +62,7 @@ class SpeculativeGenerator(Generator):
         self.K = K
         self.R = R_   # candidates per depth of the draft tree: rank 0 extends the chain, ranks 1.. are side branches
         self.sampling = sampling  # runtime.program.SamplingParams for stochastic verification; None / greedy = arg-max
-        self.drafter = drafter  # "mtp" | "ngram" | "hook"
+        self.drafter = drafter  # "mtp" | "dflash" | "ngram" | "hook"
         self.draft_hook: Optional[Callable[[int, List[int], int], Optional[List[int]]]] = None
         dev, g = self.device, self.model.g
         Tv = max_batch * (1 + self.R * K)
@@ -101,6 +102,21 @@ class SpeculativeGenerator(Generator):
             one_attn = cfg.shrink(cfg.full_attn_interval)  # geometry of a cache with a single attention layer
             self.kv_mtp = PagedKvCache(one_attn, max_batch * pages_per_row, self.page_size, max_batch, pages_per_row,
                                        dev, formats="bf16", n_kv_heads=g.n_kv_heads)
+        self.dflash = None
+        if drafter == "dflash":
+            # block-diffusion drafter: conditions on tapped residual streams of the target, proposes K tokens in one pass
+            if "dflash/feature_proj" not in weights:
+                raise ValueError("weights have no DFlash draft model (models.dflash.random_dflash_weights)")
+            if self.R > 1:
+                raise ValueError("the DFlash drafter proposes a chain (tree_ranks = 1)")
+            from ..models.dflash import DFlashConfig
+            from .dflash import DFlashDrafter
+            dc = dflash_config or DFlashConfig()
+            self.dflash = DFlashDrafter(cfg, dc, weights, dev, max_batch, max_context, K, page_size=self.page_size,
+                                        pdl=self.model.pdl, max_append=max(self.ws.max_tokens, Tv))
+            fl = self.dflash.dc.feature_layers
+            self.model.feature_taps = {layer: i for i, layer in enumerate(fl)}
+            self.model.feature_buf = torch.empty((max(self.ws.max_tokens, Tv), len(fl) * h), dtype=torch.bfloat16, device=dev)
         self.history: List[List[int]] = []
         self.rounds = 0
         self.accepted = 0
@@ -170,7 +186,7 @@ class SpeculativeGenerator(Generator):
 
     # ------------------------------------------------------------------ prefill
     def prefill(self, prompts: Sequence[Sequence[int]]) -> List[int]:
-        if self.drafter != "mtp":
+        if self.drafter not in ("mtp", "dflash"):
             first = super().prefill(prompts)
             self.history = [list(p) + [t] for p, t in zip(prompts, first)]
             return first
@@ -178,16 +194,21 @@ class SpeculativeGenerator(Generator):
             raise ValueError("too many sequences")
         self.reset()
         for r in range(self.max_batch):
-            self.kv_mtp.free_row(r)
+            if self.kv_mtp is not None:
+                self.kv_mtp.free_row(r)
+        if self.dflash is not None:
+            self.dflash.reset(range(self.max_batch))
         B = len(prompts)
         for b in range(B):
             self.rows.append(b)
             self.slots.append(self.states.alloc())
             self.lengths.append(0)
             self.kv.ensure(b, len(prompts[b]) + self.K + 2)
-            self.kv_mtp.ensure(b, len(prompts[b]) + self.K + 2)
+            if self.kv_mtp is not None:
+                self.kv_mtp.ensure(b, len(prompts[b]) + self.K + 2)
         self.kv.publish()
-        self.kv_mtp.publish()
+        if self.kv_mtp is not None:
+            self.kv_mtp.publish()
         first = [0] * B
         cursor = [0] * B
         pending = list(range(B))
@@ -223,6 +244,11 @@ class SpeculativeGenerator(Generator):
                     nxt.extend(list(prompts[b][start + 1:start + n]) + [first[b]])
                 else:
                     nxt.extend(prompts[b][start + 1:start + n + 1])
+            if self.dflash is not None:
+                # the chunk's tokens are committed: their tapped features become draft context
+                self.dflash.append_context(self.model.feature_buf[:T], batch.table_row, batch.cache_pos,
+                                           {self.rows[b]: start + n for b, start, n, _ in owners})
+                continue
             # the draft module reads the same positions: hidden state of p + token p + 1
             self._mtp_pass(batch, self.h_keep[:T], self._upload_next(nxt), done_seqs)
         for b in range(B):
@@ -236,6 +262,9 @@ class SpeculativeGenerator(Generator):
     def _draft(self, B: int) -> None:
         """Fills self.drafts[:B] (device)."""
         K = self.K
+        if self.dflash is not None:
+            self.drafts[:B].copy_(self.dflash.propose(self.rows[:B], self.last_tokens[:B], self.lengths[:B]))
+            return
         if self.drafter == "mtp":
             for j in range(1, K):
                 # position n + j - 1 of the draft module: its own hidden state + the previous draft token
@@ -454,6 +483,20 @@ class SpeculativeGenerator(Generator):
             Tc = len(rows)
             torch.index_select(self.h_keep[:T], 0, idx, out=self.h_in[:Tc])
             self._mtp_pass(cb, self.h_in[:Tc], self._upload_next(nxt), list(range(B)))
+        if self.dflash is not None:
+            # the features of the positions that were just committed (verify rows 0..m of every sequence) extend the
+            # draft context; they sit at cache positions lengths[b] + j
+            rows, trow, pos, ends = [], [], [], {}
+            for b in range(B):
+                m1 = len(emitted[b])
+                rows.extend(range(b * (K + 1), b * (K + 1) + m1))
+                trow.extend([self.rows[b]] * m1)
+                pos.extend(range(self.lengths[b], self.lengths[b] + m1))
+                ends[self.rows[b]] = self.lengths[b] + m1
+            idx = torch.tensor(rows, dtype=torch.long, device=self.device)
+            feats = self.model.feature_buf[:T].index_select(0, idx)
+            self.dflash.append_context(feats, torch.tensor(trow, dtype=torch.int32, device=self.device),
+                                       torch.tensor(pos, dtype=torch.int32, device=self.device), ends)
         for b in range(B):
             self.lengths[b] += len(emitted[b])
             self.last_tokens[b] = emitted[b][-1]

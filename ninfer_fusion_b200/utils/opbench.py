@@ -136,7 +136,7 @@ def bench_attn(ops, batch, ctx, kv, hq=24, hkv=4, D=256, P=64, iters=20, impl=0)
     table = torch.randperm(n_pages, device="cuda").int().view(batch, pages_per)
     q = torch.randn(batch, hq, D, device="cuda").to(torch.bfloat16)
     from ..models.hybrid import pick_attention_split
-    split, n_splits = pick_attention_split(ctx, batch * hkv)
+    split, n_splits = pick_attention_split(ctx, batch * hkv, waves=8 if impl == 3 else 2)
     part_o = torch.empty(batch * hq * n_splits * D, device="cuda")
     part_ml = torch.empty(batch * hq * n_splits * 2, device="cuda")
     out = torch.empty((batch, hq * D), dtype=torch.bfloat16, device="cuda")
@@ -257,6 +257,7 @@ def main(argv=None):
     ap.add_argument("--kv", default="fp8")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--pdl", type=int, default=0)
+    ap.add_argument("--impl", type=int, default=0, help="attn: 1 = SIMT, 2 = mma.sync, 3 = tcgen05 (0 = all that apply)")
     a = ap.parse_args(argv)
     ops = load_native()
     rows = []
@@ -275,7 +276,8 @@ def main(argv=None):
             rows.append(r)
     if a.what in ("attn", "all"):
         for kv in (["bf16", "fp8", "int8", "nvfp4"] if a.what == "all" else [a.kv]):
-            for impl in (1, 2):
+            impls = [a.impl] if a.impl else ([1, 2, 3] if kv == "fp8" else [1, 2])   # 3 = tcgen05 (fp8-row pages)
+            for impl in impls:
                 rows.append(bench_attn(ops, a.batch, a.ctx, kv, iters=a.iters, impl=impl))
     if a.what in ("gdn", "all"):
         rows.append(bench_gdn(ops, a.batch, iters=a.iters))
