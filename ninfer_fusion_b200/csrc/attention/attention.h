@@ -64,6 +64,10 @@ struct PagedAttnParams {
   int impl;  // 0 = pick, 1 = SIMT kernel, 2 = mma.sync tensor-core kernel, 3 = tcgen05 kernel (fp8-row pages)
   long long kv_plane_rows = 0;  // rows (page x head x token) of the K / V code planes; 0 = unknown (no TMA path)
   int* status = nullptr;        // optional device status word for the bounded waits of the tcgen05 kernel
+  // optional: the merged output also as the next GEMM's nvfp4 operand (gemm/nvfp4_act.cuh): codes [Tq][Hq * D / 2]
+  // bytes and the scale plane of Tq x (Hq * D) values
+  uint8_t* q_codes = nullptr;
+  uint8_t* q_sf = nullptr;
   int window = 0;  // sliding window: a query sees only its last `window` keys (0 = all of them)
   // Selected-block attention (optional, decode only): query t attends to sel_count[t] blocks of four consecutive
   // tokens, block ids in sel_blocks[t * sel_stride ..] (each below the number of complete blocks, kv_len / 4), plus

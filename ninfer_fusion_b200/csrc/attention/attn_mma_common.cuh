@@ -2,6 +2,7 @@
 // ldmatrix / mma wrappers and the raw-unit loader that dequantises 16 cache values to fp16 pairs.
 #pragma once
 #include <cuda_fp16.h>
+#include <cuda_fp4.h>
 #include <stdint.h>
 
 #include "../common/ptx.cuh"
@@ -134,11 +135,16 @@ struct RawUnit {
         out[i] = pack_half2(static_cast<float>(c0) * scale, static_cast<float>(c1) * scale);
       }
     } else {
+      // two e2m1 codes per byte -> fp16 pair in one conversion instruction, then the block scale (the product of an
+      // e2m1 value and an e4m3 scale is exact in fp16, so this equals the fp32 route bit for bit)
       const uint32_t w[2] = {a.x, a.y};
+      const __half2 s2 = __float2half2_rn(scale);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const uint32_t nib2 = (w[i / 4] >> (8 * (i % 4))) & 0xff;
-        out[i] = pack_half2(e2m1_to_float(nib2 & 0xf) * scale, e2m1_to_float(nib2 >> 4) * scale);
+        const __nv_fp4x2_storage_t pair = static_cast<__nv_fp4x2_storage_t>((w[i / 4] >> (8 * (i % 4))) & 0xff);
+        const __half2_raw hr = __nv_cvt_fp4x2_to_halfraw2(pair, __NV_E2M1);
+        const __half2 h = __hmul2(*reinterpret_cast<const __half2*>(&hr), s2);
+        out[i] = *reinterpret_cast<const uint32_t*>(&h);
       }
     }
   }

@@ -20,6 +20,7 @@
 
 #include "../common/ptx.cuh"
 #include "../kv/codec.cuh"
+#include "../gemm/nvfp4_act.cuh"
 
 namespace nfb {
 
@@ -252,6 +253,20 @@ __global__ void __launch_bounds__(D / 4) paged_attn_merge_kernel(const PagedAttn
   ov.x = pack_bf16x2(r[0], r[1]);
   ov.y = pack_bf16x2(r[2], r[3]);
   *reinterpret_cast<uint2*>(p.out + (static_cast<long long>(t) * p.n_q_heads + h) * D + d0) = ov;
+  if (p.q_codes != nullptr) {
+    // the output row also as the next GEMM's nvfp4 operand: four threads hold one 16-value block
+    const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&ov);
+    const float mine[4] = {__bfloat162float(ob[0].x), __bfloat162float(ob[0].y), __bfloat162float(ob[1].x),
+                           __bfloat162float(ob[1].y)};
+    float v[16];
+    const int base = threadIdx.x & ~3;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[4 * j + i] = __shfl_sync(0xffffffffu, mine[i], (base + j) & 31);
+    if ((threadIdx.x & 3) == 0)
+      nvfp4_store_block(v, t, (h * D + d0) / 16, p.n_q_heads * D, p.q_codes, p.q_sf);
+  }
 }
 
 template <typename K>

@@ -68,6 +68,10 @@ struct GdnParams {
   const __nv_bfloat16* conv_w = nullptr;
   __nv_bfloat16* conv_state = nullptr;
   int conv_C = 0;
+  // Optional (recurrent kernel only): the output rows also as the next GEMM's nvfp4 operand (see gemm/nvfp4_act.cuh):
+  // codes [T][Hv * 64] bytes and the scale plane of T x (Hv * 128) values.
+  uint8_t* q_codes = nullptr;
+  uint8_t* q_sf = nullptr;
 };
 const char* gdn_recurrent(const GdnParams& p, cudaStream_t stream, bool pdl);
 // Multi-token variant (token groups staged in shared memory); gdn_recurrent dispatches to it when T > n_seq.

@@ -15,6 +15,7 @@
 #include "gdn.h"
 
 #include "../common/ptx.cuh"
+#include "../gemm/nvfp4_act.cuh"
 
 namespace nfb {
 
@@ -216,6 +217,7 @@ __global__ void __launch_bounds__(kThreads, 2) gdn_recurrent_kernel(const GdnPar
 #pragma unroll
     for (int w = 0; w < kThreads / 32; ++w) tot += red[par][w];
     const float inv = rsqrtf(tot / kDv + p.eps);
+    float yq = 0.f;
     if (q8 < kRowsPerThread) {
       // lane q8 of each 8-lane group writes row j = q8 (all eight lanes hold all four o[j])
       float oj = o[0];
@@ -226,6 +228,14 @@ __global__ void __launch_bounds__(kThreads, 2) gdn_recurrent_kernel(const GdnPar
       const float nw = __bfloat162float(p.norm_w[r]);
       const float y = oj * inv * nw * (z / (1.f + __expf(-z)));
       p.out[static_cast<long long>(t) * (p.n_v_heads * kDv) + hv * kDv + r] = __float2bfloat16(y);
+      yq = __bfloat162float(__float2bfloat16(y));
+    }
+    if (p.q_codes != nullptr) {
+      // a warp owns sixteen consecutive outputs (rows warp * 16 ..): element e = 4 * q8 + sub sits in lane 8 * sub + q8
+      float v[16];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) v[e] = __shfl_sync(0xffffffffu, yq, (e & 3) * 8 + (e >> 2));
+      if (lane == 0) nvfp4_store_block(v, t, hv * (kDv / 16) + warp, p.n_v_heads * kDv, p.q_codes, p.q_sf);
     }
   }
 

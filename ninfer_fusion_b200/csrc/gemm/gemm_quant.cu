@@ -22,6 +22,7 @@
 // Reference: src/ops/linear/nvfp4/nvfp4_w4a4_tma.cuh (mma.sync mxf4nvf4 on sm_120a, refused on
 // sm_100a), src/ops/linear/fp8/fp8_a8_mma.cuh (mma.sync f8f6f4 with row-scale epilogue).
 #include "gemm_quant.h"
+#include "nvfp4_act.cuh"
 
 #include <cstdlib>
 #include <mutex>
@@ -106,6 +107,10 @@ struct QParams {
   unsigned int* peer_flag[kMaxRanks];
   int rank, world, slice_cols, T_cap;
   const unsigned int* call_idx;
+  // SwiGLU epilogue: also write the activation as the NEXT GEMM's nvfp4 operand (codes [T][N / 4], scale plane);
+  // nullptr = bf16 output only
+  uint8_t* next_codes;
+  uint8_t* next_sf;
 };
 
 template <int TN, int QT, int EPI, bool DEEP>
@@ -305,6 +310,7 @@ __global__ void __launch_bounds__(128) gemm_q_kernel(const __grid_constant__ CUt
     if constexpr (EPI == kEpiSwiglu) {
       // rows are tile-interleaved: lanes 0..63 = gate rows, lanes 64..127 = the matching up rows
       float* up_s = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw))) + (S - 1) * TN * 128;
+      float* act_s = up_s + TN * 64;   // [TN][64] activations for the fused quantiser (behind the up rows)
       if (warp >= 2) {
         const int r = (warp - 2) * 32 + lane;
         for (int c = 0; c < TN; c += kChunk) {
@@ -332,6 +338,10 @@ __global__ void __launch_bounds__(128) gemm_q_kernel(const __grid_constant__ CUt
               const float g = v[j];
               a[h] = g / (1.f + __expf(-g)) * up_s[(c + j) * 64 + r];
             }
+            if (p.next_codes != nullptr) {   // (same rounding as the bf16 store below: the quantiser reads bf16)
+              act_s[(c + 2 * m) * 64 + r] = __bfloat162float(__float2bfloat16(a[0]));
+              act_s[(c + 2 * m + 1) * 64 + r] = __bfloat162float(__float2bfloat16(a[1]));
+            }
             const float send = (lane & 1) ? a[0] : a[1];
             const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
             const int t = t0 + c + 2 * m + (lane & 1);
@@ -341,6 +351,20 @@ __global__ void __launch_bounds__(128) gemm_q_kernel(const __grid_constant__ CUt
               *reinterpret_cast<uint32_t*>(p.out + static_cast<long long>(t) * p.ldo + ce) = packed;
             }
           }
+        }
+      }
+      if (p.next_codes != nullptr) {
+        // the activation tile (TN tokens x 64 columns) as the next GEMM's nvfp4 operand: one (token, 16-column
+        // block) per thread, the same bits the stand-alone quantiser would write from the bf16 tensor
+        __syncthreads();
+        const int K_next = p.N / 2;
+        for (int u = threadIdx.x; u < TN * 4; u += 128) {
+          const int tt = u >> 2, blk = u & 3;
+          if (t0 + tt >= p.T) continue;
+          float v[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = act_s[tt * 64 + blk * 16 + i];
+          nvfp4_store_block(v, t0 + tt, blockIdx.x * 4 + blk, K_next, p.next_codes, p.next_sf);
         }
       }
     } else if constexpr (EPI == kEpiPushAll || EPI == kEpiPushPartial) {
@@ -486,22 +510,7 @@ __global__ void __launch_bounds__(256) quant_act_nvfp4_kernel(const __nv_bfloat1
     v[2 * i] = __bfloat162float(p0[i].x); v[2 * i + 1] = __bfloat162float(p0[i].y);
     v[8 + 2 * i] = __bfloat162float(p1[i].x); v[8 + 2 * i + 1] = __bfloat162float(p1[i].y);
   }
-  float amax = 0.f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  const uint8_t sc = float_to_e4m3(amax / 6.f);
-  const float sf = e4m3_to_float(sc);
-  uint32_t lo = 0, hi = 0;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    lo |= float_to_e2m1(sf > 0.f ? __fdiv_rn(v[i], sf) : 0.f) << (4 * i);
-    hi |= float_to_e2m1(sf > 0.f ? __fdiv_rn(v[8 + i], sf) : 0.f) << (4 * i);
-  }
-  *reinterpret_cast<uint2*>(codes + static_cast<long long>(t) * (K / 2) + g * 8) = make_uint2(lo, hi);
-  const int k_tiles = K / 64;
-  const long long off = (static_cast<long long>(t / 128) * k_tiles + g / 4) * kSfTileBytes + (t % 32) * 16 +
-                        ((t % 128) / 32) * 4 + (g % 4);
-  sf_plane[off] = sc;
+  nvfp4_store_block(v, t, g, K, codes, sf_plane);
 }
 
 // ------------------------------------------------------------------------------------------------------------
@@ -1016,6 +1025,12 @@ const char* gemm_quant(const QGemmArgs& a) {
   kp.out = static_cast<__nv_bfloat16*>(a.out); kp.ldo = a.ldo;
   kp.resid = static_cast<const __nv_bfloat16*>(a.resid); kp.ldr = a.ldr;
   kp.status = a.status;
+  kp.next_codes = nullptr; kp.next_sf = nullptr;
+  if (a.next_codes != nullptr) {
+    if (a.epi != kEpiSwiglu || !bs || a.next_sf == nullptr || (a.N / 2) % 64 || a.T > 128)
+      return "gemm_quant: the fused activation quantiser is for nvfp4 SwiGLU at decode sizes (N / 2 a multiple of 64)";
+    kp.next_codes = static_cast<uint8_t*>(a.next_codes); kp.next_sf = static_cast<uint8_t*>(a.next_sf);
+  }
   if (push) {
     if (a.world < 1 || a.world > kMaxRanks || a.rank < 0 || a.rank >= a.world) return "gemm_quant: bad rank/world";
     kp.rank = a.rank; kp.world = a.world;

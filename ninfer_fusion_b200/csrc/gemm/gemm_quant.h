@@ -32,6 +32,10 @@ struct QGemmArgs {
   float* peer_recv[kMaxRanks] = {};
   unsigned int* peer_flag[kMaxRanks] = {};
   int splits = 1;                 // in-cluster split-K
+  // nvfp4 SwiGLU only: also write the activation [T, N/2] as the next GEMM's W4A4 operand (codes [T][N/4] bytes and
+  // the scale plane of nvfp4_act_scale_bytes(T, N/2) bytes); nullptr = bf16 output only
+  void* next_codes = nullptr;
+  void* next_sf = nullptr;
   int* status = nullptr;
   cudaStream_t stream = nullptr;
   bool pdl = false;

@@ -44,7 +44,8 @@ void quant_act_nvfp4(const Tensor& x, const Tensor& codes, const Tensor& sf_plan
 
 // x_codes: [T, K] (fp8) or [T, K/2] (nvfp4) bytes; w_codes likewise with N rows.
 void gemm_quant(int64_t qtype, const Tensor& x_codes, const Tensor& x_scale, const Tensor& w_codes, const Tensor& w_scale,
-                double w_divisor, const Tensor& out, int64_t epi, OptT resid, int64_t splits, OptT status, bool pdl) {
+                double w_divisor, const Tensor& out, int64_t epi, OptT resid, int64_t splits, OptT status, bool pdl,
+                OptT next_codes, OptT next_sf) {
   need(x_codes, at::kByte, "x_codes"); need(w_codes, at::kByte, "w_codes"); need(out, at::kBFloat16, "out");
   TORCH_CHECK(x_codes.dim() == 2 && w_codes.dim() == 2 && x_codes.stride(1) == 1 && w_codes.stride(1) == 1 &&
               x_codes.size(1) == w_codes.size(1), "gemm_quant: code shapes");
@@ -74,6 +75,13 @@ void gemm_quant(int64_t qtype, const Tensor& x_codes, const Tensor& x_scale, con
   }
   a.epi = static_cast<int>(epi); a.splits = static_cast<int>(splits);
   a.status = status.has_value() && status->defined() ? static_cast<int*>(status->data_ptr()) : nullptr;
+  if (next_codes.has_value() && next_codes->defined()) {
+    TORCH_CHECK(next_sf.has_value() && next_sf->defined(), "gemm_quant: next_sf required with next_codes");
+    need(*next_codes, at::kByte, "next_codes"); need(*next_sf, at::kByte, "next_sf");
+    TORCH_CHECK(next_codes->numel() >= a.T * (a.N / 4) && next_sf->numel() >= nfb::nvfp4_act_scale_bytes(a.T, a.N / 2),
+                "gemm_quant: buffers of the fused activation quantiser are too small");
+    a.next_codes = next_codes->data_ptr(); a.next_sf = next_sf->data_ptr();
+  }
   a.stream = cur_stream(); a.pdl = pdl;
   chk(nfb::gemm_quant(a));
 }
@@ -118,7 +126,7 @@ int64_t nvfp4_act_scale_bytes(int64_t T, int64_t K) { return nfb::nvfp4_act_scal
 TORCH_LIBRARY_FRAGMENT(nfb200, m) {
   m.def("quant_act_fp8(Tensor x, Tensor codes, Tensor scale, bool pdl=False) -> ()", &quant_act_fp8);
   m.def("quant_act_nvfp4(Tensor x, Tensor codes, Tensor sf_plane, bool pdl=False) -> ()", &quant_act_nvfp4);
-  m.def("gemm_quant(int qtype, Tensor x_codes, Tensor x_scale, Tensor w_codes, Tensor w_scale, float w_divisor, Tensor out, int epi, Tensor? resid, int splits, Tensor? status, bool pdl) -> ()", &gemm_quant);
+  m.def("gemm_quant(int qtype, Tensor x_codes, Tensor x_scale, Tensor w_codes, Tensor w_scale, float w_divisor, Tensor out, int epi, Tensor? resid, int splits, Tensor? status, bool pdl, Tensor? next_codes=None, Tensor? next_sf=None) -> ()", &gemm_quant);
   m.def("nvfp4_act_scale_bytes(int T, int K) -> int", &nvfp4_act_scale_bytes);
   m.def("gemm_quant_push(int qtype, Tensor x_codes, Tensor x_scale, Tensor w_codes, Tensor w_scale, float w_divisor, bool all, int splits, int world, int rank, int[] peer_bases, int recv_off, int flag_off, int T_cap, Tensor state, Tensor? status, bool pdl) -> ()", &gemm_quant_push);
 }

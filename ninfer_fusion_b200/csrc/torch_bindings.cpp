@@ -322,7 +322,7 @@ void paged_attention(const Tensor& q, int64_t n_q_heads, int64_t n_kv_heads, int
                      OptT k_scales, OptT v_scales, int64_t page_size, int64_t format, int64_t group, double sm_scale,
                      int64_t split_keys, int64_t n_splits, const Tensor& part_o, const Tensor& part_ml, OptT gate,
                      const Tensor& out, OptT tree_mask, OptT tree_base, int64_t impl, bool pdl, int64_t window,
-                     OptT sel_blocks, OptT sel_count, OptT tiers) {
+                     OptT sel_blocks, OptT sel_count, OptT tiers, OptT q_codes, OptT q_sf) {
   need(q, at::kBFloat16, "q"); need(q_seq, at::kInt, "q_seq"); need(q_kv_len, at::kInt, "q_kv_len");
   need(block_table, at::kInt, "block_table"); need(part_o, at::kFloat, "part_o"); need(part_ml, at::kFloat, "part_ml");
   need(out, at::kBFloat16, "out");
@@ -371,6 +371,14 @@ void paged_attention(const Tensor& q, int64_t n_q_heads, int64_t n_kv_heads, int
     p.sel_blocks = static_cast<const int*>(sel_blocks->data_ptr());
     p.sel_count = static_cast<const int*>(sel_count->data_ptr());
     p.sel_stride = static_cast<int>(sel_blocks->size(1));
+  }
+  if (q_codes.has_value() && q_codes->defined()) {
+    TORCH_CHECK(q_sf.has_value() && q_sf->defined(), "q_sf required with q_codes");
+    need(*q_codes, at::kByte, "q_codes"); need(*q_sf, at::kByte, "q_sf");
+    TORCH_CHECK(q_codes->numel() >= static_cast<int64_t>(p.Tq) * n_q_heads * head_dim / 2 && head_dim % 16 == 0,
+                "q_codes too small");
+    p.q_codes = static_cast<uint8_t*>(q_codes->data_ptr());
+    p.q_sf = static_cast<uint8_t*>(q_sf->data_ptr());
   }
   chk(nfb::paged_attention(p, cur_stream(), pdl));
 }
@@ -472,7 +480,7 @@ void gdn_recurrent(const Tensor& qkv, int64_t q_off, int64_t k_off, int64_t v_of
                    int64_t a_off, int64_t b_off, int64_t n_qk_heads, int64_t n_v_heads, const Tensor& A_log,
                    const Tensor& dt_bias, const Tensor& norm_w, double eps, const Tensor& cu_seqlens,
                    const Tensor& state_slot, const Tensor& state, bool write_state, const Tensor& out, bool pdl,
-                   OptT seq_end, OptT commit, OptT chunk_ws, OptT conv_w, OptT conv_state) {
+                   OptT seq_end, OptT commit, OptT chunk_ws, OptT conv_w, OptT conv_state, OptT q_codes, OptT q_sf) {
   need(qkv, at::kBFloat16, "qkv"); need_rows(qkv, "qkv"); need(proj, at::kBFloat16, "proj"); need_rows(proj, "proj");
   need(A_log, at::kFloat, "A_log"); need(dt_bias, at::kFloat, "dt_bias"); need(norm_w, at::kBFloat16, "norm_w");
   need(cu_seqlens, at::kInt, "cu_seqlens"); need(state_slot, at::kInt, "state_slot");
@@ -518,6 +526,14 @@ void gdn_recurrent(const Tensor& qkv, int64_t q_off, int64_t k_off, int64_t v_of
     p.conv_w = static_cast<const __nv_bfloat16*>(conv_w->data_ptr());
     p.conv_state = static_cast<__nv_bfloat16*>(conv_state->data_ptr());
     p.conv_C = static_cast<int>(conv_w->size(0));
+  }
+  if (q_codes.has_value() && q_codes->defined()) {
+    TORCH_CHECK(q_sf.has_value() && q_sf->defined(), "q_sf required with q_codes");
+    need(*q_codes, at::kByte, "q_codes"); need(*q_sf, at::kByte, "q_sf");
+    TORCH_CHECK(q_codes->numel() >= static_cast<int64_t>(p.T) * n_v_heads * 64, "q_codes too small");
+    TORCH_CHECK(p.T == p.n_seq, "the fused output quantiser is for decode steps (one token per sequence)");
+    p.q_codes = static_cast<uint8_t*>(q_codes->data_ptr());
+    p.q_sf = static_cast<uint8_t*>(q_sf->data_ptr());
   }
   if (chunk_ws.has_value() && chunk_ws->defined()) {
     // chunked tensor-core formulation (long prefill chunks)
@@ -894,12 +910,12 @@ TORCH_LIBRARY(nfb200, m) {
   m.def("add_rmsnorm(Tensor? partial, int splits, Tensor? delta, Tensor? resid_in, Tensor? resid_out, Tensor? norm_w, Tensor? normed, int T, int N, float eps, bool unit_offset, bool pdl, Tensor? q_codes=None, Tensor? q_sf=None) -> ()", &add_rmsnorm);
   m.def("embed_gather(Tensor ids, Tensor table, Tensor out, bool pdl) -> ()", &embed_gather);
   m.def("attn_prep(Tensor proj, int q_off, int k_off, int v_off, int n_q_heads, int n_kv_heads, int head_dim, Tensor? q_norm_w, Tensor? k_norm_w, float eps, bool unit_offset, int rot_dim, Tensor inv_freq, float attn_factor, Tensor rope_pos, Tensor token_seq, Tensor cache_pos, Tensor block_table, Tensor q_out, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, bool pdl, bool k_hadamard=False, Tensor? k_row_scale=None, Tensor? tiers=None) -> ()", &attn_prep);
-  m.def("paged_attention(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, int split_keys, int n_splits, Tensor part_o, Tensor part_ml, Tensor? gate, Tensor out, Tensor? tree_mask, Tensor? tree_base, int impl, bool pdl, int window=0, Tensor? sel_blocks=None, Tensor? sel_count=None, Tensor? tiers=None) -> ()", &paged_attention);
+  m.def("paged_attention(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, int split_keys, int n_splits, Tensor part_o, Tensor part_ml, Tensor? gate, Tensor out, Tensor? tree_mask, Tensor? tree_base, int impl, bool pdl, int window=0, Tensor? sel_blocks=None, Tensor? sel_count=None, Tensor? tiers=None, Tensor? q_codes=None, Tensor? q_sf=None) -> ()", &paged_attention);
   m.def("paged_attention_prefill(Tensor q, int n_q_heads, int n_kv_heads, int head_dim, Tensor q_seq, Tensor q_kv_len, Tensor blk_start, Tensor blk_count, Tensor block_table, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int format, int group, float sm_scale, Tensor? gate, Tensor out, bool pdl, int window=0, Tensor? tiers=None) -> ()", &paged_attention_prefill);
   m.def("kv_requant(Tensor tiers, Tensor anchor, Tensor src_cell, Tensor dst_cell, int page_size, int n_kv_heads, int head_dim) -> ()", &kv_requant);
   m.def("prefill_attn_block_tokens(int n_q_heads, int n_kv_heads) -> int", &prefill_attn_block_tokens);
   m.def("causal_conv1d_silu(Tensor x, int c_off, int C, Tensor w, Tensor cu_seqlens, Tensor token_seq, Tensor state_slot, Tensor conv_state, Tensor out, bool update_state, bool one_token_per_seq, bool pdl, Tensor? seq_end=None, bool state_only=False, Tensor? parent=None, Tensor? last_token=None) -> ()", &causal_conv1d_silu);
-  m.def("gdn_recurrent(Tensor qkv, int q_off, int k_off, int v_off, Tensor proj, int z_off, int a_off, int b_off, int n_qk_heads, int n_v_heads, Tensor A_log, Tensor dt_bias, Tensor norm_w, float eps, Tensor cu_seqlens, Tensor state_slot, Tensor state, bool write_state, Tensor out, bool pdl, Tensor? seq_end=None, Tensor? commit=None, Tensor? chunk_ws=None, Tensor? conv_w=None, Tensor? conv_state=None) -> ()", &gdn_recurrent);
+  m.def("gdn_recurrent(Tensor qkv, int q_off, int k_off, int v_off, Tensor proj, int z_off, int a_off, int b_off, int n_qk_heads, int n_v_heads, Tensor A_log, Tensor dt_bias, Tensor norm_w, float eps, Tensor cu_seqlens, Tensor state_slot, Tensor state, bool write_state, Tensor out, bool pdl, Tensor? seq_end=None, Tensor? commit=None, Tensor? chunk_ws=None, Tensor? conv_w=None, Tensor? conv_state=None, Tensor? q_codes=None, Tensor? q_sf=None) -> ()", &gdn_recurrent);
   m.def("gdn_chunked_workspace_bytes(int T, int n_seq, int n_v_heads) -> int", &gdn_chunked_workspace_bytes);
   m.def("gdn_prefill_trace(bool enable) -> Tensor", &gdn_prefill_trace);
   m.def("kv_move_rows(Tensor block_table, Tensor table_row, Tensor src_pos, Tensor dst_pos, Tensor k_codes, Tensor v_codes, Tensor? k_scales, Tensor? v_scales, int page_size, int n_kv_heads, int head_dim, int format, int group) -> ()", &kv_move_rows);

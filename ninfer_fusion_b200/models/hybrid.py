@@ -270,6 +270,8 @@ class HybridModel:
         # gathered from the owner ranks and ws.normed has not been written (tensor parallel, decode sizes)
         self._gathered = None
         self.act_nvfp4 = any(isinstance(t, QuantWeight) and t.qtype == 2 for t in weights.values())
+        # nvfp4: producers quantise their own output for the next GEMM (NFB_FUSE_ACT_QUANT=0: stand-alone quantiser)
+        self._fuse_act_quant = os.environ.get("NFB_FUSE_ACT_QUANT", "1") != "0"
         self._prequant = None
         self._qbuf: Dict[int, tuple] = {}
         self._padbuf: Dict[int, torch.Tensor] = {}
@@ -335,11 +337,29 @@ class HybridModel:
             if self._prequant != (x.data_ptr(), T, K):
                 self.ops.quant_act_nvfp4(x, xc, plane, self.pdl)
             self._prequant = None
-            self.ops.gemm_quant(2, xc, plane, w.codes, w.scale, w.divisor, out, epi, resid, splits, self.status.tensor, self.pdl)
+            nxt = (None, None)
+            if epi == EPI_SWIGLU and T <= 128 and (N // 2) % 64 == 0 and self._fuse_act_quant:
+                # the SwiGLU epilogue also writes the activation as the down projection's W4A4 operand
+                K2 = N // 2
+                _, codes2, _, plane2 = self._quant_scratch(T, K2)
+                nxt = (codes2[: T * K2 // 2], plane2)
+            self.ops.gemm_quant(2, xc, plane, w.codes, w.scale, w.divisor, out, epi, resid, splits, self.status.tensor, self.pdl,
+                                *nxt)
+            if nxt[0] is not None:
+                self._prequant = (out.data_ptr(), T, N // 2)
         else:
             xc = codes[: T * K].view(T, K)
             self.ops.quant_act_fp8(x, xc, scale, self.pdl)
             self.ops.gemm_quant(1, xc, scale, w.codes, w.scale, 1.0, out, epi, resid, splits, self.status.tensor, self.pdl)
+
+    def _next_operand(self, T: int, w_next, width: int):
+        """(codes, scale plane) of the nvfp4 operand a producer should write for the GEMM over `w_next`, or (None, None):
+        decode sizes, W4A4 weights, no K padding."""
+        if (self._fuse_act_quant and T <= 128 and isinstance(w_next, QuantWeight) and w_next.qtype == 2
+                and w_next.shape[1] == width and width % 64 == 0):
+            _, codes, _, plane = self._quant_scratch(T, width)
+            return codes[: T * width // 2], plane
+        return None, None
 
     def _pf(self, T: int, w_next):
         """The tensor a decode-sized GEMM should prefetch towards L2, or None."""
@@ -455,7 +475,11 @@ class HybridModel:
                       and os.environ.get("NFB_ATTN_TC", "1") != "0")
         split, n_splits = pick_attention_split(b.max_kv_len, T * g.n_kv_heads, max_splits=ws.max_splits_attn,
                                                waves=8 if persistent else 2)
+        if persistent:
+            n_splits = max(n_splits, 2)   # the kernel cuts rows at CTA boundaries: a row needs a second result slot
         chunk = max(1, ws.part_rows // n_splits)
+        w_out = self.w[f"{prefix}/attn/o_proj"]
+        qc, qs = self._next_operand(T, w_out, q_dim) if chunk >= T else (None, None)   # nvfp4: merge quantises its rows
         for t0 in range(0, T, chunk):
             t1 = min(T, t0 + chunk)
             ops.paged_attention(q[t0:t1], g.n_q_heads, g.n_kv_heads, D, b.table_row[t0:t1], b.kv_len[t0:t1], kv.table,
@@ -463,8 +487,10 @@ class HybridModel:
                                 planes.fmt, planes.group, self.sm_scale, split, n_splits, ws.part_o, ws.part_ml,
                                 gate[t0:t1], out[t0:t1], None if b.tree_mask is None else b.tree_mask[t0:t1],
                                 None if b.tree_base is None else b.tree_base[t0:t1], self.attn_impl, self.pdl,
-                                self.layer_window.get(layer, 0), None, None, tiers)
-        return out, self.w[f"{prefix}/attn/o_proj"]
+                                self.layer_window.get(layer, 0), None, None, tiers, qc, qs)
+        if qc is not None:
+            self._prequant = (out.data_ptr(), T, q_dim)
+        return out, w_out
 
     def _gdn_layer(self, ws: Workspace, b: StepBatch, st: GdnStatePool, layer: int, T: int, prefix: str,
                    write_state: bool = True, rec: Optional[GdnRecords] = None):
@@ -509,11 +535,17 @@ class HybridModel:
                 self._gdn_ws = torch.empty(need, dtype=torch.uint8, device=self.device)
             chunk_ws = self._gdn_ws
             ops.count += 2
+        w_out = self.w[f"{prefix}/gdn/out_proj"]
+        qc, qs = (None, None)
+        if decode and chunk_ws is None and b.tree_commit is None:
+            qc, qs = self._next_operand(T, w_out, g.gdn_v_dim)   # nvfp4: the step quantises its own output rows
         ops.gdn_recurrent(conv, 0, qk, 2 * qk, proj, C, C + g.gdn_v_dim, C + g.gdn_v_dim + g.gdn_v_heads,
                           g.gdn_qk_heads, g.gdn_v_heads, self.w[f"{prefix}/gdn/A_log"], self.w[f"{prefix}/gdn/dt_bias"],
                           self.w[f"{prefix}/gdn/norm"], cfg.rms_eps, b.cu_seqlens, b.state_slot, st.ssm[gi],
-                          write_state, out, self.pdl, None, b.tree_commit, chunk_ws)
-        return out, self.w[f"{prefix}/gdn/out_proj"]
+                          write_state, out, self.pdl, None, b.tree_commit, chunk_ws, None, None, qc, qs)
+        if qc is not None:
+            self._prequant = (out.data_ptr(), T, g.gdn_v_dim)
+        return out, w_out
 
     def _mlp(self, ws: Workspace, T: int, prefix: str, next_norm_w, normed_out, next_w=None):
         w_gu = self.w[f"{prefix}/mlp/gate_up"]

@@ -115,6 +115,28 @@ def test_quantised_weights_logits_close_to_dequantised_oracle(weight_format):
     assert all(len(o) == 6 for o in out)
 
 
+def test_nvfp4_producers_that_quantise_their_own_output_write_the_same_bits():
+    """nvfp4 decode: the SwiGLU epilogue, the GDN step and the attention merge write the next GEMM's W4A4 operand
+    themselves; the tokens AND the logits equal the run with the stand-alone quantiser kernel, with 2 launches per
+    layer fewer."""
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cuda", seed=7, std=0.05, weight_format="nvfp4")
+    torch.manual_seed(4)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (21, 40, 9)]
+    runs = []
+    for fused in (True, False):
+        gen = Generator(cfg, w, "cuda", max_batch=4, max_context=512, kv_format="bf16", page_size=16, prefill_chunk=64,
+                        use_graph=False)
+        gen.model._fuse_act_quant = fused
+        gen.prefill(prompts)
+        before = gen.model.ops.count
+        toks = [gen.decode_step() for _ in range(5)]
+        runs.append((toks, gen.ws.logits[:3].float().cpu().clone(), gen.model.ops.count - before))
+    assert runs[0][0] == runs[1][0]
+    assert torch.equal(runs[0][1], runs[1][1])
+    assert runs[1][2] - runs[0][2] == 5 * 2 * cfg.n_layers       # two quantiser launches per layer and step saved
+
+
 def test_yarn_rope_matches_reference():
     """YaRN x4 frequency table + attention factor on the engine against the oracle with the same table."""
     from dataclasses import replace
