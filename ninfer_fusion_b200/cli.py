@@ -72,9 +72,10 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--vision-layers", type=int, default=0, help="shrink the vision tower to this many blocks (debug)")
     ap.add_argument("--kv-capacity", default="full", help="main KV pool: 'full', 'auto' or a token count >= --max-context")
     ap.add_argument("--kv-headroom-gib", type=float, default=2.0, help="device memory left free by --kv-capacity auto")
-    ap.add_argument("--planner", default="lru", choices=["lru", "b200", "h100", "rtx5090"],
-                    help="which cached frontier is given up under memory pressure: least recently used, or the "
-                         "materialisation planner with that machine's cost preset")
+    ap.add_argument("--planner", default="lru",
+                    help="which cached frontier is given up under memory pressure: 'lru' (least recently used), or the "
+                         "materialisation planner with a machine cost preset: b200 | h100 | rtx5090 | file:<path> "
+                         "(a file measured on this machine by `python -m ninfer_fusion_b200.utils.calib`)")
     ap.add_argument("--cold-slots", action="store_true",
                     help="int8 KV pages leave the device as requantised cold slots (lossy, 0.55 of the bytes)")
     ap.add_argument("--anchor-interval", type=int, default=0,
@@ -189,11 +190,39 @@ def setup_ranks(args):
     return rank, world, RankChannel.create(rank, world, timeout_s=float(getattr(args, "rank_timeout", 60.0)))
 
 
+def check_device_routes(args, weights) -> None:
+    """Refuses, before any kernel runs, a GPU without the instruction families of this package's kernels or a weight
+    format without a route on it (archcaps.py); a CPU device runs the reference model and needs no route."""
+    if not str(args.device).startswith("cuda"):
+        return
+    from . import archcaps
+    major, minor = torch.cuda.get_device_capability(torch.device(args.device))
+    formats, experts = set(), set()
+    for name, t in weights.items():
+        qt = getattr(t, "qtype", None)
+        if qt == 1:
+            fmt = "FP8_E4M3FN_ROW_BF16S"
+        elif qt == 2:
+            fmt = "NVFP4"
+        elif qt is not None:
+            fmt = getattr(t, "fmt", None)          # groupwise-int objects carry their artifact format name
+        else:
+            fmt = "BF16" if getattr(t, "dtype", None) == torch.bfloat16 else None
+        if fmt is None or getattr(t, "dim", lambda: 2)() < 2 and qt is None:
+            continue
+        (experts if "/experts_" in name else formats).add(fmt)
+    try:
+        archcaps.require_artifact_formats_supported(formats, major * 10 + minor, experts)
+    except archcaps.RouteRefused as e:
+        raise SystemExit(f"this GPU cannot run the model: {e}")
+
+
 def build_engine(args, cfg: ModelConfig, weights, ranks=None) -> Optional[Engine]:
     """The engine of this process.  With `ranks` (see setup_ranks) the model is tensor-parallel: rank 0 gets an
     Engine whose Program mirrors every step to the followers; a follower runs its loop here until the leader
     stops it and gets None."""
     kv = args.kv_dtype
+    check_device_routes(args, weights)
     if ranks is not None:
         from .parallel.replicated import LeaderProgram, follower_loop
         from .parallel.tp import TensorParallel
@@ -259,8 +288,9 @@ def program_factory(args, cfg: ModelConfig, weights, kv, shard=None, comm=None):
             prog.anchor_interval = max(0, int(getattr(args, "anchor_interval", 0)))
             prog.kv.cold_slots = bool(getattr(args, "cold_slots", False))
             if getattr(args, "planner", "lru") != "lru":
-                from .runtime.planner import PRESETS, MaterializationPlanner
-                prog.planner = MaterializationPlanner(PRESETS[args.planner])
+                from .runtime.planner import MaterializationPlanner
+                from .utils.calib import load_preset   # built-in name or file:<path> written by utils/calib.py
+                prog.planner = MaterializationPlanner(load_preset(args.planner))
             return attach_vision(args, cfg, weights, prog)
     else:
         def factory():

@@ -54,6 +54,13 @@ def cufree() -> int:
     for dist in ("torch", "numpy"):
         spec = importlib.util.find_spec(dist)
         _row(f"python package {dist} (not imported)", spec.origin if spec and spec.origin else dist, spec is not None)
+    print("architectures and what this package's kernels find on them (capability table, no device is asked):")
+    spec = importlib.util.spec_from_file_location("_nfb_archcaps", os.path.join(HERE, "archcaps.py"))
+    caps = importlib.util.module_from_spec(spec)
+    sys.modules["_nfb_archcaps"] = caps
+    spec.loader.exec_module(caps)
+    for rung in caps.ARCH_LADDER:
+        print("  " + caps.device_report(rung.sm))
     print("verdict: this program cannot tell whether a GPU works; it reports which of the things a GPU run needs exist as files")
     return 0
 

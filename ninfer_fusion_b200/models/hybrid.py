@@ -455,10 +455,11 @@ class HybridModel:
         q_dim, kv_dim = g.n_q_heads * D, g.n_kv_heads * D
         planes = kv.layers[kv_index]
         tiers = getattr(planes, "desc", None)   # mixed-precision layer: addresses of its tiers and of its cell map
+        table = planes.block_table if getattr(planes, "block_table", None) is not None else kv.table
         q = ws.q[:T]
         ops.attn_prep(proj, 0, q_dim, q_dim + kv_dim + q_dim, g.n_q_heads, g.n_kv_heads, D,
                       self.w[f"{prefix}/attn/q_norm"], self.w[f"{prefix}/attn/k_norm"], cfg.rms_eps, True,
-                      cfg.rot_dim, self.inv_freq, self.rope_factor, b.rope_pos, b.table_row, b.cache_pos, kv.table, q,
+                      cfg.rot_dim, self.inv_freq, self.rope_factor, b.rope_pos, b.table_row, b.cache_pos, table, q,
                       planes.k_codes, planes.v_codes, planes.k_scales, planes.v_scales, kv.page_size, planes.fmt,
                       planes.group, self.pdl, planes.hadamard, self.k_row_scale.get(layer), tiers)
         gate = proj[:, q_dim + kv_dim: q_dim + kv_dim + q_dim]
@@ -467,7 +468,7 @@ class HybridModel:
                 and T > b.n_seqs and b.tree_mask is None):
             # prefill / wide verify: one CTA per (query block, kv head), K/V tiles dequantised once per block
             ops.paged_attention_prefill(q, g.n_q_heads, g.n_kv_heads, D, b.table_row, b.kv_len, b.qblk_start,
-                                        b.qblk_count, kv.table, planes.k_codes, planes.v_codes, planes.k_scales,
+                                        b.qblk_count, table, planes.k_codes, planes.v_codes, planes.k_scales,
                                         planes.v_scales, kv.page_size, planes.fmt, planes.group, self.sm_scale, gate,
                                         out, self.pdl, 0, tiers)
             return out, self.w[f"{prefix}/attn/o_proj"]
@@ -482,7 +483,7 @@ class HybridModel:
         qc, qs = self._next_operand(T, w_out, q_dim) if chunk >= T else (None, None)   # nvfp4: merge quantises its rows
         for t0 in range(0, T, chunk):
             t1 = min(T, t0 + chunk)
-            ops.paged_attention(q[t0:t1], g.n_q_heads, g.n_kv_heads, D, b.table_row[t0:t1], b.kv_len[t0:t1], kv.table,
+            ops.paged_attention(q[t0:t1], g.n_q_heads, g.n_kv_heads, D, b.table_row[t0:t1], b.kv_len[t0:t1], table,
                                 planes.k_codes, planes.v_codes, planes.k_scales, planes.v_scales, kv.page_size,
                                 planes.fmt, planes.group, self.sm_scale, split, n_splits, ws.part_o, ws.part_ml,
                                 gate[t0:t1], out[t0:t1], None if b.tree_mask is None else b.tree_mask[t0:t1],

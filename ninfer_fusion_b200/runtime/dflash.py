@@ -12,15 +12,53 @@ src/targets/qwen3_6/impl/runtime/dflash_impl.h:98-551.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Sequence
+from typing import Dict, List, Optional, Sequence
 
 import torch
 
 from ..models.config import ModelConfig
 from ..models.dflash import DFlashConfig, draft_model_config
 from ..models.hybrid import EPI_STORE, HybridModel, Workspace
+from .arena import BumpArena
 from .batch import SeqChunk, StepBuffers
-from .kv_cache import PagedKvCache
+from .kv_cache import CyclicKvCache, PagedKvCache
+
+
+class _SplitKv:
+    """The draft decoder's cache as the model sees it: the planes of the sliding-window layers live in a cyclic cache
+    (a bounded ring of pages per row) and carry that cache's block table, the other layers live in a full cache."""
+
+    def __init__(self, local: Optional[CyclicKvCache], full: Optional[PagedKvCache]):
+        self.local, self.full = local, full
+        main = full if full is not None else local
+        self.page_size, self.table = main.page_size, main.table
+        self.layers = []
+        if local is not None:
+            for pl in local.layers:
+                if full is not None:
+                    pl.block_table = local.table
+                self.layers.append(pl)
+        if full is not None:
+            self.layers.extend(full.layers)
+
+    def table_of(self, layer: int) -> torch.Tensor:
+        pl = self.layers[layer]
+        return pl.block_table if pl.block_table is not None else self.table
+
+    def ensure(self, row: int, n_tokens: int) -> None:
+        for c in (self.local, self.full):
+            if c is not None:
+                c.ensure(row, n_tokens)
+
+    def publish(self) -> None:
+        for c in (self.local, self.full):
+            if c is not None:
+                c.publish()
+
+    def free_row(self, row: int) -> None:
+        for c in (self.local, self.full):
+            if c is not None:
+                c.free_row(row)
 
 
 class DFlashDrafter:
@@ -37,14 +75,25 @@ class DFlashDrafter:
         T = max_batch * K
         self.max_append = max(max_append, T)
         self.ws = Workspace(cfg, self.max_append, T, dev)
-        pages_per_row = (max_context + K + 1 + page_size - 1) // page_size
-        self.kv = PagedKvCache(cfg, max_batch * pages_per_row, page_size, max_batch, pages_per_row, dev, formats="bf16")
+        ctx = max_context + K + 1
+        pages_per_row = (ctx + page_size - 1) // page_size
+        n_local, n_full = self.dc.local_layers, cfg.n_layers - self.dc.local_layers
+        # the block of K positions is written past the frontier and must stay inside the ring: window + K keys live
+        local = CyclicKvCache(cfg, self.dc.window + K, page_size, max_batch, ctx, dev, formats="bf16",
+                              n_layers=n_local) if n_local else None
+        full = PagedKvCache(cfg, max_batch * pages_per_row, page_size, max_batch, pages_per_row, dev, formats="bf16",
+                            n_layers=n_full) if n_full else None
+        self.kv = _SplitKv(local, full)
         self.bufs = StepBuffers(T, max_batch, dev, attn_block_tokens=16, max_logit_rows=T)
-        h = cfg.hidden
-        self.ctx_raw = torch.empty((self.max_append, h), dtype=torch.bfloat16, device=dev)
-        self.ctx = torch.empty((self.max_append, h), dtype=torch.bfloat16, device=dev)
-        self.ctx_kv = torch.empty((self.max_append, 2 * cfg.kv_dim), dtype=torch.bfloat16, device=dev)
-        self.q_scratch = torch.empty((self.max_append, cfg.kv_dim), dtype=torch.bfloat16, device=dev)
+        # scratch of the context append: the two context copies live for the whole append, the per-layer K / V
+        # projection and the append kernel's query output share one scope that every layer reuses
+        h, n = cfg.hidden, self.max_append
+        self.arena = BumpArena(2 * (2 * n * h + n * 3 * cfg.kv_dim) + 4 * 256, dev)
+        self.ctx_raw = self.arena.alloc((n, h), torch.bfloat16, "projected features")
+        self.ctx = self.arena.alloc((n, h), torch.bfloat16, "context (normed)")
+        with self.arena.scope():
+            self.ctx_kv = self.arena.alloc((n, 2 * cfg.kv_dim), torch.bfloat16, "layer context K / V")
+            self.q_scratch = self.arena.alloc((n, cfg.kv_dim), torch.bfloat16, "append kernel query scratch")
         self.all_bits = (1 << K) - 1
         self.proposals = 0
 
@@ -80,7 +129,7 @@ class DFlashDrafter:
                 # the append kernel wants query heads as well: the key columns stand in for them (n_q = n_kv), its
                 # query output goes to scratch
                 ops.attn_prep(kvp, 0, 0, cfg.kv_dim, cfg.n_kv_heads, cfg.n_kv_heads, cfg.head_dim, kn, kn, cfg.rms_eps, True,
-                              cfg.rot_dim, m.inv_freq, m.rope_factor, pos, rows, pos, self.kv.table,
+                              cfg.rot_dim, m.inv_freq, m.rope_factor, pos, rows, pos, self.kv.table_of(l),
                               self.q_scratch[:n].view(n, cfg.n_kv_heads, cfg.head_dim), planes.k_codes, planes.v_codes,
                               planes.k_scales, planes.v_scales, self.kv.page_size, planes.fmt, planes.group, m.pdl)
 

@@ -46,6 +46,9 @@ class KvLayerPlanes:
     k_scales: Optional[torch.Tensor]
     v_scales: Optional[torch.Tensor]
     hadamard: bool = False   # K (and the matching Q) live in the normalised Hadamard frame ("fp8h")
+    # set when this layer's pages are addressed through ANOTHER cache's block table (a model whose sliding-window
+    # layers live in a CyclicKvCache while its other layers live in a full cache); None = the owning cache's table
+    block_table: Optional[torch.Tensor] = None
 
     def bytes(self) -> int:
         n = self.k_codes.numel() + self.v_codes.numel()
@@ -549,6 +552,48 @@ class PagedKvCache:
             for r in self._dirty_rows:
                 self.table[r].copy_(self.table_host[r], non_blocking=True)
         self._dirty_rows.clear()
+
+
+class CyclicKvCache(PagedKvCache):
+    """KV cache of sliding-window layers: every row owns a bounded ring of pages however long the sequence grows.
+
+    A windowed layer never looks further back than `window` keys, so a row needs pages for window + slack + one
+    page of positions only.  The block table keeps one entry per logical page of the whole context (so the kernels
+    address it exactly like a full cache); `ensure` first returns the pages that slid out of the window to the pool
+    (their table entries become -1: the attention kernels skip such pages) and then maps the new positions, which
+    reuses those physical pages.  Only valid when EVERY layer of this cache is windowed.
+
+    Counterpart of the reference's cyclic cache for its sliding-window / DFlash local layers
+    (src/core/cyclic_kv_cache.h); here the ring is a property of the page map, not a second kernel interface."""
+
+    def __init__(self, cfg: ModelConfig, window: int, page_size: int, max_rows: int, max_context: int, device,
+                 formats: Sequence[str] | str = "bf16", slack: int = 64, n_kv_heads: Optional[int] = None,
+                 n_layers: Optional[int] = None):
+        if window <= 0:
+            raise ValueError("a cyclic cache needs a positive window")
+        self.window, self.slack = window, slack
+        self.ring_pages = (window + slack + page_size - 1) // page_size + 2   # + the partial pages at both ends
+        super().__init__(cfg, max_rows * self.ring_pages, page_size, max_rows, (max_context + page_size - 1) // page_size,
+                         device, formats=formats, n_kv_heads=n_kv_heads, n_layers=n_layers)
+
+    def ensure(self, row: int, n_tokens: int) -> None:
+        self.release_before(row, n_tokens, self.window, self.slack)
+        pages = self.row_pages.setdefault(row, [])
+        need = (n_tokens + self.page_size - 1) // self.page_size
+        if need > self.max_pages_per_row:
+            raise MemoryError(f"row {row}: {n_tokens} tokens exceed the block-table width")
+        # positions before the window that were never mapped stay unmapped
+        first_needed = max(0, n_tokens + 1 - self.window - self.slack) // self.page_size
+        while len(pages) < min(first_needed, need):
+            pages.append(-1)
+        while len(pages) < need:
+            p = self._page_alloc()
+            self.table_host[row, len(pages)] = p
+            pages.append(p)
+            self._dirty_rows.add(row)
+
+    def live_pages(self, row: int) -> int:
+        return sum(1 for p in self.row_pages.get(row, []) if p >= 0)
 
 
 class GdnStatePool:

@@ -200,3 +200,28 @@ def test_mixed_layer_cells_follow_logical_pages_on_cpu():
     L.alloc_cell(p0, 2)
     kv.fork_row(0, 1, 8)                           # partial first page: copied
     assert L.tier_of(kv.row_pages[1][0]) == 2 and (int(L.cell_map_host[kv.row_pages[1][0]]) >> CELL_TIER_SHIFT) == 2
+
+
+def test_cyclic_cache_keeps_a_bounded_ring_of_pages_per_row():
+    """A windowed row grows without bound in positions while holding a bounded number of pages; pages that slid out
+    of the window are unmapped (-1) and their physical pages come back for the new positions."""
+    from ninfer_fusion_b200.models.config import TINY_DENSE
+    from ninfer_fusion_b200.runtime.kv_cache import CyclicKvCache
+    P, W = 16, 64
+    kv = CyclicKvCache(TINY_DENSE, W, P, max_rows=2, max_context=4096, device="cpu", formats="bf16", slack=16, n_layers=1)
+    assert kv.n_pages == 2 * kv.ring_pages and kv.ring_pages == (64 + 16 + 15) // 16 + 2
+    seen = set()
+    for n in range(1, 3000, 37):
+        kv.ensure(0, n)
+        kv.ensure(1, max(1, n // 2))
+        assert kv.live_pages(0) <= kv.ring_pages
+        seen.update(p for p in kv.row_pages[0] if p >= 0)
+        first_visible = max(0, n - W)
+        for pos in range(first_visible, n):               # every position the window can see is mapped
+            assert kv.table_host[0, pos // P] >= 0
+    assert len(seen) <= kv.n_pages                           # 3000 positions went through at most the pool's pages
+    assert int((kv.table_host[0] >= 0).sum()) == kv.live_pages(0) <= kv.ring_pages
+    assert kv.table_host[0, 0] == -1                         # the oldest page is gone
+    kv.free_row(0)
+    kv.free_row(1)
+    assert kv.pool.free_pages == kv.n_pages
