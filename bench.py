@@ -141,7 +141,7 @@ def reference_arm(args) -> int:
 
 def speculative_run(args, cfg, device) -> int:
     """Draft-verify decoding against plain greedy decoding of the same model and prompts on one GPU: decode tok/s of
-    both (device-timed, whole rounds, host round trips included: speculative rounds are eager), acceptance rate and
+    both (device-timed, whole rounds, host round trips included), acceptance rate and
     tokens per round.  Prints one JSON line with class "speculative"."""
     import torch
 
@@ -154,7 +154,7 @@ def speculative_run(args, cfg, device) -> int:
         return 2
     B, L, Kd, R_ = args.batch, args.prompt_len, args.draft_tokens, args.tree_ranks
     n_rounds, warm = args.steps, max(3, args.warmup)
-    weights = random_weights(cfg, device, seed=0, with_mtp=True)
+    weights = random_weights(cfg, device, seed=0, with_mtp=True, weight_format=args.weights)
     if args.spec == "dflash":
         from ninfer_fusion_b200.models.dflash import DFlashConfig, random_dflash_weights
         weights.update(random_dflash_weights(cfg, DFlashConfig(), weights, device))
@@ -193,13 +193,26 @@ def speculative_run(args, cfg, device) -> int:
     spec = SpeculativeGenerator(cfg, weights, device, max_batch=B, max_context=max_ctx, draft_tokens=Kd,
                                 drafter=args.spec if args.spec in ("mtp", "dflash") else "hook", tree_ranks=R_,
                                 kv_format=args.kv_format,
-                                page_size=64, prefill_chunk=2048, pdl=bool(args.pdl))
+                                page_size=64, prefill_chunk=2048, pdl=bool(args.pdl), use_graph=not args.spec_eager)
     if args.spec == "hook":
+        # Synthetic drafts of mixed quality need the stream the VERIFY pass itself emits: with random-init weights many
+        # logits are near ties, and a (K + 1)-row verify pass does not round like a one-row decode pass, so drafts copied
+        # from the plain run above would be rejected for numerical reasons.  Record that stream first: rounds whose
+        # drafts are all wrong emit exactly one token each, the verify pass's own.
+        def wrong(b, history, k):
+            return [(history[-1] + 1 + i) % cfg.vocab for i in range(k)]
+        spec.draft_hook = wrong
+        first_v = spec.prefill(prompts)
+        stream = [[t] for t in first_v]
+        for _ in range(n_plain - 1):
+            for b, toks in enumerate(spec.decode_round()):
+                stream[b].extend(toks)
+
         def hook(b, history, k):
             done = len(history) - L
             truth = stream[b][done:done + k]
             truth = truth + [0] * (k - len(truth))
-            cut = (done + b) % (k + 1)
+            cut = (spec.rounds + b) % (k + 1)   # by round, not by position: a position rule locks into "all right"
             return [t if i < cut else (t + 1) % cfg.vocab for i, t in enumerate(truth)]
         spec.draft_hook = hook
         if R_ > 1:
@@ -228,11 +241,12 @@ def speculative_run(args, cfg, device) -> int:
     out = {
         "class": "speculative", "metric": "decode tokens/sec, draft-verify vs plain greedy (same model, prompts, GPU)",
         "value": round(emitted / (spec_ms / 1e3), 2), "unit": "tokens/s", "n_gpus": 1, "steps": n_rounds, "warmup": warm,
-        "ms_per_step": round(spec_ms / n_rounds, 4), "higher_is_better": True, "dtype": "bf16",
+        "ms_per_step": round(spec_ms / n_rounds, 4), "higher_is_better": True, "dtype": args.weights,
         "data": "synthetic uniform-random token prompts, random-init weights",
         "config": {"model": cfg.name + ("" if not args.layers else " (SHRUNK: INVALID)"), "global_batch": B, "seq_len": L,
                    "kv": args.kv_format, "drafter": args.spec, "draft_tokens": Kd, "tree_ranks": R_,
-                   "rounds": "eager (no CUDA graph), host round trip per round"},
+                   "rounds": ("eager (no CUDA graph)" if not spec._graph_round_ok() else "one CUDA graph per round")
+                   + ", one host round trip per round (accepted lengths and tokens)"},
         "tokens_per_round": round(emitted / max(1, (spec.rounds - r0) * B), 3),
         "acceptance": round((emitted / max(1, (spec.rounds - r0) * B) - 1.0) / Kd, 4),
         "plain": {"tokens_per_s": round(plain_tok_s, 2), "ms_per_step": round(plain_ms / steps_plain, 4),
@@ -267,11 +281,12 @@ def main() -> int:
                     help="tensor-parallel reduction: fused = reduce-scatter + all-gather inside the GEMMs, oneshot = "
                          "every rank receives every tile + one sum kernel, nccl = NCCL all-reduce baseline, auto = the "
                          "faster of fused / oneshot at this GPU count as measured (TensorParallel.best_mode)")
+    ap.add_argument("--spec-eager", action="store_true", help="speculative rounds without CUDA graphs")
     ap.add_argument("--spec", default="none", choices=["none", "mtp", "dflash", "hook"],
-                    help="speculative decoding run (one GPU, eager rounds): mtp = the draft module proposes, dflash = the "
+                    help="speculative decoding run (one GPU): mtp = the draft module proposes, dflash = the "
                          "block-diffusion draft model proposes the whole block in one pass (random-init "
-                         "weights accept next to nothing), hook = synthetic drafts of mixed quality taken from the plain "
-                         "greedy stream (the first (round + b) mod (K + 1) drafts right, the rest wrong)")
+                         "weights accept next to nothing), hook = synthetic drafts of mixed quality taken from the stream "
+                         "the verify pass itself emits (the first (round + b) mod (K + 1) drafts right, the rest wrong)")
     ap.add_argument("--draft-tokens", type=int, default=4)
     ap.add_argument("--tree-ranks", type=int, default=1, help="candidates per depth of the draft tree (1 = chain)")
     ap.add_argument("--parallel", default="", choices=["", "tp", "ep"],

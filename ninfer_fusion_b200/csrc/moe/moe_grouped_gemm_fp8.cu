@@ -8,10 +8,17 @@
 // buffer.  Warp roles: 0 = TMA producer, 1 = MMA issuer, 2..5 = scale-and-accumulate + final epilogue
 // (SwiGLU or "return" exactly as in the bf16 kernel, moe_grouped_gemm.cu).
 //
+// WIDE variant (decode-sized tiles, num_kb * TN <= 512): every k-block gets TMEM columns of its own, so the MMA issuer
+// never waits for the accumulate warps and the weight stream runs at the pace of TMA alone; the accumulate warps follow
+// one mbarrier per k-block and read the tile's activation scales from shared memory.  With two buffers the issuer is at
+// most one k-block ahead, and a 128-deep MMA is far shorter than the read-scale-add of one k-block: the hand-shake,
+// not the bytes, set the pace of the kernel at a few tokens per expert.
+//
 // The reference has no fp8 block-scaled expert format (its routed banks are Q4+Q5 / Q4+Q6 / W8 row-split,
 // src/ops/sparse_moe); the container registers it as FP8_E4M3FN_BLOCK128_F32S / blockscale-128x128-f32-v1.
 #include "moe.h"
 
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -28,6 +35,9 @@ constexpr int kKBytes = 128;           // one k-block: 128 fp8 values = one swiz
 constexpr int kTileN = 128;
 constexpr int kWTileBytes = kTileN * kKBytes;
 constexpr int kThreads = 192;
+
+constexpr int kWideMaxKb = 32;         // WIDE: one accumulator and one mbarrier per k-block
+constexpr int kWideCols = 512;
 
 template <int TN>
 struct Fp8Cfg {
@@ -57,7 +67,7 @@ struct Fp8Params {
 
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-template <int TN, int EPI>
+template <int TN, int EPI, bool WIDE>
 __global__ void __launch_bounds__(kThreads) moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w,
                                                                  const __grid_constant__ CUtensorMap tmap_x,
                                                                  const Fp8Params p) {
@@ -66,8 +76,10 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_fp8_kernel(const __grid_con
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kStages];
   __shared__ __align__(8) uint64_t bar_empty[kStages];
-  __shared__ __align__(8) uint64_t bar_acc_full[2];
+  constexpr int kAccBars = WIDE ? kWideMaxKb : 2;
+  __shared__ __align__(8) uint64_t bar_acc_full[kAccBars];
   __shared__ __align__(8) uint64_t bar_acc_free[2];
+  __shared__ float sx_s[WIDE ? kWideCols : 1];   // WIDE: activation scales of the tile, [token][k-block]
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ int meta_s[TN];
@@ -93,10 +105,8 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_fp8_kernel(const __grid_con
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&bar_acc_full[b]), 1);
-      mbar_init(smem_u32(&bar_acc_free[b]), 4);   // one arrival per epilogue warp
-    }
+    for (int b = 0; b < kAccBars; ++b) mbar_init(smem_u32(&bar_acc_full[b]), 1);
+    for (int b = 0; b < 2; ++b) mbar_init(smem_u32(&bar_acc_free[b]), 4);   // one arrival per epilogue warp
     mbar_fence_init();
     tma_prefetch_desc(&tmap_w);
     tma_prefetch_desc(&tmap_x);
@@ -106,8 +116,14 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_fp8_kernel(const __grid_con
   if (EPI == kMoeEpiReturn) {
     for (int j = threadIdx.x; j < TN; j += kThreads) meta_s[j] = j < rows ? p.recv_meta[row0 + j] : -1;
   }
+  // WIDE: num_kb * TN columns, rounded up to a power of two (the host admits the variant only up to 512)
+  uint32_t tmem_cols = Cfg::kTmemCols;
+  if (WIDE) {
+    tmem_cols = 32;
+    while (tmem_cols < static_cast<uint32_t>(num_kb * TN)) tmem_cols <<= 1;
+  }
   if (warp == 2) {
-    tmem_alloc(smem_u32(&tmem_base_slot), Cfg::kTmemCols);
+    tmem_alloc(smem_u32(&tmem_base_slot), tmem_cols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -156,9 +172,9 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_fp8_kernel(const __grid_con
       for (int it = 0; it < num_kb; ++it) {
         const int s = it % kStages;
         const uint32_t ph = (it / kStages) & 1;
-        const int b = it & 1;
+        const int b = WIDE ? it : (it & 1);
         const int use = it >> 1;   // how often buffer b has been filled before
-        if (use > 0 &&
+        if (!WIDE && use > 0 &&
             !mbar_wait(smem_u32(&bar_acc_free[b]), (use - 1) & 1, &abort_flag, p.status, kStatusAccumWaitTimeout))
           break;
         if (!mbar_wait(smem_u32(&bar_full[s]), ph, &abort_flag, p.status, kStatusTmaWaitTimeout)) break;
@@ -189,9 +205,14 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_fp8_kernel(const __grid_con
 #pragma unroll
     for (int c = 0; c < TN; ++c) acc[c] = 0.f;
     bool ok = true;
+    if (WIDE) {
+      // the tile's rows are consecutive in x_scale: rows * num_kb floats, zero beyond the tile's live rows
+      for (int i = threadIdx.x - 64; i < TN * num_kb; i += 128) sx_s[i] = i < rows * num_kb ? sx[i] : 0.f;
+      epi_bar_sync();
+    }
     for (int it = 0; it < num_kb; ++it) {
-      const int b = it & 1;
-      const int use = it >> 1;
+      const int b = WIDE ? it : (it & 1);
+      const int use = WIDE ? 0 : (it >> 1);
       if (!mbar_wait(smem_u32(&bar_acc_full[b]), use & 1, &abort_flag, p.status, kStatusAccumWaitTimeout)) {
         ok = false;
         break;
@@ -206,14 +227,18 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_fp8_kernel(const __grid_con
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const float s = (c + j < rows) ? swk * sx[(c + j) * num_kb + it] : 0.f;
+            float s;
+            if (WIDE) s = swk * sx_s[(c + j) * num_kb + it];
+            else s = (c + j < rows) ? swk * sx[(c + j) * num_kb + it] : 0.f;
             acc[c + j] += __uint_as_float(v[j]) * s;
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_acc_free[b]));
+      if (!WIDE) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_acc_free[b]));
+      }
     }
 
     // ---------------- final epilogue from the register accumulators ----------------
@@ -280,7 +305,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemm_fp8_kernel(const __grid_con
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 2) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  if (warp == 2) tmem_dealloc(tmem_base, tmem_cols);
 }
 
 // ---- activation quantiser: per row and 128-wide k-block, scale = amax / 448 ----
@@ -308,10 +333,10 @@ __global__ void __launch_bounds__(128) quant_rows_block128_kernel(const __nv_bfl
   }
 }
 
-template <int TN, int EPI>
+template <int TN, int EPI, bool WIDE>
 cudaError_t launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const Fp8Params& kp, dim3 grid, cudaStream_t stream) {
   using Cfg = Fp8Cfg<TN>;
-  auto kern = moe_gemm_fp8_kernel<TN, EPI>;
+  auto kern = moe_gemm_fp8_kernel<TN, EPI, WIDE>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
@@ -325,11 +350,16 @@ cudaError_t launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const Fp8Pa
 template <int EPI>
 cudaError_t launch_tn(int tn, const CUtensorMap& tw, const CUtensorMap& tx, const Fp8Params& kp, dim3 grid,
                       cudaStream_t stream) {
+  static const bool wide_on = [] {
+    const char* e = std::getenv("NFB_MOE_FP8_WIDE");
+    return e == nullptr || e[0] != '0';
+  }();
+  const bool wide = wide_on && kp.num_kb <= kWideMaxKb && kp.num_kb * tn <= kWideCols;
   switch (tn) {
-    case 16: return launch_one<16, EPI>(tw, tx, kp, grid, stream);
-    case 32: return launch_one<32, EPI>(tw, tx, kp, grid, stream);
-    case 64: return launch_one<64, EPI>(tw, tx, kp, grid, stream);
-    default: return launch_one<128, EPI>(tw, tx, kp, grid, stream);
+    case 16: return wide ? launch_one<16, EPI, true>(tw, tx, kp, grid, stream) : launch_one<16, EPI, false>(tw, tx, kp, grid, stream);
+    case 32: return wide ? launch_one<32, EPI, true>(tw, tx, kp, grid, stream) : launch_one<32, EPI, false>(tw, tx, kp, grid, stream);
+    case 64: return wide ? launch_one<64, EPI, true>(tw, tx, kp, grid, stream) : launch_one<64, EPI, false>(tw, tx, kp, grid, stream);
+    default: return launch_one<128, EPI, false>(tw, tx, kp, grid, stream);
   }
 }
 

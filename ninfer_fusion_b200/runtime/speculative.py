@@ -19,6 +19,7 @@ include/ninfer/ops/speculative_round.h:40-151, include/ninfer/ops/gdn_replay.h:1
 """
 from __future__ import annotations
 
+from dataclasses import replace
 from typing import Callable, Dict, List, Optional, Sequence
 
 import torch
@@ -26,7 +27,7 @@ import torch
 from ..models.config import ModelConfig
 from ..models.hybrid import GdnRecords
 from .batch import SeqChunk, StepBuffers
-from .generator import Generator
+from .generator import Generator, context_bucket
 from .kv_cache import PagedKvCache
 
 
@@ -117,6 +118,12 @@ class SpeculativeGenerator(Generator):
             fl = self.dflash.dc.feature_layers
             self.model.feature_taps = {layer: i for i, layer in enumerate(fl)}
             self.model.feature_buf = torch.empty((max(self.ws.max_tokens, Tv), len(fl) * h), dtype=torch.bfloat16, device=dev)
+        # a chained greedy round as ONE CUDA graph per (batch, context bucket): draft passes, verify, acceptance, state
+        # fold and draft catch-up run back to back with the accepted lengths staying on the device
+        self.seq_end = torch.zeros(max_batch, dtype=torch.int32, device=dev)
+        self.catch_rows = torch.zeros(max_batch, dtype=torch.int32, device=dev)
+        self.draft_col = torch.zeros(max_batch, dtype=torch.int32, device=dev)
+        self._round_graphs: Dict[tuple, tuple] = {}
         self.history: List[List[int]] = []
         self.rounds = 0
         self.accepted = 0
@@ -409,10 +416,130 @@ class SpeculativeGenerator(Generator):
             self.history[b].extend(emitted[b])
         return emitted
 
+    # ------------------------------------------------------------------ chained round as one graph
+    def _graph_round_ok(self) -> bool:
+        """A chained round can be replayed as a graph when nothing in it needs the host: greedy verification and a
+        drafter that either runs on the device (the draft module) or proposes before the round (hook, n-gram)."""
+        if not self.use_graph or self.R > 1 or self.dflash is not None:
+            return False
+        sps = self.sampling if isinstance(self.sampling, (list, tuple)) else [self.sampling]
+        return all(sp is None or sp.greedy for sp in sps)
+
+    def _round_descriptors(self, B: int):
+        K = self.K
+        bd = self.bufs_draft.build([SeqChunk(self.rows[b], self.slots[b], self.lengths[b], [0], True) for b in range(B)])
+        bv = self.bufs_verify.build([SeqChunk(self.rows[b], self.slots[b], self.lengths[b],
+                                              [self.last_tokens[b]] + [0] * K, True, True) for b in range(B)])
+        return bd, bv
+
+    def _round_body(self, B: int, bd, bv) -> None:
+        """The device work of one chained greedy round, free of host reads.  The draft module's catch-up runs over
+        all K + 1 verify rows of every sequence: rows past the accepted prefix compute values nobody reads (their
+        cache positions are rewritten by the next round before any query can see them), and the row that carries the
+        next first draft is picked on the device from the accepted length."""
+        K, ops, model, ws = self.K, self.model.ops, self.model, self.ws
+        T = B * (K + 1)
+        if self.drafter == "mtp":
+            for j in range(1, K):
+                self.h_in[:B].copy_(self.mtp_h[:B])
+                self.draft_col[:B].copy_(self.drafts[:B, j - 1])
+                hid = model.forward_mtp(ws, bd, self.kv_mtp, self.h_in[:B], self.draft_col[:B])
+                lg = model.logits(ws, bd, hid)
+                ids = ws.next_ids[:B]
+                ops.argmax_rows(lg, ids, model.pdl)
+                self.drafts[:B, j] = ids
+                self.mtp_h[:B].copy_(hid)
+                bd.cache_pos.add_(1)
+                bd.kv_len.add_(1)
+                bd.rope_pos.add_(1)
+        bv.ids.view(B, K + 1)[:, 1:] = self.drafts[:B]
+        hidden = model.forward_hidden(ws, bv, self.kv, self.states, write_state=False, rec=self.rec)
+        self.h_keep[:T].copy_(hidden)
+        lg = model.logits(ws, bv, hidden)
+        target = ws.next_ids[:T]
+        ops.argmax_rows(lg, target, model.pdl)
+        ops.accept_greedy_chain(target.view(B, K + 1), self.drafts[:B], self.n_acc[:B], self.out_tok[:B])
+        torch.add(bv.cu_seqlens[:B], self.n_acc[:B], out=self.catch_rows[:B])
+        torch.add(self.catch_rows[:B], 1, out=self.seq_end[:B])
+        model.fold_gdn(ws, bv, self.states, self.rec, self.seq_end[:B])
+        if self.drafter == "mtp":
+            cb = replace(bv, logit_rows=self.catch_rows[:B])
+            torch.clamp(self.out_tok[:B].view(-1), min=0, out=self.next_dev[:T])
+            self.h_in[:T].copy_(self.h_keep[:T])
+            hid = model.forward_mtp(ws, cb, self.kv_mtp, self.h_in[:T], self.next_dev[:T])
+            torch.index_select(hid, 0, self.catch_rows[:B].long(), out=self.mtp_h[:B])
+            lg = model.logits(ws, cb, hid)
+            ids = ws.next_ids[:B]
+            ops.argmax_rows(lg, ids, model.pdl)
+            self.drafts[:B, 0] = ids
+
+    def _round_graph(self, B: int, bucket: int):
+        key = (B, bucket)
+        if key in self._round_graphs:
+            return self._round_graphs[key]
+        bd, bv = self._round_descriptors(B)
+        bd.max_kv_len = bv.max_kv_len = bucket   # bake the bucket's split geometry, not this round's
+        keep = (self.mtp_h.clone(), self.drafts.clone())
+
+        def restore():
+            self._rollback_states()
+            self.mtp_h.copy_(keep[0])
+            self.drafts.copy_(keep[1])
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            for _ in range(2):   # warm-up outside capture; a round moves the recurrent state and the draft inputs
+                self._snapshot_states()
+                self.bufs_draft.dev.copy_(self.bufs_draft.host, non_blocking=True)
+                self._round_body(B, bd, bv)
+                restore()
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize(self.device)
+        self.bufs_draft.dev.copy_(self.bufs_draft.host, non_blocking=True)
+        graph = torch.cuda.CUDAGraph()
+        self._snapshot_states()
+        with torch.cuda.graph(graph):
+            self._round_body(B, bd, bv)
+        restore()
+        self._round_graphs[key] = (graph, bd, bv)
+        return self._round_graphs[key]
+
+    def _decode_round_graph(self) -> List[List[int]]:
+        B, K = len(self.rows), self.K
+        for b, r in enumerate(self.rows):
+            self.kv.ensure(r, self.lengths[b] + K + 2)
+            if self.kv_mtp is not None:
+                self.kv_mtp.ensure(r, self.lengths[b] + K + 2)
+        self.kv.publish()
+        if self.kv_mtp is not None:
+            self.kv_mtp.publish()
+        if self.drafter != "mtp":
+            self._draft(B)   # host proposals: one upload before the graph
+        graph, _, _ = self._round_graph(B, context_bucket(max(self.lengths) + K + 2))
+        self._round_descriptors(B)
+        graph.replay()
+        self.acc_host[:B].copy_(self.n_acc[:B], non_blocking=True)
+        self.tok_host[:B].copy_(self.out_tok[:B], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        emitted: List[List[int]] = []
+        for b in range(B):
+            m = int(self.acc_host[b])
+            toks = [int(v) for v in self.tok_host[b, : m + 1]]
+            emitted.append(toks)
+            self.accepted += m
+            self.emitted += m + 1
+            self.lengths[b] += m + 1
+            self.last_tokens[b] = toks[-1]
+            self.history[b].extend(toks)
+        self.rounds += 1
+        return emitted
+
     def decode_round(self) -> List[List[int]]:
         """One draft-verify round; returns the tokens emitted for every sequence (1..K+1 each)."""
         if self.R > 1:
             return self.decode_round_tree()
+        if self._graph_round_ok():
+            return self._decode_round_graph()
         B, K = len(self.rows), self.K
         ops = self.model.ops
         for b, r in enumerate(self.rows):

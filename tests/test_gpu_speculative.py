@@ -202,3 +202,44 @@ def test_stochastic_mtp_drafts_run_reproducibly_and_keep_the_greedy_stream():
     # proposal is rejected and the residual is p), and the text must be the greedy text exactly
     one, _ = run(5, True, [SamplingParams(temperature=0.9, top_k=1, seed=5), SamplingParams()])
     assert one == plain
+
+
+@pytest.mark.parametrize("drafter", ["hook", "mtp", "ngram"])
+@pytest.mark.parametrize("pdl", [False, True], ids=["plain-launch", "dependent-launch"])
+def test_chained_round_as_one_graph_keeps_the_greedy_stream(drafter, pdl):
+    """A whole chained round (draft passes, verify, acceptance, state fold, draft catch-up over a fixed K + 1 rows)
+    replayed as one CUDA graph: the stream is the target's greedy stream, acceptance matches the drafts' quality, and
+    the eager round of the same generator class emits the same tokens where the oracle is decisive."""
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cuda", seed=9, std=0.05, with_mtp=True)
+    torch.manual_seed(4)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (33, 90, 7)]
+    if drafter == "ngram":
+        prompts = [[3, 9, 27, 81] * 8, [5, 6] * 11, [8, 1, 2] * 5]
+    K, n_new = 3, 30
+    kw = dict(max_batch=4, max_context=512, draft_tokens=K, drafter=drafter, kv_format="bf16", page_size=16,
+              prefill_chunk=64, pdl=pdl)
+    plain = Generator(cfg, w, "cuda", max_batch=4, max_context=512, kv_format="bf16", page_size=16, prefill_chunk=64,
+                      use_graph=False).generate(prompts, n_new + 8)
+    plen = [len(p) for p in prompts]
+
+    def hook(b, history, k):
+        done = len(history) - plen[b]
+        truth = (plain[b][done:done + k] + [0] * k)[:k]
+        cut = (done + b) % (k + 1)
+        return [t if i < cut else (t + 1) % cfg.vocab for i, t in enumerate(truth)]
+
+    outs = {}
+    for graph in (True, False):
+        gen = SpeculativeGenerator(cfg, w, "cuda", use_graph=graph, **kw)
+        gen.draft_hook = hook
+        assert gen._graph_round_ok() == graph
+        outs[graph] = gen.generate(prompts, n_new)
+        agree, total = _teacher_forced_agreement(cfg, w, prompts, outs[graph])
+        assert total > 30 and agree / total >= 0.95, f"graph={graph}: {agree}/{total}"
+        if graph:
+            assert len(gen._round_graphs) >= 1 and gen.rounds > 0
+            if drafter == "hook":
+                assert 1.0 < gen.tokens_per_round < K + 1
+    same = sum(int(a == b) for x, y in zip(outs[True], outs[False]) for a, b in zip(x, y))
+    assert same >= 0.9 * n_new * len(prompts), same
