@@ -163,10 +163,13 @@ class MoeBlock:
                      self.off["recv_x"], self.off["recv_meta"], self.off["arrive_flag"], self.state, status)
         if self.expert_format == "fp8_block":
             gu_q, gu_s, dn_q, dn_s = self._experts(model.w, prefix)
-            ops.moe_quant_rows_block128(self.recv_x, self.recv_q, self.recv_qs, self.state)
+            # one CTA per row that this step can deliver here (not per row of the worst-case receive capacity, which
+            # is world x max_tokens x top-k rows: 131072 CTAs that exit at once cost more than the GEMM they feed)
+            rb = rows_bound
+            ops.moe_quant_rows_block128(self.recv_x[:rb], self.recv_q[:rb], self.recv_qs[:rb], self.state)
             ops.moe_gemm_fp8(self.recv_q, self.recv_qs, gu_q, gu_s, MOE_EPI_SWIGLU, tn, max_tiles, self.tiles, self.state,
                              self.act, W, None, self.peer_bases, 0, 0, status)
-            ops.moe_quant_rows_block128(self.act, self.act_q, self.act_qs, self.state)
+            ops.moe_quant_rows_block128(self.act[:rb], self.act_q[:rb], self.act_qs[:rb], self.state)
             ops.moe_gemm_fp8(self.act_q, self.act_qs, dn_q, dn_s, MOE_EPI_RETURN, tn, max_tiles, self.tiles, self.state,
                              None, W, self.recv_meta, self.peer_bases, self.off["ret"], self.off["ret_flag"], status)
         else:
