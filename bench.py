@@ -193,7 +193,9 @@ def speculative_run(args, cfg, device) -> int:
     spec = SpeculativeGenerator(cfg, weights, device, max_batch=B, max_context=max_ctx, draft_tokens=Kd,
                                 drafter=args.spec if args.spec in ("mtp", "dflash") else "hook", tree_ranks=R_,
                                 kv_format=args.kv_format,
-                                page_size=64, prefill_chunk=2048, pdl=bool(args.pdl), use_graph=not args.spec_eager)
+                                page_size=64, prefill_chunk=2048, pdl=bool(args.pdl), use_graph=not args.spec_eager,
+                                adaptive_width=bool(args.adaptive_width),
+                                draft_head_ids=list(range(args.draft_head)) if args.draft_head else None)
     if args.spec == "hook":
         # Synthetic drafts of mixed quality need the stream the VERIFY pass itself emits: with random-init weights many
         # logits are near ties, and a (K + 1)-row verify pass does not round like a one-row decode pass, so drafts copied
@@ -247,6 +249,9 @@ def speculative_run(args, cfg, device) -> int:
                    "kv": args.kv_format, "drafter": args.spec, "draft_tokens": Kd, "tree_ranks": R_,
                    "rounds": ("eager (no CUDA graph)" if not spec._graph_round_ok() else "one CUDA graph per round")
                    + ", one host round trip per round (accepted lengths and tokens)"},
+        "draft_head_rows": args.draft_head or cfg.vocab,
+        "adaptive_width": None if spec.width_ctl is None else {"width_now": spec.K, "decisions": spec.width_ctl.trace[-6:],
+                                                                "cost_line_ms": spec.width_ctl.cost.fit()},
         "tokens_per_round": round(emitted / max(1, (spec.rounds - r0) * B), 3),
         "acceptance": round((emitted / max(1, (spec.rounds - r0) * B) - 1.0) / Kd, 4),
         "plain": {"tokens_per_s": round(plain_tok_s, 2), "ms_per_step": round(plain_ms / steps_plain, 4),
@@ -282,6 +287,10 @@ def main() -> int:
                          "every rank receives every tile + one sum kernel, nccl = NCCL all-reduce baseline, auto = the "
                          "faster of fused / oneshot at this GPU count as measured (TensorParallel.best_mode)")
     ap.add_argument("--spec-eager", action="store_true", help="speculative rounds without CUDA graphs")
+    ap.add_argument("--adaptive-width", action="store_true",
+                    help="--spec: the draft width follows acceptance and measured round cost (ladder up to --draft-tokens)")
+    ap.add_argument("--draft-head", type=int, default=0,
+                    help="--spec mtp: propose from a shortlist head of this many LM-head rows (0 = the full head)")
     ap.add_argument("--spec", default="none", choices=["none", "mtp", "dflash", "hook"],
                     help="speculative decoding run (one GPU): mtp = the draft module proposes, dflash = the "
                          "block-diffusion draft model proposes the whole block in one pass (random-init "

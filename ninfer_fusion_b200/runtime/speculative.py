@@ -19,6 +19,7 @@ include/ninfer/ops/speculative_round.h:40-151, include/ninfer/ops/gdn_replay.h:1
 """
 from __future__ import annotations
 
+import time
 from dataclasses import replace
 from typing import Callable, Dict, List, Optional, Sequence
 
@@ -50,7 +51,7 @@ class SpeculativeGenerator(Generator):
 
     def __init__(self, cfg: ModelConfig, weights: Dict[str, torch.Tensor], device, max_batch: int, max_context: int,
                  draft_tokens: int = 3, drafter: str = "mtp", sampling=None, tree_ranks: int = 1,
-                 stochastic_drafts: bool = False, **kw):
+                 stochastic_drafts: bool = False, adaptive_width=False, draft_head_ids=None, **kw):
         K = draft_tokens
         if K < 1:
             raise ValueError("draft_tokens must be >= 1")
@@ -95,6 +96,34 @@ class SpeculativeGenerator(Generator):
         DK = 32   # pairs per exported distribution: the sampler keeps at most its top-k cap (32) candidates
         self.q_ids = torch.full((max_batch, K + 1, DK), -1, dtype=torch.int32, device=dev)
         self.q_probs = torch.zeros((max_batch, K + 1, DK), dtype=torch.float32, device=dev)
+        # Adaptive draft width (chained rounds only): one set of [batch, k] buffers and one round graph per ladder
+        # width; the first draft of the next round is carried across a change of width.
+        self.width_ctl = None
+        self._width_bufs = {K: (self.drafts, self.out_tok, self.tok_host, self.draft_host)}
+        if adaptive_width:
+            if self.R > 1 or self.stochastic_drafts or drafter == "dflash":
+                raise ValueError("adaptive width drives chained rounds of the MTP, hook and n-gram drafters")
+            from .spec_width import AdaptiveWidth
+            self.width_ctl = adaptive_width if isinstance(adaptive_width, AdaptiveWidth) else AdaptiveWidth(max_width=K)
+            if self.width_ctl.max_width != K:
+                raise ValueError("the width controller's maximum must equal draft_tokens")
+        # Shortlist draft head: the draft module's proposals are the arg-max over a subset of the vocabulary (rows of
+        # the LM head gathered once), mapped back to token ids.  A draft only has to be right often, not always: the
+        # target verifies with the full head, and a draft pass no longer streams the whole LM head.
+        self.head_ids = self.head_w = self.head_logits = None
+        if draft_head_ids is not None:
+            if drafter != "mtp" or self.R > 1 or self.stochastic_drafts:
+                raise ValueError("the shortlist head serves chained arg-max drafts of the draft module (no tree ranks, "
+                                 "no sampled drafts: both need the full distribution)")
+            head = weights[f"{self.model.prefix}/lm_head"]
+            if not isinstance(head, torch.Tensor) or head.dtype != torch.bfloat16:
+                raise ValueError("the shortlist head is gathered from a bf16 LM head")
+            ids = torch.as_tensor(draft_head_ids, dtype=torch.int64).flatten().unique(sorted=True)
+            if ids.numel() < 8 or ids.numel() % 8 or int(ids[0]) < 0 or int(ids[-1]) >= head.shape[0]:
+                raise ValueError("draft_head_ids: a multiple of 8 distinct token ids inside the vocabulary")
+            self.head_ids = ids.to(device=dev, dtype=torch.int32)
+            self.head_w = head.index_select(0, ids.to(dev)).contiguous()
+            self.head_logits = torch.empty((max(self.ws.max_tokens, Tv), ids.numel()), dtype=torch.bfloat16, device=dev)
         self.kv_mtp = None
         if drafter == "mtp":
             if "mtp/fc" not in weights:
@@ -173,18 +202,58 @@ class SpeculativeGenerator(Generator):
         self.q_ids[idx, col] = q_i
         self.q_probs[idx, col] = q_p
 
+    def _propose(self, batch, hid: torch.Tensor) -> torch.Tensor:
+        """Arg-max proposals of the draft module for the logit rows of `batch` (ws.next_ids[:R]): over the whole
+        vocabulary, or over the shortlist head with its ids mapped back (ascending ids, so ties resolve to the
+        lowest token id as in the full head)."""
+        model, ops = self.model, self.model.ops
+        if self.head_w is None:
+            lg = model.logits(self.ws, batch, hid)
+            ids = self.ws.next_ids[: lg.shape[0]]
+            ops.argmax_rows(lg, ids, model.pdl)
+            return ids
+        R = batch.logit_rows.numel()
+        head_in = hid
+        if R != hid.shape[0]:
+            head_in = self.ws.head_in[:R]
+            torch.index_select(hid, 0, batch.logit_rows.long(), out=head_in)
+        lg = self.head_logits[:R]
+        model._gemm(head_in, self.head_w, lg)
+        ids = self.ws.next_ids[:R]
+        ops.argmax_rows(lg, ids, model.pdl)
+        ids.copy_(self.head_ids[ids.long()])
+        return ids
+
+    def _set_width(self, k: int) -> None:
+        """Switches the chained round to k drafts per sequence."""
+        if k == self.K:
+            return
+        if k not in self._width_bufs:
+            dev, B = self.device, self.max_batch
+            pin = dev.type == "cuda"
+            self._width_bufs[k] = (torch.zeros((B, k), dtype=torch.int32, device=dev),
+                                   torch.zeros((B, k + 1), dtype=torch.int32, device=dev),
+                                   torch.zeros((B, k + 1), dtype=torch.int32, pin_memory=pin),
+                                   torch.zeros((B, k), dtype=torch.int32, pin_memory=pin))
+        drafts, out_tok, tok_host, draft_host = self._width_bufs[k]
+        drafts[:, 0].copy_(self.drafts[:, 0])   # the draft module already proposed the next round's first token
+        self.K, self.drafts, self.out_tok, self.tok_host, self.draft_host = k, drafts, out_tok, tok_host, draft_host
+
     def _mtp_pass(self, batch, hidden_in: torch.Tensor, next_ids: torch.Tensor, seqs: Sequence[int]) -> None:
         """Draft module over `batch`; for the sequences `seqs` (whose last token is a logit row, in order) store
         the first draft token and the module's hidden state."""
         hid = self.model.forward_mtp(self.ws, batch, self.kv_mtp, hidden_in, next_ids)
         if not seqs:
             return
-        lg = self.model.logits(self.ws, batch, hid)
-        ids = self.ws.next_ids[: lg.shape[0]]
-        if self._draft_stochastically() and len(self.lengths) > max(seqs):
-            self._sample_draft(lg, ids, list(seqs), 0)
+        if self.head_w is not None:
+            ids = self._propose(batch, hid)
         else:
-            self.model.ops.argmax_rows(lg, ids, self.model.pdl)
+            lg = self.model.logits(self.ws, batch, hid)
+            ids = self.ws.next_ids[: lg.shape[0]]
+            if self._draft_stochastically() and len(self.lengths) > max(seqs):
+                self._sample_draft(lg, ids, list(seqs), 0)
+            else:
+                self.model.ops.argmax_rows(lg, ids, self.model.pdl)
         idx = torch.tensor(list(seqs), dtype=torch.long, device=self.device)
         self.drafts[idx, 0] = ids
         if self.R > 1:
@@ -279,12 +348,15 @@ class SpeculativeGenerator(Generator):
                 batch = self.bufs_draft.build(chunks)
                 self.h_in[:B].copy_(self.mtp_h[:B])
                 hid = self.model.forward_mtp(self.ws, batch, self.kv_mtp, self.h_in[:B], self.drafts[:B, j - 1].contiguous())
-                lg = self.model.logits(self.ws, batch, hid)
-                ids = self.ws.next_ids[:B]
-                if self._draft_stochastically():
-                    self._sample_draft(lg, ids, list(range(B)), j)
+                if self.head_w is not None:
+                    ids = self._propose(batch, hid)
                 else:
-                    self.model.ops.argmax_rows(lg, ids, self.model.pdl)
+                    lg = self.model.logits(self.ws, batch, hid)
+                    ids = self.ws.next_ids[:B]
+                    if self._draft_stochastically():
+                        self._sample_draft(lg, ids, list(range(B)), j)
+                    else:
+                        self.model.ops.argmax_rows(lg, ids, self.model.pdl)
                 self.drafts[:B, j] = ids
                 if self.R > 1:
                     self.drafts_r[:B, j] = torch.topk(lg.float(), self.R, dim=-1).indices.to(torch.int32)
@@ -444,10 +516,7 @@ class SpeculativeGenerator(Generator):
                 self.h_in[:B].copy_(self.mtp_h[:B])
                 self.draft_col[:B].copy_(self.drafts[:B, j - 1])
                 hid = model.forward_mtp(ws, bd, self.kv_mtp, self.h_in[:B], self.draft_col[:B])
-                lg = model.logits(ws, bd, hid)
-                ids = ws.next_ids[:B]
-                ops.argmax_rows(lg, ids, model.pdl)
-                self.drafts[:B, j] = ids
+                self.drafts[:B, j] = self._propose(bd, hid)
                 self.mtp_h[:B].copy_(hid)
                 bd.cache_pos.add_(1)
                 bd.kv_len.add_(1)
@@ -468,13 +537,10 @@ class SpeculativeGenerator(Generator):
             self.h_in[:T].copy_(self.h_keep[:T])
             hid = model.forward_mtp(ws, cb, self.kv_mtp, self.h_in[:T], self.next_dev[:T])
             torch.index_select(hid, 0, self.catch_rows[:B].long(), out=self.mtp_h[:B])
-            lg = model.logits(ws, cb, hid)
-            ids = ws.next_ids[:B]
-            ops.argmax_rows(lg, ids, model.pdl)
-            self.drafts[:B, 0] = ids
+            self.drafts[:B, 0] = self._propose(cb, hid)
 
     def _round_graph(self, B: int, bucket: int):
-        key = (B, bucket)
+        key = (B, bucket, self.K)
         if key in self._round_graphs:
             return self._round_graphs[key]
         bd, bv = self._round_descriptors(B)
@@ -502,6 +568,7 @@ class SpeculativeGenerator(Generator):
             self._round_body(B, bd, bv)
         restore()
         self._round_graphs[key] = (graph, bd, bv)
+        self._fresh_graph = True
         return self._round_graphs[key]
 
     def _decode_round_graph(self) -> List[List[int]]:
@@ -538,8 +605,20 @@ class SpeculativeGenerator(Generator):
         """One draft-verify round; returns the tokens emitted for every sequence (1..K+1 each)."""
         if self.R > 1:
             return self.decode_round_tree()
-        if self._graph_round_ok():
-            return self._decode_round_graph()
+        ctl = self.width_ctl
+        if ctl is None:
+            return self._decode_round_graph() if self._graph_round_ok() else self._decode_round_eager()
+        self._set_width(ctl.width)
+        self._fresh_graph = False
+        t0 = time.perf_counter()
+        emitted = self._decode_round_graph() if self._graph_round_ok() else self._decode_round_eager()
+        # the round ends with a stream synchronisation, so the host clock brackets the whole round; a round that
+        # captured its graph first says nothing about the cost of its width
+        ms = None if self._fresh_graph else (time.perf_counter() - t0) * 1e3
+        ctl.observe_round([len(e) - 1 for e in emitted], self.K, ms)
+        return emitted
+
+    def _decode_round_eager(self) -> List[List[int]]:
         B, K = len(self.rows), self.K
         ops = self.model.ops
         for b, r in enumerate(self.rows):

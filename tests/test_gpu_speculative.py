@@ -243,3 +243,61 @@ def test_chained_round_as_one_graph_keeps_the_greedy_stream(drafter, pdl):
                 assert 1.0 < gen.tokens_per_round < K + 1
     same = sum(int(a == b) for x, y in zip(outs[True], outs[False]) for a, b in zip(x, y))
     assert same >= 0.9 * n_new * len(prompts), same
+
+
+@pytest.mark.parametrize("use_graph", [False, True], ids=["eager", "graph"])
+def test_shortlist_draft_head_proposes_from_a_subset_and_keeps_the_greedy_stream(use_graph):
+    """A shortlist that holds the whole vocabulary proposes exactly what the full head proposes; half the vocabulary
+    proposes worse drafts, never wrong output (the target verifies with the full head)."""
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cuda", seed=9, std=0.05, with_mtp=True)
+    torch.manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (33, 90)]
+    kw = dict(max_batch=2, max_context=512, draft_tokens=3, drafter="mtp", kv_format="bf16", page_size=16,
+              prefill_chunk=64, use_graph=use_graph)
+    base = SpeculativeGenerator(cfg, w, "cuda", **kw)
+    out0 = base.generate(prompts, 20)
+    full = SpeculativeGenerator(cfg, w, "cuda", draft_head_ids=range(cfg.vocab), **kw)
+    out1 = full.generate(prompts, 20)
+    assert out1 == out0 and full.accepted == base.accepted
+    half = SpeculativeGenerator(cfg, w, "cuda", draft_head_ids=range(0, cfg.vocab, 2), **kw)
+    out2 = half.generate(prompts, 20)
+    agree, total = _teacher_forced_agreement(cfg, w, prompts, out2)
+    assert total > 12 and agree / total >= 0.9, f"{agree}/{total}"
+    assert all(int(t) % 2 == 0 for t in half.drafts.flatten().tolist())     # proposals come from the shortlist only
+    with pytest.raises(ValueError):
+        SpeculativeGenerator(cfg, w, "cuda", draft_head_ids=range(64), tree_ranks=2, **kw)
+
+
+@pytest.mark.parametrize("quality,expect", [("perfect", "top"), ("garbage", "bottom")])
+def test_adaptive_width_follows_acceptance_and_keeps_the_greedy_stream(quality, expect):
+    from ninfer_fusion_b200.runtime.spec_width import AdaptiveWidth
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cuda", seed=7, std=0.05)
+    torch.manual_seed(1)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (21, 70, 5)]
+    n_new, K = 120, 6
+    # the stream the verify pass itself emits (drafts all wrong: one token per round)
+    rec = SpeculativeGenerator(cfg, w, "cuda", max_batch=4, max_context=512, draft_tokens=K, drafter="hook",
+                               kv_format="bf16", page_size=16, prefill_chunk=64, use_graph=True)
+    rec.draft_hook = lambda b, history, k: [(history[-1] + 1 + i) % cfg.vocab for i in range(k)]
+    truth = rec.generate(prompts, n_new + 2 * K)
+    plen = [len(p) for p in prompts]
+    ctl = AdaptiveWidth(max_width=K, cadence=4, base_ms=2.0, per_column_ms=0.2, calibrate=False)
+    gen = SpeculativeGenerator(cfg, w, "cuda", max_batch=4, max_context=512, draft_tokens=K, drafter="hook",
+                               kv_format="bf16", page_size=16, prefill_chunk=64, use_graph=True, adaptive_width=ctl)
+
+    def hook(b, history, k):
+        done = len(history) - plen[b]
+        t = (truth[b][done:done + k] + [0] * k)[:k]
+        return t if quality == "perfect" else [(x + 1) % cfg.vocab for x in t]
+    gen.draft_hook = hook
+    out = gen.generate(prompts, n_new)
+    agree, total = _teacher_forced_agreement(cfg, w, prompts, out)
+    assert total > 100 and agree / total >= 0.95, f"{agree}/{total}"
+    widths = [k for _, k, _ in ctl.trace]
+    assert len(widths) >= 2
+    # (a verify pass of another width may round a near-tie the other way; from there on the recorded stream is no
+    # longer this generator's future, so "perfect" only has to reach the top rung, not stay there)
+    assert (max(widths) == ctl.ladder[-1]) if expect == "top" else (gen.K == ctl.ladder[0]), (gen.K, ctl.trace)
+    assert len({key[2] for key in gen._round_graphs}) >= 2          # one captured round per width that was used
