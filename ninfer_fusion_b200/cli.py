@@ -64,6 +64,12 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--spec-stochastic", action="store_true",
                     help="with --spec mtp and sampled requests: the draft module samples its proposals and the verifier "
                          "accepts with min(1, p / q) (general speculative sampling) instead of arg-max proposals")
+    ap.add_argument("--spec-adaptive-width", action="store_true",
+                    help="with --spec mtp: the number of drafts per round follows measured acceptance and round cost "
+                         "(a ladder of widths up to --draft-tokens, one captured round per width)")
+    ap.add_argument("--draft-head", default="",
+                    help="with --spec mtp: shortlist draft head, either a count N (token ids 0..N-1) or a file of token "
+                         "ids (one per line, or a .npy / .pt tensor); the target still verifies with the full head")
     ap.add_argument("--allow-unknown-template", action="store_true")
     ap.add_argument("--weight-budget-gib", type=float, default=0.0,
                     help="device bytes for weights; layers beyond it rotate in from pinned host memory (eager decode)")
@@ -260,10 +266,36 @@ def build_engine(args, cfg: ModelConfig, weights, ranks=None) -> Optional[Engine
         def factory():
             return SpeculativeProgram(cfg, weights, args.device, max_lanes=args.max_lanes, max_context=args.max_context,
                                       draft_tokens=args.draft_tokens, kv_format=kv, page_size=args.page_size,
-                                      prefill_chunk=args.prefill_chunk,
-                                      stochastic_drafts=getattr(args, "spec_stochastic", False))
+                                      prefill_chunk=args.prefill_chunk, use_graph=not getattr(args, "no_graphs", False),
+                                      stochastic_drafts=getattr(args, "spec_stochastic", False),
+                                      adaptive_width=getattr(args, "spec_adaptive_width", False),
+                                      draft_head_ids=_draft_head_ids(getattr(args, "draft_head", ""), cfg))
         return Engine(factory, prefill_chunk=args.prefill_chunk)
     return Engine(program_factory(args, cfg, weights, kv), prefill_chunk=args.prefill_chunk)
+
+
+def _draft_head_ids(spec: str, cfg: ModelConfig):
+    """Token ids of the shortlist draft head named by --draft-head (None: the full head)."""
+    if not spec:
+        return None
+    if spec.isdigit():
+        n = int(spec)
+        if not 8 <= n <= cfg.vocab:
+            raise SystemExit(f"--draft-head: a count between 8 and the vocabulary size ({cfg.vocab})")
+        return list(range(n - n % 8))
+    import os
+    if not os.path.exists(spec):
+        raise SystemExit(f"--draft-head: {spec} is neither a count nor a file")
+    if spec.endswith(".npy"):
+        import numpy as np
+        ids = [int(v) for v in np.load(spec).reshape(-1)]
+    elif spec.endswith(".pt"):
+        ids = [int(v) for v in torch.load(spec).reshape(-1)]
+    else:
+        with open(spec) as f:
+            ids = [int(line) for line in f.read().split()]
+    ids = sorted(set(ids))
+    return ids[: len(ids) - len(ids) % 8]
 
 
 def program_factory(args, cfg: ModelConfig, weights, kv, shard=None, comm=None):

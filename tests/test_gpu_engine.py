@@ -118,14 +118,18 @@ def test_host_cold_tier_round_trip_on_gpu(setup):
         pass
 
 
-def test_engine_with_speculative_program():
+@pytest.mark.parametrize("extra", [{}, {"use_graph": True},
+                                   {"use_graph": True, "adaptive_width": True, "draft_head_ids": range(0, 1024)}],
+                         ids=["eager", "graph-rounds", "graph-adaptive-shortlist"])
+def test_engine_with_speculative_program(extra):
     """MTP speculation behind the ordinary Engine API: several tokens committed per lane and round, lanes joining and
-    leaving between rounds, greedy and sampled lanes side by side."""
+    leaving between rounds, greedy and sampled lanes side by side.  With graphs, a round whose lanes are all greedy
+    replays the captured round of its (lane count, context bucket, width); a round with a sampled lane runs eager."""
     from ninfer_fusion_b200.runtime.speculative import SpeculativeProgram
     cfg = TINY_DENSE
     w = random_weights(cfg, "cuda", seed=9, std=0.05, with_mtp=True)
     eng = Engine(lambda: SpeculativeProgram(cfg, w, "cuda", max_lanes=3, max_context=512, draft_tokens=3,
-                                            kv_format="bf16", page_size=16, prefill_chunk=64), prefill_chunk=64)
+                                            kv_format="bf16", page_size=16, prefill_chunk=64, **extra), prefill_chunk=64)
     try:
         torch.manual_seed(6)
         prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (12, 80, 33, 7)]   # one more request than lanes
@@ -148,6 +152,8 @@ def test_engine_with_speculative_program():
                 hid = ref.forward(seq, torch.tensor([tok]))
         assert total > 20 and agree / total >= 0.9, f"{agree}/{total}"
         assert eng.program.gen.rounds > 0 and eng.health()["status"] == "ok"
+        if extra.get("use_graph"):
+            assert len(eng.program.gen._round_graphs) >= 1
     finally:
         eng.shutdown()
 
