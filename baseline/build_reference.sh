@@ -18,7 +18,7 @@
 #  * Each bench has its own main() and would link the whole Op library (~740 MB each): the `main` symbol of every
 #    compiled bench OBJECT is renamed (objcopy) and all of them are linked once behind ref_bench_mux.cpp.
 set -euo pipefail
-REF=${1:-/root/reference}
+REF=${1:-${NINFER_REFERENCE_TREE:?give the reference source tree as the first argument or in NINFER_REFERENCE_TREE}}
 BUILD=${2:-/tmp/ninfer_ref_build}
 HERE=$(cd "$(dirname "$0")" && pwd)
 OUT="$HERE/_ref"
