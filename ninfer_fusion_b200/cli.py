@@ -57,6 +57,10 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--max-context", type=int, default=4096)
     ap.add_argument("--max-lanes", type=int, default=8, help="concurrent sequences")
     ap.add_argument("--prefill-chunk", type=int, default=2048)
+    ap.add_argument("--prefill-chunk-mode", default=None, choices=["dynamic", "manual"],
+                    help="dynamic: the bandwidth governor shrinks / restores the prefill unit and its share against "
+                         "decode latency (default; NINFER_FT_BW_GOV=0 in the environment selects manual); manual: the "
+                         "unit stays --prefill-chunk.  NINFER_FT_BW_TRACE=1 prints every change")
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--no-graphs", action="store_true", help="eager decode instead of CUDA graphs")
     ap.add_argument("--spec", default="none", choices=["none", "mtp"], help="speculative decoding with the MTP draft module")
@@ -252,7 +256,8 @@ def build_engine(args, cfg: ModelConfig, weights, ranks=None) -> Optional[Engine
         if rank != 0:
             follower_loop(inner_factory(), channel)
             return None
-        return Engine(lambda: LeaderProgram(inner_factory(), channel), prefill_chunk=args.prefill_chunk)
+        return Engine(lambda: LeaderProgram(inner_factory(), channel), prefill_chunk=args.prefill_chunk,
+                      prefill_chunk_mode=getattr(args, "prefill_chunk_mode", None))
     if args.kv_layer_spec:
         from .kv.policy import parse_layer_storage
         kv = parse_layer_storage(args.kv_layer_spec, len(cfg.attn_layers))
@@ -270,8 +275,10 @@ def build_engine(args, cfg: ModelConfig, weights, ranks=None) -> Optional[Engine
                                       stochastic_drafts=getattr(args, "spec_stochastic", False),
                                       adaptive_width=getattr(args, "spec_adaptive_width", False),
                                       draft_head_ids=_draft_head_ids(getattr(args, "draft_head", ""), cfg))
-        return Engine(factory, prefill_chunk=args.prefill_chunk)
-    return Engine(program_factory(args, cfg, weights, kv), prefill_chunk=args.prefill_chunk)
+        return Engine(factory, prefill_chunk=args.prefill_chunk,
+                      prefill_chunk_mode=getattr(args, "prefill_chunk_mode", None))
+    return Engine(program_factory(args, cfg, weights, kv), prefill_chunk=args.prefill_chunk,
+                      prefill_chunk_mode=getattr(args, "prefill_chunk_mode", None))
 
 
 def _draft_head_ids(spec: str, cfg: ModelConfig):

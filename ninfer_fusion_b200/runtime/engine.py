@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import os
 import queue
+import sys
 import threading
 import time
 from dataclasses import dataclass, field
@@ -23,6 +24,7 @@ from typing import Callable, Dict, List, Optional, Sequence
 
 from ..utils import trace
 from .program import Lane, ProgramBase, SamplingParams
+from .scheduler import ExecutionAction, Scheduler, ServiceAccount, projected_service_work
 
 
 class RequestError(Exception):
@@ -131,23 +133,68 @@ class _Request:
     lane: Optional[Lane] = None
     state: str = "pending"     # pending | prefill | decode | finished
     n_generated: int = 0
+    service: Optional[ServiceAccount] = None   # remaining work in quanta (prefill units + tokens to generate)
+    borrower: bool = False                     # admitted past a blocked FIFO head
+
+
+def resolve_prefill_chunk_mode(cli_value: Optional[str] = None) -> str:
+    """'dynamic' (the governor owns the prefill unit) or 'manual' (the unit stays what the caller asked for).
+    Command line > environment (`NINFER_FT_BW_GOV`: 0 = manual, 1 = dynamic) > default (dynamic).  An unreadable value
+    is refused by name rather than read as the default."""
+    if cli_value:
+        if cli_value not in ("dynamic", "manual"):
+            raise ValueError(f"prefill chunk mode must be 'dynamic' or 'manual', got '{cli_value}'")
+        return cli_value
+    env = os.environ.get("NINFER_FT_BW_GOV")
+    if env is None or env == "":
+        return "dynamic"
+    if env not in ("0", "1"):
+        raise ValueError(f"NINFER_FT_BW_GOV must be 0 or 1, got '{env}'")
+    return "dynamic" if env == "1" else "manual"
 
 
 class BandwidthGovernor:
-    """Shrinks the prefill chunk when decode rounds slow down, restores it when they recover.
+    """Paces prefill against decode: shrinks the prefill unit when decode rounds slow down, then thins the share of
+    prefill units, and restores both when the rounds recover.
 
-    Decode latency is compared with its own running floor (fastest recent rounds); when a round that
-    shared the loop with a prefill step exceeds floor * tolerance the prefill unit halves (not below
-    `min_unit`), and it doubles back after `recover_rounds` clean rounds."""
+    Signal: the duration of a decode round against its own running floor (fastest recent rounds).  When a round that
+    shared the loop with a prefill unit exceeds floor * tolerance the prefill unit halves (not below `min_unit`); once
+    the unit is at its minimum the prefill SHARE halves instead (not below `min_share`): credit accrues `share` per
+    completed decode round and a prefill unit costs one, so share 0.5 admits one prefill unit per two rounds and
+    share 1 is the plain 1:1 alternation.  After `recover_rounds` clean rounds the share doubles back first, then the
+    unit.  With no decode work the scheduler runs prefill whatever the credit (starvation is its business, not ours).
+    `NINFER_FT_BW_TRACE=1` prints every change.  Reference: src/runtime/engine/bandwidth_governor.h."""
 
     def __init__(self, max_unit: int, min_unit: int = 128, tolerance: float = 1.5, recover_rounds: int = 8,
-                 enabled: bool = True):
+                 enabled: bool = True, min_share: float = 0.125):
         self.max_unit, self.min_unit = max_unit, min(min_unit, max_unit)
         self.unit = max_unit
         self.tolerance, self.recover_rounds = tolerance, recover_rounds
         self.enabled = enabled
         self.floor_ms: Optional[float] = None
         self._clean = 0
+        self.share, self.min_share = 1.0, min_share
+        self.credit = 1.0
+        self._trace = os.environ.get("NINFER_FT_BW_TRACE", "") == "1"
+
+    @property
+    def mode(self) -> str:
+        return "dynamic" if self.enabled else "manual"
+
+    def _changed(self, why: str) -> None:
+        if self._trace:
+            print(f"[bandwidth governor] mode={self.mode} prefill unit={self.unit} share={self.share:g} ({why})",
+                  file=sys.stderr, flush=True)
+
+    # ---- consumption: asked at every decision point, charged when a prefill unit actually runs
+    def prefill_allowed(self) -> bool:
+        return not self.enabled or self.credit >= 1.0
+
+    def charge_prefill(self) -> None:
+        self.credit = max(0.0, self.credit - 1.0)
+
+    def on_decode_round(self) -> None:
+        self.credit = min(2.0, self.credit + self.share)
 
     def observe(self, decode_ms: float, shared_with_prefill: bool) -> None:
         if not self.enabled:
@@ -158,20 +205,32 @@ class BandwidthGovernor:
         if self.floor_ms is None:
             return
         if shared_with_prefill and decode_ms > self.floor_ms * self.tolerance:
-            self.unit = max(self.min_unit, self.unit // 2)
+            if self.unit > self.min_unit:
+                self.unit = max(self.min_unit, self.unit // 2)
+                self._changed("decode round above tolerance: unit halved")
+            elif self.share > self.min_share:
+                self.share = max(self.min_share, self.share / 2)
+                self._changed("decode round above tolerance at the minimum unit: share halved")
             self._clean = 0
         else:
             self._clean += 1
-            if self._clean >= self.recover_rounds and self.unit < self.max_unit:
-                self.unit = min(self.max_unit, self.unit * 2)
-                self._clean = 0
+            if self._clean >= self.recover_rounds:
+                if self.share < 1.0:
+                    self.share = min(1.0, self.share * 2)
+                    self._clean = 0
+                    self._changed("clean rounds: share doubled")
+                elif self.unit < self.max_unit:
+                    self.unit = min(self.max_unit, self.unit * 2)
+                    self._clean = 0
+                    self._changed("clean rounds: unit doubled")
 
 
 class Engine:
     """Opaque engine facade: `submit()` from any thread, one worker thread does the rest."""
 
     def __init__(self, program_factory: Callable[[], ProgramBase], max_pending: int = 256,
-                 prefill_chunk: int = 2048, governor: bool = True):
+                 prefill_chunk: int = 2048, governor: bool = True, prefill_chunk_mode: Optional[str] = None,
+                 backfill_window: int = 8):
         self._factory = program_factory
         self.program = program_factory()
         # limits that submit() checks, cached so that it never touches the Program while the worker swaps it
@@ -179,7 +238,12 @@ class Engine:
         self._supports_media = bool(getattr(self.program, "supports_media", False))
         self._reload = None      # (factory, done event, result box) posted by reload_kv_storage, served by the worker
         self.max_pending = max_pending
-        self.governor = BandwidthGovernor(prefill_chunk, enabled=governor)
+        # prefill unit: 'dynamic' = the governor owns it, 'manual' = it stays `prefill_chunk`
+        mode = resolve_prefill_chunk_mode(prefill_chunk_mode) if governor else "manual"
+        self.governor = BandwidthGovernor(prefill_chunk, enabled=mode == "dynamic")
+        self.scheduler = Scheduler()
+        self.backfill_window = backfill_window   # requests behind a blocked head that are looked at per iteration
+        self._shared_round = False               # a prefill unit ran since the last decode round
         self.stats = RuntimeStats()
         self._pending: List[_Request] = []
         self._active: List[_Request] = []
@@ -229,6 +293,8 @@ class Engine:
             prog = self.program   # None for the moment in which the worker rebuilds it (storage reload)
             out = {"status": "failed" if self._failed else "ok", "pending": len(self._pending),
                    "active": len(self._active), "free_lanes": prog.free_lanes() if prog is not None else 0}
+            out["scheduler"] = dict(self.scheduler.stats, blocked_head=self.scheduler.protection is not None)
+            out["prefill_pacing"] = {"mode": self.governor.mode, "unit": self.governor.unit, "share": self.governor.share}
         census = getattr(prog, "census", None)
         if census is not None:
             try:   # counts only (no tokens, no session names); the worker may be changing the catalogue meanwhile
@@ -341,6 +407,8 @@ class Engine:
         """Commit-before-publish: budget and stop rules are applied before the token becomes visible."""
         req.n_generated += 1
         self.stats.completion_tokens += 1
+        if req.service is not None and req.service.remaining > 0:
+            req.service.consume(1)
         if tok in req.opts.stop_token_ids:
             self._finish(req, "stop")
             return
@@ -356,13 +424,47 @@ class Engine:
             if kind == "invariant_once":
                 raise InvariantError("injected invariant fault")
 
+    def _open(self, req: _Request) -> None:
+        """Gives `req` its lane (the caller has removed it from the pending queue)."""
+        try:
+            self._maybe_inject(req)
+            req.lane = (self.program.open(req.prompt, req.opts.sampling, session=req.opts.session)
+                        if req.opts.media is None else
+                        self.program.open(req.prompt, req.opts.sampling, session=req.opts.session, media=req.opts.media))
+            reserve = getattr(self.program, "reserve", None)
+            if reserve is not None:
+                # the pages this request may still grow into are spoken for from now on: a later admission
+                # must not count them as free
+                reserve(req.lane, len(req.prompt) + req.opts.max_tokens)
+            req.handle.t_admit = time.perf_counter()
+            if req.lane.reused:
+                self.stats.prefix_hits += 1
+                self.stats.prefix_tokens_reused += req.lane.reused
+                req.handle.cached_tokens = int(req.lane.reused)
+                req.handle.reuse_kind = getattr(req.lane, "reuse_kind", "") or "turn"
+            left = len(req.prompt) - req.lane.n_cached
+            req.service = ServiceAccount(projected_service_work(left, self.governor.unit, req.opts.max_tokens),
+                                         self.governor.unit)
+            req.state = "prefill"
+            self._active.append(req)
+        except RequestError as e:
+            self._finish(req, "error", str(e))
+        except Exception:
+            self._active.append(req)  # it must be among the victims of the engine-wide failure
+            raise
+
     def _admit(self) -> None:
+        """FIFO admission.  A head that does not fit freezes the active requests as its donors; requests behind it
+        are admitted out of order only with the Program's proof that the head still fits once the donors have left
+        (runtime/scheduler.py)."""
         if self._draining or self.program is None:
             time.sleep(0.002)   # a storage reload is waiting for the lanes to drain
             return
         now = time.perf_counter()
         with self._lock:
             pend = list(self._pending)
+        head: Optional[_Request] = None
+        looked = 0
         for req in pend:
             if req.handle.cancelled:
                 with self._lock:
@@ -375,28 +477,99 @@ class Engine:
                     self._pending.remove(req)
                 self._finish(req, "error", "request_queue_timeout")
                 continue
-            if not self.program.can_admit(len(req.prompt), req.opts.max_tokens):
-                break  # FIFO: do not let later requests overtake the head
-            with self._lock:
-                self._pending.remove(req)
-            try:
-                self._maybe_inject(req)
-                req.lane = (self.program.open(req.prompt, req.opts.sampling, session=req.opts.session)
-                            if req.opts.media is None else
-                            self.program.open(req.prompt, req.opts.sampling, session=req.opts.session, media=req.opts.media))
-                req.handle.t_admit = time.perf_counter()
-                if req.lane.reused:
-                    self.stats.prefix_hits += 1
-                    self.stats.prefix_tokens_reused += req.lane.reused
-                    req.handle.cached_tokens = int(req.lane.reused)
-                    req.handle.reuse_kind = getattr(req.lane, "reuse_kind", "") or "turn"
-                req.state = "prefill"
-                self._active.append(req)
-            except RequestError as e:
-                self._finish(req, "error", str(e))
-            except Exception:
-                self._active.append(req)  # it must be among the victims of the engine-wide failure
-                raise
+            if head is None:
+                self.scheduler.observe_head(req.handle.request_id)
+                if self.program.can_admit(len(req.prompt), req.opts.max_tokens):
+                    with self._lock:
+                        self._pending.remove(req)
+                    self._open(req)
+                    continue
+                head = req
+                self.scheduler.protect(req.handle.request_id, [r.handle.request_id for r in self._active])
+                continue
+            # behind a blocked head
+            looked += 1
+            if looked > self.backfill_window:
+                break
+            proof_fn = getattr(self.program, "admission_proof", None)
+            if proof_fn is None or not self.program.can_admit(len(req.prompt), req.opts.max_tokens):
+                continue
+            prot = self.scheduler.protection
+            active_ids = [r.handle.request_id for r in self._active]
+            donors = [r.lane for r in self._active if r.handle.request_id in prot.donors and r.lane is not None]
+            proof = proof_fn(len(head.prompt) + head.opts.max_tokens, len(req.prompt) + req.opts.max_tokens, donors)
+            if self.scheduler.authorize_backfill(req.handle.request_id, active_ids, proof):
+                with self._lock:
+                    self._pending.remove(req)
+                req.borrower = True
+                self._open(req)
+        if head is None:
+            self.scheduler.observe_head(None)
+
+    def _prefill_unit(self, req: _Request) -> None:
+        """One prefill unit of `req` (at most the governor's unit, cut at a frontier boundary)."""
+        t0 = time.perf_counter()
+        try:
+            n_before = req.lane.n_cached
+            budget = self.governor.unit
+            if req.service is not None and req.service.unit != budget:
+                req.service.reconcile(len(req.prompt) - n_before, budget)   # the unit moved under this request
+            edge = req.opts.shared_prefix_tokens
+            replay = req.opts.replay_edge_tokens if req.opts.session else 0
+            for e in (edge, replay):
+                if 0 < e < len(req.prompt) and n_before < e:
+                    budget = min(budget, e - n_before)     # stop exactly at the boundary
+            with trace.span("engine", "prefill_chunk", budget=int(budget), cached=int(n_before)):
+                first = self.program.prefill_step(req.lane, budget)
+            req.handle.prefill_chunks += 1
+            if req.service is not None and req.service.remaining > req.opts.max_tokens - req.n_generated:
+                # one quantum per completed unit, out of the prefill part of the reservation only (a unit cut short
+                # at a frontier boundary is one more unit than the projection counted)
+                req.service.consume(1)
+            self.stats.prompt_tokens += req.lane.n_cached - n_before
+            if first is None and req.lane.n_cached == edge and n_before < edge:
+                self.program.checkpoint(req.lane, "shared", "shared")   # any session may start from here
+            if first is None and req.lane.n_cached == replay and n_before < replay:
+                # the history up to, not including, the generation opener: a request that asks for this
+                # response again (other sampling, other opener) starts here
+                self.program.checkpoint(req.lane, req.opts.session, "replay")
+            step = getattr(self.program, "anchor_interval", 0)
+            if first is None and step > 0 and req.opts.session and req.lane.n_cached // step > n_before // step:
+                self.program.checkpoint(req.lane, req.opts.session, "anchor")   # recovery point inside a long prompt
+        except RequestError as e:
+            self._active.remove(req)
+            self._finish(req, "error", str(e))
+            return
+        self.stats.prefill_s += time.perf_counter() - t0
+        if first is not None:
+            if req.opts.session:
+                self.program.checkpoint(req.lane, req.opts.session, "turn")   # the prompt boundary
+            req.state = "decode"
+            self._commit_token(req, first)
+
+    def _decode_unit(self, ready: List[_Request]) -> None:
+        """One decode round over the decode-ready lanes."""
+        t0 = time.perf_counter()
+        with trace.span("engine", "decode_round", lanes=len(ready)):
+            toks = self.program.decode_round([r.lane for r in ready])
+        dt = time.perf_counter() - t0
+        self.stats.decode_s += dt
+        self.stats.decode_rounds += 1
+        self.governor.observe(dt * 1e3, self._shared_round)
+        self.governor.on_decode_round()
+        self._shared_round = False
+        descend = getattr(self.program, "kv_descent_step", None)
+        if descend is not None:
+            descend()   # per-cell KV precision descent between rounds (a no-op unless the program is set up for it)
+        for r in ready:
+            r.handle.decode_rounds += 1
+        for r, t in zip(ready, toks):
+            # a speculative program returns several tokens per lane and round; each one goes through the
+            # same commit-before-publish gate, and nothing after a stop / budget hit becomes visible
+            for tok in (t if isinstance(t, (list, tuple)) else (t,)):
+                if r.state == "finished":
+                    break
+                self._commit_token(r, tok)
 
     def _worker_loop(self) -> None:
         while True:
@@ -432,62 +605,16 @@ class Engine:
                 self._active.remove(req)
                 self._finish(req, "timeout")
         self._admit()
-        did_prefill = False
-        for req in self._active:
-            if req.state == "prefill":
-                t0 = time.perf_counter()
-                try:
-                    n_before = req.lane.n_cached
-                    budget = self.governor.unit
-                    edge = req.opts.shared_prefix_tokens
-                    replay = req.opts.replay_edge_tokens if req.opts.session else 0
-                    for e in (edge, replay):
-                        if 0 < e < len(req.prompt) and n_before < e:
-                            budget = min(budget, e - n_before)     # stop exactly at the boundary
-                    with trace.span("engine", "prefill_chunk", budget=int(budget), cached=int(n_before)):
-                        first = self.program.prefill_step(req.lane, budget)
-                    req.handle.prefill_chunks += 1
-                    self.stats.prompt_tokens += req.lane.n_cached - n_before
-                    if first is None and req.lane.n_cached == edge and n_before < edge:
-                        self.program.checkpoint(req.lane, "shared", "shared")   # any session may start from here
-                    if first is None and req.lane.n_cached == replay and n_before < replay:
-                        # the history up to, not including, the generation opener: a request that asks for this
-                        # response again (other sampling, other opener) starts here
-                        self.program.checkpoint(req.lane, req.opts.session, "replay")
-                    step = getattr(self.program, "anchor_interval", 0)
-                    if first is None and step > 0 and req.opts.session and req.lane.n_cached // step > n_before // step:
-                        self.program.checkpoint(req.lane, req.opts.session, "anchor")   # recovery point inside a long prompt
-                except RequestError as e:
-                    self._active.remove(req)
-                    self._finish(req, "error", str(e))
-                    break
-                self.stats.prefill_s += time.perf_counter() - t0
-                did_prefill = True
-                if first is not None:
-                    if req.opts.session:
-                        self.program.checkpoint(req.lane, req.opts.session, "turn")   # the prompt boundary
-                    req.state = "decode"
-                    self._commit_token(req, first)
-                break  # one prefill chunk per iteration, then give the decode lanes a round
+        pre = next((r for r in self._active if r.state == "prefill"), None)
         ready = [r for r in self._active if r.state == "decode"]
-        if ready:
-            t0 = time.perf_counter()
-            with trace.span("engine", "decode_round", lanes=len(ready)):
-                toks = self.program.decode_round([r.lane for r in ready])
-            dt = time.perf_counter() - t0
-            self.stats.decode_s += dt
-            self.stats.decode_rounds += 1
-            self.governor.observe(dt * 1e3, did_prefill)
-            descend = getattr(self.program, "kv_descent_step", None)
-            if descend is not None:
-                descend()   # per-cell KV precision descent between rounds (a no-op unless the program is set up for it)
-            for r in ready:
-                r.handle.decode_rounds += 1
-            for r, t in zip(ready, toks):
-                # a speculative program returns several tokens per lane and round; each one goes through the
-                # same commit-before-publish gate, and nothing after a stop / budget hit becomes visible
-                for tok in (t if isinstance(t, (list, tuple)) else (t,)):
-                    if r.state == "finished":
-                        break
-                    self._commit_token(r, tok)
+        action = self.scheduler.choose(bool(ready), pre is not None, self.governor.prefill_allowed())
+        if action is ExecutionAction.PREFILL:
+            self._prefill_unit(pre)
+            self.governor.charge_prefill()
+            self._shared_round = True
+        elif action is ExecutionAction.DECODE:
+            self._decode_unit(ready)
+        else:
+            time.sleep(0.001)   # nothing runnable: a head that does not fit is waiting for its time-out or its donors
+        self.scheduler.ran(action)
         self._active = [r for r in self._active if r.state != "finished"]

@@ -127,9 +127,18 @@ class GpuProgram(ProgramBase):
         self.states.import_slot(cold["tensors"][1], slot)
         return (pages, slot)
 
+    def _pages_for(self, n_tokens: int) -> int:
+        return (max(0, n_tokens) + self.kv.page_size - 1) // self.kv.page_size
+
+    def _pages_free(self) -> int:
+        return int(self.kv.pool.free_pages)
+
+    def _pages_held(self, lane: Lane) -> int:
+        return len(self.kv.row_pages.get(lane.row, ()))
+
     def _kv_room(self, n_tokens: int) -> bool:
-        need = (n_tokens + self.kv.page_size - 1) // self.kv.page_size
-        if self.kv.pool.free_pages < need:
+        need = self._pages_for(n_tokens)
+        if self.pages_available() < need:   # free pages minus what admitted requests may still take
             return False
         # mixed layers: every new page needs a cell in the hot tier of each of them
         return all(len(l.free[l.hot_tier]) >= need for l in self.kv.mixed)

@@ -51,6 +51,7 @@ class Lane:
     media: object = None     # frontend.media.PreparedPrompt of a multimodal request
     visual: object = None    # [V, hidden] vision-tower output of `media` (filled at the first prefill step)
     rope_delta: int = 0      # rope position - cache position once the prompt is in (multimodal prompts)
+    reserved_tokens: int = 0  # cache positions this request may still grow into (prompt + generation budget)
 
 
 @dataclass
@@ -114,6 +115,45 @@ class ProgramBase:
             if not self._evict_checkpoint():   # cached frontiers give way to live requests, oldest first
                 return False
         return True
+
+    # ---- page reservations and the admission proof ----
+    # A program with a page pool overrides the three hooks; the base (no pool) never runs short.
+    def _pages_for(self, n_tokens: int) -> int:
+        return 0
+
+    def _pages_free(self) -> int:
+        return 1 << 60
+
+    def _pages_held(self, lane: Lane) -> int:
+        return 0
+
+    def reserve(self, lane: Lane, n_tokens: int) -> None:
+        """The request on `lane` may grow to `n_tokens` cache positions: the pages it has not taken yet are no longer
+        free for admission (pages are handed out step by step, so without this two requests could each be admitted
+        against the same free pages and run out half-way)."""
+        lane.reserved_tokens = max(lane.reserved_tokens, int(n_tokens))
+
+    def outstanding_reservation(self) -> int:
+        """Pages that admitted requests are still entitled to take."""
+        return sum(max(0, self._pages_for(l.reserved_tokens) - self._pages_held(l)) for l in self.lanes.values())
+
+    def pages_available(self) -> int:
+        return self._pages_free() - self.outstanding_reservation()
+
+    def admission_proof(self, head_tokens: int, candidate_tokens: int, donors: Sequence[Lane]) -> bool:
+        """May a request of `candidate_tokens` positions be admitted ahead of a blocked head of `head_tokens`?  Yes if
+        it fits now and the head still fits once every donor lane has left while the candidate is still resident
+        (the donors give back their whole reservation and their lanes; cached frontiers are not counted: they can
+        only add room)."""
+        need_c, need_h = self._pages_for(candidate_tokens), self._pages_for(head_tokens)
+        free = self.pages_available()
+        if not self._free_rows or free < need_c:
+            return False
+        live = [l for l in donors if l.lane_id in self.lanes]
+        released = sum(max(self._pages_for(l.reserved_tokens), self._pages_held(l)) for l in live)
+        lanes_then = len(self._free_rows) - 1 + len(live)
+        pages_then = free - need_c + released
+        return lanes_then >= 1 and pages_then >= need_h
 
     # ---- census ----
     def census(self) -> dict:
