@@ -63,8 +63,12 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
                          "unit stays --prefill-chunk.  NINFER_FT_BW_TRACE=1 prints every change")
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--no-graphs", action="store_true", help="eager decode instead of CUDA graphs")
-    ap.add_argument("--spec", default="none", choices=["none", "mtp"], help="speculative decoding with the MTP draft module")
-    ap.add_argument("--draft-tokens", type=int, default=3)
+    ap.add_argument("--spec", default="none", choices=["none", "off", "auto", "mtp", "dflash", "dspark"],
+                    help="speculative decoding: mtp = the draft module proposes; auto = mtp when the weights carry a "
+                         "draft module; none / off = ordinary decode")
+    ap.add_argument("--draft-tokens", type=int, default=0,
+                    help="drafts per round, 1..15; 0 with --spec mtp = adaptive (the width follows acceptance and round "
+                         "cost over a ladder of captured widths)")
     ap.add_argument("--spec-stochastic", action="store_true",
                     help="with --spec mtp and sampled requests: the draft module samples its proposals and the verifier "
                          "accepts with min(1, p / q) (general speculative sampling) instead of arg-max proposals")
@@ -261,20 +265,34 @@ def build_engine(args, cfg: ModelConfig, weights, ranks=None) -> Optional[Engine
     if args.kv_layer_spec:
         from .kv.policy import parse_layer_storage
         kv = parse_layer_storage(args.kv_layer_spec, len(cfg.attn_layers))
-    if getattr(args, "spec", "none") == "mtp":
+    from .runtime.spec_options import from_strings
+    try:
+        head_ids = _draft_head_ids(getattr(args, "draft_head", ""), cfg)
+        if head_ids is None and "text/draft_head_token_ids" in weights:
+            head_ids = [int(v) for v in weights["text/draft_head_token_ids"].reshape(-1)]
+        spec = from_strings(getattr(args, "spec", "none"), getattr(args, "draft_tokens", 0),
+                            "shortlist" if getattr(args, "draft_head", "") else "auto", None,
+                            getattr(args, "spec_stochastic", False))
+        spec = spec.resolve("mtp/fc" in weights, "dflash/feature_proj" in weights, head_ids is not None)
+    except ValueError as e:
+        raise SystemExit(str(e)) from None
+    if spec.backend == "dflash":
+        raise SystemExit("--spec dflash: the engine's lanes draft with the MTP module; the DFlash drafter runs in the "
+                         "static-batch generator (bench.py --spec dflash)")
+    if spec.backend == "mtp":
         if not str(args.device).startswith("cuda"):
             raise SystemExit("--spec mtp needs a GPU")
-        if "mtp/fc" not in weights:
-            raise SystemExit("--spec mtp: the weights have no draft module (make-artifact --with-mtp)")
         from .runtime.speculative import SpeculativeProgram
+        adaptive = (spec.adaptive or getattr(args, "spec_adaptive_width", False)) and not spec.stochastic_drafts
+        width = spec.width if adaptive or spec.draft_tokens else 3   # sampled drafts keep one width: three unless told
 
         def factory():
             return SpeculativeProgram(cfg, weights, args.device, max_lanes=args.max_lanes, max_context=args.max_context,
-                                      draft_tokens=args.draft_tokens, kv_format=kv, page_size=args.page_size,
+                                      draft_tokens=width, kv_format=kv, page_size=args.page_size,
                                       prefill_chunk=args.prefill_chunk, use_graph=not getattr(args, "no_graphs", False),
-                                      stochastic_drafts=getattr(args, "spec_stochastic", False),
-                                      adaptive_width=getattr(args, "spec_adaptive_width", False),
-                                      draft_head_ids=_draft_head_ids(getattr(args, "draft_head", ""), cfg))
+                                      stochastic_drafts=spec.stochastic_drafts,
+                                      adaptive_width=adaptive,
+                                      draft_head_ids=head_ids if spec.proposal_head == "shortlist" else None)
         return Engine(factory, prefill_chunk=args.prefill_chunk,
                       prefill_chunk_mode=getattr(args, "prefill_chunk_mode", None))
     return Engine(program_factory(args, cfg, weights, kv), prefill_chunk=args.prefill_chunk,
@@ -466,7 +484,7 @@ def cmd_serve(args) -> int:
                             queue_timeout_s=args.queue_timeout)
     relayout = None
     if args.kv_auto_relayout > 0:
-        if not str(args.device).startswith("cuda") or args.spec != "none":
+        if not str(args.device).startswith("cuda") or args.spec not in ("none", "off"):
             raise SystemExit("--kv-auto-relayout needs the GPU program without speculative decoding")
         from .serve.kv_auto_relayout import KvAutoRelayout, RelayoutConfig, kv_scale_energy
         relayout = KvAutoRelayout(engine, len(cfg.attn_layers), lambda: kv_scale_energy(engine.program.kv),
