@@ -54,6 +54,17 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8", "fp8h", "int8", "nvfp4", "mixed"],
                     help="KV cache codec (fp8h = fp8 per-row with K in the Hadamard frame)")
     ap.add_argument("--kv-layer-spec", default="", help="per-layer KV storage, e.g. 'all:fp8' or '0-3:bf16,4-15:nvfp4'")
+    ap.add_argument("--kv-bits", type=float, default=None,
+                    help="one ceiling on the average bits per KV element: the bit-budget planner picks a tier per layer")
+    ap.add_argument("--kv-k-bits", type=float, default=None, help="ceiling of the K planes (with --kv-v-bits)")
+    ap.add_argument("--kv-v-bits", type=float, default=None, help="ceiling of the V planes (with --kv-k-bits)")
+    ap.add_argument("--kv-bits-mode", default=None, choices=["joint", "split", "ceiling"],
+                    help="split: each plane is layered on its own ceiling and a layer both planes cannot share is refused "
+                         "by index; ceiling: deploy min(k, v) on both planes and report the unspendable headroom")
+    ap.add_argument("--kv-tier-scores", default="", help="tier=penalty table replacing the ladder's priors (see "
+                                                         "`python -m ninfer_fusion_b200.kv.kv_bits score-table show`)")
+    ap.add_argument("--kv-k-tier-scores", default="", help="score table of the K planes (split reading)")
+    ap.add_argument("--kv-v-tier-scores", default="", help="score table of the V planes (split reading)")
     ap.add_argument("--max-context", type=int, default=4096)
     ap.add_argument("--max-lanes", type=int, default=8, help="concurrent sequences")
     ap.add_argument("--prefill-chunk", type=int, default=2048)
@@ -237,11 +248,12 @@ def build_engine(args, cfg: ModelConfig, weights, ranks=None) -> Optional[Engine
     stops it and gets None."""
     kv = args.kv_dtype
     check_device_routes(args, weights)
+    _kv_spec_from_ceilings(args, cfg)
     if ranks is not None:
         from .parallel.replicated import LeaderProgram, follower_loop
         from .parallel.tp import TensorParallel
         rank, world, channel = ranks
-        if getattr(args, "spec", "none") != "none" or getattr(args, "vision", False) or args.weight_budget_gib > 0:
+        if getattr(args, "spec", "none") not in ("none", "off") or getattr(args, "vision", False) or args.weight_budget_gib > 0:
             raise SystemExit("--tp does not combine with --spec, --vision or --weight-budget-gib yet")
         if args.kv_layer_spec:
             from .kv.policy import parse_layer_storage
@@ -297,6 +309,33 @@ def build_engine(args, cfg: ModelConfig, weights, ranks=None) -> Optional[Engine
                       prefill_chunk_mode=getattr(args, "prefill_chunk_mode", None))
     return Engine(program_factory(args, cfg, weights, kv), prefill_chunk=args.prefill_chunk,
                       prefill_chunk_mode=getattr(args, "prefill_chunk_mode", None))
+
+
+def _kv_spec_from_ceilings(args, cfg: ModelConfig) -> None:
+    """--kv-bits / --kv-k-bits + --kv-v-bits -> the per-layer storage spec (kv/kv_bits.py); fills args.kv_layer_spec."""
+    bits, kb, vb = getattr(args, "kv_bits", None), getattr(args, "kv_k_bits", None), getattr(args, "kv_v_bits", None)
+    tables = [getattr(args, n, "") for n in ("kv_tier_scores", "kv_k_tier_scores", "kv_v_tier_scores")]
+    if bits is None and kb is None and vb is None:
+        if any(tables) or getattr(args, "kv_bits_mode", None):
+            raise SystemExit("--kv-tier-scores / --kv-bits-mode steer the bit-budget planner: give --kv-bits or the two "
+                             "per-plane ceilings")
+        return
+    if args.kv_layer_spec:
+        raise SystemExit("--kv-layer-spec names the tiers itself; a bit ceiling would compute them: give one of the two")
+    from .kv import kv_bits as KB
+
+    def load(path):
+        if not path:
+            return None
+        with open(path) as f:
+            return KB.parse_scores(f.read(), path)
+    try:
+        plan = KB.resolve(len(cfg.attn_layers), bits, kb, vb, getattr(args, "kv_bits_mode", None), *(load(t) for t in tables))
+    except (KB.KvBitsRefused, ValueError) as e:
+        raise SystemExit(f"KV bit ceilings: {e}") from None
+    args.kv_layer_spec = plan.spec
+    head = getattr(plan, "headroom_bits", None)
+    print(f"[kv-bits] per-layer storage: {plan.spec}" + (f"; unspendable headroom {head}" if head else ""), file=sys.stderr)
 
 
 def _draft_head_ids(spec: str, cfg: ModelConfig):
