@@ -73,6 +73,12 @@ class RuntimeStats:
     decode_rounds: int = 0
     prefix_hits: int = 0
     prefix_tokens_reused: int = 0
+    # the worker's wall time, each segment counted once whatever the batch size: host-active and device-wait seconds
+    # per work class
+    host_prefill_s: float = 0.0
+    host_decode_s: float = 0.0
+    device_wait_prefill_s: float = 0.0
+    device_wait_decode_s: float = 0.0
 
     def as_dict(self) -> dict:
         d = dict(self.__dict__)
@@ -97,6 +103,15 @@ class GenerationHandle:
         self.reuse_kind = ""            # kind of that frontier ("" = started at the root)
         self.prefill_chunks = 0
         self.decode_rounds = 0
+        # wall time of the units this request took part in, split into time blocked on the device and host-active
+        # time; in a batched round every participant is delayed by the whole round, so these explain one request's
+        # latency and must not be summed across concurrent requests
+        self.device_wait_s = 0.0
+        self.host_exposed_s = 0.0
+        self.decode_device_wait_s = 0.0
+        self.decode_host_exposed_s = 0.0
+        # draft-verify rounds this request took part in (a speculative program): what was drafted, what was accepted
+        self.speculative: Optional[dict] = None
         self._cancel = threading.Event()
 
     def cancel(self) -> None:
@@ -509,6 +524,7 @@ class Engine:
     def _prefill_unit(self, req: _Request) -> None:
         """One prefill unit of `req` (at most the governor's unit, cut at a frontier boundary)."""
         t0 = time.perf_counter()
+        w0 = getattr(self.program, "device_wait_s", 0.0)
         try:
             n_before = req.lane.n_cached
             budget = self.governor.unit
@@ -540,7 +556,13 @@ class Engine:
             self._active.remove(req)
             self._finish(req, "error", str(e))
             return
-        self.stats.prefill_s += time.perf_counter() - t0
+        dt = time.perf_counter() - t0
+        wait = min(dt, max(0.0, getattr(self.program, "device_wait_s", 0.0) - w0))
+        self.stats.prefill_s += dt
+        self.stats.device_wait_prefill_s += wait
+        self.stats.host_prefill_s += dt - wait
+        req.handle.device_wait_s += wait
+        req.handle.host_exposed_s += dt - wait
         if first is not None:
             if req.opts.session:
                 self.program.checkpoint(req.lane, req.opts.session, "turn")   # the prompt boundary
@@ -550,9 +572,18 @@ class Engine:
     def _decode_unit(self, ready: List[_Request]) -> None:
         """One decode round over the decode-ready lanes."""
         t0 = time.perf_counter()
+        w0 = getattr(self.program, "device_wait_s", 0.0)
         with trace.span("engine", "decode_round", lanes=len(ready)):
             toks = self.program.decode_round([r.lane for r in ready])
         dt = time.perf_counter() - t0
+        wait = min(dt, max(0.0, getattr(self.program, "device_wait_s", 0.0) - w0))
+        self.stats.device_wait_decode_s += wait
+        self.stats.host_decode_s += dt - wait
+        for r in ready:
+            r.handle.device_wait_s += wait
+            r.handle.host_exposed_s += dt - wait
+            r.handle.decode_device_wait_s += wait
+            r.handle.decode_host_exposed_s += dt - wait
         self.stats.decode_s += dt
         self.stats.decode_rounds += 1
         self.governor.observe(dt * 1e3, self._shared_round)
@@ -564,6 +595,21 @@ class Engine:
         for r in ready:
             r.handle.decode_rounds += 1
         for r, t in zip(ready, toks):
+            if isinstance(t, (list, tuple)):
+                window = int(getattr(self.program, "draft_window", 0) or max(0, len(t) - 1))
+                sp = r.handle.speculative
+                if sp is None:
+                    sp = r.handle.speculative = {"backend": getattr(self.program, "speculative_backend", "mtp"),
+                                                 "draft_window": window, "rounds": 0, "drafted_tokens": 0,
+                                                 "accepted_tokens": 0, "fallback_steps": 0, "accepted_per_position": []}
+                sp["rounds"] += 1
+                sp["draft_window"] = max(sp["draft_window"], window)
+                sp["drafted_tokens"] += window
+                sp["accepted_tokens"] += len(t) - 1
+                per = sp["accepted_per_position"]
+                per.extend([0] * (len(t) - 1 - len(per)))
+                for j in range(len(t) - 1):
+                    per[j] += 1
             # a speculative program returns several tokens per lane and round; each one goes through the
             # same commit-before-publish gate, and nothing after a stop / budget hit becomes visible
             for tok in (t if isinstance(t, (list, tuple)) else (t,)):

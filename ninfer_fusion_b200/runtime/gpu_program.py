@@ -6,6 +6,7 @@ advances one lane by a chunk through the same ragged forward.  See `program.Prog
 """
 from __future__ import annotations
 
+import time
 from typing import Dict, List, Optional, Sequence
 
 import numpy as np
@@ -126,6 +127,12 @@ class GpuProgram(ProgramBase):
         slot = self.states.alloc()
         self.states.import_slot(cold["tensors"][1], slot)
         return (pages, slot)
+
+    def _wait_device(self) -> None:
+        """Blocks until the step's results are on the host; the blocked time is the step's exposed device wait."""
+        t0 = time.perf_counter()
+        torch.cuda.current_stream().synchronize()
+        self.device_wait_s += time.perf_counter() - t0
 
     def _pages_for(self, n_tokens: int) -> int:
         return (max(0, n_tokens) + self.kv.page_size - 1) // self.kv.page_size
@@ -254,7 +261,7 @@ class GpuProgram(ProgramBase):
         if not done:
             return None
         self.out_host[:1].copy_(ids[:1], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        self._wait_device()
         self.model.status.check("after prefill")
         lane.last_token = int(self.out_host[0])
         return lane.last_token
@@ -340,7 +347,7 @@ class GpuProgram(ProgramBase):
             batch = self.bufs_decode.build(self._chunks(lanes), upload=True, rope_delta=[l.rope_delta for l in lanes])
             ids = self._forward_select(batch, greedy, batch.table_row)
         self.out_host[:B].copy_(ids, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        self._wait_device()
         toks = [int(v) for v in self.out_host[:B]]
         if self.token_counts is not None:
             r = torch.tensor([l.row for l in lanes], device=self.device)

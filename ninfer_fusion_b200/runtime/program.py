@@ -103,6 +103,7 @@ class ProgramBase:
         self.anchor_interval = 0
         self.max_anchors = 3
         self.shared_stats = {"published": 0, "hits": 0}
+        self.device_wait_s = 0.0   # wall time this program's steps spent blocked on the device (the engine reads deltas)
 
     # ---- capacity ----
     def free_lanes(self) -> int:

@@ -19,6 +19,7 @@ include/ninfer/ops/speculative_round.h:40-151, include/ninfer/ops/gdn_replay.h:1
 """
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import replace
 from typing import Callable, Dict, List, Optional, Sequence
@@ -153,6 +154,7 @@ class SpeculativeGenerator(Generator):
         self.catch_rows = torch.zeros(max_batch, dtype=torch.int32, device=dev)
         self.draft_col = torch.zeros(max_batch, dtype=torch.int32, device=dev)
         self._round_graphs: Dict[tuple, tuple] = {}
+        self.device_wait_s = 0.0
         self.history: List[List[int]] = []
         self.rounds = 0
         self.accepted = 0
@@ -587,7 +589,9 @@ class SpeculativeGenerator(Generator):
         graph.replay()
         self.acc_host[:B].copy_(self.n_acc[:B], non_blocking=True)
         self.tok_host[:B].copy_(self.out_tok[:B], non_blocking=True)
+        t_wait = time.perf_counter()
         torch.cuda.current_stream().synchronize()
+        self.device_wait_s += time.perf_counter() - t_wait
         emitted: List[List[int]] = []
         for b in range(B):
             m = int(self.acc_host[b])
@@ -601,13 +605,24 @@ class SpeculativeGenerator(Generator):
         self.rounds += 1
         return emitted
 
+    def _accept_log(self, emitted: List[List[int]]) -> List[List[int]]:
+        """`NINFER_ACCEPTLOG=<path>`: one JSON line per round (round, drafts per sequence, tree ranks, accepted drafts
+        of every sequence), for acceptance studies without touching the request log."""
+        path = os.environ.get("NINFER_ACCEPTLOG", "")
+        if path:
+            import json
+            with open(path, "a", encoding="utf-8") as f:
+                f.write(json.dumps({"round": self.rounds, "width": self.K, "ranks": self.R, "drafter": self.drafter,
+                                    "accepted": [len(e) - 1 for e in emitted]}) + "\n")
+        return emitted
+
     def decode_round(self) -> List[List[int]]:
         """One draft-verify round; returns the tokens emitted for every sequence (1..K+1 each)."""
         if self.R > 1:
-            return self.decode_round_tree()
+            return self._accept_log(self.decode_round_tree())
         ctl = self.width_ctl
         if ctl is None:
-            return self._decode_round_graph() if self._graph_round_ok() else self._decode_round_eager()
+            return self._accept_log(self._decode_round_graph() if self._graph_round_ok() else self._decode_round_eager())
         self._set_width(ctl.width)
         self._fresh_graph = False
         t0 = time.perf_counter()
@@ -616,7 +631,7 @@ class SpeculativeGenerator(Generator):
         # captured its graph first says nothing about the cost of its width
         ms = None if self._fresh_graph else (time.perf_counter() - t0) * 1e3
         ctl.observe_round([len(e) - 1 for e in emitted], self.K, ms)
-        return emitted
+        return self._accept_log(emitted)
 
     def _decode_round_eager(self) -> List[List[int]]:
         B, K = len(self.rows), self.K
@@ -667,7 +682,9 @@ class SpeculativeGenerator(Generator):
         self.model.fold_gdn(self.ws, batch, self.states, self.rec, seq_end)
         self.acc_host[:B].copy_(self.n_acc[:B], non_blocking=True)
         self.tok_host[:B].copy_(self.out_tok[:B], non_blocking=True)
+        t_wait = time.perf_counter()
         torch.cuda.current_stream().synchronize()
+        self.device_wait_s += time.perf_counter() - t_wait
         emitted: List[List[int]] = []
         for b in range(B):
             m = int(self.acc_host[b])
@@ -749,6 +766,17 @@ class SpeculativeProgram:
         # the first draft token's distribution q (stochastic drafts) belongs to the row as well
         self.row_q_ids = torch.full((max_lanes, self.gen.q_ids.shape[2]), -1, dtype=torch.int32, device=self.gen.device)
         self.row_q_probs = torch.zeros((max_lanes, self.gen.q_ids.shape[2]), dtype=torch.float32, device=self.gen.device)
+
+    @property
+    def device_wait_s(self) -> float:
+        return self.gen.device_wait_s
+
+    speculative_backend = "mtp"
+
+    @property
+    def draft_window(self) -> int:
+        """Drafts per sequence in the round that just ran (the width in force: it moves under the adaptive controller)."""
+        return self.gen.K
 
     # ---- Program API ----
     def free_lanes(self) -> int:

@@ -83,9 +83,16 @@ class RequestLog:
             "timings_seconds": {"prepare": None, "ttft": ttft, "vision": None,
                                 "prefill": None if ttft is None else max(0.0, ttft - res.queue_wait_s),
                                 "decode": decode_s, "total": res.total_s},
-            "engine_timing": {"queue_wait_seconds": res.queue_wait_s, "device_wait_exposed_seconds": None,
-                              "host_exposed_seconds": None,
-                              "decode": {"rounds": res.decode_rounds},
+            # host_exposed_seconds: the reference splits it into five phases (engine boundary, program submit / post,
+            # commit, maintenance); this engine measures their sum per unit, so the phases are null and `total` is set
+            "engine_timing": {"queue_wait_seconds": res.queue_wait_s,
+                              "device_wait_exposed_seconds": getattr(res, "device_wait_s", None),
+                              "host_exposed_seconds": {"engine_boundary": None, "program_submit": None, "program_post": None,
+                                                       "engine_commit_output": None, "engine_maintenance": None,
+                                                       "total": getattr(res, "host_exposed_s", None)},
+                              "decode": {"rounds": res.decode_rounds,
+                                         "host_exposed_seconds": getattr(res, "decode_host_exposed_s", None),
+                                         "device_wait_seconds": getattr(res, "decode_device_wait_s", None)},
                               "units": {"prefill": res.prefill_chunks}},
             "speculative": speculative or {"backend": "none", "draft_window": 0, "rounds": 0, "drafted_tokens": 0,
                                            "accepted_tokens": 0, "fallback_steps": 0, "accepted_per_position": []},
@@ -106,12 +113,19 @@ class RequestLog:
         dt = now - self._last_tp
         self._last_tp = now
         keys = ("prompt_tokens", "completion_tokens", "decode_rounds", "requests_done", "requests_failed",
-                "requests_rejected", "prefix_hits", "prefix_tokens_reused")
+                "requests_rejected", "prefix_hits", "prefix_tokens_reused", "host_prefill_s", "host_decode_s",
+                "device_wait_prefill_s", "device_wait_decode_s")
         delta = {k: (stats.get(k, 0) or 0) - self._prev.get(k, 0) for k in keys}
         self._prev = {k: stats.get(k, 0) or 0 for k in keys}
         if not any(delta.values()):
             return
         rounds = delta["decode_rounds"]
+        host_work = {"elapsed_seconds": {"total": delta["host_prefill_s"] + delta["host_decode_s"]},
+                     "device_wait_seconds": delta["device_wait_prefill_s"] + delta["device_wait_decode_s"],
+                     "work_class_seconds": {"decode": {"host": delta["host_decode_s"], "device_wait": delta["device_wait_decode_s"]},
+                                            "prefill": {"host": delta["host_prefill_s"], "device_wait": delta["device_wait_prefill_s"]}},
+                     "per_round": {"decode_host_us": (delta["host_decode_s"] / rounds * 1e6) if rounds else None,
+                                   "decode_device_wait_us": (delta["device_wait_decode_s"] / rounds * 1e6) if rounds else None}}
         self.event("throughput", interval_seconds=dt,
                    prefill_tokens=delta["prompt_tokens"], decode_tokens=delta["completion_tokens"],
                    decode_rounds=rounds,
@@ -119,6 +133,7 @@ class RequestLog:
                    requests={"done": delta["requests_done"], "failed": delta["requests_failed"],
                              "rejected": delta["requests_rejected"]},
                    context_cache={"prefix_hits": delta["prefix_hits"], "prefix_tokens_reused": delta["prefix_tokens_reused"]},
+                   host_work=host_work,
                    scheduler=gauges or {})
 
     def close(self) -> None:

@@ -176,7 +176,7 @@ def make_handler(state: ServeState):
                                 thinking=bool(getattr(req, "enable_thinking", True)), session=bool(req.session))
 
             def finished(res: GenResult):
-                state.log.request_done(res, api, stream)
+                state.log.request_done(res, api, stream, speculative=getattr(res, "speculative", None))
 
             try:
                 events = svc.stream(req, on_start=on_start, cancelled=gone.is_set)

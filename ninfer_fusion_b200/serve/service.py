@@ -62,6 +62,11 @@ class GenResult:
     queue_wait_s: float = 0.0     # submit -> lane
     prefill_chunks: int = 0
     decode_rounds: int = 0
+    device_wait_s: float = 0.0            # time of this request's units spent blocked on the device
+    host_exposed_s: float = 0.0           # the rest of those units' wall time
+    decode_device_wait_s: float = 0.0
+    decode_host_exposed_s: float = 0.0
+    speculative: Optional[dict] = None    # draft-verify counters of this request (None: ordinary decode)
 
 
 class GenerationService:
@@ -223,6 +228,9 @@ class GenerationService:
             res.cached_tokens, res.reuse_kind = handle.cached_tokens, handle.reuse_kind
             res.queue_wait_s = (handle.t_admit - handle.t_submit) if handle.t_admit is not None else 0.0
             res.prefill_chunks, res.decode_rounds = handle.prefill_chunks, handle.decode_rounds
+            res.device_wait_s, res.host_exposed_s = handle.device_wait_s, handle.host_exposed_s
+            res.decode_device_wait_s, res.decode_host_exposed_s = handle.decode_device_wait_s, handle.decode_host_exposed_s
+            res.speculative = handle.speculative
             yield ("done", res)
         finally:
             self._permits.release()

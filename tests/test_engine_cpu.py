@@ -349,3 +349,38 @@ def test_health_carries_a_residency_census(tmp_path):
         assert c["cold_stats"]["demoted_host"] >= 1 and "pages" not in c          # the oracle program has no page pool
     finally:
         eng.shutdown()
+
+
+def test_speculative_rounds_are_counted_per_request_and_logged_by_position(tmp_path, monkeypatch):
+    """A program that commits several tokens per lane and round: the handle carries the draft-verify counters the
+    request log publishes (rounds, drafted, accepted, accepted per draft position)."""
+    from ninfer_fusion_b200.models.config import TINY_DENSE
+    from ninfer_fusion_b200.models.weights import random_weights
+    from ninfer_fusion_b200.runtime.program import ReferenceProgram
+
+    class TwoPerRound(ReferenceProgram):
+        speculative_backend = "mtp"
+        draft_window = 3
+
+        def decode_round(self, lanes):
+            out = []
+            for lane in lanes:                      # "one of three drafts accepted": two tokens per round
+                a = super().decode_round([lane])[0]
+                lane.tokens.append(lane.last_token)
+                b = super().decode_round([lane])[0]
+                lane.tokens.pop()
+                out.append([a, b])
+            return out
+
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cpu", seed=5, std=0.05)
+    eng = Engine(lambda: TwoPerRound(cfg, w, max_lanes=2, max_context=128), prefill_chunk=16)
+    try:
+        h = eng.submit(list(range(10, 30)), RequestOptions(max_tokens=7))
+        assert len(h.wait(timeout=120)) == 7
+        sp = h.speculative
+        assert sp["backend"] == "mtp" and sp["draft_window"] == 3 and sp["rounds"] == 3     # 1 (prefill) + 2 + 2 + 2
+        assert sp["drafted_tokens"] == 9 and sp["accepted_tokens"] == 3 and sp["accepted_per_position"] == [3]
+        assert h.host_exposed_s > 0 and h.device_wait_s == 0.0 and h.decode_rounds == 3
+    finally:
+        eng.shutdown()

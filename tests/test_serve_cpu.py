@@ -198,6 +198,14 @@ def test_request_log_lines(server):
     t = done["timings_seconds"]
     assert set(t) == {"prepare", "ttft", "vision", "prefill", "decode", "total"} and t["total"] >= t["ttft"] > 0
     assert done["engine_timing"]["queue_wait_seconds"] >= 0 and done["engine_timing"]["units"]["prefill"] >= 1
+    et = done["engine_timing"]
+    # exposure accounting: the units this request took part in, split into device wait (none on the CPU program) and
+    # host-active time; the five host phases of the reference's schema are present, only their total is measured
+    assert et["device_wait_exposed_seconds"] == 0.0 and et["host_exposed_seconds"]["total"] > 0
+    assert set(et["host_exposed_seconds"]) == {"engine_boundary", "program_submit", "program_post", "engine_commit_output",
+                                               "engine_maintenance", "total"}
+    assert et["decode"]["rounds"] >= 1 and 0 < et["decode"]["host_exposed_seconds"] <= et["host_exposed_seconds"]["total"]
+    assert et["host_exposed_seconds"]["total"] <= t["total"] + 1e-6
     assert set(done["speculative"]) == {"backend", "draft_window", "rounds", "drafted_tokens", "accepted_tokens",
                                         "fallback_steps", "accepted_per_position"}
     start = [r for r in recs if r["event"] == "server_start"][-1]
