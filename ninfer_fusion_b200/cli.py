@@ -111,6 +111,11 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--tp", type=int, default=1,
                     help="tensor-parallel ranks; launch the command with `python -m torch.distributed.run --nproc-per-node N "
                          "--master-addr 127.0.0.1 -m ninfer_fusion_b200.cli ...`: rank 0 serves, the others follow its steps")
+    ap.add_argument("--ep", type=int, default=1,
+                    help="expert-parallel ranks (MoE models): routed experts are split over the ranks, every request's "
+                         "attention / GDN work lives on one rank, the ranks run in lock step; launch like --tp")
+    ap.add_argument("--dp", type=int, default=1,
+                    help="data-parallel ranks: independent replicas of the model behind one front end; launch like --tp")
     ap.add_argument("--rank-timeout", type=float, default=60.0,
                     help="seconds after which a silent rank fails the engine (control channel time-out)")
 
@@ -200,11 +205,15 @@ def setup_ranks(args):
     (rank, world, channel).  Must run before the model is loaded: it decides `args.device`."""
     from .parallel.replicated import RankChannel, world_from_env
     rank, world = world_from_env()
-    want = max(int(getattr(args, "tp", 1)), 1)
+    plans = {k: max(int(getattr(args, k, 1)), 1) for k in ("tp", "ep", "dp")}
+    if sum(1 for v in plans.values() if v > 1) > 1:
+        raise SystemExit("give one of --tp, --ep and --dp")
+    want = max(plans.values())
     if world == 1 and want == 1:
         return None
     if world != want:
-        raise SystemExit(f"--tp {want} needs {want} ranks (python -m torch.distributed.run --nproc-per-node {want} "
+        flag = max(plans, key=plans.get)
+        raise SystemExit(f"--{flag} {want} needs {want} ranks (python -m torch.distributed.run --nproc-per-node {want} "
                          f"--master-addr 127.0.0.1 -m ninfer_fusion_b200.cli ...); found {world}")
     import torch.distributed as dist
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -249,6 +258,31 @@ def build_engine(args, cfg: ModelConfig, weights, ranks=None) -> Optional[Engine
     kv = args.kv_dtype
     check_device_routes(args, weights)
     _kv_spec_from_ceilings(args, cfg)
+    if ranks is not None and max(int(getattr(args, "ep", 1)), int(getattr(args, "dp", 1))) > 1:
+        # every request lives on one rank (parallel/partitioned.py); expert parallelism adds the MoE exchange between
+        # the ranks inside every forward pass, hence lock step
+        from .parallel.partitioned import PartitionedLeader, partitioned_follower_loop
+        rank, world, channel = ranks
+        ep = int(getattr(args, "ep", 1)) > 1
+        if getattr(args, "spec", "none") not in ("none", "off") or getattr(args, "vision", False) or args.weight_budget_gib > 0:
+            raise SystemExit("--ep / --dp do not combine with --spec, --vision or --weight-budget-gib yet")
+        if ep and cfg.moe is None:
+            raise SystemExit("--ep shards routed experts: the model has none (use --dp for replicas of a dense model)")
+        if args.kv_layer_spec:
+            from .kv.policy import parse_layer_storage
+            kv = parse_layer_storage(args.kv_layer_spec, len(cfg.attn_layers))
+        inner_factory = program_factory(args, cfg, weights, kv)
+
+        def make_inner():
+            prog = inner_factory()
+            if ep:
+                prog.model.ep = (rank, world, None)     # this rank's contiguous range of experts; the rest is replicated
+            return prog
+        if rank != 0:
+            partitioned_follower_loop(make_inner(), channel, lockstep=ep)
+            return None
+        return Engine(lambda: PartitionedLeader(make_inner(), channel, args.max_lanes, lockstep=ep),
+                      prefill_chunk=args.prefill_chunk, prefill_chunk_mode=getattr(args, "prefill_chunk_mode", None))
     if ranks is not None:
         from .parallel.replicated import LeaderProgram, follower_loop
         from .parallel.tp import TensorParallel

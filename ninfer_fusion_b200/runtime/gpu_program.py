@@ -128,6 +128,11 @@ class GpuProgram(ProgramBase):
         self.states.import_slot(cold["tensors"][1], slot)
         return (pages, slot)
 
+    def set_global_tokens(self, n_tokens: int) -> None:
+        """Expert parallelism: bound on the tokens that all ranks together run in the next step (the MoE exchange
+        sizes its tiles and receive rows by it)."""
+        self.model.moe_global_tokens = int(n_tokens)
+
     def _wait_device(self) -> None:
         """Blocks until the step's results are on the host; the blocked time is the step's exposed device wait."""
         t0 = time.perf_counter()
