@@ -271,6 +271,10 @@ def build_engine(args, cfg: ModelConfig, weights, ranks=None) -> Optional[Engine
         if args.kv_layer_spec:
             from .kv.policy import parse_layer_storage
             kv = parse_layer_storage(args.kv_layer_spec, len(cfg.attn_layers))
+        if ep:
+            # a rank that captures a decode graph runs warm-up passes the other ranks do not run: graphs would break
+            # the lock step unless every rank captured the same ladder at the same moment, so EP serving runs eager
+            args.no_graphs = True
         inner_factory = program_factory(args, cfg, weights, kv)
 
         def make_inner():
