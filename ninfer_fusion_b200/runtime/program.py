@@ -52,6 +52,7 @@ class Lane:
     visual: object = None    # [V, hidden] vision-tower output of `media` (filled at the first prefill step)
     rope_delta: int = 0      # rope position - cache position once the prompt is in (multimodal prompts)
     reserved_tokens: int = 0  # cache positions this request may still grow into (prompt + generation budget)
+    session: Optional[str] = None  # continuation key of the request on this lane (its session is "live" meanwhile)
 
 
 @dataclass
@@ -73,6 +74,12 @@ class Checkpoint:
 
 
 SHARED_SESSION = "__shared__"
+
+# Retention classes of reusable frontiers and the weight each carries when a victim is chosen (a frontier of weight w
+# is given up before one of weight > w; shared prefixes live in their own bounded catalogue and are only taken when no
+# private frontier is left).  Reference: RetentionClass in src/runtime/contract/types.h:383-388 and
+# ResourceManager::private_retention_weight (src/runtime/engine/resource_manager.h:1298-1310).
+RETENTION_WEIGHT = {"disposable": 1, "recent_private": 4, "live_session": 16, "shared_stable": 0}
 
 
 class ProgramBase:
@@ -172,6 +179,11 @@ class ProgramBase:
         out = {"lanes": {"active": len(self.lanes), "max": self.max_lanes}, "frontiers": tiers, "kinds": kinds,
                "cold_bytes": cold_bytes, "budgets": {"host": self.host_budget_bytes, "disk": self.disk_budget_bytes},
                "cold_stats": dict(self.cold_stats), "shared_stats": dict(self.shared_stats)}
+        retention = {k: 0 for k in RETENTION_WEIGHT}
+        for c in self.checkpoints:
+            retention[self.retention_class(c)] += 1
+        out["retention"] = retention                                  # counts only: no session names leave the engine
+        out["sessions"] = len({c.session for c in self.checkpoints if c.session != SHARED_SESSION})
         kv = getattr(self, "kv", None)
         pool = getattr(kv, "pool", None)
         if pool is not None:
@@ -203,7 +215,41 @@ class ProgramBase:
         self._trim_cold()
         return True
 
+    def retention_class(self, c: Checkpoint) -> str:
+        """shared_stable: an entry of the shared-prefix catalogue.  live_session: a request of the frontier's session
+        is on a lane right now (its next turn is the most likely one to arrive).  disposable: a longer frontier of
+        the same session extends this one, so only an edited history would still want it.  recent_private: the rest."""
+        if c.kind == "shared" or c.session == SHARED_SESSION:
+            return "shared_stable"
+        n = len(c.tokens)
+        for o in self.checkpoints:
+            if o is not c and o.session == c.session and len(o.tokens) > n and o.tokens[:n] == c.tokens:
+                return "disposable"
+        if any(l.session == c.session for l in self.lanes.values()):
+            return "live_session"
+        return "recent_private"
+
+    def session_index(self) -> Dict[str, dict]:
+        """Session -> what is kept for it: number of frontiers, the longest one, where it lives, its retention class."""
+        out: Dict[str, dict] = {}
+        for c in self.checkpoints:
+            if c.session == SHARED_SESSION:
+                continue
+            e = out.setdefault(c.session, {"frontiers": 0, "longest_tokens": 0, "tier": "", "retention": "", "hits": 0})
+            e["frontiers"] += 1
+            e["hits"] += c.hits
+            if len(c.tokens) >= e["longest_tokens"]:
+                e["longest_tokens"], e["tier"], e["retention"] = len(c.tokens), c.tier, self.retention_class(c)
+        return out
+
     def _choose_victim(self, hot: List[Checkpoint]) -> Checkpoint:
+        private = [c for c in hot if self.retention_class(c) != "shared_stable"]
+        if private:
+            low = min(RETENTION_WEIGHT[self.retention_class(c)] for c in private)
+            hot = [c for c in private if RETENTION_WEIGHT[self.retention_class(c)] == low]
+        return self._cheapest_loss(hot)
+
+    def _cheapest_loss(self, hot: List[Checkpoint]) -> Checkpoint:
         """Least recently used without a planner; with one (`self.planner`, runtime/planner.py) the frontier whose loss
         costs least per token of context it holds: demand (hits, recency, shared credit) times the cost of getting
         it back from the tier it would fall to."""
@@ -414,6 +460,7 @@ class ProgramBase:
         lane = Lane(self._next_id, row, slot, list(prompt), 0, sampling or SamplingParams())
         if media is not None:
             lane.media, lane.rope_delta = media, int(media.rope_delta)
+        lane.session = session
         self._next_id += 1
         self.lanes[lane.lane_id] = lane
         ck = self._match(session, prompt)

@@ -384,3 +384,52 @@ def test_speculative_rounds_are_counted_per_request_and_logged_by_position(tmp_p
         assert h.host_exposed_s > 0 and h.device_wait_s == 0.0 and h.decode_rounds == 3
     finally:
         eng.shutdown()
+
+
+def test_retention_classes_order_the_victims():
+    """A frontier covered by a longer one of its session goes first, then private frontiers of sessions with nothing
+    in flight, and a session with a request on a lane keeps its frontier longest; shared prefixes are only taken when
+    no private frontier is left."""
+    from ninfer_fusion_b200.models.config import TINY_DENSE
+    from ninfer_fusion_b200.models.weights import random_weights
+    from ninfer_fusion_b200.runtime.program import RETENTION_WEIGHT, ReferenceProgram
+    cfg = TINY_DENSE.shrink(2)
+    w = random_weights(cfg, "cpu", seed=5, std=0.05)
+    prog = ReferenceProgram(cfg, w, max_lanes=4, max_context=128)
+
+    def run(session, prompt, n_new=2, keep_open=False):
+        lane = prog.open(prompt, None, session=session)
+        while prog.prefill_step(lane, 64) is None:
+            pass
+        prog.checkpoint(lane, session, "turn")
+        for _ in range(n_new):
+            prog.decode_round([lane])
+        prog.checkpoint(lane, session, "endpoint")
+        if not keep_open:
+            prog.close(lane)
+        return lane
+
+    run("old", list(range(10, 20)))                          # turn (covered by its endpoint) + endpoint
+    live = run("busy", list(range(30, 45)), keep_open=True)  # this session still has a request on a lane
+    sys_lane = prog.open(list(range(50, 58)), None, session=None)
+    while prog.prefill_step(sys_lane, 64) is None:
+        pass
+    prog.checkpoint(sys_lane, "x", "shared")
+    prog.close(sys_lane)
+    cls = {(c.session, c.kind): prog.retention_class(c) for c in prog.checkpoints}
+    assert cls[("old", "turn")] == "disposable" and cls[("old", "endpoint")] == "recent_private"
+    assert cls[("busy", "endpoint")] == "live_session" and cls[("busy", "turn")] == "disposable"
+    assert [k for k, v in cls.items() if v == "shared_stable"] == [("__shared__", "shared")]
+    assert prog.census()["retention"] == {"disposable": 2, "recent_private": 1, "live_session": 1, "shared_stable": 1}
+    idx = prog.session_index()
+    assert set(idx) == {"old", "busy"} and idx["busy"]["retention"] == "live_session" and idx["old"]["frontiers"] == 2
+    order = []
+    while prog._evict_checkpoint():
+        left = {(c.session, c.kind) for c in prog.checkpoints}
+        order.append([k for k in cls if k not in left and k not in order][0])
+    # the two covered turn frontiers first (least recently used of them first), then the idle session's endpoint, the
+    # live session's endpoint after it, and the shared prefix only when nothing private is left
+    assert order[:2] == [("old", "turn"), ("busy", "turn")]
+    assert order[2:] == [("old", "endpoint"), ("busy", "endpoint"), ("__shared__", "shared")]
+    assert RETENTION_WEIGHT["disposable"] < RETENTION_WEIGHT["recent_private"] < RETENTION_WEIGHT["live_session"]
+    prog.close(live)
