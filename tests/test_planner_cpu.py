@@ -112,6 +112,7 @@ def test_program_uses_the_planner_for_its_victim():
     old_long = Checkpoint("s1", "turn", list(range(400)), None, last_used=10)
     recent_short = Checkpoint("s2", "turn", list(range(20)), None, last_used=99, hits=5)
     shared = Checkpoint(SHARED_SESSION, "shared", list(range(50)), None, last_used=5, hits=4)
-    assert p._choose_victim([recent_short, shared, old_long]) is shared          # plain LRU takes the oldest
+    assert p._choose_victim([recent_short, shared, old_long]) is old_long        # plain LRU: the oldest PRIVATE frontier
+    assert p._choose_victim([shared]) is shared                                  # a shared prefix only when nothing private is left
     p.planner = P.MaterializationPlanner(P.PRESETS["b200"])
     assert p._choose_victim([recent_short, shared, old_long]) is old_long        # cold, unhit: cheapest to lose
