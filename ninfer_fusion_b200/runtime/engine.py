@@ -49,6 +49,7 @@ class RequestOptions:
     session: Optional[str] = None            # continuation key for prefix reuse
     media: object = None                     # frontend.media.PreparedPrompt for a request with images / videos
     shared_prefix_tokens: int = 0            # publish the first N prompt tokens (system prompt) in the shared catalogue
+    shared_prefix_edges: Sequence[int] = ()  # further token frontiers to publish there (explicit cache breakpoints)
     replay_edge_tokens: int = 0              # session frontier before the generation opener (regenerate-this-response point)
 
 
@@ -530,9 +531,9 @@ class Engine:
             budget = self.governor.unit
             if req.service is not None and req.service.unit != budget:
                 req.service.reconcile(len(req.prompt) - n_before, budget)   # the unit moved under this request
-            edge = req.opts.shared_prefix_tokens
+            shared_edges = sorted({int(e) for e in (req.opts.shared_prefix_tokens, *req.opts.shared_prefix_edges) if e})
             replay = req.opts.replay_edge_tokens if req.opts.session else 0
-            for e in (edge, replay):
+            for e in (*shared_edges, replay):
                 if 0 < e < len(req.prompt) and n_before < e:
                     budget = min(budget, e - n_before)     # stop exactly at the boundary
             with trace.span("engine", "prefill_chunk", budget=int(budget), cached=int(n_before)):
@@ -543,7 +544,7 @@ class Engine:
                 # at a frontier boundary is one more unit than the projection counted)
                 req.service.consume(1)
             self.stats.prompt_tokens += req.lane.n_cached - n_before
-            if first is None and req.lane.n_cached == edge and n_before < edge:
+            if first is None and req.lane.n_cached in shared_edges and n_before < req.lane.n_cached:
                 self.program.checkpoint(req.lane, "shared", "shared")   # any session may start from here
             if first is None and req.lane.n_cached == replay and n_before < replay:
                 # the history up to, not including, the generation opener: a request that asks for this

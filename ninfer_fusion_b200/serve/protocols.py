@@ -52,6 +52,55 @@ def sse(data, event: Optional[str] = None) -> bytes:
 
 
 # =========================================================================================================
+# Prompt-cache hints
+# =========================================================================================================
+def _openai_cache_hints(body: dict, msgs: List[dict]) -> dict:
+    """OpenAI prompt caching (`prompt_cache_options`, `prompt_cache_breakpoint` on messages or content parts,
+    `prompt_cache_key`, `prompt_cache_retention`) as write candidates for the shared-prefix catalogue.  The fields are
+    optimisation hints: they are validated, never change the prompt, and promise no wall-clock residency."""
+    out = {"cache_implicit": True, "cache_breakpoints": [], "cache_key": None, "cache_retention": None}
+    po = body.get("prompt_cache_options")
+    if po is not None:
+        if not isinstance(po, dict) or po.get("mode", "implicit") not in ("implicit", "explicit"):
+            raise BadRequest("prompt_cache_options.mode must be 'implicit' or 'explicit'", "prompt_cache_options")
+        out["cache_implicit"] = po.get("mode", "implicit") == "implicit"
+    key = body.get("prompt_cache_key")
+    if key is not None:
+        if not isinstance(key, str) or len(key) > 512:
+            raise BadRequest("prompt_cache_key must be a string of at most 512 characters", "prompt_cache_key")
+        out["cache_key"] = key
+    ret = body.get("prompt_cache_retention")
+    if ret is not None:
+        if ret not in ("in_memory", "24h"):
+            raise BadRequest("prompt_cache_retention must be 'in_memory' or '24h'", "prompt_cache_retention")
+        out["cache_retention"] = ret
+
+    def marked(obj) -> bool:
+        bp = obj.get("prompt_cache_breakpoint") if isinstance(obj, dict) else None
+        if bp is None:
+            return False
+        if not isinstance(bp, dict) or bp.get("mode", "explicit") != "explicit":
+            raise BadRequest("prompt_cache_breakpoint.mode must be 'explicit'", "prompt_cache_breakpoint")
+        return True
+    for i, m in enumerate(msgs):
+        parts = m.get("content") if isinstance(m.get("content"), list) else []
+        if marked(m) or any(marked(p) for p in parts):
+            out["cache_breakpoints"].append(i)
+    return out
+
+
+def _anthropic_cache_marked(obj) -> bool:
+    cc = obj.get("cache_control") if isinstance(obj, dict) else None
+    if cc is None:
+        return False
+    if not isinstance(cc, dict) or cc.get("type") != "ephemeral":
+        raise BadRequest("cache_control.type must be 'ephemeral'", "cache_control")
+    if cc.get("ttl") not in (None, "5m", "1h"):
+        raise BadRequest("cache_control.ttl must be '5m' or '1h'", "cache_control")
+    return True
+
+
+# =========================================================================================================
 # OpenAI chat completions
 # =========================================================================================================
 def parse_openai_chat(body: dict) -> Tuple[GenRequest, dict]:
@@ -75,7 +124,7 @@ def parse_openai_chat(body: dict) -> Tuple[GenRequest, dict]:
                      presence_penalty=_num(body, "presence_penalty", -2.0, 2.0),
                      frequency_penalty=_num(body, "frequency_penalty", -2.0, 2.0),
                      seed=_num(body, "seed", 0, 2 ** 63 - 1, int), stop=_stops(body.get("stop")),
-                     enable_thinking=thinking, session=body.get("user"))
+                     enable_thinking=thinking, session=body.get("user"), **_openai_cache_hints(body, msgs))
     opts = {"stream": bool(body.get("stream", False)),
             "include_usage": bool((body.get("stream_options") or {}).get("include_usage", False))}
     return req, opts
@@ -83,7 +132,8 @@ def parse_openai_chat(body: dict) -> Tuple[GenRequest, dict]:
 
 def _usage_openai(res: GenResult) -> dict:
     return {"prompt_tokens": res.prompt_tokens, "completion_tokens": res.completion_tokens,
-            "total_tokens": res.prompt_tokens + res.completion_tokens}
+            "total_tokens": res.prompt_tokens + res.completion_tokens,
+            "prompt_tokens_details": {"cached_tokens": int(getattr(res, "cached_tokens", 0) or 0)}}
 
 
 def _finish_openai(reason: str) -> str:
@@ -181,7 +231,8 @@ def parse_openai_responses(body: dict, store: Optional[dict] = None) -> Tuple[Ge
     reasoning = body.get("reasoning") or {}
     req = GenRequest(messages=msgs, tools=tools, max_tokens=int(body.get("max_output_tokens") or 512),
                      temperature=_num(body, "temperature", 0.0, 2.0), top_p=_num(body, "top_p", 0.0, 1.0),
-                     enable_thinking=reasoning.get("effort", "medium") not in ("none", "minimal"))
+                     enable_thinking=reasoning.get("effort", "medium") not in ("none", "minimal"),
+                     **_openai_cache_hints(body, msgs))
     return req, {"stream": bool(body.get("stream", False)), "store": bool(body.get("store", True)), "messages": msgs}
 
 
@@ -201,7 +252,8 @@ def openai_responses_object(res: GenResult, model: str, status: str = "completed
             "status": "incomplete" if incomplete else status, "incomplete_details": incomplete, "model": model,
             "output": out, "output_text": res.content,
             "usage": {"input_tokens": res.prompt_tokens, "output_tokens": res.completion_tokens,
-                      "total_tokens": res.prompt_tokens + res.completion_tokens}}
+                      "total_tokens": res.prompt_tokens + res.completion_tokens,
+                      "input_tokens_details": {"cached_tokens": int(getattr(res, "cached_tokens", 0) or 0)}}}
 
 
 def openai_responses_stream(events: Iterator[tuple], model: str, on_done=None) -> Iterator[bytes]:
@@ -281,9 +333,12 @@ def parse_anthropic_messages(body: dict) -> Tuple[GenRequest, dict]:
     if "max_tokens" not in body:
         raise BadRequest("max_tokens is required", "max_tokens")
     msgs: List[dict] = []
+    breakpoints: List[int] = []
     system = body.get("system")
     if system:
         if isinstance(system, list):
+            if any(_anthropic_cache_marked(b) for b in system):
+                breakpoints.append(0)
             system = "".join(b.get("text", "") for b in system)
         msgs.append({"role": "system", "content": system})
     raw = body.get("messages")
@@ -293,6 +348,9 @@ def parse_anthropic_messages(body: dict) -> Tuple[GenRequest, dict]:
         if m.get("role") not in ("user", "assistant"):
             raise BadRequest("message role must be user or assistant", "messages")
         msgs.extend(_anthropic_blocks_to_messages(m["role"], m.get("content")))
+        blocks = m.get("content") if isinstance(m.get("content"), list) else []
+        if any(_anthropic_cache_marked(b) for b in blocks):
+            breakpoints.append(len(msgs) - 1)     # the boundary sits after the last message this turn produced
     tools = None
     if body.get("tools"):
         tools = [{"type": "function", "function": {"name": t.get("name"), "description": t.get("description", ""),
@@ -301,7 +359,7 @@ def parse_anthropic_messages(body: dict) -> Tuple[GenRequest, dict]:
     req = GenRequest(messages=msgs, tools=tools, max_tokens=int(body["max_tokens"]),
                      temperature=_num(body, "temperature", 0.0, 1.0), top_p=_num(body, "top_p", 0.0, 1.0),
                      top_k=_num(body, "top_k", 1, 20, int), stop=_stops(body.get("stop_sequences")),
-                     enable_thinking=thinking)
+                     enable_thinking=thinking, cache_breakpoints=breakpoints)
     return req, {"stream": bool(body.get("stream", False))}
 
 
@@ -329,7 +387,10 @@ def anthropic_message_response(res: GenResult, model: str) -> dict:
         content.append({"type": "tool_use", "id": f"toolu_{uuid.uuid4().hex[:24]}", "name": c.name, "input": inp})
     return {"id": f"msg_{res.request_id}", "type": "message", "role": "assistant", "model": model, "content": content,
             "stop_reason": _stop_reason_anthropic(res.finish_reason), "stop_sequence": None,
-            "usage": {"input_tokens": res.prompt_tokens, "output_tokens": res.completion_tokens}}
+            # Anthropic counts cached reads apart from the computed input
+            "usage": {"input_tokens": res.prompt_tokens - int(getattr(res, "cached_tokens", 0) or 0),
+                      "cache_read_input_tokens": int(getattr(res, "cached_tokens", 0) or 0),
+                      "cache_creation_input_tokens": 0, "output_tokens": res.completion_tokens}}
 
 
 def anthropic_stream(events: Iterator[tuple], model: str, prompt_tokens_hint: int = 0) -> Iterator[bytes]:

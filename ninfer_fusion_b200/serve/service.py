@@ -42,6 +42,15 @@ class GenRequest:
     queue_timeout_s: Optional[float] = None
     deadline_s: Optional[float] = None
     session: Optional[str] = None
+    # prompt-cache hints (OpenAI prompt_cache_options / prompt_cache_breakpoint, Anthropic cache_control): whether the
+    # automatic shared-prefix candidate is written, and the messages after which the client asked for a boundary
+    cache_implicit: bool = True
+    cache_breakpoints: Sequence[int] = ()      # indices into `messages`; a boundary sits after that message
+    cache_key: Optional[str] = None            # accepted client hint; not a session key, not a prefix identity
+    cache_retention: Optional[str] = None      # accepted; residency follows the engine's retention classes
+
+
+MAX_CACHE_WRITES = 4     # distinct shared-prefix write candidates one request may carry
 
 
 @dataclass
@@ -133,6 +142,35 @@ class GenerationService:
             return 0
         return n
 
+    def shared_prefix_edges(self, req: GenRequest, ids: Sequence[int]) -> List[int]:
+        """Token frontiers this request may publish in the shared-prefix catalogue, ascending: the implicit candidate
+        (the leading system block, unless the client switched implicit writes off) and the latest explicit
+        breakpoints, at most MAX_CACHE_WRITES distinct ones.  A breakpoint whose rendered history is not an exact
+        token prefix of the prompt is ignored: the hints never change the prompt."""
+        edges = set()
+        if req.cache_implicit:
+            n = self.shared_prefix_tokens(req, ids)
+            if n:
+                edges.add(n)
+        explicit: List[int] = []
+        if req.messages:
+            for i in sorted({int(b) for b in req.cache_breakpoints if 0 <= int(b) < len(req.messages)}):
+                text = render_chat(req.messages[: i + 1], req.tools, add_generation_prompt=False,
+                                   enable_thinking=req.enable_thinking)
+                head = self.tok.encode(text)
+                n = len(head)
+                if self.min_shared_prefix_tokens <= n < len(ids) and list(ids[:n]) == head:
+                    explicit.append(n)
+        room = MAX_CACHE_WRITES - len(edges)
+        for n in explicit[::-1]:                      # the latest boundaries win the remaining slots
+            if n in edges:
+                continue
+            if room <= 0:
+                break
+            edges.add(n)
+            room -= 1
+        return sorted(edges)
+
     def replay_edge_tokens(self, req: GenRequest, ids: Sequence[int]) -> int:
         """Tokens of the rendered history without the generation opener (what the template appends to make the model
         answer): the frontier a regenerated response restarts from.  0 when the prompt is not a chat or the opener
@@ -181,7 +219,9 @@ class GenerationService:
             opts = self._options(req)
             opts.media = media
             if media is None:
-                opts.shared_prefix_tokens = self.shared_prefix_tokens(req, ids)
+                edges = self.shared_prefix_edges(req, ids)
+                opts.shared_prefix_edges = tuple(edges)
+                opts.shared_prefix_tokens = edges[0] if edges else 0
                 opts.replay_edge_tokens = self.replay_edge_tokens(req, ids)
             handle = self.engine.submit(ids, opts)
             dec = StreamDecoder(self.tok, skip_special=True)

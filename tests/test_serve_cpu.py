@@ -350,3 +350,50 @@ def test_artifact_diff(tmp_path, capsys):
     assert changed and all(l["formats"] == ["BF16", "W8G32_F16S"] and 0 < l["relative"] < 0.02 for l in changed)
     assert cli.main(["diff", a, c, "--tolerance", "0.02"]) == 0            # within the int8 envelope
     capsys.readouterr()
+
+
+def test_prompt_cache_hints_are_validated_and_become_write_candidates():
+    from ninfer_fusion_b200.serve import protocols as P
+    msgs = [{"role": "system", "content": "s" * 10},
+            {"role": "user", "content": [{"type": "text", "text": "doc", "prompt_cache_breakpoint": {"mode": "explicit"}}]},
+            {"role": "assistant", "content": "ok"},
+            {"role": "user", "content": "q", "prompt_cache_breakpoint": {"mode": "explicit"}}]
+    req, _ = P.parse_openai_chat({"messages": msgs, "prompt_cache_options": {"mode": "explicit"},
+                                  "prompt_cache_key": "tenant-7", "prompt_cache_retention": "24h"})
+    assert req.cache_implicit is False and list(req.cache_breakpoints) == [1, 3]
+    assert req.cache_key == "tenant-7" and req.cache_retention == "24h" and req.session is None   # the key is not a session
+    req, _ = P.parse_openai_chat({"messages": msgs[:1] + [{"role": "user", "content": "q"}]})
+    assert req.cache_implicit is True and list(req.cache_breakpoints) == []
+    for bad in ({"prompt_cache_options": {"mode": "always"}}, {"prompt_cache_options": "implicit"},
+                {"prompt_cache_retention": "7d"}, {"prompt_cache_key": 5}):
+        with pytest.raises(P.BadRequest):
+            P.parse_openai_chat(dict({"messages": msgs}, **bad))
+    with pytest.raises(P.BadRequest):
+        P.parse_openai_chat({"messages": [{"role": "user", "content": "q", "prompt_cache_breakpoint": {"mode": "implicit"}}]})
+    # Anthropic cache_control marks the same kind of boundary
+    areq, _ = P.parse_anthropic_messages({
+        "max_tokens": 8, "system": [{"type": "text", "text": "be brief", "cache_control": {"type": "ephemeral"}}],
+        "messages": [{"role": "user", "content": [{"type": "text", "text": "long doc", "cache_control": {"type": "ephemeral", "ttl": "1h"}}]},
+                     {"role": "assistant", "content": "ok"}, {"role": "user", "content": "q"}]})
+    assert list(areq.cache_breakpoints) == [0, 1]
+    with pytest.raises(P.BadRequest):
+        P.parse_anthropic_messages({"max_tokens": 8, "messages": [{"role": "user", "content": [
+            {"type": "text", "text": "x", "cache_control": {"type": "persistent"}}]}]})
+
+
+def test_explicit_breakpoints_publish_shared_prefixes_and_usage_reports_cached_tokens(server):
+    port, svc, _ = server
+    doc = "The quarterly report lists seventeen regional offices and their budgets. " * 6
+    base = [{"role": "user", "content": [{"type": "text", "text": doc, "prompt_cache_breakpoint": {"mode": "explicit"}}]},
+            {"role": "assistant", "content": "Noted."}]
+    st, _, data = call(port, "POST", "/v1/chat/completions",
+                       {"messages": base + [{"role": "user", "content": "How many offices?"}], "max_tokens": 2,
+                        "prompt_cache_options": {"mode": "explicit"}})
+    assert st == 200 and json.loads(data)["usage"]["prompt_tokens_details"]["cached_tokens"] == 0
+    published = svc.engine.program.shared_stats["published"] if hasattr(svc.engine.program, "shared_stats") else None
+    # another client, another question, same document: the explicit boundary after the document message is a read hit
+    st, _, data = call(port, "POST", "/v1/chat/completions",
+                       {"messages": base + [{"role": "user", "content": "Which office is largest?"}], "max_tokens": 2})
+    usage = json.loads(data)["usage"]
+    assert st == 200 and usage["prompt_tokens_details"]["cached_tokens"] >= 32 and usage["prompt_tokens"] > usage["prompt_tokens_details"]["cached_tokens"]
+    assert published is None or svc.engine.program.shared_stats["hits"] >= 1
