@@ -557,8 +557,17 @@ def cmd_serve(args) -> int:
     engine = build_engine(args, cfg, weights, ranks)
     if engine is None:
         return 0     # a follower rank
+    timeout_s = args.queue_timeout if args.pending_timeout_ms is None else args.pending_timeout_ms / 1e3
     svc = GenerationService(engine, tok, args.served_model_name or name, max_concurrent=args.max_concurrent,
-                            queue_timeout_s=args.queue_timeout)
+                            queue_timeout_s=timeout_s)
+    engine.max_pending = max(0, int(args.max_pending_requests))
+    svc.sampling_overrides = {k: getattr(args, k) for k in ("temperature", "top_p", "top_k", "min_p", "presence_penalty",
+                                                            "frequency_penalty") if getattr(args, k, None) is not None}
+    svc.force_greedy, svc.prefix_reuse = bool(args.greedy), not args.no_prefix_reuse
+    svc.media_threads = max(1, int(args.media_preprocess_threads))
+    if args.sampling_seed is not None:
+        svc.fixed_seed = int(args.sampling_seed)
+    apply_retention_options(engine, args)
     relayout = None
     if args.kv_auto_relayout > 0:
         if not str(args.device).startswith("cuda") or args.spec not in ("none", "off"):
@@ -575,7 +584,12 @@ def cmd_serve(args) -> int:
         t0 = time.perf_counter()
         svc.generate(GenRequest(prompt="warm-up", max_tokens=int(args.warmup), temperature=0.0))
         print(json.dumps({"warmup_s": round(time.perf_counter() - t0, 3)}), file=sys.stderr, flush=True)
-    httpd = serve(svc, args.host, args.port, args.api_key, args.request_log)
+    httpd = serve(svc, args.host, args.port, args.api_key, args.request_log,
+                  max_stored_responses=args.response_store_max_records,
+                  max_stored_bytes=int(args.response_store_max_mib * (1 << 20)),
+                  max_body_bytes=int(args.max_request_mib * (1 << 20)), cors=args.cors,
+                  log_interval_s=args.log_stats_interval_ms / 1e3,
+                  default_max_tokens=args.default_max_tokens or None, default_thinking=not args.no_thinking)
     print(f"ninfer-serve: {name} on http://{args.host}:{httpd.server_address[1]}", file=sys.stderr, flush=True)
     try:
         httpd.serve_forever()
@@ -585,6 +599,24 @@ def cmd_serve(args) -> int:
         httpd.server_close()
         _shutdown(engine)
     return 0
+
+
+def apply_retention_options(engine: Engine, args) -> None:
+    """Catalogue capacities of the server's option table, applied to the engine's Program (and to every Program a
+    recover() or a storage reload builds later: the factory is wrapped)."""
+    def apply(prog):
+        if getattr(args, "max_private_continuations", 0) > 0 and hasattr(prog, "max_checkpoints"):
+            prog.max_checkpoints = int(args.max_private_continuations)
+        if getattr(args, "max_shared_prefixes", 0) > 0 and hasattr(prog, "max_shared_prefixes"):
+            prog.max_shared_prefixes = int(args.max_shared_prefixes)
+        if getattr(args, "max_long_anchors_per_continuation", 0) > 0 and hasattr(prog, "max_anchors"):
+            prog.max_anchors = int(args.max_long_anchors_per_continuation)
+        if getattr(args, "host_kv_mib", 0.0) > 0 and hasattr(prog, "host_budget_bytes"):
+            prog.host_budget_bytes = int(args.host_kv_mib * (1 << 20))
+        return prog
+    apply(engine.program)
+    inner = engine._factory
+    engine._factory = lambda: apply(inner())
 
 
 def _shutdown(engine: Engine) -> None:
@@ -782,7 +814,29 @@ def main(argv=None) -> int:
     s.add_argument("--served-model-name", default=None)
     s.add_argument("--max-concurrent", type=int, default=64)
     s.add_argument("--queue-timeout", type=float, default=30.0)
-    s.add_argument("--request-log", default=None, help="JSONL request log path")
+    s.add_argument("--request-log", "--request-log-jsonl", dest="request_log", default=None, help="JSONL request log path")
+    s.add_argument("--model-id", dest="served_model_name", default=None, help="public model alias (same as --served-model-name)")
+    s.add_argument("--max-pending-requests", type=int, default=256, help="requests that may wait for admission; more get 429")
+    s.add_argument("--pending-timeout-ms", type=float, default=None,
+                   help="longest wait for admission in milliseconds, then 503 request_queue_timeout (same as --queue-timeout in seconds)")
+    s.add_argument("--log-stats-interval-ms", type=float, default=5000.0, help="throughput record interval; 0 disables it")
+    s.add_argument("--max-request-mib", type=float, default=32.0, help="body-size limit before JSON parsing")
+    s.add_argument("--response-store-max-records", type=int, default=512, help="locally retained Responses objects")
+    s.add_argument("--response-store-max-mib", type=float, default=256.0, help="total bytes of the local Responses store")
+    s.add_argument("--media-preprocess-threads", type=int, default=4, help="media decoding / resizing workers")
+    s.add_argument("--default-max-tokens", type=int, default=0, help="output limit of a request that names none (0: the protocol's own default)")
+    s.add_argument("--no-thinking", action="store_true", help="thinking off for requests that do not say")
+    s.add_argument("--no-prefix-reuse", action="store_true", help="no session continuations, shared prefixes or replay frontiers")
+    s.add_argument("--max-private-continuations", type=int, default=0, help="retained private frontiers (0: twice the lanes)")
+    s.add_argument("--max-shared-prefixes", type=int, default=0, help="shared stable-prefix catalogue size (0: 8)")
+    s.add_argument("--max-long-anchors-per-continuation", type=int, default=0, help="long anchors kept per session (0: 3)")
+    s.add_argument("--host-kv-mib", type=float, default=0.0, help="pinned host budget for frontiers pushed out of the device pool")
+    s.add_argument("--cors", action="store_true", help="permissive browser CORS headers")
+    for flag, typ in (("temperature", float), ("top-p", float), ("top-k", int), ("min-p", float),
+                      ("presence-penalty", float), ("frequency-penalty", float)):
+        s.add_argument(f"--{flag}", type=typ, default=None, help=f"process-level {flag} default (a request's own value wins)")
+    s.add_argument("--greedy", action="store_true", help="exact arg-max for every request")
+    s.add_argument("--sampling-seed", type=int, default=None, help="seed of requests that give none (default: 0)")
     s.add_argument("--warmup", type=int, default=8, help="tokens of one warm-up generation before the port opens (0 = none)")
     s.set_defaults(fn=cmd_serve)
     i = sub.add_parser("inspect", help="print an artifact's directory")

@@ -62,9 +62,16 @@ class _Keepalive:
 
 class ServeState:
     def __init__(self, service: GenerationService, api_key: Optional[str] = None, log_path: Optional[str] = None,
-                 max_body_bytes: int = 32 << 20, max_stored_responses: int = 512):
+                 max_body_bytes: int = 32 << 20, max_stored_responses: int = 512, max_stored_bytes: int = 256 << 20,
+                 cors: bool = False, log_interval_s: float = 5.0, default_max_tokens: Optional[int] = None,
+                 default_thinking: bool = True):
         self.service, self.api_key, self.max_body = service, api_key, max_body_bytes
-        self.log = RequestLog(log_path)
+        self.cors = bool(cors)
+        self.default_max_tokens = default_max_tokens       # output limit of a request that names none
+        self.default_thinking = bool(default_thinking)     # thinking mode of a request that names none
+        self.max_stored_bytes = max(1, int(max_stored_bytes))
+        self.stored_bytes = 0
+        self.log = RequestLog(log_path, throughput_every_s=log_interval_s if log_interval_s > 0 else float("inf"))
         # local response store: bounded, the least recently used entry goes first (a stored response keeps its
         # whole message history, so an unbounded store would grow with the server's life)
         self.responses: "OrderedDict[str, dict]" = OrderedDict()
@@ -110,8 +117,21 @@ def make_handler(state: ServeState):
             self.send_header("Content-Length", str(len(data)))
             for k, v in (headers or {}).items():
                 self.send_header(k, v)
+            self._cors_headers()
             self.end_headers()
             self.wfile.write(data)
+
+        def _cors_headers(self) -> None:
+            if state.cors:      # permissive browser access (--cors): any origin may call, the key still applies
+                self.send_header("Access-Control-Allow-Origin", "*")
+                self.send_header("Access-Control-Allow-Headers", "authorization, content-type, x-api-key, anthropic-version")
+                self.send_header("Access-Control-Allow-Methods", "GET, POST, DELETE, OPTIONS")
+
+        def do_OPTIONS(self):
+            self.send_response(204 if state.cors else 405)
+            self._cors_headers()
+            self.send_header("Content-Length", "0")
+            self.end_headers()
 
         def _error(self, code: int, message: str, etype: str = "invalid_request_error", param=None, ecode=None,
                    anthropic: bool = False) -> None:
@@ -152,6 +172,7 @@ def make_handler(state: ServeState):
             self.send_header("Content-Type", "text/event-stream")
             self.send_header("Cache-Control", "no-cache")
             self.send_header("Connection", "close")
+            self._cors_headers()
             self.end_headers()
             self.close_connection = True
             try:
@@ -279,7 +300,10 @@ def make_handler(state: ServeState):
             if path.startswith("/v1/responses/"):
                 rid = path[len("/v1/responses/"):]
                 with state.lock:
-                    found = state.responses.pop(rid, None) is not None
+                    gone = state.responses.pop(rid, None)
+                    found = gone is not None
+                    if found:
+                        state.stored_bytes -= gone.get("_bytes", 0)
                 if found:
                     return self._send_json(200, {"id": rid, "object": "response", "deleted": True})
                 return self._error(404, f"response '{rid}' not found", "not_found_error")
@@ -292,6 +316,13 @@ def make_handler(state: ServeState):
                 return self._error(401, "invalid API key", "authentication_error", anthropic=anthropic)
             try:
                 body = self._body()
+                if state.default_max_tokens and not anthropic:
+                    key = "max_output_tokens" if path.startswith("/v1/responses") else "max_tokens"
+                    if body.get(key) is None and body.get("max_completion_tokens") is None:
+                        body[key] = int(state.default_max_tokens)
+                if not state.default_thinking and path == "/v1/chat/completions" and "enable_thinking" not in body \
+                        and "enable_thinking" not in (body.get("chat_template_kwargs") or {}):
+                    body["enable_thinking"] = False
                 if path == "/v1/chat/completions":
                     req, o = P.parse_openai_chat(body)
                     return self._run("openai_chat", req, o["stream"], lambda r: P.openai_chat_response(r, svc.model_id),
@@ -306,11 +337,18 @@ def make_handler(state: ServeState):
                             rec = dict(obj)
                             rec["_input"] = o["messages"]
                             rec["_messages"] = o["messages"] + [{"role": "assistant", "content": res.content}]
+                            rec["_bytes"] = len(json.dumps(rec, ensure_ascii=False))
                             with state.lock:
+                                old = state.responses.pop(obj["id"], None)
+                                if old is not None:
+                                    state.stored_bytes -= old.get("_bytes", 0)
                                 state.responses[obj["id"]] = rec
-                                state.responses.move_to_end(obj["id"])
-                                while len(state.responses) > state.max_stored_responses:
-                                    state.responses.popitem(last=False)
+                                state.stored_bytes += rec["_bytes"]
+                                # two bounds: records and bytes (a stored response keeps its whole message history)
+                                while len(state.responses) > 1 and (len(state.responses) > state.max_stored_responses
+                                                                    or state.stored_bytes > state.max_stored_bytes):
+                                    _, gone = state.responses.popitem(last=False)
+                                    state.stored_bytes -= gone.get("_bytes", 0)
 
                     def build(res: GenResult):
                         obj = P.openai_responses_object(res, svc.model_id)
@@ -355,9 +393,11 @@ def make_handler(state: ServeState):
 
 
 def serve(service: GenerationService, host: str = "127.0.0.1", port: int = 8080, api_key: Optional[str] = None,
-          log_path: Optional[str] = None, max_stored_responses: int = 512) -> ThreadingHTTPServer:
-    """Builds the server (not yet serving): call `.serve_forever()` or run it in a thread; `.shutdown()` stops it."""
-    state = ServeState(service, api_key, log_path, max_stored_responses=max_stored_responses)
+          log_path: Optional[str] = None, max_stored_responses: int = 512, **state_options) -> ThreadingHTTPServer:
+    """Builds the server (not yet serving): call `.serve_forever()` or run it in a thread; `.shutdown()` stops it.
+    `state_options`: ServeState's further settings (max_body_bytes, max_stored_bytes, cors, log_interval_s,
+    default_max_tokens, default_thinking)."""
+    state = ServeState(service, api_key, log_path, max_stored_responses=max_stored_responses, **state_options)
     httpd = ThreadingHTTPServer((host, port), make_handler(state))
     httpd.daemon_threads = True
     httpd.state = state  # type: ignore[attr-defined]

@@ -92,6 +92,12 @@ class GenerationService:
         self.auto_shared_prefix = True    # publish the leading system block of chat prompts in the shared-prefix catalogue
         self.min_shared_prefix_tokens = 32
         self.allow_media_files = False    # local paths in media parts (CLI use); gateways leave this off
+        # process-level settings of the server's option table
+        self.sampling_overrides: Dict[str, float] = {}   # replace the registered sampler defaults; a request's own value still wins
+        self.force_greedy = False         # exact arg-max for every request, whatever it asks for
+        self.fixed_seed: Optional[int] = None   # seed of requests that give none (default: a fresh one per request)
+        self.prefix_reuse = True          # off: no session continuations, no shared prefixes, no replay frontiers
+        self.media_threads = 4
 
     # ------------------------------------------------------------------ prompt side
     def prepare(self, req: GenRequest) -> List[int]:
@@ -113,7 +119,7 @@ class GenerationService:
                 try:
                     if self.media_pool is None:
                         from ..runtime.worker_pool import HostWorkerPool
-                        self.media_pool = HostWorkerPool(threads=4, queue_capacity=16)
+                        self.media_pool = HostWorkerPool(threads=self.media_threads, queue_capacity=16)
                     pm = M.prepare_messages(self.tok, text, req.messages, self.media, allow_files=self.allow_media_files,
                                             pool=self.media_pool)
                 except (ValueError, OSError) as e:
@@ -189,10 +195,15 @@ class GenerationService:
 
     def _options(self, req: GenRequest) -> RequestOptions:
         d = dict(DEFAULT_SAMPLING[bool(req.enable_thinking)])
+        d.update(self.sampling_overrides)
+        if self.fixed_seed is not None:
+            d["seed"] = self.fixed_seed
         for k in ("temperature", "top_p", "top_k", "min_p", "presence_penalty", "frequency_penalty", "seed"):
             v = getattr(req, k)
             if v is not None:
                 d[k] = v
+        if self.force_greedy:
+            d.update(temperature=0.0, top_k=1)
         sp = SamplingParams(temperature=float(d.get("temperature", 0.0)), top_k=int(d.get("top_k", 20)),
                             top_p=float(d.get("top_p", 1.0)), min_p=float(d.get("min_p", 0.0)),
                             presence_penalty=float(d.get("presence_penalty", 0.0)),
@@ -200,7 +211,7 @@ class GenerationService:
         return RequestOptions(max_tokens=max(1, int(req.max_tokens)), sampling=sp, stop_token_ids=tuple(self.eos_ids),
                               deadline_s=req.deadline_s,
                               pending_timeout_s=req.queue_timeout_s if req.queue_timeout_s is not None else self.queue_timeout_s,
-                              session=req.session)
+                              session=req.session if self.prefix_reuse else None)
 
     # ------------------------------------------------------------------ generation
     def stream(self, req: GenRequest, on_start: Optional[Callable[[str, int], None]] = None,
@@ -218,7 +229,7 @@ class GenerationService:
                 on_start(rid, len(ids))
             opts = self._options(req)
             opts.media = media
-            if media is None:
+            if media is None and self.prefix_reuse:
                 edges = self.shared_prefix_edges(req, ids)
                 opts.shared_prefix_edges = tuple(edges)
                 opts.shared_prefix_tokens = edges[0] if edges else 0

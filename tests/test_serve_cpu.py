@@ -397,3 +397,68 @@ def test_explicit_breakpoints_publish_shared_prefixes_and_usage_reports_cached_t
     usage = json.loads(data)["usage"]
     assert st == 200 and usage["prompt_tokens_details"]["cached_tokens"] >= 32 and usage["prompt_tokens"] > usage["prompt_tokens_details"]["cached_tokens"]
     assert published is None or svc.engine.program.shared_stats["hits"] >= 1
+
+
+def test_server_option_table_process_settings(tmp_path):
+    """The process-level settings of the server's option table: sampler defaults and forced arg-max, default output
+    budget and thinking mode, prefix reuse off, CORS, body-size limit, the response store's record and byte bounds,
+    catalogue capacities applied to every Program the engine builds."""
+    cfg = TINY_DENSE
+    w = random_weights(cfg, "cpu", seed=3, std=0.05)
+    tok = Tokenizer.train_toy(cli.DEFAULT_CORPUS, 200, cli.SPECIAL_TOKENS)
+    engine = Engine(lambda: ReferenceProgram(cfg, w, max_lanes=2, max_context=256), prefill_chunk=64)
+    svc = GenerationService(engine, tok, "tiny-dense:test", max_concurrent=2, queue_timeout_s=20.0)
+    from ninfer_fusion_b200.serve.service import GenRequest
+    # sampler: registered default < process override < the request's own value; --greedy beats all
+    svc.sampling_overrides = {"temperature": 0.3, "top_k": 7}
+    sp = svc._options(GenRequest(prompt="x")).sampling
+    assert sp.temperature == 0.3 and sp.top_k == 7
+    assert svc._options(GenRequest(prompt="x", temperature=0.9)).sampling.temperature == 0.9
+    svc.fixed_seed = 1234
+    assert svc._options(GenRequest(prompt="x")).sampling.seed == 1234 and svc._options(GenRequest(prompt="x", seed=5)).sampling.seed == 5
+    svc.force_greedy = True
+    sp = svc._options(GenRequest(prompt="x", temperature=0.9)).sampling
+    assert sp.temperature == 0.0 and sp.top_k == 1
+    svc.prefix_reuse = False
+    assert svc._options(GenRequest(prompt="x", session="s")).session is None
+    # catalogue capacities survive a recover()
+    import argparse
+    cli.apply_retention_options(engine, argparse.Namespace(max_private_continuations=3, max_shared_prefixes=2,
+                                                           max_long_anchors_per_continuation=1, host_kv_mib=1.5))
+    for _ in range(2):
+        p = engine.program
+        assert (p.max_checkpoints, p.max_shared_prefixes, p.max_anchors, p.host_budget_bytes) == (3, 2, 1, int(1.5 * (1 << 20)))
+        engine.program = engine._factory()
+    httpd = serve(svc, "127.0.0.1", 0, api_key=None, log_path=None, max_stored_responses=100, max_stored_bytes=2500,
+                  max_body_bytes=4096, cors=True, log_interval_s=0, default_max_tokens=2, default_thinking=False)
+    t = threading.Thread(target=httpd.serve_forever, daemon=True)
+    t.start()
+    port = httpd.server_address[1]
+    try:
+        c = http.client.HTTPConnection("127.0.0.1", port, timeout=60)
+        c.request("OPTIONS", "/v1/chat/completions", None, {"Origin": "http://localhost:3000"})
+        r = c.getresponse()
+        r.read()
+        assert r.status == 204 and r.getheader("Access-Control-Allow-Origin") == "*"
+        c.request("GET", "/health")
+        r = c.getresponse()
+        r.read()
+        assert r.status == 200 and r.getheader("Access-Control-Allow-Origin") == "*"
+        c.close()
+        st, _, data = call(port, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}]}, key=None)
+        assert st == 200 and json.loads(data)["usage"]["completion_tokens"] <= 2           # --default-max-tokens 2
+        st, _, data = call(port, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "x" * 5000}]}, key=None)
+        assert st == 413 or (st == 400 and b"large" in data.lower())                          # --max-request-mib
+        ids = []
+        for i in range(4):
+            st, _, data = call(port, "POST", "/v1/responses", {"input": f"question number {i} " + "pad " * 40, "max_output_tokens": 1}, key=None)
+            assert st == 200
+            ids.append(json.loads(data)["id"])
+        state = httpd.state
+        assert 1 <= len(state.responses) < 4 and state.stored_bytes <= max(2500, max(r["_bytes"] for r in state.responses.values()))
+        assert call(port, "GET", f"/v1/responses/{ids[-1]}", key=None)[0] == 200 and call(port, "GET", f"/v1/responses/{ids[0]}", key=None)[0] == 404
+        assert call(port, "DELETE", f"/v1/responses/{ids[-1]}", key=None)[0] == 200 and state.stored_bytes == sum(r["_bytes"] for r in state.responses.values())
+    finally:
+        httpd.shutdown()
+        httpd.server_close()
+        engine.shutdown()
