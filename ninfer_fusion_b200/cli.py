@@ -506,7 +506,8 @@ def cmd_generate(args) -> int:
         return 0     # a follower rank: it executed the leader's steps until told to stop
     svc = GenerationService(engine, tok, name)
     req = GenRequest(max_tokens=args.max_tokens, temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
-                     seed=args.seed, enable_thinking=not args.no_think, stop=args.stop or ())
+                     seed=args.seed, enable_thinking=not args.no_think, stop=args.stop or (),
+                     thinking_budget=args.thinking_budget or None)
     if args.prompt_ids:
         req.prompt_ids = [int(v) for v in args.prompt_ids.split(",")]
     elif args.messages_json:
@@ -565,6 +566,7 @@ def cmd_serve(args) -> int:
                                                             "frequency_penalty") if getattr(args, k, None) is not None}
     svc.force_greedy, svc.prefix_reuse = bool(args.greedy), not args.no_prefix_reuse
     svc.media_threads = max(1, int(args.media_preprocess_threads))
+    svc.default_thinking_budget = int(args.default_thinking_budget) or None
     if args.sampling_seed is not None:
         svc.fixed_seed = int(args.sampling_seed)
     apply_retention_options(engine, args)
@@ -799,7 +801,9 @@ def main(argv=None) -> int:
     g.add_argument("--top-p", type=float, default=None)
     g.add_argument("--top-k", type=int, default=None)
     g.add_argument("--stop", action="append")
-    g.add_argument("--no-think", action="store_true")
+    g.add_argument("--no-think", "--no-thinking", dest="no_think", action="store_true")
+    g.add_argument("--thinking-budget", type=int, default=0,
+                   help="reasoning tokens after which the reasoning frame is closed for the model (0: no cap)")
     g.add_argument("--show-thinking", action="store_true")
     g.add_argument("--print-ids", action="store_true", help="add the completion's token ids to the stats line")
     g.set_defaults(fn=cmd_generate)
@@ -826,6 +830,8 @@ def main(argv=None) -> int:
     s.add_argument("--media-preprocess-threads", type=int, default=4, help="media decoding / resizing workers")
     s.add_argument("--default-max-tokens", type=int, default=0, help="output limit of a request that names none (0: the protocol's own default)")
     s.add_argument("--no-thinking", action="store_true", help="thinking off for requests that do not say")
+    s.add_argument("--default-thinking-budget", type=int, default=0,
+                   help="reasoning-token cap inherited by thinking-enabled requests that name none (0: none)")
     s.add_argument("--no-prefix-reuse", action="store_true", help="no session continuations, shared prefixes or replay frontiers")
     s.add_argument("--max-private-continuations", type=int, default=0, help="retained private frontiers (0: twice the lanes)")
     s.add_argument("--max-shared-prefixes", type=int, default=0, help="shared stable-prefix catalogue size (0: 8)")

@@ -103,6 +103,10 @@ class _Worker:
                 if mine and f is not None:
                     f(self.lanes[msg["lane"]], msg["tokens"])
                 return None, None
+            if op == "force":
+                if mine:
+                    self.inner.force_next_token(self.lanes[msg["lane"]], msg["token"])
+                return None, None
             if op == "close":
                 lane = self.lanes.pop(msg["lane"], None) if mine else None
                 if lane is not None:
@@ -256,6 +260,11 @@ class PartitionedLeader:
         lane.reserved_tokens = int(n_tokens)
         _, errs = self._verb({"op": "reserve", "owner": lane.owner, "lane": lane.lane_id, "tokens": int(n_tokens)})
         _raise_first(errs, "could not reserve the request's pages")
+
+    def force_next_token(self, lane: ProxyLane, token: int) -> None:
+        lane.last_token = int(token)
+        _, errs = self._verb({"op": "force", "owner": lane.owner, "lane": lane.lane_id, "token": int(token)})
+        _raise_first(errs, "could not replace the next token")
 
     def close(self, lane: ProxyLane) -> None:
         if self.lanes.pop(lane.lane_id, None) is None:

@@ -38,7 +38,7 @@ import torch.distributed as dist
 
 from ..runtime.engine import RequestError, ResourceError
 
-OP_STOP, OP_CAN_ADMIT, OP_OPEN, OP_CLOSE, OP_PREFILL, OP_DECODE, OP_CHECKPOINT, OP_PING, OP_DESCENT = range(9)
+OP_STOP, OP_CAN_ADMIT, OP_OPEN, OP_CLOSE, OP_PREFILL, OP_DECODE, OP_CHECKPOINT, OP_PING, OP_DESCENT, OP_FORCE = range(10)
 _DESC_WORDS = 72   # op, count, then up to 64 lane ids / scalar arguments
 _KINDS = ("turn", "endpoint", "replay", "anchor", "shared")
 
@@ -184,6 +184,10 @@ class LeaderProgram:
         self.replicated_stats["steps"] += 1
         return self.inner.decode_round(lanes)
 
+    def force_next_token(self, lane, token: int) -> None:
+        self.ch.send_desc(OP_FORCE, (lane.lane_id, int(token)))
+        self.inner.force_next_token(lane, token)
+
     def checkpoint(self, lane, session, kind: str) -> bool:
         self.ch.send_desc(OP_CHECKPOINT, (lane.lane_id, _KINDS.index(kind)))
         self.ch.bcast_object(session)
@@ -251,6 +255,10 @@ def follower_loop(inner, channel: RankChannel, on_step: Optional[Callable[[int],
             inner.decode_round([inner.lanes[int(i)] for i in a])
         elif op == OP_DESCENT:
             inner.kv_descent_step()
+        elif op == OP_FORCE:
+            lane = inner.lanes.get(int(a[0]))
+            if lane is not None:
+                inner.force_next_token(lane, int(a[1]))
         elif op == OP_CHECKPOINT:
             session = channel.bcast_object()
             inner.checkpoint(inner.lanes[int(a[0])], session, _KINDS[int(a[1])])

@@ -50,6 +50,13 @@ class RequestOptions:
     media: object = None                     # frontend.media.PreparedPrompt for a request with images / videos
     shared_prefix_tokens: int = 0            # publish the first N prompt tokens (system prompt) in the shared catalogue
     shared_prefix_edges: Sequence[int] = ()  # further token frontiers to publish there (explicit cache breakpoints)
+    # thinking budget: after `thinking_budget` tokens inside an open reasoning frame the engine feeds `think_close_ids`
+    # (the frame's closing sequence) instead of what the model sampled, then hands generation back to the model
+    thinking_budget: Optional[int] = None
+    think_open_id: int = -1
+    think_close_id: int = -1
+    think_close_ids: Sequence[int] = ()
+    thinking_open_at_start: bool = False     # the prompt itself leaves a reasoning frame open
     replay_edge_tokens: int = 0              # session frontier before the generation opener (regenerate-this-response point)
 
 
@@ -113,6 +120,8 @@ class GenerationHandle:
         self.decode_host_exposed_s = 0.0
         # draft-verify rounds this request took part in (a speculative program): what was drafted, what was accepted
         self.speculative: Optional[dict] = None
+        self.thinking_budget_applied = False   # the engine closed this request's reasoning frame at its budget
+        self.thinking_tokens = 0
         self._cancel = threading.Event()
 
     def cancel(self) -> None:
@@ -151,6 +160,10 @@ class _Request:
     n_generated: int = 0
     service: Optional[ServiceAccount] = None   # remaining work in quanta (prefill units + tokens to generate)
     borrower: bool = False                     # admitted past a blocked FIFO head
+    thinking: bool = False                     # inside an open reasoning frame
+    think_tokens: int = 0
+    forced: Optional[list] = None              # control tokens still to be fed instead of sampled ones
+    budget_applied: bool = False
 
 
 def resolve_prefill_chunk_mode(cli_value: Optional[str] = None) -> str:
@@ -419,8 +432,37 @@ class Engine:
             self.stats.requests_done += 1
             self._publish(req, Event("done", finish_reason=reason))
 
-    def _commit_token(self, req: _Request, tok: int) -> None:
+    def _control(self, req: _Request, tok: int, last_of_round: bool) -> int:
+        """Thinking budget.  Returns the token that is committed in place of the sampled `tok`: a pending control
+        token when there is one and the sampled token has not been fed yet (it is the round's last), else `tok`."""
+        o = req.opts
+        if o.thinking_budget is None:
+            return tok
+        if req.n_generated == 0:
+            req.thinking = bool(o.thinking_open_at_start)
+        forced = bool(req.forced) and last_of_round
+        if forced:
+            tok = int(req.forced.pop(0))
+            force = getattr(self.program, "force_next_token", None)
+            if force is not None:
+                force(req.lane, tok)          # the sampled token was only a proposal: this one is fed next
+            else:
+                req.lane.last_token = tok
+        if tok == o.think_open_id:
+            req.thinking = True
+        elif tok == o.think_close_id:
+            req.thinking = False
+        elif req.thinking and not forced:
+            req.think_tokens += 1
+            req.handle.thinking_tokens = req.think_tokens
+            if req.think_tokens >= o.thinking_budget and not req.budget_applied and o.think_close_ids:
+                req.forced = [int(t) for t in o.think_close_ids]
+                req.budget_applied = req.handle.thinking_budget_applied = True
+        return tok
+
+    def _commit_token(self, req: _Request, tok: int, last_of_round: bool = True) -> None:
         """Commit-before-publish: budget and stop rules are applied before the token becomes visible."""
+        tok = self._control(req, tok, last_of_round)
         req.n_generated += 1
         self.stats.completion_tokens += 1
         if req.service is not None and req.service.remaining > 0:
@@ -613,10 +655,11 @@ class Engine:
                     per[j] += 1
             # a speculative program returns several tokens per lane and round; each one goes through the
             # same commit-before-publish gate, and nothing after a stop / budget hit becomes visible
-            for tok in (t if isinstance(t, (list, tuple)) else (t,)):
+            seq = t if isinstance(t, (list, tuple)) else (t,)
+            for j, tok in enumerate(seq):
                 if r.state == "finished":
                     break
-                self._commit_token(r, tok)
+                self._commit_token(r, tok, last_of_round=j == len(seq) - 1)
 
     def _worker_loop(self) -> None:
         while True:

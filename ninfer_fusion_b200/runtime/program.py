@@ -475,6 +475,11 @@ class ProgramBase:
             ck.hits += 1
         return lane
 
+    def force_next_token(self, lane: Lane, token: int) -> None:
+        """The token that is fed next on `lane` instead of the one the last step sampled (that one has not been run
+        through the model yet, so replacing it rewrites nothing)."""
+        lane.last_token = int(token)
+
     def close(self, lane: Lane) -> None:
         if self.lanes.pop(lane.lane_id, None) is None:
             return

@@ -773,6 +773,11 @@ class SpeculativeProgram:
 
     speculative_backend = "mtp"
 
+    def force_next_token(self, lane, token: int) -> None:
+        """The next round verifies from `token`; the draft module's first proposal was made for the sampled token and
+        is simply rejected if it no longer fits."""
+        lane.last_token = int(token)
+
     @property
     def draft_window(self) -> int:
         """Drafts per sequence in the round that just ran (the width in force: it moves under the adaptive controller)."""

@@ -118,7 +118,10 @@ def parse_openai_chat(body: dict) -> Tuple[GenRequest, dict]:
     if tools is not None and body.get("tool_choice") == "none":
         tools = None
     max_tokens = body.get("max_completion_tokens", body.get("max_tokens", 512))
-    req = GenRequest(messages=msgs, tools=tools, max_tokens=int(max_tokens),
+    budget = kw.get("thinking_budget", body.get("thinking_budget"))
+    if budget is not None and (not isinstance(budget, int) or isinstance(budget, bool) or budget < 1):
+        raise BadRequest("thinking_budget must be a positive integer", "thinking_budget")
+    req = GenRequest(messages=msgs, tools=tools, max_tokens=int(max_tokens), thinking_budget=budget,
                      temperature=_num(body, "temperature", 0.0, 2.0), top_p=_num(body, "top_p", 0.0, 1.0),
                      top_k=_num(body, "top_k", 1, 20, int), min_p=_num(body, "min_p", 0.0, 1.0),
                      presence_penalty=_num(body, "presence_penalty", -2.0, 2.0),
@@ -355,8 +358,12 @@ def parse_anthropic_messages(body: dict) -> Tuple[GenRequest, dict]:
     if body.get("tools"):
         tools = [{"type": "function", "function": {"name": t.get("name"), "description": t.get("description", ""),
                                                    "parameters": t.get("input_schema", {})}} for t in body["tools"]]
-    thinking = (body.get("thinking") or {}).get("type") == "enabled"
-    req = GenRequest(messages=msgs, tools=tools, max_tokens=int(body["max_tokens"]),
+    th = body.get("thinking") or {}
+    thinking = th.get("type") == "enabled"
+    budget = th.get("budget_tokens") if thinking else None
+    if budget is not None and (not isinstance(budget, int) or isinstance(budget, bool) or budget < 1):
+        raise BadRequest("thinking.budget_tokens must be a positive integer", "thinking")
+    req = GenRequest(messages=msgs, tools=tools, max_tokens=int(body["max_tokens"]), thinking_budget=budget,
                      temperature=_num(body, "temperature", 0.0, 1.0), top_p=_num(body, "top_p", 0.0, 1.0),
                      top_k=_num(body, "top_k", 1, 20, int), stop=_stops(body.get("stop_sequences")),
                      enable_thinking=thinking, cache_breakpoints=breakpoints)

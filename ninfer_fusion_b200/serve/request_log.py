@@ -97,6 +97,9 @@ class RequestLog:
             "speculative": speculative or {"backend": "none", "draft_window": 0, "rounds": 0, "drafted_tokens": 0,
                                            "accepted_tokens": 0, "fallback_steps": 0, "accepted_per_position": []},
             "materialization": None,
+            "thinking_budget": {"budget": getattr(res, "thinking_budget", None),
+                                "applied": bool(getattr(res, "thinking_budget_applied", False)),
+                                "reasoning_tokens": int(getattr(res, "thinking_tokens", 0) or 0)},
         }
         if res.finish_reason == "error":
             fields["error"] = res.error

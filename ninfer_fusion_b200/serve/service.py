@@ -42,6 +42,7 @@ class GenRequest:
     queue_timeout_s: Optional[float] = None
     deadline_s: Optional[float] = None
     session: Optional[str] = None
+    thinking_budget: Optional[int] = None      # reasoning tokens after which the engine closes the reasoning frame
     # prompt-cache hints (OpenAI prompt_cache_options / prompt_cache_breakpoint, Anthropic cache_control): whether the
     # automatic shared-prefix candidate is written, and the messages after which the client asked for a boundary
     cache_implicit: bool = True
@@ -76,6 +77,9 @@ class GenResult:
     decode_device_wait_s: float = 0.0
     decode_host_exposed_s: float = 0.0
     speculative: Optional[dict] = None    # draft-verify counters of this request (None: ordinary decode)
+    thinking_budget: Optional[int] = None
+    thinking_budget_applied: bool = False
+    thinking_tokens: int = 0
 
 
 class GenerationService:
@@ -98,6 +102,9 @@ class GenerationService:
         self.fixed_seed: Optional[int] = None   # seed of requests that give none (default: a fresh one per request)
         self.prefix_reuse = True          # off: no session continuations, no shared prefixes, no replay frontiers
         self.media_threads = 4
+        self.default_thinking_budget: Optional[int] = None   # inherited by thinking-enabled requests that name none
+        # the reasoning frame in token ids (None when the tokenizer has no such tokens: budgets are then ignored)
+        self._think_ids = (tokenizer.token_id("<think>"), tokenizer.token_id("</think>"))
 
     # ------------------------------------------------------------------ prompt side
     def prepare(self, req: GenRequest) -> List[int]:
@@ -208,10 +215,17 @@ class GenerationService:
                             top_p=float(d.get("top_p", 1.0)), min_p=float(d.get("min_p", 0.0)),
                             presence_penalty=float(d.get("presence_penalty", 0.0)),
                             frequency_penalty=float(d.get("frequency_penalty", 0.0)), seed=int(d.get("seed", 0)))
-        return RequestOptions(max_tokens=max(1, int(req.max_tokens)), sampling=sp, stop_token_ids=tuple(self.eos_ids),
+        opts = RequestOptions(max_tokens=max(1, int(req.max_tokens)), sampling=sp, stop_token_ids=tuple(self.eos_ids),
                               deadline_s=req.deadline_s,
                               pending_timeout_s=req.queue_timeout_s if req.queue_timeout_s is not None else self.queue_timeout_s,
                               session=req.session if self.prefix_reuse else None)
+        budget = req.thinking_budget if req.thinking_budget is not None else self.default_thinking_budget
+        open_id, close_id = self._think_ids
+        if budget is not None and budget > 0 and req.enable_thinking and open_id is not None and close_id is not None:
+            opts.thinking_budget = int(budget)
+            opts.think_open_id, opts.think_close_id = int(open_id), int(close_id)
+            opts.think_close_ids = tuple(self.tok.encode("\n</think>\n\n"))
+        return opts
 
     # ------------------------------------------------------------------ generation
     def stream(self, req: GenRequest, on_start: Optional[Callable[[str, int], None]] = None,
@@ -282,6 +296,8 @@ class GenerationService:
             res.device_wait_s, res.host_exposed_s = handle.device_wait_s, handle.host_exposed_s
             res.decode_device_wait_s, res.decode_host_exposed_s = handle.decode_device_wait_s, handle.decode_host_exposed_s
             res.speculative = handle.speculative
+            res.thinking_budget = opts.thinking_budget
+            res.thinking_budget_applied, res.thinking_tokens = handle.thinking_budget_applied, handle.thinking_tokens
             yield ("done", res)
         finally:
             self._permits.release()

@@ -433,3 +433,65 @@ def test_retention_classes_order_the_victims():
     assert order[2:] == [("old", "endpoint"), ("busy", "endpoint"), ("__shared__", "shared")]
     assert RETENTION_WEIGHT["disposable"] < RETENTION_WEIGHT["recent_private"] < RETENTION_WEIGHT["live_session"]
     prog.close(live)
+
+
+def test_thinking_budget_closes_the_reasoning_frame_with_control_tokens():
+    """A model that would reason forever: after `thinking_budget` reasoning tokens the engine feeds the frame's closing
+    sequence in place of the sampled tokens (and tells the Program, so the forced tokens are what runs next), then the
+    model continues on its own; without a budget nothing is touched."""
+    from ninfer_fusion_b200.models.config import TINY_DENSE
+    from ninfer_fusion_b200.models.weights import random_weights
+    from ninfer_fusion_b200.runtime.program import ReferenceProgram
+    OPEN, CLOSE, NL = 900, 901, 902
+
+    class Thinker(ReferenceProgram):
+        """Emits OPEN first, then 7 forever while its last fed token is not CLOSE / NL-after-close; after the closing
+        sequence it answers 5, 5, ...  What it is FED is recorded."""
+
+        def __init__(self, *a, **k):
+            super().__init__(*a, **k)
+            self.fed, self.forced = [], []
+
+        def force_next_token(self, lane, token):
+            self.forced.append(int(token))
+            super().force_next_token(lane, token)
+
+        def prefill_step(self, lane, budget):
+            first = super().prefill_step(lane, budget)
+            if first is not None:
+                lane.last_token = OPEN
+                return OPEN
+            return None
+
+        def decode_round(self, lanes):
+            out = []
+            for lane in lanes:
+                self.fed.append(lane.last_token)
+                super().decode_round([lane])
+                closed = CLOSE in self.fed
+                lane.last_token = 5 if closed else 7
+                out.append(lane.last_token)
+            return out
+
+    cfg = TINY_DENSE.shrink(2)
+    w = random_weights(cfg, "cpu", seed=5, std=0.05)
+    prog = {}
+
+    def factory():
+        prog["p"] = Thinker(cfg, w, max_lanes=2, max_context=128)
+        return prog["p"]
+    eng = Engine(factory, prefill_chunk=16)
+    try:
+        opts = RequestOptions(max_tokens=12, thinking_budget=3, think_open_id=OPEN, think_close_id=CLOSE,
+                              think_close_ids=(NL, CLOSE, NL))
+        h = eng.submit(list(range(10, 20)), opts)
+        out = h.wait(timeout=120)
+        #      frame   three reasoning tokens   forced closing sequence   the model again
+        assert out == [OPEN, 7, 7, 7, NL, CLOSE, NL, 5, 5, 5, 5, 5]
+        assert h.thinking_budget_applied and h.thinking_tokens == 3
+        assert prog["p"].forced == [NL, CLOSE, NL]
+        assert prog["p"].fed[:7] == [OPEN, 7, 7, 7, NL, CLOSE, NL]      # the forced tokens are what ran, not the samples
+        free = eng.submit(list(range(10, 20)), RequestOptions(max_tokens=6))
+        assert free.wait(timeout=120) == [OPEN, 5, 5, 5, 5, 5] and not free.thinking_budget_applied   # (CLOSE was fed before)
+    finally:
+        eng.shutdown()

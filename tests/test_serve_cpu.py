@@ -462,3 +462,31 @@ def test_server_option_table_process_settings(tmp_path):
         httpd.shutdown()
         httpd.server_close()
         engine.shutdown()
+
+
+def test_thinking_budget_reaches_the_engine_from_every_protocol(server):
+    from ninfer_fusion_b200.serve import protocols as P
+    from ninfer_fusion_b200.serve.service import GenRequest
+    _, svc, _ = server
+    req, _ = P.parse_anthropic_messages({"max_tokens": 64, "thinking": {"type": "enabled", "budget_tokens": 20},
+                                         "messages": [{"role": "user", "content": "q"}]})
+    assert req.enable_thinking and req.thinking_budget == 20
+    req2, _ = P.parse_openai_chat({"messages": [{"role": "user", "content": "q"}], "thinking_budget": 9})
+    assert req2.thinking_budget == 9
+    for bad in ({"thinking_budget": 0}, {"thinking_budget": "many"}, {"chat_template_kwargs": {"thinking_budget": -1}}):
+        with pytest.raises(P.BadRequest):
+            P.parse_openai_chat(dict({"messages": [{"role": "user", "content": "q"}]}, **bad))
+    with pytest.raises(P.BadRequest):
+        P.parse_anthropic_messages({"max_tokens": 8, "thinking": {"type": "enabled", "budget_tokens": 0},
+                                    "messages": [{"role": "user", "content": "q"}]})
+    o = svc._options(req)
+    close = svc.tok.token_id("</think>")
+    assert o.thinking_budget == 20 and o.think_close_id == close and close in o.think_close_ids
+    assert o.think_open_id == svc.tok.token_id("<think>")
+    assert svc._options(GenRequest(prompt="x")).thinking_budget is None
+    svc.default_thinking_budget = 50
+    try:
+        assert svc._options(GenRequest(prompt="x")).thinking_budget == 50
+        assert svc._options(GenRequest(prompt="x", enable_thinking=False)).thinking_budget is None   # nothing to cap
+    finally:
+        svc.default_thinking_budget = None
