@@ -499,13 +499,23 @@ def cmd_kv_rowscale(args) -> int:
 # ---------------------------------------------------------------------------------------------------------
 def cmd_generate(args) -> int:
     from .serve.service import GenerationService, GenRequest
+    if getattr(args, "kv_score_table", ""):
+        from .kv import kv_bits
+        return kv_bits.main(["score-table", args.kv_score_table] + (["--from", args.kv_tier_scores] if args.kv_tier_scores else []))
+    if getattr(args, "capability_report", False):
+        from . import hostdiag
+        return hostdiag.main(["hostdiag", "cufree"])
     ranks = setup_ranks(args)
     cfg, weights, tok, name = load_model(args)
     engine = build_engine(args, cfg, weights, ranks)
     if engine is None:
         return 0     # a follower rank: it executed the leader's steps until told to stop
     svc = GenerationService(engine, tok, name)
+    svc.force_greedy = bool(getattr(args, "greedy", False))
+    svc.eos_ids = list(svc.eos_ids) + [int(t) for t in (getattr(args, "stop_token_id", None) or [])]
     req = GenRequest(max_tokens=args.max_tokens, temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
+                     min_p=getattr(args, "min_p", None), presence_penalty=getattr(args, "presence_penalty", None),
+                     frequency_penalty=getattr(args, "frequency_penalty", None),
                      seed=args.seed, enable_thinking=not args.no_think, stop=args.stop or (),
                      thinking_budget=args.thinking_budget or None)
     if args.prompt_ids:
@@ -545,9 +555,40 @@ def cmd_generate(args) -> int:
              "weights_bytes": total_bytes(weights)}
     if args.print_ids:
         stats["completion_ids"] = list(result.token_ids)
+    if getattr(args, "print_prompt_ids", False):
+        stats["prompt_ids"] = svc.prepare(req)
     print(json.dumps(stats), file=sys.stderr)
     _shutdown(engine)
     return 0 if result.finish_reason != "error" else 1
+
+
+def cmd_stage_walk(args) -> int:
+    """The forward pass as a walk over pipeline stages on the CPU oracle: every stage runs its layer range, the
+    residual stream crosses each boundary through a checksummed hand-off file when --stage-handoff names a directory
+    (--stage-handoff-cut skips the writes: the negative control, the next stage must then refuse a missing or stale
+    file).  Prints the next token and the plan; the GPU pipeline is `parallel.pp.PipelineStage` (one stage per GPU)."""
+    from .models.reference_model import ReferenceModel, ReferenceSequence
+    from .ops import reference as R
+    from .parallel.pp import StagePlan, StagePlanError, stage_walk_reference
+    args.device = "cpu"
+    cfg, weights, tok, name = load_model(args)
+    try:
+        plan = (StagePlan.parse(args.stage_layers, cfg.n_layers) if args.stage_layers
+                else StagePlan.balanced(cfg.n_layers, max(1, args.stages), cfg.full_attn_interval))
+    except StagePlanError as e:
+        raise SystemExit(str(e)) from None
+    ids = [int(v) for v in args.prompt_ids.split(",")] if args.prompt_ids else tok.encode(args.prompt)
+    model = ReferenceModel(cfg, {k: v for k, v in weights.items() if not k.startswith(("mtp/", "vision/", "dflash/"))})
+    try:
+        hid = stage_walk_reference(model, ReferenceSequence(cfg, R.KV_BF16), torch.tensor(ids), plan,
+                                   args.stage_handoff or None, cut=bool(args.stage_handoff_cut))
+    except (OSError, ValueError) as e:
+        print(json.dumps({"plan": plan.spec(), "refused": str(e)}))
+        return 3
+    nxt = int(R.argmax_lowest(model.logits(hid[-1:]))[0])
+    print(json.dumps({"model": name, "plan": plan.spec(), "stages": plan.world, "uniform": plan.uniform,
+                      "handoff": args.stage_handoff or None, "prompt_tokens": len(ids), "next_token": nxt}))
+    return 0
 
 
 def cmd_serve(args) -> int:
@@ -800,13 +841,33 @@ def main(argv=None) -> int:
     g.add_argument("--temperature", type=float, default=None)
     g.add_argument("--top-p", type=float, default=None)
     g.add_argument("--top-k", type=int, default=None)
+    g.add_argument("--min-p", type=float, default=None)
+    g.add_argument("--presence-penalty", type=float, default=None)
+    g.add_argument("--frequency-penalty", type=float, default=None)
+    g.add_argument("--greedy", action="store_true", help="exact arg-max whatever the sampler settings say")
     g.add_argument("--stop", action="append")
+    g.add_argument("--stop-token-id", type=int, action="append", help="additional token id that ends the generation")
+    g.add_argument("--print-prompt-ids", action="store_true", help="add the prompt's token ids to the stats line")
+    g.add_argument("--print-token-ids", dest="print_ids", action="store_true", help="same as --print-ids")
+    g.add_argument("--kv-score-table", default="", metavar="show|emit=PATH",
+                   help="print or write the KV tier penalty table and exit (no model is loaded)")
+    g.add_argument("--capability-report", action="store_true",
+                   help="print the architecture ladder, this GPU's capability bits and the (op, format) routes, and exit")
     g.add_argument("--no-think", "--no-thinking", dest="no_think", action="store_true")
     g.add_argument("--thinking-budget", type=int, default=0,
                    help="reasoning tokens after which the reasoning frame is closed for the model (0: no cap)")
     g.add_argument("--show-thinking", action="store_true")
     g.add_argument("--print-ids", action="store_true", help="add the completion's token ids to the stats line")
     g.set_defaults(fn=cmd_generate)
+    w = sub.add_parser("stage-walk", help="run the forward pass stage by stage on the CPU oracle (pipeline plan check)")
+    add_model_args(w)
+    w.add_argument("--stage-layers", default="", help="SPEC first-last[,first-last...] with inclusive bounds, e.g. 0-31,32-63")
+    w.add_argument("--stages", type=int, default=2, help="without --stage-layers: an even split into this many stages")
+    w.add_argument("--stage-handoff", default="", help="directory for the checksummed boundary files")
+    w.add_argument("--stage-handoff-cut", action="store_true", help="negative control: do not write the boundary files")
+    w.add_argument("--prompt", default="Hello")
+    w.add_argument("--prompt-ids", default="")
+    w.set_defaults(fn=cmd_stage_walk)
     s = sub.add_parser("serve", help="OpenAI / Anthropic compatible HTTP server")
     s.add_argument("--kv-auto-relayout", type=float, default=0.0,
                    help="average KV bits per element to hold: per-layer tiers follow the layers' key energy (0 = off)")

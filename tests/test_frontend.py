@@ -139,3 +139,27 @@ def test_unicode_normal_form_from_tokenizer_json():
     assert nfc.encode("<|im_start|>x")[0] == nfc.added["<|im_start|>"]
     with pytest.raises(ValueError):
         Tokenizer(base.vocab, [], normalizer="lowercase")
+
+
+def test_cli_stage_walk_and_model_free_entries(tmp_path, capsys):
+    """`stage-walk` runs the CPU oracle stage by stage (same next token as one stage; a cut hand-off is refused with
+    exit code 3; a plan that does not partition the layers is refused before anything runs); `generate
+    --kv-score-table` and `--capability-report` answer without loading a model."""
+    import json
+
+    from ninfer_fusion_b200 import cli
+    base = ["stage-walk", "--random-init", "--model", "tiny-dense", "--prompt-ids", "5,6,7,8"]
+    assert cli.main(base + ["--stages", "1"]) == 0
+    one = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert cli.main(base + ["--stage-layers", "0-1,2-3", "--stage-handoff", str(tmp_path / "h")]) == 0
+    two = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert two["stages"] == 2 and two["next_token"] == one["next_token"] and (tmp_path / "h" / "stage_0.bin").exists()
+    assert cli.main(base + ["--stage-layers", "0-1,2-3", "--stage-handoff", str(tmp_path / "cut"), "--stage-handoff-cut"]) == 3
+    assert "refused-stage-handoff" in capsys.readouterr().out
+    import pytest
+    with pytest.raises(SystemExit, match="refused-stage-layers-partition"):
+        cli.main(base + ["--stage-layers", "0-1,3-3"])
+    assert cli.main(["generate", "--kv-score-table", "show"]) == 0
+    assert "nvfp4=" in capsys.readouterr().out
+    assert cli.main(["generate", "--capability-report"]) == 0
+    assert "host report" in capsys.readouterr().out
