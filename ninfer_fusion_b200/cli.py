@@ -53,6 +53,9 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
                     help="stop descending once the live KV cells of the mixed layers fit in this many MiB (0 = no target)")
     ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8", "fp8h", "int8", "nvfp4", "mixed"],
                     help="KV cache codec (fp8h = fp8 per-row with K in the Hadamard frame)")
+    ap.add_argument("--kv-tier-formats", default="",
+                    help="with --kv-dtype mixed: hot=<tier>,tail=<tier>,cold=<tier> over bf16 / fp8 / nvfp4: new pages "
+                         "start in the hot tier, cells descend no further than the cold tier")
     ap.add_argument("--kv-layer-spec", default="", help="per-layer KV storage, e.g. 'all:fp8' or '0-3:bf16,4-15:nvfp4'")
     ap.add_argument("--kv-bits", type=float, default=None,
                     help="one ceiling on the average bits per KV element: the bit-budget planner picks a tier per layer")
@@ -101,6 +104,13 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
                     help="which cached frontier is given up under memory pressure: 'lru' (least recently used), or the "
                          "materialisation planner with a machine cost preset: b200 | h100 | rtx5090 | file:<path> "
                          "(a file measured on this machine by `python -m ninfer_fusion_b200.utils.calib`)")
+    ap.add_argument("--cold-policy", default="none", choices=["none", "off", "host", "disk", "host-then-disk", "host+disk"],
+                    help="where session frontiers go when the device pool needs their pages: pinned host memory, files, "
+                         "or host first with files as its overflow (none: they are dropped)")
+    ap.add_argument("--cold-host-bytes", default="0", help="pinned host budget, N[k|m|g]")
+    ap.add_argument("--cold-disk-path", default="", help="directory of the file tier")
+    ap.add_argument("--cold-disk-bytes", default="0", help="file tier budget, N[k|m|g]")
+    ap.add_argument("--cold-entropy", action="store_true", help="entropy-code frontiers written to the file tier")
     ap.add_argument("--cold-slots", action="store_true",
                     help="int8 KV pages leave the device as requantised cold slots (lossy, 0.55 of the bytes)")
     ap.add_argument("--anchor-interval", type=int, default=0,
@@ -349,6 +359,45 @@ def build_engine(args, cfg: ModelConfig, weights, ranks=None) -> Optional[Engine
                       prefill_chunk_mode=getattr(args, "prefill_chunk_mode", None))
 
 
+def parse_bytes(text: str) -> int:
+    """'N', 'Nk', 'Nm', 'Ng' (binary multiples) -> bytes.  Anything else is refused, not read as zero."""
+    t = str(text).strip().lower()
+    mult = {"k": 1 << 10, "m": 1 << 20, "g": 1 << 30}.get(t[-1:], 1)
+    num = t[:-1] if t[-1:] in "kmg" else t
+    try:
+        v = float(num)
+    except ValueError:
+        raise SystemExit(f"'{text}' is not a byte count (N, Nk, Nm or Ng)") from None
+    if v < 0:
+        raise SystemExit(f"'{text}' is negative")
+    return int(v * mult)
+
+
+def apply_cold_policy(args, prog) -> None:
+    """--cold-policy / --cold-host-bytes / --cold-disk-path / --cold-disk-bytes: where frontiers that are pushed out
+    of the device pool go (pinned host memory first, files as its overflow, dropped otherwise)."""
+    policy = getattr(args, "cold_policy", "none") or "none"
+    policy = {"off": "none", "host+disk": "host-then-disk"}.get(policy, policy)
+    host_b = parse_bytes(getattr(args, "cold_host_bytes", "0") or "0")
+    disk_b = parse_bytes(getattr(args, "cold_disk_bytes", "0") or "0")
+    path = getattr(args, "cold_disk_path", "") or ""
+    if policy == "none":
+        if host_b or disk_b or path:
+            raise SystemExit("--cold-host-bytes / --cold-disk-* need --cold-policy host | disk | host-then-disk")
+        return
+    if policy in ("host", "host-then-disk") and host_b <= 0:
+        raise SystemExit(f"--cold-policy {policy} needs --cold-host-bytes")
+    if policy in ("disk", "host-then-disk") and (not path or disk_b <= 0):
+        raise SystemExit(f"--cold-policy {policy} needs --cold-disk-path and --cold-disk-bytes")
+    if not hasattr(prog, "host_budget_bytes"):
+        raise SystemExit("this program keeps no frontiers: --cold-policy does not apply")
+    # the disk tier is fed from the host tier: with the plain `disk` policy the host tier is only a staging page
+    prog.host_budget_bytes = host_b if policy != "disk" else max(host_b, 1)
+    if policy in ("disk", "host-then-disk"):
+        prog.cold_dir, prog.disk_budget_bytes = path, disk_b
+        prog.cold_entropy = bool(getattr(args, "cold_entropy", False))
+
+
 def _kv_spec_from_ceilings(args, cfg: ModelConfig) -> None:
     """--kv-bits / --kv-k-bits + --kv-v-bits -> the per-layer storage spec (kv/kv_bits.py); fills args.kv_layer_spec."""
     bits, kb, vb = getattr(args, "kv_bits", None), getattr(args, "kv_k_bits", None), getattr(args, "kv_v_bits", None)
@@ -407,20 +456,31 @@ def program_factory(args, cfg: ModelConfig, weights, kv, shard=None, comm=None):
         from .runtime.gpu_program import GpuProgram
 
         descent = None
+        hot_tier, floor = 0, ""
+        if getattr(args, "kv_tier_formats", ""):
+            from .kv.policy import parse_tier_formats, tier_formats_on_ladder
+            if kv != "mixed" and not (isinstance(kv, (list, tuple)) and "mixed" in kv):
+                raise SystemExit("--kv-tier-formats shapes the per-cell tiers of --kv-dtype mixed")
+            try:
+                hot_tier, floor = tier_formats_on_ladder(parse_tier_formats(args.kv_tier_formats))
+            except ValueError as e:
+                raise SystemExit(f"--kv-tier-formats: {e}") from None
         if getattr(args, "kv_descent_age", 0) > 0:
             from .kv.descent import DescentConfig
-            descent = DescentConfig(min_age_tokens=int(args.kv_descent_age),
+            descent = DescentConfig(min_age_tokens=int(args.kv_descent_age), floor=floor,
                                     target_resident_bytes=int(getattr(args, "kv_descent_target_mib", 0.0) * (1 << 20)))
 
         def factory():
             text = {k: v for k, v in weights.items() if not k.startswith("vision/")}
-            prog = GpuProgram(cfg, text, args.device, descent=descent, max_lanes=args.max_lanes, max_context=args.max_context,
+            prog = GpuProgram(cfg, text, args.device, descent=descent, mixed_hot_tier=hot_tier, max_lanes=args.max_lanes,
+                              max_context=args.max_context,
                               kv_format=kv, page_size=args.page_size, prefill_chunk=args.prefill_chunk,
                               use_graph=not args.no_graphs, kv_pages=resolve_kv_pages(args, cfg, kv), shard=shard,
                               comm=comm, weight_budget_bytes=int(args.weight_budget_gib * (1 << 30)) if args.weight_budget_gib > 0 else None)
             load_row_scale(args, cfg, prog.model)
             prog.anchor_interval = max(0, int(getattr(args, "anchor_interval", 0)))
             prog.kv.cold_slots = bool(getattr(args, "cold_slots", False))
+            apply_cold_policy(args, prog)
             if getattr(args, "planner", "lru") != "lru":
                 from .runtime.planner import MaterializationPlanner
                 from .utils.calib import load_preset   # built-in name or file:<path> written by utils/calib.py
@@ -430,6 +490,7 @@ def program_factory(args, cfg: ModelConfig, weights, kv, shard=None, comm=None):
         def factory():
             prog = ReferenceProgram(cfg, weights, max_lanes=args.max_lanes, max_context=args.max_context,
                                     kv_format=kv if isinstance(kv, str) else "bf16")
+            apply_cold_policy(args, prog)
             return attach_vision(args, cfg, weights, prog)
     return factory
 

@@ -25,6 +25,7 @@ class DescentConfig:
     max_bytes_per_pass: int = 1 << 30
     target_resident_bytes: int = 0    # 0 = no target: descend whatever the other budgets allow
     sink_blocks: int = 1              # leading blocks of a sequence that never descend (attention sinks)
+    floor: str = ""                   # ladder tier below which no cell descends ("" = the ladder's last rung)
 
 
 @dataclass(frozen=True)
@@ -81,6 +82,10 @@ def plan_descent_pass(cells: CellMap, cfg: DescentConfig, n_kv_heads: int, head_
     tiers = tiers or build_ladder(head_dim)
     per = [cell_bytes(tiers[name], cells.page_tokens, n_kv_heads, head_dim) for name in cfg.ladder]
     last = len(cfg.ladder) - 1
+    if cfg.floor:
+        if cfg.floor not in cfg.ladder:
+            raise ValueError(f"descent floor '{cfg.floor}' is not a rung of the ladder {cfg.ladder}")
+        last = cfg.ladder.index(cfg.floor)     # the `cold=` tier of the tier-format grammar: the deepest resident rung
     resident = resident_bytes(cells, cfg, tiers, n_kv_heads, head_dim)
     cands = []
     for (seq, layer, block), rung in cells.rungs.items():

@@ -108,6 +108,19 @@ def parse_tier_formats(spec: str) -> TierFormats:
     return TierFormats(**vals)
 
 
+def tier_formats_on_ladder(tf: TierFormats, ladder: Sequence[str] = ("bf16", "fp8", "nvfp4")) -> Tuple[int, str]:
+    """What a `hot=,tail=,cold=` triple means for per-cell tiers on a fixed precision ladder: (index of the tier new
+    pages start in, deepest tier a resident cell may descend to).  The three roles must walk DOWN the ladder (a tail
+    wider than the hot tier would re-encode upwards) and every role must be a rung of it."""
+    for role in ("hot", "tail", "cold"):
+        if getattr(tf, role) not in ladder:
+            raise ValueError(f"{role}={getattr(tf, role)} is not a tier of the per-cell ladder {'/'.join(ladder)}")
+    h, t, c = (ladder.index(getattr(tf, r)) for r in ("hot", "tail", "cold"))
+    if not h <= t <= c:
+        raise ValueError(f"hot={tf.hot},tail={tf.tail},cold={tf.cold} does not descend the ladder {'/'.join(ladder)}")
+    return h, tf.cold
+
+
 # ----------------------------------------------------------------------------- bit-budget allocator
 @dataclass
 class BitBudgetPlan:

@@ -163,3 +163,36 @@ def test_cli_stage_walk_and_model_free_entries(tmp_path, capsys):
     assert "nvfp4=" in capsys.readouterr().out
     assert cli.main(["generate", "--capability-report"]) == 0
     assert "host report" in capsys.readouterr().out
+
+
+def test_cold_policy_flags_are_checked_and_applied(tmp_path):
+    import argparse
+
+    import pytest
+
+    from ninfer_fusion_b200 import cli
+    assert [cli.parse_bytes(t) for t in ("0", "512", "4k", "1.5m", "2G")] == [0, 512, 4096, int(1.5 * (1 << 20)), 2 << 30]
+    for bad in ("lots", "-1", "3x"):
+        with pytest.raises(SystemExit):
+            cli.parse_bytes(bad)
+
+    class Prog:
+        host_budget_bytes = 0
+        disk_budget_bytes = 0
+        cold_dir = None
+        cold_entropy = False
+
+    def ns(**kw):
+        base = dict(cold_policy="none", cold_host_bytes="0", cold_disk_path="", cold_disk_bytes="0", cold_entropy=False)
+        base.update(kw)
+        return argparse.Namespace(**base)
+    p = Prog()
+    cli.apply_cold_policy(ns(), p)
+    assert p.host_budget_bytes == 0 and p.cold_dir is None
+    cli.apply_cold_policy(ns(cold_policy="host+disk", cold_host_bytes="64m", cold_disk_path=str(tmp_path), cold_disk_bytes="1g",
+                             cold_entropy=True), p)
+    assert (p.host_budget_bytes, p.disk_budget_bytes, p.cold_dir, p.cold_entropy) == (64 << 20, 1 << 30, str(tmp_path), True)
+    for bad in (ns(cold_host_bytes="1m"), ns(cold_policy="host"), ns(cold_policy="disk", cold_disk_bytes="1g"),
+                ns(cold_policy="host-then-disk", cold_host_bytes="1m")):
+        with pytest.raises(SystemExit):
+            cli.apply_cold_policy(bad, Prog())

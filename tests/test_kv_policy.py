@@ -225,3 +225,24 @@ def test_cyclic_cache_keeps_a_bounded_ring_of_pages_per_row():
     kv.free_row(0)
     kv.free_row(1)
     assert kv.pool.free_pages == kv.n_pages
+
+
+def test_tier_formats_shape_the_per_cell_ladder_and_the_descent_floor():
+    from ninfer_fusion_b200.kv.descent import CellMap, DescentConfig, plan_descent_pass
+    from ninfer_fusion_b200.kv.policy import parse_tier_formats, tier_formats_on_ladder
+    assert tier_formats_on_ladder(parse_tier_formats("")) == (0, "nvfp4")
+    assert tier_formats_on_ladder(parse_tier_formats("hot=fp8,tail=fp8,cold=nvfp4")) == (1, "nvfp4")
+    assert tier_formats_on_ladder(parse_tier_formats("hot=bf16,tail=fp8,cold=fp8")) == (0, "fp8")
+    for bad in ("hot=fp8,tail=bf16", "hot=nvfp4,tail=fp8,cold=fp8", "hot=int8"):
+        with pytest.raises(ValueError):
+            tier_formats_on_ladder(parse_tier_formats(bad))
+    cells = CellMap(64, 1)
+    cells.frontier[0] = 64 * 12
+    for b in range(12):
+        cells.rungs[(0, 0, b)] = 1 if b < 6 else 0          # old blocks already at fp8, newer ones at bf16
+    free = plan_descent_pass(cells, DescentConfig(min_age_tokens=64), 2, 256)
+    floor = plan_descent_pass(cells, DescentConfig(min_age_tokens=64, floor="fp8"), 2, 256)
+    assert any(m.dst == "nvfp4" for m in free)
+    assert floor and all(m.dst == "fp8" for m in floor)     # nothing goes below the floor
+    with pytest.raises(ValueError):
+        plan_descent_pass(cells, DescentConfig(floor="int8"), 2, 256)
