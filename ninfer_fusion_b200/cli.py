@@ -679,7 +679,8 @@ def cmd_serve(args) -> int:
         from .serve.kv_auto_relayout import KvAutoRelayout, RelayoutConfig, kv_scale_energy
         relayout = KvAutoRelayout(engine, len(cfg.attn_layers), lambda: kv_scale_energy(engine.program.kv),
                                   lambda tiers: program_factory(args, cfg, weights, list(tiers)),
-                                  RelayoutConfig(target_bits=args.kv_auto_relayout, period_s=args.kv_relayout_period),
+                                  RelayoutConfig(target_bits=args.kv_auto_relayout, period_s=args.kv_relayout_period,
+                                                 assignment=args.kv_relayout_assignment),
                                   log=lambda rec: print(json.dumps(rec), file=sys.stderr, flush=True))
         relayout.start()
     if getattr(args, "warmup", 0) > 0:
@@ -933,6 +934,9 @@ def main(argv=None) -> int:
     s.add_argument("--kv-auto-relayout", type=float, default=0.0,
                    help="average KV bits per element to hold: per-layer tiers follow the layers' key energy (0 = off)")
     s.add_argument("--kv-relayout-period", type=float, default=300.0, help="seconds between relayout decisions")
+    s.add_argument("--kv-relayout-assignment", default="rank", choices=["rank", "knapsack"],
+                   help="rank: the bit-budget allocator's tiers handed out by energy rank; knapsack: exact per-layer "
+                        "choice with every layer's penalties scaled by its energy")
     add_model_args(s)
     s.add_argument("--host", default="127.0.0.1")
     s.add_argument("--port", type=int, default=8080)

@@ -27,6 +27,11 @@ class RelayoutConfig:
     min_observations: int = 3         # no relayout before this many samples
     hysteresis: float = 0.05          # relative energy margin a layer needs to overtake another (stability)
     drain_timeout_s: float = 30.0
+    # how the tiers are spread over the layers: "rank" = the bit-budget allocator's multiset handed out by energy rank
+    # (stable under the hysteresis); "knapsack" = the exact per-layer knapsack with every layer's prior penalties
+    # scaled by its own energy (kv/adapt_solver.py), which also honours per-layer allowed sets
+    assignment: str = "rank"
+    allowed: Optional[Sequence[Optional[Sequence[str]]]] = None
 
 
 @dataclass
@@ -77,6 +82,16 @@ class ColdPolicy:
         if self.observations < self.cfg.min_observations:
             return RelayoutDecision(format_layer_storage(self.current), list(self.current), e, False,
                                     reason="not enough observations")
+        if self.cfg.assignment == "knapsack":
+            from ..kv.adapt_solver import solve_for_bits
+            mean = sum(e) / max(1, len(e)) or 1.0
+            plan = solve_for_bits(self.n_layers, self.cfg.target_bits, [v / mean for v in e], self.cfg.allowed)
+            keep = (plan.tiers != self.current and self._close_call(e, plan.tiers))
+            tiers = list(self.current) if keep else list(plan.tiers)
+            return RelayoutDecision(format_layer_storage(tiers), tiers, e, tiers != self.current,
+                                    reason="within the hysteresis of the current layout" if keep else "")
+        if self.cfg.assignment != "rank":
+            raise ValueError(f"unknown relayout assignment '{self.cfg.assignment}' (rank | knapsack)")
         plan = solve_bit_budget(self.n_layers, self.cfg.target_bits)
         ladder = build_ladder()
         multiset = sorted((t for t in plan.tiers if t != "cold"), key=lambda n: -ladder[n].bits_centi)   # precise first
@@ -85,6 +100,21 @@ class ColdPolicy:
         for tier, layer in zip(multiset, self._ranking()):
             tiers[layer] = tier
         return RelayoutDecision(format_layer_storage(tiers), tiers, e, tiers != self.current)
+
+
+    def _close_call(self, energy: Sequence[float], proposed: Sequence[str]) -> bool:
+        """Knapsack mode's stability rule: keep the current layout when it is feasible and its energy-weighted penalty is
+        within the hysteresis of the proposed one (a relayout drains the lanes; a marginal gain does not pay for it)."""
+        ladder = build_ladder()
+        if any(t not in ladder for t in self.current):
+            return False
+        bits = sum(ladder[t].bits_centi for t in self.current) / 100.0 / self.n_layers
+        if bits > self.cfg.target_bits + 1e-9:
+            return False
+
+        def cost(tiers):
+            return sum(v * ladder[t].penalty_milli for v, t in zip(energy, tiers))
+        return cost(self.current) <= cost(proposed) * (1 + self.cfg.hysteresis)
 
 
 class KvAutoRelayout:

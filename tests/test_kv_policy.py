@@ -246,3 +246,23 @@ def test_tier_formats_shape_the_per_cell_ladder_and_the_descent_floor():
     assert floor and all(m.dst == "fp8" for m in floor)     # nothing goes below the floor
     with pytest.raises(ValueError):
         plan_descent_pass(cells, DescentConfig(floor="int8"), 2, 256)
+
+
+def test_relayout_knapsack_assignment_follows_energy_and_allowed_sets():
+    from ninfer_fusion_b200.serve.kv_auto_relayout import ColdPolicy, RelayoutConfig
+    cfg = RelayoutConfig(target_bits=6.5, min_observations=1, assignment="knapsack",
+                         allowed=[None, None, None, ["bf16", "fp8", "int8"], None, None, None, None])
+    pol = ColdPolicy(8, cfg, initial=["fp8"] * 8)
+    pol.observe([1, 1, 1, 1, 1, 1, 9, 1])
+    d = pol.decide()
+    order = {"nvfp4": 0, "fp8": 1, "int8": 2, "bf16": 3}
+    assert d.changed and order[d.tiers[6]] == max(order[t] for t in d.tiers)      # the energetic layer keeps the precision
+    assert d.tiers[3] != "nvfp4"                                                    # a hole the rank assignment cannot express
+    ladder_bits = {"bf16": 16.0, "int8": 8.25, "fp8": 8.0625, "nvfp4": 4.5}
+    assert sum(ladder_bits[t] for t in d.tiers) / 8 <= 6.5 + 1e-6
+    # stability: once applied, a slightly different sample does not trigger another relayout
+    pol.current = list(d.tiers)
+    pol.observe([1.02, 1, 1, 1, 1, 0.99, 9, 1])
+    assert not pol.decide().changed
+    with pytest.raises(ValueError):
+        ColdPolicy(2, RelayoutConfig(min_observations=0, assignment="greedy")).decide()
