@@ -30,6 +30,7 @@ from ..models.config import ModelConfig
 from ..models.hybrid import GdnRecords
 from .batch import SeqChunk, StepBuffers
 from .generator import Generator, context_bucket
+from .lookup_fuse import lookup_drafter
 from .kv_cache import PagedKvCache
 
 
@@ -65,7 +66,7 @@ class SpeculativeGenerator(Generator):
         self.K = K
         self.R = R_   # candidates per depth of the draft tree: rank 0 extends the chain, ranks 1.. are side branches
         self.sampling = sampling  # runtime.program.SamplingParams for stochastic verification; None / greedy = arg-max
-        self.drafter = drafter  # "mtp" | "dflash" | "ngram" | "hook"
+        self.drafter = drafter  # "mtp" | "dflash" | "ngram" | "lookup" | "hook"
         self.draft_hook: Optional[Callable[[int, List[int], int], Optional[List[int]]]] = None
         dev, g = self.device, self.model.g
         Tv = max_batch * (1 + self.R * K)
@@ -380,6 +381,8 @@ class SpeculativeGenerator(Generator):
                 d = self.draft_hook(b, self.history[b], K)
             elif self.drafter == "ngram":
                 d = ngram_drafter(self.history[b], K)
+            elif self.drafter == "lookup":
+                d = lookup_drafter(self.history[b], K)   # history chain: K tokens on a full match, a padded probe on a partial one
             if d is None:
                 d = [self.last_tokens[b]] * K
             self.draft_host[b] = torch.tensor(list(d)[:K], dtype=torch.int32)
