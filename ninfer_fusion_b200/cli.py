@@ -53,6 +53,12 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
                     help="stop descending once the live KV cells of the mixed layers fit in this many MiB (0 = no target)")
     ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8", "fp8h", "int8", "nvfp4", "mixed"],
                     help="KV cache codec (fp8h = fp8 per-row with K in the Hadamard frame)")
+    ap.add_argument("--kv-descent-floor-nats", type=float, default=0.0,
+                    help="with --kv-descent-target-mib: solve the whole per-cell allocation every pass (cells may be "
+                         "assigned several rungs down at once) and never spend more than this total precision loss; a "
+                         "target that cannot be reached inside it moves nothing (0: the incremental one-rung walk)")
+    ap.add_argument("--kv-descent-rung-nats", default="0.01,0.08",
+                    help="measured loss, in nats per cell, of a cell entering fp8 and nvfp4")
     ap.add_argument("--kv-tier-formats", default="",
                     help="with --kv-dtype mixed: hot=<tier>,tail=<tier>,cold=<tier> over bf16 / fp8 / nvfp4: new pages "
                          "start in the hot tier, cells descend no further than the cold tier")
@@ -467,7 +473,16 @@ def program_factory(args, cfg: ModelConfig, weights, kv, shard=None, comm=None):
                 raise SystemExit(f"--kv-tier-formats: {e}") from None
         if getattr(args, "kv_descent_age", 0) > 0:
             from .kv.descent import DescentConfig
-            descent = DescentConfig(min_age_tokens=int(args.kv_descent_age), floor=floor,
+            table = None
+            if getattr(args, "kv_descent_floor_nats", 0.0) > 0:
+                from .kv.descent import CellCostTable
+                if getattr(args, "kv_descent_target_mib", 0.0) <= 0:
+                    raise SystemExit("--kv-descent-floor-nats bounds the solve toward --kv-descent-target-mib: give the target")
+                costs = [float(v) for v in str(args.kv_descent_rung_nats).split(",")]
+                if len(costs) != 2 or min(costs) < 0:
+                    raise SystemExit("--kv-descent-rung-nats takes two non-negative numbers: loss of a cell entering fp8, nvfp4")
+                table = CellCostTable((0.0, costs[0], costs[1]), float(args.kv_descent_floor_nats), floor_measured=True)
+            descent = DescentConfig(min_age_tokens=int(args.kv_descent_age), floor=floor, solve_table=table,
                                     target_resident_bytes=int(getattr(args, "kv_descent_target_mib", 0.0) * (1 << 20)))
 
         def factory():

@@ -266,3 +266,69 @@ def test_relayout_knapsack_assignment_follows_energy_and_allowed_sets():
     assert not pol.decide().changed
     with pytest.raises(ValueError):
         ColdPolicy(2, RelayoutConfig(min_observations=0, assignment="greedy")).decide()
+
+
+def test_stateless_cell_allocation_solve_and_its_named_refusals():
+    from ninfer_fusion_b200.kv import descent as D
+    cfg = D.DescentConfig(min_age_tokens=64, sink_blocks=1)
+    cells = D.CellMap(64, 2)
+    cells.touch(0, 64 * 10)                       # one sequence, 10 blocks, 2 layers, all at bf16
+    H, Dh = 2, 256
+    per = [D.cell_bytes(D.build_ladder(Dh)[n], 64, H, Dh) for n in cfg.ladder]
+    full = 20 * per[0]
+    table = D.CellCostTable((0.0, 0.01, 0.08), floor_nats=1.0, floor_measured=True)
+    # no pressure: the status quo, nothing spent
+    a = D.solve_cell_allocation(cells, cfg, full, table, H, Dh)
+    assert a.outcome == D.NO_PRESSURE and a.target == cells.rungs
+    # a budget reachable with first steps only: every cheap step (bf16 -> fp8) is taken before any expensive one,
+    # oldest blocks first among equals, the sink block and the newest block untouched
+    budget = full - 6 * (per[0] - per[1])
+    a = D.solve_cell_allocation(cells, cfg, budget, table, H, Dh)
+    assert a.outcome == D.SOLVED and a.resident_bytes <= budget and a.cells_demoted == 6
+    assert all(r <= 1 for r in a.target.values()) and a.spent_nats == pytest.approx(0.06)
+    moved = sorted(k for k, r in a.target.items() if r == 1)
+    assert {k[2] for k in moved} == {1, 2, 3} and all(a.target[(0, l, 0)] == 0 and a.target[(0, l, 9)] == 0 for l in (0, 1))
+    # a deeper budget takes cells down two rungs in ONE solve (no one-rung-per-pass rule: nothing iterates)
+    deep = D.solve_cell_allocation(cells, cfg, full // 2, D.CellCostTable((0.0, 0.01, 0.08), 5.0, True), H, Dh)
+    assert deep.outcome == D.SOLVED and max(deep.target.values()) == 2 and deep.resident_bytes <= full // 2
+    # the device still re-encodes rung by rung: one pass of moves toward the solved allocation, oldest first
+    mv = D.moves_toward(cells, cfg, deep, H, Dh)
+    assert mv and all(m.src == "bf16" and m.dst == "fp8" for m in mv) and [m.block for m in mv] == sorted(m.block for m in mv)
+    D.apply_moves(cells, cfg, mv)
+    again = D.solve_cell_allocation(cells, cfg, full // 2, D.CellCostTable((0.0, 0.01, 0.08), 5.0, True), H, Dh)
+    assert again.outcome == D.SOLVED                                   # re-solved from the new state, no carry needed
+    # the floor is the one quality constraint: a budget that needs more loss than the floor allows is refused by name
+    tight = D.solve_cell_allocation(cells, cfg, full // 4, D.CellCostTable((0.0, 0.01, 0.08), 0.05, True), H, Dh)
+    assert tight.outcome == D.REFUSED_BUDGET_UNREACHABLE and tight.deficit_bytes > 0 and tight.target == cells.rungs
+    unmeasured = D.solve_cell_allocation(cells, cfg, full // 2, D.CellCostTable((0.0, 0.01, 0.08), 5.0, False), H, Dh)
+    assert unmeasured.outcome == D.REFUSED_FLOOR_UNMEASURED
+    assert D.solve_cell_allocation(cells, cfg, full // 2, D.CellCostTable((0.0, 0.01), 5.0, True), H, Dh).outcome == D.REFUSED_BAD_TABLE
+    assert D.solve_cell_allocation(D.CellMap(64, 2), cfg, 1, table, H, Dh).outcome == D.REFUSED_EMPTY
+    # the descent floor of the tier-format grammar bounds the solve as well
+    capped = D.solve_cell_allocation(cells, D.DescentConfig(min_age_tokens=64, floor="fp8"), full * 3 // 4,
+                                     D.CellCostTable((0.0, 0.01, 0.08), 5.0, True), H, Dh)
+    assert max(capped.target.values()) <= 1
+
+
+def test_descent_pass_in_solve_mode_moves_toward_the_solved_allocation():
+    from ninfer_fusion_b200.kv import descent as D
+    H, Dh = 2, 256
+    cells = D.CellMap(64, 1)
+    cells.touch(0, 64 * 8)
+    per0 = D.cell_bytes(D.build_ladder(Dh)["bf16"], 64, H, Dh)
+    table = D.CellCostTable((0.0, 0.01, 0.08), 1.0, True)
+    cfg = D.DescentConfig(min_age_tokens=64, target_resident_bytes=8 * per0 * 3 // 4, solve_table=table)
+    passes = 0
+    while True:
+        mv = D.plan_descent_pass(cells, cfg, H, Dh)
+        if not mv:
+            break
+        D.apply_moves(cells, cfg, mv)
+        passes += 1
+        assert passes < 10
+    assert D.resident_bytes(cells, cfg, D.build_ladder(Dh), H, Dh) <= cfg.target_resident_bytes and passes >= 1
+    # a floor that cannot pay for the target: the pass moves nothing (no silent compromise)
+    cells2 = D.CellMap(64, 1)
+    cells2.touch(0, 64 * 8)
+    stuck = D.DescentConfig(min_age_tokens=64, target_resident_bytes=per0, solve_table=D.CellCostTable((0.0, 0.01, 0.08), 0.02, True))
+    assert D.plan_descent_pass(cells2, stuck, H, Dh) == []
