@@ -1,4 +1,4 @@
-"""python -m ninfer_fusion_b200.archkit adapt MODEL_ID config.json | gates ... | matrix --model ID"""
+"""python -m ninfer_fusion_b200.archkit adapt MODEL_ID config.json | matrix --model ID | import PATH"""
 from __future__ import annotations
 
 import argparse
@@ -18,7 +18,16 @@ def main(argv=None) -> int:
     m = sub.add_parser("matrix", help="GPU budget matrix of a registered model")
     m.add_argument("--model", default="qwen3.6-27b"); m.add_argument("--world", type=int, default=1)
     m.add_argument("--batch", type=int, default=1)
+    i = sub.add_parser("import", help="what is this path, can it be served, what fits on which GPU, how to start it")
+    i.add_argument("path")
+    i.add_argument("--gpu", default="b200"); i.add_argument("--context", type=int, default=32768)
+    i.add_argument("--lanes", type=int, default=8); i.add_argument("--world", type=int, default=1)
     args = ap.parse_args(argv)
+    if args.cmd == "import":
+        from .model_import import advise
+        out = advise(args.path, args.gpu, args.context, args.lanes, args.world)
+        print(json.dumps(out, indent=1))
+        return 0 if str(out.get("verdict", "")).startswith(("servable", "convert first")) else 1
     if args.cmd == "adapt":
         with open(args.config, encoding="utf-8") as f:
             desc = adapt_config(args.model_id, json.load(f))

@@ -75,3 +75,48 @@ def test_cli(tmp_path, capsys):
     out = capsys.readouterr().out.splitlines()
     assert json.loads(out[0])["servable"] and len(json.loads(out[1])["layer_table"]) == 64
     assert main(["matrix", "--model", "tiny-dense"]) == 0
+
+
+def test_model_import_recognises_judges_and_advises(tmp_path):
+    from ninfer_fusion_b200 import cli
+    from ninfer_fusion_b200.archkit import model_import as MI
+    # a Hugging Face checkpoint directory of the 27B geometry (header-sized shards: nothing is loaded)
+    hf = tmp_path / "Qwen3.6-27B"
+    hf.mkdir()
+    (hf / "config.json").write_text(json.dumps(_qwen_hf()))
+    (hf / "model-00001-of-00002.safetensors").write_bytes(b"\0" * 64)
+    (hf / "model-00002-of-00002.safetensors").write_bytes(b"\0" * 64)
+    rec = MI.recognise(str(hf))
+    assert rec["kind"] == "hf" and rec["shards"] == 2 and rec["bytes"] == 128
+    adv = MI.advise(str(hf), gpu="b200", context=32768, lanes=8)
+    assert adv["package"] == "qwen3.6-27b" and adv["verdict"].startswith("servable as qwen3.6-27b: bf16")
+    assert adv["commands"][0].startswith("python -m ninfer_fusion_b200.cli convert") and "--kv-dtype" in adv["commands"][1]
+    by = {r["weights"]: r for r in adv["fit"]}
+    assert by["nvfp4"]["weight_gib"] < by["fp8"]["weight_gib"] < by["bf16"]["weight_gib"] and by["bf16"]["fits"]
+    # a 32 GiB card: bf16 weights do not fit, a 4-bit format does, and the advice says so
+    small = MI.advise(str(hf), gpu="rtx5090", context=8192, lanes=1)
+    sby = {r["weights"]: r for r in small["fit"]}
+    assert not sby["bf16"]["fits"] and sby["nvfp4"]["fits"] and "nvfp4" in small["verdict"] or "q4" in small["verdict"]
+    # eight ranks: the launcher line and --tp
+    tp = MI.advise(str(hf), gpu="b200", context=131072, lanes=8, world=8)
+    assert "--nproc-per-node 8" in tp["commands"][-1] and tp["commands"][-1].endswith("--tp 8")
+    # a geometry the engine does not serve is refused with what is missing
+    odd = tmp_path / "other"
+    odd.mkdir()
+    (odd / "config.json").write_text(json.dumps({"num_hidden_layers": 8, "hidden_size": 2560, "num_attention_heads": 16,
+                                                 "num_key_value_heads": 4, "head_dim": 256, "hidden_act": "gelu",
+                                                 "intermediate_size": 10240, "vocab_size": 131072}))
+    assert MI.advise(str(odd))["verdict"].startswith("not servable")
+    # an artifact, a GGUF header, junk
+    art = tmp_path / "t.ninfer"
+    assert cli.main(["make-artifact", "--model", "tiny-dense", "--out", str(art)]) == 0
+    a = MI.advise(str(art))
+    assert a["recognised"]["kind"] == "ninfer" and a["package"] == "tiny-dense" and len(a["commands"]) == 1
+    g = tmp_path / "m.gguf"
+    g.write_bytes(b"GGUF" + (3).to_bytes(4, "little") + b"\0" * 8)
+    assert MI.recognise(str(g)) == {"kind": "gguf", "version": 3, "bytes": 16} and MI.advise(str(g))["verdict"].startswith("convert first")
+    junk = tmp_path / "x.bin"
+    junk.write_bytes(b"hello")
+    assert MI.advise(str(junk))["verdict"].startswith("unknown") and MI.recognise(str(tmp_path / "nope"))["kind"] == "unknown"
+    from ninfer_fusion_b200.archkit.__main__ import main as archkit_main
+    assert archkit_main(["import", str(hf)]) == 0 and archkit_main(["import", str(junk)]) == 1
