@@ -38,7 +38,10 @@ SPECIAL_TOKENS = ["<|endoftext|>", "<|im_start|>", "<|im_end|>", "<think>", "</t
 
 def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--artifact", help=".ninfer artifact (weights + embedded tokenizer / chat template)")
-    ap.add_argument("--model", default="tiny-dense", help="registered geometry for --random-init (see models/config.py)")
+    ap.add_argument("--model", default="tiny-dense", help="registered geometry for --random-init (see models/config.py); an "
+                    "attention-only package (spark-x2.5-4b, muse-glimmer-30b, gemma4-31b, optionally NAME@LAYERS) runs on "
+                    "the CPU oracle at a reduced debug geometry unless --full-geometry is given")
+    ap.add_argument("--full-geometry", action="store_true", help="attention-only packages: the full widths and vocabulary")
     ap.add_argument("--random-init", action="store_true", help="random weights of --model instead of an artifact")
     ap.add_argument("--layers", type=int, default=0, help="shrink the geometry to this many layers (debug)")
     ap.add_argument("--tokenizer", help="tokenizer.json (overrides the artifact's embedded one)")
@@ -136,6 +139,18 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
                     help="seconds after which a silent rank fails the engine (control channel time-out)")
 
 
+def _oracle_package(args):
+    """The attention-only package --model names (random-init runs only: their checkpoints have no converter here)."""
+    from .models.packages import GDN, PACKAGES, construct_oracle
+    base = str(getattr(args, "model", "")).split("@")[0]
+    if base not in PACKAGES or PACKAGES[base].count(GDN) or PACKAGES[base].config is not None:
+        return None
+    # random-init debug geometry: a few layers, a small vocabulary, narrow widths unless the caller asks for all of it
+    full = bool(getattr(args, "full_geometry", False))
+    return construct_oracle(args.model, layers=int(getattr(args, "layers", 0) or 0) or (0 if full else 4),
+                            vocab=0 if full else 2048, hidden_div=1 if full else 8)
+
+
 def load_model(args) -> Tuple[ModelConfig, Dict[str, object], Tokenizer, str]:
     tok: Optional[Tokenizer] = None
     template: Optional[str] = None
@@ -166,6 +181,18 @@ def load_model(args) -> Tuple[ModelConfig, Dict[str, object], Tokenizer, str]:
                        and not k.endswith(("A_log", "dt_bias")) else v) for k, v in weights.items()}
         weights = {k: (v.to(args.device) if torch.is_tensor(v) else v) for k, v in weights.items()}
         name = f"{model_id}:{weights_id}"
+    elif _oracle_package(args) is not None:
+        # an attention-only package: served on the CPU by its fp32 oracle (the GPU gate names what the kernels lack)
+        from .models.all_attention import package_model_config, random_package_weights
+        pkg = _oracle_package(args)
+        if str(args.device) != "cpu":
+            from .models.packages import PACKAGES
+            raise SystemExit(f"{pkg.model_id}: the GPU runtime lacks {', '.join(PACKAGES[pkg.model_id.split('@')[0]].missing())}; "
+                             f"--device cpu runs the package on its oracle")
+        args._package = pkg
+        cfg = package_model_config(pkg, args.max_context)
+        weights = random_package_weights(pkg, seed=args.seed)
+        name = f"{pkg.model_id}:random-init"
     else:
         cfg = get_config(args.model)
         if args.layers:
@@ -501,6 +528,12 @@ def program_factory(args, cfg: ModelConfig, weights, kv, shard=None, comm=None):
                 from .utils.calib import load_preset   # built-in name or file:<path> written by utils/calib.py
                 prog.planner = MaterializationPlanner(load_preset(args.planner))
             return attach_vision(args, cfg, weights, prog)
+    elif getattr(args, "_package", None) is not None:
+        def factory():
+            from .runtime.program import PackageProgram
+            prog = PackageProgram(args._package, weights, max_lanes=args.max_lanes, max_context=args.max_context)
+            apply_cold_policy(args, prog)
+            return prog
     else:
         def factory():
             prog = ReferenceProgram(cfg, weights, max_lanes=args.max_lanes, max_context=args.max_context,

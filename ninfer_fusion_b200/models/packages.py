@@ -56,6 +56,8 @@ class Package:
     tie_word_embeddings: bool = False
     config: Optional[ModelConfig] = None      # set for packages the hybrid runtime serves
     notes: str = ""
+    qk_scale: float = 1.0                     # learned-constant factor on q . k (on top of 1 / sqrt(head_dim))
+    output_multiplier: float = 1.0            # factor on the logits before soft-capping
 
     def count(self, kind: str) -> int:
         return sum(1 for l in self.layers if l.kind == kind)
@@ -99,7 +101,8 @@ def _muse() -> Package:
     return Package("muse-glimmer-30b", 6656, 52, 19968, 202048, kinds,
                    frozenset({"sliding-window-attention", "head-dim-128", "nope-layers", "logit-softcap", "qk-norm",
                               "post-branch-norms", "qk-scale-factor", "all-attention-schedule", "swiglu-mlp"}),
-                   final_logit_softcap=20.0, notes="output multiplier 0.19611613513818404, vocab rows padded to 202112")
+                   final_logit_softcap=20.0, output_multiplier=0.19611613513818404,
+                   notes="output multiplier 0.19611613513818404, vocab rows padded to 202112")
 
 
 def _gemma() -> Package:
@@ -143,10 +146,24 @@ def construct(model_id: str, have: FrozenSet[str] = ENGINE_CAPABILITIES) -> Mode
     return p.config
 
 
+def construct_oracle(model_id: str, layers: int = 0, vocab: int = 0, hidden_div: int = 1) -> Package:
+    """The package as the CPU oracle runtime serves it (models/all_attention.py): attention-only schedules, whatever
+    the GPU gate says about them.  `model_id@N` or `layers` takes the first N layers of the schedule."""
+    base, _, n = model_id.partition("@")
+    p = lookup(base)
+    if p.count(GDN):
+        raise PackageRefused(f"{base}: a GDN hybrid is served by the hybrid runtime, not by the attention-only oracle")
+    n_layers = int(n) if n else int(layers)
+    if n_layers or vocab or hidden_div > 1:
+        from .all_attention import shrink_package
+        p = shrink_package(p, n_layers or p.n_layers, vocab or None, hidden_div)
+    return p
+
+
 def describe(model_id: str) -> dict:
     p = lookup(model_id)
     return {"model_id": p.model_id, "hidden": p.hidden, "layers": p.n_layers, "full": p.count(FULL),
             "sliding": p.count(SLIDING), "gdn": p.count(GDN), "intermediate": p.intermediate, "vocab": p.vocab,
             "activation": p.activation, "final_logit_softcap": p.final_logit_softcap,
             "needs": sorted(p.needs), "missing": list(p.missing()), "servable": not p.missing() and p.config is not None,
-            "notes": p.notes}
+            "oracle_runtime": p.count(GDN) == 0 or p.config is not None, "notes": p.notes}

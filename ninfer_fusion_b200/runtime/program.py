@@ -600,3 +600,19 @@ class ReferenceProgram(ProgramBase):
             lane.last_token = self._sample(lane, self.model.logits(h)[0])
             out.append(lane.last_token)
         return out
+
+
+class PackageProgram(ReferenceProgram):
+    """CPU program of an attention-only package on its fp32 oracle (models/all_attention.py): the same lanes, sampling,
+    frontiers and cold copies as the hybrid oracle program, another decoder underneath."""
+
+    def __init__(self, pkg, weights, max_lanes: int = 8, max_context: int = 4096):
+        from ..models.all_attention import PackageReference, PackageSequence, package_model_config
+        ProgramBase.__init__(self, package_model_config(pkg, max_context), max_lanes, max_context)
+        self.pkg = pkg
+        self.model = PackageReference(pkg, weights)
+        self._Seq = lambda cfg, fmt: PackageSequence(pkg)
+        self.kv_fmt = R.KV_BF16
+        self._seqs: Dict[int, object] = {}
+        self._slots = 0
+
