@@ -716,6 +716,9 @@ def cmd_serve(args) -> int:
                                                             "frequency_penalty") if getattr(args, k, None) is not None}
     svc.force_greedy, svc.prefix_reuse = bool(args.greedy), not args.no_prefix_reuse
     svc.media_threads = max(1, int(args.media_preprocess_threads))
+    if args.allow_remote_media:
+        from .frontend import media as _media
+        _media.REMOTE_FETCH["enabled"] = True
     svc.default_thinking_budget = int(args.default_thinking_budget) or None
     if args.sampling_seed is not None:
         svc.fixed_seed = int(args.sampling_seed)
@@ -1012,6 +1015,9 @@ def main(argv=None) -> int:
     s.add_argument("--max-long-anchors-per-continuation", type=int, default=0, help="long anchors kept per session (0: 3)")
     s.add_argument("--host-kv-mib", type=float, default=0.0, help="pinned host budget for frontiers pushed out of the device pool")
     s.add_argument("--cors", action="store_true", help="permissive browser CORS headers")
+    s.add_argument("--allow-remote-media", action="store_true",
+                   help="fetch http(s):// image / video URLs of requests (size-bounded, 10 s, at most 3 redirects); off: "
+                        "clients send data: URIs")
     for flag, typ in (("temperature", float), ("top-p", float), ("top-k", int), ("min-p", float),
                       ("presence-penalty", float), ("frequency-penalty", float)):
         s.add_argument(f"--{flag}", type=typ, default=None, help=f"process-level {flag} default (a request's own value wins)")

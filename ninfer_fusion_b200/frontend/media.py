@@ -310,10 +310,43 @@ def collect_media(messages: Sequence[dict]) -> List[Tuple[str, object]]:
     return out
 
 
+REMOTE_FETCH = {"enabled": False, "timeout_s": 10.0, "max_redirects": 3}   # set by the gateway (--allow-remote-media)
+
+
+def fetch_remote(url: str, max_bytes: int, timeout_s: float = 10.0, max_redirects: int = 3) -> bytes:
+    """Size-bounded HTTP(S) download of one media item: refuses other schemes, follows at most `max_redirects`
+    redirects, refuses a declared or actual body larger than `max_bytes` (it stops reading at the limit), and turns
+    every transport failure into a ValueError so that a bad URL fails the request, not the server.
+    Reference: src/product/media_acquire/acquire.cpp (path / data: URI / HTTP(S), size-bounded)."""
+    import urllib.error
+    import urllib.request
+
+    class Bounded(urllib.request.HTTPRedirectHandler):
+        max_redirections = max_redirects
+    if not url.startswith(("http://", "https://")):
+        raise ValueError("only http:// and https:// media URLs are fetched")
+    opener = urllib.request.build_opener(Bounded)
+    try:
+        with opener.open(urllib.request.Request(url, headers={"User-Agent": "ninfer-media/1"}), timeout=timeout_s) as r:
+            if not r.geturl().startswith(("http://", "https://")):
+                raise ValueError("media URL redirected to another scheme")
+            declared = r.headers.get("Content-Length")
+            if declared is not None and declared.isdigit() and int(declared) > max_bytes:
+                raise ValueError("media source exceeds the byte limit")
+            body = r.read(max_bytes + 1)
+    except (urllib.error.URLError, OSError) as e:
+        raise ValueError(f"media URL could not be fetched: {getattr(e, 'reason', e)}") from None
+    if len(body) > max_bytes:
+        raise ValueError("media source exceeds the byte limit")
+    if not body:
+        raise ValueError("media URL returned no content")
+    return body
+
+
 def acquire_source(source, allow_files: bool = False, max_bytes: int = 256 * 1024 * 1024):
     """Turns a message's media reference into something `decode_media` accepts.  `data:` URIs and in-memory
-    objects always pass; `file://` / plain paths only when the gateway allows local files; remote URLs are refused
-    (this build has no network fetcher)."""
+    objects always pass; `file://` / plain paths only when the gateway allows local files; remote URLs are fetched
+    (size-bounded) only when the gateway switched remote media on."""
     if source is None:
         raise ValueError("media part has no source")
     if not isinstance(source, str):
@@ -323,7 +356,9 @@ def acquire_source(source, allow_files: bool = False, max_bytes: int = 256 * 102
             raise ValueError("media source exceeds the byte limit")
         return source
     if source.startswith(("http://", "https://")):
-        raise ValueError("remote media URLs are not fetched by this server; send a data: URI")
+        if not REMOTE_FETCH["enabled"]:
+            raise ValueError("remote media URLs are not fetched by this server; send a data: URI")
+        return fetch_remote(source, max_bytes, REMOTE_FETCH["timeout_s"], REMOTE_FETCH["max_redirects"])
     path = source[len("file://"):] if source.startswith("file://") else source
     if not allow_files:
         raise ValueError("local media files are disabled on this gateway")

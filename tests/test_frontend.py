@@ -196,3 +196,65 @@ def test_cold_policy_flags_are_checked_and_applied(tmp_path):
                 ns(cold_policy="host-then-disk", cold_host_bytes="1m")):
         with pytest.raises(SystemExit):
             cli.apply_cold_policy(bad, Prog())
+
+
+def test_remote_media_is_fetched_size_bounded_and_only_when_switched_on():
+    import io
+    import threading
+    from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+
+    import numpy as np
+    import pytest
+    from PIL import Image
+
+    from ninfer_fusion_b200.frontend import media as M
+    buf = io.BytesIO()
+    Image.fromarray(np.full((8, 8, 3), 200, dtype=np.uint8)).save(buf, format="PNG")
+    png = buf.getvalue()
+
+    class H(BaseHTTPRequestHandler):
+        def log_message(self, *a):
+            pass
+
+        def do_GET(self):
+            if self.path == "/img.png":
+                body = png
+            elif self.path == "/big":
+                body = b"x" * 5000
+            elif self.path.startswith("/hop"):
+                n = int(self.path[4:] or 0)
+                self.send_response(302)
+                self.send_header("Location", f"/hop{n + 1}" if n < 10 else "/img.png")
+                self.send_header("Content-Length", "0")
+                self.end_headers()
+                return
+            else:
+                self.send_response(404)
+                self.send_header("Content-Length", "0")
+                self.end_headers()
+                return
+            self.send_response(200)
+            self.send_header("Content-Length", str(len(body)))
+            self.end_headers()
+            self.wfile.write(body)
+    srv = ThreadingHTTPServer(("127.0.0.1", 0), H)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    base = f"http://127.0.0.1:{srv.server_address[1]}"
+    try:
+        with pytest.raises(ValueError, match="not fetched"):
+            M.acquire_source(base + "/img.png")                      # off by default
+        M.REMOTE_FETCH["enabled"] = True
+        got = M.acquire_source(base + "/img.png", max_bytes=1 << 20)
+        assert got == png and M.decode_media(got).shape == (1, 8, 8, 3)
+        with pytest.raises(ValueError, match="byte limit"):
+            M.acquire_source(base + "/big", max_bytes=1000)
+        with pytest.raises(ValueError, match="could not be fetched"):
+            M.acquire_source(base + "/missing", max_bytes=1000)
+        with pytest.raises(ValueError, match="could not be fetched"):
+            M.acquire_source(base + "/hop0", max_bytes=1 << 20)      # more redirects than allowed
+        with pytest.raises(ValueError, match="only http"):
+            M.fetch_remote("ftp://example.invalid/x", 10)
+    finally:
+        M.REMOTE_FETCH["enabled"] = False
+        srv.shutdown()
+        srv.server_close()
