@@ -71,6 +71,8 @@ class ServeState:
         self.default_thinking = bool(default_thinking)     # thinking mode of a request that names none
         self.max_stored_bytes = max(1, int(max_stored_bytes))
         self.stored_bytes = 0
+        from .rag import DocumentStore
+        self.documents = DocumentStore()       # retrieval-augmented answering (serve/rag.py)
         self.log = RequestLog(log_path, throughput_every_s=log_interval_s if log_interval_s > 0 else float("inf"))
         # local response store: bounded, the least recently used entry goes first (a stored response keeps its
         # whole message history, so an unbounded store would grow with the server's life)
@@ -257,10 +259,11 @@ def make_handler(state: ServeState):
             path = self.path.split("?", 1)[0].rstrip("/") or "/"
             if path == "/health":
                 return self._send_json(200, svc.health())
-            if path in ("/", "/console"):
-                # the browser console: a static page without data of its own, so it needs no key (its calls do)
+            if path in ("/", "/console", "/rag"):
+                # the browser pages: static, without data of their own, so they need no key (their calls do)
                 from .console import page_bytes
-                data = page_bytes()
+                from .rag import page_bytes as rag_page
+                data = rag_page() if path == "/rag" else page_bytes()
                 self.send_response(200)
                 self.send_header("Content-Type", "text/html; charset=utf-8")
                 self.send_header("Content-Length", str(len(data)))
@@ -277,6 +280,8 @@ def make_handler(state: ServeState):
                 if path[len("/v1/models/"):] == svc.model_id:
                     return self._send_json(200, model_obj)
                 return self._error(404, "model not found", "not_found_error")
+            if path == "/v1/rag/documents":
+                return self._send_json(200, {"object": "list", "data": state.documents.list()})
             if path.startswith("/v1/responses/"):
                 rest = path[len("/v1/responses/"):]
                 rid, _, tail = rest.partition("/")
@@ -307,6 +312,11 @@ def make_handler(state: ServeState):
                 if found:
                     return self._send_json(200, {"id": rid, "object": "response", "deleted": True})
                 return self._error(404, f"response '{rid}' not found", "not_found_error")
+            if path.startswith("/v1/rag/documents/"):
+                did = path[len("/v1/rag/documents/"):]
+                if state.documents.remove(did):
+                    return self._send_json(200, {"id": did, "object": "rag.document", "deleted": True})
+                return self._error(404, f"document '{did}' not found", "not_found_error")
             return self._error(404, f"no route for DELETE {path}", "not_found_error")
 
         def do_POST(self):
@@ -356,6 +366,26 @@ def make_handler(state: ServeState):
                         return obj
                     return self._run("openai_responses", req, o["stream"], build,
                                      lambda ev: P.openai_responses_stream(ev, svc.model_id, remember))
+                if path == "/v1/rag/documents":
+                    try:
+                        return self._send_json(200, dict(state.documents.add(body.get("title", ""), body.get("text")), object="rag.document"))
+                    except ValueError as e:
+                        raise P.BadRequest(str(e), "text") from None
+                if path == "/v1/rag/query":
+                    query = body.get("query")
+                    if not isinstance(query, str) or not query.strip():
+                        raise P.BadRequest("query must be a non-empty string", "query")
+                    hits = state.documents.retrieve(query, int(body.get("top_k", 4)))
+                    msgs, sources = state.documents.build_messages(query, hits)
+                    chat = {k: body[k] for k in ("max_tokens", "temperature", "top_p", "top_k_sampling", "seed", "thinking_budget")
+                            if k in body}
+                    chat["messages"] = msgs
+                    chat.setdefault("enable_thinking", bool(body.get("enable_thinking", False)))
+                    req, _ = P.parse_openai_chat(chat)
+                    return self._run("rag_query", req, False,
+                                     lambda r: {"object": "rag.answer", "answer": r.content, "sources": sources,
+                                                "usage": P._usage_openai(r), "finish_reason": r.finish_reason},
+                                     lambda ev: iter(()))
                 if path == "/v1/responses/input_tokens":
                     req, _ = P.parse_openai_responses(body, dict(state.responses))
                     return self._send_json(200, {"object": "response.input_tokens", "input_tokens": svc.count_tokens(req)})

@@ -490,3 +490,49 @@ def test_thinking_budget_reaches_the_engine_from_every_protocol(server):
         assert svc._options(GenRequest(prompt="x", enable_thinking=False)).thinking_budget is None   # nothing to cap
     finally:
         svc.default_thinking_budget = None
+
+
+def test_rag_store_chunks_indexes_and_retrieves():
+    from ninfer_fusion_b200.serve import rag
+    assert rag.tokenize("Hello, World_1! 東京") == ["hello", "world_1", "東", "京"]
+    text = "\n\n".join(f"Paragraph {i} talks about topic{i}. " + "filler words here. " * 20 for i in range(6))
+    parts = rag.chunk_text(text, 500)
+    assert len(parts) >= 6 and all(len(p) <= 500 for p in parts) and "topic3" in "".join(parts)
+    assert all(len(p) <= 80 for p in rag.chunk_text("x" * 300, 80))              # a sentence longer than the limit is cut
+    store = rag.DocumentStore(max_documents=3, max_bytes=10_000, chunk_chars=300)
+    a = store.add("fruit", "Apples are red or green. They grow on trees.\n\nBananas are yellow and grow in bunches.")
+    b = store.add("metal", "Iron rusts in wet air. Copper turns green over the years.\n\nGold does not tarnish.")
+    hits = store.retrieve("what colour are bananas", top_k=2)
+    assert hits and hits[0][1].document == a["id"] and "Bananas" in hits[0][1].text
+    assert store.retrieve("zebra quantum", 3) == [] and store.retrieve("", 3) == []
+    msgs, sources = store.build_messages("Does gold tarnish?", store.retrieve("gold tarnish", 2))
+    assert msgs[0]["role"] == "system" and "[1] metal" in msgs[0]["content"] and sources[0]["document"] == b["id"]
+    assert store.remove(a["id"]) and not store.remove(a["id"]) and store.retrieve("bananas", 2) == []
+    assert "banana" not in store.df and "bananas" not in store.df
+    for i in range(4):                                                            # bounded: the oldest document goes first
+        store.add(f"d{i}", f"document number {i} about widgets")
+    assert len(store.list()) == 3 and b["id"] not in [d["id"] for d in store.list()]
+    with pytest.raises(ValueError):
+        store.add("empty", "   ")
+    with pytest.raises(ValueError):
+        store.add("huge", "x" * 20_000)
+
+
+def test_rag_routes_answer_with_sources(server):
+    port, _, _ = server
+    st, _, data = call(port, "POST", "/v1/rag/documents", {"title": "handbook", "text": "The office opens at nine.\n\nLunch is at noon."})
+    doc = json.loads(data)
+    assert st == 200 and doc["chunks"] >= 1
+    st, _, data = call(port, "GET", "/v1/rag/documents")
+    assert st == 200 and doc["id"] in [d["id"] for d in json.loads(data)["data"]]
+    st, _, data = call(port, "POST", "/v1/rag/query", {"query": "When does the office open?", "top_k": 2, "max_tokens": 3})
+    ans = json.loads(data)
+    assert st == 200 and ans["object"] == "rag.answer" and ans["sources"] and ans["sources"][0]["title"] == "handbook"
+    assert ans["usage"]["completion_tokens"] <= 3 and "office" in ans["sources"][0]["text"]
+    assert call(port, "POST", "/v1/rag/query", {"query": ""})[0] == 400
+    assert call(port, "POST", "/v1/rag/documents", {"title": "x", "text": ""})[0] == 400
+    assert call(port, "GET", "/v1/rag/documents", key=None)[0] == 401                 # the data routes need the key
+    st, ctype, page = call(port, "GET", "/rag", key=None)
+    assert st == 200 and "text/html" in ctype and b"/v1/rag/query" in page            # the page itself holds no data
+    assert call(port, "DELETE", f"/v1/rag/documents/{doc['id']}")[0] == 200
+    assert call(port, "DELETE", f"/v1/rag/documents/{doc['id']}")[0] == 404
