@@ -119,7 +119,25 @@ def advise(path: str, gpu: str = "b200", context: int = 32768, lanes: int = 8, w
     out["fit"] = rows
     best = next((r for r in rows if r["weights"] == "bf16" and r["fits"]), None) or next((r for r in rows if r["fits"]), None)
     if best is None:
-        out["verdict"] = f"does not fit one {gpu} at {lanes} x {context} tokens in any weight format: shard it (--tp) or shorten the context"
+        # nothing fits resident: would it fit with part of the weights in pinned host memory, and at what price?
+        from ..runtime.offload_budget import offload_verdict
+        spec = GPUS[gpu]
+        kv_values = 2 * len(cfg.attn_layers) * cfg.n_kv_heads * cfg.head_dim / world
+        state = len(cfg.gdn_layers) * (cfg.gdn_v_heads * cfg.gdn_head_dim * cfg.gdn_head_dim * 4) / world
+        kv = int(lanes * context * kv_values * KV_BITS["nvfp4"] / 8)
+        small = min(rows, key=lambda r: r["weight_gib"])
+        v = offload_verdict(int(small["weight_gib"] * (1 << 30)), kv, int(2 * lanes * state + 6 * (1 << 30)),
+                            int(spec["mem_gib"] * (1 << 30)))
+        out["offload"] = {"weights": small["weights"], "state": v.state, "offloaded_gib": round(v.offloaded_bytes / (1 << 30), 2),
+                          "added_ms_per_round": round(v.added_ms_per_round, 1), "note": v.note}
+        if v.state == "offload":
+            keep = small["weight_gib"] - v.offloaded_bytes / (1 << 30)
+            out["verdict"] = (f"fits one {gpu} only with weights off-loaded: {small['weights']} weights, nvfp4 KV, "
+                              f"--weight-budget-gib {keep:.0f} (about {v.added_ms_per_round:.0f} ms more per decode round); "
+                              f"sharding (--tp) avoids that price")
+        else:
+            out["verdict"] = (f"does not fit one {gpu} at {lanes} x {context} tokens in any weight format: shard it (--tp) "
+                              f"or shorten the context")
         return out
     out["verdict"] = f"servable as {cfg.name}: {best['weights']} weights ({best['weight_gib']} GiB), {best['widest_kv']} KV"
     art = path if rec["kind"] == "ninfer" else "model.ninfer"

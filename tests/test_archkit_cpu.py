@@ -120,3 +120,28 @@ def test_model_import_recognises_judges_and_advises(tmp_path):
     assert MI.advise(str(junk))["verdict"].startswith("unknown") and MI.recognise(str(tmp_path / "nope"))["kind"] == "unknown"
     from ninfer_fusion_b200.archkit.__main__ import main as archkit_main
     assert archkit_main(["import", str(hf)]) == 0 and archkit_main(["import", str(junk)]) == 1
+
+
+def test_offload_budget_math_and_the_import_advice_that_uses_it(tmp_path):
+    from ninfer_fusion_b200.archkit import model_import as MI
+    from ninfer_fusion_b200.runtime.offload_budget import KvCapacityFit, KvCapacityPoint, offload_verdict
+    fit = KvCapacityFit.from_points(KvCapacityPoint(1000, 10_000_000 + 4096, 16.0), KvCapacityPoint(4000, 20_000_000 + 4096, 8.0))
+    assert fit.bytes_per_token_bit == pytest.approx(625.0) and fit.constant_bytes == pytest.approx(4096.0)
+    assert fit.bytes_for(2000, 8.0) == pytest.approx(10_004_096.0)
+    assert fit.bits_within(2000, 10_004_096) == pytest.approx(8.0) and fit.bits_within(0, 1) == 0.0
+    with pytest.raises(ValueError):
+        KvCapacityFit.from_points(KvCapacityPoint(1000, 1, 8.0), KvCapacityPoint(500, 2, 16.0))
+    G = 1 << 30
+    assert offload_verdict(50 * G, 20 * G, 5 * G, 80 * G).state == "resident"
+    v = offload_verdict(50 * G, 40 * G, 5 * G, 80 * G, host_link_gbs=50.0)
+    assert v.state == "offload" and v.offloaded_bytes == 15 * G and v.added_ms_per_round == pytest.approx(15 * G / 50e9 * 1e3)
+    assert offload_verdict(50 * G, 80 * G, 5 * G, 80 * G).state == "does_not_fit"            # the KV leaves no room for the weights
+    assert offload_verdict(50 * G, 40 * G, 5 * G, 80 * G, host_bytes=10 * G).state == "does_not_fit"
+    # the import advice: 27B on a 32 GiB card at a long context fits only with off-loaded weights, and says what that costs
+    hf = tmp_path / "Qwen3.6-27B"
+    hf.mkdir()
+    (hf / "config.json").write_text(json.dumps(_qwen_hf()))
+    adv = MI.advise(str(hf), gpu="rtx5090", context=262144, lanes=4)
+    assert adv["offload"]["state"] == "offload" and adv["offload"]["weights"] == "q4"
+    if adv["offload"]["state"] == "offload":
+        assert "--weight-budget-gib" in adv["verdict"] and adv["offload"]["added_ms_per_round"] > 0
