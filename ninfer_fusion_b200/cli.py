@@ -120,6 +120,15 @@ def add_model_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--cold-disk-path", default="", help="directory of the file tier")
     ap.add_argument("--cold-disk-bytes", default="0", help="file tier budget, N[k|m|g]")
     ap.add_argument("--cold-entropy", action="store_true", help="entropy-code frontiers written to the file tier")
+    ap.add_argument("--cold-journal", action="store_true",
+                    help="keep the file tier's frontier -> file map in a journal inside --cold-disk-path and adopt the frontiers "
+                         "a previous process left there (bound to the program, the model, the KV storage and the weights)")
+    ap.add_argument("--cold-journal-flush", default="none", choices=["none", "flush", "fsync"],
+                    help="what is forced after every journal record (the journal is a mirror: losing its tail costs a re-prefill)")
+    ap.add_argument("--cold-read-gbs", type=float, default=0.0,
+                    help="measured read rate of the file tier in GB/s; with --cold-prefill-tok-s a frontier is read back "
+                         "only when that beats prefilling its tokens again (0 = always read back)")
+    ap.add_argument("--cold-prefill-tok-s", type=float, default=0.0, help="measured prefill rate in tokens/s for that comparison")
     ap.add_argument("--cold-slots", action="store_true",
                     help="int8 KV pages leave the device as requantised cold slots (lossy, 0.55 of the bytes)")
     ap.add_argument("--anchor-interval", type=int, default=0,
@@ -417,6 +426,8 @@ def apply_cold_policy(args, prog) -> None:
     if policy == "none":
         if host_b or disk_b or path:
             raise SystemExit("--cold-host-bytes / --cold-disk-* need --cold-policy host | disk | host-then-disk")
+        if getattr(args, "cold_journal", False) or getattr(args, "cold_read_gbs", 0.0) or getattr(args, "cold_prefill_tok_s", 0.0):
+            raise SystemExit("--cold-journal / --cold-read-gbs / --cold-prefill-tok-s need a file tier (--cold-policy disk | host-then-disk)")
         return
     if policy in ("host", "host-then-disk") and host_b <= 0:
         raise SystemExit(f"--cold-policy {policy} needs --cold-host-bytes")
@@ -429,6 +440,33 @@ def apply_cold_policy(args, prog) -> None:
     if policy in ("disk", "host-then-disk"):
         prog.cold_dir, prog.disk_budget_bytes = path, disk_b
         prog.cold_entropy = bool(getattr(args, "cold_entropy", False))
+    journal = bool(getattr(args, "cold_journal", False))
+    read_gbs, tok_s = float(getattr(args, "cold_read_gbs", 0.0) or 0.0), float(getattr(args, "cold_prefill_tok_s", 0.0) or 0.0)
+    if (journal or read_gbs or tok_s) and policy not in ("disk", "host-then-disk"):
+        raise SystemExit("--cold-journal / --cold-read-gbs / --cold-prefill-tok-s need a file tier (--cold-policy disk | host-then-disk)")
+    if (read_gbs > 0) != (tok_s > 0):
+        raise SystemExit("--cold-read-gbs and --cold-prefill-tok-s are given together")
+    if read_gbs > 0:
+        from .runtime.cold_journal import RecallCost
+        prog.recall_cost = RecallCost(read_gbs=read_gbs, prefill_tok_s=tok_s)
+    if journal:
+        rep = prog.enable_cold_journal(weights_id=_weights_identity(args), flush=getattr(args, "cold_journal_flush", "none"))
+        print(f"[cold-journal] adopted {rep['adopted']} frontiers ({rep['records']} records, {len(rep['holes'])} holes, "
+              f"{rep['orphans_removed']} orphan files removed)" + (f"; previous journal refused: {rep['refused']}" if rep["refused"] else ""),
+              file=sys.stderr, flush=True)
+
+
+def _weights_identity(args) -> str:
+    """What names the set of weights a cold copy was computed with: the artifact file (path, size, modification time) or
+    the seed of random weights."""
+    art = getattr(args, "artifact", None)
+    if art:
+        try:
+            st = os.stat(art)
+            return f"artifact:{os.path.abspath(art)}:{st.st_size}:{int(st.st_mtime)}"
+        except OSError:
+            return f"artifact:{art}"
+    return f"random:{getattr(args, 'model', '')}:{getattr(args, 'seed', 0)}:{getattr(args, 'weights', '')}"
 
 
 def _kv_spec_from_ceilings(args, cfg: ModelConfig) -> None:

@@ -102,6 +102,10 @@ class ProgramBase:
         self.cold_dir: Optional[str] = None
         self.cold_entropy = False   # entropy-code frontiers written to the disk tier (kv/cold_codec.py)
         self.cold_stats = {"demoted_host": 0, "demoted_disk": 0, "promoted": 0, "dropped": 0}
+        # persistent map frontier -> disk file (runtime/cold_journal.py): off until enable_cold_journal()
+        self.cold_journal = None
+        self.recall_cost = None     # RecallCost: read a disk frontier back only when that beats prefilling it again
+        self._cold_nonce = ""
         # shared-prefix catalogue: frontiers of prompt prefixes that any request may start from (system prompts)
         self.max_shared_prefixes = 8
         # long anchors: while a long prompt is prefilled, a frontier is kept every `anchor_interval` tokens (0 = off) so
@@ -276,7 +280,7 @@ class ProgramBase:
             victim = min((c for c in self.checkpoints if c.tier == "host"), key=lambda c: c.last_used)
             on_disk = sum(c.nbytes for c in self.checkpoints if c.tier == "disk")
             if self.cold_dir and on_disk + victim.nbytes <= self.disk_budget_bytes:
-                path = os.path.join(self.cold_dir, f"ckpt_{id(victim):x}_{self._clock}.pt")
+                path = os.path.join(self.cold_dir, f"ckpt_{id(victim):x}_{self._clock}{self._cold_nonce}.pt")
                 try:
                     os.makedirs(self.cold_dir, exist_ok=True)
                     if self.cold_entropy and set(victim.handle) == {"n_pages", "tensors"}:
@@ -300,6 +304,10 @@ class ProgramBase:
                     continue
                 victim.handle, victim.tier = {"path": path}, "disk"
                 self.cold_stats["demoted_disk"] += 1
+                if self.cold_journal is not None:
+                    from .cold_journal import SpillRecord
+                    self.cold_journal.spill(SpillRecord(os.path.basename(path), victim.nbytes, os.path.getsize(path),
+                                                        victim.session, victim.kind, list(victim.tokens)))
             else:
                 self.checkpoints.remove(victim)
                 self.cold_stats["dropped"] += 1
@@ -310,18 +318,32 @@ class ProgramBase:
     def _forget_cold(self, c: Checkpoint) -> None:
         import os
         if c.tier == "disk":
-            try:
-                os.remove(c.handle["path"])
-            except OSError:
-                pass
+            self._release_cold_file(c.handle["path"], "dropped")
         self.checkpoints.remove(c)
         self.cold_stats["dropped"] += 1
+
+    def _release_cold_file(self, path: str, reason: str) -> None:
+        import os
+        try:
+            os.remove(path)
+        except OSError:
+            pass
+        if self.cold_journal is not None:
+            self.cold_journal.release(os.path.basename(path), reason)
 
     def _warm_up(self, c: Checkpoint) -> bool:
         """Brings a cold frontier back into the device pool (disk -> host -> device).  False if there is no room."""
         if c.tier == "gpu":
             return True
-        cold = self._read_cold_file(c.handle["path"]) if c.tier == "disk" else c.handle
+        if c.tier == "disk" and self.recall_cost is not None and not self.recall_cost.worthwhile(c.nbytes, len(c.tokens)):
+            return False     # prefilling these tokens again is faster than reading their cold copy
+        try:
+            cold = self._read_cold_file(c.handle["path"]) if c.tier == "disk" else c.handle
+        except Exception:
+            # a cold file that cannot be read back (damaged, truncated, gone) costs this frontier, not the request
+            self.cold_stats["read_failed"] = self.cold_stats.get("read_failed", 0) + 1
+            self._forget_cold(c)
+            return False
         handle = self._promote(cold)
         while handle is None:
             others = [o for o in self.checkpoints if o.tier == "gpu" and o is not c]
@@ -329,14 +351,50 @@ class ProgramBase:
                 return False
             handle = self._promote(cold)
         if c.tier == "disk":
-            import os
-            try:
-                os.remove(c.handle["path"])
-            except OSError:
-                pass
+            self._release_cold_file(c.handle["path"], "promoted")
         c.handle, c.tier, c.nbytes = handle, "gpu", 0
         self.cold_stats["promoted"] += 1
         return True
+
+    def cold_fingerprint(self, weights_id: str = "") -> str:
+        """What a cold copy is only valid for: this program class, model geometry, KV storage and set of weights."""
+        cfg = self.cfg
+        kv = getattr(self, "kv_layer_formats", None) or getattr(self, "kv_dtype", "") or "reference"
+        return "|".join(str(x) for x in (type(self).__name__, cfg.name, cfg.n_layers, cfg.hidden, cfg.n_kv_heads, cfg.head_dim,
+                                         kv, weights_id))
+
+    def enable_cold_journal(self, weights_id: str = "", flush: str = "none", remove_orphans: bool = True) -> dict:
+        """Keeps the disk tier's frontier -> file map in a journal inside the cold directory and adopts the frontiers
+        a previous process left there: each becomes a disk-tier frontier of its session again, reusable for a prompt
+        that starts with exactly its tokens.  Returns what was found."""
+        import os
+        from .cold_journal import ColdJournal
+        if not self.cold_dir or self.disk_budget_bytes <= 0:
+            raise ValueError("the cold journal needs a disk tier (a cold directory and a byte budget)")
+        self._cold_nonce = "_" + os.urandom(4).hex()      # file names of this process never collide with adopted ones
+        j = ColdJournal(self.cold_dir, self.cold_fingerprint(weights_id), flush)
+        self.cold_journal = j
+        good, holes = j.adoptable()
+        adopted = skipped = 0
+        on_disk = sum(c.nbytes for c in self.checkpoints if c.tier == "disk")
+        for r in sorted(good, key=lambda r: -len(r.tokens)):
+            if on_disk + r.nbytes > self.disk_budget_bytes:
+                self._release_cold_file(os.path.join(self.cold_dir, r.file), "over budget at adoption")
+                skipped += 1
+                continue
+            self.checkpoints.append(Checkpoint(r.session, r.kind, list(r.tokens), {"path": os.path.join(self.cold_dir, r.file)},
+                                               0.0, "disk", r.nbytes))
+            on_disk += r.nbytes
+            adopted += 1
+        orphans = j.orphans() if remove_orphans else []
+        for name in orphans:
+            try:
+                os.remove(os.path.join(self.cold_dir, name))
+            except OSError:
+                pass
+        self.cold_stats["adopted"] = self.cold_stats.get("adopted", 0) + adopted
+        return {"adopted": adopted, "over_budget": skipped, "holes": holes, "orphans_removed": len(orphans),
+                "refused": j.report.refused, "ignored_tail_bytes": j.report.ignored_tail_bytes, "records": j.report.records}
 
     @staticmethod
     def _read_cold_file(path: str):
