@@ -103,6 +103,24 @@ def _anthropic_cache_marked(obj) -> bool:
 # =========================================================================================================
 # OpenAI chat completions
 # =========================================================================================================
+def _soft_max(body: dict, key: str, hard: int) -> Optional[int]:
+    """Extension field: completion tokens after which the generation ends at the next syntax-safe boundary."""
+    v = body.get(key)
+    if v is None:
+        return None
+    if not isinstance(v, int) or isinstance(v, bool) or v < 1:
+        raise BadRequest(f"{key} must be a positive integer", key)
+    if v > hard:
+        raise BadRequest(f"{key} must not exceed the hard limit ({hard})", key)
+    return v
+
+
+def _with_boundary(obj: dict, res: GenResult) -> dict:
+    if getattr(res, "stop_boundary", None):
+        obj["stop_boundary"] = res.stop_boundary       # out of band: never part of the generated text
+    return obj
+
+
 def parse_openai_chat(body: dict) -> Tuple[GenRequest, dict]:
     msgs = body.get("messages")
     if not isinstance(msgs, list) or not msgs:
@@ -127,7 +145,8 @@ def parse_openai_chat(body: dict) -> Tuple[GenRequest, dict]:
                      presence_penalty=_num(body, "presence_penalty", -2.0, 2.0),
                      frequency_penalty=_num(body, "frequency_penalty", -2.0, 2.0),
                      seed=_num(body, "seed", 0, 2 ** 63 - 1, int), stop=_stops(body.get("stop")),
-                     enable_thinking=thinking, session=body.get("user"), **_openai_cache_hints(body, msgs))
+                     enable_thinking=thinking, session=body.get("user"),
+                     soft_max_tokens=_soft_max(body, "soft_max_tokens", int(max_tokens)), **_openai_cache_hints(body, msgs))
     opts = {"stream": bool(body.get("stream", False)),
             "include_usage": bool((body.get("stream_options") or {}).get("include_usage", False))}
     return req, opts
@@ -150,20 +169,21 @@ def openai_chat_response(res: GenResult, model: str) -> dict:
     if res.tool_calls:
         msg["tool_calls"] = [{"id": f"call_{uuid.uuid4().hex[:24]}", "type": "function",
                               "function": {"name": c.name, "arguments": c.arguments}} for c in res.tool_calls]
-    return {"id": f"chatcmpl-{res.request_id}", "object": "chat.completion", "created": int(time.time()), "model": model,
-            "choices": [{"index": 0, "message": msg, "finish_reason": _finish_openai(res.finish_reason), "logprobs": None}],
-            "usage": _usage_openai(res)}
+    return _with_boundary(
+        {"id": f"chatcmpl-{res.request_id}", "object": "chat.completion", "created": int(time.time()), "model": model,
+         "choices": [{"index": 0, "message": msg, "finish_reason": _finish_openai(res.finish_reason), "logprobs": None}],
+         "usage": _usage_openai(res)}, res)
 
 
 def openai_chat_stream(events: Iterator[tuple], model: str, include_usage: bool) -> Iterator[bytes]:
     cid, created = f"chatcmpl-{uuid.uuid4().hex[:24]}", int(time.time())
 
-    def chunk(delta: dict, finish=None, usage=None) -> bytes:
+    def chunk(delta: dict, finish=None, usage=None, res=None) -> bytes:
         d = {"id": cid, "object": "chat.completion.chunk", "created": created, "model": model,
              "choices": [{"index": 0, "delta": delta, "finish_reason": finish}]}
         if usage is not None:
             d["usage"] = usage
-        return sse(d)
+        return sse(_with_boundary(d, res) if res is not None else d)
 
     yield chunk({"role": "assistant", "content": ""})
     n_calls = 0
@@ -180,7 +200,7 @@ def openai_chat_stream(events: Iterator[tuple], model: str, include_usage: bool)
                 n_calls += 1
         else:
             res: GenResult = item
-            yield chunk({}, finish=_finish_openai(res.finish_reason))
+            yield chunk({}, finish=_finish_openai(res.finish_reason), res=res)
             if include_usage:
                 d = {"id": cid, "object": "chat.completion.chunk", "created": created, "model": model, "choices": [],
                      "usage": _usage_openai(res)}
@@ -235,6 +255,7 @@ def parse_openai_responses(body: dict, store: Optional[dict] = None) -> Tuple[Ge
     req = GenRequest(messages=msgs, tools=tools, max_tokens=int(body.get("max_output_tokens") or 512),
                      temperature=_num(body, "temperature", 0.0, 2.0), top_p=_num(body, "top_p", 0.0, 1.0),
                      enable_thinking=reasoning.get("effort", "medium") not in ("none", "minimal"),
+                     soft_max_tokens=_soft_max(body, "soft_max_output_tokens", int(body.get("max_output_tokens") or 512)),
                      **_openai_cache_hints(body, msgs))
     return req, {"stream": bool(body.get("stream", False)), "store": bool(body.get("store", True)), "messages": msgs}
 
@@ -251,12 +272,13 @@ def openai_responses_object(res: GenResult, model: str, status: str = "completed
         out.append({"id": f"fc_{uuid.uuid4().hex[:24]}", "type": "function_call", "status": "completed",
                     "call_id": f"call_{uuid.uuid4().hex[:24]}", "name": c.name, "arguments": c.arguments})
     incomplete = {"reason": "max_output_tokens"} if res.finish_reason == "length" else None
-    return {"id": f"resp_{res.request_id}", "object": "response", "created_at": int(time.time()),
-            "status": "incomplete" if incomplete else status, "incomplete_details": incomplete, "model": model,
-            "output": out, "output_text": res.content,
-            "usage": {"input_tokens": res.prompt_tokens, "output_tokens": res.completion_tokens,
-                      "total_tokens": res.prompt_tokens + res.completion_tokens,
-                      "input_tokens_details": {"cached_tokens": int(getattr(res, "cached_tokens", 0) or 0)}}}
+    return _with_boundary(
+        {"id": f"resp_{res.request_id}", "object": "response", "created_at": int(time.time()),
+         "status": "incomplete" if incomplete else status, "incomplete_details": incomplete, "model": model,
+         "output": out, "output_text": res.content,
+         "usage": {"input_tokens": res.prompt_tokens, "output_tokens": res.completion_tokens,
+                   "total_tokens": res.prompt_tokens + res.completion_tokens,
+                   "input_tokens_details": {"cached_tokens": int(getattr(res, "cached_tokens", 0) or 0)}}}, res)
 
 
 def openai_responses_stream(events: Iterator[tuple], model: str, on_done=None) -> Iterator[bytes]:
@@ -366,7 +388,8 @@ def parse_anthropic_messages(body: dict) -> Tuple[GenRequest, dict]:
     req = GenRequest(messages=msgs, tools=tools, max_tokens=int(body["max_tokens"]), thinking_budget=budget,
                      temperature=_num(body, "temperature", 0.0, 1.0), top_p=_num(body, "top_p", 0.0, 1.0),
                      top_k=_num(body, "top_k", 1, 20, int), stop=_stops(body.get("stop_sequences")),
-                     enable_thinking=thinking, cache_breakpoints=breakpoints)
+                     enable_thinking=thinking, cache_breakpoints=breakpoints,
+                     soft_max_tokens=_soft_max(body, "soft_max_tokens", int(body["max_tokens"])))
     return req, {"stream": bool(body.get("stream", False))}
 
 
@@ -392,12 +415,13 @@ def anthropic_message_response(res: GenResult, model: str) -> dict:
         except json.JSONDecodeError:
             inp = {"_raw": c.arguments}
         content.append({"type": "tool_use", "id": f"toolu_{uuid.uuid4().hex[:24]}", "name": c.name, "input": inp})
-    return {"id": f"msg_{res.request_id}", "type": "message", "role": "assistant", "model": model, "content": content,
-            "stop_reason": _stop_reason_anthropic(res.finish_reason), "stop_sequence": None,
-            # Anthropic counts cached reads apart from the computed input
-            "usage": {"input_tokens": res.prompt_tokens - int(getattr(res, "cached_tokens", 0) or 0),
-                      "cache_read_input_tokens": int(getattr(res, "cached_tokens", 0) or 0),
-                      "cache_creation_input_tokens": 0, "output_tokens": res.completion_tokens}}
+    return _with_boundary(
+        {"id": f"msg_{res.request_id}", "type": "message", "role": "assistant", "model": model, "content": content,
+         "stop_reason": _stop_reason_anthropic(res.finish_reason), "stop_sequence": None,
+         # Anthropic counts cached reads apart from the computed input
+         "usage": {"input_tokens": res.prompt_tokens - int(getattr(res, "cached_tokens", 0) or 0),
+                   "cache_read_input_tokens": int(getattr(res, "cached_tokens", 0) or 0),
+                   "cache_creation_input_tokens": 0, "output_tokens": res.completion_tokens}}, res)
 
 
 def anthropic_stream(events: Iterator[tuple], model: str, prompt_tokens_hint: int = 0) -> Iterator[bytes]:
@@ -450,6 +474,8 @@ def anthropic_stream(events: Iterator[tuple], model: str, prompt_tokens_hint: in
         else:
             res: GenResult = item
             yield from close()
-            yield sse({"type": "message_delta", "delta": {"stop_reason": _stop_reason_anthropic(res.finish_reason), "stop_sequence": None},
-                       "usage": {"input_tokens": res.prompt_tokens, "output_tokens": res.completion_tokens}}, "message_delta")
+            yield sse(_with_boundary({"type": "message_delta",
+                                      "delta": {"stop_reason": _stop_reason_anthropic(res.finish_reason), "stop_sequence": None},
+                                      "usage": {"input_tokens": res.prompt_tokens, "output_tokens": res.completion_tokens}}, res),
+                      "message_delta")
             yield sse({"type": "message_stop"}, "message_stop")

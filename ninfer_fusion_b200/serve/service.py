@@ -49,6 +49,9 @@ class GenRequest:
     cache_breakpoints: Sequence[int] = ()      # indices into `messages`; a boundary sits after that message
     cache_key: Optional[str] = None            # accepted client hint; not a session key, not a prefix identity
     cache_retention: Optional[str] = None      # accepted; residency follows the engine's retention classes
+    # soft length limit: from this many completion tokens on, the generation ends at the next syntax-safe boundary
+    # (frontend/stop_boundary.py) instead of running into max_tokens in the middle of a statement
+    soft_max_tokens: Optional[int] = None
 
 
 MAX_CACHE_WRITES = 4     # distinct shared-prefix write candidates one request may carry
@@ -80,6 +83,7 @@ class GenResult:
     thinking_budget: Optional[int] = None
     thinking_budget_applied: bool = False
     thinking_tokens: int = 0
+    stop_boundary: Optional[dict] = None  # out-of-band notice of a soft length limit: where the stop was taken / deferred
 
 
 class GenerationService:
@@ -254,6 +258,10 @@ class GenerationService:
             # opened one; this template leaves the frame to the model, so parsing starts in content mode
             parser = OutputParser(thinking=False, stop=req.stop)
             eos = set(self.eos_ids)
+            scanner = soft_stop = None
+            if req.soft_max_tokens is not None:
+                from ..frontend.stop_boundary import BoundaryScanner, pause_notice
+                scanner = BoundaryScanner()
             while True:
                 try:
                     ev: Event = handle.events.get(timeout=0.25)
@@ -264,9 +272,15 @@ class GenerationService:
                 if ev.kind == "token":
                     res.completion_tokens += 1
                     res.token_ids.append(int(ev.token))
-                    if ev.token in eos:
-                        continue
+                    if ev.token in eos or soft_stop is not None:
+                        continue               # after a soft stop: tokens the engine committed before it saw the cancel
                     piece = dec.feed(ev.token)
+                    if scanner is not None:
+                        where = scanner.observe_token(piece or "")
+                        if res.completion_tokens >= req.soft_max_tokens and where.safe:
+                            soft_stop = pause_notice(where, "soft_max_tokens")
+                            handle.cancel()
+                            res.finish_reason = "length"
                     d = parser.feed(piece) if piece else ParsedDelta()
                     if d.content or d.reasoning or d.tool_calls:
                         yield ("delta", d)
@@ -282,8 +296,12 @@ class GenerationService:
                         yield ("delta", tail)
                     if ev.kind == "error":
                         res.finish_reason, res.error = "error", ev.message
-                    elif res.finish_reason != "stop_sequence":
+                    elif res.finish_reason != "stop_sequence" and soft_stop is None:
                         res.finish_reason = ev.finish_reason or "stop"
+                    if scanner is not None:
+                        # taken at a boundary, or (the hard limit came first) how far from one the output ends
+                        res.stop_boundary = soft_stop or (pause_notice(scanner.decision(), "max_tokens")
+                                                          if res.finish_reason == "length" else None)
                     break
             res.content, res.reasoning, res.tool_calls = parser.content, parser.reasoning, list(parser.tool_calls)
             if res.tool_calls and res.finish_reason == "stop":
