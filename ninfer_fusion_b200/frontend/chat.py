@@ -11,7 +11,7 @@ from __future__ import annotations
 import hashlib
 import json
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, List, Optional, Sequence, Tuple
 
 IM_START, IM_END = "<|im_start|>", "<|im_end|>"
 TOOLS_HEADER = ("# Tools\n\nYou may call one or more functions to assist with the user query.\n\n"
@@ -41,41 +41,89 @@ def renderer_for(template_text: Optional[str], allow_unknown: bool = False) -> s
     return name
 
 
-def _text_of(content) -> str:
-    """OpenAI-style content: a string or a list of typed parts (text parts are concatenated)."""
+IMAGE_PLACEHOLDER = "<|vision_start|><|image_pad|><|vision_end|>"
+VIDEO_PLACEHOLDER = "<|vision_start|><|video_pad|><|vision_end|>"
+
+
+def _parts_of(content) -> List[Tuple[str, bool]]:
+    """OpenAI-style content (a string or a list of typed parts) as (text, is_literal) fragments: text parts are the
+    caller's literal text, media parts become the template's own placeholder."""
     if content is None:
-        return ""
+        return []
     if isinstance(content, str):
-        return content
-    out = []
+        return [(content, True)]
+    out: List[Tuple[str, bool]] = []
     for part in content:
         if isinstance(part, str):
-            out.append(part)
+            out.append((part, True))
         elif part.get("type") in ("text", "input_text", "output_text"):
-            out.append(part.get("text", ""))
+            out.append((part.get("text", ""), True))
         elif part.get("type") in ("image_url", "image", "input_image"):
-            out.append("<|vision_start|><|image_pad|><|vision_end|>")
+            out.append((IMAGE_PLACEHOLDER, False))
         elif part.get("type") in ("video_url", "video"):
-            out.append("<|vision_start|><|video_pad|><|vision_end|>")
-    return "".join(out)
+            out.append((VIDEO_PLACEHOLDER, False))
+    return out
 
 
-def render_chat(messages: Sequence[dict], tools: Optional[Sequence[dict]] = None, add_generation_prompt: bool = True,
-                enable_thinking: bool = True) -> str:
-    """messages: [{"role", "content", optional "reasoning_content", "tool_calls", "tool_call_id"}]."""
+def _text_of(content) -> str:
+    return "".join(t for t, _ in _parts_of(content))
+
+
+class _Fragments:
+    """The rendered prompt as it is built: text plus the character spans that are the caller's literal text.  What
+    the template writes may carry control tokens; what the caller wrote may not (the tokenizer reads the spans)."""
+
+    def __init__(self) -> None:
+        self.parts: List[str] = []
+        self.spans: List[Tuple[int, int]] = []
+        self.n = 0
+
+    def template(self, text: str) -> None:
+        if text:
+            self.parts.append(text)
+            self.n += len(text)
+
+    def literal(self, text: str) -> None:
+        if text:
+            if self.spans and self.spans[-1][1] == self.n:
+                self.spans[-1] = (self.spans[-1][0], self.n + len(text))
+            else:
+                self.spans.append((self.n, self.n + len(text)))
+            self.parts.append(text)
+            self.n += len(text)
+
+    def content(self, content) -> None:
+        for text, lit in _parts_of(content):
+            (self.literal if lit else self.template)(text)
+
+
+def render_chat_spans(messages: Sequence[dict], tools: Optional[Sequence[dict]] = None, add_generation_prompt: bool = True,
+                      enable_thinking: bool = True) -> Tuple[str, List[Tuple[int, int]]]:
+    """The rendered prompt and the character spans [begin, end) of it that came from the caller: message contents,
+    earlier reasoning, tool-call arguments, tool results and tool schemas.  Everything else is the template.
+    Reference: src/spec/frame_axis.h (the template / literal origin of every prompt position, kept as a column),
+    src/targets/qwen3_6/impl/frontend/chat_template.cpp (literal spans recorded while rendering)."""
     msgs = list(messages)
-    out: List[str] = []
-    system = ""
+    f = _Fragments()
+    system = None
     if msgs and msgs[0].get("role") in ("system", "developer"):
-        system = _text_of(msgs[0].get("content"))
+        system = msgs[0].get("content")
         msgs = msgs[1:]
+    has_system = bool(_text_of(system))
     if tools:
-        body = (system + "\n\n" if system else "") + TOOLS_HEADER
+        f.template(f"{IM_START}system\n")
+        if has_system:
+            f.content(system)
+            f.template("\n\n")
+        f.template(TOOLS_HEADER)
         for t in tools:
-            body += "\n" + json.dumps(t, ensure_ascii=False)
-        out.append(f"{IM_START}system\n{body}{TOOLS_FOOTER}{IM_END}\n")
-    elif system:
-        out.append(f"{IM_START}system\n{system}{IM_END}\n")
+            f.template("\n")
+            f.literal(json.dumps(t, ensure_ascii=False))
+        f.template(f"{TOOLS_FOOTER}{IM_END}\n")
+    elif has_system:
+        f.template(f"{IM_START}system\n")
+        f.content(system)
+        f.template(f"{IM_END}\n")
     # reasoning of earlier turns is dropped; only turns after the last real user query keep it
     last_query = -1
     for i, m in enumerate(msgs):
@@ -86,7 +134,9 @@ def render_chat(messages: Sequence[dict], tools: Optional[Sequence[dict]] = None
         m = msgs[i]
         role = m.get("role")
         if role in ("user", "system", "developer"):
-            out.append(f"{IM_START}{'system' if role != 'user' else 'user'}\n{_text_of(m.get('content'))}{IM_END}\n")
+            f.template(f"{IM_START}{'system' if role != 'user' else 'user'}\n")
+            f.content(m.get("content"))
+            f.template(f"{IM_END}\n")
         elif role == "assistant":
             content = _text_of(m.get("content"))
             reasoning = m.get("reasoning_content") or ""
@@ -94,10 +144,15 @@ def render_chat(messages: Sequence[dict], tools: Optional[Sequence[dict]] = None
                 head, _, content = content.partition("</think>")
                 reasoning = head.split("<think>")[-1].strip("\n")
                 content = content.lstrip("\n")
-            block = f"{IM_START}assistant\n"
+            f.template(f"{IM_START}assistant\n")
             if reasoning and i > last_query:
-                block += f"<think>\n{reasoning.strip()}\n</think>\n\n"
-            block += content
+                f.template("<think>\n")
+                f.literal(reasoning.strip())
+                f.template("\n</think>\n\n")
+            if content == _text_of(m.get("content")):
+                f.content(m.get("content"))        # untouched by the reasoning split: media parts stay the template's
+            else:
+                f.literal(content)
             for k, call in enumerate(m.get("tool_calls") or []):
                 fn = call.get("function", call)
                 args = fn.get("arguments", {})
@@ -107,25 +162,35 @@ def render_chat(messages: Sequence[dict], tools: Optional[Sequence[dict]] = None
                     except json.JSONDecodeError:
                         pass
                 if content or k > 0:
-                    block += "\n"
-                block += "<tool_call>\n" + json.dumps({"name": fn.get("name"), "arguments": args}, ensure_ascii=False) + "\n</tool_call>"
-            out.append(block + f"{IM_END}\n")
+                    f.template("\n")
+                f.template("<tool_call>\n")
+                f.literal(json.dumps({"name": fn.get("name"), "arguments": args}, ensure_ascii=False))
+                f.template("\n</tool_call>")
+            f.template(f"{IM_END}\n")
         elif role == "tool":
             # consecutive tool results share one user frame
-            block = f"{IM_START}user"
+            f.template(f"{IM_START}user")
             while i < len(msgs) and msgs[i].get("role") == "tool":
-                block += f"\n<tool_response>\n{_text_of(msgs[i].get('content'))}\n</tool_response>"
+                f.template("\n<tool_response>\n")
+                f.content(msgs[i].get("content"))
+                f.template("\n</tool_response>")
                 i += 1
-            out.append(block + f"{IM_END}\n")
+            f.template(f"{IM_END}\n")
             continue
         else:
             raise ValueError(f"unknown message role '{role}'")
         i += 1
     if add_generation_prompt:
-        out.append(f"{IM_START}assistant\n")
+        f.template(f"{IM_START}assistant\n")
         if not enable_thinking:
-            out.append("<think>\n\n</think>\n\n")
-    return "".join(out)
+            f.template("<think>\n\n</think>\n\n")
+    return "".join(f.parts), f.spans
+
+
+def render_chat(messages: Sequence[dict], tools: Optional[Sequence[dict]] = None, add_generation_prompt: bool = True,
+                enable_thinking: bool = True) -> str:
+    """messages: [{"role", "content", optional "reasoning_content", "tool_calls", "tool_call_id"}]."""
+    return render_chat_spans(messages, tools, add_generation_prompt, enable_thinking)[0]
 
 
 # ---------------------------------------------------------------------------------------------------------

@@ -64,6 +64,10 @@ def _load_native():
         return None
 
 
+# where a prompt token came from (see Tokenizer.encode_framed)
+ORIGIN_TEMPLATE, ORIGIN_LITERAL, ORIGIN_MIXED = 0, 1, 2
+
+
 class Tokenizer:
     def __init__(self, vocab: Dict[str, int], merges: Sequence[Tuple[str, str]], added_tokens: Sequence[dict] = (),
                  split_pattern: str = QWEN_SPLIT, use_native: bool = True, normalizer: str = ""):
@@ -241,6 +245,100 @@ class Tokenizer:
             for piece in self._split.findall(part):
                 ids.extend(self._bpe(piece))
         return ids
+
+    def encode_framed(self, text: str, literal_spans: Sequence[Tuple[int, int]]) -> Tuple[List[int], List[int]]:
+        """Token ids of a rendered prompt whose character spans `literal_spans` came from the caller, and per token
+        where it came from (ORIGIN_TEMPLATE / ORIGIN_LITERAL / ORIGIN_MIXED).  Inside a literal span a control
+        (special) token's spelling is ordinary text: only the template can produce control tokens, so a message
+        that spells an end-of-turn marker cannot close its own frame.  Added tokens that are not special (reasoning
+        and tool tags) are matched everywhere, as the stock tokenizer does.  For a prompt without such spellings the
+        ids are exactly those of `encode(text)`: ordinary text is still split and merged across span edges.
+        Reference: src/spec/frame_axis.h (the origin column), src/targets/qwen3_6/impl/frontend/tokenizer.cpp
+        (encode_with_frame_classes; literal spans never yield control tokens)."""
+        n = len(text)
+        spans = sorted((max(0, int(a)), min(n, int(b))) for a, b in literal_spans if int(b) > int(a))
+        # segments: alternating template / literal pieces that cover the text
+        segs: List[Tuple[int, int, bool]] = []
+        at = 0
+        for a, b in spans:
+            a = max(a, at)
+            if b <= a:
+                continue
+            if a > at:
+                segs.append((at, a, False))
+            segs.append((a, b, True))
+            at = b
+        if at < n:
+            segs.append((at, n, False))
+        # added-token matches, found inside one segment at a time (a control token never straddles an edge)
+        kept: List[Tuple[int, int, int]] = []
+        if self._added_re is not None:
+            for a, b, lit in segs:
+                for m in self._added_re.finditer(text, a, b):
+                    tid = self.added[m.group()]
+                    if lit and tid in self.special_ids:
+                        continue
+                    kept.append((m.start(), m.end(), tid))
+        ids: List[int] = []
+        origin: List[int] = []
+
+        def is_literal(pos: int) -> bool:
+            for a, b, lit in segs:
+                if a <= pos < b:
+                    return lit
+            return False
+
+        def ordinary(a: int, b: int) -> None:
+            if b <= a:
+                return
+            # the run's text, normalised piece by piece so that byte offsets can be mapped back to their origin
+            pieces: List[Tuple[str, bool]] = []
+            for sa, sb, lit in segs:
+                lo, hi = max(a, sa), min(b, sb)
+                if lo < hi:
+                    t = text[lo:hi]
+                    pieces.append((unicodedata.normalize(self.normalizer, t) if self.normalizer else t, lit))
+            joined = "".join(t for t, _ in pieces)
+            whole = unicodedata.normalize(self.normalizer, text[a:b]) if self.normalizer else text[a:b]
+            exact = joined == whole       # false when normalisation composes characters across an edge
+            edges: List[Tuple[int, int, bool]] = []
+            off = 0
+            for t, lit in pieces:
+                nb = len(t.encode("utf-8"))
+                edges.append((off, off + nb, lit))
+                off += nb
+            pos = 0
+            for piece in self._split.findall(whole):
+                for tid in self._bpe(piece):
+                    nb = len(self.id_to_bytes[tid])
+                    if not exact:
+                        cls = ORIGIN_MIXED
+                    else:
+                        kinds = {lit for ea, eb, lit in edges if ea < pos + nb and eb > pos}
+                        cls = ORIGIN_MIXED if len(kinds) != 1 else (ORIGIN_LITERAL if kinds.pop() else ORIGIN_TEMPLATE)
+                    ids.append(tid)
+                    origin.append(cls)
+                    pos += nb
+        at = 0
+        for a, b, tid in sorted(kept):
+            if a < at:
+                continue                  # overlapping match (cannot happen within one alternation; kept for safety)
+            ordinary(at, a)
+            ids.append(tid)
+            origin.append(ORIGIN_LITERAL if is_literal(a) else ORIGIN_TEMPLATE)
+            at = b
+        ordinary(at, n)
+        return ids, origin
+
+    def spells_control(self, text: str, literal_spans: Sequence[Tuple[int, int]]) -> bool:
+        """Does any literal span spell a control (special) token?"""
+        if self._added_re is None:
+            return False
+        for a, b in literal_spans:
+            for m in self._added_re.finditer(text, max(0, int(a)), min(len(text), int(b))):
+                if self.added[m.group()] in self.special_ids:
+                    return True
+        return False
 
     def decode_bytes(self, ids: Sequence[int], skip_special: bool = False) -> bytes:
         return b"".join(self.id_to_bytes[i] for i in ids

@@ -11,7 +11,7 @@ import uuid
 from dataclasses import dataclass, field
 from typing import Callable, Dict, Iterator, List, Optional, Sequence
 
-from ..frontend.chat import OutputParser, ParsedDelta, ToolCall, render_chat
+from ..frontend.chat import OutputParser, ParsedDelta, ToolCall, render_chat, render_chat_spans
 from ..frontend.tokenizer import StreamDecoder, Tokenizer
 from ..runtime.engine import Engine, Event, RequestError, RequestOptions, ResourceError
 from ..runtime.program import SamplingParams
@@ -120,9 +120,14 @@ class GenerationService:
         if req.prompt_ids is not None:
             return list(req.prompt_ids), None
         if req.messages is not None:
-            text = render_chat(req.messages, req.tools, add_generation_prompt=True, enable_thinking=req.enable_thinking)
+            text, spans = render_chat_spans(req.messages, req.tools, add_generation_prompt=True,
+                                            enable_thinking=req.enable_thinking)
             from ..frontend import media as M
             if M.collect_media(req.messages):
+                if self.tok.spells_control(text, spans):
+                    # the media path tokenises the expanded text as a whole: a message that spells a control token
+                    # (a pad, an end-of-turn marker) would be read as one
+                    raise RequestError("message text of a media prompt may not spell control tokens")
                 if not getattr(self.engine.program, "supports_media", False):
                     raise RequestError("this deployment has no vision tower: image and video parts are not supported")
                 if self.media is None:
@@ -136,11 +141,43 @@ class GenerationService:
                 except (ValueError, OSError) as e:
                     raise RequestError(f"invalid media: {e}")
                 return list(pm.ids), pm
+            # what the caller wrote is literal text: only the template's own fragments may become control tokens
+            return self.tok.encode_framed(text, spans)[0], None
         elif req.prompt is not None:
-            text = req.prompt
+            text = req.prompt     # a raw prompt is the caller's own template: control tokens are read as such
         else:
             raise RequestError("request has neither messages nor prompt")
         return self.tok.encode(text), None
+
+    def prompt_origin(self, req: GenRequest) -> Tuple[List[int], List[int]]:
+        """(token ids, origin per token) of a text-only chat request: 0 = the template wrote the token, 1 = it lies in
+        the caller's literal text, 2 = it straddles an edge."""
+        if req.messages is None:
+            raise RequestError("only chat requests have a template / literal origin")
+        text, spans = render_chat_spans(req.messages, req.tools, add_generation_prompt=True,
+                                        enable_thinking=req.enable_thinking)
+        return self.tok.encode_framed(text, spans)
+
+    def _encode_chat(self, messages, tools, add_generation_prompt: bool, enable_thinking: bool,
+                     until_first_frame_end: bool = False) -> List[int]:
+        """Token ids of a rendered history under the same rule as `prepare_full` (literal text yields no control
+        tokens); optionally only up to and including the first end-of-turn marker the TEMPLATE wrote."""
+        text, spans = render_chat_spans(messages, tools, add_generation_prompt=add_generation_prompt,
+                                        enable_thinking=enable_thinking)
+        if until_first_frame_end:
+            mark, at, end = "<|im_end|>\n", 0, -1
+            while True:
+                at = text.find(mark, at)
+                if at < 0:
+                    break
+                if not any(a < at + len(mark) and b > at for a, b in spans):
+                    end = at + len(mark)
+                    break
+                at += 1
+            if end < 0:
+                return []
+            text, spans = text[:end], [(a, min(b, end)) for a, b in spans if a < end]
+        return self.tok.encode_framed(text, spans)[0]
 
     def shared_prefix_tokens(self, req: GenRequest, ids: Sequence[int]) -> int:
         """Length in tokens of the prompt's leading system block (system / developer message with the tool
@@ -149,11 +186,7 @@ class GenerationService:
             return 0
         if req.messages[0].get("role") not in ("system", "developer") and not req.tools:
             return 0
-        text = render_chat(req.messages, req.tools, add_generation_prompt=True, enable_thinking=req.enable_thinking)
-        end = text.find("<|im_end|>\n")
-        if end < 0:
-            return 0
-        head = self.tok.encode(text[: end + len("<|im_end|>\n")])
+        head = self._encode_chat(req.messages, req.tools, True, req.enable_thinking, until_first_frame_end=True)
         n = len(head)
         if n < self.min_shared_prefix_tokens or n >= len(ids) or list(ids[:n]) != head:
             return 0
@@ -172,9 +205,7 @@ class GenerationService:
         explicit: List[int] = []
         if req.messages:
             for i in sorted({int(b) for b in req.cache_breakpoints if 0 <= int(b) < len(req.messages)}):
-                text = render_chat(req.messages[: i + 1], req.tools, add_generation_prompt=False,
-                                   enable_thinking=req.enable_thinking)
-                head = self.tok.encode(text)
+                head = self._encode_chat(req.messages[: i + 1], req.tools, False, req.enable_thinking)
                 n = len(head)
                 if self.min_shared_prefix_tokens <= n < len(ids) and list(ids[:n]) == head:
                     explicit.append(n)
@@ -194,8 +225,7 @@ class GenerationService:
         is not a clean token suffix."""
         if req.messages is None or not req.messages or not req.session:
             return 0
-        text = render_chat(req.messages, req.tools, add_generation_prompt=False, enable_thinking=req.enable_thinking)
-        head = self.tok.encode(text)
+        head = self._encode_chat(req.messages, req.tools, False, req.enable_thinking)
         n = len(head)
         if n == 0 or n >= len(ids) or list(ids[:n]) != head:
             return 0
