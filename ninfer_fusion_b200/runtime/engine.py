@@ -303,6 +303,11 @@ class Engine:
                     raise RequestError("this engine has no vision tower: media prompts are not supported")
                 if list(opts.media.ids) != list(prompt):
                     raise RequestError("the prepared media prompt does not match the request's token ids")
+            elif opts.media is not None and getattr(opts.media, "rows", None) is not None:
+                if not getattr(self.program, "supports_injection", False):
+                    raise RequestError("this engine's program does not accept injected embedding rows")
+                if list(opts.media.ids) != list(prompt):
+                    raise RequestError("the injected prompt does not match the request's token ids")
             if len(prompt) + opts.max_tokens > self._max_context:
                 self.stats.requests_rejected += 1
                 raise RequestError(f"prompt ({len(prompt)}) + max_tokens ({opts.max_tokens}) exceeds the "

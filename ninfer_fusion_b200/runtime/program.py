@@ -498,6 +498,7 @@ class ProgramBase:
         return True
 
     supports_media = False
+    supports_injection = False
 
     def open(self, prompt: Sequence[int], sampling: Optional[SamplingParams] = None,
              session: Optional[str] = None, media=None) -> Lane:
@@ -505,7 +506,15 @@ class ProgramBase:
             raise MemoryError("no free lane")
         if len(prompt) == 0:
             raise ValueError("empty prompt")
-        if media is not None and getattr(media, "items", None):
+        injected = media is not None and getattr(media, "rows", None) is not None and not getattr(media, "items", None)
+        if injected:
+            # rows of the embedding space at declared columns (runtime/inject.py): the multimodal mechanism without a tower
+            if not self.supports_injection:
+                raise ValueError("this program does not accept injected embedding rows")
+            if list(media.ids) != list(prompt):
+                raise ValueError("the injected prompt does not match the request's token ids")
+            session = None   # frontiers are keyed by token ids only; injected rows are not part of that identity
+        elif media is not None and getattr(media, "items", None):
             if not self.supports_media:
                 raise ValueError("this program has no vision tower: media prompts are not supported")
             if list(media.ids) != list(prompt):
@@ -518,6 +527,8 @@ class ProgramBase:
         lane = Lane(self._next_id, row, slot, list(prompt), 0, sampling or SamplingParams())
         if media is not None:
             lane.media, lane.rope_delta = media, int(media.rope_delta)
+            if injected:
+                lane.visual = media.rows
         lane.session = session
         self._next_id += 1
         self.lanes[lane.lane_id] = lane
@@ -561,6 +572,7 @@ class ProgramBase:
 
 class ReferenceProgram(ProgramBase):
     """CPU program on the fp32 oracle model (tiny configurations only)."""
+    supports_injection = True
 
     def __init__(self, cfg: ModelConfig, weights, max_lanes: int = 8, max_context: int = 4096, kv_format: str = "bf16"):
         super().__init__(cfg, max_lanes, max_context)
@@ -663,6 +675,7 @@ class ReferenceProgram(ProgramBase):
 class PackageProgram(ReferenceProgram):
     """CPU program of an attention-only package on its fp32 oracle (models/all_attention.py): the same lanes, sampling,
     frontiers and cold copies as the hybrid oracle program, another decoder underneath."""
+    supports_injection = False      # this decoder's forward takes token ids only
 
     def __init__(self, pkg, weights, max_lanes: int = 8, max_context: int = 4096):
         from ..models.all_attention import PackageReference, PackageSequence, package_model_config

@@ -52,6 +52,9 @@ class GenRequest:
     # soft length limit: from this many completion tokens on, the generation ends at the next syntax-safe boundary
     # (frontend/stop_boundary.py) instead of running into max_tokens in the middle of a statement
     soft_max_tokens: Optional[int] = None
+    # rows of the input-embedding space at declared columns of `prompt_ids` (runtime/inject.py): a payload object
+    # {"dtype", "scale", "columns", "data"}; only with pre-tokenised prompts, only on programs that accept it
+    inject: Optional[dict] = None
 
 
 MAX_CACHE_WRITES = 4     # distinct shared-prefix write candidates one request may carry
@@ -117,6 +120,14 @@ class GenerationService:
     def prepare_full(self, req: GenRequest):
         """(token ids, prepared media prompt or None).  Image / video parts of chat messages go through the media
         processor: placeholders expand to one pad token per visual token and positions become three-axis."""
+        if req.inject is not None:
+            if req.prompt_ids is None:
+                raise RequestError("injected rows address token columns: they need prompt_ids")
+            from ..runtime.inject import InjectRefused, parse_injection
+            try:
+                return list(req.prompt_ids), parse_injection(req.inject, req.prompt_ids, self.engine.program.cfg.hidden)
+            except InjectRefused as e:
+                raise RequestError(f"invalid injection: {e}")
         if req.prompt_ids is not None:
             return list(req.prompt_ids), None
         if req.messages is not None:
