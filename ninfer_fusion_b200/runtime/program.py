@@ -226,9 +226,14 @@ class ProgramBase:
         if c.kind == "shared" or c.session == SHARED_SESSION:
             return "shared_stable"
         n = len(c.tokens)
-        for o in self.checkpoints:
-            if o is not c and o.session == c.session and len(o.tokens) > n and o.tokens[:n] == c.tokens:
-                return "disposable"
+        # the latest replay frontier of a session is where "regenerate this response" restarts: the turn frontier
+        # that extends it by the generation opener does not make it disposable
+        regenerate_point = c.kind == "replay" and not any(
+            o.kind == "replay" and o.session == c.session and len(o.tokens) > n for o in self.checkpoints)
+        if not regenerate_point:
+            for o in self.checkpoints:
+                if o is not c and o.session == c.session and len(o.tokens) > n and o.tokens[:n] == c.tokens:
+                    return "disposable"
         if any(l.session == c.session for l in self.lanes.values()):
             return "live_session"
         return "recent_private"

@@ -495,3 +495,19 @@ def test_thinking_budget_closes_the_reasoning_frame_with_control_tokens():
         assert free.wait(timeout=120) == [OPEN, 5, 5, 5, 5, 5] and not free.thinking_budget_applied   # (CLOSE was fed before)
     finally:
         eng.shutdown()
+
+
+def test_the_latest_replay_frontier_of_a_session_is_not_disposable():
+    """'Regenerate this response' restarts from the replay frontier; the turn frontier that extends it by the
+    generation opener must not push it into the class that is given up first."""
+    from ninfer_fusion_b200.models.config import TINY_DENSE
+    from ninfer_fusion_b200.runtime.program import Checkpoint, ProgramBase
+    p = ProgramBase(TINY_DENSE, max_lanes=2, max_context=64)
+    old_replay = Checkpoint("s", "replay", [1, 2, 3], None)
+    replay = Checkpoint("s", "replay", [1, 2, 3, 4, 5, 6], None)
+    turn = Checkpoint("s", "turn", [1, 2, 3, 4, 5, 6, 7, 8], None)
+    anchor = Checkpoint("s", "anchor", [1, 2], None)
+    p.checkpoints = [old_replay, replay, turn, anchor]
+    assert p.retention_class(replay) == "recent_private"       # the regenerate point of the latest turn
+    assert p.retention_class(old_replay) == "disposable"       # an earlier turn's: a longer replay frontier exists
+    assert p.retention_class(anchor) == "disposable" and p.retention_class(turn) == "recent_private"

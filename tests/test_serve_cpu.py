@@ -256,6 +256,20 @@ def test_loadgen_against_the_server(server):
     assert bad["ok"] == 0 and bad["errors"] == 1
 
 
+def test_first_token_campaign_reports_cold_and_warm_runs(server):
+    from ninfer_fusion_b200.serve.loadgen import FILLER, sized_prompt, ttft_campaign
+    port, svc, _ = server
+    assert sized_prompt(300, "a", 100.0).count(FILLER) == 3 and sized_prompt(300, "a", 100.0).startswith("[a] ")
+    per = len(svc.tok.encode(FILLER))
+    recs = ttft_campaign(f"http://127.0.0.1:{port}/v1", "tiny-dense:test", [per, 2 * per], repeats=2, api_key="sekret")
+    assert [r["target_tokens"] for r in recs] == [per, 2 * per]
+    for r in recs:
+        assert r["ok"] == 2 and r["errors"] == 0 and r["ttft_cold_ms_p50"] > 0 and r["prefill_tok_s"] > 0
+        assert r["cold_cached_tokens_max"] == 0 and r["ttft_warm_ms"] > 0       # unique heads: nothing to reuse when cold
+        assert r["warm_cached_tokens"] > 0                                     # the repeat starts from the kept frontier
+    assert recs[1]["prompt_tokens"] > recs[0]["prompt_tokens"] >= per
+
+
 def test_service_finds_the_shared_system_prefix(server):
     _, svc, _ = server
     long_system = "You are a careful assistant. " * 12
