@@ -100,6 +100,8 @@ class RequestLog:
             "thinking_budget": {"budget": getattr(res, "thinking_budget", None),
                                 "applied": bool(getattr(res, "thinking_budget_applied", False)),
                                 "reasoning_tokens": int(getattr(res, "thinking_tokens", 0) or 0)},
+            # soft length limit: where the stop was taken or how far from a boundary the hard limit cut (None: not asked)
+            "stop_boundary": getattr(res, "stop_boundary", None),
         }
         if res.finish_reason == "error":
             fields["error"] = res.error

@@ -550,3 +550,19 @@ def test_rag_routes_answer_with_sources(server):
     assert st == 200 and "text/html" in ctype and b"/v1/rag/query" in page            # the page itself holds no data
     assert call(port, "DELETE", f"/v1/rag/documents/{doc['id']}")[0] == 200
     assert call(port, "DELETE", f"/v1/rag/documents/{doc['id']}")[0] == 404
+
+
+def test_soft_limit_over_http_carries_the_notice_and_logs_it(server):
+    port, _, log = server
+    body = {"model": "tiny-dense:test", "messages": [{"role": "user", "content": "hello"}], "max_tokens": 6, "soft_max_tokens": 6,
+            "temperature": 0.0}
+    status, _, data = call(port, "POST", "/v1/chat/completions", body)
+    out = json.loads(data)
+    assert status == 200 and out["choices"][0]["finish_reason"] in ("length", "stop")
+    if out["choices"][0]["finish_reason"] == "length":
+        assert out["stop_boundary"]["state"] in ("stopped", "deferred") and out["stop_boundary"]["emits_tokens"] is False
+    status, _, err = call(port, "POST", "/v1/chat/completions", {**body, "soft_max_tokens": 7})
+    assert status == 400 and b"soft_max_tokens" in err
+    with open(log, encoding="utf-8") as f:
+        done = [json.loads(l) for l in f if '"request_done"' in l]
+    assert "stop_boundary" in done[-1]
