@@ -665,6 +665,10 @@ def cmd_generate(args) -> int:
                      frequency_penalty=getattr(args, "frequency_penalty", None),
                      seed=args.seed, enable_thinking=not args.no_think, stop=args.stop or (),
                      thinking_budget=args.thinking_budget or None)
+    if getattr(args, "soft_max_tokens", 0):
+        if not 1 <= args.soft_max_tokens <= args.max_tokens:
+            raise SystemExit("--soft-max-tokens must lie in [1, --max-tokens]")
+        req.soft_max_tokens = int(args.soft_max_tokens)
     if args.prompt_ids:
         req.prompt_ids = [int(v) for v in args.prompt_ids.split(",")]
     elif args.messages_json:
@@ -700,6 +704,8 @@ def cmd_generate(args) -> int:
              "finish_reason": result.finish_reason, "ttft_ms": result.ttft_ms, "total_s": round(dt, 3),
              "decode_tok_s": round((result.completion_tokens - 1) / max(1e-9, dt - (result.ttft_ms or 0) / 1e3), 2),
              "weights_bytes": total_bytes(weights)}
+    if result.stop_boundary is not None:
+        stats["stop_boundary"] = result.stop_boundary
     if args.print_ids:
         stats["completion_ids"] = list(result.token_ids)
     if getattr(args, "print_prompt_ids", False):
@@ -1005,6 +1011,9 @@ def main(argv=None) -> int:
     g.add_argument("--capability-report", action="store_true",
                    help="print the architecture ladder, this GPU's capability bits and the (op, format) routes, and exit")
     g.add_argument("--no-think", "--no-thinking", dest="no_think", action="store_true")
+    g.add_argument("--soft-max-tokens", type=int, default=0,
+                   help="from this many completion tokens on, stop at the next syntax-safe boundary (statement end, block "
+                        "close, fence close, paragraph) instead of running into --max-tokens; 0 = off")
     g.add_argument("--thinking-budget", type=int, default=0,
                    help="reasoning tokens after which the reasoning frame is closed for the model (0: no cap)")
     g.add_argument("--show-thinking", action="store_true")
