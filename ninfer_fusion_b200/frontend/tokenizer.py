@@ -307,14 +307,26 @@ class Tokenizer:
                 nb = len(t.encode("utf-8"))
                 edges.append((off, off + nb, lit))
                 off += nb
-            pos = 0
+            if not exact or len(edges) == 1:
+                # one origin for the whole run (or no byte map to trust): no per-token bookkeeping
+                cls = ORIGIN_MIXED if not exact else (ORIGIN_LITERAL if edges[0][2] else ORIGIN_TEMPLATE)
+                first = len(ids)
+                for piece in self._split.findall(whole):
+                    ids.extend(self._bpe(piece))
+                origin.extend([cls] * (len(ids) - first))
+                return
+            pos, e, last = 0, 0, len(edges) - 1
+            nbytes = self.id_to_bytes
             for piece in self._split.findall(whole):
                 for tid in self._bpe(piece):
-                    nb = len(self.id_to_bytes[tid])
-                    if not exact:
-                        cls = ORIGIN_MIXED
+                    nb = len(nbytes[tid])
+                    while e < last and pos >= edges[e][1]:
+                        e += 1
+                    # inside one piece: that piece's origin; across an edge: mixed, unless both sides agree
+                    if pos + nb <= edges[e][1]:
+                        cls = ORIGIN_LITERAL if edges[e][2] else ORIGIN_TEMPLATE
                     else:
-                        kinds = {lit for ea, eb, lit in edges if ea < pos + nb and eb > pos}
+                        kinds = {lit for ea, eb, lit in edges[e:] if ea < pos + nb}
                         cls = ORIGIN_MIXED if len(kinds) != 1 else (ORIGIN_LITERAL if kinds.pop() else ORIGIN_TEMPLATE)
                     ids.append(tid)
                     origin.append(cls)
